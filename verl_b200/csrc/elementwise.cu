@@ -1,0 +1,390 @@
+// Memory-bound training ops for sm_100a: RMSNorm (+residual) fwd/bwd, RoPE, SwiGLU fwd/bwd, fused AdamW over
+// flat shards, squared-norm reduction. All use 16-byte vector accesses; HBM bandwidth is the roofline.
+// These replace the HF eager / Liger Triton ops the reference runs (verl/workers/engine/fsdp/transformer_impl.py:311-320)
+// and torch.optim.AdamW (verl/workers/config/optimizer.py).
+#include "common.cuh"
+
+namespace vb {
+
+struct alignas(16) bf16x8 { __nv_bfloat162 h[4]; };
+
+__device__ __forceinline__ void load8(const bf16* p, float* f) {
+  bf16x8 v = *reinterpret_cast<const bf16x8*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(v.h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(bf16* p, const float* f) {
+  bf16x8 v;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v.h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<bf16x8*>(p) = v;
+}
+
+// ------------------------------------------------------------------ RMSNorm forward
+// One warp per row. y = (x [+ res]) * rstd * w ; optionally writes the summed residual stream and rstd.
+template <int MAXV>
+__global__ void __launch_bounds__(128) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
+                                                          const bf16* __restrict__ w, bf16* __restrict__ y,
+                                                          bf16* __restrict__ res_out, float* __restrict__ rstd_out,
+                                                          int T, int H, float eps) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const int lane = threadIdx.x & 31;
+  const int nv = H / 8;  // 8-element vectors per row
+  const bf16* xr = x + (size_t)row * H;
+  float buf[MAXV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int v = i * 32 + lane;
+    if (v < nv) {
+      load8(xr + v * 8, buf[i]);
+      if (res != nullptr) {
+        float r[8];
+        load8(res + (size_t)row * H + v * 8, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) buf[i][j] += r[j];
+        if (res_out != nullptr) {
+          store8(res_out + (size_t)row * H + v * 8, buf[i]);
+          // the normalised value must be computed from the rounded residual stream to match a two-op reference
+          load8(res_out + (size_t)row * H + v * 8, buf[i]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += buf[i][j] * buf[i][j];
+    }
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / (float)H + eps);
+  if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int v = i * 32 + lane;
+    if (v < nv) {
+      float wv[8], o[8];
+      load8(w + v * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = buf[i][j] * rstd * wv[j];
+      store8(y + (size_t)row * H + v * 8, o);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm backward (dx) ; dw by column-sum kernel
+// dx = rstd * (dy*w) - x * rstd^3/H * sum(dy*w*x)  (+ dres_in if the residual stream also carries gradient)
+template <int MAXV>
+__global__ void __launch_bounds__(128) rmsnorm_bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                             const bf16* __restrict__ w, const float* __restrict__ rstd,
+                                                             const bf16* __restrict__ dres, bf16* __restrict__ dx, int T,
+                                                             int H) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const int lane = threadIdx.x & 31;
+  const int nv = H / 8;
+  float xb[MAXV][8], gb[MAXV][8];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int v = i * 32 + lane;
+    if (v < nv) {
+      float wv[8];
+      load8(x + (size_t)row * H + v * 8, xb[i]);
+      load8(dy + (size_t)row * H + v * 8, gb[i]);
+      load8(w + v * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        gb[i][j] *= wv[j];
+        dot += gb[i][j] * xb[i][j];
+      }
+    }
+  }
+  dot = warp_sum(dot);
+  const float r = rstd[row];
+  const float c = dot * r * r * r / (float)H;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int v = i * 32 + lane;
+    if (v < nv) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = gb[i][j] * r - xb[i][j] * c;
+      if (dres != nullptr) {
+        float d[8];
+        load8(dres + (size_t)row * H + v * 8, d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += d[j];
+      }
+      store8(dx + (size_t)row * H + v * 8, o);
+    }
+  }
+}
+
+// dw[c] += sum_t dy[t,c] * x[t,c] * rstd[t]; grid (H/256, row_chunks); each thread owns 2 columns... 8 columns.
+__global__ void __launch_bounds__(256) rmsnorm_bwd_dw_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                             const float* __restrict__ rstd, float* __restrict__ dw,
+                                                             int T, int H, int rows_per_block) {
+  // block = 32 column-vectors (256 columns) x 8 row lanes
+  const int cv = blockIdx.x * 32 + (threadIdx.x & 31);
+  const int rl = threadIdx.x >> 5;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(T, r0 + rows_per_block);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (cv * 8 < H) {
+    for (int r = r0 + rl; r < r1; r += 8) {
+      float a[8], b[8];
+      load8(dy + (size_t)r * H + cv * 8, a);
+      load8(x + (size_t)r * H + cv * 8, b);
+      const float s = rstd[r];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += a[j] * b[j] * s;
+    }
+  }
+  __shared__ float red[8][32][8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[rl][threadIdx.x & 31][j] = acc[j];
+  __syncthreads();
+  if (rl == 0 && cv * 8 < H) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) s += red[k][threadIdx.x & 31][j];
+      atomicAdd(dw + cv * 8 + j, s);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ RoPE (rotate-half convention), in place
+// x: [T, nheads, D] (row stride `ld` elements between tokens), cos/sin: [max_pos, D/2] fp32. sign=-1 gives the inverse
+// rotation, which is the backward of the forward rotation.
+__global__ void rope_kernel(bf16* __restrict__ x, const int* __restrict__ pos, const float* __restrict__ cs,
+                            const float* __restrict__ sn, int T, int nheads, int D, long ld, float sign) {
+  const int half = D / 2;
+  const int vec_per_head = half / 8;
+  const long total = (long)T * nheads * vec_per_head;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int v = i % vec_per_head;
+    const int h = (i / vec_per_head) % nheads;
+    const long t = i / ((long)vec_per_head * nheads);
+    const int p = pos[t];
+    bf16* base = x + t * ld + (long)h * D + v * 8;
+    float a[8], b[8], c[8], s[8];
+    load8(base, a);
+    load8(base + half, b);
+    const float* cp = cs + (long)p * half + v * 8;
+    const float* sp = sn + (long)p * half + v * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { c[j] = cp[j]; s[j] = sign * sp[j]; }
+    float o1[8], o2[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o1[j] = a[j] * c[j] - b[j] * s[j];
+      o2[j] = b[j] * c[j] + a[j] * s[j];
+    }
+    store8(base, o1);
+    store8(base + half, o2);
+  }
+}
+
+// ------------------------------------------------------------------ SwiGLU
+// gu: [T, 2I] with gate in columns [0,I) and up in [I,2I); out: [T, I]
+__global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long T, int I) {
+  const int vpr = I / 8;
+  const long total = T * vpr;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / vpr;
+    const int v = i % vpr;
+    float g[8], u[8], o[8];
+    load8(gu + t * 2 * I + v * 8, g);
+    load8(gu + t * 2 * I + I + v * 8, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    store8(out + t * I + v * 8, o);
+  }
+}
+__global__ void swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ dout, bf16* __restrict__ dgu,
+                                  long T, int I) {
+  const int vpr = I / 8;
+  const long total = T * vpr;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / vpr;
+    const int v = i % vpr;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gu + t * 2 * I + v * 8, g);
+    load8(gu + t * 2 * I + I + v * 8, u);
+    load8(dout + t * I + v * 8, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = 1.f / (1.f + __expf(-g[j]));
+      const float silu = g[j] * sg;
+      dg[j] = d[j] * u[j] * sg * (1.f + g[j] * (1.f - sg));
+      du[j] = d[j] * silu;
+    }
+    store8(dgu + t * 2 * I + v * 8, dg);
+    store8(dgu + t * 2 * I + I + v * 8, du);
+  }
+}
+
+// ------------------------------------------------------------------ fused AdamW on a flat shard
+// p32 (fp32 master), m, v (fp32), g (fp32 or bf16), p16 (bf16 working copy, optional).
+// scalars[0] = grad scale (clip coefficient etc.), scalars[1] = skip flag (non-zero => leave everything untouched).
+template <typename GT>
+__global__ void adamw_kernel(float* __restrict__ p32, float* __restrict__ m, float* __restrict__ v,
+                             const GT* __restrict__ g, bf16* __restrict__ p16, long n, float lr, float b1, float b2,
+                             float eps, float wd, float bc1, float bc2, const float* __restrict__ scalars) {
+  const float gscale = scalars ? scalars[0] : 1.f;
+  if (scalars && scalars[1] != 0.f) return;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    float gi;
+    if constexpr (sizeof(GT) == 2) gi = __bfloat162float(g[i]); else gi = g[i];
+    gi *= gscale;
+    float p = p32[i];
+    float mi = b1 * m[i] + (1.f - b1) * gi;
+    float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    p = p * (1.f - lr * wd);
+    const float denom = sqrtf(vi) / bc2 + eps;   // bc2 = sqrt(1 - b2^t)
+    p -= (lr / bc1) * (mi / denom);               // bc1 = 1 - b1^t
+    p32[i] = p;
+    m[i] = mi;
+    v[i] = vi;
+    if (p16) p16[i] = __float2bfloat16(p);
+  }
+}
+
+// ------------------------------------------------------------------ sum of squares into out[0] (fp32 atomics)
+template <typename GT>
+__global__ void sqnorm_kernel(const GT* __restrict__ g, long n, float* __restrict__ out) {
+  float acc = 0.f;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    float x;
+    if constexpr (sizeof(GT) == 2) x = __bfloat162float(g[i]); else x = g[i];
+    acc += x * x;
+  }
+  acc = warp_sum(acc);
+  __shared__ float part[32];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float s = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.f;
+    s = warp_sum(s);
+    if (threadIdx.x == 0) atomicAdd(out, s);
+  }
+}
+
+// scalars[0] = min(1, max_norm / (sqrt(sumsq) + 1e-6)), scalars[1] = non-finite flag, scalars[2] = norm
+__global__ void clip_coef_kernel(const float* __restrict__ sumsq, float max_norm, float* __restrict__ scalars) {
+  const float norm = sqrtf(sumsq[0]);
+  const bool bad = !isfinite(norm);
+  float c = max_norm > 0.f ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
+  scalars[0] = bad ? 0.f : c;
+  scalars[1] = bad ? 1.f : 0.f;
+  scalars[2] = norm;
+}
+
+static inline int grid_for(long n, int block) {
+  long g = (n + block - 1) / block;
+  long cap = 148L * 16;
+  return (int)(g < cap ? (g > 0 ? g : 1) : cap);
+}
+
+}  // namespace vb
+
+using namespace vb;
+
+template <int MAXV>
+static void launch_rms_fwd(const void* x, const void* res, const void* w, void* y, void* res_out, float* rstd, int T,
+                           int H, float eps, cudaStream_t st) {
+  rmsnorm_fwd_kernel<MAXV><<<(T + 3) / 4, 128, 0, st>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y,
+                                                        (bf16*)res_out, rstd, T, H, eps);
+}
+template <int MAXV>
+static void launch_rms_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                           int T, int H, cudaStream_t st) {
+  rmsnorm_bwd_dx_kernel<MAXV><<<(T + 3) / 4, 128, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
+                                                           (const bf16*)dres, (bf16*)dx, T, H);
+}
+
+// rows are held in registers: MAXV vectors of 8 per lane; pick the smallest instantiation that covers H
+#define VB_DISPATCH_MAXV(H, FN, ...)                     \
+  do {                                                   \
+    int nv_ = ((H) / 8 + 31) / 32;                       \
+    if (nv_ <= 2) FN<2>(__VA_ARGS__);                    \
+    else if (nv_ <= 8) FN<8>(__VA_ARGS__);               \
+    else if (nv_ <= 14) FN<14>(__VA_ARGS__);             \
+    else if (nv_ <= 16) FN<16>(__VA_ARGS__);             \
+    else if (nv_ <= 32) FN<32>(__VA_ARGS__);             \
+    else return -1;                                      \
+  } while (0)
+
+extern "C" int vb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* res_out, float* rstd, int T,
+                              int H, float eps, cudaStream_t st) {
+  if (H % 8) return -2;
+  if (T == 0) return 0;
+  VB_DISPATCH_MAXV(H, launch_rms_fwd, x, res, w, y, res_out, rstd, T, H, eps, st);
+  return 0;
+}
+
+extern "C" int vb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                              float* dw, int T, int H, cudaStream_t st) {
+  if (H % 8) return -2;
+  if (T == 0) return 0;
+  VB_DISPATCH_MAXV(H, launch_rms_bwd, dy, x, w, rstd, dres, dx, T, H, st);
+  if (dw != nullptr) {
+    int rows_per_block = 512;
+    dim3 grid((H / 8 + 31) / 32, (T + rows_per_block - 1) / rows_per_block);
+    rmsnorm_bwd_dw_kernel<<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, rstd, dw, T, H, rows_per_block);
+  }
+  return 0;
+}
+
+extern "C" int vb_rope(void* x, const int* pos, const float* cs, const float* sn, int T, int nheads, int D, long ld,
+                       float sign, cudaStream_t st) {
+  if (D % 16) return -2;
+  long total = (long)T * nheads * (D / 16);
+  if (total == 0) return 0;
+  rope_kernel<<<grid_for(total, 256), 256, 0, st>>>((bf16*)x, pos, cs, sn, T, nheads, D, ld, sign);
+  return 0;
+}
+
+extern "C" int vb_swiglu_fwd(const void* gu, void* out, long T, int I, cudaStream_t st) {
+  if (I % 8) return -2;
+  if (T == 0) return 0;
+  swiglu_fwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, st>>>((const bf16*)gu, (bf16*)out, T, I);
+  return 0;
+}
+extern "C" int vb_swiglu_bwd(const void* gu, const void* dout, void* dgu, long T, int I, cudaStream_t st) {
+  if (I % 8) return -2;
+  if (T == 0) return 0;
+  swiglu_bwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, st>>>((const bf16*)gu, (const bf16*)dout, (bf16*)dgu, T, I);
+  return 0;
+}
+
+extern "C" int vb_adamw(float* p32, float* m, float* v, const void* g, int g_is_bf16, void* p16, long n, float lr,
+                        float b1, float b2, float eps, float wd, int step, const float* scalars, cudaStream_t st) {
+  if (n == 0) return 0;
+  const float bc1 = 1.f - powf(b1, (float)step);
+  const float bc2 = sqrtf(1.f - powf(b2, (float)step));
+  int grid = grid_for(n, 256);
+  if (g_is_bf16)
+    adamw_kernel<bf16><<<grid, 256, 0, st>>>(p32, m, v, (const bf16*)g, (bf16*)p16, n, lr, b1, b2, eps, wd, bc1, bc2, scalars);
+  else
+    adamw_kernel<float><<<grid, 256, 0, st>>>(p32, m, v, (const float*)g, (bf16*)p16, n, lr, b1, b2, eps, wd, bc1, bc2, scalars);
+  return 0;
+}
+
+extern "C" int vb_sqnorm(const void* g, int is_bf16, long n, float* out, cudaStream_t st) {
+  if (n == 0) return 0;
+  int grid = grid_for(n, 512);
+  if (is_bf16) sqnorm_kernel<bf16><<<grid, 512, 0, st>>>((const bf16*)g, n, out);
+  else sqnorm_kernel<float><<<grid, 512, 0, st>>>((const float*)g, n, out);
+  return 0;
+}
+
+extern "C" int vb_clip_coef(const float* sumsq, float max_norm, float* scalars, cudaStream_t st) {
+  clip_coef_kernel<<<1, 1, 0, st>>>(sumsq, max_norm, scalars);
+  return 0;
+}

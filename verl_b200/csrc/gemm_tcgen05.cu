@@ -1,0 +1,335 @@
+// Persistent bf16 GEMM for sm_100a: TMA-fed shared-memory ring, tcgen05.mma with fp32 accumulators in TMEM
+// (double buffered so the epilogue of tile i overlaps the main loop of tile i+1), tcgen05.ld epilogue.
+//
+//   C[M,N] (+)= op(A) * op(B) (+ bias)
+//
+// Both operands may be K-major ("row = M or N index, K contiguous": x[T,in], W[out,in]) or MN-major
+// ("row = K index, M or N contiguous": dy[T,out] as A of a weight gradient, W[out,in] as B of an input
+// gradient), so forward, input-gradient and weight-gradient GEMMs of a linear layer run without a transpose
+// copy. Replaces the cuBLAS calls a torch nn.Linear makes under autocast in the reference
+// (verl/workers/engine/fsdp/transformer_impl.py:1581-1590).
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2-5 = epilogue
+// (warp w reads TMEM lanes 32*(w%4)..+31).
+#include "common.cuh"
+#include "tma_host.h"
+
+namespace vb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;       // 64 bf16 = 128 B = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int A_TILE_BYTES = BM * BK * 2;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int B_TILE_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+  static constexpr int MAX_STAGES = (220 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
+};
+
+enum : int { GEMM_OUT_F32 = 1, GEMM_ACCUM = 2 };
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
+                 const bf16* __restrict__ bias, int M, int N, int K, int ldc, int flags, int* err_word) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (M + BM - 1) / BM;
+  const int num_n = (N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc<Cfg::TMEM_COLS>(tmem_slot);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Tile order: groups of GROUP_M row-blocks sweep N together so a B column block stays in L2.
+  constexpr int GROUP_M = 8;
+  auto tile_coords = [&](int t, int& mb, int& nb) {
+    int per_group = GROUP_M * num_n;
+    int g = t / per_group;
+    int first_m = g * GROUP_M;
+    int gsz = min(num_m - first_m, GROUP_M);
+    int r = t - g * per_group;
+    mb = first_m + (r % gsz);
+    nb = r / gsz;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mb, nb;
+        tile_coords(t, mb, nb);
+        const int m0 = mb * BM, n0 = nb * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_EMPTY)) { ok = false; break; }
+          uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + A_TILE_BYTES;
+          mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sa, &tmA, k0, m0, &full_bar[s]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * (BK * 128), &tmA, m0 + 64 * i, k0, &full_bar[s]);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tmB, k0, n0, &full_bar[s]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * (BK * 128), &tmB, n0 + 64 * i, k0, &full_bar[s]);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1, A_MN, B_MN);
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const uint32_t acc = it & 1;
+        const uint32_t acc_ph = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + A_TILE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: 8-row groups are 1024 B apart, a K step of 16 elements is 32 B inside the swizzle row.
+            // MN-major: 64-element column atoms are BK*128 B apart (LBO), 8-row K groups 1024 B apart (SBO);
+            //           a K step of 16 rows is 2048 B.
+            uint64_t ad = A_MN ? make_sdesc_sw128(sa + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sa + k * 32, 16, 1024);
+            uint64_t bd = B_MN ? make_sdesc_sw128(sb + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sb + k * 32, 16, 1024);
+            umma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty_bar[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (128 threads)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const bool out_f32 = flags & GEMM_OUT_F32;
+    const bool accum = flags & GEMM_ACCUM;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      int mb, nb;
+      tile_coords(t, mb, nb);
+      const uint32_t acc = it & 1;
+      const uint32_t acc_ph = (it >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, err_word, VB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int row = mb * BM + q * 32 + lane;
+      const int n0 = nb * BN;
+      const uint32_t taddr = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < N) f[j] += __bfloat162float(bias[col0 + j]);
+          }
+          const bool full = (col0 + 32 <= N);
+          if (out_f32) {
+            float* crow = reinterpret_cast<float*>(Cv) + (size_t)row * ldc + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                if (accum) {
+                  float4 p = *reinterpret_cast<float4*>(crow + j);
+                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                }
+                *reinterpret_cast<float4*>(crow + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) crow[j] = accum ? crow[j] + f[j] : f[j];
+            }
+          } else {
+            bf16* crow = reinterpret_cast<bf16*>(Cv) + (size_t)row * ldc + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (accum) {
+                  uint4 p = *reinterpret_cast<uint4*>(crow + j);
+                  const __nv_bfloat162* ph2 = reinterpret_cast<const __nv_bfloat162*>(&p);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    float2 pf = __bfloat1622float2(ph2[e]);
+                    f[j + 2 * e] += pf.x;
+                    f[j + 2 * e + 1] += pf.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(f[j], f[j + 1]);
+                o.y = pack_bf16x2(f[j + 2], f[j + 3]);
+                o.z = pack_bf16x2(f[j + 4], f[j + 5]);
+                o.w = pack_bf16x2(f[j + 6], f[j + 7]);
+                *reinterpret_cast<uint4*>(crow + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) {
+                  float o = accum ? __bfloat162float(crow[j]) + f[j] : f[j];
+                  crow[j] = __float2bfloat16(o);
+                }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      // A wait was abandoned: give copies and MMAs still in flight time to land before TMEM and the
+      // shared-memory ring go away with the CTA.
+      uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 2000000ull) { __nanosleep(1000); }
+    }
+    tc_fence_after();
+    tmem_dealloc<Cfg::TMEM_COLS>(tmem_base);
+  }
+}
+
+// ---------------------------------------------------------------- host launcher
+static int g_num_sms = 0;
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb,
+                       int ldc, int flags, int* err_word, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN) rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK);
+  else       rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, BK, 64);
+  if (rc) return rc;
+  if (!B_MN) rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BN, BK);
+  else       rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
+  if (rc) return rc;
+  static bool attr_set = false;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  if (g_num_sms == 0) {
+    int dev;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags,
+                                                err_word);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace vb
+
+// C[M,N] (+)= op(A) op(B) (+ bias). a_mn / b_mn: 0 = K contiguous ([M,K] / [N,K] row-major), 1 = M/N contiguous
+// ([K,M] / [K,N] row-major). lda/ldb/ldc are row strides in elements. Requirements: A, B 16-byte aligned,
+// lda/ldb multiples of 8. `bn` = 0 picks the N tile from the problem shape.
+extern "C" int vb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
+                            int ldb, int ldc, int a_mn, int b_mn, int out_f32, int accumulate, int bn, int* err_word,
+                            cudaStream_t stream) {
+  using namespace vb;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return -3;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -4;
+  int flags = (out_f32 ? GEMM_OUT_F32 : 0) | (accumulate ? GEMM_ACCUM : 0);
+  if (bn == 0) {
+    // Prefer the widest tile that still yields at least ~one wave of CTAs; narrow tiles keep small-M
+    // (decode) problems spread over all SMs so the weight stream can saturate HBM.
+    int num_m = (M + BM - 1) / BM;
+    bn = 256;
+    while (bn > 32 && (long)num_m * ((N + bn - 1) / bn) < 148) bn >>= 1;
+    if (b_mn && bn < 64) bn = 64;
+  }
+#define VB_LAUNCH(BN_, AM_, BM_) \
+  return launch_gemm<BN_, AM_, BM_>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream)
+#define VB_DISPATCH_BN(AM_, BM_)                   \
+  switch (bn) {                                    \
+    case 256: VB_LAUNCH(256, AM_, BM_);            \
+    case 128: VB_LAUNCH(128, AM_, BM_);            \
+    case 64: VB_LAUNCH(64, AM_, BM_);              \
+    default: break;                                \
+  }
+  if (!a_mn && !b_mn) {
+    if (bn == 32) VB_LAUNCH(32, false, false);
+    VB_DISPATCH_BN(false, false)
+  } else if (!a_mn && b_mn) {
+    VB_DISPATCH_BN(false, true)
+  } else if (a_mn && b_mn) {
+    VB_DISPATCH_BN(true, true)
+  } else {
+    VB_DISPATCH_BN(true, false)
+  }
+  return -5;
+}
