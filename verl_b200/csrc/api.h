@@ -24,6 +24,25 @@ int vb_adamw(float* p32, float* m, float* v, const void* g, int g_is_bf16, void*
 int vb_sqnorm(const void* g, int is_bf16, long n, float* out, cudaStream_t st);
 int vb_clip_coef(const float* sumsq, float max_norm, float* scalars, cudaStream_t st);
 
+long vb_lmhead_scratch_floats(int M, int V);
+int vb_lmhead_logprob_fwd(const void* h, const void* W, const long* labels, int M, int V, int K, int ldh, int ldw,
+                          float inv_temp, float* scratch, float* logp, float* ent, float* lse, int* err_word,
+                          cudaStream_t stream);
+int vb_lmhead_dlogits(const void* h, const void* W, const long* labels, int M, int Vc, int K, int ldh, int ldw, float inv_temp,
+                      int col_offset, const float* lse, const float* ent, const float* g_lp, const float* g_ent, void* dlogits,
+                      int ldd, int* err_word, cudaStream_t stream);
+
+int vb_attn_varlen_fwd(const void* q, const void* k, const void* v, long ld, int T, int n_q_heads, int n_kv_heads,
+                       const void* tiles, int n_tiles, void* out, long ld_out, float* lse, long lse_stride, float scale,
+                       int* err_word, cudaStream_t st);
+int vb_attn_paged_decode(const void* q, long ld_q, const void* cache, long num_blocks, const int* block_table, int max_blocks,
+                         const int* kv_lens, int B, int n_q_heads, int n_kv_heads, void* out, long ld_out, float scale,
+                         int num_splits, int max_kv_len, float* part_o, float* part_ml, int* err_word, cudaStream_t st);
+int vb_attn_varlen_bwd(const void* q, const void* k, const void* v, long ld, const void* dO, const void* O, long ld_o, int T,
+                       int n_q_heads, int n_kv_heads, const void* tiles, int n_tiles, const float* lse, float* delta,
+                       long stat_stride, float* dq_acc, void* dq, void* dk, void* dv, long ld_d, float scale, int* err_word,
+                       cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

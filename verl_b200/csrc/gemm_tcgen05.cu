@@ -32,11 +32,29 @@ struct GemmCfg {
 };
 
 enum : int { GEMM_OUT_F32 = 1, GEMM_ACCUM = 2 };
+enum : int { EPI_STORE = 0, EPI_LOGPROB = 1, EPI_DLOGITS = 2 };
 
-template <int BN, bool A_MN, bool B_MN>
+// Extra epilogue inputs of the fused lm_head variants (rows = tokens, columns = vocabulary entries).
+struct LmHeadEpi {
+  float inv_temp;
+  const long* labels;     // [M]
+  int col_offset;         // global vocabulary index of column 0 of this launch (vocab-chunked backward)
+  // EPI_LOGPROB: per (column tile, row) partial softmax statistics of x = logit * inv_temp
+  float* part_max;        // [num_n_tiles, M]
+  float* part_sum;        // sum exp(x - max)
+  float* part_sumx;       // sum x * exp(x - max)
+  float* label_logit;     // [M] x at the label column (written by the one tile that contains it)
+  // EPI_DLOGITS: dL/dlogit = inv_temp * ( g_lp * (1[label] - p) - g_ent * p * (x - lse + H) ),  p = exp(x - lse)
+  const float* lse;       // [M]
+  const float* ent;       // [M]
+  const float* g_lp;      // [M]
+  const float* g_ent;     // [M] or null
+};
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
-                 const bf16* __restrict__ bias, int M, int N, int K, int ldc, int flags, int* err_word) {
+                 const bf16* __restrict__ bias, int M, int N, int K, int ldc, int flags, int* err_word, const LmHeadEpi epi) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -173,6 +191,92 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int row = mb * BM + q * 32 + lane;
       const int n0 = nb * BN;
       const uint32_t taddr = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
+      if constexpr (EPI == EPI_LOGPROB) {
+        // online softmax statistics of this row over the BN columns of the tile; one thread owns one row
+        float m_run = -INFINITY, s_run = 0.f, sx_run = 0.f;
+        const long label = (row < M) ? epi.labels[row] - epi.col_offset : -1;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, v);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          float x[32];
+          float cmax = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            x[j] = (col0 + j < N) ? __uint_as_float(v[j]) * epi.inv_temp : -INFINITY;
+            cmax = fmaxf(cmax, x[j]);
+          }
+          if (cmax > -INFINITY) {
+            const float m_new = fmaxf(m_run, cmax);
+            const float a = __expf(m_run - m_new);
+            float cs = 0.f, cx = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float e = __expf(x[j] - m_new);
+              cs += e;
+              cx += (col0 + j < N) ? e * x[j] : 0.f;
+            }
+            s_run = s_run * a + cs;
+            sx_run = sx_run * a + cx;
+            m_run = m_new;
+          }
+          if (label >= col0 && label < col0 + 32 && row < M) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (label == col0 + j) epi.label_logit[row] = x[j];
+          }
+        }
+        if (row < M) {
+          const long pi = (long)nb * M + row;
+          epi.part_max[pi] = m_run;
+          epi.part_sum[pi] = s_run;
+          epi.part_sumx[pi] = sx_run;
+        }
+      } else if constexpr (EPI == EPI_DLOGITS) {
+        float lse = 0.f, hh = 0.f, glp = 0.f, gen = 0.f;
+        long label = -1;
+        if (row < M) {
+          lse = epi.lse[row];
+          glp = epi.g_lp[row];
+          if (epi.g_ent != nullptr) { gen = epi.g_ent[row]; hh = epi.ent[row]; }
+          label = epi.labels[row] - epi.col_offset;
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, v);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (row < M && col0 < N) {
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float x = __uint_as_float(v[j]) * epi.inv_temp;
+              const float pr = __expf(x - lse);
+              float g = -glp * pr - gen * pr * (x - lse + hh);
+              if (label == col0 + j) g += glp;
+              f[j] = g * epi.inv_temp;
+            }
+            bf16* crow = reinterpret_cast<bf16*>(Cv) + (size_t)row * ldc + col0;
+            if (col0 + 32 <= N && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 o;
+                o.x = pack_bf16x2(f[j], f[j + 1]);
+                o.y = pack_bf16x2(f[j + 2], f[j + 3]);
+                o.z = pack_bf16x2(f[j + 4], f[j + 5]);
+                o.w = pack_bf16x2(f[j + 6], f[j + 7]);
+                *reinterpret_cast<uint4*>(crow + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) crow[j] = __float2bfloat16(f[j]);
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
@@ -237,6 +341,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
+      }
       tc_fence_before();
       mbar_arrive(&tempty_bar[acc]);
     }
@@ -260,9 +365,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ---------------------------------------------------------------- host launcher
 static int g_num_sms = 0;
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int EPI = EPI_STORE>
 static int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb,
-                       int ldc, int flags, int* err_word, cudaStream_t stream) {
+                       int ldc, int flags, int* err_word, cudaStream_t stream, const LmHeadEpi& epi = LmHeadEpi{}) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmA, tmB;
   int rc;
@@ -273,7 +378,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   else       rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
   if (rc) return rc;
   static bool attr_set = false;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI>;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return -10;
@@ -287,7 +392,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < g_num_sms ? tiles : g_num_sms;
   kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags,
-                                                err_word);
+                                                err_word, epi);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -332,4 +437,80 @@ extern "C" int vb_gemm_bf16(const void* A, const void* B, void* C, const void* b
     VB_DISPATCH_BN(true, false)
   }
   return -5;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Fused lm_head -> log-prob / entropy. Forward never writes logits: each 128x256 tile of h W^T leaves the SM as three
+// partial softmax statistics per row; a second tiny kernel merges the partials.
+// Replaces the reference's Triton kernels (verl/utils/kernel/kernels.py:186-563) and the torch-chunked
+// FusedLinearForPPO (verl/utils/experimental/torch_functional.py:96-217).
+namespace vb {
+
+constexpr int LM_BN = 256;
+
+__global__ void lmhead_merge_kernel(const float* __restrict__ pmax, const float* __restrict__ psum, const float* __restrict__ psumx,
+                                    const float* __restrict__ label_logit, int M, int num_n, float* __restrict__ logp,
+                                    float* __restrict__ ent, float* __restrict__ lse_out) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  float m = -INFINITY;
+  for (int nb = 0; nb < num_n; ++nb) m = fmaxf(m, pmax[(long)nb * M + row]);
+  float s = 0.f, sx = 0.f;
+  for (int nb = 0; nb < num_n; ++nb) {
+    const long i = (long)nb * M + row;
+    const float pm = pmax[i];
+    const float w = (pm == -INFINITY) ? 0.f : __expf(pm - m);
+    s += w * psum[i];
+    sx += w * psumx[i];
+  }
+  const float lse = m + logf(s);
+  logp[row] = label_logit[row] - lse;
+  if (ent != nullptr) ent[row] = lse - sx / s;
+  if (lse_out != nullptr) lse_out[row] = lse;
+}
+
+}  // namespace vb
+
+extern "C" long vb_lmhead_scratch_floats(int M, int V) {
+  const long num_n = (V + vb::LM_BN - 1) / vb::LM_BN;
+  return 3 * num_n * (long)M + M;
+}
+
+// h: [M, K] bf16 (row stride ldh), W: [V, K] bf16 (row stride ldw), labels: int64 [M].
+// scratch: vb_lmhead_scratch_floats(M, V) floats. Outputs fp32 [M]: logp, ent (nullable), lse (nullable).
+extern "C" int vb_lmhead_logprob_fwd(const void* h, const void* W, const long* labels, int M, int V, int K, int ldh, int ldw,
+                                     float inv_temp, float* scratch, float* logp, float* ent, float* lse, int* err_word,
+                                     cudaStream_t stream) {
+  using namespace vb;
+  if (M <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) || (ldh & 7) || (ldw & 7)) return -4;
+  const long num_n = (V + LM_BN - 1) / LM_BN;
+  LmHeadEpi epi = {};
+  epi.inv_temp = inv_temp;
+  epi.labels = labels;
+  epi.col_offset = 0;
+  epi.part_max = scratch;
+  epi.part_sum = scratch + num_n * M;
+  epi.part_sumx = scratch + 2 * num_n * M;
+  epi.label_logit = scratch + 3 * num_n * M;
+  int rc = launch_gemm<LM_BN, false, false, EPI_LOGPROB>(h, W, nullptr, nullptr, M, V, K, ldh, ldw, 0, 0, err_word, stream, epi);
+  if (rc) return rc;
+  lmhead_merge_kernel<<<(M + 127) / 128, 128, 0, stream>>>(epi.part_max, epi.part_sum, epi.part_sumx, epi.label_logit, M,
+                                                           (int)num_n, logp, ent, lse);
+  return cudaGetLastError() == cudaSuccess ? 0 : -12;
+}
+
+// dlogits[M, Vc] (bf16, row stride ldd) for vocabulary columns [col_offset, col_offset + Vc): W points at row col_offset.
+extern "C" int vb_lmhead_dlogits(const void* h, const void* W, const long* labels, int M, int Vc, int K, int ldh, int ldw,
+                                 float inv_temp, int col_offset, const float* lse, const float* ent, const float* g_lp,
+                                 const float* g_ent, void* dlogits, int ldd, int* err_word, cudaStream_t stream) {
+  using namespace vb;
+  if (M <= 0 || Vc <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) || (ldh & 7) || (ldw & 7)) return -4;
+  LmHeadEpi epi = {};
+  epi.inv_temp = inv_temp;
+  epi.labels = labels;
+  epi.col_offset = col_offset;
+  epi.lse = lse; epi.ent = ent; epi.g_lp = g_lp; epi.g_ent = g_ent;
+  return launch_gemm<LM_BN, false, false, EPI_DLOGITS>(h, W, dlogits, nullptr, M, Vc, K, ldh, ldw, ldd, 0, err_word, stream, epi);
 }

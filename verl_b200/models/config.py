@@ -1,0 +1,178 @@
+"""Architecture description of the decoder-only model families this framework trains and serves.
+
+A ``ModelConfig`` can be built from a HuggingFace ``config.json`` (llama, qwen2, qwen3, qwen3_moe, mistral) so that
+checkpoints and configs of the reference ecosystem load unchanged, and converts back with :meth:`to_hf_dict`.
+The reference gets the same information from ``transformers.AutoConfig`` (``verl/utils/model.py:84-134``).
+"""
+
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+from typing import Optional
+
+__all__ = ["ModelConfig", "PRESETS"]
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "qwen2"
+    vocab_size: int = 152064
+    hidden_size: int = 3584
+    intermediate_size: int = 18944
+    num_hidden_layers: int = 28
+    num_attention_heads: int = 28
+    num_key_value_heads: int = 4
+    head_dim: Optional[int] = None
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    max_position_embeddings: int = 32768
+    tie_word_embeddings: bool = False
+    attention_bias: bool = True          # qwen2: bias on q/k/v projections
+    qk_norm: bool = False                # qwen3: RMSNorm on q and k heads
+    initializer_range: float = 0.02
+    # mixture of experts (qwen3_moe)
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    router_aux_loss_coef: float = 0.0
+    # heads
+    value_head: bool = False             # scalar value head instead of lm_head (critic / reward model)
+    pad_token_id: Optional[int] = 0
+    eos_token_id: Optional[int] = None
+    bos_token_id: Optional[int] = None
+    torch_dtype: str = "bfloat16"
+    extra: dict = field(default_factory=dict)
+
+    def __post_init__(self):
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+        assert self.num_attention_heads % self.num_key_value_heads == 0
+
+    # ------------------------------------------------------------------ derived sizes
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    def num_parameters(self, include_embedding: bool = True) -> int:
+        h, L = self.hidden_size, self.num_hidden_layers
+        attn = h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+        if self.attention_bias:
+            attn += self.q_size + 2 * self.kv_size
+        if self.qk_norm:
+            attn += 2 * self.head_dim
+        if self.is_moe:
+            mlp = self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
+        else:
+            mlp = 3 * h * self.intermediate_size
+        n = L * (attn + mlp + 2 * h) + h
+        if include_embedding:
+            n += self.vocab_size * h * (1 if self.tie_word_embeddings else 2)
+        return n
+
+    # ------------------------------------------------------------------ HF interop
+    @classmethod
+    def from_hf_dict(cls, d: dict) -> "ModelConfig":
+        mt = d.get("model_type", "llama")
+        known = dict(
+            model_type=mt,
+            vocab_size=d["vocab_size"],
+            hidden_size=d["hidden_size"],
+            intermediate_size=d.get("intermediate_size", 0),
+            num_hidden_layers=d["num_hidden_layers"],
+            num_attention_heads=d["num_attention_heads"],
+            num_key_value_heads=d.get("num_key_value_heads", d["num_attention_heads"]),
+            head_dim=d.get("head_dim"),
+            rms_norm_eps=d.get("rms_norm_eps", 1e-6),
+            rope_theta=d.get("rope_theta", (d.get("rope_parameters") or {}).get("rope_theta", 10000.0)),
+            max_position_embeddings=d.get("max_position_embeddings", 32768),
+            tie_word_embeddings=d.get("tie_word_embeddings", False),
+            attention_bias=d.get("attention_bias", mt == "qwen2"),
+            qk_norm=mt in ("qwen3", "qwen3_moe"),
+            initializer_range=d.get("initializer_range", 0.02),
+            num_experts=d.get("num_experts", d.get("num_local_experts", 0)) if "moe" in mt or "mixtral" in mt else 0,
+            num_experts_per_tok=d.get("num_experts_per_tok", 0),
+            moe_intermediate_size=d.get("moe_intermediate_size", 0),
+            norm_topk_prob=d.get("norm_topk_prob", True),
+            router_aux_loss_coef=d.get("router_aux_loss_coef", 0.0),
+            pad_token_id=d.get("pad_token_id"),
+            eos_token_id=d.get("eos_token_id") if not isinstance(d.get("eos_token_id"), list) else d["eos_token_id"][0],
+            bos_token_id=d.get("bos_token_id"),
+            torch_dtype=str(d.get("torch_dtype", d.get("dtype", "bfloat16"))),
+        )
+        return cls(**known)
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "ModelConfig":
+        p = Path(path)
+        if p.is_dir():
+            p = p / "config.json"
+        return cls.from_hf_dict(json.loads(p.read_text()))
+
+    def to_hf_dict(self) -> dict:
+        arch = {"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
+                "llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
+        if self.value_head:
+            arch = arch.replace("ForCausalLM", "ForTokenClassification")
+        d = dict(
+            architectures=[arch], model_type=self.model_type, vocab_size=self.vocab_size, hidden_size=self.hidden_size,
+            intermediate_size=self.intermediate_size, num_hidden_layers=self.num_hidden_layers,
+            num_attention_heads=self.num_attention_heads, num_key_value_heads=self.num_key_value_heads,
+            head_dim=self.head_dim, rms_norm_eps=self.rms_norm_eps, rope_theta=self.rope_theta,
+            max_position_embeddings=self.max_position_embeddings, tie_word_embeddings=self.tie_word_embeddings,
+            attention_bias=self.attention_bias, initializer_range=self.initializer_range, hidden_act="silu",
+            pad_token_id=self.pad_token_id, eos_token_id=self.eos_token_id, bos_token_id=self.bos_token_id,
+            torch_dtype=self.torch_dtype,
+        )
+        if self.is_moe:
+            d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
+                     moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob,
+                     router_aux_loss_coef=self.router_aux_loss_coef)
+        if self.value_head:
+            d["num_labels"] = 1
+        return d
+
+    def save_pretrained(self, path: str):
+        Path(path).mkdir(parents=True, exist_ok=True)
+        (Path(path) / "config.json").write_text(json.dumps(self.to_hf_dict(), indent=2))
+
+    def replace(self, **kw) -> "ModelConfig":
+        d = asdict(self)
+        d.update(kw)
+        return ModelConfig(**d)
+
+
+PRESETS: dict[str, ModelConfig] = {
+    # 2-layer plumbing model of the CPU/gloo correctness configuration
+    "tiny-qwen2": ModelConfig(model_type="qwen2", vocab_size=2048, hidden_size=128, intermediate_size=512,
+                              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-6,
+                              rope_theta=1e4, tie_word_embeddings=True, max_position_embeddings=4096, torch_dtype="float32"),
+    "tiny-qwen2-gpu": ModelConfig(model_type="qwen2", vocab_size=4096, hidden_size=512, intermediate_size=1536,
+                                  num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                                  rope_theta=1e4, max_position_embeddings=4096),
+    "qwen2.5-0.5b": ModelConfig(model_type="qwen2", vocab_size=151936, hidden_size=896, intermediate_size=4864,
+                                num_hidden_layers=24, num_attention_heads=14, num_key_value_heads=2,
+                                tie_word_embeddings=True),
+    "qwen2.5-7b": ModelConfig(model_type="qwen2", vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+                              num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, rope_theta=1e6),
+    "llama3.1-8b": ModelConfig(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
+                               num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, rope_theta=5e5,
+                               attention_bias=False, rms_norm_eps=1e-5, max_position_embeddings=131072),
+    "qwen3-8b": ModelConfig(model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
+                            num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                            attention_bias=False, qk_norm=True, rope_theta=1e6),
+    "qwen3-30b-a3b": ModelConfig(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                                 num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4, head_dim=128,
+                                 attention_bias=False, qk_norm=True, rope_theta=1e6, num_experts=128,
+                                 num_experts_per_tok=8, moe_intermediate_size=768),
+}

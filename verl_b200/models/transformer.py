@@ -1,0 +1,321 @@
+"""Decoder-only transformer (Llama / Qwen2 / Qwen3 / Qwen3-MoE families) on packed variable-length batches.
+
+The model is written against ``verl_b200.ops`` so the same definition runs the sm_100a kernels on a B200 and plain
+PyTorch on CPU. Inputs are *packed*: all sequences of a micro-batch back to back in one ``[T]`` row with
+``cu_seqlens`` marking the boundaries (what the reference obtains by monkey-patching HF models for
+``use_remove_padding``: ``verl/models/transformers/monkey_patch.py:87-156``,
+``verl/workers/engine/fsdp/transformer_impl.py:1155-1342``). Projections are stored fused (``qkv_proj``,
+``gate_up_proj``) and converted from/to HF tensor names on import/export.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Iterator, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from verl_b200 import ops
+from verl_b200.models.config import ModelConfig
+
+__all__ = ["DecoderLM", "PackedBatch", "hf_to_native_state_dict", "native_to_hf_tensors"]
+
+
+class PackedBatch:
+    """Device-side description of a packed micro-batch."""
+
+    __slots__ = ("input_ids", "position_ids", "cu_seqlens", "cu_seqlens_cpu", "max_seqlen", "routed_experts")
+
+    def __init__(self, input_ids, position_ids, cu_seqlens, cu_seqlens_cpu=None, max_seqlen=None, routed_experts=None):
+        self.input_ids = input_ids
+        self.position_ids = position_ids
+        self.cu_seqlens = cu_seqlens.to(torch.int32)
+        self.cu_seqlens_cpu = cu_seqlens_cpu if cu_seqlens_cpu is not None else cu_seqlens.cpu()
+        lens = self.cu_seqlens_cpu[1:] - self.cu_seqlens_cpu[:-1]
+        self.max_seqlen = int(max_seqlen if max_seqlen is not None else (lens.max() if lens.numel() else 0))
+        self.routed_experts = routed_experts  # optional [T, layers, topk] forced routing (router replay)
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        kw = dict(dtype=dtype, device=device)
+        self.qkv_proj = nn.Parameter(torch.empty(cfg.q_size + 2 * cfg.kv_size, cfg.hidden_size, **kw))
+        self.qkv_bias = nn.Parameter(torch.zeros(cfg.q_size + 2 * cfg.kv_size, **kw)) if cfg.attention_bias else None
+        self.o_proj = nn.Parameter(torch.empty(cfg.hidden_size, cfg.q_size, **kw))
+        if cfg.qk_norm:
+            self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, **kw))
+            self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, **kw))
+
+    def forward(self, x: torch.Tensor, pb: PackedBatch, cos, sin, sp_group=None) -> torch.Tensor:
+        cfg = self.cfg
+        qkv = ops.linear(x, self.qkv_proj, self.qkv_bias)
+        if cfg.qk_norm:
+            T = qkv.shape[0]
+            q, k, v = qkv.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=-1)
+            q = ops.rmsnorm(q.reshape(-1, cfg.head_dim), self.q_norm, cfg.rms_norm_eps).reshape(T, cfg.q_size)
+            k = ops.rmsnorm(k.reshape(-1, cfg.head_dim), self.k_norm, cfg.rms_norm_eps).reshape(T, cfg.kv_size)
+            qkv = torch.cat([q, k, v], dim=-1)
+        qkv = ops.apply_rope_(qkv, pb.position_ids, cos, sin, cfg.num_attention_heads + cfg.num_key_value_heads, cfg.head_dim)
+        if sp_group is not None:
+            from verl_b200.parallel.ulysses import ulysses_attention
+
+            o = ulysses_attention(qkv, pb, cfg, sp_group)
+        else:
+            o = ops.attention_varlen(qkv, pb.cu_seqlens, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                                     pb.max_seqlen, pb.cu_seqlens_cpu)
+        return ops.linear(o, self.o_proj)
+
+
+class MLP(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        kw = dict(dtype=dtype, device=device)
+        self.gate_up_proj = nn.Parameter(torch.empty(2 * cfg.intermediate_size, cfg.hidden_size, **kw))
+        self.down_proj = nn.Parameter(torch.empty(cfg.hidden_size, cfg.intermediate_size, **kw))
+
+    def forward(self, x):
+        return ops.linear(ops.swiglu(ops.linear(x, self.gate_up_proj)), self.down_proj)
+
+
+class MoE(nn.Module):
+    """Top-k softmax-routed experts (Qwen3-MoE). Experts are stored packed [E, 2I, H] / [E, H, I]; the token
+    permutation + grouped GEMM path lives in ``verl_b200.ops.moe``; expert parallelism in ``verl_b200.parallel.ep``."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device, layer_idx: int):
+        super().__init__()
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        kw = dict(dtype=dtype, device=device)
+        E, I, H = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
+        self.router = nn.Parameter(torch.empty(E, H, **kw))
+        self.experts_gate_up = nn.Parameter(torch.empty(E, 2 * I, H, **kw))
+        self.experts_down = nn.Parameter(torch.empty(E, H, I, **kw))
+        self.ep_group = None
+        self.last_topk: Optional[torch.Tensor] = None   # recorded routing (router replay R2)
+        self.record_routing = False
+
+    def forward(self, x, forced_topk: Optional[torch.Tensor] = None):
+        from verl_b200.ops.moe import moe_forward
+
+        out, topk_idx = moe_forward(x, self.router, self.experts_gate_up, self.experts_down, self.cfg.num_experts_per_tok,
+                                    self.cfg.norm_topk_prob, forced_topk=forced_topk, ep_group=self.ep_group)
+        if self.record_routing:
+            self.last_topk = topk_idx.detach()
+        return out
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device, layer_idx: int):
+        super().__init__()
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        kw = dict(dtype=dtype, device=device)
+        self.input_layernorm = nn.Parameter(torch.ones(cfg.hidden_size, **kw))
+        self.post_attention_layernorm = nn.Parameter(torch.ones(cfg.hidden_size, **kw))
+        self.self_attn = Attention(cfg, dtype, device)
+        self.mlp = MoE(cfg, dtype, device, layer_idx) if cfg.is_moe else MLP(cfg, dtype, device)
+
+    def forward(self, h, residual, pb: PackedBatch, cos, sin, sp_group=None):
+        """(h, residual) carry the un-normalised stream split in two so the add is fused into the next norm."""
+        if residual is None:
+            residual = h
+            x = ops.rmsnorm(h, self.input_layernorm, self.cfg.rms_norm_eps)
+        else:
+            x, residual = ops.add_rmsnorm(h, residual, self.input_layernorm, self.cfg.rms_norm_eps)
+        a = self.self_attn(x, pb, cos, sin, sp_group)
+        x, residual = ops.add_rmsnorm(a, residual, self.post_attention_layernorm, self.cfg.rms_norm_eps)
+        if self.cfg.is_moe:
+            forced = pb.routed_experts[:, self.layer_idx] if pb.routed_experts is not None else None
+            m = self.mlp(x, forced)
+        else:
+            m = self.mlp(x)
+        return m, residual
+
+
+class DecoderLM(nn.Module):
+    """Embedding → N decoder layers → final norm → (lm_head | value head)."""
+
+    def __init__(self, cfg: ModelConfig, dtype: torch.dtype = torch.bfloat16, device="cpu", init: bool = True, seed: int = 0):
+        super().__init__()
+        self.cfg = cfg
+        self.dtype = dtype
+        kw = dict(dtype=dtype, device=device)
+        self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))
+        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, i) for i in range(cfg.num_hidden_layers)])
+        self.norm = nn.Parameter(torch.ones(cfg.hidden_size, **kw))
+        if cfg.value_head:
+            self.score = nn.Parameter(torch.empty(1, cfg.hidden_size, **kw))
+            self.lm_head = None
+        elif cfg.tie_word_embeddings:
+            self.lm_head = None
+        else:
+            self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))
+        self.gradient_checkpointing = False
+        self.sp_group = None
+        if init:
+            self.reset_parameters(seed)
+
+    # ------------------------------------------------------------------ init
+    @torch.no_grad()
+    def reset_parameters(self, seed: int = 0):
+        """normal(0, initializer_range) for matrices, ones for norms, zeros for biases (HF ``_init_weights``)."""
+        gen = torch.Generator(device=self.embed_tokens.device)
+        gen.manual_seed(seed)
+        std = self.cfg.initializer_range
+        for name, p in self.named_parameters():
+            if name.endswith("layernorm") or name.endswith("norm"):
+                p.fill_(1.0)
+            elif name.endswith("bias"):
+                p.zero_()
+            else:
+                p.normal_(0.0, std, generator=gen)
+
+    @property
+    def output_weight(self) -> torch.Tensor:
+        return self.embed_tokens if self.lm_head is None else self.lm_head
+
+    # ------------------------------------------------------------------ forward
+    def rope(self, device):
+        return ops.rope_tables(self.cfg.max_position_embeddings, self.cfg.head_dim, self.cfg.rope_theta, device)
+
+    def forward_hidden(self, pb: PackedBatch, layer_range: Optional[range] = None, h_in: Optional[torch.Tensor] = None):
+        """Returns final-normed hidden states [T, H] (or the raw stream if ``layer_range`` stops early, for PP)."""
+        cos, sin = self.rope(pb.input_ids.device)
+        first = layer_range is None or layer_range.start == 0
+        last = layer_range is None or layer_range.stop == self.cfg.num_hidden_layers
+        h = ops.embedding(pb.input_ids, self.embed_tokens) if first else h_in
+        residual = None
+        layers = self.layers if layer_range is None else [self.layers[i] for i in layer_range]
+        for layer in layers:
+            if self.gradient_checkpointing and torch.is_grad_enabled():
+                h, residual = checkpoint(layer, h, residual, pb, cos, sin, self.sp_group, use_reentrant=False)
+            else:
+                h, residual = layer(h, residual, pb, cos, sin, self.sp_group)
+        if not last:
+            return h + residual if residual is not None else h
+        if residual is None:
+            return ops.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)
+        return ops.add_rmsnorm(h, residual, self.norm, self.cfg.rms_norm_eps)[0]
+
+    def forward(self, pb: PackedBatch, labels: Optional[torch.Tensor] = None, temperature: float = 1.0,
+                need_entropy: bool = True, return_logits: bool = False):
+        """Training/inference forward on a packed batch.
+
+        * value-head models return ``{"values": [T]}``;
+        * with ``labels`` returns ``{"log_probs": [T], "entropy": [T] or None}`` through the fused lm_head kernel;
+        * with ``return_logits`` returns ``{"logits": [T, V]}`` (debug / sampling on CPU).
+        """
+        h = self.forward_hidden(pb)
+        if self.cfg.value_head:
+            return {"values": F.linear(h, self.score).squeeze(-1).float()}
+        out = {}
+        if labels is not None:
+            lp, ent = ops.linear_logprob_entropy(h, self.output_weight, labels, temperature, need_entropy)
+            out["log_probs"], out["entropy"] = lp, ent
+        if return_logits:
+            out["logits"] = F.linear(h, self.output_weight)
+        out["hidden"] = h
+        return out
+
+    # ------------------------------------------------------------------ (de)serialisation with HF names
+    def hf_named_tensors(self) -> Iterator[tuple[str, torch.Tensor]]:
+        return native_to_hf_tensors(self.cfg, dict(self.named_parameters()))
+
+    def load_hf_state_dict(self, sd: dict, strict: bool = True):
+        native = hf_to_native_state_dict(self.cfg, sd)
+        own = dict(self.named_parameters())
+        missing = [k for k in own if k not in native]
+        if strict and missing:
+            raise KeyError(f"missing tensors for {missing[:5]} ...")
+        with torch.no_grad():
+            for k, v in native.items():
+                if k in own:
+                    own[k].copy_(v.to(own[k].dtype))
+
+
+# ---------------------------------------------------------------------------------------------------- name mapping
+def native_to_hf_tensors(cfg: ModelConfig, params: dict) -> Iterator[tuple[str, torch.Tensor]]:
+    """Yield (hf_name, tensor) splitting the fused projections; tensors are views where possible."""
+    yield "model.embed_tokens.weight", params["embed_tokens"]
+    for i in range(cfg.num_hidden_layers):
+        p = f"layers.{i}."
+        hp = f"model.layers.{i}."
+        if p + "input_layernorm" not in params:
+            continue  # pipeline stage that does not own this layer
+        yield hp + "input_layernorm.weight", params[p + "input_layernorm"]
+        yield hp + "post_attention_layernorm.weight", params[p + "post_attention_layernorm"]
+        qkv = params[p + "self_attn.qkv_proj"]
+        q, k, v = qkv.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=0)
+        yield hp + "self_attn.q_proj.weight", q
+        yield hp + "self_attn.k_proj.weight", k
+        yield hp + "self_attn.v_proj.weight", v
+        if cfg.attention_bias:
+            qb, kb, vb = params[p + "self_attn.qkv_bias"].split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=0)
+            yield hp + "self_attn.q_proj.bias", qb
+            yield hp + "self_attn.k_proj.bias", kb
+            yield hp + "self_attn.v_proj.bias", vb
+        yield hp + "self_attn.o_proj.weight", params[p + "self_attn.o_proj"]
+        if cfg.qk_norm:
+            yield hp + "self_attn.q_norm.weight", params[p + "self_attn.q_norm"]
+            yield hp + "self_attn.k_norm.weight", params[p + "self_attn.k_norm"]
+        if cfg.is_moe:
+            yield hp + "mlp.gate.weight", params[p + "mlp.router"]
+            gu, dn = params[p + "mlp.experts_gate_up"], params[p + "mlp.experts_down"]
+            I = cfg.moe_intermediate_size
+            for e in range(cfg.num_experts):
+                yield hp + f"mlp.experts.{e}.gate_proj.weight", gu[e, :I]
+                yield hp + f"mlp.experts.{e}.up_proj.weight", gu[e, I:]
+                yield hp + f"mlp.experts.{e}.down_proj.weight", dn[e]
+        else:
+            gu = params[p + "mlp.gate_up_proj"]
+            I = cfg.intermediate_size
+            yield hp + "mlp.gate_proj.weight", gu[:I]
+            yield hp + "mlp.up_proj.weight", gu[I:]
+            yield hp + "mlp.down_proj.weight", params[p + "mlp.down_proj"]
+    if "norm" in params:
+        yield "model.norm.weight", params["norm"]
+    if "score" in params:
+        yield "score.weight", params["score"]
+    if "lm_head" in params and params.get("lm_head") is not None:
+        yield "lm_head.weight", params["lm_head"]
+
+
+def hf_to_native_state_dict(cfg: ModelConfig, sd: dict) -> dict:
+    """Fuse q/k/v and gate/up tensors of an HF state dict into this model's parameter names."""
+    out = {}
+    g = sd.get
+    out["embed_tokens"] = sd["model.embed_tokens.weight"]
+    for i in range(cfg.num_hidden_layers):
+        hp, p = f"model.layers.{i}.", f"layers.{i}."
+        if hp + "input_layernorm.weight" not in sd:
+            continue
+        out[p + "input_layernorm"] = sd[hp + "input_layernorm.weight"]
+        out[p + "post_attention_layernorm"] = sd[hp + "post_attention_layernorm.weight"]
+        out[p + "self_attn.qkv_proj"] = torch.cat([sd[hp + f"self_attn.{n}_proj.weight"] for n in "qkv"], 0)
+        if cfg.attention_bias and hp + "self_attn.q_proj.bias" in sd:
+            out[p + "self_attn.qkv_bias"] = torch.cat([sd[hp + f"self_attn.{n}_proj.bias"] for n in "qkv"], 0)
+        out[p + "self_attn.o_proj"] = sd[hp + "self_attn.o_proj.weight"]
+        if cfg.qk_norm:
+            out[p + "self_attn.q_norm"] = sd[hp + "self_attn.q_norm.weight"]
+            out[p + "self_attn.k_norm"] = sd[hp + "self_attn.k_norm.weight"]
+        if cfg.is_moe:
+            out[p + "mlp.router"] = sd[hp + "mlp.gate.weight"]
+            out[p + "mlp.experts_gate_up"] = torch.stack(
+                [torch.cat([sd[hp + f"mlp.experts.{e}.gate_proj.weight"], sd[hp + f"mlp.experts.{e}.up_proj.weight"]], 0)
+                 for e in range(cfg.num_experts)], 0)
+            out[p + "mlp.experts_down"] = torch.stack([sd[hp + f"mlp.experts.{e}.down_proj.weight"] for e in range(cfg.num_experts)], 0)
+        else:
+            out[p + "mlp.gate_up_proj"] = torch.cat([sd[hp + "mlp.gate_proj.weight"], sd[hp + "mlp.up_proj.weight"]], 0)
+            out[p + "mlp.down_proj"] = sd[hp + "mlp.down_proj.weight"]
+    if "model.norm.weight" in sd:
+        out["norm"] = sd["model.norm.weight"]
+    if g("lm_head.weight") is not None and not cfg.tie_word_embeddings and not cfg.value_head:
+        out["lm_head"] = sd["lm_head.weight"]
+    if g("score.weight") is not None:
+        out["score"] = sd["score.weight"]
+    return out

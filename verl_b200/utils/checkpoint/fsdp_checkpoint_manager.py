@@ -1,0 +1,137 @@
+"""Per-rank sharded checkpoints of the fsdp engine.
+
+Directory layout (same file names as the reference, ``verl/utils/checkpoint/fsdp_checkpoint_manager.py:364-527``):
+
+    model_world_size_{W}_rank_{r}.pt        this rank's slice of the flat parameter buffer + layout table
+    optim_world_size_{W}_rank_{r}.pt        fp32 master slice, Adam moments, step counters
+    extra_state_world_size_{W}_rank_{r}.pt  LR-schedule position + RNG states (cpu / numpy / random / cuda)
+    fsdp_config.json                        {"FSDP_version": 2, "world_size": W, "format": "flat_v1"}
+    huggingface/                            config.json (+ safetensors shards when ``hf_model`` is in save_contents)
+
+Only same-world-size reloads are supported for the sharded files (as in the reference); ``huggingface/`` and
+``python -m verl_b200.model_merger`` give the world-size-independent form.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import threading
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .checkpoint_manager import BaseCheckpointManager
+
+__all__ = ["FSDPCheckpointManager"]
+
+
+class FSDPCheckpointManager(BaseCheckpointManager):
+    def __init__(self, engine, checkpoint_config=None):
+        super().__init__(checkpoint_config)
+        self.engine = engine
+        self._async_thread: Optional[threading.Thread] = None
+
+    @property
+    def rank(self):
+        return self.engine.fsdp_rank + self.engine.fsdp_size * (self.engine.rank // self.engine.fsdp_size)
+
+    def _names(self, local_path):
+        W, r = self.engine.world, self.engine.rank
+        return (os.path.join(local_path, f"model_world_size_{W}_rank_{r}.pt"),
+                os.path.join(local_path, f"optim_world_size_{W}_rank_{r}.pt"),
+                os.path.join(local_path, f"extra_state_world_size_{W}_rank_{r}.pt"))
+
+    def save_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, global_step: int = 0,
+                        max_ckpt_to_keep: Optional[int] = None):
+        if local_path is None:
+            return
+        e = self.engine
+        self.previous_global_step = global_step
+        if e.rank == 0:
+            self.ensure_checkpoint_capacity(max_ckpt_to_keep)
+        self.local_mkdir_safe(local_path)
+        if dist.is_initialized():
+            dist.barrier()
+        if self._async_thread is not None:
+            self._async_thread.join()
+        model_f, optim_f, extra_f = self._names(local_path)
+        s = e.store
+        payload = []
+        if self.should_save_model:
+            shard = s.flat[s.shard_slice].detach().to("cpu", copy=True)
+            payload.append((model_f, {"format": "flat_v1", "names": s.names, "shapes": [tuple(p.shape) for p in s.params],
+                                      "offsets": s.offsets, "total": s.total, "shard_size": s.shard_size,
+                                      "fsdp_rank": e.fsdp_rank, "fsdp_size": e.fsdp_size, "dtype": str(s.flat.dtype),
+                                      "flat_shard": shard}))
+        if self.should_save_optimizer and not e.forward_only:
+            payload.append((optim_f, {"master": e.master.detach().to("cpu", copy=True), "exp_avg": e.exp_avg.detach().to("cpu", copy=True),
+                                      "exp_avg_sq": e.exp_avg_sq.detach().to("cpu", copy=True), "step_count": e.step_count}))
+        if self.should_save_extra:
+            payload.append((extra_f, {"lr_scheduler": {"sched_step": e.sched_step}, "rng": self.get_rng_state()}))
+
+        def write():
+            for fn, obj in payload:
+                tmp = fn + ".tmp"
+                torch.save(obj, tmp)
+                os.replace(tmp, fn)
+
+        if self.async_save:
+            self._async_thread = threading.Thread(target=write, daemon=True)
+            self._async_thread.start()
+        else:
+            write()
+        if e.rank == 0:
+            with open(os.path.join(local_path, "fsdp_config.json"), "w") as f:
+                json.dump({"FSDP_version": 2, "world_size": e.world, "format": "flat_v1"}, f, indent=2)
+            hf_dir = os.path.join(local_path, "huggingface")
+            e.cfg.save_pretrained(hf_dir)
+            tok_src = getattr(e, "tokenizer_path", None)
+            if tok_src and os.path.isdir(tok_src):
+                import shutil
+                for fn in os.listdir(tok_src):
+                    if fn.startswith("tokenizer") or fn in ("vocab.json", "merges.txt", "special_tokens_map.json", "generation_config.json"):
+                        shutil.copy(os.path.join(tok_src, fn), os.path.join(hf_dir, fn))
+            if self.should_save_hf_model:
+                from verl_b200.models.hf_io import save_hf_weights
+
+                save_hf_weights(e.model.hf_named_tensors(), hf_dir)
+        if dist.is_initialized():
+            dist.barrier()
+        if e.rank == 0:
+            self.register_checkpoint(local_path, max_ckpt_to_keep)
+
+    def load_checkpoint(self, local_path: Optional[str], hdfs_path: Optional[str] = None, del_local_after_load: bool = False):
+        if local_path is None:
+            return
+        e = self.engine
+        model_f, optim_f, extra_f = self._names(local_path)
+        s = e.store
+        if self.should_load_model:
+            if not os.path.exists(model_f):
+                raise FileNotFoundError(f"{model_f} not found (sharded checkpoints reload only at the same world size)")
+            st = torch.load(model_f, map_location="cpu", weights_only=False)
+            assert st["total"] == s.total and st["names"] == s.names, "checkpoint layout does not match this model"
+            s.flat[s.shard_slice].copy_(st["flat_shard"].to(s.flat.dtype))
+            if e.world > 1 and e.fsdp_size > 1:
+                if s.flat.is_cuda:
+                    dist.all_gather_into_tensor(s.flat, s.flat[s.shard_slice].clone(), group=e.fsdp_group)
+                else:
+                    parts = [torch.empty(s.shard_size, dtype=s.flat.dtype) for _ in range(e.fsdp_size)]
+                    dist.all_gather(parts, s.flat[s.shard_slice].clone(), group=e.fsdp_group)
+                    s.flat.copy_(torch.cat(parts))
+        if self.should_load_optimizer and not e.forward_only and os.path.exists(optim_f):
+            st = torch.load(optim_f, map_location="cpu", weights_only=False)
+            e.master.copy_(st["master"])
+            e.exp_avg.copy_(st["exp_avg"])
+            e.exp_avg_sq.copy_(st["exp_avg_sq"])
+            e.step_count = int(st["step_count"])
+        if self.should_load_extra and os.path.exists(extra_f):
+            st = torch.load(extra_f, map_location="cpu", weights_only=False)
+            e.sched_step = int(st["lr_scheduler"]["sched_step"])
+            self.load_rng_state(st["rng"])
+        if dist.is_initialized():
+            dist.barrier()
+        if del_local_after_load:
+            self.remove_previous_save_local_path(local_path)

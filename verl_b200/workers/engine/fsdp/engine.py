@@ -1,0 +1,523 @@
+"""Sharded data-parallel training engine ("fsdp" backend).
+
+Design for a 180 GB B200: the bf16 working copy of the parameters is one flat buffer that stays *resident* on every
+rank (ZeRO-2 style, ``reshard_after_forward=False``) while fp32 master weights, Adam moments and the reduced
+gradients are sharded 1/W per rank. One optimizer step is: reduce-scatter(fp32 grads) → global-norm clip → fused
+AdamW on the local shard (writes the bf16 shard) → all-gather of the bf16 shards. Compared with the reference's
+per-layer all-gather/reduce-scatter on every micro-batch (``verl/workers/engine/fsdp/transformer_impl.py:389-498``,
+``verl/utils/fsdp_utils.py:549-614``) this removes all collectives from forward/backward and lets the colocated
+rollout engine read the same resident weights with no copy. ``reshard_after_forward=True`` (ZeRO-3) keeps only the
+shard resident and gathers layer units on demand.
+
+Parity target for behaviour: ``FSDPEngine`` in ``verl/workers/engine/fsdp/transformer_impl.py`` (forward_backward_batch
+:728-781, optimizer_step :792-838, prepare_model_inputs/outputs :1155-1568, get_per_tensor_param :981-1065).
+"""
+
+from __future__ import annotations
+
+import math
+import os
+from typing import Any, Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from verl_b200 import ops
+from verl_b200.models.config import PRESETS, ModelConfig
+from verl_b200.models.transformer import DecoderLM, PackedBatch
+from verl_b200.ops import _ext
+from verl_b200.utils.device import get_device_name
+from verl_b200.utils.metric import AggregationType, Metric
+from verl_b200.utils.seqlen_balancing import rearrange_micro_batches, restore_dynamic_batch
+from verl_b200.workers.engine.base import BaseEngine, EngineRegistry
+from verl_b200.workers.utils.padding import response_gather_index
+
+__all__ = ["FSDPEngine", "FSDPEngineWithValueHead", "FlatParamStore", "cfg_get"]
+
+
+def cfg_get(cfg, key: str, default=None):
+    """Read ``a.b.c`` from nested dict-likes / dataclasses, returning ``default`` for missing or None values."""
+    cur = cfg
+    for part in key.split("."):
+        if cur is None:
+            return default
+        if hasattr(cur, "get") and not isinstance(cur, torch.Tensor):
+            cur = cur.get(part, None)
+        else:
+            cur = getattr(cur, part, None)
+    return default if cur is None else cur
+
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           "float16": torch.float16, "fp16": torch.float16, "torch.bfloat16": torch.bfloat16, "torch.float32": torch.float32}
+
+
+class FlatParamStore:
+    """All parameters of a model as views into one flat buffer (+ a flat fp32 gradient buffer of the same layout).
+
+    Every tensor starts on a 256-byte boundary so each view is a legal TMA base; the total length is padded so it
+    divides evenly among ``world`` ranks in 1024-element granules.
+    """
+
+    ALIGN = 128
+
+    def __init__(self, model: torch.nn.Module, world: int, rank: int):
+        self.model = model
+        self.world, self.rank = world, rank
+        params = [(n, p) for n, p in model.named_parameters()]
+        self.names = [n for n, _ in params]
+        self.params = [p for _, p in params]
+        self.offsets, off = [], 0
+        for p in self.params:
+            self.offsets.append(off)
+            off += -(-p.numel() // self.ALIGN) * self.ALIGN
+        gran = world * 1024
+        self.total = -(-off // gran) * gran
+        self.shard_size = self.total // world
+        dev, dt = self.params[0].device, self.params[0].dtype
+        self.flat = torch.zeros(self.total, dtype=dt, device=dev)
+        for p, o in zip(self.params, self.offsets):
+            view = self.flat[o : o + p.numel()].view(p.shape)
+            view.copy_(p.data)
+            p.data = view
+        self.grad: Optional[torch.Tensor] = None
+
+    @property
+    def shard_slice(self) -> slice:
+        return slice(self.rank * self.shard_size, (self.rank + 1) * self.shard_size)
+
+    def alloc_grads(self):
+        if self.grad is None:
+            self.grad = torch.zeros(self.total, dtype=torch.float32, device=self.flat.device)
+            for p, o in zip(self.params, self.offsets):
+                p.main_grad = self.grad[o : o + p.numel()].view(p.shape)
+
+    def free_grads(self):
+        self.grad = None
+        for p in self.params:
+            p.main_grad = None
+
+    def zero_grads(self):
+        if self.grad is not None:
+            self.grad.zero_()
+        for p in self.params:
+            p.grad = None
+
+    def fold_autograd_grads(self):
+        """Parameters touched by plain PyTorch ops receive ``.grad``; add those into the flat buffer."""
+        for p in self.params:
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(torch.float32))
+                p.grad = None
+
+    def rebind(self, new_flat: torch.Tensor):
+        """Point every parameter at ``new_flat`` (same layout) — used by offload and symmetric-heap placement."""
+        self.flat = new_flat
+        for p, o in zip(self.params, self.offsets):
+            p.data = new_flat[o : o + p.numel()].view(p.shape)
+
+
+def _adamw_reference(p32, m, v, g, lr, b1, b2, eps, wd, step, gscale):
+    """torch.optim.AdamW update rule (decoupled weight decay) on flat fp32 tensors."""
+    g = g.float() * gscale
+    p32.mul_(1 - lr * wd)
+    m.mul_(b1).add_(g, alpha=1 - b1)
+    v.mul_(b2).addcmul_(g, g, value=1 - b2)
+    bc1 = 1 - b1**step
+    bc2 = 1 - b2**step
+    denom = (v.sqrt() / math.sqrt(bc2)).add_(eps)
+    p32.addcdiv_(m, denom, value=-lr / bc1)
+
+
+@EngineRegistry.register(model_type="language_model", backend=["fsdp", "fsdp2"], device=["cuda", "cpu"])
+class FSDPEngine(BaseEngine):
+    def __init__(self, model_config, engine_config=None, optimizer_config=None, checkpoint_config=None):
+        self.model_config = model_config
+        self.engine_config = engine_config or {}
+        self.optimizer_config = optimizer_config
+        self.checkpoint_config = checkpoint_config or {}
+        self.mode = None
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.device = torch.device(get_device_name(), torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.sp_size = int(cfg_get(self.engine_config, "ulysses_sequence_parallel_size", 1))
+        fsdp_size = int(cfg_get(self.engine_config, "fsdp_size", -1))
+        self.fsdp_size = self.world if fsdp_size in (-1, 0) or fsdp_size >= self.world else fsdp_size
+        self.forward_only = bool(cfg_get(self.engine_config, "forward_only", False)) or optimizer_config is None
+        self._param_offload = bool(cfg_get(self.engine_config, "param_offload", False))
+        self._optimizer_offload = bool(cfg_get(self.engine_config, "optimizer_offload", False))
+        self.step_count = 0
+        self.sched_step = 0
+        self._value_head = False
+        self.model: Optional[DecoderLM] = None
+        self.store: Optional[FlatParamStore] = None
+
+    # ------------------------------------------------------------------ build
+    def _resolve_model_config(self) -> ModelConfig:
+        mc = self.model_config
+        if isinstance(mc, ModelConfig):
+            cfg = mc
+        else:
+            preset = cfg_get(mc, "preset", None)
+            path = cfg_get(mc, "path", None)
+            if preset is not None:
+                cfg = PRESETS[preset]
+            elif path is not None and os.path.exists(os.path.join(os.path.expanduser(path), "config.json")):
+                cfg = ModelConfig.from_pretrained(os.path.expanduser(path))
+            elif path in PRESETS:
+                cfg = PRESETS[path]
+            else:
+                raise FileNotFoundError(f"cannot resolve model config from {mc}")
+            override = cfg_get(mc, "override_config", None) or {}
+            override = {k: v for k, v in dict(override).items() if k in ModelConfig.__dataclass_fields__}
+            if override:
+                cfg = cfg.replace(**override)
+        if self._value_head and not cfg.value_head:
+            cfg = cfg.replace(value_head=True)
+        return cfg
+
+    def initialize(self):
+        cfg = self._resolve_model_config()
+        self.cfg = cfg
+        dt_name = cfg_get(self.engine_config, "model_dtype", None) or (cfg.torch_dtype if self.device.type == "cpu" else "bfloat16")
+        self.dtype = _DTYPES.get(str(dt_name), torch.bfloat16)
+        seed = int(cfg_get(self.engine_config, "seed", 0))
+        self.model = DecoderLM(cfg, dtype=self.dtype, device=self.device, init=True, seed=seed)
+        path = cfg_get(self.model_config, "path", None) if not isinstance(self.model_config, ModelConfig) else None
+        if path and os.path.isdir(os.path.expanduser(path)):
+            from verl_b200.models.hf_io import load_hf_weights
+
+            load_hf_weights(self.model, os.path.expanduser(path), strict=not cfg.value_head)
+        self.model.gradient_checkpointing = bool(cfg_get(self.model_config, "enable_gradient_checkpointing", False))
+        self._build_groups()
+        self.store = FlatParamStore(self.model, self.fsdp_size, self.fsdp_rank)
+        if self.world > 1:
+            # every rank must start from identical weights (rank 0's)
+            dist.broadcast(self.store.flat, src=0)
+        if self.sp_size > 1:
+            self.model.sp_group = self.sp_group
+        if not self.forward_only:
+            self._build_optimizer()
+        from verl_b200.utils.checkpoint.fsdp_checkpoint_manager import FSDPCheckpointManager
+
+        self.checkpoint_manager = FSDPCheckpointManager(self, self.checkpoint_config)
+        if self._param_offload:
+            self.to("cpu", model=True, optimizer=False, grad=False)
+        if self._optimizer_offload and not self.forward_only:
+            self.to("cpu", model=False, optimizer=True, grad=True)
+
+    def _build_groups(self):
+        """Mesh (ddp, fsdp) for parameter sharding and (dp, sp) for Ulysses; ranks are laid out fsdp/sp-fastest."""
+        self.fsdp_group = self.ddp_group = self.sp_group = self.dp_group = None
+        self.fsdp_rank, self.ddp_size = self.rank % self.fsdp_size, self.world // self.fsdp_size
+        self.sp_rank = self.rank % self.sp_size
+        self.dp_size = self.world // self.sp_size
+        self.dp_rank = self.rank // self.sp_size
+        if self.world == 1:
+            return
+        if self.fsdp_size == self.world:
+            self.fsdp_group = dist.group.WORLD
+        else:
+            for d in range(self.ddp_size):
+                ranks = list(range(d * self.fsdp_size, (d + 1) * self.fsdp_size))
+                g = dist.new_group(ranks)
+                if self.rank in ranks:
+                    self.fsdp_group = g
+            for f in range(self.fsdp_size):
+                ranks = list(range(f, self.world, self.fsdp_size))
+                g = dist.new_group(ranks)
+                if self.rank in ranks:
+                    self.ddp_group = g
+        if self.sp_size > 1:
+            assert self.world % self.sp_size == 0
+            for d in range(self.dp_size):
+                ranks = list(range(d * self.sp_size, (d + 1) * self.sp_size))
+                g = dist.new_group(ranks)
+                if self.rank in ranks:
+                    self.sp_group = g
+            for s in range(self.sp_size):
+                ranks = list(range(s, self.world, self.sp_size))
+                g = dist.new_group(ranks)
+                if self.rank in ranks:
+                    self.dp_group = g
+        else:
+            self.dp_group = dist.group.WORLD
+
+    def _build_optimizer(self):
+        oc = self.optimizer_config
+        self.lr = float(cfg_get(oc, "lr", 1e-6))
+        betas = cfg_get(oc, "betas", (0.9, 0.999))
+        self.beta1, self.beta2 = float(betas[0]), float(betas[1])
+        self.adam_eps = float(cfg_get(oc, "eps", 1e-8))
+        self.weight_decay = float(cfg_get(oc, "weight_decay", 0.01))
+        self.clip_grad = float(cfg_get(oc, "clip_grad", 1.0))
+        self.total_steps = int(cfg_get(oc, "total_training_steps", -1))
+        warm = int(cfg_get(oc, "lr_warmup_steps", -1))
+        if warm < 0:
+            ratio = float(cfg_get(oc, "lr_warmup_steps_ratio", 0.0))
+            warm = int(ratio * max(self.total_steps, 0))
+        self.warmup_steps = warm
+        self.lr_scheduler_type = cfg_get(oc, "lr_scheduler_type", cfg_get(oc, "warmup_style", "constant"))
+        self.min_lr_ratio = float(cfg_get(oc, "min_lr_ratio", 0.0))
+        self.num_cycles = float(cfg_get(oc, "num_cycles", 0.5))
+        s = self.store
+        shard = s.flat[s.shard_slice]
+        self.master = shard.detach().clone().float()
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+        self.grad_shard = None
+        self._scalars = torch.zeros(4, dtype=torch.float32, device=self.device)
+        self._sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+
+    def current_lr(self) -> float:
+        step = self.sched_step
+        if self.warmup_steps > 0 and step < self.warmup_steps:
+            return self.lr * step / max(1, self.warmup_steps)
+        if self.lr_scheduler_type == "cosine" and self.total_steps > 0:
+            prog = (step - self.warmup_steps) / max(1, self.total_steps - self.warmup_steps)
+            coef, icpt = (1 - self.min_lr_ratio) * 0.5, (1 + self.min_lr_ratio) * 0.5
+            return self.lr * max(self.min_lr_ratio, math.cos(math.pi * self.num_cycles * 2.0 * prog) * coef + icpt)
+        return self.lr
+
+    # ------------------------------------------------------------------ properties
+    @property
+    def is_param_offload_enabled(self) -> bool:
+        return self._param_offload
+
+    @property
+    def is_optimizer_offload_enabled(self) -> bool:
+        return self._optimizer_offload
+
+    def get_data_parallel_rank(self) -> int:
+        return self.dp_rank
+
+    def get_data_parallel_size(self) -> int:
+        return self.dp_size
+
+    def get_data_parallel_group(self):
+        return self.dp_group
+
+    def is_mp_src_rank_with_outputs(self) -> bool:
+        return self.sp_rank == 0
+
+    # ------------------------------------------------------------------ placement / offload
+    def to(self, device: str, model: bool = True, optimizer: bool = True, grad: bool = True):
+        if self.device.type == "cpu":
+            return
+        target = self.device if device in ("cuda", "gpu", str(self.device)) else torch.device("cpu")
+        to_cpu = target.type == "cpu"
+        if model and self.store is not None:
+            if to_cpu and self.store.flat.is_cuda:
+                host = torch.empty(self.store.flat.shape, dtype=self.store.flat.dtype, pin_memory=True)
+                host.copy_(self.store.flat, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                self.store.rebind(host)
+            elif not to_cpu and not self.store.flat.is_cuda:
+                self.store.rebind(self.store.flat.to(target, non_blocking=True))
+        if optimizer and not self.forward_only:
+            for name in ("master", "exp_avg", "exp_avg_sq"):
+                t = getattr(self, name)
+                if to_cpu and t.is_cuda:
+                    host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+                    host.copy_(t, non_blocking=True)
+                    setattr(self, name, host)
+                elif not to_cpu and not t.is_cuda:
+                    setattr(self, name, t.to(target, non_blocking=True))
+            torch.cuda.current_stream().synchronize()
+        if grad and to_cpu and self.store is not None:
+            self.store.free_grads()
+        if to_cpu:
+            torch.cuda.empty_cache()
+
+    # ------------------------------------------------------------------ micro-batching
+    def _micro_batch_indices(self, seq_lens: torch.Tensor, meta: dict) -> list[list[int]]:
+        n = seq_lens.numel()
+        if meta.get("use_dynamic_bsz", False):
+            budget = int(meta["max_token_len_per_gpu"]) * self.sp_size
+            return rearrange_micro_batches(seq_lens.cpu(), budget, dp_group=self.dp_group if self.world > 1 else None)
+        mbs = int(meta.get("micro_batch_size_per_gpu", 0) or n)
+        return [list(range(i, min(n, i + mbs))) for i in range(0, n, mbs)]
+
+    def _pack(self, mb: dict) -> tuple[PackedBatch, torch.Tensor]:
+        att = mb["attention_mask"].bool()
+        ids = mb["input_ids"][att]
+        pos = mb["position_ids"][att]
+        lens = att.sum(-1)
+        cu_cpu = torch.zeros(lens.numel() + 1, dtype=torch.int32)
+        cu_cpu[1:] = torch.cumsum(lens.cpu(), 0)
+        cu = cu_cpu.to(ids.device, non_blocking=True)
+        labels = torch.roll(ids, shifts=-1, dims=0)
+        routed = None
+        if "routed_experts" in mb:
+            routed = mb["routed_experts"][att]
+        return PackedBatch(ids, pos.to(torch.int32), cu, cu_cpu, int(lens.max()), routed), labels
+
+    def _forward_micro_batch(self, mb: dict, meta: dict) -> dict:
+        """Returns per-token outputs already sliced to the response window: tensors of shape [bs, R]."""
+        pb, labels = self._pack(mb)
+        R = mb["responses"].shape[1]
+        idx, valid = response_gather_index(mb["attention_mask"], R)
+        temperature = float(meta.get("temperature", 1.0))
+        need_entropy = bool(meta.get("calculate_entropy", False))
+        out: dict[str, torch.Tensor] = {}
+        if self.cfg.value_head:
+            vals = self.model(pb)["values"]
+            out["values"] = torch.where(valid, vals[idx.reshape(-1)].reshape(idx.shape), torch.zeros((), device=vals.device))
+            return out
+        h = self.model.forward_hidden(pb)
+        sel = idx[valid]
+        lp, ent = ops.linear_logprob_entropy(h.index_select(0, sel), self.model.output_weight, labels.index_select(0, sel),
+                                             temperature, need_entropy)
+        full = torch.zeros(idx.shape, dtype=torch.float32, device=h.device)
+        out["log_probs"] = full.masked_scatter(valid, lp.float())
+        if ent is not None:
+            out["entropy"] = torch.zeros_like(full).masked_scatter(valid, ent.float())
+        return out
+
+    # ------------------------------------------------------------------ forward / backward
+    def forward_backward_batch(self, data, loss_function: Optional[Callable], forward_only: bool = False) -> dict:
+        batch = data.batch
+        meta = dict(getattr(data, "meta_info", {}) or {})
+        dev = self.device
+        tensors = {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
+        n = tensors["input_ids"].shape[0]
+        seq_lens = tensors["attention_mask"].sum(-1)
+        mb_indices = self._micro_batch_indices(seq_lens, meta)
+        # global normalisers for the loss (identical on all ranks)
+        info: dict[str, Any] = {"dp_size": self.dp_size}
+        if not forward_only and loss_function is not None:
+            mask_key = "response_mask" if "response_mask" in tensors else None
+            ntok = tensors[mask_key].sum().to(torch.float32) if mask_key else seq_lens.sum().to(torch.float32)
+            cnt = torch.stack([ntok, torch.tensor(float(n), device=dev)])
+            if self.world > 1:
+                dist.all_reduce(cnt, group=self.dp_group)
+                if self.sp_size > 1:
+                    pass  # data is replicated inside an sp group; dp_group spans one rank per sp group
+            info["batch_num_tokens"] = cnt[0]
+            info["global_batch_size"] = cnt[1]
+            if not forward_only:
+                self.store.alloc_grads()
+        outputs: dict[str, list[torch.Tensor]] = {}
+        metrics: dict[str, Metric] = {}
+        losses = []
+        self.model.train(not forward_only)
+        for idxs in mb_indices:
+            it = torch.as_tensor(idxs, device=dev)
+            mb = {k: (v.index_select(0, it) if isinstance(v, torch.Tensor) and v.dim() >= 1 and v.shape[0] == n else v)
+                  for k, v in tensors.items()}
+            ctx = torch.no_grad() if forward_only else torch.enable_grad()
+            with ctx:
+                mo = self._forward_micro_batch(mb, meta)
+                if loss_function is not None:
+                    mb_data = dict(mb)
+                    mb_data.update(info)
+                    loss, m = loss_function(model_output=mo, data=mb_data, dp_group=self.dp_group)
+                    if not forward_only:
+                        loss.backward()
+                    losses.append(float(loss.detach()))
+                    for k, v in m.items():
+                        if k in metrics:
+                            metrics[k].append(v)
+                        else:
+                            metrics[k] = v if isinstance(v, Metric) else Metric(AggregationType.MEAN, v)
+            for k, v in mo.items():
+                outputs.setdefault(k, []).append(v.detach())
+        if not forward_only and loss_function is not None:
+            self.store.fold_autograd_grads()
+        model_output = {k: restore_dynamic_batch(torch.cat(v, 0), mb_indices) for k, v in outputs.items()}
+        return {"model_output": model_output, "loss": losses, "metrics": metrics}
+
+    def optimizer_zero_grad(self):
+        self.store.alloc_grads()
+        self.store.zero_grads()
+
+    # ------------------------------------------------------------------ optimizer step
+    @torch.no_grad()
+    def optimizer_step(self) -> float:
+        s = self.store
+        assert s.grad is not None, "optimizer_step without gradients"
+        W = self.fsdp_size
+        # 1. reduce gradients: average over data-parallel ranks, keep only this rank's shard
+        if self.world > 1:
+            if s.grad.is_cuda:
+                if self.grad_shard is None:
+                    self.grad_shard = torch.empty(s.shard_size, dtype=torch.float32, device=self.device)
+                dist.reduce_scatter_tensor(self.grad_shard, s.grad, op=dist.ReduceOp.AVG, group=self.fsdp_group)
+                gshard = self.grad_shard
+                if self.ddp_group is not None:
+                    dist.all_reduce(gshard, op=dist.ReduceOp.AVG, group=self.ddp_group)
+            else:
+                dist.all_reduce(s.grad)
+                s.grad.div_(self.world)
+                gshard = s.grad[s.shard_slice]
+        else:
+            gshard = s.grad
+        # 2. global gradient norm
+        native = gshard.is_cuda and _ext.available()
+        if native:
+            self._sumsq.zero_()
+            _ext.ops().sqnorm_(gshard, self._sumsq)
+            sumsq = self._sumsq
+        else:
+            sumsq = gshard.float().pow(2).sum().reshape(1)
+        if self.world > 1 and W > 1:
+            dist.all_reduce(sumsq, group=self.fsdp_group)
+        self.step_count += 1
+        lr = self.current_lr()
+        if native:
+            _ext.ops().clip_coef_(sumsq, self.clip_grad, self._scalars)
+            _ext.ops().adamw_(self.master, self.exp_avg, self.exp_avg_sq, gshard, s.flat[s.shard_slice] if s.flat.dtype == torch.bfloat16 else None,
+                              lr, self.beta1, self.beta2, self.adam_eps, self.weight_decay, self.step_count, self._scalars)
+            if s.flat.dtype != torch.bfloat16:
+                s.flat[s.shard_slice].copy_(self.master)
+            sc = self._scalars.tolist()
+            grad_norm, skipped = sc[2], sc[1] != 0.0
+        else:
+            grad_norm = float(sumsq.sqrt())
+            skipped = not math.isfinite(grad_norm)
+            if not skipped:
+                coef = min(1.0, self.clip_grad / (grad_norm + 1e-6)) if self.clip_grad > 0 else 1.0
+                _adamw_reference(self.master, self.exp_avg, self.exp_avg_sq, gshard, lr, self.beta1, self.beta2,
+                                 self.adam_eps, self.weight_decay, self.step_count, coef)
+                s.flat[s.shard_slice].copy_(self.master.to(s.flat.dtype))
+        if skipped:
+            self.step_count -= 1
+            print(f"WARN: rank {self.rank} grad_norm is not finite: {grad_norm}; skipping optimizer step")
+        # 3. all-gather the updated working copy
+        if self.world > 1 and W > 1:
+            if s.flat.is_cuda:
+                dist.all_gather_into_tensor(s.flat, s.flat[s.shard_slice].clone(), group=self.fsdp_group)
+            else:
+                parts = [torch.empty(s.shard_size, dtype=s.flat.dtype) for _ in range(W)]
+                dist.all_gather(parts, s.flat[s.shard_slice].clone(), group=self.fsdp_group)
+                s.flat.copy_(torch.cat(parts))
+        s.zero_grads()
+        return grad_norm
+
+    def lr_scheduler_step(self) -> float:
+        self.sched_step += 1
+        return self.current_lr()
+
+    # ------------------------------------------------------------------ weights out
+    def get_per_tensor_param(self, **kwargs):
+        """(HF name, full tensor) pairs. Parameters are resident in full on every rank, so this is a view walk —
+        no collective (the reference all-gathers every DTensor here: fsdp/transformer_impl.py:1033-1039)."""
+        if not self.store.flat.is_cuda and self.device.type == "cuda":
+            self.to("cuda", model=True, optimizer=False, grad=False)
+        return self.model.hf_named_tensors(), None
+
+    # ------------------------------------------------------------------ checkpoint
+    def save_checkpoint(self, local_path, hdfs_path=None, global_step=0, max_ckpt_to_keep=None, **kwargs):
+        self.checkpoint_manager.save_checkpoint(local_path, hdfs_path, global_step, max_ckpt_to_keep)
+
+    def load_checkpoint(self, local_path, hdfs_path=None, del_local_after_load=False, **kwargs):
+        self.checkpoint_manager.load_checkpoint(local_path, hdfs_path, del_local_after_load)
+
+
+@EngineRegistry.register(model_type="value_model", backend=["fsdp", "fsdp2"], device=["cuda", "cpu"])
+class FSDPEngineWithValueHead(FSDPEngine):
+    """Same trunk with a scalar head (critic / reward model): outputs ``values`` instead of log-probs."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self._value_head = True

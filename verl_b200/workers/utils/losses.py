@@ -1,0 +1,98 @@
+"""Loss adapters between engine outputs (per-token log-probs / entropy / values in the response window) and the
+algorithm layer.
+
+Parity target: ``verl/workers/utils/losses.py`` (sft_loss :28, ppo_loss :57, value_loss :158).
+"""
+
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+
+from verl_b200.trainer.ppo import core_algos
+from verl_b200.utils import torch_functional as VF
+from verl_b200.utils.metric import AggregationType, Metric
+
+__all__ = ["ppo_loss", "value_loss", "sft_loss"]
+
+
+def _get(cfg, key, default=None):
+    if cfg is None:
+        return default
+    v = cfg.get(key, default) if hasattr(cfg, "get") else getattr(cfg, key, default)
+    return default if v is None else v
+
+
+class _LossCfgView(dict):
+    """dict view handed to policy-loss functions: actor config + per-call global batch info."""
+
+    def __getattr__(self, k):
+        try:
+            return self[k]
+        except KeyError as e:
+            raise AttributeError(k) from e
+
+
+def ppo_loss(config, model_output: dict, data, dp_group=None) -> tuple[torch.Tensor, dict[str, Any]]:
+    """Policy loss (+ entropy bonus, + KL-to-reference loss) on one micro-batch.
+
+    ``model_output`` holds ``log_probs`` and optionally ``entropy`` as [bs, R]; ``data`` holds ``old_log_probs``,
+    ``advantages``, ``response_mask`` (+ ``ref_log_prob``, ``rollout_is_weights``) and the normalisation info
+    ``dp_size / batch_num_tokens / global_batch_size``.
+    """
+    log_prob = model_output["log_probs"]
+    entropy = model_output.get("entropy")
+    mask = data["response_mask"].to(log_prob.dtype)
+    info = {k: data[k] for k in ("dp_size", "batch_num_tokens", "global_batch_size", "loss_scale_factor") if k in data and data[k] is not None}
+    loss_mode = _get(_get(config, "policy_loss", {}), "loss_mode", "vanilla")
+    agg_mode = _get(config, "loss_agg_mode", "token-mean")
+    view = _LossCfgView({k: _get(config, k) for k in ("clip_ratio", "clip_ratio_low", "clip_ratio_high", "clip_ratio_c",
+                                                       "policy_loss", "tau_pos", "tau_neg")})
+    view["global_batch_info"] = info
+    fn = core_algos.get_policy_loss_fn(loss_mode)
+    pg_loss, pg_metrics = fn(old_log_prob=data["old_log_probs"], log_prob=log_prob, advantages=data["advantages"],
+                             response_mask=mask, loss_agg_mode=agg_mode, config=view,
+                             rollout_is_weights=data.get("rollout_is_weights") if hasattr(data, "get") else None)
+    metrics: dict[str, Any] = {k: Metric(AggregationType.MEAN, v) for k, v in pg_metrics.items()}
+    loss = pg_loss
+    ent_coeff = _get(config, "entropy_coeff", 0.0)
+    if entropy is not None and ent_coeff != 0:
+        ent_loss = core_algos.agg_loss(entropy, mask, agg_mode, **info)
+        loss = loss - ent_coeff * ent_loss
+        metrics["actor/entropy_loss"] = Metric(AggregationType.MEAN, ent_loss.detach().item())
+    if _get(config, "use_kl_loss", False):
+        kld = core_algos.kl_penalty(log_prob, data["ref_log_prob"], _get(config, "kl_loss_type", "low_var_kl"))
+        kl_loss = core_algos.agg_loss(kld, mask, agg_mode, **info)
+        coef = _get(config, "kl_loss_coef", 0.001)
+        loss = loss + coef * kl_loss
+        metrics["actor/kl_loss"] = Metric(AggregationType.MEAN, kl_loss.detach().item())
+        metrics["actor/kl_coef"] = Metric(AggregationType.MEAN, coef)
+    metrics["actor/pg_loss"] = Metric(AggregationType.MEAN, pg_loss.detach().item())
+    return loss, metrics
+
+
+def value_loss(config, model_output: dict, data, dp_group=None):
+    vpreds = model_output["values"]
+    mask = data["response_mask"].to(vpreds.dtype)
+    info = {k: data[k] for k in ("dp_size", "batch_num_tokens", "global_batch_size") if k in data and data[k] is not None}
+    loss, clipfrac = core_algos.compute_value_loss(vpreds, data["returns"], data["values"], mask,
+                                                   _get(config, "cliprange_value", 0.5),
+                                                   _get(config, "loss_agg_mode", "token-mean"), **info)
+    metrics = {
+        "critic/vf_loss": Metric(AggregationType.MEAN, loss.detach().item()),
+        "critic/vf_clipfrac": Metric(AggregationType.MEAN, clipfrac.detach().item()),
+        "critic/vpred_mean": Metric(AggregationType.MEAN, VF.masked_mean(vpreds, mask).detach().item()),
+    }
+    return loss, metrics
+
+
+def sft_loss(config, model_output: dict, data, dp_group=None):
+    """Negative log-likelihood over loss-masked tokens, normalised by the global token count."""
+    log_prob = model_output["log_probs"]
+    mask = data["loss_mask"].to(log_prob.dtype)
+    n = data.get("batch_num_tokens") if hasattr(data, "get") else None
+    dp = data.get("dp_size", 1) if hasattr(data, "get") else 1
+    denom = n if n is not None else mask.sum().clamp(min=1)
+    loss = -(log_prob * mask).sum() / denom * dp
+    return loss, {"sft/loss": Metric(AggregationType.MEAN, loss.detach().item() / dp)}
