@@ -24,6 +24,11 @@ int vb_adamw(float* p32, float* m, float* v, const void* g, int g_is_bf16, void*
 int vb_sqnorm(const void* g, int is_bf16, long n, float* out, cudaStream_t st);
 int vb_clip_coef(const float* sumsq, float max_norm, float* scalars, cudaStream_t st);
 
+int vb_kv_cache_write(const void* k, const void* v, long ld, const long* slots, void* cache, int n_kv_heads, long T,
+                      cudaStream_t st);
+int vb_sample(const void* logits, int is_bf16, long ld, int B, int V, float temperature, int top_k, float top_p,
+              const long* rng, const int* row_ids, long* out_token, float* out_logprob, cudaStream_t st);
+
 long vb_lmhead_scratch_floats(int M, int V);
 int vb_lmhead_logprob_fwd(const void* h, const void* W, const long* labels, int M, int V, int K, int ldh, int ldw,
                           float inv_temp, float* scratch, float* logp, float* ent, float* lse, int* err_word,

@@ -198,7 +198,7 @@ int vb_sched_step(void* h, int64_t* out_ids, int* out_slots, int* out_lens, int6
     s->free_slots.push_back(victim.slot);
     victim.slot = -1;
     victim.state = WAITING;
-    victim.prompt_len = victim.num_tokens;  // recompute prompt + generated so far
+    victim.prompt_len = victim.num_tokens + 1;  // recompute prompt + every token sampled so far (the last one has no KV yet)
     victim.num_tokens = 0;
     victim.num_preempted++;
     s->num_preemptions++;

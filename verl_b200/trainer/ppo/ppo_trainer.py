@@ -1,0 +1,445 @@
+"""Synchronous PPO / GRPO trainer (single-controller dataflow).
+
+One step: generate → reward → (balance) → old log-prob → ref log-prob → values → advantages (on the controller) →
+update critic → update actor → (validate / checkpoint) → weight hand-off → metrics. Parity target:
+``verl/trainer/ppo/ray_trainer.py`` (apply_kl_penalty :78, compute_response_mask :120, compute_advantage :187,
+RayPPOTrainer.init_workers :772, _validate :596, _save_checkpoint :983, _load_checkpoint :1052, fit :1405-1823).
+"""
+
+from __future__ import annotations
+
+import os
+import time
+import uuid
+from collections import defaultdict
+from contextlib import contextmanager
+from typing import Optional
+
+import numpy as np
+import torch
+
+from verl_b200.protocol import DataProto, collate_fn
+from verl_b200.single_controller.base import ClassWithInitArgs, ResourcePool
+from verl_b200.trainer.ppo import core_algos
+from verl_b200.trainer.ppo.core_algos import AdvantageEstimator, agg_loss
+from verl_b200.trainer.ppo.metric_utils import (compute_data_metrics, compute_throughout_metrics, compute_timing_metrics,
+                                                compute_variance_proxy_metrics, process_validation_metrics, reduce_metrics)
+from verl_b200.trainer.ppo.reward import compute_reward, load_reward_manager
+from verl_b200.utils import torch_functional as VF
+from verl_b200.utils.checkpoint.checkpoint_manager import find_latest_ckpt_path, should_save_ckpt_esi
+from verl_b200.utils.seqlen_balancing import calculate_workload, get_seqlen_balanced_partitions, log_seqlen_unbalance
+from verl_b200.utils.tracking import Tracking, ValidationGenerationsLogger
+
+__all__ = ["PPOTrainer", "RayPPOTrainer", "apply_kl_penalty", "compute_response_mask", "compute_advantage", "marked_timer"]
+
+
+@contextmanager
+def marked_timer(name: str, timing_raw: dict, **kwargs):
+    """Accumulate wall time of a section into ``timing_raw[name]`` (and emit an NVTX range when CUDA is present)."""
+    use_nvtx = torch.cuda.is_available()
+    if use_nvtx:
+        torch.cuda.nvtx.range_push(name)
+    t0 = time.perf_counter()
+    try:
+        yield
+    finally:
+        timing_raw[name] = timing_raw.get(name, 0.0) + time.perf_counter() - t0
+        if use_nvtx:
+            torch.cuda.nvtx.range_pop()
+
+
+def apply_kl_penalty(data: DataProto, kl_ctrl, kl_penalty: str = "kl"):
+    """token_level_rewards = token_level_scores − β·KL(π_old ‖ π_ref); updates the adaptive controller."""
+    mask = data.batch["response_mask"]
+    kld = core_algos.kl_penalty(data.batch["old_log_probs"], data.batch["ref_log_prob"], kl_penalty=kl_penalty) * mask
+    beta = kl_ctrl.value
+    data.batch["token_level_rewards"] = data.batch["token_level_scores"] - beta * kld
+    current_kl = torch.mean(VF.masked_mean(kld, mask=mask, axis=-1), dim=0).item()
+    kl_ctrl.update(current_kl=current_kl, n_steps=data.batch["responses"].shape[0])
+    return data, {"actor/reward_kl_penalty": current_kl, "actor/reward_kl_penalty_coeff": beta}
+
+
+def compute_response_mask(data: DataProto) -> torch.Tensor:
+    R = data.batch["responses"].size(1)
+    return data.batch["attention_mask"][:, -R:]
+
+
+def compute_advantage(data: DataProto, adv_estimator, gamma: float = 1.0, lam: float = 1.0, num_repeat: int = 1,
+                      norm_adv_by_std_in_grpo: bool = True, config=None) -> DataProto:
+    if "response_mask" not in data.batch.keys():
+        data.batch["response_mask"] = compute_response_mask(data)
+    name = adv_estimator.value if isinstance(adv_estimator, AdvantageEstimator) else adv_estimator
+    fn = core_algos.get_adv_estimator_fn(name)
+    b = data.batch
+    kwargs = dict(token_level_rewards=b["token_level_rewards"], response_mask=b["response_mask"], config=config)
+    if name == "gae":
+        kwargs.update(values=b["values"], gamma=gamma, lam=lam)
+    else:
+        if "uid" in data.non_tensor_batch:
+            kwargs["index"] = data.non_tensor_batch["uid"]
+        if name in ("grpo", "grpo_vectorized", "gdpo", "grpo_passk"):
+            kwargs["norm_adv_by_std_in_grpo"] = norm_adv_by_std_in_grpo
+        if name == "gdpo":
+            kwargs.update(non_tensor_batch=data.non_tensor_batch, batch=b)
+        if name == "remax":
+            kwargs["reward_baselines"] = b["reward_baselines"]
+        if name == "reinforce_plus_plus":
+            kwargs["gamma"] = gamma
+        if name in ("optimal_token_baseline", "tir_optimal_token_baseline"):
+            kwargs.update(old_log_probs=b["old_log_probs"], sum_pi_squared=b["sum_pi_squared"],
+                          rollout_is_weights=b.get("rollout_is_weights"))
+    adv, ret = fn(**kwargs)
+    data.batch["advantages"], data.batch["returns"] = adv, ret
+    return data
+
+
+def _g(cfg, key, default=None):
+    cur = cfg
+    for part in key.split("."):
+        if cur is None:
+            return default
+        cur = cur.get(part) if hasattr(cur, "get") else getattr(cur, part, None)
+    return default if cur is None else cur
+
+
+class PPOTrainer:
+    """Controller-side trainer. With the ``spmd`` worker backend every rank runs this same object (torchrun); with the
+    ``process`` backend one driver owns spawned workers."""
+
+    def __init__(self, config, tokenizer=None, processor=None, reward_fn=None, val_reward_fn=None, train_dataset=None,
+                 val_dataset=None, collate=None, train_sampler=None, device_name: Optional[str] = None):
+        self.config = config
+        self.tokenizer = tokenizer
+        self.processor = processor
+        self.device_name = device_name or _g(config, "trainer.device", "cuda")
+        self.reward_fn = reward_fn
+        self.val_reward_fn = val_reward_fn
+        self.collate = collate or collate_fn
+        adv = _g(config, "algorithm.adv_estimator", "gae")
+        self.use_critic = _g(config, "critic.enable", None)
+        if self.use_critic is None:
+            self.use_critic = adv == "gae"
+        self.use_reference_policy = bool(_g(config, "algorithm.use_kl_in_reward", False)) or bool(_g(config, "actor_rollout_ref.actor.use_kl_loss", False))
+        self.kl_ctrl_in_reward = core_algos.get_kl_controller(config.algorithm.kl_ctrl) if _g(config, "algorithm.use_kl_in_reward", False) else None
+        self.n_gpus = int(_g(config, "trainer.n_gpus_per_node", 1)) * int(_g(config, "trainer.nnodes", 1))
+        self.global_steps = 0
+        self.validation_generations_logger = ValidationGenerationsLogger(_g(config, "trainer.project_name"), _g(config, "trainer.experiment_name"))
+        self._create_dataloader(train_dataset, val_dataset, train_sampler)
+
+    # ------------------------------------------------------------------ data
+    def _create_dataloader(self, train_dataset, val_dataset, train_sampler):
+        from torch.utils.data import DataLoader
+
+        from verl_b200.utils.dataset import create_rl_dataset, create_rl_sampler
+
+        dc = self.config.data
+        if train_dataset is None:
+            train_dataset = create_rl_dataset(dc.get("train_files"), dc, self.tokenizer, self.processor, is_train=True)
+        if val_dataset is None and (dc.get("val_files") or _g(dc, "synthetic.enable", False)):
+            val_dataset = create_rl_dataset(dc.get("val_files"), dc, self.tokenizer, self.processor, is_train=False)
+        self.train_dataset, self.val_dataset = train_dataset, val_dataset
+        if train_sampler is None:
+            train_sampler = create_rl_sampler(dc, train_dataset)
+        try:
+            from torchdata.stateful_dataloader import StatefulDataLoader as Loader
+        except Exception:  # noqa: BLE001
+            Loader = DataLoader
+        self.train_dataloader = Loader(train_dataset, batch_size=int(dc.get("gen_batch_size", dc.train_batch_size)), num_workers=int(dc.get("dataloader_num_workers", 0)),
+                                       drop_last=True, collate_fn=self.collate, sampler=train_sampler)
+        self.val_dataloader = None
+        if val_dataset is not None:
+            vbs = dc.get("val_batch_size") or len(val_dataset)
+            self.val_dataloader = Loader(val_dataset, batch_size=int(vbs), num_workers=0, shuffle=False, drop_last=False, collate_fn=self.collate)
+        total = len(self.train_dataloader) * int(_g(self.config, "trainer.total_epochs", 1))
+        if _g(self.config, "trainer.total_training_steps") is not None:
+            total = int(self.config.trainer.total_training_steps)
+        self.total_training_steps = total
+        self.config.actor_rollout_ref.actor.optim["total_training_steps"] = total
+        if "critic" in self.config and self.config.critic.get("optim") is not None:
+            self.config.critic.optim["total_training_steps"] = total
+
+    # ------------------------------------------------------------------ workers
+    def init_workers(self):
+        from verl_b200.workers.engine_workers import ActorRolloutRefWorker, CriticWorker
+
+        backend = _g(self.config, "trainer.worker_backend", "spmd")
+        role = "actor_rollout_ref" if self.use_reference_policy else "actor_rollout"
+        arr = ClassWithInitArgs(ActorRolloutRefWorker, config=self.config.actor_rollout_ref, role=role)
+        crit = ClassWithInitArgs(CriticWorker, config=self.config.critic) if self.use_critic else None
+        if backend == "spmd":
+            from verl_b200.single_controller.spmd import SPMDWorkerGroup, init_spmd_process_group
+
+            init_spmd_process_group(int(_g(self.config, "actor_rollout_ref.nccl_timeout", 600)))
+            self.actor_rollout_wg = SPMDWorkerGroup(cls_with_init_args=arr)
+            self.critic_wg = SPMDWorkerGroup(cls_with_init_args=crit) if crit is not None else None
+        elif backend == "process":
+            from verl_b200.single_controller.process import ProcessWorkerGroup, create_colocated_worker_cls
+
+            pool = ResourcePool([int(self.config.trainer.n_gpus_per_node)] * int(self.config.trainer.nnodes))
+            class_dict = {"actor_rollout": arr}
+            if crit is not None:
+                class_dict["critic"] = crit
+            wg = ProcessWorkerGroup(pool, create_colocated_worker_cls(class_dict), use_gpu=self.device_name == "cuda")
+            views = wg.spawn(set(class_dict))
+            self._root_wg = wg
+            self.actor_rollout_wg = views["actor_rollout"]
+            self.critic_wg = views.get("critic")
+            wg.start_worker_aliveness_check(1.0)
+        else:
+            raise ValueError(f"unknown trainer.worker_backend {backend}")
+        self.ref_policy_wg = self.actor_rollout_wg
+        if self.critic_wg is not None:
+            self.critic_wg.init_model()
+        self.actor_rollout_wg.init_model()
+        self.actor_rollout_wg.update_weights()
+
+    # ------------------------------------------------------------------ checkpoint
+    def _save_checkpoint(self):
+        root = os.path.expanduser(self.config.trainer.default_local_dir)
+        step_dir = os.path.join(root, f"global_step_{self.global_steps}")
+        print(f"local_global_step_folder: {step_dir}")
+        self.actor_rollout_wg.save_checkpoint(os.path.join(step_dir, "actor"), None, self.global_steps, _g(self.config, "trainer.max_actor_ckpt_to_keep"))
+        if self.use_critic:
+            self.critic_wg.save_checkpoint(os.path.join(step_dir, "critic"), None, self.global_steps, _g(self.config, "trainer.max_critic_ckpt_to_keep"))
+        rank = int(os.environ.get("RANK", "0")) if _g(self.config, "trainer.worker_backend", "spmd") == "spmd" else 0
+        if rank == 0:
+            os.makedirs(step_dir, exist_ok=True)
+            if hasattr(self.train_dataloader, "state_dict"):
+                torch.save(self.train_dataloader.state_dict(), os.path.join(step_dir, "data.pt"))
+            tmp = os.path.join(root, "latest_checkpointed_iteration.txt.tmp")
+            with open(tmp, "w") as f:
+                f.write(str(self.global_steps))
+            os.replace(tmp, os.path.join(root, "latest_checkpointed_iteration.txt"))
+
+    def _load_checkpoint(self) -> int:
+        mode = _g(self.config, "trainer.resume_mode", "auto")
+        if mode == "disable":
+            return 0
+        root = os.path.expanduser(self.config.trainer.default_local_dir)
+        if mode == "resume_path":
+            step_dir = _g(self.config, "trainer.resume_from_path")
+            assert step_dir and "global_step_" in step_dir, "resume_from_path must point at a global_step_N folder"
+        else:
+            step_dir = find_latest_ckpt_path(root)
+        if step_dir is None:
+            print("Training from scratch")
+            return 0
+        self.global_steps = int(str(step_dir).rstrip("/").split("global_step_")[-1])
+        print(f"Resuming from {step_dir} (global step {self.global_steps})")
+        self.actor_rollout_wg.load_checkpoint(os.path.join(step_dir, "actor"), None, bool(_g(self.config, "trainer.del_local_ckpt_after_load", False)))
+        if self.use_critic:
+            self.critic_wg.load_checkpoint(os.path.join(step_dir, "critic"), None, False)
+        data_pt = os.path.join(step_dir, "data.pt")
+        if os.path.exists(data_pt) and hasattr(self.train_dataloader, "load_state_dict"):
+            self.train_dataloader.load_state_dict(torch.load(data_pt, weights_only=False))
+        return self.global_steps
+
+    # ------------------------------------------------------------------ helpers
+    def _balance_batch(self, batch: DataProto, metrics: dict, logging_prefix: str = "global_seqlen"):
+        """Reorder samples so that each data-parallel rank's contiguous chunk carries an equal attention+MLP workload."""
+        lens = batch.batch["attention_mask"].view(len(batch), -1).sum(-1)
+        world = self.actor_rollout_wg.world_size
+        if world <= 1 or len(batch) % world != 0:
+            return
+        parts = get_seqlen_balanced_partitions(calculate_workload(lens).tolist(), world, equal_size=True)
+        for p in parts:   # shortest-first inside a rank keeps micro-batches homogeneous
+            p.sort(key=lambda i: int(lens[i]))
+        batch.reorder(torch.tensor([i for p in parts for i in p]))
+        metrics.update(log_seqlen_unbalance(lens.tolist(), parts, logging_prefix))
+
+    def _gen_meta(self, validate: bool = False) -> dict:
+        tk = self.tokenizer
+        return {"eos_token_id": getattr(tk, "eos_token_id", None) if tk is not None else _g(self.config, "data.eos_token_id"),
+                "pad_token_id": (getattr(tk, "pad_token_id", 0) if tk is not None else 0) or 0,
+                "do_sample": not validate or bool(_g(self.config, "actor_rollout_ref.rollout.val_kwargs.do_sample", False)),
+                "validate": validate, "global_steps": self.global_steps,
+                "response_length": int(self.config.data.max_response_length)}
+
+    def _validate(self) -> dict:
+        if self.val_dataloader is None or self.val_reward_fn is None:
+            return {}
+        scores, sources, uids = [], [], []
+        extra_all = defaultdict(list)
+        n = int(_g(self.config, "actor_rollout_ref.rollout.val_kwargs.n", 1))
+        for test_data in self.val_dataloader:
+            tb = DataProto.from_single_dict(test_data)
+            tb.non_tensor_batch["uid"] = np.array([str(uuid.uuid4()) for _ in range(len(tb))], dtype=object)
+            tb = tb.repeat(n, interleave=True)
+            gen = tb.select(batch_keys=["input_ids", "attention_mask", "position_ids"], non_tensor_batch_keys=[])
+            gen.meta_info = self._gen_meta(validate=True)
+            gen, pad = _pad_to(gen, self.actor_rollout_wg.world_size)
+            out = self.actor_rollout_wg.generate_sequences(gen)
+            out = out[: len(out) - pad] if pad else out
+            tb = tb.union(out.select(batch_keys=["prompts", "responses", "response_mask"], non_tensor_batch_keys=[]))
+            tb.batch["attention_mask"] = out.batch["attention_mask"]
+            tb.batch["input_ids"] = out.batch["input_ids"]
+            r, extra = compute_reward(tb, self.val_reward_fn)
+            scores.extend(r.sum(-1).tolist())
+            for k, v in extra.items():
+                extra_all[k].extend(v)
+            sources.extend(tb.non_tensor_batch.get("data_source", np.array(["unknown"] * len(tb), dtype=object)).tolist())
+            uids.extend(tb.non_tensor_batch["uid"].tolist())
+        infos = {"reward": scores, **{k: v for k, v in extra_all.items() if len(v) == len(scores)}}
+        res = process_validation_metrics(sources, uids, infos)
+        metrics = {}
+        for src, var2m in res.items():
+            core = "acc" if "acc" in var2m else "reward"
+            for var, m2v in var2m.items():
+                n_max = max(int(name.split("@")[-1].split("/")[0]) for name in m2v)
+                for name, val in m2v.items():
+                    sec = "val-core" if var == core and any(name.startswith(p) for p in ("mean", "maj", "best")) and f"@{n_max}" in name else "val-aux"
+                    metrics[f"{sec}/{src}/{var}/{name}"] = val
+        return metrics
+
+
+def _pad_to(data: DataProto, divisor: int):
+    from verl_b200.protocol import pad_dataproto_to_divisor
+
+    return pad_dataproto_to_divisor(data, divisor)
+
+
+def _train_step(self: PPOTrainer, batch_dict: dict) -> dict:
+    """One full RL step on a batch of prompts; returns the step's metrics."""
+    cfg = self.config
+    metrics: dict = {}
+    timing_raw: dict = {}
+    batch = DataProto.from_single_dict(batch_dict)
+    n = int(cfg.actor_rollout_ref.rollout.n)
+    batch.non_tensor_batch["uid"] = np.array([str(uuid.uuid4()) for _ in range(len(batch))], dtype=object)
+    with marked_timer("step", timing_raw):
+        gen_batch = batch.select(batch_keys=["input_ids", "attention_mask", "position_ids"], non_tensor_batch_keys=[])
+        gen_batch.meta_info = self._gen_meta()
+        gen_batch = gen_batch.repeat(repeat_times=n, interleave=True)
+        with marked_timer("gen", timing_raw):
+            gen_out = self.actor_rollout_wg.generate_sequences(gen_batch)
+            timing_raw.update({f"gen/{k}": float(np.max(v)) if isinstance(v, list) else v
+                               for k, v in (gen_out.meta_info.pop("timing", {}) or {}).items()})
+            ro_metrics = gen_out.meta_info.pop("metrics", None)
+            if ro_metrics:
+                metrics.update(reduce_metrics(ro_metrics if isinstance(ro_metrics, dict) else {}))
+        if cfg.algorithm.adv_estimator == "remax":
+            with marked_timer("gen_max", timing_raw):
+                base = batch.select(batch_keys=["input_ids", "attention_mask", "position_ids"], non_tensor_batch_keys=[])
+                base.meta_info = {**self._gen_meta(), "do_sample": False}
+                base_out = self.actor_rollout_wg.generate_sequences(base)
+                tmp = batch.union(base_out.select(batch_keys=["prompts", "responses", "input_ids", "attention_mask", "position_ids", "response_mask"]))
+                rb, _ = compute_reward(tmp, self.reward_fn)
+                batch.pop(batch_keys=[k for k in base_out.batch.keys() if k in batch.batch.keys() and k not in ("input_ids", "attention_mask", "position_ids")])
+                batch.batch["reward_baselines"] = rb.sum(-1)
+        batch = batch.repeat(repeat_times=n, interleave=True)
+        batch.pop(batch_keys=["input_ids", "attention_mask", "position_ids"])
+        batch = batch.union(gen_out)
+        if "response_mask" not in batch.batch.keys():
+            batch.batch["response_mask"] = compute_response_mask(batch)
+        if _g(cfg, "trainer.balance_batch", True):
+            self._balance_batch(batch, metrics)
+        batch.meta_info["global_token_num"] = torch.sum(batch.batch["attention_mask"], dim=-1).tolist()
+        batch.meta_info["temperature"] = float(cfg.actor_rollout_ref.rollout.temperature)
+        with marked_timer("reward", timing_raw):
+            reward_tensor, reward_extra = compute_reward(batch, self.reward_fn)
+        rc = cfg.algorithm.get("rollout_correction") or {}
+        bypass = bool(rc.get("bypass_mode", False))
+        if bypass:
+            from verl_b200.trainer.ppo.rollout_corr_helper import apply_bypass_mode
+
+            apply_bypass_mode(batch, rc, cfg.actor_rollout_ref.actor.policy_loss)
+        else:
+            with marked_timer("old_log_prob", timing_raw):
+                old = self.actor_rollout_wg.compute_log_prob(batch)
+                ent = old.batch.pop("entropys") if "entropys" in old.batch.keys() else None
+                if ent is not None:
+                    ea = agg_loss(ent, batch.batch["response_mask"].float(), cfg.actor_rollout_ref.actor.get("loss_agg_mode", "token-mean"))
+                    metrics["actor/entropy"] = ea.item()
+                batch = batch.union(old)
+                if "rollout_log_probs" in batch.batch.keys():
+                    from verl_b200.utils.debug.metrics import calculate_debug_metrics
+
+                    metrics.update(calculate_debug_metrics(batch))
+        if self.use_reference_policy:
+            with marked_timer("ref", timing_raw):
+                batch = batch.union(self.ref_policy_wg.compute_ref_log_prob(batch))
+        if self.use_critic:
+            with marked_timer("values", timing_raw):
+                batch = batch.union(self.critic_wg.compute_values(batch))
+        with marked_timer("adv", timing_raw):
+            batch.batch["token_level_scores"] = reward_tensor
+            if reward_extra:
+                batch.non_tensor_batch.update({k: np.array(v, dtype=object) for k, v in reward_extra.items() if len(v) == len(batch)})
+            if cfg.algorithm.get("use_kl_in_reward", False):
+                batch, kl_m = apply_kl_penalty(batch, self.kl_ctrl_in_reward, cfg.algorithm.kl_penalty)
+                metrics.update(kl_m)
+            else:
+                batch.batch["token_level_rewards"] = batch.batch["token_level_scores"]
+            if not bypass and (rc.get("rollout_is") or rc.get("rollout_rs")) and "rollout_log_probs" in batch.batch.keys():
+                from verl_b200.trainer.ppo.rollout_corr_helper import compute_rollout_correction_and_add_to_batch
+
+                batch, is_m = compute_rollout_correction_and_add_to_batch(batch, rc)
+                metrics.update(is_m)
+            batch = compute_advantage(batch, cfg.algorithm.adv_estimator, gamma=cfg.algorithm.gamma, lam=cfg.algorithm.lam, num_repeat=n,
+                                      norm_adv_by_std_in_grpo=cfg.algorithm.get("norm_adv_by_std_in_grpo", True), config=cfg.algorithm)
+            if cfg.algorithm.get("use_pf_ppo", False):
+                batch = core_algos.compute_pf_ppo_reweight_data(batch, cfg.algorithm.pf_ppo.reweight_method, cfg.algorithm.pf_ppo.weight_pow)
+        if self.use_critic:
+            with marked_timer("update_critic", timing_raw):
+                co = self.critic_wg.update_critic(batch)
+            metrics.update(reduce_metrics(co.meta_info["metrics"]))
+        if int(_g(cfg, "trainer.critic_warmup", 0)) <= self.global_steps:
+            with marked_timer("update_actor", timing_raw):
+                batch.meta_info["multi_turn"] = bool(_g(cfg, "actor_rollout_ref.rollout.multi_turn.enable", False))
+                ao = self.actor_rollout_wg.update_actor(batch)
+            metrics.update(reduce_metrics(ao.meta_info["metrics"]))
+        with marked_timer("update_weights", timing_raw):
+            self.actor_rollout_wg.update_weights()
+    metrics.update(compute_data_metrics(batch=batch, use_critic=self.use_critic))
+    metrics.update(compute_timing_metrics(batch=batch, timing_raw=timing_raw))
+    metrics.update(compute_throughout_metrics(batch=batch, timing_raw=timing_raw, n_gpus=max(1, self.actor_rollout_wg.world_size)))
+    metrics.update(compute_variance_proxy_metrics(batch, metrics.get("actor/grad_norm")))
+    self._last_batch = batch
+    return metrics
+
+
+def _fit(self: PPOTrainer):
+    cfg = self.config
+    is_main = int(os.environ.get("RANK", "0")) == 0 or _g(cfg, "trainer.worker_backend", "spmd") != "spmd"
+    logger = Tracking(cfg.trainer.project_name, cfg.trainer.experiment_name, cfg.trainer.logger if is_main else [],
+                      config=dict(cfg)) if is_main else None
+    self.global_steps = 0
+    self._load_checkpoint()
+    if self.val_reward_fn is not None and _g(cfg, "trainer.val_before_train", True):
+        val = self._validate()
+        if val and logger:
+            logger.log(data=val, step=self.global_steps)
+        if _g(cfg, "trainer.val_only", False):
+            return
+    self.global_steps += 1
+    last_val = None
+    max_step_time = 0.0
+    for epoch in range(int(cfg.trainer.total_epochs)):
+        for batch_dict in self.train_dataloader:
+            t0 = time.perf_counter()
+            is_last = self.global_steps >= self.total_training_steps
+            metrics = self.step(batch_dict)
+            max_step_time = max(max_step_time, time.perf_counter() - t0)
+            test_freq = int(_g(cfg, "trainer.test_freq", -1))
+            if self.val_reward_fn is not None and test_freq > 0 and (is_last or self.global_steps % test_freq == 0):
+                last_val = self._validate()
+                metrics.update(last_val)
+            save_freq = int(_g(cfg, "trainer.save_freq", -1))
+            esi = should_save_ckpt_esi(max_step_time, redundant_time=float(_g(cfg, "trainer.esi_redundant_time", 0)))
+            if save_freq > 0 and (is_last or self.global_steps % save_freq == 0 or esi):
+                if esi:
+                    print("Force saving checkpoint: the announced capacity expiry is near.")
+                self._save_checkpoint()
+            metrics.update({"training/global_step": self.global_steps, "training/epoch": epoch})
+            if logger:
+                logger.log(data=metrics, step=self.global_steps)
+            self.global_steps += 1
+            if is_last:
+                if last_val:
+                    print(f"Final validation metrics: {last_val}")
+                return
+
+
+PPOTrainer.step = _train_step
+PPOTrainer.fit = _fit
+RayPPOTrainer = PPOTrainer

@@ -1,0 +1,137 @@
+"""Prompt datasets for RL training.
+
+* :class:`RLHFDataset` — parquet/json rows with a chat ``prompt`` column, tokenised with the model's chat template,
+  left-padded to ``max_prompt_length`` (reference: ``verl/utils/dataset/rl_dataset.py:72-570``).
+* :class:`SyntheticPromptDataset` — random token-id prompts of a given length range (benchmark / plumbing configs).
+"""
+
+from __future__ import annotations
+
+import copy
+import os
+from typing import Optional
+
+import numpy as np
+import torch
+from torch.utils.data import Dataset, RandomSampler, SequentialSampler
+
+from verl_b200.protocol import collate_fn  # noqa: F401
+from verl_b200.utils import torch_functional as VF
+
+__all__ = ["RLHFDataset", "SyntheticPromptDataset", "collate_fn", "create_rl_dataset", "create_rl_sampler"]
+
+
+def _g(cfg, key, default=None):
+    v = cfg.get(key, default) if hasattr(cfg, "get") else getattr(cfg, key, default)
+    return default if v is None else v
+
+
+class SyntheticPromptDataset(Dataset):
+    def __init__(self, num_prompts: int, min_len: int, max_len: int, id_low: int, id_high: int, max_prompt_length: int,
+                 pad_token_id: int = 0, seed: int = 0, data_source: str = "synthetic/mod7"):
+        g = torch.Generator().manual_seed(seed)
+        self.lens = torch.randint(min_len, max_len + 1, (num_prompts,), generator=g)
+        self.ids = [torch.randint(id_low, id_high, (int(n),), generator=g) for n in self.lens]
+        self.max_prompt_length = max_prompt_length
+        self.pad = pad_token_id
+        self.data_source = data_source
+
+    def __len__(self):
+        return len(self.ids)
+
+    def __getitem__(self, i):
+        ids = self.ids[i]
+        P = self.max_prompt_length
+        n = ids.numel()
+        input_ids = torch.full((P,), self.pad, dtype=torch.int64)
+        att = torch.zeros(P, dtype=torch.int64)
+        input_ids[P - n:] = ids
+        att[P - n:] = 1
+        return {"input_ids": input_ids, "attention_mask": att, "position_ids": VF.compute_position_id_with_mask(att),
+                "data_source": self.data_source, "reward_model": {"style": "rule", "ground_truth": int(ids.sum()) % 7},
+                "index": i, "extra_info": {"index": i}}
+
+
+class RLHFDataset(Dataset):
+    def __init__(self, data_files, tokenizer, config, processor=None, max_samples: int = -1):
+        import pandas as pd
+
+        self.tokenizer = tokenizer
+        self.config = config
+        files = [data_files] if isinstance(data_files, str) else list(data_files)
+        frames = []
+        for f in files:
+            f = os.path.expanduser(f)
+            frames.append(pd.read_parquet(f) if f.endswith(".parquet") else pd.read_json(f, lines=f.endswith(".jsonl")))
+        self.df = pd.concat(frames, ignore_index=True)
+        if max_samples and max_samples > 0:
+            self.df = self.df.iloc[:max_samples]
+        self.prompt_key = _g(config, "prompt_key", "prompt")
+        self.max_prompt_length = int(_g(config, "max_prompt_length", 1024))
+        self.truncation = _g(config, "truncation", "error")
+        self.return_raw_chat = bool(_g(config, "return_raw_chat", True))
+        self.return_full_prompt = bool(_g(config, "return_full_prompt", False))
+        self.apply_chat_template_kwargs = dict(_g(config, "apply_chat_template_kwargs", {}) or {})
+        if bool(_g(config, "filter_overlong_prompts", False)):
+            keep = [len(self._tokenize(self._messages(row))) <= self.max_prompt_length for _, row in self.df.iterrows()]
+            self.df = self.df[np.asarray(keep)].reset_index(drop=True)
+
+    def _messages(self, row):
+        msgs = row[self.prompt_key]
+        if isinstance(msgs, np.ndarray):
+            msgs = msgs.tolist()
+        if isinstance(msgs, str):
+            msgs = [{"role": "user", "content": msgs}]
+        return [dict(m) for m in msgs]
+
+    def _tokenize(self, messages):
+        if getattr(self.tokenizer, "chat_template", None):
+            text = self.tokenizer.apply_chat_template(messages, add_generation_prompt=True, tokenize=False, **self.apply_chat_template_kwargs)
+        else:
+            text = "\n".join(m["content"] for m in messages)
+        return self.tokenizer(text, add_special_tokens=False)["input_ids"]
+
+    def __len__(self):
+        return len(self.df)
+
+    def __getitem__(self, i):
+        row = self.df.iloc[i].to_dict()
+        messages = self._messages(row)
+        ids = torch.tensor(self._tokenize(messages), dtype=torch.int64)[None]
+        att = torch.ones_like(ids)
+        pad = self.tokenizer.pad_token_id if self.tokenizer.pad_token_id is not None else 0
+        ids, att = VF.postprocess_data(ids, att, self.max_prompt_length, pad, left_pad=True, truncation=self.truncation)
+        out = {k: v for k, v in row.items() if k != self.prompt_key}
+        out.update({"input_ids": ids[0], "attention_mask": att[0], "position_ids": VF.compute_position_id_with_mask(att[0])})
+        if self.return_raw_chat:
+            out["raw_prompt"] = messages
+        extra = out.get("extra_info") or {}
+        out["index"] = extra.get("index", i) if isinstance(extra, dict) else i
+        out.setdefault("data_source", "unknown")
+        return out
+
+    def resume_dataset_state(self):
+        pass
+
+
+def create_rl_dataset(data_files, data_config, tokenizer, processor=None, is_train: bool = True, max_samples: int = -1):
+    syn = _g(data_config, "synthetic", None)
+    if syn is not None and _g(syn, "enable", False):
+        return SyntheticPromptDataset(int(_g(syn, "num_prompts", 4096)), int(_g(syn, "min_prompt_length", 16)), int(_g(syn, "max_prompt_length", 32)),
+                                      int(_g(syn, "id_low", 10)), int(_g(syn, "id_high", 2048)), int(_g(data_config, "max_prompt_length", 512)),
+                                      seed=int(_g(data_config, "seed", 0)) + (0 if is_train else 1))
+    custom = _g(data_config, "custom_cls", None)
+    if custom is not None and _g(custom, "path", None):
+        from verl_b200.utils.import_utils import load_extern_type
+
+        cls = load_extern_type(custom["path"], custom["name"])
+        return cls(data_files=data_files, tokenizer=tokenizer, config=data_config, processor=processor)
+    return RLHFDataset(data_files, tokenizer, data_config, processor, max_samples)
+
+
+def create_rl_sampler(data_config, dataset):
+    if bool(_g(data_config, "shuffle", True)):
+        g = torch.Generator()
+        g.manual_seed(int(_g(data_config, "seed", 1)))
+        return RandomSampler(dataset, generator=g)
+    return SequentialSampler(dataset)

@@ -1,0 +1,17 @@
+"""Rule-based scorers selected by ``data_source`` (reference: ``verl/utils/reward_score/__init__.py:19``)."""
+
+from __future__ import annotations
+
+from . import gsm8k, math_reward, synthetic
+
+__all__ = ["default_compute_score"]
+
+
+def default_compute_score(data_source: str, solution_str: str, ground_truth, extra_info=None, **kwargs):
+    if data_source in ("openai/gsm8k", "gsm8k"):
+        return gsm8k.compute_score(solution_str, ground_truth)
+    if data_source in ("lighteval/MATH", "DigitalLearningGmbH/MATH-lighteval", "HuggingFaceH4/MATH-500", "math", "math_dapo") or str(data_source).startswith("aime"):
+        return math_reward.compute_score(solution_str, ground_truth)
+    if data_source in ("synthetic/mod7", "mod7"):
+        return synthetic.compute_score_from_text(solution_str, ground_truth)
+    raise NotImplementedError(f"Reward function is not implemented for data_source={data_source!r}")

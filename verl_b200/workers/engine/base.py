@@ -182,6 +182,8 @@ class EngineRegistry:
     def new(cls, model_type: str, backend: str, *args, **kwargs) -> BaseEngine:
         # importing the implementations registers them
         import verl_b200.workers.engine.fsdp  # noqa: F401
-        import verl_b200.workers.engine.megatron  # noqa: F401
+
+        if backend == "megatron":
+            import verl_b200.workers.engine.megatron  # noqa: F401
 
         return cls.get_engine_cls(model_type, backend)(*args, **kwargs)

@@ -1,0 +1,391 @@
+"""Role workers that sit between the trainer and the engines.
+
+* :class:`TrainingWorker` — one trainable or frozen model behind the engine contract (mini-batch loop, metrics).
+* :class:`ActorRolloutRefWorker` — the colocated "hybrid engine": actor + reference policy + in-house rollout engine in
+  one process per GPU, sharing the resident bf16 weights between training and generation.
+
+Parity target: ``verl/workers/engine_workers.py`` (TrainingWorker :160-450, ActorRolloutRefWorker :453-848).
+"""
+
+from __future__ import annotations
+
+import os
+import time
+from functools import partial
+from typing import Any, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from verl_b200.protocol import DataProto, TensorBatch
+from verl_b200.single_controller.base import Dispatch, Worker, register
+from verl_b200.single_controller.base.decorator import make_nd_compute_dataproto_dispatch_fn
+from verl_b200.utils.device import get_device_name
+from verl_b200.utils.flops_counter import FlopsCounter
+from verl_b200.utils.metric import AggregationType, Metric
+from verl_b200.utils.torch_functional import compute_position_id_with_mask
+from verl_b200.workers.engine.base import EngineRegistry
+from verl_b200.workers.engine.fsdp.engine import cfg_get
+from verl_b200.workers.utils.losses import ppo_loss, value_loss
+
+__all__ = ["TrainingWorker", "ActorRolloutRefWorker", "CriticWorker", "ensure_process_group"]
+
+
+def ensure_process_group(timeout_s: int = 600):
+    """Join the global process group described by the launcher's environment (no-op for world size 1)."""
+    import datetime
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if torch.cuda.is_available():
+            lr = int(os.environ.get("LOCAL_RANK", "0")) % torch.cuda.device_count()
+            torch.cuda.set_device(lr)
+            dist.init_process_group("cpu:gloo,cuda:nccl", timeout=datetime.timedelta(seconds=timeout_s))
+        else:
+            dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=timeout_s))
+
+
+class TrainingWorker(Worker):
+    """Mini-batch / epoch loop around one engine. ``config`` keys: model_type, backend, model, engine, optim, checkpoint
+    plus the batching knobs (ppo_mini_batch_size, ppo_epochs, micro-batch / dynamic-bsz settings)."""
+
+    def __init__(self, config, role: str = "actor"):
+        super().__init__()
+        ensure_process_group(int(cfg_get(config, "nccl_timeout", 600)))
+        self.config = config
+        self.role = role
+        self.engine = EngineRegistry.new(cfg_get(config, "model_type", "language_model"), cfg_get(config, "backend", "fsdp"),
+                                         model_config=cfg_get(config, "model"), engine_config=cfg_get(config, "engine"),
+                                         optimizer_config=cfg_get(config, "optim"), checkpoint_config=cfg_get(config, "checkpoint"))
+        self.loss_fn = None
+        self.flops_counter: Optional[FlopsCounter] = None
+        self._mesh_registered = False
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def reset(self):
+        self.engine.initialize()
+        self.flops_counter = FlopsCounter(self.engine.cfg)
+        if not self._mesh_registered:
+            self._register_dispatch_collect_info(self.role, dp_rank=self.engine.get_data_parallel_rank(),
+                                                 is_collect=self.engine.is_mp_src_rank_with_outputs())
+            self._mesh_registered = True
+
+    def set_loss_fn(self, loss_fn):
+        self.loss_fn = loss_fn
+
+    # ------------------------------------------------------------------ helpers
+    def _batch_meta(self, data: DataProto, prefix: str) -> dict:
+        """Micro-batching + sampling knobs for the engine, resolved from the worker config and the call's meta_info."""
+        c = self.config
+        meta = dict(data.meta_info)
+        if "use_dynamic_bsz" not in meta:
+            meta["use_dynamic_bsz"] = bool(cfg_get(c, f"{prefix}use_dynamic_bsz", cfg_get(c, "use_dynamic_bsz", False)))
+        if meta["use_dynamic_bsz"]:
+            meta.setdefault("max_token_len_per_gpu", int(cfg_get(c, f"{prefix}max_token_len_per_gpu", cfg_get(c, "ppo_max_token_len_per_gpu", 16384))))
+        else:
+            mbs = cfg_get(c, f"{prefix}micro_batch_size_per_gpu", cfg_get(c, "ppo_micro_batch_size_per_gpu", None))
+            meta.setdefault("micro_batch_size_per_gpu", int(mbs) if mbs else len(data))
+        return meta
+
+    def _postprocess_metrics(self, metrics: dict, n_tokens: int, dt: float, forward_only: bool) -> dict:
+        out = {k: (v.aggregate() if isinstance(v, Metric) else v) for k, v in metrics.items()}
+        if self.flops_counter is not None and dt > 0:
+            est, promised = self.flops_counter.estimate_flops([n_tokens], dt)
+            out[f"perf/mfu/{self.role}"] = est / promised / (3.0 if forward_only else 1.0)
+        if torch.cuda.is_available():
+            out[f"perf/max_memory_allocated_gb/{self.role}"] = torch.cuda.max_memory_allocated() / 1024**3
+        return out
+
+    # ------------------------------------------------------------------ compute
+    def train_mini_batch(self, data: DataProto) -> dict:
+        """Split the local batch into mini-batches (one optimizer step each), repeated ``ppo_epochs`` times."""
+        c = self.config
+        eng = self.engine
+        dp = eng.get_data_parallel_size()
+        n_local = len(data)
+        mini_global = int(cfg_get(c, "ppo_mini_batch_size", n_local * dp))
+        mini = max(1, min(n_local, mini_global // dp))
+        epochs = int(cfg_get(c, "ppo_epochs", 1))
+        shuffle = bool(cfg_get(c, "shuffle", False))
+        meta = self._batch_meta(data, "ppo_")
+        all_metrics: dict[str, Metric] = {}
+        t0 = time.perf_counter()
+        with eng.train_mode():
+            n_steps = epochs * ((n_local + mini - 1) // mini)
+            step_i = 0
+            for ep in range(epochs):
+                order = torch.randperm(n_local, generator=torch.Generator().manual_seed(int(cfg_get(c, "data_loader_seed", 42)) + ep + eng.get_data_parallel_rank())) \
+                    if shuffle else torch.arange(n_local)
+                for s in range(0, n_local, mini):
+                    mb = data.select_idxs(order[s : s + mini])
+                    mb.meta_info = meta
+                    out = eng.train_batch(mb, self.loss_fn)
+                    step_i += 1
+                    for k, v in out["metrics"].items():
+                        if k == "grad_norm":
+                            k, v = f"{self.role}/grad_norm", Metric(AggregationType.MEAN, v)
+                        if k in all_metrics:
+                            all_metrics[k].append(v)
+                        else:
+                            all_metrics[k] = v if isinstance(v, Metric) else Metric(AggregationType.MEAN, v)
+                    if step_i == n_steps:
+                        all_metrics[f"{self.role}/lr"] = Metric(AggregationType.MEAN, eng.lr_scheduler_step())
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        n_tok = int(data.batch["attention_mask"].sum()) * epochs
+        return self._postprocess_metrics(all_metrics, n_tok, dt, forward_only=False)
+
+    def infer_batch(self, data: DataProto, prefix: str = "log_prob_") -> dict:
+        meta = self._batch_meta(data, prefix)
+        data = DataProto(batch=data.batch, non_tensor_batch=data.non_tensor_batch, meta_info=meta)
+        with self.engine.eval_mode():
+            return self.engine.infer_batch(data, None)
+
+    # ------------------------------------------------------------------ placement / checkpoint
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def to(self, device, model=True, optimizer=True, grad=True):
+        self.engine.to(device, model=model, optimizer=optimizer, grad=grad)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def save_checkpoint(self, local_path, hdfs_path=None, global_step=0, max_ckpt_to_keep=None):
+        self.engine.save_checkpoint(local_path, hdfs_path, global_step, max_ckpt_to_keep)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def load_checkpoint(self, local_path, hdfs_path=None, del_local_after_load=False):
+        self.engine.load_checkpoint(local_path, hdfs_path, del_local_after_load)
+
+
+def _role_cfg(full, role: str, model_type: str):
+    """Flatten the reference-style config tree (actor_rollout_ref.{model,actor,ref,rollout} / critic) into the keys a
+    TrainingWorker reads."""
+    if role == "critic":
+        c = full
+        strategy = cfg_get(c, "strategy", "fsdp")
+        eng = dict(cfg_get(c, "fsdp_config", {}) or {}) if strategy.startswith("fsdp") else dict(cfg_get(c, "megatron", {}) or {})
+        return {"model_type": "value_model", "backend": strategy, "model": cfg_get(c, "model"), "engine": eng, "optim": cfg_get(c, "optim"),
+                "checkpoint": cfg_get(c, "checkpoint"), "ppo_mini_batch_size": cfg_get(c, "ppo_mini_batch_size"),
+                "ppo_epochs": cfg_get(c, "ppo_epochs", 1), "shuffle": cfg_get(c, "shuffle", False),
+                "use_dynamic_bsz": cfg_get(c, "use_dynamic_bsz", False), "ppo_max_token_len_per_gpu": cfg_get(c, "ppo_max_token_len_per_gpu"),
+                "ppo_micro_batch_size_per_gpu": cfg_get(c, "ppo_micro_batch_size_per_gpu"),
+                "log_prob_micro_batch_size_per_gpu": cfg_get(c, "forward_micro_batch_size_per_gpu", cfg_get(c, "ppo_micro_batch_size_per_gpu")),
+                "log_prob_max_token_len_per_gpu": cfg_get(c, "forward_max_token_len_per_gpu"), "nccl_timeout": cfg_get(c, "nccl_timeout", 600)}
+    sub = cfg_get(full, role)
+    strategy = cfg_get(sub, "strategy", "fsdp")
+    eng = dict(cfg_get(sub, "fsdp_config", {}) or {}) if strategy.startswith("fsdp") else dict(cfg_get(sub, "megatron", {}) or {})
+    out = {"model_type": model_type, "backend": strategy, "model": cfg_get(full, "model"), "engine": eng,
+           "checkpoint": cfg_get(sub, "checkpoint"), "nccl_timeout": cfg_get(full, "nccl_timeout", 600)}
+    if role == "actor":
+        out.update({k: cfg_get(sub, k) for k in ("ppo_mini_batch_size", "ppo_epochs", "shuffle", "use_dynamic_bsz", "data_loader_seed",
+                                                 "ppo_max_token_len_per_gpu", "ppo_micro_batch_size_per_gpu")})
+        out["optim"] = cfg_get(sub, "optim")
+        ro = cfg_get(full, "rollout")
+        out["log_prob_micro_batch_size_per_gpu"] = cfg_get(ro, "log_prob_micro_batch_size_per_gpu", cfg_get(sub, "ppo_micro_batch_size_per_gpu"))
+        out["log_prob_use_dynamic_bsz"] = cfg_get(ro, "log_prob_use_dynamic_bsz", cfg_get(sub, "use_dynamic_bsz", False))
+        out["log_prob_max_token_len_per_gpu"] = cfg_get(ro, "log_prob_max_token_len_per_gpu", cfg_get(sub, "ppo_max_token_len_per_gpu"))
+    else:  # ref: frozen
+        eng["forward_only"] = True
+        out["optim"] = None
+        for k in ("log_prob_micro_batch_size_per_gpu", "log_prob_use_dynamic_bsz", "log_prob_max_token_len_per_gpu"):
+            out[k] = cfg_get(sub, k)
+    return out
+
+
+class ActorRolloutRefWorker(Worker):
+    """Colocated actor / reference / rollout roles of one GPU. ``role`` ∈ {actor, ref, rollout, actor_rollout,
+    actor_rollout_ref}; ``config`` is the ``actor_rollout_ref`` subtree."""
+
+    def __init__(self, config, role: str = "actor_rollout_ref"):
+        super().__init__()
+        ensure_process_group(int(cfg_get(config, "nccl_timeout", 600)))
+        self.config = config
+        self.role = role
+        self._is_actor = "actor" in role
+        self._is_rollout = "rollout" in role
+        self._is_ref = "ref" in role
+        self.actor: Optional[TrainingWorker] = None
+        self.ref: Optional[TrainingWorker] = None
+        self.rollout = None
+        self.device = torch.device(get_device_name())
+
+    # ------------------------------------------------------------------ build
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def init_model(self):
+        c = self.config
+        if self._is_ref:
+            self.ref = TrainingWorker(_role_cfg(c, "ref", "language_model"), role="ref")
+            self.ref.reset()
+        if self._is_actor:
+            self.actor = TrainingWorker(_role_cfg(c, "actor", "language_model"), role="actor")
+            self.actor.reset()
+            self.actor.set_loss_fn(partial(ppo_loss, cfg_get(c, "actor")))
+            eng = self.actor.engine
+            self._register_dispatch_collect_info("actor", dp_rank=eng.get_data_parallel_rank(), is_collect=eng.is_mp_src_rank_with_outputs())
+        if self._is_ref and not self._is_actor:
+            eng = self.ref.engine
+            self._register_dispatch_collect_info("actor", dp_rank=eng.get_data_parallel_rank(), is_collect=eng.is_mp_src_rank_with_outputs())
+        if self._is_rollout:
+            self._build_rollout()
+        self._register_dispatch_collect_info("rollout", dp_rank=self.rank, is_collect=True)
+
+    def _build_rollout(self):
+        from verl_b200.workers.rollout.engine import InferenceEngine
+
+        ro = cfg_get(self.config, "rollout")
+        src = self.actor if self.actor is not None else self.ref
+        model = src.engine.model
+        max_len = cfg_get(ro, "max_model_len", None) or (int(cfg_get(ro, "prompt_length", 512)) + int(cfg_get(ro, "response_length", 512)))
+        self.rollout = InferenceEngine(
+            model, max_num_seqs=int(cfg_get(ro, "max_num_seqs", 256)), max_model_len=int(max_len),
+            max_num_batched_tokens=int(cfg_get(ro, "max_num_batched_tokens", 8192)),
+            gpu_memory_utilization=float(cfg_get(ro, "gpu_memory_utilization", 0.5)), enforce_eager=bool(cfg_get(ro, "enforce_eager", False)),
+            sync_interval=int(cfg_get(ro, "sync_interval", 16)), enable_prefix_sharing=bool(cfg_get(ro, "enable_prefix_caching", True)),
+            num_blocks=cfg_get(ro, "num_blocks", None))
+
+    # ------------------------------------------------------------------ rollout
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("rollout"))
+    def generate_sequences(self, prompts: DataProto) -> DataProto:
+        """Left-padded prompts in → prompts + right-padded responses out (with rollout log-probs)."""
+        from verl_b200.workers.rollout.engine import SamplingParams
+
+        ro = cfg_get(self.config, "rollout")
+        meta = prompts.meta_info
+        ids = prompts.batch["input_ids"]
+        att = prompts.batch["attention_mask"]
+        bs, P = ids.shape
+        R = int(meta.get("response_length", cfg_get(ro, "response_length", 512)))
+        do_sample = meta.get("do_sample", cfg_get(ro, "do_sample", True))
+        validate = meta.get("validate", False)
+        vk = cfg_get(ro, "val_kwargs", {}) or {}
+        temperature = float(cfg_get(vk, "temperature", 0.0)) if validate else float(meta.get("temperature", cfg_get(ro, "temperature", 1.0)))
+        sp = SamplingParams(
+            temperature=temperature if do_sample or validate else 0.0,
+            top_p=float(cfg_get(vk, "top_p", 1.0)) if validate else float(meta.get("top_p", cfg_get(ro, "top_p", 1.0))),
+            top_k=int(cfg_get(vk, "top_k", -1)) if validate else int(meta.get("top_k", cfg_get(ro, "top_k", -1))),
+            max_tokens=R, ignore_eos=bool(cfg_get(ro, "ignore_eos", False)), seed=int(meta.get("seed", 0)) + 1000003 * self.rank + int(meta.get("global_steps", 0)))
+        eos = meta.get("eos_token_id", None)
+        pad_id = int(meta.get("pad_token_id", 0) or 0)
+        ids_cpu, att_cpu = ids.cpu(), att.cpu().bool()
+        plist = [ids_cpu[i][att_cpu[i]].tolist() for i in range(bs)]
+        t0 = time.perf_counter()
+        self.rollout.wake_up()
+        outs = self.rollout.generate(plist, sp, eos_token_id=eos)
+        if bool(cfg_get(ro, "free_cache_engine", True)):
+            self.rollout.sleep()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        resp = torch.full((bs, R), pad_id, dtype=ids_cpu.dtype)
+        lps = torch.zeros(bs, R, dtype=torch.float32)
+        rmask = torch.zeros(bs, R, dtype=att.dtype)
+        for i, o in enumerate(outs):
+            n = len(o.token_ids)
+            resp[i, :n] = torch.tensor(o.token_ids, dtype=ids_cpu.dtype)
+            rmask[i, :n] = 1
+            if o.log_probs is not None:
+                lps[i, :n] = torch.tensor(o.log_probs)
+        full_ids = torch.cat([ids_cpu, resp], dim=1)
+        full_att = torch.cat([att.cpu(), rmask], dim=1)
+        batch = TensorBatch({"prompts": ids_cpu, "responses": resp, "input_ids": full_ids, "attention_mask": full_att,
+                             "position_ids": compute_position_id_with_mask(full_att), "response_mask": rmask,
+                             "rollout_log_probs": lps}, batch_size=(bs,))
+        n_tok = int(rmask.sum())
+        out = DataProto(batch=batch, non_tensor_batch=dict(prompts.non_tensor_batch),
+                        meta_info={"timing": {"generate_sequences": dt}, "metrics": [{"rollout/tokens_per_s": n_tok / max(dt, 1e-9)}]})
+        return out
+
+    # ------------------------------------------------------------------ log-probs
+    def _logprob_pass(self, worker: TrainingWorker, data: DataProto, calculate_entropy: bool) -> dict:
+        meta = dict(data.meta_info)
+        meta["calculate_entropy"] = calculate_entropy
+        meta.setdefault("temperature", float(cfg_get(self.config, "rollout.temperature", 1.0)))
+        d = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=meta)
+        return worker.infer_batch(d)["model_output"]
+
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
+    def compute_log_prob(self, data: DataProto) -> DataProto:
+        mo = self._logprob_pass(self.actor, data, calculate_entropy=True)
+        tensors = {"old_log_probs": mo["log_probs"].cpu()}
+        if "entropy" in mo:
+            tensors["entropys"] = mo["entropy"].cpu()
+        return DataProto.from_dict(tensors=tensors, meta_info={"temperature": data.meta_info.get("temperature", 1.0)})
+
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
+    def compute_ref_log_prob(self, data: DataProto) -> DataProto:
+        worker = self.ref if self.ref is not None else self.actor
+        mo = self._logprob_pass(worker, data, calculate_entropy=False)
+        return DataProto.from_dict(tensors={"ref_log_prob": mo["log_probs"].cpu()})
+
+    # ------------------------------------------------------------------ update
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
+    def update_actor(self, data: DataProto) -> DataProto:
+        ac = cfg_get(self.config, "actor")
+        meta = dict(data.meta_info)
+        meta.setdefault("temperature", float(cfg_get(self.config, "rollout.temperature", 1.0)))
+        meta["calculate_entropy"] = bool(cfg_get(ac, "calculate_entropy", False)) or float(cfg_get(ac, "entropy_coeff", 0.0)) != 0.0
+        data = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=meta)
+        metrics = self.actor.train_mini_batch(data)
+        return DataProto(batch=None, non_tensor_batch={}, meta_info={"metrics": metrics})
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def update_weights(self):
+        """Actor → rollout weight hand-off. The colocated TP=1 rollout reads the actor's resident parameters, so this
+        only has to make them resident (if offloaded) and drop stale CUDA graphs bound to moved storage."""
+        t0 = time.perf_counter()
+        if self.actor is not None and self.rollout is not None:
+            eng = self.actor.engine
+            if not eng.store.flat.is_cuda and torch.cuda.is_available():
+                eng.to("cuda", model=True, optimizer=False, grad=False)
+                self.rollout._graph = None
+        if dist.is_initialized():
+            dist.barrier()
+        return time.perf_counter() - t0
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def save_checkpoint(self, local_path, hdfs_path=None, global_step=0, max_ckpt_to_keep=None):
+        self.actor.engine.save_checkpoint(local_path, hdfs_path, global_step, max_ckpt_to_keep)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def load_checkpoint(self, local_path, hdfs_path=None, del_local_after_load=False):
+        self.actor.engine.load_checkpoint(local_path, hdfs_path, del_local_after_load)
+
+
+class CriticWorker(Worker):
+    """Value model: ``compute_values`` (forward) and ``update_critic`` (clipped value loss)."""
+
+    def __init__(self, config):
+        super().__init__()
+        ensure_process_group(int(cfg_get(config, "nccl_timeout", 600)))
+        self.config = config
+        self.critic: Optional[TrainingWorker] = None
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def init_model(self):
+        self.critic = TrainingWorker(_role_cfg(self.config, "critic", "value_model"), role="critic")
+        self.critic.reset()
+        self.critic.set_loss_fn(partial(value_loss, self.config))
+        eng = self.critic.engine
+        self._register_dispatch_collect_info("critic", dp_rank=eng.get_data_parallel_rank(), is_collect=eng.is_mp_src_rank_with_outputs())
+
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("critic"))
+    def compute_values(self, data: DataProto) -> DataProto:
+        d = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=dict(data.meta_info))
+        mo = self.critic.infer_batch(d)["model_output"]
+        vals = mo["values"].cpu() * data.batch["response_mask"].to(mo["values"].dtype).cpu()
+        return DataProto.from_dict(tensors={"values": vals})
+
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("critic"))
+    def update_critic(self, data: DataProto) -> DataProto:
+        d = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=dict(data.meta_info))
+        metrics = self.critic.train_mini_batch(d)
+        return DataProto(batch=None, non_tensor_batch={}, meta_info={"metrics": metrics})
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def save_checkpoint(self, local_path, hdfs_path=None, global_step=0, max_ckpt_to_keep=None):
+        self.critic.engine.save_checkpoint(local_path, hdfs_path, global_step, max_ckpt_to_keep)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def load_checkpoint(self, local_path, hdfs_path=None, del_local_after_load=False):
+        self.critic.engine.load_checkpoint(local_path, hdfs_path, del_local_after_load)

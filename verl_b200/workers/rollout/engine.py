@@ -1,0 +1,501 @@
+"""In-house rollout engine: paged-KV continuous-batching generation on the training process's own weights.
+
+It replaces the vLLM / SGLang servers of the reference (``verl/workers/rollout/vllm_rollout/vllm_async_server.py``,
+``verl/workers/rollout/replica.py``). Design points for a B200:
+
+* **Zero-copy weights.** The engine reads the trainer's resident bf16 parameters; "weight sync" for a colocated
+  TP=1 replica is a no-op (the reference all-gathers every tensor and ships it through CUDA IPC,
+  ``verl/workers/engine_workers.py:734-836``).
+* **Static decode batch + CUDA graph.** A decode step always runs over all ``max_num_seqs`` slots with device-side
+  position / slot bookkeeping, so one captured graph serves every step; idle slots have kv_len 0.
+* **Prompt sharing.** The n samples of a GRPO prompt prefill once; siblings fork the prompt's KV blocks by reference.
+* **Lazy EOS detection.** Sampled tokens are kept on the device and read back every ``sync_interval`` steps, so the
+  host never blocks on a decode step.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from verl_b200 import ops
+from verl_b200.models.transformer import DecoderLM
+from verl_b200.ops import _ext
+from verl_b200.ops.attention import build_tile_tables, paged_decode_attention
+from verl_b200.workers.rollout.scheduler import STEP_DECODE, STEP_IDLE, STEP_PREFILL, Scheduler
+
+__all__ = ["SamplingParams", "TokenOutput", "InferenceEngine", "BLOCK_SIZE"]
+
+BLOCK_SIZE = 64
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    max_tokens: int = 1024
+    ignore_eos: bool = False
+    logprobs: bool = True
+    seed: int = 0
+    stop_token_ids: Sequence[int] = ()
+
+
+@dataclass
+class TokenOutput:
+    """Result of one generation request (same fields as the reference's ``TokenOutput``, rollout/replica.py:34-46)."""
+
+    token_ids: list
+    log_probs: Optional[list] = None
+    routed_experts: Optional[np.ndarray] = None
+    stop_reason: Optional[str] = None
+    num_preempted: int = 0
+    extra_fields: dict = field(default_factory=dict)
+
+
+def _sample_reference(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, gen: torch.Generator):
+    """PyTorch oracle of the sampling kernel (exact sort-based top-k / top-p)."""
+    x = logits.float()
+    if temperature <= 0:
+        tok = x.argmax(-1)
+        lp = torch.log_softmax(x, -1).gather(-1, tok[:, None]).squeeze(-1)
+        return tok, lp
+    x = x / temperature
+    if top_k and 0 < top_k < x.shape[-1]:
+        kth = torch.topk(x, top_k, dim=-1).values[:, -1:]
+        x = x.masked_fill(x < kth, float("-inf"))
+    if top_p < 1.0:
+        sx, si = torch.sort(x, dim=-1, descending=True)
+        cp = torch.softmax(sx, -1).cumsum(-1)
+        drop = cp - torch.softmax(sx, -1) >= top_p
+        sx = sx.masked_fill(drop, float("-inf"))
+        x = torch.full_like(x, float("-inf")).scatter(-1, si, sx)
+    logp = torch.log_softmax(x, -1)
+    tok = torch.multinomial(logp.exp(), 1, generator=gen).squeeze(-1)
+    return tok, logp.gather(-1, tok[:, None]).squeeze(-1)
+
+
+class InferenceEngine:
+    def __init__(self, model: DecoderLM, max_num_seqs: int = 256, max_model_len: int = 2048, num_blocks: Optional[int] = None,
+                 max_num_batched_tokens: int = 8192, gpu_memory_utilization: float = 0.5, enforce_eager: bool = False,
+                 sync_interval: int = 16, enable_prefix_sharing: bool = True, decode_splits: int = 0):
+        self.model = model
+        self.cfg = model.cfg
+        self.device = model.embed_tokens.device
+        self.dtype = model.embed_tokens.dtype
+        self.max_num_seqs = max_num_seqs
+        self.max_model_len = max_model_len
+        self.max_blocks_per_seq = (max_model_len + BLOCK_SIZE - 1) // BLOCK_SIZE + 1
+        self.max_num_batched_tokens = max_num_batched_tokens
+        self.gpu_memory_utilization = gpu_memory_utilization
+        self.enforce_eager = enforce_eager or self.device.type != "cuda"
+        self.sync_interval = max(1, sync_interval)
+        self.enable_prefix_sharing = enable_prefix_sharing
+        self.native = self.device.type == "cuda" and self.dtype == torch.bfloat16 and _ext.available()
+        self._num_blocks_cfg = num_blocks
+        self.cache: Optional[torch.Tensor] = None
+        self.sched: Optional[Scheduler] = None
+        self._graph = None
+        self.decode_splits = decode_splits
+        self._cpu_gen = torch.Generator(device="cpu")
+        self.stats = {"prefill_tokens": 0, "decode_steps": 0, "preemptions": 0, "forked": 0}
+
+    # ------------------------------------------------------------------ memory lifecycle (sleep / wake_up)
+    def _decide_num_blocks(self) -> int:
+        if self._num_blocks_cfg:
+            return int(self._num_blocks_cfg)
+        c = self.cfg
+        per_block = c.num_hidden_layers * 2 * c.num_key_value_heads * BLOCK_SIZE * c.head_dim * self.model.embed_tokens.element_size()
+        want = self.max_num_seqs * self.max_blocks_per_seq + 1
+        if self.device.type == "cuda":
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = min(free * 0.9, total * self.gpu_memory_utilization)
+            want = min(want, max(int(budget // per_block), self.max_blocks_per_seq + 2))
+        return want
+
+    def wake_up(self):
+        """Allocate the KV cache and the static decode buffers."""
+        if self.cache is not None:
+            return
+        c = self.cfg
+        nb = self._decide_num_blocks()
+        self.num_blocks = nb
+        # zero-filled: masked (probability 0) positions still enter the P·V product, so they must hold finite values
+        self.cache = torch.zeros(c.num_hidden_layers, nb, 2, c.num_key_value_heads, BLOCK_SIZE, c.head_dim, dtype=self.dtype,
+                                 device=self.device)
+        S, dev = self.max_num_seqs, self.device
+        self.cur_tokens = torch.zeros(S, dtype=torch.int64, device=dev)
+        self.positions = torch.zeros(S, dtype=torch.int32, device=dev)
+        self.active = torch.zeros(S, dtype=torch.int32, device=dev)
+        self.block_table = torch.zeros(S, self.max_blocks_per_seq, dtype=torch.int32, device=dev)
+        self.kv_lens = torch.zeros(S, dtype=torch.int32, device=dev)
+        self.rng = torch.zeros(2, dtype=torch.int64, device=dev)
+        self.row_ids = torch.arange(S, dtype=torch.int32, device=dev)
+        self.out_tok = torch.zeros(S, dtype=torch.int64, device=dev)
+        self.out_lp = torch.zeros(S, dtype=torch.float32, device=dev)
+        K = self.sync_interval
+        self.hist_tok = torch.zeros(K, S, dtype=torch.int64, device=dev)
+        self.hist_lp = torch.zeros(K, S, dtype=torch.float32, device=dev)
+        self.hist_idx = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.block_table_host = np.zeros((S, self.max_blocks_per_seq), dtype=np.int32)
+        pin = self.device.type == "cuda"
+        self._bt_pinned = [torch.zeros(S, self.max_blocks_per_seq, dtype=torch.int32, pin_memory=pin) for _ in range(4)]
+        self._bt_events = [None] * 4
+        self._bt_ring = 0
+        if self.decode_splits <= 0:
+            # enough CTAs to fill the machine: B * Hkv * splits >= ~2 waves of 148 SMs
+            self.decode_splits = max(1, min(8, (296 + S * c.num_key_value_heads - 1) // (S * c.num_key_value_heads)))
+        self.workspace = torch.empty(S * c.num_attention_heads * self.decode_splits * 130, dtype=torch.float32, device=dev) \
+            if self.decode_splits > 1 else None
+        self.sched = Scheduler(nb, BLOCK_SIZE, S, self.max_num_batched_tokens)
+        self._graph = None
+
+    def sleep(self):
+        """Release the KV cache and graphs so training can use the memory (reference: rollout ``sleep``/``release``)."""
+        self._graph = None
+        self.cache = None
+        self.sched = None
+        self.workspace = None
+        for n in ("hist_tok", "hist_lp", "block_table", "cur_tokens", "positions", "kv_lens", "active"):
+            if hasattr(self, n):
+                delattr(self, n)
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    # ------------------------------------------------------------------ model forward (shared by prefill and decode)
+    def _layer_stack(self, tokens, positions, slots, attn_fn):
+        """Runs embedding → layers → final norm; ``attn_fn(layer_idx, qkv)`` returns the attention output."""
+        m, c = self.model, self.cfg
+        cos, sin = m.rope(self.device)
+        h = m.embed_tokens.index_select(0, tokens)
+        res = None
+        n_rot = c.num_attention_heads + c.num_key_value_heads
+        for li, layer in enumerate(m.layers):
+            if res is None:
+                res = h
+                x = ops.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
+            else:
+                x, res = ops.add_rmsnorm(h, res, layer.input_layernorm, c.rms_norm_eps)
+            at = layer.self_attn
+            qkv = ops.linear(x, at.qkv_proj, at.qkv_bias)
+            if c.qk_norm:
+                T = qkv.shape[0]
+                q, k, v = qkv.split([c.q_size, c.kv_size, c.kv_size], dim=-1)
+                q = ops.rmsnorm(q.reshape(-1, c.head_dim), at.q_norm, c.rms_norm_eps).reshape(T, c.q_size)
+                k = ops.rmsnorm(k.reshape(-1, c.head_dim), at.k_norm, c.rms_norm_eps).reshape(T, c.kv_size)
+                qkv = torch.cat([q, k, v], dim=-1)
+            qkv = ops.apply_rope_(qkv, positions, cos, sin, n_rot, c.head_dim)
+            self._cache_write(li, qkv, slots)
+            o = attn_fn(li, qkv)
+            a = ops.linear(o, at.o_proj)
+            x, res = ops.add_rmsnorm(a, res, layer.post_attention_layernorm, c.rms_norm_eps)
+            h = layer.mlp(x)
+        return ops.add_rmsnorm(h, res, m.norm, c.rms_norm_eps)[0]
+
+    def _cache_write(self, li: int, qkv: torch.Tensor, slots: torch.Tensor):
+        c = self.cfg
+        if self.native and c.head_dim == 128:
+            _ext.ops().kv_cache_write(qkv, slots, self.cache[li], c.num_attention_heads, c.num_key_value_heads)
+            return
+        T = qkv.shape[0]
+        k = qkv[:, c.q_size : c.q_size + c.kv_size].reshape(T, c.num_key_value_heads, c.head_dim)
+        v = qkv[:, c.q_size + c.kv_size :].reshape(T, c.num_key_value_heads, c.head_dim)
+        ok = slots >= 0
+        blk, off = (slots[ok] // BLOCK_SIZE), (slots[ok] % BLOCK_SIZE)
+        self.cache[li, blk, 0, :, off] = k[ok]
+        self.cache[li, blk, 1, :, off] = v[ok]
+
+    def _sample(self, logits, temperature, top_k, top_p, row_ids=None, out_tok=None, out_lp=None):
+        B = logits.shape[0]
+        if out_tok is None:
+            out_tok = torch.empty(B, dtype=torch.int64, device=logits.device)
+            out_lp = torch.empty(B, dtype=torch.float32, device=logits.device)
+        if self.native:
+            _ext.ops().sample(logits, float(temperature), int(top_k if top_k else -1), float(top_p), self.rng, row_ids, out_tok, out_lp)
+        else:
+            t, lp = _sample_reference(logits.cpu(), temperature, top_k, top_p, self._cpu_gen)
+            out_tok.copy_(t)
+            out_lp.copy_(lp)
+        return out_tok, out_lp
+
+    # ------------------------------------------------------------------ prefill
+    def _push_block_table(self):
+        i = self._bt_ring
+        self._bt_ring = (i + 1) % len(self._bt_pinned)
+        if self._bt_events[i] is not None:
+            self._bt_events[i].synchronize()
+        self._bt_pinned[i].copy_(torch.from_numpy(self.block_table_host))
+        self.block_table.copy_(self._bt_pinned[i], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self._bt_events[i] = ev
+
+    def _prefill(self, seqs: list, sp: SamplingParams):
+        """``seqs``: list of (request, slot) to compute from scratch (prompt + anything generated before a preemption)."""
+        c = self.cfg
+        toks, pos, slots, lens = [], [], [], []
+        for req, slot in seqs:
+            ids = req["prompt"] + req["out"]
+            L = len(ids)
+            blocks = self.sched.blocks(req["id"])
+            self.block_table_host[slot, : len(blocks)] = blocks
+            self.block_table_host[slot, len(blocks):] = 0
+            p = np.arange(L)
+            toks.append(np.asarray(ids, dtype=np.int64))
+            pos.append(p.astype(np.int32))
+            slots.append(blocks[p // BLOCK_SIZE].astype(np.int64) * BLOCK_SIZE + p % BLOCK_SIZE)
+            lens.append(L)
+        dev = self.device
+        tokens = torch.from_numpy(np.concatenate(toks)).to(dev)
+        positions = torch.from_numpy(np.concatenate(pos)).to(dev)
+        slot_map = torch.from_numpy(np.concatenate(slots)).to(dev)
+        cu_cpu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+        cu_cpu[1:] = torch.cumsum(torch.tensor(lens), 0)
+        cu = cu_cpu.to(dev)
+        max_len = max(lens)
+
+        def attn(li, qkv):
+            return ops.attention_varlen(qkv, cu, c.num_attention_heads, c.num_key_value_heads, c.head_dim, max_len, cu_cpu)
+
+        h = self._layer_stack(tokens, positions, slot_map, attn)
+        last = (cu[1:] - 1).long()
+        logits = ops.linear(h.index_select(0, last), self.model.output_weight)
+        self.stats["prefill_tokens"] += int(sum(lens))
+        return logits
+
+    def _start_sequences(self, reqs_slots: list, logits: torch.Tensor, sp: SamplingParams):
+        """Sample the first new token of each sequence from its last-prompt-token logits and arm its decode slot."""
+        slots = torch.tensor([s for _, s in reqs_slots], dtype=torch.int64, device=self.device)
+        rid = slots.to(torch.int32)
+        tok, lp = self._sample(logits, sp.temperature, sp.top_k, sp.top_p, row_ids=rid)
+        if self.native:
+            self.rng[1] += 1
+        plen = torch.tensor([len(r["prompt"]) + len(r["out"]) for r, _ in reqs_slots], dtype=torch.int32, device=self.device)
+        self.cur_tokens.index_copy_(0, slots, tok)
+        self.positions.index_copy_(0, slots, plen)
+        self.kv_lens.index_copy_(0, slots, plen)
+        self.active.index_fill_(0, slots, 1)
+        tok_h, lp_h = tok.tolist(), lp.tolist()
+        for (req, _), t, l in zip(reqs_slots, tok_h, lp_h):
+            req["out"].append(int(t))
+            req["lp"].append(float(l))
+            req["n_gen"] = len(req["out"])
+
+    # ------------------------------------------------------------------ decode
+    def _decode_body(self, sp: SamplingParams):
+        """One token for every slot. All bookkeeping is on the device so the body can be captured in a CUDA graph."""
+        c = self.cfg
+        pos = self.positions
+        act = self.active
+        blk = torch.gather(self.block_table, 1, (pos // BLOCK_SIZE).long().clamp_(max=self.max_blocks_per_seq - 1)[:, None]).squeeze(1)
+        slot_map = torch.where(act > 0, blk.long() * BLOCK_SIZE + (pos % BLOCK_SIZE).long(), torch.full_like(blk, -1, dtype=torch.int64))
+        self.kv_lens.copy_(torch.where(act > 0, pos + 1, torch.zeros_like(pos)))
+        scale = 1.0 / math.sqrt(c.head_dim)
+
+        def attn(li, qkv):
+            q = qkv[:, : c.q_size].contiguous()
+            if self.native and c.head_dim == 128:
+                return paged_decode_attention(q, self.cache[li], self.block_table, self.kv_lens, scale, self.decode_splits,
+                                              self.max_model_len, self.workspace)
+            from verl_b200.ops.attention import paged_decode_attention_ref
+
+            return paged_decode_attention_ref(q, self.cache[li], self.block_table, self.kv_lens, scale)
+
+        h = self._layer_stack(self.cur_tokens, pos, slot_map, attn)
+        logits = ops.linear(h, self.model.output_weight)
+        self._sample(logits, sp.temperature, sp.top_k, sp.top_p, self.row_ids, self.out_tok, self.out_lp)
+        self.cur_tokens.copy_(self.out_tok)
+        self.positions.add_(act)
+        self.hist_tok.index_copy_(0, self.hist_idx, self.out_tok[None])
+        self.hist_lp.index_copy_(0, self.hist_idx, self.out_lp[None])
+        self.hist_idx.add_(1).remainder_(self.sync_interval)
+        if self.native:
+            self.rng[1] += 1
+
+    def _decode_step(self, sp: SamplingParams):
+        if self.enforce_eager:
+            self._decode_body(sp)
+            return
+        key = (sp.temperature, sp.top_k, sp.top_p)
+        if self._graph is None or self._graph[0] != key:
+            # warm-up on a side stream, then capture
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            saved = [t.clone() for t in (self.cur_tokens, self.positions, self.kv_lens, self.hist_idx, self.rng, self.hist_tok, self.hist_lp)]
+            with torch.cuda.stream(s):
+                self._decode_body(sp)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            _ext.check_status("rollout decode warm-up")
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._decode_body(sp)
+            # warm-up and capture do not advance real state: the graph has not been replayed yet, restore the warm-up's effects
+            for t, sv in zip((self.cur_tokens, self.positions, self.kv_lens, self.hist_idx, self.rng, self.hist_tok, self.hist_lp), saved):
+                t.copy_(sv)
+            self._graph = (key, g)
+        self._graph[1].replay()
+
+    # ------------------------------------------------------------------ request loop
+    def _flush(self, pending: list, reqs: dict, sp: SamplingParams, eos_ids: set):
+        """Read back the sampled tokens of the un-synchronised decode steps and retire finished sequences."""
+        if not pending:
+            return
+        tok = self.hist_tok.cpu().numpy()
+        lp = self.hist_lp.cpu().numpy()
+        freed = []
+        for ring, ids, slots in pending:
+            for sid, slot in zip(ids, slots):
+                r = reqs[int(sid)]
+                if r["done"]:
+                    continue
+                t = int(tok[ring, slot])
+                r["out"].append(t)
+                r["lp"].append(float(lp[ring, slot]))
+                if (not sp.ignore_eos) and t in eos_ids:
+                    r["done"], r["stop"] = True, "stop"
+                elif len(r["out"]) >= r["max_new"]:
+                    r["done"], r["stop"] = True, "length"
+                if r["done"]:
+                    freed.append(slot)
+                    r["num_preempted"] = self.sched.num_preempted(int(sid))
+                    self.sched.finish(int(sid))
+        pending.clear()
+        if freed:
+            self.active.index_fill_(0, torch.tensor(freed, dtype=torch.int64, device=self.device), 0)
+
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[Sequence[int]], sampling_params: Optional[SamplingParams] = None,
+                 eos_token_id=None) -> list[TokenOutput]:
+        sp = sampling_params or SamplingParams()
+        self.wake_up()
+        eos_ids = set() if eos_token_id is None else ({eos_token_id} if isinstance(eos_token_id, int) else set(eos_token_id))
+        eos_ids |= set(sp.stop_token_ids)
+        self.rng[0] = sp.seed
+        self._cpu_gen.manual_seed(sp.seed)
+        self.active.zero_()
+        reqs: dict[int, dict] = {}
+        counts: dict[tuple, int] = {}
+        if self.enable_prefix_sharing:
+            for p in prompts:
+                k = tuple(p)
+                counts[k] = counts.get(k, 0) + 1
+        for i, p in enumerate(prompts):
+            p = list(p)
+            max_new = min(sp.max_tokens, self.max_model_len - len(p))
+            if max_new <= 0:
+                raise ValueError(f"prompt {i} of length {len(p)} leaves no room below max_model_len={self.max_model_len}")
+            key = 0
+            if counts.get(tuple(p), 0) > 1:
+                key = (hash(tuple(p)) & 0x3FFFFFFFFFFFFFFF) or 1
+            reqs[i] = {"id": i, "prompt": p, "out": [], "lp": [], "done": False, "stop": None, "max_new": max_new, "n_gen": 0,
+                       "num_preempted": 0, "slot": -1}
+            self.sched.add(i, len(p), max_new, key)
+        owner_logits: dict[int, torch.Tensor] = {}
+        owner_partial_block: dict[int, int] = {}
+        pending: list = []
+        ring = int(self.hist_idx.item())
+        n_preempt = self.sched.num_preemptions
+        while True:
+            kind, ids, slots, lens, forks = self.sched.step()
+            if kind == STEP_IDLE:
+                self._flush(pending, reqs, sp, eos_ids)
+                if self.sched.num_running == 0 and self.sched.num_waiting == 0:
+                    break
+                if all(r["done"] for r in reqs.values()):
+                    break
+                continue
+            if kind == STEP_PREFILL:
+                self._flush(pending, reqs, sp, eos_ids)
+                ids, slots, forks = ids.copy(), slots.copy(), forks.copy()
+                fresh = [(reqs[int(s)], int(sl)) for s, sl, f in zip(ids, slots, forks) if f < 0 and not reqs[int(s)]["done"]]
+                forked = [(reqs[int(s)], int(sl), int(f)) for s, sl, f in zip(ids, slots, forks) if f >= 0]
+                for s in ids:  # a sequence that finished while waiting for re-admission
+                    if reqs[int(s)]["done"]:
+                        self.sched.finish(int(s))
+                if fresh:
+                    logits = self._prefill(fresh, sp)
+                    for row, (r, sl) in enumerate(fresh):
+                        r["slot"] = sl
+                        if counts.get(tuple(r["prompt"]), 0) > 1 and not r["out"]:
+                            owner_logits[r["id"]] = logits[row]
+                            owner_partial_block[r["id"]] = int(self.block_table_host[sl, len(r["prompt"]) // BLOCK_SIZE])
+                    self._start_sequences(fresh, logits, sp)
+                if forked:
+                    src_b, dst_b, rows = [], [], []
+                    for r, slot, owner in forked:
+                        blocks = self.sched.blocks(r["id"])
+                        self.block_table_host[slot, : len(blocks)] = blocks
+                        self.block_table_host[slot, len(blocks):] = 0
+                        P = len(r["prompt"])
+                        if P % BLOCK_SIZE:
+                            src_b.append(owner_partial_block[owner])
+                            dst_b.append(int(blocks[P // BLOCK_SIZE]))
+                        rows.append(owner_logits[owner])
+                    if src_b:
+                        si = torch.tensor(src_b, device=self.device)
+                        di = torch.tensor(dst_b, device=self.device)
+                        self.cache[:, di] = self.cache[:, si]
+                    self._start_sequences([(r, s) for r, s, _ in forked], torch.stack(rows), sp)
+                    self.stats["forked"] += len(forked)
+                for r, sl in fresh:
+                    r["slot"] = sl
+                for r, sl, _ in forked:
+                    r["slot"] = sl
+                self._push_block_table()
+                # sequences whose single allowed token came from the prefill are complete
+                done_now = [(r, sl) for r, sl in fresh + [(r, s) for r, s, _ in forked]
+                            if len(r["out"]) >= r["max_new"] or ((not sp.ignore_eos) and r["out"][-1] in eos_ids)]
+                for r, sl in done_now:
+                    r["done"], r["stop"] = True, ("length" if len(r["out"]) >= r["max_new"] else "stop")
+                    self.sched.finish(r["id"])
+                    self.active[sl] = 0
+                continue
+            # ---- decode
+            ids, slots, lens = ids.copy(), slots.copy(), lens.copy()
+            if self.sched.num_preemptions != n_preempt:
+                n_preempt = self.sched.num_preemptions
+                self.stats["preemptions"] = n_preempt
+                self._flush(pending, reqs, sp, eos_ids)
+                self.active.zero_()
+                live = [int(sl) for s, sl in zip(ids, slots) if not reqs[int(s)]["done"]]
+                if live:
+                    self.active.index_fill_(0, torch.tensor(live, dtype=torch.int64, device=self.device), 1)
+            grew = np.nonzero((lens - 1) % BLOCK_SIZE == 0)[0]   # these sequences write the first slot of a new block
+            for j in grew:
+                blocks = self.sched.blocks(int(ids[j]))
+                self.block_table_host[slots[j], : len(blocks)] = blocks
+            if len(grew):
+                self._push_block_table()
+            self._decode_step(sp)
+            self.stats["decode_steps"] += 1
+            pending.append((ring, ids, slots))
+            ring = (ring + 1) % self.sync_interval
+            at_limit = False
+            for s in ids.tolist():
+                r = reqs[s]
+                r["n_gen"] += 1
+                if r["n_gen"] >= r["max_new"] and not r["done"]:
+                    at_limit = True
+            if at_limit or len(pending) >= self.sync_interval:
+                self._flush(pending, reqs, sp, eos_ids)
+        if self.native:
+            _ext.check_status("rollout generate")
+        outs = []
+        for i in range(len(prompts)):
+            r = reqs[i]
+            outs.append(TokenOutput(token_ids=r["out"][: r["max_new"]], log_probs=r["lp"][: r["max_new"]] if sp.logprobs else None,
+                                    stop_reason=r["stop"] or "length", num_preempted=r["num_preempted"]))
+        return outs
+
+    def abort_all(self) -> list[int]:
+        """Drop every live request (used when a weight update interrupts generation)."""
+        ids = self.sched.abort_all() if self.sched is not None else []
+        if hasattr(self, "active"):
+            self.active.zero_()
+        return ids
