@@ -1,0 +1,130 @@
+import numpy as np
+import pytest
+import torch
+
+from verl_b200.models.config import PRESETS
+from verl_b200.models.transformer import DecoderLM, PackedBatch
+from verl_b200.workers.rollout import InferenceEngine, SamplingParams
+from verl_b200.workers.rollout.engine import _sample_reference
+from verl_b200.workers.rollout.scheduler import STEP_DECODE, STEP_IDLE, STEP_PREFILL, Scheduler
+
+
+def greedy_oracle(model, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        t = torch.tensor(ids)
+        pb = PackedBatch(t, torch.arange(len(ids), dtype=torch.int32), torch.tensor([0, len(ids)], dtype=torch.int32))
+        with torch.no_grad():
+            ids.append(int(model(pb, return_logits=True)["logits"][-1].argmax()))
+    return ids[len(prompt):]
+
+
+@pytest.fixture(scope="module")
+def model():
+    return DecoderLM(PRESETS["tiny-qwen2"], dtype=torch.float32, seed=3)
+
+
+def test_scheduler_prefill_decode_and_limits():
+    s = Scheduler(num_blocks=9, block_size=64, max_num_seqs=4, max_batched_tokens=1024)
+    s.add(0, 100, 10)
+    s.add(1, 60, 10)
+    kind, ids, slots, lens, forks = s.step()
+    assert kind == STEP_PREFILL and ids.tolist() == [0, 1] and lens.tolist() == [100, 60] and (forks < 0).all()
+    assert len(s.blocks(0)) == 2 and len(s.blocks(1)) == 1
+    kind, ids, slots, lens, _ = s.step()
+    assert kind == STEP_DECODE and lens.tolist() == [101, 61]
+    for _ in range(4):
+        s.step()
+    assert len(s.blocks(1)) == 2          # crossed a block boundary at 65 tokens
+    s.finish(0)
+    s.finish(1)
+    assert s.step()[0] == STEP_IDLE and s.num_free_blocks == 8
+    with pytest.raises(ValueError):
+        s.add(5, 64 * 9, 1)               # can never fit
+
+
+def test_scheduler_fork_shares_prompt_blocks():
+    s = Scheduler(num_blocks=16, block_size=64, max_num_seqs=8, max_batched_tokens=4096)
+    for i in range(3):
+        s.add(i, 150, 20, share_key=77)
+    kind, ids, slots, lens, forks = s.step()
+    assert kind == STEP_PREFILL and forks.tolist() == [-1, 0, 0]
+    b0, b1, b2 = s.blocks(0), s.blocks(1), s.blocks(2)
+    assert b0[:2].tolist() == b1[:2].tolist() == b2[:2].tolist()    # two full blocks shared
+    assert len({int(b0[2]), int(b1[2]), int(b2[2])}) == 3            # private partial blocks
+    for i in range(3):
+        s.finish(i)
+    assert s.num_free_blocks == 15
+
+
+def test_scheduler_preempts_newest_when_out_of_blocks():
+    s = Scheduler(num_blocks=4, block_size=64, max_num_seqs=4, max_batched_tokens=4096)   # 3 usable blocks
+    s.add(0, 60, 100)
+    s.add(1, 60, 100)
+    kind, ids, *_ = s.step()
+    assert kind == STEP_PREFILL and ids.tolist() == [0, 1]        # one block each, one block left
+    seen_preempt = False
+    for _ in range(12):
+        kind, ids, slots, lens, _f = s.step()
+        if s.num_preemptions > 0:
+            seen_preempt = True
+            break
+    assert seen_preempt and ids.tolist() == [0]                    # the newest sequence (1) was evicted
+    assert s.num_waiting == 1 and s.num_preempted(1) == 1
+    s.finish(0)
+    kind, ids, slots, lens, _f = s.step()
+    assert kind == STEP_PREFILL and ids.tolist() == [1] and lens[0] > 60   # recompute prompt + generated tokens
+
+
+def test_generate_matches_greedy_oracle_with_forks(model):
+    eng = InferenceEngine(model, max_num_seqs=8, max_model_len=128, num_blocks=16, sync_interval=4)
+    g = torch.Generator().manual_seed(0)
+    base = [torch.randint(10, 2048, (n,), generator=g).tolist() for n in (20, 33)]
+    prompts = [base[0], base[0], base[1], base[1], base[0]]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12))
+    assert eng.stats["forked"] == 3
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == greedy_oracle(model, p, 12)
+        assert o.stop_reason == "length" and len(o.log_probs) == 12 and all(lp <= 0 for lp in o.log_probs)
+
+
+def test_generate_with_preemption_still_matches(model):
+    # 3 blocks of 64 tokens for two sequences that each grow to 70+ tokens forces a recompute preemption
+    eng = InferenceEngine(model, max_num_seqs=4, max_model_len=128, num_blocks=4, sync_interval=2, enable_prefix_sharing=False)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(10, 2048, (50,), generator=g).tolist() for _ in range(2)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=30))
+    assert eng.sched.num_preemptions >= 1
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == greedy_oracle(model, p, 30)
+
+
+def test_eos_stops_generation(model):
+    eng = InferenceEngine(model, max_num_seqs=4, max_model_len=128, num_blocks=8, sync_interval=4)
+    p = list(range(10, 30))
+    ref = greedy_oracle(model, p, 10)
+    eos = ref[4]
+    first = ref.index(eos)
+    out = eng.generate([p], SamplingParams(temperature=0.0, max_tokens=10), eos_token_id=eos)[0]
+    assert out.token_ids == ref[: first + 1] and out.stop_reason == "stop"
+
+
+def test_sleep_and_wake(model):
+    eng = InferenceEngine(model, max_num_seqs=2, max_model_len=64, num_blocks=4)
+    eng.wake_up()
+    assert eng.cache is not None
+    eng.sleep()
+    assert eng.cache is None
+    out = eng.generate([[11, 12, 13]], SamplingParams(temperature=0.0, max_tokens=3))
+    assert len(out[0].token_ids) == 3
+
+
+def test_sampling_reference_topk_topp():
+    g = torch.Generator().manual_seed(0)
+    logits = torch.tensor([[5.0, 4.0, 1.0, 0.0, -1.0]]).repeat(200, 1)
+    tok, lp = _sample_reference(logits, 1.0, 2, 1.0, g)
+    assert set(tok.tolist()) <= {0, 1}
+    tok, _ = _sample_reference(logits, 1.0, -1, 0.5, g)
+    assert set(tok.tolist()) == {0}
+    tok, lp = _sample_reference(logits, 0.0, -1, 1.0, g)
+    assert tok.tolist() == [0] * 200

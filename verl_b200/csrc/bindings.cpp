@@ -5,6 +5,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include <atomic>
+
 #include "api.h"
 
 namespace {
@@ -14,6 +16,10 @@ using at::Tensor;
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 
 }  // namespace
+
+// Number of kernel-launching calls made through this library (for benchmark accounting).
+static std::atomic<long> g_launch_calls{0};
+void vb_count_launch(int n) { g_launch_calls.fetch_add(n, std::memory_order_relaxed); }
 
 // One status word per device, shared by all kernels with bounded waits.
 at::Tensor& vb_status_tensor(int dev) {
@@ -31,6 +37,7 @@ Tensor& status_word(int dev) { return vb_status_tensor(dev); }
 
 void check_rc(int rc, const char* what) {
   TORCH_CHECK(rc == 0, "verl_b200::", what, " failed with code ", rc);
+  vb_count_launch(1);
 }
 
 #define CHECK_CUDA_BF16(t) TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kBFloat16, #t " must be a CUDA bf16 tensor")
@@ -201,4 +208,5 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("sqnorm_(Tensor g, Tensor(a!) out) -> ()", &sqnorm_);
   m.def("clip_coef_(Tensor sumsq, float max_norm, Tensor(a!) scalars) -> ()", &clip_coef_);
   m.def("take_status() -> int", &take_status);
+  m.def("launch_count() -> int", []() -> int64_t { return (int64_t)g_launch_calls.load(); });
 }

@@ -8,11 +8,16 @@
 
 at::Tensor& vb_status_tensor(int dev);
 
+void vb_count_launch(int n);
+
 namespace {
 using at::Tensor;
 
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
-void check_rc(int rc, const char* what) { TORCH_CHECK(rc == 0, "verl_b200::", what, " failed with code ", rc); }
+void check_rc(int rc, const char* what) {
+  TORCH_CHECK(rc == 0, "verl_b200::", what, " failed with code ", rc);
+  vb_count_launch(1);
+}
 
 // qkv: [T, (Hq+2Hkv)*128] bf16 fused projection rows; tiles: int32 [n_tiles, 4] on device.
 // Returns (out [T, Hq*128] bf16, lse [Hq, T] fp32).

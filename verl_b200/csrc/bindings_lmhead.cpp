@@ -8,10 +8,15 @@
 
 at::Tensor& vb_status_tensor(int dev);
 
+void vb_count_launch(int n);
+
 namespace {
 using at::Tensor;
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
-void check_rc(int rc, const char* what) { TORCH_CHECK(rc == 0, "verl_b200::", what, " failed with code ", rc); }
+void check_rc(int rc, const char* what) {
+  TORCH_CHECK(rc == 0, "verl_b200::", what, " failed with code ", rc);
+  vb_count_launch(1);
+}
 
 // Returns (logp [M], entropy [M], lse [M]) in fp32.
 std::tuple<Tensor, Tensor, Tensor> lmhead_logprob_fwd(const Tensor& h, const Tensor& w, const Tensor& labels, double inv_temp) {

@@ -6,10 +6,15 @@
 
 #include "api.h"
 
+void vb_count_launch(int n);
+
 namespace {
 using at::Tensor;
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
-void check_rc(int rc, const char* what) { TORCH_CHECK(rc == 0, "verl_b200::", what, " failed with code ", rc); }
+void check_rc(int rc, const char* what) {
+  TORCH_CHECK(rc == 0, "verl_b200::", what, " failed with code ", rc);
+  vb_count_launch(1);
+}
 
 // qkv: [T, (Hq+2Hkv)*128] after RoPE; slots int64 [T]; cache layer [num_blocks, 2, Hkv, 64, 128]
 void kv_cache_write(const Tensor& qkv, const Tensor& slots, Tensor& cache, int64_t n_q_heads, int64_t n_kv_heads) {

@@ -55,3 +55,19 @@ def check_status(where: str = "") -> None:
     code = int(torch.ops.verl_b200.take_status())
     if code != 0:
         raise RuntimeError(f"verl_b200 kernel reported status {code & 0xFF} (block {code >> 8}) {where}")
+
+
+_graph_launches = 0
+
+
+def add_graph_launches(n: int) -> None:
+    """Kernels replayed from a captured CUDA graph never pass through the bindings; account for them here."""
+    global _graph_launches
+    _graph_launches += int(n)
+
+
+def launch_count() -> int:
+    """Kernel-launching calls into the native library so far (direct calls + graph replays)."""
+    if not _loaded:
+        return 0
+    return int(torch.ops.verl_b200.launch_count()) + _graph_launches

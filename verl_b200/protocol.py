@@ -523,6 +523,12 @@ class DataProto:
                     elif v is not None:
                         merged_metrics.append(v)
                     continue
+                if k == "timing" and isinstance(v, dict):   # per-worker timings: keep every worker's value
+                    t = meta.setdefault("timing", {})
+                    for tk, tv in v.items():
+                        t.setdefault(tk, [])
+                        t[tk].extend(tv if isinstance(tv, list) else [tv])
+                    continue
                 if k in meta:
                     assert _py_equal(meta[k], v), f"meta_info key {k} differs between concatenated batches"
                 else:

@@ -48,6 +48,19 @@ def cfg_get(cfg, key: str, default=None):
     return default if cur is None else cur
 
 
+# bytes moved host->device (inputs, from pinned memory) and device->host (results) by the engines of this process
+IO_STATS = {"h2d_bytes": 0, "d2h_bytes": 0}
+
+
+def _to_device(v: torch.Tensor, dev: torch.device) -> torch.Tensor:
+    if v.device == dev:
+        return v
+    if dev.type == "cuda" and v.device.type == "cpu":
+        IO_STATS["h2d_bytes"] += v.numel() * v.element_size()
+        return v.pin_memory().to(dev, non_blocking=True)
+    return v.to(dev)
+
+
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            "float16": torch.float16, "fp16": torch.float16, "torch.bfloat16": torch.bfloat16, "torch.float32": torch.float32}
 
@@ -379,7 +392,7 @@ class FSDPEngine(BaseEngine):
         batch = data.batch
         meta = dict(getattr(data, "meta_info", {}) or {})
         dev = self.device
-        tensors = {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
+        tensors = {k: (_to_device(v, dev) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
         n = tensors["input_ids"].shape[0]
         seq_lens = tensors["attention_mask"].sum(-1)
         mb_indices = self._micro_batch_indices(seq_lens, meta)

@@ -26,7 +26,7 @@ from verl_b200.utils.flops_counter import FlopsCounter
 from verl_b200.utils.metric import AggregationType, Metric
 from verl_b200.utils.torch_functional import compute_position_id_with_mask
 from verl_b200.workers.engine.base import EngineRegistry
-from verl_b200.workers.engine.fsdp.engine import cfg_get
+from verl_b200.workers.engine.fsdp.engine import IO_STATS, cfg_get
 from verl_b200.workers.utils.losses import ppo_loss, value_loss
 
 __all__ = ["TrainingWorker", "ActorRolloutRefWorker", "CriticWorker", "ensure_process_group"]
@@ -134,6 +134,7 @@ class TrainingWorker(Worker):
                         all_metrics[f"{self.role}/lr"] = Metric(AggregationType.MEAN, eng.lr_scheduler_step())
         if torch.cuda.is_available():
             torch.cuda.synchronize()
+        eng.store.free_grads()   # the fp32 gradient buffer is only needed inside an update; the KV cache wants the room
         dt = time.perf_counter() - t0
         n_tok = int(data.batch["attention_mask"].sum()) * epochs
         return self._postprocess_metrics(all_metrics, n_tok, dt, forward_only=False)
@@ -156,6 +157,12 @@ class TrainingWorker(Worker):
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def load_checkpoint(self, local_path, hdfs_path=None, del_local_after_load=False):
         self.engine.load_checkpoint(local_path, hdfs_path, del_local_after_load)
+
+
+def _to_host(t: torch.Tensor) -> torch.Tensor:
+    if t.is_cuda:
+        IO_STATS["d2h_bytes"] += t.numel() * t.element_size()
+    return t.cpu()
 
 
 def _role_cfg(full, role: str, model_type: str):
@@ -307,16 +314,16 @@ class ActorRolloutRefWorker(Worker):
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
     def compute_log_prob(self, data: DataProto) -> DataProto:
         mo = self._logprob_pass(self.actor, data, calculate_entropy=True)
-        tensors = {"old_log_probs": mo["log_probs"].cpu()}
+        tensors = {"old_log_probs": _to_host(mo["log_probs"])}
         if "entropy" in mo:
-            tensors["entropys"] = mo["entropy"].cpu()
+            tensors["entropys"] = _to_host(mo["entropy"])
         return DataProto.from_dict(tensors=tensors, meta_info={"temperature": data.meta_info.get("temperature", 1.0)})
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
     def compute_ref_log_prob(self, data: DataProto) -> DataProto:
         worker = self.ref if self.ref is not None else self.actor
         mo = self._logprob_pass(worker, data, calculate_entropy=False)
-        return DataProto.from_dict(tensors={"ref_log_prob": mo["log_probs"].cpu()})
+        return DataProto.from_dict(tensors={"ref_log_prob": _to_host(mo["log_probs"])})
 
     # ------------------------------------------------------------------ update
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))

@@ -333,13 +333,16 @@ class InferenceEngine:
             torch.cuda.synchronize()
             _ext.check_status("rollout decode warm-up")
             g = torch.cuda.CUDAGraph()
+            n0 = _ext.launch_count()
             with torch.cuda.graph(g):
                 self._decode_body(sp)
+            self._graph_launches = _ext.launch_count() - n0
             # warm-up and capture do not advance real state: the graph has not been replayed yet, restore the warm-up's effects
             for t, sv in zip((self.cur_tokens, self.positions, self.kv_lens, self.hist_idx, self.rng, self.hist_tok, self.hist_lp), saved):
                 t.copy_(sv)
             self._graph = (key, g)
         self._graph[1].replay()
+        _ext.add_graph_launches(self._graph_launches)
 
     # ------------------------------------------------------------------ request loop
     def _flush(self, pending: list, reqs: dict, sp: SamplingParams, eos_ids: set):
