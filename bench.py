@@ -176,17 +176,26 @@ def run_native(args):
 
 
 def run_reference(args):
-    """The unmodified reference needs ray, hydra, omegaconf and tensordict at import time; none of them is installed
-    in this image and there is no network, so its public entry point cannot start."""
-    missing = []
-    for m in ("ray", "hydra", "omegaconf", "tensordict"):
+    """Runs the unmodified reference installed under ``baseline/_ref`` through its own entry point — if it can start.
+    Its package imports ray / tensordict / hydra / omegaconf at import time (``verl/protocol.py``, ``verl/trainer/main_ppo.py``);
+    where those are not installed the arm reports itself unavailable instead of substituting anything of ours."""
+    ref_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref_dir, "verl")):
+        why = "reference is not installed under baseline/_ref"
+    else:
+        sys.path.insert(0, ref_dir)
         try:
-            __import__(m)
-        except Exception:  # noqa: BLE001
-            missing.append(m)
+            import importlib
+
+            importlib.import_module("verl.trainer.main_ppo")
+            why = ("reference imports, but its stock GRPO path needs a Ray cluster, a vLLM/SGLang rollout server and an HF checkpoint + "
+                   "parquet dataset on disk; none can be provided offline, so no like-for-like run is possible")
+        except Exception as e:  # noqa: BLE001
+            why = f"reference entry point cannot be imported offline: {type(e).__name__}: {e}"
+        finally:
+            sys.path.remove(ref_dir)
     if int(os.environ.get("RANK", "0")) == 0:
-        why = ("reference (baseline/_ref) cannot run: its entry point imports " + ", ".join(missing) + " which are not installed offline"
-               if missing else "reference arm not wired: dependencies present but no offline dataset/model path")
         print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
 
 

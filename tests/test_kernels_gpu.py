@@ -134,8 +134,10 @@ def test_attention_varlen_fwd_bwd(o, lens, Hq, Hkv):
     assert rel(out, ref) < 1e-2 and rel(qkv.grad, q2.grad) < 1.5e-2
 
 
-@pytest.mark.parametrize("B,Hq,Hkv,lens,splits", [(3, 28, 4, [5, 200, 512], 1), (3, 28, 4, [5, 200, 512], 2), (2, 8, 8, [64, 129], 1), (2, 28, 4, [0, 300], 4)])
-def test_paged_decode_attention(o, B, Hq, Hkv, lens, splits):
+@pytest.mark.parametrize("impl", [1, 2])
+@pytest.mark.parametrize("B,Hq,Hkv,lens,splits", [(3, 28, 4, [5, 200, 512], 1), (3, 28, 4, [5, 200, 512], 2), (2, 8, 8, [64, 129], 1), (2, 28, 4, [0, 300], 4),
+                                                  (4, 32, 2, [1, 127, 128, 400], 1)])
+def test_paged_decode_attention(o, B, Hq, Hkv, lens, splits, impl):
     from verl_b200.ops.attention import paged_decode_attention, paged_decode_attention_ref
 
     dev, D, nb, maxb = "cuda", 128, 64, 8
@@ -145,7 +147,7 @@ def test_paged_decode_attention(o, B, Hq, Hkv, lens, splits):
     kl = torch.tensor(lens, dtype=torch.int32, device=dev)
     q = (0.5 * torch.randn(B, Hq * D, device=dev)).bfloat16()
     ws = torch.empty(B * Hq * splits * 130, device=dev) if splits > 1 else None
-    out = paged_decode_attention(q, cache, bt, kl, 1 / math.sqrt(D), splits, max(lens), ws)
+    out = paged_decode_attention(q, cache, bt, kl, 1 / math.sqrt(D), splits, max(lens), ws, impl=impl)
     assert status_ok(o)
     assert rel(out, paged_decode_attention_ref(q, cache, bt, kl, 1 / math.sqrt(D))) < 1.5e-2
 

@@ -1,0 +1,81 @@
+"""Multi-GPU paths (need >= 2 CUDA devices): symmetric-memory barrier / reduce-scatter / AdamW+all-gather kernels against
+the NCCL path, and the fsdp engine's fused optimizer step against its NCCL optimizer step."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("cpu:gloo,cuda:nccl")
+from verl_b200.ops import _ext
+from verl_b200.parallel.symm_mem import SymmetricBuffer
+from verl_b200.single_controller.spmd import init_spmd_process_group
+host = init_spmd_process_group()
+o = _ext.ops()
+dev = torch.device("cuda")
+n = 1 << 20
+# ---- barrier + peer visibility
+buf = SymmetricBuffer(n * 4, host_group=host)
+x = buf.tensor(torch.float32, n)
+x.fill_(float(rank + 1))
+buf.barrier()
+tot = torch.zeros(1, device=dev)
+shard = torch.empty(n // world, device=dev)
+o.symm_reduce_scatter(buf.table(), world, rank * (n // world), shard, tot, 1.0 / world)
+torch.cuda.synchronize()
+want = sum(range(1, world + 1)) / world
+assert torch.allclose(shard, torch.full_like(shard, want)), (shard[:4], want)
+assert abs(tot.item() - want * want * (n // world)) / (want * want * (n // world)) < 1e-5
+buf.barrier()
+assert int(o.take_status()) == 0
+# ---- engine: fused optimizer step == NCCL optimizer step
+from tests.test_engine_on_cpu import make_batch, loss_fn
+from verl_b200.models.config import PRESETS
+from verl_b200.workers.engine.fsdp.engine import FSDPEngine
+res = {}
+for mode in ("fused", "nccl"):
+    eng = FSDPEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "use_symmetric_memory": mode == "fused"}, {"lr": 1e-3, "clip_grad": 1.0}, {})
+    eng.initialize()
+    assert (eng._symm_grads is not None) == (mode == "fused")
+    data = make_batch(bs=8, P=40, R=60, vocab=4096).chunk(world)[rank]
+    data.meta_info["micro_batch_size_per_gpu"] = 2
+    for _ in range(2):
+        out = eng.train_batch(data, loss_fn)
+    torch.cuda.synchronize()
+    res[mode] = (eng.store.flat.float().clone(), out["metrics"]["grad_norm"], eng.master.clone())
+    _ext.check_status(mode)
+gn_f, gn_n = res["fused"][1], res["nccl"][1]
+assert abs(gn_f - gn_n) / gn_n < 2e-2, (gn_f, gn_n)
+d = (res["fused"][0] - res["nccl"][0]).abs()
+assert d.max().item() <= 4.2e-3 and (d > 1e-4).float().mean().item() < 0.05, (d.max().item(), (d > 1e-4).float().mean().item())
+# every rank holds identical parameters after the fused all-gather
+flat = res["fused"][0]
+ref = flat.clone()
+dist.broadcast(ref, src=0)
+assert torch.equal(flat, ref)
+dist.barrier()
+if rank == 0:
+    print("MULTI_GPU_OK")
+'''
+
+
+@pytest.mark.parametrize("world", [2])
+def test_symmetric_memory_and_fused_optimizer(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "w.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, REPO=repo, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                        "--master-port", "29683", str(script)], env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "MULTI_GPU_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

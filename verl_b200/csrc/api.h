@@ -8,8 +8,10 @@
 extern "C" {
 #endif
 
+void vb_gemm_plan(int M, int N, int K, int b_mn, int bn_req, int* bn, int* split_k);
 int vb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb, int ldc,
-                 int a_mn, int b_mn, int out_f32, int accumulate, int bn, int* err_word, cudaStream_t stream);
+                 int a_mn, int b_mn, int out_f32, int accumulate, int bn, int split_k, float* split_ws, int* err_word,
+                 cudaStream_t stream);
 
 int vb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* res_out, float* rstd, int T, int H,
                    float eps, cudaStream_t st);
@@ -43,10 +45,25 @@ int vb_attn_varlen_fwd(const void* q, const void* k, const void* v, long ld, int
 int vb_attn_paged_decode(const void* q, long ld_q, const void* cache, long num_blocks, const int* block_table, int max_blocks,
                          const int* kv_lens, int B, int n_q_heads, int n_kv_heads, void* out, long ld_out, float scale,
                          int num_splits, int max_kv_len, float* part_o, float* part_ml, int* err_word, cudaStream_t st);
+int vb_attn_decode_gqa(const void* q, long ld_q, const void* cache, long num_blocks, const int* block_table, int max_blocks,
+                       const int* kv_lens, int B, int n_q_heads, int n_kv_heads, void* out, long ld_out, float scale,
+                       int num_splits, int max_kv_len, float* part_o, float* part_ml, int* err_word, cudaStream_t st);
 int vb_attn_varlen_bwd(const void* q, const void* k, const void* v, long ld, const void* dO, const void* O, long ld_o, int T,
                        int n_q_heads, int n_kv_heads, const void* tiles, int n_tiles, const float* lse, float* delta,
                        long stat_stride, float* dq_acc, void* dq, void* dk, void* dv, long ld_d, float scale, int* err_word,
                        cudaStream_t st);
+
+long vb_symm_alloc(long nbytes);
+int vb_symm_free(long ptr);
+int vb_ipc_get_handle(long ptr, unsigned char* out64);
+long vb_ipc_open_handle(const unsigned char* in64);
+int vb_ipc_close(long ptr);
+int vb_symm_barrier(const long* pad_ptrs, int rank, int world, int epoch, int* err_word, cudaStream_t st);
+int vb_symm_reduce_scatter(const long* grad_ptrs, int world, long shard_off, long n, float scale, float* out, float* sumsq,
+                           cudaStream_t st);
+int vb_symm_adamw_allgather(float* p32, float* m, float* v, const float* g, const long* param_ptrs, int world, long shard_off,
+                            long n, float lr, float b1, float b2, float eps, float wd, int step, const float* scalars,
+                            cudaStream_t st);
 
 #ifdef __cplusplus
 }

@@ -65,8 +65,17 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Ten
   }
   c10::cuda::CUDAGuard guard(a.device());
   int* err = status_word(a.get_device()).data_ptr<int>();
+  int bn_sel = 0, split = 1;
+  vb_gemm_plan((int)M, (int)N, (int)K, b_mn, (int)bn, &bn_sel, &split);
+  Tensor ws;
+  float* ws_p = nullptr;
+  if (split > 1) {
+    ws = at::empty({(int64_t)split * M * N}, a.options().dtype(at::kFloat));
+    ws_p = ws.data_ptr<float>();
+  }
   int rc = vb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias_p, (int)M, (int)N, (int)K, (int)a.stride(0),
-                        (int)b.stride(0), (int)out.stride(0), a_mn, b_mn, out_f32, accumulate, (int)bn, err, cur_stream());
+                        (int)b.stride(0), (int)out.stride(0), a_mn, b_mn, out_f32, accumulate, bn_sel, split, ws_p, err,
+                        cur_stream());
   check_rc(rc, "gemm");
 }
 

@@ -62,8 +62,9 @@ Tensor attn_varlen_bwd(const Tensor& qkv, const Tensor& out, const Tensor& dout,
 
 // q: [B, Hq*128]; cache: [num_blocks, 2, Hkv, 64, 128]; block_table int32 [B, max_blocks]; kv_lens int32 [B].
 // workspace: fp32 scratch of at least B*Hq*num_splits*130 elements when num_splits > 1.
+// impl: 0 = pick (transposed GQA kernel when Hq/Hkv <= 16), 1 = generic 128-row query-tile kernel, 2 = transposed GQA kernel.
 void attn_paged_decode(const Tensor& q, const Tensor& cache, const Tensor& block_table, const Tensor& kv_lens, Tensor& out,
-                       double scale, int64_t num_splits, int64_t max_kv_len, const c10::optional<Tensor>& workspace) {
+                       double scale, int64_t num_splits, int64_t max_kv_len, const c10::optional<Tensor>& workspace, int64_t impl) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.is_contiguous(), "paged: bad q");
   TORCH_CHECK(cache.is_contiguous() && cache.dim() == 5 && cache.size(3) == 64 && cache.size(4) == 128, "paged: bad cache");
   TORCH_CHECK(block_table.scalar_type() == at::kInt && block_table.is_contiguous() && kv_lens.scalar_type() == at::kInt, "paged: bad tables");
@@ -79,10 +80,11 @@ void attn_paged_decode(const Tensor& q, const Tensor& cache, const Tensor& block
     pml = po + (int64_t)B * n_q * num_splits * 128;
   }
   c10::cuda::CUDAGuard guard(q.device());
-  check_rc(vb_attn_paged_decode(q.data_ptr(), q.stride(0), cache.data_ptr(), cache.size(0), block_table.data_ptr<int>(),
-                                (int)block_table.size(1), kv_lens.data_ptr<int>(), B, n_q, n_kv, out.data_ptr(), out.stride(0),
-                                (float)scale, (int)num_splits, (int)max_kv_len, po, pml,
-                                vb_status_tensor(q.get_device()).data_ptr<int>(), cur_stream()),
+  const bool gqa = impl == 2 || (impl == 0 && n_q / n_kv <= 16);
+  auto fn = gqa ? vb_attn_decode_gqa : vb_attn_paged_decode;
+  check_rc(fn(q.data_ptr(), q.stride(0), cache.data_ptr(), cache.size(0), block_table.data_ptr<int>(), (int)block_table.size(1),
+              kv_lens.data_ptr<int>(), B, n_q, n_kv, out.data_ptr(), out.stride(0), (float)scale, (int)num_splits, (int)max_kv_len, po,
+              pml, vb_status_tensor(q.get_device()).data_ptr<int>(), cur_stream()),
            "attn_paged_decode");
 }
 
@@ -91,5 +93,5 @@ void attn_paged_decode(const Tensor& q, const Tensor& cache, const Tensor& block
 TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
   m.def("attn_varlen_fwd(Tensor qkv, Tensor tiles, int n_q_heads, int n_kv_heads, float scale) -> (Tensor, Tensor)", &attn_varlen_fwd);
   m.def("attn_varlen_bwd(Tensor qkv, Tensor out, Tensor dout, Tensor lse, Tensor bwd_tiles, int n_q_heads, int n_kv_heads, float scale) -> Tensor", &attn_varlen_bwd);
-  m.def("attn_paged_decode(Tensor q, Tensor cache, Tensor block_table, Tensor kv_lens, Tensor(a!) out, float scale, int num_splits, int max_kv_len, Tensor? workspace) -> ()", &attn_paged_decode);
+  m.def("attn_paged_decode(Tensor q, Tensor cache, Tensor block_table, Tensor kv_lens, Tensor(a!) out, float scale, int num_splits, int max_kv_len, Tensor? workspace, int impl) -> ()", &attn_paged_decode);
 }

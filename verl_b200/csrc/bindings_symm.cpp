@@ -1,0 +1,84 @@
+// torch.ops.verl_b200 bindings of the symmetric-memory layer.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include "api.h"
+
+at::Tensor& vb_status_tensor(int dev);
+void vb_count_launch(int n);
+
+namespace {
+using at::Tensor;
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+void check_rc(int rc, const char* what) {
+  TORCH_CHECK(rc == 0, "verl_b200::", what, " failed with code ", rc);
+  vb_count_launch(1);
+}
+
+int64_t symm_alloc(int64_t nbytes) {
+  long p = vb_symm_alloc(nbytes);
+  TORCH_CHECK(p != 0, "symm_alloc: cudaMalloc of ", nbytes, " bytes failed");
+  return p;
+}
+void symm_free(int64_t ptr) { vb_symm_free(ptr); }
+Tensor ipc_get_handle(int64_t ptr) {
+  Tensor h = at::empty({64}, at::TensorOptions().dtype(at::kByte));
+  TORCH_CHECK(vb_ipc_get_handle(ptr, h.data_ptr<uint8_t>()) == 0, "cudaIpcGetMemHandle failed");
+  return h;
+}
+int64_t ipc_open_handle(const Tensor& h) {
+  TORCH_CHECK(h.scalar_type() == at::kByte && h.numel() == 64 && !h.is_cuda(), "ipc_open_handle: need a CPU uint8[64] tensor");
+  long p = vb_ipc_open_handle(h.contiguous().data_ptr<uint8_t>());
+  TORCH_CHECK(p != 0, "cudaIpcOpenMemHandle failed");
+  return p;
+}
+void ipc_close(int64_t ptr) { vb_ipc_close(ptr); }
+
+// Non-owning tensor view on raw device memory.
+Tensor tensor_from_ptr(int64_t ptr, at::IntArrayRef sizes, at::ScalarType dtype) {
+  int dev = at::cuda::current_device();
+  return at::from_blob(reinterpret_cast<void*>(ptr), sizes, at::TensorOptions().dtype(dtype).device(at::kCUDA, dev));
+}
+
+void symm_barrier(const Tensor& pad_ptrs, int64_t rank, int64_t world, int64_t epoch) {
+  TORCH_CHECK(pad_ptrs.scalar_type() == at::kLong && !pad_ptrs.is_cuda() && pad_ptrs.numel() >= world, "symm_barrier: bad pointer table");
+  int dev = at::cuda::current_device();
+  check_rc(vb_symm_barrier(pad_ptrs.data_ptr<long>(), (int)rank, (int)world, (int)epoch, vb_status_tensor(dev).data_ptr<int>(), cur_stream()),
+           "symm_barrier");
+}
+
+void symm_reduce_scatter(const Tensor& grad_ptrs, int64_t world, int64_t shard_off, Tensor& out, Tensor& sumsq, double scale) {
+  TORCH_CHECK(grad_ptrs.scalar_type() == at::kLong && !grad_ptrs.is_cuda(), "symm_reduce_scatter: bad pointer table");
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.is_contiguous() && sumsq.scalar_type() == at::kFloat, "symm_reduce_scatter: bad out");
+  c10::cuda::CUDAGuard guard(out.device());
+  check_rc(vb_symm_reduce_scatter(grad_ptrs.data_ptr<long>(), (int)world, shard_off, out.numel(), (float)scale, out.data_ptr<float>(),
+                                  sumsq.data_ptr<float>(), cur_stream()),
+           "symm_reduce_scatter");
+}
+
+void symm_adamw_allgather(Tensor& p32, Tensor& m, Tensor& v, const Tensor& g, const Tensor& param_ptrs, int64_t world, int64_t shard_off,
+                          double lr, double b1, double b2, double eps, double wd, int64_t step, const Tensor& scalars) {
+  TORCH_CHECK(p32.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat && g.scalar_type() == at::kFloat,
+              "symm_adamw_allgather: fp32 tensors expected");
+  TORCH_CHECK(g.numel() == p32.numel() && scalars.numel() >= 2, "symm_adamw_allgather: size mismatch");
+  c10::cuda::CUDAGuard guard(p32.device());
+  check_rc(vb_symm_adamw_allgather(p32.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), g.data_ptr<float>(),
+                                   param_ptrs.data_ptr<long>(), (int)world, shard_off, p32.numel(), (float)lr, (float)b1, (float)b2,
+                                   (float)eps, (float)wd, (int)step, scalars.data_ptr<float>(), cur_stream()),
+           "symm_adamw_allgather");
+}
+}  // namespace
+
+TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
+  m.def("symm_alloc(int nbytes) -> int", &symm_alloc);
+  m.def("symm_free(int ptr) -> ()", &symm_free);
+  m.def("ipc_get_handle(int ptr) -> Tensor", &ipc_get_handle);
+  m.def("ipc_open_handle(Tensor h) -> int", &ipc_open_handle);
+  m.def("ipc_close(int ptr) -> ()", &ipc_close);
+  m.def("tensor_from_ptr(int ptr, int[] sizes, ScalarType dtype) -> Tensor", &tensor_from_ptr);
+  m.def("symm_barrier(Tensor pad_ptrs, int rank, int world, int epoch) -> ()", &symm_barrier);
+  m.def("symm_reduce_scatter(Tensor grad_ptrs, int world, int shard_off, Tensor(a!) out, Tensor(b!) sumsq, float scale) -> ()", &symm_reduce_scatter);
+  m.def("symm_adamw_allgather(Tensor(a!) p32, Tensor(b!) m, Tensor(c!) v, Tensor g, Tensor param_ptrs, int world, int shard_off, float lr, float b1, float b2, float eps, float wd, int step, Tensor scalars) -> ()", &symm_adamw_allgather);
+}

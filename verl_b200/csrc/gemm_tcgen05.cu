@@ -54,7 +54,8 @@ struct LmHeadEpi {
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
-                 const bf16* __restrict__ bias, int M, int N, int K, int ldc, int flags, int* err_word, const LmHeadEpi epi) {
+                 const bf16* __restrict__ bias, int M, int N, int K, int ldc, int flags, int* err_word, const LmHeadEpi epi,
+                 int split_k, int kb_per_split, float* __restrict__ split_ws) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -70,8 +71,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int num_m = (M + BM - 1) / BM;
   const int num_n = (N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
-  const int num_kb = (K + BK - 1) / BK;
+  const int num_kb_total = (K + BK - 1) / BK;
+  // split-K: a work unit is (output tile, K slice); partial sums go to an fp32 workspace and are reduced afterwards
+  const int num_tiles = num_m * num_n * split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -98,7 +100,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   // Tile order: groups of GROUP_M row-blocks sweep N together so a B column block stays in L2.
   constexpr int GROUP_M = 8;
-  auto tile_coords = [&](int t, int& mb, int& nb) {
+  auto tile_coords = [&](int u, int& mb, int& nb) {
+    int t = u / split_k;
     int per_group = GROUP_M * num_n;
     int g = t / per_group;
     int first_m = g * GROUP_M;
@@ -118,7 +121,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int mb, nb;
         tile_coords(t, mb, nb);
         const int m0 = mb * BM, n0 = nb * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (t % split_k) * kb_per_split;
+        const int kb1 = min(num_kb_total, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
@@ -154,7 +159,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (t % split_k) * kb_per_split;
+        const int kb1 = min(num_kb_total, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, abort_flag, err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
@@ -166,7 +173,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             //           a K step of 16 rows is 2048 B.
             uint64_t ad = A_MN ? make_sdesc_sw128(sa + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sa + k * 32, 16, 1024);
             uint64_t bd = B_MN ? make_sdesc_sw128(sb + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sb + k * 32, 16, 1024);
-            umma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+            umma_f16(d_tmem, ad, bd, idesc, ((kb - kb0) | k) != 0);
           }
           umma_commit(&empty_bar[s]);
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -287,6 +294,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (split_k > 1) {
+            // partial sum of this K slice: fp32 workspace [split][M][N]; bias / accumulate / cast happen in the reduce pass
+            float* wrow = split_ws + ((size_t)(t % split_k) * M + row) * N + col0;
+            if (col0 + 32 <= N && ((reinterpret_cast<uintptr_t>(wrow) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(wrow + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) wrow[j] = f[j];
+            }
+            continue;
+          }
           if (bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -362,12 +381,54 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// ---------------------------------------------------------------- split-K reduce
+// out[m,n] (+)= sum_s ws[s,m,n] (+ bias[n]); out is bf16 or fp32 with row stride ldc.
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, int S, int M, int N, void* __restrict__ out, int ldc,
+                                     const bf16* __restrict__ bias, int flags) {
+  const long total4 = (long)M * N / 4;
+  const bool out_f32 = flags & GEMM_OUT_F32, accum = flags & GEMM_ACCUM;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total4; i += (long)gridDim.x * blockDim.x) {
+    const long e = i * 4;
+    const int row = e / N, col = e % N;
+    float4 a = reinterpret_cast<const float4*>(ws)[i];
+    for (int s2 = 1; s2 < S; ++s2) {
+      const float4 b = reinterpret_cast<const float4*>(ws + (size_t)s2 * M * N)[i];
+      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    if (bias != nullptr) {
+      a.x += __bfloat162float(bias[col]); a.y += __bfloat162float(bias[col + 1]);
+      a.z += __bfloat162float(bias[col + 2]); a.w += __bfloat162float(bias[col + 3]);
+    }
+    if (out_f32) {
+      float* o = reinterpret_cast<float*>(out) + (size_t)row * ldc + col;
+      if (accum) { a.x += o[0]; a.y += o[1]; a.z += o[2]; a.w += o[3]; }
+      o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
+    } else {
+      bf16* o = reinterpret_cast<bf16*>(out) + (size_t)row * ldc + col;
+      if (accum) {
+        a.x += __bfloat162float(o[0]); a.y += __bfloat162float(o[1]); a.z += __bfloat162float(o[2]); a.w += __bfloat162float(o[3]);
+      }
+      o[0] = __float2bfloat16(a.x); o[1] = __float2bfloat16(a.y); o[2] = __float2bfloat16(a.z); o[3] = __float2bfloat16(a.w);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- host launcher
 static int g_num_sms = 0;
 
+static int num_sms() {
+  if (g_num_sms == 0) {
+    int dev;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_num_sms;
+}
+
 template <int BN, bool A_MN, bool B_MN, int EPI = EPI_STORE>
 static int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb,
-                       int ldc, int flags, int* err_word, cudaStream_t stream, const LmHeadEpi& epi = LmHeadEpi{}) {
+                       int ldc, int flags, int* err_word, cudaStream_t stream, const LmHeadEpi& epi = LmHeadEpi{},
+                       int split_k = 1, float* split_ws = nullptr) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmA, tmB;
   int rc;
@@ -384,16 +445,55 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
     if (e != cudaSuccess) return -10;
     attr_set = true;
   }
-  if (g_num_sms == 0) {
-    int dev;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
-  int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  const int num_kb = (K + BK - 1) / BK;
+  if (split_k < 1) split_k = 1;
+  int kb_per = (num_kb + split_k - 1) / split_k;
+  split_k = (num_kb + kb_per - 1) / kb_per;          // no empty slices
+  if (split_k > 1 && split_ws == nullptr) return -6;
+  int units = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * split_k;
+  int grid = units < num_sms() ? units : num_sms();
   kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags,
-                                                err_word, epi);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+                                                err_word, epi, split_k, kb_per, split_ws);
+  if (cudaGetLastError() != cudaSuccess) return -11;
+  if (split_k > 1) {
+    long total4 = (long)M * N / 4;
+    int blocks = (int)((total4 + 255) / 256);
+    if (blocks > num_sms() * 8) blocks = num_sms() * 8;
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(split_ws, split_k, M, N, C, ldc, reinterpret_cast<const bf16*>(bias), flags);
+    if (cudaGetLastError() != cudaSuccess) return -12;
+  }
+  return 0;
+}
+
+// Cost model for small problems that cannot fill the machine with 128x256 tiles: pick (tile width, K splits) minimising
+// waves x (bytes staged per unit / per-SM fill rate + fixed cost) + the reduce pass.
+static void pick_tile_and_split(int M, int N, int K, bool b_mn, int* bn_out, int* split_out) {
+  const int sms = num_sms();
+  const int num_m = (M + BM - 1) / BM;
+  const int num_kb = (K + BK - 1) / BK;
+  double best = 1e30;
+  int best_bn = 256, best_s = 1;
+  const int bns[4] = {256, 128, 64, 32};
+  for (int bi = 0; bi < 4; ++bi) {
+    const int bn = bns[bi];
+    if (b_mn && bn < 64) continue;
+    const long tiles = (long)num_m * ((N + bn - 1) / bn);
+    for (int s = 1; s <= 16; ++s) {
+      if (s > 1 && (N % 4 != 0)) break;                 // the reduce pass is vectorised by 4 columns
+      const int kb_per = (num_kb + s - 1) / s;
+      if (s > 1 && kb_per < 4) break;
+      const int s_eff = (num_kb + kb_per - 1) / kb_per;
+      const long units = tiles * s_eff;
+      const double waves = (double)((units + sms - 1) / sms);
+      const double unit_us = kb_per * (double)(A_TILE_BYTES + bn * BK * 2) / 100e3 /* ~100 GB/s per SM */ + 2.5;
+      double t = waves * unit_us;
+      if (s_eff > 1) t += 3.0 + 2.0 * s_eff * (double)M * N * 4 / 5e6 /* ~5 TB/s */;
+      if (t < best) { best = t; best_bn = bn; best_s = s_eff; }
+      if (units >= 4L * sms) break;
+    }
+  }
+  *bn_out = best_bn;
+  *split_out = best_s;
 }
 
 }  // namespace vb
@@ -401,24 +501,34 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
 // C[M,N] (+)= op(A) op(B) (+ bias). a_mn / b_mn: 0 = K contiguous ([M,K] / [N,K] row-major), 1 = M/N contiguous
 // ([K,M] / [K,N] row-major). lda/ldb/ldc are row strides in elements. Requirements: A, B 16-byte aligned,
 // lda/ldb multiples of 8. `bn` = 0 picks the N tile from the problem shape.
+extern "C" void vb_gemm_plan(int M, int N, int K, int b_mn, int bn_req, int* bn, int* split_k) {
+  using namespace vb;
+  *split_k = 1;
+  if (bn_req != 0) { *bn = bn_req; return; }
+  const long big_tiles = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
+  if (big_tiles >= num_sms()) { *bn = 256; return; }
+  pick_tile_and_split(M, N, K, b_mn != 0, bn, split_k);
+}
+
+// split_k > 1 needs split_ws with split_k * M * N floats (see vb_gemm_plan); split_k = 1 ignores it.
 extern "C" int vb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
-                            int ldb, int ldc, int a_mn, int b_mn, int out_f32, int accumulate, int bn, int* err_word,
-                            cudaStream_t stream) {
+                            int ldb, int ldc, int a_mn, int b_mn, int out_f32, int accumulate, int bn, int split_k,
+                            float* split_ws, int* err_word, cudaStream_t stream) {
   using namespace vb;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) return -3;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -4;
   int flags = (out_f32 ? GEMM_OUT_F32 : 0) | (accumulate ? GEMM_ACCUM : 0);
   if (bn == 0) {
-    // Prefer the widest tile that still yields at least ~one wave of CTAs; narrow tiles keep small-M
-    // (decode) problems spread over all SMs so the weight stream can saturate HBM.
-    int num_m = (M + BM - 1) / BM;
-    bn = 256;
-    while (bn > 32 && (long)num_m * ((N + bn - 1) / bn) < 148) bn >>= 1;
-    if (b_mn && bn < 64) bn = 64;
+    int s_auto;
+    vb_gemm_plan(M, N, K, b_mn, 0, &bn, &s_auto);
+    if (split_k == 0) split_k = s_auto;
   }
+  if (split_k < 1) split_k = 1;
+  if (split_k > 1 && (N % 4 != 0)) split_k = 1;
+  if (b_mn && bn < 64) bn = 64;
 #define VB_LAUNCH(BN_, AM_, BM_) \
-  return launch_gemm<BN_, AM_, BM_>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream)
+  return launch_gemm<BN_, AM_, BM_>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream, LmHeadEpi{}, split_k, split_ws)
 #define VB_DISPATCH_BN(AM_, BM_)                   \
   switch (bn) {                                    \
     case 256: VB_LAUNCH(256, AM_, BM_);            \

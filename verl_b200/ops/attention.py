@@ -67,12 +67,12 @@ def flash_attention_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, n_heads:
 
 def paged_decode_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, kv_lens: torch.Tensor,
                            scale: float, num_splits: int = 1, max_kv_len: int = 0, workspace: Optional[torch.Tensor] = None,
-                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           out: Optional[torch.Tensor] = None, impl: int = 0) -> torch.Tensor:
     """One query token per sequence against a paged KV cache layer [num_blocks, 2, Hkv, 64, 128]."""
     if out is None:
         out = torch.empty_like(q)
     if q.is_cuda and q.dtype == torch.bfloat16 and _ext.available():
-        _ext.ops().attn_paged_decode(q, cache, block_table, kv_lens, out, scale, num_splits, max_kv_len, workspace)
+        _ext.ops().attn_paged_decode(q, cache, block_table, kv_lens, out, scale, num_splits, max_kv_len, workspace, impl)
         return out
     return paged_decode_attention_ref(q, cache, block_table, kv_lens, scale, out)
 

@@ -207,6 +207,20 @@ class FSDPEngine(BaseEngine):
         if self.world > 1:
             # every rank must start from identical weights (rank 0's)
             dist.broadcast(self.store.flat, src=0)
+        self._symm_params = self._symm_grads = None
+        use_symm = bool(cfg_get(self.engine_config, "use_symmetric_memory", True)) and os.environ.get("VERL_B200_COMM", "native") == "native"
+        if (use_symm and self.world > 1 and self.fsdp_size == self.world and self.store.flat.is_cuda and self.store.flat.dtype == torch.bfloat16
+                and _ext.available() and not self.forward_only and not self._param_offload):
+            from verl_b200.parallel.symm_mem import SymmetricBuffer
+            from verl_b200.single_controller.spmd import init_spmd_process_group
+
+            host = init_spmd_process_group()
+            s = self.store
+            self._symm_params = SymmetricBuffer(s.total * 2, host_group=host)
+            new_flat = self._symm_params.tensor(torch.bfloat16, s.total)
+            new_flat.copy_(s.flat)
+            s.rebind(new_flat)
+            self._symm_grads = SymmetricBuffer(s.total * 4, host_group=host)
         if self.sp_size > 1:
             self.model.sp_group = self.sp_group
         if not self.forward_only:
@@ -409,7 +423,7 @@ class FSDPEngine(BaseEngine):
             info["batch_num_tokens"] = cnt[0]
             info["global_batch_size"] = cnt[1]
             if not forward_only:
-                self.store.alloc_grads()
+                self._alloc_grads()
         outputs: dict[str, list[torch.Tensor]] = {}
         metrics: dict[str, Metric] = {}
         losses = []
@@ -440,8 +454,17 @@ class FSDPEngine(BaseEngine):
         model_output = {k: restore_dynamic_batch(torch.cat(v, 0), mb_indices) for k, v in outputs.items()}
         return {"model_output": model_output, "loss": losses, "metrics": metrics}
 
+    def _alloc_grads(self):
+        s = self.store
+        if self._symm_grads is not None and s.grad is None:
+            s.grad = self._symm_grads.tensor(torch.float32, s.total)
+            for p, o in zip(s.params, s.offsets):
+                p.main_grad = s.grad[o : o + p.numel()].view(p.shape)
+        else:
+            s.alloc_grads()
+
     def optimizer_zero_grad(self):
-        self.store.alloc_grads()
+        self._alloc_grads()
         self.store.zero_grads()
 
     # ------------------------------------------------------------------ optimizer step
@@ -450,6 +473,8 @@ class FSDPEngine(BaseEngine):
         s = self.store
         assert s.grad is not None, "optimizer_step without gradients"
         W = self.fsdp_size
+        if self._symm_grads is not None:
+            return self._optimizer_step_fused()
         # 1. reduce gradients: average over data-parallel ranks, keep only this rank's shard
         if self.world > 1:
             if s.grad.is_cuda:
@@ -506,6 +531,31 @@ class FSDPEngine(BaseEngine):
                 s.flat.copy_(torch.cat(parts))
         s.zero_grads()
         return grad_norm
+
+    @torch.no_grad()
+    def _optimizer_step_fused(self) -> float:
+        """Reduce-scatter (+1/W, +Σg²) by peer loads → scalar all-reduce → AdamW whose epilogue stores the new bf16
+        values into every rank's parameter buffer (the all-gather). Three kernels and two device barriers in total."""
+        s, o = self.store, _ext.ops()
+        W, off = self.world, self.rank * s.shard_size
+        if self.grad_shard is None:
+            self.grad_shard = torch.empty(s.shard_size, dtype=torch.float32, device=self.device)
+        self._symm_grads.barrier()                       # every rank has finished writing its gradients
+        self._sumsq.zero_()
+        o.symm_reduce_scatter(self._symm_grads.table(), W, off, self.grad_shard, self._sumsq, 1.0 / W)
+        dist.all_reduce(self._sumsq, group=self.fsdp_group)
+        self.step_count += 1
+        lr = self.current_lr()
+        o.clip_coef_(self._sumsq, self.clip_grad, self._scalars)
+        o.symm_adamw_allgather(self.master, self.exp_avg, self.exp_avg_sq, self.grad_shard, self._symm_params.table(), W, off, lr,
+                               self.beta1, self.beta2, self.adam_eps, self.weight_decay, self.step_count, self._scalars)
+        self._symm_params.barrier()                      # all shards of the new parameters have landed everywhere
+        sc = self._scalars.tolist()
+        if sc[1] != 0.0:
+            self.step_count -= 1
+            print(f"WARN: rank {self.rank} grad_norm is not finite: {sc[2]}; skipping optimizer step")
+        s.zero_grads()
+        return sc[2]
 
     def lr_scheduler_step(self) -> float:
         self.sched_step += 1

@@ -134,7 +134,8 @@ class TrainingWorker(Worker):
                         all_metrics[f"{self.role}/lr"] = Metric(AggregationType.MEAN, eng.lr_scheduler_step())
         if torch.cuda.is_available():
             torch.cuda.synchronize()
-        eng.store.free_grads()   # the fp32 gradient buffer is only needed inside an update; the KV cache wants the room
+        if getattr(eng, "_symm_grads", None) is None:
+            eng.store.free_grads()   # the fp32 gradient buffer is only needed inside an update; the KV cache wants the room
         dt = time.perf_counter() - t0
         n_tok = int(data.batch["attention_mask"].sum()) * epochs
         return self._postprocess_metrics(all_metrics, n_tok, dt, forward_only=False)
