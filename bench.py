@@ -213,7 +213,7 @@ def main():
     ap.add_argument("--max-prompt", type=int, default=512)
     ap.add_argument("--response-length", type=int, default=1024)
     ap.add_argument("--token-budget", type=int, default=16384)
-    ap.add_argument("--kv-util", type=float, default=0.25)
+    ap.add_argument("--kv-util", type=float, default=0.3)
     ap.add_argument("--grad-ckpt", type=int, default=1)
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()

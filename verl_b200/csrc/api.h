@@ -53,6 +53,12 @@ int vb_attn_varlen_bwd(const void* q, const void* k, const void* v, long ld, con
                        long stat_stride, float* dq_acc, void* dq, void* dk, void* dv, long ld_d, float scale, int* err_word,
                        cudaStream_t st);
 
+int vb_gemm_allgather(int which, const long* seg_ptrs, int world, int seg_rows, int ld_seg, const void* other, int ld_other, void* C,
+                      const void* bias, int M, int N, int K, int ldc, int* err_word, cudaStream_t st);
+int vb_gemm_peer_scatter(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int ld_slot, const long* out_ptrs,
+                         int rank, int world, int rows_per_owner, long slot_elems, int* err_word, cudaStream_t st);
+int vb_slots_reduce(const void* slots, int world, long slot_elems, long rows, int cols, int ld, const void* residual, void* out,
+                    int ld_out, cudaStream_t st);
 long vb_symm_alloc(long nbytes);
 int vb_symm_free(long ptr);
 int vb_ipc_get_handle(long ptr, unsigned char* out64);

@@ -5,8 +5,9 @@
 //   S^T[kv, q] = K[kv, :] . Q[q, :]        tcgen05.mma M = 128 KV rows (TMEM lanes), N = 16 query heads
 //   O^T[d, q]  = sum_kv V[kv, d] P[q, kv]   tcgen05.mma M = 128 head dims (V consumed MN-major), N = 16
 // Every thread owns one KV row (softmax numerators) resp. one head-dim row (output) and touches 16 values per tile;
-// row max / sum over the KV axis are warp-shuffle + shared-memory reductions. K/V tiles (128 rows) stream through a
-// 3-stage TMA ring straight from the paged cache via the block table. Optional split-KV writes partials merged by
+// row max / sum over the KV axis are warp-shuffle + shared-memory reductions. K/V tiles (128 rows) are fetched by TMA
+// straight from the paged cache via the block table; the kernel is small enough (75 KB shared memory, 32 TMEM columns)
+// for three CTAs per SM, which is what overlaps loads with the serial MMA -> softmax -> MMA chain of each tile. Optional split-KV writes partials merged by
 // attn_merge_kernel (same layout as the generic paged path).
 #include "common.cuh"
 #include "tma_host.h"
@@ -18,7 +19,7 @@ constexpr int DT = 128;                 // kv rows per tile
 constexpr int DQ = 16;                  // padded query heads per kv head
 constexpr int D_TILE = DT * DD * 2;     // 32 KB
 constexpr int D_HALF = DT * 64 * 2;     // 16 KB : one 64-column swizzle atom of a K/V tile
-constexpr int D_STAGES = 3;
+constexpr int D_STAGES = 1;             // one tile in flight per CTA; three CTAs share an SM and hide each other's TMA latency
 constexpr int D_QBYTES = DQ * DD * 2;   // 4 KB : two atoms of 16 rows x 128 B
 constexpr int D_SMEM = D_STAGES * 2 * D_TILE + 2 * D_QBYTES + 1024 + 512;
 
@@ -36,7 +37,7 @@ struct DecodeParams {
   int* err_word;
 };
 
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(128, 3)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV, const DecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -101,8 +102,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int qy = b * p.n_q_heads + kvh * p.group;
     tma_load_2d(sQ, &tmQ, 0, qy, q_bar);
     tma_load_2d(sQ + DQ * 128, &tmQ, 64, qy, q_bar);
-    load_kv(0);
-    if (n_tiles > 1) load_kv(1);
+    for (int j = 0; j < D_STAGES && j < n_tiles; ++j) load_kv(j);
   }
 
   float m_run[DQ], l_run[DQ], o_acc[DQ];
@@ -119,7 +119,6 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int stage = j % D_STAGES;
     const uint32_t kv_ph = (j / D_STAGES) & 1;
     const uint32_t it_ph = j & 1;
-    if (tid == 0 && j + 2 < n_tiles) load_kv(j + 2);      // its stage was released by the o_bar wait of iteration j-1
     if (!mbar_wait(&kv_bar[stage], kv_ph, abort_flag, p.err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
     uint8_t* sK = sKV + stage * 2 * D_TILE;
     uint8_t* sV = sK + D_TILE;
@@ -193,6 +192,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int q = 0; q < DQ; ++q) l_run[q] = l_run[q] * alpha[q] + red[q] + red[DQ + q] + red[2 * DQ + q] + red[3 * DQ + q];
     if (!mbar_wait(o_bar, it_ph, abort_flag, p.err_word, VB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
     tc_fence_after();
+    if (tid == 0 && j + D_STAGES < n_tiles) load_kv(j + D_STAGES);   // this tile's stage is free once its PV product is done
     uint32_t ov[DQ];
     tmem_ld_32x32b_x16(tm_O + lane_off, ov);
     tmem_ld_wait();

@@ -82,3 +82,56 @@ TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
   m.def("symm_reduce_scatter(Tensor grad_ptrs, int world, int shard_off, Tensor(a!) out, Tensor(b!) sumsq, float scale) -> ()", &symm_reduce_scatter);
   m.def("symm_adamw_allgather(Tensor(a!) p32, Tensor(b!) m, Tensor(c!) v, Tensor g, Tensor param_ptrs, int world, int shard_off, float lr, float b1, float b2, float eps, float wd, int step, Tensor scalars) -> ()", &symm_adamw_allgather);
 }
+
+namespace {
+// C = gather(A segments) @ B^T : a_ptrs int64 CPU [world] pointers to [seg_rows, K] bf16 segments (row stride K).
+void gemm_allgather_a(const Tensor& a_ptrs, int64_t seg_rows, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias) {
+  TORCH_CHECK(a_ptrs.scalar_type() == at::kLong && !a_ptrs.is_cuda(), "gemm_allgather_a: pointer table must be a CPU int64 tensor");
+  TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.dim() == 2 && b.stride(1) == 1, "gemm_allgather_a: bad b");
+  const int world = a_ptrs.numel(), K = b.size(1), N = b.size(0), M = seg_rows * world;
+  TORCH_CHECK(out.size(0) == M && out.size(1) == N && out.scalar_type() == at::kBFloat16 && out.stride(1) == 1, "gemm_allgather_a: bad out");
+  const void* bias_p = (bias.has_value() && bias->defined()) ? bias->data_ptr() : nullptr;
+  c10::cuda::CUDAGuard guard(b.device());
+  check_rc(vb_gemm_allgather(0, a_ptrs.data_ptr<long>(), world, (int)seg_rows, K, b.data_ptr(), (int)b.stride(0), out.data_ptr(), bias_p, M, N, K,
+                             (int)out.stride(0), vb_status_tensor(b.get_device()).data_ptr<int>(), cur_stream()),
+           "gemm_allgather_a");
+}
+
+// C = A @ gather(B segments)^T : weight rows sharded over ranks (ZeRO-3 style all-gather fused into the consuming GEMM).
+void gemm_allgather_b(const Tensor& a, const Tensor& b_ptrs, int64_t seg_rows, Tensor& out, const c10::optional<Tensor>& bias) {
+  TORCH_CHECK(b_ptrs.scalar_type() == at::kLong && !b_ptrs.is_cuda(), "gemm_allgather_b: pointer table must be a CPU int64 tensor");
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && a.dim() == 2 && a.stride(1) == 1, "gemm_allgather_b: bad a");
+  const int world = b_ptrs.numel(), K = a.size(1), M = a.size(0), N = seg_rows * world;
+  TORCH_CHECK(out.size(0) == M && out.size(1) == N && out.scalar_type() == at::kBFloat16 && out.stride(1) == 1, "gemm_allgather_b: bad out");
+  const void* bias_p = (bias.has_value() && bias->defined()) ? bias->data_ptr() : nullptr;
+  c10::cuda::CUDAGuard guard(a.device());
+  check_rc(vb_gemm_allgather(1, b_ptrs.data_ptr<long>(), world, (int)seg_rows, K, a.data_ptr(), (int)a.stride(0), out.data_ptr(), bias_p, M, N, K,
+                             (int)out.stride(0), vb_status_tensor(a.get_device()).data_ptr<int>(), cur_stream()),
+           "gemm_allgather_b");
+}
+
+void gemm_peer_scatter(const Tensor& a, const Tensor& b, const Tensor& out_ptrs, int64_t rank, int64_t rows_per_owner, int64_t slot_elems) {
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_peer_scatter: bad operands");
+  TORCH_CHECK(out_ptrs.scalar_type() == at::kLong && !out_ptrs.is_cuda(), "gemm_peer_scatter: pointer table must be a CPU int64 tensor");
+  const int M = a.size(0), K = a.size(1), N = b.size(0), world = out_ptrs.numel();
+  c10::cuda::CUDAGuard guard(a.device());
+  check_rc(vb_gemm_peer_scatter(a.data_ptr(), b.data_ptr(), M, N, K, (int)a.stride(0), (int)b.stride(0), N, out_ptrs.data_ptr<long>(), (int)rank,
+                                world, (int)rows_per_owner, slot_elems, vb_status_tensor(a.get_device()).data_ptr<int>(), cur_stream()),
+           "gemm_peer_scatter");
+}
+
+void slots_reduce(const Tensor& slots, int64_t world, int64_t slot_elems, int64_t rows, int64_t cols, const c10::optional<Tensor>& residual, Tensor& out) {
+  TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "slots_reduce: bf16 tensors expected");
+  const void* res = (residual.has_value() && residual->defined()) ? residual->data_ptr() : nullptr;
+  c10::cuda::CUDAGuard guard(slots.device());
+  check_rc(vb_slots_reduce(slots.data_ptr(), (int)world, slot_elems, rows, (int)cols, (int)cols, res, out.data_ptr(), (int)out.stride(0), cur_stream()),
+           "slots_reduce");
+}
+}  // namespace
+
+TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
+  m.def("gemm_allgather_a(Tensor a_ptrs, int seg_rows, Tensor b, Tensor(a!) out, Tensor? bias) -> ()", &gemm_allgather_a);
+  m.def("gemm_allgather_b(Tensor a, Tensor b_ptrs, int seg_rows, Tensor(a!) out, Tensor? bias) -> ()", &gemm_allgather_b);
+  m.def("gemm_peer_scatter(Tensor a, Tensor b, Tensor out_ptrs, int rank, int rows_per_owner, int slot_elems) -> ()", &gemm_peer_scatter);
+  m.def("slots_reduce(Tensor slots, int world, int slot_elems, int rows, int cols, Tensor? residual, Tensor(a!) out) -> ()", &slots_reduce);
+}

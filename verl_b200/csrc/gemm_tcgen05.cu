@@ -32,7 +32,23 @@ struct GemmCfg {
 };
 
 enum : int { GEMM_OUT_F32 = 1, GEMM_ACCUM = 2 };
-enum : int { EPI_STORE = 0, EPI_LOGPROB = 1, EPI_DLOGITS = 2 };
+enum : int { EPI_STORE = 0, EPI_LOGPROB = 1, EPI_DLOGITS = 2, EPI_PEER = 3 };
+
+// Multi-GPU arguments. Operand segmentation: rows of A (seg_mode 1) or of B (seg_mode 2) are split into n_seg equal
+// segments, each living in a different rank's memory and described by its own tensor map; the producer warp reads a
+// tile from whichever rank owns it (plain TMA load from peer memory, no multicast) -> all-gather fused into the GEMM.
+// EPI_PEER epilogue: the bf16 output tile is stored into symmetric buffers of other ranks, slot `rank` of each
+// destination (all ranks when rows_per_owner == 0 -> all-reduce input; the owner of the row block otherwise ->
+// reduce-scatter input). A barrier and a slot-sum kernel finish the collective.
+constexpr int MAX_TP = 8;
+struct DistArgs {
+  int seg_mode, seg_rows, n_seg;
+  int rank, world;
+  int rows_per_owner;
+  long slot_elems;
+  void* peer_out[MAX_TP];
+  CUtensorMap seg[MAX_TP];
+};
 
 // Extra epilogue inputs of the fused lm_head variants (rows = tokens, columns = vocabulary entries).
 struct LmHeadEpi {
@@ -55,7 +71,7 @@ template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
                  const bf16* __restrict__ bias, int M, int N, int K, int ldc, int flags, int* err_word, const LmHeadEpi epi,
-                 int split_k, int kb_per_split, float* __restrict__ split_ws) {
+                 int split_k, int kb_per_split, float* __restrict__ split_ws, const __grid_constant__ DistArgs dist) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -130,13 +146,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_2d(sa, &tmA, k0, m0, &full_bar[s]);
+            if (dist.seg_mode == 1) tma_load_2d(sa, &dist.seg[m0 / dist.seg_rows], k0, m0 % dist.seg_rows, &full_bar[s]);
+            else tma_load_2d(sa, &tmA, k0, m0, &full_bar[s]);
           } else {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * (BK * 128), &tmA, m0 + 64 * i, k0, &full_bar[s]);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &tmB, k0, n0, &full_bar[s]);
+            if (dist.seg_mode == 2) tma_load_2d(sb, &dist.seg[n0 / dist.seg_rows], k0, n0 % dist.seg_rows, &full_bar[s]);
+            else tma_load_2d(sb, &tmB, k0, n0, &full_bar[s]);
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * (BK * 128), &tmB, n0 + 64 * i, k0, &full_bar[s]);
@@ -280,6 +298,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             } else {
               for (int j = 0; j < 32; ++j)
                 if (col0 + j < N) crow[j] = __float2bfloat16(f[j]);
+            }
+          }
+        }
+      } else if constexpr (EPI == EPI_PEER) {
+        int r_lo = 0, r_hi = dist.world;
+        long row_local = row;
+        if (dist.rows_per_owner > 0) {
+          r_lo = row / dist.rows_per_owner;
+          r_hi = r_lo + 1;
+          row_local = row - (long)r_lo * dist.rows_per_owner;
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, v);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (row < M && col0 + 32 <= N) {
+            uint4 o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              o[j].x = pack_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1]));
+              o[j].y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+              o[j].z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+              o[j].w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            }
+            for (int r = r_lo; r < r_hi; ++r) {
+              bf16* dst = reinterpret_cast<bf16*>(dist.peer_out[r]) + dist.rank * dist.slot_elems + row_local * ldc + col0;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = o[j];
             }
           }
         }
@@ -428,8 +476,10 @@ static int num_sms() {
 template <int BN, bool A_MN, bool B_MN, int EPI = EPI_STORE>
 static int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb,
                        int ldc, int flags, int* err_word, cudaStream_t stream, const LmHeadEpi& epi = LmHeadEpi{},
-                       int split_k = 1, float* split_ws = nullptr) {
+                       int split_k = 1, float* split_ws = nullptr, const DistArgs* dist_in = nullptr) {
   using Cfg = GemmCfg<BN>;
+  static const DistArgs no_dist = {};
+  const DistArgs& dist = dist_in ? *dist_in : no_dist;
   CUtensorMap tmA, tmB;
   int rc;
   if (!A_MN) rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK);
@@ -453,7 +503,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   int units = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * split_k;
   int grid = units < num_sms() ? units : num_sms();
   kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags,
-                                                err_word, epi, split_k, kb_per, split_ws);
+                                                err_word, epi, split_k, kb_per, split_ws, dist);
   if (cudaGetLastError() != cudaSuccess) return -11;
   if (split_k > 1) {
     long total4 = (long)M * N / 4;
@@ -623,4 +673,118 @@ extern "C" int vb_lmhead_dlogits(const void* h, const void* W, const long* label
   epi.col_offset = col_offset;
   epi.lse = lse; epi.ent = ent; epi.g_lp = g_lp; epi.g_ent = g_ent;
   return launch_gemm<LM_BN, false, false, EPI_DLOGITS>(h, W, dlogits, nullptr, M, Vc, K, ldh, ldw, ldd, 0, err_word, stream, epi);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// GEMMs fused with tensor/data-parallel collectives over NVLink peer memory.
+namespace vb {
+
+// out[r, c] = sum_s slots[s][r, c] (+ residual[r, c]); bf16 in/out, fp32 accumulation. cols % 8 == 0.
+__global__ void slots_reduce_kernel(const bf16* __restrict__ slots, int world, long slot_elems, long rows, int cols, int ld,
+                                    const bf16* __restrict__ residual, bf16* __restrict__ out, int ld_out) {
+  const int vpr = cols / 8;
+  const long total = rows * vpr;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / vpr;
+    const int c = (i % vpr) * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < world; ++s) {
+      const uint4 v = *reinterpret_cast<const uint4*>(slots + s * slot_elems + r * ld + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+    if (residual != nullptr) {
+      const uint4 v = *reinterpret_cast<const uint4*>(residual + r * ld_out + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + r * ld_out + c) = o;
+  }
+}
+
+template <int EPI>
+static int launch_dist(int bn, const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb, int ldc,
+                       int* err_word, cudaStream_t st, const DistArgs& d) {
+  switch (bn) {
+    case 256: return launch_gemm<256, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
+    case 128: return launch_gemm<128, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
+    case 64: return launch_gemm<64, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
+    default: return -5;
+  }
+}
+
+static int pick_bn_dist(int M, int N) {
+  int bn = 256;
+  const int num_m = (M + BM - 1) / BM;
+  while (bn > 64 && (long)num_m * ((N + bn - 1) / bn) < num_sms()) bn >>= 1;
+  return bn;
+}
+
+}  // namespace vb
+
+// All-gather fused into the GEMM: C[M,N] = A B^T (+bias) where the rows of A (which = 0) or of B (which = 1) are split in
+// `world` equal segments; seg_ptrs[r] is rank r's segment ([seg_rows, K] bf16, row stride ld_seg) reachable from this GPU.
+extern "C" int vb_gemm_allgather(int which, const long* seg_ptrs, int world, int seg_rows, int ld_seg, const void* other, int ld_other,
+                                 void* C, const void* bias, int M, int N, int K, int ldc, int* err_word, cudaStream_t st) {
+  using namespace vb;
+  if (world > MAX_TP || world < 1) return -2;
+  const int rows_total = which == 0 ? M : N;
+  if (seg_rows * world != rows_total || (ld_seg & 7) || (ld_other & 7)) return -4;
+  const int bn = pick_bn_dist(M, N);
+  const int tile_rows = which == 0 ? BM : bn;
+  if (seg_rows % tile_rows != 0) return -6;      // a tile must not straddle two ranks' segments
+  DistArgs d = {};
+  d.seg_mode = which == 0 ? 1 : 2;
+  d.seg_rows = seg_rows;
+  d.n_seg = world;
+  for (int r = 0; r < world; ++r) {
+    if (make_tmap_2d(&d.seg[r], reinterpret_cast<const void*>(seg_ptrs[r]), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, seg_rows, K, ld_seg, tile_rows, BK))
+      return -1;
+  }
+  const void* A = which == 0 ? reinterpret_cast<const void*>(seg_ptrs[0]) : other;
+  const void* B = which == 0 ? other : reinterpret_cast<const void*>(seg_ptrs[0]);
+  const int lda = which == 0 ? ld_seg : ld_other, ldb = which == 0 ? ld_other : ld_seg;
+  // the unsegmented maps built by the launcher for the segmented operand are never used; give them legal extents
+  const int Mm = which == 0 ? seg_rows : M, Nn = which == 1 ? seg_rows : N;
+  (void)Mm; (void)Nn;
+  return launch_dist<EPI_STORE>(bn, A, B, C, bias, M, N, K, lda, ldb, ldc, err_word, st, d);
+}
+
+// GEMM whose epilogue scatters the bf16 result into peers' symmetric slot buffers (see DistArgs). rows_per_owner == 0:
+// every rank receives the whole [M,N] partial (all-reduce); > 0: only the owner of each row block (reduce-scatter).
+extern "C" int vb_gemm_peer_scatter(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int ld_slot,
+                                    const long* out_ptrs, int rank, int world, int rows_per_owner, long slot_elems, int* err_word,
+                                    cudaStream_t st) {
+  using namespace vb;
+  if (world > MAX_TP || (N % 32) != 0 || (ld_slot & 7)) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -4;
+  DistArgs d = {};
+  d.rank = rank; d.world = world; d.rows_per_owner = rows_per_owner; d.slot_elems = slot_elems;
+  for (int r = 0; r < world; ++r) d.peer_out[r] = reinterpret_cast<void*>(out_ptrs[r]);
+  return launch_dist<EPI_PEER>(pick_bn_dist(M, N), A, B, nullptr, nullptr, M, N, K, lda, ldb, ld_slot, err_word, st, d);
+}
+
+extern "C" int vb_slots_reduce(const void* slots, int world, long slot_elems, long rows, int cols, int ld, const void* residual,
+                               void* out, int ld_out, cudaStream_t st) {
+  using namespace vb;
+  if (cols % 8) return -2;
+  long total = rows * (cols / 8);
+  if (total == 0) return 0;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > num_sms() * 8) blocks = num_sms() * 8;
+  slots_reduce_kernel<<<blocks, 256, 0, st>>>((const bf16*)slots, world, slot_elems, rows, cols, ld, (const bf16*)residual, (bf16*)out, ld_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -1,0 +1,192 @@
+"""Micro-benchmarks of the sm_100a kernels: CUDA-event timing after warm-up with an L2 flush between iterations,
+reported as achieved TFLOP/s or GB/s and as a fraction of the measured machine peaks (``MEASURED_PEAKS.json`` at the
+repository root: cuBLAS bf16 burst throughput and STREAM-style copy bandwidth; fallbacks 1590 TFLOP/s and 6650 GB/s).
+
+    python -m verl_b200.ops.kernel_bench gemm --m 8192 --n 8192 --k 4096
+    python -m verl_b200.ops.kernel_bench all
+
+The same entry point is what the committed ``profiles/*.md`` summaries were captured with (under ``ncu``, one kernel,
+small case).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "of measured"
+    return 1590.0, 6650.0, "of fallback"
+
+
+def timeit(fn, iters=10, warmup=3, flush=True):
+    buf = torch.empty(64 * 1024 * 1024, device="cuda", dtype=torch.float32) if flush else None   # 256 MB > L2
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            buf.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def report(name, ms, flops=None, bytes_=None):
+    tf, gbs, tag = peaks()
+    msg = f"{name}: {ms * 1e3:.1f} us"
+    if flops:
+        a = flops / ms / 1e9
+        msg += f"  {a:.0f} TFLOP/s ({a / tf:.2f} {tag} cuBLAS bf16)"
+    if bytes_:
+        a = bytes_ / ms / 1e6
+        msg += f"  {a:.0f} GB/s ({a / gbs:.2f} {tag} copy bandwidth)"
+    print(msg, flush=True)
+
+
+def bench_gemm(a):
+    from verl_b200.ops import _ext
+
+    o = _ext.ops()
+    M, N, K = a.m, a.n, a.k
+    x = (torch.randn(K, M, device="cuda") if a.a_mn else torch.randn(M, K, device="cuda")).bfloat16()
+    w = (torch.randn(K, N, device="cuda") if a.b_mn else torch.randn(N, K, device="cuda")).bfloat16()
+    out = torch.empty(M, N, device="cuda", dtype=torch.float32 if a.f32 else torch.bfloat16)
+    ms = timeit(lambda: o.gemm(x, w, out, None, a.a_mn, a.b_mn, False, a.bn), a.iters)
+    report(f"gemm M={M} N={N} K={K} a_mn={a.a_mn} b_mn={a.b_mn}", ms, flops=2.0 * M * N * K)
+    if a.compare:
+        A = x.t() if a.a_mn else x
+        B = w if a.b_mn else w.t()
+        ms2 = timeit(lambda: torch.matmul(A, B), a.iters)
+        report("  cuBLAS (torch.matmul) same shape", ms2, flops=2.0 * M * N * K)
+
+
+def bench_attn(a, backward=False):
+    from verl_b200 import ops
+
+    Hq, Hkv, D = a.heads, a.kv_heads, 128
+    lens = [a.seqlen] * a.batch
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    cud = cu.cuda()
+    qkv = (0.5 * torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda")).bfloat16().requires_grad_(backward)
+    fl = sum(2 * 2 * L * L / 2 * D * Hq for L in lens)
+    if not backward:
+        with torch.no_grad():
+            ms = timeit(lambda: ops.attention_varlen(qkv, cud, Hq, Hkv, D, a.seqlen, cu), a.iters)
+        report(f"attention fwd T={T} L={a.seqlen} {Hq}/{Hkv} heads (causal FLOPs)", ms, flops=fl)
+    else:
+        out = ops.attention_varlen(qkv, cud, Hq, Hkv, D, a.seqlen, cu)
+        dout = torch.randn_like(out)
+        ms = timeit(lambda: torch.autograd.grad(out, qkv, dout, retain_graph=True), a.iters)
+        report(f"attention bwd T={T} L={a.seqlen} {Hq}/{Hkv} heads (causal FLOPs x2.5)", ms, flops=2.5 * fl)
+
+
+def bench_lmhead(a):
+    from verl_b200 import ops
+
+    M, V, K = a.m, a.vocab, a.k
+    h = (0.5 * torch.randn(M, K, device="cuda")).bfloat16()
+    w = (0.02 * torch.randn(V, K, device="cuda")).bfloat16()
+    lab = torch.randint(0, V, (M,), device="cuda")
+    with torch.no_grad():
+        ms = timeit(lambda: ops.linear_logprob_entropy(h, w, lab, 1.0, True), a.iters)
+    report(f"lm_head->logprob+entropy fwd M={M} V={V} K={K}", ms, flops=2.0 * M * V * K)
+
+
+def bench_decode_attn(a):
+    from verl_b200.ops.attention import paged_decode_attention
+
+    Hq, Hkv, D, B = a.heads, a.kv_heads, 128, a.batch
+    blocks_per = (a.seqlen + 63) // 64 + 1
+    nb = B * blocks_per + 1
+    cache = torch.zeros(nb, 2, Hkv, 64, D, device="cuda", dtype=torch.bfloat16).normal_()
+    bt = (torch.arange(B * blocks_per, device="cuda", dtype=torch.int32) + 1).reshape(B, blocks_per)
+    kl = torch.full((B,), a.seqlen, dtype=torch.int32, device="cuda")
+    q = torch.randn(B, Hq * D, device="cuda").bfloat16()
+    out = torch.empty_like(q)
+    ws = torch.empty(B * Hq * max(1, a.splits) * 130, device="cuda")
+    ms = timeit(lambda: paged_decode_attention(q, cache, bt, kl, 1 / math.sqrt(D), a.splits, a.seqlen, ws, out, a.impl), a.iters)
+    report(f"paged decode attention B={B} kv={a.seqlen} {Hq}/{Hkv} heads impl={a.impl}", ms, bytes_=B * a.seqlen * Hkv * D * 2 * 2)
+
+
+def bench_elementwise(a):
+    from verl_b200.ops import _ext, functional as Fn
+
+    o = _ext.ops()
+    T, H = a.m, a.k
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    w = torch.ones(H, device="cuda").bfloat16()
+    report(f"rmsnorm fwd T={T} H={H}", timeit(lambda: Fn.rmsnorm(x, w, 1e-6), a.iters), bytes_=2 * T * H * 2)
+    gu = torch.randn(T, 2 * H, device="cuda").bfloat16()
+    report(f"swiglu fwd T={T} I={H}", timeit(lambda: Fn.swiglu(gu), a.iters), bytes_=3 * T * H * 2)
+    n = T * H
+    p32, m, v, g = (torch.randn(n, device="cuda") for _ in range(4))
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    sc = torch.tensor([1.0, 0.0, 0.0, 0.0], device="cuda")
+    report(f"adamw n={n}", timeit(lambda: o.adamw_(p32, m, v, g, p16, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1, sc), a.iters), bytes_=n * (4 * 4 + 3 * 4 + 2))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "lmhead", "decode_attn", "elementwise", "all"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--a-mn", dest="a_mn", action="store_true")
+    ap.add_argument("--b-mn", dest="b_mn", action="store_true")
+    ap.add_argument("--f32", action="store_true")
+    ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--heads", type=int, default=28)
+    ap.add_argument("--kv-heads", dest="kv_heads", type=int, default=4)
+    ap.add_argument("--seqlen", type=int, default=1408)
+    ap.add_argument("--batch", type=int, default=12)
+    ap.add_argument("--vocab", type=int, default=152064)
+    ap.add_argument("--splits", type=int, default=1)
+    ap.add_argument("--impl", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    from verl_b200.ops import _ext
+
+    _ext.load()
+    if a.kernel in ("gemm", "all"):
+        bench_gemm(a)
+    if a.kernel in ("attn_fwd", "all"):
+        bench_attn(a, False)
+    if a.kernel in ("attn_bwd", "all"):
+        bench_attn(a, True)
+    if a.kernel in ("lmhead", "all"):
+        a2 = argparse.Namespace(**vars(a))
+        a2.m, a2.k = (a.m if a.kernel == "lmhead" else 4096), (a.k if a.kernel == "lmhead" else 3584)
+        bench_lmhead(a2)
+    if a.kernel in ("decode_attn", "all"):
+        a2 = argparse.Namespace(**vars(a))
+        if a.kernel == "all":
+            a2.batch, a2.seqlen = 256, 900
+        bench_decode_attn(a2)
+    if a.kernel in ("elementwise", "all"):
+        a2 = argparse.Namespace(**vars(a))
+        if a.kernel == "all":
+            a2.m, a2.k = 16384, 3584
+        bench_elementwise(a2)
+    _ext.check_status("kernel_bench")
+
+
+if __name__ == "__main__":
+    main()

@@ -278,8 +278,11 @@ class ActorRolloutRefWorker(Worker):
         ids_cpu, att_cpu = ids.cpu(), att.cpu().bool()
         plist = [ids_cpu[i][att_cpu[i]].tolist() for i in range(bs)]
         t0 = time.perf_counter()
+        self.rollout.profile = bool(os.environ.get("VERL_B200_PROFILE_ROLLOUT"))
         self.rollout.wake_up()
         outs = self.rollout.generate(plist, sp, eos_token_id=eos)
+        if self.rollout.profile and self.rank == 0:
+            print(f"[rollout stats] {self.rollout.stats}", flush=True)
         if bool(cfg_get(ro, "free_cache_engine", True)):
             self.rollout.sleep()
         if torch.cuda.is_available():

@@ -102,7 +102,9 @@ class InferenceEngine:
         self._graph = None
         self.decode_splits = decode_splits
         self._cpu_gen = torch.Generator(device="cpu")
-        self.stats = {"prefill_tokens": 0, "decode_steps": 0, "preemptions": 0, "forked": 0}
+        self.stats = {"prefill_tokens": 0, "decode_steps": 0, "preemptions": 0, "forked": 0, "t_prefill": 0.0, "t_capture": 0.0,
+                      "t_decode": 0.0, "t_flush": 0.0, "t_wake": 0.0}
+        self.profile = False   # when set, phases are bracketed by device synchronisations and timed
 
     # ------------------------------------------------------------------ memory lifecycle (sleep / wake_up)
     def _decide_num_blocks(self) -> int:
@@ -112,15 +114,34 @@ class InferenceEngine:
         per_block = c.num_hidden_layers * 2 * c.num_key_value_heads * BLOCK_SIZE * c.head_dim * self.model.embed_tokens.element_size()
         want = self.max_num_seqs * self.max_blocks_per_seq + 1
         if self.device.type == "cuda":
+            torch.cuda.empty_cache()          # memory cached by the training phase must count as free
             free, total = torch.cuda.mem_get_info(self.device)
             budget = min(free * 0.9, total * self.gpu_memory_utilization)
-            want = min(want, max(int(budget // per_block), self.max_blocks_per_seq + 2))
+            got = min(want, max(int(budget // per_block), self.max_blocks_per_seq + 2))
+            if got < want:
+                print(f"[rollout] KV cache limited to {got} blocks ({got * per_block / 2**30:.1f} GiB) of the {want} needed to hold "
+                      f"{self.max_num_seqs} sequences of {self.max_model_len} tokens; expect preemptions", flush=True)
+            want = got
         return want
+
+    def _tick(self):
+        import time
+
+        if self.profile and self.device.type == "cuda":
+            torch.cuda.synchronize()
+        return time.perf_counter()
 
     def wake_up(self):
         """Allocate the KV cache and the static decode buffers."""
         if self.cache is not None:
             return
+        t0 = self._tick()
+        try:
+            self._wake_up_impl()
+        finally:
+            self.stats["t_wake"] += self._tick() - t0
+
+    def _wake_up_impl(self):
         c = self.cfg
         nb = self._decide_num_blocks()
         self.num_blocks = nb
@@ -349,6 +370,9 @@ class InferenceEngine:
         """Read back the sampled tokens of the un-synchronised decode steps and retire finished sequences."""
         if not pending:
             return
+        import time
+
+        t_f = time.perf_counter()
         tok = self.hist_tok.cpu().numpy()
         lp = self.hist_lp.cpu().numpy()
         freed = []
@@ -371,6 +395,7 @@ class InferenceEngine:
         pending.clear()
         if freed:
             self.active.index_fill_(0, torch.tensor(freed, dtype=torch.int64, device=self.device), 0)
+        self.stats["t_flush"] += time.perf_counter() - t_f
 
     @torch.no_grad()
     def generate(self, prompts: Sequence[Sequence[int]], sampling_params: Optional[SamplingParams] = None,
@@ -421,6 +446,7 @@ class InferenceEngine:
                 for s in ids:  # a sequence that finished while waiting for re-admission
                     if reqs[int(s)]["done"]:
                         self.sched.finish(int(s))
+                t_pf = self._tick()
                 if fresh:
                     logits = self._prefill(fresh, sp)
                     for row, (r, sl) in enumerate(fresh):
@@ -458,6 +484,7 @@ class InferenceEngine:
                     r["done"], r["stop"] = True, ("length" if len(r["out"]) >= r["max_new"] else "stop")
                     self.sched.finish(r["id"])
                     self.active[sl] = 0
+                self.stats["t_prefill"] += self._tick() - t_pf
                 continue
             # ---- decode
             ids, slots, lens = ids.copy(), slots.copy(), lens.copy()
@@ -475,7 +502,12 @@ class InferenceEngine:
                 self.block_table_host[slots[j], : len(blocks)] = blocks
             if len(grew):
                 self._push_block_table()
-            self._decode_step(sp)
+            if self._graph is None and not self.enforce_eager:
+                t_c = self._tick()
+                self._decode_step(sp)
+                self.stats["t_capture"] += self._tick() - t_c
+            else:
+                self._decode_step(sp)
             self.stats["decode_steps"] += 1
             pending.append((ring, ids, slots))
             ring = (ring + 1) % self.sync_interval
