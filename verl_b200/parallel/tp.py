@@ -1,0 +1,103 @@
+"""Tensor-parallel building blocks whose collectives are fused into the GEMM kernels (NVLink peer memory), with the
+NCCL versions kept as baseline/oracle (selected by ``VERL_B200_COMM=nccl``).
+
+* ``AllGatherLinear``   y = all_gather(x_shard) @ W_localᵀ       — column-parallel layer after a sequence-sharded region
+  (Megatron sequence parallelism): tiles of x are TMA-loaded straight from the owning rank, nothing is gathered first.
+* ``GemmAllReduce``     y = Σ_r x_r @ W_rᵀ  on every rank         — row-parallel layer in the rollout engine: the epilogue
+  scatters bf16 partial tiles into every rank's slot buffer, a device barrier and one slot-sum kernel finish it.
+* ``GemmReduceScatter`` y_shard = (Σ_r x_r @ W_rᵀ)[rows of rank]   — row-parallel layer feeding a sequence-sharded region.
+* ``WeightGatherLinear`` y = x @ all_gather(W_shard)ᵀ              — ZeRO-3 parameter all-gather fused into the consuming GEMM.
+
+The reference reaches these through Megatron-Core/TransformerEngine and vLLM (``verl/workers/engine/megatron/
+transformer_impl.py:260-340``).
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from verl_b200.ops import _ext
+from verl_b200.parallel.symm_mem import SymmetricBuffer
+
+__all__ = ["TPContext", "fused_comm_enabled"]
+
+
+def fused_comm_enabled() -> bool:
+    return os.environ.get("VERL_B200_COMM", "native") == "native" and torch.cuda.is_available() and _ext.available()
+
+
+class TPContext:
+    """Symmetric staging buffers + fused ops for one tensor-parallel group."""
+
+    def __init__(self, group, host_group, max_tokens: int, hidden: int, max_out: int):
+        self.group, self.host_group = group, host_group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.ops = _ext.ops()
+        self.max_tokens, self.hidden, self.max_out = max_tokens, hidden, max_out
+        # activations that peers read (sequence-sharded inputs of column-parallel layers)
+        self.act = SymmetricBuffer(max_tokens * hidden * 2, group, host_group)
+        # slots[src_rank][tokens, out] written by peers' GEMM epilogues
+        self.slot_elems = max_tokens * max_out
+        self.slots = SymmetricBuffer(self.world * self.slot_elems * 2, group, host_group)
+
+    # ------------------------------------------------------------------ all-gather → GEMM
+    def stage_activation(self, x_shard: torch.Tensor) -> None:
+        """Publish this rank's [T/W, H] shard for the peers (copy into the symmetric buffer, then barrier)."""
+        n = x_shard.numel()
+        self.act.tensor(torch.bfloat16, n).view_as(x_shard).copy_(x_shard)
+        self.act.barrier()
+
+    def allgather_linear(self, x_shard: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        rows = x_shard.shape[0]
+        out = torch.empty(rows * self.world, w.shape[0], dtype=torch.bfloat16, device=x_shard.device)
+        if fused_comm_enabled() and rows % 128 == 0:
+            self.stage_activation(x_shard)
+            self.ops.gemm_allgather_a(self.act.table(), rows, w, out, bias)
+            self.act.barrier()      # nobody overwrites its shard while a peer may still be reading it
+            return out
+        full = torch.empty(rows * self.world, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
+        dist.all_gather_into_tensor(full, x_shard.contiguous(), group=self.group)
+        return torch.nn.functional.linear(full, w, bias)
+
+    # ------------------------------------------------------------------ GEMM → all-reduce / reduce-scatter
+    def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T, N = x.shape[0], w.shape[0]
+        if fused_comm_enabled() and N % 32 == 0 and T * N <= self.slot_elems:
+            out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+            self.ops.gemm_peer_scatter(x, w, self.slots.table(), self.rank, 0, self.slot_elems)
+            self.slots.barrier()
+            self.ops.slots_reduce(self.slots.tensor(torch.bfloat16), self.world, self.slot_elems, T, N, residual, out)
+            self.slots.barrier()    # slots may be overwritten by the next call only after everyone has summed them
+            return out
+        y = torch.nn.functional.linear(x, w)
+        dist.all_reduce(y, group=self.group)
+        return y + residual if residual is not None else y
+
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        T, N = x.shape[0], w.shape[0]
+        assert T % self.world == 0
+        rows = T // self.world
+        if fused_comm_enabled() and N % 32 == 0 and rows * N <= self.slot_elems:
+            out = torch.empty(rows, N, dtype=torch.bfloat16, device=x.device)
+            self.ops.gemm_peer_scatter(x, w, self.slots.table(), self.rank, rows, self.slot_elems)
+            self.slots.barrier()
+            self.ops.slots_reduce(self.slots.tensor(torch.bfloat16), self.world, self.slot_elems, rows, N, None, out)
+            self.slots.barrier()
+            return out
+        y = torch.nn.functional.linear(x, w)
+        out = torch.empty(rows, N, dtype=y.dtype, device=y.device)
+        dist.reduce_scatter_tensor(out, y, group=self.group)
+        return out
+
+    # ------------------------------------------------------------------ ZeRO-3 weight gather → GEMM
+    @staticmethod
+    def weight_gather_linear(x: torch.Tensor, w_symm: SymmetricBuffer, shard_rows: int, in_features: int, byte_offset: int = 0) -> torch.Tensor:
+        """y = x @ concat_r(W_r)ᵀ with W_r = rank r's [shard_rows, in_features] slice living in ``w_symm``."""
+        ops = _ext.ops()
+        out = torch.empty(x.shape[0], shard_rows * w_symm.world, dtype=torch.bfloat16, device=x.device)
+        ops.gemm_allgather_b(x, w_symm.table(byte_offset), shard_rows, out, None)
+        return out
