@@ -212,11 +212,16 @@ def main():
     ap.add_argument("--min-prompt", type=int, default=256)
     ap.add_argument("--max-prompt", type=int, default=512)
     ap.add_argument("--response-length", type=int, default=1024)
-    ap.add_argument("--token-budget", type=int, default=16384)
+    ap.add_argument("--token-budget", type=int, default=0, help="tokens per training micro-batch; 0 = 16384 with recomputation, 8192 without")
     ap.add_argument("--kv-util", type=float, default=0.3)
-    ap.add_argument("--grad-ckpt", type=int, default=1)
+    ap.add_argument("--grad-ckpt", type=int, default=-1,
+                    help="activation recomputation: -1 = only on 1 GPU, where the unsharded fp32 optimizer state leaves no room for stored activations")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
+    if args.grad_ckpt < 0:
+        args.grad_ckpt = 1 if int(os.environ.get("WORLD_SIZE", "1")) == 1 else 0
+    if args.token_budget <= 0:
+        args.token_budget = 16384 if args.grad_ckpt else 8192
     if args.impl == "reference":
         run_reference(args)
     else:

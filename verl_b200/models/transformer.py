@@ -20,6 +20,7 @@ from torch.utils.checkpoint import checkpoint
 
 from verl_b200 import ops
 from verl_b200.models.config import ModelConfig
+from verl_b200.parallel.tp import copy_to_tp, reduce_from_tp, vocab_parallel_embedding
 
 __all__ = ["DecoderLM", "PackedBatch", "hf_to_native_state_dict", "native_to_hf_tensors"]
 
@@ -50,10 +51,11 @@ class Attention(nn.Module):
         if cfg.qk_norm:
             self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, **kw))
             self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, **kw))
+        self.tp_group = None    # set by the tensor-parallel engine; cfg then describes the LOCAL head counts
 
     def forward(self, x: torch.Tensor, pb: PackedBatch, cos, sin, sp_group=None) -> torch.Tensor:
         cfg = self.cfg
-        qkv = ops.linear(x, self.qkv_proj, self.qkv_bias)
+        qkv = ops.linear(copy_to_tp(x, self.tp_group), self.qkv_proj, self.qkv_bias)
         if cfg.qk_norm:
             T = qkv.shape[0]
             q, k, v = qkv.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=-1)
@@ -68,7 +70,7 @@ class Attention(nn.Module):
         else:
             o = ops.attention_varlen(qkv, pb.cu_seqlens, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                                      pb.max_seqlen, pb.cu_seqlens_cpu)
-        return ops.linear(o, self.o_proj)
+        return reduce_from_tp(ops.linear(o, self.o_proj), self.tp_group)
 
 
 class MLP(nn.Module):
@@ -77,9 +79,11 @@ class MLP(nn.Module):
         kw = dict(dtype=dtype, device=device)
         self.gate_up_proj = nn.Parameter(torch.empty(2 * cfg.intermediate_size, cfg.hidden_size, **kw))
         self.down_proj = nn.Parameter(torch.empty(cfg.hidden_size, cfg.intermediate_size, **kw))
+        self.tp_group = None
 
     def forward(self, x):
-        return ops.linear(ops.swiglu(ops.linear(x, self.gate_up_proj)), self.down_proj)
+        y = ops.linear(ops.swiglu(ops.linear(copy_to_tp(x, self.tp_group), self.gate_up_proj)), self.down_proj)
+        return reduce_from_tp(y, self.tp_group)
 
 
 class MoE(nn.Module):
@@ -96,17 +100,18 @@ class MoE(nn.Module):
         self.experts_gate_up = nn.Parameter(torch.empty(E, 2 * I, H, **kw))
         self.experts_down = nn.Parameter(torch.empty(E, H, I, **kw))
         self.ep_group = None
+        self.tp_group = None    # expert tensor parallelism: every expert's intermediate dimension is split
         self.last_topk: Optional[torch.Tensor] = None   # recorded routing (router replay R2)
         self.record_routing = False
 
     def forward(self, x, forced_topk: Optional[torch.Tensor] = None):
         from verl_b200.ops.moe import moe_forward
 
-        out, topk_idx = moe_forward(x, self.router, self.experts_gate_up, self.experts_down, self.cfg.num_experts_per_tok,
-                                    self.cfg.norm_topk_prob, forced_topk=forced_topk, ep_group=self.ep_group)
+        out, topk_idx = moe_forward(copy_to_tp(x, self.tp_group), self.router, self.experts_gate_up, self.experts_down,
+                                    self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, forced_topk=forced_topk, ep_group=self.ep_group)
         if self.record_routing:
             self.last_topk = topk_idx.detach()
-        return out
+        return reduce_from_tp(out, self.tp_group)
 
 
 class DecoderLayer(nn.Module):
@@ -140,13 +145,28 @@ class DecoderLayer(nn.Module):
 class DecoderLM(nn.Module):
     """Embedding → N decoder layers → final norm → (lm_head | value head)."""
 
-    def __init__(self, cfg: ModelConfig, dtype: torch.dtype = torch.bfloat16, device="cpu", init: bool = True, seed: int = 0):
+    def __init__(self, cfg: ModelConfig, dtype: torch.dtype = torch.bfloat16, device="cpu", init: bool = True, seed: int = 0,
+                 layer_range: Optional[range] = None, pre_process: bool = True, post_process: bool = True):
+        """``layer_range`` / ``pre_process`` / ``post_process`` build one pipeline stage: only those decoder layers, the
+        embedding only on the first stage, final norm and head only on the last. Local layer j is global layer
+        ``layer_range.start + j``."""
         super().__init__()
         self.cfg = cfg
         self.dtype = dtype
         kw = dict(dtype=dtype, device=device)
-        self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))
-        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, i) for i in range(cfg.num_hidden_layers)])
+        layer_range = range(cfg.num_hidden_layers) if layer_range is None else layer_range
+        self.layer_offset, self.pre_process, self.post_process = layer_range.start, pre_process, post_process
+        self.tp_group, self.vocab_offset = None, 0
+        self.gradient_checkpointing = False
+        self.sp_group = None
+        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, i) for i in layer_range])
+        if pre_process or (post_process and cfg.tie_word_embeddings and not cfg.value_head):
+            self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))
+        self.lm_head = None
+        if not post_process:
+            if init:
+                self.reset_parameters(seed)
+            return
         self.norm = nn.Parameter(torch.ones(cfg.hidden_size, **kw))
         if cfg.value_head:
             self.score = nn.Parameter(torch.empty(1, cfg.hidden_size, **kw))
@@ -155,8 +175,6 @@ class DecoderLM(nn.Module):
             self.lm_head = None
         else:
             self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))
-        self.gradient_checkpointing = False
-        self.sp_group = None
         if init:
             self.reset_parameters(seed)
 
@@ -164,7 +182,7 @@ class DecoderLM(nn.Module):
     @torch.no_grad()
     def reset_parameters(self, seed: int = 0):
         """normal(0, initializer_range) for matrices, ones for norms, zeros for biases (HF ``_init_weights``)."""
-        gen = torch.Generator(device=self.embed_tokens.device)
+        gen = torch.Generator(device=next(self.parameters()).device)
         gen.manual_seed(seed)
         std = self.cfg.initializer_range
         for name, p in self.named_parameters():
@@ -183,20 +201,31 @@ class DecoderLM(nn.Module):
     def rope(self, device):
         return ops.rope_tables(self.cfg.max_position_embeddings, self.cfg.head_dim, self.cfg.rope_theta, device)
 
-    def forward_hidden(self, pb: PackedBatch, layer_range: Optional[range] = None, h_in: Optional[torch.Tensor] = None):
-        """Returns final-normed hidden states [T, H] (or the raw stream if ``layer_range`` stops early, for PP)."""
+    def set_tp_group(self, group, vocab_offset: int = 0):
+        """Switch the model to tensor-parallel execution: ``cfg`` must already describe the local shard."""
+        self.tp_group, self.vocab_offset = group, vocab_offset
+        for layer in self.layers:
+            layer.self_attn.tp_group = group
+            layer.mlp.tp_group = group
+
+    def forward_hidden(self, pb: PackedBatch, h_in: Optional[torch.Tensor] = None):
+        """Final-normed hidden states [T, H] on the last pipeline stage, the raw residual stream on earlier stages.
+        ``h_in`` is the stream received from the previous stage (stages without the embedding)."""
         cos, sin = self.rope(pb.input_ids.device)
-        first = layer_range is None or layer_range.start == 0
-        last = layer_range is None or layer_range.stop == self.cfg.num_hidden_layers
-        h = ops.embedding(pb.input_ids, self.embed_tokens) if first else h_in
+        if self.pre_process:
+            if self.tp_group is not None:
+                h = vocab_parallel_embedding(pb.input_ids, self.embed_tokens, self.vocab_offset, self.tp_group)
+            else:
+                h = ops.embedding(pb.input_ids, self.embed_tokens)
+        else:
+            h = h_in
         residual = None
-        layers = self.layers if layer_range is None else [self.layers[i] for i in layer_range]
-        for layer in layers:
+        for layer in self.layers:
             if self.gradient_checkpointing and torch.is_grad_enabled():
                 h, residual = checkpoint(layer, h, residual, pb, cos, sin, self.sp_group, use_reentrant=False)
             else:
                 h, residual = layer(h, residual, pb, cos, sin, self.sp_group)
-        if not last:
+        if not self.post_process:
             return h + residual if residual is not None else h
         if residual is None:
             return ops.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)
@@ -238,10 +267,40 @@ class DecoderLM(nn.Module):
                     own[k].copy_(v.to(own[k].dtype))
 
 
+    @torch.no_grad()
+    def load_hf_stream(self, named_tensors) -> int:
+        """Consume (hf_name, tensor) pairs in model order, fusing and copying one decoder layer at a time so that at most
+        one layer's worth of source tensors is alive (weight hand-off from a model-parallel trainer to a rollout copy).
+        Returns the number of native parameters written."""
+        own = dict(self.named_parameters())
+        written = 0
+
+        def flush(group: dict):
+            nonlocal written
+            for k, v in hf_to_native_state_dict(self.cfg, group).items():
+                if k in own:
+                    own[k].copy_(v.to(own[k].dtype))
+                    written += 1
+
+        group, key = {}, None
+        for name, t in named_tensors:
+            parts = name.split(".")
+            k = ".".join(parts[:3]) if name.startswith("model.layers.") else name
+            if key is not None and k != key and group:
+                flush(group)
+                group = {}
+            key = k
+            group[name] = t
+        if group:
+            flush(group)
+        return written
+
+
 # ---------------------------------------------------------------------------------------------------- name mapping
 def native_to_hf_tensors(cfg: ModelConfig, params: dict) -> Iterator[tuple[str, torch.Tensor]]:
     """Yield (hf_name, tensor) splitting the fused projections; tensors are views where possible."""
-    yield "model.embed_tokens.weight", params["embed_tokens"]
+    if "embed_tokens" in params:
+        yield "model.embed_tokens.weight", params["embed_tokens"]
     for i in range(cfg.num_hidden_layers):
         p = f"layers.{i}."
         hp = f"model.layers.{i}."
@@ -289,7 +348,8 @@ def hf_to_native_state_dict(cfg: ModelConfig, sd: dict) -> dict:
     """Fuse q/k/v and gate/up tensors of an HF state dict into this model's parameter names."""
     out = {}
     g = sd.get
-    out["embed_tokens"] = sd["model.embed_tokens.weight"]
+    if "model.embed_tokens.weight" in sd:
+        out["embed_tokens"] = sd["model.embed_tokens.weight"]
     for i in range(cfg.num_hidden_layers):
         hp, p = f"model.layers.{i}.", f"layers.{i}."
         if hp + "input_layernorm.weight" not in sd:

@@ -101,3 +101,54 @@ class TPContext:
         out = torch.empty(x.shape[0], shard_rows * w_symm.world, dtype=torch.bfloat16, device=x.device)
         ops.gemm_allgather_b(x, w_symm.table(byte_offset), shard_rows, out, None)
         return out
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Autograd glue of Megatron-style tensor parallelism ("f" and "g" of the Megatron-LM paper) and the vocabulary-parallel
+# embedding. The reference gets these from Megatron-Core (verl/workers/engine/megatron/transformer_impl.py:260-340).
+class _CopyToTP(torch.autograd.Function):
+    """Identity in forward; all-reduce of the gradient in backward (input of a column-parallel layer)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class _ReduceFromTP(torch.autograd.Function):
+    """All-reduce in forward; identity in backward (output of a row-parallel layer)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def copy_to_tp(x: torch.Tensor, group) -> torch.Tensor:
+    return x if group is None or dist.get_world_size(group) == 1 else _CopyToTP.apply(x, group)
+
+
+def reduce_from_tp(x: torch.Tensor, group) -> torch.Tensor:
+    return x if group is None or dist.get_world_size(group) == 1 else _ReduceFromTP.apply(x, group)
+
+
+def vocab_parallel_embedding(ids: torch.Tensor, w_local: torch.Tensor, vocab_offset: int, group) -> torch.Tensor:
+    """Rows [vocab_offset, vocab_offset + w_local.shape[0]) live on this rank; others contribute zeros, then all-reduce."""
+    from verl_b200 import ops
+
+    local = ids - vocab_offset
+    mine = (local >= 0) & (local < w_local.shape[0])
+    h = ops.embedding(torch.where(mine, local, torch.zeros_like(local)), w_local)
+    h = h * mine.unsqueeze(-1).to(h.dtype)
+    return reduce_from_tp(h, group)

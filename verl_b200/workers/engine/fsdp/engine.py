@@ -476,17 +476,23 @@ class FSDPEngine(BaseEngine):
         if self._symm_grads is not None:
             return self._optimizer_step_fused()
         # 1. reduce gradients: average over data-parallel ranks, keep only this rank's shard
-        if self.world > 1:
+        if W > 1 or self.ddp_group is not None:
             if s.grad.is_cuda:
-                if self.grad_shard is None:
-                    self.grad_shard = torch.empty(s.shard_size, dtype=torch.float32, device=self.device)
-                dist.reduce_scatter_tensor(self.grad_shard, s.grad, op=dist.ReduceOp.AVG, group=self.fsdp_group)
-                gshard = self.grad_shard
+                if W > 1:
+                    if self.grad_shard is None:
+                        self.grad_shard = torch.empty(s.shard_size, dtype=torch.float32, device=self.device)
+                    dist.reduce_scatter_tensor(self.grad_shard, s.grad, op=dist.ReduceOp.AVG, group=self.fsdp_group)
+                    gshard = self.grad_shard
+                else:
+                    gshard = s.grad
                 if self.ddp_group is not None:
                     dist.all_reduce(gshard, op=dist.ReduceOp.AVG, group=self.ddp_group)
             else:
-                dist.all_reduce(s.grad)
-                s.grad.div_(self.world)
+                if W > 1:
+                    dist.all_reduce(s.grad, group=self.fsdp_group)
+                if self.ddp_group is not None:
+                    dist.all_reduce(s.grad, group=self.ddp_group)
+                s.grad.div_(W * self.ddp_size)
                 gshard = s.grad[s.shard_slice]
         else:
             gshard = s.grad
@@ -498,8 +504,9 @@ class FSDPEngine(BaseEngine):
             sumsq = self._sumsq
         else:
             sumsq = gshard.float().pow(2).sum().reshape(1)
-        if self.world > 1 and W > 1:
+        if W > 1:
             dist.all_reduce(sumsq, group=self.fsdp_group)
+        sumsq = self._sumsq_across_model_parallel(sumsq, gshard)
         self.step_count += 1
         lr = self.current_lr()
         if native:
@@ -522,7 +529,7 @@ class FSDPEngine(BaseEngine):
             self.step_count -= 1
             print(f"WARN: rank {self.rank} grad_norm is not finite: {grad_norm}; skipping optimizer step")
         # 3. all-gather the updated working copy
-        if self.world > 1 and W > 1:
+        if W > 1:
             if s.flat.is_cuda:
                 dist.all_gather_into_tensor(s.flat, s.flat[s.shard_slice].clone(), group=self.fsdp_group)
             else:
@@ -531,6 +538,10 @@ class FSDPEngine(BaseEngine):
                 s.flat.copy_(torch.cat(parts))
         s.zero_grads()
         return grad_norm
+
+    def _sumsq_across_model_parallel(self, sumsq: torch.Tensor, gshard: torch.Tensor) -> torch.Tensor:
+        """Hook for engines whose parameters are also split over tensor/pipeline ranks; a no-op for pure data parallelism."""
+        return sumsq
 
     @torch.no_grad()
     def _optimizer_step_fused(self) -> float:

@@ -244,6 +244,15 @@ class ActorRolloutRefWorker(Worker):
         ro = cfg_get(self.config, "rollout")
         src = self.actor if self.actor is not None else self.ref
         model = src.engine.model
+        self._rollout_owns_model = False
+        if getattr(src.engine, "tp_size", 1) * getattr(src.engine, "pp_size", 1) > 1:
+            # the trainer holds only a tensor/pipeline shard: the rollout replica keeps its own full copy, refreshed by
+            # update_weights() from the engine's per-tensor export
+            from verl_b200.models.transformer import DecoderLM
+
+            model = DecoderLM(src.engine.cfg, dtype=src.engine.dtype, device=src.engine.device, init=False)
+            model.load_hf_stream(src.engine.get_per_tensor_param()[0])
+            self._rollout_owns_model = True
         max_len = cfg_get(ro, "max_model_len", None) or (int(cfg_get(ro, "prompt_length", 512)) + int(cfg_get(ro, "response_length", 512)))
         self.rollout = InferenceEngine(
             model, max_num_seqs=int(cfg_get(ro, "max_num_seqs", 256)), max_model_len=int(max_len),
@@ -347,7 +356,9 @@ class ActorRolloutRefWorker(Worker):
         t0 = time.perf_counter()
         if self.actor is not None and self.rollout is not None:
             eng = self.actor.engine
-            if not eng.store.flat.is_cuda and torch.cuda.is_available():
+            if getattr(self, "_rollout_owns_model", False):
+                self.rollout.model.load_hf_stream(eng.get_per_tensor_param()[0])
+            elif not eng.store.flat.is_cuda and torch.cuda.is_available():
                 eng.to("cuda", model=True, optimizer=False, grad=False)
                 self.rollout._graph = None
         if dist.is_initialized():
