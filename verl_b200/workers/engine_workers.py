@@ -262,12 +262,35 @@ class ActorRolloutRefWorker(Worker):
             num_blocks=cfg_get(ro, "num_blocks", None))
 
     # ------------------------------------------------------------------ rollout
+    def _agent_loop_manager(self):
+        """Server-mode rollout inside this worker: the engine is wrapped in a hybrid replica and the agent loops of this
+        rank's share of the batch run against it (the reference reaches its servers through Ray actors instead:
+        verl/experimental/agent_loop/agent_loop.py:1190-1312)."""
+        if getattr(self, "_agent_mgr", None) is None:
+            from verl_b200.experimental.agent_loop import AgentLoopManager
+            from verl_b200.utils.tokenizer import ByteChatTokenizer, hf_tokenizer
+            from verl_b200.workers.rollout.llm_server import LLMServerManager
+            from verl_b200.workers.rollout.replica import RolloutReplica
+
+            path = cfg_get(self.config, "model.path", None)
+            if path and os.path.isdir(os.path.expanduser(path)):
+                tok = hf_tokenizer(os.path.expanduser(path))
+            else:
+                tok = ByteChatTokenizer()
+            eos = getattr(tok, "eos_token_id", None)
+            fully_async = str(cfg_get(self.config, "rollout.agent.client", "sync")) == "fully_async"
+            self._replica = RolloutReplica(self.rank, cfg_get(self.config, "rollout")).init_hybrid(self.rollout, eos_token_id=eos, tokenizer=tok)
+            self._agent_mgr = AgentLoopManager(self.config, LLMServerManager([self._replica], fully_async=fully_async), tok)
+        return self._agent_mgr
+
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("rollout"))
     def generate_sequences(self, prompts: DataProto) -> DataProto:
         """Left-padded prompts in → prompts + right-padded responses out (with rollout log-probs)."""
         from verl_b200.workers.rollout.engine import SamplingParams
 
         ro = cfg_get(self.config, "rollout")
+        if str(cfg_get(ro, "mode", "sync")) == "async" or bool(cfg_get(ro, "multi_turn.enable", False)):
+            return self._agent_loop_manager().generate_sequences(prompts)
         meta = prompts.meta_info
         ids = prompts.batch["input_ids"]
         att = prompts.batch["attention_mask"]

@@ -16,6 +16,7 @@ It replaces the vLLM / SGLang servers of the reference (``verl/workers/rollout/v
 from __future__ import annotations
 
 import math
+import time
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
@@ -392,6 +393,7 @@ class InferenceEngine:
                     freed.append(slot)
                     r["num_preempted"] = self.sched.num_preempted(int(sid))
                     self.sched.finish(int(sid))
+                    self._report(r)
         pending.clear()
         if freed:
             self.active.index_fill_(0, torch.tensor(freed, dtype=torch.int64, device=self.device), 0)
@@ -399,7 +401,16 @@ class InferenceEngine:
 
     @torch.no_grad()
     def generate(self, prompts: Sequence[Sequence[int]], sampling_params: Optional[SamplingParams] = None,
-                 eos_token_id=None) -> list[TokenOutput]:
+                 eos_token_id=None, admit=None, on_done=None, keep_alive=None, should_abort=None) -> list[TokenOutput]:
+        """Batch generation, optionally kept open as a serving loop.
+
+        With ``admit`` (a callable returning a list of ``(prompt_ids, max_tokens or None)``) new requests join the
+        running batch whenever the loop synchronises with the device; they are numbered consecutively after the initial
+        prompts. ``on_done(request_index, TokenOutput)`` fires as each request finishes; the loop runs while work is left
+        or ``keep_alive()`` is true. ``should_abort()`` returning true ends every live request with
+        ``stop_reason="aborted"`` and its partial output. All requests of one call share ``sampling_params`` except
+        ``max_tokens``.
+        """
         sp = sampling_params or SamplingParams()
         self.wake_up()
         eos_ids = set() if eos_token_id is None else ({eos_token_id} if isinstance(eos_token_id, int) else set(eos_token_id))
@@ -409,33 +420,60 @@ class InferenceEngine:
         self.active.zero_()
         reqs: dict[int, dict] = {}
         counts: dict[tuple, int] = {}
-        if self.enable_prefix_sharing:
-            for p in prompts:
-                k = tuple(p)
-                counts[k] = counts.get(k, 0) + 1
-        for i, p in enumerate(prompts):
-            p = list(p)
-            max_new = min(sp.max_tokens, self.max_model_len - len(p))
-            if max_new <= 0:
-                raise ValueError(f"prompt {i} of length {len(p)} leaves no room below max_model_len={self.max_model_len}")
-            key = 0
-            if counts.get(tuple(p), 0) > 1:
-                key = (hash(tuple(p)) & 0x3FFFFFFFFFFFFFFF) or 1
-            reqs[i] = {"id": i, "prompt": p, "out": [], "lp": [], "done": False, "stop": None, "max_new": max_new, "n_gen": 0,
-                       "num_preempted": 0, "slot": -1}
-            self.sched.add(i, len(p), max_new, key)
+        self._on_done, self._sp_logprobs = on_done, sp.logprobs
+        poll_no = 0
+
+        def add_requests(items):
+            nonlocal poll_no
+            poll_no += 1
+            local: dict[tuple, int] = {}
+            if self.enable_prefix_sharing:
+                for p, _ in items:
+                    k = tuple(p)
+                    local[k] = local.get(k, 0) + 1
+            for p, mt in items:
+                i = len(reqs)
+                p = list(p)
+                max_new = min(int(mt) if mt else sp.max_tokens, self.max_model_len - len(p))
+                if max_new <= 0:
+                    raise ValueError(f"prompt {i} of length {len(p)} leaves no room below max_model_len={self.max_model_len}")
+                key = 0
+                if local.get(tuple(p), 0) > 1:
+                    key = (hash((poll_no, tuple(p))) & 0x3FFFFFFFFFFFFFFF) or 1
+                    counts[tuple(p)] = local[tuple(p)]
+                reqs[i] = {"id": i, "prompt": p, "out": [], "lp": [], "done": False, "stop": None, "max_new": max_new, "n_gen": 0,
+                           "num_preempted": 0, "slot": -1, "reported": False}
+                self.sched.add(i, len(p), max_new, key)
+
+        add_requests([(p, None) for p in prompts])
         owner_logits: dict[int, torch.Tensor] = {}
         owner_partial_block: dict[int, int] = {}
         pending: list = []
         ring = int(self.hist_idx.item())
         n_preempt = self.sched.num_preemptions
         while True:
+            if not pending:     # the host is in sync with the device here: a safe point to change the request set
+                if should_abort is not None and should_abort():
+                    for r in reqs.values():
+                        if not r["done"]:
+                            r["done"], r["stop"] = True, "aborted"
+                            self._report(r)
+                    self.sched.abort_all()
+                    self.active.zero_()
+                    break
+                if admit is not None:
+                    fresh_items = admit()
+                    if fresh_items:
+                        add_requests(fresh_items)
             kind, ids, slots, lens, forks = self.sched.step()
             if kind == STEP_IDLE:
                 self._flush(pending, reqs, sp, eos_ids)
                 if self.sched.num_running == 0 and self.sched.num_waiting == 0:
+                    if keep_alive is not None and keep_alive():
+                        time.sleep(0.001)
+                        continue
                     break
-                if all(r["done"] for r in reqs.values()):
+                if all(r["done"] for r in reqs.values()) and not (keep_alive is not None and keep_alive()):
                     break
                 continue
             if kind == STEP_PREFILL:
@@ -484,6 +522,7 @@ class InferenceEngine:
                     r["done"], r["stop"] = True, ("length" if len(r["out"]) >= r["max_new"] else "stop")
                     self.sched.finish(r["id"])
                     self.active[sl] = 0
+                    self._report(r)
                 self.stats["t_prefill"] += self._tick() - t_pf
                 continue
             # ---- decode
@@ -527,6 +566,13 @@ class InferenceEngine:
             outs.append(TokenOutput(token_ids=r["out"][: r["max_new"]], log_probs=r["lp"][: r["max_new"]] if sp.logprobs else None,
                                     stop_reason=r["stop"] or "length", num_preempted=r["num_preempted"]))
         return outs
+
+    def _report(self, r: dict):
+        if r.get("reported") or getattr(self, "_on_done", None) is None:
+            return
+        r["reported"] = True
+        self._on_done(r["id"], TokenOutput(token_ids=r["out"][: r["max_new"]], log_probs=r["lp"][: r["max_new"]] if self._sp_logprobs else None,
+                                           stop_reason=r["stop"] or "length", num_preempted=r["num_preempted"]))
 
     def abort_all(self) -> list[int]:
         """Drop every live request (used when a weight update interrupts generation)."""
