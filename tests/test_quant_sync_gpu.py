@@ -1,0 +1,54 @@
+"""sm_100a quantisation casts and weight-delta kernels against their PyTorch formulations."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_fp8_block_cast_matches_reference():
+    from verl_b200.ops.quant import _blockwise_ref, act_cast_to_fp8, blockwise_cast_to_fp8
+
+    for M, N in ((512, 1024), (300, 200), (129, 136)):
+        x = (torch.randn(M, N, device="cuda") * 2).bfloat16()
+        q, s = blockwise_cast_to_fp8(x)
+        qr, sr = _blockwise_ref(x, 128, 128)
+        torch.testing.assert_close(s, sr, rtol=1e-6, atol=0)
+        assert (q.float() - qr.float()).abs().max() <= 32.0 and (q.float() != qr.float()).float().mean() < 1e-3   # at most rounding ties
+        qa, sa = act_cast_to_fp8(x) if N % 4 == 0 else (None, None)
+        if qa is not None:
+            qar, sar = _blockwise_ref(x, 1, 128)
+            torch.testing.assert_close(sa, sar, rtol=1e-6, atol=0)
+            assert (qa.float() != qar.float()).float().mean() < 1e-3
+
+
+def test_fp4_fake_quant_matches_reference():
+    from verl_b200.ops.quant import _fp4_ref, fp4_fake_quant
+
+    x = (torch.randn(257, 512, device="cuda") * 0.05).bfloat16()
+    amax = x.abs().max().float().reshape(1)
+    y = fp4_fake_quant(x, amax)
+    ref = _fp4_ref(x, amax)
+    assert (y.float() != ref.float()).float().mean() < 1e-3
+    torch.testing.assert_close(y.float(), ref.float(), rtol=0, atol=float(amax) * 0.2)
+
+
+def test_delta_compact_and_apply_kernels():
+    from verl_b200.checkpoint_engine import delta_apply, delta_compact
+
+    n = 8 * 1024 * 1024 + 4096
+    old = torch.randn(n, device="cuda").bfloat16()
+    new = old.clone()
+    idx = torch.randperm(n, device="cuda")[:50000]
+    new[idx] = (new[idx].float() + 1.0).bfloat16()
+    changed = (new.view(torch.int16) != old.view(torch.int16)).sum().item()
+    snap, recv = old.clone(), old.clone()
+    count, pos, val = delta_compact(new, snap)
+    assert count == changed and torch.equal(snap, new)
+    assert torch.equal(torch.sort(pos.long())[0], torch.nonzero(new.view(torch.int16) != old.view(torch.int16)).reshape(-1))
+    delta_apply(recv, pos, val)
+    assert torch.equal(recv, new)
+    # overflow of the pair buffers is reported through the count
+    snap2 = old.clone()
+    count2, pos2, _ = delta_compact(new, snap2, cap=1000)
+    assert count2 == changed and pos2.numel() == 1000

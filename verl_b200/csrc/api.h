@@ -71,6 +71,13 @@ int vb_symm_adamw_allgather(float* p32, float* m, float* v, const float* g, cons
                             long n, float lr, float b1, float b2, float eps, float wd, int step, const float* scalars,
                             cudaStream_t st);
 
+int vb_fp8_block_cast(const void* x, long ldx, void* y, long ldy, float* scale, int M, int N, cudaStream_t st);
+int vb_fp8_act_cast(const void* x, long ldx, void* y, long ldy, float* scale, long M, int K, cudaStream_t st);
+int vb_fp4_fake_quant(const void* x, void* y, long n, const float* global_amax, cudaStream_t st);
+int vb_delta_compact16(const void* cur, void* snap, long n, int* pos_out, void* val_out, unsigned long long* counter, long cap,
+                       cudaStream_t st);
+int vb_delta_apply16(void* dst, const int* pos, const void* val, long count, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,80 @@
+// torch.ops.verl_b200 bindings of the quantisation casts and the weight-delta kernels.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include "api.h"
+
+void vb_count_launch(int n);
+
+namespace {
+using at::Tensor;
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+void check_rc(int rc, const char* what) {
+  TORCH_CHECK(rc == 0, "verl_b200::", what, " failed with code ", rc);
+  vb_count_launch(1);
+}
+
+// x [M, N] bf16 -> (y [M, N] float8_e4m3fn, scale [ceil(M/128), ceil(N/128)] fp32, multiply to dequantise)
+std::tuple<Tensor, Tensor> fp8_block_cast(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "fp8_block_cast: bad x");
+  const int M = x.size(0), N = x.size(1);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty({M, N}, x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor s = at::empty({(M + 127) / 128, (N + 127) / 128}, x.options().dtype(at::kFloat));
+  check_rc(vb_fp8_block_cast(x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), s.data_ptr<float>(), M, N, cur_stream()), "fp8_block_cast");
+  return {y, s};
+}
+
+// x [M, K] bf16 -> (y [M, K] fp8, scale [M, ceil(K/128)] fp32)
+std::tuple<Tensor, Tensor> fp8_act_cast(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "fp8_act_cast: bad x");
+  const long M = x.size(0);
+  const int K = x.size(1);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty({M, K}, x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor s = at::empty({M, (K + 127) / 128}, x.options().dtype(at::kFloat));
+  check_rc(vb_fp8_act_cast(x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), s.data_ptr<float>(), M, K, cur_stream()), "fp8_act_cast");
+  return {y, s};
+}
+
+Tensor fp4_fake_quant(const Tensor& x, const Tensor& global_amax) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.size(-1) % 16 == 0, "fp4_fake_quant: bad x");
+  TORCH_CHECK(global_amax.is_cuda() && global_amax.scalar_type() == at::kFloat && global_amax.numel() == 1, "fp4_fake_quant: bad amax");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty_like(x);
+  check_rc(vb_fp4_fake_quant(x.data_ptr(), y.data_ptr(), x.numel(), global_amax.data_ptr<float>(), cur_stream()), "fp4_fake_quant");
+  return y;
+}
+
+// cur, snap: flat 16-bit tensors of equal length (multiple of 8). Returns the number of changed elements; the first
+// min(count, cap) (position, value) pairs are in pos_out / val_out. The snapshot is refreshed.
+int64_t delta_compact16(const Tensor& cur, Tensor& snap, Tensor& pos_out, Tensor& val_out) {
+  TORCH_CHECK(cur.is_cuda() && cur.is_contiguous() && snap.is_contiguous() && cur.element_size() == 2 && snap.element_size() == 2 &&
+                  cur.numel() == snap.numel(), "delta_compact16: bad inputs");
+  TORCH_CHECK(pos_out.scalar_type() == at::kInt && val_out.element_size() == 2 && pos_out.numel() == val_out.numel(), "delta_compact16: bad outputs");
+  c10::cuda::CUDAGuard guard(cur.device());
+  Tensor counter = at::zeros({1}, cur.options().dtype(at::kLong));
+  check_rc(vb_delta_compact16(cur.data_ptr(), snap.data_ptr(), cur.numel(), pos_out.data_ptr<int>(), val_out.data_ptr(),
+                              reinterpret_cast<unsigned long long*>(counter.data_ptr<int64_t>()), pos_out.numel(), cur_stream()),
+           "delta_compact16");
+  return counter.item<int64_t>();
+}
+
+void delta_apply16(Tensor& dst, const Tensor& pos, const Tensor& val, int64_t count) {
+  TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && dst.element_size() == 2 && pos.scalar_type() == at::kInt && val.element_size() == 2,
+              "delta_apply16: bad inputs");
+  TORCH_CHECK(count <= pos.numel() && count <= val.numel(), "delta_apply16: count exceeds the buffers");
+  c10::cuda::CUDAGuard guard(dst.device());
+  check_rc(vb_delta_apply16(dst.data_ptr(), pos.data_ptr<int>(), val.data_ptr(), count, cur_stream()), "delta_apply16");
+}
+}  // namespace
+
+TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
+  m.def("fp8_block_cast(Tensor x) -> (Tensor, Tensor)", &fp8_block_cast);
+  m.def("fp8_act_cast(Tensor x) -> (Tensor, Tensor)", &fp8_act_cast);
+  m.def("fp4_fake_quant(Tensor x, Tensor global_amax) -> Tensor", &fp4_fake_quant);
+  m.def("delta_compact16(Tensor cur, Tensor(a!) snap, Tensor(b!) pos_out, Tensor(c!) val_out) -> int", &delta_compact16);
+  m.def("delta_apply16(Tensor(a!) dst, Tensor pos, Tensor val, int count) -> ()", &delta_apply16);
+}

@@ -1,0 +1,128 @@
+"""Low-precision casts: block-wise fp8 (e4m3) for rollout weights / activations and NVFP4 fake quantisation for QAT.
+
+Each function runs the sm_100a kernel on CUDA bf16 inputs and an equivalent PyTorch formulation elsewhere (which is also
+the oracle of the GPU tests). Reference: ``verl/utils/kernel/fp8_kernel.py:53-260`` (scale convention: the stored
+``scale`` is what you MULTIPLY by to dequantise, i.e. ``weight_scale_inv`` in vLLM terms) and ``verl/utils/qat/linear.py:
+42-330`` (``fp4_fake_quant_weight``, ``STEFP4QuantTriton``, ``QATLinear``).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _ext
+from .functional import use_native
+
+__all__ = ["blockwise_cast_to_fp8", "act_cast_to_fp8", "dequant_blockwise_fp8", "fp4_fake_quant", "fp4_fake_quant_ste", "QATLinear",
+           "FP8_MAX", "FP4_MAX"]
+
+FP8_MAX, FP4_MAX = 448.0, 6.0
+
+
+def _blockwise_ref(x: torch.Tensor, bm: int, bn: int):
+    M, N = x.shape
+    pm, pn = (-M) % bm, (-N) % bn
+    xp = torch.nn.functional.pad(x.float(), (0, pn, 0, pm))
+    blocks = xp.reshape((M + pm) // bm, bm, (N + pn) // bn, bn)
+    s = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-10) / FP8_MAX
+    q = (blocks * (1.0 / s)[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).reshape(M + pm, N + pn)[:M, :N]
+    return q.to(torch.float8_e4m3fn), s
+
+
+def blockwise_cast_to_fp8(x: torch.Tensor, block_size=(128, 128)):
+    """``x [M, N]`` → ``(fp8 [M, N], scale [ceil(M/bm), ceil(N/bn)])`` with ``scale = max(absmax, 1e-10) / 448``."""
+    assert x.dim() == 2
+    if tuple(block_size) == (128, 128) and use_native(x):
+        return _ext.ops().fp8_block_cast(x if x.stride(1) == 1 else x.contiguous())
+    return _blockwise_ref(x, int(block_size[0]), int(block_size[1]))
+
+
+def act_cast_to_fp8(x: torch.Tensor):
+    """Dynamic per-token 1×128 group quantisation of activations: ``(fp8 [M, K], scale [M, ceil(K/128)])``."""
+    assert x.dim() == 2
+    if use_native(x) and x.shape[1] % 4 == 0:
+        return _ext.ops().fp8_act_cast(x if x.stride(1) == 1 else x.contiguous())
+    return _blockwise_ref(x, 1, 128)
+
+
+def dequant_blockwise_fp8(q: torch.Tensor, scale: torch.Tensor, block_size=(128, 128), dtype=torch.bfloat16) -> torch.Tensor:
+    M, N = q.shape
+    s = scale.repeat_interleave(block_size[0], 0)[:M].repeat_interleave(block_size[1], 1)[:, :N]
+    return (q.float() * s).to(dtype)
+
+
+_E2M1_EDGES = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)
+_E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def _fp4_ref(x: torch.Tensor, global_amax: torch.Tensor, block: int = 16) -> torch.Tensor:
+    shape = x.shape
+    g = x.float().reshape(-1, block)
+    gs = global_amax.float() / (FP4_MAX * FP8_MAX)
+    gs_safe = torch.where(gs > 0, gs, torch.full_like(gs, 1e-12))
+    sc = (g.abs().amax(-1, keepdim=True) / (FP4_MAX * gs_safe)).clamp(max=FP8_MAX)
+    sc = sc.to(torch.float8_e4m3fn).float() * gs
+    sc = torch.where(sc >= 1e-5, sc, torch.ones_like(sc))
+    a = g.abs() / sc
+    q = torch.zeros_like(a)
+    # round half to even on the E2M1 grid: ties at .25, 1.25, 2.5, 5 go down; ties at .75, 1.75, 3.5 go up
+    for k, (edge, val) in enumerate(zip(_E2M1_EDGES, _E2M1_VALUES[1:])):
+        up_on_tie = k % 2 == 1
+        q = torch.where((a >= edge) if up_on_tie else (a > edge), torch.full_like(a, val), q)
+    return (torch.sign(g) * q * sc).reshape(shape).to(x.dtype)
+
+
+def fp4_fake_quant(x: torch.Tensor, global_amax: torch.Tensor = None, block_size: int = 16) -> torch.Tensor:
+    """Quantise-dequantise to NVFP4 (E2M1 values, e4m3 group scales relative to ``global_amax / (6·448)``)."""
+    if global_amax is None:
+        global_amax = x.detach().abs().max().float()
+    global_amax = global_amax.reshape(1).float()
+    if block_size == 16 and use_native(x) and x.shape[-1] % 16 == 0:
+        return _ext.ops().fp4_fake_quant(x.contiguous(), global_amax.to(x.device))
+    return _fp4_ref(x, global_amax.to(x.device), block_size)
+
+
+class _FP4STE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, global_amax, block_size):
+        return fp4_fake_quant(x, global_amax, block_size)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None, None
+
+
+def fp4_fake_quant_ste(x: torch.Tensor, global_amax: torch.Tensor = None, block_size: int = 16) -> torch.Tensor:
+    """Fake quantisation with a straight-through gradient (quantisation-aware training)."""
+    return _FP4STE.apply(x, global_amax, block_size)
+
+
+class QATLinear(torch.nn.Module):
+    """Linear layer whose weight (and, in ``w4a4`` mode, input) passes through NVFP4 fake quantisation in forward.
+
+    ``weight_amax`` is the global amax used for the group scales; it is initialised from the weight on first use and can
+    be synchronised across ranks with ``sync_amax(group)`` (an all-reduce MAX, as the reference does for FSDP shards).
+    """
+
+    def __init__(self, weight: torch.nn.Parameter, bias=None, mode: str = "w4a16", block_size: int = 16):
+        super().__init__()
+        assert mode in ("w4a16", "w4a4")
+        self.weight, self.bias, self.mode, self.block_size = weight, bias, mode, block_size
+        self.register_buffer("weight_amax", torch.full((1,), -1.0, dtype=torch.float32, device=weight.device))
+
+    @torch.no_grad()
+    def sync_amax(self, group=None):
+        import torch.distributed as dist
+
+        amax = self.weight.detach().abs().max().float().reshape(1)
+        if dist.is_initialized() and (group is not None or dist.get_world_size() > 1):
+            dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
+        self.weight_amax.copy_(amax)
+
+    def forward(self, x):
+        if float(self.weight_amax) < 0:
+            self.sync_amax()
+        w = fp4_fake_quant_ste(self.weight, self.weight_amax, self.block_size)
+        if self.mode == "w4a4":
+            x = fp4_fake_quant_ste(x, None, self.block_size)
+        return torch.nn.functional.linear(x, w, self.bias)
