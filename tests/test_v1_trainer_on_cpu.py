@@ -1,0 +1,84 @@
+"""TransferQueue, replay buffers and the v1 trainers (sync and colocated-async) on the CPU plumbing configuration."""
+
+import json
+
+import torch
+
+from tests.test_trainer_e2e_on_cpu import OV
+from verl_b200.protocol import DataProto
+from verl_b200.trainer.ppo.reward import load_reward_manager
+from verl_b200.trainer.ppo.v1 import ReplayBuffer, ReplayBufferAsync, get_trainer_cls
+from verl_b200.trainer.ppo.v1.checkpoint_callback import CheckpointCallback
+from verl_b200.utils.config import load_config
+from verl_b200.utils.transfer_queue import KVBatchMeta, TransferQueue, tqbridge
+
+
+def test_transfer_queue_roundtrip_and_bridge():
+    tq = TransferQueue()
+    data = DataProto.from_dict(tensors={"x": torch.arange(6).reshape(3, 2)}, non_tensors={"name": ["a", "b", "c"]})
+    meta = KVBatchMeta("p", ["k0", "k1", "k2"])
+    tq.kv_batch_put(meta, data, tags={"status": "finished"})
+    got = tq.kv_get(KVBatchMeta("p", ["k2", "k0"], ["x", "name"]))
+    assert got.batch["x"].tolist() == [[4, 5], [0, 1]] and got.non_tensor_batch["name"].tolist() == ["c", "a"]
+    assert tq.kv_tags("p")["k1"]["status"] == "finished" and tq.size("p") == 3
+
+    import verl_b200.utils.transfer_queue as mod
+
+    mod._TQ = tq
+
+    class W:
+        @tqbridge()
+        def double(self, d: DataProto) -> DataProto:
+            return DataProto.from_dict(tensors={"y": d.batch["x"] * 2})
+
+    m2 = W().double(KVBatchMeta("p", ["k0", "k1"], ["x"]))
+    assert isinstance(m2, KVBatchMeta) and "y" in m2.fields
+    assert tq.kv_get(KVBatchMeta("p", ["k1"], ["y"])).batch["y"].tolist() == [[4, 6]]
+    assert W().double(data).batch["y"].shape == (3, 2)       # plain batches pass through
+    mod._TQ = None
+
+
+def test_replay_buffer_groups_filters_and_staleness():
+    tq = TransferQueue()
+    for uid, scores, step, status in (("a", (1.0, 0.0), 1, "finished"), ("b", (1.0, 1.0), 1, "finished"), ("c", (0.0, 1.0), 3, "finished"),
+                                      ("d", (0.0, 1.0), 3, "running"), ("e", (0.0, 1.0), 3, "failure")):
+        for j, sc in enumerate(scores):
+            tq.kv_put("train", f"{uid}#{j}", {"v": torch.tensor(j)}, {"uid": uid, "status": status if j else "finished", "gen_step": step, "score": sc})
+    rb = ReplayBuffer(tq, rollout_n=2, filter_groups=True)
+    assert rb.get_sampleable_count(3, "train") == 2            # b filtered (equal scores), d running, e failed
+    meta, m = rb.sample(3, "train", 2)
+    assert meta.keys == ["a#0", "a#1", "c#0", "c#1"] and m["replay/evicted_filtered"] == 1 and m["replay/evicted_failure"] == 1
+    assert "b#0" not in tq.kv_tags("train") and "d#0" in tq.kv_tags("train")
+    rba = ReplayBufferAsync(tq, rollout_n=2, max_off_policy_threshold=1)
+    assert rba.get_sampleable_count(3, "train") == 1           # group a (step 1) is two steps old at step 3
+    cb = CheckpointCallback({"save_freq": 2})
+    assert [cb.should_save(i, False) for i in (1, 2, 3)] == [False, True, False] and cb.should_save(3, True)
+
+
+def _run(tmp_path, name, extra=()):
+    logf = tmp_path / f"{name}.jsonl"
+    import os
+
+    os.environ["VERL_FILE_LOGGER_PATH"] = str(logf)
+    try:
+        cfg = load_config("ppo_trainer", [o for o in OV if not o.startswith("trainer.logger")] +
+                          ["trainer.logger=[file]", "trainer.total_training_steps=3", f"trainer.default_local_dir={tmp_path}/ckpt_{name}",
+                           "actor_rollout_ref.rollout.mode=async", "actor_rollout_ref.rollout.free_cache_engine=false",
+                           "trainer.resume_mode=disable"] + list(extra))
+        tr = get_trainer_cls(name)(cfg, reward_fn=load_reward_manager(cfg, None))
+        tr.init()
+        tr.fit()
+    finally:
+        os.environ.pop("VERL_FILE_LOGGER_PATH", None)
+    return [json.loads(x)["data"] for x in logf.read_text().splitlines()]
+
+
+def test_v1_sync_trainer_is_on_policy(tmp_path):
+    rows = _run(tmp_path, "sync")
+    assert len(rows) == 3 and all(r["replay/staleness_max"] == 0 for r in rows) and rows[-1]["perf/total_num_tokens"] > 0
+    assert abs(rows[0]["actor/ppo_kl"]) < 1e-4
+
+
+def test_v1_colocate_async_trainer_runs_ahead(tmp_path):
+    rows = _run(tmp_path, "colocate_async", ["+trainer.v1.async_warmup_batches=1", "+trainer.v1.max_off_policy_threshold=2"])
+    assert len(rows) == 3 and max(r["replay/staleness_max"] for r in rows) >= 1 and rows[-1]["perf/total_num_tokens"] > 0

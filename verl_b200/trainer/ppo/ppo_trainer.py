@@ -329,6 +329,19 @@ def _train_step(self: PPOTrainer, batch_dict: dict) -> dict:
         batch = batch.repeat(repeat_times=n, interleave=True)
         batch.pop(batch_keys=["input_ids", "attention_mask", "position_ids"])
         batch = batch.union(gen_out)
+        metrics.update(self.train_on_rollouts(batch, timing_raw, n))
+    metrics.update(compute_timing_metrics(batch=self._last_batch, timing_raw=timing_raw))
+    metrics.update(compute_throughout_metrics(batch=self._last_batch, timing_raw=timing_raw, n_gpus=max(1, self.actor_rollout_wg.world_size)))
+    return metrics
+
+
+def _train_on_rollouts(self: PPOTrainer, batch: DataProto, timing_raw: dict, n: int) -> dict:
+    """Everything of an RL step after generation: reward, old/ref log-probs, values, advantages, critic and actor updates,
+    weight hand-off. ``batch`` holds prompts joined with their rollouts (one row per trajectory, ``uid`` marks the
+    prompt group). Returns the metrics; timings go to ``timing_raw``. Shared by the v0 step and the v1 trainers."""
+    cfg = self.config
+    metrics: dict = {}
+    with marked_timer("train", timing_raw):
         if "response_mask" not in batch.batch.keys():
             batch.batch["response_mask"] = compute_response_mask(batch)
         if _g(cfg, "trainer.balance_batch", True):
@@ -391,8 +404,6 @@ def _train_step(self: PPOTrainer, batch_dict: dict) -> dict:
         with marked_timer("update_weights", timing_raw):
             self.actor_rollout_wg.update_weights()
     metrics.update(compute_data_metrics(batch=batch, use_critic=self.use_critic))
-    metrics.update(compute_timing_metrics(batch=batch, timing_raw=timing_raw))
-    metrics.update(compute_throughout_metrics(batch=batch, timing_raw=timing_raw, n_gpus=max(1, self.actor_rollout_wg.world_size)))
     metrics.update(compute_variance_proxy_metrics(batch, metrics.get("actor/grad_norm")))
     self._last_batch = batch
     return metrics
@@ -441,5 +452,6 @@ def _fit(self: PPOTrainer):
 
 
 PPOTrainer.step = _train_step
+PPOTrainer.train_on_rollouts = _train_on_rollouts
 PPOTrainer.fit = _fit
 RayPPOTrainer = PPOTrainer

@@ -71,6 +71,7 @@ class LLMServerClient:
         self.servers = dict(servers)
         self.balancer = balancer or GlobalRequestLoadBalancer(list(self.servers))
         self._session = None
+        self.closed = False     # set at shutdown: aborted requests are then returned as they are instead of being resumed
 
     async def _http(self):
         import aiohttp
@@ -130,7 +131,7 @@ class FullyAsyncLLMServerClient(LLMServerClient):
             lps += list(out.log_probs or [])
             preempted += out.num_preempted
             budget = sp.max_tokens - len(toks)
-            if out.stop_reason != "aborted" or budget <= 0:
+            if out.stop_reason != "aborted" or budget <= 0 or self.closed:
                 break
             await asyncio.sleep(self.resume_delay_s)
         reason = out.stop_reason if out.stop_reason != "aborted" or budget > 0 else "length"
