@@ -1,0 +1,134 @@
+"""Small utilities: containers, padding templates, trace/skip helpers, group statistics, score centering."""
+
+import json
+import os
+
+import numpy as np
+import torch
+
+from verl_b200.protocol import DataProto
+
+
+def test_py_functional_and_net_and_dtypes(tmp_path):
+    from verl_b200.utils.fs import copy_to_local, is_non_local, md5_encode
+    from verl_b200.utils.net_utils import format_host_port, get_free_port, is_ipv4, is_ipv6
+    from verl_b200.utils.py_functional import DynamicEnum, append_to_dict, temp_env_var, timeout_limit
+    from verl_b200.utils.torch_dtypes import PrecisionType
+
+    d = {}
+    append_to_dict(d, {"a": 1}, "x/")
+    append_to_dict(d, {"a": 2}, "x/")
+    assert d == {"x/a": [1, 2]}
+    with temp_env_var("VB_T", "1"):
+        assert os.environ["VB_T"] == "1"
+    assert "VB_T" not in os.environ
+
+    class Est(DynamicEnum):
+        pass
+
+    Est.register("gae")
+    Est.register("grpo")
+    assert Est.GRPO.value == 1 and Est.from_name("gae") is Est.GAE and "GAE" in Est and len(list(Est)) == 2
+    with timeout_limit(5):
+        pass
+    assert is_ipv4("127.0.0.1") and is_ipv6("::1") and format_host_port("::1", 80) == "[::1]:80" and get_free_port() > 0
+    assert PrecisionType.to_dtype("bf16") is torch.bfloat16 and PrecisionType.to_str(torch.float32) == "fp32"
+    f = tmp_path / "a.txt"
+    f.write_text("x")
+    assert copy_to_local(str(f)) == str(f) and not is_non_local(str(f)) and len(md5_encode("a")) == 32
+
+
+def test_unpad_pad_roundtrip_with_grad():
+    from verl_b200.utils.attention_utils import pad_input, unpad_input
+
+    x = torch.randn(3, 5, 4, requires_grad=True)
+    mask = torch.tensor([[1, 1, 0, 0, 0], [1, 1, 1, 1, 1], [0, 1, 1, 0, 0]])
+    flat, idx, cu, mx, lens = unpad_input(x, mask)
+    assert flat.shape == (9, 4) and cu.tolist() == [0, 2, 7, 9] and mx == 5
+    back = pad_input(flat, idx, 3, 5)
+    assert torch.equal(back * mask[..., None], back) and torch.allclose(back[mask.bool()], x[mask.bool()])
+    back.sum().backward()
+    assert torch.equal(x.grad, mask[..., None].expand_as(x).float())
+
+
+def test_tensordict_utils_and_padding_templates():
+    from verl_b200.trainer.ppo.padding_utils import remove_padding_samples, upsample_batch_to_divisible_size
+    from verl_b200.utils.tensordict_utils import assign_non_tensor, get_non_tensor_data, get_tensordict, index_select_tensor_dict, to_padded
+
+    data = get_tensordict({"input_ids": torch.arange(12).reshape(3, 4), "ragged": [torch.arange(2), torch.arange(3), torch.arange(1)]},
+                          {"names": ["a", "b", "c"], "temperature": 0.7})
+    assert len(data) == 3 and data.meta_info["temperature"] == 0.7 and data.non_tensor_batch["names"][1] == "b"
+    assert to_padded(data.batch["ragged"], pad_value=-1).tolist() == [[0, 1, -1], [0, 1, 2], [0, -1, -1]]
+    assign_non_tensor(data, uid=["u0", "u1", "u2"], step=3)
+    assert get_non_tensor_data(data, "step") == 3 and index_select_tensor_dict(data, [2, 0]).non_tensor_batch["uid"].tolist() == ["u2", "u0"]
+    b = DataProto.from_dict(tensors={"input_ids": torch.ones(5, 6, dtype=torch.int64), "attention_mask": torch.ones(5, 6, dtype=torch.int64),
+                                     "responses": torch.ones(5, 2, dtype=torch.int64), "response_mask": torch.ones(5, 2, dtype=torch.int64),
+                                     "advantages": torch.ones(5, 2)}, non_tensors={"uid": ["a"] * 5})
+    out, pad = upsample_batch_to_divisible_size(b, 4)
+    assert len(out) == 8 and pad == 3 and out.batch["response_mask"][5:].sum() == 0 and out.batch["attention_mask"][5:].sum() == 3
+    assert out.batch["advantages"][5:].abs().sum() == 0 and len(remove_padding_samples(out)) == 5
+
+
+def test_trace_skip_and_tracker(tmp_path):
+    from verl_b200.utils.rollout_skip import SkipManager
+    from verl_b200.utils.rollout_trace import RolloutTraceConfig, TrajectoryTracker, rollout_trace_attr, rollout_trace_op
+
+    class S:
+        @rollout_trace_op
+        def gen(self, ids, k=1):
+            return {"out": [i + k for i in ids]}
+
+    RolloutTraceConfig.init("p", "e", "jsonl", path=str(tmp_path / "t.jsonl"))
+    with rollout_trace_attr(sample_index=3, step=1):
+        S().gen([1, 2], k=2)
+    RolloutTraceConfig.reset()
+    rec = json.loads((tmp_path / "t.jsonl").read_text().splitlines()[0])
+    assert rec["attrs"]["sample_index"] == 3 and rec["output"] == {"out": [3, 4]} and rec["inputs"] == {"ids": [1, 2], "k": 2}
+    calls = []
+
+    def gen(p):
+        calls.append(1)
+        return DataProto.from_dict(tensors={"r": p.batch["x"] + 1})
+
+    sm = SkipManager(True, str(tmp_path / "dump"), max_dump_step=1)
+    p = DataProto.from_dict(tensors={"x": torch.zeros(2, 1)}, meta_info={"global_steps": 1})
+    a, b = sm.wrap(gen)(p), sm.wrap(gen)(p)
+    assert len(calls) == 1 and torch.equal(a.batch["r"], b.batch["r"]) and sm.hits == 1
+    tr = TrajectoryTracker(str(tmp_path / "traj"))
+    tr.track("logp", torch.ones(3))
+    path = tr.dump(1)
+    assert TrajectoryTracker.compare(torch.load(path), {"logp": torch.ones(3)})["logp"]["close"]
+
+
+def test_group_mean_std_and_score_centering():
+    from verl_b200.trainer.ppo.score_centering import (pad_rollout_topk, score_centering_correction, score_centering_weight_fn,
+                                                       topk_log_probs_from_hidden, topk_log_probs_from_logits)
+    from verl_b200.utils.groupwise import as_torch_index, group_mean_std
+
+    g = as_torch_index(np.array(["a", "b", "a", "c"], dtype=object))
+    mean, std, cnt = group_mean_std(torch.tensor([1.0, 5.0, 3.0, 7.0]), g)
+    assert g.tolist() == [0, 1, 0, 2] and mean.tolist() == [2.0, 0.0, 0.0] and abs(float(std[0]) - 2 ** 0.5) < 1e-6 and std[1] == 1
+    torch.manual_seed(0)
+    logits = torch.randn(10, 50, requires_grad=True)
+    ids = torch.topk(logits.detach() + 0.3 * torch.randn(10, 50), 5).indices
+    lp = topk_log_probs_from_logits(logits, ids, chunk_size=4)
+    ref = torch.log_softmax(logits, -1).gather(-1, ids)
+    assert torch.allclose(lp, ref, atol=1e-6)
+    gref = torch.autograd.grad(ref.sum() * 2, logits)[0]
+    gl = torch.autograd.grad(lp.sum() * 2, logits)[0]
+    assert torch.allclose(gl, gref, atol=1e-6)
+    h, w = torch.randn(10, 16, requires_grad=True), torch.randn(50, 16)
+    assert torch.allclose(topk_log_probs_from_hidden(h, w, ids, chunk_size=3), torch.log_softmax(h @ w.t(), -1).gather(-1, ids), atol=1e-5)
+    # when sampler == trainer and no IS weight, the coefficients q - rho*p vanish: no correction and no gradient
+    corr, qm, pm = score_centering_correction(lp, lp.detach(), score_centering_weight_fn(None))
+    assert corr.abs().max() < 1e-5 and torch.allclose(qm, pm)
+    # full-vocabulary head: the gradient equals that of sum_j sg[q_j - p_j] log p_j
+    all_ids = torch.arange(50).expand(10, 50)
+    q = torch.log_softmax(torch.randn(10, 50), -1)
+    lp_all = topk_log_probs_from_logits(logits, all_ids)
+    w_tis = score_centering_weight_fn("token", 2.0)
+    corr, _, _ = score_centering_correction(lp_all, q, w_tis)
+    assert corr.shape == (10,) and torch.isfinite(corr).all()
+    ids2, lps2 = pad_rollout_topk(torch.ones(3, 4, dtype=torch.int64), torch.zeros(3, 4), prompt_length=5)
+    assert ids2.shape == (8, 4) and (ids2[4:7] == 1).all() and (lps2[:4] < 0).all()
+    assert score_centering_weight_fn("token", "0.5_2.0")(torch.tensor([0.1, 1.0, 3.0])).tolist() == [0.0, 1.0, 0.0]
