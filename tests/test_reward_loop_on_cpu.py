@@ -1,0 +1,72 @@
+"""Reward-loop managers and the extra rule-based scorers."""
+
+import asyncio
+import time
+
+import torch
+
+from verl_b200.experimental.reward_loop import RewardLoopManager, get_reward_loop_manager_cls
+from verl_b200.protocol import DataProto
+from verl_b200.utils.config import Config
+from verl_b200.utils.reward_score import default_compute_score
+from verl_b200.utils.tokenizer import ByteChatTokenizer
+
+
+def test_scorers():
+    assert default_compute_score("math_dapo", "blah blah\nAnswer: $\\boxed{42}$", "42")["score"] == 1.0
+    assert default_compute_score("aime2024", "Answer: 7", "8")["score"] == -1.0
+    assert default_compute_score("searchR1_nq", "<answer>The Eiffel Tower</answer>", {"target": ["eiffel tower"]}) == 1.0
+    s = default_compute_score("geo3k", "<think>x</think> so \\boxed{12}", "12")
+    assert abs(s - 1.0) < 1e-9 and default_compute_score("geo3k", "\\boxed{12}", "12") == 0.9
+
+
+def _batch(tok, texts, R=24):
+    ids = torch.full((len(texts), 4 + R), tok.pad_token_id)
+    att = torch.zeros(len(texts), 4 + R, dtype=torch.int64)
+    att[:, :4] = 1
+    for i, t in enumerate(texts):
+        e = tok.encode(t)
+        ids[i, 4: 4 + len(e)] = torch.tensor(e)
+        att[i, 4: 4 + len(e)] = 1
+    return DataProto.from_dict(tensors={"input_ids": ids, "attention_mask": att, "responses": ids[:, 4:]},
+                               non_tensors={"data_source": ["gsm8k"] * len(texts), "reward_model": [{"ground_truth": "5"}] * len(texts)})
+
+
+def test_reward_loop_manager_scores_at_last_token():
+    tok = ByteChatTokenizer()
+    texts = ["so #### 5", "hmm #### 6", "#### 5"]
+    mgr = RewardLoopManager(Config({"reward": {"reward_manager": "naive"}}), tok, num_workers=2)
+    out = mgr.compute_rm_score(_batch(tok, texts))
+    sc = out.batch["rm_scores"]
+    assert sc.sum(-1).tolist() == [1.0, 0.0, 1.0] and sc[0, len(texts[0]) - 1] == 1.0 and sc[2, len(texts[2]) - 1] == 1.0
+    assert out.non_tensor_batch["acc"].tolist() == [1.0, 0.0, 1.0]
+    mgr.shutdown()
+
+
+def test_dapo_overlong_gdpo_components_and_rate_limit():
+    tok = ByteChatTokenizer()
+    cfg = Config({"data": {"max_response_length": 20}, "reward": {"reward_kwargs": {"overlong_buffer_cfg": {"enable": True, "len": 10, "penalty_factor": 1.0, "log": True},
+                                                                                     "max_concurrent": 2, "max_rpm": 0, "timeout": 0.05}}})
+    dapo = get_reward_loop_manager_cls("dapo")(cfg, tok, lambda **kw: 1.0)
+    r = asyncio.run(dapo.run_single({"response_str": "x", "valid_response_length": 15}))
+    assert abs(r["reward_score"] - 0.5) < 1e-9 and r["reward_extra_info"]["overlong"]
+    gdpo = get_reward_loop_manager_cls("gdpo")(cfg, tok, lambda **kw: {"components": {"correct": 1.0, "format": 0.25}})
+    r = asyncio.run(gdpo.run_single({"response_str": "x", "valid_response_length": 1}))
+    assert r["reward_score"] == 1.25 and r["reward_extra_info"]["reward_components"] == {"correct": 1.0, "format": 0.25}
+
+    running, peak = [0], [0]
+
+    async def slow(**kw):
+        running[0] += 1
+        peak[0] = max(peak[0], running[0])
+        await asyncio.sleep(0.01 if kw["solution_str"] != "slow" else 1.0)
+        running[0] -= 1
+        return 1.0
+
+    lim = get_reward_loop_manager_cls("limited")(cfg, tok, slow)
+
+    async def go():
+        return await asyncio.gather(*[lim.run_single({"response_str": "slow" if i == 0 else "ok", "valid_response_length": 1}) for i in range(6)])
+
+    res = asyncio.run(go())
+    assert peak[0] <= 2 and res[0]["reward_extra_info"].get("timeout") and res[1]["reward_score"] == 1.0

@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from . import gsm8k, math_reward, synthetic
+from . import geo3k, gsm8k, math_dapo, math_reward, search_r1_like_qa_em, synthetic
 
 __all__ = ["default_compute_score"]
 
@@ -10,8 +10,15 @@ __all__ = ["default_compute_score"]
 def default_compute_score(data_source: str, solution_str: str, ground_truth, extra_info=None, **kwargs):
     if data_source in ("openai/gsm8k", "gsm8k"):
         return gsm8k.compute_score(solution_str, ground_truth)
-    if data_source in ("lighteval/MATH", "DigitalLearningGmbH/MATH-lighteval", "HuggingFaceH4/MATH-500", "math", "math_dapo") or str(data_source).startswith("aime"):
+    if data_source in ("lighteval/MATH", "DigitalLearningGmbH/MATH-lighteval", "HuggingFaceH4/MATH-500", "math"):
         return math_reward.compute_score(solution_str, ground_truth)
+    if data_source in ("math_dapo", "math", "math_dapo_reasoning") or str(data_source).startswith("aime"):
+        return math_dapo.compute_score(solution_str, ground_truth)
+    if data_source in ("hiyouga/geometry3k", "geo3k"):
+        return geo3k.compute_score(solution_str, ground_truth)
+    if data_source in ("searchR1_nq", "searchR1_triviaqa", "searchR1_popqa", "searchR1_hotpotqa", "searchR1_2wikimultihopqa",
+                       "searchR1_musique", "searchR1_bamboogle"):
+        return search_r1_like_qa_em.compute_score(solution_str, ground_truth)
     if data_source in ("synthetic/mod7", "mod7"):
         return synthetic.compute_score_from_text(solution_str, ground_truth)
     raise NotImplementedError(f"Reward function is not implemented for data_source={data_source!r}")

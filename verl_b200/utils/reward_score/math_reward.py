@@ -47,3 +47,14 @@ def compute_score(solution_str: str, ground_truth: str) -> float:
         return 1.0 if normalize(remove_boxed(boxed)) == normalize(str(ground_truth)) else 0.0
     except Exception:
         return 0.0
+
+
+def is_equiv(a: str, b: str) -> bool:
+    """Answers are equivalent when their normalised forms match as text (or as numbers when both parse)."""
+    na, nb = normalize(a), normalize(b)
+    if na == nb:
+        return True
+    try:
+        return abs(float(na) - float(nb)) < 1e-9
+    except ValueError:
+        return False
