@@ -82,3 +82,31 @@ def test_v1_sync_trainer_is_on_policy(tmp_path):
 def test_v1_colocate_async_trainer_runs_ahead(tmp_path):
     rows = _run(tmp_path, "colocate_async", ["+trainer.v1.async_warmup_batches=1", "+trainer.v1.max_off_policy_threshold=2"])
     assert len(rows) == 3 and max(r["replay/staleness_max"] for r in rows) >= 1 and rows[-1]["perf/total_num_tokens"] > 0
+
+
+def test_one_step_off_policy_and_fully_async_trainers(tmp_path):
+    import verl_b200.experimental.fully_async_policy  # noqa: F401 - registers "fully_async"
+    import verl_b200.experimental.one_step_off_policy  # noqa: F401 - registers "one_step_off_policy"
+
+    rows = _run(tmp_path, "one_step_off_policy")
+    assert len(rows) == 3 and [r["replay/staleness_max"] for r in rows] == [1, 1, 1]
+    rows = _run(tmp_path, "fully_async", ["+trainer.v1.staleness_threshold=3", "+trainer.v1.queue_batches=2"])
+    assert len(rows) == 3 and rows[-1]["perf/total_num_tokens"] > 0 and max(r["replay/staleness_max"] for r in rows) <= 3
+
+
+def test_distillation_losses():
+    from verl_b200.trainer.distillation import forward_kl, jsd, reverse_kl, topk_distillation_loss
+
+    torch.manual_seed(0)
+    t = torch.log_softmax(torch.randn(6, 30), -1)
+    s = torch.log_softmax(torch.randn(6, 30), -1).requires_grad_(True)
+    idx = t.topk(5).indices
+    th, sh = t.gather(-1, idx), s.gather(-1, idx)
+    for f in (forward_kl, reverse_kl, jsd):
+        assert (f(sh, th) >= -1e-6).all() and f(th, th).abs().max() < 1e-6
+    # with the whole vocabulary in the head the forward KL is the exact KL
+    full = forward_kl(s, t)
+    assert torch.allclose(full, (t.exp() * (t - s)).sum(-1), atol=1e-4)
+    loss, m = topk_distillation_loss(sh, th, torch.ones(2, 3), "jsd")
+    loss.backward()
+    assert s.grad is not None and 0 <= m["distill/top1_agreement"] <= 1
