@@ -14,7 +14,7 @@ from typing import Iterable, Iterator
 
 import torch
 
-__all__ = ["load_hf_weights", "iter_safetensors", "save_hf_weights", "MAX_SHARD_BYTES"]
+__all__ = ["load_hf_weights", "iter_safetensors", "save_hf_weights", "save_hf_checkpoint", "MAX_SHARD_BYTES"]
 
 MAX_SHARD_BYTES = 5 * 1024**3
 
@@ -70,3 +70,11 @@ def save_hf_weights(named_tensors: Iterable[tuple[str, torch.Tensor]], path: str
         with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
             json.dump({"metadata": {"total_size": sum(sizes)}, "weight_map": weight_map}, f, indent=2)
     return files
+
+
+def save_hf_checkpoint(model, path: str, dtype: torch.dtype = torch.bfloat16) -> None:
+    """``config.json`` + safetensors shards of a ``DecoderLM`` in HuggingFace layout (loadable by ``transformers``)."""
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(model.cfg.to_hf_dict(), f, indent=2)
+    save_hf_weights(model.hf_named_tensors(), path, dtype=dtype)
