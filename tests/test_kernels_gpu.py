@@ -215,3 +215,25 @@ def test_kv_cache_write(o):
         b, off = int(slots[t]) // 64, int(slots[t]) % 64
         assert torch.equal(cache[b, 0, :, off], k[t]) and torch.equal(cache[b, 1, :, off], v[t])
     assert cache.abs().sum(dim=(1, 2, 3, 4)).count_nonzero() <= 8
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_pair_cta_group_2(a_mn, b_mn):
+    """256 x 256 tiles computed by SM pairs (tcgen05.mma.cta_group::2) against an fp32 matmul, ragged edges included."""
+    from verl_b200.ops import _ext
+
+    o = _ext.ops()
+    torch.manual_seed(0)
+    for M, N, K in ((512, 512, 256), (1000, 776, 328), (2304, 1536, 1024)):
+        a = (torch.randn(K, M, device="cuda") if a_mn else torch.randn(M, K, device="cuda")).bfloat16()
+        b = (torch.randn(K, N, device="cuda") if b_mn else torch.randn(N, K, device="cuda")).bfloat16()
+        ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        o.gemm(a, b, out, None, a_mn, b_mn, False, 512)
+        _ext.check_status("gemm_pair")
+        torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=0.35)
+        acc = torch.ones(M, N, device="cuda", dtype=torch.float32)
+        bias = torch.randn(N, device="cuda").bfloat16()
+        o.gemm(a, b, acc, bias, a_mn, b_mn, True, 512)
+        _ext.check_status("gemm_pair accumulate")
+        torch.testing.assert_close(acc, ref + 1.0 + bias.float()[None], rtol=1e-3, atol=2e-2)

@@ -1,5 +1,7 @@
 // torch.ops.verl_b200.* bindings: thin argument checks + raw-pointer launches of the extern "C" kernels.
 // The kernels themselves do not depend on libtorch.
+#include <cstdlib>
+
 #include <ATen/ATen.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -65,6 +67,16 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Ten
   }
   c10::cuda::CUDAGuard guard(a.device());
   int* err = status_word(a.get_device()).data_ptr<int>();
+  // bn == 512 asks for the paired-CTA kernel (256 x 256 tiles on two SMs); bn == 0 picks it when the problem fills
+  // every SM pair with such tiles, unless VERL_B200_GEMM_PAIR=0.
+  static const bool pair_auto = []() { const char* e = getenv("VERL_B200_GEMM_PAIR"); return e == nullptr || e[0] != '0'; }();
+  const bool pair_fits = ((M + 255) / 256) * ((N + 255) / 256) >= 74 && K >= 256;
+  if (bn == 512 || (bn == 0 && pair_auto && pair_fits)) {
+    check_rc(vb_gemm_bf16_pair(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias_p, (int)M, (int)N, (int)K, (int)a.stride(0),
+                               (int)b.stride(0), (int)out.stride(0), a_mn, b_mn, out_f32, accumulate, err, cur_stream()),
+             "gemm_pair");
+    return;
+  }
   int bn_sel = 0, split = 1;
   vb_gemm_plan((int)M, (int)N, (int)K, b_mn, (int)bn, &bn_sel, &split);
   Tensor ws;

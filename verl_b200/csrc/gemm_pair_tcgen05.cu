@@ -1,0 +1,381 @@
+// bf16 GEMM with two CTAs (one thread-block cluster of 2 = two SMs) cooperating on one 256 x BN output tile through
+// tcgen05.mma.cta_group::2.
+//
+// Why: with a single-CTA 128x256 MMA every SM streams 128 rows of A and 256 rows of B from shared memory for each K
+// step, which nearly saturates the shared-memory read path. In pair mode the two SMs each hold their own 128 rows of
+// A but only HALF of the B tile (BN/2 rows); the tensor cores of both SMs read both halves, so per-SM operand
+// traffic drops by a third and the same ring holds deeper pipelines.
+//
+// Layout of a pair (cluster rank r = 0 "leader", r = 1 "peer"):
+//   * shared memory ring per CTA: A[128 x 64] of rows m0 + 128 r, B[(BN/2) x 64] of columns n0 + (BN/2) r;
+//   * TMEM per CTA: accumulator rows m0 + 128 r .. +127, BN fp32 columns, double buffered;
+//   * producer warp (each CTA): waits its own `empty`, announces its bytes on the LEADER's `full` barrier and issues
+//     its TMA loads with the leader's barrier as completion target (cp.async.bulk.tensor ... cta_group::2);
+//   * MMA thread (leader only): waits `full`, issues the 256-row MMAs, then commits to `empty` of BOTH CTAs;
+//   * epilogue warps (each CTA): wait their own `tmem full`, read their own TMEM lanes, store their 128 rows, and
+//     arrive on the leader's `tmem empty` barrier (count 256).
+// Every wait is bounded; a pair that gives up records a status word and both CTAs still meet at the closing cluster
+// barrier so neither exits while the other may touch its shared memory.
+#include "common.cuh"
+#include "tma_host.h"
+
+namespace vb {
+namespace pair {
+
+constexpr int BM = 128;          // rows per CTA; a pair covers 256
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int A_TILE_BYTES = BM * BK * 2;
+
+template <int BN>
+struct Cfg {
+  static constexpr int B_TILE_BYTES = (BN / 2) * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+  static constexpr int MAX_STAGES = (216 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 2 * BN;
+};
+
+enum : int { OUT_F32 = 1, ACCUM = 2 };
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of `local_addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
+  return a;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  // relaxed: the barrier only counts bytes here; the data itself is published by the TMA completion mechanism
+  asm volatile("mbarrier.arrive.expect_tx.relaxed.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory whose completion bytes are credited to a barrier given as a cluster address
+// (the leader's barrier for both CTAs of the pair).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, int x, int y, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(bar_cluster_addr)
+      : "memory");
+}
+template <int NCOLS>
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst) {  // one whole warp in EACH CTA, same warp id
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(NCOLS) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+template <int NCOLS>
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(NCOLS) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// Arrive on the barrier at `bar_cluster_addr` once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
+                 const bf16* __restrict__ bias, int M, int N, int K, int ldc, int flags, int* err_word) {
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES);   // used in the leader only
+  uint64_t* empty_bar = full_bar + STAGES;                                              // one set per CTA
+  uint64_t* tfull_bar = empty_bar + STAGES;                                             // one set per CTA
+  uint64_t* tempty_bar = tfull_bar + 2;                                                 // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_m = (M + 2 * BM - 1) / (2 * BM);
+  const int num_n = (N + BN - 1) / BN;
+  const int num_kb = (K + BK - 1) / BK;
+  const int num_tiles = num_m * num_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 2);      // one arrive.expect_tx from each CTA's producer
+      mbar_init(&empty_bar[s], 1);     // one commit from the leader's MMA thread
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 256);  // the epilogue threads of both CTAs
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair<C::TMEM_COLS>(tmem_slot);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                  // barriers of both CTAs exist before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  constexpr int GROUP_M = 4;           // 4 x 256 rows share a B column block in L2
+  auto tile_coords = [&](int t, int& mb, int& nb) {
+    int per_group = GROUP_M * num_n;
+    int g = t / per_group;
+    int first_m = g * GROUP_M;
+    int gsz = min(num_m - first_m, GROUP_M);
+    int r = t - g * per_group;
+    mb = first_m + (r % gsz);
+    nb = r / gsz;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+        int mb, nb;
+        tile_coords(t, mb, nb);
+        const int m0 = mb * 2 * BM + (int)rank * BM;
+        const int n0 = nb * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_EMPTY)) { ok = false; break; }
+          uint8_t* sa = smem + s * C::STAGE_BYTES;
+          uint8_t* sb = sa + A_TILE_BYTES;
+          const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[s]), 0);
+          mbar_arrive_expect_tx_cluster(full_leader, C::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d_pair(sa, &tmA, k0, m0, full_leader);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d_pair(sa + i * (BK * 128), &tmA, m0 + 64 * i, k0, full_leader);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sb, &tmB, k0, n0, full_leader);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 128; ++i) tma_load_2d_pair(sb + i * (BK * 128), &tmB, n0 + 64 * i, k0, full_leader);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc(2 * BM, BN, 1, 1, A_MN, B_MN);
+      int s = 0;
+      uint32_t ph = 0, it = 0;
+      bool ok = true;
+      for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+        const uint32_t acc = it & 1;
+        const uint32_t acc_ph = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint32_t sb = sa + A_TILE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t ad = A_MN ? make_sdesc_sw128(sa + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sa + k * 32, 16, 1024);
+            uint64_t bd = B_MN ? make_sdesc_sw128(sb + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sb + k * 32, 16, 1024);
+            umma_f16_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
+          }
+          const uint32_t e_local = smem_u32(&empty_bar[s]);
+          umma_commit_pair(map_to_cta(e_local, 0));
+          umma_commit_pair(map_to_cta(e_local, 1));
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) {
+          const uint32_t f_local = smem_u32(&tfull_bar[acc]);
+          umma_commit_pair(map_to_cta(f_local, 0));
+          umma_commit_pair(map_to_cta(f_local, 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (128 threads per CTA, own rows)
+    const int q = warp & 3;
+    const bool out_f32 = flags & OUT_F32;
+    const bool accum = flags & ACCUM;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+      int mb, nb;
+      tile_coords(t, mb, nb);
+      const uint32_t acc = it & 1;
+      const uint32_t acc_ph = (it >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, err_word, VB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int row = mb * 2 * BM + (int)rank * BM + q * 32 + lane;
+      const int n0 = nb * BN;
+      const uint32_t taddr = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < N) f[j] += __bfloat162float(bias[col0 + j]);
+          }
+          const bool full = (col0 + 32 <= N);
+          if (out_f32) {
+            float* crow = reinterpret_cast<float*>(Cv) + (size_t)row * ldc + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                if (accum) {
+                  const float4 p = *reinterpret_cast<float4*>(crow + j);
+                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                }
+                *reinterpret_cast<float4*>(crow + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) crow[j] = accum ? crow[j] + f[j] : f[j];
+            }
+          } else {
+            bf16* crow = reinterpret_cast<bf16*>(Cv) + (size_t)row * ldc + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (accum) {
+                  const uint4 p = *reinterpret_cast<uint4*>(crow + j);
+                  const __nv_bfloat162* ph2 = reinterpret_cast<const __nv_bfloat162*>(&p);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 pf = __bfloat1622float2(ph2[e]);
+                    f[j + 2 * e] += pf.x;
+                    f[j + 2 * e + 1] += pf.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(f[j], f[j + 1]);
+                o.y = pack_bf16x2(f[j + 2], f[j + 3]);
+                o.z = pack_bf16x2(f[j + 4], f[j + 5]);
+                o.w = pack_bf16x2(f[j + 6], f[j + 7]);
+                *reinterpret_cast<uint4*>(crow + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) {
+                  const float o = accum ? __bfloat162float(crow[j]) + f[j] : f[j];
+                  crow[j] = __float2bfloat16(o);
+                }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // a wait was abandoned: let copies and MMAs that are still in flight land before the ring and TMEM go away
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) { __nanosleep(1000); }
+  }
+  __syncthreads();
+  cluster_sync_all();                  // the peer may still be signalling this CTA's barriers until here
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair<C::TMEM_COLS>(tmem_base);
+  }
+}
+
+static int g_sms = 0;
+static int sm_count() {
+  if (g_sms == 0) {
+    int dev;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_sms;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch(const void* A, const void* B, void* Cp, const void* bias, int M, int N, int K, int lda, int ldb, int ldc, int flags,
+                  int* err_word, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN) rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK);
+  else       rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, BK, 64);
+  if (rc) return rc;
+  if (!B_MN) rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BN / 2, BK);
+  else       rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
+  if (rc) return rc;
+  static bool attr_set = false;
+  auto kern = gemm_pair_kernel<BN, A_MN, B_MN>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  int pairs = sm_count() / 2;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<2 * pairs, 192, C::SMEM_BYTES, stream>>>(tmA, tmB, Cp, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags, err_word);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace pair
+}  // namespace vb
+
+// Same contract as vb_gemm_bf16 without split-K: C[M,N] (+)= op(A) op(B) (+ bias), 256 x 256 tiles on SM pairs.
+// Requirements beyond vb_gemm_bf16's: N % 128 == 0 is NOT required (edges are masked), but the K-major B tile is
+// loaded in halves of 128 rows, so ldb and the base must satisfy the same 16-byte rules.
+extern "C" int vb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb, int ldc,
+                                 int a_mn, int b_mn, int out_f32, int accumulate, int* err_word, cudaStream_t stream) {
+  using namespace vb::pair;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return -3;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -4;
+  const int flags = (out_f32 ? OUT_F32 : 0) | (accumulate ? ACCUM : 0);
+  if (!a_mn && !b_mn) return launch<256, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream);
+  if (!a_mn && b_mn) return launch<256, false, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream);
+  if (a_mn && b_mn) return launch<256, true, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream);
+  return launch<256, true, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream);
+}
