@@ -75,6 +75,8 @@ def build_config(args, world: int):
         f"trainer.n_gpus_per_node={world}", "trainer.nnodes=1", f"trainer.total_training_steps={args.steps + args.warmup}",
         "trainer.resume_mode=disable", "trainer.save_freq=-1",
     ]
+    if args.ref_offload:
+        ov.append("actor_rollout_ref.ref.fsdp_config.param_offload=true")
     return load_config("ppo_trainer", ov)
 
 
@@ -161,13 +163,14 @@ def run_native(args):
                        "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + response <= {args.response_length}",
                        "parallelism": f"dp{world} (ZeRO-2 sharded optimizer, resident bf16 params), rollout tp1 x {world} replicas colocated",
                        "ppo_mini_batch_prompts": args.mini_prompts_per_gpu * world, "token_budget_per_micro_batch": args.token_budget,
-                       "gradient_checkpointing": bool(args.grad_ckpt), "loss": "grpo clip 0.2 + low_var_kl 1e-3, AdamW lr 1e-6",
+                       "gradient_checkpointing": bool(args.grad_ckpt), "ref_param_offload": bool(args.ref_offload), "loss": "grpo clip 0.2 + low_var_kl 1e-3, AdamW lr 1e-6",
                        "l2_policy": "inputs larger than L2: each step streams >15 GB of weights and fresh activations"},
             "clocks": _summarise_clocks(samples),
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches,
             "step_breakdown_s": {k.split("/", 1)[1]: round(v, 3) for k, v in last.items() if k.startswith("timing_s/")},
             "tokens_per_step": tokens / args.steps,
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1),
         }
         print(json.dumps(out), flush=True)
     if world > 1:
@@ -215,11 +218,17 @@ def main():
     ap.add_argument("--token-budget", type=int, default=0, help="tokens per training micro-batch; 0 = 16384 with recomputation, 8192 without")
     ap.add_argument("--kv-util", type=float, default=0.3)
     ap.add_argument("--grad-ckpt", type=int, default=-1,
-                    help="activation recomputation: -1 = only on 1 GPU, where the unsharded fp32 optimizer state leaves no room for stored activations")
+                    help="activation recomputation (default off: activations of an 8192-token micro-batch are stored)")
+    ap.add_argument("--ref-offload", type=int, default=-1, help="keep the frozen reference weights in pinned host memory between its passes")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
+    single = int(os.environ.get("WORLD_SIZE", "1")) == 1
     if args.grad_ckpt < 0:
-        args.grad_ckpt = 1 if int(os.environ.get("WORLD_SIZE", "1")) == 1 else 0
+        args.grad_ckpt = 0
+    if args.ref_offload < 0:
+        # on one GPU the unsharded fp32 optimizer state (91 GB) leaves room for stored activations only if the frozen
+        # reference weights wait in pinned host memory between their passes
+        args.ref_offload = 1 if single and not args.grad_ckpt else 0
     if args.token_budget <= 0:
         args.token_budget = 16384 if args.grad_ckpt else 8192
     if args.impl == "reference":

@@ -335,11 +335,17 @@ class FSDPEngine(BaseEngine):
         to_cpu = target.type == "cpu"
         if model and self.store is not None:
             if to_cpu and self.store.flat.is_cuda:
-                host = torch.empty(self.store.flat.shape, dtype=self.store.flat.dtype, pin_memory=True)
-                host.copy_(self.store.flat, non_blocking=True)
-                torch.cuda.current_stream().synchronize()
+                host = getattr(self, "_host_flat", None)
+                if host is None or not self.forward_only:
+                    host = torch.empty(self.store.flat.shape, dtype=self.store.flat.dtype, pin_memory=True)
+                    host.copy_(self.store.flat, non_blocking=True)
+                    torch.cuda.current_stream().synchronize()
+                    IO_STATS["d2h_bytes"] += host.numel() * host.element_size()
+                    if self.forward_only:
+                        self._host_flat = host      # frozen weights: the pinned copy stays valid, later offloads copy nothing
                 self.store.rebind(host)
             elif not to_cpu and not self.store.flat.is_cuda:
+                IO_STATS["h2d_bytes"] += self.store.flat.numel() * self.store.flat.element_size()
                 self.store.rebind(self.store.flat.to(target, non_blocking=True))
         if optimizer and not self.forward_only:
             for name in ("master", "exp_avg", "exp_avg_sq"):
@@ -585,6 +591,7 @@ class FSDPEngine(BaseEngine):
         self.checkpoint_manager.save_checkpoint(local_path, hdfs_path, global_step, max_ckpt_to_keep)
 
     def load_checkpoint(self, local_path, hdfs_path=None, del_local_after_load=False, **kwargs):
+        self._host_flat = None           # a cached pinned copy of frozen weights would be stale after this
         self.checkpoint_manager.load_checkpoint(local_path, hdfs_path, del_local_after_load)
 
 
