@@ -132,3 +132,32 @@ def test_group_mean_std_and_score_centering():
     ids2, lps2 = pad_rollout_topk(torch.ones(3, 4, dtype=torch.int64), torch.zeros(3, 4), prompt_length=5)
     assert ids2.shape == (8, 4) and (ids2[4:7] == 1).all() and (lps2[:4] < 0).all()
     assert score_centering_weight_fn("token", "0.5_2.0")(torch.tensor([0.1, 1.0, 3.0])).tolist() == [0.0, 1.0, 0.0]
+
+
+def test_naive_rollout_matches_engine_greedy_and_engine_aliases():
+    from verl_b200.models.config import PRESETS
+    from verl_b200.models.transformer import DecoderLM
+    from verl_b200.workers.engine.base import EngineRegistry
+    from verl_b200.workers.rollout.engine import InferenceEngine, SamplingParams
+    from verl_b200.workers.rollout.naive import NaiveRollout
+
+    model = DecoderLM(PRESETS["tiny-qwen2"], dtype=torch.float32, seed=5)
+    prompts = [[11, 12, 13, 14, 15], [21, 22, 23]]
+    P = 6
+    ids = torch.zeros(2, P, dtype=torch.int64)
+    att = torch.zeros(2, P, dtype=torch.int64)
+    for i, p in enumerate(prompts):
+        ids[i, P - len(p):] = torch.tensor(p)
+        att[i, P - len(p):] = 1
+    out = NaiveRollout(model, response_length=6, do_sample=False).generate_sequences(
+        DataProto.from_dict(tensors={"input_ids": ids, "attention_mask": att}, meta_info={"do_sample": False}))
+    want = InferenceEngine(model, max_num_seqs=4, max_model_len=64, num_blocks=16).generate(prompts, SamplingParams(temperature=0.0, max_tokens=6))
+    for i, w in enumerate(want):
+        assert out.batch["responses"][i].tolist() == w.token_ids
+        assert torch.allclose(out.batch["rollout_log_probs"][i], torch.tensor(w.log_probs), atol=1e-4)
+    eng = EngineRegistry.new("language_model", "veomni", PRESETS["tiny-qwen2"], {"seed": 1}, None, {})
+    assert type(eng).__name__ == "FSDPEngine"
+    assert type(EngineRegistry.new("language_model", "mindspeed", PRESETS["tiny-qwen2"], {"seed": 1}, None, {})).__name__ == "MegatronEngine"
+    from verl_b200.utils.transformers_compat import drop_tied_weight_keys, is_transformers_version_in_range
+
+    assert is_transformers_version_in_range("4.0") and "lm_head.weight" not in drop_tied_weight_keys({"lm_head.weight": 1, "a": 2}, True)

@@ -185,5 +185,7 @@ class EngineRegistry:
 
         if backend == "megatron":
             import verl_b200.workers.engine.megatron  # noqa: F401
+        elif not backend.startswith("fsdp"):
+            import verl_b200.workers.engine.aliases  # noqa: F401 - third-party backend names of the reference
 
         return cls.get_engine_cls(model_type, backend)(*args, **kwargs)
