@@ -1,0 +1,71 @@
+"""LoRA adapters through the engine, and the supervised datasets."""
+
+import torch
+
+from tests.test_engine_on_cpu import loss_fn, make_batch
+from verl_b200.models.config import PRESETS
+from verl_b200.models.lora import apply_lora, lora_state_dict, merge_lora_, merged_hf_named_tensors
+from verl_b200.models.transformer import DecoderLM, PackedBatch
+from verl_b200.utils.config import Config
+from verl_b200.utils.dataset.samplers import DifficultyCurriculumSampler
+from verl_b200.utils.dataset.sft_dataset import MultiTurnSFTDataset, RMDataset
+from verl_b200.utils.tokenizer import ByteChatTokenizer
+from verl_b200.workers.engine.fsdp.engine import FSDPEngine
+
+
+def _logits(m, ids):
+    pb = PackedBatch(ids, torch.arange(len(ids), dtype=torch.int32), torch.tensor([0, len(ids)], dtype=torch.int32))
+    with torch.no_grad():
+        return m(pb, return_logits=True)["logits"]
+
+
+def test_lora_is_identity_at_init_trains_only_adapters_and_merges():
+    base = DecoderLM(PRESETS["tiny-qwen2"], dtype=torch.float32, seed=1)
+    ids = torch.arange(10, 30)
+    want = _logits(base, ids)
+    apply_lora(base, rank=4, alpha=8, target_modules=["q_proj", "down_proj"])
+    assert torch.allclose(_logits(base, ids), want, atol=1e-6)          # B starts at zero
+    assert set(base.lora_config["targets"]) == {"qkv_proj", "down_proj"} and len(lora_state_dict(base)) == 2 * 2 * 2
+    eng = FSDPEngine(Config({"preset": "tiny-qwen2", "lora_rank": 4, "lora_alpha": 8}), {"seed": 1}, {"lr": 1e-2, "weight_decay": 0.0}, {})
+    eng.initialize()
+    n_train = sum(p.numel() for p in eng.store.params)
+    assert n_train < 0.1 * sum(p.numel() for p in eng.model.parameters()) and all("lora_" in n for n in eng.store.names)
+    frozen_before = eng.model.layers[0].mlp.down_proj.clone()
+    for _ in range(2):
+        eng.train_batch(make_batch(), loss_fn)
+    assert torch.equal(eng.model.layers[0].mlp.down_proj, frozen_before)
+    assert eng.model.layers[0].mlp.lora_B_down_proj.abs().sum() > 0
+    got = _logits(eng.model, ids)
+    exported = dict(eng.get_per_tensor_param()[0])
+    fresh = DecoderLM(PRESETS["tiny-qwen2"], dtype=torch.float32, seed=1)
+    fresh.load_hf_state_dict(exported)
+    assert torch.allclose(_logits(fresh, ids), got, atol=1e-4)
+    merge_lora_(eng.model)
+    assert torch.allclose(_logits(eng.model, ids), got, atol=1e-4) and not lora_state_dict(eng.model)
+    assert len(dict(merged_hf_named_tensors(eng.model))) == len(exported)
+
+
+def test_multiturn_sft_dataset_masks_only_assistant_tokens():
+    tok = ByteChatTokenizer()
+    rows = [{"messages": [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"},
+                          {"role": "user", "content": "2+2?"}, {"role": "assistant", "content": "4"}], "tools": None}]
+    ds = MultiTurnSFTDataset(rows=rows, tokenizer=tok, max_length=160)
+    item = ds[0]
+    n = int(item["attention_mask"].sum())
+    ids, lm = item["input_ids"][:n], item["loss_mask"][:n]
+    targets = ids[1:][lm[:-1].bool()]
+    assert tok.decode(targets.tolist()) == "yo<|im_end|>\n4<|im_end|>\n"
+    assert item["position_ids"][n - 1] == n - 1 and lm[n - 1] == 0
+    rm = RMDataset(rows=[{"prompt": "q: ", "chosen": "good", "rejected": "bad"}], tokenizer=tok, max_length=16)[0]
+    assert rm["input_ids"].shape == (2, 16) and rm["attention_mask"][0].sum() == len("q: good") + 1
+
+
+def test_curriculum_sampler_prefers_medium_difficulty():
+    from verl_b200.protocol import DataProto
+
+    s = DifficultyCurriculumSampler(list(range(6)), explore=0.0)
+    batch = DataProto.from_dict(tensors={"token_level_scores": torch.tensor([[1.0], [0.0], [0.5], [1.0], [0.0], [0.45]])},
+                                non_tensors={"index": [0, 1, 2, 3, 4, 5]})
+    s.update(batch)
+    order = list(iter(s))
+    assert order[0] == 2 and order[1] == 5 and sorted(order) == list(range(6))

@@ -40,6 +40,17 @@ class PackedBatch:
         self.routed_experts = routed_experts  # optional [T, layers, topk] forced routing (router replay)
 
 
+def _proj(mod: nn.Module, name: str, x: torch.Tensor, bias=None) -> torch.Tensor:
+    """``x @ Wᵀ (+ bias)`` plus the low-rank update ``scale · (x Aᵀ) Bᵀ`` when the module carries a LoRA adapter for ``name``
+    (see ``verl_b200.models.lora``)."""
+    y = ops.linear(x, getattr(mod, name), bias)
+    adapters = getattr(mod, "_lora", None)
+    if adapters and name in adapters:
+        a, b, scale = adapters[name]
+        y = y + ops.linear(ops.linear(x, getattr(mod, a)), getattr(mod, b)) * scale
+    return y
+
+
 class Attention(nn.Module):
     def __init__(self, cfg: ModelConfig, dtype, device):
         super().__init__()
@@ -55,7 +66,7 @@ class Attention(nn.Module):
 
     def forward(self, x: torch.Tensor, pb: PackedBatch, cos, sin, sp_group=None) -> torch.Tensor:
         cfg = self.cfg
-        qkv = ops.linear(copy_to_tp(x, self.tp_group), self.qkv_proj, self.qkv_bias)
+        qkv = _proj(self, "qkv_proj", copy_to_tp(x, self.tp_group), self.qkv_bias)
         if cfg.qk_norm:
             T = qkv.shape[0]
             q, k, v = qkv.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=-1)
@@ -70,7 +81,7 @@ class Attention(nn.Module):
         else:
             o = ops.attention_varlen(qkv, pb.cu_seqlens, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                                      pb.max_seqlen, pb.cu_seqlens_cpu)
-        return reduce_from_tp(ops.linear(o, self.o_proj), self.tp_group)
+        return reduce_from_tp(_proj(self, "o_proj", o), self.tp_group)
 
 
 class MLP(nn.Module):
@@ -82,7 +93,7 @@ class MLP(nn.Module):
         self.tp_group = None
 
     def forward(self, x):
-        y = ops.linear(ops.swiglu(ops.linear(copy_to_tp(x, self.tp_group), self.gate_up_proj)), self.down_proj)
+        y = _proj(self, "down_proj", ops.swiglu(_proj(self, "gate_up_proj", copy_to_tp(x, self.tp_group))))
         return reduce_from_tp(y, self.tp_group)
 
 

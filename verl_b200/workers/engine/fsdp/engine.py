@@ -77,7 +77,7 @@ class FlatParamStore:
     def __init__(self, model: torch.nn.Module, world: int, rank: int):
         self.model = model
         self.world, self.rank = world, rank
-        params = [(n, p) for n, p in model.named_parameters()]
+        params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]   # frozen tensors (LoRA base) stay outside
         self.names = [n for n, _ in params]
         self.params = [p for _, p in params]
         self.offsets, off = [], 0
@@ -202,6 +202,12 @@ class FSDPEngine(BaseEngine):
 
             load_hf_weights(self.model, os.path.expanduser(path), strict=not cfg.value_head)
         self.model.gradient_checkpointing = bool(cfg_get(self.model_config, "enable_gradient_checkpointing", False))
+        lora_rank = int(cfg_get(self.model_config, "lora_rank", 0) or 0) if not isinstance(self.model_config, ModelConfig) else 0
+        if lora_rank > 0 and not self.forward_only:
+            from verl_b200.models.lora import apply_lora
+
+            apply_lora(self.model, lora_rank, float(cfg_get(self.model_config, "lora_alpha", 2 * lora_rank)),
+                       cfg_get(self.model_config, "target_modules", "all-linear"), seed=seed)
         self._build_groups()
         self.store = FlatParamStore(self.model, self.fsdp_size, self.fsdp_rank)
         if self.world > 1:
@@ -584,6 +590,10 @@ class FSDPEngine(BaseEngine):
         no collective (the reference all-gathers every DTensor here: fsdp/transformer_impl.py:1033-1039)."""
         if not self.store.flat.is_cuda and self.device.type == "cuda":
             self.to("cuda", model=True, optimizer=False, grad=False)
+        if getattr(self.model, "lora_config", None):
+            from verl_b200.models.lora import merged_hf_named_tensors
+
+            return merged_hf_named_tensors(self.model), None
         return self.model.hf_named_tensors(), None
 
     # ------------------------------------------------------------------ checkpoint
