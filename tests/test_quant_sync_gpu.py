@@ -52,3 +52,19 @@ def test_delta_compact_and_apply_kernels():
     snap2 = old.clone()
     count2, pos2, _ = delta_compact(new, snap2, cap=1000)
     assert count2 == changed and pos2.numel() == 1000
+
+
+def test_reshard_gather_and_requant_from_row_shards():
+    """Two 'trainer shards' (here both in this GPU's memory) are gathered into a rollout row range and block-quantised."""
+    from verl_b200.checkpoint_engine.reshard import gather_rows, gather_rows_fp8
+    from verl_b200.ops.quant import _blockwise_ref
+
+    full = (torch.randn(768, 520, device="cuda") * 1.5).bfloat16()
+    shards = [full[:384].contiguous(), full[384:].contiguous()]
+    ptrs = [s.data_ptr() for s in shards]
+    got = gather_rows(ptrs, 384, 520, 256, 300, full)
+    assert torch.equal(got, full[256:556])
+    q, sc, keep = gather_rows_fp8(ptrs, 384, 520, 256, 300, full, keep_bf16=True)
+    qr, sr = _blockwise_ref(full[256:556], 128, 128)
+    torch.testing.assert_close(sc, sr, rtol=1e-6, atol=0)
+    assert torch.equal(keep, full[256:556]) and (q.float() != qr.float()).float().mean() < 1e-3

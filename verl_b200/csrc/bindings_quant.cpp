@@ -39,6 +39,29 @@ std::tuple<Tensor, Tensor> fp8_act_cast(const Tensor& x) {
   return {y, s};
 }
 
+// ptrs: CPU int64 [world] peer pointers of the row shards. Returns (fp8 [M_out, N], scales) and, if keep_bf16, also the
+// gathered bf16 rows.
+std::tuple<Tensor, Tensor, Tensor> reshard_quant(const Tensor& ptrs, int64_t rows_per_rank, int64_t ld_src, int64_t row_begin, int64_t M_out,
+                                                 int64_t N, bool quantize, bool keep_bf16, const Tensor& like) {
+  TORCH_CHECK(!ptrs.is_cuda() && ptrs.scalar_type() == at::kLong, "reshard_quant: ptrs must be a CPU int64 tensor");
+  TORCH_CHECK(like.is_cuda(), "reshard_quant: `like` selects the device");
+  c10::cuda::CUDAGuard guard(like.device());
+  Tensor y, s, o;
+  if (quantize) {
+    y = at::empty({M_out, N}, like.options().dtype(at::kFloat8_e4m3fn));
+    s = at::empty({(M_out + 127) / 128, (N + 127) / 128}, like.options().dtype(at::kFloat));
+  } else {
+    y = at::empty({0}, like.options().dtype(at::kFloat8_e4m3fn));
+    s = at::empty({0}, like.options().dtype(at::kFloat));
+  }
+  o = keep_bf16 ? at::empty({M_out, N}, like.options().dtype(at::kBFloat16)) : at::empty({0}, like.options().dtype(at::kBFloat16));
+  check_rc(vb_reshard_quant(ptrs.data_ptr<int64_t>() ? reinterpret_cast<const long*>(ptrs.data_ptr<int64_t>()) : nullptr, (int)ptrs.numel(),
+                            (int)rows_per_rank, ld_src, (int)row_begin, quantize ? y.data_ptr() : nullptr, N, quantize ? s.data_ptr<float>() : nullptr,
+                            keep_bf16 ? o.data_ptr() : nullptr, N, (int)M_out, (int)N, cur_stream()),
+           "reshard_quant");
+  return {y, s, o};
+}
+
 Tensor fp4_fake_quant(const Tensor& x, const Tensor& global_amax) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.size(-1) % 16 == 0, "fp4_fake_quant: bad x");
   TORCH_CHECK(global_amax.is_cuda() && global_amax.scalar_type() == at::kFloat && global_amax.numel() == 1, "fp4_fake_quant: bad amax");
@@ -75,6 +98,7 @@ TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
   m.def("fp8_block_cast(Tensor x) -> (Tensor, Tensor)", &fp8_block_cast);
   m.def("fp8_act_cast(Tensor x) -> (Tensor, Tensor)", &fp8_act_cast);
   m.def("fp4_fake_quant(Tensor x, Tensor global_amax) -> Tensor", &fp4_fake_quant);
+  m.def("reshard_quant(Tensor ptrs, int rows_per_rank, int ld_src, int row_begin, int M_out, int N, bool quantize, bool keep_bf16, Tensor like) -> (Tensor, Tensor, Tensor)", &reshard_quant);
   m.def("delta_compact16(Tensor cur, Tensor(a!) snap, Tensor(b!) pos_out, Tensor(c!) val_out) -> int", &delta_compact16);
   m.def("delta_apply16(Tensor(a!) dst, Tensor pos, Tensor val, int count) -> ()", &delta_apply16);
 }

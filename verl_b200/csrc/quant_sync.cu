@@ -73,6 +73,68 @@ __global__ void __launch_bounds__(256) fp8_block_cast_kernel(const bf16* __restr
   }
 }
 
+// Reshard + requantise: the source matrix is split by rows over `world` ranks (rank r holds rows [r * rows_per_rank, ...)
+// of a tensor-parallel or flat shard) and is read straight from the peers' memory (plain P2P loads) while the
+// destination is this rank's fp8 copy in rollout layout: rows [row_begin, row_begin + M_out) of the full matrix, block
+// scales as in fp8_block_cast_kernel. With out_bf16 != null the gathered rows are also kept in bf16 (no quantisation
+// on that copy). One pass over NVLink, no staging buffer.
+struct PeerRows {
+  const bf16* ptr[16];
+};
+__global__ void __launch_bounds__(256) reshard_quant_kernel(PeerRows src, int rows_per_rank, long ld_src, int row_begin,
+                                                            __nv_fp8_e4m3* __restrict__ y, long ldy, float* __restrict__ scale,
+                                                            bf16* __restrict__ out_bf16, long ld_bf16, int M_out, int N) {
+  __shared__ float red[8];
+  const int r0 = blockIdx.y * 128, c0 = blockIdx.x * 128 + (threadIdx.x & 15) * 8;
+  const bool vec = (c0 + 8 <= N) && ((ld_src & 7) == 0);
+  uint4 regs[8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = r0 + (threadIdx.x >> 4) + 16 * i;
+    regs[i] = make_uint4(0, 0, 0, 0);
+    if (r < M_out) {
+      const int g = row_begin + r;                      // row of the full matrix
+      const bf16* base = src.ptr[g / rows_per_rank] + (long)(g % rows_per_rank) * ld_src;
+      if (vec) {
+        regs[i] = *reinterpret_cast<const uint4*>(base + c0);
+      } else {
+        bf16* e = reinterpret_cast<bf16*>(&regs[i]);
+        for (int j = 0; j < 8; ++j) e[j] = (c0 + j < N) ? base[c0 + j] : __float2bfloat16(0.f);
+      }
+      if (out_bf16 != nullptr) {
+        if (vec && (ld_bf16 & 7) == 0) {
+          *reinterpret_cast<uint4*>(out_bf16 + (long)r * ld_bf16 + c0) = regs[i];
+        } else {
+          const bf16* e = reinterpret_cast<const bf16*>(&regs[i]);
+          for (int j = 0; j < 8 && c0 + j < N; ++j) out_bf16[(long)r * ld_bf16 + c0 + j] = e[j];
+        }
+      }
+    }
+    const bf16* e = reinterpret_cast<const bf16*>(&regs[i]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(__bfloat162float(e[j])));
+  }
+  if (y == nullptr) return;
+  amax = fmaxf(block_max_256(amax, red), 1e-10f);
+  const float s = amax / 448.f, inv = 1.f / s;
+  if (threadIdx.x == 0) scale[(long)blockIdx.y * gridDim.x + blockIdx.x] = s;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = r0 + (threadIdx.x >> 4) + 16 * i;
+    if (r >= M_out) continue;
+    const bf16* e = reinterpret_cast<const bf16*>(&regs[i]);
+    __nv_fp8_e4m3 q[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q[j] = __nv_fp8_e4m3(fminf(fmaxf(__bfloat162float(e[j]) * inv, -448.f), 448.f));
+    if (c0 + 8 <= N && (ldy & 7) == 0) {
+      *reinterpret_cast<uint2*>(y + (long)r * ldy + c0) = *reinterpret_cast<const uint2*>(q);
+    } else {
+      for (int j = 0; j < 8 && c0 + j < N; ++j) y[(long)r * ldy + c0 + j] = q[j];
+    }
+  }
+}
+
 // One warp per (row, 128-column group): scale[row, g] = max(absmax, 1e-10) / 448. K % 8 == 0.
 __global__ void __launch_bounds__(256) fp8_act_cast_kernel(const bf16* __restrict__ x, long ldx, __nv_fp8_e4m3* __restrict__ y, long ldy,
                                                            float* __restrict__ scale, long M, int K) {
@@ -211,6 +273,21 @@ int vb_fp8_block_cast(const void* x, long ldx, void* y, long ldy, float* scale, 
   if (M <= 0 || N <= 0) return 0;
   dim3 grid((N + 127) / 128, (M + 127) / 128);
   fp8_block_cast_kernel<<<grid, 256, 0, st>>>((const bf16*)x, ldx, (__nv_fp8_e4m3*)y, ldy, scale, M, N);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// src_ptrs[r]: rank r's [rows_per_rank, N] bf16 shard (row stride ld_src) as seen from this GPU. Writes rows
+// [row_begin, row_begin + M_out) of the full matrix: fp8 + scales into (y, scale) when y != null, bf16 into out_bf16
+// when that is != null.
+int vb_reshard_quant(const long* src_ptrs, int world, int rows_per_rank, long ld_src, int row_begin, void* y, long ldy, float* scale,
+                     void* out_bf16, long ld_bf16, int M_out, int N, cudaStream_t st) {
+  if (M_out <= 0 || N <= 0) return 0;
+  if (world < 1 || world > 16 || rows_per_rank <= 0 || row_begin < 0 || (long)row_begin + M_out > (long)world * rows_per_rank) return -2;
+  PeerRows pr = {};
+  for (int r = 0; r < world; ++r) pr.ptr[r] = reinterpret_cast<const bf16*>(src_ptrs[r]);
+  dim3 grid((N + 127) / 128, (M_out + 127) / 128);
+  reshard_quant_kernel<<<grid, 256, 0, st>>>(pr, rows_per_rank, ld_src, row_begin, (__nv_fp8_e4m3*)y, ldy, scale, (bf16*)out_bf16, ld_bf16,
+                                             M_out, N);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
