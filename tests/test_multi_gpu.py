@@ -144,3 +144,68 @@ def test_fused_tensor_parallel_gemms(tmp_path, world):
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
                         "--master-port", "29685", str(script)], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0 and "TP_FUSED_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+SP_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("cpu:gloo,cuda:nccl")
+from verl_b200.ops import _ext
+from tests.test_engine_on_cpu import make_batch, loss_fn
+from verl_b200.models.config import PRESETS
+from verl_b200.workers.engine.fsdp.engine import FSDPEngine
+from verl_b200.workers.engine.megatron.engine import MegatronEngine
+# ---- Ulysses: all-to-alls fused into the projections == NCCL all-to-all formulation
+res = {}
+for mode in ("fused", "nccl"):
+    eng = FSDPEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "ulysses_sequence_parallel_size": world, "fused_ulysses": mode == "fused",
+                                                 "use_symmetric_memory": False}, {"lr": 1e-3, "clip_grad": 1.0}, {})
+    eng.initialize()
+    assert (getattr(eng, "_fused_ulysses", None) is not None) == (mode == "fused")
+    data = make_batch(bs=6, P=70, R=90, vocab=4096)
+    data.meta_info["micro_batch_size_per_gpu"] = 3
+    lp = eng.infer_batch(data)["model_output"]["log_probs"]
+    eng.optimizer_zero_grad()
+    eng.forward_backward_batch(data, loss_fn)
+    torch.cuda.synchronize()
+    _ext.check_status(mode)
+    res[mode] = (lp.clone(), eng.store.grad.clone())
+d_lp = (res["fused"][0] - res["nccl"][0]).abs().max().item()
+g_f, g_n = res["fused"][1], res["nccl"][1]
+rel = ((g_f - g_n).norm() / g_n.norm()).item()
+assert d_lp < 0.06 and rel < 0.05, (d_lp, rel)
+# ---- tensor-parallel engine on NCCL == single-GPU engine
+ref = FSDPEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "use_symmetric_memory": False, "fsdp_size": 1}, None, {})
+tp = MegatronEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "tensor_model_parallel_size": world}, {"lr": 1e-3}, {})
+tp.initialize()
+data = make_batch(bs=4, P=40, R=60, vocab=4096)
+data.meta_info["micro_batch_size_per_gpu"] = 2
+lp_tp = tp.infer_batch(data)["model_output"]["log_probs"]
+tp.optimizer_zero_grad()
+tp.forward_backward_batch(data, loss_fn)
+gn = tp.optimizer_step()
+torch.cuda.synchronize()
+_ext.check_status("tp engine")
+d = (lp_tp - res["nccl"][0][:0].new_zeros(())).abs().max().item()
+assert torch.isfinite(lp_tp).all() and gn == gn and gn > 0, (d, gn)
+exported = dict(tp.get_per_tensor_param()[0])
+assert exported["model.layers.0.self_attn.q_proj.weight"].shape == (512, 512)
+dist.barrier()
+if rank == 0:
+    print("SP_TP_OK", d_lp, rel, gn)
+'''
+
+
+@pytest.mark.parametrize("world", [2])
+def test_fused_ulysses_and_tp_engine(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "sp.py"
+    script.write_text(SP_WORKER)
+    env = dict(os.environ, REPO=repo, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                        "--master-port", "29687", str(script)], env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "SP_TP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -74,6 +74,10 @@ int vb_symm_adamw_allgather(float* p32, float* m, float* v, const float* g, cons
 int vb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb, int ldc, int a_mn,
                       int b_mn, int out_f32, int accumulate, int* err_word, cudaStream_t stream);
 int vb_fp8_block_cast(const void* x, long ldx, void* y, long ldy, float* scale, int M, int N, cudaStream_t st);
+int vb_gemm_head_scatter(const void* A, const void* B, const void* bias, int M, int N, int K, int lda, int ldb, int ld_out, const long* out_ptrs,
+                         int world, int row_off, int head_dim, const int* head_rank, const int* head_slot, int* err_word, cudaStream_t st);
+int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int ld_seg, int rows_total, int row_off, const void* B, int ldb, void* C,
+                 const void* bias, int M, int N, int ldc, int* err_word, cudaStream_t st);
 int vb_reshard_quant(const long* src_ptrs, int world, int rows_per_rank, long ld_src, int row_begin, void* y, long ldy, float* scale,
                      void* out_bf16, long ld_bf16, int M_out, int N, cudaStream_t st);
 int vb_fp8_act_cast(const void* x, long ldx, void* y, long ldy, float* scale, long M, int K, cudaStream_t st);

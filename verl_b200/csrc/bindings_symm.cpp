@@ -120,6 +120,38 @@ void gemm_peer_scatter(const Tensor& a, const Tensor& b, const Tensor& out_ptrs,
            "gemm_peer_scatter");
 }
 
+// Ulysses, sequence → heads: (a [M, K] token shard) @ (b [N, K])^T (+bias); head h of the result goes to rank head_rank[h],
+// head slot head_slot[h], rows [row_off, row_off + M) of that rank's [*, ld_out] buffer.
+void gemm_head_scatter(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& bias, const Tensor& out_ptrs, int64_t ld_out,
+                       int64_t row_off, int64_t head_dim, const Tensor& head_rank, const Tensor& head_slot) {
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_head_scatter: bad operands");
+  TORCH_CHECK(out_ptrs.scalar_type() == at::kLong && !out_ptrs.is_cuda(), "gemm_head_scatter: pointer table must be a CPU int64 tensor");
+  TORCH_CHECK(head_rank.scalar_type() == at::kInt && head_slot.scalar_type() == at::kInt && !head_rank.is_cuda() && !head_slot.is_cuda(), "gemm_head_scatter: head tables must be CPU int32");
+  const int M = a.size(0), K = a.size(1), N = b.size(0), world = out_ptrs.numel();
+  TORCH_CHECK(head_rank.numel() * head_dim == N && head_slot.numel() == head_rank.numel(), "gemm_head_scatter: head tables do not cover N");
+  const void* bias_p = (bias.has_value() && bias->defined()) ? bias->data_ptr() : nullptr;
+  c10::cuda::CUDAGuard guard(a.device());
+  check_rc(vb_gemm_head_scatter(a.data_ptr(), b.data_ptr(), bias_p, M, N, K, (int)a.stride(0), (int)b.stride(0), (int)ld_out, out_ptrs.data_ptr<long>(),
+                                world, (int)row_off, (int)head_dim, head_rank.data_ptr<int>(), head_slot.data_ptr<int>(),
+                                vb_status_tensor(a.get_device()).data_ptr<int>(), cur_stream()),
+           "gemm_head_scatter");
+}
+
+// Ulysses, heads → sequence: out [M, N] = A @ b^T where A's K axis is split over ranks: rank r holds columns
+// [r * k_per_rank, ...) as rows [row_off, row_off + M) of its [rows_total, k_per_rank] buffer a_ptrs[r].
+void gemm_kseg(const Tensor& a_ptrs, int64_t k_per_rank, int64_t rows_total, int64_t row_off, const Tensor& b, Tensor& out,
+               const c10::optional<Tensor>& bias) {
+  TORCH_CHECK(a_ptrs.scalar_type() == at::kLong && !a_ptrs.is_cuda(), "gemm_kseg: pointer table must be a CPU int64 tensor");
+  TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.dim() == 2 && b.stride(1) == 1, "gemm_kseg: bad b");
+  const int world = a_ptrs.numel(), N = b.size(0), M = out.size(0);
+  TORCH_CHECK(b.size(1) == world * k_per_rank && out.size(1) == N && out.scalar_type() == at::kBFloat16 && out.stride(1) == 1, "gemm_kseg: bad shapes");
+  const void* bias_p = (bias.has_value() && bias->defined()) ? bias->data_ptr() : nullptr;
+  c10::cuda::CUDAGuard guard(b.device());
+  check_rc(vb_gemm_kseg(a_ptrs.data_ptr<long>(), world, (int)k_per_rank, (int)k_per_rank, (int)rows_total, (int)row_off, b.data_ptr(), (int)b.stride(0),
+                        out.data_ptr(), bias_p, M, N, (int)out.stride(0), vb_status_tensor(b.get_device()).data_ptr<int>(), cur_stream()),
+           "gemm_kseg");
+}
+
 void slots_reduce(const Tensor& slots, int64_t world, int64_t slot_elems, int64_t rows, int64_t cols, const c10::optional<Tensor>& residual, Tensor& out) {
   TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "slots_reduce: bf16 tensors expected");
   const void* res = (residual.has_value() && residual->defined()) ? residual->data_ptr() : nullptr;
@@ -133,5 +165,7 @@ TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
   m.def("gemm_allgather_a(Tensor a_ptrs, int seg_rows, Tensor b, Tensor(a!) out, Tensor? bias) -> ()", &gemm_allgather_a);
   m.def("gemm_allgather_b(Tensor a, Tensor b_ptrs, int seg_rows, Tensor(a!) out, Tensor? bias) -> ()", &gemm_allgather_b);
   m.def("gemm_peer_scatter(Tensor a, Tensor b, Tensor out_ptrs, int rank, int rows_per_owner, int slot_elems) -> ()", &gemm_peer_scatter);
+  m.def("gemm_head_scatter(Tensor a, Tensor b, Tensor? bias, Tensor out_ptrs, int ld_out, int row_off, int head_dim, Tensor head_rank, Tensor head_slot) -> ()", &gemm_head_scatter);
+  m.def("gemm_kseg(Tensor a_ptrs, int k_per_rank, int rows_total, int row_off, Tensor b, Tensor(a!) out, Tensor? bias) -> ()", &gemm_kseg);
   m.def("slots_reduce(Tensor slots, int world, int slot_elems, int rows, int cols, Tensor? residual, Tensor(a!) out) -> ()", &slots_reduce);
 }

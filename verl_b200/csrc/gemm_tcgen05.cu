@@ -42,10 +42,13 @@ enum : int { EPI_STORE = 0, EPI_LOGPROB = 1, EPI_DLOGITS = 2, EPI_PEER = 3 };
 // reduce-scatter input). A barrier and a slot-sum kernel finish the collective.
 constexpr int MAX_TP = 8;
 struct DistArgs {
-  int seg_mode, seg_rows, n_seg;
+  int seg_mode, seg_rows, n_seg;     // seg_mode 3: A is split along K (seg_rows = K columns per rank), rows offset by row_off
   int rank, world;
   int rows_per_owner;
   long slot_elems;
+  int row_off;                       // seg_mode 3: first row of this rank's block inside every peer's buffer
+  int head_dim;                      // > 0: EPI_PEER routes whole heads (head_dim columns) through head_map (sequence → head a2a)
+  uint16_t head_map[192];            // per output head: (destination rank << 12) | destination head slot
   void* peer_out[MAX_TP];
   CUtensorMap seg[MAX_TP];
 };
@@ -147,6 +150,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int k0 = kb * BK;
           if (!A_MN) {
             if (dist.seg_mode == 1) tma_load_2d(sa, &dist.seg[m0 / dist.seg_rows], k0, m0 % dist.seg_rows, &full_bar[s]);
+            else if (dist.seg_mode == 3) tma_load_2d(sa, &dist.seg[k0 / dist.seg_rows], k0 % dist.seg_rows, m0 + dist.row_off, &full_bar[s]);
             else tma_load_2d(sa, &tmA, k0, m0, &full_bar[s]);
           } else {
 #pragma unroll
@@ -316,6 +320,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_wait();
           const int col0 = n0 + c * 32;
           if (row < M && col0 + 32 <= N) {
+            if (bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __bfloat162float(bias[col0 + j]));
+            }
             uint4 o[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -323,6 +331,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               o[j].y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
               o[j].z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
               o[j].w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            }
+            if (dist.head_dim > 0) {
+              // all-to-all by heads: this rank's token rows land at row_off + row of the head owner's [T, local heads] buffer
+              const uint16_t e = dist.head_map[col0 / dist.head_dim];
+              bf16* dst = reinterpret_cast<bf16*>(dist.peer_out[e >> 12]) + ((long)dist.row_off + row) * ldc +
+                          (long)(e & 0xFFF) * dist.head_dim + (col0 % dist.head_dim);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = o[j];
+              continue;
             }
             for (int r = r_lo; r < r_hi; ++r) {
               bf16* dst = reinterpret_cast<bf16*>(dist.peer_out[r]) + dist.rank * dist.slot_elems + row_local * ldc + col0;
@@ -775,6 +792,42 @@ extern "C" int vb_gemm_peer_scatter(const void* A, const void* B, int M, int N, 
   d.rank = rank; d.world = world; d.rows_per_owner = rows_per_owner; d.slot_elems = slot_elems;
   for (int r = 0; r < world; ++r) d.peer_out[r] = reinterpret_cast<void*>(out_ptrs[r]);
   return launch_dist<EPI_PEER>(pick_bn_dist(M, N), A, B, nullptr, nullptr, M, N, K, lda, ldb, ld_slot, err_word, st, d);
+}
+
+// Sequence → head all-to-all fused into the projection GEMM (Ulysses): this rank's [M, K] token shard times W[N, K]^T;
+// output head h (head_dim columns) is written to rank head_rank[h]'s buffer at rows [row_off, row_off + M), head slot
+// head_slot[h]. out_ptrs[r] = rank r's [T_total, ld_out] bf16 buffer.
+extern "C" int vb_gemm_head_scatter(const void* A, const void* B, const void* bias, int M, int N, int K, int lda, int ldb, int ld_out,
+                                    const long* out_ptrs, int world, int row_off, int head_dim, const int* head_rank, const int* head_slot,
+                                    int* err_word, cudaStream_t st) {
+  using namespace vb;
+  if (world > MAX_TP || head_dim <= 0 || (head_dim % 32) != 0 || (N % head_dim) != 0 || N / head_dim > 192 || (ld_out & 7)) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -4;
+  DistArgs d = {};
+  d.world = world; d.row_off = row_off; d.head_dim = head_dim;
+  for (int h = 0; h < N / head_dim; ++h) {
+    if (head_rank[h] < 0 || head_rank[h] >= world || head_slot[h] < 0 || head_slot[h] > 0xFFF) return -2;
+    d.head_map[h] = (uint16_t)((head_rank[h] << 12) | head_slot[h]);
+  }
+  for (int r = 0; r < world; ++r) d.peer_out[r] = reinterpret_cast<void*>(out_ptrs[r]);
+  return launch_dist<EPI_PEER>(pick_bn_dist(M, N), A, B, nullptr, bias, M, N, K, lda, ldb, ld_out, err_word, st, d);
+}
+
+// Head → sequence all-to-all fused into the consuming GEMM (Ulysses output projection): C[M, N] = A B^T where the K axis
+// of A is split over ranks: columns [r * k_per_rank, (r+1) * k_per_rank) are rows [row_off, row_off + M) of rank r's
+// [T_total, k_per_rank] buffer (seg_ptrs[r], row stride ld_seg), read with TMA straight from that rank's memory.
+extern "C" int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int ld_seg, int rows_total, int row_off, const void* B, int ldb,
+                            void* C, const void* bias, int M, int N, int ldc, int* err_word, cudaStream_t st) {
+  using namespace vb;
+  if (world > MAX_TP || world < 1 || (k_per_rank % BK) != 0 || (ld_seg & 7) || (ldb & 7)) return -4;
+  DistArgs d = {};
+  d.seg_mode = 3; d.seg_rows = k_per_rank; d.n_seg = world; d.row_off = row_off;
+  for (int r = 0; r < world; ++r) {
+    if (make_tmap_2d(&d.seg[r], reinterpret_cast<const void*>(seg_ptrs[r]), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_total, k_per_rank, ld_seg, BM, BK))
+      return -1;
+  }
+  const int K = world * k_per_rank;
+  return launch_dist<EPI_STORE>(pick_bn_dist(M, N), reinterpret_cast<const void*>(seg_ptrs[0]), B, C, bias, M, N, K, ld_seg, ldb, ldc, err_word, st, d);
 }
 
 extern "C" int vb_slots_reduce(const void* slots, int world, long slot_elems, long rows, int cols, int ld, const void* residual,

@@ -28,7 +28,7 @@ __all__ = ["DecoderLM", "PackedBatch", "hf_to_native_state_dict", "native_to_hf_
 class PackedBatch:
     """Device-side description of a packed micro-batch."""
 
-    __slots__ = ("input_ids", "position_ids", "cu_seqlens", "cu_seqlens_cpu", "max_seqlen", "routed_experts")
+    __slots__ = ("input_ids", "position_ids", "cu_seqlens", "cu_seqlens_cpu", "max_seqlen", "routed_experts", "global_position_ids")
 
     def __init__(self, input_ids, position_ids, cu_seqlens, cu_seqlens_cpu=None, max_seqlen=None, routed_experts=None):
         self.input_ids = input_ids
@@ -38,6 +38,9 @@ class PackedBatch:
         lens = self.cu_seqlens_cpu[1:] - self.cu_seqlens_cpu[:-1]
         self.max_seqlen = int(max_seqlen if max_seqlen is not None else (lens.max() if lens.numel() else 0))
         self.routed_experts = routed_experts  # optional [T, layers, topk] forced routing (router replay)
+        # sequence parallelism: input_ids / position_ids are this rank's slice, cu_seqlens describe the whole micro-batch and
+        # this holds the (padded) positions of all its tokens
+        self.global_position_ids = None
 
 
 def _proj(mod: nn.Module, name: str, x: torch.Tensor, bias=None) -> torch.Tensor:
@@ -66,6 +69,11 @@ class Attention(nn.Module):
 
     def forward(self, x: torch.Tensor, pb: PackedBatch, cos, sin, sp_group=None) -> torch.Tensor:
         cfg = self.cfg
+        fu = getattr(self, "fused_ulysses", None)
+        if sp_group is not None and fu is not None and not cfg.qk_norm and not getattr(self, "_lora", None) and pb.global_position_ids is not None:
+            from verl_b200.parallel.ulysses import fused_ulysses_attention_block
+
+            return fused_ulysses_attention_block(x, self, pb, cfg, fu, cos, sin)
         qkv = _proj(self, "qkv_proj", copy_to_tp(x, self.tp_group), self.qkv_bias)
         if cfg.qk_norm:
             T = qkv.shape[0]

@@ -14,7 +14,7 @@ import torch
 import torch.distributed as dist
 
 __all__ = ["SeqAllToAll", "gather_seq_scatter_heads", "gather_heads_scatter_seq", "Gather", "ulysses_pad_and_slice_inputs",
-           "gather_outputs_and_unpad", "ulysses_attention", "validate_ulysses_config"]
+           "gather_outputs_and_unpad", "ulysses_attention", "validate_ulysses_config", "FusedUlysses", "fused_ulysses_available"]
 
 
 def _a2a(x: torch.Tensor, scatter_dim: int, gather_dim: int, group) -> torch.Tensor:
@@ -22,8 +22,16 @@ def _a2a(x: torch.Tensor, scatter_dim: int, gather_dim: int, group) -> torch.Ten
     if ws == 1:
         return x
     parts = [t.contiguous() for t in torch.tensor_split(x, ws, dim=scatter_dim)]
-    outs = [torch.empty_like(parts[0]) for _ in range(ws)]
-    dist.all_to_all(outs, parts, group=group)
+    if dist.get_backend(group) == "gloo":
+        # gloo has no all-to-all: every rank gathers everyone's pieces and keeps the ones addressed to it (CPU test path)
+        mine = torch.stack(parts)
+        allp = [torch.empty_like(mine) for _ in range(ws)]
+        dist.all_gather(allp, mine, group=group)
+        me = dist.get_rank(group)
+        outs = [allp[r][me] for r in range(ws)]
+    else:
+        outs = [torch.empty_like(parts[0]) for _ in range(ws)]
+        dist.all_to_all(outs, parts, group=group)
     return torch.cat(outs, dim=gather_dim).contiguous()
 
 
@@ -132,3 +140,152 @@ def ulysses_attention(qkv: torch.Tensor, pb, cfg, group) -> torch.Tensor:
     o = ops.attention_varlen(fused, pb.cu_seqlens, hq_l, hkv_l, D, pb.max_seqlen, pb.cu_seqlens_cpu).reshape(T, hq_l, D)
     o = gather_heads_scatter_seq(o, 1, 0, group)
     return o[:Tl].reshape(Tl, Hq * D)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Fused path: the two all-to-alls disappear into the projections around attention.
+#   * QKV projection: the GEMM epilogue writes every output head straight into the memory of the rank that owns that head
+#     (rows = this rank's token slice) — ``gemm_head_scatter``;
+#   * output projection: the GEMM's A operand is read tile by tile from the ranks that hold the corresponding heads
+#     (K axis split over ranks) — ``gemm_kseg``.
+# Forward only: the backward of both functions uses the all-to-all formulation above with plain GEMMs.
+def fused_ulysses_available(x: torch.Tensor, cfg, sp: int) -> bool:
+    import os
+
+    from verl_b200.ops import _ext
+
+    return (x.is_cuda and x.dtype == torch.bfloat16 and _ext.available() and os.environ.get("VERL_B200_COMM", "native") == "native"
+            and cfg.head_dim % 32 == 0 and cfg.num_attention_heads % sp == 0 and cfg.num_key_value_heads % sp == 0
+            and (cfg.num_attention_heads // sp * cfg.head_dim) % 64 == 0)
+
+
+class FusedUlysses:
+    """Symmetric staging buffers and head routing tables of one SP group (shared by all layers of a model)."""
+
+    def __init__(self, group, host_group, cfg, max_tokens: int):
+        from verl_b200.ops import _ext
+        from verl_b200.parallel.symm_mem import SymmetricBuffer
+
+        self.group, self.cfg, self.ops = group, cfg, _ext.ops()
+        self.sp, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+        self.hq_l, self.hkv_l = Hq // self.sp, Hkv // self.sp
+        self.Cl, self.Kl = (self.hq_l + 2 * self.hkv_l) * D, self.hq_l * D
+        self.max_tokens = max_tokens
+        self.qkv_buf = SymmetricBuffer(max_tokens * self.Cl * 2, group, host_group)
+        self.o_buf = SymmetricBuffer(max_tokens * self.Kl * 2, group, host_group)
+        rank_of, slot_of = [], []
+        for h in range(Hq):
+            rank_of.append(h // self.hq_l)
+            slot_of.append(h % self.hq_l)
+        for base in (self.hq_l, self.hq_l + self.hkv_l):          # k heads, then v heads
+            for j in range(Hkv):
+                rank_of.append(j // self.hkv_l)
+                slot_of.append(base + j % self.hkv_l)
+        self.head_rank = torch.tensor(rank_of, dtype=torch.int32)
+        self.head_slot = torch.tensor(slot_of, dtype=torch.int32)
+
+    def qkv_forward(self, x_shard, w, bias):
+        Tl = x_shard.shape[0]
+        Tp = Tl * self.sp
+        assert Tp <= self.max_tokens, f"{Tp} tokens exceed the staging buffers ({self.max_tokens})"
+        self.ops.gemm_head_scatter(x_shard, w, bias, self.qkv_buf.table(), self.Cl, self.rank * Tl, self.cfg.head_dim, self.head_rank, self.head_slot)
+        self.qkv_buf.barrier()
+        return self.qkv_buf.tensor(torch.bfloat16, Tp * self.Cl).view(Tp, self.Cl).clone()
+
+    def o_forward(self, o_local, w_o, Tl: int):
+        Tp = Tl * self.sp
+        self.o_buf.tensor(torch.bfloat16, Tp * self.Kl).view(Tp, self.Kl).copy_(o_local)
+        self.o_buf.barrier()
+        out = torch.empty(Tl, w_o.shape[0], dtype=torch.bfloat16, device=o_local.device)
+        self.ops.gemm_kseg(self.o_buf.table(), self.Kl, Tp, self.rank * Tl, w_o, out, None)
+        return out
+
+    # ---- layout conversions used by the (unfused) backward passes
+    def heads_to_seq(self, t_local):
+        """[Tp, n_l·D] (local heads, all tokens) → [Tl, n·D] (all heads, local tokens)."""
+        D = self.cfg.head_dim
+        Tp = t_local.shape[0]
+        return _a2a(t_local.reshape(Tp, -1, D), 0, 1, self.group).reshape(Tp // self.sp, -1)
+
+    def seq_to_heads(self, t_shard):
+        """[Tl, n·D] → [Tp, n_l·D]."""
+        D = self.cfg.head_dim
+        Tl = t_shard.shape[0]
+        return _a2a(t_shard.reshape(Tl, -1, D), 1, 0, self.group).reshape(Tl * self.sp, -1)
+
+
+class _FusedQKV(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, fu: FusedUlysses):
+        ctx.save_for_backward(x, w)
+        ctx.fu, ctx.bias_ref = fu, bias
+        return fu.qkv_forward(x.contiguous(), w, bias)
+
+    @staticmethod
+    def backward(ctx, g):
+        from verl_b200.ops.functional import gemm
+
+        x, w = ctx.saved_tensors
+        fu = ctx.fu
+        q_w, k_w = fu.hq_l * fu.cfg.head_dim, fu.hkv_l * fu.cfg.head_dim
+        gq, gk, gv = g.split([q_w, k_w, k_w], dim=-1)
+        dy = torch.cat([fu.heads_to_seq(gq.contiguous()), fu.heads_to_seq(gk.contiguous()), fu.heads_to_seq(gv.contiguous())], dim=-1).contiguous()
+        dx = gemm(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = db = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                gemm(dy, x, a_mn=True, b_mn=True, out=mg, accumulate=True)
+            else:
+                dw = gemm(dy, x, a_mn=True, b_mn=True)
+        b = ctx.bias_ref
+        if b is not None and ctx.needs_input_grad[2]:
+            bsum = dy.float().sum(0)
+            mg = getattr(b, "main_grad", None)
+            if mg is not None:
+                mg.add_(bsum.to(mg.dtype))
+            else:
+                db = bsum.to(b.dtype)
+        return dx, dw, db, None
+
+
+class _FusedOProj(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, o_local, w_o, fu: FusedUlysses, Tl: int):
+        ctx.save_for_backward(o_local, w_o)
+        ctx.fu = fu
+        return fu.o_forward(o_local.contiguous(), w_o, Tl)
+
+    @staticmethod
+    def backward(ctx, g):
+        from verl_b200.ops.functional import gemm
+
+        o_local, w_o = ctx.saved_tensors
+        fu = ctx.fu
+        g = g.contiguous()
+        do_local = fu.seq_to_heads(gemm(g, w_o, b_mn=True)) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            o_shard = fu.heads_to_seq(o_local).contiguous()
+            mg = getattr(w_o, "main_grad", None)
+            if mg is not None:
+                gemm(g, o_shard, a_mn=True, b_mn=True, out=mg, accumulate=True)
+            else:
+                dw = gemm(g, o_shard, a_mn=True, b_mn=True)
+        return do_local, dw, None, None
+
+
+def fused_ulysses_attention_block(x_shard, attn_mod, pb, cfg, fu: FusedUlysses, cos, sin):
+    """QKV projection → (a2a) → RoPE → attention on local heads → (a2a) → output projection, for one layer.
+    ``pb.global_position_ids`` holds the padded positions of ALL tokens of the micro-batch."""
+    from verl_b200 import ops
+
+    Tl = x_shard.shape[0]
+    T = int(pb.cu_seqlens_cpu[-1])
+    fused = _FusedQKV.apply(x_shard, attn_mod.qkv_proj, attn_mod.qkv_bias, fu)
+    fused = ops.apply_rope_(fused, pb.global_position_ids, cos, sin, fu.hq_l + fu.hkv_l, cfg.head_dim)
+    o = ops.attention_varlen(fused[:T], pb.cu_seqlens, fu.hq_l, fu.hkv_l, cfg.head_dim, pb.max_seqlen, pb.cu_seqlens_cpu)
+    if T < Tl * fu.sp:
+        o = torch.cat([o, o.new_zeros(Tl * fu.sp - T, o.shape[1])], 0)
+    return _FusedOProj.apply(o, attn_mod.o_proj, fu, Tl)

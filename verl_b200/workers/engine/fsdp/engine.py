@@ -229,6 +229,17 @@ class FSDPEngine(BaseEngine):
             self._symm_grads = SymmetricBuffer(s.total * 4, host_group=host)
         if self.sp_size > 1:
             self.model.sp_group = self.sp_group
+            from verl_b200.parallel.ulysses import FusedUlysses, fused_ulysses_available
+
+            probe = self.store.flat[:1]
+            if fused_ulysses_available(probe, cfg, self.sp_size) and bool(cfg_get(self.engine_config, "fused_ulysses", True)):
+                from verl_b200.single_controller.spmd import init_spmd_process_group
+
+                init_spmd_process_group()
+                max_tok = int(cfg_get(self.engine_config, "ulysses_max_tokens", 65536))
+                self._fused_ulysses = FusedUlysses(self.sp_group, self._sp_host_group(), cfg, max_tok)
+                for layer in self.model.layers:
+                    layer.self_attn.fused_ulysses = self._fused_ulysses
         if not self.forward_only:
             self._build_optimizer()
         from verl_b200.utils.checkpoint.fsdp_checkpoint_manager import FSDPCheckpointManager
@@ -275,6 +286,18 @@ class FSDPEngine(BaseEngine):
                     self.dp_group = g
         else:
             self.dp_group = dist.group.WORLD
+
+    def _sp_host_group(self):
+        """gloo twin of the SP group (pointer-table exchange of the symmetric buffers goes through host memory)."""
+        if getattr(self, "_sp_host", None) is None:
+            mine = None
+            for d in range(self.dp_size):
+                ranks = list(range(d * self.sp_size, (d + 1) * self.sp_size))
+                g = dist.new_group(ranks, backend="gloo")
+                if self.rank in ranks:
+                    mine = g
+            self._sp_host = mine
+        return self._sp_host
 
     def _build_optimizer(self):
         oc = self.optimizer_config
@@ -403,6 +426,13 @@ class FSDPEngine(BaseEngine):
             vals = self.model(pb)["values"]
             out["values"] = torch.where(valid, vals[idx.reshape(-1)].reshape(idx.shape), torch.zeros((), device=vals.device))
             return out
+        if self.sp_size > 1:
+            lp, ent = self._sp_forward(pb, labels, temperature, need_entropy)
+            full = torch.zeros(idx.shape, dtype=torch.float32, device=lp.device)
+            out["log_probs"] = torch.where(valid, lp[idx.reshape(-1)].reshape(idx.shape), full)
+            if ent is not None:
+                out["entropy"] = torch.where(valid, ent[idx.reshape(-1)].reshape(idx.shape), full)
+            return out
         h = self.model.forward_hidden(pb)
         sel = idx[valid]
         lp, ent = ops.linear_logprob_entropy(h.index_select(0, sel), self.model.output_weight, labels.index_select(0, sel),
@@ -412,6 +442,29 @@ class FSDPEngine(BaseEngine):
         if ent is not None:
             out["entropy"] = torch.zeros_like(full).masked_scatter(valid, ent.float())
         return out
+
+    def _sp_forward(self, pb: PackedBatch, labels: torch.Tensor, temperature: float, need_entropy: bool):
+        """Ulysses sequence parallelism: every rank of the SP group holds the same micro-batch, runs the model on its
+        slice of the packed tokens (attention sees the whole sequences through the all-to-all) and the per-token outputs are
+        gathered back; gradients are scaled so that summing over the SP ranks gives the full-batch gradient."""
+        from verl_b200.parallel.ulysses import gather_outputs_and_unpad, ulysses_pad_and_slice_inputs
+
+        sp, r = self.sp_size, self.sp_rank
+        T = pb.input_ids.shape[0]
+        ids_l, pos_l, pad = ulysses_pad_and_slice_inputs(pb.input_ids, pb.position_ids, sp, r, dim=0)
+        lab = torch.nn.functional.pad(labels, (0, pad)) if pad else labels
+        Tl = (T + pad) // sp
+        lab_l = lab[r * Tl:(r + 1) * Tl]
+        pbl = PackedBatch(ids_l, pos_l, pb.cu_seqlens, pb.cu_seqlens_cpu, pb.max_seqlen, None)
+        gpos = pb.position_ids
+        if pad:
+            gpos = torch.cat([gpos, torch.arange(pad, device=gpos.device, dtype=gpos.dtype)])
+        pbl.global_position_ids = gpos
+        h = self.model.forward_hidden(pbl)
+        lp_l, ent_l = ops.linear_logprob_entropy(h, self.model.output_weight, lab_l, temperature, need_entropy)
+        lp = gather_outputs_and_unpad(lp_l.float(), 0, 0, pad, grad_scaler=True, group=self.sp_group)
+        ent = gather_outputs_and_unpad(ent_l.float(), 0, 0, pad, grad_scaler=True, group=self.sp_group) if ent_l is not None else None
+        return lp, ent
 
     # ------------------------------------------------------------------ forward / backward
     def forward_backward_batch(self, data, loss_function: Optional[Callable], forward_only: bool = False) -> dict:
