@@ -65,6 +65,7 @@ int vb_ipc_get_handle(long ptr, unsigned char* out64);
 long vb_ipc_open_handle(const unsigned char* in64);
 int vb_ipc_close(long ptr);
 int vb_symm_barrier(const long* pad_ptrs, int rank, int world, int epoch, int* err_word, cudaStream_t st);
+int vb_symm_barrier_auto(const long* pad_ptrs, int rank, int world, int* err_word, cudaStream_t st);
 int vb_symm_reduce_scatter(const long* grad_ptrs, int world, long shard_off, long n, float scale, float* out, float* sumsq,
                            cudaStream_t st);
 int vb_symm_adamw_allgather(float* p32, float* m, float* v, const float* g, const long* param_ptrs, int world, long shard_off,

@@ -49,6 +49,14 @@ void symm_barrier(const Tensor& pad_ptrs, int64_t rank, int64_t world, int64_t e
            "symm_barrier");
 }
 
+// Barrier whose epoch lives in device memory: no host state per launch, so it can sit inside a captured CUDA graph.
+void symm_barrier_auto(const Tensor& pad_ptrs, int64_t rank, int64_t world) {
+  TORCH_CHECK(pad_ptrs.scalar_type() == at::kLong && !pad_ptrs.is_cuda() && pad_ptrs.numel() >= world, "symm_barrier_auto: bad pointer table");
+  int dev = at::cuda::current_device();
+  check_rc(vb_symm_barrier_auto(pad_ptrs.data_ptr<long>(), (int)rank, (int)world, vb_status_tensor(dev).data_ptr<int>(), cur_stream()),
+           "symm_barrier_auto");
+}
+
 void symm_reduce_scatter(const Tensor& grad_ptrs, int64_t world, int64_t shard_off, Tensor& out, Tensor& sumsq, double scale) {
   TORCH_CHECK(grad_ptrs.scalar_type() == at::kLong && !grad_ptrs.is_cuda(), "symm_reduce_scatter: bad pointer table");
   TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.is_contiguous() && sumsq.scalar_type() == at::kFloat, "symm_reduce_scatter: bad out");
@@ -79,6 +87,7 @@ TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
   m.def("ipc_close(int ptr) -> ()", &ipc_close);
   m.def("tensor_from_ptr(int ptr, int[] sizes, ScalarType dtype) -> Tensor", &tensor_from_ptr);
   m.def("symm_barrier(Tensor pad_ptrs, int rank, int world, int epoch) -> ()", &symm_barrier);
+  m.def("symm_barrier_auto(Tensor pad_ptrs, int rank, int world) -> ()", &symm_barrier_auto);
   m.def("symm_reduce_scatter(Tensor grad_ptrs, int world, int shard_off, Tensor(a!) out, Tensor(b!) sumsq, float scale) -> ()", &symm_reduce_scatter);
   m.def("symm_adamw_allgather(Tensor(a!) p32, Tensor(b!) m, Tensor(c!) v, Tensor g, Tensor param_ptrs, int world, int shard_off, float lr, float b1, float b2, float eps, float wd, int step, Tensor scalars) -> ()", &symm_adamw_allgather);
 }

@@ -50,6 +50,44 @@ __global__ void symm_barrier_kernel(PeerTable pads, int rank, int world, int epo
   }
 }
 
+// Same barrier with the epoch kept in device memory (pad word `AUTO_COUNTER`, flags at `AUTO_FLAGS`), so the launch
+// carries no host-side state and can be replayed from a CUDA graph: every replay advances the epoch by one on every rank.
+constexpr int AUTO_COUNTER = 256;   // int32 index inside the pad
+constexpr int AUTO_FLAGS = 512;
+__global__ void symm_barrier_auto_kernel(PeerTable pads, int rank, int world, int* err_word) {
+  __shared__ int epoch_s;
+  int* my_pad = reinterpret_cast<int*>(pads.ptr[rank]);
+  if (threadIdx.x == 0) {
+    epoch_s = my_pad[AUTO_COUNTER] + 1;
+    my_pad[AUTO_COUNTER] = epoch_s;
+  }
+  __syncthreads();
+  const int epoch = epoch_s;
+  const int p = threadIdx.x;
+  if (p < world) {
+    int* remote = reinterpret_cast<int*>(pads.ptr[p]) + AUTO_FLAGS + rank;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    const int* mine = my_pad + AUTO_FLAGS + p;
+    uint64_t t0 = 0;
+    uint32_t n = 0;
+    while (true) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if (v >= epoch) break;
+      if ((++n & 0xFF) == 0) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > VB_WAIT_LIMIT_NS) {
+          atomicCAS(err_word, 0, VB_ERR_WAIT_PEER | (p << 8));
+          break;
+        }
+        __nanosleep(200);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- reduce-scatter (+ scale, + sum of squares)
 // out[i] = scale * sum_r grads_r[shard_off + i] for i in [0, n); sumsq += sum out[i]^2. n % 4 == 0.
 __global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(PeerTable grads, int world, long shard_off, long n, float scale,
@@ -165,6 +203,12 @@ int vb_ipc_close(long ptr) { return cudaIpcCloseMemHandle(reinterpret_cast<void*
 int vb_symm_barrier(const long* pad_ptrs, int rank, int world, int epoch, int* err_word, cudaStream_t st) {
   if (world > MAX_RANKS) return -2;
   symm_barrier_kernel<<<1, 32, 0, st>>>(make_table(pad_ptrs, world), rank, world, epoch, err_word);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int vb_symm_barrier_auto(const long* pad_ptrs, int rank, int world, int* err_word, cudaStream_t st) {
+  if (world > MAX_RANKS) return -2;
+  symm_barrier_auto_kernel<<<1, 32, 0, st>>>(make_table(pad_ptrs, world), rank, world, err_word);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

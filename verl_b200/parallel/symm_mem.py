@@ -68,6 +68,10 @@ class SymmetricBuffer:
         self.epoch += 1
         self.ops.symm_barrier(self.pad_table, self.rank, self.world, self.epoch)
 
+    def barrier_auto(self):
+        """Same, with the epoch counted on the device: safe to capture into a CUDA graph and replay."""
+        self.ops.symm_barrier_auto(self.pad_table, self.rank, self.world)
+
     def close(self):
         for p in self._opened:
             self.ops.ipc_close(p)

@@ -33,8 +33,9 @@ def fused_comm_enabled() -> bool:
 class TPContext:
     """Symmetric staging buffers + fused ops for one tensor-parallel group."""
 
-    def __init__(self, group, host_group, max_tokens: int, hidden: int, max_out: int):
+    def __init__(self, group, host_group, max_tokens: int, hidden: int, max_out: int, graph_safe: bool = False):
         self.group, self.host_group = group, host_group
+        self.graph_safe = graph_safe      # device-side barrier epochs: the ops may be captured into CUDA graphs
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.ops = _ext.ops()
         self.max_tokens, self.hidden, self.max_out = max_tokens, hidden, max_out
@@ -68,10 +69,11 @@ class TPContext:
         T, N = x.shape[0], w.shape[0]
         if fused_comm_enabled() and N % 32 == 0 and T * N <= self.slot_elems:
             out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+            bar = self.slots.barrier_auto if self.graph_safe else self.slots.barrier
             self.ops.gemm_peer_scatter(x, w, self.slots.table(), self.rank, 0, self.slot_elems)
-            self.slots.barrier()
+            bar()
             self.ops.slots_reduce(self.slots.tensor(torch.bfloat16), self.world, self.slot_elems, T, N, residual, out)
-            self.slots.barrier()    # slots may be overwritten by the next call only after everyone has summed them
+            bar()                   # slots may be overwritten by the next call only after everyone has summed them
             return out
         y = torch.nn.functional.linear(x, w)
         dist.all_reduce(y, group=self.group)
