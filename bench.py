@@ -77,6 +77,9 @@ def build_config(args, world: int):
     ]
     if args.ref_offload:
         ov.append("actor_rollout_ref.ref.fsdp_config.param_offload=true")
+    if args.rollout_tp > 1:
+        ov.append(f"actor_rollout_ref.rollout.tensor_model_parallel_size={args.rollout_tp}")
+        ov.append(f"actor_rollout_ref.rollout.max_num_seqs={prompts_per_gpu * args.n * args.rollout_tp}")
     return load_config("ppo_trainer", ov)
 
 
@@ -161,7 +164,7 @@ def run_native(args):
             "impl": "native",
             "config": {"model": args.model, "global_batch": f"{args.prompts_per_gpu * world} prompts x n={args.n}",
                        "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + response <= {args.response_length}",
-                       "parallelism": f"dp{world} (ZeRO-2 sharded optimizer, resident bf16 params), rollout tp1 x {world} replicas colocated",
+                       "parallelism": f"dp{world} (ZeRO-2 sharded optimizer, resident bf16 params), rollout tp{args.rollout_tp} x {world // args.rollout_tp} replicas colocated",
                        "ppo_mini_batch_prompts": args.mini_prompts_per_gpu * world, "token_budget_per_micro_batch": args.token_budget,
                        "gradient_checkpointing": bool(args.grad_ckpt), "ref_param_offload": bool(args.ref_offload), "loss": "grpo clip 0.2 + low_var_kl 1e-3, AdamW lr 1e-6",
                        "l2_policy": "inputs larger than L2: each step streams >15 GB of weights and fresh activations"},
@@ -220,6 +223,7 @@ def main():
     ap.add_argument("--grad-ckpt", type=int, default=-1,
                     help="activation recomputation (default off: activations of an 8192-token micro-batch are stored)")
     ap.add_argument("--ref-offload", type=int, default=-1, help="keep the frozen reference weights in pinned host memory between its passes")
+    ap.add_argument("--rollout-tp", type=int, default=1, help="GPUs per rollout replica (1 = one replica per GPU, the fastest layout for a 7B model)")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
     single = int(os.environ.get("WORLD_SIZE", "1")) == 1

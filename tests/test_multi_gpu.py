@@ -124,6 +124,11 @@ ws.tensor(torch.bfloat16).view(N // world, H).copy_(w[rank * (N // world):(rank 
 ws.barrier()
 y4 = TPContext.weight_gather_linear(x_full, ws, N // world, H)
 assert rel(y4, ref) < 1e-2
+w_stage = torch.empty(N * H, device=dev, dtype=torch.bfloat16)
+w_flags = torch.zeros(N // 128 + 8, device=dev, dtype=torch.int32)
+for ep in (1, 2):       # staged variant: remote rows are copied into local memory once inside the kernel
+    y5 = TPContext.weight_gather_linear(x_full, ws, N // world, H, 0, w_stage, w_flags, ep)
+    assert rel(y5, ref) < 1e-2
 ws.barrier()
 torch.cuda.synchronize()
 _ext.check_status("tp")
@@ -209,3 +214,57 @@ def test_fused_ulysses_and_tp_engine(tmp_path, world):
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
                         "--master-port", "29687", str(script)], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0 and "SP_TP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+RTP_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("cpu:gloo,cuda:nccl")
+from verl_b200.ops import _ext
+from verl_b200.models.config import PRESETS
+from verl_b200.models.parallel_model import build_rollout_shard
+from verl_b200.models.transformer import DecoderLM
+from verl_b200.parallel.tp import TPContext
+from verl_b200.single_controller.spmd import init_spmd_process_group
+from verl_b200.workers.rollout.engine import InferenceEngine, SamplingParams
+host = init_spmd_process_group()
+full = DecoderLM(PRESETS["tiny-qwen2-gpu"], dtype=torch.bfloat16, device="cuda", seed=3)
+local = build_rollout_shard(full, rank, world)
+g = torch.Generator().manual_seed(0)
+prompts = [torch.randint(10, 4000, (int(torch.randint(20, 200, (1,), generator=g)),), generator=g).tolist() for _ in range(24)]
+sp = SamplingParams(temperature=0.0, max_tokens=40)
+want = InferenceEngine(full, max_num_seqs=32, max_model_len=512, num_blocks=300).generate(prompts, sp)
+res = {}
+for mode in ("fused", "nccl"):
+    ctx = TPContext(dist.group.WORLD, host, max_tokens=8192, hidden=full.cfg.hidden_size, max_out=full.cfg.hidden_size, graph_safe=True) if mode == "fused" else None
+    eng = InferenceEngine(local, max_num_seqs=32, max_model_len=512, num_blocks=300, tp_group=dist.group.WORLD, tp_ctx=ctx)
+    out = eng.generate(prompts, sp)
+    out = eng.generate(prompts, sp)          # second call replays the captured decode graph
+    torch.cuda.synchronize()
+    _ext.check_status("rollout tp " + mode)
+    res[mode] = out
+    same = sum(o.token_ids[:8] == w.token_ids[:8] for o, w in zip(out, want))
+    lp_err = max(abs(o.log_probs[0] - w.log_probs[0]) for o, w in zip(out, want))
+    assert same >= 20 and lp_err < 0.05, (mode, same, lp_err)
+    peer = [None, None]
+    dist.all_gather_object(peer, [o.token_ids for o in out])
+    assert peer[0] == peer[1], "tensor-parallel ranks diverged"
+dist.barrier()
+if rank == 0:
+    print("ROLLOUT_TP_OK")
+'''
+
+
+@pytest.mark.parametrize("world", [2])
+def test_tensor_parallel_rollout_replica(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "rtp.py"
+    script.write_text(RTP_WORKER)
+    env = dict(os.environ, REPO=repo, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                        "--master-port", "29689", str(script)], env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "ROLLOUT_TP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

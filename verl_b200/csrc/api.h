@@ -54,7 +54,8 @@ int vb_attn_varlen_bwd(const void* q, const void* k, const void* v, long ld, con
                        cudaStream_t st);
 
 int vb_gemm_allgather(int which, const long* seg_ptrs, int world, int seg_rows, int ld_seg, const void* other, int ld_other, void* C,
-                      const void* bias, int M, int N, int K, int ldc, int* err_word, cudaStream_t st);
+                      const void* bias, int M, int N, int K, int ldc, int rank, void* stage, int* stage_flags, int stage_epoch, int* err_word,
+                      cudaStream_t st);
 int vb_gemm_peer_scatter(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int ld_slot, const long* out_ptrs,
                          int rank, int world, int rows_per_owner, long slot_elems, int* err_word, cudaStream_t st);
 int vb_slots_reduce(const void* slots, int world, long slot_elems, long rows, int cols, int ld, const void* residual, void* out,
@@ -78,7 +79,8 @@ int vb_fp8_block_cast(const void* x, long ldx, void* y, long ldy, float* scale, 
 int vb_gemm_head_scatter(const void* A, const void* B, const void* bias, int M, int N, int K, int lda, int ldb, int ld_out, const long* out_ptrs,
                          int world, int row_off, int head_dim, const int* head_rank, const int* head_slot, int* err_word, cudaStream_t st);
 int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int ld_seg, int rows_total, int row_off, const void* B, int ldb, void* C,
-                 const void* bias, int M, int N, int ldc, int* err_word, cudaStream_t st);
+                 const void* bias, int M, int N, int ldc, int rank, void* stage, int* stage_flags, int stage_epoch, int* err_word,
+                 cudaStream_t st);
 int vb_reshard_quant(const long* src_ptrs, int world, int rows_per_rank, long ld_src, int row_begin, void* y, long ldy, float* scale,
                      void* out_bf16, long ld_bf16, int M_out, int N, cudaStream_t st);
 int vb_fp8_act_cast(const void* x, long ldx, void* y, long ldy, float* scale, long M, int K, cudaStream_t st);

@@ -94,28 +94,50 @@ TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
 
 namespace {
 // C = gather(A segments) @ B^T : a_ptrs int64 CPU [world] pointers to [seg_rows, K] bf16 segments (row stride K).
-void gemm_allgather_a(const Tensor& a_ptrs, int64_t seg_rows, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias) {
+// Optional staging (`stage` [rows_total, K] bf16, `flags` int32 [rows_total / 128], `epoch` > every earlier call's): remote
+// segments then cross NVLink once instead of once per output tile column.
+struct Stage {
+  void* ptr = nullptr;
+  int* flags = nullptr;
+};
+static Stage stage_of(const c10::optional<Tensor>& stage, const c10::optional<Tensor>& flags, int64_t need_elems, int64_t need_flags) {
+  Stage s;
+  if (stage.has_value() && stage->defined()) {
+    TORCH_CHECK(flags.has_value() && flags->defined(), "staging needs a flags tensor");
+    TORCH_CHECK(stage->is_cuda() && stage->scalar_type() == at::kBFloat16 && stage->is_contiguous() && stage->numel() >= need_elems, "bad stage buffer");
+    TORCH_CHECK(flags->is_cuda() && flags->scalar_type() == at::kInt && flags->numel() >= need_flags, "bad stage flags");
+    s.ptr = stage->data_ptr();
+    s.flags = flags->data_ptr<int>();
+  }
+  return s;
+}
+
+void gemm_allgather_a(const Tensor& a_ptrs, int64_t seg_rows, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias, int64_t rank,
+                      const c10::optional<Tensor>& stage, const c10::optional<Tensor>& flags, int64_t epoch) {
   TORCH_CHECK(a_ptrs.scalar_type() == at::kLong && !a_ptrs.is_cuda(), "gemm_allgather_a: pointer table must be a CPU int64 tensor");
   TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.dim() == 2 && b.stride(1) == 1, "gemm_allgather_a: bad b");
   const int world = a_ptrs.numel(), K = b.size(1), N = b.size(0), M = seg_rows * world;
   TORCH_CHECK(out.size(0) == M && out.size(1) == N && out.scalar_type() == at::kBFloat16 && out.stride(1) == 1, "gemm_allgather_a: bad out");
   const void* bias_p = (bias.has_value() && bias->defined()) ? bias->data_ptr() : nullptr;
   c10::cuda::CUDAGuard guard(b.device());
+  const Stage st = stage_of(stage, flags, (int64_t)M * K, M / 128);
   check_rc(vb_gemm_allgather(0, a_ptrs.data_ptr<long>(), world, (int)seg_rows, K, b.data_ptr(), (int)b.stride(0), out.data_ptr(), bias_p, M, N, K,
-                             (int)out.stride(0), vb_status_tensor(b.get_device()).data_ptr<int>(), cur_stream()),
+                             (int)out.stride(0), (int)rank, st.ptr, st.flags, (int)epoch, vb_status_tensor(b.get_device()).data_ptr<int>(), cur_stream()),
            "gemm_allgather_a");
 }
 
 // C = A @ gather(B segments)^T : weight rows sharded over ranks (ZeRO-3 style all-gather fused into the consuming GEMM).
-void gemm_allgather_b(const Tensor& a, const Tensor& b_ptrs, int64_t seg_rows, Tensor& out, const c10::optional<Tensor>& bias) {
+void gemm_allgather_b(const Tensor& a, const Tensor& b_ptrs, int64_t seg_rows, Tensor& out, const c10::optional<Tensor>& bias, int64_t rank,
+                      const c10::optional<Tensor>& stage, const c10::optional<Tensor>& flags, int64_t epoch) {
   TORCH_CHECK(b_ptrs.scalar_type() == at::kLong && !b_ptrs.is_cuda(), "gemm_allgather_b: pointer table must be a CPU int64 tensor");
   TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && a.dim() == 2 && a.stride(1) == 1, "gemm_allgather_b: bad a");
   const int world = b_ptrs.numel(), K = a.size(1), M = a.size(0), N = seg_rows * world;
   TORCH_CHECK(out.size(0) == M && out.size(1) == N && out.scalar_type() == at::kBFloat16 && out.stride(1) == 1, "gemm_allgather_b: bad out");
   const void* bias_p = (bias.has_value() && bias->defined()) ? bias->data_ptr() : nullptr;
   c10::cuda::CUDAGuard guard(a.device());
+  const Stage st = stage_of(stage, flags, (int64_t)N * K, N / 128);
   check_rc(vb_gemm_allgather(1, b_ptrs.data_ptr<long>(), world, (int)seg_rows, K, a.data_ptr(), (int)a.stride(0), out.data_ptr(), bias_p, M, N, K,
-                             (int)out.stride(0), vb_status_tensor(a.get_device()).data_ptr<int>(), cur_stream()),
+                             (int)out.stride(0), (int)rank, st.ptr, st.flags, (int)epoch, vb_status_tensor(a.get_device()).data_ptr<int>(), cur_stream()),
            "gemm_allgather_b");
 }
 
@@ -149,15 +171,18 @@ void gemm_head_scatter(const Tensor& a, const Tensor& b, const c10::optional<Ten
 // Ulysses, heads → sequence: out [M, N] = A @ b^T where A's K axis is split over ranks: rank r holds columns
 // [r * k_per_rank, ...) as rows [row_off, row_off + M) of its [rows_total, k_per_rank] buffer a_ptrs[r].
 void gemm_kseg(const Tensor& a_ptrs, int64_t k_per_rank, int64_t rows_total, int64_t row_off, const Tensor& b, Tensor& out,
-               const c10::optional<Tensor>& bias) {
+               const c10::optional<Tensor>& bias, int64_t rank, const c10::optional<Tensor>& stage, const c10::optional<Tensor>& flags, int64_t epoch) {
   TORCH_CHECK(a_ptrs.scalar_type() == at::kLong && !a_ptrs.is_cuda(), "gemm_kseg: pointer table must be a CPU int64 tensor");
   TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.dim() == 2 && b.stride(1) == 1, "gemm_kseg: bad b");
   const int world = a_ptrs.numel(), N = b.size(0), M = out.size(0);
   TORCH_CHECK(b.size(1) == world * k_per_rank && out.size(1) == N && out.scalar_type() == at::kBFloat16 && out.stride(1) == 1, "gemm_kseg: bad shapes");
   const void* bias_p = (bias.has_value() && bias->defined()) ? bias->data_ptr() : nullptr;
   c10::cuda::CUDAGuard guard(b.device());
+  const int64_t Mp = (M + 127) / 128 * 128;
+  const Stage st = stage_of(stage, flags, Mp * world * k_per_rank, (Mp / 128) * world);
   check_rc(vb_gemm_kseg(a_ptrs.data_ptr<long>(), world, (int)k_per_rank, (int)k_per_rank, (int)rows_total, (int)row_off, b.data_ptr(), (int)b.stride(0),
-                        out.data_ptr(), bias_p, M, N, (int)out.stride(0), vb_status_tensor(b.get_device()).data_ptr<int>(), cur_stream()),
+                        out.data_ptr(), bias_p, M, N, (int)out.stride(0), (int)rank, st.ptr, st.flags, (int)epoch,
+                        vb_status_tensor(b.get_device()).data_ptr<int>(), cur_stream()),
            "gemm_kseg");
 }
 
@@ -171,10 +196,10 @@ void slots_reduce(const Tensor& slots, int64_t world, int64_t slot_elems, int64_
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
-  m.def("gemm_allgather_a(Tensor a_ptrs, int seg_rows, Tensor b, Tensor(a!) out, Tensor? bias) -> ()", &gemm_allgather_a);
-  m.def("gemm_allgather_b(Tensor a, Tensor b_ptrs, int seg_rows, Tensor(a!) out, Tensor? bias) -> ()", &gemm_allgather_b);
+  m.def("gemm_allgather_a(Tensor a_ptrs, int seg_rows, Tensor b, Tensor(a!) out, Tensor? bias, int rank=0, Tensor? stage=None, Tensor? flags=None, int epoch=0) -> ()", &gemm_allgather_a);
+  m.def("gemm_allgather_b(Tensor a, Tensor b_ptrs, int seg_rows, Tensor(a!) out, Tensor? bias, int rank=0, Tensor? stage=None, Tensor? flags=None, int epoch=0) -> ()", &gemm_allgather_b);
   m.def("gemm_peer_scatter(Tensor a, Tensor b, Tensor out_ptrs, int rank, int rows_per_owner, int slot_elems) -> ()", &gemm_peer_scatter);
   m.def("gemm_head_scatter(Tensor a, Tensor b, Tensor? bias, Tensor out_ptrs, int ld_out, int row_off, int head_dim, Tensor head_rank, Tensor head_slot) -> ()", &gemm_head_scatter);
-  m.def("gemm_kseg(Tensor a_ptrs, int k_per_rank, int rows_total, int row_off, Tensor b, Tensor(a!) out, Tensor? bias) -> ()", &gemm_kseg);
+  m.def("gemm_kseg(Tensor a_ptrs, int k_per_rank, int rows_total, int row_off, Tensor b, Tensor(a!) out, Tensor? bias, int rank=0, Tensor? stage=None, Tensor? flags=None, int epoch=0) -> ()", &gemm_kseg);
   m.def("slots_reduce(Tensor slots, int world, int slot_elems, int rows, int cols, Tensor? residual, Tensor(a!) out) -> ()", &slots_reduce);
 }

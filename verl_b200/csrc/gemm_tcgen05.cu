@@ -50,8 +50,43 @@ struct DistArgs {
   int head_dim;                      // > 0: EPI_PEER routes whole heads (head_dim columns) through head_map (sequence → head a2a)
   uint16_t head_map[192];            // per output head: (destination rank << 12) | destination head slot
   void* peer_out[MAX_TP];
+  // Staging of the remote part of a gathered operand: tiles that live on another rank are copied ONCE over NVLink into
+  // `stage` (laid out like the gathered operand) by the epilogue warps at kernel start, 128-row chunk by chunk; a chunk's
+  // flag is set to `stage_epoch` when it has landed and the TMA producer waits for the flags of the tile it is about to
+  // load. Without staging every output tile would fetch its operand tile from the peer again.
+  void* stage;
+  int* stage_flags;
+  int stage_epoch;
+  int ld_stage;                      // row stride of `stage` in elements
+  int ld_seg;                        // row stride of the peers' segments in elements
+  const void* seg_ptr[MAX_TP];
+  CUtensorMap stage_map;
   CUtensorMap seg[MAX_TP];
 };
+
+__device__ __forceinline__ bool stage_wait(const int* flag, int epoch, volatile int* abort_flag, int* err_word) {
+  uint64_t t0 = 0;
+  uint32_t n = 0;
+  while (true) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= epoch) {
+      asm volatile("fence.proxy.async;" ::: "memory");   // the staged bytes were written by ordinary stores, TMA reads them next
+      return true;
+    }
+    if ((++n & 0x3F) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > VB_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        atomicCAS(err_word, 0, VB_ERR_WAIT_PEER | (blockIdx.x << 8));
+        return false;
+      }
+      __nanosleep(100);
+    }
+  }
+}
 
 // Extra epilogue inputs of the fused lm_head variants (rows = tokens, columns = vocabulary entries).
 struct LmHeadEpi {
@@ -128,6 +163,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int r = t - g * per_group;
     mb = first_m + (r % gsz);
     nb = r / gsz;
+    if (dist.stage != nullptr) {       // start with the tiles whose gathered operand rows are this rank's own
+      if (dist.seg_mode == 1) mb = (mb + (dist.rank * dist.seg_rows) / BM) % num_m;
+      else if (dist.seg_mode == 2) nb = (nb + (dist.rank * dist.seg_rows) / BN) % num_n;
+    }
   };
 
   if (warp == 0) {
@@ -149,16 +188,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
           const int k0 = kb * BK;
           if (!A_MN) {
-            if (dist.seg_mode == 1) tma_load_2d(sa, &dist.seg[m0 / dist.seg_rows], k0, m0 % dist.seg_rows, &full_bar[s]);
-            else if (dist.seg_mode == 3) tma_load_2d(sa, &dist.seg[k0 / dist.seg_rows], k0 % dist.seg_rows, m0 + dist.row_off, &full_bar[s]);
-            else tma_load_2d(sa, &tmA, k0, m0, &full_bar[s]);
+            if (dist.seg_mode == 1) {
+              const int owner = m0 / dist.seg_rows;
+              if (dist.stage != nullptr && owner != dist.rank) {
+                if (kb == kb0 && !stage_wait(dist.stage_flags + m0 / 128, dist.stage_epoch, abort_flag, err_word)) { ok = false; break; }
+                tma_load_2d(sa, &dist.stage_map, k0, m0, &full_bar[s]);
+              } else {
+                tma_load_2d(sa, &dist.seg[owner], k0, m0 % dist.seg_rows, &full_bar[s]);
+              }
+            } else if (dist.seg_mode == 3) {
+              const int owner = k0 / dist.seg_rows;
+              if (dist.stage != nullptr && owner != dist.rank) {
+                if (k0 % dist.seg_rows == 0 &&
+                    !stage_wait(dist.stage_flags + (m0 / 128) * dist.n_seg + owner, dist.stage_epoch, abort_flag, err_word)) { ok = false; break; }
+                tma_load_2d(sa, &dist.stage_map, k0, m0, &full_bar[s]);
+              } else {
+                tma_load_2d(sa, &dist.seg[owner], k0 % dist.seg_rows, m0 + dist.row_off, &full_bar[s]);
+              }
+            } else {
+              tma_load_2d(sa, &tmA, k0, m0, &full_bar[s]);
+            }
           } else {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * (BK * 128), &tmA, m0 + 64 * i, k0, &full_bar[s]);
           }
           if (!B_MN) {
-            if (dist.seg_mode == 2) tma_load_2d(sb, &dist.seg[n0 / dist.seg_rows], k0, n0 % dist.seg_rows, &full_bar[s]);
-            else tma_load_2d(sb, &tmB, k0, n0, &full_bar[s]);
+            if (dist.seg_mode == 2) {
+              const int owner = n0 / dist.seg_rows;
+              if (dist.stage != nullptr && owner != dist.rank) {
+                if (kb == kb0) {
+                  bool got = true;
+                  for (int c = 0; c < BN / 128 && got; ++c) got = stage_wait(dist.stage_flags + n0 / 128 + c, dist.stage_epoch, abort_flag, err_word);
+                  if (BN < 128 && got) got = stage_wait(dist.stage_flags + n0 / 128, dist.stage_epoch, abort_flag, err_word);
+                  if (!got) { ok = false; break; }
+                }
+                tma_load_2d(sb, &dist.stage_map, k0, n0, &full_bar[s]);
+              } else {
+                tma_load_2d(sb, &dist.seg[owner], k0, n0 % dist.seg_rows, &full_bar[s]);
+              }
+            } else {
+              tma_load_2d(sb, &tmB, k0, n0, &full_bar[s]);
+            }
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * (BK * 128), &tmB, n0 + 64 * i, k0, &full_bar[s]);
@@ -205,6 +275,53 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------ epilogue (128 threads)
+    if (dist.stage != nullptr) {
+      // Bring the remote chunks of the gathered operand into local memory, once. The 128 epilogue threads of every CTA
+      // share the chunks round-robin; nothing here waits on another CTA, so the copies always make progress.
+      const int et = threadIdx.x - 64;                    // 0..127
+      const bf16* const* srcs = reinterpret_cast<const bf16* const*>(dist.seg_ptr);
+      bf16* stage = reinterpret_cast<bf16*>(dist.stage);
+      if (dist.seg_mode == 1 || dist.seg_mode == 2) {
+        const int n_chunks = dist.seg_rows * dist.n_seg / 128;
+        const int vec_per_row = K / 8;
+        for (int c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+          const int row0 = c * 128, owner = row0 / dist.seg_rows;
+          if (owner == dist.rank) continue;
+          const bf16* src = srcs[owner] + (long)(row0 - owner * dist.seg_rows) * dist.ld_seg;
+          bf16* dst = stage + (long)row0 * dist.ld_stage;
+          for (int i = et; i < 128 * vec_per_row; i += 128) {
+            const int r = i / vec_per_row, v = i - r * vec_per_row;
+            *reinterpret_cast<uint4*>(dst + (long)r * dist.ld_stage + v * 8) = __ldcs(reinterpret_cast<const uint4*>(src + (long)r * dist.ld_seg + v * 8));
+          }
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (et == 0) {
+            asm volatile("fence.proxy.async;" ::: "memory");
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(dist.stage_flags + c), "r"(dist.stage_epoch) : "memory");
+          }
+        }
+      } else if (dist.seg_mode == 3) {
+        const int m_chunks = (M + 127) / 128;
+        const int vec_per_row = dist.seg_rows / 8;          // K columns per rank
+        for (int u = blockIdx.x; u < m_chunks * dist.n_seg; u += gridDim.x) {
+          const int c = u / dist.n_seg, owner = u - c * dist.n_seg;
+          if (owner == dist.rank) continue;
+          const int rows = min(128, M - c * 128);
+          const bf16* src = srcs[owner] + (long)(dist.row_off + c * 128) * dist.ld_seg;
+          bf16* dst = stage + (long)c * 128 * dist.ld_stage + (long)owner * dist.seg_rows;
+          for (int i = et; i < rows * vec_per_row; i += 128) {
+            const int r = i / vec_per_row, v = i - r * vec_per_row;
+            *reinterpret_cast<uint4*>(dst + (long)r * dist.ld_stage + v * 8) = __ldcs(reinterpret_cast<const uint4*>(src + (long)r * dist.ld_seg + v * 8));
+          }
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (et == 0) {
+            asm volatile("fence.proxy.async;" ::: "memory");
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(dist.stage_flags + u), "r"(dist.stage_epoch) : "memory");
+          }
+        }
+      }
+    }
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const bool out_f32 = flags & GEMM_OUT_F32;
     const bool accum = flags & GEMM_ACCUM;
@@ -755,7 +872,8 @@ static int pick_bn_dist(int M, int N) {
 // All-gather fused into the GEMM: C[M,N] = A B^T (+bias) where the rows of A (which = 0) or of B (which = 1) are split in
 // `world` equal segments; seg_ptrs[r] is rank r's segment ([seg_rows, K] bf16, row stride ld_seg) reachable from this GPU.
 extern "C" int vb_gemm_allgather(int which, const long* seg_ptrs, int world, int seg_rows, int ld_seg, const void* other, int ld_other,
-                                 void* C, const void* bias, int M, int N, int K, int ldc, int* err_word, cudaStream_t st) {
+                                 void* C, const void* bias, int M, int N, int K, int ldc, int rank, void* stage, int* stage_flags,
+                                 int stage_epoch, int* err_word, cudaStream_t st) {
   using namespace vb;
   if (world > MAX_TP || world < 1) return -2;
   const int rows_total = which == 0 ? M : N;
@@ -770,6 +888,13 @@ extern "C" int vb_gemm_allgather(int which, const long* seg_ptrs, int world, int
   for (int r = 0; r < world; ++r) {
     if (make_tmap_2d(&d.seg[r], reinterpret_cast<const void*>(seg_ptrs[r]), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, seg_rows, K, ld_seg, tile_rows, BK))
       return -1;
+  }
+  if (stage != nullptr) {
+    // `stage` is a local [rows_total, K] bf16 buffer (row stride K), `stage_flags` one int per 128 rows
+    if (seg_rows % 128 != 0 || rank < 0 || rank >= world) return -6;
+    d.stage = stage; d.stage_flags = stage_flags; d.stage_epoch = stage_epoch; d.ld_stage = K; d.ld_seg = ld_seg; d.rank = rank;
+    for (int r = 0; r < world; ++r) d.seg_ptr[r] = reinterpret_cast<const void*>(seg_ptrs[r]);
+    if (make_tmap_2d(&d.stage_map, stage, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_total, K, K, tile_rows, BK)) return -1;
   }
   const void* A = which == 0 ? reinterpret_cast<const void*>(seg_ptrs[0]) : other;
   const void* B = which == 0 ? other : reinterpret_cast<const void*>(seg_ptrs[0]);
@@ -817,7 +942,8 @@ extern "C" int vb_gemm_head_scatter(const void* A, const void* B, const void* bi
 // of A is split over ranks: columns [r * k_per_rank, (r+1) * k_per_rank) are rows [row_off, row_off + M) of rank r's
 // [T_total, k_per_rank] buffer (seg_ptrs[r], row stride ld_seg), read with TMA straight from that rank's memory.
 extern "C" int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int ld_seg, int rows_total, int row_off, const void* B, int ldb,
-                            void* C, const void* bias, int M, int N, int ldc, int* err_word, cudaStream_t st) {
+                            void* C, const void* bias, int M, int N, int ldc, int rank, void* stage, int* stage_flags, int stage_epoch,
+                            int* err_word, cudaStream_t st) {
   using namespace vb;
   if (world > MAX_TP || world < 1 || (k_per_rank % BK) != 0 || (ld_seg & 7) || (ldb & 7)) return -4;
   DistArgs d = {};
@@ -827,6 +953,13 @@ extern "C" int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int
       return -1;
   }
   const int K = world * k_per_rank;
+  if (stage != nullptr) {
+    // `stage` is a local [ceil128(M), K] bf16 buffer (row stride K); `stage_flags` has ceil(M/128) * world ints
+    if (rank < 0 || rank >= world) return -6;
+    d.stage = stage; d.stage_flags = stage_flags; d.stage_epoch = stage_epoch; d.ld_stage = K; d.ld_seg = ld_seg; d.rank = rank;
+    for (int r = 0; r < world; ++r) d.seg_ptr[r] = reinterpret_cast<const void*>(seg_ptrs[r]);
+    if (make_tmap_2d(&d.stage_map, stage, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (M + 127) / 128 * 128, K, K, BM, BK)) return -1;
+  }
   return launch_dist<EPI_STORE>(pick_bn_dist(M, N), reinterpret_cast<const void*>(seg_ptrs[0]), B, C, bias, M, N, K, ld_seg, ldb, ldc, err_word, st, d);
 }
 

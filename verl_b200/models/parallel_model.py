@@ -21,16 +21,18 @@ import torch
 
 from verl_b200.models.config import ModelConfig
 
-__all__ = ["local_model_config", "stage_layer_range", "shard_param", "unshard_param", "local_to_global_name", "tp_rule"]
+__all__ = ["local_model_config", "stage_layer_range", "shard_param", "unshard_param", "local_to_global_name", "tp_rule",
+           "build_rollout_shard", "refresh_rollout_shard"]
 
 
-def local_model_config(cfg: ModelConfig, tp: int) -> ModelConfig:
+def local_model_config(cfg: ModelConfig, tp: int, shard_vocab: bool = True) -> ModelConfig:
     if tp == 1:
         return cfg
     assert cfg.num_attention_heads % tp == 0 and cfg.num_key_value_heads % tp == 0, "head counts must divide by the TP size"
-    assert cfg.vocab_size % tp == 0 and cfg.intermediate_size % tp == 0
+    assert (cfg.vocab_size % tp == 0 or not shard_vocab) and cfg.intermediate_size % tp == 0
     kw = dict(num_attention_heads=cfg.num_attention_heads // tp, num_key_value_heads=cfg.num_key_value_heads // tp,
-              intermediate_size=cfg.intermediate_size // tp, vocab_size=cfg.vocab_size // tp, head_dim=cfg.head_dim)
+              intermediate_size=cfg.intermediate_size // tp, vocab_size=cfg.vocab_size // tp if shard_vocab else cfg.vocab_size,
+              head_dim=cfg.head_dim)
     if cfg.is_moe:
         assert cfg.moe_intermediate_size % tp == 0
         kw["moe_intermediate_size"] = cfg.moe_intermediate_size // tp
@@ -98,3 +100,32 @@ def local_to_global_name(name: str, layer_offset: int) -> str:
         _, idx, rest = name.split(".", 2)
         return f"layers.{int(idx) + layer_offset}.{rest}"
     return name
+
+
+def build_rollout_shard(full, tp_rank: int, tp: int):
+    """Tensor-parallel slice of ``full`` for the rollout engine: decoder layers are cut like in training (copies), while
+    embedding, final norm and output matrix stay whole and SHARE the trainer's storage (the sampler wants full logits on
+    every rank, and those tensors are read-only here)."""
+    import torch
+
+    from verl_b200.models.transformer import DecoderLM
+
+    cfg = full.cfg
+    local = DecoderLM(local_model_config(cfg, tp, shard_vocab=False), dtype=full.dtype, device=full.embed_tokens.device, init=False)
+    local.embed_tokens = full.embed_tokens
+    local.norm = full.norm
+    if full.lm_head is not None:
+        local.lm_head = full.lm_head
+    refresh_rollout_shard(local, full, tp_rank, tp)
+    return local
+
+
+def refresh_rollout_shard(local, full, tp_rank: int, tp: int) -> None:
+    """Re-cut the layer shards after the trainer's weights changed (one device-to-device copy of 1/tp of the layers)."""
+    import torch
+
+    src = dict(full.named_parameters())
+    with torch.no_grad():
+        for name, p in local.named_parameters():
+            if name.startswith("layers."):
+                p.copy_(shard_param(name, src[name], full.cfg, tp_rank, tp))

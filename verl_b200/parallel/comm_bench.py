@@ -161,7 +161,15 @@ def main():
         dist.all_gather_into_tensor(w_full, w_loc)
         torch.nn.functional.linear(x_full, w_full)
 
-    ms_f = timer(lambda: TPContext.weight_gather_linear(x_full, ws, 2 * F // W, H))
+    w_stage = torch.empty(2 * F * H, device=dev, dtype=torch.bfloat16)
+    w_flags = torch.zeros(2 * F // 128 + 8, device=dev, dtype=torch.int32)
+    ep = [0]
+
+    def wg_fused():
+        ep[0] += 1
+        return TPContext.weight_gather_linear(x_full, ws, 2 * F // W, H, 0, w_stage, w_flags, ep[0])
+
+    ms_f = timer(wg_fused)
     ms_b = timer(wg_nccl)
     report(rank, f"weight all-gather -> GEMM  [{T}x{H}] x [{2 * F}x{H}]^T, shards={W}", ms_f, ms_b, 2.0 * T * H * 2 * F, (W - 1) * (2 * F // W) * H * 2)
     ws.barrier()

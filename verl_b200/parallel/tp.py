@@ -44,6 +44,11 @@ class TPContext:
         # slots[src_rank][tokens, out] written by peers' GEMM epilogues
         self.slot_elems = max_tokens * max_out
         self.slots = SymmetricBuffer(self.world * self.slot_elems * 2, group, host_group)
+        # local staging of the peers' activation shards (each crosses NVLink once per call) + per-128-row arrival flags
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.stage = torch.empty(max_tokens * hidden, dtype=torch.bfloat16, device=dev)
+        self.stage_flags = torch.zeros(max(1, max_tokens // 128) + 8, dtype=torch.int32, device=dev)
+        self.stage_epoch = 0
 
     # ------------------------------------------------------------------ all-gather → GEMM
     def stage_activation(self, x_shard: torch.Tensor) -> None:
@@ -57,7 +62,8 @@ class TPContext:
         out = torch.empty(rows * self.world, w.shape[0], dtype=torch.bfloat16, device=x_shard.device)
         if fused_comm_enabled() and rows % 128 == 0:
             self.stage_activation(x_shard)
-            self.ops.gemm_allgather_a(self.act.table(), rows, w, out, bias)
+            self.stage_epoch += 1
+            self.ops.gemm_allgather_a(self.act.table(), rows, w, out, bias, self.rank, self.stage, self.stage_flags, self.stage_epoch)
             self.act.barrier()      # nobody overwrites its shard while a peer may still be reading it
             return out
         full = torch.empty(rows * self.world, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
@@ -97,11 +103,13 @@ class TPContext:
 
     # ------------------------------------------------------------------ ZeRO-3 weight gather → GEMM
     @staticmethod
-    def weight_gather_linear(x: torch.Tensor, w_symm: SymmetricBuffer, shard_rows: int, in_features: int, byte_offset: int = 0) -> torch.Tensor:
-        """y = x @ concat_r(W_r)ᵀ with W_r = rank r's [shard_rows, in_features] slice living in ``w_symm``."""
+    def weight_gather_linear(x: torch.Tensor, w_symm: SymmetricBuffer, shard_rows: int, in_features: int, byte_offset: int = 0,
+                             stage: Optional[torch.Tensor] = None, flags: Optional[torch.Tensor] = None, epoch: int = 0) -> torch.Tensor:
+        """y = x @ concat_r(W_r)ᵀ with W_r = rank r's [shard_rows, in_features] slice living in ``w_symm``. With ``stage``
+        ([rows_total, in_features] bf16) and ``flags`` the remote slices are copied into local memory once by the kernel."""
         ops = _ext.ops()
         out = torch.empty(x.shape[0], shard_rows * w_symm.world, dtype=torch.bfloat16, device=x.device)
-        ops.gemm_allgather_b(x, w_symm.table(byte_offset), shard_rows, out, None)
+        ops.gemm_allgather_b(x, w_symm.table(byte_offset), shard_rows, out, None, w_symm.rank, stage, flags, epoch)
         return out
 
 

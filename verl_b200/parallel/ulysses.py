@@ -184,6 +184,11 @@ class FusedUlysses:
                 slot_of.append(base + j % self.hkv_l)
         self.head_rank = torch.tensor(rank_of, dtype=torch.int32)
         self.head_slot = torch.tensor(slot_of, dtype=torch.int32)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        tl_max = -(-max_tokens // self.sp // 128) * 128 + 128
+        self.o_stage = torch.empty(tl_max * Hq * D, dtype=torch.bfloat16, device=dev)     # peers' head slices of the local token rows
+        self.o_flags = torch.zeros((tl_max // 128) * self.sp + 8, dtype=torch.int32, device=dev)
+        self.o_epoch = 0
 
     def qkv_forward(self, x_shard, w, bias):
         Tl = x_shard.shape[0]
@@ -198,7 +203,8 @@ class FusedUlysses:
         self.o_buf.tensor(torch.bfloat16, Tp * self.Kl).view(Tp, self.Kl).copy_(o_local)
         self.o_buf.barrier()
         out = torch.empty(Tl, w_o.shape[0], dtype=torch.bfloat16, device=o_local.device)
-        self.ops.gemm_kseg(self.o_buf.table(), self.Kl, Tp, self.rank * Tl, w_o, out, None)
+        self.o_epoch += 1
+        self.ops.gemm_kseg(self.o_buf.table(), self.Kl, Tp, self.rank * Tl, w_o, out, None, self.rank, self.o_stage, self.o_flags, self.o_epoch)
         return out
 
     # ---- layout conversions used by the (unfused) backward passes

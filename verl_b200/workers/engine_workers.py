@@ -236,7 +236,8 @@ class ActorRolloutRefWorker(Worker):
             self._register_dispatch_collect_info("actor", dp_rank=eng.get_data_parallel_rank(), is_collect=eng.is_mp_src_rank_with_outputs())
         if self._is_rollout:
             self._build_rollout()
-        self._register_dispatch_collect_info("rollout", dp_rank=self.rank, is_collect=True)
+        tp = getattr(self, "_rollout_tp", 1) if self._is_rollout else 1
+        self._register_dispatch_collect_info("rollout", dp_rank=self.rank // tp, is_collect=self.rank % tp == 0)
 
     def _build_rollout(self):
         from verl_b200.workers.rollout.engine import InferenceEngine
@@ -254,12 +255,42 @@ class ActorRolloutRefWorker(Worker):
             model.load_hf_stream(src.engine.get_per_tensor_param()[0])
             self._rollout_owns_model = True
         max_len = cfg_get(ro, "max_model_len", None) or (int(cfg_get(ro, "prompt_length", 512)) + int(cfg_get(ro, "response_length", 512)))
+        self._rollout_tp = int(cfg_get(ro, "tensor_model_parallel_size", 1) or 1)
+        tp_group = tp_ctx = None
+        if self._rollout_tp > 1:
+            model, tp_group, tp_ctx = self._build_rollout_tp(model, ro)
         self.rollout = InferenceEngine(
             model, max_num_seqs=int(cfg_get(ro, "max_num_seqs", 256)), max_model_len=int(max_len),
             max_num_batched_tokens=int(cfg_get(ro, "max_num_batched_tokens", 8192)),
             gpu_memory_utilization=float(cfg_get(ro, "gpu_memory_utilization", 0.5)), enforce_eager=bool(cfg_get(ro, "enforce_eager", False)),
             sync_interval=int(cfg_get(ro, "sync_interval", 16)), enable_prefix_sharing=bool(cfg_get(ro, "enable_prefix_caching", True)),
-            num_blocks=cfg_get(ro, "num_blocks", None))
+            num_blocks=cfg_get(ro, "num_blocks", None), tp_group=tp_group, tp_ctx=tp_ctx)
+
+    def _build_rollout_tp(self, full_model, ro):
+        """Rollout replicas of ``tp`` adjacent ranks: every rank keeps a tensor-parallel slice of the decoder layers cut from
+        the full weights it holds for training (reference: vLLM ``tensor_parallel_size`` replicas,
+        ``verl/workers/rollout/replica.py:102-106``)."""
+        from verl_b200.models.parallel_model import build_rollout_shard
+        from verl_b200.parallel.tp import TPContext, fused_comm_enabled
+
+        tp, world, rank = self._rollout_tp, dist.get_world_size(), dist.get_rank()
+        assert world % tp == 0, "world size must be a multiple of rollout.tensor_model_parallel_size"
+        mine = host = None
+        cuda = torch.cuda.is_available()
+        for b in range(0, world, tp):
+            ranks = list(range(b, b + tp))
+            g = dist.new_group(ranks)
+            hgrp = dist.new_group(ranks, backend="gloo") if cuda else g
+            if rank in ranks:
+                mine, host = g, hgrp
+        self._rollout_full_model = full_model
+        local = build_rollout_shard(full_model, rank % tp, tp)
+        ctx = None
+        if cuda and fused_comm_enabled():
+            max_tok = int(cfg_get(ro, "max_num_batched_tokens", 8192))
+            ctx = TPContext(mine, host, max_tokens=max(max_tok, int(cfg_get(ro, "max_num_seqs", 256))), hidden=full_model.cfg.hidden_size,
+                            max_out=full_model.cfg.hidden_size, graph_safe=True)
+        return local, mine, ctx
 
     # ------------------------------------------------------------------ rollout
     def _agent_loop_manager(self):
@@ -304,7 +335,7 @@ class ActorRolloutRefWorker(Worker):
             temperature=temperature if do_sample or validate else 0.0,
             top_p=float(cfg_get(vk, "top_p", 1.0)) if validate else float(meta.get("top_p", cfg_get(ro, "top_p", 1.0))),
             top_k=int(cfg_get(vk, "top_k", -1)) if validate else int(meta.get("top_k", cfg_get(ro, "top_k", -1))),
-            max_tokens=R, ignore_eos=bool(cfg_get(ro, "ignore_eos", False)), seed=int(meta.get("seed", 0)) + 1000003 * self.rank + int(meta.get("global_steps", 0)))
+            max_tokens=R, ignore_eos=bool(cfg_get(ro, "ignore_eos", False)), seed=int(meta.get("seed", 0)) + 1000003 * (self.rank // getattr(self, "_rollout_tp", 1)) + int(meta.get("global_steps", 0)))
         eos = meta.get("eos_token_id", None)
         pad_id = int(meta.get("pad_token_id", 0) or 0)
         ids_cpu, att_cpu = ids.cpu(), att.cpu().bool()
@@ -380,10 +411,17 @@ class ActorRolloutRefWorker(Worker):
         if self.actor is not None and self.rollout is not None:
             eng = self.actor.engine
             if getattr(self, "_rollout_owns_model", False):
-                self.rollout.model.load_hf_stream(eng.get_per_tensor_param()[0])
+                target = getattr(self, "_rollout_full_model", None) or self.rollout.model
+                target.load_hf_stream(eng.get_per_tensor_param()[0])
             elif not eng.store.flat.is_cuda and torch.cuda.is_available():
                 eng.to("cuda", model=True, optimizer=False, grad=False)
                 self.rollout._graph = None
+        if self.rollout is not None and getattr(self, "_rollout_tp", 1) > 1:
+            from verl_b200.models.parallel_model import refresh_rollout_shard
+
+            if not self._rollout_full_model.embed_tokens.is_cuda and torch.cuda.is_available():
+                self.actor.engine.to("cuda", model=True, optimizer=False, grad=False)
+            refresh_rollout_shard(self.rollout.model, self._rollout_full_model, self.rank % self._rollout_tp, self._rollout_tp)
         if dist.is_initialized():
             dist.barrier()
         return time.perf_counter() - t0

@@ -83,8 +83,13 @@ def _sample_reference(logits: torch.Tensor, temperature: float, top_k: int, top_
 class InferenceEngine:
     def __init__(self, model: DecoderLM, max_num_seqs: int = 256, max_model_len: int = 2048, num_blocks: Optional[int] = None,
                  max_num_batched_tokens: int = 8192, gpu_memory_utilization: float = 0.5, enforce_eager: bool = False,
-                 sync_interval: int = 16, enable_prefix_sharing: bool = True, decode_splits: int = 0):
+                 sync_interval: int = 16, enable_prefix_sharing: bool = True, decode_splits: int = 0, tp_group=None, tp_ctx=None):
+        """``tp_group`` / ``tp_ctx``: tensor-parallel replica. ``model`` is then this rank's slice (``build_rollout_shard``); every
+        rank of the group runs the same requests in lockstep (same scheduler decisions, same sampled tokens) and the
+        row-parallel projections end in an all-reduce — fused into the GEMM epilogue over NVLink peer memory when
+        ``tp_ctx`` (a ``TPContext``) is given, NCCL otherwise."""
         self.model = model
+        self.tp_group, self.tp = tp_group, tp_ctx
         self.cfg = model.cfg
         self.device = model.embed_tokens.device
         self.dtype = model.embed_tokens.dtype
@@ -213,10 +218,25 @@ class InferenceEngine:
             qkv = ops.apply_rope_(qkv, positions, cos, sin, n_rot, c.head_dim)
             self._cache_write(li, qkv, slots)
             o = attn_fn(li, qkv)
-            a = ops.linear(o, at.o_proj)
+            a = self._row_parallel(o, at.o_proj)
             x, res = ops.add_rmsnorm(a, res, layer.post_attention_layernorm, c.rms_norm_eps)
-            h = layer.mlp(x)
+            if self.tp_group is not None and not c.is_moe:
+                h = self._row_parallel(ops.swiglu(ops.linear(x, layer.mlp.gate_up_proj)), layer.mlp.down_proj)
+            else:
+                h = layer.mlp(x)
         return ops.add_rmsnorm(h, res, m.norm, c.rms_norm_eps)[0]
+
+    def _row_parallel(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """``x @ wᵀ`` summed over the tensor-parallel ranks (plain GEMM when the replica is a single GPU)."""
+        if self.tp_group is None:
+            return ops.linear(x, w)
+        if self.tp is not None:
+            return self.tp.gemm_allreduce(x.contiguous(), w)
+        import torch.distributed as dist
+
+        y = ops.linear(x, w).contiguous()
+        dist.all_reduce(y, group=self.tp_group)
+        return y
 
     def _cache_write(self, li: int, qkv: torch.Tensor, slots: torch.Tensor):
         c = self.cfg
