@@ -64,7 +64,10 @@ struct DistArgs {
   CUtensorMap seg[MAX_TP];
 };
 
+constexpr int STAGE_PARTS = 8;
+
 __device__ __forceinline__ bool stage_wait(const int* flag, int epoch, volatile int* abort_flag, int* err_word) {
+  epoch *= STAGE_PARTS;
   uint64_t t0 = 0;
   uint32_t n = 0;
   while (true) {
@@ -105,8 +108,9 @@ struct LmHeadEpi {
   const float* g_ent;     // [M] or null
 };
 
-template <int BN, bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(192, 1)
+// COPY_WARPS > 0 adds that many warps (after the six role warps) whose only job is to stage remote operand chunks.
+template <int BN, bool A_MN, bool B_MN, int EPI, int COPY_WARPS = 0>
+__global__ void __launch_bounds__(192 + 32 * COPY_WARPS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
                  const bf16* __restrict__ bias, int M, int N, int K, int ldc, int flags, int* err_word, const LmHeadEpi epi,
                  int split_k, int kb_per_split, float* __restrict__ split_ws, const __grid_constant__ DistArgs dist) {
@@ -273,55 +277,76 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (ok) umma_commit(&tfull_bar[acc]);
       }
     }
-  } else {
-    // ------------------------------------------------------------ epilogue (128 threads)
+  } else if (COPY_WARPS > 0 && warp >= 6) {
+    // ------------------------------------------------------------ staging copies (dedicated warps)
+    if constexpr (COPY_WARPS > 0) {
     if (dist.stage != nullptr) {
-      // Bring the remote chunks of the gathered operand into local memory, once. The 128 epilogue threads of every CTA
-      // share the chunks round-robin; nothing here waits on another CTA, so the copies always make progress.
-      const int et = threadIdx.x - 64;                    // 0..127
+      // Bring the remote chunks of the gathered operand into local memory, once. A 128-row chunk is copied in
+      // STAGE_PARTS pieces of 16 rows, spread round-robin over the copy warps of all CTAs; each finished piece adds 1 to
+      // the chunk's flag, and a chunk is complete when its flag reaches stage_epoch * STAGE_PARTS. Nothing here waits on
+      // another CTA, so the copies always make progress.
+      constexpr int CT = 32 * COPY_WARPS;                 // copy threads per CTA
+      const int et = threadIdx.x - 192;
       const bf16* const* srcs = reinterpret_cast<const bf16* const*>(dist.seg_ptr);
       bf16* stage = reinterpret_cast<bf16*>(dist.stage);
-      if (dist.seg_mode == 1 || dist.seg_mode == 2) {
-        const int n_chunks = dist.seg_rows * dist.n_seg / 128;
-        const int vec_per_row = K / 8;
-        for (int c = blockIdx.x; c < n_chunks; c += gridDim.x) {
-          const int row0 = c * 128, owner = row0 / dist.seg_rows;
-          if (owner == dist.rank) continue;
-          const bf16* src = srcs[owner] + (long)(row0 - owner * dist.seg_rows) * dist.ld_seg;
-          bf16* dst = stage + (long)row0 * dist.ld_stage;
-          for (int i = et; i < 128 * vec_per_row; i += 128) {
-            const int r = i / vec_per_row, v = i - r * vec_per_row;
-            *reinterpret_cast<uint4*>(dst + (long)r * dist.ld_stage + v * 8) = __ldcs(reinterpret_cast<const uint4*>(src + (long)r * dist.ld_seg + v * 8));
+      const bool by_k = dist.seg_mode == 3;
+      const int cols = by_k ? dist.seg_rows : K;          // bf16 elements per copied row
+      const int vec_per_row = cols / 8;
+      const int n_chunks = by_k ? ((M + 127) / 128) * dist.n_seg : dist.seg_rows * dist.n_seg / 128;
+      const int n_units = n_chunks * STAGE_PARTS;
+      // skip this rank's own chunks when dealing out the work, so that the remote ones are spread evenly
+      int mine = 0;
+      for (int u = 0; u < n_units; ++u) {
+        const int c = u / STAGE_PARTS, part = u - c * STAGE_PARTS;
+        int owner, row0;
+        const bf16* src;
+        bf16* dst;
+        if (by_k) {
+          const int mc = c / dist.n_seg;
+          owner = c - mc * dist.n_seg;
+          row0 = mc * 128 + part * 16;
+          src = srcs[owner] + (long)(dist.row_off + row0) * dist.ld_seg;
+          dst = stage + (long)row0 * dist.ld_stage + (long)owner * dist.seg_rows;
+        } else {
+          row0 = c * 128 + part * 16;
+          owner = row0 / dist.seg_rows;
+          src = srcs[owner] + (long)(row0 - owner * dist.seg_rows) * dist.ld_seg;
+          dst = stage + (long)row0 * dist.ld_stage;
+        }
+        if (owner == dist.rank) continue;
+        if ((mine++ % gridDim.x) != blockIdx.x) continue;
+        const int rows = by_k ? max(0, min(16, M - row0)) : 16;
+        const int total = rows * vec_per_row;
+        for (int i0 = 0; i0 < total; i0 += CT * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j * CT + et;
+            if (i < total) {
+              const int r = i / vec_per_row, x = i - r * vec_per_row;
+              v[j] = __ldcs(reinterpret_cast<const uint4*>(src + (long)r * dist.ld_seg + x * 8));
+            }
           }
-          __threadfence();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (et == 0) {
-            asm volatile("fence.proxy.async;" ::: "memory");
-            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(dist.stage_flags + c), "r"(dist.stage_epoch) : "memory");
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j * CT + et;
+            if (i < total) {
+              const int r = i / vec_per_row, x = i - r * vec_per_row;
+              *reinterpret_cast<uint4*>(dst + (long)r * dist.ld_stage + x * 8) = v[j];
+            }
           }
         }
-      } else if (dist.seg_mode == 3) {
-        const int m_chunks = (M + 127) / 128;
-        const int vec_per_row = dist.seg_rows / 8;          // K columns per rank
-        for (int u = blockIdx.x; u < m_chunks * dist.n_seg; u += gridDim.x) {
-          const int c = u / dist.n_seg, owner = u - c * dist.n_seg;
-          if (owner == dist.rank) continue;
-          const int rows = min(128, M - c * 128);
-          const bf16* src = srcs[owner] + (long)(dist.row_off + c * 128) * dist.ld_seg;
-          bf16* dst = stage + (long)c * 128 * dist.ld_stage + (long)owner * dist.seg_rows;
-          for (int i = et; i < rows * vec_per_row; i += 128) {
-            const int r = i / vec_per_row, v = i - r * vec_per_row;
-            *reinterpret_cast<uint4*>(dst + (long)r * dist.ld_stage + v * 8) = __ldcs(reinterpret_cast<const uint4*>(src + (long)r * dist.ld_seg + v * 8));
-          }
-          __threadfence();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (et == 0) {
-            asm volatile("fence.proxy.async;" ::: "memory");
-            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(dist.stage_flags + u), "r"(dist.stage_epoch) : "memory");
-          }
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
+        if (et == 0) {
+          asm volatile("fence.proxy.async;" ::: "memory");
+          asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(dist.stage_flags + c) : "memory");
         }
       }
     }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (128 threads)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const bool out_f32 = flags & GEMM_OUT_F32;
     const bool accum = flags & GEMM_ACCUM;
@@ -607,7 +632,7 @@ static int num_sms() {
   return g_num_sms;
 }
 
-template <int BN, bool A_MN, bool B_MN, int EPI = EPI_STORE>
+template <int BN, bool A_MN, bool B_MN, int EPI = EPI_STORE, int COPY_WARPS = 0>
 static int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb,
                        int ldc, int flags, int* err_word, cudaStream_t stream, const LmHeadEpi& epi = LmHeadEpi{},
                        int split_k = 1, float* split_ws = nullptr, const DistArgs* dist_in = nullptr) {
@@ -623,7 +648,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   else       rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
   if (rc) return rc;
   static bool attr_set = false;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI, COPY_WARPS>;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return -10;
@@ -636,7 +661,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   if (split_k > 1 && split_ws == nullptr) return -6;
   int units = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * split_k;
   int grid = units < num_sms() ? units : num_sms();
-  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags,
+  kern<<<grid, 192 + 32 * COPY_WARPS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags,
                                                 err_word, epi, split_k, kb_per, split_ws, dist);
   if (cudaGetLastError() != cudaSuccess) return -11;
   if (split_k > 1) {
@@ -852,6 +877,16 @@ __global__ void slots_reduce_kernel(const bf16* __restrict__ slots, int world, l
 template <int EPI>
 static int launch_dist(int bn, const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb, int ldc,
                        int* err_word, cudaStream_t st, const DistArgs& d) {
+  if constexpr (EPI == EPI_STORE) {
+    if (d.stage != nullptr) {
+      switch (bn) {
+        case 256: return launch_gemm<256, false, false, EPI, 8>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
+        case 128: return launch_gemm<128, false, false, EPI, 8>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
+        case 64: return launch_gemm<64, false, false, EPI, 8>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
+        default: return -5;
+      }
+    }
+  }
   switch (bn) {
     case 256: return launch_gemm<256, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
     case 128: return launch_gemm<128, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
