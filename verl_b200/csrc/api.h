@@ -81,6 +81,11 @@ int vb_gemm_head_scatter(const void* A, const void* B, const void* bias, int M, 
 int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int ld_seg, int rows_total, int row_off, const void* B, int ldb, void* C,
                  const void* bias, int M, int N, int ldc, int rank, void* stage, int* stage_flags, int stage_epoch, int* err_word,
                  cudaStream_t st);
+int vb_ppo_loss(const float* lp, const float* old_lp, const float* ref_lp, const float* adv, const float* weight, const float* mask,
+                const float* is_w, long n, float clip_lo, float clip_hi, float clip_c, int kl_type, float kl_coef, float* grad,
+                float* loss_out, float* stats, cudaStream_t st);
+int vb_grpo_advantage(const float* scores, const int* group, int B, int G, const float* mask, int R, float eps, int norm_by_std,
+                      float* mean, float* stdv, float* adv, cudaStream_t st);
 int vb_reshard_quant(const long* src_ptrs, int world, int rows_per_rank, long ld_src, int row_begin, void* y, long ldy, float* scale,
                      void* out_bf16, long ld_bf16, int M_out, int N, cudaStream_t st);
 int vb_fp8_act_cast(const void* x, long ldx, void* y, long ldy, float* scale, long M, int K, cudaStream_t st);

@@ -142,9 +142,52 @@ def bench_elementwise(a):
     report(f"adamw n={n}", timeit(lambda: o.adamw_(p32, m, v, g, p16, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1, sc), a.iters), bytes_=n * (4 * 4 + 3 * 4 + 2))
 
 
+def bench_fused_gather(a):
+    """Gather-fused GEMMs on ONE GPU: the "peers" are separate buffers in this GPU's memory, so the kernels run their full
+    multi-rank code path (per-rank tensor maps, staging copies by the copy warps, arrival flags, head routing) without a
+    second process. Used for single-GPU profiler captures of the fused kernels; NVLink figures come from
+    ``verl_b200.parallel.comm_bench`` on real multi-GPU runs."""
+    from verl_b200.ops import _ext
+
+    o = _ext.ops()
+    W, T, H, N = a.world, a.m, a.k, a.n
+    Tl = T // W
+    segs = [(torch.randn(Tl, H, device="cuda")).bfloat16() for _ in range(W)]
+    ptrs = torch.tensor([s.data_ptr() for s in segs], dtype=torch.int64)
+    w = (0.02 * torch.randn(N, H, device="cuda")).bfloat16()
+    out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    stage = torch.empty(T * H, device="cuda", dtype=torch.bfloat16)
+    flags = torch.zeros(T // 128 + 8, device="cuda", dtype=torch.int32)
+    ep = [0]
+
+    def ag():
+        ep[0] += 1
+        o.gemm_allgather_a(ptrs, Tl, w, out, None, 0, stage, flags, ep[0])
+
+    report(f"all-gather -> GEMM (staged, {W} segments on one GPU) M={T} N={N} K={H}", timeit(ag, a.iters), flops=2.0 * T * N * H)
+    ref = torch.cat(segs).float() @ w.float().t()
+    err = ((out.float() - ref).abs().max() / ref.abs().max()).item()
+    print(f"  max rel err vs fp32 matmul: {err:.2e}")
+    # sequence -> head all-to-all fused into the QKV projection: every "rank" buffer is local
+    D, Hq, Hkv = 128, a.heads, a.kv_heads
+    C = (Hq + 2 * Hkv) * D
+    wq = (0.02 * torch.randn(C, H, device="cuda")).bfloat16()
+    hq_l, hkv_l = Hq // W, Hkv // W
+    Cl = (hq_l + 2 * hkv_l) * D
+    bufs = [torch.empty(T, Cl, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    optr = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64)
+    rank_of = [h // hq_l for h in range(Hq)] + [j // hkv_l for j in range(Hkv)] * 2
+    slot_of = [h % hq_l for h in range(Hq)] + [hq_l + j % hkv_l for j in range(Hkv)] + [hq_l + hkv_l + j % hkv_l for j in range(Hkv)]
+    hr, hs = torch.tensor(rank_of, dtype=torch.int32), torch.tensor(slot_of, dtype=torch.int32)
+    x = segs[0]
+    report(f"QKV projection + head scatter ({W} destinations on one GPU) M={Tl} N={C} K={H}",
+           timeit(lambda: o.gemm_head_scatter(x, wq, None, optr, Cl, 0, D, hr, hs), a.iters), flops=2.0 * Tl * C * H)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "lmhead", "decode_attn", "elementwise", "all"])
+    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "lmhead", "decode_attn", "elementwise", "fused_gather", "all"])
+    ap.add_argument("--world", type=int, default=2)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=4096)
@@ -167,6 +210,8 @@ def main():
     _ext.load()
     if a.kernel in ("gemm", "all"):
         bench_gemm(a)
+    if a.kernel == "fused_gather":
+        bench_fused_gather(a)
     if a.kernel in ("attn_fwd", "all"):
         bench_attn(a, False)
     if a.kernel in ("attn_bwd", "all"):

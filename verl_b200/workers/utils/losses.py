@@ -50,6 +50,31 @@ def ppo_loss(config, model_output: dict, data, dp_group=None) -> tuple[torch.Ten
     view = _LossCfgView({k: _get(config, k) for k in ("clip_ratio", "clip_ratio_low", "clip_ratio_high", "clip_ratio_c",
                                                        "policy_loss", "tau_pos", "tau_neg")})
     view["global_batch_info"] = info
+    from verl_b200.ops import rl as rl_ops
+
+    kl_type = _get(config, "kl_loss_type", "low_var_kl") if _get(config, "use_kl_loss", False) else None
+    if loss_mode == "vanilla" and rl_ops.fused_ppo_available(log_prob) and kl_type in rl_ops.KL_TYPES:
+        # one kernel: surrogate + KL term, their gradient and the logging sums
+        clip = _get(config, "clip_ratio", 0.2)
+        lo, hi = _get(config, "clip_ratio_low", None), _get(config, "clip_ratio_high", None)
+        w = rl_ops.agg_weights(mask, agg_mode, **info)
+        coef = _get(config, "kl_loss_coef", 0.001) if kl_type else 0.0
+        loss, stats = rl_ops.fused_ppo_loss(log_prob, data["old_log_probs"], data.get("ref_log_prob") if hasattr(data, "get") else None,
+                                            data["advantages"], mask, w, data.get("rollout_is_weights") if hasattr(data, "get") else None,
+                                            clip if lo is None else lo, clip if hi is None else hi, _get(config, "clip_ratio_c", 3.0), kl_type, coef)
+        metrics = {}
+        if entropy is not None and _get(config, "entropy_coeff", 0.0) != 0:
+            ent_loss = core_algos.agg_loss(entropy, mask, agg_mode, **info)
+            loss = loss - _get(config, "entropy_coeff", 0.0) * ent_loss
+            metrics["actor/entropy_loss"] = Metric(AggregationType.MEAN, ent_loss.detach().item())
+        st = stats.tolist()
+        n = max(st[4], 1.0)
+        metrics.update({"actor/pg_clipfrac": Metric(AggregationType.MEAN, st[0] / n), "actor/ppo_kl": Metric(AggregationType.MEAN, st[1] / n),
+                        "actor/pg_clipfrac_lower": Metric(AggregationType.MEAN, st[2] / n), "actor/pg_loss": Metric(AggregationType.MEAN, st[5])})
+        if kl_type:
+            metrics["actor/kl_loss"] = Metric(AggregationType.MEAN, st[6])
+            metrics["actor/kl_coef"] = Metric(AggregationType.MEAN, coef)
+        return loss, metrics
     fn = core_algos.get_policy_loss_fn(loss_mode)
     pg_loss, pg_metrics = fn(old_log_prob=data["old_log_probs"], log_prob=log_prob, advantages=data["advantages"],
                              response_mask=mask, loss_agg_mode=agg_mode, config=view,
