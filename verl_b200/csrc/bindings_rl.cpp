@@ -59,3 +59,42 @@ TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
   m.def("ppo_loss(Tensor lp, Tensor old_lp, Tensor? ref_lp, Tensor adv, Tensor weight, Tensor mask, Tensor? is_w, float clip_lo, float clip_hi, float clip_c, int kl_type, float kl_coef) -> (Tensor, Tensor, Tensor)", &ppo_loss);
   m.def("grpo_advantage(Tensor scores, Tensor group, int G, Tensor mask, float eps, bool norm_by_std) -> Tensor", &grpo_advantage);
 }
+
+at::Tensor& vb_status_tensor(int dev);
+
+namespace {
+// y[R, N] = x[R, K] @ w[e]^T per 128-row block (w [E, N, K]); transposed = true reads w [E, K, N] as the dgrad operand.
+Tensor gemm_grouped(const Tensor& x, const Tensor& w, const Tensor& blk_expert, bool transposed) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "gemm_grouped: bad x");
+  TORCH_CHECK(w.scalar_type() == at::kBFloat16 && w.dim() == 3 && w.is_contiguous(), "gemm_grouped: w must be contiguous [E, N, K]");
+  TORCH_CHECK(blk_expert.is_cuda() && blk_expert.scalar_type() == at::kInt && blk_expert.numel() * 128 == x.size(0), "gemm_grouped: bad block table");
+  const int R = x.size(0), K = x.size(1), E = w.size(0);
+  const int N = transposed ? w.size(2) : w.size(1);
+  TORCH_CHECK((transposed ? w.size(1) : w.size(2)) == K, "gemm_grouped: K mismatch");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::zeros({R, N}, x.options());
+  check_rc(vb_gemm_grouped(x.data_ptr(), w.data_ptr(), y.data_ptr(), blk_expert.data_ptr<int>(), R, N, K, E, (int)x.stride(0), N, transposed,
+                           vb_status_tensor(x.get_device()).data_ptr<int>(), cur_stream()),
+           "gemm_grouped");
+  return y;
+}
+
+// dw[E, M, N] (+)= dy[rows_e, M]^T @ x[rows_e, N]; expert_rng int32 [E, 2] = (first block, end block)
+void gemm_grouped_wgrad(const Tensor& dy, const Tensor& x, const Tensor& expert_rng, Tensor& dw, bool accumulate) {
+  TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16 && dy.stride(1) == 1 && x.stride(1) == 1, "gemm_grouped_wgrad: bad operands");
+  TORCH_CHECK(expert_rng.is_cuda() && expert_rng.scalar_type() == at::kInt && expert_rng.is_contiguous() && expert_rng.dim() == 2 && expert_rng.size(1) == 2, "gemm_grouped_wgrad: bad ranges");
+  TORCH_CHECK(dw.is_contiguous() && dw.dim() == 3 && dw.size(1) == dy.size(1) && dw.size(2) == x.size(1) && dw.size(0) == expert_rng.size(0), "gemm_grouped_wgrad: bad dw");
+  const bool f32 = dw.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || dw.scalar_type() == at::kBFloat16, "gemm_grouped_wgrad: dw must be fp32 or bf16");
+  c10::cuda::CUDAGuard guard(dy.device());
+  check_rc(vb_gemm_grouped_wgrad(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), expert_rng.data_ptr<int>(), (int)dy.size(0), (int)dy.size(1), (int)x.size(1),
+                                 (int)dw.size(0), (int)dy.stride(0), (int)x.stride(0), f32, accumulate, vb_status_tensor(dy.get_device()).data_ptr<int>(),
+                                 cur_stream()),
+           "gemm_grouped_wgrad");
+}
+}  // namespace
+
+TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
+  m.def("gemm_grouped(Tensor x, Tensor w, Tensor blk_expert, bool transposed) -> Tensor", &gemm_grouped);
+  m.def("gemm_grouped_wgrad(Tensor dy, Tensor x, Tensor expert_rng, Tensor(a!) dw, bool accumulate) -> ()", &gemm_grouped_wgrad);
+}

@@ -54,6 +54,16 @@ struct DistArgs {
   // `stage` (laid out like the gathered operand) by the epilogue warps at kernel start, 128-row chunk by chunk; a chunk's
   // flag is set to `stage_epoch` when it has landed and the TMA producer waits for the flags of the tile it is about to
   // load. Without staging every output tile would fetch its operand tile from the peer again.
+  // Grouped (mixture-of-experts) GEMM. Token rows are sorted by expert and every expert's segment is padded to a multiple
+  // of 128 rows, so a 128-row block belongs to exactly one expert.
+  //   group_mode 1: C[rows, N] = A[rows, K] * B[e]^T with e = blk_expert[row block] (< 0: block unused, tile skipped);
+  //                 tmB is a 3-D map whose outermost coordinate is the expert.
+  //   group_mode 2: C[e][M, N] (+)= A[rows_e, M]^T * B[rows_e, N] over the rows of expert e (weight gradient);
+  //                 expert_rng[e] = (first block, end block); the tile index runs over (expert, m block, n block).
+  int group_mode;
+  int num_experts;
+  const int* blk_expert;
+  const int2* expert_rng;
   void* stage;
   int* stage_flags;
   int stage_epoch;
@@ -131,7 +141,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_n = (N + BN - 1) / BN;
   const int num_kb_total = (K + BK - 1) / BK;
   // split-K: a work unit is (output tile, K slice); partial sums go to an fp32 workspace and are reduced afterwards
-  const int num_tiles = num_m * num_n * split_k;
+  const int num_tiles = dist.group_mode == 2 ? num_m * num_n * dist.num_experts : num_m * num_n * split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -180,11 +190,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int mb, nb;
-        tile_coords(t, mb, nb);
+        int mb, nb, expert = 0;
+        int kb0, kb1;
+        if (dist.group_mode == 2) {
+          expert = t / (num_m * num_n);
+          tile_coords(t - expert * num_m * num_n, mb, nb);
+          const int2 rng = dist.expert_rng[expert];
+          kb0 = rng.x * (128 / BK);
+          kb1 = rng.y * (128 / BK);
+          if (kb1 <= kb0) continue;
+        } else {
+          tile_coords(t, mb, nb);
+          kb0 = (t % split_k) * kb_per_split;
+          kb1 = min(num_kb_total, kb0 + kb_per_split);
+          if (dist.group_mode == 1) {
+            expert = dist.blk_expert[mb];
+            if (expert < 0) continue;
+          }
+        }
         const int m0 = mb * BM, n0 = nb * BN;
-        const int kb0 = (t % split_k) * kb_per_split;
-        const int kb1 = min(num_kb_total, kb0 + kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
@@ -230,9 +254,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               } else {
                 tma_load_2d(sb, &dist.seg[owner], k0, n0 % dist.seg_rows, &full_bar[s]);
               }
+            } else if (dist.group_mode == 1) {
+              tma_load_3d(sb, &tmB, k0, n0, expert, &full_bar[s]);
             } else {
               tma_load_2d(sb, &tmB, k0, n0, &full_bar[s]);
             }
+          } else if (dist.group_mode == 1) {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_3d(sb + i * (BK * 128), &tmB, n0 + 64 * i, k0, expert, &full_bar[s]);
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * (BK * 128), &tmB, n0 + 64 * i, k0, &full_bar[s]);
@@ -250,13 +279,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        int kb0, kb1;
+        if (dist.group_mode == 2) {
+          const int2 rng = dist.expert_rng[t / (num_m * num_n)];
+          kb0 = rng.x * (128 / BK);
+          kb1 = rng.y * (128 / BK);
+          if (kb1 <= kb0) { --it; continue; }          // skipped tiles do not consume an accumulator buffer
+        } else {
+          kb0 = (t % split_k) * kb_per_split;
+          kb1 = min(num_kb_total, kb0 + kb_per_split);
+          if (dist.group_mode == 1) {
+            int mb, nb;
+            tile_coords(t, mb, nb);
+            if (dist.blk_expert[mb] < 0) { --it; continue; }
+          }
+        }
         const uint32_t acc = it & 1;
         const uint32_t acc_ph = (it >> 1) & 1;
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        const int kb0 = (t % split_k) * kb_per_split;
-        const int kb1 = min(num_kb_total, kb0 + kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, abort_flag, err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
@@ -354,7 +396,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
       int mb, nb;
-      tile_coords(t, mb, nb);
+      long c_off = 0;                                  // element offset of this tile's output matrix inside Cv
+      if (dist.group_mode == 2) {
+        const int expert = t / (num_m * num_n);
+        tile_coords(t - expert * num_m * num_n, mb, nb);
+        const int2 rng = dist.expert_rng[expert];
+        if (rng.y <= rng.x) { --it; continue; }
+        c_off = (long)expert * M * ldc;
+      } else {
+        tile_coords(t, mb, nb);
+        if (dist.group_mode == 1 && dist.blk_expert[mb] < 0) { --it; continue; }
+      }
       const uint32_t acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
       if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, err_word, VB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
@@ -520,7 +572,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           const bool full = (col0 + 32 <= N);
           if (out_f32) {
-            float* crow = reinterpret_cast<float*>(Cv) + (size_t)row * ldc + col0;
+            float* crow = reinterpret_cast<float*>(Cv) + c_off + (size_t)row * ldc + col0;
             if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
@@ -536,7 +588,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (col0 + j < N) crow[j] = accum ? crow[j] + f[j] : f[j];
             }
           } else {
-            bf16* crow = reinterpret_cast<bf16*>(Cv) + (size_t)row * ldc + col0;
+            bf16* crow = reinterpret_cast<bf16*>(Cv) + c_off + (size_t)row * ldc + col0;
             if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
@@ -952,6 +1004,73 @@ extern "C" int vb_gemm_peer_scatter(const void* A, const void* B, int M, int N, 
   d.rank = rank; d.world = world; d.rows_per_owner = rows_per_owner; d.slot_elems = slot_elems;
   for (int r = 0; r < world; ++r) d.peer_out[r] = reinterpret_cast<void*>(out_ptrs[r]);
   return launch_dist<EPI_PEER>(pick_bn_dist(M, N), A, B, nullptr, nullptr, M, N, K, lda, ldb, ld_slot, err_word, st, d);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Grouped GEMMs of a mixture-of-experts layer (see DistArgs::group_mode). R = padded number of token rows.
+namespace vb {
+template <bool B_MN>
+static int launch_grouped_fwd(const void* A, const void* B, void* C, const int* blk_expert, int R, int N, int K, int E, int lda, int ldc,
+                              int* err_word, cudaStream_t stream) {
+  constexpr int BN = 256;
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, K, lda, BM, BK)) return -1;
+  int rc;
+  if (!B_MN) rc = make_tmap_3d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, E, (uint64_t)K * 2, (uint64_t)N * K * 2, BK, BN, 1);
+  else       rc = make_tmap_3d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, E, (uint64_t)N * 2, (uint64_t)N * K * 2, 64, BK, 1);
+  if (rc) return rc;
+  static bool attr_set = false;
+  auto kern = gemm_bf16_kernel<BN, false, B_MN, EPI_STORE>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  DistArgs d = {};
+  d.group_mode = 1; d.num_experts = E; d.blk_expert = blk_expert;
+  const int units = (R / BM) * ((N + BN - 1) / BN);
+  const int grid = units < num_sms() ? units : num_sms();
+  const int num_kb = (K + BK - 1) / BK;
+  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, nullptr, R, N, K, ldc, 0, err_word, LmHeadEpi{}, 1, num_kb, nullptr, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+}  // namespace vb
+
+// Y[R, N] = X[R, K] * W[e(row block)]^T. b_mn = 0: W is [E, N, K]; b_mn = 1: W is [E, K, N] (the same storage read as the
+// input-gradient operand: dX[R, N] = dY[R, K] * W[e] with W stored [E, K(out), N(in)]). Rows of unused blocks are not written.
+extern "C" int vb_gemm_grouped(const void* A, const void* B, void* C, const int* blk_expert, int R, int N, int K, int E, int lda, int ldc,
+                               int b_mn, int* err_word, cudaStream_t stream) {
+  using namespace vb;
+  if (R <= 0) return 0;
+  if ((R % BM) != 0 || (lda & 7) || (N & 7) || (K & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -4;
+  return b_mn ? launch_grouped_fwd<true>(A, B, C, blk_expert, R, N, K, E, lda, ldc, err_word, stream)
+              : launch_grouped_fwd<false>(A, B, C, blk_expert, R, N, K, E, lda, ldc, err_word, stream);
+}
+
+// dW[e][M, N] (+)= dY[rows_e, M]^T * X[rows_e, N] for every expert; expert_rng[e] = (first 128-row block, end block).
+extern "C" int vb_gemm_grouped_wgrad(const void* dY, const void* X, void* dW, const void* expert_rng, int R, int M, int N, int E, int ld_dy,
+                                     int ld_x, int out_f32, int accumulate, int* err_word, cudaStream_t stream) {
+  using namespace vb;
+  if (R <= 0 || E <= 0) return 0;
+  if ((R % BM) != 0 || (ld_dy & 7) || (ld_x & 7) || (M % BM) != 0) return -4;
+  constexpr int BN = 256;
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  if (make_tmap_2d(&tmA, dY, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, M, ld_dy, BK, 64)) return -1;
+  if (make_tmap_2d(&tmB, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, N, ld_x, BK, 64)) return -1;
+  static bool attr_set = false;
+  auto kern = gemm_bf16_kernel<BN, true, true, EPI_STORE>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  DistArgs d = {};
+  d.group_mode = 2; d.num_experts = E; d.expert_rng = reinterpret_cast<const int2*>(expert_rng);
+  const long units = (long)E * (M / BM) * ((N + BN - 1) / BN);
+  const int grid = units < num_sms() ? (int)units : num_sms();
+  const int flags = (out_f32 ? GEMM_OUT_F32 : 0) | (accumulate ? GEMM_ACCUM : 0);
+  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, dW, nullptr, M, N, R, N, flags, err_word, LmHeadEpi{}, 1, (R + BK - 1) / BK, nullptr, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 // Sequence → head all-to-all fused into the projection GEMM (Ulysses): this rank's [M, K] token shard times W[N, K]^T;

@@ -53,8 +53,73 @@ def unpermute_tokens(y: torch.Tensor, order: torch.Tensor, weights: torch.Tensor
     return out
 
 
+GROUP_BLOCK = 128
+
+
+def padded_layout(counts: torch.Tensor, n_rows: int, block: int = GROUP_BLOCK):
+    """For rows sorted by expert (``counts[e]`` rows each): destination row of every sorted row in a layout where each
+    expert's segment is padded to a multiple of ``block`` rows, plus the tables the grouped GEMM kernels take. Everything
+    stays on the device; the padded size is the static upper bound ``ceil((n + E·(block−1)) / block)·block``.
+    Returns (dest [n] int64, R, blk_expert [R/block] int32 (−1 = unused), expert_rng [E, 2] int32 block ranges)."""
+    E = counts.numel()
+    dev = counts.device
+    padded = (counts + block - 1) // block * block
+    pad_end = torch.cumsum(padded, 0)
+    pad_off = pad_end - padded
+    off = torch.cumsum(counts, 0) - counts
+    sorted_e = torch.repeat_interleave(torch.arange(E, device=dev), counts, output_size=n_rows)
+    dest = pad_off[sorted_e] + (torch.arange(n_rows, device=dev) - off[sorted_e])
+    R = (n_rows + E * (block - 1) + block - 1) // block * block
+    starts = torch.arange(R // block, device=dev) * block
+    be = torch.searchsorted(pad_end, starts, right=True)
+    blk_expert = torch.where(starts < pad_end[-1], be, torch.full_like(be, -1)).to(torch.int32)
+    rng = torch.stack([pad_off // block, pad_end // block], 1).to(torch.int32).contiguous()
+    return dest, R, blk_expert, rng
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """y[rows of expert e] = x[rows] @ w[e]ᵀ for row blocks sorted and padded per expert (one kernel for all experts)."""
+
+    @staticmethod
+    def forward(ctx, x, w, blk_expert, expert_rng):
+        from . import _ext
+
+        ctx.save_for_backward(x, w, blk_expert, expert_rng)
+        return _ext.ops().gemm_grouped(x.contiguous(), w, blk_expert, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import _ext
+
+        x, w, blk_expert, expert_rng = ctx.saved_tensors
+        o = _ext.ops()
+        dy = dy.contiguous()
+        dx = o.gemm_grouped(dy, w, blk_expert, True) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                o.gemm_grouped_wgrad(dy, x, expert_rng, mg, True)
+            else:
+                dw = torch.zeros_like(w)
+                o.gemm_grouped_wgrad(dy, x, expert_rng, dw, False)
+        return dx, dw, None, None
+
+
+def _experts_grouped(xp: torch.Tensor, counts: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
+    """Same contract as ``_experts_local`` on the sm_100a grouped GEMM: three launches per layer instead of 2·E."""
+    n = xp.shape[0]
+    dest, R, blk_expert, rng = padded_layout(counts, n)
+    xpad = torch.zeros(R, xp.shape[1], dtype=xp.dtype, device=xp.device).index_copy(0, dest, xp)
+    h = Fn.swiglu(_GroupedLinear.apply(xpad, gate_up, blk_expert, rng))
+    y = _GroupedLinear.apply(h, down, blk_expert, rng)
+    return y.index_select(0, dest)
+
+
 def _experts_local(xp: torch.Tensor, counts: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, first_expert: int = 0):
     """Grouped SwiGLU MLP over rows already sorted by (local) expert."""
+    if Fn.use_native(xp) and gate_up.shape[1] % 8 == 0 and xp.shape[1] % 128 == 0 and gate_up.shape[1] % 256 == 0 and xp.shape[0] > 0:
+        return _experts_grouped(xp, counts, gate_up, down)
     out = torch.empty(xp.shape[0], down.shape[1], dtype=xp.dtype, device=xp.device)
     start = 0
     for e, n in enumerate(counts.tolist()):
