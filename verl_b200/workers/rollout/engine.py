@@ -128,6 +128,13 @@ class InferenceEngine:
                 print(f"[rollout] KV cache limited to {got} blocks ({got * per_block / 2**30:.1f} GiB) of the {want} needed to hold "
                       f"{self.max_num_seqs} sequences of {self.max_model_len} tokens; expect preemptions", flush=True)
             want = got
+        if self.tp_group is not None:
+            # every rank of a tensor-parallel replica must run the same schedule: agree on the smallest cache
+            import torch.distributed as dist
+
+            t = torch.tensor([want], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.tp_group)
+            want = int(t.item())
         return want
 
     def _tick(self):
