@@ -233,6 +233,18 @@ class InferenceEngine:
                 h = layer.mlp(x)
         return ops.add_rmsnorm(h, res, m.norm, c.rms_norm_eps)[0]
 
+    def _tp_sync_samples(self, tok: torch.Tensor, lp: torch.Tensor) -> None:
+        """The ranks of a tensor-parallel replica compute identical logits and draw with identical random streams, but the
+        schedule (who finished, who is admitted) must never depend on that staying bit-exact: the first rank's tokens are
+        the replica's tokens."""
+        if self.tp_group is None:
+            return
+        import torch.distributed as dist
+
+        src = dist.get_global_rank(self.tp_group, 0)
+        dist.broadcast(tok, src=src, group=self.tp_group)
+        dist.broadcast(lp, src=src, group=self.tp_group)
+
     def _row_parallel(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """``x @ wᵀ`` summed over the tensor-parallel ranks (plain GEMM when the replica is a single GPU)."""
         if self.tp_group is None:
@@ -322,6 +334,7 @@ class InferenceEngine:
         slots = torch.tensor([s for _, s in reqs_slots], dtype=torch.int64, device=self.device)
         rid = slots.to(torch.int32)
         tok, lp = self._sample(logits, sp.temperature, sp.top_k, sp.top_p, row_ids=rid)
+        self._tp_sync_samples(tok, lp)
         if self.native:
             self.rng[1] += 1
         plen = torch.tensor([len(r["prompt"]) + len(r["out"]) for r, _ in reqs_slots], dtype=torch.int32, device=self.device)
@@ -358,6 +371,7 @@ class InferenceEngine:
         h = self._layer_stack(self.cur_tokens, pos, slot_map, attn)
         logits = ops.linear(h, self.model.output_weight)
         self._sample(logits, sp.temperature, sp.top_k, sp.top_p, self.row_ids, self.out_tok, self.out_lp)
+        self._tp_sync_samples(self.out_tok, self.out_lp)
         self.cur_tokens.copy_(self.out_tok)
         self.positions.add_(act)
         self.hist_tok.index_copy_(0, self.hist_idx, self.out_tok[None])
