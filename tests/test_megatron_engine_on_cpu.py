@@ -23,7 +23,8 @@ from verl_b200.workers.engine.megatron.engine import MegatronEngine
 dist.init_process_group("gloo")
 rank, world = dist.get_rank(), dist.get_world_size()
 cfg = PRESETS["tiny-qwen2"].replace(num_hidden_layers=3, tie_word_embeddings=os.environ["TIED"] == "1")
-eng = MegatronEngine(cfg, {"seed": 1, "tensor_model_parallel_size": int(os.environ["TP"]), "pipeline_model_parallel_size": int(os.environ["PP"])},
+eng = MegatronEngine(cfg, {"seed": 1, "tensor_model_parallel_size": int(os.environ["TP"]), "pipeline_model_parallel_size": int(os.environ["PP"]),
+                           "sequence_parallel": os.environ.get("SP", "0") == "1"},
                      {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, {})
 eng.initialize()
 exported = {k: v.clone() for k, v in eng.get_per_tensor_param()[0]}
@@ -64,15 +65,16 @@ def test_shard_unshard_roundtrip():
     assert [list(stage_layer_range(7, 3, s)) for s in range(3)] == [[0, 1, 2], [3, 4], [5, 6]]
 
 
-@pytest.mark.parametrize("world,tp,pp,tied", [(4, 2, 2, False), (4, 1, 2, True), (3, 1, 3, True), (2, 2, 1, True)])
-def test_parallel_ranks_match_single_rank(tmp_path, world, tp, pp, tied):
+@pytest.mark.parametrize("world,tp,pp,tied,sp", [(4, 2, 2, False, False), (4, 1, 2, True, False), (3, 1, 3, True, False), (2, 2, 1, True, False),
+                                                 (2, 2, 1, False, True), (4, 2, 2, True, True)])
+def test_parallel_ranks_match_single_rank(tmp_path, world, tp, pp, tied, sp):
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     script = tmp_path / "w.py"
     script.write_text(WORKER)
     out = tmp_path / "out.pt"
-    env = dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1", TP=str(tp), PP=str(pp), TIED="1" if tied else "0")
+    env = dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1", TP=str(tp), PP=str(pp), TIED="1" if tied else "0", SP="1" if sp else "0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-                        "--master-port", str(29660 + world + tp), str(script)], env=env, capture_output=True, text=True, timeout=900)
+                        "--master-port", str(29660 + world + tp + (10 if sp else 0)), str(script)], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     cfg = PRESETS["tiny-qwen2"].replace(num_hidden_layers=3, tie_word_embeddings=tied)
     eng = FSDPEngine(cfg, {"seed": 1}, {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, {})

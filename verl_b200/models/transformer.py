@@ -20,7 +20,8 @@ from torch.utils.checkpoint import checkpoint
 
 from verl_b200 import ops
 from verl_b200.models.config import ModelConfig
-from verl_b200.parallel.tp import copy_to_tp, reduce_from_tp, vocab_parallel_embedding
+from verl_b200.parallel.tp import (allgather_linear, copy_to_tp, gather_from_sp, linear_reduce_scatter, reduce_from_tp, reduce_scatter_to_sp,
+                                  vocab_parallel_embedding)
 
 __all__ = ["DecoderLM", "PackedBatch", "hf_to_native_state_dict", "native_to_hf_tensors"]
 
@@ -74,7 +75,10 @@ class Attention(nn.Module):
             from verl_b200.parallel.ulysses import fused_ulysses_attention_block
 
             return fused_ulysses_attention_block(x, self, pb, cfg, fu, cos, sin)
-        qkv = _proj(self, "qkv_proj", copy_to_tp(x, self.tp_group), self.qkv_bias)
+        if getattr(self, "tp_sp", False):       # sequence-parallel region boundary: all-gather fused into the projection
+            qkv = allgather_linear(x, self.qkv_proj, self.qkv_bias, self.tp_group, getattr(self, "tp_ctx", None))
+        else:
+            qkv = _proj(self, "qkv_proj", copy_to_tp(x, self.tp_group), self.qkv_bias)
         if cfg.qk_norm:
             T = qkv.shape[0]
             q, k, v = qkv.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=-1)
@@ -89,6 +93,8 @@ class Attention(nn.Module):
         else:
             o = ops.attention_varlen(qkv, pb.cu_seqlens, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                                      pb.max_seqlen, pb.cu_seqlens_cpu)
+        if getattr(self, "tp_sp", False):
+            return linear_reduce_scatter(o, self.o_proj, self.tp_group, getattr(self, "tp_ctx", None))
         return reduce_from_tp(_proj(self, "o_proj", o), self.tp_group)
 
 
@@ -101,6 +107,10 @@ class MLP(nn.Module):
         self.tp_group = None
 
     def forward(self, x):
+        if getattr(self, "tp_sp", False):
+            tpctx = getattr(self, "tp_ctx", None)
+            h = ops.swiglu(allgather_linear(x, self.gate_up_proj, None, self.tp_group, tpctx))
+            return linear_reduce_scatter(h, self.down_proj, self.tp_group, tpctx)
         y = _proj(self, "down_proj", ops.swiglu(_proj(self, "gate_up_proj", copy_to_tp(x, self.tp_group))))
         return reduce_from_tp(y, self.tp_group)
 
@@ -220,19 +230,24 @@ class DecoderLM(nn.Module):
     def rope(self, device):
         return ops.rope_tables(self.cfg.max_position_embeddings, self.cfg.head_dim, self.cfg.rope_theta, device)
 
-    def set_tp_group(self, group, vocab_offset: int = 0):
-        """Switch the model to tensor-parallel execution: ``cfg`` must already describe the local shard."""
-        self.tp_group, self.vocab_offset = group, vocab_offset
+    def set_tp_group(self, group, vocab_offset: int = 0, sequence_parallel: bool = False, tp_ctx=None):
+        """Switch the model to tensor-parallel execution: ``cfg`` must already describe the local shard. With
+        ``sequence_parallel`` the stream between the attention / MLP blocks is split over tokens (``[T/tp, H]`` per rank)."""
+        self.tp_group, self.vocab_offset, self.tp_sp = group, vocab_offset, sequence_parallel
         for layer in self.layers:
-            layer.self_attn.tp_group = group
-            layer.mlp.tp_group = group
+            for mod in (layer.self_attn, layer.mlp):
+                mod.tp_group, mod.tp_sp, mod.tp_ctx = group, sequence_parallel, tp_ctx
 
     def forward_hidden(self, pb: PackedBatch, h_in: Optional[torch.Tensor] = None):
         """Final-normed hidden states [T, H] on the last pipeline stage, the raw residual stream on earlier stages.
         ``h_in`` is the stream received from the previous stage (stages without the embedding)."""
         cos, sin = self.rope(pb.input_ids.device)
+        sp = getattr(self, "tp_sp", False)
         if self.pre_process:
-            if self.tp_group is not None:
+            if self.tp_group is not None and sp:
+                h = vocab_parallel_embedding(pb.input_ids, self.embed_tokens, self.vocab_offset, None)    # partial sums
+                h = reduce_scatter_to_sp(h, self.tp_group)
+            elif self.tp_group is not None:
                 h = vocab_parallel_embedding(pb.input_ids, self.embed_tokens, self.vocab_offset, self.tp_group)
             else:
                 h = ops.embedding(pb.input_ids, self.embed_tokens)
@@ -247,8 +262,10 @@ class DecoderLM(nn.Module):
         if not self.post_process:
             return h + residual if residual is not None else h
         if residual is None:
-            return ops.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)
-        return ops.add_rmsnorm(h, residual, self.norm, self.cfg.rms_norm_eps)[0]
+            out = ops.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)
+        else:
+            out = ops.add_rmsnorm(h, residual, self.norm, self.cfg.rms_norm_eps)[0]
+        return gather_from_sp(out, self.tp_group, replicated_grad=True) if sp else out
 
     def forward(self, pb: PackedBatch, labels: Optional[torch.Tensor] = None, temperature: float = 1.0,
                 need_entropy: bool = True, return_logits: bool = False):

@@ -162,3 +162,161 @@ def vocab_parallel_embedding(ids: torch.Tensor, w_local: torch.Tensor, vocab_off
     h = ops.embedding(torch.where(mine, local, torch.zeros_like(local)), w_local)
     h = h * mine.unsqueeze(-1).to(h.dtype)
     return reduce_from_tp(h, group)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Megatron-style SEQUENCE parallelism: between the tensor-parallel regions the hidden stream is split over the token axis
+# ([T/tp, H] per rank), so norms, residual adds and the pipeline sends work on 1/tp of the tokens. A column-parallel
+# layer is entered through an all-gather and a row-parallel layer is left through a reduce-scatter; both are fused into
+# the GEMM kernels in forward when a ``TPContext`` is attached (``allgather_linear`` / ``gemm_reduce_scatter``), and run
+# as collective + GEMM in backward.
+def _all_gather_rows(x: torch.Tensor, group) -> torch.Tensor:
+    W = dist.get_world_size(group)
+    out = torch.empty(W * x.shape[0], *x.shape[1:], dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+    return out
+
+
+def _reduce_scatter_rows(x: torch.Tensor, group) -> torch.Tensor:
+    W = dist.get_world_size(group)
+    x = x.contiguous()
+    if dist.get_backend(group) == "gloo":          # gloo has no reduce-scatter: all-reduce and keep the own slice
+        dist.all_reduce(x, group=group)
+        n = x.shape[0] // W
+        r = dist.get_rank(group)
+        return x[r * n:(r + 1) * n].clone()
+    out = torch.empty(x.shape[0] // W, *x.shape[1:], dtype=x.dtype, device=x.device)
+    dist.reduce_scatter_tensor(out, x, group=group)
+    return out
+
+
+class _GatherFromSP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _all_gather_rows(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _reduce_scatter_rows(g, ctx.group), None
+
+
+class _ReduceScatterToSP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _reduce_scatter_rows(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_gather_rows(g, ctx.group), None
+
+
+class _GatherFromSPReplicatedGrad(torch.autograd.Function):
+    """All-gather whose consumer computes the SAME gradient on every rank (e.g. the hidden states entering a replicated
+    loss): backward keeps this rank's slice instead of summing the copies."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group, ctx.n = group, x.shape[0]
+        return _all_gather_rows(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        r = dist.get_rank(ctx.group)
+        return g[r * ctx.n:(r + 1) * ctx.n].contiguous(), None
+
+
+def gather_from_sp(x, group, replicated_grad: bool = False):
+    if group is None or dist.get_world_size(group) == 1:
+        return x
+    return _GatherFromSPReplicatedGrad.apply(x, group) if replicated_grad else _GatherFromSP.apply(x, group)
+
+
+def reduce_scatter_to_sp(x, group):
+    return x if group is None or dist.get_world_size(group) == 1 else _ReduceScatterToSP.apply(x, group)
+
+
+def _dgrad(dy, w):
+    """dx = dy @ w (w stored [out, in]) on the tcgen05 GEMM when available."""
+    from verl_b200.ops.functional import gemm, use_native
+
+    return gemm(dy, w, b_mn=True) if use_native(dy) else torch.matmul(dy, w)
+
+
+def _wgrad(dy, x, w):
+    """dW (+)= dyᵀ x into ``w.main_grad`` when the engine provides one; returns the gradient tensor otherwise."""
+    from verl_b200.ops.functional import gemm, use_native
+
+    mg = getattr(w, "main_grad", None)
+    if use_native(dy):
+        if mg is not None:
+            gemm(dy, x, a_mn=True, b_mn=True, out=mg, accumulate=True)
+            return None
+        return gemm(dy, x, a_mn=True, b_mn=True)
+    dw = dy.float().t() @ x.float()
+    if mg is not None:
+        mg.add_(dw.to(mg.dtype))
+        return None
+    return dw.to(w.dtype)
+
+
+class _AllGatherLinear(torch.autograd.Function):
+    """y [T, out_local] = all_gather(x_shard) @ wᵀ (+ bias)."""
+
+    @staticmethod
+    def forward(ctx, x_shard, w, bias, group, tpctx):
+        ctx.save_for_backward(x_shard, w)
+        ctx.group, ctx.bias_ref = group, bias
+        if tpctx is not None and fused_comm_enabled() and x_shard.is_cuda and x_shard.shape[0] % 128 == 0 and \
+                x_shard.shape[0] * tpctx.world <= tpctx.max_tokens:
+            return tpctx.allgather_linear(x_shard.contiguous(), w, bias)
+        return torch.nn.functional.linear(_all_gather_rows(x_shard, group), w, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_shard, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = _reduce_scatter_rows(_dgrad(dy, w), ctx.group)
+        dw = _wgrad(dy, _all_gather_rows(x_shard, ctx.group), w) if ctx.needs_input_grad[1] else None
+        db = None
+        b = ctx.bias_ref
+        if b is not None and ctx.needs_input_grad[2]:
+            bsum = dy.float().sum(0)
+            mg = getattr(b, "main_grad", None)
+            if mg is not None:
+                mg.add_(bsum.to(mg.dtype))
+            else:
+                db = bsum.to(b.dtype)
+        return dx, dw, db, None, None
+
+
+class _LinearReduceScatter(torch.autograd.Function):
+    """y_shard [T/tp, out] = reduce_scatter(x @ wᵀ) with x [T, in_local], w [out, in_local]."""
+
+    @staticmethod
+    def forward(ctx, x, w, group, tpctx):
+        ctx.save_for_backward(x, w)
+        ctx.group = group
+        if tpctx is not None and fused_comm_enabled() and x.is_cuda and x.shape[0] % tpctx.world == 0 and w.shape[0] % 32 == 0 and \
+                (x.shape[0] // tpctx.world) * w.shape[0] <= tpctx.slot_elems:
+            return tpctx.gemm_reduce_scatter(x.contiguous(), w)
+        return _reduce_scatter_rows(torch.nn.functional.linear(x, w), group)
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        x, w = ctx.saved_tensors
+        dy = _all_gather_rows(dy_shard.contiguous(), ctx.group)
+        dx = _dgrad(dy, w) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(dy, x, w) if ctx.needs_input_grad[1] else None
+        return dx, dw, None, None
+
+
+def allgather_linear(x_shard, w, bias, group, tpctx=None):
+    return _AllGatherLinear.apply(x_shard, w, bias, group, tpctx)
+
+
+def linear_reduce_scatter(x, w, group, tpctx=None):
+    return _LinearReduceScatter.apply(x, w, group, tpctx)

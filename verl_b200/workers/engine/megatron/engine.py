@@ -54,6 +54,9 @@ class MegatronEngine(FSDPEngine):
         super().__init__(model_config, engine_config, optimizer_config, checkpoint_config)
         ec = self.engine_config
         self.tp_size = int(cfg_get(ec, "tensor_model_parallel_size", 1) or 1)
+        # Megatron sequence parallelism: token-sharded stream between the TP regions, all-gather / reduce-scatter fused
+        # into the projections. Off unless asked for (the reference's megatron.yaml turns it on by default).
+        self.tp_sp = bool(cfg_get(ec, "sequence_parallel", False)) and self.tp_size > 1
         self.pp_size = int(cfg_get(ec, "pipeline_model_parallel_size", 1) or 1)
         for key in ("context_parallel_size", "expert_model_parallel_size", "virtual_pipeline_model_parallel_size"):
             v = cfg_get(ec, key, None)
@@ -122,7 +125,14 @@ class MegatronEngine(FSDPEngine):
                     p.copy_(shard_param(g, full_params[g], cfg, self.tp_rank, tp))
             del full, full_params
             if tp > 1:
-                self.model.set_tp_group(self.tp_group, self.tp_rank * self.local_cfg.vocab_size)
+                tp_ctx = None
+                if self.tp_sp and self.device.type == "cuda":
+                    from verl_b200.parallel.tp import TPContext, fused_comm_enabled
+
+                    if fused_comm_enabled():
+                        max_tok = int(cfg_get(self.engine_config, "sequence_parallel_max_tokens", 32768))
+                        tp_ctx = TPContext(self.tp_group, self._tp_host_group(), max_tokens=max_tok, hidden=cfg.hidden_size, max_out=cfg.hidden_size)
+                self.model.set_tp_group(self.tp_group, self.tp_rank * self.local_cfg.vocab_size, sequence_parallel=self.tp_sp, tp_ctx=tp_ctx)
         self.model.gradient_checkpointing = bool(cfg_get(self.model_config, "enable_gradient_checkpointing", False))
         self.store = FlatParamStore(self.model, self.dp_size, self.dp_rank)
         if self.dp_size > 1:
@@ -138,6 +148,35 @@ class MegatronEngine(FSDPEngine):
             self.to("cpu", model=True, optimizer=False, grad=False)
         if self._optimizer_offload and not self.forward_only:
             self.to("cpu", model=False, optimizer=True, grad=True)
+
+    def _tp_host_group(self):
+        """gloo twin of this rank's TP group (pointer tables of the symmetric buffers travel through host memory)."""
+        if getattr(self, "_tp_host", None) is None:
+            tp = self.tp_size
+            self._tp_host, _ = None, None
+            for b in range(0, self.world, tp):
+                g = dist.new_group(list(range(b, b + tp)), backend="gloo")
+                if b <= self.rank < b + tp:
+                    self._tp_host = g
+        return self._tp_host
+
+    def _pack(self, mb: dict):
+        pb, labels = super()._pack(mb)
+        if not self.tp_sp:
+            return pb, labels
+        # the token axis is split over the TP ranks: round the packed length up with one dummy sequence
+        from verl_b200.models.transformer import PackedBatch
+
+        T = pb.input_ids.shape[0]
+        pad = (-T) % self.tp_size
+        if pad == 0:
+            return pb, labels
+        dev = pb.input_ids.device
+        ids = torch.cat([pb.input_ids, torch.zeros(pad, dtype=pb.input_ids.dtype, device=dev)])
+        pos = torch.cat([pb.position_ids, torch.arange(pad, dtype=pb.position_ids.dtype, device=dev)])
+        cu_cpu = torch.cat([pb.cu_seqlens_cpu, torch.tensor([T + pad], dtype=pb.cu_seqlens_cpu.dtype)])
+        lab = torch.cat([labels, torch.zeros(pad, dtype=labels.dtype, device=dev)])
+        return PackedBatch(ids, pos, cu_cpu.to(dev), cu_cpu, max(pb.max_seqlen, pad), pb.routed_experts), lab
 
     def _replicated_ranges(self) -> list[tuple[int, int, float]]:
         """(start, stop, weight) ranges of the flat buffer whose squared gradient must be down-weighted in the global
@@ -238,6 +277,8 @@ class MegatronEngine(FSDPEngine):
 
         H = self.cfg.hidden_size
         ntoks = [int(seq_lens[torch.as_tensor(ix, device=seq_lens.device)].sum()) for ix in mb_indices]
+        if self.tp_sp:      # stage boundaries carry this rank's 1/tp of the (padded) tokens
+            ntoks = [-(-t // self.tp_size) for t in ntoks]
         m = len(mb_indices)
         outputs: dict[str, list[torch.Tensor]] = {}
         metrics: dict[str, Metric] = {}
@@ -333,6 +374,12 @@ class MegatronEngine(FSDPEngine):
         if self.tp_size > 1 and self.cfg.is_moe:
             for layer in self.model.layers:
                 dist.all_reduce(layer.mlp.router.main_grad, group=self.tp_group)
+        if self.tp_sp:
+            # norms see a different token slice on every TP rank: their gradients are partial sums
+            for name, p in self.model.named_parameters():
+                if tp_rule(local_to_global_name(name, self.model.layer_offset), self.cfg) is None and getattr(p, "main_grad", None) is not None \
+                        and not name.endswith("router"):
+                    dist.all_reduce(p.main_grad, group=self.tp_group)
         if self.pp_size > 1 and self.cfg.tie_word_embeddings and not self.cfg.value_head and (self.is_first or self.is_last):
             dist.all_reduce(self.model.embed_tokens.main_grad, group=self.embed_group)
 
