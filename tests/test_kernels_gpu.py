@@ -237,3 +237,28 @@ def test_gemm_pair_cta_group_2(a_mn, b_mn):
         o.gemm(a, b, acc, bias, a_mn, b_mn, True, 512)
         _ext.check_status("gemm_pair accumulate")
         torch.testing.assert_close(acc, ref + 1.0 + bias.float()[None], rtol=1e-3, atol=2e-2)
+
+
+def test_device_barrier_gives_up_with_a_status_when_the_peer_never_signals():
+    """Failure detection on the device: the barrier of rank 0 in a 2-rank table whose second signal pad nobody ever writes
+    runs into its time limit, records status 5 (peer wait) and returns; the context stays usable and the host-side check
+    turns the status into an exception."""
+    from verl_b200.ops import _ext
+
+    o = _ext.ops()
+    _ext.check_status("before")
+    my_pad = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    absent_peer_pad = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    table = torch.tensor([my_pad.data_ptr(), absent_peer_pad.data_ptr()], dtype=torch.int64)
+    import time
+
+    t0 = time.time()
+    o.symm_barrier(table, 0, 2, 1)
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 1.0 < waited < 10.0, waited                              # gave up after its ~2 s limit instead of spinning forever
+    assert int(absent_peer_pad[0]) == 1 and int(my_pad[0]) == 1     # this rank did announce itself to both pads
+    with pytest.raises(RuntimeError, match="status 5"):
+        _ext.check_status("barrier without a peer")
+    _ext.check_status("status word was cleared by the failed check")
+    assert float(torch.ones(8, device="cuda").sum()) == 8.0         # the context is still usable

@@ -25,75 +25,88 @@ __device__ __forceinline__ void store8(bf16* p, const float* f) {
 }
 
 // ------------------------------------------------------------------ RMSNorm forward
-// One warp per row. y = (x [+ res]) * rstd * w ; optionally writes the summed residual stream and rstd.
-template <int MAXV>
-__global__ void __launch_bounds__(128) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
-                                                          const bf16* __restrict__ w, bf16* __restrict__ y,
-                                                          bf16* __restrict__ res_out, float* __restrict__ rstd_out,
-                                                          int T, int H, float eps) {
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (row >= T) return;
-  const int lane = threadIdx.x & 31;
-  const int nv = H / 8;  // 8-element vectors per row
-  const bf16* xr = x + (size_t)row * H;
-  float buf[MAXV][8];
+// One CTA per row, VPT 8-element vectors per thread (VPT = 1 up to H = 8192), so a row lives in 8 registers per thread
+// and an SM keeps ~50 warps of loads in flight. y = (x [+ res]) * rstd * w ; optionally writes the summed residual
+// stream and rstd.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = lane < nw ? red[lane] : 0.f;
+  r = warp_sum(r);
+  __syncthreads();
+  return r;
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(1024) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
+                                                           const bf16* __restrict__ w, bf16* __restrict__ y,
+                                                           bf16* __restrict__ res_out, float* __restrict__ rstd_out,
+                                                           int T, int H, float eps) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int nv = H / 8;
+  const size_t base = (size_t)row * H;
+  float buf[VPT][8];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    int v = i * 32 + lane;
+  for (int i = 0; i < VPT; ++i) {
+    const int v = i * blockDim.x + threadIdx.x;
     if (v < nv) {
-      load8(xr + v * 8, buf[i]);
+      load8(x + base + v * 8, buf[i]);
       if (res != nullptr) {
         float r[8];
-        load8(res + (size_t)row * H + v * 8, r);
+        load8(res + base + v * 8, r);
 #pragma unroll
         for (int j = 0; j < 8; ++j) buf[i][j] += r[j];
         if (res_out != nullptr) {
-          store8(res_out + (size_t)row * H + v * 8, buf[i]);
-          // the normalised value must be computed from the rounded residual stream to match a two-op reference
-          load8(res_out + (size_t)row * H + v * 8, buf[i]);
+          store8(res_out + base + v * 8, buf[i]);
+          // the normalised value is computed from the ROUNDED residual stream, as a two-op formulation would
+#pragma unroll
+          for (int j = 0; j < 8; ++j) buf[i][j] = __bfloat162float(__float2bfloat16(buf[i][j]));
         }
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) ss += buf[i][j] * buf[i][j];
     }
   }
-  ss = warp_sum(ss);
+  ss = block_sum(ss, red);
   const float rstd = rsqrtf(ss / (float)H + eps);
-  if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+  if (threadIdx.x == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    int v = i * 32 + lane;
+  for (int i = 0; i < VPT; ++i) {
+    const int v = i * blockDim.x + threadIdx.x;
     if (v < nv) {
       float wv[8], o[8];
       load8(w + v * 8, wv);
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = buf[i][j] * rstd * wv[j];
-      store8(y + (size_t)row * H + v * 8, o);
+      store8(y + base + v * 8, o);
     }
   }
 }
 
 // ------------------------------------------------------------------ RMSNorm backward (dx) ; dw by column-sum kernel
 // dx = rstd * (dy*w) - x * rstd^3/H * sum(dy*w*x)  (+ dres_in if the residual stream also carries gradient)
-template <int MAXV>
-__global__ void __launch_bounds__(128) rmsnorm_bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
-                                                             const bf16* __restrict__ w, const float* __restrict__ rstd,
-                                                             const bf16* __restrict__ dres, bf16* __restrict__ dx, int T,
-                                                             int H) {
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (row >= T) return;
-  const int lane = threadIdx.x & 31;
+template <int VPT>
+__global__ void __launch_bounds__(1024) rmsnorm_bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                              const bf16* __restrict__ w, const float* __restrict__ rstd,
+                                                              const bf16* __restrict__ dres, bf16* __restrict__ dx, int T,
+                                                              int H) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
   const int nv = H / 8;
-  float xb[MAXV][8], gb[MAXV][8];
+  const size_t base = (size_t)row * H;
+  float xb[VPT][8], gb[VPT][8];
   float dot = 0.f;
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    int v = i * 32 + lane;
+  for (int i = 0; i < VPT; ++i) {
+    const int v = i * blockDim.x + threadIdx.x;
     if (v < nv) {
       float wv[8];
-      load8(x + (size_t)row * H + v * 8, xb[i]);
-      load8(dy + (size_t)row * H + v * 8, gb[i]);
+      load8(x + base + v * 8, xb[i]);
+      load8(dy + base + v * 8, gb[i]);
       load8(w + v * 8, wv);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -102,23 +115,23 @@ __global__ void __launch_bounds__(128) rmsnorm_bwd_dx_kernel(const bf16* __restr
       }
     }
   }
-  dot = warp_sum(dot);
+  dot = block_sum(dot, red);
   const float r = rstd[row];
   const float c = dot * r * r * r / (float)H;
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    int v = i * 32 + lane;
+  for (int i = 0; i < VPT; ++i) {
+    const int v = i * blockDim.x + threadIdx.x;
     if (v < nv) {
       float o[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = gb[i][j] * r - xb[i][j] * c;
       if (dres != nullptr) {
         float d[8];
-        load8(dres + (size_t)row * H + v * 8, d);
+        load8(dres + base + v * 8, d);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] += d[j];
       }
-      store8(dx + (size_t)row * H + v * 8, o);
+      store8(dx + base + v * 8, o);
     }
   }
 }
@@ -295,28 +308,106 @@ static inline int grid_for(long n, int block) {
 
 using namespace vb;
 
-template <int MAXV>
-static void launch_rms_fwd(const void* x, const void* res, const void* w, void* y, void* res_out, float* rstd, int T,
-                           int H, float eps, cudaStream_t st) {
-  rmsnorm_fwd_kernel<MAXV><<<(T + 3) / 4, 128, 0, st>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y,
-                                                        (bf16*)res_out, rstd, T, H, eps);
-}
-template <int MAXV>
-static void launch_rms_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
-                           int T, int H, cudaStream_t st) {
-  rmsnorm_bwd_dx_kernel<MAXV><<<(T + 3) / 4, 128, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
-                                                           (const bf16*)dres, (bf16*)dx, T, H);
+// Rows of at most 256 elements (per-head q/k norms): one warp per row, eight rows per CTA.
+__global__ void __launch_bounds__(256) rmsnorm_fwd_small_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
+                                                                const bf16* __restrict__ w, bf16* __restrict__ y,
+                                                                bf16* __restrict__ res_out, float* __restrict__ rstd_out,
+                                                                int T, int H, float eps) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const int lane = threadIdx.x & 31, nv = H / 8;
+  const size_t base = (size_t)row * H;
+  float b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  float ss = 0.f;
+  if (lane < nv) {
+    load8(x + base + lane * 8, b);
+    if (res != nullptr) {
+      float r[8];
+      load8(res + base + lane * 8, r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) b[j] += r[j];
+      if (res_out != nullptr) {
+        store8(res_out + base + lane * 8, b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) b[j] = __bfloat162float(__float2bfloat16(b[j]));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += b[j] * b[j];
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / (float)H + eps);
+  if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+  if (lane < nv) {
+    float wv[8], o[8];
+    load8(w + lane * 8, wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = b[j] * rstd * wv[j];
+    store8(y + base + lane * 8, o);
+  }
 }
 
-// rows are held in registers: MAXV vectors of 8 per lane; pick the smallest instantiation that covers H
+__global__ void __launch_bounds__(256) rmsnorm_bwd_dx_small_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                                   const bf16* __restrict__ w, const float* __restrict__ rstd,
+                                                                   const bf16* __restrict__ dres, bf16* __restrict__ dx, int T, int H) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const int lane = threadIdx.x & 31, nv = H / 8;
+  const size_t base = (size_t)row * H;
+  float xb[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  float dot = 0.f;
+  if (lane < nv) {
+    float wv[8];
+    load8(x + base + lane * 8, xb);
+    load8(dy + base + lane * 8, gb);
+    load8(w + lane * 8, wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      gb[j] *= wv[j];
+      dot += gb[j] * xb[j];
+    }
+  }
+  dot = warp_sum(dot);
+  const float r = rstd[row];
+  const float c = dot * r * r * r / (float)H;
+  if (lane < nv) {
+    float o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = gb[j] * r - xb[j] * c;
+    if (dres != nullptr) {
+      float d[8];
+      load8(dres + base + lane * 8, d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] += d[j];
+    }
+    store8(dx + base + lane * 8, o);
+  }
+}
+
+static int rms_threads(int H, int vpt) {
+  int t = ((H / 8 + vpt - 1) / vpt + 31) / 32 * 32;
+  return t < 32 ? 32 : t;
+}
+template <int VPT>
+static void launch_rms_fwd(const void* x, const void* res, const void* w, void* y, void* res_out, float* rstd, int T,
+                           int H, float eps, cudaStream_t st) {
+  rmsnorm_fwd_kernel<VPT><<<T, rms_threads(H, VPT), 0, st>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y,
+                                                            (bf16*)res_out, rstd, T, H, eps);
+}
+template <int VPT>
+static void launch_rms_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                           int T, int H, cudaStream_t st) {
+  rmsnorm_bwd_dx_kernel<VPT><<<T, rms_threads(H, VPT), 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
+                                                               (const bf16*)dres, (bf16*)dx, T, H);
+}
+
+// a row is spread over one CTA: VPT vectors of 8 elements per thread, at most 1024 threads
 #define VB_DISPATCH_MAXV(H, FN, ...)                     \
   do {                                                   \
-    int nv_ = ((H) / 8 + 31) / 32;                       \
-    if (nv_ <= 2) FN<2>(__VA_ARGS__);                    \
-    else if (nv_ <= 8) FN<8>(__VA_ARGS__);               \
-    else if (nv_ <= 14) FN<14>(__VA_ARGS__);             \
-    else if (nv_ <= 16) FN<16>(__VA_ARGS__);             \
-    else if (nv_ <= 32) FN<32>(__VA_ARGS__);             \
+    int nv_ = (H) / 8;                                   \
+    if (nv_ <= 1024) FN<1>(__VA_ARGS__);                 \
+    else if (nv_ <= 2048) FN<2>(__VA_ARGS__);            \
+    else if (nv_ <= 4096) FN<4>(__VA_ARGS__);            \
     else return -1;                                      \
   } while (0)
 
@@ -324,6 +415,10 @@ extern "C" int vb_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
                               int H, float eps, cudaStream_t st) {
   if (H % 8) return -2;
   if (T == 0) return 0;
+  if (H <= 256) {
+    rmsnorm_fwd_small_kernel<<<(T + 7) / 8, 256, 0, st>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y, (bf16*)res_out, rstd, T, H, eps);
+    return 0;
+  }
   VB_DISPATCH_MAXV(H, launch_rms_fwd, x, res, w, y, res_out, rstd, T, H, eps, st);
   return 0;
 }
@@ -332,7 +427,11 @@ extern "C" int vb_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
                               float* dw, int T, int H, cudaStream_t st) {
   if (H % 8) return -2;
   if (T == 0) return 0;
-  VB_DISPATCH_MAXV(H, launch_rms_bwd, dy, x, w, rstd, dres, dx, T, H, st);
+  if (H <= 256) {
+    rmsnorm_bwd_dx_small_kernel<<<(T + 7) / 8, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, (bf16*)dx, T, H);
+  } else {
+    VB_DISPATCH_MAXV(H, launch_rms_bwd, dy, x, w, rstd, dres, dx, T, H, st);
+  }
   if (dw != nullptr) {
     int rows_per_block = 512;
     dim3 grid((H / 8 + 31) / 32, (T + rows_per_block - 1) / rows_per_block);
