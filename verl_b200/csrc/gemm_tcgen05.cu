@@ -60,6 +60,11 @@ struct DistArgs {
   //                 tmB is a 3-D map whose outermost coordinate is the expert.
   //   group_mode 2: C[e][M, N] (+)= A[rows_e, M]^T * B[rows_e, N] over the rows of expert e (weight gradient);
   //                 expert_rng[e] = (first block, end block); the tile index runs over (expert, m block, n block).
+  // Signalled all-reduce (EPI_PEER, rows_per_owner == 0): instead of a separate barrier launch, the LAST CTA of the GEMM
+  // advances this rank's epoch (sig_local[0]) and stores it into every peer's flag word for this rank; the slot-sum kernel
+  // waits for the peers' flags. Slots are double buffered by epoch parity, so no second barrier is needed.
+  int* sig_local;                    // [0] epoch, [1] finished-CTA counter, [SIG_FLAGS + p] flag written by rank p
+  int* sig_peer[MAX_TP];
   int group_mode;
   int num_experts;
   const int* blk_expert;
@@ -75,6 +80,7 @@ struct DistArgs {
 };
 
 constexpr int STAGE_PARTS = 8;
+constexpr int SIG_FLAGS = 16;
 
 __device__ __forceinline__ bool stage_wait(const int* flag, int epoch, volatile int* abort_flag, int* err_word) {
   epoch *= STAGE_PARTS;
@@ -165,6 +171,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // signalled all-reduce: the slot buffer of this call is chosen by the parity of the epoch BEFORE this launch
+  const long sig_slot_off = (dist.sig_local != nullptr) ? (long)(dist.sig_local[0] & 1) * dist.world * dist.slot_elems : 0;
 
   // Tile order: groups of GROUP_M row-blocks sweep N together so a B column block stays in L2.
   constexpr int GROUP_M = 8;
@@ -536,7 +544,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               continue;
             }
             for (int r = r_lo; r < r_hi; ++r) {
-              bf16* dst = reinterpret_cast<bf16*>(dist.peer_out[r]) + dist.rank * dist.slot_elems + row_local * ldc + col0;
+              bf16* dst = reinterpret_cast<bf16*>(dist.peer_out[r]) + sig_slot_off + dist.rank * dist.slot_elems + row_local * ldc + col0;
 #pragma unroll
               for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = o[j];
             }
@@ -626,8 +634,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 
   // ------------------------------------------------------------ teardown
+  if (EPI == EPI_PEER && dist.sig_local != nullptr) __threadfence_system();   // this thread's peer stores before the signal
   tc_fence_before();
   __syncthreads();
+  if (EPI == EPI_PEER && dist.sig_local != nullptr && threadIdx.x == 0) {
+    const int done = atomicAdd(dist.sig_local + 1, 1);
+    if (done == (int)gridDim.x - 1) {                 // every CTA of this launch has published its tiles
+      dist.sig_local[1] = 0;
+      const int e = dist.sig_local[0] + 1;
+      dist.sig_local[0] = e;
+      __threadfence_system();
+      for (int p = 0; p < dist.world; ++p)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(dist.sig_peer[p] + SIG_FLAGS + dist.rank), "r"(e) : "memory");
+    }
+  }
   if (warp == 1) {
     if (*abort_flag) {
       // A wait was abandoned: give copies and MMAs still in flight time to land before TMEM and the
@@ -890,6 +910,71 @@ extern "C" int vb_lmhead_dlogits(const void* h, const void* W, const long* label
 // GEMMs fused with tensor/data-parallel collectives over NVLink peer memory.
 namespace vb {
 
+// Slot sum of the signalled all-reduce: every block first waits (bounded) until all ranks' flags have reached this rank's
+// epoch, then sums the slot buffer selected by the epoch's parity.
+__global__ void slots_reduce_sig_kernel(const bf16* __restrict__ slots, const int* __restrict__ sig, int world, long slot_elems, long rows,
+                                        int cols, int ld, const bf16* __restrict__ residual, bf16* __restrict__ out, int ld_out,
+                                        int* err_word) {
+  __shared__ int ok_s;
+  const int e = sig[0];
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const int* f = sig + SIG_FLAGS + threadIdx.x;
+    uint64_t t0 = 0;
+    uint32_t n = 0;
+    while (true) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if (v >= e) break;
+      if ((++n & 0xFF) == 0) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > VB_WAIT_LIMIT_NS) {
+          atomicCAS(err_word, 0, VB_ERR_WAIT_PEER | (threadIdx.x << 8));
+          ok_s = 0;
+          break;
+        }
+        __nanosleep(100);
+      }
+    }
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  slots += (long)((e - 1) & 1) * world * slot_elems;
+  const int vpr = cols / 8;
+  const long total = rows * vpr;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / vpr;
+    const int c = (i % vpr) * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s2 = 0; s2 < world; ++s2) {
+      const uint4 v = *reinterpret_cast<const uint4*>(slots + s2 * slot_elems + r * ld + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f2 = __bfloat1622float2(h[k]);
+        acc[2 * k] += f2.x;
+        acc[2 * k + 1] += f2.y;
+      }
+    }
+    if (residual != nullptr) {
+      const uint4 v = *reinterpret_cast<const uint4*>(residual + r * ld_out + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f2 = __bfloat1622float2(h[k]);
+        acc[2 * k] += f2.x;
+        acc[2 * k + 1] += f2.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + r * ld_out + c) = o;
+  }
+}
+
 // out[r, c] = sum_s slots[s][r, c] (+ residual[r, c]); bf16 in/out, fp32 accumulation. cols % 8 == 0.
 __global__ void slots_reduce_kernel(const bf16* __restrict__ slots, int world, long slot_elems, long rows, int cols, int ld,
                                     const bf16* __restrict__ residual, bf16* __restrict__ out, int ld_out) {
@@ -1115,6 +1200,37 @@ extern "C" int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int
     if (make_tmap_2d(&d.stage_map, stage, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (M + 127) / 128 * 128, K, K, BM, BK)) return -1;
   }
   return launch_dist<EPI_STORE>(pick_bn_dist(M, N), reinterpret_cast<const void*>(seg_ptrs[0]), B, C, bias, M, N, K, ld_seg, ldb, ldc, err_word, st, d);
+}
+
+// Signalled all-reduce in two launches: this GEMM scatters the partial result into every rank's slot buffer (double
+// buffered by epoch parity; out_ptrs[r] must hold 2 * world * slot_elems elements) and its last CTA signals the peers;
+// vb_slots_reduce_sig then waits for all ranks' signals and sums. sig_ptrs[r] = rank r's signal pad (>= 64 ints, zeroed once).
+extern "C" int vb_gemm_allreduce_sig(const void* A, const void* B, int M, int N, int K, int lda, int ldb, const long* out_ptrs,
+                                     const long* sig_ptrs, int rank, int world, long slot_elems, int* err_word, cudaStream_t st) {
+  using namespace vb;
+  if (world > MAX_TP || (N % 32) != 0) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -4;
+  DistArgs d = {};
+  d.rank = rank; d.world = world; d.rows_per_owner = 0; d.slot_elems = slot_elems;
+  for (int r = 0; r < world; ++r) {
+    d.peer_out[r] = reinterpret_cast<void*>(out_ptrs[r]);
+    d.sig_peer[r] = reinterpret_cast<int*>(sig_ptrs[r]);
+  }
+  d.sig_local = reinterpret_cast<int*>(sig_ptrs[rank]);
+  return launch_dist<EPI_PEER>(pick_bn_dist(M, N), A, B, nullptr, nullptr, M, N, K, lda, ldb, N, err_word, st, d);
+}
+
+extern "C" int vb_slots_reduce_sig(const void* slots, const void* sig, int world, long slot_elems, long rows, int cols, const void* residual,
+                                   void* out, int ld_out, int* err_word, cudaStream_t st) {
+  using namespace vb;
+  if (cols % 8) return -2;
+  long total = rows * (cols / 8);
+  if (total == 0) return 0;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > num_sms() * 4) blocks = num_sms() * 4;
+  slots_reduce_sig_kernel<<<blocks, 256, 0, st>>>((const bf16*)slots, (const int*)sig, world, slot_elems, rows, cols, cols, (const bf16*)residual,
+                                                  (bf16*)out, ld_out, err_word);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 extern "C" int vb_slots_reduce(const void* slots, int world, long slot_elems, long rows, int cols, int ld, const void* residual,

@@ -44,6 +44,12 @@ class TPContext:
         # slots[src_rank][tokens, out] written by peers' GEMM epilogues
         self.slot_elems = max_tokens * max_out
         self.slots = SymmetricBuffer(self.world * self.slot_elems * 2, group, host_group)
+        # signalled all-reduce: double-buffered slots + one signal pad per rank (epoch, CTA counter, per-rank flags)
+        self.slots2 = SymmetricBuffer(2 * self.world * self.slot_elems * 2, group, host_group)
+        self.sig = SymmetricBuffer(256, group, host_group)
+        self.sig.tensor(torch.int32, 64).zero_()
+        torch.cuda.synchronize()
+        self.sig.barrier()
         # local staging of the peers' activation shards (each crosses NVLink once per call) + per-128-row arrival flags
         dev = torch.device("cuda", torch.cuda.current_device())
         self.stage = torch.empty(max_tokens * hidden, dtype=torch.bfloat16, device=dev)
@@ -73,6 +79,12 @@ class TPContext:
     # ------------------------------------------------------------------ GEMM → all-reduce / reduce-scatter
     def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         T, N = x.shape[0], w.shape[0]
+        if fused_comm_enabled() and N % 32 == 0 and T * N <= self.slot_elems and os.environ.get("VERL_B200_ALLREDUCE", "signal") == "signal":
+            # two launches: GEMM whose last CTA signals the peers, then a slot sum that waits for their signals
+            out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+            self.ops.gemm_allreduce_sig(x, w, self.slots2.table(), self.sig.table(), self.rank, self.slot_elems,
+                                        self.slots2.tensor(torch.bfloat16), self.sig.tensor(torch.int32, 64), residual, out)
+            return out
         if fused_comm_enabled() and N % 32 == 0 and T * N <= self.slot_elems:
             out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
             bar = self.slots.barrier_auto if self.graph_safe else self.slots.barrier
