@@ -81,10 +81,11 @@ int vb_gemm_head_scatter(const void* A, const void* B, const void* bias, int M, 
 int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int ld_seg, int rows_total, int row_off, const void* B, int ldb, void* C,
                  const void* bias, int M, int N, int ldc, int rank, void* stage, int* stage_flags, int stage_epoch, int* err_word,
                  cudaStream_t st);
+void vb_allreduce_plan(int M, int N, int K, int* bn, int* split_k);
 int vb_gemm_allreduce_sig(const void* A, const void* B, int M, int N, int K, int lda, int ldb, const long* out_ptrs, const long* sig_ptrs,
-                          int rank, int world, long slot_elems, int* err_word, cudaStream_t st);
-int vb_slots_reduce_sig(const void* slots, const void* sig, int world, long slot_elems, long rows, int cols, const void* residual, void* out,
-                        int ld_out, int* err_word, cudaStream_t st);
+                          int rank, int world, long slot_elems, long half_elems, int bn, int split_k, int* err_word, cudaStream_t st);
+int vb_slots_reduce_sig(const long* slot_ptrs, const void* sig, int rank, int world, int split_k, long slot_elems, long half_elems, long rows,
+                        int cols, const void* residual, void* out, int ld_out, int* err_word, cudaStream_t st);
 int vb_gemm_grouped(const void* A, const void* B, void* C, const int* blk_expert, int R, int N, int K, int E, int lda, int ldc, int b_mn,
                     int* err_word, cudaStream_t stream);
 int vb_gemm_grouped_wgrad(const void* dY, const void* X, void* dW, const void* expert_rng, int R, int M, int N, int E, int ld_dy, int ld_x,

@@ -187,20 +187,29 @@ void gemm_kseg(const Tensor& a_ptrs, int64_t k_per_rank, int64_t rows_total, int
 }
 
 // Two-launch all-reduce (see vb_gemm_allreduce_sig): out = sum over ranks of (a_r @ b_r^T) (+ residual)
-void gemm_allreduce_sig(const Tensor& a, const Tensor& b, const Tensor& out_ptrs, const Tensor& sig_ptrs, int64_t rank, int64_t slot_elems,
-                        const Tensor& slots_local, const Tensor& sig_local, const c10::optional<Tensor>& residual, Tensor& out) {
+void gemm_allreduce_sig(const Tensor& a, const Tensor& b, const Tensor& out_ptrs, const Tensor& sig_ptrs, int64_t rank, int64_t half_elems,
+                        const Tensor& slots_local, const Tensor& sig_local, const c10::optional<Tensor>& residual, Tensor& out, int64_t bn,
+                        int64_t split_k, int64_t max_split) {
   TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_allreduce_sig: bad operands");
   TORCH_CHECK(out_ptrs.scalar_type() == at::kLong && !out_ptrs.is_cuda() && sig_ptrs.scalar_type() == at::kLong && !sig_ptrs.is_cuda() &&
                   out_ptrs.numel() == sig_ptrs.numel(), "gemm_allreduce_sig: pointer tables must be CPU int64 tensors of equal length");
   const int M = a.size(0), K = a.size(1), N = b.size(0), world = out_ptrs.numel();
-  TORCH_CHECK((int64_t)M * N <= slot_elems && out.size(0) == M && out.size(1) == N && out.scalar_type() == at::kBFloat16 && out.is_contiguous(), "gemm_allreduce_sig: bad out / slot size");
+  const int64_t slot_elems = (int64_t)M * N;
+  TORCH_CHECK(slot_elems <= half_elems && slots_local.numel() >= 2 * half_elems && out.size(0) == M && out.size(1) == N &&
+                  out.scalar_type() == at::kBFloat16 && out.is_contiguous(), "gemm_allreduce_sig: bad out / slot size");
   const void* res = (residual.has_value() && residual->defined()) ? residual->data_ptr() : nullptr;
   c10::cuda::CUDAGuard guard(a.device());
   int* err = vb_status_tensor(a.get_device()).data_ptr<int>();
+  int pbn = 0, ps = 1;
+  vb_allreduce_plan(M, N, K, &pbn, &ps);
+  if (bn > 0) pbn = (int)bn;
+  if (split_k > 0) ps = (int)split_k;
+  if (ps > max_split) ps = (int)max_split;
+  while (ps > 1 && (int64_t)ps * slot_elems > half_elems) --ps;
   check_rc(vb_gemm_allreduce_sig(a.data_ptr(), b.data_ptr(), M, N, K, (int)a.stride(0), (int)b.stride(0), out_ptrs.data_ptr<long>(), sig_ptrs.data_ptr<long>(),
-                                 (int)rank, world, slot_elems, err, cur_stream()),
+                                 (int)rank, world, slot_elems, half_elems, pbn, ps, err, cur_stream()),
            "gemm_allreduce_sig");
-  check_rc(vb_slots_reduce_sig(slots_local.data_ptr(), sig_local.data_ptr(), world, slot_elems, M, N, res, out.data_ptr(), N, err, cur_stream()),
+  check_rc(vb_slots_reduce_sig(out_ptrs.data_ptr<long>(), sig_local.data_ptr(), (int)rank, world, ps, slot_elems, half_elems, M, N, res, out.data_ptr(), N, err, cur_stream()),
            "slots_reduce_sig");
 }
 
@@ -219,6 +228,6 @@ TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
   m.def("gemm_peer_scatter(Tensor a, Tensor b, Tensor out_ptrs, int rank, int rows_per_owner, int slot_elems) -> ()", &gemm_peer_scatter);
   m.def("gemm_head_scatter(Tensor a, Tensor b, Tensor? bias, Tensor out_ptrs, int ld_out, int row_off, int head_dim, Tensor head_rank, Tensor head_slot) -> ()", &gemm_head_scatter);
   m.def("gemm_kseg(Tensor a_ptrs, int k_per_rank, int rows_total, int row_off, Tensor b, Tensor(a!) out, Tensor? bias, int rank=0, Tensor? stage=None, Tensor? flags=None, int epoch=0) -> ()", &gemm_kseg);
-  m.def("gemm_allreduce_sig(Tensor a, Tensor b, Tensor out_ptrs, Tensor sig_ptrs, int rank, int slot_elems, Tensor slots_local, Tensor sig_local, Tensor? residual, Tensor(a!) out) -> ()", &gemm_allreduce_sig);
+  m.def("gemm_allreduce_sig(Tensor a, Tensor b, Tensor out_ptrs, Tensor sig_ptrs, int rank, int half_elems, Tensor slots_local, Tensor sig_local, Tensor? residual, Tensor(a!) out, int bn=0, int split_k=0, int max_split=8) -> ()", &gemm_allreduce_sig);
   m.def("slots_reduce(Tensor slots, int world, int slot_elems, int rows, int cols, Tensor? residual, Tensor(a!) out) -> ()", &slots_reduce);
 }

@@ -60,9 +60,11 @@ struct DistArgs {
   //                 tmB is a 3-D map whose outermost coordinate is the expert.
   //   group_mode 2: C[e][M, N] (+)= A[rows_e, M]^T * B[rows_e, N] over the rows of expert e (weight gradient);
   //                 expert_rng[e] = (first block, end block); the tile index runs over (expert, m block, n block).
-  // Signalled all-reduce (EPI_PEER, rows_per_owner == 0): instead of a separate barrier launch, the LAST CTA of the GEMM
-  // advances this rank's epoch (sig_local[0]) and stores it into every peer's flag word for this rank; the slot-sum kernel
-  // waits for the peers' flags. Slots are double buffered by epoch parity, so no second barrier is needed.
+  // Signalled all-reduce (EPI_PEER, rows_per_owner == 0): partials stay in this rank's buffer; instead of a separate barrier
+  // launch, the LAST CTA of the GEMM advances this rank's epoch (sig_local[0]) and stores it into every peer's flag word for
+  // this rank; the slot-sum kernel waits for the peers' flags and pulls. Buffers alternate by epoch parity, so a rank can
+  // start its next GEMM while a peer still reads the previous result.
+  long sig_half;                     // elements between the two slot buffers (fixed per context; slot_elems may change per call)
   int* sig_local;                    // [0] epoch, [1] finished-CTA counter, [SIG_FLAGS + p] flag written by rank p
   int* sig_peer[MAX_TP];
   int group_mode;
@@ -172,7 +174,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // signalled all-reduce: the slot buffer of this call is chosen by the parity of the epoch BEFORE this launch
-  const long sig_slot_off = (dist.sig_local != nullptr) ? (long)(dist.sig_local[0] & 1) * dist.world * dist.slot_elems : 0;
+  // (split-K: every K slice of every rank has a slot of its own, summed by the slot-sum kernel)
+  const long sig_slot_off = (dist.sig_local != nullptr) ? (long)(dist.sig_local[0] & 1) * dist.sig_half : 0;
 
   // Tile order: groups of GROUP_M row-blocks sweep N together so a B column block stays in L2.
   constexpr int GROUP_M = 8;
@@ -510,7 +513,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       } else if constexpr (EPI == EPI_PEER) {
         int r_lo = 0, r_hi = dist.world;
         long row_local = row;
-        if (dist.rows_per_owner > 0) {
+        if (dist.sig_local != nullptr) {          // signalled all-reduce: partials stay local, the peers pull them
+          r_lo = dist.rank;
+          r_hi = r_lo + 1;
+        } else if (dist.rows_per_owner > 0) {
           r_lo = row / dist.rows_per_owner;
           r_hi = r_lo + 1;
           row_local = row - (long)r_lo * dist.rows_per_owner;
@@ -544,7 +550,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               continue;
             }
             for (int r = r_lo; r < r_hi; ++r) {
-              bf16* dst = reinterpret_cast<bf16*>(dist.peer_out[r]) + sig_slot_off + dist.rank * dist.slot_elems + row_local * ldc + col0;
+              const long slot = dist.sig_local != nullptr ? (long)(t % split_k) : (long)dist.rank;
+              bf16* dst = reinterpret_cast<bf16*>(dist.peer_out[r]) + sig_slot_off + slot * dist.slot_elems + row_local * ldc + col0;
 #pragma unroll
               for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = o[j];
             }
@@ -634,7 +641,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 
   // ------------------------------------------------------------ teardown
-  if (EPI == EPI_PEER && dist.sig_local != nullptr) __threadfence_system();   // this thread's peer stores before the signal
+  if (EPI == EPI_PEER && dist.sig_local != nullptr) __threadfence_system();   // this thread's partials visible to the peers before the signal
   tc_fence_before();
   __syncthreads();
   if (EPI == EPI_PEER && dist.sig_local != nullptr && threadIdx.x == 0) {
@@ -730,13 +737,13 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   if (split_k < 1) split_k = 1;
   int kb_per = (num_kb + split_k - 1) / split_k;
   split_k = (num_kb + kb_per - 1) / kb_per;          // no empty slices
-  if (split_k > 1 && split_ws == nullptr) return -6;
+  if (split_k > 1 && split_ws == nullptr && EPI != EPI_PEER) return -6;
   int units = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * split_k;
   int grid = units < num_sms() ? units : num_sms();
   kern<<<grid, 192 + 32 * COPY_WARPS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags,
                                                 err_word, epi, split_k, kb_per, split_ws, dist);
   if (cudaGetLastError() != cudaSuccess) return -11;
-  if (split_k > 1) {
+  if (split_k > 1 && EPI != EPI_PEER) {
     long total4 = (long)M * N / 4;
     int blocks = (int)((total4 + 255) / 256);
     if (blocks > num_sms() * 8) blocks = num_sms() * 8;
@@ -910,11 +917,16 @@ extern "C" int vb_lmhead_dlogits(const void* h, const void* W, const long* label
 // GEMMs fused with tensor/data-parallel collectives over NVLink peer memory.
 namespace vb {
 
-// Slot sum of the signalled all-reduce: every block first waits (bounded) until all ranks' flags have reached this rank's
-// epoch, then sums the slot buffer selected by the epoch's parity.
-__global__ void slots_reduce_sig_kernel(const bf16* __restrict__ slots, const int* __restrict__ sig, int world, long slot_elems, long rows,
-                                        int cols, int ld, const bf16* __restrict__ residual, bf16* __restrict__ out, int ld_out,
-                                        int* err_word) {
+// Slot sum of the signalled all-reduce (one-shot, pull): every block first waits (bounded) until all ranks' flags have
+// reached this rank's epoch, then reads every rank's K-slice partials straight from that rank's memory (coalesced 16-byte
+// loads over NVLink) and sums them in fp32. The buffer half is selected by the epoch's parity.
+struct PeerSlots {
+  const bf16* p[MAX_TP];
+};
+
+__global__ void slots_reduce_sig_kernel(const PeerSlots peers, const int* __restrict__ sig, int rank, int world, int split_k, long slot_elems,
+                                        long half_elems, long rows, int cols, const bf16* __restrict__ residual, bf16* __restrict__ out,
+                                        int ld_out, int* err_word) {
   __shared__ int ok_s;
   const int e = sig[0];
   if (threadIdx.x == 0) ok_s = 1;
@@ -941,21 +953,25 @@ __global__ void slots_reduce_sig_kernel(const bf16* __restrict__ slots, const in
   }
   __syncthreads();
   if (!ok_s) return;
-  slots += (long)((e - 1) & 1) * world * slot_elems;
+  const long base = (long)((e - 1) & 1) * half_elems;
   const int vpr = cols / 8;
   const long total = rows * vpr;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
     const long r = i / vpr;
     const int c = (i % vpr) * 8;
+    const long off = base + r * cols + c;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int s2 = 0; s2 < world; ++s2) {
-      const uint4 v = *reinterpret_cast<const uint4*>(slots + s2 * slot_elems + r * ld + c);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    for (int q = 0; q < world; ++q) {
+      const bf16* src = peers.p[(rank + q) % world] + off;        // own partial first while the remote loads are in flight
+      for (int s2 = 0; s2 < split_k; ++s2) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src + s2 * slot_elems);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f2 = __bfloat1622float2(h[k]);
-        acc[2 * k] += f2.x;
-        acc[2 * k + 1] += f2.y;
+        for (int k = 0; k < 4; ++k) {
+          const float2 f2 = __bfloat1622float2(h[k]);
+          acc[2 * k] += f2.x;
+          acc[2 * k + 1] += f2.y;
+        }
       }
     }
     if (residual != nullptr) {
@@ -1013,7 +1029,7 @@ __global__ void slots_reduce_kernel(const bf16* __restrict__ slots, int world, l
 
 template <int EPI>
 static int launch_dist(int bn, const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb, int ldc,
-                       int* err_word, cudaStream_t st, const DistArgs& d) {
+                       int* err_word, cudaStream_t st, const DistArgs& d, int split_k = 1) {
   if constexpr (EPI == EPI_STORE) {
     if (d.stage != nullptr) {
       switch (bn) {
@@ -1024,10 +1040,11 @@ static int launch_dist(int bn, const void* A, const void* B, void* C, const void
       }
     }
   }
+  if (EPI != EPI_PEER) split_k = 1;
   switch (bn) {
-    case 256: return launch_gemm<256, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
-    case 128: return launch_gemm<128, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
-    case 64: return launch_gemm<64, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
+    case 256: return launch_gemm<256, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, split_k, nullptr, &d);
+    case 128: return launch_gemm<128, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, split_k, nullptr, &d);
+    case 64: return launch_gemm<64, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, split_k, nullptr, &d);
     default: return -5;
   }
 }
@@ -1202,11 +1219,37 @@ extern "C" int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int
   return launch_dist<EPI_STORE>(pick_bn_dist(M, N), reinterpret_cast<const void*>(seg_ptrs[0]), B, C, bias, M, N, K, ld_seg, ldb, ldc, err_word, st, d);
 }
 
-// Signalled all-reduce in two launches: this GEMM scatters the partial result into every rank's slot buffer (double
-// buffered by epoch parity; out_ptrs[r] must hold 2 * world * slot_elems elements) and its last CTA signals the peers;
-// vb_slots_reduce_sig then waits for all ranks' signals and sums. sig_ptrs[r] = rank r's signal pad (>= 64 ints, zeroed once).
+// Signalled all-reduce in two launches: this GEMM writes its partial result (per K slice) into this rank's own symmetric
+// buffer and its last CTA stores the new epoch into every peer's flag word; vb_slots_reduce_sig then waits for all ranks'
+// flags, pulls their partials over NVLink and sums. sig_ptrs[r] = rank r's signal pad (>= 64 ints, zeroed once).
+// K slice s of buffer half `parity` starts at parity * half_elems + s * slot_elems in this rank's OWN buffer (the slot sum
+// pulls the peers' slices), so out_ptrs[r] must hold 2 * half_elems elements and split_k * slot_elems <= half_elems.
+extern "C" void vb_allreduce_plan(int M, int N, int K, int* bn, int* split_k) {
+  using namespace vb;
+  // decode-sized M leaves few output tiles: slice K until (nearly) every SM streams its share of the weight
+  const int num_m = (M + BM - 1) / BM;
+  int best_bn = 128, best_s = 1;
+  double best = 1e30;
+  for (int b : {64, 128, 256}) {
+    const int tiles = num_m * ((N + b - 1) / b);
+    for (int s2 = 1; s2 <= 8; ++s2) {
+      const int num_kb = (K + BK - 1) / BK;
+      if (num_kb / s2 < 8) break;
+      const int units = tiles * s2;
+      const int waves = (units + num_sms() - 1) / num_sms();
+      // per-unit cost: bytes staged through one SM (≈ 100 GB/s per SM) + fixed prologue/epilogue; slot traffic grows with s
+      const double bytes = (double)(BM + b) * 2.0 * ((K + s2 - 1) / s2);
+      const double t = waves * (bytes / 100e3 + 4.0) + 1.5 * s2;       // microseconds
+      if (t < best) { best = t; best_bn = b; best_s = s2; }
+    }
+  }
+  *bn = best_bn;
+  *split_k = best_s;
+}
+
 extern "C" int vb_gemm_allreduce_sig(const void* A, const void* B, int M, int N, int K, int lda, int ldb, const long* out_ptrs,
-                                     const long* sig_ptrs, int rank, int world, long slot_elems, int* err_word, cudaStream_t st) {
+                                     const long* sig_ptrs, int rank, int world, long slot_elems, long half_elems, int bn, int split_k,
+                                     int* err_word, cudaStream_t st) {
   using namespace vb;
   if (world > MAX_TP || (N % 32) != 0) return -2;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -4;
@@ -1217,19 +1260,23 @@ extern "C" int vb_gemm_allreduce_sig(const void* A, const void* B, int M, int N,
     d.sig_peer[r] = reinterpret_cast<int*>(sig_ptrs[r]);
   }
   d.sig_local = reinterpret_cast<int*>(sig_ptrs[rank]);
-  return launch_dist<EPI_PEER>(pick_bn_dist(M, N), A, B, nullptr, nullptr, M, N, K, lda, ldb, N, err_word, st, d);
+  d.sig_half = half_elems;
+  if ((long)split_k * slot_elems > half_elems) return -2;
+  return launch_dist<EPI_PEER>(bn, A, B, nullptr, nullptr, M, N, K, lda, ldb, N, err_word, st, d, split_k);
 }
 
-extern "C" int vb_slots_reduce_sig(const void* slots, const void* sig, int world, long slot_elems, long rows, int cols, const void* residual,
-                                   void* out, int ld_out, int* err_word, cudaStream_t st) {
+extern "C" int vb_slots_reduce_sig(const long* slot_ptrs, const void* sig, int rank, int world, int split_k, long slot_elems, long half_elems,
+                                   long rows, int cols, const void* residual, void* out, int ld_out, int* err_word, cudaStream_t st) {
   using namespace vb;
-  if (cols % 8) return -2;
+  if (cols % 8 || world > MAX_TP) return -2;
   long total = rows * (cols / 8);
   if (total == 0) return 0;
+  PeerSlots ps = {};
+  for (int r = 0; r < world; ++r) ps.p[r] = reinterpret_cast<const bf16*>(slot_ptrs[r]);
   int blocks = (int)((total + 255) / 256);
   if (blocks > num_sms() * 4) blocks = num_sms() * 4;
-  slots_reduce_sig_kernel<<<blocks, 256, 0, st>>>((const bf16*)slots, (const int*)sig, world, slot_elems, rows, cols, cols, (const bf16*)residual,
-                                                  (bf16*)out, ld_out, err_word);
+  slots_reduce_sig_kernel<<<blocks, 256, 0, st>>>(ps, (const int*)sig, rank, world, split_k, slot_elems, half_elems, rows, cols,
+                                                  (const bf16*)residual, (bf16*)out, ld_out, err_word);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

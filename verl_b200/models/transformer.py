@@ -29,7 +29,8 @@ __all__ = ["DecoderLM", "PackedBatch", "hf_to_native_state_dict", "native_to_hf_
 class PackedBatch:
     """Device-side description of a packed micro-batch."""
 
-    __slots__ = ("input_ids", "position_ids", "cu_seqlens", "cu_seqlens_cpu", "max_seqlen", "routed_experts", "global_position_ids")
+    __slots__ = ("input_ids", "position_ids", "cu_seqlens", "cu_seqlens_cpu", "max_seqlen", "routed_experts", "global_position_ids",
+                 "attn_expand")
 
     def __init__(self, input_ids, position_ids, cu_seqlens, cu_seqlens_cpu=None, max_seqlen=None, routed_experts=None):
         self.input_ids = input_ids
@@ -42,6 +43,10 @@ class PackedBatch:
         # sequence parallelism: input_ids / position_ids are this rank's slice, cu_seqlens describe the whole micro-batch and
         # this holds the (padded) positions of all its tokens
         self.global_position_ids = None
+        # prefix sharing: (expand [E], back [T]) int64 index tensors. input_ids / position_ids then hold every distinct prompt
+        # once; cu_seqlens describe the E-row layout of full sequences that attention runs on (rows = x[expand]) and
+        # back picks, for each of the T stored tokens, its row of that layout (see verl_b200.utils.prefix_sharing)
+        self.attn_expand = None
 
 
 def _proj(mod: nn.Module, name: str, x: torch.Tensor, bias=None) -> torch.Tensor:
@@ -90,6 +95,10 @@ class Attention(nn.Module):
             from verl_b200.parallel.ulysses import ulysses_attention
 
             o = ulysses_attention(qkv, pb, cfg, sp_group)
+        elif pb.attn_expand is not None:
+            expand, back = pb.attn_expand
+            o = ops.attention_varlen(qkv.index_select(0, expand), pb.cu_seqlens, cfg.num_attention_heads, cfg.num_key_value_heads,
+                                     cfg.head_dim, pb.max_seqlen, pb.cu_seqlens_cpu).index_select(0, back)
         else:
             o = ops.attention_varlen(qkv, pb.cu_seqlens, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                                      pb.max_seqlen, pb.cu_seqlens_cpu)

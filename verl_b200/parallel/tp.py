@@ -45,7 +45,9 @@ class TPContext:
         self.slot_elems = max_tokens * max_out
         self.slots = SymmetricBuffer(self.world * self.slot_elems * 2, group, host_group)
         # signalled all-reduce: double-buffered slots + one signal pad per rank (epoch, CTA counter, per-rank flags)
-        self.slots2 = SymmetricBuffer(2 * self.world * self.slot_elems * 2, group, host_group)
+        # (decode-sized calls slice K; every slice of every rank then owns a slot of tokens x out elements inside one half)
+        self.half_elems = self.world * self.slot_elems
+        self.slots2 = SymmetricBuffer(2 * self.half_elems * 2, group, host_group)
         self.sig = SymmetricBuffer(256, group, host_group)
         self.sig.tensor(torch.int32, 64).zero_()
         torch.cuda.synchronize()
@@ -82,8 +84,9 @@ class TPContext:
         if fused_comm_enabled() and N % 32 == 0 and T * N <= self.slot_elems and os.environ.get("VERL_B200_ALLREDUCE", "signal") == "signal":
             # two launches: GEMM whose last CTA signals the peers, then a slot sum that waits for their signals
             out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
-            self.ops.gemm_allreduce_sig(x, w, self.slots2.table(), self.sig.table(), self.rank, self.slot_elems,
-                                        self.slots2.tensor(torch.bfloat16), self.sig.tensor(torch.int32, 64), residual, out)
+            self.ops.gemm_allreduce_sig(x, w, self.slots2.table(), self.sig.table(), self.rank, self.half_elems,
+                                        self.slots2.tensor(torch.bfloat16), self.sig.tensor(torch.int32, 64), residual, out,
+                                        int(os.environ.get("VERL_B200_AR_BN", 0)), int(os.environ.get("VERL_B200_AR_SPLIT", 0)))
             return out
         if fused_comm_enabled() and N % 32 == 0 and T * N <= self.slot_elems:
             out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)

@@ -241,6 +241,21 @@ class PPOTrainer:
         world = self.actor_rollout_wg.world_size
         if world <= 1 or len(batch) % world != 0:
             return
+        uid = batch.non_tensor_batch.get("uid") if _g(self.config, "actor_rollout_ref.actor.use_prefix_grouper", False) else None
+        if uid is not None:
+            # prefix sharing: the samples of one prompt stay on one rank (reference: group-level balancing,
+            # verl/trainer/ppo/ray_trainer.py:1185-1240); whole groups are balanced instead of single samples
+            groups: dict = {}
+            for i, u in enumerate(uid.tolist()):
+                groups.setdefault(u, []).append(i)
+            members = list(groups.values())
+            if len(members) % world == 0 and len({len(m) for m in members}) == 1:
+                work = [float(sum(calculate_workload(lens[m]).tolist())) for m in members]
+                gparts = get_seqlen_balanced_partitions(work, world, equal_size=True)
+                parts = [[i for g in gp for i in members[g]] for gp in gparts]
+                batch.reorder(torch.tensor([i for p in parts for i in p]))
+                metrics.update(log_seqlen_unbalance(lens.tolist(), parts, logging_prefix))
+                return
         parts = get_seqlen_balanced_partitions(calculate_workload(lens).tolist(), world, equal_size=True)
         for p in parts:   # shortest-first inside a rank keeps micro-batches homogeneous
             p.sort(key=lambda i: int(lens[i]))

@@ -154,6 +154,7 @@ class ActorConfig(BaseConfig):
     ppo_micro_batch_size_per_gpu: Optional[int] = None
     use_dynamic_bsz: bool = False
     ppo_max_token_len_per_gpu: int = 16384
+    use_prefix_grouper: bool = False     # share one prompt forward/backward among the n responses of its group
     clip_ratio: float = 0.2
     clip_ratio_low: float = 0.2
     clip_ratio_high: float = 0.2

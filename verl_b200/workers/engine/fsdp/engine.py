@@ -392,8 +392,26 @@ class FSDPEngine(BaseEngine):
             torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ micro-batching
-    def _micro_batch_indices(self, seq_lens: torch.Tensor, meta: dict) -> list[list[int]]:
+    def _prefix_sharing(self, meta: dict, tensors: dict) -> bool:
+        """Prefix sharing (one prompt forward for its n responses) applies to policy passes without Ulysses slicing."""
+        return bool(meta.get("use_prefix_grouper", False)) and self.sp_size == 1 and not self.cfg.value_head and "responses" in tensors
+
+    def _micro_batch_indices(self, seq_lens: torch.Tensor, meta: dict, tensors: Optional[dict] = None) -> list[list[int]]:
         n = seq_lens.numel()
+        if tensors is not None and meta.get("use_dynamic_bsz", False) and self._prefix_sharing(meta, tensors):
+            from verl_b200.utils.prefix_sharing import group_preserving_micro_batches, prompt_groups
+
+            att = tensors["attention_mask"]
+            P = att.shape[1] - tensors["responses"].shape[1]
+            gid, _ = prompt_groups(tensors["input_ids"], att, P)
+            pl, rl = att[:, :P].sum(-1).cpu(), att[:, P:].sum(-1).cpu()
+            budget = int(meta["max_token_len_per_gpu"])
+            parts = group_preserving_micro_batches(rl, pl, gid.cpu(), budget)
+            if self.world > 1 and dist.is_initialized():
+                t = torch.tensor([len(parts)], device=self.device if dist.get_backend(self.dp_group) == "nccl" else "cpu")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.dp_group)
+                parts = group_preserving_micro_batches(rl, pl, gid.cpu(), budget, num_micro_batches=int(t.item()))
+            return parts
         if meta.get("use_dynamic_bsz", False):
             budget = int(meta["max_token_len_per_gpu"]) * self.sp_size
             return rearrange_micro_batches(seq_lens.cpu(), budget, dp_group=self.dp_group if self.world > 1 else None)
@@ -419,6 +437,8 @@ class FSDPEngine(BaseEngine):
         pb, labels = self._pack(mb)
         R = mb["responses"].shape[1]
         idx, valid = response_gather_index(mb["attention_mask"], R)
+        if self._prefix_sharing(meta, mb):
+            return self._forward_shared_prefix(mb, pb, labels, idx, valid, meta)
         temperature = float(meta.get("temperature", 1.0))
         need_entropy = bool(meta.get("calculate_entropy", False))
         out: dict[str, torch.Tensor] = {}
@@ -439,6 +459,32 @@ class FSDPEngine(BaseEngine):
                                              temperature, need_entropy)
         full = torch.zeros(idx.shape, dtype=torch.float32, device=h.device)
         out["log_probs"] = full.masked_scatter(valid, lp.float())
+        if ent is not None:
+            out["entropy"] = torch.zeros_like(full).masked_scatter(valid, ent.float())
+        return out
+
+    def _forward_shared_prefix(self, mb: dict, pb_full: PackedBatch, labels_full: torch.Tensor, idx, valid, meta: dict) -> dict:
+        """Policy forward on the unique tokens of the micro-batch: every distinct prompt once plus all responses. Attention
+        expands to full sequences through ``PackedBatch.attn_expand``; the rows that predict response tokens are looked up
+        in the unique layout (the last prompt row serves all n first response tokens of its group)."""
+        from verl_b200.utils.prefix_sharing import build_shared_pack, prompt_groups
+
+        att = mb["attention_mask"]
+        P = att.shape[1] - mb["responses"].shape[1]
+        _, first_row = prompt_groups(mb["input_ids"], att, P)
+        sp = build_shared_pack(att, P, first_row)
+        routed = mb["routed_experts"][sp.keep] if "routed_experts" in mb else None
+        pb = PackedBatch(mb["input_ids"][sp.keep], mb["position_ids"][sp.keep].to(torch.int32), pb_full.cu_seqlens, pb_full.cu_seqlens_cpu,
+                         pb_full.max_seqlen, routed)
+        pb.attn_expand = (sp.expand, sp.back)
+        h = self.model.forward_hidden(pb)
+        sel = idx[valid]
+        temperature = float(meta.get("temperature", 1.0))
+        need_entropy = bool(meta.get("calculate_entropy", False))
+        lp, ent = ops.linear_logprob_entropy(h.index_select(0, sp.expand.index_select(0, sel)), self.model.output_weight,
+                                             labels_full.index_select(0, sel), temperature, need_entropy)
+        full = torch.zeros(idx.shape, dtype=torch.float32, device=h.device)
+        out = {"log_probs": full.masked_scatter(valid, lp.float())}
         if ent is not None:
             out["entropy"] = torch.zeros_like(full).masked_scatter(valid, ent.float())
         return out
@@ -474,7 +520,7 @@ class FSDPEngine(BaseEngine):
         tensors = {k: (_to_device(v, dev) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
         n = tensors["input_ids"].shape[0]
         seq_lens = tensors["attention_mask"].sum(-1)
-        mb_indices = self._micro_batch_indices(seq_lens, meta)
+        mb_indices = self._micro_batch_indices(seq_lens, meta, tensors)
         # global normalisers for the loss (identical on all ranks)
         info: dict[str, Any] = {"dp_size": self.dp_size}
         if not forward_only and loss_function is not None:

@@ -87,6 +87,7 @@ class TrainingWorker(Worker):
         else:
             mbs = cfg_get(c, f"{prefix}micro_batch_size_per_gpu", cfg_get(c, "ppo_micro_batch_size_per_gpu", None))
             meta.setdefault("micro_batch_size_per_gpu", int(mbs) if mbs else len(data))
+        meta.setdefault("use_prefix_grouper", bool(cfg_get(c, "use_prefix_grouper", False)))
         return meta
 
     def _postprocess_metrics(self, metrics: dict, n_tokens: int, dt: float, forward_only: bool) -> dict:
@@ -184,7 +185,9 @@ def _role_cfg(full, role: str, model_type: str):
     strategy = cfg_get(sub, "strategy", "fsdp")
     eng = dict(cfg_get(sub, "fsdp_config", {}) or {}) if strategy.startswith("fsdp") else dict(cfg_get(sub, "megatron", {}) or {})
     out = {"model_type": model_type, "backend": strategy, "model": cfg_get(full, "model"), "engine": eng,
-           "checkpoint": cfg_get(sub, "checkpoint"), "nccl_timeout": cfg_get(full, "nccl_timeout", 600)}
+           "checkpoint": cfg_get(sub, "checkpoint"), "nccl_timeout": cfg_get(full, "nccl_timeout", 600),
+           # one switch for actor update, old log-probs and reference log-probs (reference: actor.use_prefix_grouper)
+           "use_prefix_grouper": bool(cfg_get(cfg_get(full, "actor"), "use_prefix_grouper", False))}
     if role == "actor":
         out.update({k: cfg_get(sub, k) for k in ("ppo_mini_batch_size", "ppo_epochs", "shuffle", "use_dynamic_bsz", "data_loader_seed",
                                                  "ppo_max_token_len_per_gpu", "ppo_micro_batch_size_per_gpu")})
