@@ -87,3 +87,37 @@ def test_shared_prefix_matches_plain_forward_and_backward():
     lp2, g2 = _run({"use_prefix_grouper": True, "use_dynamic_bsz": True, "max_token_len_per_gpu": 100})
     assert torch.allclose(lp0["log_probs"], lp2["log_probs"], atol=2e-4)
     assert (g0 - g2).abs().max() <= 2e-3 * g0.abs().max() + 1e-6
+
+
+def test_trainer_step_with_prefix_sharing_and_score_centering(tmp_path):
+    """End to end on CPU: the rollout engine returns the sampler's top-k head, the update pass (prefix-shared packing)
+    evaluates that head under the trainer and the REINFORCE bypass loss adds the centering term."""
+    from verl_b200.trainer.ppo.ppo_trainer import PPOTrainer
+    from verl_b200.trainer.ppo.reward import load_reward_manager
+    from verl_b200.utils.config import load_config
+
+    ov = ["data.synthetic.enable=true", "data.synthetic.num_prompts=32", "data.train_batch_size=4", "data.max_prompt_length=32",
+          "data.max_response_length=8", "actor_rollout_ref.model.preset=tiny-qwen2", "actor_rollout_ref.rollout.n=4",
+          "actor_rollout_ref.actor.ppo_mini_batch_size=4", "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=16",
+          "actor_rollout_ref.actor.use_kl_loss=false", "actor_rollout_ref.rollout.log_prob_micro_batch_size_per_gpu=16",
+          "actor_rollout_ref.rollout.max_num_seqs=16", "actor_rollout_ref.rollout.topk_log_probs=4",
+          "actor_rollout_ref.actor.use_prefix_grouper=true", "actor_rollout_ref.model.enable_gradient_checkpointing=false",
+          "algorithm.adv_estimator=grpo", "algorithm.rollout_correction.bypass_mode=true", "algorithm.rollout_correction.loss_type=reinforce",
+          "algorithm.rollout_correction.rollout_is=token", "algorithm.rollout_correction.score_centering=true",
+          "reward.reward_manager=token_rule", "trainer.device=cpu", "trainer.val_before_train=false", "trainer.logger=[]",
+          "trainer.n_gpus_per_node=1", "data.shuffle=false", f"trainer.default_local_dir={tmp_path}/ckpt", "trainer.total_training_steps=1"]
+    cfg = load_config("ppo_trainer", ov)
+    tr = PPOTrainer(cfg, reward_fn=load_reward_manager(cfg, None), val_reward_fn=None)
+    tr.init_workers()
+    tr.global_steps = 1
+    m = tr.step(next(iter(tr.train_dataloader)))
+    b = tr._last_batch.batch
+    assert b["rollout_topk_ids"].shape == (16, 8, 4)
+    # the sampled token's log-prob can never exceed the best head entry; head entries are sorted
+    lps, top = b["rollout_log_probs"], b["rollout_topk_log_probs"]
+    mask = b["response_mask"].bool()
+    assert (lps[mask] <= top[..., 0][mask] + 1e-5).all() and (top[..., 0] >= top[..., 1]).all()
+    for k in ("actor/sc_correction", "actor/sc_sampler_head_mass", "actor/sc_train_head_mass", "actor/grad_norm"):
+        assert k in m, (k, sorted(m))
+    # same weights on both sides in the first step: the trainer's head mass equals the sampler's
+    assert abs(m["actor/sc_sampler_head_mass"] - m["actor/sc_train_head_mass"]) < 1e-4

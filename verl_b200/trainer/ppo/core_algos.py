@@ -696,18 +696,25 @@ def compute_policy_loss_cispo(old_log_prob, log_prob, advantages, response_mask,
 
 
 def compute_policy_loss_reinforce(rollout_log_prob, log_prob, advantages, response_mask, loss_agg_mode="seq-mean-token-sum",
-                                  config=None, rollout_is_weights=None):
-    """REINFORCE with optional (detached) importance weights: L = −w·logπ·A."""
+                                  config=None, rollout_is_weights=None, sc_correction=None):
+    """REINFORCE with optional (detached) importance weights: L = −w·logπ·A. ``sc_correction`` is the per-token
+    score-centering term (``verl_b200.trainer.ppo.score_centering``), added as ``A · sc_correction`` after the weighting
+    (reference: verl/trainer/ppo/core_algos.py:2396-2397)."""
     w = rollout_is_weights if rollout_is_weights is not None else torch.ones_like(advantages)
     losses = -w * log_prob * advantages
+    if sc_correction is not None:
+        losses = losses + advantages * sc_correction
     loss = agg_loss(losses, response_mask, loss_agg_mode, **_global_info(config))
     nkl = log_prob - rollout_log_prob
-    return loss, {"actor/ppo_kl": VF.masked_mean(-nkl, response_mask).detach().item()}
+    m = {"actor/ppo_kl": VF.masked_mean(-nkl, response_mask).detach().item()}
+    if sc_correction is not None:
+        m["actor/sc_correction"] = VF.masked_mean(sc_correction.detach(), response_mask).item()
+    return loss, m
 
 
 @register_policy_loss("bypass_mode")
 def compute_policy_loss_bypass_mode(old_log_prob, log_prob, advantages, response_mask, loss_agg_mode="token-mean",
-                                    config=None, rollout_is_weights=None):
+                                    config=None, rollout_is_weights=None, sc_correction=None):
     """Bypass mode: ``old_log_prob`` *is* the rollout log-prob (no recompute pass). Importance weights and rejection
     masks between the current policy and the rollout policy are computed on the fly, then either a REINFORCE or a
     PPO-clip objective (``policy_loss.rollout_correction.loss_type``) is applied."""
@@ -722,8 +729,10 @@ def compute_policy_loss_bypass_mode(old_log_prob, log_prob, advantages, response
         rollout_rs=_cfg_get(rc, "rollout_rs", None), rollout_rs_threshold=_cfg_get(rc, "rollout_rs_threshold", None),
         rollout_is_batch_normalize=_cfg_get(rc, "rollout_is_batch_normalize", False),
     )
+    if sc_correction is not None and loss_type != "reinforce":
+        raise ValueError("score centering needs policy_loss.rollout_correction.loss_type=reinforce")
     if loss_type == "reinforce":
-        loss, m = compute_policy_loss_reinforce(old_log_prob, log_prob, advantages, mask, loss_agg_mode, config, weights)
+        loss, m = compute_policy_loss_reinforce(old_log_prob, log_prob, advantages, mask, loss_agg_mode, config, weights, sc_correction)
     else:
         loss, m = compute_policy_loss_vanilla(old_log_prob, log_prob, advantages, mask, loss_agg_mode, config, None)
     m.update(metrics)

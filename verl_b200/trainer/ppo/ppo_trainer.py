@@ -414,6 +414,13 @@ def _train_on_rollouts(self: PPOTrainer, batch: DataProto, timing_raw: dict, n: 
         if int(_g(cfg, "trainer.critic_warmup", 0)) <= self.global_steps:
             with marked_timer("update_actor", timing_raw):
                 batch.meta_info["multi_turn"] = bool(_g(cfg, "actor_rollout_ref.rollout.multi_turn.enable", False))
+                if rc.get("score_centering", False):
+                    # the update pass also evaluates the sampler's top-k head (rollout.topk_log_probs) under the trainer
+                    if not bypass or rc.get("loss_type", "ppo_clip") != "reinforce" or "rollout_topk_ids" not in batch.batch.keys():
+                        raise ValueError("score centering needs rollout_correction.bypass_mode=true, loss_type=reinforce and "
+                                         "actor_rollout_ref.rollout.topk_log_probs > 0")
+                    batch.meta_info.update({"score_centering": True, "rollout_is": rc.get("rollout_is"),
+                                            "rollout_is_threshold": rc.get("rollout_is_threshold", 2.0)})
                 ao = self.actor_rollout_wg.update_actor(batch)
             metrics.update(reduce_metrics(ao.meta_info["metrics"]))
         with marked_timer("update_weights", timing_raw):

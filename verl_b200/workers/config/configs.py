@@ -291,6 +291,7 @@ class RolloutConfig(BaseConfig):
     enable_chunked_prefill: bool = True
     enable_prefix_caching: bool = True
     calculate_log_probs: bool = True
+    topk_log_probs: int = 0      # return the sampler's k most likely tokens per step (needed by score centering)
     quantization: Optional[str] = None
     sync_interval: int = 16
     log_prob_micro_batch_size_per_gpu: Optional[int] = None

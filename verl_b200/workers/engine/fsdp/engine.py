@@ -455,13 +455,32 @@ class FSDPEngine(BaseEngine):
             return out
         h = self.model.forward_hidden(pb)
         sel = idx[valid]
-        lp, ent = ops.linear_logprob_entropy(h.index_select(0, sel), self.model.output_weight, labels.index_select(0, sel),
-                                             temperature, need_entropy)
+        h_sel = h.index_select(0, sel)
+        lp, ent = ops.linear_logprob_entropy(h_sel, self.model.output_weight, labels.index_select(0, sel), temperature, need_entropy)
         full = torch.zeros(idx.shape, dtype=torch.float32, device=h.device)
         out["log_probs"] = full.masked_scatter(valid, lp.float())
         if ent is not None:
             out["entropy"] = torch.zeros_like(full).masked_scatter(valid, ent.float())
+        self._score_centering_terms(out, mb, meta, h_sel, valid, temperature)
         return out
+
+    def _score_centering_terms(self, out: dict, mb: dict, meta: dict, h_sel: torch.Tensor, valid: torch.Tensor, temperature: float) -> None:
+        """Score centering (train–inference mismatch correction): log-probs of the sampler's top-k head under the trainer,
+        turned into the per-token correction term that the REINFORCE loss adds (reference:
+        verl/trainer/ppo/score_centering.py:217-257). ``h_sel`` are the hidden rows that predict the valid response tokens."""
+        if not meta.get("score_centering", False) or "rollout_topk_ids" not in mb:
+            return
+        from verl_b200.trainer.ppo.score_centering import score_centering_correction, score_centering_weight_fn, topk_log_probs_from_hidden
+
+        ids = mb["rollout_topk_ids"][valid]
+        lq = mb["rollout_topk_log_probs"][valid]
+        lp_head = topk_log_probs_from_hidden(h_sel, self.model.output_weight, ids, temperature)
+        wfn = score_centering_weight_fn(meta.get("rollout_is", None), meta.get("rollout_is_threshold", 2.0))
+        corr, q_mass, p_mass = score_centering_correction(lp_head, lq, wfn)
+        zero = torch.zeros(valid.shape, dtype=torch.float32, device=h_sel.device)
+        out["sc_correction"] = zero.masked_scatter(valid, corr.float())
+        out["sc_sampler_head_mass"] = zero.masked_scatter(valid, q_mass.float()).detach()
+        out["sc_train_head_mass"] = zero.masked_scatter(valid, p_mass.float()).detach()
 
     def _forward_shared_prefix(self, mb: dict, pb_full: PackedBatch, labels_full: torch.Tensor, idx, valid, meta: dict) -> dict:
         """Policy forward on the unique tokens of the micro-batch: every distinct prompt once plus all responses. Attention
@@ -481,12 +500,13 @@ class FSDPEngine(BaseEngine):
         sel = idx[valid]
         temperature = float(meta.get("temperature", 1.0))
         need_entropy = bool(meta.get("calculate_entropy", False))
-        lp, ent = ops.linear_logprob_entropy(h.index_select(0, sp.expand.index_select(0, sel)), self.model.output_weight,
-                                             labels_full.index_select(0, sel), temperature, need_entropy)
+        h_sel = h.index_select(0, sp.expand.index_select(0, sel))
+        lp, ent = ops.linear_logprob_entropy(h_sel, self.model.output_weight, labels_full.index_select(0, sel), temperature, need_entropy)
         full = torch.zeros(idx.shape, dtype=torch.float32, device=h.device)
         out = {"log_probs": full.masked_scatter(valid, lp.float())}
         if ent is not None:
             out["entropy"] = torch.zeros_like(full).masked_scatter(valid, ent.float())
+        self._score_centering_terms(out, mb, meta, h_sel, valid, temperature)
         return out
 
     def _sp_forward(self, pb: PackedBatch, labels: torch.Tensor, temperature: float, need_entropy: bool):

@@ -88,6 +88,8 @@ class TrainingWorker(Worker):
             mbs = cfg_get(c, f"{prefix}micro_batch_size_per_gpu", cfg_get(c, "ppo_micro_batch_size_per_gpu", None))
             meta.setdefault("micro_batch_size_per_gpu", int(mbs) if mbs else len(data))
         meta.setdefault("use_prefix_grouper", bool(cfg_get(c, "use_prefix_grouper", False)))
+        if prefix != "ppo_":
+            meta.pop("score_centering", None)      # only the update pass computes the centering term
         return meta
 
     def _postprocess_metrics(self, metrics: dict, n_tokens: int, dt: float, forward_only: bool) -> dict:
@@ -338,7 +340,7 @@ class ActorRolloutRefWorker(Worker):
             temperature=temperature if do_sample or validate else 0.0,
             top_p=float(cfg_get(vk, "top_p", 1.0)) if validate else float(meta.get("top_p", cfg_get(ro, "top_p", 1.0))),
             top_k=int(cfg_get(vk, "top_k", -1)) if validate else int(meta.get("top_k", cfg_get(ro, "top_k", -1))),
-            max_tokens=R, ignore_eos=bool(cfg_get(ro, "ignore_eos", False)), seed=int(meta.get("seed", 0)) + 1000003 * (self.rank // getattr(self, "_rollout_tp", 1)) + int(meta.get("global_steps", 0)))
+            max_tokens=R, ignore_eos=bool(cfg_get(ro, "ignore_eos", False)), top_logprobs=0 if validate else int(cfg_get(ro, "topk_log_probs", 0) or 0), seed=int(meta.get("seed", 0)) + 1000003 * (self.rank // getattr(self, "_rollout_tp", 1)) + int(meta.get("global_steps", 0)))
         eos = meta.get("eos_token_id", None)
         pad_id = int(meta.get("pad_token_id", 0) or 0)
         ids_cpu, att_cpu = ids.cpu(), att.cpu().bool()
@@ -368,6 +370,17 @@ class ActorRolloutRefWorker(Worker):
         batch = TensorBatch({"prompts": ids_cpu, "responses": resp, "input_ids": full_ids, "attention_mask": full_att,
                              "position_ids": compute_position_id_with_mask(full_att), "response_mask": rmask,
                              "rollout_log_probs": lps}, batch_size=(bs,))
+        if sp.top_logprobs > 0:
+            # the sampler's top-k head per response token (padding rows: ids 0..k-1 with log-prob -1e4, i.e. zero mass)
+            k = sp.top_logprobs
+            tids = torch.arange(k).expand(bs, R, k).clone()
+            tlps = torch.full((bs, R, k), -1e4, dtype=torch.float32)
+            for i, o in enumerate(outs):
+                n = len(o.token_ids)
+                if n and o.top_ids is not None:
+                    tids[i, :n] = torch.tensor(o.top_ids)
+                    tlps[i, :n] = torch.tensor(o.top_log_probs)
+            batch["rollout_topk_ids"], batch["rollout_topk_log_probs"] = tids, tlps
         n_tok = int(rmask.sum())
         out = DataProto(batch=batch, non_tensor_batch=dict(prompts.non_tensor_batch),
                         meta_info={"timing": {"generate_sequences": dt}, "metrics": [{"rollout/tokens_per_s": n_tok / max(dt, 1e-9)}]})

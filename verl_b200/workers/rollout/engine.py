@@ -42,6 +42,7 @@ class SamplingParams:
     max_tokens: int = 1024
     ignore_eos: bool = False
     logprobs: bool = True
+    top_logprobs: int = 0      # also return the k most likely tokens (ids + log-probs) at every step (score centering)
     seed: int = 0
     stop_token_ids: Sequence[int] = ()
 
@@ -52,6 +53,8 @@ class TokenOutput:
 
     token_ids: list
     log_probs: Optional[list] = None
+    top_ids: Optional[list] = None           # [steps][k] with SamplingParams.top_logprobs = k
+    top_log_probs: Optional[list] = None
     routed_experts: Optional[np.ndarray] = None
     stop_reason: Optional[str] = None
     num_preempted: int = 0
@@ -343,10 +346,29 @@ class InferenceEngine:
         self.kv_lens.index_copy_(0, slots, plen)
         self.active.index_fill_(0, slots, 1)
         tok_h, lp_h = tok.tolist(), lp.tolist()
-        for (req, _), t, l in zip(reqs_slots, tok_h, lp_h):
+        top = None
+        if sp.top_logprobs > 0:
+            tv, ti = self._top_head(logits, sp)
+            top = (ti.tolist(), tv.tolist())
+        for j, ((req, _), t, l) in enumerate(zip(reqs_slots, tok_h, lp_h)):
             req["out"].append(int(t))
             req["lp"].append(float(l))
+            if top is not None:
+                req.setdefault("topi", []).append(top[0][j])
+                req.setdefault("topv", []).append(top[1][j])
             req["n_gen"] = len(req["out"])
+
+    @staticmethod
+    def _top_head(logits: torch.Tensor, sp: SamplingParams):
+        """(log-probs [B, k], ids [B, k]) of the k most likely tokens under the sampling temperature."""
+        lsm = torch.log_softmax(logits.float() / max(float(sp.temperature), 1e-6), dim=-1)
+        return lsm.topk(int(sp.top_logprobs), dim=-1)
+
+    def _ensure_top_hist(self, k: int):
+        if getattr(self, "hist_topi", None) is None or self.hist_topi.shape[-1] != k:
+            K, S = self.hist_tok.shape
+            self.hist_topi = torch.zeros(K, S, k, dtype=torch.int64, device=self.device)
+            self.hist_topv = torch.zeros(K, S, k, dtype=torch.float32, device=self.device)
 
     # ------------------------------------------------------------------ decode
     def _decode_body(self, sp: SamplingParams):
@@ -376,15 +398,21 @@ class InferenceEngine:
         self.positions.add_(act)
         self.hist_tok.index_copy_(0, self.hist_idx, self.out_tok[None])
         self.hist_lp.index_copy_(0, self.hist_idx, self.out_lp[None])
+        if sp.top_logprobs > 0:
+            tv, ti = self._top_head(logits, sp)
+            self.hist_topi.index_copy_(0, self.hist_idx, ti[None])
+            self.hist_topv.index_copy_(0, self.hist_idx, tv[None])
         self.hist_idx.add_(1).remainder_(self.sync_interval)
         if self.native:
             self.rng[1] += 1
 
     def _decode_step(self, sp: SamplingParams):
+        if sp.top_logprobs > 0:
+            self._ensure_top_hist(int(sp.top_logprobs))
         if self.enforce_eager:
             self._decode_body(sp)
             return
-        key = (sp.temperature, sp.top_k, sp.top_p)
+        key = (sp.temperature, sp.top_k, sp.top_p, sp.top_logprobs)
         if self._graph is None or self._graph[0] != key:
             # warm-up on a side stream, then capture
             s = torch.cuda.Stream()
@@ -417,6 +445,9 @@ class InferenceEngine:
         t_f = time.perf_counter()
         tok = self.hist_tok.cpu().numpy()
         lp = self.hist_lp.cpu().numpy()
+        topi = topv = None
+        if sp.top_logprobs > 0:
+            topi, topv = self.hist_topi.cpu().numpy(), self.hist_topv.cpu().numpy()
         freed = []
         for ring, ids, slots in pending:
             for sid, slot in zip(ids, slots):
@@ -426,6 +457,9 @@ class InferenceEngine:
                 t = int(tok[ring, slot])
                 r["out"].append(t)
                 r["lp"].append(float(lp[ring, slot]))
+                if topi is not None:
+                    r.setdefault("topi", []).append(topi[ring, slot].tolist())
+                    r.setdefault("topv", []).append(topv[ring, slot].tolist())
                 if (not sp.ignore_eos) and t in eos_ids:
                     r["done"], r["stop"] = True, "stop"
                 elif len(r["out"]) >= r["max_new"]:
@@ -605,6 +639,8 @@ class InferenceEngine:
         for i in range(len(prompts)):
             r = reqs[i]
             outs.append(TokenOutput(token_ids=r["out"][: r["max_new"]], log_probs=r["lp"][: r["max_new"]] if sp.logprobs else None,
+                                    top_ids=r["topi"][: r["max_new"]] if "topi" in r else None,
+                                    top_log_probs=r["topv"][: r["max_new"]] if "topv" in r else None,
                                     stop_reason=r["stop"] or "length", num_preempted=r["num_preempted"]))
         return outs
 
@@ -613,6 +649,8 @@ class InferenceEngine:
             return
         r["reported"] = True
         self._on_done(r["id"], TokenOutput(token_ids=r["out"][: r["max_new"]], log_probs=r["lp"][: r["max_new"]] if self._sp_logprobs else None,
+                                           top_ids=r["topi"][: r["max_new"]] if "topi" in r else None,
+                                           top_log_probs=r["topv"][: r["max_new"]] if "topv" in r else None,
                                            stop_reason=r["stop"] or "length", num_preempted=r["num_preempted"]))
 
     def abort_all(self) -> list[int]:

@@ -53,7 +53,7 @@ def ppo_loss(config, model_output: dict, data, dp_group=None) -> tuple[torch.Ten
     from verl_b200.ops import rl as rl_ops
 
     kl_type = _get(config, "kl_loss_type", "low_var_kl") if _get(config, "use_kl_loss", False) else None
-    if loss_mode == "vanilla" and rl_ops.fused_ppo_available(log_prob) and kl_type in rl_ops.KL_TYPES:
+    if loss_mode == "vanilla" and rl_ops.fused_ppo_available(log_prob) and kl_type in rl_ops.KL_TYPES and "sc_correction" not in model_output:
         # one kernel: surrogate + KL term, their gradient and the logging sums
         clip = _get(config, "clip_ratio", 0.2)
         lo, hi = _get(config, "clip_ratio_low", None), _get(config, "clip_ratio_high", None)
@@ -76,10 +76,22 @@ def ppo_loss(config, model_output: dict, data, dp_group=None) -> tuple[torch.Ten
             metrics["actor/kl_coef"] = Metric(AggregationType.MEAN, coef)
         return loss, metrics
     fn = core_algos.get_policy_loss_fn(loss_mode)
+    rc = _get(_get(config, "policy_loss", {}) or {}, "rollout_correction", None) or {}
+    sc_kwargs = {}
+    if _get(rc, "score_centering", False):
+        if "sc_correction" not in model_output:
+            # a pass that never computed the head log-probs would silently train plain bypass policy gradient
+            raise RuntimeError("score centering is enabled but the engine produced no sc_correction: the batch needs "
+                               "rollout_topk_ids / rollout_topk_log_probs (rollout.topk_log_probs > 0)")
+        sc_kwargs["sc_correction"] = model_output["sc_correction"]
     pg_loss, pg_metrics = fn(old_log_prob=data["old_log_probs"], log_prob=log_prob, advantages=data["advantages"],
                              response_mask=mask, loss_agg_mode=agg_mode, config=view,
-                             rollout_is_weights=data.get("rollout_is_weights") if hasattr(data, "get") else None)
+                             rollout_is_weights=data.get("rollout_is_weights") if hasattr(data, "get") else None, **sc_kwargs)
     metrics: dict[str, Any] = {k: Metric(AggregationType.MEAN, v) for k, v in pg_metrics.items()}
+    if sc_kwargs:
+        for key in ("sc_sampler_head_mass", "sc_train_head_mass"):
+            if key in model_output:
+                metrics[f"actor/{key}"] = Metric(AggregationType.MEAN, VF.masked_mean(model_output[key].detach(), mask).item())
     loss = pg_loss
     ent_coeff = _get(config, "entropy_coeff", 0.0)
     if entropy is not None and ent_coeff != 0:
