@@ -68,3 +68,35 @@ def test_reshard_gather_and_requant_from_row_shards():
     qr, sr = _blockwise_ref(full[256:556], 128, 128)
     torch.testing.assert_close(sc, sr, rtol=1e-6, atol=0)
     assert torch.equal(keep, full[256:556]) and (q.float() != qr.float()).float().mean() < 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(512, 768, 1024), (300, 520, 2064), (2048, 4096, 4096), (17, 40, 144)])
+def test_fp8_gemm_matches_dequantised_reference(M, N, K):
+    """e4m3 tcgen05 GEMM with row/column scales vs the fp32 product of the dequantised operands (ragged edges included)."""
+    from verl_b200.ops import _ext
+    from verl_b200.ops.quant import fp8_gemm, fp8_linear, rowwise_cast_to_fp8
+
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    a8, sa = rowwise_cast_to_fp8(x)
+    b8, sb = rowwise_cast_to_fp8(w)
+    # the cast kernel against its definition
+    sa_ref = x.float().abs().amax(-1).clamp_min(1e-12) / 448.0
+    assert torch.allclose(sa, sa_ref, rtol=1e-6)
+    assert torch.equal(a8.view(torch.uint8), (x.float() * (1.0 / sa_ref)[:, None]).to(torch.float8_e4m3fn).view(torch.uint8))
+    ref = (a8.float() * sa[:, None]) @ (b8.float() * sb[:, None]).t() + bias.float()
+    y = fp8_gemm(a8, b8, sa, sb, bias)
+    y32 = fp8_gemm(a8, b8, sa, sb, bias, out_dtype=torch.float32)
+    assert (y32 - ref).abs().max() <= 1e-3 * ref.abs().max()
+    assert (y.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+    raw = fp8_gemm(a8, b8, out_dtype=torch.float32)                      # unscaled product
+    assert (raw - a8.float() @ b8.float().t()).abs().max() <= 1e-3 * raw.abs().max()
+    # W8A8 linear is close to the bf16 linear (quantisation error only)
+    z = fp8_linear(x, b8, sb, bias)
+    full = x.float() @ w.float().t() + bias.float()
+    assert ((z.float() - full).norm() / full.norm()).item() < 0.06
+    torch.cuda.synchronize()
+    _ext.check_status("fp8 gemm")

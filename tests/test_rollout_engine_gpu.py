@@ -1,0 +1,108 @@
+"""Rollout engine and prefix-shared training pass on the GPU kernels (tcgen05 GEMMs, paged decode, CUDA-graph decode)."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(seed=0):
+    from verl_b200.models.config import PRESETS
+    from verl_b200.models.transformer import DecoderLM
+
+    return DecoderLM(PRESETS["tiny-qwen2-gpu"], dtype=torch.bfloat16, device="cuda", seed=seed)
+
+
+def test_rollout_log_probs_match_a_training_forward_and_fp8_mode_stays_close():
+    from verl_b200.models.transformer import PackedBatch
+    from verl_b200.ops import _ext
+    from verl_b200.workers.rollout import InferenceEngine, SamplingParams
+
+    model = _model()
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(10, model.cfg.vocab_size, (int(n),), generator=g).tolist() for n in (33, 70, 129, 18)]
+    sp = SamplingParams(temperature=1.0, max_tokens=24, seed=3, top_logprobs=4)
+    eng = InferenceEngine(model, max_num_seqs=8, max_model_len=256, num_blocks=64, sync_interval=4)
+    outs = eng.generate(prompts, sp)
+    assert eng._graph is not None                                  # the decode step ran as a CUDA graph
+    worst = 0.0
+    for p, o in zip(prompts, outs):
+        ids = torch.tensor(p + o.token_ids, device="cuda")
+        pb = PackedBatch(ids, torch.arange(len(ids), dtype=torch.int32, device="cuda"), torch.tensor([0, len(ids)], dtype=torch.int32, device="cuda"))
+        with torch.no_grad():
+            lp = torch.log_softmax(model(pb, return_logits=True)["logits"].float(), -1)
+        want = lp[len(p) - 1: len(ids) - 1].gather(1, ids[len(p):, None])[:, 0]
+        got = torch.tensor(o.log_probs, device="cuda")
+        worst = max(worst, (want - got).abs().max().item())
+        top = torch.tensor(o.top_log_probs, device="cuda")
+        assert top.shape == (24, 4) and (top[:, 0] >= top[:, 1]).all() and (got <= top[:, 0] + 1e-4).all()
+        ref_top = lp[len(p) - 1: len(ids) - 1].topk(4, -1).values
+        assert (ref_top - top).abs().max() < 0.08
+    assert worst < 0.08, worst                                     # bf16 decode path vs bf16 packed forward
+    eng.sleep()
+
+    # W8A8 rollout: same sampler seed, log-probs of ITS tokens re-scored by the bf16 model stay close
+    eng8 = InferenceEngine(model, max_num_seqs=8, max_model_len=256, num_blocks=64, sync_interval=4, quantization="fp8")
+    outs8 = eng8.generate(prompts, SamplingParams(temperature=1.0, max_tokens=24, seed=3))
+    assert len(eng8._w8) == 4 * model.cfg.num_hidden_layers
+    diffs = []
+    for p, o in zip(prompts, outs8):
+        ids = torch.tensor(p + o.token_ids, device="cuda")
+        pb = PackedBatch(ids, torch.arange(len(ids), dtype=torch.int32, device="cuda"), torch.tensor([0, len(ids)], dtype=torch.int32, device="cuda"))
+        with torch.no_grad():
+            lp = torch.log_softmax(model(pb, return_logits=True)["logits"].float(), -1)
+        want = lp[len(p) - 1: len(ids) - 1].gather(1, ids[len(p):, None])[:, 0]
+        diffs.append((want - torch.tensor(o.log_probs, device="cuda")).abs())
+    d = torch.cat(diffs)
+    assert d.mean() < 0.1 and d.max() < 1.0, (d.mean().item(), d.max().item())
+    eng8.sleep()
+    assert not eng8._w8
+    torch.cuda.synchronize()
+    _ext.check_status("rollout engine test")
+
+
+def test_prefix_shared_training_pass_matches_plain_pass_on_gpu():
+    from verl_b200.models.config import PRESETS
+    from verl_b200.ops import _ext
+    from verl_b200.protocol import DataProto
+    from verl_b200.workers.engine.fsdp.engine import FSDPEngine
+    from verl_b200.workers.utils.losses import ppo_loss
+
+    cfg = {"clip_ratio": 0.2, "use_kl_loss": True, "kl_loss_coef": 1e-3, "entropy_coeff": 0.0, "loss_agg_mode": "token-mean"}
+
+    def batch(**meta):
+        g = torch.Generator().manual_seed(0)
+        n_prompts, n, P, R, V = 4, 8, 200, 150, 4096
+        bs = n_prompts * n
+        prompts = torch.randint(10, V, (n_prompts, P), generator=g)
+        patt = torch.ones(n_prompts, P, dtype=torch.int64)
+        for i in range(n_prompts):
+            patt[i, : 17 * i] = 0
+        ids = torch.cat([prompts.repeat_interleave(n, 0), torch.randint(10, V, (bs, R), generator=g)], 1)
+        att = torch.cat([patt.repeat_interleave(n, 0), torch.ones(bs, R, dtype=torch.int64)], 1)
+        for i in range(bs):
+            att[i, P + R - (i % 5) * 11:] = 0
+        pos = torch.clip(torch.cumsum(att, -1) - 1, min=0)
+        m = {"use_dynamic_bsz": True, "max_token_len_per_gpu": 4096, "temperature": 1.0, "calculate_entropy": True}
+        m.update(meta)
+        return DataProto.from_dict(tensors={
+            "input_ids": ids, "attention_mask": att, "position_ids": pos, "responses": ids[:, -R:], "response_mask": att[:, -R:],
+            "old_log_probs": torch.full((bs, R), -8.3), "ref_log_prob": torch.full((bs, R), -8.3),
+            "advantages": torch.randn(bs, R, generator=g)}, meta_info=m)
+
+    res = []
+    for meta in ({}, {"use_prefix_grouper": True}):
+        eng = FSDPEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1}, {"lr": 1e-4}, {})
+        eng.initialize()
+        data = batch(**meta)
+        lp = eng.infer_batch(data)["model_output"]["log_probs"]
+        eng.optimizer_zero_grad()
+        eng.forward_backward_batch(data, lambda model_output, data, dp_group=None: ppo_loss(cfg, model_output, data))
+        res.append((lp.float().cpu(), eng.store.grad.float().cpu().clone()))
+    (lp0, g0), (lp1, g1) = res
+    assert (lp0 - lp1).abs().max() < 0.06, (lp0 - lp1).abs().max()
+    cos = torch.nn.functional.cosine_similarity(g0.flatten(), g1.flatten(), dim=0).item()
+    assert cos > 0.995, cos
+    assert abs(g0.norm() / g1.norm() - 1) < 0.03
+    torch.cuda.synchronize()
+    _ext.check_status("prefix sharing on gpu")

@@ -7,6 +7,7 @@
 #include "api.h"
 
 void vb_count_launch(int n);
+at::Tensor& vb_status_tensor(int dev);
 
 namespace {
 using at::Tensor;
@@ -37,6 +38,42 @@ std::tuple<Tensor, Tensor> fp8_act_cast(const Tensor& x) {
   Tensor s = at::empty({M, (K + 127) / 128}, x.options().dtype(at::kFloat));
   check_rc(vb_fp8_act_cast(x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), s.data_ptr<float>(), M, K, cur_stream()), "fp8_act_cast");
   return {y, s};
+}
+
+// x [M, K] bf16 -> (y [M, K] fp8, scale [M] fp32): one scale per row (per token for activations, per output channel for weights)
+std::tuple<Tensor, Tensor> fp8_row_cast(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "fp8_row_cast: bad x");
+  const long M = x.size(0);
+  const int K = x.size(1);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty({M, K}, x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor s = at::empty({M}, x.options().dtype(at::kFloat));
+  check_rc(vb_fp8_row_cast(x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), s.data_ptr<float>(), M, K, cur_stream()), "fp8_row_cast");
+  return {y, s};
+}
+
+// out[M, N] = diag(a_scale) (a8 b8^T) diag(b_scale) (+ bias): e4m3 operands on the tcgen05 f8f6f4 path (SM pairs, 256 x 256 tiles)
+Tensor gemm_fp8(const Tensor& a8, const Tensor& b8, const c10::optional<Tensor>& a_scale, const c10::optional<Tensor>& b_scale,
+                const c10::optional<Tensor>& bias, bool out_f32) {
+  TORCH_CHECK(a8.is_cuda() && b8.is_cuda() && a8.scalar_type() == at::kFloat8_e4m3fn && b8.scalar_type() == at::kFloat8_e4m3fn, "gemm_fp8: operands must be e4m3 CUDA tensors");
+  TORCH_CHECK(a8.dim() == 2 && b8.dim() == 2 && a8.size(1) == b8.size(1) && a8.stride(1) == 1 && b8.stride(1) == 1, "gemm_fp8: shapes");
+  const int M = a8.size(0), K = a8.size(1), N = b8.size(0);
+  const bool scaled = a_scale.has_value() && a_scale->defined();
+  TORCH_CHECK(scaled == (b_scale.has_value() && b_scale->defined()), "gemm_fp8: give both scales or none");
+  if (scaled) TORCH_CHECK(a_scale->numel() == M && b_scale->numel() == N && a_scale->scalar_type() == at::kFloat && b_scale->scalar_type() == at::kFloat &&
+                              a_scale->is_contiguous() && b_scale->is_contiguous(), "gemm_fp8: scales must be fp32 [M] and [N]");
+  c10::cuda::CUDAGuard guard(a8.device());
+  Tensor out = at::empty({M, N}, a8.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
+  const void* bp = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N, "gemm_fp8: bias must be bf16 [N]");
+    bp = bias->data_ptr();
+  }
+  int* err = vb_status_tensor(a8.get_device()).data_ptr<int>();
+  check_rc(vb_gemm_fp8_pair(a8.data_ptr(), b8.data_ptr(), out.data_ptr(), bp, scaled ? a_scale->data_ptr<float>() : nullptr,
+                            scaled ? b_scale->data_ptr<float>() : nullptr, M, N, K, (int)a8.stride(0), (int)b8.stride(0), N, out_f32 ? 1 : 0, err, cur_stream()),
+           "gemm_fp8");
+  return out;
 }
 
 // ptrs: CPU int64 [world] peer pointers of the row shards. Returns (fp8 [M_out, N], scales) and, if keep_bf16, also the
@@ -97,6 +134,8 @@ void delta_apply16(Tensor& dst, const Tensor& pos, const Tensor& val, int64_t co
 TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
   m.def("fp8_block_cast(Tensor x) -> (Tensor, Tensor)", &fp8_block_cast);
   m.def("fp8_act_cast(Tensor x) -> (Tensor, Tensor)", &fp8_act_cast);
+  m.def("fp8_row_cast(Tensor x) -> (Tensor, Tensor)", &fp8_row_cast);
+  m.def("gemm_fp8(Tensor a8, Tensor b8, Tensor? a_scale, Tensor? b_scale, Tensor? bias, bool out_f32=False) -> Tensor", &gemm_fp8);
   m.def("fp4_fake_quant(Tensor x, Tensor global_amax) -> Tensor", &fp4_fake_quant);
   m.def("reshard_quant(Tensor ptrs, int rows_per_rank, int ld_src, int row_begin, int M_out, int N, bool quantize, bool keep_bf16, Tensor like) -> (Tensor, Tensor, Tensor)", &reshard_quant);
   m.def("delta_compact16(Tensor cur, Tensor(a!) snap, Tensor(b!) pos_out, Tensor(c!) val_out) -> int", &delta_compact16);

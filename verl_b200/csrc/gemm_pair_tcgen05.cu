@@ -88,15 +88,30 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, u
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
       : "memory");
 }
+// Same for fp8 (e4m3) operands: kind::f8f6f4, 32 elements (= 32 bytes) of K per instruction.
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
 // Arrive on the barrier at `bar_cluster_addr` once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-template <int BN, bool A_MN, bool B_MN>
+// FP8: operands are e4m3 bytes, K-major; a stage row is still 128 bytes (128 elements of K instead of 64) so the ring, the
+// swizzle and the descriptors are unchanged. The epilogue applies per-row (a_scale[M]) and per-column (b_scale[N]) scales.
+template <int BN, bool A_MN, bool B_MN, bool FP8 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
-                 const bf16* __restrict__ bias, int M, int N, int K, int ldc, int flags, int* err_word) {
+                 const bf16* __restrict__ bias, int M, int N, int K, int ldc, int flags, int* err_word,
+                 const float* __restrict__ a_scale = nullptr, const float* __restrict__ b_scale = nullptr) {
+  static_assert(!FP8 || (!A_MN && !B_MN), "fp8 operands are K-major");
+  constexpr int BKE = FP8 ? 2 * BK : BK;      // elements of K per stage
   using C = Cfg<BN>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -116,7 +131,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_pairs = gridDim.x >> 1;
   const int num_m = (M + 2 * BM - 1) / (2 * BM);
   const int num_n = (N + BN - 1) / BN;
-  const int num_kb = (K + BK - 1) / BK;
+  const int num_kb = (K + BKE - 1) / BKE;
   const int num_tiles = num_m * num_n;
 
   if (threadIdx.x == 0) {
@@ -171,7 +186,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sb = sa + A_TILE_BYTES;
           const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[s]), 0);
           mbar_arrive_expect_tx_cluster(full_leader, C::STAGE_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = kb * BKE;
           if (!A_MN) {
             tma_load_2d_pair(sa, &tmA, k0, m0, full_leader);
           } else {
@@ -191,7 +206,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = make_idesc(2 * BM, BN, 1, 1, A_MN, B_MN);
+      constexpr uint32_t idesc = FP8 ? make_idesc(2 * BM, BN, 0, 0, false, false) : make_idesc(2 * BM, BN, 1, 1, A_MN, B_MN);
       int s = 0;
       uint32_t ph = 0, it = 0;
       bool ok = true;
@@ -210,7 +225,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int k = 0; k < BK / UMMA_K; ++k) {
             uint64_t ad = A_MN ? make_sdesc_sw128(sa + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sa + k * 32, 16, 1024);
             uint64_t bd = B_MN ? make_sdesc_sw128(sb + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sb + k * 32, 16, 1024);
-            umma_f16_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
+            if constexpr (FP8) umma_f8_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
+            else umma_f16_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
           }
           const uint32_t e_local = smem_u32(&empty_bar[s]);
           umma_commit_pair(map_to_cta(e_local, 0));
@@ -251,6 +267,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if constexpr (FP8) {
+            if (a_scale != nullptr) {
+              const float rs = a_scale[row];
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) f[j] *= rs * b_scale[col0 + j];
+            }
+          }
           if (bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -357,12 +381,43 @@ static int launch(const void* A, const void* B, void* Cp, const void* bias, int 
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
   int pairs = sm_count() / 2;
   if (tiles < pairs) pairs = tiles;
-  kern<<<2 * pairs, 192, C::SMEM_BYTES, stream>>>(tmA, tmB, Cp, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags, err_word);
+  kern<<<2 * pairs, 192, C::SMEM_BYTES, stream>>>(tmA, tmB, Cp, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags, err_word, nullptr, nullptr);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+static int launch_fp8(const void* A, const void* B, void* Cp, const void* bias, const float* a_scale, const float* b_scale, int M, int N,
+                      int K, int lda, int ldb, int ldc, int flags, int* err_word, cudaStream_t stream) {
+  using C = Cfg<256>;
+  CUtensorMap tmA, tmB;
+  if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, lda, BM, 2 * BK)) return -1;
+  if (make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, ldb, 128, 2 * BK)) return -1;
+  static bool attr_set = false;
+  auto kern = gemm_pair_kernel<256, false, false, true>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+  int pairs = sm_count() / 2;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<2 * pairs, 192, C::SMEM_BYTES, stream>>>(tmA, tmB, Cp, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags, err_word, a_scale, b_scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 }  // namespace pair
 }  // namespace vb
+
+// fp8 (e4m3) GEMM on SM pairs: C[M,N] = diag(a_scale) (A8 B8^T) diag(b_scale) (+ bias); A8 [M,K], B8 [N,K] row-major bytes,
+// lda/ldb in elements (multiples of 16), fp32 accumulation in TMEM, bf16 or fp32 output. a_scale/b_scale may both be null.
+extern "C" int vb_gemm_fp8_pair(const void* A, const void* B, void* C, const void* bias, const float* a_scale, const float* b_scale, int M, int N,
+                                int K, int lda, int ldb, int ldc, int out_f32, int* err_word, cudaStream_t stream) {
+  using namespace vb::pair;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return -3;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 15) || (ldb & 15)) return -4;
+  if ((a_scale == nullptr) != (b_scale == nullptr)) return -2;
+  return launch_fp8(A, B, C, bias, a_scale, b_scale, M, N, K, lda, ldb, ldc, out_f32 ? OUT_F32 : 0, err_word, stream);
+}
 
 // Same contract as vb_gemm_bf16 without split-K: C[M,N] (+)= op(A) op(B) (+ bias), 256 x 256 tiles on SM pairs.
 // Requirements beyond vb_gemm_bf16's: N % 128 == 0 is NOT required (edges are masked), but the K-major B tile is

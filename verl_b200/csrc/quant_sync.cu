@@ -263,11 +263,64 @@ __global__ void delta_apply16_kernel(uint16_t* __restrict__ dst, const int* __re
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < count; i += (long)gridDim.x * blockDim.x) dst[pos[i]] = val[i];
 }
 
+// Per-row (per-token / per-output-channel) e4m3 cast: scale[r] = amax(x[r, :]) / 448, y = x / scale. One CTA per row;
+// the row is read once into registers (K <= 8 * 256 * 8 elements) or re-read from L2 for longer rows.
+__global__ void __launch_bounds__(256) fp8_row_cast_kernel(const bf16* __restrict__ x, long ldx, __nv_fp8_e4m3* __restrict__ y, long ldy,
+                                                           float* __restrict__ scale, int K) {
+  __shared__ float red[8];
+  const long r = blockIdx.x;
+  const bf16* xr = x + r * ldx;
+  const int nvec = K / 8;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += 256) {
+    const uint4 v = reinterpret_cast<const uint4*>(xr)[i];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < K; i += 256) amax = fmaxf(amax, fabsf(__bfloat162float(xr[i])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+  const float sc = fmaxf(amax, 1e-12f) / 448.f;
+  const float inv = 1.f / sc;
+  if (threadIdx.x == 0) scale[r] = sc;
+  __nv_fp8_e4m3* yr = y + r * ldy;
+  for (int i = threadIdx.x; i < nvec; i += 256) {
+    const uint4 v = reinterpret_cast<const uint4*>(xr)[i];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    __nv_fp8_e4m3 o[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      o[2 * k] = __nv_fp8_e4m3(f.x * inv);
+      o[2 * k + 1] = __nv_fp8_e4m3(f.y * inv);
+    }
+    reinterpret_cast<uint2*>(yr)[i] = *reinterpret_cast<const uint2*>(o);
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < K; i += 256) yr[i] = __nv_fp8_e4m3(__bfloat162float(xr[i]) * inv);
+}
+
 }  // namespace vb
 
 using namespace vb;
 
 extern "C" {
+
+// x [M, K] bf16 (row stride ldx, 16-byte aligned rows) -> y [M, K] e4m3 (row stride ldy, 8-byte aligned rows), scale [M]
+int vb_fp8_row_cast(const void* x, long ldx, void* y, long ldy, float* scale, long M, int K, cudaStream_t st) {
+  if (M <= 0 || K <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (ldx & 7) || (reinterpret_cast<uintptr_t>(y) & 7) || (ldy & 7)) return -4;
+  fp8_row_cast_kernel<<<(unsigned)M, 256, 0, st>>>((const bf16*)x, ldx, (__nv_fp8_e4m3*)y, ldy, scale, K);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
 
 int vb_fp8_block_cast(const void* x, long ldx, void* y, long ldy, float* scale, int M, int N, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;

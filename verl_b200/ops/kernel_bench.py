@@ -76,6 +76,32 @@ def bench_gemm(a):
         report("  cuBLAS (torch.matmul) same shape", ms2, flops=2.0 * M * N * K)
 
 
+def bench_gemm_fp8(a):
+    """e4m3 GEMM (per-row / per-column scales in the epilogue) against the bf16 kernel and torch._scaled_mm on the same shape."""
+    from verl_b200.ops import _ext
+    from verl_b200.ops.quant import rowwise_cast_to_fp8
+
+    o = _ext.ops()
+    M, N, K = a.m, a.n, a.k
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda").bfloat16()
+    a8, sa = rowwise_cast_to_fp8(x)
+    b8, sb = rowwise_cast_to_fp8(w)
+    ms = timeit(lambda: o.gemm_fp8(a8, b8, sa, sb, None, False), a.iters)
+    report(f"gemm fp8 e4m3 M={M} N={N} K={K} (row/col scales, bf16 out)", ms, flops=2.0 * M * N * K)
+    ms_c = timeit(lambda: o.fp8_row_cast(x), a.iters)
+    report(f"  per-token e4m3 cast [{M}x{K}]", ms_c, bytes_=M * K * 3.0)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ms_b = timeit(lambda: o.gemm(x, w, out, None, False, False, False, 0), a.iters)
+    report("  bf16 kernel, same shape", ms_b, flops=2.0 * M * N * K)
+    if a.compare:
+        try:
+            ms2 = timeit(lambda: torch._scaled_mm(a8, b8.t(), scale_a=sa[:, None], scale_b=sb[None, :], out_dtype=torch.bfloat16), a.iters)
+            report("  cuBLASLt (torch._scaled_mm, row-wise scales) same shape", ms2, flops=2.0 * M * N * K)
+        except Exception as e:  # noqa: BLE001
+            print(f"  torch._scaled_mm unavailable: {type(e).__name__}: {str(e)[:120]}", flush=True)
+
+
 def bench_attn(a, backward=False):
     from verl_b200 import ops
 
@@ -186,7 +212,7 @@ def bench_fused_gather(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "lmhead", "decode_attn", "elementwise", "fused_gather", "all"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "attn_fwd", "attn_bwd", "lmhead", "decode_attn", "elementwise", "fused_gather", "all"])
     ap.add_argument("--world", type=int, default=2)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -210,6 +236,8 @@ def main():
     _ext.load()
     if a.kernel in ("gemm", "all"):
         bench_gemm(a)
+    if a.kernel in ("gemm_fp8", "all"):
+        bench_gemm_fp8(a)
     if a.kernel == "fused_gather":
         bench_fused_gather(a)
     if a.kernel in ("attn_fwd", "all"):

@@ -13,7 +13,7 @@ import torch
 from . import _ext
 from .functional import use_native
 
-__all__ = ["blockwise_cast_to_fp8", "act_cast_to_fp8", "dequant_blockwise_fp8", "fp4_fake_quant", "fp4_fake_quant_ste", "QATLinear",
+__all__ = ["blockwise_cast_to_fp8", "act_cast_to_fp8", "dequant_blockwise_fp8", "rowwise_cast_to_fp8", "fp8_gemm", "fp8_linear", "FP8Linear", "fp4_fake_quant", "fp4_fake_quant_ste", "QATLinear",
            "FP8_MAX", "FP4_MAX"]
 
 FP8_MAX, FP4_MAX = 448.0, 6.0
@@ -43,6 +43,59 @@ def act_cast_to_fp8(x: torch.Tensor):
     if use_native(x) and x.shape[1] % 4 == 0:
         return _ext.ops().fp8_act_cast(x if x.stride(1) == 1 else x.contiguous())
     return _blockwise_ref(x, 1, 128)
+
+
+def rowwise_cast_to_fp8(x: torch.Tensor):
+    """One scale per row: ``(fp8 [M, K], scale [M])``, ``scale = max(absmax(row), 1e-12) / 448``. Per-token for activations,
+    per-output-channel for ``[N, K]`` weights — the scales then factor out of the K sum and the GEMM applies them in its
+    epilogue (``fp8_gemm``)."""
+    assert x.dim() == 2
+    if use_native(x) and x.shape[1] % 8 == 0:
+        return _ext.ops().fp8_row_cast(x if x.stride(1) == 1 else x.contiguous())
+    s = x.float().abs().amax(-1).clamp_min(1e-12) / FP8_MAX
+    return (x.float() / s[:, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), s
+
+
+def fp8_gemm(a8: torch.Tensor, b8: torch.Tensor, a_scale: torch.Tensor = None, b_scale: torch.Tensor = None, bias: torch.Tensor = None,
+             out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``diag(a_scale) · (a8 @ b8ᵀ) · diag(b_scale) (+ bias)`` with e4m3 operands ``a8 [M, K]``, ``b8 [N, K]``.
+
+    On sm_100a this is one tcgen05 ``kind::f8f6f4`` kernel on SM pairs (256×256 tiles, fp32 accumulation in TMEM, scales and
+    bias in the epilogue); elsewhere the operands are dequantised and multiplied in fp32."""
+    if a8.is_cuda and _ext.available() and a8.shape[1] % 16 == 0 and out_dtype in (torch.bfloat16, torch.float32):
+        a8 = a8 if a8.stride(1) == 1 and a8.stride(0) % 16 == 0 else a8.contiguous()
+        b8 = b8 if b8.stride(1) == 1 and b8.stride(0) % 16 == 0 else b8.contiguous()
+        return _ext.ops().gemm_fp8(a8, b8, a_scale, b_scale, bias, out_dtype == torch.float32)
+    y = a8.float() @ b8.float().t()
+    if a_scale is not None:
+        y = y * a_scale[:, None] * b_scale[None, :]
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(out_dtype)
+
+
+def fp8_linear(x: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor, bias: torch.Tensor = None) -> torch.Tensor:
+    """W8A8 linear for inference: ``x`` (bf16, any leading shape) is quantised per token on the fly, ``w8 / w_scale`` come from
+    ``rowwise_cast_to_fp8(weight)``."""
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    a8, a_s = rowwise_cast_to_fp8(x2)
+    return fp8_gemm(a8, w8, a_s, w_scale, bias, x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.bfloat16).reshape(*shp[:-1], w8.shape[0])
+
+
+class FP8Linear(torch.nn.Module):
+    """Frozen linear layer with per-output-channel e4m3 weights (built from a bf16 weight), dynamic per-token activations."""
+
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor = None):
+        super().__init__()
+        w8, ws = rowwise_cast_to_fp8(weight.detach())
+        self.register_buffer("weight", w8)
+        self.register_buffer("weight_scale", ws)
+        self.register_buffer("bias", bias.detach().clone() if bias is not None else None)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return fp8_linear(x, self.weight, self.weight_scale, self.bias)
 
 
 def dequant_blockwise_fp8(q: torch.Tensor, scale: torch.Tensor, block_size=(128, 128), dtype=torch.bfloat16) -> torch.Tensor:

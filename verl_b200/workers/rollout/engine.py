@@ -86,13 +86,20 @@ def _sample_reference(logits: torch.Tensor, temperature: float, top_k: int, top_
 class InferenceEngine:
     def __init__(self, model: DecoderLM, max_num_seqs: int = 256, max_model_len: int = 2048, num_blocks: Optional[int] = None,
                  max_num_batched_tokens: int = 8192, gpu_memory_utilization: float = 0.5, enforce_eager: bool = False,
-                 sync_interval: int = 16, enable_prefix_sharing: bool = True, decode_splits: int = 0, tp_group=None, tp_ctx=None):
+                 sync_interval: int = 16, enable_prefix_sharing: bool = True, decode_splits: int = 0, tp_group=None, tp_ctx=None,
+                 quantization: Optional[str] = None):
         """``tp_group`` / ``tp_ctx``: tensor-parallel replica. ``model`` is then this rank's slice (``build_rollout_shard``); every
         rank of the group runs the same requests in lockstep (same scheduler decisions, same sampled tokens) and the
         row-parallel projections end in an all-reduce — fused into the GEMM epilogue over NVLink peer memory when
         ``tp_ctx`` (a ``TPContext``) is given, NCCL otherwise."""
         self.model = model
         self.tp_group, self.tp = tp_group, tp_ctx
+        # "fp8": W8A8 projections (per-output-channel e4m3 weights re-quantised from the live bf16 weights at every wake_up,
+        # per-token e4m3 activations, tcgen05 f8f6f4 GEMM); embeddings, norms, lm_head and the KV cache stay bf16.
+        # Reference: FP8 rollout, verl/utils/fp8_utils.py + verl/utils/kernel/fp8_kernel.py (weights quantised during sync).
+        assert quantization in (None, "", "fp8"), f"unsupported rollout quantization {quantization!r}"
+        self.quantization = quantization or None
+        self._w8: dict = {}
         self.cfg = model.cfg
         self.device = model.embed_tokens.device
         self.dtype = model.embed_tokens.dtype
@@ -157,8 +164,31 @@ class InferenceEngine:
         finally:
             self.stats["t_wake"] += self._tick() - t0
 
+    def _quantise_weights(self):
+        """(Re)build the e4m3 copies of the dense projection weights from the current bf16 weights."""
+        self._w8 = {}
+        if self.quantization != "fp8" or not self.native or self.tp_group is not None:
+            return
+        from verl_b200.ops.quant import rowwise_cast_to_fp8
+
+        for layer in self.model.layers:
+            ws = [layer.self_attn.qkv_proj, layer.self_attn.o_proj]
+            if not self.cfg.is_moe:
+                ws += [layer.mlp.gate_up_proj, layer.mlp.down_proj]
+            for w in ws:
+                self._w8[id(w)] = rowwise_cast_to_fp8(w.detach())
+
+    def _linear(self, x: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
+        q = self._w8.get(id(w))
+        if q is None:
+            return ops.linear(x, w, bias)
+        from verl_b200.ops.quant import fp8_linear
+
+        return fp8_linear(x, q[0], q[1], bias)
+
     def _wake_up_impl(self):
         c = self.cfg
+        self._quantise_weights()
         nb = self._decide_num_blocks()
         self.num_blocks = nb
         # zero-filled: masked (probability 0) positions still enter the P·V product, so they must hold finite values
@@ -197,6 +227,7 @@ class InferenceEngine:
         self.cache = None
         self.sched = None
         self.workspace = None
+        self._w8 = {}
         for n in ("hist_tok", "hist_lp", "block_table", "cur_tokens", "positions", "kv_lens", "active"):
             if hasattr(self, n):
                 delattr(self, n)
@@ -218,7 +249,7 @@ class InferenceEngine:
             else:
                 x, res = ops.add_rmsnorm(h, res, layer.input_layernorm, c.rms_norm_eps)
             at = layer.self_attn
-            qkv = ops.linear(x, at.qkv_proj, at.qkv_bias)
+            qkv = self._linear(x, at.qkv_proj, at.qkv_bias)
             if c.qk_norm:
                 T = qkv.shape[0]
                 q, k, v = qkv.split([c.q_size, c.kv_size, c.kv_size], dim=-1)
@@ -232,6 +263,8 @@ class InferenceEngine:
             x, res = ops.add_rmsnorm(a, res, layer.post_attention_layernorm, c.rms_norm_eps)
             if self.tp_group is not None and not c.is_moe:
                 h = self._row_parallel(ops.swiglu(ops.linear(x, layer.mlp.gate_up_proj)), layer.mlp.down_proj)
+            elif self._w8 and not c.is_moe:
+                h = self._linear(ops.swiglu(self._linear(x, layer.mlp.gate_up_proj)), layer.mlp.down_proj)
             else:
                 h = layer.mlp(x)
         return ops.add_rmsnorm(h, res, m.norm, c.rms_norm_eps)[0]
@@ -251,7 +284,7 @@ class InferenceEngine:
     def _row_parallel(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """``x @ wᵀ`` summed over the tensor-parallel ranks (plain GEMM when the replica is a single GPU)."""
         if self.tp_group is None:
-            return ops.linear(x, w)
+            return self._linear(x, w)
         if self.tp is not None:
             return self.tp.gemm_allreduce(x.contiguous(), w)
         import torch.distributed as dist
