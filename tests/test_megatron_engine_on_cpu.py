@@ -46,7 +46,17 @@ for n, p in eng.model.named_parameters():
         mg = unshard_param(g, parts, cfg)
     grads[g] = mg
 gn = eng.optimizer_step()
-torch.save({"grads": grads, "gn": gn, "lp": lp, "ent": ent, "dp_rank": eng.dp_rank, "exported": exported if rank == 0 else None,
+after = None
+if os.environ.get("CKPT"):
+    # Megatron-layout checkpoint: save, take another step, reload -> parameters and optimizer state are back
+    eng.save_checkpoint(os.environ["CKPT"], global_step=1)
+    after = {k: v.clone() for k, v in eng.get_per_tensor_param()[0]}
+    flat0, m0, step0 = eng.store.flat.clone(), eng.exp_avg.clone(), eng.step_count
+    eng.optimizer_zero_grad(); eng.forward_backward_batch(data, loss_fn); eng.optimizer_step()
+    assert not torch.equal(eng.store.flat, flat0)
+    eng.load_checkpoint(os.environ["CKPT"])
+    assert torch.equal(eng.store.flat, flat0) and torch.equal(eng.exp_avg, m0) and eng.step_count == step0
+torch.save({"grads": grads, "after": after if rank == 0 else None, "gn": gn, "lp": lp, "ent": ent, "dp_rank": eng.dp_rank, "exported": exported if rank == 0 else None,
             "src": eng.is_mp_src_rank_with_outputs()}, os.environ["OUT"] + f".{rank}")
 dist.barrier()
 '''
@@ -73,6 +83,9 @@ def test_parallel_ranks_match_single_rank(tmp_path, world, tp, pp, tied, sp):
     script.write_text(WORKER)
     out = tmp_path / "out.pt"
     env = dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1", TP=str(tp), PP=str(pp), TIED="1" if tied else "0", SP="1" if sp else "0")
+    ckpt = tmp_path / "ckpt"
+    if (world, tp, pp) in ((4, 2, 2), (4, 1, 2)) and not sp:
+        env["CKPT"] = str(ckpt)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
                         "--master-port", str(29660 + world + tp + (10 if sp else 0)), str(script)], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
@@ -105,6 +118,24 @@ def test_parallel_ranks_match_single_rank(tmp_path, world, tp, pp, tied, sp):
     assert set(res[0]["exported"]) == set(want)
     for k, v in want.items():
         assert torch.equal(res[0]["exported"][k], v), k
+    if "CKPT" in env:
+        # the merger rebuilds parallelism-independent HF weights from the (tp, pp, dp) shards
+        for f in ("transformer_config.json", "ckpt_contents.json", "model/huggingface/config.json", "model/dist_ckpt/shard_tp0_pp1_dp0.pt",
+                  "optimizer/dist_ckpt/shard_tp0_pp0_dp0.pt", "extra/dist_ckpt/shard_tp0_pp0_dp0.pt"):
+            assert (ckpt / f).exists(), f
+        from safetensors.torch import load_file
+
+        from verl_b200.model_merger.__main__ import main as merger_main
+
+        merger_main(["merge", "--backend", "megatron", "--local_dir", str(ckpt), "--target_dir", str(tmp_path / "hf")])
+        merged = {}
+        for fn in os.listdir(tmp_path / "hf"):
+            if fn.endswith(".safetensors"):
+                merged.update(load_file(str(tmp_path / "hf" / fn)))
+        after = res[0]["after"]
+        assert set(merged) == set(after)
+        for k, v in after.items():
+            assert torch.equal(merged[k].float(), v.to(torch.bfloat16).float()), k
 
 
 def test_grpo_fit_with_tensor_and_pipeline_parallel_actor(tmp_path):

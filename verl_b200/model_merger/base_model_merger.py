@@ -67,7 +67,7 @@ class ModelMergerConfig:
 def generate_config_from_args(args) -> ModelMergerConfig:
     common = dict(operation=args.operation, backend=args.backend, tie_word_embedding=args.tie_word_embedding,
                   trust_remote_code=args.trust_remote_code, is_value_model=args.is_value_model, local_dir=args.local_dir,
-                  hf_model_config_path=os.path.join(args.local_dir, "huggingface"), use_cpu_initialization=args.use_cpu_initialization)
+                  hf_model_config_path=os.path.join(args.local_dir, "model", "huggingface") if args.backend == "megatron" else os.path.join(args.local_dir, "huggingface"), use_cpu_initialization=args.use_cpu_initialization)
     if args.operation == "merge":
         cfg = ModelMergerConfig(**common, target_dir=args.target_dir, hf_upload_path=args.hf_upload_path, private=args.private, test_hf_dir=None)
         os.makedirs(cfg.target_dir, exist_ok=True)

@@ -141,9 +141,9 @@ class MegatronEngine(FSDPEngine):
         self._dup_ranges = self._replicated_ranges()
         if not self.forward_only:
             self._build_optimizer()
-        from verl_b200.utils.checkpoint.fsdp_checkpoint_manager import FSDPCheckpointManager
+        from verl_b200.utils.checkpoint.megatron_checkpoint_manager import MegatronCheckpointManager
 
-        self.checkpoint_manager = FSDPCheckpointManager(self, self.checkpoint_config)
+        self.checkpoint_manager = MegatronCheckpointManager(self, self.checkpoint_config)
         if self._param_offload:
             self.to("cpu", model=True, optimizer=False, grad=False)
         if self._optimizer_offload and not self.forward_only:
