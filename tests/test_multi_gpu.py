@@ -274,3 +274,31 @@ def test_tensor_parallel_rollout_replica(tmp_path, world):
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
                         "--master-port", "29689", str(script)], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0 and "ROLLOUT_TP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_weight_push_to_a_replica_process_on_another_gpu(tmp_path):
+    """Separate-pool weight hand-off: the trainer's parameter buffer on GPU 0 is exported through a CUDA IPC handle and a
+    rollout server process on GPU 1 copies it device-to-device; the replica then holds the trainer's weights and generates."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from verl_b200.models.config import PRESETS
+    from verl_b200.workers.engine.fsdp.engine import FSDPEngine
+    from verl_b200.workers.rollout.replica import RolloutMode, RolloutReplica
+
+    torch.cuda.set_device(0)
+    eng = FSDPEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 5}, {"lr": 1e-4}, {})
+    eng.initialize()
+    replica = RolloutReplica(0, {}, mode=RolloutMode.STANDALONE).init_standalone(
+        "tiny-qwen2-gpu", device="1", extra_args=["--max-num-seqs", "8", "--max-model-len", "256", "--num-blocks", "64", "--seed", "0"])
+    try:
+        before = replica.weights_version(checksum=True)
+        want = float(sum(p.detach().double().sum() for p in eng.model.parameters()))
+        assert abs(before["checksum"] - want) > 1e-3          # different seed: different weights
+        v = replica.update_weights(eng.export_weights_source())
+        after = replica.weights_version(checksum=True)
+        assert v == 1 and after["weights_version"] == 1
+        assert abs(after["checksum"] - want) <= 1e-6 * max(1.0, abs(want)), (after["checksum"], want)
+        out = replica._post("/generate", {"prompt_ids": list(range(10, 40)), "sampling_params": {"max_tokens": 8, "temperature": 1.0}})
+        assert len(out["token_ids"]) == 8
+    finally:
+        replica.shutdown()

@@ -110,3 +110,39 @@ def test_distillation_losses():
     loss, m = topk_distillation_loss(sh, th, torch.ones(2, 3), "jsd")
     loss.backward()
     assert s.grad is not None and 0 <= m["distill/top1_agreement"] <= 1
+
+
+def test_v1_separate_async_trainer_feeds_a_standalone_replica_and_pushes_weights(tmp_path):
+    """Rollout runs in its own server process; the trainer streams prompts to it over HTTP and hands over new weights after
+    every update (file hand-off on CPU). The replica ends with exactly the trainer's weights."""
+    import os
+
+    logf = tmp_path / "sep.jsonl"
+    os.environ["VERL_FILE_LOGGER_PATH"] = str(logf)
+    try:
+        cfg = load_config("ppo_trainer", [o for o in OV if not o.startswith("trainer.logger")] +
+                          ["trainer.logger=[file]", "trainer.total_training_steps=2", f"trainer.default_local_dir={tmp_path}/ckpt_sep",
+                           "actor_rollout_ref.rollout.mode=async", "actor_rollout_ref.rollout.free_cache_engine=false", "trainer.resume_mode=disable",
+                           "+trainer.v1.max_off_policy_threshold=3", "+trainer.v1.async_warmup_batches=1", "+trainer.v1.rollout_num_blocks=64"])
+        tr = get_trainer_cls("separate_async")(cfg, reward_fn=load_reward_manager(cfg, None))
+        tr.init()
+        assert len(tr.replicas) == 1 and tr.replicas[0].address and tr.replicas[0]._proc is not None
+        replica = tr.replicas[0]
+        orig_end = tr.on_train_end
+        seen = {}
+
+        def end():
+            seen.update(replica.weights_version(checksum=True))
+            orig_end()
+
+        tr.on_train_end = end
+        tr.fit()
+    finally:
+        os.environ.pop("VERL_FILE_LOGGER_PATH", None)
+    rows = [json.loads(x)["data"] for x in logf.read_text().splitlines()]
+    assert len(rows) == 2 and rows[-1]["sync/param_version"] == 3 and rows[-1]["perf/total_num_tokens"] > 0
+    assert seen["weights_version"] == 3                       # initial hand-off + one per step
+    eng = tr.stages.actor_rollout_wg.worker.actor.engine
+    want = float(sum(p.detach().double().sum() for p in eng.model.parameters()))
+    assert abs(seen["checksum"] - want) < 1e-6 * max(1.0, abs(want))
+    assert replica._proc.poll() is not None                   # the pool was shut down with the trainer

@@ -5,6 +5,7 @@ land in the queue → ``ReplayBuffer.sample`` picks whole prompt groups → the 
 values, advantages, updates) → weight hand-off. Subclasses decide how far generation may run ahead of training:
 
 * ``PPOTrainerSync``            on-policy: submit one batch, wait for it, train;
+* ``PPOTrainerSeparateAsync``   rollout replicas on their own GPUs (server processes); weights are pushed after every update;
 * ``PPOTrainerColocateAsync``   keeps ``async_warmup_batches`` batches in flight on the shared GPUs; when
                                 ``switch_threshold`` of the needed groups are ready the rest is interrupted and resumed
                                 after the update (partial rollout), stale groups are evicted.
@@ -48,7 +49,7 @@ def register_trainer(name: str):
 
 def get_trainer_cls(name: str):
     if name not in _TRAINERS:
-        from . import trainer_colocate_async, trainer_sync  # noqa: F401
+        from . import trainer_colocate_async, trainer_separate_async, trainer_sync  # noqa: F401
 
     if name not in _TRAINERS:
         raise ValueError(f"unknown v1 trainer {name!r}; known: {sorted(_TRAINERS)}")

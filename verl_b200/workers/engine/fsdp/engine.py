@@ -716,6 +716,34 @@ class FSDPEngine(BaseEngine):
         return self.model.hf_named_tensors(), None
 
     # ------------------------------------------------------------------ checkpoint
+    def export_weights_source(self, file_path: Optional[str] = None) -> dict:
+        """Description of the current bf16 weights that a rollout replica in ANOTHER process can pull
+        (``AsyncRolloutServer.update_weights``). On CUDA the flat parameter buffer is copied into an export buffer that was
+        allocated outside the caching allocator and its CUDA IPC handle is returned: the replica maps it and copies
+        device-to-device over NVLink, no collective spans the two jobs. On CPU (or with ``file_path`` given) the buffer is
+        written to a file instead."""
+        s = self.store
+        layout = {"names": list(s.names), "shapes": [list(p.shape) for p in s.params], "offsets": [int(o) for o in s.offsets],
+                  "dtype": str(s.flat.dtype).replace("torch.", "")}
+        if s.flat.is_cuda and file_path is None:
+            import base64
+
+            from verl_b200.ops import _ext
+
+            ops_ = _ext.ops()
+            nbytes = s.flat.numel() * s.flat.element_size()
+            if getattr(self, "_export_ptr", None) is None:
+                self._export_ptr = int(ops_.symm_alloc(nbytes))
+                self._export_handle = base64.b64encode(ops_.ipc_get_handle(self._export_ptr).numpy().tobytes()).decode()
+            ops_.tensor_from_ptr(self._export_ptr, [s.flat.numel()], s.flat.dtype).copy_(s.flat)
+            torch.cuda.synchronize()
+            return {"kind": "cuda_ipc", "handle": self._export_handle, "nbytes": nbytes, **layout}
+        assert file_path is not None, "a file path is needed to export weights from a CPU engine"
+        tmp = file_path + ".tmp"
+        torch.save({"flat": s.flat.detach().to("cpu"), **layout}, tmp)
+        os.replace(tmp, file_path)
+        return {"kind": "file", "path": file_path}
+
     def save_checkpoint(self, local_path, hdfs_path=None, global_step=0, max_ckpt_to_keep=None, **kwargs):
         self.checkpoint_manager.save_checkpoint(local_path, hdfs_path, global_step, max_ckpt_to_keep)
 

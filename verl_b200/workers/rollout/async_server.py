@@ -93,6 +93,62 @@ class AsyncRolloutServer:
         self._stop.set()
         self._thread.join(timeout=30)
 
+    # ------------------------------------------------------------------ weight hand-off (replicas on their own GPUs)
+    def update_weights(self, source: dict) -> int:
+        """Replace the model weights of this replica from ``source`` and return the new weights version.
+
+        The running batch is interrupted (its requests come back ``aborted`` with their partial output, resumable clients
+        continue them under the new weights), admission is paused while the copy runs. ``source`` describes a flat parameter
+        buffer and its layout (``names / shapes / offsets``):
+
+        * ``{"kind": "cuda_ipc", "handle": <base64 CUDA IPC handle>, "nbytes": n, "dtype": "bfloat16", ...}`` — the trainer's
+          export buffer on another GPU of this machine; it is mapped here and copied device-to-device over NVLink;
+        * ``{"kind": "file", "path": p, ...}`` — a ``torch.save``d dict holding ``flat`` (CPU path, also the fallback).
+        """
+        import base64
+
+        import torch
+
+        self.pause()
+        try:
+            self.abort_all_requests()
+            self.wait_idle()
+            params = dict(self.engine.model.named_parameters())
+            opened = None
+            if source["kind"] == "cuda_ipc":
+                from verl_b200.ops import _ext
+
+                ops_ = _ext.ops()
+                hb = torch.frombuffer(bytearray(base64.b64decode(source["handle"])), dtype=torch.uint8)
+                opened = int(ops_.ipc_open_handle(hb))
+                dt = getattr(torch, source.get("dtype", "bfloat16"))
+                flat = ops_.tensor_from_ptr(opened, [int(source["nbytes"]) // torch.empty(0, dtype=dt).element_size()], dt)
+                layout = source
+            elif source["kind"] == "file":
+                layout = torch.load(source["path"], map_location="cpu", weights_only=False)
+                flat = layout["flat"]
+            else:
+                raise ValueError(f"unknown weight source kind {source['kind']!r}")
+            with torch.no_grad():
+                for name, shape, off in zip(layout["names"], layout["shapes"], layout["offsets"]):
+                    n = 1
+                    for d in shape:
+                        n *= int(d)
+                    params[name].copy_(flat[int(off): int(off) + n].view(*[int(d) for d in shape]))
+            if opened is not None:
+                torch.cuda.synchronize()
+                ops_.ipc_close(opened)
+            self.weights_version = getattr(self, "weights_version", 0) + 1
+        finally:
+            self.resume()
+        return self.weights_version
+
+    def weights_checksum(self) -> float:
+        import torch
+
+        with torch.no_grad():
+            return float(sum(p.double().sum() for p in self.engine.model.parameters()))
+
     # ------------------------------------------------------------------ server thread
     def _take(self, key) -> list[tuple]:
         """Queued requests compatible with ``key`` (everything else is held back for the next batch)."""
@@ -212,6 +268,17 @@ def build_http_app(server: AsyncRolloutServer):
         await asyncio.get_running_loop().run_in_executor(None, server.abort_all_requests)
         return web.json_response({"status": "aborted"})
 
+    async def update_weights(req):
+        body = await req.json()
+        v = await asyncio.get_running_loop().run_in_executor(None, server.update_weights, body)
+        return web.json_response({"status": "ok", "weights_version": v})
+
+    async def weights_version(req):
+        d = {"weights_version": getattr(server, "weights_version", 0)}
+        if req.query.get("checksum"):
+            d["checksum"] = await asyncio.get_running_loop().run_in_executor(None, server.weights_checksum)
+        return web.json_response(d)
+
     async def sleep(_):
         await asyncio.get_running_loop().run_in_executor(None, server.sleep)
         return web.json_response({"status": "sleeping"})
@@ -223,7 +290,7 @@ def build_http_app(server: AsyncRolloutServer):
     app = web.Application(client_max_size=256 * 1024 * 1024)
     app.add_routes([web.post("/generate", generate), web.post("/v1/completions", completions), web.post("/v1/chat/completions", chat),
                     web.get("/health", health), web.get("/metrics", metrics), web.post("/abort", abort), web.post("/sleep", sleep),
-                    web.post("/wake_up", wake)])
+                    web.post("/wake_up", wake), web.post("/update_weights", update_weights), web.get("/weights_version", weights_version)])
     return app
 
 

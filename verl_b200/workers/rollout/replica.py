@@ -68,18 +68,58 @@ class RolloutReplica:
         self.mode = RolloutMode.STANDALONE
         return self
 
+    def init_remote(self, address: str):
+        """Attach to a replica that already serves at ``host:port`` (started by another job or by ``init_standalone``)."""
+        self.address, self.mode = address, RolloutMode.STANDALONE
+        return self
+
     # ------------------------------------------------------------------ control
+    def _post(self, path: str, body: Optional[dict] = None, timeout: float = 600.0) -> dict:
+        import json
+        import urllib.request
+
+        req = urllib.request.Request(f"http://{self.address}{path}", data=json.dumps(body or {}).encode(), headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=timeout) as r:
+            return json.loads(r.read().decode())
+
+    def _get(self, path: str, timeout: float = 600.0) -> dict:
+        import json
+        import urllib.request
+
+        with urllib.request.urlopen(f"http://{self.address}{path}", timeout=timeout) as r:
+            return json.loads(r.read().decode())
+
     def wake_up(self):
         if self.server is not None:
             self.server.wake_up()
+        elif self.address:
+            self._post("/wake_up")
 
     def sleep(self):
         if self.server is not None:
             self.server.sleep()
+        elif self.address:
+            self._post("/sleep")
 
     def abort_all_requests(self):
         if self.server is not None:
             self.server.abort_all_requests()
+        elif self.address:
+            self._post("/abort")
+
+    def update_weights(self, source: dict) -> int:
+        """Hand new weights to the replica (see ``AsyncRolloutServer.update_weights``); returns its weights version."""
+        if self.server is not None:
+            return self.server.update_weights(source)
+        return int(self._post("/update_weights", source)["weights_version"])
+
+    def weights_version(self, checksum: bool = False) -> dict:
+        if self.server is not None:
+            d = {"weights_version": getattr(self.server, "weights_version", 0)}
+            if checksum:
+                d["checksum"] = self.server.weights_checksum()
+            return d
+        return self._get("/weights_version" + ("?checksum=1" if checksum else ""))
 
     def shutdown(self):
         if self._stop_http:
