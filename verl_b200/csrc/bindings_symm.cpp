@@ -36,6 +36,16 @@ int64_t ipc_open_handle(const Tensor& h) {
 }
 void ipc_close(int64_t ptr) { vb_ipc_close(ptr); }
 
+// dst (local tensor) <- nbytes from a device pointer that may be another GPU's memory mapped through CUDA IPC. The copy is
+// one DMA transfer (cudaMemcpyAsync, no kernel reads the peer's memory); consumers then work on the local copy.
+void peer_memcpy(Tensor& dst, int64_t src_ptr, int64_t nbytes) {
+  TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && (int64_t)(dst.numel() * dst.element_size()) >= nbytes, "peer_memcpy: dst too small or not contiguous");
+  c10::cuda::CUDAGuard guard(dst.device());
+  cudaError_t e = cudaMemcpyAsync(dst.data_ptr(), reinterpret_cast<const void*>(src_ptr), (size_t)nbytes, cudaMemcpyDeviceToDevice,
+                                  at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(e == cudaSuccess, "peer_memcpy: ", cudaGetErrorString(e));
+}
+
 // Non-owning tensor view on raw device memory.
 Tensor tensor_from_ptr(int64_t ptr, at::IntArrayRef sizes, at::ScalarType dtype) {
   int dev = at::cuda::current_device();
@@ -85,6 +95,7 @@ TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
   m.def("ipc_get_handle(int ptr) -> Tensor", &ipc_get_handle);
   m.def("ipc_open_handle(Tensor h) -> int", &ipc_open_handle);
   m.def("ipc_close(int ptr) -> ()", &ipc_close);
+  m.def("peer_memcpy(Tensor(a!) dst, int src_ptr, int nbytes) -> ()", &peer_memcpy);
   m.def("tensor_from_ptr(int ptr, int[] sizes, ScalarType dtype) -> Tensor", &tensor_from_ptr);
   m.def("symm_barrier(Tensor pad_ptrs, int rank, int world, int epoch) -> ()", &symm_barrier);
   m.def("symm_barrier_auto(Tensor pad_ptrs, int rank, int world) -> ()", &symm_barrier_auto);

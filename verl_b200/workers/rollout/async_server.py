@@ -122,7 +122,13 @@ class AsyncRolloutServer:
                 hb = torch.frombuffer(bytearray(base64.b64decode(source["handle"])), dtype=torch.uint8)
                 opened = int(ops_.ipc_open_handle(hb))
                 dt = getattr(torch, source.get("dtype", "bfloat16"))
-                flat = ops_.tensor_from_ptr(opened, [int(source["nbytes"]) // torch.empty(0, dtype=dt).element_size()], dt)
+                dev = next(iter(params.values())).device
+                # one DMA transfer into local memory; the per-tensor copies below then read this GPU's own memory
+                flat = torch.empty(int(source["nbytes"]) // torch.empty(0, dtype=dt).element_size(), dtype=dt, device=dev)
+                ops_.peer_memcpy(flat, opened, int(source["nbytes"]))
+                torch.cuda.synchronize()
+                ops_.ipc_close(opened)
+                opened = None
                 layout = source
             elif source["kind"] == "file":
                 layout = torch.load(source["path"], map_location="cpu", weights_only=False)
@@ -136,7 +142,6 @@ class AsyncRolloutServer:
                         n *= int(d)
                     params[name].copy_(flat[int(off): int(off) + n].view(*[int(d) for d in shape]))
             if opened is not None:
-                torch.cuda.synchronize()
                 ops_.ipc_close(opened)
             self.weights_version = getattr(self, "weights_version", 0) + 1
         finally:

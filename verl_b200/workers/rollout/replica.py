@@ -50,10 +50,11 @@ class RolloutReplica:
 
         addr_file = tempfile.mktemp(prefix="verl_b200_replica_")
         env = dict(os.environ)
-        if device is not None:
-            env["CUDA_VISIBLE_DEVICES"] = str(device)
         cmd = [sys.executable, "-m", "verl_b200.workers.rollout.replica", "--model", model, "--port", str(port), "--address-file", addr_file,
                "--name", f"replica-{self.replica_rank}", *extra_args]
+        if device is not None:
+            # the other GPUs stay visible: weight hand-off maps the trainer's export buffer through CUDA IPC
+            cmd += ["--device", str(device)]
         self._proc = subprocess.Popen(cmd, env=env)
         t0 = time.time()
         while not os.path.exists(addr_file):
@@ -167,17 +168,21 @@ def main(argv=None):
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.8)
     ap.add_argument("--num-blocks", type=int, default=None)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--device", type=int, default=0, help="CUDA device index of this replica")
     a = ap.parse_args(argv)
-    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    dev = "cpu"
+    if torch.cuda.is_available():
+        torch.cuda.set_device(a.device)
+        dev = f"cuda:{a.device}"
     tok = None
     if a.model in PRESETS:
         cfg = PRESETS[a.model]
-        model = DecoderLM(cfg, dtype=torch.bfloat16 if dev == "cuda" else torch.float32, device=dev, seed=a.seed)
+        model = DecoderLM(cfg, dtype=torch.bfloat16 if dev != "cpu" else torch.float32, device=dev, seed=a.seed)
     else:
         from verl_b200.models.hf_io import load_hf_weights
 
         cfg = ModelConfig.from_pretrained(a.model)
-        model = DecoderLM(cfg, dtype=torch.bfloat16 if dev == "cuda" else torch.float32, device=dev, init=False)
+        model = DecoderLM(cfg, dtype=torch.bfloat16 if dev != "cpu" else torch.float32, device=dev, init=False)
         load_hf_weights(model, a.model)
         try:
             from transformers import AutoTokenizer
