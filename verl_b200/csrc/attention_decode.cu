@@ -19,7 +19,8 @@ constexpr int DT = 128;                 // kv rows per tile
 constexpr int DQ = 16;                  // padded query heads per kv head
 constexpr int D_TILE = DT * DD * 2;     // 32 KB
 constexpr int D_HALF = DT * 64 * 2;     // 16 KB : one 64-column swizzle atom of a K/V tile
-constexpr int D_STAGES = 1;             // one tile in flight per CTA; three CTAs share an SM and hide each other's TMA latency
+constexpr int D_STAGES = 1;             // one K and one V buffer per CTA: K(j+1) streams in during softmax + PV of tile j, V(j+1) during
+                                        // QK^T + softmax of tile j+1; three CTAs share an SM and hide the rest of the TMA latency
 constexpr int D_QBYTES = DQ * DD * 2;   // 4 KB : two atoms of 16 rows x 128 B
 constexpr int D_SMEM = D_STAGES * 2 * D_TILE + 2 * D_QBYTES + 1024 + 512;
 
@@ -46,7 +47,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* sP = sQ + D_QBYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + D_QBYTES);
   uint64_t* q_bar = bars;
-  uint64_t* kv_bar = bars + 1;          // [3]
+  uint64_t* k_bar = bars + 1;
+  uint64_t* v_bar = bars + 2;
   uint64_t* s_bar = bars + 4;
   uint64_t* o_bar = bars + 5;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
@@ -62,7 +64,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (tid == 0) {
     mbar_init(q_bar, 1);
-    for (int i = 0; i < D_STAGES; ++i) mbar_init(&kv_bar[i], 1);
+    mbar_init(k_bar, 1);
+    mbar_init(v_bar, 1);
     mbar_init(s_bar, 1);
     mbar_init(o_bar, 1);
     *abort_flag = 0;
@@ -79,21 +82,18 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t tm_S = tmem_base, tm_O = tmem_base + 16;
   const uint32_t lane_off = uint32_t(warp * 32) << 16;
 
-  auto load_kv = [&](int j) {  // thread 0
-    const int stage = j % D_STAGES;
-    uint8_t* sK = sKV + stage * 2 * D_TILE;
-    uint8_t* sV = sK + D_TILE;
-    mbar_expect_tx(&kv_bar[stage], 2 * D_TILE);
+  // which = 0: K rows of tile j into sK, which = 1: V rows into sV (thread 0)
+  auto load_half = [&](int j, int which) {
+    uint8_t* dst = sKV + which * D_TILE;
+    uint64_t* bar = which ? v_bar : k_bar;
+    mbar_expect_tx(bar, D_TILE);
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
       const int bi = (tile0 + j) * 2 + h2;
       const int blk = bi < p.max_blocks ? p.block_table[(long)b * p.max_blocks + bi] : 0;
-      const int yk = ((blk * 2 + 0) * p.n_kv_heads + kvh) * 64;
-      const int yv = ((blk * 2 + 1) * p.n_kv_heads + kvh) * 64;
-      tma_load_2d(sK + h2 * 64 * 128, &tmKV, 0, yk, &kv_bar[stage]);
-      tma_load_2d(sK + D_HALF + h2 * 64 * 128, &tmKV, 64, yk, &kv_bar[stage]);
-      tma_load_2d(sV + h2 * 64 * 128, &tmKV, 0, yv, &kv_bar[stage]);
-      tma_load_2d(sV + D_HALF + h2 * 64 * 128, &tmKV, 64, yv, &kv_bar[stage]);
+      const int y = ((blk * 2 + which) * p.n_kv_heads + kvh) * 64;
+      tma_load_2d(dst + h2 * 64 * 128, &tmKV, 0, y, bar);
+      tma_load_2d(dst + D_HALF + h2 * 64 * 128, &tmKV, 64, y, bar);
     }
   };
 
@@ -102,7 +102,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int qy = b * p.n_q_heads + kvh * p.group;
     tma_load_2d(sQ, &tmQ, 0, qy, q_bar);
     tma_load_2d(sQ + DQ * 128, &tmQ, 64, qy, q_bar);
-    for (int j = 0; j < D_STAGES && j < n_tiles; ++j) load_kv(j);
+    load_half(0, 0);
+    load_half(0, 1);
   }
 
   float m_run[DQ], l_run[DQ], o_acc[DQ];
@@ -116,11 +117,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (n_tiles > 0) ok = mbar_wait(q_bar, 0, abort_flag, p.err_word, VB_ERR_WAIT_MISC);
 
   for (int j = 0; j < n_tiles && ok; ++j) {
-    const int stage = j % D_STAGES;
-    const uint32_t kv_ph = (j / D_STAGES) & 1;
     const uint32_t it_ph = j & 1;
-    if (!mbar_wait(&kv_bar[stage], kv_ph, abort_flag, p.err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
-    uint8_t* sK = sKV + stage * 2 * D_TILE;
+    if (!mbar_wait(k_bar, it_ph, abort_flag, p.err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
+    uint8_t* sK = sKV;
     uint8_t* sV = sK + D_TILE;
     if (tid == 0) {
       tc_fence_after();
@@ -134,6 +133,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     if (!mbar_wait(s_bar, it_ph, abort_flag, p.err_word, VB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
     tc_fence_after();
+    if (tid == 0 && j + 1 < n_tiles) load_half(j + 1, 0);        // the K buffer is free once QK^T has completed
     uint32_t sv[DQ];
     tmem_ld_32x32b_x16(tm_S + lane_off, sv);
     tmem_ld_wait();
@@ -178,6 +178,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    if (!mbar_wait(v_bar, it_ph, abort_flag, p.err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
     if (tid == 0) {
       tc_fence_after();
       const uint32_t va = smem_u32(sV), pa = smem_u32(sP);
@@ -192,7 +193,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int q = 0; q < DQ; ++q) l_run[q] = l_run[q] * alpha[q] + red[q] + red[DQ + q] + red[2 * DQ + q] + red[3 * DQ + q];
     if (!mbar_wait(o_bar, it_ph, abort_flag, p.err_word, VB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
     tc_fence_after();
-    if (tid == 0 && j + D_STAGES < n_tiles) load_kv(j + D_STAGES);   // this tile's stage is free once its PV product is done
+    if (tid == 0 && j + 1 < n_tiles) load_half(j + 1, 1);        // the V buffer is free once the PV product has completed
     uint32_t ov[DQ];
     tmem_ld_32x32b_x16(tm_O + lane_off, ov);
     tmem_ld_wait();
