@@ -239,6 +239,27 @@ def test_gemm_pair_cta_group_2(a_mn, b_mn):
         torch.testing.assert_close(acc, ref + 1.0 + bias.float()[None], rtol=1e-3, atol=2e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 3584, 18944), (200, 1000, 4160), (512, 37888, 3584), (130, 256, 520)])
+def test_gemm_pair_split_k_for_decode_shapes(M, N, K):
+    """Decode-sized GEMMs on SM pairs with K slices (fp32 partial tiles + reduce pass) against an fp32 matmul."""
+    from verl_b200.ops import _ext
+
+    o = _ext.ops()
+    torch.manual_seed(M + N)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    ref = a.float() @ b.float().t()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    o.gemm(a, b, out, bias, False, False, False, 513)
+    _ext.check_status("gemm_pair split-k")
+    torch.testing.assert_close(out.float(), ref + bias.float()[None], rtol=2e-2, atol=0.2)
+    acc = torch.full((M, N), 2.0, device="cuda", dtype=torch.float32)
+    o.gemm(a, b, acc, None, False, False, True, 513)
+    _ext.check_status("gemm_pair split-k accumulate")
+    torch.testing.assert_close(acc, ref + 2.0, rtol=1e-3, atol=2e-2)
+
+
 def test_device_barrier_gives_up_with_a_status_when_the_peer_never_signals():
     """Failure detection on the device: the barrier of rank 0 in a 2-rank table whose second signal pad nobody ever writes
     runs into its time limit, records status 5 (peer wait) and returns; the context stays usable and the host-side check

@@ -77,8 +77,26 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Ten
              "gemm_pair");
     return;
   }
+  // decode-sized problems (one or two row blocks): the paired kernel with K slices reads every B tile once per pair
+  // (bn == 513 forces it, VERL_B200_GEMM_PAIR_SPLITK=1 makes it the automatic choice)
+  static const bool pair_split_auto = []() { const char* e = getenv("VERL_B200_GEMM_PAIR_SPLITK"); return e != nullptr && e[0] == '1'; }();
+  if (!a_mn && !b_mn && (bn == 513 || (bn == 0 && pair_auto && pair_split_auto && M > 128 && M <= 512))) {
+    const int s2 = vb_gemm_pair_plan((int)M, (int)N, (int)K);
+    if (s2 >= 1) {
+      Tensor ws2;
+      float* wp = nullptr;
+      if (s2 > 1) {
+        ws2 = at::empty({(int64_t)s2 * M * N}, a.options().dtype(at::kFloat));
+        wp = ws2.data_ptr<float>();
+      }
+      check_rc(vb_gemm_bf16_pair_splitk(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias_p, (int)M, (int)N, (int)K, (int)a.stride(0), (int)b.stride(0),
+                                        (int)out.stride(0), out_f32, accumulate, s2, wp, err, cur_stream()),
+               "gemm_pair_splitk");
+      return;
+    }
+  }
   int bn_sel = 0, split = 1;
-  vb_gemm_plan((int)M, (int)N, (int)K, b_mn, (int)bn, &bn_sel, &split);
+  vb_gemm_plan((int)M, (int)N, (int)K, b_mn, (int)bn == 513 ? 0 : (int)bn, &bn_sel, &split);
   Tensor ws;
   float* ws_p = nullptr;
   if (split > 1) {

@@ -19,6 +19,9 @@
 #include "common.cuh"
 #include "tma_host.h"
 
+extern "C" int vb_splitk_reduce(const float* ws, int S, int M, int N, void* out, int ldc, const void* bias, int out_f32, int accumulate,
+                                cudaStream_t stream);
+
 namespace vb {
 namespace pair {
 
@@ -109,7 +112,10 @@ template <int BN, bool A_MN, bool B_MN, bool FP8 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
                  const bf16* __restrict__ bias, int M, int N, int K, int ldc, int flags, int* err_word,
-                 const float* __restrict__ a_scale = nullptr, const float* __restrict__ b_scale = nullptr) {
+                 const float* __restrict__ a_scale, const float* __restrict__ b_scale, int split_k, int kb_per_split,
+                 float* __restrict__ split_ws) {
+  // split_k > 1: a work unit is (output tile, K slice); every slice stores its fp32 partial tile into
+  // split_ws[slice][M][N] and a reduce pass (vb_splitk_reduce) adds them up, applies bias / accumulate and casts
   static_assert(!FP8 || (!A_MN && !B_MN), "fp8 operands are K-major");
   constexpr int BKE = FP8 ? 2 * BK : BK;      // elements of K per stage
   using C = Cfg<BN>;
@@ -131,8 +137,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_pairs = gridDim.x >> 1;
   const int num_m = (M + 2 * BM - 1) / (2 * BM);
   const int num_n = (N + BN - 1) / BN;
-  const int num_kb = (K + BKE - 1) / BKE;
-  const int num_tiles = num_m * num_n;
+  const int num_kb_total = (K + BKE - 1) / BKE;
+  const int num_tiles = num_m * num_n * split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -159,7 +165,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
 
   constexpr int GROUP_M = 4;           // 4 x 256 rows share a B column block in L2
-  auto tile_coords = [&](int t, int& mb, int& nb) {
+  auto k_range = [&](int u, int& kb0, int& kb1) {
+    kb0 = (u % split_k) * kb_per_split;
+    kb1 = min(num_kb_total, kb0 + kb_per_split);
+  };
+  auto tile_coords = [&](int u, int& mb, int& nb) {
+    const int t = u / split_k;
     int per_group = GROUP_M * num_n;
     int g = t / per_group;
     int first_m = g * GROUP_M;
@@ -180,7 +191,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tile_coords(t, mb, nb);
         const int m0 = mb * 2 * BM + (int)rank * BM;
         const int n0 = nb * BN + (int)rank * (BN / 2);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int kb0, kb1;
+        k_range(t, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + s * C::STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
@@ -216,7 +229,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int kb0, kb1;
+        k_range(t, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, abort_flag, err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * C::STAGE_BYTES);
@@ -225,8 +240,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int k = 0; k < BK / UMMA_K; ++k) {
             uint64_t ad = A_MN ? make_sdesc_sw128(sa + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sa + k * 32, 16, 1024);
             uint64_t bd = B_MN ? make_sdesc_sw128(sb + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sb + k * 32, 16, 1024);
-            if constexpr (FP8) umma_f8_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
-            else umma_f16_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
+            if constexpr (FP8) umma_f8_pair(d_tmem, ad, bd, idesc, ((kb - kb0) | k) != 0);
+            else umma_f16_pair(d_tmem, ad, bd, idesc, ((kb - kb0) | k) != 0);
           }
           const uint32_t e_local = smem_u32(&empty_bar[s]);
           umma_commit_pair(map_to_cta(e_local, 0));
@@ -267,6 +282,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (split_k > 1) {
+            float* wrow = split_ws + ((size_t)(t % split_k) * M + row) * N + col0;
+            if (col0 + 32 <= N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(wrow + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) wrow[j] = f[j];
+            }
+            continue;
+          }
           if constexpr (FP8) {
             if (a_scale != nullptr) {
               const float rs = a_scale[row];
@@ -362,7 +388,7 @@ static int sm_count() {
 
 template <int BN, bool A_MN, bool B_MN>
 static int launch(const void* A, const void* B, void* Cp, const void* bias, int M, int N, int K, int lda, int ldb, int ldc, int flags,
-                  int* err_word, cudaStream_t stream) {
+                  int* err_word, cudaStream_t stream, int split_k = 1, float* split_ws = nullptr) {
   using C = Cfg<BN>;
   CUtensorMap tmA, tmB;
   int rc;
@@ -378,11 +404,18 @@ static int launch(const void* A, const void* B, void* Cp, const void* bias, int 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return -10;
     attr_set = true;
   }
-  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  const int num_kb = (K + BK - 1) / BK;
+  if (split_k < 1 || split_ws == nullptr) split_k = 1;
+  int kb_per = (num_kb + split_k - 1) / split_k;
+  split_k = (num_kb + kb_per - 1) / kb_per;            // no empty slices
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * split_k;
   int pairs = sm_count() / 2;
   if (tiles < pairs) pairs = tiles;
-  kern<<<2 * pairs, 192, C::SMEM_BYTES, stream>>>(tmA, tmB, Cp, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags, err_word, nullptr, nullptr);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  kern<<<2 * pairs, 192, C::SMEM_BYTES, stream>>>(tmA, tmB, Cp, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags, err_word, nullptr, nullptr,
+                                                  split_k, kb_per, split_ws);
+  if (cudaGetLastError() != cudaSuccess) return -11;
+  if (split_k > 1) return vb_splitk_reduce(split_ws, split_k, M, N, Cp, ldc, bias, (flags & OUT_F32) ? 1 : 0, (flags & ACCUM) ? 1 : 0, stream);
+  return 0;
 }
 
 static int launch_fp8(const void* A, const void* B, void* Cp, const void* bias, const float* a_scale, const float* b_scale, int M, int N,
@@ -400,7 +433,8 @@ static int launch_fp8(const void* A, const void* B, void* Cp, const void* bias, 
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
   int pairs = sm_count() / 2;
   if (tiles < pairs) pairs = tiles;
-  kern<<<2 * pairs, 192, C::SMEM_BYTES, stream>>>(tmA, tmB, Cp, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags, err_word, a_scale, b_scale);
+  kern<<<2 * pairs, 192, C::SMEM_BYTES, stream>>>(tmA, tmB, Cp, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags, err_word, a_scale, b_scale,
+                                                  1, (K + 2 * BK - 1) / (2 * BK), nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -422,6 +456,29 @@ extern "C" int vb_gemm_fp8_pair(const void* A, const void* B, void* C, const voi
 // Same contract as vb_gemm_bf16 without split-K: C[M,N] (+)= op(A) op(B) (+ bias), 256 x 256 tiles on SM pairs.
 // Requirements beyond vb_gemm_bf16's: N % 128 == 0 is NOT required (edges are masked), but the K-major B tile is
 // loaded in halves of 128 rows, so ldb and the base must satisfy the same 16-byte rules.
+// Number of K slices that lets decode-sized problems (few 256 x 256 tiles) occupy the SM pairs: 0 = the paired kernel is no fit.
+extern "C" int vb_gemm_pair_plan(int M, int N, int K) {
+  using namespace vb::pair;
+  if (M <= 128 || (N % 4) != 0) return 0;             // a pair needs rows for both CTAs; the reduce pass works on float4
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  const int pairs = sm_count() / 2;
+  if (tiles >= pairs) return 1;
+  const int num_kb = (K + BK - 1) / BK;
+  int s = pairs / tiles;
+  while (s > 1 && num_kb / s < 8) --s;                // keep at least 8 stages of K per slice
+  return s > 8 ? 8 : s;
+}
+
+extern "C" int vb_gemm_bf16_pair_splitk(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb, int ldc,
+                                        int out_f32, int accumulate, int split_k, float* split_ws, int* err_word, cudaStream_t stream) {
+  using namespace vb::pair;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return -3;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -4;
+  const int flags = (out_f32 ? OUT_F32 : 0) | (accumulate ? ACCUM : 0);
+  return launch<256, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream, split_k, split_ws);
+}
+
 extern "C" int vb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb, int ldc,
                                  int a_mn, int b_mn, int out_f32, int accumulate, int* err_word, cudaStream_t stream) {
   using namespace vb::pair;

@@ -753,6 +753,23 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   return 0;
 }
 
+}  // namespace vb
+
+// out[M,N] (+)= sum over S fp32 partials ws[s][M][N] (+ bias): the reduce pass of the split-K GEMMs, also used by the paired-CTA kernel.
+extern "C" int vb_splitk_reduce(const float* ws, int S, int M, int N, void* out, int ldc, const void* bias, int out_f32, int accumulate,
+                                cudaStream_t stream) {
+  using namespace vb;
+  if ((long)M * N % 4) return -2;
+  const long total4 = (long)M * N / 4;
+  int blocks = (int)((total4 + 255) / 256);
+  if (blocks > num_sms() * 8) blocks = num_sms() * 8;
+  const int flags = (out_f32 ? GEMM_OUT_F32 : 0) | (accumulate ? GEMM_ACCUM : 0);
+  splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(ws, S, M, N, out, ldc, reinterpret_cast<const bf16*>(bias), flags);
+  return cudaGetLastError() == cudaSuccess ? 0 : -12;
+}
+
+namespace vb {
+
 // Cost model for small problems that cannot fill the machine with 128x256 tiles: pick (tile width, K splits) minimising
 // waves x (bytes staged per unit / per-SM fill rate + fixed cost) + the reduce pass.
 static void pick_tile_and_split(int M, int N, int K, bool b_mn, int* bn_out, int* split_out) {
