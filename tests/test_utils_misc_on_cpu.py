@@ -161,3 +161,36 @@ def test_naive_rollout_matches_engine_greedy_and_engine_aliases():
     from verl_b200.utils.transformers_compat import drop_tied_weight_keys, is_transformers_version_in_range
 
     assert is_transformers_version_in_range("4.0") and "lm_head.weight" not in drop_tied_weight_keys({"lm_head.weight": 1, "a": 2}, True)
+
+
+def test_tool_call_dialects():
+    """Every chat-template family's function-call syntax parses to (name, JSON arguments) and is cut out of the content."""
+    import json
+
+    from verl_b200.experimental.agent_loop.tool_parser import get_tool_parser as g
+
+    cases = {
+        "glm": ('hi<tool_call>get_weather<arg_key>city</arg_key><arg_value>Paris</arg_value><arg_key>days</arg_key><arg_value>3</arg_value></tool_call>',
+                "hi", [("get_weather", {"city": "Paris", "days": 3})]),
+        "seed": ('<seed:tool_call><function=f><parameter=a>[1,2]</parameter></function></seed:tool_call>ok', "ok", [("f", {"a": [1, 2]})]),
+        "minimax": ('<minimax:tool_call><invoke name="s"><parameter name="q">x y</parameter></invoke><invoke name="t"></invoke></minimax:tool_call>',
+                    "", [("s", {"q": "x y"}), ("t", {})]),
+        "kimi": ('a<|tool_calls_section_begin|><|tool_call_begin|>functions.calc:0<|tool_call_argument_begin|>{"x": 1}<|tool_call_end|><|tool_calls_section_end|>',
+                 "a", [("calc", {"x": 1})]),
+        "deepseek_v4": ('<｜DSML｜tool_calls>\n<｜DSML｜invoke name="f">\n<｜DSML｜parameter name="k" string="true">5</｜DSML｜parameter>\n'
+                        '<｜DSML｜parameter name="n" string="false">5</｜DSML｜parameter>\n</｜DSML｜invoke>\n</｜DSML｜tool_calls>', "", [("f", {"k": "5", "n": 5})]),
+        "gemma4": ('<|tool_call>call:lookup{q:<|"|>a, b<|"|>,n:3,ok:true,r:1.5}<tool_call|>', "", [("lookup", {"q": "a, b", "n": 3, "ok": True, "r": 1.5})]),
+        "qwen3_coder": ('<tool_call>\n<function=run>\n<parameter=cmd>\nls -l\n</parameter>\n</function>\n</tool_call>', "", [("run", {"cmd": "ls -l"})]),
+        "hermes": ('x<tool_call>{"name": "a", "arguments": {"b": 1}}</tool_call><tool_call>not json</tool_call>', "x", [("a", {"b": 1})]),
+    }
+    for name, (text, content, want) in cases.items():
+        got_text, calls = g(name).extract_tool_calls(text)
+        assert got_text.strip() == content, name
+        assert [(c.name, json.loads(c.arguments)) for c in calls] == want, (name, calls)
+
+    class Tok:
+        def convert_tokens_to_ids(self, t):
+            return {"<|observation|>": 7, "<tool_call|>": 9}.get(t, -1)
+
+    assert g("glm", Tok()).stop_token_ids == [7] and g("gemma4", Tok()).stop_token_ids == [9] and g("kimi", Tok()).stop_token_ids == []
+    assert g("hermes", Tok()).stop_token_ids == []
