@@ -72,6 +72,8 @@ class ToolAgentLoop(AgentLoopBase):
         return self._truncate(resp.text or ""), float(reward or 0.0)
 
     async def run(self, sampling_params, **kwargs) -> AgentLoopOutput:
+        # template families whose tool turn does not end with EOS add their own stop token (e.g. <|observation|>, <tool_call|>)
+        stop_ids = tuple(sampling_params.stop_token_ids) + tuple(self.parser.stop_token_ids)
         import dataclasses
 
         messages = list(kwargs["raw_prompt"])
@@ -87,7 +89,7 @@ class ToolAgentLoop(AgentLoopBase):
                 if budget <= 0 or a_turns >= self.max_assistant_turns:
                     break
                 t0 = time.perf_counter()
-                out = await self.client.generate(request_id, prompt_ids + resp_ids, dataclasses.replace(sampling_params, max_tokens=budget))
+                out = await self.client.generate(request_id, prompt_ids + resp_ids, dataclasses.replace(sampling_params, max_tokens=budget, stop_token_ids=stop_ids))
                 m.generate_sequences += time.perf_counter() - t0
                 m.num_preempted += out.num_preempted
                 a_turns += 1
