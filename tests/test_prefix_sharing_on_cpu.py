@@ -121,3 +121,37 @@ def test_trainer_step_with_prefix_sharing_and_score_centering(tmp_path):
         assert k in m, (k, sorted(m))
     # same weights on both sides in the first step: the trainer's head mass equals the sampler's
     assert abs(m["actor/sc_sampler_head_mass"] - m["actor/sc_train_head_mass"]) < 1e-4
+
+
+def test_on_policy_distillation_step(tmp_path):
+    """A frozen teacher (same architecture, other weights) scores the student's samples; the actor's loss is the forward KL to
+    the teacher's top-k head and a few steps reduce it."""
+    from verl_b200.trainer.ppo.ppo_trainer import PPOTrainer
+    from verl_b200.trainer.ppo.reward import load_reward_manager
+    from verl_b200.utils.config import load_config
+
+    ov = ["data.synthetic.enable=true", "data.synthetic.num_prompts=64", "data.train_batch_size=4", "data.max_prompt_length=32",
+          "data.max_response_length=8", "actor_rollout_ref.model.preset=tiny-qwen2", "actor_rollout_ref.rollout.n=2",
+          "actor_rollout_ref.actor.ppo_mini_batch_size=4", "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=8",
+          "actor_rollout_ref.actor.use_kl_loss=false", "actor_rollout_ref.rollout.log_prob_micro_batch_size_per_gpu=8",
+          "actor_rollout_ref.rollout.max_num_seqs=8", "actor_rollout_ref.model.enable_gradient_checkpointing=false",
+          "actor_rollout_ref.actor.optim.lr=3e-3", "actor_rollout_ref.distillation.enable=true", "actor_rollout_ref.distillation.teacher_model.preset=tiny-qwen2",
+          "actor_rollout_ref.distillation.topk=8", "+actor_rollout_ref.ref.fsdp_config.seed=7", "+actor_rollout_ref.actor.fsdp_config.seed=1",
+          "algorithm.adv_estimator=grpo", "reward.reward_manager=token_rule", "trainer.device=cpu", "trainer.val_before_train=false",
+          "trainer.logger=[]", "trainer.n_gpus_per_node=1", "data.shuffle=false", f"trainer.default_local_dir={tmp_path}/ckpt",
+          "trainer.total_training_steps=4"]
+    cfg = load_config("ppo_trainer", ov)
+    tr = PPOTrainer(cfg, reward_fn=load_reward_manager(cfg, None), val_reward_fn=None)
+    tr.init_workers()
+    w = tr.actor_rollout_wg.worker
+    assert w.teacher is not None and not torch.equal(w.teacher.engine.store.flat, w.actor.engine.store.flat)   # a different model
+    it = iter(tr.train_dataloader)
+    losses = []
+    for step in range(1, 5):
+        tr.global_steps = step
+        m = tr.step(next(it))
+        losses.append(m["distill/forward_kl"])
+        assert "timing_s/teacher" in m and 0.0 <= m["distill/top1_agreement"] <= 1.0
+    b = tr._last_batch.batch
+    assert b["teacher_topk_ids"].shape == (8, 8, 8) and (b["teacher_topk_log_probs"][..., 0] >= b["teacher_topk_log_probs"][..., 1]).all()
+    assert losses[0] > 0 and min(losses[1:]) < losses[0], losses

@@ -11,6 +11,8 @@
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2-5 = epilogue
 // (warp w reads TMEM lanes 32*(w%4)..+31).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "tma_host.h"
 
@@ -809,7 +811,15 @@ static void pick_tile_and_split(int M, int N, int K, bool b_mn, int* bn_out, int
 extern "C" void vb_gemm_plan(int M, int N, int K, int b_mn, int bn_req, int* bn, int* split_k) {
   using namespace vb;
   *split_k = 1;
-  if (bn_req != 0) { *bn = bn_req; return; }
+  if (bn_req != 0) {
+    *bn = bn_req;
+    // tuning hook: an explicit tile width may be combined with an explicit number of K slices
+    if (const char* e = getenv("VERL_B200_GEMM_SPLIT")) {
+      const int s = atoi(e);
+      if (s > 1 && (N % 4) == 0) *split_k = s;
+    }
+    return;
+  }
   const long big_tiles = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
   if (big_tiles >= num_sms()) { *bn = 256; return; }
   pick_tile_and_split(M, N, K, b_mn != 0, bn, split_k);

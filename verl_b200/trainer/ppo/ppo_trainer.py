@@ -386,6 +386,9 @@ def _train_on_rollouts(self: PPOTrainer, batch: DataProto, timing_raw: dict, n: 
         if self.use_reference_policy:
             with marked_timer("ref", timing_raw):
                 batch = batch.union(self.ref_policy_wg.compute_ref_log_prob(batch))
+        if bool(_g(cfg, "actor_rollout_ref.distillation.enable", False)):
+            with marked_timer("teacher", timing_raw):
+                batch = batch.union(self.actor_rollout_wg.compute_teacher_topk(batch))
         if self.use_critic:
             with marked_timer("values", timing_raw):
                 batch = batch.union(self.critic_wg.compute_values(batch))

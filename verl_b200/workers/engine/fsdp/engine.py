@@ -468,6 +468,7 @@ class FSDPEngine(BaseEngine):
         """Score centering (train–inference mismatch correction): log-probs of the sampler's top-k head under the trainer,
         turned into the per-token correction term that the REINFORCE loss adds (reference:
         verl/trainer/ppo/score_centering.py:217-257). ``h_sel`` are the hidden rows that predict the valid response tokens."""
+        self._distillation_terms(out, mb, meta, h_sel, valid, temperature)
         if not meta.get("score_centering", False) or "rollout_topk_ids" not in mb:
             return
         from verl_b200.trainer.ppo.score_centering import score_centering_correction, score_centering_weight_fn, topk_log_probs_from_hidden
@@ -481,6 +482,36 @@ class FSDPEngine(BaseEngine):
         out["sc_correction"] = zero.masked_scatter(valid, corr.float())
         out["sc_sampler_head_mass"] = zero.masked_scatter(valid, q_mass.float()).detach()
         out["sc_train_head_mass"] = zero.masked_scatter(valid, p_mass.float()).detach()
+
+    def _distillation_terms(self, out: dict, mb: dict, meta: dict, h_sel: torch.Tensor, valid: torch.Tensor, temperature: float) -> None:
+        """On-policy distillation. Teacher pass (``meta["return_topk"] = k``): the k most likely next tokens and their
+        log-probs at every response position. Student pass (batch holds ``teacher_topk_ids``): the student's log-probs of
+        those ids, with gradient. Logits exist for 1024 rows at a time only. Reference: prompt-logprob requests to a
+        teacher server, verl/experimental/teacher_loop/teacher_manager.py:36-144."""
+        k = int(meta.get("return_topk", 0) or 0)
+        W = self.model.output_weight
+        if k > 0:
+            ids, lps = [], []
+            with torch.no_grad():
+                for s0 in range(0, h_sel.shape[0], 1024):
+                    x = ops.linear(h_sel[s0: s0 + 1024], W).float() / temperature
+                    v, i = torch.log_softmax(x, -1).topk(k, -1)
+                    ids.append(i)
+                    lps.append(v)
+            bs, R = valid.shape
+            tid = torch.zeros(bs, R, k, dtype=torch.int64, device=h_sel.device)
+            tlp = torch.full((bs, R, k), -1e4, dtype=torch.float32, device=h_sel.device)
+            if ids:
+                tid[valid] = torch.cat(ids)
+                tlp[valid] = torch.cat(lps)
+            out["topk_ids"], out["topk_log_probs"] = tid, tlp
+        if meta.get("distillation", False) and "teacher_topk_ids" in mb:
+            from verl_b200.trainer.ppo.score_centering import topk_log_probs_from_hidden
+
+            ids = mb["teacher_topk_ids"][valid]
+            lp = topk_log_probs_from_hidden(h_sel, W, ids, temperature)
+            full = torch.full((*valid.shape, ids.shape[-1]), -1e4, dtype=torch.float32, device=h_sel.device)
+            out["student_topk_log_probs"] = full.masked_scatter(valid[..., None].expand_as(full), lp.float())
 
     def _forward_shared_prefix(self, mb: dict, pb_full: PackedBatch, labels_full: torch.Tensor, idx, valid, meta: dict) -> dict:
         """Policy forward on the unique tokens of the micro-batch: every distinct prompt once plus all responses. Attention

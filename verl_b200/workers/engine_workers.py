@@ -230,10 +230,19 @@ class ActorRolloutRefWorker(Worker):
         if self._is_ref:
             self.ref = TrainingWorker(_role_cfg(c, "ref", "language_model"), role="ref")
             self.ref.reset()
+        dcfg = cfg_get(c, "distillation", None)
+        self.teacher = None
+        if dcfg is not None and cfg_get(dcfg, "enable", False) and self._is_actor:
+            # frozen teacher colocated with the student (same engine type as the reference policy, its own weights)
+            tcfg = _role_cfg(c, "ref" if cfg_get(c, "ref", None) is not None else "actor", "language_model")
+            tcfg = dict(tcfg, model=cfg_get(dcfg, "teacher_model"), optim=None)
+            tcfg["engine"] = dict(tcfg.get("engine") or {}, forward_only=True)
+            self.teacher = TrainingWorker(tcfg, role="teacher")
+            self.teacher.reset()
         if self._is_actor:
             self.actor = TrainingWorker(_role_cfg(c, "actor", "language_model"), role="actor")
             self.actor.reset()
-            self.actor.set_loss_fn(partial(ppo_loss, cfg_get(c, "actor")))
+            self.actor.set_loss_fn(partial(ppo_loss, cfg_get(c, "actor"), distillation=dcfg))
             eng = self.actor.engine
             self._register_dispatch_collect_info("actor", dp_rank=eng.get_data_parallel_rank(), is_collect=eng.is_mp_src_rank_with_outputs())
         if self._is_ref and not self._is_actor:
@@ -408,11 +417,26 @@ class ActorRolloutRefWorker(Worker):
         mo = self._logprob_pass(worker, data, calculate_entropy=False)
         return DataProto.from_dict(tensors={"ref_log_prob": _to_host(mo["log_probs"])})
 
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
+    def compute_teacher_topk(self, data: DataProto) -> DataProto:
+        """Teacher forward over the student's samples: its k most likely tokens and their log-probs per response position."""
+        assert self.teacher is not None, "distillation.enable=true is needed for a teacher pass"
+        meta = dict(data.meta_info)
+        meta["calculate_entropy"] = False
+        meta["return_topk"] = int(cfg_get(self.config, "distillation.topk", 32))
+        meta["temperature"] = 1.0
+        meta.pop("use_prefix_grouper", None)
+        d = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=meta)
+        mo = self.teacher.infer_batch(d)["model_output"]
+        return DataProto.from_dict(tensors={"teacher_topk_ids": _to_host(mo["topk_ids"]), "teacher_topk_log_probs": _to_host(mo["topk_log_probs"])})
+
     # ------------------------------------------------------------------ update
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
     def update_actor(self, data: DataProto) -> DataProto:
         ac = cfg_get(self.config, "actor")
         meta = dict(data.meta_info)
+        if self.teacher is not None:
+            meta["distillation"] = True
         meta.setdefault("temperature", float(cfg_get(self.config, "rollout.temperature", 1.0)))
         meta["calculate_entropy"] = bool(cfg_get(ac, "calculate_entropy", False)) or float(cfg_get(ac, "entropy_coeff", 0.0)) != 0.0
         data = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=meta)

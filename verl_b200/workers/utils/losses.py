@@ -34,7 +34,24 @@ class _LossCfgView(dict):
             raise AttributeError(k) from e
 
 
-def ppo_loss(config, model_output: dict, data, dp_group=None) -> tuple[torch.Tensor, dict[str, Any]]:
+def _distillation_term(distillation, model_output: dict, data, mask, agg_mode: str, info: dict):
+    from verl_b200.trainer.distillation.losses import DISTILLATION_LOSSES
+
+    if "student_topk_log_probs" not in model_output:
+        raise RuntimeError("distillation is enabled but the engine produced no student_topk_log_probs: the batch needs "
+                           "teacher_topk_ids / teacher_topk_log_probs (the teacher pass did not run)")
+    kind = _get(distillation, "loss", "forward_kl")
+    kw = {"beta": float(_get(distillation, "jsd_beta", 0.5))} if kind == "jsd" else {}
+    per_tok = DISTILLATION_LOSSES[kind](model_output["student_topk_log_probs"], data["teacher_topk_log_probs"].to(mask.device), **kw)
+    loss = core_algos.agg_loss(per_tok, mask, agg_mode, **info)
+    with torch.no_grad():
+        agree = (model_output["student_topk_log_probs"].argmax(-1) == 0).float()      # the teacher's head is sorted: index 0 is its top-1
+        m = {"distill/" + kind: Metric(AggregationType.MEAN, loss.detach().item()),
+             "distill/top1_agreement": Metric(AggregationType.MEAN, VF.masked_mean(agree, mask).item())}
+    return loss, m
+
+
+def ppo_loss(config, model_output: dict, data, dp_group=None, distillation=None) -> tuple[torch.Tensor, dict[str, Any]]:
     """Policy loss (+ entropy bonus, + KL-to-reference loss) on one micro-batch.
 
     ``model_output`` holds ``log_probs`` and optionally ``entropy`` as [bs, R]; ``data`` holds ``old_log_probs``,
@@ -45,6 +62,16 @@ def ppo_loss(config, model_output: dict, data, dp_group=None) -> tuple[torch.Ten
     entropy = model_output.get("entropy")
     mask = data["response_mask"].to(log_prob.dtype)
     info = {k: data[k] for k in ("dp_size", "batch_num_tokens", "global_batch_size", "loss_scale_factor") if k in data and data[k] is not None}
+    if distillation is not None and _get(distillation, "enable", False):
+        # on-policy distillation: divergence to the teacher's top-k head on the student's own samples, optionally on top of
+        # the policy-gradient loss (reference: verl/trainer/distillation/losses.py, distillation.loss_settings)
+        d_loss, d_metrics = _distillation_term(distillation, model_output, data, mask, _get(config, "loss_agg_mode", "token-mean"), info)
+        coef = float(_get(distillation, "loss_coef", 1.0))
+        if not _get(distillation, "use_policy_loss", False):
+            return coef * d_loss, d_metrics
+        pg, m = ppo_loss(config, model_output, data, dp_group)
+        m.update(d_metrics)
+        return pg + coef * d_loss, m
     loss_mode = _get(_get(config, "policy_loss", {}), "loss_mode", "vanilla")
     agg_mode = _get(config, "loss_agg_mode", "token-mean")
     view = _LossCfgView({k: _get(config, k) for k in ("clip_ratio", "clip_ratio_low", "clip_ratio_high", "clip_ratio_c",
