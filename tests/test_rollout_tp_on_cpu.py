@@ -5,6 +5,7 @@ import os
 import subprocess
 import sys
 
+import pytest
 import torch
 
 from verl_b200.models.config import PRESETS
@@ -52,12 +53,14 @@ def test_tp2_engine_matches_tp1(tmp_path):
         assert w.token_ids == got and torch.allclose(torch.tensor(w.log_probs), torch.tensor(lp), atol=1e-4)
 
 
-def test_grpo_fit_with_tp2_rollout(tmp_path):
+@pytest.mark.parametrize("world", [2, 4])
+def test_grpo_fit_with_tp2_rollout(tmp_path, world):
+    """world = 4: two tensor-parallel replicas of two ranks each next to four data-parallel trainer ranks."""
     from tests.test_trainer_e2e_on_cpu import OV
 
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     logf = tmp_path / "log.jsonl"
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29773",
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", str(29771 + world),
            "-m", "verl_b200.trainer.main_ppo"] + [o for o in OV if not o.startswith("trainer.logger")] + \
           ["trainer.logger=[file]", "trainer.total_training_steps=2", f"trainer.default_local_dir={tmp_path}/ckpt", "trainer.resume_mode=disable",
            "actor_rollout_ref.rollout.tensor_model_parallel_size=2"]
