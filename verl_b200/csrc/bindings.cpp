@@ -77,10 +77,11 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Ten
              "gemm_pair");
     return;
   }
-  // decode-sized problems (one or two row blocks): the paired kernel with K slices reads every B tile once per pair
-  // (bn == 513 forces it, VERL_B200_GEMM_PAIR_SPLITK=1 makes it the automatic choice)
-  static const bool pair_split_auto = []() { const char* e = getenv("VERL_B200_GEMM_PAIR_SPLITK"); return e != nullptr && e[0] == '1'; }();
-  if (!a_mn && !b_mn && (bn == 513 || (bn == 0 && pair_auto && pair_split_auto && M > 128 && M <= 512))) {
+  // decode-sized problems (one or two row blocks) with a long K: the paired kernel with K slices reads every B tile once
+  // per pair. Measured on B200: M=256,N=3584,K=18944 56.3 us vs 60.5 us for the best single-CTA plan, M=512 76.9 vs 87.0;
+  // for K=3584 the single-CTA plans win. bn == 513 forces this path, VERL_B200_GEMM_PAIR_SPLITK=0 turns the automatic choice off.
+  static const bool pair_split_auto = []() { const char* e = getenv("VERL_B200_GEMM_PAIR_SPLITK"); return e == nullptr || e[0] != '0'; }();
+  if (!a_mn && !b_mn && (bn == 513 || (bn == 0 && pair_auto && pair_split_auto && M > 128 && M <= 512 && K >= 8192))) {
     const int s2 = vb_gemm_pair_plan((int)M, (int)N, (int)K);
     if (s2 >= 1) {
       Tensor ws2;
