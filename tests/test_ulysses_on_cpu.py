@@ -1,4 +1,5 @@
-"""Ulysses sequence parallelism in the sharded-DP engine on gloo ranks: outputs and gradients equal the single-rank run."""
+"""Ulysses sequence parallelism and context parallelism (all-gathered K/V) in the sharded-DP engine on gloo ranks: outputs
+and gradients equal the single-rank run."""
 
 import os
 import subprocess
@@ -20,7 +21,8 @@ from verl_b200.workers.engine.fsdp.engine import FSDPEngine
 dist.init_process_group("gloo")
 rank, world = dist.get_rank(), dist.get_world_size()
 sp = int(os.environ["SP"])
-eng = FSDPEngine(PRESETS["tiny-qwen2"], {"seed": 1, "ulysses_sequence_parallel_size": sp}, {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, {})
+key = "context_parallel_size" if os.environ.get("MODE") == "context" else "ulysses_sequence_parallel_size"
+eng = FSDPEngine(PRESETS["tiny-qwen2"], {"seed": 1, key: sp}, {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, {})
 eng.initialize()
 assert eng.get_data_parallel_size() == world // sp
 data = make_batch().chunk(eng.get_data_parallel_size())[eng.get_data_parallel_rank()]
@@ -37,15 +39,15 @@ dist.barrier()
 '''
 
 
-@pytest.mark.parametrize("world,sp", [(2, 2), (4, 2)])
-def test_ulysses_ranks_match_single_rank(tmp_path, world, sp):
+@pytest.mark.parametrize("world,sp,mode", [(2, 2, "ulysses"), (4, 2, "ulysses"), (2, 2, "context"), (3, 3, "context"), (4, 2, "context")])
+def test_ulysses_ranks_match_single_rank(tmp_path, world, sp, mode):
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     script = tmp_path / "w.py"
     script.write_text(WORKER)
     out = tmp_path / "out.pt"
-    env = dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1", SP=str(sp))
+    env = dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1", SP=str(sp), MODE=mode)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-                        "--master-port", str(29750 + world), str(script)], env=env, capture_output=True, text=True, timeout=900)
+                        "--master-port", str(29750 + world + (10 if mode == "context" else 0)), str(script)], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     eng = FSDPEngine(PRESETS["tiny-qwen2"], {"seed": 1}, {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, {})
     eng.initialize()

@@ -24,6 +24,9 @@ struct AttnBwdTile {
   int kv_row0;     // in-sequence index of that row (multiple of 128)
   int seq_tok0;
   int seq_len;
+  int q_tile_begin;   // first 128-row query tile of the sequence that has real queries (context parallelism: the rows before
+                      // it only carry keys/values); 0 for ordinary batches
+  int pad[3];
 };
 
 struct AttnBwdParams {
@@ -66,7 +69,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int kv_head = blockIdx.y;
   const int group = p.n_q_heads / p.n_kv_heads;
   const int n_q_tiles_total = (t.seq_len + 127) / 128;
-  const int first_q_tile = t.kv_row0 / 128;
+  const int first_q_tile = max(t.kv_row0 / 128, t.q_tile_begin);
   const int iters_per_head = n_q_tiles_total - first_q_tile;
   const int n_iters = iters_per_head * group;
 

@@ -40,10 +40,13 @@ std::tuple<Tensor, Tensor> attn_varlen_fwd(const Tensor& qkv, const Tensor& tile
 }
 
 // Returns dqkv [T, (Hq+2Hkv)*128] bf16.
+// bwd_tiles: int32 [n_tiles, 8] = (kv_tok0, kv_row0, seq_tok0, seq_len, q_tile_begin, 0, 0, 0)
 Tensor attn_varlen_bwd(const Tensor& qkv, const Tensor& out, const Tensor& dout, const Tensor& lse, const Tensor& bwd_tiles,
                        int64_t n_q_heads, int64_t n_kv_heads, double scale) {
   TORCH_CHECK(qkv.is_cuda() && qkv.scalar_type() == at::kBFloat16 && qkv.stride(1) == 1, "attn_bwd: bad qkv");
   TORCH_CHECK(out.is_contiguous() && dout.is_contiguous() && dout.scalar_type() == at::kBFloat16, "attn_bwd: bad out/dout");
+  TORCH_CHECK(bwd_tiles.is_cuda() && bwd_tiles.scalar_type() == at::kInt && bwd_tiles.is_contiguous() && bwd_tiles.dim() == 2 && bwd_tiles.size(1) == 8,
+              "attn_bwd: the work list must be int32 [n_tiles, 8]");
   const int T = qkv.size(0);
   c10::cuda::CUDAGuard guard(qkv.device());
   Tensor dqkv = at::empty({T, (n_q_heads + 2 * n_kv_heads) * 128}, qkv.options());

@@ -91,7 +91,11 @@ class Attention(nn.Module):
             k = ops.rmsnorm(k.reshape(-1, cfg.head_dim), self.k_norm, cfg.rms_norm_eps).reshape(T, cfg.kv_size)
             qkv = torch.cat([q, k, v], dim=-1)
         qkv = ops.apply_rope_(qkv, pb.position_ids, cos, sin, cfg.num_attention_heads + cfg.num_key_value_heads, cfg.head_dim)
-        if sp_group is not None:
+        if sp_group is not None and getattr(self, "sp_mode", "ulysses") == "context":
+            from verl_b200.parallel.context_parallel import context_parallel_attention
+
+            o = context_parallel_attention(qkv, pb, cfg, sp_group)     # all-gather K/V, attention for the local query rows
+        elif sp_group is not None:
             from verl_b200.parallel.ulysses import ulysses_attention
 
             o = ulysses_attention(qkv, pb, cfg, sp_group)

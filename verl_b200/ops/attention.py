@@ -13,29 +13,35 @@ __all__ = ["flash_attention_varlen", "paged_decode_attention", "build_tile_table
 
 
 @lru_cache(maxsize=64)
-def _tile_tables_cached(lens: tuple, device_str: str):
+def _tile_tables_cached(lens: tuple, q_starts: tuple, device_str: str):
     fwd, bwd = [], []
     tok = 0
-    for L in lens:
+    for L, qs in zip(lens, q_starts):
         n = (L + 127) // 128
+        q0 = min(qs // 128, n)        # first query tile with real queries (0 unless context parallel)
         for i in range(n):
-            # forward tile i of a sequence touches i+1 kv tiles; backward kv tile i is visited by n-i query tiles
-            fwd.append((i + 1, (tok + i * 128, i * 128, tok, L)))
-            bwd.append((n - i, (tok + i * 128, i * 128, tok, L)))
+            # forward tile i of a sequence touches i+1 kv tiles; backward kv tile i is visited by the query tiles at or below it
+            if i >= q0:
+                fwd.append((i + 1, (tok + i * 128, i * 128, tok, L)))
+            bwd.append((n - max(i, q0), (tok + i * 128, i * 128, tok, L, q0, 0, 0, 0)))
         tok += L
     fwd.sort(key=lambda t: -t[0])
     bwd.sort(key=lambda t: -t[0])
     dev = torch.device(device_str)
     ft = torch.tensor([t[1] for t in fwd], dtype=torch.int32).reshape(-1, 4).to(dev, non_blocking=True)
-    bt = torch.tensor([t[1] for t in bwd], dtype=torch.int32).reshape(-1, 4).to(dev, non_blocking=True)
+    bt = torch.tensor([t[1] for t in bwd], dtype=torch.int32).reshape(-1, 8).to(dev, non_blocking=True)
     return ft, bt
 
 
-def build_tile_tables(cu_seqlens_cpu: torch.Tensor, device) -> tuple[torch.Tensor, torch.Tensor]:
-    """Work lists (heaviest first) for the forward (per 128-row query tile) and backward (per 128-row kv tile)."""
+def build_tile_tables(cu_seqlens_cpu: torch.Tensor, device, q_starts=None) -> tuple[torch.Tensor, torch.Tensor]:
+    """Work lists (heaviest first) for the forward (per 128-row query tile) and backward (per 128-row kv tile).
+
+    ``q_starts[s]`` (context parallelism): rows before it in sequence ``s`` carry only keys/values — no forward tile is
+    emitted for query tiles that lie entirely before it and the backward skips them; their output rows are undefined."""
     cs = cu_seqlens_cpu.tolist()
     lens = tuple(cs[i + 1] - cs[i] for i in range(len(cs) - 1))
-    return _tile_tables_cached(lens, str(device))
+    qs = tuple(int(x) for x in q_starts) if q_starts is not None else (0,) * len(lens)
+    return _tile_tables_cached(lens, qs, str(device))
 
 
 class _FlashVarlen(torch.autograd.Function):
@@ -55,11 +61,11 @@ class _FlashVarlen(torch.autograd.Function):
 
 
 def flash_attention_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-                           max_seqlen: int, scale: float, cu_seqlens_cpu: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           max_seqlen: int, scale: float, cu_seqlens_cpu: Optional[torch.Tensor] = None, q_starts=None) -> torch.Tensor:
     assert head_dim == 128, "the sm_100a attention kernels are specialised for head_dim 128"
     if cu_seqlens_cpu is None:
         cu_seqlens_cpu = cu_seqlens.cpu()
-    ft, bt = build_tile_tables(cu_seqlens_cpu, qkv.device)
+    ft, bt = build_tile_tables(cu_seqlens_cpu, qkv.device, q_starts)
     if qkv.stride(1) != 1:
         qkv = qkv.contiguous()
     return _FlashVarlen.apply(qkv, ft, bt, n_heads, n_kv_heads, scale)

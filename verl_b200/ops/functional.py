@@ -286,15 +286,16 @@ def _attention_ref(q, k, v, cu_seqlens, scale):
 
 
 def attention_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-                     max_seqlen: int, cu_seqlens_cpu: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     max_seqlen: int, cu_seqlens_cpu: Optional[torch.Tensor] = None, q_starts=None) -> torch.Tensor:
     """Causal self-attention over a packed batch. ``qkv`` is the fused projection output [T, (Hq+2Hkv)·D];
-    returns [T, Hq·D]."""
+    returns [T, Hq·D]. ``q_starts`` (one per sequence): the rows before it only serve as keys/values, their outputs are
+    undefined (the GPU kernels skip them, the reference path computes and the caller drops them)."""
     T = qkv.shape[0]
     scale = 1.0 / math.sqrt(head_dim)
     if use_native(qkv) and head_dim == 128:
         from .attention import flash_attention_varlen
 
-        return flash_attention_varlen(qkv, cu_seqlens, n_heads, n_kv_heads, head_dim, max_seqlen, scale, cu_seqlens_cpu)
+        return flash_attention_varlen(qkv, cu_seqlens, n_heads, n_kv_heads, head_dim, max_seqlen, scale, cu_seqlens_cpu, q_starts)
     q, k, v = qkv.split([n_heads * head_dim, n_kv_heads * head_dim, n_kv_heads * head_dim], dim=-1)
     o = _attention_ref(q.reshape(T, n_heads, head_dim), k.reshape(T, n_kv_heads, head_dim),
                        v.reshape(T, n_kv_heads, head_dim), cu_seqlens if cu_seqlens_cpu is None else cu_seqlens_cpu, scale)

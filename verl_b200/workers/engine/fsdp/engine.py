@@ -153,7 +153,14 @@ class FSDPEngine(BaseEngine):
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         self.world = dist.get_world_size() if dist.is_initialized() else 1
         self.device = torch.device(get_device_name(), torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
-        self.sp_size = int(cfg_get(self.engine_config, "ulysses_sequence_parallel_size", 1))
+        self.sp_size = int(cfg_get(self.engine_config, "ulysses_sequence_parallel_size", 1) or 1)
+        # context parallelism shares the sequence-parallel plumbing (token slicing, output gather, gradient scaling); only
+        # attention differs: K/V are all-gathered instead of scattering heads (verl_b200.parallel.context_parallel)
+        cp = int(cfg_get(self.engine_config, "context_parallel_size", 1) or 1)
+        self.sp_mode = "ulysses"
+        if cp > 1:
+            assert self.sp_size == 1, "choose either ulysses_sequence_parallel_size or context_parallel_size"
+            self.sp_size, self.sp_mode = cp, "context"
         fsdp_size = int(cfg_get(self.engine_config, "fsdp_size", -1))
         self.fsdp_size = self.world if fsdp_size in (-1, 0) or fsdp_size >= self.world else fsdp_size
         self.forward_only = bool(cfg_get(self.engine_config, "forward_only", False)) or optimizer_config is None
@@ -231,8 +238,10 @@ class FSDPEngine(BaseEngine):
             self.model.sp_group = self.sp_group
             from verl_b200.parallel.ulysses import FusedUlysses, fused_ulysses_available
 
+            for layer in self.model.layers:
+                layer.self_attn.sp_mode = self.sp_mode
             probe = self.store.flat[:1]
-            if fused_ulysses_available(probe, cfg, self.sp_size) and bool(cfg_get(self.engine_config, "fused_ulysses", True)):
+            if self.sp_mode == "ulysses" and fused_ulysses_available(probe, cfg, self.sp_size) and bool(cfg_get(self.engine_config, "fused_ulysses", True)):
                 from verl_b200.single_controller.spmd import init_spmd_process_group
 
                 init_spmd_process_group()
