@@ -134,6 +134,34 @@ def test_attention_varlen_fwd_bwd(o, lens, Hq, Hkv):
     assert rel(out, ref) < 1e-2 and rel(qkv.grad, q2.grad) < 1.5e-2
 
 
+@pytest.mark.parametrize("lens,q_starts", [([640, 300], [256, 0]), ([1000, 77, 515], [700, 40, 384]), ([384], [383])])
+def test_attention_varlen_with_key_only_prefix_rows(o, lens, q_starts):
+    """Context-parallel form: rows before q_starts[s] carry only keys/values. Their query tiles are skipped in forward and
+    backward; the remaining rows and all K/V gradients equal the plain causal attention."""
+    from verl_b200 import ops
+    from verl_b200.ops import functional as Fn
+
+    dev, D, Hq, Hkv, T = "cuda", 128, 4, 2, sum(lens)
+    torch.manual_seed(1)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    live = torch.cat([torch.arange(L) >= qs for L, qs in zip(lens, q_starts)]).to(dev)
+    base = (0.5 * torch.randn(T, (Hq + 2 * Hkv) * D, device=dev)).bfloat16()
+    base[:, : Hq * D] *= live[:, None]                     # no queries before q_start
+    qkv = base.clone().requires_grad_(True)
+    out = ops.attention_varlen(qkv, cu.to(dev), Hq, Hkv, D, max(lens), cu, q_starts=tuple(q_starts))
+    dout = torch.randn_like(out) * live[:, None]
+    torch.where(live[:, None], out, torch.zeros_like(out)).backward(dout)
+    assert status_ok(o)
+    q2 = base.float().requires_grad_(True)
+    q, k, v = q2.split([Hq * D, Hkv * D, Hkv * D], -1)
+    ref = Fn._attention_ref(q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), cu, 1 / math.sqrt(D)).reshape(T, Hq * D)
+    ref.backward(dout.float())
+    assert rel(out[live], ref[live]) < 1e-2
+    g, gr = qkv.grad.float(), q2.grad
+    assert torch.isfinite(g[:, Hq * D:]).all() and rel(g[:, Hq * D:], gr[:, Hq * D:]) < 1.5e-2       # dK, dV of every row
+    assert rel(g[live][:, : Hq * D], gr[live][:, : Hq * D]) < 1.5e-2                                    # dQ of the live rows
+
+
 @pytest.mark.parametrize("impl", [1, 2])
 @pytest.mark.parametrize("B,Hq,Hkv,lens,splits", [(3, 28, 4, [5, 200, 512], 1), (3, 28, 4, [5, 200, 512], 2), (2, 8, 8, [64, 129], 1), (2, 28, 4, [0, 300], 4),
                                                   (4, 32, 2, [1, 127, 128, 400], 1)])
