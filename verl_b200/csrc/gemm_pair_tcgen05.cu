@@ -193,7 +193,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int n0 = nb * BN + (int)rank * (BN / 2);
         int kb0, kb1;
         k_range(t, kb0, kb1);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        // few row blocks: stagger the K order per column block so the CTAs do not all ask for the same A tile at once
+        const int nk = kb1 - kb0;
+        const int rot = (num_m <= 2 && nk > 1) ? (nb * 5) % nk : 0;
+        for (int ki = 0; ki < nk; ++ki) {
+          const int kb = kb0 + (ki + rot >= nk ? ki + rot - nk : ki + rot);
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + s * C::STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;

@@ -222,7 +222,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
         const int m0 = mb * BM, n0 = nb * BN;
-        for (int kb = kb0; kb < kb1; ++kb) {
+        // Decode-sized problems (a few row blocks): every CTA of a row block would ask for the same A tile at the same
+        // moment and queue up on one L2 slice. Start each column block at a different K step and wrap around (the order of
+        // the K steps does not matter for the sum); CTAs that share a B tile keep the same order.
+        const int nk = kb1 - kb0;
+        const int rot = (num_m <= 4 && dist.seg_mode == 0 && dist.group_mode == 0 && nk > 1) ? (nb * 5) % nk : 0;
+        for (int ki = 0; ki < nk; ++ki) {
+          const int kb = kb0 + (ki + rot >= nk ? ki + rot - nk : ki + rot);
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
