@@ -170,9 +170,13 @@ from verl_b200.workers.engine.fsdp.engine import FSDPEngine
 from verl_b200.workers.engine.megatron.engine import MegatronEngine
 # ---- Ulysses: all-to-alls fused into the projections == NCCL all-to-all formulation
 res = {}
-for mode in ("fused", "nccl"):
-    eng = FSDPEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "ulysses_sequence_parallel_size": world, "fused_ulysses": mode == "fused",
-                                                 "use_symmetric_memory": False}, {"lr": 1e-3, "clip_grad": 1.0}, {})
+for mode in ("fused", "nccl", "context"):
+    ecfg = {"seed": 1, "use_symmetric_memory": False}
+    if mode == "context":      # context parallelism: K/V all-gather, attention kernels skip the other rank's query tiles
+        ecfg["context_parallel_size"] = world
+    else:
+        ecfg.update({"ulysses_sequence_parallel_size": world, "fused_ulysses": mode == "fused"})
+    eng = FSDPEngine(PRESETS["tiny-qwen2-gpu"], ecfg, {"lr": 1e-3, "clip_grad": 1.0}, {})
     eng.initialize()
     assert (getattr(eng, "_fused_ulysses", None) is not None) == (mode == "fused")
     data = make_batch(bs=6, P=70, R=90, vocab=4096)
@@ -187,6 +191,9 @@ d_lp = (res["fused"][0] - res["nccl"][0]).abs().max().item()
 g_f, g_n = res["fused"][1], res["nccl"][1]
 rel = ((g_f - g_n).norm() / g_n.norm()).item()
 assert d_lp < 0.06 and rel < 0.05, (d_lp, rel)
+d_cp = (res["context"][0] - res["nccl"][0]).abs().max().item()
+rel_cp = ((res["context"][1] - g_n).norm() / g_n.norm()).item()
+assert d_cp < 0.06 and rel_cp < 0.05, (d_cp, rel_cp)
 # ---- tensor-parallel engine on NCCL == single-GPU engine
 ref = FSDPEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "use_symmetric_memory": False, "fsdp_size": 1}, None, {})
 tp = MegatronEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "tensor_model_parallel_size": world}, {"lr": 1e-3}, {})
