@@ -23,10 +23,12 @@ constexpr int BK = 64;       // 64 bf16 = 128 B = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_TILE_BYTES = BM * BK * 2;
 
-template <int BN>
+// KA: 64-element K atoms per pipeline stage. KA = 2 fetches 256 contiguous bytes of every operand row per stage (two TMA
+// boxes): memory-bound decode-sized problems then touch each DRAM page in longer bursts and pay half the barrier traffic.
+template <int BN, int KA = 1>
 struct GemmCfg {
   static constexpr int B_TILE_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+  static constexpr int STAGE_BYTES = KA * (A_TILE_BYTES + B_TILE_BYTES);
   static constexpr int MAX_STAGES = (220 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
@@ -129,12 +131,13 @@ struct LmHeadEpi {
 };
 
 // COPY_WARPS > 0 adds that many warps (after the six role warps) whose only job is to stage remote operand chunks.
-template <int BN, bool A_MN, bool B_MN, int EPI, int COPY_WARPS = 0>
+template <int BN, bool A_MN, bool B_MN, int EPI, int COPY_WARPS = 0, int KA = 1>
 __global__ void __launch_bounds__(192 + 32 * COPY_WARPS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
                  const bf16* __restrict__ bias, int M, int N, int K, int ldc, int flags, int* err_word, const LmHeadEpi epi,
                  int split_k, int kb_per_split, float* __restrict__ split_ws, const __grid_constant__ DistArgs dist) {
-  using Cfg = GemmCfg<BN>;
+  static_assert(KA == 1 || (!A_MN && !B_MN && COPY_WARPS == 0), "multi-atom stages: K-major operands, no staging warps");
+  using Cfg = GemmCfg<BN, KA>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -149,7 +152,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int num_m = (M + BM - 1) / BM;
   const int num_n = (N + BN - 1) / BN;
-  const int num_kb_total = (K + BK - 1) / BK;
+  const int num_kb_total = (K + BK * KA - 1) / (BK * KA);      // K blocks of one pipeline stage
   // split-K: a work unit is (output tile, K slice); partial sums go to an fp32 workspace and are reduced afterwards
   const int num_tiles = dist.group_mode == 2 ? num_m * num_n * dist.num_experts : num_m * num_n * split_k;
 
@@ -231,9 +234,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int kb = kb0 + (ki + rot >= nk ? ki + rot - nk : ki + rot);
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, err_word, VB_ERR_WAIT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
-          uint8_t* sb = sa + A_TILE_BYTES;
+          uint8_t* sb = sa + KA * A_TILE_BYTES;
           mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = kb * BK * KA;
+          if constexpr (KA > 1) {
+            // plain K-major problem: KA adjacent 64-column atoms of A and of B (columns past K read as zeros)
+#pragma unroll
+            for (int a = 0; a < KA; ++a) {
+              tma_load_2d(sa + a * A_TILE_BYTES, &tmA, k0 + a * BK, m0, &full_bar[s]);
+              tma_load_2d(sb + a * Cfg::B_TILE_BYTES, &tmB, k0 + a * BK, n0, &full_bar[s]);
+            }
+            if (++s == STAGES) { s = 0; ph ^= 1; }
+            continue;
+          }
           if (!A_MN) {
             if (dist.seg_mode == 1) {
               const int owner = m0 / dist.seg_rows;
@@ -322,14 +335,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!mbar_wait(&full_bar[s], ph, abort_flag, err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
-          const uint32_t sb = sa + A_TILE_BYTES;
+          const uint32_t sb = sa + KA * A_TILE_BYTES;
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // K-major: 8-row groups are 1024 B apart, a K step of 16 elements is 32 B inside the swizzle row.
+          for (int k = 0; k < KA * BK / UMMA_K; ++k) {
+            // K-major: 8-row groups are 1024 B apart, a K step of 16 elements is 32 B inside the swizzle row; with KA > 1 the
+            //          next 64-column atom is a whole tile further.
             // MN-major: 64-element column atoms are BK*128 B apart (LBO), 8-row K groups 1024 B apart (SBO);
             //           a K step of 16 rows is 2048 B.
-            uint64_t ad = A_MN ? make_sdesc_sw128(sa + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sa + k * 32, 16, 1024);
-            uint64_t bd = B_MN ? make_sdesc_sw128(sb + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sb + k * 32, 16, 1024);
+            const uint32_t ka_off = (KA > 1) ? (k >> 2) * A_TILE_BYTES + (k & 3) * 32 : k * 32;
+            const uint32_t kb_off = (KA > 1) ? (k >> 2) * Cfg::B_TILE_BYTES + (k & 3) * 32 : k * 32;
+            uint64_t ad = A_MN ? make_sdesc_sw128(sa + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sa + ka_off, 16, 1024);
+            uint64_t bd = B_MN ? make_sdesc_sw128(sb + k * 2048, BK * 128, 1024) : make_sdesc_sw128(sb + kb_off, 16, 1024);
             umma_f16(d_tmem, ad, bd, idesc, ((kb - kb0) | k) != 0);
           }
           umma_commit(&empty_bar[s]);
@@ -719,11 +735,11 @@ static int num_sms() {
   return g_num_sms;
 }
 
-template <int BN, bool A_MN, bool B_MN, int EPI = EPI_STORE, int COPY_WARPS = 0>
+template <int BN, bool A_MN, bool B_MN, int EPI = EPI_STORE, int COPY_WARPS = 0, int KA = 1>
 static int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb,
                        int ldc, int flags, int* err_word, cudaStream_t stream, const LmHeadEpi& epi = LmHeadEpi{},
                        int split_k = 1, float* split_ws = nullptr, const DistArgs* dist_in = nullptr) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, KA>;
   static const DistArgs no_dist = {};
   const DistArgs& dist = dist_in ? *dist_in : no_dist;
   CUtensorMap tmA, tmB;
@@ -735,13 +751,13 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   else       rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
   if (rc) return rc;
   static bool attr_set = false;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI, COPY_WARPS>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI, COPY_WARPS, KA>;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return -10;
     attr_set = true;
   }
-  const int num_kb = (K + BK - 1) / BK;
+  const int num_kb = (K + BK * KA - 1) / (BK * KA);
   if (split_k < 1) split_k = 1;
   int kb_per = (num_kb + split_k - 1) / split_k;
   split_k = (num_kb + kb_per - 1) / kb_per;          // no empty slices
@@ -859,6 +875,16 @@ extern "C" int vb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   }
   if (!a_mn && !b_mn) {
     if (bn == 32) VB_LAUNCH(32, false, false);
+    // decode-sized problems (at most four row blocks) are memory bound: 256-byte row bursts per stage (KA = 2)
+    static const int ka_small = []() { const char* e = getenv("VERL_B200_GEMM_KA"); return e ? atoi(e) : 1; }();
+    if (ka_small == 2 && M <= 4 * BM) {
+      switch (bn) {
+        case 256: return launch_gemm<256, false, false, EPI_STORE, 0, 2>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream, LmHeadEpi{}, split_k, split_ws);
+        case 128: return launch_gemm<128, false, false, EPI_STORE, 0, 2>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream, LmHeadEpi{}, split_k, split_ws);
+        case 64: return launch_gemm<64, false, false, EPI_STORE, 0, 2>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream, LmHeadEpi{}, split_k, split_ws);
+        default: break;
+      }
+    }
     VB_DISPATCH_BN(false, false)
   } else if (!a_mn && b_mn) {
     VB_DISPATCH_BN(false, true)
