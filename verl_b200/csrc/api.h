@@ -19,6 +19,7 @@ int vb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rs
                    int T, int H, cudaStream_t st);
 int vb_rope(void* x, const int* pos, const float* cs, const float* sn, int T, int nheads, int D, long ld, float sign,
             cudaStream_t st);
+int vb_segment_sum_rows(const void* g, const long* order, const long* offsets, void* out, long U, int C, cudaStream_t st);
 int vb_swiglu_fwd(const void* gu, void* out, long T, int I, cudaStream_t st);
 int vb_swiglu_bwd(const void* gu, const void* dout, void* dgu, long T, int I, cudaStream_t st);
 int vb_adamw(float* p32, float* m, float* v, const void* g, int g_is_bf16, void* p16, long n, float lr, float b1, float b2,

@@ -170,6 +170,21 @@ void rope_(Tensor& x, const Tensor& pos, const Tensor& cos, const Tensor& sin, i
            "rope");
 }
 
+// backward of a row gather with repeated indices: out[u] = sum_j g[order[j]] over j in [offsets[u], offsets[u+1])
+Tensor segment_sum_rows(const Tensor& g, const Tensor& order, const Tensor& offsets) {
+  CHECK_CUDA_BF16(g);
+  TORCH_CHECK(g.is_contiguous() && g.dim() == 2 && g.size(1) % 8 == 0, "segment_sum_rows: contiguous [E, C] with C % 8 == 0 expected");
+  TORCH_CHECK(order.is_cuda() && offsets.is_cuda() && order.scalar_type() == at::kLong && offsets.scalar_type() == at::kLong &&
+                  order.is_contiguous() && offsets.is_contiguous() && order.numel() == g.size(0) && offsets.numel() >= 1,
+              "segment_sum_rows: order [E] / offsets [U + 1] must be contiguous int64 CUDA tensors");
+  c10::cuda::CUDAGuard guard(g.device());
+  const long U = offsets.numel() - 1;
+  Tensor out = at::empty({U, g.size(1)}, g.options());
+  check_rc(vb_segment_sum_rows(g.data_ptr(), order.data_ptr<long>(), offsets.data_ptr<long>(), out.data_ptr(), U, (int)g.size(1), cur_stream()),
+           "segment_sum_rows");
+  return out;
+}
+
 Tensor swiglu_fwd(const Tensor& gu) {
   CHECK_CUDA_BF16(gu);
   TORCH_CHECK(gu.is_contiguous() && gu.dim() == 2, "swiglu: contiguous [T,2I] expected");
@@ -242,6 +257,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("rmsnorm_fwd(Tensor x, Tensor? res, Tensor w, float eps, bool write_res) -> (Tensor, Tensor, Tensor)", &rmsnorm_fwd);
   m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor? dres, Tensor(a!)? dw) -> Tensor", &rmsnorm_bwd);
   m.def("rope_(Tensor(a!) x, Tensor pos, Tensor cos, Tensor sin, int nheads, int D, float sign) -> ()", &rope_);
+  m.def("segment_sum_rows(Tensor g, Tensor order, Tensor offsets) -> Tensor", &segment_sum_rows);
   m.def("swiglu_fwd(Tensor gu) -> Tensor", &swiglu_fwd);
   m.def("swiglu_bwd(Tensor gu, Tensor dout) -> Tensor", &swiglu_bwd);
   m.def("adamw_(Tensor(a!) p32, Tensor(b!) m, Tensor(c!) v, Tensor g, Tensor? p16, float lr, float b1, float b2, float eps, float wd, int step, Tensor? scalars) -> ()", &adamw_);

@@ -449,6 +449,43 @@ extern "C" int vb_rope(void* x, const int* pos, const float* cs, const float* sn
   return 0;
 }
 
+// out[u, :] = sum of g[order[j], :] for j in [offsets[u], offsets[u + 1]) — the backward of a row gather with repeated
+// indices (prefix sharing: the shared prompt rows receive the gradients of all their copies). One CTA per output row,
+// fp32 accumulation, no atomics, deterministic. C % 8 == 0.
+namespace vb {
+__global__ void __launch_bounds__(256) segment_sum_rows_kernel(const bf16* __restrict__ g, const long* __restrict__ order,
+                                                               const long* __restrict__ offsets, bf16* __restrict__ out, int C) {
+  const long u = blockIdx.x;
+  const long j0 = offsets[u], j1 = offsets[u + 1];
+  const int nvec = C / 8;
+  for (int v = threadIdx.x; v < nvec; v += 256) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (long j = j0; j < j1; ++j) {
+      const uint4 x = reinterpret_cast<const uint4*>(g + order[j] * (long)C)[v];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        acc[2 * k] += f.x;
+        acc[2 * k + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+    reinterpret_cast<uint4*>(out + u * (long)C)[v] = o;
+  }
+}
+}  // namespace vb
+
+extern "C" int vb_segment_sum_rows(const void* g, const long* order, const long* offsets, void* out, long U, int C, cudaStream_t st) {
+  if (U <= 0) return 0;
+  if (C % 8) return -2;
+  vb::segment_sum_rows_kernel<<<(unsigned)U, 256, 0, st>>>((const vb::bf16*)g, order, offsets, (vb::bf16*)out, C);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
 extern "C" int vb_swiglu_fwd(const void* gu, void* out, long T, int I, cudaStream_t st) {
   if (I % 8) return -2;
   if (T == 0) return 0;

@@ -43,7 +43,7 @@ class PackedBatch:
         # sequence parallelism: input_ids / position_ids are this rank's slice, cu_seqlens describe the whole micro-batch and
         # this holds the (padded) positions of all its tokens
         self.global_position_ids = None
-        # prefix sharing: (expand [E], back [T]) int64 index tensors. input_ids / position_ids then hold every distinct prompt
+        # prefix sharing: (expand [E], back [T], order [E], offsets [T + 1]) int64 index tensors. input_ids / position_ids then hold every distinct prompt
         # once; cu_seqlens describe the E-row layout of full sequences that attention runs on (rows = x[expand]) and
         # back picks, for each of the T stored tokens, its row of that layout (see verl_b200.utils.prefix_sharing)
         self.attn_expand = None
@@ -100,9 +100,11 @@ class Attention(nn.Module):
 
             o = ulysses_attention(qkv, pb, cfg, sp_group)
         elif pb.attn_expand is not None:
-            expand, back = pb.attn_expand
-            o = ops.attention_varlen(qkv.index_select(0, expand), pb.cu_seqlens, cfg.num_attention_heads, cfg.num_key_value_heads,
-                                     cfg.head_dim, pb.max_seqlen, pb.cu_seqlens_cpu).index_select(0, back)
+            from verl_b200.utils.prefix_sharing import expand_rows, select_rows
+
+            expand, back, order, offsets = pb.attn_expand
+            o = select_rows(ops.attention_varlen(expand_rows(qkv, expand, order, offsets), pb.cu_seqlens, cfg.num_attention_heads,
+                                                 cfg.num_key_value_heads, cfg.head_dim, pb.max_seqlen, pb.cu_seqlens_cpu), back)
         else:
             o = ops.attention_varlen(qkv, pb.cu_seqlens, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                                      pb.max_seqlen, pb.cu_seqlens_cpu)

@@ -17,7 +17,7 @@ from typing import Optional
 
 import torch
 
-__all__ = ["prompt_groups", "SharedPack", "build_shared_pack", "group_preserving_micro_batches"]
+__all__ = ["prompt_groups", "SharedPack", "build_shared_pack", "group_preserving_micro_batches", "expand_rows", "select_rows"]
 
 
 def prompt_groups(input_ids: torch.Tensor, attention_mask: torch.Tensor, prompt_len: int) -> tuple[torch.Tensor, torch.Tensor]:
@@ -34,6 +34,49 @@ def prompt_groups(input_ids: torch.Tensor, attention_mask: torch.Tensor, prompt_
     return inv, first[inv]
 
 
+class _ExpandRows(torch.autograd.Function):
+    """``x[idx]`` for an index with repeats. Backward sums the gradients of all copies of a row in one pass over a
+    (order, offsets) list — one CTA per source row on the GPU kernel, no atomics — instead of an atomic scatter-add."""
+
+    @staticmethod
+    def forward(ctx, x, idx, order, offsets):
+        ctx.save_for_backward(idx, order, offsets)
+        ctx.n = x.shape[0]
+        return x.index_select(0, idx)
+
+    @staticmethod
+    def backward(ctx, g):
+        idx, order, offsets = ctx.saved_tensors
+        from verl_b200.ops import _ext
+
+        if g.is_cuda and g.dtype == torch.bfloat16 and _ext.available() and g.shape[1] % 8 == 0:
+            return _ext.ops().segment_sum_rows(g.contiguous(), order, offsets), None, None, None
+        return torch.zeros(ctx.n, *g.shape[1:], dtype=g.dtype, device=g.device).index_add_(0, idx, g), None, None, None
+
+
+class _SelectRows(torch.autograd.Function):
+    """``x[idx]`` for an index WITHOUT repeats: the backward is a plain row copy into zeros."""
+
+    @staticmethod
+    def forward(ctx, x, idx):
+        ctx.save_for_backward(idx)
+        ctx.n = x.shape[0]
+        return x.index_select(0, idx)
+
+    @staticmethod
+    def backward(ctx, g):
+        (idx,) = ctx.saved_tensors
+        return torch.zeros(ctx.n, *g.shape[1:], dtype=g.dtype, device=g.device).index_copy_(0, idx, g), None
+
+
+def expand_rows(x: torch.Tensor, expand: torch.Tensor, order: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+    return _ExpandRows.apply(x, expand, order, offsets)
+
+
+def select_rows(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    return _SelectRows.apply(x, idx)
+
+
 class SharedPack:
     """Index tensors of one prefix-shared micro-batch.
 
@@ -42,11 +85,15 @@ class SharedPack:
     ``back``      [U] int64      full-layout row of every unique token
     """
 
-    __slots__ = ("keep", "expand", "back", "n_unique", "n_full")
+    __slots__ = ("keep", "expand", "back", "n_unique", "n_full", "order", "offsets")
 
     def __init__(self, keep, expand, back):
         self.keep, self.expand, self.back = keep, expand, back
         self.n_unique, self.n_full = int(back.numel()), int(expand.numel())
+        # copies of every unique row, grouped: order[offsets[u]:offsets[u+1]] are the full-layout rows that read unique row u
+        self.order = torch.argsort(expand, stable=True)
+        self.offsets = torch.zeros(self.n_unique + 1, dtype=torch.int64, device=expand.device)
+        self.offsets[1:] = torch.cumsum(torch.bincount(expand, minlength=self.n_unique), 0)
 
 
 def build_shared_pack(attention_mask: torch.Tensor, prompt_len: int, first_row: torch.Tensor) -> SharedPack:

@@ -535,12 +535,12 @@ class FSDPEngine(BaseEngine):
         routed = mb["routed_experts"][sp.keep] if "routed_experts" in mb else None
         pb = PackedBatch(mb["input_ids"][sp.keep], mb["position_ids"][sp.keep].to(torch.int32), pb_full.cu_seqlens, pb_full.cu_seqlens_cpu,
                          pb_full.max_seqlen, routed)
-        pb.attn_expand = (sp.expand, sp.back)
+        pb.attn_expand = (sp.expand, sp.back, sp.order, sp.offsets)
         h = self.model.forward_hidden(pb)
         sel = idx[valid]
         temperature = float(meta.get("temperature", 1.0))
         need_entropy = bool(meta.get("calculate_entropy", False))
-        h_sel = h.index_select(0, sp.expand.index_select(0, sel))
+        h_sel = h.index_select(0, sp.expand.index_select(0, sel))      # a few repeats only (last prompt row of each group)
         lp, ent = ops.linear_logprob_entropy(h_sel, self.model.output_weight, labels_full.index_select(0, sel), temperature, need_entropy)
         full = torch.zeros(idx.shape, dtype=torch.float32, device=h.device)
         out = {"log_probs": full.masked_scatter(valid, lp.float())}
