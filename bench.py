@@ -79,6 +79,8 @@ def build_config(args, world: int):
         ov.append("actor_rollout_ref.ref.fsdp_config.param_offload=true")
     if args.prefix_sharing:
         ov.append("actor_rollout_ref.actor.use_prefix_grouper=true")
+    if args.rollout_quant:
+        ov.append(f"actor_rollout_ref.rollout.quantization={args.rollout_quant}")
     if args.rollout_tp > 1:
         ov.append(f"actor_rollout_ref.rollout.tensor_model_parallel_size={args.rollout_tp}")
         ov.append(f"actor_rollout_ref.rollout.max_num_seqs={prompts_per_gpu * args.n * args.rollout_tp}")
@@ -162,13 +164,13 @@ def run_native(args):
         out = {
             "metric": "GRPO step tokens/s (rollout+train), Qwen2.5-7B arch", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None, "dtype": "bf16", "data": "synthetic prompts, random-init weights",
+            "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None, "dtype": "bf16" if not args.rollout_quant else f"bf16 training, {args.rollout_quant} rollout projections", "data": "synthetic prompts, random-init weights",
             "impl": "native",
             "config": {"model": args.model, "global_batch": f"{args.prompts_per_gpu * world} prompts x n={args.n}",
                        "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + response <= {args.response_length}",
                        "parallelism": f"dp{world} (ZeRO-2 sharded optimizer, resident bf16 params), rollout tp{args.rollout_tp} x {world // args.rollout_tp} replicas colocated",
                        "ppo_mini_batch_prompts": args.mini_prompts_per_gpu * world, "token_budget_per_micro_batch": args.token_budget,
-                       "gradient_checkpointing": bool(args.grad_ckpt), "ref_param_offload": bool(args.ref_offload), "prefix_sharing": bool(args.prefix_sharing), "loss": "grpo clip 0.2 + low_var_kl 1e-3, AdamW lr 1e-6",
+                       "gradient_checkpointing": bool(args.grad_ckpt), "ref_param_offload": bool(args.ref_offload), "prefix_sharing": bool(args.prefix_sharing), "rollout_quantization": args.rollout_quant or None, "loss": "grpo clip 0.2 + low_var_kl 1e-3, AdamW lr 1e-6",
                        "l2_policy": "inputs larger than L2: each step streams >15 GB of weights and fresh activations"},
             "clocks": _summarise_clocks(samples),
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -224,6 +226,7 @@ def main():
     ap.add_argument("--kv-util", type=float, default=0.3)
     ap.add_argument("--grad-ckpt", type=int, default=-1,
                     help="activation recomputation (default off: activations of an 8192-token micro-batch are stored)")
+    ap.add_argument("--rollout-quant", type=str, default="", help="fp8: W8A8 rollout projections (not the headline config; dtype is then reported as bf16+fp8 rollout)")
     ap.add_argument("--prefix-sharing", type=int, default=0,
                     help="forward/backward every distinct prompt once for its n responses (actor.use_prefix_grouper); off = the reference's default")
     ap.add_argument("--ref-offload", type=int, default=-1, help="keep the frozen reference weights in pinned host memory between its passes")
