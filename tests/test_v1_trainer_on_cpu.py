@@ -146,3 +146,48 @@ def test_v1_separate_async_trainer_feeds_a_standalone_replica_and_pushes_weights
     want = float(sum(p.detach().double().sum() for p in eng.model.parameters()))
     assert abs(seen["checksum"] - want) < 1e-6 * max(1.0, abs(want))
     assert replica._proc.poll() is not None                   # the pool was shut down with the trainer
+
+
+def test_transfer_queue_over_tcp_between_processes(tmp_path):
+    """A served TransferQueue: a child process writes trajectories, this process blocks on the server until they are tagged
+    finished, reads them back as a batch and sees the child's tags; server-side errors come back as exceptions."""
+    import subprocess
+    import sys
+
+    import pytest
+
+    from verl_b200.utils.transfer_queue_remote import RemoteTransferQueue, TransferQueueServer
+
+    srv = TransferQueueServer()
+    child = (
+        "import sys, torch\n"
+        "from verl_b200.protocol import DataProto\n"
+        "from verl_b200.utils.transfer_queue import KVBatchMeta\n"
+        "from verl_b200.utils.transfer_queue_remote import RemoteTransferQueue\n"
+        "q = RemoteTransferQueue(sys.argv[1])\n"
+        "d = DataProto.from_dict(tensors={'x': torch.arange(8).reshape(4, 2)}, non_tensors={'name': ['a', 'b', 'c', 'd']})\n"
+        "q.kv_batch_put(KVBatchMeta('train', ['k0', 'k1', 'k2', 'k3']), d, tags={'status': 'finished', 'gen_step': 3})\n"
+        "q.kv_put('train', 'k4', tags={'status': 'running'})\n"
+    )
+    import os
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.Popen([sys.executable, "-c", child, srv.address], env=dict(os.environ, PYTHONPATH=repo))
+    q = RemoteTransferQueue(srv.address)
+    try:
+        assert q.wait_for_tags("train", 4, {"status": "finished"}, timeout=120)
+        assert p.wait(timeout=60) == 0
+        got = q.kv_get(KVBatchMeta("train", ["k2", "k0"], ["x", "name"]))
+        assert got.batch["x"].tolist() == [[4, 5], [0, 1]] and got.non_tensor_batch["name"].tolist() == ["c", "a"]
+        tags = q.kv_tags("train")
+        assert tags["k1"] == {"status": "finished", "gen_step": 3} and tags["k4"]["status"] == "running" and q.size("train") == 5
+        assert not q.wait_for_tags("train", 5, {"status": "finished"}, timeout=0.2)
+        q.kv_clear("train", ["k4"])
+        assert srv.queue.size("train") == 4                     # the server's store is the one being edited
+        with pytest.raises(RuntimeError, match="KeyError"):
+            q.kv_get(KVBatchMeta("train", ["missing"]))
+        rb = ReplayBuffer(q, rollout_n=1)                       # the replay buffer works against the remote store unchanged
+        assert rb.get_sampleable_count(3, "train") == 4
+    finally:
+        q.close()
+        srv.shutdown()
