@@ -13,6 +13,8 @@
 //   PAGED   decode: the G query heads of one KV group of one sequence form the (zero-padded) 128-row tile, K/V come
 //           from a paged cache through the block table, optional split-KV with partial results merged afterwards.
 //           Replaces vLLM's paged attention (verl/workers/rollout/vllm_rollout/vllm_async_server.py:690-697).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "tma_host.h"
 
@@ -24,6 +26,7 @@ constexpr int ATT_BN = 128;       // kv rows per tile
 constexpr int ATT_TILE_BYTES = 128 * 128 * 2;  // one [128 x 128] bf16 tile = two 64-column swizzle atoms
 constexpr int ATT_HALF = 128 * 64 * 2;         // one atom: 128 rows x 128 B
 constexpr int ATT_SMEM = ATT_TILE_BYTES * (1 + 4 + 1) + 1024 + 128;
+constexpr int ATT_SMEM_COMPACT = ATT_TILE_BYTES * 3 + 1024 + 128;      // two CTAs per SM
 
 struct AttnVarlenTile {  // host-built work list entry
   int q_tok0;      // global token index of the first query row
@@ -53,16 +56,19 @@ struct AttnParams {
   int* err_word;
 };
 
-template <bool PAGED>
-__global__ void __launch_bounds__(128, 1)
+// COMPACT: three tiles of shared memory (Q, K, V) instead of six so that TWO CTAs share an SM and one CTA's softmax
+// overlaps the other's tensor-core work. P is written over the K tile (K is dead once S = Q K^T has completed); the next K
+// and V tiles are requested as soon as the PV product has consumed P and V.
+template <bool PAGED, bool COMPACT>
+__global__ void __launch_bounds__(128, COMPACT ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sKV = smem + ATT_TILE_BYTES;                // stage s: K at +s*2*TILE, V at +s*2*TILE + TILE
-  uint8_t* sP = smem + ATT_TILE_BYTES * 5;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATT_TILE_BYTES * 6);
+  uint8_t* sP = COMPACT ? sKV : smem + ATT_TILE_BYTES * 5;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATT_TILE_BYTES * (COMPACT ? 3 : 6));
   uint64_t* q_bar = bars;
   uint64_t* kv_bar = bars + 1;   // [2]
   uint64_t* s_bar = bars + 3;
@@ -117,32 +123,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_O = tmem_base + 128;    // columns [128,256)
   const uint32_t lane_off = uint32_t(warp * 32) << 16;
 
-  auto load_kv = [&](int j, int stage) {  // thread 0 only
-    uint8_t* sK = sKV + stage * 2 * ATT_TILE_BYTES;
-    uint8_t* sV = sK + ATT_TILE_BYTES;
-    mbar_expect_tx(&kv_bar[stage], 2 * ATT_TILE_BYTES);
+  // which = 0: K rows of kv tile j, which = 1: V rows; `dst` one tile of shared memory, `bar` gets the bytes (thread 0 only)
+  auto load_half = [&](int j, int which, uint8_t* dst, uint64_t* bar) {
+    const CUtensorMap* tm = which ? &tmV : &tmK;
     if (!PAGED) {
       const int y = seq_tok0 + j * ATT_BN;
       const int x = kv_head * ATT_D;
-      tma_load_2d(sK, &tmK, x, y, &kv_bar[stage]);
-      tma_load_2d(sK + ATT_HALF, &tmK, x + 64, y, &kv_bar[stage]);
-      tma_load_2d(sV, &tmV, x, y, &kv_bar[stage]);
-      tma_load_2d(sV + ATT_HALF, &tmV, x + 64, y, &kv_bar[stage]);
+      tma_load_2d(dst, tm, x, y, bar);
+      tma_load_2d(dst + ATT_HALF, tm, x + 64, y, bar);
     } else {
       // cache layer viewed as rows [(block*2 + kv)*Hkv + head]*64 + slot, 128 columns; block size 64
 #pragma unroll
       for (int h2 = 0; h2 < 2; ++h2) {
         const int blk_idx = (kv_tile0 + j) * 2 + h2;
         const int blk = blk_idx < p.max_blocks ? p.block_table[(long)b * p.max_blocks + blk_idx] : 0;
-        const int yk = ((blk * 2 + 0) * p.n_kv_heads + kv_head) * 64;
-        const int yv = ((blk * 2 + 1) * p.n_kv_heads + kv_head) * 64;
+        const int y = ((blk * 2 + which) * p.n_kv_heads + kv_head) * 64;
         // rows [64*h2, 64*h2+64) of each 64-column atom
-        tma_load_2d(sK + h2 * 64 * 128, &tmK, 0, yk, &kv_bar[stage]);
-        tma_load_2d(sK + ATT_HALF + h2 * 64 * 128, &tmK, 64, yk, &kv_bar[stage]);
-        tma_load_2d(sV + h2 * 64 * 128, &tmV, 0, yv, &kv_bar[stage]);
-        tma_load_2d(sV + ATT_HALF + h2 * 64 * 128, &tmV, 64, yv, &kv_bar[stage]);
+        tma_load_2d(dst + h2 * 64 * 128, tm, 0, y, bar);
+        tma_load_2d(dst + ATT_HALF + h2 * 64 * 128, tm, 64, y, bar);
       }
     }
+  };
+  auto load_kv = [&](int j, int stage) {  // thread 0 only; double-buffered layout: both halves on the stage's barrier
+    uint8_t* sK = sKV + stage * 2 * ATT_TILE_BYTES;
+    mbar_expect_tx(&kv_bar[stage], 2 * ATT_TILE_BYTES);
+    load_half(j, 0, sK, &kv_bar[stage]);
+    load_half(j, 1, sK + ATT_TILE_BYTES, &kv_bar[stage]);
+  };
+  auto load_compact = [&](int j) {        // thread 0 only; compact layout: kv_bar[0] counts K, kv_bar[1] counts V
+    mbar_expect_tx(&kv_bar[0], ATT_TILE_BYTES);
+    load_half(j, 0, sKV, &kv_bar[0]);
+    mbar_expect_tx(&kv_bar[1], ATT_TILE_BYTES);
+    load_half(j, 1, sKV + ATT_TILE_BYTES, &kv_bar[1]);
   };
 
   bool ok = true;
@@ -150,7 +162,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_expect_tx(q_bar, ATT_TILE_BYTES);
     tma_load_2d(sQ, &tmQ, q_x, q_y, q_bar);
     tma_load_2d(sQ + ATT_HALF, &tmQ, q_x + 64, q_y, q_bar);
-    load_kv(0, 0);
+    if (COMPACT) load_compact(0);
+    else load_kv(0, 0);
   }
 
   float o_acc[ATT_D];
@@ -167,10 +180,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 
   for (int j = 0; j < num_kv_tiles && ok; ++j) {
-    const int stage = j & 1;
-    const uint32_t kv_phase = (j >> 1) & 1;
+    const int stage = COMPACT ? 0 : (j & 1);
+    const uint32_t kv_phase = COMPACT ? (j & 1) : ((j >> 1) & 1);
     const uint32_t it_phase = j & 1;
-    if (tid == 0 && j + 1 < num_kv_tiles) load_kv(j + 1, stage ^ 1);   // stage^1 was released by the o_bar wait of j-1
+    if (!COMPACT && tid == 0 && j + 1 < num_kv_tiles) load_kv(j + 1, stage ^ 1);   // stage^1 was released by the o_bar wait of j-1
     if (!mbar_wait(&kv_bar[stage], kv_phase, abort_flag, p.err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
     uint8_t* sK = sKV + stage * 2 * ATT_TILE_BYTES;
     uint8_t* sV = sK + ATT_TILE_BYTES;
@@ -242,6 +255,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    if (COMPACT && !mbar_wait(&kv_bar[1], kv_phase, abort_flag, p.err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
     if (tid == 0) {
       tc_fence_after();
       const uint32_t pa = smem_u32(sP), va = smem_u32(sV);
@@ -256,6 +270,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     if (!mbar_wait(o_bar, it_phase, abort_flag, p.err_word, VB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
     tc_fence_after();
+    if (COMPACT && tid == 0 && j + 1 < num_kv_tiles) load_compact(j + 1);   // P (in the K tile) and V have been consumed
 #pragma unroll
     for (int c = 0; c < ATT_D / 32; ++c) {
       uint32_t v[32];
@@ -339,11 +354,22 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   out[(long)b * ld_out + h * ATT_D + d] = __float2bfloat16(l > 0.f ? acc / l : 0.f);
 }
 
+// VERL_B200_ATTN_COMPACT=0 selects the double-buffered one-CTA-per-SM layout
+static bool attn_compact() {
+  static const bool on = []() { const char* e = getenv("VERL_B200_ATTN_COMPACT"); return e == nullptr || e[0] != '0'; }();
+  return on;
+}
+
 static int set_attn_smem() {
   static bool done = false;
   if (!done) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess) return -10;
-    if (cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess) return -10;
+    if (cudaFuncSetAttribute(attn_fwd_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess) return -10;
+    if (cudaFuncSetAttribute(attn_fwd_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess) return -10;
+    if (cudaFuncSetAttribute(attn_fwd_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM_COMPACT) != cudaSuccess) return -10;
+    if (cudaFuncSetAttribute(attn_fwd_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM_COMPACT) != cudaSuccess) return -10;
+    // both CTAs of an SM need their shared memory at the same time: ask for the largest carve-out
+    cudaFuncSetAttribute(attn_fwd_kernel<false, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(attn_fwd_kernel<true, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     done = true;
   }
   return 0;
@@ -371,7 +397,8 @@ extern "C" int vb_attn_varlen_fwd(const void* q, const void* k, const void* v, l
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err_word = err_word;
   dim3 grid(n_tiles, n_q_heads);
-  attn_fwd_kernel<false><<<grid, 128, ATT_SMEM, st>>>(tmQ, tmK, tmV, p);
+  if (attn_compact()) attn_fwd_kernel<false, true><<<grid, 128, ATT_SMEM_COMPACT, st>>>(tmQ, tmK, tmV, p);
+  else attn_fwd_kernel<false, false><<<grid, 128, ATT_SMEM, st>>>(tmQ, tmK, tmV, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -403,7 +430,8 @@ extern "C" int vb_attn_paged_decode(const void* q, long ld_q, const void* cache,
   p.part_o = part_o; p.part_ml = part_ml; p.err_word = err_word;
   if (p.num_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return -4;
   dim3 grid(B, n_kv_heads, p.num_splits);
-  attn_fwd_kernel<true><<<grid, 128, ATT_SMEM, st>>>(tmQ, tmK, tmV, p);
+  if (attn_compact()) attn_fwd_kernel<true, true><<<grid, 128, ATT_SMEM_COMPACT, st>>>(tmQ, tmK, tmV, p);
+  else attn_fwd_kernel<true, false><<<grid, 128, ATT_SMEM, st>>>(tmQ, tmK, tmV, p);
   if (cudaGetLastError() != cudaSuccess) return -11;
   if (p.num_splits > 1) {
     dim3 g2(B, n_q_heads);
