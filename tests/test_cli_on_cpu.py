@@ -36,3 +36,24 @@ def test_print_cfg(capsys):
 
     main(["data.train_batch_size=12"])
     assert "train_batch_size: 12" in capsys.readouterr().out
+
+
+def test_main_ppo_dispatches_v1_trainers(tmp_path):
+    """``trainer.use_v1=true trainer.trainer_mode=sync`` runs the v1 sync trainer from the same entry point."""
+    import json
+    import os
+
+    from tests.test_trainer_e2e_on_cpu import OV
+    from verl_b200.trainer.main_ppo import main
+
+    logf = tmp_path / "v1.jsonl"
+    os.environ["VERL_FILE_LOGGER_PATH"] = str(logf)
+    try:
+        tr = main([o for o in OV if not o.startswith("trainer.logger")] +
+                  ["trainer.logger=[file]", "trainer.total_training_steps=1", f"trainer.default_local_dir={tmp_path}/ckpt", "trainer.resume_mode=disable",
+                   "trainer.use_v1=true", "trainer.trainer_mode=sync", "actor_rollout_ref.rollout.mode=async", "actor_rollout_ref.rollout.free_cache_engine=false"])
+    finally:
+        os.environ.pop("VERL_FILE_LOGGER_PATH", None)
+    assert type(tr).__name__ == "PPOTrainerSync"
+    rows = [json.loads(x)["data"] for x in logf.read_text().splitlines()]
+    assert len(rows) == 1 and "replay/staleness_max" in rows[0]

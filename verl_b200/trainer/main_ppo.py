@@ -43,6 +43,15 @@ def run_ppo(config):
     tokenizer = _load_tokenizer(config.data.get("tokenizer") or config.actor_rollout_ref.model.get("path"))
     reward_fn = load_reward_manager(config, tokenizer, num_examine=0)
     val_reward_fn = load_reward_manager(config, tokenizer, num_examine=1)
+    v1 = config.trainer.get("trainer_mode", "sync") if config.trainer.get("use_v1", False) else None
+    if v1:
+        # v1 family (generation decoupled through the TransferQueue): sync | colocate_async | separate_async
+        from verl_b200.trainer.ppo.v1 import get_trainer_cls
+
+        trainer = get_trainer_cls(str(v1))(config, tokenizer=tokenizer, reward_fn=reward_fn, val_reward_fn=val_reward_fn)
+        trainer.init()
+        trainer.fit()
+        return trainer
     trainer = PPOTrainer(config, tokenizer=tokenizer, reward_fn=reward_fn, val_reward_fn=val_reward_fn)
     trainer.init_workers()
     trainer.fit()
