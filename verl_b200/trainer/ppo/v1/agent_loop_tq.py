@@ -80,5 +80,9 @@ class AgentLoopManagerTQ:
         while self.inflight > 0 and time.time() - t0 < timeout_s:
             self.server_manager.abort_all_requests()
             time.sleep(0.01)
+        try:        # close the HTTP session of remote replicas inside its own event loop
+            asyncio.run_coroutine_threadsafe(self.worker.client.close(), self._loop).result(timeout=5)
+        except Exception:  # noqa: BLE001 - best effort at shutdown
+            pass
         self._loop.call_soon_threadsafe(self._loop.stop)
         self._thread.join(timeout=10)
