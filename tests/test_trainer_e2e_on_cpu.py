@@ -86,3 +86,22 @@ def test_two_rank_gloo_fit(tmp_path):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     rows = [json.loads(x) for x in logf.read_text().splitlines()]
     assert len(rows) == 2 and rows[-1]["data"]["perf/total_num_tokens"] > 0 and abs(rows[0]["data"]["actor/ppo_kl"]) < 1e-4
+
+
+def test_reward_model_worker_scores_the_last_response_token(tmp_path):
+    """A frozen scalar-head model scores every trajectory; its score lands on the last response token and is added to the rule
+    reward before advantages are computed."""
+    tr = build(tmp_path, ["trainer.total_training_steps=1", "reward.reward_model.enable=true", "reward.reward_model.preset=tiny-qwen2",
+                          "reward.reward_model.micro_batch_size_per_gpu=16"])
+    assert tr.rm_wg is not None and tr.rm_wg.worker.rm.engine.cfg.value_head and tr.rm_wg.worker.rm.engine.forward_only
+    tr.global_steps = 1
+    m = tr.step(next(iter(tr.train_dataloader)))
+    assert "reward_model/score_mean" in m
+    b = tr._last_batch.batch
+    rm = tr.rm_wg.compute_rm_score(tr._last_batch).batch["rm_scores"]
+    mask = b["response_mask"]
+    last = (mask.sum(-1) - 1).long()
+    rows = torch.arange(rm.shape[0])
+    assert (rm.abs().sum(-1) == rm[rows, last].abs()).all() and rm[rows, last].abs().sum() > 0       # one non-zero entry per row, at the last token
+    rule = b["token_level_scores"] - rm
+    assert ((rule == 0) | (rule == 1)).all()                                                            # what is left is the 0/1 rule reward

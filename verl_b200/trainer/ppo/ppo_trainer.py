@@ -160,7 +160,7 @@ class PPOTrainer:
 
     # ------------------------------------------------------------------ workers
     def init_workers(self):
-        from verl_b200.workers.engine_workers import ActorRolloutRefWorker, CriticWorker
+        from verl_b200.workers.engine_workers import ActorRolloutRefWorker, CriticWorker, RewardModelWorker
 
         backend = _g(self.config, "trainer.worker_backend", "spmd")
         role = "actor_rollout_ref" if self.use_reference_policy else "actor_rollout"
@@ -188,6 +188,15 @@ class PPOTrainer:
         else:
             raise ValueError(f"unknown trainer.worker_backend {backend}")
         self.ref_policy_wg = self.actor_rollout_wg
+        self.rm_wg = None
+        if bool(_g(self.config, "reward.reward_model.enable", False)):
+            # a frozen scalar-head model scores the samples; rule rewards (if any) are added on top
+            if backend != "spmd":
+                raise NotImplementedError("the reward-model worker runs on the spmd backend")
+            from verl_b200.single_controller.spmd import SPMDWorkerGroup
+
+            self.rm_wg = SPMDWorkerGroup(cls_with_init_args=ClassWithInitArgs(RewardModelWorker, config=self.config.reward.reward_model))
+            self.rm_wg.init_model()
         if self.critic_wg is not None:
             self.critic_wg.init_model()
         self.actor_rollout_wg.init_model()
@@ -365,6 +374,10 @@ def _train_on_rollouts(self: PPOTrainer, batch: DataProto, timing_raw: dict, n: 
         batch.meta_info["temperature"] = float(cfg.actor_rollout_ref.rollout.temperature)
         with marked_timer("reward", timing_raw):
             reward_tensor, reward_extra = compute_reward(batch, self.reward_fn)
+            if getattr(self, "rm_wg", None) is not None:
+                rm = self.rm_wg.compute_rm_score(batch).batch["rm_scores"]
+                metrics["reward_model/score_mean"] = float(rm.sum(-1).mean())
+                reward_tensor = reward_tensor + rm.to(reward_tensor.dtype) if bool(_g(cfg, "reward.reward_model.add_rule_reward", True)) else rm.to(reward_tensor.dtype)
         rc = cfg.algorithm.get("rollout_correction") or {}
         bypass = bool(rc.get("bypass_mode", False))
         if bypass:

@@ -512,3 +512,44 @@ class CriticWorker(Worker):
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def load_checkpoint(self, local_path, hdfs_path=None, del_local_after_load=False):
         self.critic.engine.load_checkpoint(local_path, hdfs_path, del_local_after_load)
+
+
+class RewardModelWorker(Worker):
+    """Discriminative reward model: a frozen model with a scalar head scores every (prompt, response) pair; the score of the
+    last response token becomes the sequence reward (``rm_scores`` [bs, R], zero elsewhere). Same engines as the critic, forward
+    only. Reference: the reward-model server behind the reward loop (``verl/experimental/reward_loop/reward_loop.py:93-343``,
+    discriminative ``/classify``-style scoring) and the legacy ``RewardModelWorker``."""
+
+    def __init__(self, config):
+        super().__init__()
+        ensure_process_group(int(cfg_get(config, "nccl_timeout", 600)))
+        self.config = config
+        self.rm: Optional[TrainingWorker] = None
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def init_model(self):
+        c = self.config
+        strategy = cfg_get(c, "strategy", "fsdp")
+        eng = dict(cfg_get(c, "fsdp_config", {}) or {}) if str(strategy).startswith("fsdp") else dict(cfg_get(c, "megatron", {}) or {})
+        eng["forward_only"] = True
+        model = cfg_get(c, "model", None) or {"path": cfg_get(c, "path", None), "preset": cfg_get(c, "preset", None)}
+        mbs = cfg_get(c, "micro_batch_size_per_gpu", None)
+        cfg = {"model_type": "value_model", "backend": strategy, "model": model, "engine": eng, "optim": None, "checkpoint": None,
+               "log_prob_micro_batch_size_per_gpu": mbs, "ppo_micro_batch_size_per_gpu": mbs,
+               "log_prob_use_dynamic_bsz": cfg_get(c, "use_dynamic_bsz", False), "log_prob_max_token_len_per_gpu": cfg_get(c, "forward_max_token_len_per_gpu", None),
+               "nccl_timeout": cfg_get(c, "nccl_timeout", 600)}
+        self.rm = TrainingWorker(cfg, role="reward_model")
+        self.rm.reset()
+        e = self.rm.engine
+        self._register_dispatch_collect_info("reward_model", dp_rank=e.get_data_parallel_rank(), is_collect=e.is_mp_src_rank_with_outputs())
+
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("reward_model"))
+    def compute_rm_score(self, data: DataProto) -> DataProto:
+        d = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=dict(data.meta_info))
+        vals = self.rm.infer_batch(d)["model_output"]["values"].float().cpu()           # [bs, R] head output per response token
+        mask = data.batch["response_mask"].cpu()
+        last = (mask.sum(-1) - 1).clamp(min=0).long()
+        scores = torch.zeros_like(vals)
+        rows = torch.arange(vals.shape[0])
+        scores[rows, last] = vals[rows, last] * (mask.sum(-1) > 0).to(vals.dtype)
+        return DataProto.from_dict(tensors={"rm_scores": scores})
