@@ -234,6 +234,12 @@ class MegatronEngine(FSDPEngine):
         out["log_probs"] = full.masked_scatter(valid, lp.float())
         if ent is not None:
             out["entropy"] = torch.zeros_like(full).masked_scatter(valid, ent.float())
+        if meta.get("score_centering") or meta.get("distillation") or meta.get("return_topk"):
+            # top-k head passes (score centering, distillation) need the whole vocabulary on one rank
+            if self.tp_size > 1:
+                raise NotImplementedError("score centering / distillation heads are not available with a vocabulary-parallel lm_head; "
+                                          "use tensor_model_parallel_size=1 for this role or the sharded-DP engine")
+            self._score_centering_terms(out, mb, meta, h_sel, valid, temperature)
         return None, out
 
     # ------------------------------------------------------------------ p2p
