@@ -9,7 +9,7 @@ NCCL versions kept as baseline/oracle (selected by ``VERL_B200_COMM=nccl``).
 * ``WeightGatherLinear`` y = x @ all_gather(W_shard)ᵀ              — ZeRO-3 parameter all-gather fused into the consuming GEMM.
 
 The reference reaches these through Megatron-Core/TransformerEngine and vLLM (``verl/workers/engine/megatron/
-transformer_impl.py:260-340``).
+transformer_impl.py:260-340``, ``verl/workers/rollout/vllm_rollout/vllm_async_server.py:328-418``).
 """
 
 from __future__ import annotations
