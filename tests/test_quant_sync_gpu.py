@@ -103,3 +103,31 @@ def test_fp8_gemm_matches_dequantised_reference(M, N, K):
     assert ((z.float() - full).norm() / full.norm()).item() < 0.06
     torch.cuda.synchronize()
     _ext.check_status("fp8 gemm")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (300, 520, 2064), (1024, 3584, 4096), (17, 40, 144)])
+def test_fp8_block_scaled_gemm(M, N, K):
+    """Block-scaled e4m3 GEMM (1x128 activation scales, 128x128 weight scales) vs the fp32 product of the dequantised operands."""
+    from verl_b200.ops import _ext
+    from verl_b200.ops.quant import act_cast_to_fp8, blockwise_cast_to_fp8, fp8_block_gemm, fp8_block_linear
+
+    torch.manual_seed(M + N + K)
+    # rows and blocks of very different magnitude: wrong scale indexing would show immediately
+    x = (torch.randn(M, K, device="cuda") * torch.logspace(-2, 1, M, device="cuda")[:, None]).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05 * (1 + torch.arange(N, device="cuda")[:, None] // 128) * (1 + torch.arange(K, device="cuda")[None, :] // 128)).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    a8, sa = act_cast_to_fp8(x)
+    b8, sb = blockwise_cast_to_fp8(w)
+    a_deq = a8.float() * sa.repeat_interleave(128, 1)[:, :K]
+    b_deq = b8.float() * sb.repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+    ref = a_deq @ b_deq.t() + bias.float()
+    y32 = fp8_block_gemm(a8, sa, b8, sb, bias, out_dtype=torch.float32)
+    y = fp8_block_gemm(a8, sa, b8, sb, bias)
+    torch.cuda.synchronize()
+    _ext.check_status("fp8 block gemm")
+    assert (y32 - ref).abs().max() <= 2e-3 * ref.abs().max(), ((y32 - ref).abs().max().item(), ref.abs().max().item())
+    assert (y.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+    z = fp8_block_linear(x, b8, sb, bias)
+    full = x.float() @ w.float().t() + bias.float()
+    assert ((z.float() - full).norm() / full.norm()).item() < 0.06

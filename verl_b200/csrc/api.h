@@ -85,6 +85,8 @@ int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int ld_seg, in
 int vb_fp8_row_cast(const void* x, long ldx, void* y, long ldy, float* scale, long M, int K, cudaStream_t st);
 int vb_gemm_fp8_pair(const void* A, const void* B, void* C, const void* bias, const float* a_scale, const float* b_scale, int M, int N, int K,
                      int lda, int ldb, int ldc, int out_f32, int* err_word, cudaStream_t stream);
+int vb_gemm_fp8_block(const void* A, const void* B, void* C, const float* a_scale, const float* b_scale, const void* bias, int M, int N, int K,
+                      int lda, int ldb, int ldc, int out_f32, int* err_word, cudaStream_t stream);
 int vb_gemm_pair_plan(int M, int N, int K);
 int vb_gemm_bf16_pair_splitk(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb, int ldc, int out_f32,
                              int accumulate, int split_k, float* split_ws, int* err_word, cudaStream_t stream);

@@ -76,6 +76,30 @@ Tensor gemm_fp8(const Tensor& a8, const Tensor& b8, const c10::optional<Tensor>&
   return out;
 }
 
+// Block-scaled e4m3 GEMM: a_scale [M, ceil(K/128)] (1 x 128 groups), b_scale [ceil(N/128), ceil(K/128)] (128 x 128 blocks)
+Tensor gemm_fp8_block(const Tensor& a8, const Tensor& a_scale, const Tensor& b8, const Tensor& b_scale, const c10::optional<Tensor>& bias, bool out_f32) {
+  TORCH_CHECK(a8.is_cuda() && b8.is_cuda() && a8.scalar_type() == at::kFloat8_e4m3fn && b8.scalar_type() == at::kFloat8_e4m3fn, "gemm_fp8_block: operands must be e4m3 CUDA tensors");
+  TORCH_CHECK(a8.dim() == 2 && b8.dim() == 2 && a8.size(1) == b8.size(1) && a8.stride(1) == 1 && b8.stride(1) == 1, "gemm_fp8_block: shapes");
+  const int M = a8.size(0), K = a8.size(1), N = b8.size(0);
+  const int kb = (K + 127) / 128, nb = (N + 127) / 128;
+  TORCH_CHECK(a_scale.scalar_type() == at::kFloat && a_scale.is_contiguous() && a_scale.dim() == 2 && a_scale.size(0) == M && a_scale.size(1) == kb,
+              "gemm_fp8_block: a_scale must be fp32 [M, ceil(K/128)]");
+  TORCH_CHECK(b_scale.scalar_type() == at::kFloat && b_scale.is_contiguous() && b_scale.dim() == 2 && b_scale.size(0) == nb && b_scale.size(1) == kb,
+              "gemm_fp8_block: b_scale must be fp32 [ceil(N/128), ceil(K/128)]");
+  c10::cuda::CUDAGuard guard(a8.device());
+  Tensor out = at::empty({M, N}, a8.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
+  const void* bp = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N, "gemm_fp8_block: bias must be bf16 [N]");
+    bp = bias->data_ptr();
+  }
+  int* err = vb_status_tensor(a8.get_device()).data_ptr<int>();
+  check_rc(vb_gemm_fp8_block(a8.data_ptr(), b8.data_ptr(), out.data_ptr(), a_scale.data_ptr<float>(), b_scale.data_ptr<float>(), bp, M, N, K,
+                             (int)a8.stride(0), (int)b8.stride(0), N, out_f32 ? 1 : 0, err, cur_stream()),
+           "gemm_fp8_block");
+  return out;
+}
+
 // ptrs: CPU int64 [world] peer pointers of the row shards. Returns (fp8 [M_out, N], scales) and, if keep_bf16, also the
 // gathered bf16 rows.
 std::tuple<Tensor, Tensor, Tensor> reshard_quant(const Tensor& ptrs, int64_t rows_per_rank, int64_t ld_src, int64_t row_begin, int64_t M_out,
@@ -135,6 +159,7 @@ TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
   m.def("fp8_block_cast(Tensor x) -> (Tensor, Tensor)", &fp8_block_cast);
   m.def("fp8_act_cast(Tensor x) -> (Tensor, Tensor)", &fp8_act_cast);
   m.def("fp8_row_cast(Tensor x) -> (Tensor, Tensor)", &fp8_row_cast);
+  m.def("gemm_fp8_block(Tensor a8, Tensor a_scale, Tensor b8, Tensor b_scale, Tensor? bias, bool out_f32=False) -> Tensor", &gemm_fp8_block);
   m.def("gemm_fp8(Tensor a8, Tensor b8, Tensor? a_scale, Tensor? b_scale, Tensor? bias, bool out_f32=False) -> Tensor", &gemm_fp8);
   m.def("fp4_fake_quant(Tensor x, Tensor global_amax) -> Tensor", &fp4_fake_quant);
   m.def("reshard_quant(Tensor ptrs, int rows_per_rank, int ld_src, int row_begin, int M_out, int N, bool quantize, bool keep_bf16, Tensor like) -> (Tensor, Tensor, Tensor)", &reshard_quant);

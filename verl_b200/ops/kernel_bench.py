@@ -94,6 +94,12 @@ def bench_gemm_fp8(a):
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     ms_b = timeit(lambda: o.gemm(x, w, out, None, False, False, False, 0), a.iters)
     report("  bf16 kernel, same shape", ms_b, flops=2.0 * M * N * K)
+    from verl_b200.ops.quant import act_cast_to_fp8, blockwise_cast_to_fp8
+
+    a8b, sab = act_cast_to_fp8(x)
+    b8b, sbb = blockwise_cast_to_fp8(w)
+    ms_blk = timeit(lambda: o.gemm_fp8_block(a8b, sab, b8b, sbb, None, False), a.iters)
+    report("  block-scaled variant (1x128 activation / 128x128 weight scales, promotion per K block)", ms_blk, flops=2.0 * M * N * K)
     if a.compare:
         try:
             ms2 = timeit(lambda: torch._scaled_mm(a8, b8.t(), scale_a=sa[:, None], scale_b=sb[None, :], out_dtype=torch.bfloat16), a.iters)

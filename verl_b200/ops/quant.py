@@ -13,7 +13,7 @@ import torch
 from . import _ext
 from .functional import use_native
 
-__all__ = ["blockwise_cast_to_fp8", "act_cast_to_fp8", "dequant_blockwise_fp8", "rowwise_cast_to_fp8", "fp8_gemm", "fp8_linear", "FP8Linear", "fp4_fake_quant", "fp4_fake_quant_ste", "QATLinear",
+__all__ = ["blockwise_cast_to_fp8", "act_cast_to_fp8", "dequant_blockwise_fp8", "rowwise_cast_to_fp8", "fp8_gemm", "fp8_linear", "FP8Linear", "fp8_block_gemm", "fp8_block_linear", "fp4_fake_quant", "fp4_fake_quant_ste", "QATLinear",
            "FP8_MAX", "FP4_MAX"]
 
 FP8_MAX, FP4_MAX = 448.0, 6.0
@@ -81,6 +81,32 @@ def fp8_linear(x: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor, bias: t
     x2 = x.reshape(-1, shp[-1])
     a8, a_s = rowwise_cast_to_fp8(x2)
     return fp8_gemm(a8, w8, a_s, w_scale, bias, x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.bfloat16).reshape(*shp[:-1], w8.shape[0])
+
+
+def fp8_block_gemm(a8: torch.Tensor, a_scale: torch.Tensor, b8: torch.Tensor, b_scale: torch.Tensor, bias: torch.Tensor = None,
+                   out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Block-scaled e4m3 GEMM: ``a8 [M, K]`` with 1×128 scales ``a_scale [M, ⌈K/128⌉]`` (``act_cast_to_fp8``), ``b8 [N, K]`` with
+    128×128 scales ``b_scale [⌈N/128⌉, ⌈K/128⌉]`` (``blockwise_cast_to_fp8``) — the layout fp8 rollout weights are shipped in.
+    sm_100a: tcgen05 ``kind::f8f6f4`` partial products per K block, promoted with their scales in registers."""
+    if a8.is_cuda and _ext.available() and a8.shape[1] % 16 == 0 and out_dtype in (torch.bfloat16, torch.float32):
+        a8 = a8 if a8.stride(1) == 1 and a8.stride(0) % 16 == 0 else a8.contiguous()
+        b8 = b8 if b8.stride(1) == 1 and b8.stride(0) % 16 == 0 else b8.contiguous()
+        return _ext.ops().gemm_fp8_block(a8, a_scale.contiguous(), b8, b_scale.contiguous(), bias, out_dtype == torch.float32)
+    M, K = a8.shape
+    N = b8.shape[0]
+    a = a8.float() * a_scale.repeat_interleave(128, 1)[:, :K]
+    b = b8.float() * b_scale.repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+    y = a @ b.t()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(out_dtype)
+
+
+def fp8_block_linear(x: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor, bias: torch.Tensor = None) -> torch.Tensor:
+    """Linear layer on block-quantised weights (``blockwise_cast_to_fp8(weight)``) with 1×128 dynamic activation scales."""
+    shp = x.shape
+    a8, a_s = act_cast_to_fp8(x.reshape(-1, shp[-1]))
+    return fp8_block_gemm(a8, a_s, w8, w_scale, bias, x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.bfloat16).reshape(*shp[:-1], w8.shape[0])
 
 
 class FP8Linear(torch.nn.Module):
