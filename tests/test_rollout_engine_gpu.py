@@ -42,21 +42,22 @@ def test_rollout_log_probs_match_a_training_forward_and_fp8_mode_stays_close():
     eng.sleep()
 
     # W8A8 rollout: same sampler seed, log-probs of ITS tokens re-scored by the bf16 model stay close
-    eng8 = InferenceEngine(model, max_num_seqs=8, max_model_len=256, num_blocks=64, sync_interval=4, quantization="fp8")
-    outs8 = eng8.generate(prompts, SamplingParams(temperature=1.0, max_tokens=24, seed=3))
-    assert len(eng8._w8) == 4 * model.cfg.num_hidden_layers
-    diffs = []
-    for p, o in zip(prompts, outs8):
-        ids = torch.tensor(p + o.token_ids, device="cuda")
-        pb = PackedBatch(ids, torch.arange(len(ids), dtype=torch.int32, device="cuda"), torch.tensor([0, len(ids)], dtype=torch.int32, device="cuda"))
-        with torch.no_grad():
-            lp = torch.log_softmax(model(pb, return_logits=True)["logits"].float(), -1)
-        want = lp[len(p) - 1: len(ids) - 1].gather(1, ids[len(p):, None])[:, 0]
-        diffs.append((want - torch.tensor(o.log_probs, device="cuda")).abs())
-    d = torch.cat(diffs)
-    assert d.mean() < 0.1 and d.max() < 1.0, (d.mean().item(), d.max().item())
-    eng8.sleep()
-    assert not eng8._w8
+    for quant in ("fp8", "fp8_block"):
+        eng8 = InferenceEngine(model, max_num_seqs=8, max_model_len=256, num_blocks=64, sync_interval=4, quantization=quant)
+        outs8 = eng8.generate(prompts, SamplingParams(temperature=1.0, max_tokens=24, seed=3))
+        assert len(eng8._w8) == 4 * model.cfg.num_hidden_layers
+        diffs = []
+        for p, o in zip(prompts, outs8):
+            ids = torch.tensor(p + o.token_ids, device="cuda")
+            pb = PackedBatch(ids, torch.arange(len(ids), dtype=torch.int32, device="cuda"), torch.tensor([0, len(ids)], dtype=torch.int32, device="cuda"))
+            with torch.no_grad():
+                lp = torch.log_softmax(model(pb, return_logits=True)["logits"].float(), -1)
+            want = lp[len(p) - 1: len(ids) - 1].gather(1, ids[len(p):, None])[:, 0]
+            diffs.append((want - torch.tensor(o.log_probs, device="cuda")).abs())
+        d = torch.cat(diffs)
+        assert d.mean() < 0.1 and d.max() < 1.0, (quant, d.mean().item(), d.max().item())
+        eng8.sleep()
+        assert not eng8._w8
     torch.cuda.synchronize()
     _ext.check_status("rollout engine test")
 

@@ -97,7 +97,8 @@ class InferenceEngine:
         # "fp8": W8A8 projections (per-output-channel e4m3 weights re-quantised from the live bf16 weights at every wake_up,
         # per-token e4m3 activations, tcgen05 f8f6f4 GEMM); embeddings, norms, lm_head and the KV cache stay bf16.
         # Reference: FP8 rollout, verl/utils/fp8_utils.py + verl/utils/kernel/fp8_kernel.py (weights quantised during sync).
-        assert quantization in (None, "", "fp8"), f"unsupported rollout quantization {quantization!r}"
+        # "fp8_block": the same with 128x128 weight blocks and 1x128 activation groups (the block-scaled GEMM)
+        assert quantization in (None, "", "fp8", "fp8_block"), f"unsupported rollout quantization {quantization!r}"
         self.quantization = quantization or None
         self._w8: dict = {}
         self.cfg = model.cfg
@@ -167,24 +168,26 @@ class InferenceEngine:
     def _quantise_weights(self):
         """(Re)build the e4m3 copies of the dense projection weights from the current bf16 weights."""
         self._w8 = {}
-        if self.quantization != "fp8" or not self.native or self.tp_group is not None:
+        if self.quantization not in ("fp8", "fp8_block") or not self.native or self.tp_group is not None:
             return
-        from verl_b200.ops.quant import rowwise_cast_to_fp8
+        from verl_b200.ops.quant import blockwise_cast_to_fp8, rowwise_cast_to_fp8
+
+        cast = rowwise_cast_to_fp8 if self.quantization == "fp8" else blockwise_cast_to_fp8
 
         for layer in self.model.layers:
             ws = [layer.self_attn.qkv_proj, layer.self_attn.o_proj]
             if not self.cfg.is_moe:
                 ws += [layer.mlp.gate_up_proj, layer.mlp.down_proj]
             for w in ws:
-                self._w8[id(w)] = rowwise_cast_to_fp8(w.detach())
+                self._w8[id(w)] = cast(w.detach())
 
     def _linear(self, x: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
         q = self._w8.get(id(w))
         if q is None:
             return ops.linear(x, w, bias)
-        from verl_b200.ops.quant import fp8_linear
+        from verl_b200.ops.quant import fp8_block_linear, fp8_linear
 
-        return fp8_linear(x, q[0], q[1], bias)
+        return (fp8_linear if self.quantization == "fp8" else fp8_block_linear)(x, q[0], q[1], bias)
 
     def _wake_up_impl(self):
         c = self.cfg
