@@ -70,3 +70,28 @@ def test_dapo_overlong_gdpo_components_and_rate_limit():
 
     res = asyncio.run(go())
     assert peak[0] <= 2 and res[0]["reward_extra_info"].get("timeout") and res[1]["reward_score"] == 1.0
+
+
+def test_prime_math_and_code_scorers():
+    from verl_b200.utils.reward_score import default_compute_score, prime_code, prime_math
+
+    assert prime_math.compute_score("Step 2: so \\boxed{\\frac{1}{2}}", "0.5")[:2] == (True, True)
+    assert prime_math.compute_score("The answer is 50%", "0.5")[0] and prime_math.compute_score("\\boxed{2\\pi}", "6.2832")[0]
+    assert prime_math.compute_score("\\boxed{(1, 2.0)}", "(1,2)")[0] and not prime_math.compute_score("\\boxed{(1, 3)}", "(1,2)")[0]
+    assert not prime_math.compute_score("\\boxed{7}", "8")[0]
+    assert default_compute_score("numina_cn_k12", "\\boxed{x=3}", "3") == 1.0
+
+    tests = {"inputs": ["1 2\n", "10 20\n", "5 5\n"], "outputs": ["3\n", "30\n", "10\n"]}
+    good = "Here:\n```python\na, b = map(int, input().split())\nprint(a + b)\n```"
+    half = "```python\na, b = map(int, input().split())\nprint(a + b if a < 10 else 0)\n```"
+    assert prime_code.compute_score(good, tests)[0] is True
+    score, recs = prime_code.compute_score(half, tests, continuous=True)
+    assert abs(score - 2 / 3) < 1e-9 and [r["passed"] for r in recs] == [True, False, True]
+    slow = "```python\nwhile True:\n    pass\n```"
+    ok, recs = prime_code.compute_score(slow, tests, timeout=1.0)
+    assert ok is False and recs[0]["status"] == "timeout"
+    boom = "```python\nraise SystemExit(3)\n```"
+    assert prime_code.compute_score(boom, tests)[1][0]["status"] == "error"
+    fn = {"fn_name": "add", "inputs": [[1, 2], [3, 4]], "outputs": [3, [7]]}
+    assert prime_code.compute_score("```python\ndef add(a, b):\n    return a + b\n```", fn)[0] is True
+    assert default_compute_score("apps", good, tests) == 1.0

@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from . import geo3k, gsm8k, math_dapo, math_reward, search_r1_like_qa_em, synthetic
+from . import geo3k, gsm8k, math_dapo, math_reward, prime_code, prime_math, search_r1_like_qa_em, synthetic
 
 __all__ = ["default_compute_score"]
 
@@ -14,6 +14,11 @@ def default_compute_score(data_source: str, solution_str: str, ground_truth, ext
         return math_reward.compute_score(solution_str, ground_truth)
     if data_source in ("math_dapo", "math", "math_dapo_reasoning") or str(data_source).startswith("aime"):
         return math_dapo.compute_score(solution_str, ground_truth)
+    if data_source in ("numina_aops_forum", "numina_synthetic_math", "numina_amc_aime", "numina_synthetic_amc", "numina_cn_k12", "numina_olympiads"):
+        return float(prime_math.compute_score(solution_str, ground_truth)[0])
+    if data_source in ("codecontests", "apps", "codeforces", "taco"):
+        # test cases run in a local subprocess sandbox (the reference posts them to a remote sandbox service when one is configured)
+        return float(prime_code.compute_score(solution_str, ground_truth, continuous=True)[0])
     if data_source in ("hiyouga/geometry3k", "geo3k"):
         return geo3k.compute_score(solution_str, ground_truth)
     if data_source in ("searchR1_nq", "searchR1_triviaqa", "searchR1_popqa", "searchR1_hotpotqa", "searchR1_2wikimultihopqa",
