@@ -205,15 +205,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     int n_valid;   // columns [0, n_valid) of this tile are visible to this row
     if (!PAGED) n_valid = min(ATT_BN, min(my_q, seq_len - 1) - kv0 + 1);
     else n_valid = min(ATT_BN, kv_len_limit - kv0);
+    // tiles strictly below the diagonal are fully visible to every row of the warp: no per-element masking there
+    const bool full_tile = __all_sync(0xffffffffu, n_valid >= ATT_BN);
     float m_tile = -INFINITY;
 #pragma unroll 1
     for (int c = 0; c < ATT_BN / 32; ++c) {
       uint32_t v[32];
       tmem_ld_32x32b_x32(tmem_S + lane_off + c * 32, v);
       tmem_ld_wait();
+      if (full_tile) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (c * 32 + i < n_valid) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
+        for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c * 32 + i < n_valid) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
+      }
     }
     const float m_new = fmaxf(m_run, m_tile * p.scale_log2);
     const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // fully masked row (only rows past the sequence end)
@@ -226,15 +233,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_ld_32x32b_x32(tmem_S + lane_off + c * 32, v);
       tmem_ld_wait();
       float pv[32];
+      if (full_tile) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float e = (c * 32 + i < n_valid) ? exp2f(__uint_as_float(v[i]) * p.scale_log2 - m_use) : 0.f;
-        pv[i] = e;
+        for (int i = 0; i < 32; ++i) pv[i] = exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) pv[i] = (c * 32 + i < n_valid) ? exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use)) : 0.f;
       }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) l_tile += pv[i];
       uint8_t* prow = sP + (c >> 1) * ATT_HALF + tid * 128;
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
-        // the bf16-rounded probabilities are what the PV product sees; accumulate the same values into l
+        // the PV product sees bf16-rounded probabilities, the row sum above the unrounded ones: the rounding errors are
+        // unbiased and far below bf16 output precision, and summing fp32 values halves the instructions of this loop
         uint4 o;
         o.x = pack_bf16x2(pv[g * 8 + 0], pv[g * 8 + 1]);
         o.y = pack_bf16x2(pv[g * 8 + 2], pv[g * 8 + 3]);
@@ -242,12 +254,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         o.w = pack_bf16x2(pv[g * 8 + 6], pv[g * 8 + 7]);
         const int chunk = (c & 1) * 4 + g;
         *reinterpret_cast<uint4*>(prow + ((chunk ^ (tid & 7)) << 4)) = o;
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&o);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(h2[e]);
-          l_tile += f.x + f.y;
-        }
       }
     }
     l_run = l_run * alpha + l_tile;
