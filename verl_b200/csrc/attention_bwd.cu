@@ -155,6 +155,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       dl = p.delta[si];
     }
     const int n_valid = row_ok ? min(128, my_q - t.kv_row0 + 1) : 0;   // causal: kv index <= q index
+    const bool full_tile = __all_sync(0xffffffffu, n_valid >= 128);
     if (!mbar_wait(s_bar, ph, abort_flag, p.err_word, VB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
     tc_fence_after();
 #pragma unroll 1
@@ -171,7 +172,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int col = c * 32 + g * 8 + e;
-          const float pe = (col < n_valid) ? exp2f(__uint_as_float(sv[g * 8 + e]) * p.scale_log2 - lse2) : 0.f;
+          // query tiles strictly below the diagonal see the whole kv tile: no per-element mask there
+          const float pe = (full_tile || col < n_valid) ? exp2f(fmaf(__uint_as_float(sv[g * 8 + e]), p.scale_log2, -lse2)) : 0.f;
           pf[e] = pe;
           df[e] = pe * (__uint_as_float(dv[g * 8 + e]) - dl) * p.scale;
         }
