@@ -1,0 +1,119 @@
+"""ZeRO-3 mode of the fsdp engine on gloo ranks: same log-probs, gradient norms, weights and merged checkpoint as one rank
+holding everything.
+
+Reference behaviour: FSDP FULL_SHARD (verl/workers/engine/fsdp/transformer_impl.py:389-498)."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from tests.test_engine_on_cpu import loss_fn, make_batch
+from verl_b200.models.config import PRESETS
+from verl_b200.workers.engine.base import EngineRegistry
+from verl_b200.workers.engine.fsdp.engine import FSDPEngine
+
+OPT = {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}
+
+WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+from tests.test_engine_on_cpu import make_batch, loss_fn
+from verl_b200.models.config import PRESETS
+from verl_b200.workers.engine.base import EngineRegistry
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+eng = EngineRegistry.new("language_model", "fsdp", model_config=PRESETS["tiny-qwen2"], engine_config={"seed": 1, "reshard_after_forward": True},
+                         optimizer_config={"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, checkpoint_config={"save_contents": ["model", "optimizer", "extra", "hf_model"]})
+eng.initialize()
+assert type(eng).__name__ == "Zero3Engine" and eng.get_data_parallel_size() == world
+cfg = eng.cfg
+qkv = dict(eng.model.named_parameters())["layers.0.self_attn.qkv_proj"]
+assert qkv.shape[0] * world == cfg.q_size + 2 * cfg.kv_size, qkv.shape
+data = make_batch().chunk(world)[rank]
+data.meta_info["micro_batch_size_per_gpu"] = 3
+lp = eng.infer_batch(data)["model_output"]["log_probs"]
+gns = []
+for _ in range(2):
+    eng.optimizer_zero_grad()
+    eng.forward_backward_batch(data, loss_fn)
+    gns.append(eng.optimizer_step())
+tensors = {k: v.detach().clone() for k, v in eng.get_per_tensor_param()[0]}
+eng.save_checkpoint(os.environ["OUT"] + ".ckpt", global_step=2)
+# a reload restores weights and optimizer state of the shards
+before = eng.store.flat.clone()
+eng.store.flat.zero_()
+eng.load_checkpoint(os.environ["OUT"] + ".ckpt")
+assert torch.equal(eng.store.flat, before)
+torch.save({"lp": lp, "gns": gns, "tensors": tensors}, os.environ["OUT"] + f".{rank}")
+dist.barrier()
+'''
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_zero3_ranks_match_single_rank(tmp_path, world):
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "w.py"
+    script.write_text(WORKER)
+    out = tmp_path / "out.pt"
+    env = dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                        "--master-port", str(29790 + world), str(script)], env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    eng = FSDPEngine(PRESETS["tiny-qwen2"], {"seed": 1}, OPT, {})
+    eng.initialize()
+    data = make_batch()
+    data.meta_info["micro_batch_size_per_gpu"] = 3
+    lp = eng.infer_batch(data)["model_output"]["log_probs"]
+    gns = []
+    for _ in range(2):
+        eng.optimizer_zero_grad()
+        eng.forward_backward_batch(data, loss_fn)
+        gns.append(eng.optimizer_step())
+    want = {k: v.detach().clone() for k, v in eng.get_per_tensor_param()[0]}
+    per = len(data) // world
+    for rk in range(world):
+        res = torch.load(str(out) + f".{rk}")
+        assert torch.allclose(res["lp"], lp[rk * per:(rk + 1) * per], atol=2e-5)
+        for a, b in zip(res["gns"], gns):
+            assert abs(a - b) < 1e-4 * max(1.0, b), (res["gns"], gns)
+        assert res["tensors"].keys() == want.keys()
+        for k in want:
+            assert res["tensors"][k].shape == want[k].shape, k
+            # AdamW normalises the step, so fp32 summation-order noise in a near-zero gradient moves a weight by up to ~lr
+            d = (res["tensors"][k] - want[k]).abs()
+            assert d.max() < 2.5e-3 and d.mean() < 2e-5, (k, float(d.max()), float(d.mean()))
+    # per-rank files merge back into the full weights; the collective HF export wrote the same tensors
+    from verl_b200.model_merger.base_model_merger import ModelMergerConfig
+    from verl_b200.model_merger.fsdp_model_merger import FSDPModelMerger
+
+    ckpt = str(out) + ".ckpt"
+    merger = FSDPModelMerger(ModelMergerConfig(operation="merge", backend="fsdp", local_dir=ckpt, target_dir=str(tmp_path / "hf"),
+                                               hf_model_config_path=os.path.join(ckpt, "huggingface")))
+    sd = merger._merge()
+    for k in want:
+        assert torch.allclose(sd[k].float(), want[k].float(), atol=1e-2, rtol=1e-2), k
+    from verl_b200.models.hf_io import iter_safetensors
+
+    hf = dict(iter_safetensors(os.path.join(ckpt, "huggingface")))
+    for k in want:
+        assert torch.allclose(hf[k].float(), want[k].float(), atol=1e-2, rtol=1e-2), k
+
+
+def test_zero3_single_rank_is_plain_engine():
+    eng = EngineRegistry.new("language_model", "fsdp", model_config=PRESETS["tiny-qwen2"], engine_config={"seed": 1, "zero3": True},
+                             optimizer_config=OPT, checkpoint_config={})
+    eng.initialize()
+    ref = FSDPEngine(PRESETS["tiny-qwen2"], {"seed": 1}, OPT, {})
+    ref.initialize()
+    data = make_batch()
+    for e in (eng, ref):
+        e.optimizer_zero_grad()
+        e.forward_backward_batch(data, loss_fn)
+    a, b = eng.optimizer_step(), ref.optimizer_step()
+    assert abs(a - b) < 1e-5 * max(1.0, b)
+    got, want = dict(eng.get_per_tensor_param()[0]), dict(ref.get_per_tensor_param()[0])
+    for k in want:
+        assert torch.allclose(got[k], want[k], atol=1e-6), k

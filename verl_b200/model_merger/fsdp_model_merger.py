@@ -36,6 +36,8 @@ class FSDPModelMerger(BaseModelMerger):
         first = self._load_rank(world, 0)
         if first.get("format") != "flat_v1":
             raise ValueError("unsupported shard format (expected flat_v1 written by verl_b200's fsdp engine)")
+        if first.get("zero3_rows"):
+            return self._merge_zero3(world, first)
         fsdp_size = int(first["fsdp_size"])
         with ThreadPoolExecutor(max_workers=min(32, os.cpu_count() or 1)) as ex:
             shards = [first] + list(ex.map(lambda r: self._load_rank(world, r), range(1, fsdp_size)))
@@ -48,6 +50,30 @@ class FSDPModelMerger(BaseModelMerger):
             for d in shape:
                 n *= d
             native[name] = flat[off : off + n].view(*shape)
+        from verl_b200.models.transformer import native_to_hf_tensors
+
+        return {k: v.to(torch.bfloat16).clone() for k, v in native_to_hf_tensors(self.model_config, native)}
+
+    def _merge_zero3(self, world: int, first: dict) -> dict[str, torch.Tensor]:
+        """ZeRO-3 checkpoints: every rank's file holds its row slice of the sharded projections plus a full copy of the
+        replicated tensors; sharded tensors are concatenated by rows in rank order, the rest is taken from rank 0."""
+        with ThreadPoolExecutor(max_workers=min(32, os.cpu_count() or 1)) as ex:
+            shards = [first] + list(ex.map(lambda r: self._load_rank(world, r), range(1, world)))
+        shards.sort(key=lambda s: s["rank"])
+
+        def tensor_of(sh, name):
+            i = sh["names"].index(name)
+            n = 1
+            for d in sh["shapes"][i]:
+                n *= d
+            return sh["flat_shard"][sh["offsets"][i]: sh["offsets"][i] + n].view(*sh["shapes"][i])
+
+        native = {}
+        for name in first["names"]:
+            if name in first["zero3_rows"]:
+                native[name] = torch.cat([tensor_of(sh, name) for sh in shards], 0)
+            else:
+                native[name] = tensor_of(first, name)
         from verl_b200.models.transformer import native_to_hf_tensors
 
         return {k: v.to(torch.bfloat16).clone() for k, v in native_to_hf_tensors(self.model_config, native)}

@@ -52,7 +52,12 @@ class PackedBatch:
 def _proj(mod: nn.Module, name: str, x: torch.Tensor, bias=None) -> torch.Tensor:
     """``x @ Wᵀ (+ bias)`` plus the low-rank update ``scale · (x Aᵀ) Bᵀ`` when the module carries a LoRA adapter for ``name``
     (see ``verl_b200.models.lora``)."""
-    y = ops.linear(x, getattr(mod, name), bias)
+    w = getattr(mod, name)
+    if getattr(w, "_zero3", None) is not None:      # row-sharded weight of the ZeRO-3 engine: gather fused into the GEMM
+        from verl_b200.workers.engine.fsdp.zero3 import zero3_linear
+
+        return zero3_linear(x, w, bias)
+    y = ops.linear(x, w, bias)
     adapters = getattr(mod, "_lora", None)
     if adapters and name in adapters:
         a, b, scale = adapters[name]

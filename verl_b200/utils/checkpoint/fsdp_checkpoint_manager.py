@@ -64,6 +64,7 @@ class FSDPCheckpointManager(BaseCheckpointManager):
             payload.append((model_f, {"format": "flat_v1", "names": s.names, "shapes": [tuple(p.shape) for p in s.params],
                                       "offsets": s.offsets, "total": s.total, "shard_size": s.shard_size,
                                       "fsdp_rank": e.fsdp_rank, "fsdp_size": e.fsdp_size, "dtype": str(s.flat.dtype),
+                                      "zero3_rows": dict(getattr(e, "_zero3_rows", None) or {}), "rank": e.rank, "world": e.world,
                                       "flat_shard": shard}))
         if self.should_save_optimizer and not e.forward_only:
             payload.append((optim_f, {"master": e.master.detach().to("cpu", copy=True), "exp_avg": e.exp_avg.detach().to("cpu", copy=True),
@@ -82,6 +83,7 @@ class FSDPCheckpointManager(BaseCheckpointManager):
             self._async_thread.start()
         else:
             write()
+        zero3 = bool(getattr(e, "_zero3_rows", None))
         if e.rank == 0:
             with open(os.path.join(local_path, "fsdp_config.json"), "w") as f:
                 json.dump({"FSDP_version": 2, "world_size": e.world, "format": "flat_v1"}, f, indent=2)
@@ -93,10 +95,20 @@ class FSDPCheckpointManager(BaseCheckpointManager):
                 for fn in os.listdir(tok_src):
                     if fn.startswith("tokenizer") or fn in ("vocab.json", "merges.txt", "special_tokens_map.json", "generation_config.json"):
                         shutil.copy(os.path.join(tok_src, fn), os.path.join(hf_dir, fn))
-            if self.should_save_hf_model:
+            if self.should_save_hf_model and not zero3:
                 from verl_b200.models.hf_io import save_hf_weights
 
                 save_hf_weights(e.model.hf_named_tensors(), hf_dir)
+        if self.should_save_hf_model and zero3:
+            # row-sharded weights: the export gathers them one by one, a collective that every rank walks through
+            it = e.hf_named_tensors_for_save()
+            if e.rank == 0:
+                from verl_b200.models.hf_io import save_hf_weights
+
+                save_hf_weights(it, os.path.join(local_path, "huggingface"))
+            else:
+                for _ in it:
+                    pass
         if dist.is_initialized():
             dist.barrier()
         if e.rank == 0:

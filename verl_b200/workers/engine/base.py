@@ -188,4 +188,13 @@ class EngineRegistry:
         elif not backend.startswith("fsdp"):
             import verl_b200.workers.engine.aliases  # noqa: F401 - third-party backend names of the reference
 
+        engine_config = kwargs.get("engine_config", args[1] if len(args) > 1 else None)
+        if backend in ("fsdp", "fsdp2") and model_type == "language_model" and engine_config is not None:
+            def opt(key):
+                return engine_config.get(key, False) if hasattr(engine_config, "get") else getattr(engine_config, key, False)
+
+            if opt("zero3") or opt("reshard_after_forward"):     # ZeRO-3: row-sharded weights gathered inside the GEMMs
+                import verl_b200.workers.engine.fsdp.zero3  # noqa: F401
+
+                backend = "fsdp_zero3"
         return cls.get_engine_cls(model_type, backend)(*args, **kwargs)

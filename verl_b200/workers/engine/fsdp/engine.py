@@ -74,10 +74,12 @@ class FlatParamStore:
 
     ALIGN = 128
 
-    def __init__(self, model: torch.nn.Module, world: int, rank: int):
+    def __init__(self, model: torch.nn.Module, world: int, rank: int, order_key=None):
         self.model = model
         self.world, self.rank = world, rank
         params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]   # frozen tensors (LoRA base) stay outside
+        if order_key is not None:
+            params.sort(key=order_key)                                              # stable: model order within equal keys
         self.names = [n for n, _ in params]
         self.params = [p for _, p in params]
         self.offsets, off = [], 0
@@ -216,24 +218,7 @@ class FSDPEngine(BaseEngine):
             apply_lora(self.model, lora_rank, float(cfg_get(self.model_config, "lora_alpha", 2 * lora_rank)),
                        cfg_get(self.model_config, "target_modules", "all-linear"), seed=seed)
         self._build_groups()
-        self.store = FlatParamStore(self.model, self.fsdp_size, self.fsdp_rank)
-        if self.world > 1:
-            # every rank must start from identical weights (rank 0's)
-            dist.broadcast(self.store.flat, src=0)
-        self._symm_params = self._symm_grads = None
-        use_symm = bool(cfg_get(self.engine_config, "use_symmetric_memory", True)) and os.environ.get("VERL_B200_COMM", "native") == "native"
-        if (use_symm and self.world > 1 and self.fsdp_size == self.world and self.store.flat.is_cuda and self.store.flat.dtype == torch.bfloat16
-                and _ext.available() and not self.forward_only and not self._param_offload):
-            from verl_b200.parallel.symm_mem import SymmetricBuffer
-            from verl_b200.single_controller.spmd import init_spmd_process_group
-
-            host = init_spmd_process_group()
-            s = self.store
-            self._symm_params = SymmetricBuffer(s.total * 2, host_group=host)
-            new_flat = self._symm_params.tensor(torch.bfloat16, s.total)
-            new_flat.copy_(s.flat)
-            s.rebind(new_flat)
-            self._symm_grads = SymmetricBuffer(s.total * 4, host_group=host)
+        self._place_parameters()
         if self.sp_size > 1:
             self.model.sp_group = self.sp_group
             from verl_b200.parallel.ulysses import FusedUlysses, fused_ulysses_available
@@ -258,6 +243,27 @@ class FSDPEngine(BaseEngine):
             self.to("cpu", model=True, optimizer=False, grad=False)
         if self._optimizer_offload and not self.forward_only:
             self.to("cpu", model=False, optimizer=True, grad=True)
+
+    def _place_parameters(self):
+        """Lay the parameters out in the flat store (replicated working copy; symmetric memory when the fused optimizer applies)."""
+        self.store = FlatParamStore(self.model, self.fsdp_size, self.fsdp_rank)
+        if self.world > 1:
+            # every rank must start from identical weights (rank 0's)
+            dist.broadcast(self.store.flat, src=0)
+        self._symm_params = self._symm_grads = None
+        use_symm = bool(cfg_get(self.engine_config, "use_symmetric_memory", True)) and os.environ.get("VERL_B200_COMM", "native") == "native"
+        if (use_symm and self.world > 1 and self.fsdp_size == self.world and self.store.flat.is_cuda and self.store.flat.dtype == torch.bfloat16
+                and _ext.available() and not self.forward_only and not self._param_offload):
+            from verl_b200.parallel.symm_mem import SymmetricBuffer
+            from verl_b200.single_controller.spmd import init_spmd_process_group
+
+            host = init_spmd_process_group()
+            s = self.store
+            self._symm_params = SymmetricBuffer(s.total * 2, host_group=host)
+            new_flat = self._symm_params.tensor(torch.bfloat16, s.total)
+            new_flat.copy_(s.flat)
+            s.rebind(new_flat)
+            self._symm_grads = SymmetricBuffer(s.total * 4, host_group=host)
 
     def _build_groups(self):
         """Mesh (ddp, fsdp) for parameter sharding and (dp, sp) for Ulysses; ranks are laid out fsdp/sp-fastest."""
@@ -678,6 +684,21 @@ class FSDPEngine(BaseEngine):
         if W > 1:
             dist.all_reduce(sumsq, group=self.fsdp_group)
         sumsq = self._sumsq_across_model_parallel(sumsq, gshard)
+        grad_norm = self._adamw_update(gshard, sumsq, native)
+        # 3. all-gather the updated working copy
+        if W > 1:
+            if s.flat.is_cuda:
+                dist.all_gather_into_tensor(s.flat, s.flat[s.shard_slice].clone(), group=self.fsdp_group)
+            else:
+                parts = [torch.empty(s.shard_size, dtype=s.flat.dtype) for _ in range(W)]
+                dist.all_gather(parts, s.flat[s.shard_slice].clone(), group=self.fsdp_group)
+                s.flat.copy_(torch.cat(parts))
+        s.zero_grads()
+        return grad_norm
+
+    def _adamw_update(self, gshard: torch.Tensor, sumsq: torch.Tensor, native: bool) -> float:
+        """Clip by the global norm ``sqrt(sumsq)`` and apply AdamW to this rank's slice (fp32 master → working copy)."""
+        s = self.store
         self.step_count += 1
         lr = self.current_lr()
         if native:
@@ -699,15 +720,6 @@ class FSDPEngine(BaseEngine):
         if skipped:
             self.step_count -= 1
             print(f"WARN: rank {self.rank} grad_norm is not finite: {grad_norm}; skipping optimizer step")
-        # 3. all-gather the updated working copy
-        if W > 1:
-            if s.flat.is_cuda:
-                dist.all_gather_into_tensor(s.flat, s.flat[s.shard_slice].clone(), group=self.fsdp_group)
-            else:
-                parts = [torch.empty(s.shard_size, dtype=s.flat.dtype) for _ in range(W)]
-                dist.all_gather(parts, s.flat[s.shard_slice].clone(), group=self.fsdp_group)
-                s.flat.copy_(torch.cat(parts))
-        s.zero_grads()
         return grad_norm
 
     def _sumsq_across_model_parallel(self, sumsq: torch.Tensor, gshard: torch.Tensor) -> torch.Tensor:
