@@ -75,17 +75,23 @@ def test_gae_with_critic_runs(tmp_path):
     assert "critic/vf_loss" in m and "critic/values/mean" in m and "actor/reward_kl_penalty" in m and "critic/grad_norm" in m
 
 
-def test_two_rank_gloo_fit(tmp_path):
+@pytest.mark.parametrize("zero3", [False, True])
+def test_two_rank_gloo_fit(tmp_path, zero3):
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     logf = tmp_path / "log.jsonl"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29671",
            "-m", "verl_b200.trainer.main_ppo"] + [o for o in OV if not o.startswith("trainer.logger")] + \
           ["trainer.logger=[file]", "trainer.total_training_steps=2", f"trainer.default_local_dir={tmp_path}/ckpt", "trainer.resume_mode=disable"]
+    if zero3:      # row-sharded projections in actor and reference; the rollout keeps its own gathered copy
+        cmd += ["actor_rollout_ref.actor.fsdp_config.reshard_after_forward=true", "+actor_rollout_ref.ref.fsdp_config.reshard_after_forward=true",
+                "trainer.save_freq=2"]
     env = dict(os.environ, VERL_FILE_LOGGER_PATH=str(logf), OMP_NUM_THREADS="2", PYTHONPATH=repo)
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900, cwd=repo)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     rows = [json.loads(x) for x in logf.read_text().splitlines()]
     assert len(rows) == 2 and rows[-1]["data"]["perf/total_num_tokens"] > 0 and abs(rows[0]["data"]["actor/ppo_kl"]) < 1e-4
+    if zero3:
+        assert os.path.exists(tmp_path / "ckpt" / "global_step_2" / "actor" / "model_world_size_2_rank_1.pt")
 
 
 def test_reward_model_worker_scores_the_last_response_token(tmp_path):

@@ -260,8 +260,8 @@ class ActorRolloutRefWorker(Worker):
         src = self.actor if self.actor is not None else self.ref
         model = src.engine.model
         self._rollout_owns_model = False
-        if getattr(src.engine, "tp_size", 1) * getattr(src.engine, "pp_size", 1) > 1:
-            # the trainer holds only a tensor/pipeline shard: the rollout replica keeps its own full copy, refreshed by
+        if getattr(src.engine, "tp_size", 1) * getattr(src.engine, "pp_size", 1) > 1 or getattr(src.engine, "_zero3_rows", None):
+            # the trainer holds only a tensor/pipeline shard (or ZeRO-3 row shards): the rollout replica keeps its own full copy, refreshed by
             # update_weights() from the engine's per-tensor export
             from verl_b200.models.transformer import DecoderLM
 
