@@ -95,3 +95,61 @@ def test_prime_math_and_code_scorers():
     fn = {"fn_name": "add", "inputs": [[1, 2], [3, 4]], "outputs": [3, [7]]}
     assert prime_code.compute_score("```python\ndef add(a, b):\n    return a + b\n```", fn)[0] is True
     assert default_compute_score("apps", good, tests) == 1.0
+
+
+def test_sandbox_fusion_client_against_a_local_service():
+    """The remote code scorer posts every test case to a sandbox service; here a stand-in service on 127.0.0.1 runs the posted
+    program with the local sandbox and answers in the service's JSON form. One request fails with 503 first (retried)."""
+    import json
+    import threading
+    from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+    from verl_b200.utils.reward_score import default_compute_score, sandbox_fusion
+    from verl_b200.utils.reward_score.prime_code import run_case
+
+    state = {"calls": 0, "failed_once": False}
+
+    class Handler(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_POST(self):
+            req = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            state["calls"] += 1
+            if not state["failed_once"]:
+                state["failed_once"] = True
+                self.send_response(503)
+                self.end_headers()
+                return
+            status, out = run_case(req["code"], req["stdin"], None, timeout=float(req["run_timeout"]))
+            body = {"status": "Success" if status == "ok" else "Failed",
+                    "run_result": {"status": "Finished" if status != "timeout" else "TimeLimitExceeded", "stdout": out if status == "ok" else "",
+                                   "stderr": "" if status == "ok" else out, "return_code": 0 if status == "ok" else 1}}
+            data = json.dumps(body).encode()
+            self.send_response(200)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
+
+    srv = ThreadingHTTPServer(("127.0.0.1", 0), Handler)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    url = f"http://127.0.0.1:{srv.server_address[1]}/run_code"
+    try:
+        tests = {"inputs": ["1 2\n", "5 7\n", "10 -3\n"], "outputs": ["3\n", "12\n", "7\n"]}
+        good = "```python\na, b = map(int, input().split())\nprint(a + b)\n```"
+        half = "```python\na, b = map(int, input().split())\nprint(a + b if a < 6 else 0)\n```"
+        score, recs = sandbox_fusion.compute_score(url, None, 512, good, tests)
+        assert score == 1.0 and all(r["passed"] for r in recs) and state["calls"] == 4          # one 503 was retried
+        score, _ = sandbox_fusion.compute_score(url, threading.Semaphore(2), 512, half, tests, continuous=True)
+        assert abs(score - 2 / 3) < 1e-6
+        fn_tests = {"fn_name": "add", "inputs": [[1, 2], [3, 4]], "outputs": [3, 7]}
+        assert sandbox_fusion.compute_score(url, None, 512, "def add(a, b):\n    return a + b\n", fn_tests)[0] == 1.0
+        assert sandbox_fusion.compute_score(url, None, 512, "def add(a, b):\n    return a - b\n", fn_tests)[0] == 0.0
+        # dispatch by data source with the service configured
+        assert default_compute_score("codecontests", good, json.dumps(tests), sandbox_fusion_url=url) == 1.0
+    finally:
+        srv.shutdown()
+    # an unreachable service scores 0 instead of raising
+    score, recs = sandbox_fusion.compute_score("http://127.0.0.1:9/run_code", None, 512, good, tests, timeout=0.5)
+    assert score == 0.0 and recs[0]["status"] == "sandbox_error"

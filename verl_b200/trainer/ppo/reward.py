@@ -50,7 +50,19 @@ def get_custom_reward_fn(config):
 def load_reward_manager(config, tokenizer, num_examine: int = 0, **reward_kwargs):
     name = _g(config, "reward.reward_manager") or _g(config, "reward_model.reward_manager") or "naive"
     cls = get_reward_manager_cls(name)
-    return cls(tokenizer=tokenizer, num_examine=num_examine, compute_score=get_custom_reward_fn(config),
+    compute_score = get_custom_reward_fn(config)
+    url = _g(config, "reward.sandbox_fusion.url")
+    if compute_score is None and url:
+        # code test cases go to the configured sandbox service; one semaphore bounds the requests of all scoring threads
+        # (reference: verl/trainer/ppo/reward.py, sandbox_fusion branch of load_reward_manager)
+        import threading
+
+        from verl_b200.utils.reward_score import default_compute_score
+
+        compute_score = partial(default_compute_score, sandbox_fusion_url=url,
+                                concurrent_semaphore=threading.Semaphore(int(_g(config, "reward.sandbox_fusion.max_concurrent", 64))),
+                                memory_limit_mb=int(_g(config, "reward.sandbox_fusion.memory_limit_mb", 1024)))
+    return cls(tokenizer=tokenizer, num_examine=num_examine, compute_score=compute_score,
                reward_fn_key=_g(config, "data.reward_fn_key", "data_source"), **reward_kwargs)
 
 

@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from . import geo3k, gsm8k, math_dapo, math_reward, prime_code, prime_math, search_r1_like_qa_em, synthetic
+from . import geo3k, gsm8k, math_dapo, math_reward, prime_code, prime_math, sandbox_fusion, search_r1_like_qa_em, synthetic
 
 __all__ = ["default_compute_score"]
 
@@ -17,7 +17,11 @@ def default_compute_score(data_source: str, solution_str: str, ground_truth, ext
     if data_source in ("numina_aops_forum", "numina_synthetic_math", "numina_amc_aime", "numina_synthetic_amc", "numina_cn_k12", "numina_olympiads"):
         return float(prime_math.compute_score(solution_str, ground_truth)[0])
     if data_source in ("codecontests", "apps", "codeforces", "taco"):
-        # test cases run in a local subprocess sandbox (the reference posts them to a remote sandbox service when one is configured)
+        url = kwargs.get("sandbox_fusion_url")
+        if url:        # a remote sandbox service is configured: post the test cases there
+            return float(sandbox_fusion.compute_score(url, kwargs.get("concurrent_semaphore"), int(kwargs.get("memory_limit_mb", 1024)),
+                                                      solution_str, ground_truth, continuous=True)[0])
+        # otherwise the test cases run in a local subprocess sandbox
         return float(prime_code.compute_score(solution_str, ground_truth, continuous=True)[0])
     if data_source in ("hiyouga/geometry3k", "geo3k"):
         return geo3k.compute_score(solution_str, ground_truth)
