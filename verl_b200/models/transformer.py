@@ -30,7 +30,7 @@ class PackedBatch:
     """Device-side description of a packed micro-batch."""
 
     __slots__ = ("input_ids", "position_ids", "cu_seqlens", "cu_seqlens_cpu", "max_seqlen", "routed_experts", "global_position_ids",
-                 "attn_expand")
+                 "attn_expand", "visual_embeds", "visual_token_ids", "rope_override")
 
     def __init__(self, input_ids, position_ids, cu_seqlens, cu_seqlens_cpu=None, max_seqlen=None, routed_experts=None):
         self.input_ids = input_ids
@@ -47,6 +47,9 @@ class PackedBatch:
         # once; cu_seqlens describe the E-row layout of full sequences that attention runs on (rows = x[expand]) and
         # back picks, for each of the T stored tokens, its row of that layout (see verl_b200.utils.prefix_sharing)
         self.attn_expand = None
+        # vision-language models (verl_b200.models.vision): rows that replace the embeddings of the image placeholder tokens,
+        # and per-token rotary tables (cos, sin) [T, D/2] of the multimodal rotary embedding
+        self.visual_embeds = self.visual_token_ids = self.rope_override = None
 
 
 def _proj(mod: nn.Module, name: str, x: torch.Tensor, bias=None) -> torch.Tensor:
@@ -262,6 +265,10 @@ class DecoderLM(nn.Module):
         """Final-normed hidden states [T, H] on the last pipeline stage, the raw residual stream on earlier stages.
         ``h_in`` is the stream received from the previous stage (stages without the embedding)."""
         cos, sin = self.rope(pb.input_ids.device)
+        if pb.rope_override is not None:
+            # multimodal rotary embedding: the tables already hold one row per token, so the rotary kernel indexes them by row
+            cos, sin = pb.rope_override
+            pb.position_ids = torch.arange(pb.input_ids.shape[0], dtype=torch.int32, device=pb.input_ids.device)
         sp = getattr(self, "tp_sp", False)
         if self.pre_process:
             if self.tp_group is not None and sp:
@@ -271,6 +278,9 @@ class DecoderLM(nn.Module):
                 h = vocab_parallel_embedding(pb.input_ids, self.embed_tokens, self.vocab_offset, self.tp_group)
             else:
                 h = ops.embedding(pb.input_ids, self.embed_tokens)
+            if pb.visual_embeds is not None:
+                is_vis = torch.isin(pb.input_ids, torch.tensor(pb.visual_token_ids, device=pb.input_ids.device))
+                h = h.index_put((is_vis.nonzero(as_tuple=True)[0],), pb.visual_embeds.to(h.dtype))
         else:
             h = h_in
         residual = None

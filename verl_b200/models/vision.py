@@ -1,0 +1,264 @@
+"""Vision-language family (Qwen2-VL architecture): a ViT tower whose merged patch embeddings replace the image placeholder
+tokens of a decoder LM that runs multimodal rotary embedding (M-RoPE: temporal / height / width position streams).
+
+* :class:`VisionTower` — patch embedding (the 3-D convolution over ``[C, T_p, P, P]`` written as one linear layer), pre-norm
+  blocks with bidirectional attention inside each frame and 2-D rotary embedding, 2×2 patch merger into the LM width.
+  Parameter names follow the Hugging Face checkpoint below ``visual.`` so the name mapping is a prefix.
+* :func:`get_rope_index` — the 3-stream position ids of a token sequence with image blocks.
+* :func:`mrope_tables` — per-token cos/sin ``[T, D/2]`` built from the three streams; the decoder's rotary kernel is reused by
+  passing these as its tables with ``position = arange(T)``.
+* :class:`VisionLanguageModel` — tower + :class:`~verl_b200.models.transformer.DecoderLM` on packed batches.
+
+Reference: the Qwen2-VL patches of the reference (``verl/models/transformers/qwen2_vl.py:36-250``: rope index, Ulysses-aware
+attention, embedding merge) and ``verl/utils/dataset/vision_utils.py`` for the inputs. Qwen2.5-VL's window attention and
+video inputs with more than one temporal patch per frame pair are not implemented.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import json
+import os
+from typing import Iterator, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from verl_b200.models.config import ModelConfig
+from verl_b200.models.transformer import DecoderLM, PackedBatch
+
+__all__ = ["VisionConfig", "VisionTower", "VisionLanguageModel", "get_rope_index", "mrope_tables"]
+
+
+@dataclasses.dataclass(frozen=True)
+class VisionConfig:
+    depth: int = 32
+    embed_dim: int = 1280
+    num_heads: int = 16
+    mlp_ratio: float = 4.0
+    in_channels: int = 3
+    patch_size: int = 14
+    temporal_patch_size: int = 2
+    spatial_merge_size: int = 2
+    hidden_size: int = 3584                 # width of the language model (output of the merger)
+    image_token_id: int = 151655
+    video_token_id: int = 151656
+    vision_start_token_id: int = 151652
+    mrope_section: tuple = (16, 24, 24)
+
+    @property
+    def patch_dim(self) -> int:
+        return self.in_channels * self.temporal_patch_size * self.patch_size * self.patch_size
+
+    @classmethod
+    def from_hf_dict(cls, d: dict, text: Optional[dict] = None) -> "VisionConfig":
+        v = d.get("vision_config", {})
+        rope = (text or d).get("rope_scaling") or (text or d).get("rope_parameters") or {}
+        return cls(depth=v.get("depth", 32), embed_dim=v.get("embed_dim", 1280), num_heads=v.get("num_heads", 16), mlp_ratio=v.get("mlp_ratio", 4.0),
+                   in_channels=v.get("in_channels", v.get("in_chans", 3)), patch_size=v.get("patch_size", 14),
+                   temporal_patch_size=v.get("temporal_patch_size", 2), spatial_merge_size=v.get("spatial_merge_size", 2),
+                   hidden_size=v.get("hidden_size", (text or d).get("hidden_size", 3584)), image_token_id=d.get("image_token_id", 151655),
+                   video_token_id=d.get("video_token_id", 151656), vision_start_token_id=d.get("vision_start_token_id", 151652),
+                   mrope_section=tuple(rope.get("mrope_section", (16, 24, 24))))
+
+
+def _rotate_half(x):
+    x1, x2 = x.chunk(2, dim=-1)
+    return torch.cat([-x2, x1], dim=-1)
+
+
+class _VisionBlock(nn.Module):
+    def __init__(self, cfg: VisionConfig, dtype, device):
+        super().__init__()
+        E, Hm = cfg.embed_dim, int(cfg.embed_dim * cfg.mlp_ratio)
+        kw = dict(dtype=dtype, device=device)
+        self.norm1, self.norm2 = nn.LayerNorm(E, eps=1e-6, **kw), nn.LayerNorm(E, eps=1e-6, **kw)
+        self.attn = nn.Module()
+        self.attn.qkv, self.attn.proj = nn.Linear(E, 3 * E, **kw), nn.Linear(E, E, **kw)
+        self.mlp = nn.Module()
+        self.mlp.fc1, self.mlp.fc2 = nn.Linear(E, Hm, **kw), nn.Linear(Hm, E, **kw)
+        self.num_heads = cfg.num_heads
+
+    def forward(self, x, cos, sin, seg_lens):
+        N, E = x.shape
+        H = self.num_heads
+        q, k, v = self.attn.qkv(self.norm1(x)).reshape(N, 3, H, E // H).unbind(1)
+        q = (q.float() * cos + _rotate_half(q.float()) * sin).to(x.dtype)
+        k = (k.float() * cos + _rotate_half(k.float()) * sin).to(x.dtype)
+        outs, s = [], 0
+        for n in seg_lens:                  # bidirectional attention inside each frame, none across frames
+            qs, ks, vs = (t[s:s + n].transpose(0, 1).unsqueeze(0) for t in (q, k, v))
+            outs.append(F.scaled_dot_product_attention(qs, ks, vs).squeeze(0).transpose(0, 1).reshape(n, E))
+            s += n
+        x = x + self.attn.proj(torch.cat(outs, 0))
+        h = self.mlp.fc1(self.norm2(x))
+        return x + self.mlp.fc2(h * torch.sigmoid(1.702 * h))       # QuickGELU
+
+
+class VisionTower(nn.Module):
+    def __init__(self, cfg: VisionConfig, dtype=torch.bfloat16, device=None, seed: int = 0):
+        super().__init__()
+        self.cfg = cfg
+        kw = dict(dtype=dtype, device=device)
+        E, m2 = cfg.embed_dim, cfg.spatial_merge_size ** 2
+        self.patch_embed = nn.Module()
+        self.patch_embed.proj = nn.Linear(cfg.patch_dim, E, bias=False, **kw)
+        self.blocks = nn.ModuleList([_VisionBlock(cfg, dtype, device) for _ in range(cfg.depth)])
+        self.merger = nn.Module()
+        self.merger.ln_q = nn.LayerNorm(E, eps=1e-6, **kw)
+        self.merger.mlp = nn.Sequential(nn.Linear(E * m2, E * m2, **kw), nn.GELU(), nn.Linear(E * m2, cfg.hidden_size, **kw))
+        g = torch.Generator(device="cpu").manual_seed(seed + 7919)
+        with torch.no_grad():
+            for p in self.parameters():
+                if p.dim() >= 2:
+                    p.copy_((torch.randn(p.shape, generator=g) * 0.02).to(p.dtype))
+
+    def _rot_pos(self, grid_thw: torch.Tensor) -> torch.Tensor:
+        """(h, w) index of every patch in the processor's order: patches of one merge window are adjacent."""
+        m = self.cfg.spatial_merge_size
+        out = []
+        for t, h, w in grid_thw.tolist():
+            hp = torch.arange(h).unsqueeze(1).expand(h, w).reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).flatten()
+            wp = torch.arange(w).unsqueeze(0).expand(h, w).reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).flatten()
+            out.append(torch.stack([hp, wp], -1).repeat(t, 1))
+        return torch.cat(out, 0)
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+        """``pixel_values`` [N, C·T_p·P·P] flattened patches, ``grid_thw`` [n_images, 3] → [N / merge², hidden_size]."""
+        cfg = self.cfg
+        x = self.patch_embed.proj(pixel_values.to(self.patch_embed.proj.weight.dtype))
+        D = cfg.embed_dim // cfg.num_heads
+        pos = self._rot_pos(grid_thw.cpu()).to(x.device)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, D // 2, 2, dtype=torch.float32, device=x.device) / (D // 2)))
+        ang = (pos[:, :, None].float() * inv[None, None, :]).flatten(1)              # [N, D/2]: (h freqs, w freqs)
+        emb = torch.cat([ang, ang], -1)
+        cos, sin = emb.cos()[:, None, :], emb.sin()[:, None, :]
+        seg = [int(h * w) for t, h, w in grid_thw.tolist() for _ in range(int(t))]
+        for blk in self.blocks:
+            x = blk(x, cos, sin, seg)
+        m2 = cfg.spatial_merge_size ** 2
+        return self.merger.mlp(self.merger.ln_q(x).reshape(-1, cfg.embed_dim * m2))
+
+
+def get_rope_index(input_ids: torch.Tensor, image_grid_thw: Optional[torch.Tensor], cfg: VisionConfig,
+                   attention_mask: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, int]:
+    """3-stream positions ``[3, L]`` of ONE sequence and the offset ``delta`` such that generated token ``j`` (0-based index
+    in the unpadded sequence) sits at position ``j + delta`` in all three streams.
+
+    Text tokens advance all streams together. An image block of ``t × h × w`` patches (``h, w`` in merged units) keeps the
+    temporal stream at the block start and walks the height / width streams over the grid; the text after it continues
+    from the largest position used so far + 1. Masked (padding) positions get 0."""
+    ids = input_ids if attention_mask is None else input_ids[attention_mask.bool()]
+    L = ids.numel()
+    m = cfg.spatial_merge_size
+    pos = torch.zeros(3, L, dtype=torch.long)
+    ids_l = ids.tolist()
+    grids = image_grid_thw.tolist() if image_grid_thw is not None else []
+    i, nxt, g = 0, 0, 0
+    while i < L:
+        if ids_l[i] in (cfg.image_token_id, cfg.video_token_id) and g < len(grids):
+            t, h, w = grids[g]
+            g += 1
+            gh, gw = h // m, w // m
+            n = t * gh * gw
+            assert ids_l[i:i + n] == [ids_l[i]] * n, "image placeholder run does not match image_grid_thw"
+            tt = torch.arange(t).view(t, 1, 1).expand(t, gh, gw).flatten()
+            hh = torch.arange(gh).view(1, gh, 1).expand(t, gh, gw).flatten()
+            ww = torch.arange(gw).view(1, 1, gw).expand(t, gh, gw).flatten()
+            pos[:, i:i + n] = torch.stack([tt, hh, ww]) + nxt
+            nxt += max(t, gh, gw)
+            i += n
+        else:
+            pos[:, i] = nxt
+            nxt += 1
+            i += 1
+    delta = nxt - L
+    if attention_mask is None:
+        return pos, delta
+    full = torch.zeros(3, input_ids.numel(), dtype=torch.long)
+    full[:, attention_mask.bool()] = pos
+    return full, delta
+
+
+def mrope_tables(pos3: torch.Tensor, head_dim: int, theta: float, mrope_section) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-token fp32 cos/sin ``[T, head_dim/2]``: frequency ``i`` reads the temporal, height or width stream according
+    to ``mrope_section`` (their sizes add up to ``head_dim/2``)."""
+    half = head_dim // 2
+    assert sum(mrope_section) == half, (mrope_section, head_dim)
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=pos3.device) / head_dim))
+    comp = torch.repeat_interleave(torch.arange(3, device=pos3.device), torch.tensor(list(mrope_section), device=pos3.device))
+    p = pos3.float().index_select(0, comp)                    # [half, T]: the stream each frequency follows
+    ang = (p * inv[:, None]).t().contiguous()
+    return ang.cos().contiguous(), ang.sin().contiguous()
+
+
+class VisionLanguageModel(nn.Module):
+    """``visual`` tower + ``language_model`` decoder. :meth:`forward` takes the decoder's packed batch plus the flattened
+    patches of all images of the micro-batch (in token order) and the 3-stream positions of its tokens."""
+
+    def __init__(self, cfg: ModelConfig, vcfg: VisionConfig, dtype=torch.bfloat16, device=None, init: bool = True, seed: int = 0):
+        super().__init__()
+        self.cfg, self.vcfg = cfg, vcfg
+        self.language_model = DecoderLM(cfg, dtype=dtype, device=device, init=init, seed=seed)
+        self.visual = VisionTower(vcfg, dtype=dtype, device=device, seed=seed)
+
+    @property
+    def gradient_checkpointing(self):
+        return self.language_model.gradient_checkpointing
+
+    @gradient_checkpointing.setter
+    def gradient_checkpointing(self, v):
+        self.language_model.gradient_checkpointing = v
+
+    def embed(self, pb: PackedBatch, pixel_values: Optional[torch.Tensor], image_grid_thw: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """Rows for the image placeholder tokens of ``pb`` (``None`` for a text-only batch)."""
+        if pixel_values is None or pixel_values.numel() == 0:
+            return None
+        vis = self.visual(pixel_values, image_grid_thw)
+        n_tok = int(((pb.input_ids == self.vcfg.image_token_id) | (pb.input_ids == self.vcfg.video_token_id)).sum())
+        assert vis.shape[0] == n_tok, f"{n_tok} image placeholder tokens but {vis.shape[0]} merged patch embeddings"
+        return vis
+
+    def forward(self, pb: PackedBatch, pixel_values=None, image_grid_thw=None, mrope_positions: Optional[torch.Tensor] = None, **kw):
+        pb.visual_embeds = self.embed(pb, pixel_values, image_grid_thw)
+        pb.visual_token_ids = (self.vcfg.image_token_id, self.vcfg.video_token_id)
+        if mrope_positions is not None:
+            pb.rope_override = mrope_tables(mrope_positions.to(pb.input_ids.device), self.cfg.head_dim, self.cfg.rope_theta, self.vcfg.mrope_section)
+        return self.language_model(pb, **kw)
+
+    # ------------------------------------------------------------------ Hugging Face names
+    def hf_named_tensors(self) -> Iterator[tuple[str, torch.Tensor]]:
+        yield from self.language_model.hf_named_tensors()
+        P = self.vcfg
+        for n, p in self.visual.named_parameters():
+            if n == "patch_embed.proj.weight":
+                p = p.view(P.embed_dim, P.in_channels, P.temporal_patch_size, P.patch_size, P.patch_size)
+            yield "visual." + n, p
+
+    def load_hf_state_dict(self, sd: dict, strict: bool = True):
+        sd = {(k[len("model."):] if k.startswith("model.visual.") else k): v for k, v in sd.items()}      # both checkpoint generations
+        vis = {k[len("visual."):]: v for k, v in sd.items() if k.startswith("visual.")}
+        own = dict(self.visual.named_parameters())
+        missing = [k for k in own if k not in vis]
+        if strict and missing:
+            raise KeyError(f"missing vision tensors {missing[:5]} ...")
+        with torch.no_grad():
+            for k, v in vis.items():
+                if k in own:
+                    own[k].copy_(v.reshape(own[k].shape).to(own[k].dtype))
+        lm = {k.replace("model.language_model.", "model."): v for k, v in sd.items() if not k.startswith("visual.")}
+        self.language_model.load_hf_state_dict(lm, strict=strict)
+
+    def save_pretrained_config(self, path: str):
+        os.makedirs(path, exist_ok=True)
+        self.cfg.save_pretrained(path)
+        fn = os.path.join(path, "config.json")
+        with open(fn) as f:
+            d = json.load(f)
+        v = dataclasses.asdict(self.vcfg)
+        d.update({"model_type": "qwen2_vl", "image_token_id": v.pop("image_token_id"), "video_token_id": v.pop("video_token_id"),
+                  "vision_start_token_id": v.pop("vision_start_token_id"), "rope_scaling": {"type": "mrope", "mrope_section": list(v.pop("mrope_section"))},
+                  "vision_config": v})
+        with open(fn, "w") as f:
+            json.dump(d, f, indent=2)
