@@ -86,3 +86,92 @@ def test_mrope_tables_reduce_to_plain_rope_for_text():
     cos, sin = mrope_tables(pos[None].expand(3, -1), 16, 10000.0, (2, 3, 3))
     inv = 1.0 / (10000.0 ** (torch.arange(0, 16, 2).float() / 16))
     assert torch.allclose(cos, (pos[:, None].float() * inv).cos()) and torch.allclose(sin, (pos[:, None].float() * inv).sin())
+
+
+def _vl_config():
+    return ModelConfig(model_type="qwen2", vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=16, rope_theta=10000.0, max_position_embeddings=512, attention_bias=True, torch_dtype="float32",
+                       vision=dict(depth=2, embed_dim=32, num_heads=2, mlp_ratio=2.0, in_channels=3, patch_size=4, temporal_patch_size=2,
+                                   spatial_merge_size=2, hidden_size=64, image_token_id=500, video_token_id=501, vision_start_token_id=502,
+                                   mrope_section=[2, 3, 3]))
+
+
+def test_config_round_trips_through_the_hf_layout(tmp_path):
+    cfg = _vl_config()
+    cfg.save_pretrained(str(tmp_path))
+    back = ModelConfig.from_pretrained(str(tmp_path))
+    assert back.vision == cfg.vision and back.hidden_size == 64 and back.model_type == "qwen2"
+    import json
+
+    d = json.loads((tmp_path / "config.json").read_text())
+    assert d["model_type"] == "qwen2_vl" and d["vision_config"]["embed_dim"] == 32 and d["rope_scaling"]["mrope_section"] == [2, 3, 3]
+    # the nested text_config layout of newer checkpoints parses to the same thing
+    text_keys = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads", "rope_theta",
+                 "max_position_embeddings", "rms_norm_eps", "rope_scaling", "head_dim")
+    nested = {k: v for k, v in d.items() if k not in text_keys}
+    nested["text_config"] = {k: d[k] for k in text_keys}
+    assert ModelConfig.from_hf_dict(nested).vision == cfg.vision
+
+
+def test_engine_trains_a_vision_language_model_on_image_prompts():
+    """The sharded-DP engine with a vision-language config: log-probs of a batch whose prompts hold images equal a direct
+    forward of the model per sequence, the vision tower receives gradients, and an optimizer step changes it."""
+    import numpy as np
+
+    from verl_b200.protocol import DataProto
+    from verl_b200.workers.engine.fsdp.engine import FSDPEngine
+
+    eng = FSDPEngine(_vl_config(), {"seed": 3, "model_dtype": "float32"}, {"lr": 1e-3, "clip_grad": 1.0}, {})
+    eng.initialize()
+    assert type(eng.model).__name__ == "VisionLanguageModel"
+    g = torch.Generator().manual_seed(5)
+    P, R, bs = 16, 6, 3
+    rows, mm = [], []
+    for i, grid in enumerate([[[1, 4, 4]], [], [[1, 2, 2], [1, 2, 4]]]):
+        ids = []
+        for t, h, w in grid:
+            ids += [502] + [500] * (t * h * w // 4) + [503]
+        ids += torch.randint(1, 400, (4,), generator=g).tolist()
+        rows.append(ids)
+        n_patch = sum(t * h * w for t, h, w in grid)
+        mm.append({"pixel_values": torch.randn(n_patch, 96, generator=g), "image_grid_thw": torch.tensor(grid).reshape(-1, 3)} if grid else {})
+    input_ids = torch.zeros(bs, P + R, dtype=torch.long)
+    att = torch.zeros(bs, P + R, dtype=torch.long)
+    for i, ids in enumerate(rows):
+        resp = torch.randint(1, 400, (R - i,), generator=g).tolist()
+        input_ids[i, P - len(ids):P] = torch.tensor(ids)
+        att[i, P - len(ids):P] = 1
+        input_ids[i, P:P + len(resp)] = torch.tensor(resp)
+        att[i, P:P + len(resp)] = 1
+    pos = torch.clip(torch.cumsum(att, -1) - 1, min=0)
+    data = DataProto.from_dict(tensors={"input_ids": input_ids, "attention_mask": att, "position_ids": pos, "responses": input_ids[:, P:],
+                                        "response_mask": att[:, P:], "advantages": torch.randn(bs, R, generator=g),
+                                        "old_log_probs": torch.zeros(bs, R), "ref_log_prob": torch.zeros(bs, R)},
+                               non_tensors={"multi_modal_inputs": np.array(mm, dtype=object)},
+                               meta_info={"micro_batch_size_per_gpu": 2, "temperature": 1.0})
+    lp = eng.infer_batch(data)["model_output"]["log_probs"]
+    from verl_b200.models.vision import VisionConfig
+
+    v = dict(eng.cfg.vision)
+    vcfg = VisionConfig(**{**v, "mrope_section": tuple(v["mrope_section"])})
+    for i in range(bs):
+        ids = input_ids[i][att[i].bool()]
+        grid = mm[i].get("image_grid_thw")
+        pos3, _ = get_rope_index(ids, grid, vcfg)
+        pb = PackedBatch(ids, torch.arange(len(ids), dtype=torch.int32), torch.tensor([0, len(ids)], dtype=torch.int32))
+        with torch.no_grad():
+            logits = eng.model(pb, pixel_values=mm[i].get("pixel_values"), image_grid_thw=grid, mrope_positions=pos3, return_logits=True)["logits"]
+        ref = torch.log_softmax(logits.float(), -1)
+        n_prompt = int(att[i, :P].sum())
+        for t in range(int(att[i, P:].sum())):
+            assert abs(lp[i, t] - ref[n_prompt - 1 + t, ids[n_prompt + t]]) < 1e-4
+    from tests.test_engine_on_cpu import loss_fn
+
+    before = eng.model.visual.merger.mlp[2].weight.detach().clone()
+    eng.optimizer_zero_grad()
+    eng.forward_backward_batch(data, loss_fn)
+    assert eng.model.visual.patch_embed.proj.weight.main_grad.abs().sum() > 0
+    gn = eng.optimizer_step()
+    assert gn > 0 and not torch.equal(before, eng.model.visual.merger.mlp[2].weight)
+    names = [k for k, _ in eng.get_per_tensor_param()[0]]
+    assert "visual.patch_embed.proj.weight" in names and "model.layers.0.self_attn.q_proj.weight" in names

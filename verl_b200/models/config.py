@@ -40,6 +40,7 @@ class ModelConfig:
     router_aux_loss_coef: float = 0.0
     # heads
     value_head: bool = False             # scalar value head instead of lm_head (critic / reward model)
+    vision: Optional[dict] = None        # vision-language models: fields of verl_b200.models.vision.VisionConfig
     pad_token_id: Optional[int] = 0
     eos_token_id: Optional[int] = None
     bos_token_id: Optional[int] = None
@@ -84,6 +85,18 @@ class ModelConfig:
     @classmethod
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
         mt = d.get("model_type", "llama")
+        vision = None
+        if mt in ("qwen2_vl",):
+            # vision-language checkpoint: decoder fields sit in text_config (newer layout) or at the top level (older one)
+            import dataclasses as _dc
+
+            from verl_b200.models.vision import VisionConfig
+
+            text = d.get("text_config") or {}
+            vision = _dc.asdict(VisionConfig.from_hf_dict(d, text or None))
+            vision["mrope_section"] = list(vision["mrope_section"])
+            d = {**{k: v for k, v in d.items() if k not in ("text_config", "vision_config")}, **text, "attention_bias": True}
+            mt = "qwen2"
         known = dict(
             model_type=mt,
             vocab_size=d["vocab_size"],
@@ -109,6 +122,7 @@ class ModelConfig:
             eos_token_id=d.get("eos_token_id") if not isinstance(d.get("eos_token_id"), list) else d["eos_token_id"][0],
             bos_token_id=d.get("bos_token_id"),
             torch_dtype=str(d.get("torch_dtype", d.get("dtype", "bfloat16"))),
+            vision=vision,
         )
         return cls(**known)
 
@@ -140,6 +154,11 @@ class ModelConfig:
                      router_aux_loss_coef=self.router_aux_loss_coef)
         if self.value_head:
             d["num_labels"] = 1
+        if self.vision:
+            v = dict(self.vision)
+            d.update(model_type="qwen2_vl", architectures=["Qwen2VLForConditionalGeneration"], image_token_id=v.pop("image_token_id"),
+                     video_token_id=v.pop("video_token_id"), vision_start_token_id=v.pop("vision_start_token_id"),
+                     rope_scaling={"type": "mrope", "mrope_section": list(v.pop("mrope_section"))}, vision_config=v)
         return d
 
     def save_pretrained(self, path: str):

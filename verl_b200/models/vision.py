@@ -17,8 +17,6 @@ video inputs with more than one temporal patch per frame pair are not implemente
 from __future__ import annotations
 
 import dataclasses
-import json
-import os
 from typing import Iterator, Optional
 
 import torch
@@ -197,8 +195,11 @@ class VisionLanguageModel(nn.Module):
     """``visual`` tower + ``language_model`` decoder. :meth:`forward` takes the decoder's packed batch plus the flattened
     patches of all images of the micro-batch (in token order) and the 3-stream positions of its tokens."""
 
-    def __init__(self, cfg: ModelConfig, vcfg: VisionConfig, dtype=torch.bfloat16, device=None, init: bool = True, seed: int = 0):
+    def __init__(self, cfg: ModelConfig, vcfg: Optional[VisionConfig] = None, dtype=torch.bfloat16, device=None, init: bool = True, seed: int = 0):
         super().__init__()
+        if vcfg is None:
+            v = dict(cfg.vision)
+            vcfg = VisionConfig(**{**v, "mrope_section": tuple(v["mrope_section"])})
         self.cfg, self.vcfg = cfg, vcfg
         self.language_model = DecoderLM(cfg, dtype=dtype, device=device, init=init, seed=seed)
         self.visual = VisionTower(vcfg, dtype=dtype, device=device, seed=seed)
@@ -211,6 +212,32 @@ class VisionLanguageModel(nn.Module):
     def gradient_checkpointing(self, v):
         self.language_model.gradient_checkpointing = v
 
+    # the engine drives a decoder through these members; they resolve to the language model
+    @property
+    def output_weight(self):
+        return self.language_model.output_weight
+
+    @property
+    def layers(self):
+        return self.language_model.layers
+
+    @property
+    def embed_tokens(self):
+        return self.language_model.embed_tokens
+
+    def _prepare(self, pb: PackedBatch) -> PackedBatch:
+        mm = pb.mm
+        if mm:
+            pb.visual_embeds = self.embed(pb, mm.get("pixel_values"), mm.get("image_grid_thw"))
+            pb.visual_token_ids = (self.vcfg.image_token_id, self.vcfg.video_token_id)
+            if mm.get("mrope_positions") is not None:
+                pb.rope_override = mrope_tables(mm["mrope_positions"].to(pb.input_ids.device), self.cfg.head_dim, self.cfg.rope_theta,
+                                                self.vcfg.mrope_section)
+        return pb
+
+    def forward_hidden(self, pb: PackedBatch, h_in=None):
+        return self.language_model.forward_hidden(self._prepare(pb), h_in)
+
     def embed(self, pb: PackedBatch, pixel_values: Optional[torch.Tensor], image_grid_thw: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Rows for the image placeholder tokens of ``pb`` (``None`` for a text-only batch)."""
         if pixel_values is None or pixel_values.numel() == 0:
@@ -221,11 +248,9 @@ class VisionLanguageModel(nn.Module):
         return vis
 
     def forward(self, pb: PackedBatch, pixel_values=None, image_grid_thw=None, mrope_positions: Optional[torch.Tensor] = None, **kw):
-        pb.visual_embeds = self.embed(pb, pixel_values, image_grid_thw)
-        pb.visual_token_ids = (self.vcfg.image_token_id, self.vcfg.video_token_id)
-        if mrope_positions is not None:
-            pb.rope_override = mrope_tables(mrope_positions.to(pb.input_ids.device), self.cfg.head_dim, self.cfg.rope_theta, self.vcfg.mrope_section)
-        return self.language_model(pb, **kw)
+        if pixel_values is not None or mrope_positions is not None:
+            pb.mm = {"pixel_values": pixel_values, "image_grid_thw": image_grid_thw, "mrope_positions": mrope_positions}
+        return self.language_model(self._prepare(pb), **kw)
 
     # ------------------------------------------------------------------ Hugging Face names
     def hf_named_tensors(self) -> Iterator[tuple[str, torch.Tensor]]:
@@ -249,16 +274,3 @@ class VisionLanguageModel(nn.Module):
                     own[k].copy_(v.reshape(own[k].shape).to(own[k].dtype))
         lm = {k.replace("model.language_model.", "model."): v for k, v in sd.items() if not k.startswith("visual.")}
         self.language_model.load_hf_state_dict(lm, strict=strict)
-
-    def save_pretrained_config(self, path: str):
-        os.makedirs(path, exist_ok=True)
-        self.cfg.save_pretrained(path)
-        fn = os.path.join(path, "config.json")
-        with open(fn) as f:
-            d = json.load(f)
-        v = dataclasses.asdict(self.vcfg)
-        d.update({"model_type": "qwen2_vl", "image_token_id": v.pop("image_token_id"), "video_token_id": v.pop("video_token_id"),
-                  "vision_start_token_id": v.pop("vision_start_token_id"), "rope_scaling": {"type": "mrope", "mrope_section": list(v.pop("mrope_section"))},
-                  "vision_config": v})
-        with open(fn, "w") as f:
-            json.dump(d, f, indent=2)

@@ -204,7 +204,14 @@ class FSDPEngine(BaseEngine):
         dt_name = cfg_get(self.engine_config, "model_dtype", None) or (cfg.torch_dtype if self.device.type == "cpu" else "bfloat16")
         self.dtype = _DTYPES.get(str(dt_name), torch.bfloat16)
         seed = int(cfg_get(self.engine_config, "seed", 0))
-        self.model = DecoderLM(cfg, dtype=self.dtype, device=self.device, init=True, seed=seed)
+        if cfg.vision:
+            # vision-language family: tower + decoder behind the decoder's interface (verl_b200.models.vision)
+            from verl_b200.models.vision import VisionLanguageModel
+
+            assert self.sp_size == 1, "vision-language models do not run under sequence/context parallelism yet"
+            self.model = VisionLanguageModel(cfg, dtype=self.dtype, device=self.device, init=True, seed=seed)
+        else:
+            self.model = DecoderLM(cfg, dtype=self.dtype, device=self.device, init=True, seed=seed)
         path = cfg_get(self.model_config, "path", None) if not isinstance(self.model_config, ModelConfig) else None
         if path and os.path.isdir(os.path.expanduser(path)):
             from verl_b200.models.hf_io import load_hf_weights
@@ -436,7 +443,13 @@ class FSDPEngine(BaseEngine):
     def _pack(self, mb: dict) -> tuple[PackedBatch, torch.Tensor]:
         att = mb["attention_mask"].bool()
         ids = mb["input_ids"][att]
-        pos = mb["position_ids"][att]
+        pos_full, pos3 = mb["position_ids"], None
+        if pos_full.dim() == 3:
+            # multimodal rotary embedding: [bs, 3, L] (temporal, height, width) or [bs, 4, L] with the text positions first
+            # (reference: verl/utils/dataset/rl_dataset.py:330-360)
+            pos3 = pos_full[:, -3:].transpose(0, 1)[:, att]
+            pos_full = pos_full[:, 0]
+        pos = pos_full[att]
         lens = att.sum(-1)
         cu_cpu = torch.zeros(lens.numel() + 1, dtype=torch.int32)
         cu_cpu[1:] = torch.cumsum(lens.cpu(), 0)
@@ -445,14 +458,40 @@ class FSDPEngine(BaseEngine):
         routed = None
         if "routed_experts" in mb:
             routed = mb["routed_experts"][att]
-        return PackedBatch(ids, pos.to(torch.int32), cu, cu_cpu, int(lens.max()), routed), labels
+        pb = PackedBatch(ids, pos.to(torch.int32), cu, cu_cpu, int(lens.max()), routed)
+        mm_rows = mb.get("multi_modal_inputs")
+        if mm_rows is not None or pos3 is not None:
+            pb.mm = self._multi_modal(mb, mm_rows or [], pos3, att)
+        return pb, labels
+
+    def _multi_modal(self, mb: dict, rows: list, pos3, att: torch.Tensor) -> dict:
+        """Image patches of the micro-batch's rows in token order, their grids and the 3-stream positions of the packed tokens
+        (computed from the token ids when the batch carries plain 1-D positions)."""
+        dev = att.device
+        pix = [torch.as_tensor(r["pixel_values"]) for r in rows if r and r.get("pixel_values") is not None and len(r["pixel_values"])]
+        grids = [torch.as_tensor(r["image_grid_thw"]).reshape(-1, 3) for r in rows if r and r.get("image_grid_thw") is not None and len(r["image_grid_thw"])]
+        if pos3 is None and self.cfg.vision:
+            from verl_b200.models.vision import VisionConfig, get_rope_index
+
+            v = dict(self.cfg.vision)
+            vcfg = VisionConfig(**{**v, "mrope_section": tuple(v["mrope_section"])})
+            ids_cpu, att_cpu = mb["input_ids"].cpu(), att.cpu()
+            per_row = []
+            for i in range(ids_cpu.shape[0]):
+                r = rows[i] if i < len(rows) and rows[i] else {}
+                g = torch.as_tensor(r["image_grid_thw"]).reshape(-1, 3) if r.get("image_grid_thw") is not None and len(r["image_grid_thw"]) else None
+                p, _ = get_rope_index(ids_cpu[i], g, vcfg, attention_mask=att_cpu[i])
+                per_row.append(p[:, att_cpu[i]])
+            pos3 = torch.cat(per_row, 1).to(dev)
+        return {"pixel_values": torch.cat(pix, 0).to(dev) if pix else None, "image_grid_thw": torch.cat(grids, 0) if grids else None,
+                "mrope_positions": pos3}
 
     def _forward_micro_batch(self, mb: dict, meta: dict) -> dict:
         """Returns per-token outputs already sliced to the response window: tensors of shape [bs, R]."""
         pb, labels = self._pack(mb)
         R = mb["responses"].shape[1]
         idx, valid = response_gather_index(mb["attention_mask"], R)
-        if self._prefix_sharing(meta, mb):
+        if pb.mm is None and self._prefix_sharing(meta, mb):
             return self._forward_shared_prefix(mb, pb, labels, idx, valid, meta)
         temperature = float(meta.get("temperature", 1.0))
         need_entropy = bool(meta.get("calculate_entropy", False))
@@ -587,6 +626,7 @@ class FSDPEngine(BaseEngine):
         n = tensors["input_ids"].shape[0]
         seq_lens = tensors["attention_mask"].sum(-1)
         mb_indices = self._micro_batch_indices(seq_lens, meta, tensors)
+        mm_rows = (getattr(data, "non_tensor_batch", None) or {}).get("multi_modal_inputs")      # per-row dicts (vision-language models)
         # global normalisers for the loss (identical on all ranks)
         info: dict[str, Any] = {"dp_size": self.dp_size}
         if not forward_only and loss_function is not None:
@@ -609,6 +649,8 @@ class FSDPEngine(BaseEngine):
             it = torch.as_tensor(idxs, device=dev)
             mb = {k: (v.index_select(0, it) if isinstance(v, torch.Tensor) and v.dim() >= 1 and v.shape[0] == n else v)
                   for k, v in tensors.items()}
+            if mm_rows is not None:
+                mb["multi_modal_inputs"] = [mm_rows[i] for i in idxs]
             ctx = torch.no_grad() if forward_only else torch.enable_grad()
             with ctx:
                 mo = self._forward_micro_batch(mb, meta)
