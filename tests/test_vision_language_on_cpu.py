@@ -175,3 +175,65 @@ def test_engine_trains_a_vision_language_model_on_image_prompts():
     assert gn > 0 and not torch.equal(before, eng.model.visual.merger.mlp[2].weight)
     names = [k for k, _ in eng.get_per_tensor_param()[0]]
     assert "visual.patch_embed.proj.weight" in names and "model.layers.0.self_attn.q_proj.weight" in names
+
+
+def test_image_patches_match_the_hf_processor():
+    import numpy as np
+    from PIL import Image
+
+    from verl_b200.utils.dataset.vision_utils import expand_image_tokens, image_to_patches, process_image, smart_resize
+
+    assert smart_resize(100, 200) == (112, 196) and smart_resize(10, 10) == (56, 56)
+    h, w = smart_resize(4000, 3000)
+    assert h % 28 == 0 and w % 28 == 0 and h * w <= 14 * 14 * 4 * 1280
+    rng = np.random.default_rng(0)
+    img = Image.fromarray(rng.integers(0, 255, (90, 150, 3), dtype=np.uint8))
+    small = process_image({"image": img})
+    assert (small.height, small.width) == smart_resize(90, 150)
+    pix, grid = image_to_patches(small)
+    assert pix.shape == (grid[0, 1] * grid[0, 2], 3 * 2 * 14 * 14)
+    try:
+        from transformers.models.qwen2_vl.image_processing_qwen2_vl import Qwen2VLImageProcessor
+
+        proc = Qwen2VLImageProcessor()
+        want = proc(images=[small], do_resize=False, return_tensors="pt")
+    except Exception as e:  # noqa: BLE001 - the processor class moved or needs a backend that is not installed
+        pytest.skip(f"Hugging Face image processor unavailable: {e}")
+    assert torch.equal(want["image_grid_thw"], grid)
+    assert torch.allclose(want["pixel_values"].float(), pix, atol=1e-5)
+    assert expand_image_tokens([1, 500, 2, 500], torch.tensor([[1, 4, 4], [1, 2, 6]]), 500) == [1] + [500] * 4 + [2] + [500] * 3
+
+
+def test_dataset_builds_multimodal_rows(tmp_path):
+    import io
+
+    import numpy as np
+    import pandas as pd
+    from PIL import Image
+
+    from verl_b200.utils.dataset.rl_dataset import RLHFDataset, collate_fn
+
+    class Tok:
+        pad_token_id, chat_template = 0, None
+
+        def __call__(self, text, add_special_tokens=False):
+            return {"input_ids": [500 if w == "<image>" else 1 + (hash(w) % 300) for w in text.split()]}
+
+    buf = io.BytesIO()
+    Image.fromarray(np.random.default_rng(1).integers(0, 255, (60, 60, 3), dtype=np.uint8)).save(buf, format="PNG")
+    df = pd.DataFrame({"prompt": [[{"role": "user", "content": "look <image> and tell"}], [{"role": "user", "content": "no picture here"}]],
+                       "images": [[{"bytes": buf.getvalue()}], []], "data_source": ["geo3k", "geo3k"]})
+    f = tmp_path / "d.parquet"
+    df.to_parquet(f)
+    vision = dict(patch_size=4, temporal_patch_size=2, spatial_merge_size=2, image_token_id=500, mrope_section=[2, 3, 3])
+    ds = RLHFDataset(str(f), Tok(), {"max_prompt_length": 96, "vision": vision, "image_min_pixels": 256, "image_max_pixels": 1024})
+    a, b = ds[0], ds[1]
+    g = a["multi_modal_inputs"]["image_grid_thw"]
+    n_img_tok = int(g[0, 1] * g[0, 2]) // 4
+    assert int((a["input_ids"] == 500).sum()) == n_img_tok and a["multi_modal_inputs"]["pixel_values"].shape == (int(g[0, 1] * g[0, 2]), 96)
+    assert a["position_ids"].shape == (4, 96) and b["position_ids"].shape == (4, 96) and b["multi_modal_inputs"] == {}
+    live = a["attention_mask"].bool()
+    assert int(a["position_ids"][2][live].max()) < int(a["position_ids"][0][live].max())      # the image block advances less than its token count
+    assert torch.equal(b["position_ids"][0], b["position_ids"][1])                            # text only: all streams equal
+    batch = collate_fn([a, b])
+    assert batch["position_ids"].shape == (2, 4, 96) and len(batch["multi_modal_inputs"]) == 2

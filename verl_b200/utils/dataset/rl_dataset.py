@@ -72,6 +72,9 @@ class RLHFDataset(Dataset):
         self.return_raw_chat = bool(_g(config, "return_raw_chat", True))
         self.return_full_prompt = bool(_g(config, "return_full_prompt", False))
         self.apply_chat_template_kwargs = dict(_g(config, "apply_chat_template_kwargs", {}) or {})
+        # vision-language prompts: column with the images of a row and the tower geometry (VisionConfig fields)
+        self.image_key = _g(config, "image_key", "images")
+        self.vision = dict(_g(config, "vision", None) or {}) or None
         if bool(_g(config, "filter_overlong_prompts", False)):
             keep = [len(self._tokenize(self._messages(row))) <= self.max_prompt_length for _, row in self.df.iterrows()]
             self.df = self.df[np.asarray(keep)].reset_index(drop=True)
@@ -91,18 +94,47 @@ class RLHFDataset(Dataset):
             text = "\n".join(m["content"] for m in messages)
         return self.tokenizer(text, add_special_tokens=False)["input_ids"]
 
+    def _with_images(self, tok_ids, images):
+        """Patches of the row's images and the prompt with every image placeholder expanded to the image's merged patches."""
+        from verl_b200.utils.dataset.vision_utils import expand_image_tokens, image_to_patches, process_image
+
+        v = self.vision
+        P, Tp, m = int(v.get("patch_size", 14)), int(v.get("temporal_patch_size", 2)), int(v.get("spatial_merge_size", 2))
+        pix, grids = [], []
+        for img in images:
+            p, g = image_to_patches(process_image(img, factor=P * m, min_pixels=int(_g(self.config, "image_min_pixels", 4 * (P * m) ** 2)),
+                                                  max_pixels=int(_g(self.config, "image_max_pixels", 1280 * (P * m) ** 2))), P, Tp, m)
+            pix.append(p)
+            grids.append(g)
+        grids = torch.cat(grids, 0)
+        tok_ids = expand_image_tokens(tok_ids, grids, int(v.get("image_token_id", 151655)), m)
+        return tok_ids, {"pixel_values": torch.cat(pix, 0), "image_grid_thw": grids}
+
     def __len__(self):
         return len(self.df)
 
     def __getitem__(self, i):
         row = self.df.iloc[i].to_dict()
         messages = self._messages(row)
-        ids = torch.tensor(self._tokenize(messages), dtype=torch.int64)[None]
+        tok_ids = self._tokenize(messages)
+        images = row.get(self.image_key) if self.vision else None
+        mm = None
+        if images is not None and len(images):
+            tok_ids, mm = self._with_images(tok_ids, list(images))
+        ids = torch.tensor(tok_ids, dtype=torch.int64)[None]
         att = torch.ones_like(ids)
         pad = self.tokenizer.pad_token_id if self.tokenizer.pad_token_id is not None else 0
-        ids, att = VF.postprocess_data(ids, att, self.max_prompt_length, pad, left_pad=True, truncation=self.truncation)
-        out = {k: v for k, v in row.items() if k != self.prompt_key}
+        ids, att = VF.postprocess_data(ids, att, self.max_prompt_length, pad, left_pad=True, truncation="error" if mm else self.truncation)
+        out = {k: v for k, v in row.items() if k not in (self.prompt_key, self.image_key if self.vision else None)}
         out.update({"input_ids": ids[0], "attention_mask": att[0], "position_ids": VF.compute_position_id_with_mask(att[0])})
+        if self.vision:
+            # [4, L]: text positions first, then the temporal / height / width streams of the multimodal rotary embedding
+            from verl_b200.models.vision import VisionConfig, get_rope_index
+
+            vcfg = VisionConfig(**{**self.vision, "mrope_section": tuple(self.vision.get("mrope_section", (16, 24, 24)))})
+            pos3, _ = get_rope_index(ids[0], mm["image_grid_thw"] if mm else None, vcfg, attention_mask=att[0])
+            out["position_ids"] = torch.cat([out["position_ids"][None], pos3], 0)
+            out["multi_modal_inputs"] = mm or {}
         if self.return_raw_chat:
             out["raw_prompt"] = messages
         extra = out.get("extra_info") or {}
