@@ -237,3 +237,40 @@ def test_dataset_builds_multimodal_rows(tmp_path):
     assert torch.equal(b["position_ids"][0], b["position_ids"][1])                            # text only: all streams equal
     batch = collate_fn([a, b])
     assert batch["position_ids"].shape == (2, 4, 96) and len(batch["multi_modal_inputs"]) == 2
+
+
+def test_rollout_generates_from_image_prompts_like_a_full_forward():
+    """Greedy decoding with images through the paged rollout engine equals greedy decoding by repeated full forwards of the
+    model (per-token rotary tables at prefill, position offset after the image grid at decode); identical token ids with
+    different images are not shared as one prefix."""
+    from verl_b200.workers.rollout.engine import InferenceEngine, SamplingParams
+
+    torch.manual_seed(0)
+    model = VisionLanguageModel(_vl_config(), dtype=torch.float32, device=torch.device("cpu"), seed=11).eval()
+    g = torch.Generator().manual_seed(2)
+    grid = torch.tensor([[1, 4, 4]])
+    prompt = [7, 8, 502] + [500] * 4 + [503, 9, 10, 11]
+    mm_a = {"pixel_values": torch.randn(16, 96, generator=g), "image_grid_thw": grid}
+    mm_b = {"pixel_values": torch.randn(16, 96, generator=g), "image_grid_thw": grid}
+    text = [5, 6, 7, 8, 9]
+    eng = InferenceEngine(model, max_num_seqs=8, max_model_len=64, num_blocks=32, enforce_eager=True)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    outs = eng.generate([prompt, prompt, text, prompt], sp, multi_modal=[mm_a, mm_b, None, mm_a])
+
+    def greedy(ids, mm, n):
+        ids = list(ids)
+        for _ in range(n):
+            t = torch.tensor(ids)
+            pos3, _ = get_rope_index(t, mm["image_grid_thw"] if mm else None, model.vcfg)
+            pb = PackedBatch(t, torch.arange(len(ids), dtype=torch.int32), torch.tensor([0, len(ids)], dtype=torch.int32))
+            with torch.no_grad():
+                logits = model(pb, pixel_values=mm["pixel_values"] if mm else None, image_grid_thw=mm["image_grid_thw"] if mm else None,
+                               mrope_positions=pos3, return_logits=True)["logits"]
+            ids.append(int(logits[-1].argmax()))
+        return ids[-n:]
+
+    assert list(outs[0].token_ids) == greedy(prompt, mm_a, 6)
+    assert list(outs[1].token_ids) == greedy(prompt, mm_b, 6)
+    assert list(outs[2].token_ids) == greedy(text, None, 6)
+    assert list(outs[3].token_ids) == list(outs[0].token_ids)
+    assert list(outs[0].token_ids) != list(outs[1].token_ids) or not torch.equal(mm_a["pixel_values"], mm_b["pixel_values"])

@@ -88,10 +88,15 @@ class InferenceEngine:
                  max_num_batched_tokens: int = 8192, gpu_memory_utilization: float = 0.5, enforce_eager: bool = False,
                  sync_interval: int = 16, enable_prefix_sharing: bool = True, decode_splits: int = 0, tp_group=None, tp_ctx=None,
                  quantization: Optional[str] = None):
-        """``tp_group`` / ``tp_ctx``: tensor-parallel replica. ``model`` is then this rank's slice (``build_rollout_shard``); every
+        """``model`` may be a vision-language model (``verl_b200.models.vision.VisionLanguageModel``): its decoder serves the
+        tokens, its tower embeds the images of multimodal requests at prefill.
+        ``tp_group`` / ``tp_ctx``: tensor-parallel replica. ``model`` is then this rank's slice (``build_rollout_shard``); every
         rank of the group runs the same requests in lockstep (same scheduler decisions, same sampled tokens) and the
         row-parallel projections end in an all-reduce — fused into the GEMM epilogue over NVLink peer memory when
         ``tp_ctx`` (a ``TPContext``) is given, NCCL otherwise."""
+        self.visual = self.vision_config = None
+        if hasattr(model, "visual") and hasattr(model, "language_model"):
+            self.visual, self.vision_config, model = model.visual, model.vcfg, model.language_model
         self.model = model
         self.tp_group, self.tp = tp_group, tp_ctx
         # "fp8": W8A8 projections (per-output-channel e4m3 weights re-quantised from the live bf16 weights at every wake_up,
@@ -200,6 +205,7 @@ class InferenceEngine:
         S, dev = self.max_num_seqs, self.device
         self.cur_tokens = torch.zeros(S, dtype=torch.int64, device=dev)
         self.positions = torch.zeros(S, dtype=torch.int32, device=dev)
+        self.rope_delta = torch.zeros(S, dtype=torch.int32, device=dev)      # multimodal prompts: rotary position − cache position
         self.active = torch.zeros(S, dtype=torch.int32, device=dev)
         self.block_table = torch.zeros(S, self.max_blocks_per_seq, dtype=torch.int32, device=dev)
         self.kv_lens = torch.zeros(S, dtype=torch.int32, device=dev)
@@ -238,11 +244,15 @@ class InferenceEngine:
             torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ model forward (shared by prefill and decode)
-    def _layer_stack(self, tokens, positions, slots, attn_fn):
-        """Runs embedding → layers → final norm; ``attn_fn(layer_idx, qkv)`` returns the attention output."""
+    def _layer_stack(self, tokens, positions, slots, attn_fn, rope=None, visual=None):
+        """Runs embedding → layers → final norm; ``attn_fn(layer_idx, qkv)`` returns the attention output. ``rope``: per-token
+        (cos, sin) tables replacing the position-indexed ones (multimodal rotary embedding, ``positions`` = row numbers);
+        ``visual``: (row indices, embeddings) that replace the image placeholder tokens' embeddings."""
         m, c = self.model, self.cfg
-        cos, sin = m.rope(self.device)
+        cos, sin = rope if rope is not None else m.rope(self.device)
         h = m.embed_tokens.index_select(0, tokens)
+        if visual is not None:
+            h = h.index_copy(0, visual[0], visual[1].to(h.dtype))
         res = None
         n_rot = c.num_attention_heads + c.num_key_value_heads
         for li, layer in enumerate(m.layers):
@@ -362,11 +372,40 @@ class InferenceEngine:
         def attn(li, qkv):
             return ops.attention_varlen(qkv, cu, c.num_attention_heads, c.num_key_value_heads, c.head_dim, max_len, cu_cpu)
 
-        h = self._layer_stack(tokens, positions, slot_map, attn)
+        rope = visual = None
+        if self.visual is not None and any(req.get("mm") for req, _ in seqs):
+            rope, visual = self._multi_modal_prefill([req for req, _ in seqs], tokens)
+            positions = torch.arange(tokens.shape[0], dtype=torch.int32, device=dev)
+        h = self._layer_stack(tokens, positions, slot_map, attn, rope, visual)
         last = (cu[1:] - 1).long()
         logits = ops.linear(h.index_select(0, last), self.model.output_weight)
         self.stats["prefill_tokens"] += int(sum(lens))
         return logits
+
+    def _multi_modal_prefill(self, reqs: list, tokens: torch.Tensor):
+        """Vision-language prompts: per-token rotary tables from the 3-stream positions of every sequence, and the vision
+        tower's rows for the image placeholder tokens (reference: the multi_modal_data path of the serving engines,
+        verl/workers/rollout/vllm_rollout/vllm_async_server.py:561-640)."""
+        from verl_b200.models.vision import get_rope_index, mrope_tables
+
+        v, c = self.vision_config, self.cfg
+        pos3, pix, grids = [], [], []
+        for req in reqs:
+            mm = req.get("mm") or {}
+            g = mm.get("image_grid_thw")
+            p, _ = get_rope_index(torch.as_tensor(req["prompt"] + req["out"]), g, v)
+            pos3.append(p)
+            if g is not None and len(g):
+                pix.append(torch.as_tensor(mm["pixel_values"]))
+                grids.append(torch.as_tensor(g).reshape(-1, 3))
+        rope = mrope_tables(torch.cat(pos3, 1).to(self.device), c.head_dim, c.rope_theta, v.mrope_section)
+        visual = None
+        if pix:
+            rows = self.visual(torch.cat(pix, 0).to(self.device), torch.cat(grids, 0))
+            idx = ((tokens == v.image_token_id) | (tokens == v.video_token_id)).nonzero(as_tuple=True)[0]
+            assert idx.numel() == rows.shape[0], f"{idx.numel()} image placeholder tokens but {rows.shape[0]} merged patch embeddings"
+            visual = (idx, rows)
+        return rope, visual
 
     def _start_sequences(self, reqs_slots: list, logits: torch.Tensor, sp: SamplingParams):
         """Sample the first new token of each sequence from its last-prompt-token logits and arm its decode slot."""
@@ -379,6 +418,9 @@ class InferenceEngine:
         plen = torch.tensor([len(r["prompt"]) + len(r["out"]) for r, _ in reqs_slots], dtype=torch.int32, device=self.device)
         self.cur_tokens.index_copy_(0, slots, tok)
         self.positions.index_copy_(0, slots, plen)
+        if self.visual is not None:      # multimodal prompts: generated tokens continue after the image grid, not after its token count
+            delta = torch.tensor([int(r.get("rope_delta", 0)) for r, _ in reqs_slots], dtype=torch.int32, device=self.device)
+            self.rope_delta.index_copy_(0, slots, delta)
         self.kv_lens.index_copy_(0, slots, plen)
         self.active.index_fill_(0, slots, 1)
         tok_h, lp_h = tok.tolist(), lp.tolist()
@@ -426,7 +468,7 @@ class InferenceEngine:
 
             return paged_decode_attention_ref(q, self.cache[li], self.block_table, self.kv_lens, scale)
 
-        h = self._layer_stack(self.cur_tokens, pos, slot_map, attn)
+        h = self._layer_stack(self.cur_tokens, pos if self.visual is None else pos + self.rope_delta, slot_map, attn)
         logits = ops.linear(h, self.model.output_weight)
         self._sample(logits, sp.temperature, sp.top_k, sp.top_p, self.row_ids, self.out_tok, self.out_lp)
         self._tp_sync_samples(self.out_tok, self.out_lp)
@@ -510,10 +552,21 @@ class InferenceEngine:
             self.active.index_fill_(0, torch.tensor(freed, dtype=torch.int64, device=self.device), 0)
         self.stats["t_flush"] += time.perf_counter() - t_f
 
+    @staticmethod
+    def _prompt_key(p, mm):
+        """Identity of a prompt for prefix sharing: the token ids, plus a digest of the images for multimodal prompts (the
+        placeholder tokens of two different images are identical)."""
+        if not mm or mm.get("pixel_values") is None:
+            return tuple(p)
+        pv = torch.as_tensor(mm["pixel_values"]).float()
+        return (tuple(p), tuple(pv.shape), round(float(pv.sum()), 4), round(float(pv.abs().sum()), 4))
+
     @torch.no_grad()
     def generate(self, prompts: Sequence[Sequence[int]], sampling_params: Optional[SamplingParams] = None,
-                 eos_token_id=None, admit=None, on_done=None, keep_alive=None, should_abort=None) -> list[TokenOutput]:
-        """Batch generation, optionally kept open as a serving loop.
+                 eos_token_id=None, admit=None, on_done=None, keep_alive=None, should_abort=None, multi_modal=None) -> list[TokenOutput]:
+        """Batch generation, optionally kept open as a serving loop. ``multi_modal``: per prompt ``None`` or
+        ``{"pixel_values", "image_grid_thw"}`` (the prompt then holds the expanded image placeholder tokens); ``admit`` may
+        return such a dict as a third tuple element.
 
         With ``admit`` (a callable returning a list of ``(prompt_ids, max_tokens or None)``) new requests join the
         running batch whenever the loop synchronises with the device; they are numbered consecutively after the initial
@@ -538,25 +591,33 @@ class InferenceEngine:
             nonlocal poll_no
             poll_no += 1
             local: dict[tuple, int] = {}
+            items = [(it[0], it[1], it[2] if len(it) > 2 else None) for it in items]
             if self.enable_prefix_sharing:
-                for p, _ in items:
-                    k = tuple(p)
+                for p, _, mm in items:
+                    k = self._prompt_key(p, mm)
                     local[k] = local.get(k, 0) + 1
-            for p, mt in items:
+            for p, mt, mm in items:
                 i = len(reqs)
                 p = list(p)
+                pk = self._prompt_key(p, mm)
                 max_new = min(int(mt) if mt else sp.max_tokens, self.max_model_len - len(p))
                 if max_new <= 0:
                     raise ValueError(f"prompt {i} of length {len(p)} leaves no room below max_model_len={self.max_model_len}")
                 key = 0
-                if local.get(tuple(p), 0) > 1:
-                    key = (hash((poll_no, tuple(p))) & 0x3FFFFFFFFFFFFFFF) or 1
-                    counts[tuple(p)] = local[tuple(p)]
+                if local.get(pk, 0) > 1:
+                    key = (hash((poll_no, pk)) & 0x3FFFFFFFFFFFFFFF) or 1
+                    counts[pk] = local[pk]
                 reqs[i] = {"id": i, "prompt": p, "out": [], "lp": [], "done": False, "stop": None, "max_new": max_new, "n_gen": 0,
-                           "num_preempted": 0, "slot": -1, "reported": False}
+                           "num_preempted": 0, "slot": -1, "reported": False, "pkey": pk}
+                if mm:
+                    assert self.visual is not None, "this engine was built without a vision tower"
+                    from verl_b200.models.vision import get_rope_index
+
+                    reqs[i]["mm"] = mm
+                    reqs[i]["rope_delta"] = get_rope_index(torch.as_tensor(p), mm.get("image_grid_thw"), self.vision_config)[1]
                 self.sched.add(i, len(p), max_new, key)
 
-        add_requests([(p, None) for p in prompts])
+        add_requests([(p, None, multi_modal[j] if multi_modal is not None else None) for j, p in enumerate(prompts)])
         owner_logits: dict[int, torch.Tensor] = {}
         owner_partial_block: dict[int, int] = {}
         pending: list = []
@@ -600,7 +661,7 @@ class InferenceEngine:
                     logits = self._prefill(fresh, sp)
                     for row, (r, sl) in enumerate(fresh):
                         r["slot"] = sl
-                        if counts.get(tuple(r["prompt"]), 0) > 1 and not r["out"]:
+                        if counts.get(r["pkey"], 0) > 1 and not r["out"]:
                             owner_logits[r["id"]] = logits[row]
                             owner_partial_block[r["id"]] = int(self.block_table_host[sl, len(r["prompt"]) // BLOCK_SIZE])
                     self._start_sequences(fresh, logits, sp)
