@@ -176,6 +176,13 @@ PRESETS: dict[str, ModelConfig] = {
     "tiny-qwen2": ModelConfig(model_type="qwen2", vocab_size=2048, hidden_size=128, intermediate_size=512,
                               num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-6,
                               rope_theta=1e4, tie_word_embeddings=True, max_position_embeddings=4096, torch_dtype="float32"),
+    # vision-language plumbing model: 2-layer decoder + 2-block tower on 4×4 patches, image token ids inside the small vocabulary
+    "tiny-qwen2-vl": ModelConfig(model_type="qwen2", vocab_size=2048, hidden_size=128, intermediate_size=512, num_hidden_layers=2,
+                                 num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-6, rope_theta=1e4, tie_word_embeddings=True,
+                                 max_position_embeddings=4096, torch_dtype="float32",
+                                 vision=dict(depth=2, embed_dim=32, num_heads=2, mlp_ratio=2.0, in_channels=3, patch_size=4, temporal_patch_size=2,
+                                             spatial_merge_size=2, hidden_size=128, image_token_id=2040, video_token_id=2041,
+                                             vision_start_token_id=2042, mrope_section=[4, 6, 6])),
     "tiny-qwen2-gpu": ModelConfig(model_type="qwen2", vocab_size=4096, hidden_size=512, intermediate_size=1536,
                                   num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
                                   rope_theta=1e4, max_position_embeddings=4096),

@@ -133,6 +133,20 @@ class PPOTrainer:
         from verl_b200.utils.dataset import create_rl_dataset, create_rl_sampler
 
         dc = self.config.data
+        if dc.get("vision") is None:
+            # vision-language actor: the dataset needs the tower geometry (patch / merge sizes, placeholder ids) to cut images
+            mc = self.config.actor_rollout_ref.model
+            vis = None
+            if mc.get("preset"):
+                from verl_b200.models.config import PRESETS
+
+                vis = PRESETS[mc.get("preset")].vision
+            elif mc.get("path") and os.path.exists(os.path.join(os.path.expanduser(str(mc.get("path"))), "config.json")):
+                from verl_b200.models.config import ModelConfig
+
+                vis = ModelConfig.from_pretrained(os.path.expanduser(str(mc.get("path")))).vision
+            if vis:
+                dc["vision"] = dict(vis)
         if train_dataset is None:
             train_dataset = create_rl_dataset(dc.get("train_files"), dc, self.tokenizer, self.processor, is_train=True)
         if val_dataset is None and (dc.get("val_files") or _g(dc, "synthetic.enable", False)):
@@ -331,7 +345,8 @@ def _train_step(self: PPOTrainer, batch_dict: dict) -> dict:
     n = int(cfg.actor_rollout_ref.rollout.n)
     batch.non_tensor_batch["uid"] = np.array([str(uuid.uuid4()) for _ in range(len(batch))], dtype=object)
     with marked_timer("step", timing_raw):
-        gen_batch = batch.select(batch_keys=["input_ids", "attention_mask", "position_ids"], non_tensor_batch_keys=[])
+        mm_keys = [k for k in ("multi_modal_inputs",) if k in batch.non_tensor_batch]      # image inputs of vision-language prompts
+        gen_batch = batch.select(batch_keys=["input_ids", "attention_mask", "position_ids"], non_tensor_batch_keys=mm_keys)
         gen_batch.meta_info = self._gen_meta()
         gen_batch = gen_batch.repeat(repeat_times=n, interleave=True)
         with marked_timer("gen", timing_raw):
@@ -343,7 +358,7 @@ def _train_step(self: PPOTrainer, batch_dict: dict) -> dict:
                 metrics.update(reduce_metrics(ro_metrics if isinstance(ro_metrics, dict) else {}))
         if cfg.algorithm.adv_estimator == "remax":
             with marked_timer("gen_max", timing_raw):
-                base = batch.select(batch_keys=["input_ids", "attention_mask", "position_ids"], non_tensor_batch_keys=[])
+                base = batch.select(batch_keys=["input_ids", "attention_mask", "position_ids"], non_tensor_batch_keys=mm_keys)
                 base.meta_info = {**self._gen_meta(), "do_sample": False}
                 base_out = self.actor_rollout_wg.generate_sequences(base)
                 tmp = batch.union(base_out.select(batch_keys=["prompts", "responses", "input_ids", "attention_mask", "position_ids", "response_mask"]))
@@ -352,6 +367,8 @@ def _train_step(self: PPOTrainer, batch_dict: dict) -> dict:
                 batch.batch["reward_baselines"] = rb.sum(-1)
         batch = batch.repeat(repeat_times=n, interleave=True)
         batch.pop(batch_keys=["input_ids", "attention_mask", "position_ids"])
+        for k in mm_keys:
+            gen_out.non_tensor_batch.pop(k, None)      # the repeated batch already holds them
         batch = batch.union(gen_out)
         metrics.update(self.train_on_rollouts(batch, timing_raw, n))
     metrics.update(compute_timing_metrics(batch=self._last_batch, timing_raw=timing_raw))

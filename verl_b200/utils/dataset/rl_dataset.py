@@ -92,6 +92,17 @@ class RLHFDataset(Dataset):
             text = self.tokenizer.apply_chat_template(messages, add_generation_prompt=True, tokenize=False, **self.apply_chat_template_kwargs)
         else:
             text = "\n".join(m["content"] for m in messages)
+        if self.vision and "<image>" in text and "<|image_pad|>" not in text:
+            # a tokenizer whose chat template knows nothing about images: every "<image>" mark becomes
+            # vision_start, ONE image placeholder (expanded to the image's size later), vision_end
+            v = self.vision
+            vs = int(v.get("vision_start_token_id", 151652))
+            mark = [vs, int(v.get("image_token_id", 151655)), int(v.get("vision_end_token_id", vs + 1))]
+            ids, parts = [], text.split("<image>")
+            for j, part in enumerate(parts):
+                ids += self.tokenizer(part, add_special_tokens=False)["input_ids"] if part else []
+                ids += mark if j < len(parts) - 1 else []
+            return ids
         return self.tokenizer(text, add_special_tokens=False)["input_ids"]
 
     def _with_images(self, tok_ids, images):
@@ -102,8 +113,8 @@ class RLHFDataset(Dataset):
         P, Tp, m = int(v.get("patch_size", 14)), int(v.get("temporal_patch_size", 2)), int(v.get("spatial_merge_size", 2))
         pix, grids = [], []
         for img in images:
-            p, g = image_to_patches(process_image(img, factor=P * m, min_pixels=int(_g(self.config, "image_min_pixels", 4 * (P * m) ** 2)),
-                                                  max_pixels=int(_g(self.config, "image_max_pixels", 1280 * (P * m) ** 2))), P, Tp, m)
+            p, g = image_to_patches(process_image(img, factor=P * m, min_pixels=int(_g(self.config, "image_min_pixels", None) or 4 * (P * m) ** 2),
+                                                  max_pixels=int(_g(self.config, "image_max_pixels", None) or 1280 * (P * m) ** 2)), P, Tp, m)
             pix.append(p)
             grids.append(g)
         grids = torch.cat(grids, 0)

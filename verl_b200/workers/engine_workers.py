@@ -47,6 +47,12 @@ def ensure_process_group(timeout_s: int = 600):
             dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=timeout_s))
 
 
+def _model_inputs(data) -> dict:
+    """Non-tensor columns that the engines consume: the per-row image inputs of vision-language models."""
+    nt = getattr(data, "non_tensor_batch", None) or {}
+    return {"multi_modal_inputs": nt["multi_modal_inputs"]} if "multi_modal_inputs" in nt else {}
+
+
 class TrainingWorker(Worker):
     """Mini-batch / epoch loop around one engine. ``config`` keys: model_type, backend, model, engine, optim, checkpoint
     plus the batching knobs (ppo_mini_batch_size, ppo_epochs, micro-batch / dynamic-bsz settings)."""
@@ -357,7 +363,8 @@ class ActorRolloutRefWorker(Worker):
         t0 = time.perf_counter()
         self.rollout.profile = bool(os.environ.get("VERL_B200_PROFILE_ROLLOUT"))
         self.rollout.wake_up()
-        outs = self.rollout.generate(plist, sp, eos_token_id=eos)
+        mm = prompts.non_tensor_batch.get("multi_modal_inputs") if prompts.non_tensor_batch else None
+        outs = self.rollout.generate(plist, sp, eos_token_id=eos, multi_modal=[(m or None) for m in mm] if mm is not None else None)
         if self.rollout.profile and self.rank == 0:
             print(f"[rollout stats] {self.rollout.stats}", flush=True)
         if bool(cfg_get(ro, "free_cache_engine", True)):
@@ -400,7 +407,7 @@ class ActorRolloutRefWorker(Worker):
         meta = dict(data.meta_info)
         meta["calculate_entropy"] = calculate_entropy
         meta.setdefault("temperature", float(cfg_get(self.config, "rollout.temperature", 1.0)))
-        d = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=meta)
+        d = DataProto(batch=data.batch, non_tensor_batch=_model_inputs(data), meta_info=meta)
         return worker.infer_batch(d)["model_output"]
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
@@ -426,7 +433,7 @@ class ActorRolloutRefWorker(Worker):
         meta["return_topk"] = int(cfg_get(self.config, "distillation.topk", 32))
         meta["temperature"] = 1.0
         meta.pop("use_prefix_grouper", None)
-        d = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=meta)
+        d = DataProto(batch=data.batch, non_tensor_batch=_model_inputs(data), meta_info=meta)
         mo = self.teacher.infer_batch(d)["model_output"]
         return DataProto.from_dict(tensors={"teacher_topk_ids": _to_host(mo["topk_ids"]), "teacher_topk_log_probs": _to_host(mo["topk_log_probs"])})
 
@@ -439,7 +446,7 @@ class ActorRolloutRefWorker(Worker):
             meta["distillation"] = True
         meta.setdefault("temperature", float(cfg_get(self.config, "rollout.temperature", 1.0)))
         meta["calculate_entropy"] = bool(cfg_get(ac, "calculate_entropy", False)) or float(cfg_get(ac, "entropy_coeff", 0.0)) != 0.0
-        data = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=meta)
+        data = DataProto(batch=data.batch, non_tensor_batch=_model_inputs(data), meta_info=meta)
         metrics = self.actor.train_mini_batch(data)
         return DataProto(batch=None, non_tensor_batch={}, meta_info={"metrics": metrics})
 
@@ -494,14 +501,14 @@ class CriticWorker(Worker):
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("critic"))
     def compute_values(self, data: DataProto) -> DataProto:
-        d = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=dict(data.meta_info))
+        d = DataProto(batch=data.batch, non_tensor_batch=_model_inputs(data), meta_info=dict(data.meta_info))
         mo = self.critic.infer_batch(d)["model_output"]
         vals = mo["values"].cpu() * data.batch["response_mask"].to(mo["values"].dtype).cpu()
         return DataProto.from_dict(tensors={"values": vals})
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("critic"))
     def update_critic(self, data: DataProto) -> DataProto:
-        d = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=dict(data.meta_info))
+        d = DataProto(batch=data.batch, non_tensor_batch=_model_inputs(data), meta_info=dict(data.meta_info))
         metrics = self.critic.train_mini_batch(d)
         return DataProto(batch=None, non_tensor_batch={}, meta_info={"metrics": metrics})
 
@@ -545,7 +552,7 @@ class RewardModelWorker(Worker):
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("reward_model"))
     def compute_rm_score(self, data: DataProto) -> DataProto:
-        d = DataProto(batch=data.batch, non_tensor_batch={}, meta_info=dict(data.meta_info))
+        d = DataProto(batch=data.batch, non_tensor_batch=_model_inputs(data), meta_info=dict(data.meta_info))
         vals = self.rm.infer_batch(d)["model_output"]["values"].float().cpu()           # [bs, R] head output per response token
         mask = data.batch["response_mask"].cpu()
         last = (mask.sum(-1) - 1).clamp(min=0).long()
