@@ -276,7 +276,8 @@ def test_rollout_generates_from_image_prompts_like_a_full_forward():
     assert list(outs[0].token_ids) != list(outs[1].token_ids) or not torch.equal(mm_a["pixel_values"], mm_b["pixel_values"])
 
 
-def test_grpo_step_on_image_prompts_end_to_end(tmp_path):
+@pytest.mark.parametrize("mode", ["sync", "async"])
+def test_grpo_step_on_image_prompts_end_to_end(tmp_path, mode):
     """GRPO through the trainer with a vision-language actor: parquet prompts with images → rollout with the tower at
     prefill → old/ref log-probs and the update on multimodal micro-batches. On-policy, so the first PPO KL is ~0 — which
     only holds if rollout and trainer agree on image embeddings and rotary positions."""
@@ -306,7 +307,7 @@ def test_grpo_step_on_image_prompts_end_to_end(tmp_path):
           "actor_rollout_ref.rollout.log_prob_micro_batch_size_per_gpu=8", "actor_rollout_ref.rollout.max_num_seqs=16",
           "actor_rollout_ref.model.enable_gradient_checkpointing=false", "algorithm.adv_estimator=grpo", "reward.reward_manager=token_rule",
           "trainer.device=cpu", "trainer.val_before_train=false", "trainer.logger=[]", "trainer.n_gpus_per_node=1", "data.shuffle=false",
-          "trainer.total_training_steps=1", f"trainer.default_local_dir={tmp_path}/ckpt"]
+          "trainer.total_training_steps=1", f"trainer.default_local_dir={tmp_path}/ckpt", f"actor_rollout_ref.rollout.mode={mode}"]
     cfg = load_config("ppo_trainer", ov)
     from verl_b200.utils.tokenizer import ByteChatTokenizer
 

@@ -132,7 +132,7 @@ class AgentLoopWorker:
         samples = []
         for i in range(n):
             s = {k: v[i] for k, v in ntb.items()}
-            if "raw_prompt" not in s and batch.batch is not None and "input_ids" in batch.batch:
+            if ("raw_prompt" not in s or s.get("multi_modal_inputs")) and batch.batch is not None and "input_ids" in batch.batch:
                 att = batch.batch["attention_mask"][i].bool()
                 s["prompt_ids"] = batch.batch["input_ids"][i][att].tolist()
             samples.append(s)

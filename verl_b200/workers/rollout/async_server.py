@@ -51,16 +51,19 @@ class AsyncRolloutServer:
         self._thread.start()
 
     # ------------------------------------------------------------------ client side
-    def submit(self, prompt_ids, sampling_params: Optional[SamplingParams] = None, request_id: Optional[str] = None) -> concurrent.futures.Future:
+    def submit(self, prompt_ids, sampling_params: Optional[SamplingParams] = None, request_id: Optional[str] = None,
+               multi_modal: Optional[dict] = None) -> concurrent.futures.Future:
+        """``multi_modal``: ``{"pixel_values", "image_grid_thw"}`` of a vision-language prompt (its placeholders already expanded)."""
         fut: concurrent.futures.Future = concurrent.futures.Future()
         sp = sampling_params or SamplingParams()
         self.stats["requests"] += 1
         self.stats["prompt_tokens"] += len(prompt_ids)
-        self._q.put((list(prompt_ids), sp, fut, request_id))
+        self._q.put((list(prompt_ids), sp, fut, request_id, multi_modal))
         return fut
 
-    async def generate(self, prompt_ids, sampling_params: Optional[SamplingParams] = None, request_id: Optional[str] = None) -> TokenOutput:
-        return await asyncio.wrap_future(self.submit(prompt_ids, sampling_params, request_id))
+    async def generate(self, prompt_ids, sampling_params: Optional[SamplingParams] = None, request_id: Optional[str] = None,
+                       multi_modal: Optional[dict] = None) -> TokenOutput:
+        return await asyncio.wrap_future(self.submit(prompt_ids, sampling_params, request_id, multi_modal))
 
     @property
     def num_inflight(self) -> int:
@@ -189,7 +192,7 @@ class AsyncRolloutServer:
                     return []
                 items = self._take(key)
                 futs.extend(it[2] for it in items)
-                return [(it[0], it[1].max_tokens) for it in items]
+                return [(it[0], it[1].max_tokens, it[4] if len(it) > 4 else None) for it in items]
 
             def on_done(i, out: TokenOutput):
                 self.stats["aborted" if out.stop_reason == "aborted" else "finished"] += 1

@@ -80,8 +80,10 @@ class LLMServerClient:
             self._session = aiohttp.ClientSession(timeout=aiohttp.ClientTimeout(total=None))
         return self._session
 
-    async def _call(self, target, prompt_ids, sp: SamplingParams, request_id: str) -> TokenOutput:
+    async def _call(self, target, prompt_ids, sp: SamplingParams, request_id: str, multi_modal=None) -> TokenOutput:
         if isinstance(target, str):
+            if multi_modal:
+                raise NotImplementedError("image inputs are only passed to in-process servers (the HTTP protocol carries token ids)")
             sess = await self._http()
             body = {"prompt_ids": list(prompt_ids), "request_id": request_id,
                     "sampling_params": {"temperature": sp.temperature, "top_p": sp.top_p, "top_k": sp.top_k, "max_tokens": sp.max_tokens,
@@ -91,14 +93,15 @@ class LLMServerClient:
                 d = await resp.json()
             return TokenOutput(token_ids=d["token_ids"], log_probs=d.get("log_probs"), stop_reason=d.get("stop_reason"),
                                num_preempted=d.get("num_preempted", 0))
-        return await target.generate(prompt_ids, sp, request_id)
+        return await (target.generate(prompt_ids, sp, request_id, multi_modal) if multi_modal else target.generate(prompt_ids, sp, request_id))
 
-    async def generate(self, request_id: Optional[str], prompt_ids, sampling_params: Optional[SamplingParams] = None) -> TokenOutput:
+    async def generate(self, request_id: Optional[str], prompt_ids, sampling_params: Optional[SamplingParams] = None,
+                       multi_modal: Optional[dict] = None) -> TokenOutput:
         request_id = request_id or uuid.uuid4().hex
         sp = sampling_params or SamplingParams()
         sid = self.balancer.acquire(request_id)
         try:
-            return await self._call(self.servers[sid], prompt_ids, sp, request_id)
+            return await self._call(self.servers[sid], prompt_ids, sp, request_id, multi_modal)
         finally:
             self.balancer.release(sid)
 
@@ -115,7 +118,7 @@ class FullyAsyncLLMServerClient(LLMServerClient):
         super().__init__(servers, balancer)
         self.max_resumes, self.resume_delay_s = max_resumes, resume_delay_s
 
-    async def generate(self, request_id, prompt_ids, sampling_params: Optional[SamplingParams] = None) -> TokenOutput:
+    async def generate(self, request_id, prompt_ids, sampling_params: Optional[SamplingParams] = None, multi_modal: Optional[dict] = None) -> TokenOutput:
         import dataclasses
 
         sp = sampling_params or SamplingParams()
@@ -126,7 +129,7 @@ class FullyAsyncLLMServerClient(LLMServerClient):
         out = None
         for attempt in range(self.max_resumes + 1):
             cur = dataclasses.replace(sp, max_tokens=budget)
-            out = await super().generate(request_id, list(prompt_ids) + toks, cur)
+            out = await super().generate(request_id, list(prompt_ids) + toks, cur, multi_modal)
             toks += list(out.token_ids)
             lps += list(out.log_probs or [])
             preempted += out.num_preempted
