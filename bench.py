@@ -81,6 +81,8 @@ def build_config(args, world: int):
         ov.append("actor_rollout_ref.actor.use_prefix_grouper=true")
     if args.rollout_quant:
         ov.append(f"actor_rollout_ref.rollout.quantization={args.rollout_quant}")
+    if args.zero3:
+        ov += ["actor_rollout_ref.actor.fsdp_config.reshard_after_forward=true", "+actor_rollout_ref.ref.fsdp_config.reshard_after_forward=true"]
     if args.rollout_tp > 1:
         ov.append(f"actor_rollout_ref.rollout.tensor_model_parallel_size={args.rollout_tp}")
         ov.append(f"actor_rollout_ref.rollout.max_num_seqs={prompts_per_gpu * args.n * args.rollout_tp}")
@@ -170,7 +172,7 @@ def run_native(args):
                        "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + response <= {args.response_length}",
                        "parallelism": f"dp{world} (ZeRO-2 sharded optimizer, resident bf16 params), rollout tp{args.rollout_tp} x {world // args.rollout_tp} replicas colocated",
                        "ppo_mini_batch_prompts": args.mini_prompts_per_gpu * world, "token_budget_per_micro_batch": args.token_budget,
-                       "gradient_checkpointing": bool(args.grad_ckpt), "ref_param_offload": bool(args.ref_offload), "prefix_sharing": bool(args.prefix_sharing), "rollout_quantization": args.rollout_quant or None, "loss": "grpo clip 0.2 + low_var_kl 1e-3, AdamW lr 1e-6",
+                       "gradient_checkpointing": bool(args.grad_ckpt), "ref_param_offload": bool(args.ref_offload), "prefix_sharing": bool(args.prefix_sharing), "rollout_quantization": args.rollout_quant or None, "zero3": bool(args.zero3), "loss": "grpo clip 0.2 + low_var_kl 1e-3, AdamW lr 1e-6",
                        "l2_policy": "inputs larger than L2: each step streams >15 GB of weights and fresh activations"},
             "clocks": _summarise_clocks(samples),
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -227,6 +229,7 @@ def main():
     ap.add_argument("--grad-ckpt", type=int, default=-1,
                     help="activation recomputation (default off: activations of an 8192-token micro-batch are stored)")
     ap.add_argument("--rollout-quant", type=str, default="", help="fp8: W8A8 rollout projections (not the headline config; dtype is then reported as bf16+fp8 rollout)")
+    ap.add_argument("--zero3", type=int, default=0, help="row-shard the actor's and the reference's decoder projections over all ranks (weight gather fused into the GEMMs)")
     ap.add_argument("--prefix-sharing", type=int, default=0,
                     help="forward/backward every distinct prompt once for its n responses (actor.use_prefix_grouper); off = the reference's default")
     ap.add_argument("--ref-offload", type=int, default=-1, help="keep the frozen reference weights in pinned host memory between its passes")

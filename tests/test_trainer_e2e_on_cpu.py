@@ -111,3 +111,24 @@ def test_reward_model_worker_scores_the_last_response_token(tmp_path):
     assert (rm.abs().sum(-1) == rm[rows, last].abs()).all() and rm[rows, last].abs().sum() > 0       # one non-zero entry per row, at the last token
     rule = b["token_level_scores"] - rm
     assert ((rule == 0) | (rule == 1)).all()                                                            # what is left is the 0/1 rule reward
+
+
+def test_rollout_dumps_and_viewer(tmp_path, capsys):
+    """``trainer.rollout_data_dir``: one JSON line per trajectory and step; the viewer lists, filters and summarises them."""
+    from verl_b200.scripts.rollout_viewer import list_steps, load_step, main as viewer_main
+
+    dump = tmp_path / "rollouts"
+    tr = build(tmp_path, ["trainer.total_training_steps=2", f"trainer.rollout_data_dir={dump}"])
+    it = iter(tr.train_dataloader)
+    for step in (1, 2):
+        tr.global_steps = step
+        tr.step(next(it))
+    assert list_steps(str(dump)) == [1, 2]
+    rows = load_step(str(dump), 2)
+    assert len(rows) == 8 * 4 and {"input", "output", "score", "step"} <= set(rows[0]) and rows[0]["step"] == 2
+    assert viewer_main([str(dump), "--stats"]) == 0
+    out = capsys.readouterr().out
+    assert "mean score" in out and out.strip().splitlines()[-1].split()[0] == "2"
+    assert viewer_main([str(dump), "--step", "1", "--sort=-score", "--limit", "3"]) == 0
+    out = capsys.readouterr().out
+    assert out.count("--- output") == 3 and "step 1: 32 trajectories" in out

@@ -194,3 +194,51 @@ def test_tool_call_dialects():
 
     assert g("glm", Tok()).stop_token_ids == [7] and g("gemma4", Tok()).stop_token_ids == [9] and g("kimi", Tok()).stop_token_ids == []
     assert g("hermes", Tok()).stop_token_ids == []
+
+
+def test_continuous_token_builder_and_template_checker():
+    """Token-level continuation of a multi-turn conversation equals a single render; a template that rewrites earlier turns is
+    reported; generation cut before the end-of-turn token gets the turn closed."""
+    from verl_b200.scripts.chat_template_checker import main as checker_main
+    from verl_b200.utils.continuous_token import MOCK_TRAJECTORIES, ContinuousTokenBuilder, check_append_only
+    from verl_b200.utils.tokenizer import ByteChatTokenizer
+
+    tok = ByteChatTokenizer()
+    rep = check_append_only(tok)
+    assert all(r["builder"] and r["raw_prefix"] for r in rep.values()) and rep["parallel_tools"]["boundaries"] == 2
+    assert checker_main([]) == 0
+    b = ContinuousTokenBuilder(tok)
+    msgs = MOCK_TRAJECTORIES["tool_call"]
+    prompt = b.initial_prompt(msgs[:1])
+    gen = tok.encode(msgs[1]["content"]) + [tok.eos_token_id]
+    merged = b.merge_context_tokens(prompt + gen, msgs[2:3])
+    assert merged == tok.apply_chat_template(msgs[:3], add_generation_prompt=True, tokenize=True)
+    cut = b.merge_context_tokens(prompt + gen[:-1], msgs[2:3])          # length-limited generation: the turn is closed first
+    assert cut == merged
+
+    class Rewriting(ByteChatTokenizer):
+        """Renders only the LAST assistant turn in full (earlier ones are shortened) — not append-only."""
+
+        def apply_chat_template(self, messages, **kw):
+            msgs = [dict(m) for m in messages]
+            last = max((i for i, m in enumerate(msgs) if m["role"] == "assistant"), default=-1)
+            for i, m in enumerate(msgs):
+                if m["role"] == "assistant" and i != last:
+                    m["content"] = "…"
+            return super().apply_chat_template(msgs, **kw)
+
+    rep = check_append_only(Rewriting())
+    # the raw template is not append-only, yet every boundary still merges correctly: the prefix keeps the sampled tokens
+    assert not rep["system_multi_turn"]["raw_prefix"] and rep["parallel_tools"]["builder"]
+
+    class Unstable(ByteChatTokenizer):
+        """Quotes the conversation's first message in every tool message — the synthetic context renders it differently."""
+
+        def apply_chat_template(self, messages, **kw):
+            msgs = [dict(m) for m in messages]
+            for m in msgs:
+                if m["role"] == "tool":
+                    m["content"] = f"[{str(msgs[0]['content'])[:4]}] " + str(m["content"])
+            return super().apply_chat_template(msgs, **kw)
+
+    assert not check_append_only(Unstable())["tool_call"]["builder"]

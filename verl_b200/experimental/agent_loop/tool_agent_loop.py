@@ -38,8 +38,9 @@ class ToolAgentLoop(AgentLoopBase):
         self.truncate_side = cfg_get(mt, "tool_response_truncate_side", "middle")
         self.parser = get_tool_parser(cfg_get(mt, "format", "hermes"), tokenizer)
         self.tool_schemas = [t.tool_schema.to_dict() for t in self.tools.values()]
-        base = [{"role": "user", "content": ""}]
-        self._base_len = len(self.tokenizer.apply_chat_template(base, add_generation_prompt=False, tokenize=True))
+        from verl_b200.utils.continuous_token import ContinuousTokenBuilder
+
+        self._builder = ContinuousTokenBuilder(self.tokenizer)
 
     def _truncate(self, text: str) -> str:
         L = self.max_tool_response_length
@@ -53,8 +54,7 @@ class ToolAgentLoop(AgentLoopBase):
 
     def _tool_turn_ids(self, tool_messages: list) -> list:
         """Tokens that the chat template adds for the tool messages plus the next assistant header."""
-        full = self.tokenizer.apply_chat_template([{"role": "user", "content": ""}] + tool_messages, add_generation_prompt=True, tokenize=True)
-        return list(full)[self._base_len:]
+        return self._builder.merge_context_tokens([], tool_messages)
 
     async def _call_tool(self, call, tool_kwargs: dict):
         tool = self.tools.get(call.name)

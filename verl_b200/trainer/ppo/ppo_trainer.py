@@ -293,6 +293,36 @@ class PPOTrainer:
                 "validate": validate, "global_steps": self.global_steps,
                 "response_length": int(self.config.data.max_response_length)}
 
+    def _dump_generations(self, batch: DataProto, scores: list, extra: dict, dump_dir: str, append: bool = False) -> str:
+        """One JSON line per trajectory in ``{dump_dir}/{global_step}.jsonl``: prompt and response (text when a tokenizer is
+        known, token ids otherwise), score, ground truth, data source and the scalar extras of the reward function
+        (reference: ``verl/trainer/ppo/ray_trainer.py:479-545``, ``trainer.rollout_data_dir`` / ``validation_data_dir``)."""
+        import json
+
+        os.makedirs(dump_dir, exist_ok=True)
+        fn = os.path.join(dump_dir, f"{self.global_steps}.jsonl")
+        b, nt = batch.batch, batch.non_tensor_batch
+        P = b["prompts"].shape[1]
+        tok = self.tokenizer
+
+        def text(ids):
+            ids = [int(t) for t in ids]
+            return tok.decode(ids, skip_special_tokens=False) if tok is not None else ids
+
+        with open(fn, "a" if append else "w") as f:
+            for i in range(len(batch)):
+                pm, rm = b["attention_mask"][i, :P].bool(), b["attention_mask"][i, P:].bool()
+                row = {"input": text(b["prompts"][i][pm]), "output": text(b["responses"][i][rm]), "score": float(scores[i]), "step": int(self.global_steps),
+                       "data_source": str(nt["data_source"][i]) if "data_source" in nt else None}
+                rmeta = nt["reward_model"][i] if "reward_model" in nt else None
+                if isinstance(rmeta, dict) and "ground_truth" in rmeta:
+                    row["gts"] = rmeta["ground_truth"] if isinstance(rmeta["ground_truth"], (str, int, float, list)) else str(rmeta["ground_truth"])
+                for k, v in (extra or {}).items():
+                    if len(v) == len(batch) and isinstance(v[i], (str, int, float, bool)):
+                        row[k] = v[i]
+                f.write(json.dumps(row, ensure_ascii=False) + "\n")
+        return fn
+
     def _validate(self) -> dict:
         if self.val_dataloader is None or self.val_reward_fn is None:
             return {}
@@ -303,7 +333,8 @@ class PPOTrainer:
             tb = DataProto.from_single_dict(test_data)
             tb.non_tensor_batch["uid"] = np.array([str(uuid.uuid4()) for _ in range(len(tb))], dtype=object)
             tb = tb.repeat(n, interleave=True)
-            gen = tb.select(batch_keys=["input_ids", "attention_mask", "position_ids"], non_tensor_batch_keys=[])
+            gen = tb.select(batch_keys=["input_ids", "attention_mask", "position_ids"],
+                            non_tensor_batch_keys=[k for k in ("multi_modal_inputs",) if k in tb.non_tensor_batch])
             gen.meta_info = self._gen_meta(validate=True)
             gen, pad = _pad_to(gen, self.actor_rollout_wg.world_size)
             out = self.actor_rollout_wg.generate_sequences(gen)
@@ -312,6 +343,8 @@ class PPOTrainer:
             tb.batch["attention_mask"] = out.batch["attention_mask"]
             tb.batch["input_ids"] = out.batch["input_ids"]
             r, extra = compute_reward(tb, self.val_reward_fn)
+            if _g(self.config, "trainer.validation_data_dir", None):
+                self._dump_generations(tb, r.sum(-1).tolist(), extra, _g(self.config, "trainer.validation_data_dir"), append=len(scores) > 0)
             scores.extend(r.sum(-1).tolist())
             for k, v in extra.items():
                 extra_all[k].extend(v)
@@ -424,6 +457,8 @@ def _train_on_rollouts(self: PPOTrainer, batch: DataProto, timing_raw: dict, n: 
                 batch = batch.union(self.critic_wg.compute_values(batch))
         with marked_timer("adv", timing_raw):
             batch.batch["token_level_scores"] = reward_tensor
+            if _g(cfg, "trainer.rollout_data_dir", None):
+                self._dump_generations(batch, reward_tensor.sum(-1).tolist(), reward_extra, _g(cfg, "trainer.rollout_data_dir"))
             if reward_extra:
                 batch.non_tensor_batch.update({k: np.array(v, dtype=object) for k, v in reward_extra.items() if len(v) == len(batch)})
             if cfg.algorithm.get("use_kl_in_reward", False):

@@ -155,7 +155,7 @@ class Zero3Engine(FSDPEngine):
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)
         assert self.sp_size == 1, "zero3 mode does not combine with sequence/context parallelism"
-        assert not self._param_offload, "zero3 mode keeps its (already sharded) parameters on the device"
+        self._param_offload = False            # the (already sharded) parameters stay on the device: peers read them in place
         self.fsdp_size = 1                     # the flat store holds only local tensors; nothing in it is sliced further
         self._zero3_rows: dict[str, int] = {}
 
