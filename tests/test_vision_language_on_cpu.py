@@ -113,7 +113,7 @@ def test_config_round_trips_through_the_hf_layout(tmp_path):
     assert ModelConfig.from_hf_dict(nested).vision == cfg.vision
 
 
-def test_engine_trains_a_vision_language_model_on_image_prompts():
+def test_engine_trains_a_vision_language_model_on_image_prompts(tmp_path):
     """The sharded-DP engine with a vision-language config: log-probs of a batch whose prompts hold images equal a direct
     forward of the model per sequence, the vision tower receives gradients, and an optimizer step changes it."""
     import numpy as np
@@ -173,8 +173,20 @@ def test_engine_trains_a_vision_language_model_on_image_prompts():
     assert eng.model.visual.patch_embed.proj.weight.main_grad.abs().sum() > 0
     gn = eng.optimizer_step()
     assert gn > 0 and not torch.equal(before, eng.model.visual.merger.mlp[2].weight)
-    names = [k for k, _ in eng.get_per_tensor_param()[0]]
-    assert "visual.patch_embed.proj.weight" in names and "model.layers.0.self_attn.q_proj.weight" in names
+    exported = dict(eng.get_per_tensor_param()[0])
+    assert "visual.patch_embed.proj.weight" in exported and "model.layers.0.self_attn.q_proj.weight" in exported
+    # checkpoint → merger → the same tensors under Hugging Face names, and a config that parses back as vision-language
+    from verl_b200.model_merger.base_model_merger import ModelMergerConfig
+    from verl_b200.model_merger.fsdp_model_merger import FSDPModelMerger
+
+    ckpt = str(tmp_path / "ckpt")
+    eng.save_checkpoint(ckpt, global_step=1)
+    assert ModelConfig.from_pretrained(ckpt + "/huggingface").vision == eng.cfg.vision
+    sd = FSDPModelMerger(ModelMergerConfig(operation="merge", backend="fsdp", local_dir=ckpt, target_dir=str(tmp_path / "hf"),
+                                           hf_model_config_path=ckpt + "/huggingface"))._merge()
+    assert sd.keys() == exported.keys()
+    for k in exported:
+        assert sd[k].shape == exported[k].shape and torch.allclose(sd[k].float(), exported[k].float(), atol=1e-2, rtol=1e-2), k
 
 
 def test_image_patches_match_the_hf_processor():

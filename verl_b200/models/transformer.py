@@ -364,7 +364,17 @@ class DecoderLM(nn.Module):
 
 # ---------------------------------------------------------------------------------------------------- name mapping
 def native_to_hf_tensors(cfg: ModelConfig, params: dict) -> Iterator[tuple[str, torch.Tensor]]:
-    """Yield (hf_name, tensor) splitting the fused projections; tensors are views where possible."""
+    """Yield (hf_name, tensor) splitting the fused projections; tensors are views where possible. Parameters of a
+    vision-language model (``language_model.*`` + ``visual.*``) are accepted too: the tower's names pass through."""
+    if any(k.startswith("language_model.") for k in params.keys()):
+        yield from native_to_hf_tensors(cfg, {k[len("language_model."):]: v for k, v in params.items() if k.startswith("language_model.")})
+        v = cfg.vision or {}
+        for k, t in params.items():
+            if k.startswith("visual."):
+                if k == "visual.patch_embed.proj.weight" and v and t.dim() == 2:
+                    t = t.view(t.shape[0], v["in_channels"], v["temporal_patch_size"], v["patch_size"], v["patch_size"])
+                yield k, t
+        return
     if "embed_tokens" in params:
         yield "model.embed_tokens.weight", params["embed_tokens"]
     for i in range(cfg.num_hidden_layers):
