@@ -117,3 +117,74 @@ def test_zero3_single_rank_is_plain_engine():
     got, want = dict(eng.get_per_tensor_param()[0]), dict(ref.get_per_tensor_param()[0])
     for k in want:
         assert torch.allclose(got[k], want[k], atol=1e-6), k
+
+
+MOE_WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+from tests.test_engine_on_cpu import make_batch, loss_fn
+from tests.test_zero3_on_cpu import moe_config
+from verl_b200.workers.engine.base import EngineRegistry
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+eng = EngineRegistry.new("language_model", "fsdp", model_config=moe_config(), engine_config={"seed": 1, "expert_parallel_size": world,
+                         "zero3": os.environ["DENSE"] == "1"}, optimizer_config={"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, checkpoint_config={})
+eng.initialize()
+assert type(eng).__name__ == "Zero3Engine"
+gu = dict(eng.model.named_parameters())["layers.0.mlp.experts_gate_up"]
+assert gu.shape[0] == 4 // world and eng.model.layers[0].mlp.ep_group is not None
+data = make_batch(vocab=512).chunk(world)[rank]
+data.meta_info["micro_batch_size_per_gpu"] = 3
+lp = eng.infer_batch(data)["model_output"]["log_probs"]
+gns = []
+for _ in range(2):
+    eng.optimizer_zero_grad()
+    eng.forward_backward_batch(data, loss_fn)
+    gns.append(eng.optimizer_step())
+tensors = {k: v.detach().clone() for k, v in eng.get_per_tensor_param()[0]}
+torch.save({"lp": lp, "gns": gns, "tensors": tensors}, os.environ["OUT"] + f".{rank}")
+dist.barrier()
+"""
+
+
+def moe_config():
+    from verl_b200.models.config import ModelConfig
+
+    return ModelConfig(model_type="qwen3_moe", vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=16, attention_bias=False, qk_norm=True, num_experts=4, num_experts_per_tok=2,
+                       moe_intermediate_size=32, rope_theta=1e4, max_position_embeddings=512, torch_dtype="float32")
+
+
+@pytest.mark.parametrize("dense", [0, 1])
+def test_expert_parallel_ranks_match_single_rank(tmp_path, dense):
+    """Experts spread over two ranks (tokens reach them by all-to-all), alone and together with row-sharded projections:
+    log-probs, gradient norms and exported weights equal a single rank holding every expert."""
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "w.py"
+    script.write_text(MOE_WORKER)
+    out = tmp_path / "out.pt"
+    env = dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1", DENSE=str(dense))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", str(29796 + dense), str(script)], env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    eng = FSDPEngine(moe_config(), {"seed": 1}, OPT, {})
+    eng.initialize()
+    data = make_batch(vocab=512)
+    data.meta_info["micro_batch_size_per_gpu"] = 3
+    lp = eng.infer_batch(data)["model_output"]["log_probs"]
+    gns = []
+    for _ in range(2):
+        eng.optimizer_zero_grad()
+        eng.forward_backward_batch(data, loss_fn)
+        gns.append(eng.optimizer_step())
+    want = {k: v.detach().clone() for k, v in eng.get_per_tensor_param()[0]}
+    per = len(data) // 2
+    for rk in range(2):
+        res = torch.load(str(out) + f".{rk}")
+        assert torch.allclose(res["lp"], lp[rk * per:(rk + 1) * per], atol=2e-5)
+        for a, b in zip(res["gns"], gns):
+            assert abs(a - b) < 1e-4 * max(1.0, b), (res["gns"], gns)
+        assert res["tensors"].keys() == want.keys()
+        for k in want:
+            d = (res["tensors"][k] - want[k]).abs()
+            assert res["tensors"][k].shape == want[k].shape and d.max() < 2.5e-3 and d.mean() < 2e-5, (k, float(d.max()), float(d.mean()))

@@ -90,6 +90,7 @@ class FSDPEngineConfig(BaseConfig):
     optimizer_offload: bool = False
     offload_policy: bool = False
     reshard_after_forward: bool = False      # False = resident bf16 parameters (ZeRO-2); True = gather per layer (ZeRO-3)
+    expert_parallel_size: int = 1            # mixture-of-experts: 1 = every rank holds all experts; world size = experts spread over all ranks
     forward_prefetch: bool = False
     model_dtype: Optional[str] = None
     use_orig_params: bool = False

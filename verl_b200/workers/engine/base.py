@@ -193,7 +193,7 @@ class EngineRegistry:
             def opt(key):
                 return engine_config.get(key, False) if hasattr(engine_config, "get") else getattr(engine_config, key, False)
 
-            if opt("zero3") or opt("reshard_after_forward"):     # ZeRO-3: row-sharded weights gathered inside the GEMMs
+            if opt("zero3") or opt("reshard_after_forward") or int(opt("expert_parallel_size") or 1) > 1:     # ZeRO-3: row-sharded weights gathered inside the GEMMs
                 import verl_b200.workers.engine.fsdp.zero3  # noqa: F401
 
                 backend = "fsdp_zero3"

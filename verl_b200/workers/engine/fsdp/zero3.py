@@ -64,6 +64,17 @@ class _GatherCtx:
         return ent[0], ent[1]
 
 
+def _gather_dim0(t: torch.Tensor, group) -> torch.Tensor:
+    """All-gather along the first dimension (expert-parallel tensors ``[E/W, ...]`` → ``[E, ...]``)."""
+    W = dist.get_world_size(group)
+    full = torch.empty(t.shape[0] * W, *t.shape[1:], dtype=t.dtype, device=t.device)
+    if t.is_cuda:
+        dist.all_gather_into_tensor(full, t.contiguous(), group=group)
+    else:
+        dist.all_gather(list(full.chunk(W, 0)), t.contiguous(), group=group)
+    return full
+
+
 def _gather_rows(w_shard: torch.Tensor, sh: Zero3Shard) -> torch.Tensor:
     full = torch.empty(sh.rows * sh.world, sh.in_features, dtype=w_shard.dtype, device=w_shard.device)
     if w_shard.is_cuda:
@@ -148,8 +159,11 @@ def _is_sharded_name(name: str) -> bool:
 
 @EngineRegistry.register(model_type="language_model", backend=["fsdp_zero3"], device=["cuda", "cpu"])
 class Zero3Engine(FSDPEngine):
-    """Data-parallel engine with the decoder projections sharded by rows over ALL ranks (selected by ``zero3: true`` in the
-    engine config of the fsdp strategy). Memory per rank: ``(sharded/W + replicated) · (2 + 4 + 12)`` bytes for working copy,
+    """Data-parallel engine with the decoder projections sharded by rows over ALL ranks (selected by ``zero3: true`` /
+    ``reshard_after_forward: true`` in the engine config of the fsdp strategy), and/or the experts of a mixture-of-experts
+    model spread over all ranks (``expert_parallel_size`` = world size): rank ``r`` owns experts ``[r·E/W, (r+1)·E/W)``, tokens
+    travel to their experts by all-to-all (``verl_b200.ops.moe.moe_forward``). An expert's gradient is complete on its owner
+    (the all-to-all backward brings every rank's contribution), so like the row shards it is only scaled by ``1/W``. Memory per rank: ``(sharded/W + replicated) · (2 + 4 + 12)`` bytes for working copy,
     fp32 gradients and AdamW state, against ``total · (2 + 4) + total/W · 12`` of the replicated-working-copy engine."""
 
     def __init__(self, *args, **kwargs):
@@ -157,6 +171,10 @@ class Zero3Engine(FSDPEngine):
         assert self.sp_size == 1, "zero3 mode does not combine with sequence/context parallelism"
         self._param_offload = False            # the (already sharded) parameters stay on the device: peers read them in place
         self.fsdp_size = 1                     # the flat store holds only local tensors; nothing in it is sliced further
+        ep = int(cfg_get(self.engine_config, "expert_parallel_size", 1) or 1)
+        assert ep in (1, self.world), "expert_parallel_size must be 1 or the world size"
+        self._ep = ep > 1
+        self._shard_dense = bool(cfg_get(self.engine_config, "zero3", False) or cfg_get(self.engine_config, "reshard_after_forward", False))
         self._zero3_rows: dict[str, int] = {}
 
     def _build_groups(self):
@@ -177,7 +195,14 @@ class Zero3Engine(FSDPEngine):
         sharded = []
         if W > 1:
             for n, p in named.items():
-                if _is_sharded_name(n) and p.dim() == 2 and p.shape[0] % W == 0:
+                if self._ep and n.rsplit(".", 1)[-1] in ("experts_gate_up", "experts_down"):
+                    assert p.shape[0] % W == 0, f"{p.shape[0]} experts do not divide over {W} ranks"
+                    e_local = p.shape[0] // W
+                    p._ep_full_shape = tuple(p.shape)
+                    p.data = p.data[r * e_local:(r + 1) * e_local].clone()
+                    self._zero3_rows[n] = e_local
+                    continue
+                if self._shard_dense and _is_sharded_name(n) and p.dim() == 2 and p.shape[0] % W == 0:
                     rows = p.shape[0] // W
                     full_shape = tuple(p.shape)
                     p.data = p.data[r * rows:(r + 1) * rows].clone()
@@ -205,8 +230,12 @@ class Zero3Engine(FSDPEngine):
         if symm is not None and sharded:
             full = [named[n]._zero3_full_shape for n in sharded]
             gctx = _GatherCtx(max(f[0] * f[1] for f in full), self.device)
+        if self._ep:
+            for layer in self.model.layers:
+                if hasattr(layer.mlp, "ep_group"):
+                    layer.mlp.ep_group = self.shard_group
         for n, p, off in zip(s.names, s.params, s.offsets):
-            if n in self._zero3_rows:
+            if n in self._zero3_rows and p.dim() == 2:
                 p._zero3 = Zero3Shard(self.shard_group, self._zero3_rows[n], p.shape[1], symm, off * 2, gctx)
         torch.cuda.empty_cache() if s.flat.is_cuda else None
 
@@ -257,7 +286,10 @@ class Zero3Engine(FSDPEngine):
         """(native name, full tensor): sharded weights are all-gathered one at a time (a collective — every rank iterates)."""
         for n, p in self.model.named_parameters():
             sh = getattr(p, "_zero3", None)
-            yield n, (p.data if sh is None else _gather_rows(p.data, sh))
+            if sh is None and getattr(p, "_ep_full_shape", None) is not None:
+                yield n, _gather_dim0(p.data, self.shard_group)
+            else:
+                yield n, (p.data if sh is None else _gather_rows(p.data, sh))
 
     def hf_named_tensors_for_save(self):
         from verl_b200.models.transformer import native_to_hf_tensors
@@ -271,8 +303,11 @@ class Zero3Engine(FSDPEngine):
             def __getitem__(self, k):
                 p = super().__getitem__(k)
                 sh = getattr(p, "_zero3", None)
+                if sh is None and getattr(p, "_ep_full_shape", None) is not None:
+                    return _gather_dim0(p.data, group)
                 return p.data if sh is None else _gather_rows(p.data, sh)
 
+        group = self.shard_group
         return native_to_hf_tensors(self.cfg, _Lazy(dict(self.model.named_parameters())))
 
     def get_per_tensor_param(self, **kwargs):
