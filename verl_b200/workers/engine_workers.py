@@ -278,6 +278,8 @@ class ActorRolloutRefWorker(Worker):
         self._rollout_tp = int(cfg_get(ro, "tensor_model_parallel_size", 1) or 1)
         tp_group = tp_ctx = None
         if self._rollout_tp > 1:
+            if hasattr(model, "visual"):
+                raise NotImplementedError("tensor-parallel rollout replicas do not serve vision-language models yet; use rollout.tensor_model_parallel_size=1")
             model, tp_group, tp_ctx = self._build_rollout_tp(model, ro)
         self.rollout = InferenceEngine(
             model, max_num_seqs=int(cfg_get(ro, "max_num_seqs", 256)), max_model_len=int(max_len),
