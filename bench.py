@@ -170,7 +170,7 @@ def run_native(args):
             "impl": "native",
             "config": {"model": args.model, "global_batch": f"{args.prompts_per_gpu * world} prompts x n={args.n}",
                        "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + response <= {args.response_length}",
-                       "parallelism": f"dp{world} (ZeRO-2 sharded optimizer, resident bf16 params), rollout tp{args.rollout_tp} x {world // args.rollout_tp} replicas colocated",
+                       "parallelism": f"dp{world} ({'ZeRO-3 row-sharded projections gathered inside the GEMMs' if args.zero3 else 'ZeRO-2 sharded optimizer, resident bf16 params'}), rollout tp{args.rollout_tp} x {world // args.rollout_tp} replicas colocated",
                        "ppo_mini_batch_prompts": args.mini_prompts_per_gpu * world, "token_budget_per_micro_batch": args.token_budget,
                        "gradient_checkpointing": bool(args.grad_ckpt), "ref_param_offload": bool(args.ref_offload), "prefix_sharing": bool(args.prefix_sharing), "rollout_quantization": args.rollout_quant or None, "zero3": bool(args.zero3), "loss": "grpo clip 0.2 + low_var_kl 1e-3, AdamW lr 1e-6",
                        "l2_policy": "inputs larger than L2: each step streams >15 GB of weights and fresh activations"},
