@@ -305,6 +305,65 @@ def test_zero3_engine_fused_weight_gather(tmp_path, world):
     assert r.returncode == 0 and "ZERO3_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-6000:]
 
 
+EP_WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("cpu:gloo,cuda:nccl")
+from verl_b200.ops import _ext
+from tests.test_engine_on_cpu import make_batch, loss_fn
+from verl_b200.models.config import ModelConfig
+from verl_b200.workers.engine.base import EngineRegistry
+cfg = ModelConfig(model_type="qwen3_moe", vocab_size=4096, hidden_size=512, intermediate_size=1536, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, head_dim=128, attention_bias=False, qk_norm=True, num_experts=4, num_experts_per_tok=2,
+                  moe_intermediate_size=256, rope_theta=1e4, max_position_embeddings=4096)
+opt = {"lr": 1e-3, "clip_grad": 1.0, "weight_decay": 0.01}
+res = {}
+for mode in ("ep", "replicated"):
+    ecfg = {"seed": 1, "use_symmetric_memory": False}
+    if mode == "ep":
+        ecfg.update({"expert_parallel_size": world, "zero3": True, "use_symmetric_memory": True})
+    eng = EngineRegistry.new("language_model", "fsdp", model_config=cfg, engine_config=ecfg, optimizer_config=opt, checkpoint_config={})
+    eng.initialize()
+    if mode == "ep":
+        assert type(eng).__name__ == "Zero3Engine" and dict(eng.model.named_parameters())["layers.0.mlp.experts_down"].shape[0] == 4 // world
+    data = make_batch(bs=8, P=70, R=90, vocab=4096).chunk(world)[rank]
+    data.meta_info["micro_batch_size_per_gpu"] = 2
+    lp = eng.infer_batch(data)["model_output"]["log_probs"]
+    eng.optimizer_zero_grad()
+    eng.forward_backward_batch(data, loss_fn)
+    gn = eng.optimizer_step()
+    torch.cuda.synchronize()
+    _ext.check_status(mode)
+    res[mode] = (lp.clone(), gn, {k: v.detach().float().clone() for k, v in eng.get_per_tensor_param()[0]})
+    del eng
+a, b = res["ep"], res["replicated"]
+d_lp = (a[0] - b[0]).abs().max().item()
+print("EP_DIAG", rank, d_lp, a[1], b[1], flush=True)
+assert d_lp < 0.08 and abs(a[1] - b[1]) < 0.05 * max(1.0, b[1]), (d_lp, a[1], b[1])
+assert a[2].keys() == b[2].keys()
+for k in b[2]:
+    assert a[2][k].shape == b[2][k].shape and (a[2][k] - b[2][k]).abs().mean().item() < 2e-3, k
+dist.barrier()
+if rank == 0:
+    print("EP_OK", d_lp, a[1], b[1])
+"""
+
+
+@pytest.mark.parametrize("world", [2])
+def test_expert_parallel_engine(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "ep.py"
+    script.write_text(EP_WORKER)
+    env = dict(os.environ, REPO=repo, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                        "--master-port", "29691", str(script)], env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "EP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-6000:]
+
+
 RTP_WORKER = r'''
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["REPO"])
