@@ -334,3 +334,50 @@ def test_grpo_step_on_image_prompts_end_to_end(tmp_path, mode):
     # rollout log-probs of the sampled tokens equal the trainer's recomputation
     d = ((b.batch["rollout_log_probs"] - b.batch["old_log_probs"]).abs() * b.batch["response_mask"]).max()
     assert d < 1e-3, d
+
+
+def test_qwen2_5_vl_tower_and_logits_match_hf():
+    """The windowed tower variant (RMSNorm, gated MLP, window attention with full-attention blocks) against Hugging Face
+    Qwen2.5-VL: tower output for images whose grids are ragged against the window, and the logits of a sequence."""
+    try:
+        from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration
+    except ImportError:
+        pytest.skip("this transformers build has no Qwen2.5-VL")
+    torch.manual_seed(0)
+    hf_cfg = Qwen2_5_VLConfig(
+        text_config=dict(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         max_position_embeddings=512, rope_theta=10000.0, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]},
+                         tie_word_embeddings=False),
+        vision_config=dict(depth=3, hidden_size=32, intermediate_size=48, num_heads=2, in_channels=3, patch_size=4, temporal_patch_size=2,
+                           spatial_merge_size=2, window_size=16, out_hidden_size=64, fullatt_block_indexes=[1]),
+        image_token_id=500, video_token_id=501, vision_start_token_id=502, vision_end_token_id=503)
+    hf = Qwen2_5_VLForConditionalGeneration(hf_cfg).float().eval()
+    cfg = ModelConfig.from_hf_dict(hf_cfg.to_dict())
+    assert cfg.vision["variant"] == "qwen2_5_vl" and cfg.vision["embed_dim"] == 32 and cfg.vision["hidden_size"] == 64 and cfg.hidden_size == 64
+    cfg = cfg.replace(torch_dtype="float32", rms_norm_eps=hf_cfg.text_config.rms_norm_eps)
+    ours = VisionLanguageModel(cfg, dtype=torch.float32, device=torch.device("cpu"))
+    ours.load_hf_state_dict(hf.state_dict())
+    ours.eval()
+    g = torch.Generator().manual_seed(1)
+    grid = torch.tensor([[1, 6, 10], [1, 4, 4], [1, 2, 6]])          # window = 2×2 merge groups: ragged, exact and narrower grids
+    pixels = torch.randn(int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum()), 96, generator=g)
+    with torch.no_grad():
+        want = hf.model.visual(pixels, grid_thw=grid)
+        want = want.pooler_output if hasattr(want, "pooler_output") else want
+        got = ours.visual(pixels, grid)
+    if isinstance(want, (tuple, list)):
+        want = torch.cat(list(want), 0)
+    assert got.shape == want.shape == (15 + 4 + 3, 64)
+    assert torch.allclose(got, want, atol=1e-5, rtol=1e-4), (got - want).abs().max()
+    text = lambda n: torch.randint(1, 400, (n,), generator=g).tolist()
+    ids = torch.tensor(text(3) + [502] + [500] * 15 + [503] + text(4) + [502] + [500] * 4 + [503] + [502] + [500] * 3 + [503] + text(5))
+    pos3, _ = get_rope_index(ids, grid, ours.vcfg)
+    with torch.no_grad():
+        want = hf(input_ids=ids[None], pixel_values=pixels, image_grid_thw=grid, attention_mask=torch.ones_like(ids)[None],
+                  position_ids=pos3[:, None].contiguous()).logits[0]
+        pb = PackedBatch(ids, torch.arange(len(ids), dtype=torch.int32), torch.tensor([0, len(ids)], dtype=torch.int32))
+        got = ours(pb, pixel_values=pixels, image_grid_thw=grid, mrope_positions=pos3, return_logits=True)["logits"]
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), (got - want).abs().max()
+    # config round trip in the newer layout
+    back = ModelConfig.from_hf_dict(cfg.to_hf_dict())
+    assert back.vision == cfg.vision

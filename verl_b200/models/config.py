@@ -86,7 +86,7 @@ class ModelConfig:
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
         mt = d.get("model_type", "llama")
         vision = None
-        if mt in ("qwen2_vl",):
+        if mt in ("qwen2_vl", "qwen2_5_vl"):
             # vision-language checkpoint: decoder fields sit in text_config (newer layout) or at the top level (older one)
             import dataclasses as _dc
 
@@ -95,6 +95,7 @@ class ModelConfig:
             text = d.get("text_config") or {}
             vision = _dc.asdict(VisionConfig.from_hf_dict(d, text or None))
             vision["mrope_section"] = list(vision["mrope_section"])
+            vision["fullatt_block_indexes"] = list(vision["fullatt_block_indexes"])
             d = {**{k: v for k, v in d.items() if k not in ("text_config", "vision_config")}, **text, "attention_bias": True}
             mt = "qwen2"
         known = dict(
@@ -156,9 +157,18 @@ class ModelConfig:
             d["num_labels"] = 1
         if self.vision:
             v = dict(self.vision)
-            d.update(model_type="qwen2_vl", architectures=["Qwen2VLForConditionalGeneration"], image_token_id=v.pop("image_token_id"),
-                     video_token_id=v.pop("video_token_id"), vision_start_token_id=v.pop("vision_start_token_id"),
-                     rope_scaling={"type": "mrope", "mrope_section": list(v.pop("mrope_section"))}, vision_config=v)
+            new = v.pop("variant", "qwen2_vl") == "qwen2_5_vl"
+            d.update(model_type="qwen2_5_vl" if new else "qwen2_vl",
+                     architectures=["Qwen2_5_VLForConditionalGeneration" if new else "Qwen2VLForConditionalGeneration"],
+                     image_token_id=v.pop("image_token_id"), video_token_id=v.pop("video_token_id"), vision_start_token_id=v.pop("vision_start_token_id"),
+                     rope_scaling={"type": "mrope", "mrope_section": list(v.pop("mrope_section"))})
+            if new:       # the newer layout names the tower width hidden_size and the merger output out_hidden_size
+                v["out_hidden_size"], v["hidden_size"] = v.pop("hidden_size"), v.pop("embed_dim")
+                v.pop("mlp_ratio", None)
+            else:
+                for k in ("intermediate_size", "window_size", "fullatt_block_indexes"):
+                    v.pop(k, None)
+            d["vision_config"] = v
         return d
 
     def save_pretrained(self, path: str):

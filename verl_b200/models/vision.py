@@ -1,4 +1,4 @@
-"""Vision-language family (Qwen2-VL architecture): a ViT tower whose merged patch embeddings replace the image placeholder
+"""Vision-language family (Qwen2-VL and Qwen2.5-VL architectures): a ViT tower whose merged patch embeddings replace the image placeholder
 tokens of a decoder LM that runs multimodal rotary embedding (M-RoPE: temporal / height / width position streams).
 
 * :class:`VisionTower` — patch embedding (the 3-D convolution over ``[C, T_p, P, P]`` written as one linear layer), pre-norm
@@ -10,8 +10,8 @@ tokens of a decoder LM that runs multimodal rotary embedding (M-RoPE: temporal /
 * :class:`VisionLanguageModel` — tower + :class:`~verl_b200.models.transformer.DecoderLM` on packed batches.
 
 Reference: the Qwen2-VL patches of the reference (``verl/models/transformers/qwen2_vl.py:36-250``: rope index, Ulysses-aware
-attention, embedding merge) and ``verl/utils/dataset/vision_utils.py`` for the inputs. Qwen2.5-VL's window attention and
-video inputs with more than one temporal patch per frame pair are not implemented.
+attention, embedding merge) and ``verl/utils/dataset/vision_utils.py`` for the inputs. The Qwen2.5-VL variant swaps in
+RMSNorm, a gated SiLU MLP and window attention (:meth:`VisionTower._window_index`). Video inputs are not implemented.
 """
 
 from __future__ import annotations
@@ -44,6 +44,11 @@ class VisionConfig:
     video_token_id: int = 151656
     vision_start_token_id: int = 151652
     mrope_section: tuple = (16, 24, 24)
+    # Qwen2.5-VL tower: RMSNorm + gated SiLU MLP, attention inside windows of window_size pixels except in the listed blocks
+    variant: str = "qwen2_vl"               # "qwen2_vl" | "qwen2_5_vl"
+    intermediate_size: int = 0
+    window_size: int = 0
+    fullatt_block_indexes: tuple = ()
 
     @property
     def patch_dim(self) -> int:
@@ -53,6 +58,14 @@ class VisionConfig:
     def from_hf_dict(cls, d: dict, text: Optional[dict] = None) -> "VisionConfig":
         v = d.get("vision_config", {})
         rope = (text or d).get("rope_scaling") or (text or d).get("rope_parameters") or {}
+        if d.get("model_type") == "qwen2_5_vl":
+            return cls(depth=v.get("depth", 32), embed_dim=v.get("hidden_size", 1280), num_heads=v.get("num_heads", 16), in_channels=v.get("in_channels", 3),
+                       patch_size=v.get("patch_size", 14), temporal_patch_size=v.get("temporal_patch_size", 2),
+                       spatial_merge_size=v.get("spatial_merge_size", 2), hidden_size=v.get("out_hidden_size", (text or d).get("hidden_size", 3584)),
+                       image_token_id=d.get("image_token_id", 151655), video_token_id=d.get("video_token_id", 151656),
+                       vision_start_token_id=d.get("vision_start_token_id", 151652), mrope_section=tuple(rope.get("mrope_section", (16, 24, 24))),
+                       variant="qwen2_5_vl", intermediate_size=v.get("intermediate_size", 3420), window_size=v.get("window_size", 112),
+                       fullatt_block_indexes=tuple(v.get("fullatt_block_indexes", (7, 15, 23, 31))))
         return cls(depth=v.get("depth", 32), embed_dim=v.get("embed_dim", 1280), num_heads=v.get("num_heads", 16), mlp_ratio=v.get("mlp_ratio", 4.0),
                    in_channels=v.get("in_channels", v.get("in_chans", 3)), patch_size=v.get("patch_size", 14),
                    temporal_patch_size=v.get("temporal_patch_size", 2), spatial_merge_size=v.get("spatial_merge_size", 2),
@@ -71,11 +84,17 @@ class _VisionBlock(nn.Module):
         super().__init__()
         E, Hm = cfg.embed_dim, int(cfg.embed_dim * cfg.mlp_ratio)
         kw = dict(dtype=dtype, device=device)
-        self.norm1, self.norm2 = nn.LayerNorm(E, eps=1e-6, **kw), nn.LayerNorm(E, eps=1e-6, **kw)
+        self.gated = cfg.variant == "qwen2_5_vl"
         self.attn = nn.Module()
         self.attn.qkv, self.attn.proj = nn.Linear(E, 3 * E, **kw), nn.Linear(E, E, **kw)
         self.mlp = nn.Module()
-        self.mlp.fc1, self.mlp.fc2 = nn.Linear(E, Hm, **kw), nn.Linear(Hm, E, **kw)
+        if self.gated:
+            I = cfg.intermediate_size
+            self.norm1, self.norm2 = nn.RMSNorm(E, eps=1e-6, **kw), nn.RMSNorm(E, eps=1e-6, **kw)
+            self.mlp.gate_proj, self.mlp.up_proj, self.mlp.down_proj = nn.Linear(E, I, **kw), nn.Linear(E, I, **kw), nn.Linear(I, E, **kw)
+        else:
+            self.norm1, self.norm2 = nn.LayerNorm(E, eps=1e-6, **kw), nn.LayerNorm(E, eps=1e-6, **kw)
+            self.mlp.fc1, self.mlp.fc2 = nn.Linear(E, Hm, **kw), nn.Linear(Hm, E, **kw)
         self.num_heads = cfg.num_heads
 
     def forward(self, x, cos, sin, seg_lens):
@@ -90,7 +109,10 @@ class _VisionBlock(nn.Module):
             outs.append(F.scaled_dot_product_attention(qs, ks, vs).squeeze(0).transpose(0, 1).reshape(n, E))
             s += n
         x = x + self.attn.proj(torch.cat(outs, 0))
-        h = self.mlp.fc1(self.norm2(x))
+        y = self.norm2(x)
+        if self.gated:
+            return x + self.mlp.down_proj(F.silu(self.mlp.gate_proj(y)) * self.mlp.up_proj(y))
+        h = self.mlp.fc1(y)
         return x + self.mlp.fc2(h * torch.sigmoid(1.702 * h))       # QuickGELU
 
 
@@ -104,7 +126,7 @@ class VisionTower(nn.Module):
         self.patch_embed.proj = nn.Linear(cfg.patch_dim, E, bias=False, **kw)
         self.blocks = nn.ModuleList([_VisionBlock(cfg, dtype, device) for _ in range(cfg.depth)])
         self.merger = nn.Module()
-        self.merger.ln_q = nn.LayerNorm(E, eps=1e-6, **kw)
+        self.merger.ln_q = nn.RMSNorm(E, eps=1e-6, **kw) if cfg.variant == "qwen2_5_vl" else nn.LayerNorm(E, eps=1e-6, **kw)
         self.merger.mlp = nn.Sequential(nn.Linear(E * m2, E * m2, **kw), nn.GELU(), nn.Linear(E * m2, cfg.hidden_size, **kw))
         g = torch.Generator(device="cpu").manual_seed(seed + 7919)
         with torch.no_grad():
@@ -133,10 +155,47 @@ class VisionTower(nn.Module):
         emb = torch.cat([ang, ang], -1)
         cos, sin = emb.cos()[:, None, :], emb.sin()[:, None, :]
         seg = [int(h * w) for t, h, w in grid_thw.tolist() for _ in range(int(t))]
-        for blk in self.blocks:
-            x = blk(x, cos, sin, seg)
         m2 = cfg.spatial_merge_size ** 2
-        return self.merger.mlp(self.merger.ln_q(x).reshape(-1, cfg.embed_dim * m2))
+        if cfg.variant != "qwen2_5_vl":
+            for blk in self.blocks:
+                x = blk(x, cos, sin, seg)
+            return self.merger.mlp(self.merger.ln_q(x).reshape(-1, cfg.embed_dim * m2))
+        # windowed variant: merge groups are reordered window by window once; most blocks attend inside a window, the
+        # listed ones inside the whole frame (in the window order, which attention does not care about); the merger's
+        # output goes back to the original order
+        win_index, win_seg = self._window_index(grid_thw.cpu())
+        win_index = win_index.to(x.device)
+
+        def reorder(t):
+            return t.reshape(-1, m2, *t.shape[1:]).index_select(0, win_index).reshape(t.shape)
+
+        x, cos, sin = reorder(x), reorder(cos), reorder(sin)
+        for i, blk in enumerate(self.blocks):
+            x = blk(x, cos, sin, seg if i in cfg.fullatt_block_indexes else win_seg)
+        out = self.merger.mlp(self.merger.ln_q(x).reshape(-1, cfg.embed_dim * m2))
+        return out.index_select(0, torch.argsort(win_index))
+
+    def _window_index(self, grid_thw: torch.Tensor):
+        """Order of the merge groups window by window (windows of ``window_size`` pixels, ragged at the right / bottom edge)
+        and the number of PATCHES in each window, in that order."""
+        cfg = self.cfg
+        m = cfg.spatial_merge_size
+        W = cfg.window_size // m // cfg.patch_size
+        index, seg, base = [], [], 0
+        for t, h, w in grid_thw.tolist():
+            gh, gw = h // m, w // m
+            idx = torch.arange(t * gh * gw).reshape(t, gh, gw)
+            ph, pw = (W - gh % W) % W, (W - gw % W) % W
+            idx = F.pad(idx, (0, pw, 0, ph), value=-1)
+            nh, nw = (gh + ph) // W, (gw + pw) // W
+            idx = idx.reshape(t, nh, W, nw, W).permute(0, 1, 3, 2, 4).reshape(t * nh * nw, W * W)
+            for row in idx:
+                keep = row[row >= 0]
+                if keep.numel():
+                    index.append(keep + base)
+                    seg.append(int(keep.numel()) * m * m)
+            base += t * gh * gw
+        return torch.cat(index), seg
 
 
 def get_rope_index(input_ids: torch.Tensor, image_grid_thw: Optional[torch.Tensor], cfg: VisionConfig,
