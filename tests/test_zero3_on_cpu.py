@@ -188,3 +188,39 @@ def test_expert_parallel_ranks_match_single_rank(tmp_path, dense):
         for k in want:
             d = (res["tensors"][k] - want[k]).abs()
             assert res["tensors"][k].shape == want[k].shape and d.max() < 2.5e-3 and d.mean() < 2e-5, (k, float(d.max()), float(d.mean()))
+
+
+VL_WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+from verl_b200.models.config import PRESETS
+from verl_b200.workers.engine.base import EngineRegistry
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+eng = EngineRegistry.new("language_model", "fsdp", model_config=PRESETS["tiny-qwen2-vl"], engine_config={"seed": 1, "zero3": True},
+                         optimizer_config={"lr": 1e-3}, checkpoint_config={})
+eng.initialize()
+named = dict(eng.model.named_parameters())
+assert named["language_model.layers.0.mlp.gate_up_proj"].shape[0] == 1024 // world and named["visual.blocks.0.attn.qkv.weight"].shape[0] == 96
+tensors = {k: v.detach().clone() for k, v in eng.get_per_tensor_param()[0]}
+torch.save(tensors, os.environ["OUT"] + f".{rank}")
+dist.barrier()
+"""
+
+
+def test_zero3_shards_the_decoder_of_a_vision_language_model(tmp_path):
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "w.py"
+    script.write_text(VL_WORKER)
+    out = tmp_path / "out.pt"
+    env = dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29799", str(script)], env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    eng = FSDPEngine(PRESETS["tiny-qwen2-vl"], {"seed": 1}, OPT, {})
+    eng.initialize()
+    want = dict(eng.get_per_tensor_param()[0])
+    got = torch.load(str(out) + ".1")
+    assert got.keys() == want.keys() and "visual.merger.mlp.2.weight" in got
+    for k in want:
+        assert got[k].shape == want[k].shape and torch.equal(got[k], want[k]), k

@@ -367,10 +367,27 @@ def native_to_hf_tensors(cfg: ModelConfig, params: dict) -> Iterator[tuple[str, 
     """Yield (hf_name, tensor) splitting the fused projections; tensors are views where possible. Parameters of a
     vision-language model (``language_model.*`` + ``visual.*``) are accepted too: the tower's names pass through."""
     if any(k.startswith("language_model.") for k in params.keys()):
-        yield from native_to_hf_tensors(cfg, {k[len("language_model."):]: v for k, v in params.items() if k.startswith("language_model.")})
+        class _Sub:
+            """The decoder's entries under their own names; values are read through ``params[...]`` one at a time (a mapping
+            that gathers sharded tensors on access keeps doing so)."""
+
+            def __contains__(self, k):
+                return "language_model." + k in params
+
+            def __getitem__(self, k):
+                return params["language_model." + k]
+
+            def get(self, k, default=None):
+                return self[k] if k in self else default
+
+            def keys(self):
+                return [k[len("language_model."):] for k in params.keys() if k.startswith("language_model.")]
+
+        yield from native_to_hf_tensors(cfg, _Sub())
         v = cfg.vision or {}
-        for k, t in params.items():
+        for k in list(params.keys()):
             if k.startswith("visual."):
+                t = params[k]
                 if k == "visual.patch_embed.proj.weight" and v and t.dim() == 2:
                     t = t.view(t.shape[0], v["in_channels"], v["temporal_patch_size"], v["patch_size"], v["patch_size"])
                 yield k, t

@@ -130,9 +130,11 @@ class VisionTower(nn.Module):
         self.merger.mlp = nn.Sequential(nn.Linear(E * m2, E * m2, **kw), nn.GELU(), nn.Linear(E * m2, cfg.hidden_size, **kw))
         g = torch.Generator(device="cpu").manual_seed(seed + 7919)
         with torch.no_grad():
-            for p in self.parameters():
+            for n, p in self.named_parameters():      # seeded, identical in every process: matrices N(0, 0.02²), biases 0, norms 1
                 if p.dim() >= 2:
                     p.copy_((torch.randn(p.shape, generator=g) * 0.02).to(p.dtype))
+                elif n.endswith(".bias"):
+                    p.zero_()
 
     def _rot_pos(self, grid_thw: torch.Tensor) -> torch.Tensor:
         """(h, w) index of every patch in the processor's order: patches of one merge window are adjacent."""
@@ -319,6 +321,13 @@ class VisionLanguageModel(nn.Module):
             if n == "patch_embed.proj.weight":
                 p = p.view(P.embed_dim, P.in_channels, P.temporal_patch_size, P.patch_size, P.patch_size)
             yield "visual." + n, p
+
+    @torch.no_grad()
+    def load_hf_stream(self, named_tensors) -> int:
+        """Consume (hf_name, tensor) pairs (weight hand-off from a sharded trainer to a rollout copy)."""
+        sd = {k: v for k, v in named_tensors}
+        self.load_hf_state_dict(sd, strict=False)
+        return len(sd)
 
     def load_hf_state_dict(self, sd: dict, strict: bool = True):
         sd = {(k[len("model."):] if k.startswith("model.visual.") else k): v for k, v in sd.items()}      # both checkpoint generations

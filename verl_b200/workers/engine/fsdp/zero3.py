@@ -154,7 +154,7 @@ __all__ += ["Zero3Engine"]
 
 
 def _is_sharded_name(name: str) -> bool:
-    return name.startswith("layers.") and name.rsplit(".", 1)[-1] in SHARDED_LEAVES
+    return name.startswith(("layers.", "language_model.layers.")) and name.rsplit(".", 1)[-1] in SHARDED_LEAVES
 
 
 @EngineRegistry.register(model_type="language_model", backend=["fsdp_zero3"], device=["cuda", "cpu"])

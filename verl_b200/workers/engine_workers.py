@@ -271,7 +271,12 @@ class ActorRolloutRefWorker(Worker):
             # update_weights() from the engine's per-tensor export
             from verl_b200.models.transformer import DecoderLM
 
-            model = DecoderLM(src.engine.cfg, dtype=src.engine.dtype, device=src.engine.device, init=False)
+            if src.engine.cfg.vision:
+                from verl_b200.models.vision import VisionLanguageModel
+
+                model = VisionLanguageModel(src.engine.cfg, dtype=src.engine.dtype, device=src.engine.device, init=False)
+            else:
+                model = DecoderLM(src.engine.cfg, dtype=src.engine.dtype, device=src.engine.device, init=False)
             model.load_hf_stream(src.engine.get_per_tensor_param()[0])
             self._rollout_owns_model = True
         max_len = cfg_get(ro, "max_model_len", None) or (int(cfg_get(ro, "prompt_length", 512)) + int(cfg_get(ro, "response_length", 512)))
