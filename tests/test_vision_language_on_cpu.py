@@ -381,3 +381,33 @@ def test_qwen2_5_vl_tower_and_logits_match_hf():
     # config round trip in the newer layout
     back = ModelConfig.from_hf_dict(cfg.to_hf_dict())
     assert back.vision == cfg.vision
+
+
+def test_sft_dataset_with_images():
+    """Multi-turn SFT rows with images: ``<image>`` marks become placeholder runs of the image's size, only assistant tokens are
+    targets, positions follow the image grid."""
+    import numpy as np
+    from PIL import Image
+
+    from verl_b200.utils.dataset.sft_dataset import MultiTurnSFTDataset
+    from verl_b200.utils.tokenizer import ByteChatTokenizer
+
+    img = Image.fromarray(np.random.default_rng(0).integers(0, 255, (16, 24, 3), dtype=np.uint8))
+    rows = [{"messages": [{"role": "user", "content": "describe <image> please"}, {"role": "assistant", "content": "a cat"}], "tools": None, "images": [img]},
+            {"messages": [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "hello"}], "tools": None, "images": None}]
+    vision = dict(patch_size=4, temporal_patch_size=2, spatial_merge_size=2, image_token_id=2040, vision_start_token_id=2042, mrope_section=[4, 6, 6])
+    ds = MultiTurnSFTDataset(tokenizer=ByteChatTokenizer(), max_length=96, rows=rows, vision=vision, image_min_pixels=64, image_max_pixels=1024)
+    a, b = ds[0], ds[1]
+    g = a["multi_modal_inputs"]["image_grid_thw"]
+    n = int(g[0, 1] * g[0, 2]) // 4
+    ids = a["input_ids"][a["attention_mask"].bool()]
+    run = (ids == 2040).nonzero().flatten()
+    assert len(run) == n and int(run[-1] - run[0]) == n - 1 and int(ids[run[0] - 1]) == 2042 and int(ids[run[-1] + 1]) == 2043
+    assert a["multi_modal_inputs"]["pixel_values"].shape == (int(g[0, 1] * g[0, 2]), 96)
+    assert int(a["loss_mask"][run[0] - 1:run[-1] + 1].sum()) == 0 and int(a["loss_mask"].sum()) > 0      # image tokens are never targets
+    assert a["position_ids"].shape == (4, 96) and b["multi_modal_inputs"] == {}
+    live = b["attention_mask"].bool()
+    assert torch.equal(b["position_ids"][0][live], b["position_ids"][3][live])
+    # the text-only dataset is unchanged by the new arguments
+    plain = MultiTurnSFTDataset(tokenizer=ByteChatTokenizer(), max_length=96, rows=rows[1:])
+    assert torch.equal(plain[0]["input_ids"], b["input_ids"]) and plain[0]["position_ids"].dim() == 1

@@ -32,12 +32,18 @@ def _ids(tok, messages, **kw):
 
 class MultiTurnSFTDataset(Dataset):
     def __init__(self, files=None, tokenizer=None, max_length: int = 1024, messages_key: str = "messages", tools_key: str = "tools",
-                 truncation: str = "right", rows: Optional[list] = None):
+                 truncation: str = "right", rows: Optional[list] = None, vision: Optional[dict] = None, images_key: str = "images",
+                 image_min_pixels: Optional[int] = None, image_max_pixels: Optional[int] = None):
+        """``vision`` (fields of ``verl_b200.models.vision.VisionConfig``) switches image support on: a row's ``images`` are cut
+        into patches, every ``<image>`` mark (or image placeholder token written by the chat template) is expanded to the
+        image's merged patches, and the item carries ``multi_modal_inputs`` and 4-stream ``position_ids``."""
         assert truncation in ("right", "left", "error")
         self.tok, self.max_length, self.truncation = tokenizer, max_length, truncation
+        self.vision, self.image_pixels = (dict(vision) if vision else None), (image_min_pixels, image_max_pixels)
         if rows is None:
             df = _read(files)
-            rows = [{"messages": list(r[messages_key]), "tools": (list(r[tools_key]) if tools_key in df.columns and r[tools_key] is not None else None)}
+            rows = [{"messages": list(r[messages_key]), "tools": (list(r[tools_key]) if tools_key in df.columns and r[tools_key] is not None else None),
+                     "images": (list(r[images_key]) if images_key in df.columns and r[images_key] is not None else None)}
                     for _, r in df.iterrows()]
         self.rows = rows
 
@@ -62,9 +68,53 @@ class MultiTurnSFTDataset(Dataset):
             prev = cur
         return ids, mask
 
+    def _with_images(self, ids: list, mask: list, images: list):
+        from verl_b200.utils.dataset.vision_utils import image_to_patches, process_image
+
+        v = self.vision
+        P, Tp, m = int(v.get("patch_size", 14)), int(v.get("temporal_patch_size", 2)), int(v.get("spatial_merge_size", 2))
+        img_id, vs = int(v.get("image_token_id", 151655)), int(v.get("vision_start_token_id", 151652))
+        if img_id not in ids:              # plain-text "<image>" marks: vision_start, one placeholder, vision_end
+            mark = self.tok("<image>", add_special_tokens=False)["input_ids"]
+            out_i, out_m, j = [], [], 0
+            while j < len(ids):
+                if ids[j:j + len(mark)] == mark:
+                    out_i += [vs, img_id, int(v.get("vision_end_token_id", vs + 1))]
+                    out_m += [0, 0, 0]
+                    j += len(mark)
+                else:
+                    out_i.append(ids[j])
+                    out_m.append(mask[j])
+                    j += 1
+            ids, mask = out_i, out_m
+        pix, grids = [], []
+        for img in images:
+            p, g = image_to_patches(process_image(img, factor=P * m, min_pixels=int(self.image_pixels[0] or 4 * (P * m) ** 2),
+                                                  max_pixels=int(self.image_pixels[1] or 1280 * (P * m) ** 2)), P, Tp, m)
+            pix.append(p)
+            grids.append(g)
+        grids = torch.cat(grids, 0)
+        out_i, out_m, k = [], [], 0
+        for t, mk in zip(ids, mask):
+            if t == img_id and k < len(grids):
+                n = int(grids[k, 0] * grids[k, 1] * grids[k, 2]) // (m * m)
+                out_i += [img_id] * n
+                out_m += [0] * n
+                k += 1
+            else:
+                out_i.append(t)
+                out_m.append(mk)
+        assert k == len(grids), f"{len(grids)} images but {k} image placeholders in the conversation"
+        return out_i, out_m, {"pixel_values": torch.cat(pix, 0), "image_grid_thw": grids}
+
     def __getitem__(self, i):
         r = self.rows[i]
         ids, mask = self._tokenize(r["messages"], r.get("tools"))
+        mm = None
+        if self.vision and r.get("images"):
+            ids, mask, mm = self._with_images(ids, mask, list(r["images"]))
+            if len(ids) > self.max_length:
+                raise ValueError(f"sample {i} has {len(ids)} tokens with its images expanded > max_length {self.max_length} (images are never truncated)")
         L = self.max_length
         if len(ids) > L:
             if self.truncation == "error":
@@ -81,7 +131,15 @@ class MultiTurnSFTDataset(Dataset):
         # the model predicts token t+1 at position t: shift so loss_mask[t] marks positions whose NEXT token is a target
         shifted = torch.zeros_like(loss_mask)
         shifted[:-1] = loss_mask[1:]
-        return {"input_ids": input_ids, "attention_mask": att, "position_ids": compute_position_id_with_mask(att), "loss_mask": shifted}
+        item = {"input_ids": input_ids, "attention_mask": att, "position_ids": compute_position_id_with_mask(att), "loss_mask": shifted}
+        if self.vision:
+            from verl_b200.models.vision import VisionConfig, get_rope_index
+
+            vcfg = VisionConfig(**{**self.vision, "mrope_section": tuple(self.vision.get("mrope_section", (16, 24, 24)))})
+            pos3, _ = get_rope_index(input_ids, mm["image_grid_thw"] if mm else None, vcfg, attention_mask=att)
+            item["position_ids"] = torch.cat([item["position_ids"][None], pos3], 0)
+            item["multi_modal_inputs"] = mm or {}
+        return item
 
 
 class RMDataset(Dataset):
