@@ -13,3 +13,31 @@ def test_sft_loss_goes_down_on_repeated_data(tmp_path, monkeypatch):
     rows = [json.loads(x)["data"] for x in logf.read_text().splitlines()]
     assert len(rows) == 12 and rows[-1]["train/loss"] < rows[0]["train/loss"] - 0.5
     assert (tmp_path / "ck" / "global_step_12" / "model_world_size_1_rank_0.pt").exists()
+
+
+def test_sft_on_conversations_with_images(tmp_path, monkeypatch):
+    """``data.multiturn.enable``: conversations (one of them with an image) through the SFT trainer with a vision-language preset;
+    only assistant tokens carry loss, and it goes down."""
+    import io
+
+    import numpy as np
+    import pandas as pd
+    from PIL import Image
+
+    buf = io.BytesIO()
+    Image.fromarray(np.random.default_rng(0).integers(0, 255, (16, 16, 3), dtype=np.uint8)).save(buf, format="PNG")
+    rows = []
+    for i in range(4):
+        rows.append({"messages": [{"role": "user", "content": ("<image> " if i % 2 == 0 else "") + f"say {i}"}, {"role": "assistant", "content": f"number {i}"},
+                                  {"role": "user", "content": "again"}, {"role": "assistant", "content": f"number {i}"}],
+                     "images": [{"bytes": buf.getvalue()}] if i % 2 == 0 else []})
+    f = tmp_path / "conv.parquet"
+    pd.DataFrame(rows).to_parquet(f)
+    logf = tmp_path / "sft.jsonl"
+    monkeypatch.setenv("VERL_FILE_LOGGER_PATH", str(logf))
+    sft_main([f"data.train_files={f}", "data.multiturn.enable=true", "data.multiturn.max_length=128", "data.multiturn.image_min_pixels=64",
+              "data.multiturn.image_max_pixels=256", "data.train_batch_size=4", "data.micro_batch_size_per_gpu=2", "model.preset=tiny-qwen2-vl",
+              "optim.lr=3e-3", "optim.lr_warmup_steps_ratio=0.0", "optim.lr_scheduler_type=constant", "trainer.total_epochs=10", "trainer.logger=[file]",
+              f"trainer.default_local_dir={tmp_path}/ck", "trainer.device=cpu"])
+    rows = [json.loads(x)["data"] for x in logf.read_text().splitlines()]
+    assert len(rows) == 10 and rows[-1]["train/loss"] < rows[0]["train/loss"] - 0.5

@@ -29,6 +29,9 @@ DEFAULT_CONFIG = {
     "data": {"train_files": None, "val_files": None, "prompt_key": "prompt", "response_key": "response", "max_prompt_length": 256,
              "max_response_length": 256, "train_batch_size": 32, "micro_batch_size_per_gpu": 4, "use_dynamic_bsz": False,
              "max_token_len_per_gpu": 8192, "truncation": "right",
+             # conversations (messages column, optional tools / images columns) instead of prompt / response strings
+             "multiturn": {"enable": False, "messages_key": "messages", "tools_key": "tools", "images_key": "images", "max_length": None,
+                           "image_min_pixels": None, "image_max_pixels": None},
              "synthetic": {"enable": False, "num_samples": 256, "vocab": 2048, "seed": 0}},
     "model": {"path": None, "preset": None, "override_config": {}, "enable_gradient_checkpointing": False},
     "optim": {"lr": 1e-5, "weight_decay": 0.01, "betas": [0.9, 0.95], "clip_grad": 1.0, "lr_warmup_steps_ratio": 0.1, "lr_scheduler_type": "cosine"},
@@ -37,6 +40,27 @@ DEFAULT_CONFIG = {
     "trainer": {"total_epochs": 1, "total_training_steps": None, "project_name": "sft", "experiment_name": "run", "logger": ["console"],
                 "default_local_dir": "checkpoints/sft", "save_freq": -1, "test_freq": -1, "resume_mode": "auto", "device": "cuda"},
 }
+
+
+class ConversationWindow(Dataset):
+    """A conversation dataset (``verl_b200.utils.dataset.sft_dataset.MultiTurnSFTDataset``: full sequence + per-position loss
+    mask) in the prompt / response layout the engine consumes: the first token is the prompt, everything after it the response
+    window, and the assistant tokens are the response mask. Image inputs and multimodal positions pass through.
+    Reference: ``verl/utils/dataset/multiturn_sft_dataset.py`` feeding ``verl/trainer/sft_trainer.py``."""
+
+    def __init__(self, ds):
+        self.ds = ds
+
+    def __len__(self):
+        return len(self.ds)
+
+    def __getitem__(self, i):
+        it = self.ds[i]
+        out = {"input_ids": it["input_ids"], "attention_mask": it["attention_mask"], "position_ids": it["position_ids"],
+               "responses": it["input_ids"][1:].clone(), "response_mask": it["loss_mask"][:-1].clone()}      # loss_mask[t]: token t+1 is a target
+        if "multi_modal_inputs" in it:
+            out["multi_modal_inputs"] = it["multi_modal_inputs"]
+        return out
 
 
 class SFTDataset(Dataset):
@@ -98,6 +122,27 @@ class SFTTrainer:
         self.engine = EngineRegistry.new("language_model", config.engine.strategy, model_config=Config(mc), engine_config=config.engine,
                                          optimizer_config=config.optim, checkpoint_config=config.checkpoint)
         dc = config.data
+        mt = dc.get("multiturn") or {}
+        if mt.get("enable", False):
+            from verl_b200.models.config import PRESETS, ModelConfig
+            from verl_b200.utils.dataset.sft_dataset import MultiTurnSFTDataset
+
+            vis = None
+            if mc.get("preset"):
+                vis = PRESETS[mc["preset"]].vision
+            elif mc.get("path") and os.path.exists(os.path.join(os.path.expanduser(str(mc["path"])), "config.json")):
+                vis = ModelConfig.from_pretrained(os.path.expanduser(str(mc["path"]))).vision
+
+            def conversations(files):
+                return ConversationWindow(MultiTurnSFTDataset(files, tokenizer, max_length=int(mt.get("max_length") or int(dc.max_prompt_length) + int(dc.max_response_length)),
+                                                              messages_key=mt.get("messages_key", "messages"), tools_key=mt.get("tools_key", "tools"),
+                                                              truncation=dc.get("truncation", "right"), vision=vis, images_key=mt.get("images_key", "images"),
+                                                              image_min_pixels=mt.get("image_min_pixels"), image_max_pixels=mt.get("image_max_pixels")))
+
+            if train_dataset is None:
+                train_dataset = conversations(dc.train_files)
+            if val_dataset is None and dc.get("val_files"):
+                val_dataset = conversations(dc.val_files)
         if train_dataset is None:
             train_dataset = SFTDataset.synthetic(dc) if dc.synthetic.enable else SFTDataset.from_files(dc.train_files, tokenizer, dc)
         if val_dataset is None and dc.get("val_files"):
@@ -217,6 +262,10 @@ def main(argv=None):
         from verl_b200.trainer.main_ppo import _load_tokenizer
 
         tok = _load_tokenizer(cfg.model.path)
+    elif (cfg.data.get("multiturn") or {}).get("enable", False):
+        from verl_b200.utils.tokenizer import ByteChatTokenizer      # preset models without tokenizer files: byte-level chat tokenizer
+
+        tok = ByteChatTokenizer()
     SFTTrainer(cfg, tokenizer=tok).fit()
 
 
