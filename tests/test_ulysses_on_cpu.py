@@ -21,8 +21,10 @@ from verl_b200.workers.engine.fsdp.engine import FSDPEngine
 dist.init_process_group("gloo")
 rank, world = dist.get_rank(), dist.get_world_size()
 sp = int(os.environ["SP"])
-key = "context_parallel_size" if os.environ.get("MODE") == "context" else "ulysses_sequence_parallel_size"
-eng = FSDPEngine(PRESETS["tiny-qwen2"], {"seed": 1, key: sp}, {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, {})
+key = "context_parallel_size" if os.environ.get("MODE", "").startswith("context") else "ulysses_sequence_parallel_size"
+eng = FSDPEngine(PRESETS["tiny-qwen2"], {"seed": 1, key: sp, "context_parallel_zigzag": os.environ.get("MODE") == "context_zigzag"},
+                 {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, {})
+assert eng._cp_zigzag == (os.environ.get("MODE") == "context_zigzag")
 eng.initialize()
 assert eng.get_data_parallel_size() == world // sp
 data = make_batch().chunk(eng.get_data_parallel_size())[eng.get_data_parallel_rank()]
@@ -39,7 +41,8 @@ dist.barrier()
 '''
 
 
-@pytest.mark.parametrize("world,sp,mode", [(2, 2, "ulysses"), (4, 2, "ulysses"), (2, 2, "context"), (3, 3, "context"), (4, 2, "context")])
+@pytest.mark.parametrize("world,sp,mode", [(2, 2, "ulysses"), (4, 2, "ulysses"), (2, 2, "context"), (3, 3, "context"), (4, 2, "context"),
+                                           (2, 2, "context_zigzag"), (3, 3, "context_zigzag"), (4, 2, "context_zigzag")])
 def test_ulysses_ranks_match_single_rank(tmp_path, world, sp, mode):
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     script = tmp_path / "w.py"
@@ -47,7 +50,7 @@ def test_ulysses_ranks_match_single_rank(tmp_path, world, sp, mode):
     out = tmp_path / "out.pt"
     env = dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1", SP=str(sp), MODE=mode)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-                        "--master-port", str(29750 + world + (10 if mode == "context" else 0)), str(script)], env=env, capture_output=True, text=True, timeout=900)
+                        "--master-port", str(29750 + world + {"ulysses": 0, "context": 10, "context_zigzag": 20}[mode]), str(script)], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     eng = FSDPEngine(PRESETS["tiny-qwen2"], {"seed": 1}, {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, {})
     eng.initialize()

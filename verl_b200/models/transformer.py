@@ -30,7 +30,7 @@ class PackedBatch:
     """Device-side description of a packed micro-batch."""
 
     __slots__ = ("input_ids", "position_ids", "cu_seqlens", "cu_seqlens_cpu", "max_seqlen", "routed_experts", "global_position_ids",
-                 "attn_expand", "visual_embeds", "visual_token_ids", "rope_override", "mm")
+                 "attn_expand", "visual_embeds", "visual_token_ids", "rope_override", "mm", "cp_zigzag")
 
     def __init__(self, input_ids, position_ids, cu_seqlens, cu_seqlens_cpu=None, max_seqlen=None, routed_experts=None):
         self.input_ids = input_ids
@@ -50,6 +50,7 @@ class PackedBatch:
         # vision-language models (verl_b200.models.vision): rows that replace the embeddings of the image placeholder tokens,
         # and per-token rotary tables (cos, sin) [T, D/2] of the multimodal rotary embedding
         self.visual_embeds = self.visual_token_ids = self.rope_override = self.mm = None
+        self.cp_zigzag = False        # context parallelism: the local rows are two chunks of the stream (zig-zag placement)
 
 
 def _proj(mod: nn.Module, name: str, x: torch.Tensor, bias=None) -> torch.Tensor:

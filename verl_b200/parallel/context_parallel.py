@@ -52,33 +52,46 @@ class AllGatherRows(torch.autograd.Function):
         return g[r * n:(r + 1) * n].clone(), None
 
 
+def zigzag_ranges(t_pad: int, world: int, rank: int) -> list:
+    """Zig-zag placement: the stream is cut into ``2·world`` chunks and rank ``r`` takes chunks ``r`` and ``2·world − 1 − r``,
+    so every rank holds an early and a late piece and the causal attention work is balanced."""
+    c = t_pad // (2 * world)
+    return [(rank * c, (rank + 1) * c), ((2 * world - 1 - rank) * c, (2 * world - rank) * c)]
+
+
+def zigzag_permutation(t_pad: int, world: int) -> torch.Tensor:
+    """Global token index of every row of the rank-order concatenation of the zig-zag slices."""
+    return torch.cat([torch.arange(a, b) for r in range(world) for a, b in zigzag_ranges(t_pad, world, r)])
+
+
 @lru_cache(maxsize=64)
-def _plan_cached(cu: tuple, t_pad: int, world: int, rank: int):
+def _plan_cached(cu: tuple, t_pad: int, world: int, rank: int, zigzag: bool = False):
     tl = t_pad // world
-    p0, p1 = rank * tl, (rank + 1) * tl
+    ranges = zigzag_ranges(t_pad, world, rank) if zigzag else [(rank * tl, (rank + 1) * tl)]
     seqs = [(cu[i], cu[i + 1]) for i in range(len(cu) - 1) if cu[i + 1] > cu[i]]
     if cu[-1] < t_pad:
         seqs.append((cu[-1], t_pad))                  # padding tokens form a sequence of their own
     kv_idx, q_pos, lens, q_starts = [], [], [], []
     base = 0
-    for s0, s1 in seqs:
-        if s1 <= p0 or s0 >= p1:
-            continue
-        e1 = min(s1, p1)
-        l0 = max(s0, p0)
-        kv_idx.append(torch.arange(s0, e1))
-        q_pos.append(torch.arange(base + (l0 - s0), base + (e1 - s0)))
-        lens.append(e1 - s0)
-        q_starts.append(l0 - s0)
-        base += e1 - s0
+    for p0, p1 in ranges:                             # local rows are ordered range by range
+        for s0, s1 in seqs:
+            if s1 <= p0 or s0 >= p1:
+                continue
+            e1 = min(s1, p1)
+            l0 = max(s0, p0)
+            kv_idx.append(torch.arange(s0, e1))
+            q_pos.append(torch.arange(base + (l0 - s0), base + (e1 - s0)))
+            lens.append(e1 - s0)
+            q_starts.append(l0 - s0)
+            base += e1 - s0
     cu_exp = torch.zeros(len(lens) + 1, dtype=torch.int32)
     cu_exp[1:] = torch.cumsum(torch.tensor(lens), 0)
     return torch.cat(kv_idx), torch.cat(q_pos), cu_exp, tuple(q_starts), max(lens)
 
 
-def build_cp_plan(cu_seqlens_cpu: torch.Tensor, t_pad: int, world: int, rank: int):
+def build_cp_plan(cu_seqlens_cpu: torch.Tensor, t_pad: int, world: int, rank: int, zigzag: bool = False):
     """→ (kv_idx [E] global token of every expanded row, q_pos [Tl] expanded row of every local token, cu_exp, q_starts, max_len)."""
-    return _plan_cached(tuple(int(x) for x in cu_seqlens_cpu.tolist()), int(t_pad), int(world), int(rank))
+    return _plan_cached(tuple(int(x) for x in cu_seqlens_cpu.tolist()), int(t_pad), int(world), int(rank), bool(zigzag))
 
 
 def context_parallel_attention(qkv: torch.Tensor, pb, cfg, group) -> torch.Tensor:
@@ -90,8 +103,11 @@ def context_parallel_attention(qkv: torch.Tensor, pb, cfg, group) -> torch.Tenso
     tl = qkv.shape[0]
     q_size = cfg.num_attention_heads * cfg.head_dim
     kv_all = AllGatherRows.apply(qkv[:, q_size:].contiguous(), group)
-    kv_idx, q_pos, cu_exp, q_starts, max_len = build_cp_plan(pb.cu_seqlens_cpu, tl * W, W, r)
+    zigzag = bool(getattr(pb, "cp_zigzag", False))
+    kv_idx, q_pos, cu_exp, q_starts, max_len = build_cp_plan(pb.cu_seqlens_cpu, tl * W, W, r, zigzag)
     dev = qkv.device
+    if zigzag:      # the gathered K/V rows come in rank order = zig-zag order: look global tokens up through the inverse
+        kv_idx = torch.argsort(zigzag_permutation(tl * W, W)).index_select(0, kv_idx)
     kv_idx, q_pos = kv_idx.to(dev), q_pos.to(dev)
     q_exp = qkv.new_zeros(kv_idx.numel(), q_size).index_copy(0, q_pos, qkv[:, :q_size])
     qkv_exp = torch.cat([q_exp, kv_all.index_select(0, kv_idx)], dim=1)

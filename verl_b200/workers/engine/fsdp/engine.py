@@ -163,6 +163,8 @@ class FSDPEngine(BaseEngine):
         if cp > 1:
             assert self.sp_size == 1, "choose either ulysses_sequence_parallel_size or context_parallel_size"
             self.sp_size, self.sp_mode = cp, "context"
+        # zig-zag placement of the context-parallel slices balances the causal attention work between the ranks
+        self._cp_zigzag = self.sp_mode == "context" and bool(cfg_get(self.engine_config, "context_parallel_zigzag", False))
         fsdp_size = int(cfg_get(self.engine_config, "fsdp_size", -1))
         self.fsdp_size = self.world if fsdp_size in (-1, 0) or fsdp_size >= self.world else fsdp_size
         self.forward_only = bool(cfg_get(self.engine_config, "forward_only", False)) or optimizer_config is None
@@ -602,6 +604,26 @@ class FSDPEngine(BaseEngine):
 
         sp, r = self.sp_size, self.sp_rank
         T = pb.input_ids.shape[0]
+        if self._cp_zigzag:
+            from verl_b200.parallel.context_parallel import zigzag_permutation
+
+            pad = (-T) % (2 * sp)
+            ids, pos, lab = pb.input_ids, pb.position_ids, labels
+            if pad:
+                ids, lab = torch.nn.functional.pad(ids, (0, pad)), torch.nn.functional.pad(lab, (0, pad))
+                pos = torch.cat([pos, torch.arange(pad, device=pos.device, dtype=pos.dtype)])
+            perm = zigzag_permutation(T + pad, sp).to(ids.device)
+            Tl = (T + pad) // sp
+            mine = perm[r * Tl:(r + 1) * Tl]
+            pbl = PackedBatch(ids.index_select(0, mine), pos.index_select(0, mine), pb.cu_seqlens, pb.cu_seqlens_cpu, pb.max_seqlen, None)
+            pbl.cp_zigzag = True
+            h = self.model.forward_hidden(pbl)
+            lp_l, ent_l = ops.linear_logprob_entropy(h, self.model.output_weight, lab.index_select(0, mine), temperature, need_entropy)
+            inv = torch.argsort(perm)          # gathered rows come in rank order; put them back into stream order
+            lp = gather_outputs_and_unpad(lp_l.float(), 0, None, 0, grad_scaler=True, group=self.sp_group).index_select(0, inv)[:T]
+            ent = gather_outputs_and_unpad(ent_l.float(), 0, None, 0, grad_scaler=True, group=self.sp_group).index_select(0, inv)[:T] \
+                if ent_l is not None else None
+            return lp, ent
         ids_l, pos_l, pad = ulysses_pad_and_slice_inputs(pb.input_ids, pb.position_ids, sp, r, dim=0)
         lab = torch.nn.functional.pad(labels, (0, pad)) if pad else labels
         Tl = (T + pad) // sp

@@ -98,6 +98,8 @@ class MegatronEngine(FSDPEngine):
     def initialize(self):
         cfg = self._resolve_model_config()
         self.cfg = cfg
+        if cfg.vision:
+            raise NotImplementedError("vision-language models run in the sharded data-parallel engine (strategy=fsdp), not under tensor/pipeline parallelism")
         dt_name = cfg_get(self.engine_config, "model_dtype", None) or (cfg.torch_dtype if self.device.type == "cpu" else "bfloat16")
         self.dtype = _DTYPES.get(str(dt_name), torch.bfloat16)
         seed = int(cfg_get(self.engine_config, "seed", 0))
