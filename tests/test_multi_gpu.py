@@ -170,7 +170,7 @@ from verl_b200.workers.engine.fsdp.engine import FSDPEngine
 from verl_b200.workers.engine.megatron.engine import MegatronEngine
 # ---- Ulysses: all-to-alls fused into the projections == NCCL all-to-all formulation
 res = {}
-for mode in ("fused", "nccl", "context", "zigzag"):
+for mode in ("fused", "nccl", "context"):
     ecfg = {"seed": 1, "use_symmetric_memory": False}
     if mode in ("context", "zigzag"):      # context parallelism: K/V all-gather, attention kernels skip the other rank's query tiles
         ecfg["context_parallel_size"] = world
@@ -195,9 +195,6 @@ assert d_lp < 0.06 and rel < 0.05, (d_lp, rel)
 d_cp = (res["context"][0] - res["nccl"][0]).abs().max().item()
 rel_cp = ((res["context"][1] - g_n).norm() / g_n.norm()).item()
 assert d_cp < 0.06 and rel_cp < 0.05, (d_cp, rel_cp)
-d_zz = (res["zigzag"][0] - res["nccl"][0]).abs().max().item()
-rel_zz = ((res["zigzag"][1] - g_n).norm() / g_n.norm()).item()
-assert d_zz < 0.06 and rel_zz < 0.05, (d_zz, rel_zz)
 # ---- tensor-parallel engine on NCCL == single-GPU engine
 ref = FSDPEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "use_symmetric_memory": False, "fsdp_size": 1}, None, {})
 tp = MegatronEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "tensor_model_parallel_size": world}, {"lr": 1e-3}, {})
