@@ -172,9 +172,8 @@ from verl_b200.workers.engine.megatron.engine import MegatronEngine
 res = {}
 for mode in ("fused", "nccl", "context"):
     ecfg = {"seed": 1, "use_symmetric_memory": False}
-    if mode in ("context", "zigzag"):      # context parallelism: K/V all-gather, attention kernels skip the other rank's query tiles
+    if mode == "context":      # context parallelism: K/V all-gather, attention kernels skip the other rank's query tiles
         ecfg["context_parallel_size"] = world
-        ecfg["context_parallel_zigzag"] = mode == "zigzag"      # every rank holds an early and a late chunk of the stream
     else:
         ecfg.update({"ulysses_sequence_parallel_size": world, "fused_ulysses": mode == "fused"})
     eng = FSDPEngine(PRESETS["tiny-qwen2-gpu"], ecfg, {"lr": 1e-3, "clip_grad": 1.0}, {})
