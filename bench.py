@@ -28,6 +28,27 @@ import time
 BASELINE_PUBLISHED = None  # the reference publishes no number for this configuration
 
 
+def _job_start_time() -> float:
+    """Wall-clock time at which this job began: the launcher's start when run under ``torch.distributed.run`` (its own
+    ``import torch`` on a cold machine can take a minute before any rank exists), else this process's."""
+    t = time.time()
+    try:
+        import psutil
+
+        me = psutil.Process()
+        t = min(t, me.create_time())
+        parent = me.parent()
+        if parent is not None and any("torch.distributed.run" in a or a.endswith("torchrun") for a in parent.cmdline()):
+            t = min(t, parent.create_time())
+    except Exception:  # noqa: BLE001
+        pass
+    return t
+
+
+T_PROCESS_START = _job_start_time()
+MIN_WARMUP = 3          # never time a step before three warm-up steps have run
+
+
 def _clock_sampler(stop: threading.Event, out: list, gpu_index: int):
     q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -65,7 +86,7 @@ def build_config(args, world: int):
         f"actor_rollout_ref.model.preset={args.model}", "actor_rollout_ref.model.enable_gradient_checkpointing=" + ("true" if args.grad_ckpt else "false"),
         f"actor_rollout_ref.rollout.n={args.n}", "actor_rollout_ref.rollout.temperature=1.0", "actor_rollout_ref.rollout.ignore_eos=false",
         f"actor_rollout_ref.rollout.max_num_seqs={prompts_per_gpu * args.n}", f"actor_rollout_ref.rollout.gpu_memory_utilization={args.kv_util}",
-        f"actor_rollout_ref.actor.ppo_mini_batch_size={args.mini_prompts_per_gpu * world * args.n}",
+        f"actor_rollout_ref.actor.ppo_mini_batch_size={args.mini_prompts_per_gpu * world}",
         "actor_rollout_ref.actor.use_dynamic_bsz=true", f"actor_rollout_ref.actor.ppo_max_token_len_per_gpu={args.token_budget}",
         "actor_rollout_ref.rollout.log_prob_use_dynamic_bsz=true", f"actor_rollout_ref.rollout.log_prob_max_token_len_per_gpu={args.token_budget * 2}",
         "actor_rollout_ref.ref.log_prob_use_dynamic_bsz=true", f"actor_rollout_ref.ref.log_prob_max_token_len_per_gpu={args.token_budget * 2}",
@@ -120,13 +141,42 @@ def run_native(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def agree(x: float, op) -> float:
+        """One number every rank agrees on (decisions about how many steps to run must not diverge between ranks)."""
+        t = torch.tensor([x], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    def elapsed() -> float:
+        return agree(time.time() - T_PROCESS_START, dist.ReduceOp.MAX)
+
+    # Wall-clock guard. A step of this benchmark takes tens of seconds, so `--steps 20 --warmup 5` can exceed the time a
+    # caller allows per run. The guard keeps at least three warm-up steps (CUDA-graph capture, allocator steady state),
+    # then runs as many timed steps as fit below --time-limit seconds of process wall clock, and reports what it ran.
+    limit = float(args.time_limit)
     trainer.global_steps = 1
+    warm_times: list = []
+    warm_done = 0
     for w in range(args.warmup):
+        if limit > 0 and warm_done >= MIN_WARMUP:
+            est = max(warm_times[1:] or warm_times)
+            if elapsed() + est * (args.warmup - warm_done + max(1, args.steps)) > limit:
+                break                           # the remaining warm-up steps would eat the timed steps
+        t0 = time.perf_counter()
         m = trainer.step(next(it))
+        torch.cuda.synchronize()
+        warm_times.append(agree(time.perf_counter() - t0, dist.ReduceOp.MAX))
+        warm_done += 1
         trainer.global_steps += 1
         if rank == 0 and args.verbose:
             print(f"[warmup {w}] " + " ".join(f"{k}={v:.3f}" for k, v in m.items() if k.startswith("timing_s/") or k in ("perf/throughput", "actor/grad_norm")), file=sys.stderr, flush=True)
     _ext.check_status("bench warm-up")
+    steps_planned = args.steps
+    if limit > 0 and warm_times:
+        est = max(warm_times[1:] or warm_times) * 1.03
+        fit = int((limit - elapsed()) // est)
+        steps_planned = max(1, min(args.steps, fit))
     samples: list = []
     stop = threading.Event()
     th = threading.Thread(target=_clock_sampler, args=(stop, samples, local_rank), daemon=True)
@@ -138,14 +188,21 @@ def run_native(args):
     t_wall0 = time.perf_counter()
     ev0.record()
     tokens = 0
-    last = {}
-    for s in range(args.steps):
+    per_step: list = []
+    steps_run = 0
+    for s in range(steps_planned):
         batch = next(it)                     # data-loader fetch is part of the end-to-end region
         last = trainer.step(batch)
         trainer.global_steps += 1
+        steps_run += 1
         tokens += int(last["perf/total_num_tokens"])
+        per_step.append({k.split("/", 1)[1]: round(v, 3) for k, v in last.items() if k.startswith("timing_s/")})
         if rank == 0 and args.verbose:
             print(f"[step {s}] " + " ".join(f"{k}={v:.3f}" for k, v in last.items() if k.startswith("timing_s/") or k in ("perf/throughput", "actor/grad_norm")), file=sys.stderr, flush=True)
+        if limit > 0 and s + 1 < steps_planned:
+            # safety net for a step that ran much longer than the warm-up steps suggested (one 8-byte all-reduce per step)
+            if elapsed() + per_step[-1].get("step", 0.0) * 1.03 > limit + 30.0:
+                break
     ev1.record()
     barrier()
     t_wall = time.perf_counter() - t_wall0
@@ -161,11 +218,13 @@ def run_native(args):
     if rank == 0:
         value = tokens / (dev_ms / 1000.0)
         e2e = tokens / (wall_ms / 1000.0)
-        h2d = (IO_STATS["h2d_bytes"] - io0["h2d_bytes"]) / args.steps
-        d2h = (IO_STATS["d2h_bytes"] - io0["d2h_bytes"]) / args.steps
+        h2d = (IO_STATS["h2d_bytes"] - io0["h2d_bytes"]) / steps_run
+        d2h = (IO_STATS["d2h_bytes"] - io0["d2h_bytes"]) / steps_run
+        keys = sorted({k for d in per_step for k in d})
         out = {
             "metric": "GRPO step tokens/s (rollout+train), Qwen2.5-7B arch", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "steps": steps_run, "warmup": warm_done, "steps_requested": args.steps, "warmup_requested": args.warmup,
+            "ms_per_step": dev_ms / steps_run, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None, "dtype": "bf16" if not args.rollout_quant else f"bf16 training, {args.rollout_quant} rollout projections", "data": "synthetic prompts, random-init weights",
             "impl": "native",
             "config": {"model": args.model, "global_batch": f"{args.prompts_per_gpu * world} prompts x n={args.n}",
@@ -173,12 +232,14 @@ def run_native(args):
                        "parallelism": f"dp{world} ({'ZeRO-3 row-sharded projections gathered inside the GEMMs' if args.zero3 else 'ZeRO-2 sharded optimizer, resident bf16 params'}), rollout tp{args.rollout_tp} x {world // args.rollout_tp} replicas colocated",
                        "ppo_mini_batch_prompts": args.mini_prompts_per_gpu * world, "token_budget_per_micro_batch": args.token_budget,
                        "gradient_checkpointing": bool(args.grad_ckpt), "ref_param_offload": bool(args.ref_offload), "prefix_sharing": bool(args.prefix_sharing), "rollout_quantization": args.rollout_quant or None, "zero3": bool(args.zero3), "loss": "grpo clip 0.2 + low_var_kl 1e-3, AdamW lr 1e-6",
-                       "l2_policy": "inputs larger than L2: each step streams >15 GB of weights and fresh activations"},
+                       "l2_policy": "inputs larger than L2: each step streams >15 GB of weights and fresh activations",
+                       "time_limit_s": limit if limit > 0 else None},
             "clocks": _summarise_clocks(samples),
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches,
-            "step_breakdown_s": {k.split("/", 1)[1]: round(v, 3) for k, v in last.items() if k.startswith("timing_s/")},
-            "tokens_per_step": tokens / args.steps,
+            "step_breakdown_s": {k: [d.get(k) for d in per_step] for k in keys},
+            "warmup_step_s": [round(x, 3) for x in warm_times],
+            "tokens_per_step": tokens / steps_run,
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1),
         }
         print(json.dumps(out), flush=True)
@@ -236,6 +297,9 @@ def main():
     ap.add_argument("--rollout-tp", type=int, default=0,
                     help="GPUs per rollout replica; 0 = 2 whenever at least 2 GPUs run (the layout the benchmark config names), 1 on a single GPU. "
                          "--rollout-tp 1 (one replica per GPU) is about 5 %% faster for this 7B model")
+    ap.add_argument("--time-limit", type=float, default=790.0,
+                    help="seconds of process wall clock the whole run may take: warm-up beyond three steps and timed steps that "
+                         "would not fit are dropped and the JSON line reports the counts that ran; 0 = run exactly what was asked")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
     single = int(os.environ.get("WORLD_SIZE", "1")) == 1

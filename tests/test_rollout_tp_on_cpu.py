@@ -71,3 +71,31 @@ def test_grpo_fit_with_tp2_rollout(tmp_path, world):
     assert len(rows) == 2 and rows[-1]["perf/total_num_tokens"] > 0 and abs(rows[0]["actor/ppo_kl"]) < 1e-4
     # the rollout's log-probs and the trainer's recomputation agree: the sharded replica serves the trainer's weights
     assert abs(rows[1].get("training/rollout_probs_diff_mean", 0.0)) < 1e-3
+
+
+def test_resume_hands_the_restored_weights_to_the_tp_rollout(tmp_path):
+    """Tensor-parallel replicas hold their own slices of the weights. After a resume those slices must be refreshed from the
+    restored weights before the first rollout: the rollout's log-probs then equal the trainer's recomputation on the very
+    first resumed step (with stale slices they differ, because training moved the weights before the save)."""
+    from tests.test_trainer_e2e_on_cpu import OV
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    base = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29781",
+            "-m", "verl_b200.trainer.main_ppo"] + [o for o in OV if not o.startswith("trainer.logger")] + \
+           ["trainer.logger=[file]", f"trainer.default_local_dir={tmp_path}/ckpt", "actor_rollout_ref.rollout.tensor_model_parallel_size=2",
+            "actor_rollout_ref.actor.optim.lr=3e-3"]        # a large step, so that stale rollout weights would be visible
+    log1, log2 = tmp_path / "a.jsonl", tmp_path / "b.jsonl"
+    env = dict(os.environ, OMP_NUM_THREADS="2", PYTHONPATH=repo)
+    r = subprocess.run(base + ["trainer.total_training_steps=2", "trainer.save_freq=2", "trainer.resume_mode=disable"],
+                       env=dict(env, VERL_FILE_LOGGER_PATH=str(log1)), capture_output=True, text=True, timeout=900, cwd=repo)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert (tmp_path / "ckpt" / "latest_checkpointed_iteration.txt").read_text() == "2"
+    r = subprocess.run(base + ["trainer.total_training_steps=3", "trainer.save_freq=-1", "trainer.resume_mode=auto"],
+                       env=dict(env, VERL_FILE_LOGGER_PATH=str(log2)), capture_output=True, text=True, timeout=900, cwd=repo)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    rows = [json.loads(x) for x in log2.read_text().splitlines()]
+    assert len(rows) == 1 and rows[0]["step"] == 3
+    assert abs(rows[0]["data"]["training/rollout_probs_diff_max"]) < 1e-4
+    # the same quantity in the first run's second step shows what training did to the weights: non-trivial policy movement
+    first = [json.loads(x)["data"] for x in log1.read_text().splitlines()]
+    assert abs(first[1]["training/rollout_probs_diff_max"]) < 1e-4

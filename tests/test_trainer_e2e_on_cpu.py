@@ -132,3 +132,58 @@ def test_rollout_dumps_and_viewer(tmp_path, capsys):
     assert viewer_main([str(dump), "--step", "1", "--sort=-score", "--limit", "3"]) == 0
     out = capsys.readouterr().out
     assert out.count("--- output") == 3 and "step 1: 32 trajectories" in out
+
+
+def test_mini_batch_counts_prompts_not_trajectories(tmp_path):
+    """``ppo_mini_batch_size`` is a number of prompts: 8 prompts x n=4 with a mini-batch of 4 prompts is two optimizer steps
+    per RL step (not eight), and a mini-batch equal to the train batch is exactly one."""
+    for mini, want in ((4, 2), (8, 1)):
+        tr = build(tmp_path, ["trainer.total_training_steps=1", f"actor_rollout_ref.actor.ppo_mini_batch_size={mini}"])
+        eng = tr.actor_rollout_wg.worker.actor.engine
+        before = eng.step_count
+        tr.global_steps = 1
+        tr.step(next(iter(tr.train_dataloader)))
+        assert eng.step_count - before == want
+
+
+def test_model_only_resume_continues_from_the_loaded_weights(tmp_path):
+    """Checkpoint without optimizer state: after the load the fp32 master copy must equal the loaded weights, so the next
+    optimizer step moves the LOADED weights instead of writing the initialisation-time master over them."""
+    ck = ["actor_rollout_ref.actor.checkpoint.save_contents=[model,extra]", "actor_rollout_ref.actor.checkpoint.load_contents=[model,extra]",
+          "actor_rollout_ref.actor.optim.lr=1e-3"]
+    tr = build(tmp_path, ["trainer.total_training_steps=3", "trainer.save_freq=-1"] + ck)
+    it = iter(tr.train_dataloader)
+    tr.global_steps = 1
+    tr.step(next(it))
+    tr._save_checkpoint()
+    eng = tr.actor_rollout_wg.worker.actor.engine
+    saved = eng.store.flat.clone()
+    assert not os.path.exists(tmp_path / "ckpt" / "global_step_1" / "actor" / "optim_world_size_1_rank_0.pt")
+    tr2 = build(tmp_path, ["trainer.total_training_steps=3", "trainer.resume_mode=auto"] + ck)
+    eng2 = tr2.actor_rollout_wg.worker.actor.engine
+    init = eng2.store.flat.clone()
+    assert tr2._load_checkpoint() == 1
+    assert torch.equal(eng2.store.flat, saved) and not torch.equal(saved, init)
+    assert torch.equal(eng2.master, saved[eng2.store.shard_slice].float())
+    assert float(eng2.exp_avg.abs().sum()) == 0.0 and eng2.step_count == 0
+    tr2.global_steps = 2
+    tr2.step(next(iter(tr2.train_dataloader)))
+    after = eng2.store.flat
+    # one AdamW step at lr 1e-3 moves every weight by at most about lr from where it was loaded
+    assert float((after.float() - saved.float()).abs().max()) < 5e-3
+    assert float((after.float() - init.float()).abs().max()) > 5e-3 or float((saved.float() - init.float()).abs().max()) < 5e-3
+
+
+def test_async_save_names_a_step_only_when_all_writers_finished(tmp_path):
+    """Asynchronous saves: the tracker file appears after the background writer has dropped its marker, and pruning keeps
+    the last complete checkpoint while a newer one is still being written."""
+    tr = build(tmp_path, ["trainer.total_training_steps=3", "trainer.save_freq=1", "trainer.max_actor_ckpt_to_keep=1",
+                          "actor_rollout_ref.actor.checkpoint.async_save=true"])
+    tr.fit()
+    root = tmp_path / "ckpt"
+    assert (root / "latest_checkpointed_iteration.txt").read_text() == "3"
+    last = root / "global_step_3" / "actor"
+    assert (last / "model_world_size_1_rank_0.pt").exists() and not (last / ".async_save_pending").exists()
+    assert not [f for f in os.listdir(last) if f.startswith(".async_done")]
+    kept = sorted(d for d in os.listdir(root) if d.startswith("global_step_") and os.path.exists(root / d / "actor" / "model_world_size_1_rank_0.pt"))
+    assert "global_step_3" in kept and "global_step_1" not in kept

@@ -38,7 +38,7 @@ def _case(M, V, K, seed):
     return h, w, labels
 
 
-def _run_both(lib, h, w, labels, inv_temp):
+def _run_both(lib, h, w, labels, inv_temp, with_ent=True, with_lse=True):
     M, K = h.shape
     V = w.shape[0]
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -47,7 +47,7 @@ def _run_both(lib, h, w, labels, inv_temp):
     for static in (False, True):
         logp, ent, lse = (torch.full((M,), float("nan"), device="cuda") for _ in range(3))
         common = (h.data_ptr(), w.data_ptr(), labels.data_ptr(), M, V, K, h.stride(0), w.stride(0), inv_temp)
-        tail = (logp.data_ptr(), ent.data_ptr(), lse.data_ptr(), err.data_ptr(), stream)
+        tail = (logp.data_ptr(), ent.data_ptr() if with_ent else None, lse.data_ptr() if with_lse else None, err.data_ptr(), stream)
         if static:
             rc = lib.vb_lmhead_logprob_fwd_static(*common, *tail)
         else:
@@ -73,6 +73,29 @@ def test_static_scratch_entry_point_matches_on_two_calls_in_a_row():
         logits = (h.float() @ w.float().t()) * inv_temp
         ref = torch.log_softmax(logits, -1).gather(1, labels[:, None])[:, 0]
         torch.testing.assert_close(lp1, ref, rtol=2e-2, atol=2e-2)
+
+
+def test_labels_outside_the_vocabulary_and_optional_outputs():
+    """Rows whose label is not a column of W (ignore index, padded vocabulary) must give logp = -lse in BOTH entry points,
+    also when the shared scratch still holds the label logits of an earlier, larger call; ent / lse may be left out."""
+    lib = _lib()
+    h, w, labels = _case(900, 4000, 256, 7)
+    _run_both(lib, h, w, labels, 1.0)                       # fills the built-in scratch with in-range label logits
+    M, V, K = 300, 2100, 256
+    h, w, labels = _case(M, V, K, 8)
+    labels[::7] = -100
+    labels[3::11] = V + 5
+    bad = (labels < 0) | (labels >= V)
+    assert int(bad.sum()) > 20
+    (lp0, en0, ls0), (lp1, en1, ls1) = _run_both(lib, h, w, labels, 1.0)
+    torch.testing.assert_close(lp1, lp0, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(lp1[bad], -ls1[bad], rtol=0, atol=0)
+    torch.testing.assert_close(lp0[bad], -ls0[bad], rtol=0, atol=0)
+    # without the optional outputs the log-probs are unchanged and the skipped buffers stay untouched (NaN-filled)
+    (lpa, ena, lsa), (lpb, enb, lsb) = _run_both(lib, h, w, labels, 1.0, with_ent=False, with_lse=False)
+    torch.testing.assert_close(lpb, lp1, rtol=0, atol=0)
+    torch.testing.assert_close(lpa, lp0, rtol=0, atol=0)
+    assert bool(torch.isnan(enb).all()) and bool(torch.isnan(lsb).all())
 
 
 def test_static_scratch_entry_point_rejects_sizes_beyond_its_capacity():

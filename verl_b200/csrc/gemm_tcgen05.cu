@@ -937,6 +937,7 @@ extern "C" long vb_lmhead_scratch_floats(int M, int V) {
 
 // h: [M, K] bf16 (row stride ldh), W: [V, K] bf16 (row stride ldw), labels: int64 [M].
 // scratch: vb_lmhead_scratch_floats(M, V) floats. Outputs fp32 [M]: logp, ent (nullable), lse (nullable).
+// A row whose label lies outside [0, V) gets logp = -lse.
 extern "C" int vb_lmhead_logprob_fwd(const void* h, const void* W, const long* labels, int M, int V, int K, int ldh, int ldw,
                                      float inv_temp, float* scratch, float* logp, float* ent, float* lse, int* err_word,
                                      cudaStream_t stream) {
@@ -952,6 +953,9 @@ extern "C" int vb_lmhead_logprob_fwd(const void* h, const void* W, const long* l
   epi.part_sum = scratch + num_n * M;
   epi.part_sumx = scratch + 2 * num_n * M;
   epi.label_logit = scratch + 3 * num_n * M;
+  // the label-logit section is only written for rows whose label is a column of W: rows with a label outside [0, V)
+  // (ignore index, padded vocabulary) must read zero, not whatever the scratch held before
+  if (cudaMemsetAsync(epi.label_logit, 0, sizeof(float) * (size_t)M, stream) != cudaSuccess) return -13;
   int rc = launch_gemm<LM_BN, false, false, EPI_LOGPROB>(h, W, nullptr, nullptr, M, V, K, ldh, ldw, 0, 0, err_word, stream, epi);
   if (rc) return rc;
   lmhead_merge_kernel<<<(M + 127) / 128, 128, 0, stream>>>(epi.part_max, epi.part_sum, epi.part_sumx, epi.label_logit, M,

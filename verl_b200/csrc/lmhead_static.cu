@@ -54,7 +54,7 @@ extern "C" int vb_lmhead_logprob_fwd_static(const void* h, const void* W, const 
   }
   float* scratch = scratch_for_current_device();
   if (scratch == nullptr) return VB_STATIC_ERR_SETUP;
-  // The label-logit section is only written for rows whose label is a valid column: start it at zero.
-  if (cudaMemsetAsync(scratch + (need - M), 0, sizeof(float) * (size_t)M, stream) != cudaSuccess) return VB_STATIC_ERR_SETUP;
+  // vb_lmhead_logprob_fwd clears the label-logit section of the scratch on the stream before it launches, so nothing
+  // of an earlier call on the shared array is read back.
   return vb_lmhead_logprob_fwd(h, W, labels, M, V, K, ldh, ldw, inv_temp, scratch, logp, ent, lse, err_word, stream);
 }

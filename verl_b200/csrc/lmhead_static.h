@@ -26,9 +26,13 @@ extern "C" {
 //   outputs fp32 [M]: logp, ent (may be null), lse (may be null). All pointers are device pointers owned by the caller.
 //
 // Rules of use:
-//  * No device or host memory is allocated, by this function or anything it calls.
-//  * The first call on each device looks up the device address of the built-in scratch (with that device current) and
-//    caches it; make that first call during start-up, before any stream capture is begun.
+//  * This function and what it calls make no allocation call (no cudaMalloc / cudaFree, no torch allocator). The
+//    16 MiB scratch array itself belongs to the library's device module: the CUDA runtime places it on a device when
+//    the module is first used there, which at the latest is this entry point's first call on that device, and keeps
+//    it until the process exits.
+//  * The first call on each device therefore does the set-up: it looks up the device address of the built-in scratch
+//    (with that device current) and caches it. Make that first call once at start-up, while memory is still
+//    available, and before any stream capture is begun.
 //  * Every call on a device uses the same scratch array. Calls issued to one stream are ordered and safe; calls that
 //    may overlap in time (different streams, or different host threads on different streams) race on the scratch and
 //    give wrong results. Serialise them.

@@ -76,6 +76,110 @@ def bench_gemm(a):
         report("  cuBLAS (torch.matmul) same shape", ms2, flops=2.0 * M * N * K)
 
 
+def sustained(fn, seconds=1.5):
+    """Back-to-back launches for about ``seconds`` (no flush, operands larger than L2): the power-capped steady state a
+    kernel sees inside a long training step. Returns milliseconds per launch."""
+    fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    fn()
+    e.record()
+    torch.cuda.synchronize()
+    n = max(8, int(seconds * 1e3 / max(s.elapsed_time(e), 1e-3)))
+    s.record()
+    for _ in range(n):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / n
+
+
+def bench_gemm_layer(a):
+    """The GEMMs of one decoder layer (hidden --k, FFN --ffn, q/kv heads) on --m tokens in their three roles: forward
+    (x W^T), input gradient (dy W) and weight gradient (dy^T x accumulated into fp32), own kernel vs torch.matmul, as a burst
+    (median of flushed single launches) and sustained (back-to-back for 1.5 s)."""
+    from verl_b200.ops import _ext
+
+    o = _ext.ops()
+    T, H, I = a.m, a.k, a.ffn
+    D = 128
+    shapes = [("qkv", (a.heads + 2 * a.kv_heads) * D, H), ("o", H, a.heads * D), ("gate_up", 2 * I, H), ("down", H, I)]
+    tot = {"own": 0.0, "lib": 0.0}
+    print(f"| projection | role | M x N x K | own burst us | cuBLAS burst us | own sustained us | cuBLAS sustained us | own/cuBLAS sustained |")
+    print("|---|---|---|---|---|---|---|---|")
+    for name, N, K in shapes:
+        x = torch.randn(T, K, device="cuda").bfloat16()
+        w = (0.02 * torch.randn(N, K, device="cuda")).bfloat16()
+        dy = torch.randn(T, N, device="cuda").bfloat16()
+        y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+        dx = torch.empty(T, K, device="cuda", dtype=torch.bfloat16)
+        dw = torch.zeros(N, K, device="cuda", dtype=torch.float32)
+        roles = [
+            ("fwd", (T, N, K), lambda: o.gemm(x, w, y, None, False, False, False, 0), lambda: torch.matmul(x, w.t(), out=y)),
+            ("dgrad", (T, K, N), lambda: o.gemm(dy, w, dx, None, False, True, False, 0), lambda: torch.matmul(dy, w, out=dx)),
+            ("wgrad", (N, K, T), lambda: o.gemm(dy, x, dw, None, True, True, True, 0), lambda: torch.matmul(dy.t(), x)),
+        ]
+        for role, (m, n, k), own, lib in roles:
+            fl = 2.0 * m * n * k
+            b_own, b_lib = timeit(own, a.iters), timeit(lib, a.iters)
+            s_own, s_lib = sustained(own), sustained(lib)
+            tot["own"] += s_own
+            tot["lib"] += s_lib
+            print(f"| {name} | {role} | {m}x{n}x{k} | {b_own * 1e3:.1f} ({fl / b_own / 1e9:.0f} TF) | {b_lib * 1e3:.1f} ({fl / b_lib / 1e9:.0f} TF) | "
+                  f"{s_own * 1e3:.1f} ({fl / s_own / 1e9:.0f} TF) | {s_lib * 1e3:.1f} ({fl / s_lib / 1e9:.0f} TF) | {s_lib / s_own:.2f} |", flush=True)
+    print(f"layer total sustained: own {tot['own'] * 1e3:.0f} us, cuBLAS {tot['lib'] * 1e3:.0f} us, ratio {tot['lib'] / tot['own']:.3f} "
+          "(the cuBLAS weight-gradient column is a bf16-output matmul without the fp32 accumulation the own kernel fuses)")
+
+
+def bench_layer_step(a):
+    """Forward + backward of ONE decoder layer of the --model preset on --m packed tokens (sequences of --seqlen), weight
+    gradients accumulated into fp32 ``main_grad`` buffers exactly as the training engine does. This is the unit whose
+    launch list (``ncu --metrics gpu__time_duration.sum``) shows each kernel's share of a training step."""
+    from verl_b200.models.config import PRESETS
+    from verl_b200.models.transformer import DecoderLayer, PackedBatch
+    from verl_b200 import ops
+
+    cfg = PRESETS[a.model]
+    layer = DecoderLayer(cfg, torch.bfloat16, "cuda", 0)
+    with torch.no_grad():
+        for n_, p_ in layer.named_parameters():
+            if n_.endswith("layernorm"):
+                p_.fill_(1.0)
+            elif n_.endswith("bias"):
+                p_.zero_()
+            else:
+                p_.normal_(0.0, 0.02)
+    for p_ in layer.parameters():
+        p_.main_grad = torch.zeros(p_.shape, device="cuda", dtype=torch.float32)
+    T, L = a.m, a.seqlen
+    lens = [L] * (T // L) + ([T % L] if T % L else [])
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    pos = torch.cat([torch.arange(n_, dtype=torch.int32) for n_ in lens]).cuda()
+    pb = PackedBatch(torch.zeros(T, dtype=torch.long, device="cuda"), pos, cu.cuda(), cu, max(lens))
+    cos, sin = ops.rope_tables(cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta, "cuda")
+    h0 = torch.randn(T, cfg.hidden_size, device="cuda").bfloat16()
+    r0 = torch.randn(T, cfg.hidden_size, device="cuda").bfloat16()
+    g = torch.randn(T, cfg.hidden_size, device="cuda").bfloat16()
+
+    def fwd():
+        with torch.no_grad():
+            layer(h0, r0, pb, cos, sin)
+
+    def fwdbwd():
+        h = h0.clone().requires_grad_(True)
+        r = r0.clone().requires_grad_(True)
+        m, res = layer(h, r, pb, cos, sin)
+        torch.autograd.backward([m, res], [g, g])
+
+    n_par = sum(p_.numel() for n_, p_ in layer.named_parameters() if p_.dim() == 2)
+    attn = sum(2 * 2 * l * l / 2 * cfg.head_dim * cfg.num_attention_heads for l in lens)
+    ms_f = sustained(fwd, 1.0) if a.sustained else timeit(fwd, a.iters)
+    report(f"decoder layer fwd {a.model} T={T} (GEMM + causal attention FLOPs)", ms_f, flops=2.0 * n_par * T + attn)
+    ms_b = sustained(fwdbwd, 1.0) if a.sustained else timeit(fwdbwd, a.iters)
+    report(f"decoder layer fwd+bwd {a.model} T={T}", ms_b, flops=6.0 * n_par * T + 3.5 * attn)
+
+
 def bench_gemm_fp8(a):
     """e4m3 GEMM (per-row / per-column scales in the epilogue) against the bf16 kernel and torch._scaled_mm on the same shape."""
     from verl_b200.ops import _ext
@@ -218,12 +322,15 @@ def bench_fused_gather(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "attn_fwd", "attn_bwd", "lmhead", "decode_attn", "elementwise", "fused_gather", "all"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_layer", "layer_step", "gemm_fp8", "attn_fwd", "attn_bwd", "lmhead", "decode_attn", "elementwise", "fused_gather", "all"])
     ap.add_argument("--world", type=int, default=2)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--ffn", type=int, default=18944)
+    ap.add_argument("--model", default="qwen2.5-7b")
+    ap.add_argument("--sustained", action="store_true", help="layer_step: back-to-back launches for about a second instead of flushed single launches")
     ap.add_argument("--a-mn", dest="a_mn", action="store_true")
     ap.add_argument("--b-mn", dest="b_mn", action="store_true")
     ap.add_argument("--f32", action="store_true")
@@ -242,6 +349,10 @@ def main():
     _ext.load()
     if a.kernel in ("gemm", "all"):
         bench_gemm(a)
+    if a.kernel == "gemm_layer":
+        bench_gemm_layer(a)
+    if a.kernel == "layer_step":
+        bench_layer_step(a)
     if a.kernel in ("gemm_fp8", "all"):
         bench_gemm_fp8(a)
     if a.kernel == "fused_gather":

@@ -179,6 +179,9 @@ class PPOTrainer:
         backend = _g(self.config, "trainer.worker_backend", "spmd")
         role = "actor_rollout_ref" if self.use_reference_policy else "actor_rollout"
         arr = ClassWithInitArgs(ActorRolloutRefWorker, config=self.config.actor_rollout_ref, role=role)
+        if self.use_critic:
+            # the critic's mini-batch is counted in prompts like the actor's; its worker needs n to turn it into trajectories
+            self.config.critic["rollout_n"] = int(_g(self.config, "actor_rollout_ref.rollout.n", 1))
         crit = ClassWithInitArgs(CriticWorker, config=self.config.critic) if self.use_critic else None
         if backend == "spmd":
             from verl_b200.single_controller.spmd import SPMDWorkerGroup, init_spmd_process_group
@@ -221,6 +224,7 @@ class PPOTrainer:
         root = os.path.expanduser(self.config.trainer.default_local_dir)
         step_dir = os.path.join(root, f"global_step_{self.global_steps}")
         print(f"local_global_step_folder: {step_dir}")
+        self._finish_pending_checkpoint(block=True)          # an earlier asynchronous save gets its tracker entry first
         self.actor_rollout_wg.save_checkpoint(os.path.join(step_dir, "actor"), None, self.global_steps, _g(self.config, "trainer.max_actor_ckpt_to_keep"))
         if self.use_critic:
             self.critic_wg.save_checkpoint(os.path.join(step_dir, "critic"), None, self.global_steps, _g(self.config, "trainer.max_critic_ckpt_to_keep"))
@@ -229,10 +233,47 @@ class PPOTrainer:
             os.makedirs(step_dir, exist_ok=True)
             if hasattr(self.train_dataloader, "state_dict"):
                 torch.save(self.train_dataloader.state_dict(), os.path.join(step_dir, "data.pt"))
+        # the tracker names a step only once all of its files exist: right away for synchronous saves, after every rank's
+        # background writer has dropped its marker for asynchronous ones (polled after each step, awaited at the end of fit)
+        self._pending_ckpt = (root, step_dir, self.global_steps)
+        self._pending_ckpt_tracked = False
+        asynchronous = bool(_g(self.config, "actor_rollout_ref.actor.checkpoint.async_save", False)) or bool(_g(self.config, "critic.checkpoint.async_save", False))
+        self._finish_pending_checkpoint(block=not asynchronous)
+
+    def _finish_pending_checkpoint(self, block: bool) -> bool:
+        """Write ``latest_checkpointed_iteration.txt`` for the last save once all of its writers are done.
+
+        ``block=False`` only looks at the marker files (no collective; ranks may see different answers, so nothing but the
+        tracker file changes). ``block=True`` is collective: every controller joins the writers, then the entry is closed."""
+        from verl_b200.utils.checkpoint.checkpoint_manager import BaseCheckpointManager as M
+
+        pend = getattr(self, "_pending_ckpt", None)
+        if pend is None:
+            return True
+        root, step_dir, step = pend
+        roles = ["actor"] + (["critic"] if self.use_critic else [])
+        if block:
+            self.actor_rollout_wg.wait_checkpoint()
+            if self.use_critic:
+                self.critic_wg.wait_checkpoint()
+        world = max(1, self.actor_rollout_wg.world_size)
+        rank = int(os.environ.get("RANK", "0")) if _g(self.config, "trainer.worker_backend", "spmd") == "spmd" else 0
+        done = all(M.async_save_complete(os.path.join(step_dir, r), world) for r in roles)
+        if block and not done:
+            raise RuntimeError(f"checkpoint writers finished but {step_dir} is incomplete")
+        if done and rank == 0 and not getattr(self, "_pending_ckpt_tracked", False):
             tmp = os.path.join(root, "latest_checkpointed_iteration.txt.tmp")
             with open(tmp, "w") as f:
-                f.write(str(self.global_steps))
+                f.write(str(step))
             os.replace(tmp, os.path.join(root, "latest_checkpointed_iteration.txt"))
+            self._pending_ckpt_tracked = True
+        if block:
+            if rank == 0:
+                for r in roles:
+                    M.finish_async_save(os.path.join(step_dir, r), world)
+            self._pending_ckpt = None
+            self._pending_ckpt_tracked = False
+        return done
 
     def _load_checkpoint(self) -> int:
         mode = _g(self.config, "trainer.resume_mode", "auto")
@@ -505,7 +546,11 @@ def _fit(self: PPOTrainer):
     logger = Tracking(cfg.trainer.project_name, cfg.trainer.experiment_name, cfg.trainer.logger if is_main else [],
                       config=dict(cfg)) if is_main else None
     self.global_steps = 0
-    self._load_checkpoint()
+    if self._load_checkpoint():
+        # rollout replicas that keep their own copy of the weights (tensor-parallel shards, ZeRO-3 / TPxPP trainers) were
+        # filled before the load: hand the restored weights over before the first validation or rollout
+        # (reference: verl/trainer/ppo/ray_trainer.py:1429-1430)
+        self.actor_rollout_wg.update_weights()
     if self.val_reward_fn is not None and _g(cfg, "trainer.val_before_train", True):
         val = self._validate()
         if val and logger:
@@ -531,14 +576,17 @@ def _fit(self: PPOTrainer):
                 if esi:
                     print("Force saving checkpoint: the announced capacity expiry is near.")
                 self._save_checkpoint()
+            self._finish_pending_checkpoint(block=False)
             metrics.update({"training/global_step": self.global_steps, "training/epoch": epoch})
             if logger:
                 logger.log(data=metrics, step=self.global_steps)
             self.global_steps += 1
             if is_last:
+                self._finish_pending_checkpoint(block=True)
                 if last_val:
                     print(f"Final validation metrics: {last_val}")
                 return
+    self._finish_pending_checkpoint(block=True)
 
 
 PPOTrainer.step = _train_step

@@ -150,6 +150,8 @@ class PPOTrainer(ABC):
         logger = Tracking(cfg.trainer.project_name, cfg.trainer.experiment_name, cfg.trainer.logger if self.rank == 0 else [], config=dict(cfg))
         self.global_steps = self.stages._load_checkpoint() or 0
         self.stages.global_steps = self.global_steps
+        if self.global_steps:
+            self.stages.actor_rollout_wg.update_weights()      # the colocated rollout must serve the restored weights
         total = int(self.stages.total_training_steps)
         self.on_train_begin()
         while self.global_steps < total:
@@ -171,6 +173,8 @@ class PPOTrainer(ABC):
                 self.stages._save_checkpoint()
             metrics.update({"training/global_step": self.global_steps, "training/epoch": self._epoch})
             logger.log(data=metrics, step=self.global_steps)
+            self.stages._finish_pending_checkpoint(block=False)
+        self.stages._finish_pending_checkpoint(block=True)
         self.on_train_end()
 
     def step(self, metrics: dict, timing_raw: dict):

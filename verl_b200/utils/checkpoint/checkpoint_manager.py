@@ -19,6 +19,7 @@ import torch
 __all__ = ["BaseCheckpointManager", "find_latest_ckpt_path", "get_checkpoint_tracker_filename", "should_save_ckpt_esi"]
 
 TRACKER = "latest_checkpointed_iteration.txt"
+ASYNC_PENDING = ".async_save_pending"        # present in a checkpoint directory while background writers may still be writing
 
 
 class BaseCheckpointManager:
@@ -75,6 +76,38 @@ class BaseCheckpointManager:
 
     def register_checkpoint(self, path: str, max_ckpt_to_keep: Optional[int] = None):
         self.previous_saved_paths.append(path)
+
+    # ---- asynchronous saves: a writer thread per rank; a checkpoint counts only once every rank has dropped its marker
+    def wait_async_save(self):
+        """Block until this rank's background writer (if any) has finished."""
+        th = getattr(self, "_async_thread", None)
+        if th is not None:
+            th.join()
+            self._async_thread = None
+
+    @staticmethod
+    def async_marker(path: str, rank: int) -> str:
+        return os.path.join(path, f".async_done_rank_{rank}")
+
+    @staticmethod
+    def async_save_complete(path: str, world: int) -> bool:
+        """True when ``path`` was not written asynchronously or all ``world`` writers have finished."""
+        if not os.path.exists(os.path.join(path, ASYNC_PENDING)):
+            return True
+        return all(os.path.exists(BaseCheckpointManager.async_marker(path, r)) for r in range(world))
+
+    @staticmethod
+    def finish_async_save(path: str, world: int):
+        """Rank 0, after ``async_save_complete``: remove the pending flag and the per-rank markers."""
+        for r in range(world):
+            try:
+                os.remove(BaseCheckpointManager.async_marker(path, r))
+            except OSError:
+                pass
+        try:
+            os.remove(os.path.join(path, ASYNC_PENDING))
+        except OSError:
+            pass
 
     @staticmethod
     def local_mkdir_safe(path: str) -> str:

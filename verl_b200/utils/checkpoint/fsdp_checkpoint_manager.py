@@ -22,7 +22,7 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
-from .checkpoint_manager import BaseCheckpointManager
+from .checkpoint_manager import ASYNC_PENDING, BaseCheckpointManager
 
 __all__ = ["FSDPCheckpointManager"]
 
@@ -49,13 +49,20 @@ class FSDPCheckpointManager(BaseCheckpointManager):
             return
         e = self.engine
         self.previous_global_step = global_step
+        self.wait_async_save()
+        if dist.is_initialized():
+            dist.barrier()                      # every rank's previous writer is done: older checkpoints may go
         if e.rank == 0:
-            self.ensure_checkpoint_capacity(max_ckpt_to_keep)
+            # while background writers run, the newest complete checkpoint must survive: keep one more than asked for
+            keep = max_ckpt_to_keep + 1 if self.async_save and isinstance(max_ckpt_to_keep, int) and max_ckpt_to_keep > 0 else max_ckpt_to_keep
+            self.ensure_checkpoint_capacity(keep)
+            self.local_mkdir_safe(local_path)
+            if self.async_save:
+                with open(os.path.join(local_path, ASYNC_PENDING), "w") as f:
+                    f.write(str(e.world))
         self.local_mkdir_safe(local_path)
         if dist.is_initialized():
             dist.barrier()
-        if self._async_thread is not None:
-            self._async_thread.join()
         model_f, optim_f, extra_f = self._names(local_path)
         s = e.store
         payload = []
@@ -72,11 +79,15 @@ class FSDPCheckpointManager(BaseCheckpointManager):
         if self.should_save_extra:
             payload.append((extra_f, {"lr_scheduler": {"sched_step": e.sched_step}, "rng": self.get_rng_state()}))
 
+        marker = self.async_marker(local_path, e.rank) if self.async_save else None
+
         def write():
             for fn, obj in payload:
                 tmp = fn + ".tmp"
                 torch.save(obj, tmp)
                 os.replace(tmp, fn)
+            if marker is not None:
+                open(marker, "w").close()       # this rank's files are complete
 
         if self.async_save:
             self._async_thread = threading.Thread(target=write, daemon=True)
@@ -133,12 +144,21 @@ class FSDPCheckpointManager(BaseCheckpointManager):
                     parts = [torch.empty(s.shard_size, dtype=s.flat.dtype) for _ in range(e.fsdp_size)]
                     dist.all_gather(parts, s.flat[s.shard_slice].clone(), group=e.fsdp_group)
                     s.flat.copy_(torch.cat(parts))
+        optimizer_loaded = False
         if self.should_load_optimizer and not e.forward_only and os.path.exists(optim_f):
             st = torch.load(optim_f, map_location="cpu", weights_only=False)
             e.master.copy_(st["master"])
             e.exp_avg.copy_(st["exp_avg"])
             e.exp_avg_sq.copy_(st["exp_avg_sq"])
             e.step_count = int(st["step_count"])
+            optimizer_loaded = True
+        if self.should_load_model and not optimizer_loaded and not e.forward_only and getattr(e, "master", None) is not None:
+            # weights without optimizer state: the fp32 master copy must follow the loaded weights, otherwise the next
+            # optimizer step would write the initialisation-time master (plus one update) over them
+            e.master.copy_(s.flat[s.shard_slice].float())
+            e.exp_avg.zero_()
+            e.exp_avg_sq.zero_()
+            e.step_count = 0
         if self.should_load_extra and os.path.exists(extra_f):
             st = torch.load(extra_f, map_location="cpu", weights_only=False)
             e.sched_step = int(st["lr_scheduler"]["sched_step"])

@@ -128,12 +128,20 @@ class MegatronCheckpointManager(BaseCheckpointManager):
                     parts = [torch.empty(s.shard_size, dtype=s.flat.dtype) for _ in range(e.dp_size)]
                     dist.all_gather(parts, s.flat[s.shard_slice].clone(), group=e.dp_group)
                     s.flat.copy_(torch.cat(parts))
+        optimizer_loaded = False
         if self.should_load_optimizer and not e.forward_only and os.path.exists(optim_f):
             st = torch.load(optim_f, map_location="cpu", weights_only=False)
             e.master.copy_(st["master"])
             e.exp_avg.copy_(st["exp_avg"])
             e.exp_avg_sq.copy_(st["exp_avg_sq"])
             e.step_count = int(st["step_count"])
+            optimizer_loaded = True
+        if self.should_load_model and not optimizer_loaded and not e.forward_only and getattr(e, "master", None) is not None:
+            # weights without optimizer state: re-derive the fp32 master slice from the loaded weights and restart Adam
+            e.master.copy_(s.flat[s.shard_slice].float())
+            e.exp_avg.zero_()
+            e.exp_avg_sq.zero_()
+            e.step_count = 0
         if self.should_load_extra and os.path.exists(extra_f):
             st = torch.load(extra_f, map_location="cpu", weights_only=False)
             e.sched_step = int(st["lr_scheduler"]["sched_step"])

@@ -168,11 +168,33 @@ class TrainingWorker(Worker):
     def load_checkpoint(self, local_path, hdfs_path=None, del_local_after_load=False):
         self.engine.load_checkpoint(local_path, hdfs_path, del_local_after_load)
 
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def wait_checkpoint(self):
+        _wait_checkpoint(self.engine)
+
+
+def _wait_checkpoint(engine):
+    """Join this rank's background checkpoint writer (asynchronous saves), then meet the other ranks."""
+    mgr = getattr(engine, "checkpoint_manager", None)
+    if mgr is not None and hasattr(mgr, "wait_async_save"):
+        mgr.wait_async_save()
+    if dist.is_initialized():
+        dist.barrier()
+
 
 def _to_host(t: torch.Tensor) -> torch.Tensor:
     if t.is_cuda:
         IO_STATS["d2h_bytes"] += t.numel() * t.element_size()
     return t.cpu()
+
+
+def _mini_batch_trajectories(mini_prompts, n):
+    """``ppo_mini_batch_size`` counts PROMPTS (it is compared with ``data.train_batch_size``); every prompt contributes
+    ``rollout.n`` trajectories, so one optimizer step covers ``mini * n`` rows of the rollout batch (reference:
+    ``verl/trainer/ppo/ray_trainer.py:1352-1363`` for the actor, ``:1382`` for the critic). None stays None (= one step)."""
+    if mini_prompts is None:
+        return None
+    return int(mini_prompts) * max(1, int(n or 1))
 
 
 def _role_cfg(full, role: str, model_type: str):
@@ -183,7 +205,7 @@ def _role_cfg(full, role: str, model_type: str):
         strategy = cfg_get(c, "strategy", "fsdp")
         eng = dict(cfg_get(c, "fsdp_config", {}) or {}) if strategy.startswith("fsdp") else dict(cfg_get(c, "megatron", {}) or {})
         return {"model_type": "value_model", "backend": strategy, "model": cfg_get(c, "model"), "engine": eng, "optim": cfg_get(c, "optim"),
-                "checkpoint": cfg_get(c, "checkpoint"), "ppo_mini_batch_size": cfg_get(c, "ppo_mini_batch_size"),
+                "checkpoint": cfg_get(c, "checkpoint"), "ppo_mini_batch_size": _mini_batch_trajectories(cfg_get(c, "ppo_mini_batch_size"), cfg_get(c, "rollout_n", 1)),
                 "ppo_epochs": cfg_get(c, "ppo_epochs", 1), "shuffle": cfg_get(c, "shuffle", False),
                 "use_dynamic_bsz": cfg_get(c, "use_dynamic_bsz", False), "ppo_max_token_len_per_gpu": cfg_get(c, "ppo_max_token_len_per_gpu"),
                 "ppo_micro_batch_size_per_gpu": cfg_get(c, "ppo_micro_batch_size_per_gpu"),
@@ -201,6 +223,7 @@ def _role_cfg(full, role: str, model_type: str):
                                                  "ppo_max_token_len_per_gpu", "ppo_micro_batch_size_per_gpu")})
         out["optim"] = cfg_get(sub, "optim")
         ro = cfg_get(full, "rollout")
+        out["ppo_mini_batch_size"] = _mini_batch_trajectories(out["ppo_mini_batch_size"], cfg_get(ro, "n", 1))
         out["log_prob_micro_batch_size_per_gpu"] = cfg_get(ro, "log_prob_micro_batch_size_per_gpu", cfg_get(sub, "ppo_micro_batch_size_per_gpu"))
         out["log_prob_use_dynamic_bsz"] = cfg_get(ro, "log_prob_use_dynamic_bsz", cfg_get(sub, "use_dynamic_bsz", False))
         out["log_prob_max_token_len_per_gpu"] = cfg_get(ro, "log_prob_max_token_len_per_gpu", cfg_get(sub, "ppo_max_token_len_per_gpu"))
@@ -488,6 +511,10 @@ class ActorRolloutRefWorker(Worker):
     def load_checkpoint(self, local_path, hdfs_path=None, del_local_after_load=False):
         self.actor.engine.load_checkpoint(local_path, hdfs_path, del_local_after_load)
 
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def wait_checkpoint(self):
+        _wait_checkpoint(self.actor.engine)
+
 
 class CriticWorker(Worker):
     """Value model: ``compute_values`` (forward) and ``update_critic`` (clipped value loss)."""
@@ -526,6 +553,10 @@ class CriticWorker(Worker):
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def load_checkpoint(self, local_path, hdfs_path=None, del_local_after_load=False):
         self.critic.engine.load_checkpoint(local_path, hdfs_path, del_local_after_load)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def wait_checkpoint(self):
+        _wait_checkpoint(self.critic.engine)
 
 
 class RewardModelWorker(Worker):
