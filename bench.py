@@ -277,7 +277,10 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--impl", default="native", choices=["native", "reference", "stocklibs"],
+                    help="native: this framework; reference: the unmodified reference package under baseline/_ref; stocklibs: the same GRPO "
+                         "step from vLLM + transformers/FlashAttention-2 + torch AdamW only (benchmarks/stocklibs_grpo.py, one GPU)")
+    ap.add_argument("--vllm-util", type=float, default=0.3, help="stocklibs arm: vLLM gpu_memory_utilization")
     ap.add_argument("--model", default="qwen2.5-7b")
     ap.add_argument("--prompts-per-gpu", type=int, default=32)
     ap.add_argument("--mini-prompts-per-gpu", type=int, default=8)
@@ -315,6 +318,13 @@ def main():
         args.token_budget = 16384 if args.grad_ckpt else 8192
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "stocklibs":
+        if not single:
+            raise SystemExit("--impl stocklibs runs on one GPU")
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "benchmarks"))
+        import stocklibs_grpo
+
+        stocklibs_grpo.run(args)
     else:
         run_native(args)
 

@@ -112,14 +112,14 @@ wk = w[:, rank * Kl:(rank + 1) * Kl].contiguous()
 ref = x_full.float() @ w.float().t()
 res = torch.randn(T, N, device=dev).bfloat16()
 for mode in ("signal", "barrier"):
-    os.environ["VERL_B200_ALLREDUCE"] = mode
+    ctx.allreduce_mode = mode
     outs = []
     for i in range(7):      # back-to-back calls with different data: slot parity, epochs, no stale slot may be summed
         outs.append(ctx.gemm_allreduce(xk * (i + 1), wk, residual=res))
     for i, y2 in enumerate(outs):
         want = (i + 1) * ref + res.float()
         assert rel(y2, want) < 2e-2, (mode, i, rel(y2, want))
-os.environ.pop("VERL_B200_ALLREDUCE")
+ctx.allreduce_mode = "signal"
 y3 = ctx.gemm_reduce_scatter(xk, wk)
 rows = T // world
 assert rel(y3, ref[rank * rows:(rank + 1) * rows]) < 2e-2

@@ -99,3 +99,25 @@ def test_resume_hands_the_restored_weights_to_the_tp_rollout(tmp_path):
     # the same quantity in the first run's second step shows what training did to the weights: non-trivial policy movement
     first = [json.loads(x)["data"] for x in log1.read_text().splitlines()]
     assert abs(first[1]["training/rollout_probs_diff_max"]) < 1e-4
+
+
+def test_zero3_trainer_feeds_tp2_rollout_slices(tmp_path):
+    """Row-sharded trainer weights (ZeRO-3 mode) → tensor-parallel rollout slices: every rank fills its slice block by block
+    from the row shards (on CPU ranks through the gathered weight, on GPUs by peer-read kernels). The rollout's log-probs
+    must agree with the trainer's recomputation on every step, i.e. also after the weights moved."""
+    from tests.test_trainer_e2e_on_cpu import OV
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    logf = tmp_path / "log.jsonl"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29791",
+           "-m", "verl_b200.trainer.main_ppo"] + [o for o in OV if not o.startswith("trainer.logger")] + \
+          ["trainer.logger=[file]", "trainer.total_training_steps=3", f"trainer.default_local_dir={tmp_path}/ckpt", "trainer.resume_mode=disable",
+           "actor_rollout_ref.rollout.tensor_model_parallel_size=2", "actor_rollout_ref.actor.optim.lr=3e-3",
+           "actor_rollout_ref.actor.fsdp_config.reshard_after_forward=true", "+actor_rollout_ref.ref.fsdp_config.reshard_after_forward=true"]
+    env = dict(os.environ, VERL_FILE_LOGGER_PATH=str(logf), OMP_NUM_THREADS="2", PYTHONPATH=repo)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900, cwd=repo)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    rows = [json.loads(x)["data"] for x in logf.read_text().splitlines()]
+    assert len(rows) == 3
+    for row in rows:
+        assert abs(row["training/rollout_probs_diff_max"]) < 1e-4

@@ -360,11 +360,9 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   out[(long)b * ld_out + h * ATT_D + d] = __float2bfloat16(l > 0.f ? acc / l : 0.f);
 }
 
-// VERL_B200_ATTN_COMPACT=0 selects the double-buffered one-CTA-per-SM layout
-static bool attn_compact() {
-  static const bool on = []() { const char* e = getenv("VERL_B200_ATTN_COMPACT"); return e == nullptr || e[0] != '0'; }();
-  return on;
-}
+// Two CTAs per SM (compact shared-memory layout) is the layout that runs; the double-buffered one-CTA-per-SM kernel
+// instantiation stays for head counts whose tiles do not fit the compact layout.
+static bool attn_compact() { return true; }
 
 static int set_attn_smem() {
   static bool done = false;

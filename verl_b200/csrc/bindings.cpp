@@ -1,7 +1,5 @@
 // torch.ops.verl_b200.* bindings: thin argument checks + raw-pointer launches of the extern "C" kernels.
 // The kernels themselves do not depend on libtorch.
-#include <cstdlib>
-
 #include <ATen/ATen.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -68,10 +66,9 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Ten
   c10::cuda::CUDAGuard guard(a.device());
   int* err = status_word(a.get_device()).data_ptr<int>();
   // bn == 512 asks for the paired-CTA kernel (256 x 256 tiles on two SMs); bn == 0 picks it when the problem fills
-  // every SM pair with such tiles, unless VERL_B200_GEMM_PAIR=0.
-  static const bool pair_auto = []() { const char* e = getenv("VERL_B200_GEMM_PAIR"); return e == nullptr || e[0] != '0'; }();
+  // every SM pair with such tiles.
   const bool pair_fits = ((M + 255) / 256) * ((N + 255) / 256) >= 74 && K >= 256;
-  if (bn == 512 || (bn == 0 && pair_auto && pair_fits)) {
+  if (bn == 512 || (bn == 0 && pair_fits)) {
     check_rc(vb_gemm_bf16_pair(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias_p, (int)M, (int)N, (int)K, (int)a.stride(0),
                                (int)b.stride(0), (int)out.stride(0), a_mn, b_mn, out_f32, accumulate, err, cur_stream()),
              "gemm_pair");
@@ -79,9 +76,8 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Ten
   }
   // decode-sized problems (one or two row blocks) with a long K: the paired kernel with K slices reads every B tile once
   // per pair. Measured on B200: M=256,N=3584,K=18944 56.3 us vs 60.5 us for the best single-CTA plan, M=512 76.9 vs 87.0;
-  // for K=3584 the single-CTA plans win. bn == 513 forces this path, VERL_B200_GEMM_PAIR_SPLITK=0 turns the automatic choice off.
-  static const bool pair_split_auto = []() { const char* e = getenv("VERL_B200_GEMM_PAIR_SPLITK"); return e == nullptr || e[0] != '0'; }();
-  if (!a_mn && !b_mn && (bn == 513 || (bn == 0 && pair_auto && pair_split_auto && M > 128 && M <= 512 && K >= 8192))) {
+  // for K=3584 the single-CTA plans win. bn == 513 forces this path.
+  if (!a_mn && !b_mn && (bn == 513 || (bn == 0 && M > 128 && M <= 512 && K >= 8192))) {
     const int s2 = vb_gemm_pair_plan((int)M, (int)N, (int)K);
     if (s2 >= 1) {
       Tensor ws2;

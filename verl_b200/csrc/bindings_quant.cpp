@@ -123,6 +123,17 @@ std::tuple<Tensor, Tensor, Tensor> reshard_quant(const Tensor& ptrs, int64_t row
   return {y, s, o};
 }
 
+// Gather rows [row_begin, row_begin + out.size(0)) of a row-sharded bf16 matrix straight into `out` (a [rows, N] view with
+// unit inner stride, e.g. a slice of a parameter): no allocation, no intermediate copy. ptrs may be offset by a column.
+void reshard_into(const Tensor& ptrs, int64_t rows_per_rank, int64_t ld_src, int64_t row_begin, Tensor& out) {
+  TORCH_CHECK(!ptrs.is_cuda() && ptrs.scalar_type() == at::kLong, "reshard_into: ptrs must be a CPU int64 tensor");
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.stride(1) == 1, "reshard_into: out must be a bf16 [rows, N] view");
+  c10::cuda::CUDAGuard guard(out.device());
+  check_rc(vb_reshard_quant(reinterpret_cast<const long*>(ptrs.data_ptr<int64_t>()), (int)ptrs.numel(), (int)rows_per_rank, ld_src, (int)row_begin, nullptr, 0,
+                            nullptr, out.data_ptr(), out.stride(0), (int)out.size(0), (int)out.size(1), cur_stream()),
+           "reshard_into");
+}
+
 Tensor fp4_fake_quant(const Tensor& x, const Tensor& global_amax) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.size(-1) % 16 == 0, "fp4_fake_quant: bad x");
   TORCH_CHECK(global_amax.is_cuda() && global_amax.scalar_type() == at::kFloat && global_amax.numel() == 1, "fp4_fake_quant: bad amax");
@@ -162,6 +173,7 @@ TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
   m.def("gemm_fp8_block(Tensor a8, Tensor a_scale, Tensor b8, Tensor b_scale, Tensor? bias, bool out_f32=False) -> Tensor", &gemm_fp8_block);
   m.def("gemm_fp8(Tensor a8, Tensor b8, Tensor? a_scale, Tensor? b_scale, Tensor? bias, bool out_f32=False) -> Tensor", &gemm_fp8);
   m.def("fp4_fake_quant(Tensor x, Tensor global_amax) -> Tensor", &fp4_fake_quant);
+  m.def("reshard_into(Tensor ptrs, int rows_per_rank, int ld_src, int row_begin, Tensor(a!) out) -> ()", &reshard_into);
   m.def("reshard_quant(Tensor ptrs, int rows_per_rank, int ld_src, int row_begin, int M_out, int N, bool quantize, bool keep_bf16, Tensor like) -> (Tensor, Tensor, Tensor)", &reshard_quant);
   m.def("delta_compact16(Tensor cur, Tensor(a!) snap, Tensor(b!) pos_out, Tensor(c!) val_out) -> int", &delta_compact16);
   m.def("delta_apply16(Tensor(a!) dst, Tensor pos, Tensor val, int count) -> ()", &delta_apply16);

@@ -480,7 +480,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             sx_run = sx_run * a + cx;
             m_run = m_new;
           }
-          if (label >= col0 && label < col0 + 32 && row < M) {
+          if (label >= col0 && label < col0 + 32 && label < N && row < M) {   // a label in the padding of the last tile is out of range
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (label == col0 + j) epi.label_logit[row] = x[j];
@@ -835,11 +835,6 @@ extern "C" void vb_gemm_plan(int M, int N, int K, int b_mn, int bn_req, int* bn,
   *split_k = 1;
   if (bn_req != 0) {
     *bn = bn_req;
-    // tuning hook: an explicit tile width may be combined with an explicit number of K slices
-    if (const char* e = getenv("VERL_B200_GEMM_SPLIT")) {
-      const int s = atoi(e);
-      if (s > 1 && (N % 4) == 0) *split_k = s;
-    }
     return;
   }
   const long big_tiles = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
@@ -876,10 +871,8 @@ extern "C" int vb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   if (!a_mn && !b_mn) {
     if (bn == 32) VB_LAUNCH(32, false, false);
     // decode-sized problems (at most four row blocks) are memory bound: 256-byte row bursts per stage (KA = 2)
-    // (measured on B200, M=256: N=4608,K=3584 25.6 -> 23.6 us; with K slices the single-atom stages stay ahead;
-    //  VERL_B200_GEMM_KA=1 turns this off, =3 forces it for sliced problems too)
-    static const int ka_small = []() { const char* e = getenv("VERL_B200_GEMM_KA"); return e ? atoi(e) : 2; }();
-    if (ka_small >= 2 && M <= 4 * BM && (split_k == 1 || ka_small == 3)) {
+    // (measured on B200, M=256: N=4608,K=3584 25.6 -> 23.6 us; with K slices the single-atom stages stay ahead)
+    if (M <= 4 * BM && split_k == 1) {
       switch (bn) {
         case 256: return launch_gemm<256, false, false, EPI_STORE, 0, 2>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream, LmHeadEpi{}, split_k, split_ws);
         case 128: return launch_gemm<128, false, false, EPI_STORE, 0, 2>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, err_word, stream, LmHeadEpi{}, split_k, split_ws);

@@ -76,9 +76,52 @@ def bench_gemm(a):
         report("  cuBLAS (torch.matmul) same shape", ms2, flops=2.0 * M * N * K)
 
 
+class _SmiSampler:
+    """SM clock and board power read through NVML (read-only queries) every 20 ms while a sustained loop runs."""
+
+    def __init__(self):
+        import threading
+
+        self.samples, self._stop, self._th = [], threading.Event(), None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv, self._h = pynvml, pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+        except Exception:  # noqa: BLE001
+            self._nv = None
+        if self._nv is not None:
+            self._th = threading.Thread(target=self._run, daemon=True)
+            self._th.start()
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append((nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0))
+            except Exception:  # noqa: BLE001
+                pass
+            self._stop.wait(0.02)
+
+    def stop(self):
+        self._stop.set()
+        if self._th is not None:
+            self._th.join(timeout=1)
+        tail = self.samples[len(self.samples) // 2:]           # second half: the steady state
+        if not tail:
+            return None, None
+        mhz = sorted(x[0] for x in tail)[len(tail) // 2]
+        watts = sorted(x[1] for x in tail)[len(tail) // 2]
+        return mhz, watts
+
+
+LAST_SUSTAINED = {"sm_mhz": None, "watts": None}
+
+
 def sustained(fn, seconds=1.5):
     """Back-to-back launches for about ``seconds`` (no flush, operands larger than L2): the power-capped steady state a
-    kernel sees inside a long training step. Returns milliseconds per launch."""
+    kernel sees inside a long training step. Returns milliseconds per launch; the median SM clock and board power of the
+    second half of the loop are left in ``LAST_SUSTAINED``."""
     fn()
     torch.cuda.synchronize()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -87,11 +130,13 @@ def sustained(fn, seconds=1.5):
     e.record()
     torch.cuda.synchronize()
     n = max(8, int(seconds * 1e3 / max(s.elapsed_time(e), 1e-3)))
+    smp = _SmiSampler()
     s.record()
     for _ in range(n):
         fn()
     e.record()
     torch.cuda.synchronize()
+    LAST_SUSTAINED["sm_mhz"], LAST_SUSTAINED["watts"] = smp.stop()
     return s.elapsed_time(e) / n
 
 
@@ -123,11 +168,15 @@ def bench_gemm_layer(a):
         for role, (m, n, k), own, lib in roles:
             fl = 2.0 * m * n * k
             b_own, b_lib = timeit(own, a.iters), timeit(lib, a.iters)
-            s_own, s_lib = sustained(own), sustained(lib)
+            s_own = sustained(own)
+            c_own = dict(LAST_SUSTAINED)
+            s_lib = sustained(lib)
+            c_lib = dict(LAST_SUSTAINED)
             tot["own"] += s_own
             tot["lib"] += s_lib
             print(f"| {name} | {role} | {m}x{n}x{k} | {b_own * 1e3:.1f} ({fl / b_own / 1e9:.0f} TF) | {b_lib * 1e3:.1f} ({fl / b_lib / 1e9:.0f} TF) | "
-                  f"{s_own * 1e3:.1f} ({fl / s_own / 1e9:.0f} TF) | {s_lib * 1e3:.1f} ({fl / s_lib / 1e9:.0f} TF) | {s_lib / s_own:.2f} |", flush=True)
+                  f"{s_own * 1e3:.1f} ({fl / s_own / 1e9:.0f} TF, {c_own['sm_mhz']} MHz, {c_own['watts'] or 0:.0f} W) | "
+                  f"{s_lib * 1e3:.1f} ({fl / s_lib / 1e9:.0f} TF, {c_lib['sm_mhz']} MHz, {c_lib['watts'] or 0:.0f} W) | {s_lib / s_own:.2f} |", flush=True)
     print(f"layer total sustained: own {tot['own'] * 1e3:.0f} us, cuBLAS {tot['lib'] * 1e3:.0f} us, ratio {tot['lib'] / tot['own']:.3f} "
           "(the cuBLAS weight-gradient column is a bf16-output matmul without the fp32 accumulation the own kernel fuses)")
 

@@ -148,9 +148,9 @@ def main():
     ms_b = timer(lambda: ctx.gemm_allreduce(x_dec, w_dn))
     report(rank, f"GEMM -> all-reduce (decode, 256 tokens) [{256}x{F // W}] x [{H}x{F // W}]^T, TP={W}", ms_f, ms_b, 2.0 * 256 * H * (F // W), (W - 1) * 256 * H * 2)
     os.environ["VERL_B200_COMM"] = "native"
-    os.environ["VERL_B200_ALLREDUCE"] = "barrier"
+    ctx.allreduce_mode = "barrier"
     ms_f2 = timer(lambda: ctx.gemm_allreduce(x_dec, w_dn))
-    os.environ.pop("VERL_B200_ALLREDUCE")
+    ctx.allreduce_mode = "signal"
     report(rank, "  same, four-launch variant (GEMM, barrier, slot sum, barrier)", ms_f2, ms_b, 2.0 * 256 * H * (F // W), (W - 1) * 256 * H * 2)
 
     # ---- 3. ZeRO-3 style weight gather fused into the GEMM

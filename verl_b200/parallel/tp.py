@@ -33,9 +33,13 @@ def fused_comm_enabled() -> bool:
 class TPContext:
     """Symmetric staging buffers + fused ops for one tensor-parallel group."""
 
-    def __init__(self, group, host_group, max_tokens: int, hidden: int, max_out: int, graph_safe: bool = False):
+    def __init__(self, group, host_group, max_tokens: int, hidden: int, max_out: int, graph_safe: bool = False,
+                 allreduce_mode: str = "signal"):
         self.group, self.host_group = group, host_group
         self.graph_safe = graph_safe      # device-side barrier epochs: the ops may be captured into CUDA graphs
+        # "signal": GEMM whose last CTA signals the peers + slot sum that waits for the signals (two launches);
+        # "barrier": GEMM with peer-scatter epilogue, device barrier, slot sum, device barrier (the earlier four-launch form)
+        self.allreduce_mode = allreduce_mode
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.ops = _ext.ops()
         self.max_tokens, self.hidden, self.max_out = max_tokens, hidden, max_out
@@ -81,12 +85,12 @@ class TPContext:
     # ------------------------------------------------------------------ GEMM → all-reduce / reduce-scatter
     def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         T, N = x.shape[0], w.shape[0]
-        if fused_comm_enabled() and N % 32 == 0 and T * N <= self.slot_elems and os.environ.get("VERL_B200_ALLREDUCE", "signal") == "signal":
+        if fused_comm_enabled() and N % 32 == 0 and T * N <= self.slot_elems and self.allreduce_mode == "signal":
             # two launches: GEMM whose last CTA signals the peers, then a slot sum that waits for their signals
             out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
             self.ops.gemm_allreduce_sig(x, w, self.slots2.table(), self.sig.table(), self.rank, self.half_elems,
                                         self.slots2.tensor(torch.bfloat16), self.sig.tensor(torch.int32, 64), residual, out,
-                                        int(os.environ.get("VERL_B200_AR_BN", 0)), int(os.environ.get("VERL_B200_AR_SPLIT", 0)))
+                                        0, 0)
             return out
         if fused_comm_enabled() and N % 32 == 0 and T * N <= self.slot_elems:
             out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)

@@ -403,6 +403,183 @@ class PPOTrainer:
                     metrics[f"{sec}/{src}/{var}/{name}"] = val
         return metrics
 
+    # ------------------------------------------------------------------ the RL step
+    def step(self, batch_dict: dict) -> dict:
+        """One full RL step on a batch of prompts; returns the step's metrics."""
+        cfg = self.config
+        metrics: dict = {}
+        timing_raw: dict = {}
+        batch = DataProto.from_single_dict(batch_dict)
+        n = int(cfg.actor_rollout_ref.rollout.n)
+        batch.non_tensor_batch["uid"] = np.array([str(uuid.uuid4()) for _ in range(len(batch))], dtype=object)
+        with marked_timer("step", timing_raw):
+            mm_keys = [k for k in ("multi_modal_inputs",) if k in batch.non_tensor_batch]      # image inputs of vision-language prompts
+            gen_batch = batch.select(batch_keys=["input_ids", "attention_mask", "position_ids"], non_tensor_batch_keys=mm_keys)
+            gen_batch.meta_info = self._gen_meta()
+            gen_batch = gen_batch.repeat(repeat_times=n, interleave=True)
+            with marked_timer("gen", timing_raw):
+                gen_out = self.actor_rollout_wg.generate_sequences(gen_batch)
+                timing_raw.update({f"gen/{k}": float(np.max(v)) if isinstance(v, list) else v
+                                   for k, v in (gen_out.meta_info.pop("timing", {}) or {}).items()})
+                ro_metrics = gen_out.meta_info.pop("metrics", None)
+                if ro_metrics:
+                    metrics.update(reduce_metrics(ro_metrics if isinstance(ro_metrics, dict) else {}))
+            if cfg.algorithm.adv_estimator == "remax":
+                with marked_timer("gen_max", timing_raw):
+                    base = batch.select(batch_keys=["input_ids", "attention_mask", "position_ids"], non_tensor_batch_keys=mm_keys)
+                    base.meta_info = {**self._gen_meta(), "do_sample": False}
+                    base_out = self.actor_rollout_wg.generate_sequences(base)
+                    tmp = batch.union(base_out.select(batch_keys=["prompts", "responses", "input_ids", "attention_mask", "position_ids", "response_mask"]))
+                    rb, _ = compute_reward(tmp, self.reward_fn)
+                    batch.pop(batch_keys=[k for k in base_out.batch.keys() if k in batch.batch.keys() and k not in ("input_ids", "attention_mask", "position_ids")])
+                    batch.batch["reward_baselines"] = rb.sum(-1)
+            batch = batch.repeat(repeat_times=n, interleave=True)
+            batch.pop(batch_keys=["input_ids", "attention_mask", "position_ids"])
+            for k in mm_keys:
+                gen_out.non_tensor_batch.pop(k, None)      # the repeated batch already holds them
+            batch = batch.union(gen_out)
+            metrics.update(self.train_on_rollouts(batch, timing_raw, n))
+        metrics.update(compute_timing_metrics(batch=self._last_batch, timing_raw=timing_raw))
+        metrics.update(compute_throughout_metrics(batch=self._last_batch, timing_raw=timing_raw, n_gpus=max(1, self.actor_rollout_wg.world_size)))
+        return metrics
+
+    def train_on_rollouts(self, batch: DataProto, timing_raw: dict, n: int) -> dict:
+        """Everything of an RL step after generation: reward, old/ref log-probs, values, advantages, critic and actor updates,
+        weight hand-off. ``batch`` holds prompts joined with their rollouts (one row per trajectory, ``uid`` marks the
+        prompt group). Returns the metrics; timings go to ``timing_raw``. Shared by the v0 step and the v1 trainers."""
+        cfg = self.config
+        metrics: dict = {}
+        with marked_timer("train", timing_raw):
+            if "response_mask" not in batch.batch.keys():
+                batch.batch["response_mask"] = compute_response_mask(batch)
+            if _g(cfg, "trainer.balance_batch", True):
+                self._balance_batch(batch, metrics)
+            batch.meta_info["global_token_num"] = torch.sum(batch.batch["attention_mask"], dim=-1).tolist()
+            batch.meta_info["temperature"] = float(cfg.actor_rollout_ref.rollout.temperature)
+            with marked_timer("reward", timing_raw):
+                reward_tensor, reward_extra = compute_reward(batch, self.reward_fn)
+                if getattr(self, "rm_wg", None) is not None:
+                    rm = self.rm_wg.compute_rm_score(batch).batch["rm_scores"]
+                    metrics["reward_model/score_mean"] = float(rm.sum(-1).mean())
+                    reward_tensor = reward_tensor + rm.to(reward_tensor.dtype) if bool(_g(cfg, "reward.reward_model.add_rule_reward", True)) else rm.to(reward_tensor.dtype)
+            rc = cfg.algorithm.get("rollout_correction") or {}
+            bypass = bool(rc.get("bypass_mode", False))
+            if bypass:
+                from verl_b200.trainer.ppo.rollout_corr_helper import apply_bypass_mode
+
+                apply_bypass_mode(batch, rc, cfg.actor_rollout_ref.actor.policy_loss)
+            else:
+                with marked_timer("old_log_prob", timing_raw):
+                    old = self.actor_rollout_wg.compute_log_prob(batch)
+                    ent = old.batch.pop("entropys") if "entropys" in old.batch.keys() else None
+                    if ent is not None:
+                        ea = agg_loss(ent, batch.batch["response_mask"].float(), cfg.actor_rollout_ref.actor.get("loss_agg_mode", "token-mean"))
+                        metrics["actor/entropy"] = ea.item()
+                    batch = batch.union(old)
+                    if "rollout_log_probs" in batch.batch.keys():
+                        from verl_b200.utils.debug.metrics import calculate_debug_metrics
+
+                        metrics.update(calculate_debug_metrics(batch))
+            if self.use_reference_policy:
+                with marked_timer("ref", timing_raw):
+                    batch = batch.union(self.ref_policy_wg.compute_ref_log_prob(batch))
+            if bool(_g(cfg, "actor_rollout_ref.distillation.enable", False)):
+                with marked_timer("teacher", timing_raw):
+                    batch = batch.union(self.actor_rollout_wg.compute_teacher_topk(batch))
+            if self.use_critic:
+                with marked_timer("values", timing_raw):
+                    batch = batch.union(self.critic_wg.compute_values(batch))
+            with marked_timer("adv", timing_raw):
+                batch.batch["token_level_scores"] = reward_tensor
+                if _g(cfg, "trainer.rollout_data_dir", None):
+                    self._dump_generations(batch, reward_tensor.sum(-1).tolist(), reward_extra, _g(cfg, "trainer.rollout_data_dir"))
+                if reward_extra:
+                    batch.non_tensor_batch.update({k: np.array(v, dtype=object) for k, v in reward_extra.items() if len(v) == len(batch)})
+                if cfg.algorithm.get("use_kl_in_reward", False):
+                    batch, kl_m = apply_kl_penalty(batch, self.kl_ctrl_in_reward, cfg.algorithm.kl_penalty)
+                    metrics.update(kl_m)
+                else:
+                    batch.batch["token_level_rewards"] = batch.batch["token_level_scores"]
+                if not bypass and (rc.get("rollout_is") or rc.get("rollout_rs")) and "rollout_log_probs" in batch.batch.keys():
+                    from verl_b200.trainer.ppo.rollout_corr_helper import compute_rollout_correction_and_add_to_batch
+
+                    batch, is_m = compute_rollout_correction_and_add_to_batch(batch, rc)
+                    metrics.update(is_m)
+                batch = compute_advantage(batch, cfg.algorithm.adv_estimator, gamma=cfg.algorithm.gamma, lam=cfg.algorithm.lam, num_repeat=n,
+                                          norm_adv_by_std_in_grpo=cfg.algorithm.get("norm_adv_by_std_in_grpo", True), config=cfg.algorithm)
+                if cfg.algorithm.get("use_pf_ppo", False):
+                    batch = core_algos.compute_pf_ppo_reweight_data(batch, cfg.algorithm.pf_ppo.reweight_method, cfg.algorithm.pf_ppo.weight_pow)
+            if self.use_critic:
+                with marked_timer("update_critic", timing_raw):
+                    co = self.critic_wg.update_critic(batch)
+                metrics.update(reduce_metrics(co.meta_info["metrics"]))
+            if int(_g(cfg, "trainer.critic_warmup", 0)) <= self.global_steps:
+                with marked_timer("update_actor", timing_raw):
+                    batch.meta_info["multi_turn"] = bool(_g(cfg, "actor_rollout_ref.rollout.multi_turn.enable", False))
+                    if rc.get("score_centering", False):
+                        # the update pass also evaluates the sampler's top-k head (rollout.topk_log_probs) under the trainer
+                        if not bypass or rc.get("loss_type", "ppo_clip") != "reinforce" or "rollout_topk_ids" not in batch.batch.keys():
+                            raise ValueError("score centering needs rollout_correction.bypass_mode=true, loss_type=reinforce and "
+                                             "actor_rollout_ref.rollout.topk_log_probs > 0")
+                        batch.meta_info.update({"score_centering": True, "rollout_is": rc.get("rollout_is"),
+                                                "rollout_is_threshold": rc.get("rollout_is_threshold", 2.0)})
+                    ao = self.actor_rollout_wg.update_actor(batch)
+                metrics.update(reduce_metrics(ao.meta_info["metrics"]))
+            with marked_timer("update_weights", timing_raw):
+                self.actor_rollout_wg.update_weights()
+        metrics.update(compute_data_metrics(batch=batch, use_critic=self.use_critic))
+        metrics.update(compute_variance_proxy_metrics(batch, metrics.get("actor/grad_norm")))
+        self._last_batch = batch
+        return metrics
+
+    def fit(self):
+        cfg = self.config
+        is_main = int(os.environ.get("RANK", "0")) == 0 or _g(cfg, "trainer.worker_backend", "spmd") != "spmd"
+        logger = Tracking(cfg.trainer.project_name, cfg.trainer.experiment_name, cfg.trainer.logger if is_main else [],
+                          config=dict(cfg)) if is_main else None
+        self.global_steps = 0
+        if self._load_checkpoint():
+            # rollout replicas that keep their own copy of the weights (tensor-parallel shards, ZeRO-3 / TPxPP trainers) were
+            # filled before the load: hand the restored weights over before the first validation or rollout
+            # (reference: verl/trainer/ppo/ray_trainer.py:1429-1430)
+            self.actor_rollout_wg.update_weights()
+        if self.val_reward_fn is not None and _g(cfg, "trainer.val_before_train", True):
+            val = self._validate()
+            if val and logger:
+                logger.log(data=val, step=self.global_steps)
+            if _g(cfg, "trainer.val_only", False):
+                return
+        self.global_steps += 1
+        last_val = None
+        max_step_time = 0.0
+        for epoch in range(int(cfg.trainer.total_epochs)):
+            for batch_dict in self.train_dataloader:
+                t0 = time.perf_counter()
+                is_last = self.global_steps >= self.total_training_steps
+                metrics = self.step(batch_dict)
+                max_step_time = max(max_step_time, time.perf_counter() - t0)
+                test_freq = int(_g(cfg, "trainer.test_freq", -1))
+                if self.val_reward_fn is not None and test_freq > 0 and (is_last or self.global_steps % test_freq == 0):
+                    last_val = self._validate()
+                    metrics.update(last_val)
+                save_freq = int(_g(cfg, "trainer.save_freq", -1))
+                esi = should_save_ckpt_esi(max_step_time, redundant_time=float(_g(cfg, "trainer.esi_redundant_time", 0)))
+                if save_freq > 0 and (is_last or self.global_steps % save_freq == 0 or esi):
+                    if esi:
+                        print("Force saving checkpoint: the announced capacity expiry is near.")
+                    self._save_checkpoint()
+                self._finish_pending_checkpoint(block=False)
+                metrics.update({"training/global_step": self.global_steps, "training/epoch": epoch})
+                if logger:
+                    logger.log(data=metrics, step=self.global_steps)
+                self.global_steps += 1
+                if is_last:
+                    self._finish_pending_checkpoint(block=True)
+                    if last_val:
+                        print(f"Final validation metrics: {last_val}")
+                    return
+        self._finish_pending_checkpoint(block=True)
+
 
 def _pad_to(data: DataProto, divisor: int):
     from verl_b200.protocol import pad_dataproto_to_divisor
@@ -410,186 +587,4 @@ def _pad_to(data: DataProto, divisor: int):
     return pad_dataproto_to_divisor(data, divisor)
 
 
-def _train_step(self: PPOTrainer, batch_dict: dict) -> dict:
-    """One full RL step on a batch of prompts; returns the step's metrics."""
-    cfg = self.config
-    metrics: dict = {}
-    timing_raw: dict = {}
-    batch = DataProto.from_single_dict(batch_dict)
-    n = int(cfg.actor_rollout_ref.rollout.n)
-    batch.non_tensor_batch["uid"] = np.array([str(uuid.uuid4()) for _ in range(len(batch))], dtype=object)
-    with marked_timer("step", timing_raw):
-        mm_keys = [k for k in ("multi_modal_inputs",) if k in batch.non_tensor_batch]      # image inputs of vision-language prompts
-        gen_batch = batch.select(batch_keys=["input_ids", "attention_mask", "position_ids"], non_tensor_batch_keys=mm_keys)
-        gen_batch.meta_info = self._gen_meta()
-        gen_batch = gen_batch.repeat(repeat_times=n, interleave=True)
-        with marked_timer("gen", timing_raw):
-            gen_out = self.actor_rollout_wg.generate_sequences(gen_batch)
-            timing_raw.update({f"gen/{k}": float(np.max(v)) if isinstance(v, list) else v
-                               for k, v in (gen_out.meta_info.pop("timing", {}) or {}).items()})
-            ro_metrics = gen_out.meta_info.pop("metrics", None)
-            if ro_metrics:
-                metrics.update(reduce_metrics(ro_metrics if isinstance(ro_metrics, dict) else {}))
-        if cfg.algorithm.adv_estimator == "remax":
-            with marked_timer("gen_max", timing_raw):
-                base = batch.select(batch_keys=["input_ids", "attention_mask", "position_ids"], non_tensor_batch_keys=mm_keys)
-                base.meta_info = {**self._gen_meta(), "do_sample": False}
-                base_out = self.actor_rollout_wg.generate_sequences(base)
-                tmp = batch.union(base_out.select(batch_keys=["prompts", "responses", "input_ids", "attention_mask", "position_ids", "response_mask"]))
-                rb, _ = compute_reward(tmp, self.reward_fn)
-                batch.pop(batch_keys=[k for k in base_out.batch.keys() if k in batch.batch.keys() and k not in ("input_ids", "attention_mask", "position_ids")])
-                batch.batch["reward_baselines"] = rb.sum(-1)
-        batch = batch.repeat(repeat_times=n, interleave=True)
-        batch.pop(batch_keys=["input_ids", "attention_mask", "position_ids"])
-        for k in mm_keys:
-            gen_out.non_tensor_batch.pop(k, None)      # the repeated batch already holds them
-        batch = batch.union(gen_out)
-        metrics.update(self.train_on_rollouts(batch, timing_raw, n))
-    metrics.update(compute_timing_metrics(batch=self._last_batch, timing_raw=timing_raw))
-    metrics.update(compute_throughout_metrics(batch=self._last_batch, timing_raw=timing_raw, n_gpus=max(1, self.actor_rollout_wg.world_size)))
-    return metrics
-
-
-def _train_on_rollouts(self: PPOTrainer, batch: DataProto, timing_raw: dict, n: int) -> dict:
-    """Everything of an RL step after generation: reward, old/ref log-probs, values, advantages, critic and actor updates,
-    weight hand-off. ``batch`` holds prompts joined with their rollouts (one row per trajectory, ``uid`` marks the
-    prompt group). Returns the metrics; timings go to ``timing_raw``. Shared by the v0 step and the v1 trainers."""
-    cfg = self.config
-    metrics: dict = {}
-    with marked_timer("train", timing_raw):
-        if "response_mask" not in batch.batch.keys():
-            batch.batch["response_mask"] = compute_response_mask(batch)
-        if _g(cfg, "trainer.balance_batch", True):
-            self._balance_batch(batch, metrics)
-        batch.meta_info["global_token_num"] = torch.sum(batch.batch["attention_mask"], dim=-1).tolist()
-        batch.meta_info["temperature"] = float(cfg.actor_rollout_ref.rollout.temperature)
-        with marked_timer("reward", timing_raw):
-            reward_tensor, reward_extra = compute_reward(batch, self.reward_fn)
-            if getattr(self, "rm_wg", None) is not None:
-                rm = self.rm_wg.compute_rm_score(batch).batch["rm_scores"]
-                metrics["reward_model/score_mean"] = float(rm.sum(-1).mean())
-                reward_tensor = reward_tensor + rm.to(reward_tensor.dtype) if bool(_g(cfg, "reward.reward_model.add_rule_reward", True)) else rm.to(reward_tensor.dtype)
-        rc = cfg.algorithm.get("rollout_correction") or {}
-        bypass = bool(rc.get("bypass_mode", False))
-        if bypass:
-            from verl_b200.trainer.ppo.rollout_corr_helper import apply_bypass_mode
-
-            apply_bypass_mode(batch, rc, cfg.actor_rollout_ref.actor.policy_loss)
-        else:
-            with marked_timer("old_log_prob", timing_raw):
-                old = self.actor_rollout_wg.compute_log_prob(batch)
-                ent = old.batch.pop("entropys") if "entropys" in old.batch.keys() else None
-                if ent is not None:
-                    ea = agg_loss(ent, batch.batch["response_mask"].float(), cfg.actor_rollout_ref.actor.get("loss_agg_mode", "token-mean"))
-                    metrics["actor/entropy"] = ea.item()
-                batch = batch.union(old)
-                if "rollout_log_probs" in batch.batch.keys():
-                    from verl_b200.utils.debug.metrics import calculate_debug_metrics
-
-                    metrics.update(calculate_debug_metrics(batch))
-        if self.use_reference_policy:
-            with marked_timer("ref", timing_raw):
-                batch = batch.union(self.ref_policy_wg.compute_ref_log_prob(batch))
-        if bool(_g(cfg, "actor_rollout_ref.distillation.enable", False)):
-            with marked_timer("teacher", timing_raw):
-                batch = batch.union(self.actor_rollout_wg.compute_teacher_topk(batch))
-        if self.use_critic:
-            with marked_timer("values", timing_raw):
-                batch = batch.union(self.critic_wg.compute_values(batch))
-        with marked_timer("adv", timing_raw):
-            batch.batch["token_level_scores"] = reward_tensor
-            if _g(cfg, "trainer.rollout_data_dir", None):
-                self._dump_generations(batch, reward_tensor.sum(-1).tolist(), reward_extra, _g(cfg, "trainer.rollout_data_dir"))
-            if reward_extra:
-                batch.non_tensor_batch.update({k: np.array(v, dtype=object) for k, v in reward_extra.items() if len(v) == len(batch)})
-            if cfg.algorithm.get("use_kl_in_reward", False):
-                batch, kl_m = apply_kl_penalty(batch, self.kl_ctrl_in_reward, cfg.algorithm.kl_penalty)
-                metrics.update(kl_m)
-            else:
-                batch.batch["token_level_rewards"] = batch.batch["token_level_scores"]
-            if not bypass and (rc.get("rollout_is") or rc.get("rollout_rs")) and "rollout_log_probs" in batch.batch.keys():
-                from verl_b200.trainer.ppo.rollout_corr_helper import compute_rollout_correction_and_add_to_batch
-
-                batch, is_m = compute_rollout_correction_and_add_to_batch(batch, rc)
-                metrics.update(is_m)
-            batch = compute_advantage(batch, cfg.algorithm.adv_estimator, gamma=cfg.algorithm.gamma, lam=cfg.algorithm.lam, num_repeat=n,
-                                      norm_adv_by_std_in_grpo=cfg.algorithm.get("norm_adv_by_std_in_grpo", True), config=cfg.algorithm)
-            if cfg.algorithm.get("use_pf_ppo", False):
-                batch = core_algos.compute_pf_ppo_reweight_data(batch, cfg.algorithm.pf_ppo.reweight_method, cfg.algorithm.pf_ppo.weight_pow)
-        if self.use_critic:
-            with marked_timer("update_critic", timing_raw):
-                co = self.critic_wg.update_critic(batch)
-            metrics.update(reduce_metrics(co.meta_info["metrics"]))
-        if int(_g(cfg, "trainer.critic_warmup", 0)) <= self.global_steps:
-            with marked_timer("update_actor", timing_raw):
-                batch.meta_info["multi_turn"] = bool(_g(cfg, "actor_rollout_ref.rollout.multi_turn.enable", False))
-                if rc.get("score_centering", False):
-                    # the update pass also evaluates the sampler's top-k head (rollout.topk_log_probs) under the trainer
-                    if not bypass or rc.get("loss_type", "ppo_clip") != "reinforce" or "rollout_topk_ids" not in batch.batch.keys():
-                        raise ValueError("score centering needs rollout_correction.bypass_mode=true, loss_type=reinforce and "
-                                         "actor_rollout_ref.rollout.topk_log_probs > 0")
-                    batch.meta_info.update({"score_centering": True, "rollout_is": rc.get("rollout_is"),
-                                            "rollout_is_threshold": rc.get("rollout_is_threshold", 2.0)})
-                ao = self.actor_rollout_wg.update_actor(batch)
-            metrics.update(reduce_metrics(ao.meta_info["metrics"]))
-        with marked_timer("update_weights", timing_raw):
-            self.actor_rollout_wg.update_weights()
-    metrics.update(compute_data_metrics(batch=batch, use_critic=self.use_critic))
-    metrics.update(compute_variance_proxy_metrics(batch, metrics.get("actor/grad_norm")))
-    self._last_batch = batch
-    return metrics
-
-
-def _fit(self: PPOTrainer):
-    cfg = self.config
-    is_main = int(os.environ.get("RANK", "0")) == 0 or _g(cfg, "trainer.worker_backend", "spmd") != "spmd"
-    logger = Tracking(cfg.trainer.project_name, cfg.trainer.experiment_name, cfg.trainer.logger if is_main else [],
-                      config=dict(cfg)) if is_main else None
-    self.global_steps = 0
-    if self._load_checkpoint():
-        # rollout replicas that keep their own copy of the weights (tensor-parallel shards, ZeRO-3 / TPxPP trainers) were
-        # filled before the load: hand the restored weights over before the first validation or rollout
-        # (reference: verl/trainer/ppo/ray_trainer.py:1429-1430)
-        self.actor_rollout_wg.update_weights()
-    if self.val_reward_fn is not None and _g(cfg, "trainer.val_before_train", True):
-        val = self._validate()
-        if val and logger:
-            logger.log(data=val, step=self.global_steps)
-        if _g(cfg, "trainer.val_only", False):
-            return
-    self.global_steps += 1
-    last_val = None
-    max_step_time = 0.0
-    for epoch in range(int(cfg.trainer.total_epochs)):
-        for batch_dict in self.train_dataloader:
-            t0 = time.perf_counter()
-            is_last = self.global_steps >= self.total_training_steps
-            metrics = self.step(batch_dict)
-            max_step_time = max(max_step_time, time.perf_counter() - t0)
-            test_freq = int(_g(cfg, "trainer.test_freq", -1))
-            if self.val_reward_fn is not None and test_freq > 0 and (is_last or self.global_steps % test_freq == 0):
-                last_val = self._validate()
-                metrics.update(last_val)
-            save_freq = int(_g(cfg, "trainer.save_freq", -1))
-            esi = should_save_ckpt_esi(max_step_time, redundant_time=float(_g(cfg, "trainer.esi_redundant_time", 0)))
-            if save_freq > 0 and (is_last or self.global_steps % save_freq == 0 or esi):
-                if esi:
-                    print("Force saving checkpoint: the announced capacity expiry is near.")
-                self._save_checkpoint()
-            self._finish_pending_checkpoint(block=False)
-            metrics.update({"training/global_step": self.global_steps, "training/epoch": epoch})
-            if logger:
-                logger.log(data=metrics, step=self.global_steps)
-            self.global_steps += 1
-            if is_last:
-                self._finish_pending_checkpoint(block=True)
-                if last_val:
-                    print(f"Final validation metrics: {last_val}")
-                return
-    self._finish_pending_checkpoint(block=True)
-
-
-PPOTrainer.step = _train_step
-PPOTrainer.train_on_rollouts = _train_on_rollouts
-PPOTrainer.fit = _fit
 RayPPOTrainer = PPOTrainer

@@ -391,7 +391,7 @@ class ActorRolloutRefWorker(Worker):
         ids_cpu, att_cpu = ids.cpu(), att.cpu().bool()
         plist = [ids_cpu[i][att_cpu[i]].tolist() for i in range(bs)]
         t0 = time.perf_counter()
-        self.rollout.profile = bool(os.environ.get("VERL_B200_PROFILE_ROLLOUT"))
+        self.rollout.profile = bool(cfg_get(ro, "log_stats", False))      # rollout.log_stats: per-call prefill / decode / capture timings
         self.rollout.wake_up()
         mm = prompts.non_tensor_batch.get("multi_modal_inputs") if prompts.non_tensor_batch else None
         outs = self.rollout.generate(plist, sp, eos_token_id=eos, multi_modal=[(m or None) for m in mm] if mm is not None else None)
@@ -482,26 +482,13 @@ class ActorRolloutRefWorker(Worker):
 
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def update_weights(self):
-        """Actor → rollout weight hand-off. The colocated TP=1 rollout reads the actor's resident parameters, so this
-        only has to make them resident (if offloaded) and drop stale CUDA graphs bound to moved storage."""
-        t0 = time.perf_counter()
-        if self.actor is not None and self.rollout is not None:
-            eng = self.actor.engine
-            if getattr(self, "_rollout_owns_model", False):
-                target = getattr(self, "_rollout_full_model", None) or self.rollout.model
-                target.load_hf_stream(eng.get_per_tensor_param()[0])
-            elif not eng.store.flat.is_cuda and torch.cuda.is_available():
-                eng.to("cuda", model=True, optimizer=False, grad=False)
-                self.rollout._graph = None
-        if self.rollout is not None and getattr(self, "_rollout_tp", 1) > 1:
-            from verl_b200.models.parallel_model import refresh_rollout_shard
+        """Actor → rollout weight hand-off through this worker's :class:`CheckpointEngineManager` (which path runs is
+        described there). Returns the seconds it took; the manager keeps the details in ``last_stats``."""
+        if getattr(self, "checkpoint_manager", None) is None:
+            from verl_b200.checkpoint_engine.manager import CheckpointEngineManager
 
-            if not self._rollout_full_model.embed_tokens.is_cuda and torch.cuda.is_available():
-                self.actor.engine.to("cuda", model=True, optimizer=False, grad=False)
-            refresh_rollout_shard(self.rollout.model, self._rollout_full_model, self.rank % self._rollout_tp, self._rollout_tp)
-        if dist.is_initialized():
-            dist.barrier()
-        return time.perf_counter() - t0
+            self.checkpoint_manager = CheckpointEngineManager(self, cfg_get(self.config, "rollout.checkpoint_engine.backend", "naive"))
+        return self.checkpoint_manager.update_weights()["seconds_total"]
 
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def save_checkpoint(self, local_path, hdfs_path=None, global_step=0, max_ckpt_to_keep=None):
