@@ -52,6 +52,43 @@ def test_gemm_layouts(o, M, N, K, a_mn, b_mn, bn, f32, acc, bias):
     assert rel(out, ref) < (1e-5 if f32 else 8e-3)
 
 
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn,f32,acc,bias", [
+    (512, 1024, 256, False, False, False, False, False),       # two row blocks x two column tiles, exact fit
+    (520, 1160, 328, False, False, False, False, True),        # ragged M, N, K tails + bias
+    (768, 1544, 512, False, True, False, False, False),        # input-gradient layout
+    (776, 1032, 1096, True, True, True, True, False),          # weight-gradient layout: fp32 reduce-add into the output
+    (512, 1024, 512, True, True, True, False, False),          # fp32 store
+    (1024, 1024, 320, True, False, False, False, False),
+    (4096, 4608, 3584, False, False, False, False, True),      # several tiles per pair: accumulator hand-over between tiles
+    (2304, 19456, 512, False, False, False, False, False),     # more tiles than SM pairs, grouped tile order
+    (3584, 3584, 8192, True, True, True, True, False),         # 98 tiles on 74 pairs: K slices that reduce-add into the output
+])
+def test_gemm_pair512_with_canaries(o, M, N, K, a_mn, b_mn, f32, acc, bias):
+    """The 256 x 512-tile kernel (bn = 514) against an fp32 matmul. The output is a window inside a larger buffer whose
+    guard rows and columns must come back untouched: the TMA-store epilogue clips at the tensor-map extents."""
+    dev = "cuda"
+    torch.manual_seed(1)
+    a = (torch.randn(K, M, device=dev) if a_mn else torch.randn(M, K, device=dev)).bfloat16()
+    b = (torch.randn(K, N, device=dev) if b_mn else torch.randn(N, K, device=dev)).bfloat16()
+    bs = torch.randn(N, device=dev).bfloat16() if bias else None
+    dt = torch.float32 if f32 else torch.bfloat16
+    G = 8                                            # guard: 8 rows above/below, 8 columns left/right (keeps 16-byte alignment)
+    big = torch.full((M + 2 * G, N + 2 * G), 7.0, device=dev, dtype=dt)
+    out = big[G:G + M, G:G + N]
+    if acc:
+        out.copy_(torch.randn(M, N, device=dev))
+    base = out.float().clone() if acc else 0
+    o.gemm(a, b, out, bs, a_mn, b_mn, acc, 514)
+    assert status_ok(o)
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    ref = A @ B + base + (bs.float() if bias else 0)
+    assert rel(out, ref) < (5e-5 if f32 else 8e-3)
+    guard = big.clone()
+    guard[G:G + M, G:G + N] = 7.0
+    assert bool((guard == 7.0).all()), "the kernel wrote outside its output window"
+
+
 def test_elementwise_ops(o):
     from verl_b200.ops import functional as Fn
 

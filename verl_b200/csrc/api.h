@@ -88,6 +88,9 @@ int vb_gemm_fp8_pair(const void* A, const void* B, void* C, const void* bias, co
 int vb_gemm_fp8_block(const void* A, const void* B, void* C, const float* a_scale, const float* b_scale, const void* bias, int M, int N, int K,
                       int lda, int ldb, int ldc, int out_f32, int* err_word, cudaStream_t stream);
 int vb_gemm_pair_plan(int M, int N, int K);
+int vb_gemm_pair512_ok(const void* C, int ldc, int out_f32, int accumulate);
+int vb_gemm_bf16_pair512(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb, int ldc, int a_mn,
+                         int b_mn, int out_f32, int accumulate, int* err_word, cudaStream_t stream);
 int vb_gemm_bf16_pair_splitk(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb, int ldc, int out_f32,
                              int accumulate, int split_k, float* split_ws, int* err_word, cudaStream_t stream);
 void vb_allreduce_plan(int M, int N, int K, int* bn, int* split_k);

@@ -161,9 +161,9 @@ def bench_gemm_layer(a):
         dx = torch.empty(T, K, device="cuda", dtype=torch.bfloat16)
         dw = torch.zeros(N, K, device="cuda", dtype=torch.float32)
         roles = [
-            ("fwd", (T, N, K), lambda: o.gemm(x, w, y, None, False, False, False, 0), lambda: torch.matmul(x, w.t(), out=y)),
-            ("dgrad", (T, K, N), lambda: o.gemm(dy, w, dx, None, False, True, False, 0), lambda: torch.matmul(dy, w, out=dx)),
-            ("wgrad", (N, K, T), lambda: o.gemm(dy, x, dw, None, True, True, True, 0), lambda: torch.matmul(dy.t(), x)),
+            ("fwd", (T, N, K), lambda: o.gemm(x, w, y, None, False, False, False, a.bn), lambda: torch.matmul(x, w.t(), out=y)),
+            ("dgrad", (T, K, N), lambda: o.gemm(dy, w, dx, None, False, True, False, a.bn), lambda: torch.matmul(dy, w, out=dx)),
+            ("wgrad", (N, K, T), lambda: o.gemm(dy, x, dw, None, True, True, True, a.bn), lambda: torch.matmul(dy.t(), x)),
         ]
         for role, (m, n, k), own, lib in roles:
             fl = 2.0 * m * n * k

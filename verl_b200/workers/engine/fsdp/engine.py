@@ -513,7 +513,20 @@ class FSDPEngine(BaseEngine):
             if ent is not None:
                 out["entropy"] = torch.where(valid, ent[idx.reshape(-1)].reshape(idx.shape), full)
             return out
+        record = bool(meta.get("record_routing", False)) and self.cfg.is_moe and pb.routed_experts is None
+        if record:
+            for layer in self.model.layers:
+                layer.mlp.record_routing = True
         h = self.model.forward_hidden(pb)
+        if record:
+            # router replay R2: the experts this pass chose, laid out like input_ids so that the update pass can force them
+            rt = torch.stack([layer.mlp.last_topk for layer in self.model.layers], 1).to(torch.int16)      # [T, layers, topk]
+            att = mb["attention_mask"].bool()
+            full_rt = torch.full((*att.shape, *rt.shape[1:]), -1, dtype=torch.int16, device=rt.device)
+            full_rt[att] = rt
+            out["routed_experts"] = full_rt
+            for layer in self.model.layers:
+                layer.mlp.record_routing = False
         sel = idx[valid]
         h_sel = h.index_select(0, sel)
         lp, ent = ops.linear_logprob_entropy(h_sel, self.model.output_weight, labels.index_select(0, sel), temperature, need_entropy)

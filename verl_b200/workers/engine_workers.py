@@ -392,6 +392,7 @@ class ActorRolloutRefWorker(Worker):
         plist = [ids_cpu[i][att_cpu[i]].tolist() for i in range(bs)]
         t0 = time.perf_counter()
         self.rollout.profile = bool(cfg_get(ro, "log_stats", False))      # rollout.log_stats: per-call prefill / decode / capture timings
+        self.rollout.record_routing = bool(cfg_get(ro, "enable_rollout_routing_replay", False))
         self.rollout.wake_up()
         mm = prompts.non_tensor_batch.get("multi_modal_inputs") if prompts.non_tensor_batch else None
         outs = self.rollout.generate(plist, sp, eos_token_id=eos, multi_modal=[(m or None) for m in mm] if mm is not None else None)
@@ -416,6 +417,16 @@ class ActorRolloutRefWorker(Worker):
         batch = TensorBatch({"prompts": ids_cpu, "responses": resp, "input_ids": full_ids, "attention_mask": full_att,
                              "position_ids": compute_position_id_with_mask(full_att), "response_mask": rmask,
                              "rollout_log_probs": lps}, batch_size=(bs,))
+        if self.rollout.record_routing and outs and outs[0].routed_experts is not None:
+            # router replay R3: the experts the rollout chose for every token, laid out like input_ids (left-padded prompt,
+            # right-padded response); -1 rows (padding) are never read because the trainer packs by the attention mask
+            Lr, kr = outs[0].routed_experts.shape[1:]
+            routed = torch.full((bs, P + R, Lr, kr), -1, dtype=torch.int16)
+            for i, o in enumerate(outs):
+                lp_i = int(att_cpu[i].sum())
+                rt = torch.from_numpy(np.ascontiguousarray(o.routed_experts))
+                routed[i, P - lp_i:P + len(o.token_ids)] = rt
+            batch["routed_experts"] = routed
         if sp.top_logprobs > 0:
             # the sampler's top-k head per response token (padding rows: ids 0..k-1 with log-prob -1e4, i.e. zero mass)
             k = sp.top_logprobs
@@ -433,25 +444,42 @@ class ActorRolloutRefWorker(Worker):
         return out
 
     # ------------------------------------------------------------------ log-probs
-    def _logprob_pass(self, worker: TrainingWorker, data: DataProto, calculate_entropy: bool) -> dict:
+    def _router_replay_mode(self) -> str:
+        """``actor.router_replay.mode``: ``disabled`` | ``R2`` (routing recorded by the old-log-prob pass, replayed by the update)
+        | ``R3`` (routing recorded by the rollout engine, replayed by the old-log-prob pass and the update). Reference:
+        verl/utils/megatron/router_replay_patch.py:38-165, verl/workers/engine/megatron/transformer_impl.py:871-907,933-971."""
+        return str(cfg_get(self.config, "actor.router_replay.mode", "disabled") or "disabled").upper()
+
+    @staticmethod
+    def _without_routing(batch):
+        if "routed_experts" not in batch:
+            return batch
+        return TensorBatch({k: v for k, v in batch.items() if k != "routed_experts"}, batch_size=batch.batch_size)
+
+    def _logprob_pass(self, worker: TrainingWorker, data: DataProto, calculate_entropy: bool, replay: bool = False, record: bool = False) -> dict:
         meta = dict(data.meta_info)
         meta["calculate_entropy"] = calculate_entropy
         meta.setdefault("temperature", float(cfg_get(self.config, "rollout.temperature", 1.0)))
-        d = DataProto(batch=data.batch, non_tensor_batch=_model_inputs(data), meta_info=meta)
+        if record:
+            meta["record_routing"] = True
+        d = DataProto(batch=data.batch if replay else self._without_routing(data.batch), non_tensor_batch=_model_inputs(data), meta_info=meta)
         return worker.infer_batch(d)["model_output"]
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
     def compute_log_prob(self, data: DataProto) -> DataProto:
-        mo = self._logprob_pass(self.actor, data, calculate_entropy=True)
+        mode = self._router_replay_mode()
+        mo = self._logprob_pass(self.actor, data, calculate_entropy=True, replay=mode == "R3", record=mode == "R2")
         tensors = {"old_log_probs": _to_host(mo["log_probs"])}
         if "entropy" in mo:
             tensors["entropys"] = _to_host(mo["entropy"])
+        if mode == "R2" and "routed_experts" in mo:
+            tensors["routed_experts"] = _to_host(mo["routed_experts"])
         return DataProto.from_dict(tensors=tensors, meta_info={"temperature": data.meta_info.get("temperature", 1.0)})
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
     def compute_ref_log_prob(self, data: DataProto) -> DataProto:
         worker = self.ref if self.ref is not None else self.actor
-        mo = self._logprob_pass(worker, data, calculate_entropy=False)
+        mo = self._logprob_pass(worker, data, calculate_entropy=False)      # the frozen policy routes by itself
         return DataProto.from_dict(tensors={"ref_log_prob": _to_host(mo["log_probs"])})
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
@@ -476,7 +504,8 @@ class ActorRolloutRefWorker(Worker):
             meta["distillation"] = True
         meta.setdefault("temperature", float(cfg_get(self.config, "rollout.temperature", 1.0)))
         meta["calculate_entropy"] = bool(cfg_get(ac, "calculate_entropy", False)) or float(cfg_get(ac, "entropy_coeff", 0.0)) != 0.0
-        data = DataProto(batch=data.batch, non_tensor_batch=_model_inputs(data), meta_info=meta)
+        replay = self._router_replay_mode() in ("R2", "R3")
+        data = DataProto(batch=data.batch if replay else self._without_routing(data.batch), non_tensor_batch=_model_inputs(data), meta_info=meta)
         metrics = self.actor.train_mini_batch(data)
         return DataProto(batch=None, non_tensor_batch={}, meta_info={"metrics": metrics})
 

@@ -127,6 +127,10 @@ class InferenceEngine:
         self.stats = {"prefill_tokens": 0, "decode_steps": 0, "preemptions": 0, "forked": 0, "t_prefill": 0.0, "t_capture": 0.0,
                       "t_decode": 0.0, "t_flush": 0.0, "t_wake": 0.0}
         self.profile = False   # when set, phases are bracketed by device synchronisations and timed
+        # router replay (R3): record the experts every fed token was routed to, per layer, and return them with the tokens
+        # (reference: vLLM ``enable_return_routed_experts``, verl/workers/rollout/vllm_rollout/vllm_async_server.py:440-454,745-747)
+        self.record_routing = False
+        self._last_routed: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ memory lifecycle (sleep / wake_up)
     def _decide_num_blocks(self) -> int:
@@ -237,7 +241,7 @@ class InferenceEngine:
         self.sched = None
         self.workspace = None
         self._w8 = {}
-        for n in ("hist_tok", "hist_lp", "block_table", "cur_tokens", "positions", "kv_lens", "active"):
+        for n in ("hist_tok", "hist_lp", "hist_routed", "block_table", "cur_tokens", "positions", "kv_lens", "active"):
             if hasattr(self, n):
                 delattr(self, n)
         if self.device.type == "cuda":
@@ -255,6 +259,8 @@ class InferenceEngine:
             h = h.index_copy(0, visual[0], visual[1].to(h.dtype))
         res = None
         n_rot = c.num_attention_heads + c.num_key_value_heads
+        record = self.record_routing and c.is_moe
+        routed = []
         for li, layer in enumerate(m.layers):
             if res is None:
                 res = h
@@ -279,7 +285,12 @@ class InferenceEngine:
             elif self._w8 and not c.is_moe:
                 h = self._linear(ops.swiglu(self._linear(x, layer.mlp.gate_up_proj)), layer.mlp.down_proj)
             else:
+                if record:
+                    layer.mlp.record_routing = True
                 h = layer.mlp(x)
+                if record:
+                    routed.append(layer.mlp.last_topk)
+        self._last_routed = torch.stack(routed, 1).to(torch.int16) if record else None      # [T, layers, topk]
         return ops.add_rmsnorm(h, res, m.norm, c.rms_norm_eps)[0]
 
     def _tp_sync_samples(self, tok: torch.Tensor, lp: torch.Tensor) -> None:
@@ -380,6 +391,13 @@ class InferenceEngine:
         last = (cu[1:] - 1).long()
         logits = ops.linear(h.index_select(0, last), self.model.output_weight)
         self.stats["prefill_tokens"] += int(sum(lens))
+        if self._last_routed is not None:
+            # a (re)prefill feeds every token the request holds so far: its routing record starts over from these rows
+            rt = self._last_routed.cpu().numpy()
+            off = 0
+            for (req, _), L in zip(seqs, lens):
+                req["routed"] = [rt[off:off + L]]
+                off += L
         return logits
 
     def _multi_modal_prefill(self, reqs: list, tokens: torch.Tensor):
@@ -476,6 +494,8 @@ class InferenceEngine:
         self.positions.add_(act)
         self.hist_tok.index_copy_(0, self.hist_idx, self.out_tok[None])
         self.hist_lp.index_copy_(0, self.hist_idx, self.out_lp[None])
+        if self._last_routed is not None:
+            self.hist_routed.index_copy_(0, self.hist_idx, self._last_routed[None])
         if sp.top_logprobs > 0:
             tv, ti = self._top_head(logits, sp)
             self.hist_topi.index_copy_(0, self.hist_idx, ti[None])
@@ -487,6 +507,10 @@ class InferenceEngine:
     def _decode_step(self, sp: SamplingParams):
         if sp.top_logprobs > 0:
             self._ensure_top_hist(int(sp.top_logprobs))
+        if self.record_routing and self.cfg.is_moe and getattr(self, "hist_routed", None) is None:
+            # static buffer (allocated outside any graph capture): routing of the tokens fed in the un-synchronised steps
+            self.hist_routed = torch.zeros(self.sync_interval, self.max_num_seqs, len(self.model.layers), self.cfg.num_experts_per_tok,
+                                           dtype=torch.int16, device=self.device)
         if self.enforce_eager:
             self._decode_body(sp)
             return
@@ -526,6 +550,7 @@ class InferenceEngine:
         topi = topv = None
         if sp.top_logprobs > 0:
             topi, topv = self.hist_topi.cpu().numpy(), self.hist_topv.cpu().numpy()
+        routed = self.hist_routed.cpu().numpy() if getattr(self, "hist_routed", None) is not None and self.record_routing else None
         freed = []
         for ring, ids, slots in pending:
             for sid, slot in zip(ids, slots):
@@ -535,6 +560,8 @@ class InferenceEngine:
                 t = int(tok[ring, slot])
                 r["out"].append(t)
                 r["lp"].append(float(lp[ring, slot]))
+                if routed is not None:
+                    r.setdefault("routed", []).append(routed[ring, slot][None].copy())      # routing of the token FED at this step
                 if topi is not None:
                     r.setdefault("topi", []).append(topi[ring, slot].tolist())
                     r.setdefault("topv", []).append(topv[ring, slot].tolist())
@@ -619,6 +646,7 @@ class InferenceEngine:
 
         add_requests([(p, None, multi_modal[j] if multi_modal is not None else None) for j, p in enumerate(prompts)])
         owner_logits: dict[int, torch.Tensor] = {}
+        owner_routed: dict[int, np.ndarray] = {}
         owner_partial_block: dict[int, int] = {}
         pending: list = []
         ring = int(self.hist_idx.item())
@@ -663,6 +691,8 @@ class InferenceEngine:
                         r["slot"] = sl
                         if counts.get(r["pkey"], 0) > 1 and not r["out"]:
                             owner_logits[r["id"]] = logits[row]
+                            if "routed" in r:
+                                owner_routed[r["id"]] = r["routed"][0]
                             owner_partial_block[r["id"]] = int(self.block_table_host[sl, len(r["prompt"]) // BLOCK_SIZE])
                     self._start_sequences(fresh, logits, sp)
                 if forked:
@@ -676,6 +706,8 @@ class InferenceEngine:
                             src_b.append(owner_partial_block[owner])
                             dst_b.append(int(blocks[P // BLOCK_SIZE]))
                         rows.append(owner_logits[owner])
+                        if owner in owner_routed:
+                            r["routed"] = [owner_routed[owner]]
                     if src_b:
                         si = torch.tensor(src_b, device=self.device)
                         di = torch.tensor(dst_b, device=self.device)
@@ -737,9 +769,22 @@ class InferenceEngine:
             r = reqs[i]
             outs.append(TokenOutput(token_ids=r["out"][: r["max_new"]], log_probs=r["lp"][: r["max_new"]] if sp.logprobs else None,
                                     top_ids=r["topi"][: r["max_new"]] if "topi" in r else None,
-                                    top_log_probs=r["topv"][: r["max_new"]] if "topv" in r else None,
+                                    top_log_probs=r["topv"][: r["max_new"]] if "topv" in r else None, routed_experts=self._routed_of(r),
                                     stop_reason=r["stop"] or "length", num_preempted=r["num_preempted"]))
         return outs
+
+    @staticmethod
+    def _routed_of(r: dict) -> Optional[np.ndarray]:
+        """[prompt + response, layers, topk] int16: the experts chosen for every token of the sequence. The last sampled token
+        is never fed to the model, so its row repeats the previous one (the trainer does not use that position's output)."""
+        if not r.get("routed"):
+            return None
+        n_out = len(r["out"][: r["max_new"]])
+        want = len(r["prompt"]) + n_out
+        rt = np.concatenate(r["routed"], 0)[:want]
+        if rt.shape[0] < want:
+            rt = np.concatenate([rt, np.repeat(rt[-1:], want - rt.shape[0], 0)], 0)
+        return rt
 
     def _report(self, r: dict):
         if r.get("reported") or getattr(self, "_on_done", None) is None:
@@ -747,7 +792,7 @@ class InferenceEngine:
         r["reported"] = True
         self._on_done(r["id"], TokenOutput(token_ids=r["out"][: r["max_new"]], log_probs=r["lp"][: r["max_new"]] if self._sp_logprobs else None,
                                            top_ids=r["topi"][: r["max_new"]] if "topi" in r else None,
-                                           top_log_probs=r["topv"][: r["max_new"]] if "topv" in r else None,
+                                           top_log_probs=r["topv"][: r["max_new"]] if "topv" in r else None, routed_experts=self._routed_of(r),
                                            stop_reason=r["stop"] or "length", num_preempted=r["num_preempted"]))
 
     def abort_all(self) -> list[int]:
