@@ -128,3 +128,42 @@ def test_sampling_reference_topk_topp():
     assert set(tok.tolist()) == {0}
     tok, lp = _sample_reference(logits, 0.0, -1, 1.0, g)
     assert tok.tolist() == [0] * 200
+
+
+def test_rollout_records_the_routed_experts_of_every_fed_token():
+    """Router replay R3: with ``record_routing`` the engine returns, per sequence, the experts chosen for every token of
+    prompt + response in every layer. They must equal what a plain forward pass of the same model chooses for those tokens
+    (siblings that share a prompt's KV blocks share its routing rows), and forcing them reproduces the same log-probs."""
+    import numpy as np
+
+    from verl_b200.models.config import PRESETS
+    from verl_b200.models.transformer import DecoderLM, PackedBatch
+    from verl_b200.workers.rollout.engine import InferenceEngine, SamplingParams
+
+    cfg = PRESETS["tiny-qwen3-moe"]
+    model = DecoderLM(cfg, dtype=torch.float32, seed=5)
+    eng = InferenceEngine(model, max_num_seqs=8, max_model_len=96, num_blocks=24, sync_interval=4)
+    eng.record_routing = True
+    g = torch.Generator().manual_seed(0)
+    base = [torch.randint(10, 2000, (int(n),), generator=g).tolist() for n in (9, 17, 30)]
+    prompts = [base[0], base[0], base[1], base[2], base[2]]          # two groups of siblings
+    outs = eng.generate(prompts, SamplingParams(temperature=1.0, max_tokens=7, seed=3))
+    L, k = cfg.num_hidden_layers, cfg.num_experts_per_tok
+    for p, o in zip(prompts, outs):
+        ids = p + o.token_ids
+        rt = o.routed_experts
+        assert rt is not None and rt.shape == (len(ids), L, k) and rt.dtype == np.int16
+        pb = PackedBatch(torch.tensor(ids), torch.arange(len(ids), dtype=torch.int32), torch.tensor([0, len(ids)], dtype=torch.int32))
+        for layer in model.layers:
+            layer.mlp.record_routing = True
+        with torch.no_grad():
+            model.forward_hidden(pb)
+        want = torch.stack([layer.mlp.last_topk for layer in model.layers], 1).numpy()
+        fed = len(ids) - 1                                         # the last sampled token was never fed to the model
+        assert (np.sort(rt[:fed], -1) == np.sort(want[:fed], -1)).all()
+        # forcing the recorded routing gives the rollout's log-probs back
+        pb.routed_experts = torch.from_numpy(rt.astype(np.int64))
+        with torch.no_grad():
+            lp = model(pb, labels=torch.roll(torch.tensor(ids), -1), need_entropy=False)["log_probs"]
+        got = lp[len(p) - 1:len(ids) - 1]
+        assert torch.allclose(got, torch.tensor(o.log_probs), atol=1e-4)

@@ -187,3 +187,26 @@ def test_async_save_names_a_step_only_when_all_writers_finished(tmp_path):
     assert not [f for f in os.listdir(last) if f.startswith(".async_done")]
     kept = sorted(d for d in os.listdir(root) if d.startswith("global_step_") and os.path.exists(root / d / "actor" / "model_world_size_1_rank_0.pt"))
     assert "global_step_3" in kept and "global_step_1" not in kept
+
+
+@pytest.mark.parametrize("mode", ["R3", "R2"])
+def test_router_replay_end_to_end(tmp_path, mode):
+    """Mixture-of-experts actor with router replay. R3: the rollout engine records the experts of every token, the
+    old-log-prob pass and the update replay them. R2: the old-log-prob pass records, the update replays. Either way the
+    batch carries ``routed_experts`` [bs, prompt + response, layers, topk] and the first mini-batch is exactly on-policy."""
+    extra = ["trainer.total_training_steps=1", "actor_rollout_ref.model.preset=tiny-qwen3-moe", f"actor_rollout_ref.actor.router_replay.mode={mode}",
+             "actor_rollout_ref.actor.use_kl_loss=false"]
+    if mode == "R3":
+        extra.append("actor_rollout_ref.rollout.enable_rollout_routing_replay=true")
+    tr = build(tmp_path, extra)
+    tr.global_steps = 1
+    m = tr.step(next(iter(tr.train_dataloader)))
+    b = tr._last_batch.batch
+    assert "routed_experts" in b.keys()
+    rt = b["routed_experts"]
+    assert rt.shape[:2] == b["input_ids"].shape and rt.shape[2:] == (2, 2)
+    att = b["attention_mask"].bool()
+    assert int(rt[att].min()) >= 0 and int(rt[att].max()) < 8 and bool((rt[~att] == -1).all())
+    assert abs(m["actor/ppo_kl"]) < 1e-4
+    if mode == "R3":
+        assert m["training/rollout_probs_diff_max"] < 1e-4

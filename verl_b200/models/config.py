@@ -193,6 +193,11 @@ PRESETS: dict[str, ModelConfig] = {
                                  vision=dict(depth=2, embed_dim=32, num_heads=2, mlp_ratio=2.0, in_channels=3, patch_size=4, temporal_patch_size=2,
                                              spatial_merge_size=2, hidden_size=128, image_token_id=2040, video_token_id=2041,
                                              vision_start_token_id=2042, mrope_section=[4, 6, 6])),
+    # mixture-of-experts plumbing model (router replay, expert parallelism tests)
+    "tiny-qwen3-moe": ModelConfig(model_type="qwen3_moe", vocab_size=2048, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                  num_attention_heads=4, num_key_value_heads=2, head_dim=16, qk_norm=True, rms_norm_eps=1e-6, rope_theta=1e4,
+                                  num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32, tie_word_embeddings=True,
+                                  max_position_embeddings=4096, torch_dtype="float32"),
     "tiny-qwen2-gpu": ModelConfig(model_type="qwen2", vocab_size=4096, hidden_size=512, intermediate_size=1536,
                                   num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
                                   rope_theta=1e4, max_position_embeddings=4096),

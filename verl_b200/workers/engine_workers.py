@@ -239,6 +239,8 @@ class ActorRolloutRefWorker(Worker):
     """Colocated actor / reference / rollout roles of one GPU. ``role`` ∈ {actor, ref, rollout, actor_rollout,
     actor_rollout_ref}; ``config`` is the ``actor_rollout_ref`` subtree."""
 
+    actor_worker_cls = TrainingWorker      # subclasses may substitute a worker with more primitives (engine_workers_tinker)
+
     def __init__(self, config, role: str = "actor_rollout_ref"):
         super().__init__()
         ensure_process_group(int(cfg_get(config, "nccl_timeout", 600)))
@@ -269,7 +271,7 @@ class ActorRolloutRefWorker(Worker):
             self.teacher = TrainingWorker(tcfg, role="teacher")
             self.teacher.reset()
         if self._is_actor:
-            self.actor = TrainingWorker(_role_cfg(c, "actor", "language_model"), role="actor")
+            self.actor = self.actor_worker_cls(_role_cfg(c, "actor", "language_model"), role="actor")
             self.actor.reset()
             self.actor.set_loss_fn(partial(ppo_loss, cfg_get(c, "actor"), distillation=dcfg))
             eng = self.actor.engine
