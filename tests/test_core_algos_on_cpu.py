@@ -189,3 +189,33 @@ def test_optimal_token_baseline_shapes():
     assert adv.shape == (bs, L) and torch.allclose(adv[5], ret[5])   # singleton group: no baseline
     adv2, _ = ca.compute_multi_turn_optimal_token_baseline_advantage(rew, mask, idx, olp, spi)
     assert torch.isfinite(adv2).all()
+
+
+def test_moe_load_balance_and_spec_decode_metrics():
+    import torch
+
+    from verl_b200.trainer.ppo.metric_utils import (RolloutMoELoadBalanceMetricsAccumulator, compute_rollout_moe_load_balance_metrics,
+                                                    compute_spec_decode_metrics, rollout_moe_load_counts)
+
+    bs, P, R, L, k, E = 2, 3, 4, 2, 2, 4
+    routed = torch.zeros(bs, P + R, L, k, dtype=torch.int16)
+    routed[:, :, 0] = torch.tensor([0, 1])                  # layer 0: always experts 0 and 1
+    routed[:, :, 1, 0] = torch.arange(P + R) % E             # layer 1: slot 0 cycles, slot 1 fixed on expert 3
+    routed[:, :, 1, 1] = 3
+    mask = torch.tensor([[1, 1, 1, 0], [1, 1, 1, 1]])
+    counts = rollout_moe_load_counts(routed, mask, E)
+    # sequence 0 contributes 2 response tokens (its 3rd = last valid is dropped), sequence 1 contributes 3
+    assert counts.shape == (L, E) and counts[0].tolist() == [5, 5, 0, 0] and int(counts.sum()) == 5 * L * k
+    m = compute_rollout_moe_load_balance_metrics(routed, mask, E)
+    assert m["rollout/moe/max_vio/layer_0"] == pytest.approx(1.0) and m["rollout/moe/min_vio/layer_0"] == pytest.approx(-1.0)
+    assert m["rollout/moe/avg_vio/layer_0"] == pytest.approx(1.0) and "rollout/moe/max_vio/avg" in m
+    assert rollout_moe_load_counts(routed + 10, mask, E) is None and compute_rollout_moe_load_balance_metrics(None, mask, E) == {}
+    acc = RolloutMoELoadBalanceMetricsAccumulator(E)
+    assert acc.update(routed, mask) and acc.update(routed, mask) and acc.total_assignments() == 2 * int(counts.sum())
+    assert acc.pop_metrics()["rollout/moe/max_vio/layer_0"] == pytest.approx(1.0) and acc.total_assignments() == 0
+
+    assert compute_spec_decode_metrics(None, None, None) == {}
+    s = compute_spec_decode_metrics([10, 0, 8], [5, 0, 8], [5, 0, 4], non_padding_mask=[True, True, True])
+    assert s["rollout/spec_accept_rate"] == pytest.approx((0.5 + 0 + 1.0) / 3) and s["rollout/spec_accept_length"] == pytest.approx((2 + 0 + 3) / 3)
+    with pytest.raises(AssertionError):
+        compute_spec_decode_metrics([1], None, None)

@@ -242,3 +242,50 @@ def test_continuous_token_builder_and_template_checker():
             return super().apply_chat_template(msgs, **kw)
 
     assert not check_append_only(Unstable())["tool_call"]["builder"]
+
+
+def test_flops_counter_architecture_families():
+    """Per-architecture FLOPs: dense formula by hand, MoE counts active experts only, sliding-window layers cost less than
+    full ones, MLA / hybrid / vision-language families resolve and scale linearly with the token count."""
+    from verl_b200.models.config import PRESETS
+    from verl_b200.utils.flops_counter import FlopsCounter, arch_cost, get_device_flops
+
+    c = PRESETS["qwen2.5-7b"]
+    fc = FlopsCounter(c)
+    lens = [1000, 2000]
+    h, L, I, V = 3584, 28, 18944, 152064
+    n_w = L * (h * (28 * 128 + 2 * 4 * 128) + 28 * 128 * h + 3 * h * I) + 2 * V * h
+    want = 6 * n_w * 3000 + 12 * (1000**2 + 2000**2) * 128 * 28 * L
+    got, peak = fc.estimate_flops(lens, 2.0)
+    assert abs(got * 2.0 * 1e12 - want) / want < 1e-9 and peak == get_device_flops("T")
+    assert get_device_flops("T", "NVIDIA B200") == 2250.0 and get_device_flops("T", "NVIDIA GB200") == 2500.0
+
+    moe = PRESETS["qwen3-30b-a3b"]
+    dense_like = arch_cost(moe).flops([4096])
+    all_experts = 6 * 4096 * moe.num_hidden_layers * 3 * moe.hidden_size * moe.moe_intermediate_size * (moe.num_experts - moe.num_experts_per_tok)
+    assert dense_like < all_experts                        # active experts only: far below the all-expert count
+
+    gem = dict(model_type="gemma3_text", hidden_size=1024, num_attention_heads=8, num_key_value_heads=4, head_dim=128, num_hidden_layers=12,
+               intermediate_size=4096, vocab_size=32000, sliding_window=512, sliding_window_pattern=6)
+    full = dict(gem, sliding_window=None)
+    assert arch_cost(gem).flops([8192]) < arch_cost(full).flops([8192])
+    assert arch_cost(gem).flops([256]) == arch_cost(full).flops([256])       # shorter than the window: identical
+
+    dsv3 = dict(model_type="deepseek_v3", hidden_size=1024, num_attention_heads=8, num_hidden_layers=6, first_k_dense_replace=2, intermediate_size=4096,
+                moe_intermediate_size=512, n_routed_experts=32, num_experts_per_tok=4, n_shared_experts=1, q_lora_rank=256, kv_lora_rank=128,
+                qk_nope_head_dim=64, qk_rope_head_dim=32, v_head_dim=64, vocab_size=32000)
+    q35 = dict(model_type="qwen3_5", hidden_size=1024, num_attention_heads=8, num_key_value_heads=2, head_dim=128, num_hidden_layers=8,
+               intermediate_size=4096, vocab_size=32000, full_attention_interval=4, linear_num_key_heads=4, linear_key_head_dim=64,
+               linear_num_value_heads=8, linear_value_head_dim=64, linear_conv_kernel_dim=4)
+    oss = dict(model_type="gpt_oss", hidden_size=1024, num_attention_heads=8, num_key_value_heads=2, head_dim=64, num_hidden_layers=4,
+               intermediate_size=1024, num_local_experts=8, num_experts_per_tok=2, vocab_size=32000, sliding_window=128)
+    for cfg in (dsv3, q35, oss, dict(gem, model_type="apertus")):
+        cost = arch_cost(cfg)
+        a, b = cost.flops([512]), cost.flops([512, 512])
+        assert a > 0 and abs(b - 2 * a) / b < 1e-12
+    assert sum(1 for _, s in arch_cost(q35).attn_layers if s is not None) == 2      # every fourth layer is full attention
+
+    vl = PRESETS["tiny-qwen2-vl"]
+    cost = arch_cost(dict(model_type="qwen2_vl", vision_config=vl.vision, text_config=None, **{k: getattr(vl, k) for k in
+                     ("hidden_size", "num_attention_heads", "num_key_value_heads", "num_hidden_layers", "intermediate_size", "vocab_size")}))
+    assert cost.flops([64], images_seqlens=[16]) > cost.flops([64])

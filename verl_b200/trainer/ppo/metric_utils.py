@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from collections import defaultdict
 from functools import partial
-from typing import Any, Callable
+from typing import Any, Callable, Optional
 
 import numpy as np
 import torch
@@ -170,3 +170,117 @@ def process_validation_metrics(data_sources: list[str], sample_uids: list[str], 
                 for name, v in metric.items():
                     out[src][var][name].append(v)
     return {src: {var: {name: float(np.mean(v)) for name, v in d.items()} for var, d in vd.items()} for src, vd in out.items()}
+
+
+# ------------------------------------------------------------------------------------------------ rollout MoE load balance
+def rollout_moe_load_counts(routed_experts, response_mask, num_experts: Optional[int]):
+    """``[layers, experts]`` counts of the experts chosen for the RESPONSE tokens of a batch.
+
+    ``routed_experts`` is ``[bs, seq, layers, topk]`` (what router replay R3 carries), ``response_mask`` ``[bs, R]``. Each
+    sequence's last response token is left out: it was sampled but never fed to the model, its row is a filler. Returns
+    ``None`` when nothing can be counted (missing inputs, ids outside ``[0, num_experts)``).
+    Reference: ``verl/trainer/ppo/metric_utils.py:205-272``."""
+    if routed_experts is None or response_mask is None or not num_experts or num_experts <= 0:
+        return None
+    if routed_experts.dim() != 4 or response_mask.dim() != 2 or response_mask.shape[0] != routed_experts.shape[0]:
+        return None
+    R = response_mask.shape[1]
+    if R == 0 or routed_experts.shape[1] < R:
+        return None
+    mask = response_mask.bool().clone()
+    n_valid = mask.sum(-1)
+    rows = torch.nonzero(n_valid > 0, as_tuple=True)[0]
+    if rows.numel():
+        pos = torch.arange(R, device=mask.device).expand_as(mask)
+        last = torch.where(mask, pos, torch.full_like(pos, -1)).amax(-1)
+        mask[rows, last[rows]] = False
+    picked = routed_experts[:, -R:][mask.to(routed_experts.device)].long().cpu()          # [tokens, layers, topk]
+    if picked.numel() == 0 or int(picked.min()) < 0 or int(picked.max()) >= num_experts:
+        return None
+    L = picked.shape[1]
+    flat = picked + torch.arange(L).view(1, L, 1) * num_experts                            # one bincount over (layer, expert)
+    return torch.bincount(flat.reshape(-1), minlength=L * num_experts).view(L, num_experts)
+
+
+def moe_load_balance_metrics(load_counts, prefix: str = "rollout/moe") -> dict:
+    """Violation of a uniform load per layer: with ``f_e`` the fraction of assignments that went to expert ``e`` and ``E``
+    experts, ``dev_e = f_e·E − 1``; ``max_vio`` / ``min_vio`` are the extremes, ``avg_vio`` the mean absolute deviation.
+    Per-layer values plus max / avg over layers (reference ``metric_utils.py:176-202``)."""
+    if load_counts is None or load_counts.numel() == 0:
+        return {}
+    frac = load_counts.float()
+    frac = frac / frac.sum(1, keepdim=True).clamp_min(1.0)
+    dev = frac * frac.shape[1] - 1.0
+    stats = {"max_vio": dev.max(1).values, "min_vio": dev.min(1).values, "avg_vio": dev.abs().mean(1)}
+    out = {}
+    for name, v in stats.items():
+        for i, x in enumerate(v.tolist()):
+            out[f"{prefix}/{name}/layer_{i}"] = x
+        out[f"{prefix}/{name}/max"] = float(v.max())
+        out[f"{prefix}/{name}/avg"] = float(v.mean())
+    return out
+
+
+def compute_rollout_moe_load_balance_metrics(routed_experts, response_mask, num_experts, prefix: str = "rollout/moe") -> dict:
+    return moe_load_balance_metrics(rollout_moe_load_counts(routed_experts, response_mask, num_experts), prefix)
+
+
+class RolloutMoELoadBalanceMetricsAccumulator:
+    """Sums the routed-expert counts of several steps and reports them every ``interval`` steps
+    (``trainer.moe_lb_metrics_interval``; reference ``metric_utils.py:312-427``)."""
+
+    def __init__(self, num_experts: Optional[int] = None):
+        self.num_experts = num_experts
+        self.load_counts = None
+
+    def update(self, routed_experts, response_mask, num_experts: Optional[int] = None) -> bool:
+        c = rollout_moe_load_counts(routed_experts, response_mask, num_experts or self.num_experts)
+        if c is None:
+            return False
+        self.load_counts = c if self.load_counts is None or self.load_counts.shape != c.shape else self.load_counts + c
+        return True
+
+    def total_assignments(self) -> int:
+        return 0 if self.load_counts is None else int(self.load_counts.sum())
+
+    def pop_metrics(self, prefix: str = "rollout/moe") -> dict:
+        m = moe_load_balance_metrics(self.load_counts, prefix)
+        self.load_counts = None
+        return m
+
+
+def compute_moe_lb_metrics(batch: DataProto, interval: int, global_steps: int, accumulator: RolloutMoELoadBalanceMetricsAccumulator) -> dict:
+    """Feed one step's batch to the accumulator; on every ``interval``-th step return (and reset) the accumulated metrics."""
+    if interval <= 0:
+        return {}
+    accumulator.update(batch.batch.get("routed_experts", None), batch.batch.get("response_mask", None))
+    if global_steps % interval != 0:
+        return {}
+    n = accumulator.total_assignments()
+    m = accumulator.pop_metrics()
+    m["rollout/moe/routed_experts_found"] = float(n > 0)
+    m["rollout/moe/routed_expert_assignments"] = n
+    return m
+
+
+# ------------------------------------------------------------------------------------------------ speculative decoding
+def compute_spec_decode_metrics(spec_drafts, spec_accepts, spec_verifies, non_padding_mask=None) -> dict:
+    """Per-request acceptance statistics of speculative decoding, averaged with equal weight per request:
+    ``accept_rate = accepted / drafted`` and ``accept_length = 1 + accepted / verify_steps`` (0 where the denominator is 0).
+    The three inputs are per-request counters reported by the rollout engine (all ``None`` = feature off → ``{}``).
+    Reference: ``verl/trainer/ppo/ray_trainer.py:138-184``."""
+    given = [x is not None for x in (spec_drafts, spec_accepts, spec_verifies)]
+    if not any(given):
+        return {}
+    assert all(given), "spec-decode metrics need drafted, accepted and verify-step counters together"
+    cols = [list(x.tolist() if hasattr(x, "tolist") else x) for x in (spec_drafts, spec_accepts, spec_verifies)]
+    if non_padding_mask is not None:
+        keep = [bool(k) for k in non_padding_mask]
+        assert len(keep) == len(cols[0])
+        cols = [[v for v, k in zip(c, keep) if k] for c in cols]
+    d, a, v = cols
+    if not d:
+        return {}
+    rate = [ai / di if di > 0 else 0.0 for ai, di in zip(a, d)]
+    length = [1.0 + ai / vi if vi > 0 else 0.0 for ai, vi in zip(a, v)]
+    return {"rollout/spec_accept_rate": float(sum(rate) / len(rate)), "rollout/spec_accept_length": float(sum(length) / len(length))}

@@ -326,6 +326,22 @@ class PPOTrainer:
         batch.reorder(torch.tensor([i for p in parts for i in p]))
         metrics.update(log_seqlen_unbalance(lens.tolist(), parts, logging_prefix))
 
+    def _num_experts(self) -> Optional[int]:
+        """Experts per MoE layer of the actor's architecture (preset or ``config.json``), for the load-balance metrics."""
+        mc = self.config.actor_rollout_ref.model
+        try:
+            if mc.get("preset"):
+                from verl_b200.models.config import PRESETS
+
+                return int(PRESETS[mc.get("preset")].num_experts) or None
+            if mc.get("path"):
+                from verl_b200.models.config import ModelConfig
+
+                return int(ModelConfig.from_pretrained(os.path.expanduser(str(mc.get("path")))).num_experts) or None
+        except Exception:  # noqa: BLE001
+            return None
+        return None
+
     def _gen_meta(self, validate: bool = False) -> dict:
         tk = self.tokenizer
         return {"eos_token_id": getattr(tk, "eos_token_id", None) if tk is not None else _g(self.config, "data.eos_token_id"),
@@ -529,6 +545,18 @@ class PPOTrainer:
                 self.actor_rollout_wg.update_weights()
         metrics.update(compute_data_metrics(batch=batch, use_critic=self.use_critic))
         metrics.update(compute_variance_proxy_metrics(batch, metrics.get("actor/grad_norm")))
+        lb_every = int(_g(cfg, "trainer.moe_lb_metrics_interval", 0) or 0)
+        if lb_every > 0 and "routed_experts" in batch.batch.keys():
+            from verl_b200.trainer.ppo.metric_utils import RolloutMoELoadBalanceMetricsAccumulator, compute_moe_lb_metrics
+
+            if getattr(self, "_moe_lb", None) is None:
+                self._moe_lb = RolloutMoELoadBalanceMetricsAccumulator(int(batch.meta_info.get("num_experts", 0)) or self._num_experts())
+            metrics.update(compute_moe_lb_metrics(batch, lb_every, self.global_steps, self._moe_lb))
+        nt = batch.non_tensor_batch
+        if "spec_num_draft_tokens" in nt:
+            from verl_b200.trainer.ppo.metric_utils import compute_spec_decode_metrics
+
+            metrics.update(compute_spec_decode_metrics(nt.get("spec_num_draft_tokens"), nt.get("spec_num_accepted_tokens"), nt.get("spec_num_verify_steps")))
         self._last_batch = batch
         return metrics
 
