@@ -280,7 +280,7 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference", "stocklibs"],
                     help="native: this framework; reference: the unmodified reference package under baseline/_ref; stocklibs: the same GRPO "
                          "step from vLLM + transformers/FlashAttention-2 + torch AdamW only (benchmarks/stocklibs_grpo.py, one GPU)")
-    ap.add_argument("--vllm-util", type=float, default=0.3, help="stocklibs arm: vLLM gpu_memory_utilization")
+    ap.add_argument("--vllm-util", type=float, default=0.25, help="stocklibs arm: vLLM gpu_memory_utilization (weights 15 GB + KV cache for 256 x 1536 tokens = 23 GB fit in 0.25 x 180 GB)")
     ap.add_argument("--model", default="qwen2.5-7b")
     ap.add_argument("--prompts-per-gpu", type=int, default=32)
     ap.add_argument("--mini-prompts-per-gpu", type=int, default=8)

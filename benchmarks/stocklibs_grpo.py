@@ -120,6 +120,8 @@ def run(args, llm=None, sampling=None):
     else:
         sp = sampling
     llm.sleep(level=1)
+    if cuda:
+        torch.cuda.empty_cache()         # what the engine's profiling run left in torch's caching allocator
 
     # ---------------------------------------------------------------- actor (fp32 + autocast), reference (bf16, frozen)
     from transformers import AutoModelForCausalLM
@@ -175,6 +177,9 @@ def run(args, llm=None, sampling=None):
         t = {}
         t0 = time.perf_counter()
         prompts = _prompts(args, s, vocab_hi)
+        opt.zero_grad(set_to_none=True)
+        if cuda:
+            torch.cuda.empty_cache()     # gradients and activations of the last update: the KV cache needs the room back
         llm.wake_up()
         push_weights()
         outs = llm.generate([{"prompt_token_ids": p} for p in prompts], sp, use_tqdm=False)
@@ -184,6 +189,8 @@ def run(args, llm=None, sampling=None):
                 seqs.append(p + list(c.token_ids))
                 resp_lens.append(len(c.token_ids))
         llm.sleep(level=1)
+        if cuda:
+            torch.cuda.empty_cache()
         sync()
         t["gen"] = time.perf_counter() - t0
         lens = [len(x) for x in seqs]

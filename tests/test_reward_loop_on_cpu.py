@@ -3,6 +3,8 @@
 import asyncio
 import time
 
+import pytest
+
 import torch
 
 from verl_b200.experimental.reward_loop import RewardLoopManager, get_reward_loop_manager_cls
@@ -153,3 +155,59 @@ def test_sandbox_fusion_client_against_a_local_service():
     # an unreachable service scores 0 instead of raising
     score, recs = sandbox_fusion.compute_score("http://127.0.0.1:9/run_code", None, 512, good, tests, timeout=0.5)
     assert score == 0.0 and recs[0]["status"] == "sandbox_error"
+
+
+def _slow_or_fast(task, completion, reference, extra):
+    import time
+
+    if completion == "hang":
+        time.sleep(30)
+    if completion == "boom":
+        raise RuntimeError("checker crashed")
+    return (1.0, "details") if completion == reference else {"score": 0.25}
+
+
+def _fake_verify(gold, out):
+    return 1.0 if gold == "\\boxed{" + out + "}" else 0.0
+
+
+def test_prime_manager_rlla_and_math_verify():
+    import numpy as np
+    import torch
+
+    from verl_b200.protocol import DataProto
+    from verl_b200.utils.reward_score import default_compute_score, math_verify, rlla
+    from verl_b200.workers.reward_manager import get_reward_manager_cls
+    from verl_b200.workers.reward_manager.prime import run_reward_scoring
+
+    # process-pool scoring: tuple / dict / failing / hanging checkers
+    s = run_reward_scoring(_slow_or_fast, ["a", "b", "boom", "hang"], ["a", "x", "y", "z"], ["t"] * 4, None, num_processes=4, timeout=2.0)
+    assert s == [1.0, 0.25, 0.0, 0.0]
+    mgr = get_reward_manager_cls("prime")(tokenizer=None, compute_score=_slow_or_fast, num_processes=2, timeout=5.0)
+    data = DataProto.from_dict(tensors={"prompts": torch.zeros(2, 3, dtype=torch.long), "responses": torch.tensor([[7, 8, 0], [9, 0, 0]]),
+                                        "attention_mask": torch.tensor([[1, 1, 1, 1, 1, 0], [0, 1, 1, 1, 0, 0]])},
+                               non_tensors={"data_source": np.array(["t", "t"], dtype=object),
+                                            "reward_model": np.array([{"ground_truth": "7 8"}, {"ground_truth": "nope"}], dtype=object)})
+    out = mgr(data, return_dict=True)
+    assert out["reward_tensor"].tolist() == [[0.0, 1.0, 0.0], [0.25, 0.0, 0.0]] and data.batch["acc"].tolist() == [1.0, 0.25]
+
+    # tool-use reward: exact call = +3 and format +1; a wrong parameter value lowers the correctness term; malformed = -3
+    gt = '<think>plan</think>\n<tool_call>\n{"name": "search", "parameters": {"q": "b200", "k": 3}}\n</tool_call>'
+    wrap = lambda body: "<|im_start|>assistant" + body + "<|im_end|>"      # noqa: E731
+    info = {"experiment_name": "qwen-test"}
+    full = rlla.compute_score("rlla", wrap(gt), gt, info)
+    assert full == {"score": 4.0, "format_reward": 1.0, "accuracy_reward": 3.0}
+    off = rlla.compute_score("rlla", wrap(gt.replace('"k": 3', '"k": 5')), gt, info)
+    assert off["format_reward"] == 1.0 and -3.0 < off["accuracy_reward"] < 3.0
+    bad = rlla.compute_score("rlla", wrap("<think>x</think>\nno call here"), gt, info)
+    assert bad == {"score": -3.0, "format_reward": 0.0, "accuracy_reward": -3.0}
+    assert rlla.multiset_overlap(["a", "a", "b"], ["a", "b", "b"]) == 0.5
+    assert default_compute_score("rlla", wrap(gt), gt, info)["score"] == 4.0
+    with pytest.raises(NotImplementedError):
+        rlla.compute_score("rlla", "x", gt, {"experiment_name": "other"})
+
+    # math_verify: same pool / time-out path with a stand-in verifier; without the package the scorer refuses to run
+    assert math_verify.compute_score("42", "42", _verify_fn=_fake_verify) == 1.0 and math_verify.compute_score("41", "42", _verify_fn=_fake_verify) == 0.0
+    if not math_verify.available():
+        with pytest.raises(ImportError):
+            math_verify.compute_score("42", "42")

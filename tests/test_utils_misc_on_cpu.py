@@ -289,3 +289,68 @@ def test_flops_counter_architecture_families():
     cost = arch_cost(dict(model_type="qwen2_vl", vision_config=vl.vision, text_config=None, **{k: getattr(vl, k) for k in
                      ("hidden_size", "num_attention_heads", "num_key_value_heads", "num_hidden_layers", "intermediate_size", "vocab_size")}))
     assert cost.flops([64], images_seqlens=[16]) > cost.flops([64])
+
+
+def test_tracking_backends_with_stand_in_sdks(monkeypatch, tmp_path):
+    """swanlab / clearml / trackio / rl_insight adapters against stand-in modules: what is initialised, what is logged, how
+    metric names are mapped."""
+    import sys
+    import types
+
+    from verl_b200.utils.tracking import RLInsightLogger, Tracking
+
+    calls = []
+    swan = types.ModuleType("swanlab")
+    swan.init = lambda **kw: calls.append(("swan.init", kw["project"], kw["experiment_name"], kw["mode"]))
+    swan.login = lambda key: calls.append(("swan.login", key))
+    swan.log = lambda data, step=None: calls.append(("swan.log", dict(data), step))
+    swan.finish = lambda: calls.append(("swan.finish",))
+    tio = types.ModuleType("trackio")
+    tio.init = lambda **kw: calls.append(("trackio.init", kw["project"], kw["name"]))
+    tio.log = lambda data, step=None: calls.append(("trackio.log", dict(data), step))
+    tio.finish = lambda: calls.append(("trackio.finish",))
+
+    class _Lg:
+        def report_scalar(self, title, series, value, iteration):
+            calls.append(("clearml.scalar", title, series, value, iteration))
+
+    class _Task:
+        @staticmethod
+        def init(**kw):
+            calls.append(("clearml.init", kw["project_name"], kw["task_name"]))
+            return _Task()
+
+        def connect_configuration(self, cfg, name):
+            calls.append(("clearml.cfg", name))
+
+        def get_logger(self):
+            return _Lg()
+
+        def close(self):
+            calls.append(("clearml.close",))
+
+    cml = types.ModuleType("clearml")
+    cml.Task = _Task
+    rli = types.ModuleType("rl_insight")
+    rli.init = lambda **kw: calls.append(("rli.init", kw["project"], kw["config"]))
+    rli.metric_gauge = lambda name, v: calls.append(("rli.gauge", name, v))
+    rli.finish = lambda: calls.append(("rli.finish",))
+    for name, mod in (("swanlab", swan), ("trackio", tio), ("clearml", cml), ("rl_insight", rli)):
+        monkeypatch.setitem(sys.modules, name, mod)
+    monkeypatch.setenv("SWANLAB_MODE", "local")
+    monkeypatch.setenv("VERL_RL_INSIGHT_ENABLE", "1")
+    RLInsightLogger._module, RLInsightLogger._started = None, False
+    tr = Tracking("proj", "exp", ["swanlab", "clearml", "trackio", "rl_insight"], config={"trainer": {"rl_insight": {"port": 1}}})
+    tr.log({"actor/pg_loss": 0.5, "note": "text"}, step=3)
+    assert ("swan.init", "proj", "exp", "local") in calls and ("trackio.init", "proj", "exp") in calls and ("clearml.init", "proj", "exp") in calls
+    assert ("rli.init", "proj", {"port": 1}) in calls and ("rli.gauge", "actor_pg_loss", 0.5) in calls
+    assert ("clearml.scalar", "actor", "pg_loss", 0.5, 3) in calls
+    assert ("trackio.log", {"actor/pg_loss": 0.5, "note": "text"}, 3) in calls
+    assert not any(c[0] == "rli.gauge" and c[1] == "note" for c in calls)
+    monkeypatch.setenv("VERL_RL_INSIGHT_ENABLE", "0")
+    n = len(calls)
+    RLInsightLogger.log({"x": 1.0}, 1)                  # opted out: nothing happens
+    with RLInsightLogger.trace_state("rollout"):
+        pass
+    assert len(calls) == n
+    RLInsightLogger._module, RLInsightLogger._started = None, False

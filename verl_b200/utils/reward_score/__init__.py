@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from . import geo3k, gsm8k, math_dapo, math_reward, prime_code, prime_math, sandbox_fusion, search_r1_like_qa_em, synthetic
+from . import geo3k, gsm8k, math_dapo, math_reward, math_verify, prime_code, prime_math, rlla, sandbox_fusion, search_r1_like_qa_em, synthetic
 
 __all__ = ["default_compute_score"]
 
@@ -28,6 +28,10 @@ def default_compute_score(data_source: str, solution_str: str, ground_truth, ext
     if data_source in ("searchR1_nq", "searchR1_triviaqa", "searchR1_popqa", "searchR1_hotpotqa", "searchR1_2wikimultihopqa",
                        "searchR1_musique", "searchR1_bamboogle"):
         return search_r1_like_qa_em.compute_score(solution_str, ground_truth)
+    if data_source in ("rlla", "rlla_gdpo", "toolrl"):
+        return rlla.compute_score(data_source, solution_str, ground_truth, extra_info or {})
+    if data_source in ("math_verify",) or (kwargs.get("use_math_verify") and math_verify.available()):
+        return math_verify.compute_score(solution_str, ground_truth)
     if data_source in ("synthetic/mod7", "mod7"):
         return synthetic.compute_score_from_text(solution_str, ground_truth)
     raise NotImplementedError(f"Reward function is not implemented for data_source={data_source!r}")

@@ -1,4 +1,5 @@
-"""Experiment tracking fan-out: console, jsonl file, tensorboard, wandb, mlflow (each optional).
+"""Experiment tracking fan-out: console, jsonl file, tensorboard, wandb (+ the vemlp flavour), mlflow, swanlab, clearml,
+trackio and rl_insight. Every SDK is imported only when its backend is selected.
 
 Parity target: ``verl/utils/tracking.py`` (Tracking :38, FileLogger :529, ValidationGenerationsLogger :664) and
 ``verl/utils/logger/aggregate_logger.py`` (LocalLogger).
@@ -12,7 +13,7 @@ import os
 import time
 from typing import Any, Optional
 
-__all__ = ["Tracking", "LocalLogger", "FileLogger", "ValidationGenerationsLogger", "concat_dict_to_str"]
+__all__ = ["Tracking", "LocalLogger", "FileLogger", "ClearMLLogger", "RLInsightLogger", "ValidationGenerationsLogger", "concat_dict_to_str"]
 
 
 def concat_dict_to_str(d: dict, step: int) -> str:
@@ -100,6 +101,32 @@ class Tracking:
 
             mlflow.start_run(run_name=experiment_name)
             self.logger["mlflow"] = _MlflowAdapter(mlflow)
+        if "vemlp_wandb" in default_backend:
+            # volcengine ML platform: its wandb fork, credentials from the environment
+            import volcengine_ml_platform
+            from volcengine_ml_platform import wandb as vemlp_wandb
+
+            volcengine_ml_platform.init(ak=os.environ["VOLC_ACCESS_KEY_ID"], sk=os.environ["VOLC_SECRET_ACCESS_KEY"], region=os.environ["MLP_TRACKING_REGION"])
+            vemlp_wandb.init(project=project_name, name=experiment_name, config=config, sync_tensorboard=True)
+            self.logger["vemlp_wandb"] = vemlp_wandb
+        if "swanlab" in default_backend:
+            import swanlab
+
+            key = os.environ.get("SWANLAB_API_KEY")
+            if key:
+                swanlab.login(key)
+            swanlab.init(project=project_name, experiment_name=experiment_name, config={"FRAMEWORK": "verl_b200", **(config or {})},
+                         logdir=os.environ.get("SWANLAB_LOG_DIR", "swanlog"), mode=os.environ.get("SWANLAB_MODE", "cloud"))
+            self.logger["swanlab"] = swanlab
+        if "clearml" in default_backend:
+            self.logger["clearml"] = ClearMLLogger(project_name, experiment_name, config)
+        if "trackio" in default_backend:
+            import trackio
+
+            trackio.init(project=project_name, name=experiment_name, config=config)
+            self.logger["trackio"] = _TrackioAdapter(trackio)
+        if "rl_insight" in default_backend:
+            self.logger["rl_insight"] = RLInsightLogger(project_name, experiment_name, config)
         for b in default_backend:
             if b not in self.logger:
                 raise ImportError(f"tracking backend '{b}' needs an SDK that is not installed in this environment")
@@ -128,6 +155,105 @@ class _MlflowAdapter:
         self.mlflow.end_run()
 
 
+class _TrackioAdapter:
+    def __init__(self, trackio):
+        self.trackio = trackio
+
+    def log(self, data, step):
+        self.trackio.log(data, step=step)
+
+    def finish(self):
+        self.trackio.finish()
+
+
+class ClearMLLogger:
+    """One ClearML task per run; scalars are reported as (title, series) split at the first ``/`` of the metric name
+    (reference: ``verl/utils/tracking.py:463-512``)."""
+
+    def __init__(self, project_name: str, experiment_name: str, config=None):
+        import clearml
+
+        self._task = clearml.Task.init(task_name=experiment_name, project_name=project_name, continue_last_task=True, output_uri=False)
+        if config is not None:
+            self._task.connect_configuration(dict(config), name="Hyperparameters")
+
+    def log(self, data, step):
+        lg = self._task.get_logger()
+        for k, v in data.items():
+            if not isinstance(v, numbers.Number):
+                continue
+            title, _, series = k.partition("/")
+            lg.report_scalar(title=title, series=series or title, value=float(v), iteration=step)
+
+    def finish(self):
+        self._task.close()
+
+
+class RLInsightLogger:
+    """Exports scalar metrics as gauges and runtime phases as traced states to ``rl_insight`` when the process opted in with
+    ``VERL_RL_INSIGHT_ENABLE=1``; otherwise every call is a no-op, so call sites need no guard
+    (reference: ``verl/utils/tracking.py:226-460``)."""
+
+    ENABLE_ENV = "VERL_RL_INSIGHT_ENABLE"
+    _module = None
+    _started = False
+
+    def __init__(self, project_name=None, experiment_name=None, config=None):
+        self.init(project_name, experiment_name, config)
+
+    @classmethod
+    def enabled(cls) -> bool:
+        return os.getenv(cls.ENABLE_ENV) == "1"
+
+    @classmethod
+    def _sdk(cls):
+        if cls._module is None:
+            import rl_insight
+
+            cls._module = rl_insight
+        return cls._module
+
+    @classmethod
+    def init(cls, project_name=None, experiment_name=None, config=None):
+        if not cls.enabled() or cls._started:
+            return
+        sub = {}
+        try:
+            sub = (config or {}).get("trainer", {}).get("rl_insight", {}) or {}
+        except (AttributeError, TypeError):
+            pass
+        cls._sdk().init(project=project_name, experiment_name=experiment_name, config=sub)
+        cls._started = True
+
+    @classmethod
+    def log(cls, data, step):
+        if not cls.enabled():
+            return
+        cls.init()
+        gauge = cls._sdk().metric_gauge
+        for k, v in data.items():
+            try:
+                gauge(str(k).replace("/", "_"), float(v))
+            except (TypeError, ValueError):
+                continue
+
+    @classmethod
+    def finish(cls):
+        if cls._started:
+            cls._sdk().finish()
+            cls._started = False
+
+    @classmethod
+    def trace_state(cls, state_name: str, *, state_lane_id=None, **labels):
+        """Context manager marking a runtime state (rollout, update, weight sync ...) on a lane of the timeline."""
+        from contextlib import nullcontext
+
+        if not cls.enabled():
+            return nullcontext()
+        cls.init()
+        return cls._sdk().trace_state(state_name, state_lane_id=state_lane_id, **labels)
+
+
 class ValidationGenerationsLogger:
     """Dump (input, output, score) triples of validation samples to jsonl (console/file backends) or a wandb table."""
 
@@ -139,3 +265,22 @@ class ValidationGenerationsLogger:
         with open(path, "a") as f:
             for inp, out, score in samples:
                 f.write(json.dumps({"step": step, "input": inp, "output": out, "score": score}) + "\n")
+        loggers = loggers or []
+        text = "\n\n".join(f"input: {i}\n---\noutput: {o}\n---\nscore: {s}" for i, o, s in samples)
+        if "swanlab" in loggers:
+            import swanlab
+
+            swanlab.log({"val/generations": [swanlab.Text(f"input: {i}\n---\noutput: {o}\n---\nscore: {s}", caption=f"sample {n + 1}")
+                                             for n, (i, o, s) in enumerate(samples)]}, step=step)
+        if "clearml" in loggers:
+            import clearml
+
+            task = clearml.Task.current_task()
+            if task is not None:
+                task.get_logger().report_text(text, print_console=False)
+        if "trackio" in loggers:
+            import trackio
+
+            trackio.log({"val/generations": text}, step=step)
+        if "tensorboard" in loggers and hasattr(self, "_tb_writer"):
+            self._tb_writer.add_text("val/generations", text, step)
