@@ -56,3 +56,11 @@ class Adder(Worker):
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def add(self, v):
         return v + self.k
+
+
+class EnvWorker(Worker):
+    """Reports the launcher environment its process received."""
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def env(self):
+        return (os.environ["RANK"], os.environ["WORLD_SIZE"], os.environ["LOCAL_RANK"])

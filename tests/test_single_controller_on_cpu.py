@@ -116,3 +116,47 @@ def test_controller_aborts_when_a_worker_dies(tmp_path):
     r = subprocess.run([sys.executable, str(script)], env=dict(os.environ, REPO=repo), capture_output=True, text=True, timeout=120)
     assert r.returncode == -signal.SIGABRT, (r.returncode, r.stdout[-500:], r.stderr[-500:])
     assert "controller survived" not in r.stdout
+
+
+def test_resource_pools_split_merge_and_manager():
+    from verl_b200.single_controller.base import ResourcePool, ResourcePoolManager, merge_resource_pool, split_resource_pool
+
+    pool = ResourcePool([4, 4])
+    a, b = split_resource_pool(pool, [6, 2])
+    assert a.world_size == 6 and b.world_size == 2
+    assert a.device_slots() == [(0, 0), (0, 1), (0, 2), (0, 3), (1, 0), (1, 1)] and b.device_slots() == [(1, 2), (1, 3)]
+    assert b.local_rank_list() == [2, 3] and a.local_world_size_list() == [4, 4, 4, 4, 2, 2]
+    halves = split_resource_pool(a, 3)                      # a slice can be split again
+    assert [h.device_slots() for h in halves] == [[(0, 0), (0, 1), (0, 2)], [(0, 3), (1, 0), (1, 1)]]
+    with pytest.raises(AssertionError):
+        split_resource_pool(pool, 3)
+    with pytest.raises(AssertionError):
+        split_resource_pool(pool, [4, 3])
+    m = merge_resource_pool(ResourcePool([2]), ResourcePool([4, 4]))
+    assert m.store == [2, 4, 4] and m.world_size == 10
+    with pytest.raises(AssertionError):
+        merge_resource_pool(ResourcePool([2], max_colocate_count=1), ResourcePool([2], max_colocate_count=3))
+
+    mgr = ResourcePoolManager({"train": [4], "rollout": [4]}, {"actor": "train", "critic": "train", "rollout": "rollout"}, available=8)
+    pools = mgr.create_resource_pool()
+    assert mgr.get_n_gpus() == 8 and mgr.get_resource_pool("critic") is pools["train"] and mgr.get_resource_pool("rollout").world_size == 4
+    with pytest.raises(ValueError):
+        ResourcePoolManager({"train": [8], "rollout": [4]}, {"actor": "train"}, available=8).create_resource_pool()
+
+
+def test_worker_groups_on_sub_pools_get_their_slice_of_devices():
+    """Two process worker groups on disjoint slices of one pool: LOCAL_RANK of every worker is its device index in the
+    parent pool, ranks are numbered inside each group."""
+    from tests._sc_workers import EnvWorker
+    from verl_b200.single_controller.base import ClassWithInitArgs, ResourcePool, split_resource_pool
+    from verl_b200.single_controller.process import ProcessWorkerGroup
+
+    left, right = split_resource_pool(ResourcePool([3]), [1, 2])
+    wg_l = ProcessWorkerGroup(left, ClassWithInitArgs(EnvWorker), use_gpu=False)
+    wg_r = ProcessWorkerGroup(right, ClassWithInitArgs(EnvWorker), use_gpu=False)
+    try:
+        assert wg_l.env() == [("0", "1", "0")]
+        assert wg_r.env() == [("0", "2", "1"), ("1", "2", "2")]
+    finally:
+        wg_l.shutdown()
+        wg_r.shutdown()

@@ -16,7 +16,7 @@ from verl_b200.protocol import DataProto, unpad_dataproto
 
 from .decorator import MAGIC_ATTR, Dispatch, get_predefined_dispatch_fn, get_predefined_execute_fn
 
-__all__ = ["ResourcePool", "ClassWithInitArgs", "WorkerGroup"]
+__all__ = ["ResourcePool", "SubResourcePool", "ResourcePoolManager", "split_resource_pool", "merge_resource_pool", "ClassWithInitArgs", "WorkerGroup"]
 
 
 class ResourcePool:
@@ -46,6 +46,105 @@ class ResourcePool:
 
     def local_rank_list(self) -> list[int]:
         return [i for n in self._store for i in range(n)]
+
+    def device_slots(self) -> list[tuple[int, int]]:
+        """(node index, device index on that node) of every worker of this pool, in rank order."""
+        return [(node, i) for node, n in enumerate(self._store) for i in range(n)]
+
+
+class SubResourcePool(ResourcePool):
+    """A contiguous slice of a parent pool's device slots (reference: ``SubRayResourcePool``,
+    ``verl/single_controller/ray/base.py:170-186``): worker ``i`` of a group built on it runs on the parent's slot
+    ``start_index + i``, so several groups can own disjoint GPUs of one machine."""
+
+    def __init__(self, parent: ResourcePool, start_index: int, size: int):
+        super().__init__(parent.store, parent.max_colocate_count, parent.n_gpus_per_node)
+        assert 0 <= start_index and start_index + size <= len(parent.device_slots()), "slice exceeds the parent pool"
+        self.parent, self.start_index, self.size = parent, start_index, size
+
+    @property
+    def world_size(self) -> int:
+        return self.size
+
+    def device_slots(self) -> list[tuple[int, int]]:
+        return self.parent.device_slots()[self.start_index:self.start_index + self.size]
+
+    def local_rank_list(self) -> list[int]:
+        return [d for _, d in self.device_slots()]
+
+    def local_world_size_list(self) -> list[int]:
+        slots = self.device_slots()
+        per_node: dict = {}
+        for node, _ in slots:
+            per_node[node] = per_node.get(node, 0) + 1
+        return [per_node[node] for node, _ in slots]
+
+
+def split_resource_pool(pool: ResourcePool, split_size) -> list:
+    """Cut ``pool`` into sub-pools of ``split_size`` workers each (an int that divides the world size, or a list of sizes
+    that sums to it). Sub-pools can be split again (reference: ``verl/single_controller/ray/base.py:280-327``)."""
+    if isinstance(split_size, int):
+        assert split_size > 0 and pool.world_size % split_size == 0, "split_size must be a divisor of world_size"
+        sizes = [split_size] * (pool.world_size // split_size)
+    else:
+        sizes = list(split_size)
+    assert sum(sizes) == pool.world_size, "split sizes must sum up to world_size"
+    out, start = [], 0
+    for n in sizes:
+        out.append(SubResourcePool(pool, start, n))
+        start += n
+    return out
+
+
+def merge_resource_pool(a: ResourcePool, b: ResourcePool) -> ResourcePool:
+    """One pool over the nodes of both (``a``'s nodes first); both must agree on colocation and GPUs per node
+    (reference: ``verl/single_controller/ray/base.py:329-345``)."""
+    assert a.max_colocate_count == b.max_colocate_count, "both pools must have the same max_colocate_count"
+    assert a.n_gpus_per_node == b.n_gpus_per_node, "both pools must have the same n_gpus_per_node"
+    assert not isinstance(a, SubResourcePool) and not isinstance(b, SubResourcePool), "merge whole pools, not slices"
+    return ResourcePool(list(a.store) + list(b.store), a.max_colocate_count, a.n_gpus_per_node)
+
+
+class ResourcePoolManager:
+    """Named pools and a role → pool mapping: ``resource_pool_spec = {"global_pool": [8, 8]}``, ``mapping = {"actor_rollout":
+    "global_pool", "critic": "global_pool"}`` (reference: ``verl/single_controller/ray/base.py:189-247``). ``available`` is
+    the number of devices this launcher can place workers on (default: what ``torch.cuda.device_count()`` reports, or no
+    limit on CPU); creation fails early when the spec asks for more."""
+
+    def __init__(self, resource_pool_spec: dict, mapping: dict, max_colocate_count: int = 3, available: Optional[int] = None):
+        self.resource_pool_spec, self.mapping, self.max_colocate_count = dict(resource_pool_spec), dict(mapping), max_colocate_count
+        self.available = available
+        self.resource_pool_dict: dict = {}
+
+    def create_resource_pool(self):
+        for name, process_on_nodes in self.resource_pool_spec.items():
+            self.resource_pool_dict[name] = ResourcePool(list(process_on_nodes), self.max_colocate_count)
+        self._check_resource_available()
+        return self.resource_pool_dict
+
+    def get_resource_pool(self, role) -> ResourcePool:
+        return self.resource_pool_dict[self.mapping[role]]
+
+    def get_n_gpus(self) -> int:
+        return sum(n for nodes in self.resource_pool_spec.values() for n in nodes)
+
+    def _check_resource_available(self):
+        have = self.available
+        if have is None:
+            try:
+                import torch
+
+                have = torch.cuda.device_count() if torch.cuda.is_available() else None
+            except Exception:  # noqa: BLE001
+                have = None
+        if have is None:
+            return
+        total = self.get_n_gpus()
+        single_node = all(len(nodes) == 1 for nodes in self.resource_pool_spec.values())
+        if single_node and total > have:
+            raise ValueError(f"Total available devices {have} is less than total desired devices {total}")
+        if any(n > have for nodes in self.resource_pool_spec.values() for n in nodes):
+            raise ValueError(f"a pool asks for more devices on one node than the {have} a node has")
 
 
 class ClassWithInitArgs:

@@ -158,7 +158,7 @@ class ProcessWorkerGroup(WorkerGroup):
         env = {"MASTER_ADDR": addr, "MASTER_PORT": port, "WG_PREFIX": name_prefix, "WG_BACKEND": "process",
                "LOCAL_WORLD_SIZE": str(resource_pool.store[0] if resource_pool.store else world)}
         env.update(env_vars or {})
-        local_ranks = resource_pool.local_rank_list()
+        local_ranks = resource_pool.local_rank_list()        # for a sub-pool: the parent's device indices of its slice
         for r in range(world):
             parent, child = ctx.Pipe()
             p = ctx.Process(target=_worker_main, args=(child, r, world, local_ranks[r], env, cls_with_init_args, use_gpu), daemon=True)

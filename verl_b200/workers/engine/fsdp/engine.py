@@ -403,7 +403,16 @@ class FSDPEngine(BaseEngine):
                 self.store.rebind(host)
             elif not to_cpu and not self.store.flat.is_cuda:
                 IO_STATS["h2d_bytes"] += self.store.flat.numel() * self.store.flat.element_size()
-                self.store.rebind(self.store.flat.to(target, non_blocking=True))
+                pre = getattr(self, "_prefetched", None)
+                self._prefetched = None
+                if pre is not None and pre[0].shape == self.store.flat.shape:
+                    # the copy was started earlier on a side stream (prefetch_params): only wait for it
+                    dev_flat, ev = pre
+                    torch.cuda.current_stream().wait_event(ev)
+                    dev_flat.record_stream(torch.cuda.current_stream())
+                    self.store.rebind(dev_flat)
+                else:
+                    self.store.rebind(self.store.flat.to(target, non_blocking=True))
         if optimizer and not self.forward_only:
             for name in ("master", "exp_avg", "exp_avg_sq"):
                 t = getattr(self, name)
@@ -418,6 +427,24 @@ class FSDPEngine(BaseEngine):
             self.store.free_grads()
         if to_cpu:
             torch.cuda.empty_cache()
+
+    def prefetch_params(self) -> bool:
+        """Start bringing offloaded (pinned-host) parameters back on a side stream, so that the copy runs under whatever the
+        GPU is doing now; the next ``to("cuda")`` only waits for it. Used for the frozen reference policy: its 2 bytes per
+        parameter cross PCIe while the actor's old-log-prob pass computes. Returns True when a copy was started."""
+        if self.device.type != "cuda" or self.store is None or self.store.flat.is_cuda or getattr(self, "_prefetched", None) is not None:
+            return False
+        if not self.store.flat.is_pinned():
+            return False
+        if getattr(self, "_prefetch_stream", None) is None:
+            self._prefetch_stream = torch.cuda.Stream()
+        with torch.cuda.stream(self._prefetch_stream):
+            dev_flat = torch.empty(self.store.flat.shape, dtype=self.store.flat.dtype, device=self.device)
+            dev_flat.copy_(self.store.flat, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self._prefetch_stream)
+        self._prefetched = (dev_flat, ev)
+        return True
 
     # ------------------------------------------------------------------ micro-batching
     def _prefix_sharing(self, meta: dict, tensors: dict) -> bool:

@@ -470,6 +470,8 @@ class ActorRolloutRefWorker(Worker):
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
     def compute_log_prob(self, data: DataProto) -> DataProto:
         mode = self._router_replay_mode()
+        if self.ref is not None and hasattr(self.ref.engine, "prefetch_params") and self.ref.engine.is_param_offload_enabled:
+            self.ref.engine.prefetch_params()       # the reference pass comes next: its parked weights travel during this pass
         mo = self._logprob_pass(self.actor, data, calculate_entropy=True, replay=mode == "R3", record=mode == "R2")
         tensors = {"old_log_probs": _to_host(mo["log_probs"])}
         if "entropy" in mo:
