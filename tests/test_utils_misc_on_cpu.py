@@ -354,3 +354,57 @@ def test_tracking_backends_with_stand_in_sdks(monkeypatch, tmp_path):
         pass
     assert len(calls) == n
     RLInsightLogger._module, RLInsightLogger._started = None, False
+
+
+def test_nsys_wrapping_and_precision_debugger(tmp_path):
+    import json
+    import os
+
+    import torch
+
+    from verl_b200.utils.profiler.config import ProfilerConfig
+    from verl_b200.utils.profiler.nsys import nsys_command_prefix, relocate_results, wrap_worker_command
+    from verl_b200.utils.profiler.precision_debugger import PrecisionDebugger, compare_dumps
+    from verl_b200.utils.profiler.profile import DistProfiler
+
+    cmd = nsys_command_prefix({"trace": "cuda,nvtx", "kill": None, "cuda-memory-usage": False}, "/tmp/out/rep", discrete=True)
+    assert cmd[:2] == ["nsys", "profile"] and "--trace=cuda,nvtx" in cmd and "--capture-range=cudaProfilerApi" in cmd
+    assert "--capture-range-end=repeat" in cmd and "--cuda-memory-usage=false" in cmd and not any(c.startswith("--kill") for c in cmd)
+    assert cmd[-2:] == ["-o", "/tmp/out/rep"]
+    full = wrap_worker_command(["python", "-m", "x"], None, str(tmp_path / "prof"), role="actor", rank=3)
+    assert full[-3:] == ["python", "-m", "x"] and "actor_rank3_" in full[full.index("-o") + 1]
+    src = tmp_path / "raylogs"
+    src.mkdir()
+    (src / "worker_process_4242.nsys-rep").write_text("x")
+    (src / "worker_process_4242.1.nsys-rep").write_text("y")
+    (src / "worker_process_9.nsys-rep").write_text("other process")
+    moved = relocate_results(str(tmp_path / "dst"), str(src), pid=4242, role="ref")
+    assert len(moved) == 2 and all(os.path.basename(m).startswith("ref_") for m in moved) and (src / "worker_process_9.nsys-rep").exists()
+    assert relocate_results(str(tmp_path / "dst"), str(src), pid=4242) == [] and relocate_results(None, str(src)) == []
+
+    def run(scale, out):
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
+        prof = DistProfiler(0, ProfilerConfig(tool="precision_debugger", enable=True, all_ranks=True, save_path=str(out),
+                                              tool_config={"stages": ["actor_update"]}))
+        prof.start(stage="actor_update", model=model, step=7)
+        x = torch.ones(2, 8)
+        with torch.no_grad():
+            model[2].weight.mul_(scale)
+        model(x).sum().backward()
+        prof.stop()
+        prof.start(stage="ref_compute_log_prob", model=model)     # not among the configured stages: records nothing
+        model(x)
+        prof.stop()
+        return os.path.join(out, "precision_rank0.jsonl")
+
+    a, b, c = run(1.0, tmp_path / "a"), run(1.0, tmp_path / "b"), run(1.5, tmp_path / "c")
+    rows = [json.loads(x) for x in open(a)]
+    assert {r["module"] for r in rows if r["kind"] == "forward"} == {"0", "1", "2"} and all(r["step"] == 7 and r["stage"] == "actor_update" for r in rows)
+    assert {r["module"] for r in rows if r["kind"] == "grad"} == {"0.weight", "0.bias", "2.weight", "2.bias"}
+    assert compare_dumps(a, b) is None
+    diff = compare_dumps(a, c)
+    assert diff is not None and diff["a"]["module"] == "2"          # the first module whose output changes
+    import pytest as _pt
+    with _pt.raises(ValueError):
+        PrecisionDebugger(0, str(tmp_path), stages=["nope"])

@@ -7,12 +7,25 @@ from typing import Optional
 
 from verl_b200.base_config import BaseConfig
 
-__all__ = ["ProfilerConfig", "TorchProfilerToolConfig", "TorchMemoryToolConfig", "NsightToolConfig"]
+__all__ = ["ProfilerConfig", "TorchProfilerToolConfig", "TorchMemoryToolConfig", "NsightToolConfig", "PrecisionDebuggerToolConfig"]
 
 
 @dataclass
 class NsightToolConfig(BaseConfig):
+    """``discrete``: one report per annotated call instead of one per step; the ``*_nsight_options`` mappings become the
+    ``nsys profile`` options of the controller / worker processes (``utils/profiler/nsys.py``)."""
+
     discrete: bool = False
+    controller_nsight_options: Optional[dict] = None
+    worker_nsight_options: Optional[dict] = None
+
+
+@dataclass
+class PrecisionDebuggerToolConfig(BaseConfig):
+    """Stages to fingerprint (``None`` = all) and whether an unknown stage name is an error."""
+
+    stages: Optional[list] = None
+    strict: bool = False
 
 
 @dataclass

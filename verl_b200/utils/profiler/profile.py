@@ -82,6 +82,26 @@ class _NsysTool:
             torch.cuda.profiler.stop()
 
 
+class _PrecisionTool:
+    """Per-module numeric fingerprints of the stages named in ``tool_config.stages`` (see ``precision_debugger.py``); the
+    worker passes ``stage=`` and ``model=`` to ``DistProfiler.start``."""
+
+    def __init__(self, rank, cfg):
+        from .precision_debugger import PrecisionDebugger
+
+        tc = cfg.tool_config or {}
+        self.dbg = PrecisionDebugger(rank, cfg.save_path, tc.get("stages"), bool(tc.get("strict", False)))
+        self._model = None
+
+    def start(self, stage: str = "actor_update", model=None, step: int = 0, **kw):
+        if model is not None and self.dbg.start(stage, model, step):
+            self._model = model
+
+    def stop(self):
+        self.dbg.stop(self._model)
+        self._model = None
+
+
 class _MemoryTool:
     def __init__(self, rank, cfg):
         self.rank, self.cfg = rank, cfg
@@ -103,7 +123,7 @@ class DistProfiler:
         self.rank = rank
         self.config = config or ProfilerConfig()
         self.enabled = bool(self.config.enable and self.config.tool) and (self.config.all_ranks or rank in self.config.ranks)
-        impl = {"torch": _TorchTool, "nsys": _NsysTool, "torch_memory": _MemoryTool}.get(self.config.tool)
+        impl = {"torch": _TorchTool, "nsys": _NsysTool, "torch_memory": _MemoryTool, "precision_debugger": _PrecisionTool}.get(self.config.tool)
         self._impl = impl(rank, self.config) if (self.enabled and impl) else None
         self._running = False
 
@@ -120,6 +140,14 @@ class DistProfiler:
             self._impl.stop()
             self._running = False
             self._run_finish_hook()
+
+    def relocate_results(self, source_dir: str, role: Optional[str] = None) -> list:
+        """nsys writes its reports where the launcher pointed it; move this process's files under ``save_path``."""
+        if self.config.tool != "nsys":
+            return []
+        from .nsys import relocate_results
+
+        return relocate_results(self.config.save_path, source_dir, role=role)
 
     def _run_finish_hook(self):
         cmd = self.config.finish_hook_cmd
