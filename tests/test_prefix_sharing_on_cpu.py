@@ -132,7 +132,7 @@ def test_on_policy_distillation_step(tmp_path):
 
     ov = ["data.synthetic.enable=true", "data.synthetic.num_prompts=64", "data.train_batch_size=4", "data.max_prompt_length=32",
           "data.max_response_length=8", "actor_rollout_ref.model.preset=tiny-qwen2", "actor_rollout_ref.rollout.n=2",
-          "actor_rollout_ref.actor.ppo_mini_batch_size=4", "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=8",
+          "actor_rollout_ref.actor.ppo_mini_batch_size=2", "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=8",
           "actor_rollout_ref.actor.use_kl_loss=false", "actor_rollout_ref.rollout.log_prob_micro_batch_size_per_gpu=8",
           "actor_rollout_ref.rollout.max_num_seqs=8", "actor_rollout_ref.model.enable_gradient_checkpointing=false",
           "actor_rollout_ref.actor.optim.lr=3e-3", "actor_rollout_ref.distillation.enable=true", "actor_rollout_ref.distillation.teacher_model.preset=tiny-qwen2",

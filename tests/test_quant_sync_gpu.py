@@ -70,6 +70,35 @@ def test_reshard_gather_and_requant_from_row_shards():
     assert torch.equal(keep, full[256:556]) and (q.float() != qr.float()).float().mean() < 1e-3
 
 
+def test_reshard_into_parameter_slices_rows_and_columns():
+    """The in-place gather behind the actor -> rollout weight hand-off, with the 'trainer ranks' emulated by two buffers of this
+    GPU: a tensor-parallel rollout slice is either a set of row ranges (column-parallel layers: q | k | v blocks) or a column
+    range of every row (row-parallel layers). Results are bitwise equal to slicing the gathered matrix; memory outside the
+    destination view stays untouched."""
+    from verl_b200.checkpoint_engine.reshard import gather_rows_into
+
+    torch.manual_seed(3)
+    N, K, W = 1536, 1024, 2
+    full = torch.randn(N, K, device="cuda").bfloat16()
+    shards = [full[r * (N // W):(r + 1) * (N // W)].contiguous() for r in range(W)]
+    ptrs = torch.tensor([s.data_ptr() for s in shards], dtype=torch.int64)
+    # column-parallel: rollout rank 1 of 2 owns the second half of each of three row blocks (sizes 1024 | 256 | 256)
+    segs, tp, tp_rank = [1024, 256, 256], 2, 1
+    dst = torch.full((sum(n // tp for n in segs) + 16, K), 7.0, device="cuda", dtype=torch.bfloat16)      # 16 guard rows
+    off = doff = 0
+    for n in segs:
+        per = n // tp
+        gather_rows_into(ptrs, N // W, K, off + tp_rank * per, dst[doff:doff + per])
+        off += n
+        doff += per
+    want = torch.cat([full[0:1024][512:], full[1024:1280][128:], full[1280:1536][128:]])
+    assert torch.equal(dst[:doff], want) and bool((dst[doff:] == 7.0).all())
+    # row-parallel: rollout rank 1 of 2 owns columns [512, 1024) of every row; the destination is a column window of a wider buffer
+    wide = torch.full((N, K // 2 + 16), 7.0, device="cuda", dtype=torch.bfloat16)
+    gather_rows_into(ptrs, N // W, K, 0, wide[:, 8:8 + K // 2], col_begin=K // 2)
+    assert torch.equal(wide[:, 8:8 + K // 2], full[:, K // 2:]) and bool((wide[:, :8] == 7.0).all()) and bool((wide[:, 8 + K // 2:] == 7.0).all())
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,N,K", [(512, 768, 1024), (300, 520, 2064), (2048, 4096, 4096), (17, 40, 144)])
 def test_fp8_gemm_matches_dequantised_reference(M, N, K):

@@ -198,9 +198,11 @@ void gemm_kseg(const Tensor& a_ptrs, int64_t k_per_rank, int64_t rows_total, int
 }
 
 // Two-launch all-reduce (see vb_gemm_allreduce_sig): out = sum over ranks of (a_r @ b_r^T) (+ residual)
+// phase 0 = both launches (the normal call); 1 = only the GEMM that writes and signals, 2 = only the slot sum. The split lets a
+// single-GPU test play several ranks: every rank's GEMM first, then every rank's slot sum, so that no launch waits for a later one.
 void gemm_allreduce_sig(const Tensor& a, const Tensor& b, const Tensor& out_ptrs, const Tensor& sig_ptrs, int64_t rank, int64_t half_elems,
                         const Tensor& slots_local, const Tensor& sig_local, const c10::optional<Tensor>& residual, Tensor& out, int64_t bn,
-                        int64_t split_k, int64_t max_split) {
+                        int64_t split_k, int64_t max_split, int64_t phase) {
   TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_allreduce_sig: bad operands");
   TORCH_CHECK(out_ptrs.scalar_type() == at::kLong && !out_ptrs.is_cuda() && sig_ptrs.scalar_type() == at::kLong && !sig_ptrs.is_cuda() &&
                   out_ptrs.numel() == sig_ptrs.numel(), "gemm_allreduce_sig: pointer tables must be CPU int64 tensors of equal length");
@@ -217,10 +219,12 @@ void gemm_allreduce_sig(const Tensor& a, const Tensor& b, const Tensor& out_ptrs
   if (split_k > 0) ps = (int)split_k;
   if (ps > max_split) ps = (int)max_split;
   while (ps > 1 && (int64_t)ps * slot_elems > half_elems) --ps;
-  check_rc(vb_gemm_allreduce_sig(a.data_ptr(), b.data_ptr(), M, N, K, (int)a.stride(0), (int)b.stride(0), out_ptrs.data_ptr<long>(), sig_ptrs.data_ptr<long>(),
-                                 (int)rank, world, slot_elems, half_elems, pbn, ps, err, cur_stream()),
-           "gemm_allreduce_sig");
-  check_rc(vb_slots_reduce_sig(out_ptrs.data_ptr<long>(), sig_local.data_ptr(), (int)rank, world, ps, slot_elems, half_elems, M, N, res, out.data_ptr(), N, err, cur_stream()),
+  if (phase != 2)
+    check_rc(vb_gemm_allreduce_sig(a.data_ptr(), b.data_ptr(), M, N, K, (int)a.stride(0), (int)b.stride(0), out_ptrs.data_ptr<long>(), sig_ptrs.data_ptr<long>(),
+                                   (int)rank, world, slot_elems, half_elems, pbn, ps, err, cur_stream()),
+             "gemm_allreduce_sig");
+  if (phase != 1)
+    check_rc(vb_slots_reduce_sig(out_ptrs.data_ptr<long>(), sig_local.data_ptr(), (int)rank, world, ps, slot_elems, half_elems, M, N, res, out.data_ptr(), N, err, cur_stream()),
            "slots_reduce_sig");
 }
 
@@ -239,6 +243,6 @@ TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
   m.def("gemm_peer_scatter(Tensor a, Tensor b, Tensor out_ptrs, int rank, int rows_per_owner, int slot_elems) -> ()", &gemm_peer_scatter);
   m.def("gemm_head_scatter(Tensor a, Tensor b, Tensor? bias, Tensor out_ptrs, int ld_out, int row_off, int head_dim, Tensor head_rank, Tensor head_slot) -> ()", &gemm_head_scatter);
   m.def("gemm_kseg(Tensor a_ptrs, int k_per_rank, int rows_total, int row_off, Tensor b, Tensor(a!) out, Tensor? bias, int rank=0, Tensor? stage=None, Tensor? flags=None, int epoch=0) -> ()", &gemm_kseg);
-  m.def("gemm_allreduce_sig(Tensor a, Tensor b, Tensor out_ptrs, Tensor sig_ptrs, int rank, int half_elems, Tensor slots_local, Tensor sig_local, Tensor? residual, Tensor(a!) out, int bn=0, int split_k=0, int max_split=8) -> ()", &gemm_allreduce_sig);
+  m.def("gemm_allreduce_sig(Tensor a, Tensor b, Tensor out_ptrs, Tensor sig_ptrs, int rank, int half_elems, Tensor slots_local, Tensor sig_local, Tensor? residual, Tensor(a!) out, int bn=0, int split_k=0, int max_split=8, int phase=0) -> ()", &gemm_allreduce_sig);
   m.def("slots_reduce(Tensor slots, int world, int slot_elems, int rows, int cols, Tensor? residual, Tensor(a!) out) -> ()", &slots_reduce);
 }

@@ -20,7 +20,7 @@ from functools import lru_cache
 import torch
 import torch.distributed as dist
 
-__all__ = ["context_parallel_attention", "build_cp_plan", "AllGatherRows"]
+__all__ = ["context_parallel_attention", "cp_attention_local", "build_cp_plan", "AllGatherRows"]
 
 
 class AllGatherRows(torch.autograd.Function):
@@ -97,19 +97,26 @@ def build_cp_plan(cu_seqlens_cpu: torch.Tensor, t_pad: int, world: int, rank: in
 def context_parallel_attention(qkv: torch.Tensor, pb, cfg, group) -> torch.Tensor:
     """``qkv`` [T/W, (Hq+2Hkv)·D]: this rank's slice of the packed stream (rope already applied); ``pb.cu_seqlens_cpu``
     describes the whole micro-batch. Returns the attention output of the local rows [T/W, Hq·D]."""
-    from verl_b200 import ops
-
     W, r = dist.get_world_size(group), dist.get_rank(group)
-    tl = qkv.shape[0]
     q_size = cfg.num_attention_heads * cfg.head_dim
     kv_all = AllGatherRows.apply(qkv[:, q_size:].contiguous(), group)
-    zigzag = bool(getattr(pb, "cp_zigzag", False))
-    kv_idx, q_pos, cu_exp, q_starts, max_len = build_cp_plan(pb.cu_seqlens_cpu, tl * W, W, r, zigzag)
-    dev = qkv.device
+    return cp_attention_local(qkv[:, :q_size], kv_all, pb.cu_seqlens_cpu, cfg, W, r, bool(getattr(pb, "cp_zigzag", False)))
+
+
+def cp_attention_local(q: torch.Tensor, kv_all: torch.Tensor, cu_seqlens_cpu: torch.Tensor, cfg, W: int, r: int, zigzag: bool) -> torch.Tensor:
+    """The rank-local part: ``q`` [T/W, Hq·D] are rank ``r``'s query rows, ``kv_all`` [T, 2·Hkv·D] the K/V rows of all ranks in
+    rank order (for the zig-zag placement that is the zig-zag order). No communication happens here, so one process can
+    play every rank in turn."""
+    from verl_b200 import ops
+
+    tl = q.shape[0]
+    q_size = cfg.num_attention_heads * cfg.head_dim
+    kv_idx, q_pos, cu_exp, q_starts, max_len = build_cp_plan(cu_seqlens_cpu, tl * W, W, r, zigzag)
+    dev = q.device
     if zigzag:      # the gathered K/V rows come in rank order = zig-zag order: look global tokens up through the inverse
         kv_idx = torch.argsort(zigzag_permutation(tl * W, W)).index_select(0, kv_idx)
     kv_idx, q_pos = kv_idx.to(dev), q_pos.to(dev)
-    q_exp = qkv.new_zeros(kv_idx.numel(), q_size).index_copy(0, q_pos, qkv[:, :q_size])
+    q_exp = q.new_zeros(kv_idx.numel(), q_size).index_copy(0, q_pos, q)
     qkv_exp = torch.cat([q_exp, kv_all.index_select(0, kv_idx)], dim=1)
     o = ops.attention_varlen(qkv_exp, cu_exp.to(dev), cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, max_len, cu_exp,
                              q_starts=q_starts)

@@ -75,9 +75,16 @@ def to_container(cfg) -> Any:
 
 def _parse_value(s: str):
     try:
-        return yaml.safe_load(s)
+        v = yaml.safe_load(s)
     except yaml.YAMLError:
         return s
+    if isinstance(v, str):
+        # YAML 1.1 does not read "1e-6" as a number (it wants "1.0e-6"); launch scripts write it that way
+        try:
+            return float(v) if any(c in v for c in "eE.") and v.lower() not in ("nan", "inf", "-inf", ".", "e") else v
+        except ValueError:
+            return v
+    return v
 
 
 def _merge(base: dict, extra: dict) -> dict:
@@ -124,9 +131,38 @@ def apply_overrides(cfg: dict, overrides: Sequence[str]) -> dict:
     return cfg
 
 
-def _load_yaml_with_defaults(path: str, seen=None) -> dict:
-    """``defaults:`` entries ``group@target.path: name`` load ``<dir>/<group>/<name>.yaml`` under ``target.path``;
-    ``_self_`` marks where this file's own keys are merged."""
+_CHOICE_RE = None
+
+
+def _split_group_overrides(overrides: Sequence[str], config_dir: str) -> tuple[dict, list]:
+    """Command-line items that choose a config GROUP member rather than set a value: ``model_engine=megatron`` or
+    ``actor@actor_rollout_ref.actor=megatron_actor``. An item counts as a group choice when ``<config_dir>/<group>/`` exists
+    and the key has no dot outside an ``@target``. Returns ({group or group@target: name}, remaining value overrides)."""
+    choices, rest = {}, []
+    for ov in overrides or []:
+        if "=" in ov and not ov.startswith(("+", "~")):
+            key, val = ov.split("=", 1)
+            group = key.split("@", 1)[0]
+            if "." not in group and os.path.isdir(os.path.join(config_dir, group)):
+                choices[key] = val
+                continue
+        rest.append(ov)
+    return choices, rest
+
+
+def _load_yaml_with_defaults(path: str, choices: Optional[dict] = None, root_dir: Optional[str] = None, selected: Optional[dict] = None) -> dict:
+    """Compose one yaml file with its ``defaults`` list (the subset of Hydra's semantics the config tree uses):
+
+    * ``- name``                      merge ``<dir>/name.yaml`` at this file's root;
+    * ``- group: name``               merge ``<dir>/group/name.yaml`` under key ``group`` and remember the choice, so that later
+                                      entries (and files) may say ``${group}`` in a member name;
+    * ``- group@a.b: name``           merge it under ``a.b`` instead;
+    * ``- ../group@a: name``          group directory relative to this file's directory (used inside group files);
+    * ``- _self_``                    where this file's own keys go (default: last);
+    * ``choices`` (from the command line) replace the member name of a ``group`` / ``group@target`` entry.
+    """
+    choices = choices or {}
+    selected = selected if selected is not None else {}
     with open(path) as f:
         data = yaml.safe_load(f) or {}
     defaults = data.pop("defaults", None)
@@ -134,68 +170,131 @@ def _load_yaml_with_defaults(path: str, seen=None) -> dict:
         return data
     root: dict = {}
     base_dir = os.path.dirname(path)
+    root_dir = root_dir or base_dir
     merged_self = False
+
+    def member(name) -> str:
+        name = str(name)
+        for g, v in selected.items():
+            name = name.replace("${" + g + "}", str(v))
+        return name
+
     for entry in defaults:
         if entry == "_self_":
             _merge(root, data)
             merged_self = True
             continue
-        if isinstance(entry, dict):
-            (k, name), = entry.items()
-            group, _, target = k.partition("@")
-            sub = _load_yaml_with_defaults(os.path.join(base_dir, group, f"{name}.yaml"))
-            node = root
-            if target:
-                for p in target.split("."):
-                    node = node.setdefault(p, {})
-            else:
-                node = root.setdefault(group, {})
+        if isinstance(entry, str):
+            _merge(root, _load_yaml_with_defaults(os.path.join(base_dir, f"{member(entry)}.yaml"), choices, root_dir, selected))
+            continue
+        (k, name), = entry.items()
+        group, _, target = k.partition("@")
+        name = choices.get(k, choices.get(os.path.basename(group), name))      # `group@target=x` or plain `group=x`
+        if name is None or name == "null":
+            continue
+        name = member(name)
+        gdir = os.path.normpath(os.path.join(base_dir, group))
+        gname = os.path.basename(gdir)
+        if not target:
+            selected[gname] = name
+        sub = _load_yaml_with_defaults(os.path.join(gdir, f"{name}.yaml"), choices, root_dir, selected)
+        node = root
+        if target:
+            for p in target.split("."):
+                node = node.setdefault(p, {})
             _merge(node, sub)
+        elif isinstance(sub, dict) and set(sub.keys()) == {gname} and not isinstance(sub[gname], dict):
+            root[gname] = sub[gname]          # a pure selector file such as ``model_engine: dp``
+        else:
+            _merge(root.setdefault(gname, {}), sub)
     if not merged_self:
         _merge(root, data)
     return root
 
 
+_MISSING = "???"
+
+
 def resolve_interpolations(root: dict) -> dict:
-    """Replace ``${a.b.c}`` references (OmegaConf style) by the value they point at, after overrides were applied."""
+    """Replace ``${a.b.c}`` (absolute), ``${.sibling}`` / ``${..uncle}`` (relative to the node holding the value) and
+    ``${oc.select:a.b,default}`` (value or default when the path is absent or null) references, after overrides were applied."""
     import re
 
-    pat = re.compile(r"\$\{([^}]+)\}")
+    pat = re.compile(r"\$\{((?:[^${}]|\$\{[^${}]*\})+)\}")
 
-    def lookup(path: str, depth=0):
+    def walk_to(path_parts):
         cur: Any = root
-        for part in path.split("."):
+        for part in path_parts:
             cur = cur[part]
-        return resolve(cur, depth + 1)
+        return cur
 
-    def resolve(v, depth=0):
+    def lookup(expr: str, here: tuple, depth: int):
         if depth > 20:
             raise ValueError("interpolation cycle in config")
-        if isinstance(v, str):
+        expr = expr.strip()
+        if expr.startswith("oc.select:"):
+            body = expr[len("oc.select:"):]
+            path, _, default = body.partition(",")
+            try:
+                v = lookup(path.strip(), here, depth + 1)
+            except (KeyError, TypeError, IndexError):
+                v = None
+            if v is None or v == _MISSING:
+                d = default.strip()
+                if not _:
+                    return None
+                return resolve(_parse_value(d) if not d.startswith("${") else d, here, depth + 1)
+            return v
+        if expr.startswith("."):
+            up = len(expr) - len(expr.lstrip("."))
+            base = here[:len(here) - (up - 1)] if up - 1 <= len(here) else ()
+            parts = tuple(base) + tuple(x for x in expr.lstrip(".").split(".") if x)
+        else:
+            parts = tuple(expr.split("."))
+        return resolve(walk_to(parts), parts[:-1], depth + 1)
+
+    def resolve(v, here: tuple, depth=0):
+        if isinstance(v, str) and "${" in v:
             m = pat.fullmatch(v.strip())
             if m:
-                return lookup(m.group(1), depth)
-            return pat.sub(lambda mm: str(lookup(mm.group(1), depth)), v)
+                return lookup(m.group(1), here, depth)
+            return pat.sub(lambda mm: str(lookup(mm.group(1), here, depth)), v)
         return v
 
-    def walk(node):
+    def walk(node, here: tuple):
         if isinstance(node, dict):
             for k in list(node.keys()):
-                node[k] = walk(node[k])
+                node[k] = walk(node[k], here + (k,)) if isinstance(node[k], (dict, list)) else resolve(node[k], here)
             return node
         if isinstance(node, list):
-            return [walk(x) for x in node]
-        return resolve(node)
+            return [walk(x, here) if isinstance(x, (dict, list)) else resolve(x, here[:-1] if False else here) for x in node]
+        return resolve(node, here)
 
-    return walk(root)
+    return walk(root, ())
+
+
+# spellings of the reference's tree that differ from this one's, rewritten on the command line
+_OVERRIDE_ALIASES = (("critic.fsdp.", "critic.fsdp_config."), ("distillation.", "actor_rollout_ref.distillation."),
+                     ("reward.reward_manager.name=", "reward.reward_manager="))
+
+
+def _alias_override(ov: str) -> str:
+    lead = ov[:len(ov) - len(ov.lstrip("+~"))]
+    body = ov[len(lead):]
+    for old, new in _OVERRIDE_ALIASES:
+        if body.startswith(old):
+            return lead + new + body[len(old):]
+    return ov
 
 
 def load_config(path_or_name: str = "ppo_trainer", overrides: Optional[Sequence[str]] = None, config_dir: Optional[str] = None) -> Config:
     if not os.path.exists(path_or_name):
         config_dir = config_dir or os.path.join(os.path.dirname(os.path.dirname(__file__)), "trainer", "config")
         path_or_name = os.path.join(config_dir, f"{path_or_name}.yaml")
-    data = _load_yaml_with_defaults(path_or_name)
-    apply_overrides(data, overrides or [])
+    config_dir = config_dir or os.path.dirname(os.path.abspath(path_or_name))
+    choices, values = _split_group_overrides([_alias_override(o) for o in (overrides or [])], config_dir)
+    data = _load_yaml_with_defaults(path_or_name, choices)
+    apply_overrides(data, values)
     resolve_interpolations(data)
     return Config(data)
 
