@@ -107,3 +107,46 @@ def test_prefix_shared_training_pass_matches_plain_pass_on_gpu():
     assert abs(g0.norm() / g1.norm() - 1) < 0.03
     torch.cuda.synchronize()
     _ext.check_status("prefix sharing on gpu")
+
+
+def test_chunked_prefill_and_prefix_cache_give_the_log_probs_of_a_plain_prefill():
+    """Prompts of 300-700 tokens under a 256-token step budget are prefilled in chunks that attend to the chunks already in
+    the paged cache (q_starts > 128: the kernels skip whole query tiles); a second call reuses the cached blocks of the first.
+    Sampled tokens are seeded identically, so the token ids must agree with the unchunked engine while the log-probs agree to
+    bf16 accuracy."""
+    from verl_b200.ops import _ext
+    from verl_b200.workers.rollout import InferenceEngine, SamplingParams
+
+    model = _model(2)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(10, model.cfg.vocab_size, (int(n),), generator=g).tolist() for n in (700, 300, 45, 513)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, seed=3)
+    plain = InferenceEngine(model, max_num_seqs=8, max_model_len=1024, num_blocks=96, sync_interval=4, max_num_batched_tokens=8192,
+                            enable_prefix_caching=False)
+    want = plain.generate(prompts, sp)
+    plain.sleep()
+    eng = InferenceEngine(model, max_num_seqs=8, max_model_len=1024, num_blocks=96, sync_interval=4, max_num_batched_tokens=256)
+    got = eng.generate(prompts, sp)
+    assert eng.stats["prefill_chunks"] == 2 + 1 + 0 + 2
+
+    def close(a, b):
+        # greedy decoding on bf16 logits: a near-tie may flip a token, after which the continuations differ legitimately
+        n = next((i for i, (x, y) in enumerate(zip(a.token_ids, b.token_ids)) if x != y), len(a.token_ids))
+        assert n >= 4, (a.token_ids, b.token_ids)
+        d = max(abs(x - y) for x, y in zip(a.log_probs[:n], b.log_probs[:n]))
+        assert d < 0.08, d
+
+    for a, b in zip(got, want):
+        close(a, b)
+    # follow-up turns inside the same wake period hit the cached blocks (prompt and generated tokens)
+    turn2 = [p + o.token_ids + [21, 22, 23] for p, o in zip(prompts[:2], got[:2])]
+    hits0 = eng.stats["prefix_cache_hit_tokens"]
+    got2 = eng.generate(turn2, sp)
+    assert eng.stats["prefix_cache_hit_tokens"] - hits0 == (711 // 64) * 64 + (311 // 64) * 64
+    eng.sleep()
+    plain.wake_up()
+    want2 = plain.generate(turn2, sp)
+    for a, b in zip(got2, want2):
+        close(a, b)
+    torch.cuda.synchronize()
+    _ext.check_status("chunked prefill")

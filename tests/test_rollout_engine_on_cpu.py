@@ -167,3 +167,90 @@ def test_rollout_records_the_routed_experts_of_every_fed_token():
             lp = model(pb, labels=torch.roll(torch.tensor(ids), -1), need_entropy=False)["log_probs"]
         got = lp[len(p) - 1:len(ids) - 1]
         assert torch.allclose(got, torch.tensor(o.log_probs), atol=1e-4)
+
+
+def test_scheduler_chunks_a_prompt_longer_than_the_step_budget():
+    s = Scheduler(num_blocks=16, block_size=64, max_num_seqs=4, max_batched_tokens=128, prefix_caching=False)
+    s.add(0, 300, 5, tokens=list(range(300)))
+    s.add(1, 40, 5, tokens=list(range(1000, 1040)))
+    seen = []
+    for _ in range(3):
+        kind, ids, slots, lens, forks = s.step()
+        assert kind == STEP_PREFILL
+        seen.append((ids.tolist(), s.starts.tolist(), lens.tolist()))
+    # 128 + 128 + 44 tokens of sequence 0; the short one joins the last chunk's step with the budget that is left
+    assert seen == [([0], [0], [128]), ([0], [128], [128]), ([0, 1], [256, 0], [44, 40])]
+    assert s.extra_prefill_chunks == 2 and s.num_running == 2
+    kind, ids, slots, lens, _ = s.step()
+    assert kind == STEP_DECODE and ids.tolist() == [0, 1] and lens.tolist() == [301, 41]
+    # with chunking off the long prompt is one oversized step, as before
+    s2 = Scheduler(num_blocks=16, block_size=64, max_num_seqs=4, max_batched_tokens=128, chunked_prefill=False)
+    s2.add(0, 300, 5)
+    kind, ids, slots, lens, _ = s2.step()
+    assert kind == STEP_PREFILL and lens.tolist() == [300] and s2.starts.tolist() == [0]
+
+
+def test_scheduler_prefix_cache_hits_eviction_and_generated_blocks():
+    s = Scheduler(num_blocks=8, block_size=64, max_num_seqs=4, max_batched_tokens=4096)          # 7 usable blocks
+    sys_prompt = list(range(500, 500 + 128))
+    a = sys_prompt + [7] * 30
+    s.add(0, len(a), 50, tokens=a)
+    kind, ids, slots, lens, _ = s.step()
+    assert kind == STEP_PREFILL and s.starts.tolist() == [0] and lens.tolist() == [158]
+    for _ in range(41):                                    # decode steps: 199 tokens have KV afterwards
+        s.step()
+    blocks_a = s.blocks(0)
+    gen = [9] * 40
+    s.finish(0, tokens=a + gen)                            # 198 tokens: three full blocks stay findable, nothing is "free" yet
+    assert s.num_free_blocks == 7
+    # same system prompt, different tail: the two shared blocks are reused, 20 + the tail is computed
+    b = sys_prompt + [8] * 20
+    s.add(1, len(b), 10, tokens=b)
+    kind, ids, slots, lens, _ = s.step()
+    assert s.starts.tolist() == [128] and lens.tolist() == [20] and s.blocks(1)[:2].tolist() == blocks_a[:2].tolist()
+    # the next turn of the first conversation: prompt + generated tokens + new user text; generated blocks hit too
+    c = a + gen + [5] * 10
+    s.add(2, len(c), 10, tokens=c)
+    kind, ids, slots, lens, _ = s.step()
+    assert s.starts.tolist() == [192] and lens.tolist() == [len(c) - 192] and s.blocks(2)[:3].tolist() == blocks_a[:3].tolist()
+    assert s.prefix_cache_hit_tokens == 128 + 192
+    s.finish(1)
+    s.finish(2)
+    # an identical prompt never hits on its last token: one token at least is computed
+    d = sys_prompt
+    s.add(3, len(d), 4, tokens=d)
+    kind, ids, slots, lens, _ = s.step()
+    assert s.starts.tolist() == [64] and lens.tolist() == [64]
+    s.finish(3)
+    # pressure: unused cached blocks are handed out again (oldest first) and stop being findable
+    big = list(range(3000, 3000 + 64 * 6))
+    s.add(4, len(big), 10, tokens=big)
+    kind, ids, slots, lens, _ = s.step()
+    assert kind == STEP_PREFILL and s.starts.tolist() == [0]
+    s.finish(4)
+    s.add(5, len(a), 10, tokens=a)
+    s.step()
+    assert s.starts.tolist() == [0]                        # the system prompt's blocks were recycled
+
+
+def test_engine_chunked_prefill_and_prefix_cache_match_the_oracle(model):
+    g = torch.Generator().manual_seed(7)
+    long_p = torch.randint(10, 2048, (150,), generator=g).tolist()
+    short_p = torch.randint(10, 2048, (20,), generator=g).tolist()
+    eng = InferenceEngine(model, max_num_seqs=4, max_model_len=256, num_blocks=24, sync_interval=4, max_num_batched_tokens=64)
+    outs = eng.generate([long_p, short_p], SamplingParams(temperature=0.0, max_tokens=8))
+    assert eng.stats["prefill_chunks"] == 2                # 64 + 64 + 22
+    assert outs[0].token_ids == greedy_oracle(model, long_p, 8) and outs[1].token_ids == greedy_oracle(model, short_p, 8)
+    # second call inside the same wake period: a follow-up turn reuses the first conversation's blocks (prompt AND response)
+    turn2 = long_p + outs[0].token_ids + [33, 34, 35]
+    other = long_p[:128] + [77] * 9
+    before = eng.stats["prefill_tokens"]
+    outs2 = eng.generate([turn2, other], SamplingParams(temperature=0.0, max_tokens=6))
+    assert eng.stats["prefix_cache_hit_tokens"] == 128 + 128          # two full blocks each (150 + 7 fed tokens < 3 blocks)
+    assert eng.stats["prefill_tokens"] - before == (len(turn2) - 128) + (len(other) - 128)
+    assert outs2[0].token_ids == greedy_oracle(model, turn2, 6) and outs2[1].token_ids == greedy_oracle(model, other, 6)
+    # with both features off the same requests give the same tokens in single oversized steps
+    eng0 = InferenceEngine(model, max_num_seqs=4, max_model_len=256, num_blocks=24, sync_interval=4, max_num_batched_tokens=64,
+                           enable_chunked_prefill=False, enable_prefix_caching=False)
+    outs0 = eng0.generate([long_p, short_p], SamplingParams(temperature=0.0, max_tokens=8))
+    assert [o.token_ids for o in outs0] == [o.token_ids for o in outs] and eng0.stats["prefill_chunks"] == 0

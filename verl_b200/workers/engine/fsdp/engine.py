@@ -165,10 +165,6 @@ class FSDPEngine(BaseEngine):
             self.sp_size, self.sp_mode = cp, "context"
         # zig-zag placement of the context-parallel slices balances the causal attention work between the ranks
         self._cp_zigzag = self.sp_mode == "context" and bool(cfg_get(self.engine_config, "context_parallel_zigzag", False))
-        if self._cp_zigzag and self.device.type == "cuda":
-            # on two B200s the zig-zag placement gave the same log-probs as the contiguous placement but gradients that did not
-            # match it (the gloo runs do match); until that is understood the placement is refused on CUDA rather than trusted
-            raise NotImplementedError("context_parallel_zigzag is validated on CPU ranks only; use the contiguous placement on CUDA")
         fsdp_size = int(cfg_get(self.engine_config, "fsdp_size", -1))
         self.fsdp_size = self.world if fsdp_size in (-1, 0) or fsdp_size >= self.world else fsdp_size
         self.forward_only = bool(cfg_get(self.engine_config, "forward_only", False)) or optimizer_config is None

@@ -316,7 +316,9 @@ class ActorRolloutRefWorker(Worker):
             max_num_batched_tokens=int(cfg_get(ro, "max_num_batched_tokens", 8192)),
             gpu_memory_utilization=float(cfg_get(ro, "gpu_memory_utilization", 0.5)), enforce_eager=bool(cfg_get(ro, "enforce_eager", False)),
             sync_interval=int(cfg_get(ro, "sync_interval", 16)), enable_prefix_sharing=bool(cfg_get(ro, "enable_prefix_caching", True)),
-            num_blocks=cfg_get(ro, "num_blocks", None), tp_group=tp_group, tp_ctx=tp_ctx, quantization=cfg_get(ro, "quantization", None))
+            num_blocks=cfg_get(ro, "num_blocks", None), tp_group=tp_group, tp_ctx=tp_ctx, quantization=cfg_get(ro, "quantization", None),
+            enable_chunked_prefill=bool(cfg_get(ro, "enable_chunked_prefill", True)),
+            enable_prefix_caching=bool(cfg_get(ro, "enable_prefix_caching", True)))
 
     def _build_rollout_tp(self, full_model, ro):
         """Rollout replicas of ``tp`` adjacent ranks: every rank keeps a tensor-parallel slice of the decoder layers cut from

@@ -87,13 +87,19 @@ class InferenceEngine:
     def __init__(self, model: DecoderLM, max_num_seqs: int = 256, max_model_len: int = 2048, num_blocks: Optional[int] = None,
                  max_num_batched_tokens: int = 8192, gpu_memory_utilization: float = 0.5, enforce_eager: bool = False,
                  sync_interval: int = 16, enable_prefix_sharing: bool = True, decode_splits: int = 0, tp_group=None, tp_ctx=None,
-                 quantization: Optional[str] = None):
+                 quantization: Optional[str] = None, enable_chunked_prefill: bool = True, enable_prefix_caching: bool = True):
         """``model`` may be a vision-language model (``verl_b200.models.vision.VisionLanguageModel``): its decoder serves the
         tokens, its tower embeds the images of multimodal requests at prefill.
         ``tp_group`` / ``tp_ctx``: tensor-parallel replica. ``model`` is then this rank's slice (``build_rollout_shard``); every
         rank of the group runs the same requests in lockstep (same scheduler decisions, same sampled tokens) and the
         row-parallel projections end in an all-reduce — fused into the GEMM epilogue over NVLink peer memory when
-        ``tp_ctx`` (a ``TPContext``) is given, NCCL otherwise."""
+        ``tp_ctx`` (a ``TPContext``) is given, NCCL otherwise.
+        ``enable_chunked_prefill``: prompts longer than ``max_num_batched_tokens`` are computed in chunks of that size, each
+        attending to the chunks already in the paged cache, so no step exceeds the token budget. ``enable_prefix_caching``:
+        full KV blocks stay findable by a hash of their tokens and later requests that begin with the same tokens (the next
+        turn of a conversation, a shared system prompt) compute only the rest. ``enable_prefix_sharing`` is the cheaper
+        special case for the n samples of one prompt submitted together (reference knobs: ``enable_chunked_prefill`` /
+        ``enable_prefix_caching`` / ``max_num_batched_tokens`` of verl/trainer/config/rollout/rollout.yaml)."""
         self.visual = self.vision_config = None
         if hasattr(model, "visual") and hasattr(model, "language_model"):
             self.visual, self.vision_config, model = model.visual, model.vcfg, model.language_model
@@ -117,6 +123,7 @@ class InferenceEngine:
         self.enforce_eager = enforce_eager or self.device.type != "cuda"
         self.sync_interval = max(1, sync_interval)
         self.enable_prefix_sharing = enable_prefix_sharing
+        self.enable_chunked_prefill, self.enable_prefix_caching = bool(enable_chunked_prefill), bool(enable_prefix_caching)
         self.native = self.device.type == "cuda" and self.dtype == torch.bfloat16 and _ext.available()
         self._num_blocks_cfg = num_blocks
         self.cache: Optional[torch.Tensor] = None
@@ -125,7 +132,7 @@ class InferenceEngine:
         self.decode_splits = decode_splits
         self._cpu_gen = torch.Generator(device="cpu")
         self.stats = {"prefill_tokens": 0, "decode_steps": 0, "preemptions": 0, "forked": 0, "t_prefill": 0.0, "t_capture": 0.0,
-                      "t_decode": 0.0, "t_flush": 0.0, "t_wake": 0.0}
+                      "t_decode": 0.0, "t_flush": 0.0, "t_wake": 0.0, "prefix_cache_hit_tokens": 0, "prefill_chunks": 0}
         self.profile = False   # when set, phases are bracketed by device synchronisations and timed
         # router replay (R3): record the experts every fed token was routed to, per layer, and return them with the tokens
         # (reference: vLLM ``enable_return_routed_experts``, verl/workers/rollout/vllm_rollout/vllm_async_server.py:440-454,745-747)
@@ -231,7 +238,9 @@ class InferenceEngine:
             self.decode_splits = max(1, min(8, (296 + S * c.num_key_value_heads - 1) // (S * c.num_key_value_heads)))
         self.workspace = torch.empty(S * c.num_attention_heads * self.decode_splits * 130, dtype=torch.float32, device=dev) \
             if self.decode_splits > 1 else None
-        self.sched = Scheduler(nb, BLOCK_SIZE, S, self.max_num_batched_tokens)
+        self.sched = Scheduler(nb, BLOCK_SIZE, S, self.max_num_batched_tokens, chunked_prefill=self.enable_chunked_prefill,
+                               prefix_caching=self.enable_prefix_caching)
+        self._sched_counted = [0, 0]
         self._graph = None
 
     def sleep(self):
@@ -357,20 +366,28 @@ class InferenceEngine:
             self._bt_events[i] = ev
 
     def _prefill(self, seqs: list, sp: SamplingParams):
-        """``seqs``: list of (request, slot) to compute from scratch (prompt + anything generated before a preemption)."""
+        """``seqs``: list of (request, slot, start, n): compute tokens ``[start, start + n)`` of prompt + anything generated
+        before a preemption; the tokens before ``start`` are in the paged cache already (prefix-cache hits or earlier chunks of
+        a long prompt). Returns (logits of the sequences whose prompt is complete after this step, their indices in ``seqs``)."""
         c = self.cfg
-        toks, pos, slots, lens = [], [], [], []
-        for req, slot in seqs:
+        toks, pos, slots, lens, starts, pre_blk, pre_off, final = [], [], [], [], [], [], [], []
+        for i, (req, slot, start, n) in enumerate(seqs):
             ids = req["prompt"] + req["out"]
-            L = len(ids)
             blocks = self.sched.blocks(req["id"])
             self.block_table_host[slot, : len(blocks)] = blocks
             self.block_table_host[slot, len(blocks):] = 0
-            p = np.arange(L)
-            toks.append(np.asarray(ids, dtype=np.int64))
+            p = np.arange(start, start + n)
+            toks.append(np.asarray(ids[start:start + n], dtype=np.int64))
             pos.append(p.astype(np.int32))
             slots.append(blocks[p // BLOCK_SIZE].astype(np.int64) * BLOCK_SIZE + p % BLOCK_SIZE)
-            lens.append(L)
+            lens.append(n)
+            starts.append(start)
+            if start:
+                pp = np.arange(start)
+                pre_blk.append(blocks[pp // BLOCK_SIZE].astype(np.int64))
+                pre_off.append((pp % BLOCK_SIZE).astype(np.int64))
+            if start + n == len(ids):
+                final.append(i)
         dev = self.device
         tokens = torch.from_numpy(np.concatenate(toks)).to(dev)
         positions = torch.from_numpy(np.concatenate(pos)).to(dev)
@@ -380,25 +397,52 @@ class InferenceEngine:
         cu = cu_cpu.to(dev)
         max_len = max(lens)
 
-        def attn(li, qkv):
-            return ops.attention_varlen(qkv, cu, c.num_attention_heads, c.num_key_value_heads, c.head_dim, max_len, cu_cpu)
+        if not any(starts):
+            def attn(li, qkv):
+                return ops.attention_varlen(qkv, cu, c.num_attention_heads, c.num_key_value_heads, c.head_dim, max_len, cu_cpu)
+        else:
+            # some sequences continue from cached tokens: attention runs on an expanded layout in which every such sequence is
+            # preceded by its cached K/V rows (gathered from the paged cache, queries left at zero); the kernels skip the query
+            # tiles that lie entirely inside those rows
+            exp_lens = [st + n for st, n in zip(starts, lens)]
+            cu_exp_cpu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+            cu_exp_cpu[1:] = torch.cumsum(torch.tensor(exp_lens), 0)
+            base = cu_exp_cpu[:-1].tolist()
+            q_pos = torch.from_numpy(np.concatenate([np.arange(b + st, b + st + n) for b, st, n in zip(base, starts, lens)])).to(dev)
+            pre_pos = torch.from_numpy(np.concatenate([np.arange(b, b + st) for b, st in zip(base, starts) if st])).to(dev)
+            blk_i, off_i = torch.from_numpy(np.concatenate(pre_blk)).to(dev), torch.from_numpy(np.concatenate(pre_off)).to(dev)
+            cu_exp, E, max_exp, q_starts = cu_exp_cpu.to(dev), int(cu_exp_cpu[-1]), max(exp_lens), tuple(starts)
+
+            def attn(li, qkv):
+                kv = self.cache[li][blk_i, :, :, off_i]                          # [rows, 2, Hkv, D]: K heads then V heads of each row
+                qkv_exp = qkv.new_zeros(E, qkv.shape[1])
+                qkv_exp.index_copy_(0, q_pos, qkv)
+                qkv_exp[pre_pos, c.q_size:] = kv.reshape(kv.shape[0], -1)
+                o = ops.attention_varlen(qkv_exp, cu_exp, c.num_attention_heads, c.num_key_value_heads, c.head_dim, max_exp, cu_exp_cpu,
+                                         q_starts=q_starts)
+                return o.index_select(0, q_pos)
 
         rope = visual = None
-        if self.visual is not None and any(req.get("mm") for req, _ in seqs):
-            rope, visual = self._multi_modal_prefill([req for req, _ in seqs], tokens)
+        if self.visual is not None and any(req.get("mm") for req, *_ in seqs):
+            rope, visual = self._multi_modal_prefill([req for req, *_ in seqs], tokens)
             positions = torch.arange(tokens.shape[0], dtype=torch.int32, device=dev)
         h = self._layer_stack(tokens, positions, slot_map, attn, rope, visual)
-        last = (cu[1:] - 1).long()
-        logits = ops.linear(h.index_select(0, last), self.model.output_weight)
         self.stats["prefill_tokens"] += int(sum(lens))
         if self._last_routed is not None:
-            # a (re)prefill feeds every token the request holds so far: its routing record starts over from these rows
+            # a (re)prefill from token 0 starts the request's routing record over; later chunks extend it
             rt = self._last_routed.cpu().numpy()
             off = 0
-            for (req, _), L in zip(seqs, lens):
-                req["routed"] = [rt[off:off + L]]
+            for (req, _, start, _n), L in zip(seqs, lens):
+                if start == 0:
+                    req["routed"] = [rt[off:off + L]]
+                else:
+                    req.setdefault("routed", []).append(rt[off:off + L])
                 off += L
-        return logits
+        if not final:
+            return None, final
+        last = (cu[1:] - 1).long().index_select(0, torch.tensor(final, device=dev))
+        logits = ops.linear(h.index_select(0, last), self.model.output_weight)
+        return logits, final
 
     def _multi_modal_prefill(self, reqs: list, tokens: torch.Tensor):
         """Vision-language prompts: per-token rotary tables from the 3-stream positions of every sequence, and the vision
@@ -572,12 +616,19 @@ class InferenceEngine:
                 if r["done"]:
                     freed.append(slot)
                     r["num_preempted"] = self.sched.num_preempted(int(sid))
-                    self.sched.finish(int(sid))
+                    self.sched.finish(int(sid), self._cacheable_tokens(r))
                     self._report(r)
         pending.clear()
         if freed:
             self.active.index_fill_(0, torch.tensor(freed, dtype=torch.int64, device=self.device), 0)
         self.stats["t_flush"] += time.perf_counter() - t_f
+
+    def _cacheable_tokens(self, r: dict):
+        """Ids of the tokens whose KV a finished request leaves in the cache (everything but the last sampled token, which was
+        never fed back), or None when its blocks must not be found by other requests."""
+        if not self.enable_prefix_caching or r.get("mm"):
+            return None
+        return (r["prompt"] + r["out"])[:-1]
 
     @staticmethod
     def _prompt_key(p, mm):
@@ -642,7 +693,7 @@ class InferenceEngine:
 
                     reqs[i]["mm"] = mm
                     reqs[i]["rope_delta"] = get_rope_index(torch.as_tensor(p), mm.get("image_grid_thw"), self.vision_config)[1]
-                self.sched.add(i, len(p), max_new, key)
+                self.sched.add(i, len(p), max_new, key, tokens=p, no_chunk=bool(mm), no_cache=bool(mm))
 
         add_requests([(p, None, multi_modal[j] if multi_modal is not None else None) for j, p in enumerate(prompts)])
         owner_logits: dict[int, torch.Tensor] = {}
@@ -678,23 +729,27 @@ class InferenceEngine:
                 continue
             if kind == STEP_PREFILL:
                 self._flush(pending, reqs, sp, eos_ids)
-                ids, slots, forks = ids.copy(), slots.copy(), forks.copy()
-                fresh = [(reqs[int(s)], int(sl)) for s, sl, f in zip(ids, slots, forks) if f < 0 and not reqs[int(s)]["done"]]
+                ids, slots, forks, lens, starts = ids.copy(), slots.copy(), forks.copy(), lens.copy(), self.sched.starts.copy()
+                fresh = [(reqs[int(s)], int(sl), int(st), int(n)) for s, sl, f, st, n in zip(ids, slots, forks, starts, lens)
+                         if f < 0 and not reqs[int(s)]["done"]]
                 forked = [(reqs[int(s)], int(sl), int(f)) for s, sl, f in zip(ids, slots, forks) if f >= 0]
                 for s in ids:  # a sequence that finished while waiting for re-admission
                     if reqs[int(s)]["done"]:
                         self.sched.finish(int(s))
                 t_pf = self._tick()
+                started = []
                 if fresh:
-                    logits = self._prefill(fresh, sp)
-                    for row, (r, sl) in enumerate(fresh):
+                    logits, fin = self._prefill(fresh, sp)
+                    started = [(fresh[i][0], fresh[i][1]) for i in fin]      # the others have more prompt chunks to go
+                    for row, (r, sl) in enumerate(started):
                         r["slot"] = sl
                         if counts.get(r["pkey"], 0) > 1 and not r["out"]:
                             owner_logits[r["id"]] = logits[row]
                             if "routed" in r:
-                                owner_routed[r["id"]] = r["routed"][0]
+                                owner_routed[r["id"]] = np.concatenate(r["routed"], 0)
                             owner_partial_block[r["id"]] = int(self.block_table_host[sl, len(r["prompt"]) // BLOCK_SIZE])
-                    self._start_sequences(fresh, logits, sp)
+                    if started:
+                        self._start_sequences(started, logits, sp)
                 if forked:
                     src_b, dst_b, rows = [], [], []
                     for r, slot, owner in forked:
@@ -714,17 +769,17 @@ class InferenceEngine:
                         self.cache[:, di] = self.cache[:, si]
                     self._start_sequences([(r, s) for r, s, _ in forked], torch.stack(rows), sp)
                     self.stats["forked"] += len(forked)
-                for r, sl in fresh:
+                for r, sl, *_ in fresh:
                     r["slot"] = sl
                 for r, sl, _ in forked:
                     r["slot"] = sl
                 self._push_block_table()
                 # sequences whose single allowed token came from the prefill are complete
-                done_now = [(r, sl) for r, sl in fresh + [(r, s) for r, s, _ in forked]
+                done_now = [(r, sl) for r, sl in started + [(r, s) for r, s, _ in forked]
                             if len(r["out"]) >= r["max_new"] or ((not sp.ignore_eos) and r["out"][-1] in eos_ids)]
                 for r, sl in done_now:
                     r["done"], r["stop"] = True, ("length" if len(r["out"]) >= r["max_new"] else "stop")
-                    self.sched.finish(r["id"])
+                    self.sched.finish(r["id"], self._cacheable_tokens(r))
                     self.active[sl] = 0
                     self._report(r)
                 self.stats["t_prefill"] += self._tick() - t_pf
@@ -764,6 +819,11 @@ class InferenceEngine:
                 self._flush(pending, reqs, sp, eos_ids)
         if self.native:
             _ext.check_status("rollout generate")
+        if self.sched is not None:
+            hit, chunks = self.sched.prefix_cache_hit_tokens, self.sched.extra_prefill_chunks
+            self.stats["prefix_cache_hit_tokens"] += hit - self._sched_counted[0]
+            self.stats["prefill_chunks"] += chunks - self._sched_counted[1]
+            self._sched_counted = [hit, chunks]
         outs = []
         for i in range(len(prompts)):
             r = reqs[i]
