@@ -369,9 +369,79 @@ def bench_fused_gather(a):
            timeit(lambda: o.gemm_head_scatter(x, wq, None, optr, Cl, 0, D, hr, hs), a.iters), flops=2.0 * Tl * C * H)
 
 
+def bench_fused_emulated(a):
+    """The other multi-rank kernels on ONE GPU at training sizes, every "peer" being a buffer of this GPU: gradient
+    reduce-scatter (+ scale + squared norm), AdamW fused with the parameter all-gather, the peer-scatter GEMM epilogue with its
+    slot sum (GEMM -> reduce-scatter), the signalled GEMM -> all-reduce pair at decode size, and the reshard + fp8 requantise
+    kernel of the weight sync. The memory-bound ones are reported against the measured copy bandwidth with their algorithmic
+    bytes; transport over NVLink is measured by ``verl_b200.parallel.comm_bench`` on real multi-GPU runs."""
+    from verl_b200.ops import _ext
+
+    o = _ext.ops()
+    W = a.world
+    tab = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64)      # noqa: E731
+    # ---- gradient reduce-scatter: every rank reads its 1/W slice of all W gradient buffers (fp32) and writes it once
+    n = 1 << 28                                                                         # 268M gradients = 1 GiB per "rank"
+    grads = [torch.randn(n, device="cuda") for _ in range(W)]
+    shard = torch.empty(n // W, device="cuda")
+    tot = torch.zeros(1, device="cuda")
+    ms = timeit(lambda: o.symm_reduce_scatter(tab(grads), W, 0, shard, tot, 1.0 / W), a.iters)
+    report(f"symm_reduce_scatter {W} x {n // W} fp32 (reads {W} slices, writes one)", ms, bytes_=(W + 1) * (n // W) * 4.0)
+    del grads
+    # ---- AdamW + all-gather: p32/m/v read+write, g read, bf16 result written to all W parameter buffers
+    sh = n // W
+    p32, m, v, g = (torch.randn(sh, device="cuda") * 0.02 for _ in range(4))
+    v = v.abs()
+    params = [torch.empty(n, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    scal = torch.tensor([1.0, 0.0], device="cuda")
+    ms = timeit(lambda: o.symm_adamw_allgather(p32, m, v, g, tab(params), W, 0, 1e-6, 0.9, 0.999, 1e-8, 0.01, 2, scal), a.iters)
+    report(f"symm_adamw_allgather shard {sh} (3 fp32 r+w, 1 fp32 r, {W} bf16 w)", ms, bytes_=sh * (7 * 4.0 + W * 2.0))
+    del p32, m, v, g, params, shard
+    # ---- GEMM -> reduce-scatter: down projection of Qwen2.5-7B under TP = W (K split), rows scattered to their owners
+    T, N, K = a.m, a.n, a.k // W
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    w = (0.02 * torch.randn(N, K, device="cuda")).bfloat16()
+    rows = T // W
+    slot = rows * N
+    slots = [torch.empty(W * slot, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    ms = timeit(lambda: o.gemm_peer_scatter(x, w, tab(slots), 0, rows, slot), a.iters)
+    report(f"GEMM with peer-scatter epilogue (reduce-scatter form) M={T} N={N} K={K}", ms, flops=2.0 * T * N * K)
+    out = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: o.slots_reduce(slots[0], W, slot, rows, N, None, out), a.iters)
+    report(f"slots_reduce {W} x [{rows}, {N}] bf16", ms, bytes_=(W + 1) * rows * N * 2.0)
+    del slots
+    # ---- decode-size GEMM -> all-reduce, signalled form, both emulated ranks per iteration
+    Td = 256
+    xd = torch.randn(Td, K, device="cuda").bfloat16()
+    half = 8 * Td * N
+    sl2 = [torch.zeros(2 * half, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    sig = [torch.zeros(64, device="cuda", dtype=torch.int32) for _ in range(W)]
+    outs = [torch.empty(Td, N, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+
+    def ar():
+        for r in range(W):
+            o.gemm_allreduce_sig(xd, w, tab(sl2), tab(sig), r, half, sl2[r], sig[r], None, outs[r], 0, 0, 8, 1)
+        for r in range(W):
+            o.gemm_allreduce_sig(xd, w, tab(sl2), tab(sig), r, half, sl2[r], sig[r], None, outs[r], 0, 0, 8, 2)
+
+    ms = timeit(ar, a.iters)
+    report(f"signalled GEMM -> all-reduce, {W} emulated ranks back to back (2 x {W} launches) M={Td} N={N} K={K}", ms,
+           bytes_=W * (N * K * 2.0 + Td * K * 2.0))
+    # ---- weight sync: gather rows from W row shards + 128 x 128 block-fp8 requantise (gate_up of Qwen2.5-7B)
+    Nw, Kw = 37888, 3584
+    shards = [(0.02 * torch.randn(Nw // W, Kw, device="cuda")).bfloat16() for _ in range(W)]
+    like = shards[0]
+    ms = timeit(lambda: o.reshard_quant(tab(shards), Nw // W, Kw, 0, Nw, Kw, True, False, like), a.iters)
+    report(f"reshard_quant {W} shards -> [{Nw}, {Kw}] e4m3 + block scales", ms, bytes_=Nw * Kw * 3.0)
+    ms = timeit(lambda: o.reshard_quant(tab(shards), Nw // W, Kw, 0, Nw, Kw, False, True, like), a.iters)
+    report(f"reshard (bf16 copy) {W} shards -> [{Nw}, {Kw}]", ms, bytes_=Nw * Kw * 4.0)
+    torch.cuda.synchronize()
+    _ext.check_status("fused_emulated")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_layer", "layer_step", "gemm_fp8", "attn_fwd", "attn_bwd", "lmhead", "decode_attn", "elementwise", "fused_gather", "all"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_layer", "layer_step", "gemm_fp8", "attn_fwd", "attn_bwd", "lmhead", "decode_attn", "elementwise", "fused_gather", "fused_emulated", "all"])
     ap.add_argument("--world", type=int, default=2)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -406,6 +476,8 @@ def main():
         bench_gemm_fp8(a)
     if a.kernel == "fused_gather":
         bench_fused_gather(a)
+    if a.kernel == "fused_emulated":
+        bench_fused_emulated(a)
     if a.kernel in ("attn_fwd", "all"):
         bench_attn(a, False)
     if a.kernel in ("attn_bwd", "all"):
