@@ -245,6 +245,7 @@ def run_native(args):
             "warmup_step_s": [round(x, 3) for x in warm_times],
             "tokens_per_step": tokens / steps_run,
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1),
+            "native_fallbacks": dict(__import__("verl_b200.ops.functional", fromlist=["fallback_counts"]).fallback_counts),
             # allocator pressure on rank 0: a retry means cudaMalloc failed once and cached blocks were freed (a device sync)
             "allocator": {"reserved_gb": round(torch.cuda.max_memory_reserved() / 1e9, 1),
                           "alloc_retries": int(torch.cuda.memory_stats().get("num_alloc_retries", 0)),

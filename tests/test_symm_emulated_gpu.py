@@ -76,12 +76,13 @@ def test_adamw_allgather_writes_every_ranks_parameter_copy(o):
     for p in params:
         assert (p[:n].float() - r16.float()).abs().max().item() < 2e-4 and torch.all(p[n:] == 3.0)
     assert torch.equal(params[0], params[1])
-    # skip flag set: nothing moves
+    # skip flag set (a non-finite gradient norm): state stays as it is, the parameter copies are rewritten with the same values
     before = [p.clone() for p in params]
-    lp = p32[:sh].clone()
-    o.symm_adamw_allgather(lp, m0[:sh].clone(), v0[:sh].clone(), g[:sh].contiguous(), _table(params), W, 0, 1e-3, 0.9, 0.95, 1e-8, 0.01, 4,
+    lp, lm, lv = rp[:sh].clone(), rm[:sh].clone(), rv[:sh].clone()
+    o.symm_adamw_allgather(lp, lm, lv, g[:sh].contiguous(), _table(params), W, 0, 1e-3, 0.9, 0.95, 1e-8, 0.01, 4,
                            torch.tensor([1.0, 1.0], device="cuda"))
-    assert torch.equal(lp, p32[:sh]) and all(torch.equal(a, b) for a, b in zip(params, before))
+    assert torch.equal(lp, rp[:sh]) and torch.equal(lm, rm[:sh]) and torch.equal(lv, rv[:sh])
+    assert all(torch.equal(a, b) for a, b in zip(params, before))
     _status_clean(o)
 
 

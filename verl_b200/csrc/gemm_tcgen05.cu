@@ -982,7 +982,7 @@ struct PeerSlots {
   const bf16* p[MAX_TP];
 };
 
-__global__ void slots_reduce_sig_kernel(const PeerSlots peers, const int* __restrict__ sig, int rank, int world, int split_k, long slot_elems,
+__global__ void slots_reduce_sig_kernel(const __grid_constant__ PeerSlots peers, const int* __restrict__ sig, int rank, int world, int split_k, long slot_elems,
                                         long half_elems, long rows, int cols, const bf16* __restrict__ residual, bf16* __restrict__ out,
                                         int ld_out, int* err_word) {
   __shared__ int ok_s;

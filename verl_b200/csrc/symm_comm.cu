@@ -24,7 +24,7 @@ struct PeerTable {
 // ---------------------------------------------------------------- barrier
 // flags: per rank an int32[MAX_RANKS] pad inside symmetric memory. Rank r writes `epoch` into peer p's flags[r] and then
 // waits until its own flags[p] >= epoch for every p. One block, `world` threads.
-__global__ void symm_barrier_kernel(PeerTable pads, int rank, int world, int epoch, int* err_word) {
+__global__ void symm_barrier_kernel(const __grid_constant__ PeerTable pads, int rank, int world, int epoch, int* err_word) {
   const int p = threadIdx.x;
   if (p < world) {
     int* remote = reinterpret_cast<int*>(pads.ptr[p]) + rank;
@@ -54,7 +54,7 @@ __global__ void symm_barrier_kernel(PeerTable pads, int rank, int world, int epo
 // carries no host-side state and can be replayed from a CUDA graph: every replay advances the epoch by one on every rank.
 constexpr int AUTO_COUNTER = 256;   // int32 index inside the pad
 constexpr int AUTO_FLAGS = 512;
-__global__ void symm_barrier_auto_kernel(PeerTable pads, int rank, int world, int* err_word) {
+__global__ void symm_barrier_auto_kernel(const __grid_constant__ PeerTable pads, int rank, int world, int* err_word) {
   __shared__ int epoch_s;
   int* my_pad = reinterpret_cast<int*>(pads.ptr[rank]);
   if (threadIdx.x == 0) {
@@ -90,7 +90,7 @@ __global__ void symm_barrier_auto_kernel(PeerTable pads, int rank, int world, in
 
 // ---------------------------------------------------------------- reduce-scatter (+ scale, + sum of squares)
 // out[i] = scale * sum_r grads_r[shard_off + i] for i in [0, n); sumsq += sum out[i]^2. n % 4 == 0.
-__global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(PeerTable grads, int world, long shard_off, long n, float scale,
+__global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(const __grid_constant__ PeerTable grads, int world, long shard_off, long n, float scale,
                                                                   float* __restrict__ out, float* __restrict__ sumsq) {
   const long n4 = n >> 2;
   float acc = 0.f;
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(PeerTable grad
 // Updates the local fp32 shard and writes the bf16 result into every rank's parameter buffer at shard_off.
 // scalars[0] = gradient scale (clip coefficient), scalars[1] = skip flag. n % 8 == 0.
 __global__ void __launch_bounds__(256) symm_adamw_allgather_kernel(float* __restrict__ p32, float* __restrict__ m, float* __restrict__ v,
-                                                                   const float* __restrict__ g, PeerTable params, int world,
+                                                                   const float* __restrict__ g, const __grid_constant__ PeerTable params, int world,
                                                                    long shard_off, long n, float lr, float b1, float b2, float eps,
                                                                    float wd, float bc1, float bc2, const float* __restrict__ scalars) {
   const float gscale = scalars[0];

@@ -32,6 +32,21 @@ def use_native(t: torch.Tensor) -> bool:
     return t.is_cuda and t.dtype == torch.bfloat16 and _ext.available()
 
 
+# bf16 CUDA operands that the native kernels could not take (misaligned base / row stride): counted per reason and reported
+# once each, so that a layout bug upstream shows up as a number instead of as a quietly slower step
+fallback_counts: dict[str, int] = {}
+
+
+def _note_fallback(reason: str, detail: str) -> None:
+    n = fallback_counts.get(reason, 0)
+    fallback_counts[reason] = n + 1
+    if n == 0:
+        import warnings
+
+        warnings.warn(f"verl_b200.ops: {reason} runs on the PyTorch reference path ({detail}); further cases are only counted in "
+                      "verl_b200.ops.functional.fallback_counts", RuntimeWarning, stacklevel=3)
+
+
 # ------------------------------------------------------------------------------------------------ GEMM / linear
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: Optional[torch.Tensor] = None,
          bias: Optional[torch.Tensor] = None, accumulate: bool = False, out_dtype: Optional[torch.dtype] = None,
@@ -45,6 +60,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if use_native(a) and _gemm_operand_ok(a) and _gemm_operand_ok(b):
         _ext.ops().gemm(a, b, out, bias, a_mn, b_mn, accumulate, bn)
         return out
+    if use_native(a):
+        _note_fallback("gemm with an operand the TMA descriptors cannot address",
+                       f"a {tuple(a.shape)} strides {a.stride()} ptr%16={a.data_ptr() % 16}, b {tuple(b.shape)} strides {b.stride()} ptr%16={b.data_ptr() % 16}")
     A = a.t() if a_mn else a
     B = b if b_mn else b.t()
     r = (A.float() @ B.float()) if a.dtype != torch.float64 else A @ B

@@ -48,6 +48,8 @@ class FSDPEngineConfig(BaseConfig):
     ulysses_sequence_parallel_size: int = 1
     context_parallel_size: int = 1
     context_parallel_zigzag: bool = False
+    dynamic_context_parallel: bool = False
+    max_seqlen_per_dp_cp_rank: Optional[int] = None
     model_dtype: Any = None
     dtype: str = 'bfloat16'
     forward_prefetch: bool = False

@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import math
 import os
+from contextlib import contextmanager
 from typing import Any, Callable, Optional
 
 import torch
@@ -165,6 +166,11 @@ class FSDPEngine(BaseEngine):
             self.sp_size, self.sp_mode = cp, "context"
         # zig-zag placement of the context-parallel slices balances the causal attention work between the ranks
         self._cp_zigzag = self.sp_mode == "context" and bool(cfg_get(self.engine_config, "context_parallel_zigzag", False))
+        # dynamic context parallelism: per micro-batch every sample gets the smallest aligned sub-group of the CP ranks that keeps
+        # its share under ``max_seqlen_per_dp_cp_rank`` (short samples run on one rank without any communication)
+        self._dynamic_cp = self.sp_mode == "context" and bool(cfg_get(self.engine_config, "dynamic_context_parallel", False))
+        if self._dynamic_cp:
+            assert self.sp_size & (self.sp_size - 1) == 0, "dynamic context parallelism needs a power-of-two context_parallel_size"
         fsdp_size = int(cfg_get(self.engine_config, "fsdp_size", -1))
         self.fsdp_size = self.world if fsdp_size in (-1, 0) or fsdp_size >= self.world else fsdp_size
         self.forward_only = bool(cfg_get(self.engine_config, "forward_only", False)) or optimizer_config is None
@@ -308,6 +314,19 @@ class FSDPEngine(BaseEngine):
                 g = dist.new_group(ranks)
                 if self.rank in ranks:
                     self.dp_group = g
+            self._dcp_groups = {}
+            if getattr(self, "_dynamic_cp", False):
+                # aligned sub-groups of every width below the full one: width k -> the group this rank belongs to
+                k = 2
+                while k < self.sp_size:
+                    for d in range(self.dp_size):
+                        for start in range(0, self.sp_size, k):
+                            ranks = [d * self.sp_size + start + i for i in range(k)]
+                            g = dist.new_group(ranks)
+                            if self.rank in ranks:
+                                self._dcp_groups[k] = g
+                    k *= 2
+                self._dcp_groups[self.sp_size] = self.sp_group
         else:
             self.dp_group = dist.group.WORLD
 
@@ -681,6 +700,8 @@ class FSDPEngine(BaseEngine):
 
     # ------------------------------------------------------------------ forward / backward
     def forward_backward_batch(self, data, loss_function: Optional[Callable], forward_only: bool = False) -> dict:
+        if getattr(self, "_dynamic_cp", False) and self.sp_size > 1:
+            return self._forward_backward_dynamic_cp(data, loss_function, forward_only)
         batch = data.batch
         meta = dict(getattr(data, "meta_info", {}) or {})
         dev = self.device
@@ -734,6 +755,105 @@ class FSDPEngine(BaseEngine):
             self.store.fold_autograd_grads()
         model_output = {k: restore_dynamic_batch(torch.cat(v, 0), mb_indices) for k, v in outputs.items()}
         return {"model_output": model_output, "loss": losses, "metrics": metrics}
+
+    @contextmanager
+    def _sub_sp(self, k: int, cp_rank: int):
+        """Run the enclosed forward with a context-parallel group of width ``k`` (1 = no sequence parallelism at all)."""
+        saved = (self.sp_size, self.sp_rank, self.sp_group, self.model.sp_group)
+        g = None if k == 1 else self._dcp_groups[k]
+        self.sp_size, self.sp_rank, self.sp_group, self.model.sp_group = k, cp_rank, g, g
+        try:
+            yield
+        finally:
+            self.sp_size, self.sp_rank, self.sp_group, self.model.sp_group = saved
+
+    def _forward_backward_dynamic_cp(self, data, loss_function: Optional[Callable], forward_only: bool) -> dict:
+        """``forward_backward_batch`` with dynamic context parallelism (reference: ``verl/utils/dynamic_cp_scheduler.py:112-286``
+        and its use in the Megatron engine). All ranks of the CP group hold the same batch; the scheduler packs its samples
+        into micro-batches in which each sample is owned by an aligned sub-group of 1, 2, 4, ... ranks. A rank runs only the
+        samples of its sub-group; the leaders' outputs are summed back over the CP group so that every rank returns the
+        whole batch, as with the static layout. A sub-group of width k sees each of its gradients k-fold (the output gather
+        scales by k) and its samples are seen by k of the ``cp`` ranks only, so the loss is scaled by cp / k: after the
+        data-parallel average every sample then counts once, exactly as in the static layout."""
+        from verl_b200.utils.dynamic_cp_scheduler import DynamicCPScheduler
+
+        batch = data.batch
+        meta = dict(getattr(data, "meta_info", {}) or {})
+        dev = self.device
+        tensors = {k: (_to_device(v, dev) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
+        n = tensors["input_ids"].shape[0]
+        seq_lens = tensors["attention_mask"].sum(-1)
+        lens = [max(1, int(x)) for x in seq_lens.tolist()]
+        cp = self.sp_size
+        cap = int(cfg_get(self.engine_config, "max_seqlen_per_dp_cp_rank", 0) or 0)
+        if cap <= 0:
+            cap = int(meta.get("max_token_len_per_gpu", 0) or 0) or -(-max(lens) // cp)
+        cap = max(cap, -(-max(lens) // cp))                  # the longest sample must fit the full group
+        plan = DynamicCPScheduler(cap, 1, cp).schedule(lens, self.sp_rank, cp_layout="zigzag" if self._cp_zigzag else "contiguous")
+        info: dict[str, Any] = {"dp_size": self.dp_size}
+        if not forward_only and loss_function is not None:
+            mask_key = "response_mask" if "response_mask" in tensors else None
+            ntok = tensors[mask_key].sum().to(torch.float32) if mask_key else seq_lens.sum().to(torch.float32)
+            cnt = torch.stack([ntok, torch.tensor(float(n), device=dev)])
+            dist.all_reduce(cnt, group=self.dp_group)
+            info["batch_num_tokens"], info["global_batch_size"] = cnt[0], cnt[1]
+            self._alloc_grads()
+        full: dict[str, torch.Tensor] = {}
+        metrics: dict[str, Metric] = {}
+        losses = []
+        self.model.train(not forward_only)
+        self.dcp_stats = {"micro_batches": len(plan), "group_sizes": [mb["local_cp_size"] for mb in plan if mb["sample_ids"]]}
+        for mbp in plan:
+            idxs = mbp["sample_ids"]
+            if not idxs:
+                continue
+            k = mbp["local_cp_size"]
+            it = torch.as_tensor(idxs, device=dev)
+            mb = {key: (v.index_select(0, it) if isinstance(v, torch.Tensor) and v.dim() >= 1 and v.shape[0] == n else v) for key, v in tensors.items()}
+            with (torch.no_grad() if forward_only else torch.enable_grad()), self._sub_sp(k, mbp["cp_rank"]):
+                mo = self._forward_micro_batch(mb, meta)
+                if loss_function is not None:
+                    mb_data = dict(mb)
+                    mb_data.update(info)
+                    loss, m = loss_function(model_output=mo, data=mb_data, dp_group=self.dp_group)
+                    if not forward_only:
+                        (loss * (cp / k)).backward()
+                    if mbp["group_leader"]:
+                        losses.append(float(loss.detach()))
+                        for key, v in m.items():
+                            if key in metrics:
+                                metrics[key].append(v)
+                            else:
+                                metrics[key] = v if isinstance(v, Metric) else Metric(AggregationType.MEAN, v)
+            if mbp["group_leader"]:
+                for key, v in mo.items():
+                    if key not in full:
+                        full[key] = torch.zeros(n, *v.shape[1:], dtype=v.dtype, device=v.device)
+                    full[key].index_copy_(0, it, v.detach())
+        if not forward_only and loss_function is not None:
+            self.store.fold_autograd_grads()
+        # every rank of the CP group returns the whole batch: exchange what the leaders hold (host side first: which outputs exist)
+        mine = {"keys": {key: (tuple(v.shape[1:]), str(v.dtype).split(".")[-1]) for key, v in full.items()}, "loss": losses,
+                "metrics": {key: (v.aggregation.value, list(v.values)) for key, v in metrics.items()}}
+        everyone = [None] * cp
+        dist.all_gather_object(everyone, mine, group=self._sp_host_group())
+        keys = {}
+        for e in everyone:
+            keys.update(e["keys"])
+        model_output = {}
+        for key in sorted(keys):
+            shape, dt = keys[key]
+            t = full.get(key)
+            if t is None:
+                t = torch.zeros(n, *shape, dtype=getattr(torch, dt), device=dev)
+            dist.all_reduce(t, group=self._dcp_groups[cp])
+            model_output[key] = t
+        losses = [x for e in everyone for x in e["loss"]]
+        merged: dict[str, Metric] = {}
+        for e in everyone:
+            for key, (agg, vals) in e["metrics"].items():
+                merged.setdefault(key, Metric(agg)).append(list(vals))
+        return {"model_output": model_output, "loss": losses, "metrics": merged}
 
     def _alloc_grads(self):
         s = self.store
