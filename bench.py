@@ -205,7 +205,8 @@ def run_native(args):
             print(f"[step {s}] " + " ".join(f"{k}={v:.3f}" for k, v in last.items() if k.startswith("timing_s/") or k in ("perf/throughput", "actor/grad_norm")), file=sys.stderr, flush=True)
         if limit > 0 and s + 1 < steps_planned:
             # safety net for a step that ran much longer than the warm-up steps suggested (one 8-byte all-reduce per step)
-            if elapsed() + per_step[-1].get("step", 0.0) * 1.03 > limit + 30.0:
+            # (the ranks must take the same decision: the projected finish time is agreed as the max over ranks)
+            if agree(time.time() - T_PROCESS_START + per_step[-1].get("step", 0.0) * 1.03, dist.ReduceOp.MAX) > limit + 30.0:
                 break
     ev1.record()
     barrier()
