@@ -24,7 +24,8 @@ dist.init_process_group("gloo")
 rank, world = dist.get_rank(), dist.get_world_size()
 cfg = PRESETS["tiny-qwen2"].replace(num_hidden_layers=3, tie_word_embeddings=os.environ["TIED"] == "1")
 eng = MegatronEngine(cfg, {"seed": 1, "tensor_model_parallel_size": int(os.environ["TP"]), "pipeline_model_parallel_size": int(os.environ["PP"]),
-                           "sequence_parallel": os.environ.get("SP", "0") == "1"},
+                           "sequence_parallel": os.environ.get("SP", "0") == "1", "context_parallel_size": int(os.environ.get("CP", "1")),
+                           "context_parallel_zigzag": os.environ.get("ZIGZAG", "0") == "1"},
                      {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, {})
 eng.initialize()
 exported = {k: v.clone() for k, v in eng.get_per_tensor_param()[0]}
@@ -38,8 +39,8 @@ grads = {}
 for n, p in eng.model.named_parameters():
     g = local_to_global_name(n, eng.model.layer_offset)
     mg = p.main_grad.clone()
-    if eng.dp_size > 1:
-        dist.all_reduce(mg, group=eng.dp_group); mg /= eng.dp_size
+    if eng.fsdp_size > 1:
+        dist.all_reduce(mg, group=eng.fsdp_group); mg /= eng.fsdp_size
     if eng.tp_size > 1 and tp_rule(g, cfg) is not None:
         parts = [torch.empty_like(mg) for _ in range(eng.tp_size)]
         dist.all_gather(parts, mg, group=eng.tp_group)
@@ -75,19 +76,23 @@ def test_shard_unshard_roundtrip():
     assert [list(stage_layer_range(7, 3, s)) for s in range(3)] == [[0, 1, 2], [3, 4], [5, 6]]
 
 
-@pytest.mark.parametrize("world,tp,pp,tied,sp", [(4, 2, 2, False, False), (4, 1, 2, True, False), (3, 1, 3, True, False), (2, 2, 1, True, False),
-                                                 (2, 2, 1, False, True), (4, 2, 2, True, True)])
-def test_parallel_ranks_match_single_rank(tmp_path, world, tp, pp, tied, sp):
+@pytest.mark.parametrize("world,tp,pp,tied,sp,cp,zigzag", [
+    (4, 2, 2, False, False, 1, False), (4, 1, 2, True, False, 1, False), (3, 1, 3, True, False, 1, False), (2, 2, 1, True, False, 1, False),
+    (2, 2, 1, False, True, 1, False), (4, 2, 2, True, True, 1, False),
+    # context parallelism: with TP, with PP (zig-zag), with sequence-parallel TP, and with DP on top
+    (4, 2, 1, True, False, 2, False), (4, 1, 2, False, False, 2, True), (4, 2, 1, False, True, 2, False), (4, 1, 1, True, False, 2, True)])
+def test_parallel_ranks_match_single_rank(tmp_path, world, tp, pp, tied, sp, cp, zigzag):
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     script = tmp_path / "w.py"
     script.write_text(WORKER)
     out = tmp_path / "out.pt"
-    env = dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1", TP=str(tp), PP=str(pp), TIED="1" if tied else "0", SP="1" if sp else "0")
+    env = dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1", TP=str(tp), PP=str(pp), TIED="1" if tied else "0", SP="1" if sp else "0", CP=str(cp),
+               ZIGZAG="1" if zigzag else "0")
     ckpt = tmp_path / "ckpt"
     if (world, tp, pp) in ((4, 2, 2), (4, 1, 2)) and not sp:
         env["CKPT"] = str(ckpt)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-                        "--master-port", str(29660 + world + tp + (10 if sp else 0)), str(script)], env=env, capture_output=True, text=True, timeout=900)
+                        "--master-port", str(29660 + world + tp + (10 if sp else 0) + 20 * (cp - 1) + (5 if zigzag else 0)), str(script)], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     cfg = PRESETS["tiny-qwen2"].replace(num_hidden_layers=3, tie_word_embeddings=tied)
     eng = FSDPEngine(cfg, {"seed": 1}, {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, {})
@@ -100,7 +105,7 @@ def test_parallel_ranks_match_single_rank(tmp_path, world, tp, pp, tied, sp):
     ref_grads = {n: p.main_grad.clone() for n, p in eng.model.named_parameters()}
     gn = eng.optimizer_step()
     res = [torch.load(str(out) + f".{r}") for r in range(world)]
-    dp = world // (tp * pp)
+    dp = world // (tp * pp * cp)
     per = len(data) // dp
     seen = set()
     for r in res:

@@ -39,7 +39,7 @@ class MegatronCheckpointManager(BaseCheckpointManager):
 
     def _files(self, root: str):
         e = self.engine
-        return tuple(shard_file(root, part, e.tp_rank, e.pp_rank, e.dp_rank) for part in ("model", "optimizer", "extra"))
+        return tuple(shard_file(root, part, e.tp_rank, e.pp_rank, e.fsdp_rank) for part in ("model", "optimizer", "extra"))
 
     def save_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, global_step: int = 0,
                         max_ckpt_to_keep: Optional[int] = None):
@@ -60,7 +60,7 @@ class MegatronCheckpointManager(BaseCheckpointManager):
             contents.append("model")
             torch.save({"format": "flat_mp_v1", "names": s.names, "shapes": [tuple(p.shape) for p in s.params], "offsets": s.offsets,
                         "total": s.total, "shard_size": s.shard_size, "dtype": str(s.flat.dtype),
-                        "tp_rank": e.tp_rank, "pp_rank": e.pp_rank, "dp_rank": e.dp_rank, "layer_offset": e.model.layer_offset,
+                        "tp_rank": e.tp_rank, "pp_rank": e.pp_rank, "dp_rank": e.fsdp_rank, "layer_offset": e.model.layer_offset,
                         "flat_shard": s.flat[s.shard_slice].detach().to("cpu", copy=True)}, model_f)
         if self.should_save_optimizer and not e.forward_only:
             contents.append("optimizer")
@@ -91,7 +91,8 @@ class MegatronCheckpointManager(BaseCheckpointManager):
 
             with open(os.path.join(local_path, "transformer_config.json"), "w") as f:
                 json.dump({"format": "flat_mp_v1", "tensor_model_parallel_size": e.tp_size, "pipeline_model_parallel_size": e.pp_size,
-                           "data_parallel_size": e.dp_size, "sequence_parallel": bool(getattr(e, "tp_sp", False)),
+                           # the weights / optimizer state of a (tp, pp) position are cut over the DP x CP ranks: that many shard files
+                           "data_parallel_size": e.fsdp_size, "context_parallel_size": int(getattr(e, "cp_size", 1)), "sequence_parallel": bool(getattr(e, "tp_sp", False)),
                            "stage_layers": [[r.start, r.stop] for r in (stage_layer_range(e.cfg.num_hidden_layers, e.pp_size, p) for p in range(e.pp_size))],
                            "model_config": dataclasses.asdict(e.cfg) if dataclasses.is_dataclass(e.cfg) else dict(vars(e.cfg))}, f, indent=2, default=str)
             with open(os.path.join(local_path, "ckpt_contents.json"), "w") as f:
@@ -112,8 +113,8 @@ class MegatronCheckpointManager(BaseCheckpointManager):
             with open(tc) as f:
                 meta = json.load(f)
             got = (meta["tensor_model_parallel_size"], meta["pipeline_model_parallel_size"], meta["data_parallel_size"])
-            if got != (e.tp_size, e.pp_size, e.dp_size):
-                raise ValueError(f"checkpoint was written with (tp, pp, dp) = {got}, this run uses {(e.tp_size, e.pp_size, e.dp_size)}; "
+            if got != (e.tp_size, e.pp_size, e.fsdp_size):
+                raise ValueError(f"checkpoint was written with (tp, pp, dp x cp) = {got}, this run uses {(e.tp_size, e.pp_size, e.fsdp_size)}; "
                                  "merge it to HF weights (python -m verl_b200.model_merger merge --backend megatron) and load those")
         if self.should_load_model:
             if not os.path.exists(model_f):
@@ -121,12 +122,12 @@ class MegatronCheckpointManager(BaseCheckpointManager):
             st = torch.load(model_f, map_location="cpu", weights_only=False)
             assert st["total"] == s.total and st["names"] == s.names, "checkpoint layout does not match this model-parallel rank"
             s.flat[s.shard_slice].copy_(st["flat_shard"].to(s.flat.dtype))
-            if e.dp_size > 1:
+            if e.fsdp_size > 1:
                 if s.flat.is_cuda:
-                    dist.all_gather_into_tensor(s.flat, s.flat[s.shard_slice].clone(), group=e.dp_group)
+                    dist.all_gather_into_tensor(s.flat, s.flat[s.shard_slice].clone(), group=e.fsdp_group)
                 else:
-                    parts = [torch.empty(s.shard_size, dtype=s.flat.dtype) for _ in range(e.dp_size)]
-                    dist.all_gather(parts, s.flat[s.shard_slice].clone(), group=e.dp_group)
+                    parts = [torch.empty(s.shard_size, dtype=s.flat.dtype) for _ in range(e.fsdp_size)]
+                    dist.all_gather(parts, s.flat[s.shard_slice].clone(), group=e.fsdp_group)
                     s.flat.copy_(torch.cat(parts))
         optimizer_loaded = False
         if self.should_load_optimizer and not e.forward_only and os.path.exists(optim_f):

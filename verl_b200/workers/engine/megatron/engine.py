@@ -4,10 +4,14 @@ Same ``BaseEngine`` contract as the sharded-DP engine, selected with ``strategy:
 this to Megatron-Core (``verl/workers/engine/megatron/transformer_impl.py:260-340`` process groups and model build,
 ``:885-971`` pipeline schedule, ``:981-1009`` weight export); here it is self-contained:
 
-* rank layout ``rank = pp_rank · (dp·tp) + dp_rank · tp + tp_rank`` (TP fastest so a TP group sits on adjacent GPUs);
+* rank layout ``rank = pp_rank · (dp·cp·tp) + dp_rank · (cp·tp) + cp_rank · tp + tp_rank`` (TP fastest so a TP group sits on
+  adjacent GPUs, the context-parallel ranks of a replica next);
 * TP: column/row-parallel projections with the f/g autograd pair, vocabulary-parallel embedding and a
   vocabulary-parallel fused lm_head→log-prob kernel (one [3, T] all-gather instead of materialised logits);
 * PP: contiguous layer ranges, 1F1B schedule over the micro-batches with paired isend/irecv, activations ``[T, H]``;
+* CP: the ranks of a context-parallel group hold the same micro-batch and each a slice of its packed token stream; attention
+  all-gathers K/V (``verl_b200.parallel.context_parallel``), the last stage gathers the per-token outputs. For parameters CP
+  ranks behave like data-parallel ranks: gradients are averaged and the optimizer state is sharded over the DP×CP group;
 * DP: gradients are averaged and the fp32 master/Adam state is sharded over the DP group (distributed optimizer),
   reusing the flat-buffer machinery of the sharded-DP engine; the gradient norm is combined over TP×PP with
   replicated parameters counted once;
@@ -58,41 +62,55 @@ class MegatronEngine(FSDPEngine):
         # into the projections. Off unless asked for (the reference's megatron.yaml turns it on by default).
         self.tp_sp = bool(cfg_get(ec, "sequence_parallel", False)) and self.tp_size > 1
         self.pp_size = int(cfg_get(ec, "pipeline_model_parallel_size", 1) or 1)
-        for key in ("context_parallel_size", "expert_model_parallel_size", "virtual_pipeline_model_parallel_size"):
+        for key in ("expert_model_parallel_size", "virtual_pipeline_model_parallel_size"):
             v = cfg_get(ec, key, None)
             if v not in (None, 1, 0):
                 raise NotImplementedError(f"{key}={v} is not supported by this engine yet")
-        assert self.world % (self.tp_size * self.pp_size) == 0, "world size must be a multiple of tp·pp"
+        self.cp_size = int(cfg_get(ec, "context_parallel_size", 1) or 1)
+        self._cp_zigzag = self.cp_size > 1 and bool(cfg_get(ec, "context_parallel_zigzag", False))
+        self._dynamic_cp = False
+        mp = self.tp_size * self.pp_size * self.cp_size
+        assert self.world % mp == 0, "world size must be a multiple of tp·pp·cp"
         self.sp_size = 1
-        self.dp_size = self.world // (self.tp_size * self.pp_size)
-        self.tp_rank = self.rank % self.tp_size
-        self.dp_rank = (self.rank // self.tp_size) % self.dp_size
-        self.pp_rank = self.rank // (self.tp_size * self.dp_size)
-        self.fsdp_size, self.fsdp_rank, self.ddp_size = self.dp_size, self.dp_rank, 1
+        self.dp_size = self.world // mp
+        tp, cp, dp = self.tp_size, self.cp_size, self.dp_size
+        self.tp_rank = self.rank % tp
+        self.cp_rank = (self.rank // tp) % cp
+        self.dp_rank = (self.rank // (tp * cp)) % dp
+        self.pp_rank = self.rank // (tp * cp * dp)
+        # parameters are replicated over DP×CP: that is the group the gradients are averaged over and the optimizer state is cut over
+        self.fsdp_size, self.fsdp_rank, self.ddp_size = dp * cp, self.dp_rank * cp + self.cp_rank, 1
 
     # ------------------------------------------------------------------ groups
     def _build_groups(self):
-        tp, dp, pp, W = self.tp_size, self.dp_size, self.pp_size, self.world
-        self.tp_group = self.pp_group = self.mp_group = self.dp_group = self.embed_group = None
+        tp, cp, dp, pp, W = self.tp_size, self.cp_size, self.dp_size, self.pp_size, self.world
+        self.tp_group = self.pp_group = self.mp_group = self.dp_group = self.embed_group = self.cp_group = None
         self.fsdp_group = self.ddp_group = self.sp_group = None
         self.sp_rank = 0
-        self.prev_rank = self.rank - dp * tp if self.pp_rank > 0 else None
-        self.next_rank = self.rank + dp * tp if self.pp_rank < pp - 1 else None
-        self.mp_ranks = [p * dp * tp + self.dp_rank * tp + t for p in range(pp) for t in range(tp)]
-        self.pp_ranks = [p * dp * tp + self.dp_rank * tp + self.tp_rank for p in range(pp)]
+        stage = dp * cp * tp                                  # ranks per pipeline stage
+        rk = lambda p, d, c, t: p * stage + d * cp * tp + c * tp + t      # noqa: E731
+        self.prev_rank = self.rank - stage if self.pp_rank > 0 else None
+        self.next_rank = self.rank + stage if self.pp_rank < pp - 1 else None
+        self.mp_ranks = [rk(p, self.dp_rank, self.cp_rank, t) for p in range(pp) for t in range(tp)]
+        self.pp_ranks = [rk(p, self.dp_rank, self.cp_rank, self.tp_rank) for p in range(pp)]
         if W == 1:
             return
         if tp > 1:
             self.tp_group, _ = _new_groups(self.rank, [list(range(b, b + tp)) for b in range(0, W, tp)])
+        if cp > 1:
+            self.cp_group, _ = _new_groups(self.rank, [[rk(p, d, c, t) for c in range(cp)] for p in range(pp) for d in range(dp) for t in range(tp)])
         if dp > 1:
-            self.dp_group, _ = _new_groups(self.rank, [[p * dp * tp + d * tp + t for d in range(dp)] for p in range(pp) for t in range(tp)])
+            self.dp_group, _ = _new_groups(self.rank, [[rk(p, d, c, t) for d in range(dp)] for p in range(pp) for c in range(cp) for t in range(tp)])
         if pp > 1:
-            self.pp_group, _ = _new_groups(self.rank, [[p * dp * tp + d * tp + t for p in range(pp)] for d in range(dp) for t in range(tp)])
+            self.pp_group, _ = _new_groups(self.rank, [[rk(p, d, c, t) for p in range(pp)] for d in range(dp) for c in range(cp) for t in range(tp)])
         if tp * pp > 1:
-            self.mp_group, _ = _new_groups(self.rank, [[p * dp * tp + d * tp + t for p in range(pp) for t in range(tp)] for d in range(dp)])
+            self.mp_group, _ = _new_groups(self.rank, [[rk(p, d, c, t) for p in range(pp) for t in range(tp)] for d in range(dp) for c in range(cp)])
         if pp > 1:   # first and last stage of each pipeline: gradient sum of tied input/output embeddings
-            self.embed_group, _ = _new_groups(self.rank, [[d * tp + t, (pp - 1) * dp * tp + d * tp + t] for d in range(dp) for t in range(tp)])
-        self.fsdp_group = self.dp_group
+            self.embed_group, _ = _new_groups(self.rank, [[rk(0, d, c, t), rk(pp - 1, d, c, t)] for d in range(dp) for c in range(cp) for t in range(tp)])
+        if cp == 1:
+            self.fsdp_group = self.dp_group
+        elif dp * cp > 1:
+            self.fsdp_group, _ = _new_groups(self.rank, [[rk(p, d, c, t) for d in range(dp) for c in range(cp)] for p in range(pp) for t in range(tp)])
 
     # ------------------------------------------------------------------ build
     def initialize(self):
@@ -136,9 +154,13 @@ class MegatronEngine(FSDPEngine):
                         tp_ctx = TPContext(self.tp_group, self._tp_host_group(), max_tokens=max_tok, hidden=cfg.hidden_size, max_out=cfg.hidden_size)
                 self.model.set_tp_group(self.tp_group, self.tp_rank * self.local_cfg.vocab_size, sequence_parallel=self.tp_sp, tp_ctx=tp_ctx)
         self.model.gradient_checkpointing = bool(cfg_get(self.model_config, "enable_gradient_checkpointing", False))
-        self.store = FlatParamStore(self.model, self.dp_size, self.dp_rank)
-        if self.dp_size > 1:
-            dist.broadcast(self.store.flat, src=self.pp_rank * self.dp_size * tp + self.tp_rank, group=self.dp_group)
+        if self.cp_size > 1:
+            self.model.sp_group = self.cp_group
+            for layer in self.model.layers:
+                layer.self_attn.sp_mode = "context"
+        self.store = FlatParamStore(self.model, self.fsdp_size, self.fsdp_rank)
+        if self.fsdp_size > 1:
+            dist.broadcast(self.store.flat, src=self.pp_rank * self.fsdp_size * tp + self.tp_rank, group=self.fsdp_group)
         self._symm_params = self._symm_grads = None
         self._dup_ranges = self._replicated_ranges()
         if not self.forward_only:
@@ -198,7 +220,7 @@ class MegatronEngine(FSDPEngine):
 
     # ------------------------------------------------------------------ contract
     def is_mp_src_rank_with_outputs(self) -> bool:
-        return self.tp_rank == 0 and self.pp_rank == self.pp_size - 1
+        return self.tp_rank == 0 and self.cp_rank == 0 and self.pp_rank == self.pp_size - 1
 
     def _micro_batch_indices(self, seq_lens, meta):
         from verl_b200.utils.seqlen_balancing import rearrange_micro_batches
@@ -210,8 +232,34 @@ class MegatronEngine(FSDPEngine):
         return [list(range(i, min(n, i + mbs))) for i in range(0, n, mbs)]
 
     # ------------------------------------------------------------------ one stage
+    def _cp_slice(self, pb, labels):
+        """This context-parallel rank's slice of the packed micro-batch (contiguous or zig-zag placement): the local
+        ``PackedBatch`` keeps the cu_seqlens of the whole stream (attention needs them), ``rows`` are the global token indices
+        of the local rows and ``t_pad`` the padded stream length."""
+        from verl_b200.models.transformer import PackedBatch
+        from verl_b200.parallel.context_parallel import zigzag_permutation
+
+        cp, r = self.cp_size, self.cp_rank
+        T = pb.input_ids.shape[0]
+        unit = cp * (2 if self._cp_zigzag else 1) * (self.tp_size if self.tp_sp else 1)
+        pad = (-T) % unit
+        ids, pos, lab = pb.input_ids, pb.position_ids, labels
+        if pad:
+            ids, lab = torch.nn.functional.pad(ids, (0, pad)), torch.nn.functional.pad(lab, (0, pad))
+            pos = torch.cat([pos, torch.arange(pad, device=pos.device, dtype=pos.dtype)])
+        tl = (T + pad) // cp
+        if self._cp_zigzag:
+            rows = zigzag_permutation(T + pad, cp).to(ids.device)[r * tl:(r + 1) * tl]
+        else:
+            rows = torch.arange(r * tl, (r + 1) * tl, device=ids.device)
+        pbl = PackedBatch(ids.index_select(0, rows), pos.index_select(0, rows), pb.cu_seqlens, pb.cu_seqlens_cpu, pb.max_seqlen, None)
+        pbl.cp_zigzag = self._cp_zigzag
+        return pbl, lab.index_select(0, rows), T + pad
+
     def _stage_forward(self, mb: dict, meta: dict, h_in: Optional[torch.Tensor]):
         """Runs this stage on one micro-batch. Returns (stream or None, model_output dict on the last stage)."""
+        if self.cp_size > 1:
+            return self._stage_forward_cp(mb, meta, h_in)
         pb, labels = self._pack(mb)
         h = self.model.forward_hidden(pb, h_in)
         if not self.is_last:
@@ -242,6 +290,49 @@ class MegatronEngine(FSDPEngine):
                 raise NotImplementedError("score centering / distillation heads are not available with a vocabulary-parallel lm_head; "
                                           "use tensor_model_parallel_size=1 for this role or the sharded-DP engine")
             self._score_centering_terms(out, mb, meta, h_sel, valid, temperature)
+        return None, out
+
+    def _stage_forward_cp(self, mb: dict, meta: dict, h_in: Optional[torch.Tensor]):
+        """The same with context parallelism: the stage works on this rank's token slice; on the last stage the per-token
+        outputs of the slices are gathered over the CP group (gradient scaled by cp: the DP×CP average then counts every
+        token once) and put back into stream order before the response window is cut out."""
+        from verl_b200.parallel.ulysses import gather_outputs_and_unpad
+
+        pb, labels = FSDPEngine._pack(self, mb)
+        T = pb.input_ids.shape[0]
+        pbl, lab_l, t_pad = self._cp_slice(pb, labels)
+        h = self.model.forward_hidden(pbl, h_in)
+        if not self.is_last:
+            return h, None
+        R = mb["responses"].shape[1]
+        idx, valid = response_gather_index(mb["attention_mask"], R)
+        out: dict[str, torch.Tensor] = {}
+
+        def to_stream(x_local):
+            x = gather_outputs_and_unpad(x_local.float(), 0, None, 0, grad_scaler=True, group=self.cp_group)
+            if self._cp_zigzag:
+                from verl_b200.parallel.context_parallel import zigzag_permutation
+
+                x = x.index_select(0, torch.argsort(zigzag_permutation(t_pad, self.cp_size).to(x.device)))
+            return x[:T]
+
+        zero = torch.zeros(idx.shape, dtype=torch.float32, device=h.device)
+        if self.cfg.value_head:
+            vals = to_stream(torch.nn.functional.linear(h, self.model.score).squeeze(-1))
+            out["values"] = torch.where(valid, vals[idx.reshape(-1)].reshape(idx.shape), zero)
+            return None, out
+        temperature = float(meta.get("temperature", 1.0))
+        need_entropy = bool(meta.get("calculate_entropy", False))
+        if self.tp_size > 1:
+            lp, ent = vocab_parallel_logprob(copy_to_tp(h, self.tp_group), self.model.output_weight, lab_l, temperature, need_entropy,
+                                             self.tp_group, self.model.vocab_offset)
+        else:
+            lp, ent = ops.linear_logprob_entropy(h, self.model.output_weight, lab_l, temperature, need_entropy)
+        out["log_probs"] = torch.where(valid, to_stream(lp)[idx.reshape(-1)].reshape(idx.shape), zero)
+        if ent is not None:
+            out["entropy"] = torch.where(valid, to_stream(ent)[idx.reshape(-1)].reshape(idx.shape), zero)
+        if meta.get("score_centering") or meta.get("distillation") or meta.get("return_topk"):
+            raise NotImplementedError("score centering / distillation heads are not available under context parallelism in this engine")
         return None, out
 
     # ------------------------------------------------------------------ p2p
@@ -285,7 +376,12 @@ class MegatronEngine(FSDPEngine):
 
         H = self.cfg.hidden_size
         ntoks = [int(seq_lens[torch.as_tensor(ix, device=seq_lens.device)].sum()) for ix in mb_indices]
-        if self.tp_sp:      # stage boundaries carry this rank's 1/tp of the (padded) tokens
+        if self.cp_size > 1:   # stage boundaries carry this rank's slice of the padded stream (and 1/tp of it under sequence parallelism)
+            unit = self.cp_size * (2 if self._cp_zigzag else 1) * (self.tp_size if self.tp_sp else 1)
+            ntoks = [-(-t // unit) * unit // self.cp_size for t in ntoks]
+            if self.tp_sp:
+                ntoks = [t // self.tp_size for t in ntoks]
+        elif self.tp_sp:      # stage boundaries carry this rank's 1/tp of the (padded) tokens
             ntoks = [-(-t // self.tp_size) for t in ntoks]
         m = len(mb_indices)
         outputs: dict[str, list[torch.Tensor]] = {}
@@ -396,14 +492,14 @@ class MegatronEngine(FSDPEngine):
         if self.tp_size * self.pp_size == 1:
             return sumsq
         s = self.store
-        lo = self.dp_rank * s.shard_size if gshard.numel() == s.shard_size and self.dp_size > 1 else 0
+        lo = self.fsdp_rank * s.shard_size if gshard.numel() == s.shard_size and self.fsdp_size > 1 else 0
         corr = torch.zeros(1, dtype=torch.float32, device=gshard.device)
         for a, b, w in self._dup_ranges:
             a2, b2 = max(a, lo), min(b, lo + gshard.numel())
             if b2 > a2:
                 corr += (1.0 - w) * gshard[a2 - lo : b2 - lo].float().pow(2).sum()
-        if self.dp_size > 1:
-            dist.all_reduce(corr, group=self.dp_group)
+        if self.fsdp_size > 1:
+            dist.all_reduce(corr, group=self.fsdp_group)
         total = (sumsq.reshape(1).float() - corr).clone()
         dist.all_reduce(total, group=self.mp_group)
         if sumsq.data_ptr() != total.data_ptr():
