@@ -280,6 +280,24 @@ def bench_attn(a, backward=False):
         dout = torch.randn_like(out)
         ms = timeit(lambda: torch.autograd.grad(out, qkv, dout, retain_graph=True), a.iters)
         report(f"attention bwd T={T} L={a.seqlen} {Hq}/{Hkv} heads (causal FLOPs x2.5)", ms, flops=2.5 * fl)
+    if a.compare:
+        # the library kernel the reference calls for the same op (verl/models/transformers/monkey_patch.py:146-148)
+        try:
+            from flash_attn import flash_attn_varlen_func
+        except ImportError as e:
+            print(f"  flash_attn not importable: {e}")
+            return
+        q, k, v = (t.reshape(T, -1, D).contiguous() for t in qkv.detach().split([Hq * D, Hkv * D, Hkv * D], dim=-1))
+        if not backward:
+            with torch.no_grad():
+                ms2 = timeit(lambda: flash_attn_varlen_func(q, k, v, cud, cud, a.seqlen, a.seqlen, causal=True), a.iters)
+            report("  flash_attn_varlen_func fwd, same shapes", ms2, flops=fl)
+        else:
+            q, k, v = (t.requires_grad_(True) for t in (q, k, v))
+            o2 = flash_attn_varlen_func(q, k, v, cud, cud, a.seqlen, a.seqlen, causal=True)
+            d2 = torch.randn_like(o2)
+            ms2 = timeit(lambda: torch.autograd.grad(o2, (q, k, v), d2, retain_graph=True), a.iters)
+            report("  flash_attn_varlen_func bwd, same shapes", ms2, flops=2.5 * fl)
 
 
 def bench_lmhead(a):
