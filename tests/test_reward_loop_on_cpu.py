@@ -211,3 +211,57 @@ def test_prime_manager_rlla_and_math_verify():
     if not math_verify.available():
         with pytest.raises(ImportError):
             math_verify.compute_score("42", "42")
+
+
+def test_reward_model_manager_serves_replicas_behind_a_router():
+    """Two in-process judge replicas behind the router: requests spread over both, a repeated request id stays on its replica,
+    answers equal the engine's own, and the `remote` reward-loop manager scores through the router client."""
+    import asyncio
+    import json
+    import urllib.request
+
+    import torch
+
+    from verl_b200.experimental.reward_loop import RewardLoopManager, RewardModelManager
+    from verl_b200.models.config import PRESETS
+    from verl_b200.models.transformer import DecoderLM
+    from verl_b200.utils.tokenizer import ByteChatTokenizer
+    from verl_b200.workers.rollout.engine import InferenceEngine, SamplingParams
+
+    model = DecoderLM(PRESETS["tiny-qwen2"], dtype=torch.float32, seed=3)
+    engines = [InferenceEngine(model, max_num_seqs=8, max_model_len=128, num_blocks=32) for _ in range(2)]
+    tok = ByteChatTokenizer()
+    mgr = RewardModelManager({"rollout": {"tensor_model_parallel_size": 1, "free_cache_engine": False}}, engines=engines, tokenizer=tok)
+    try:
+        assert len(mgr.server_addresses) == 2 and json.load(urllib.request.urlopen(f"http://{mgr.get_router_address()}/health"))["workers"] == 2
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(10, 250, (12,), generator=g).tolist() for _ in range(8)]
+        sp = SamplingParams(temperature=0.0, max_tokens=6)
+        want = engines[0].generate(prompts, sp)
+        client = mgr.client()
+
+        async def go():
+            outs = await asyncio.gather(*[client.generate(f"req-{i}", p, sp) for i, p in enumerate(prompts)])
+            again = await client.generate("req-0", prompts[0], sp)
+            await client.close()
+            return outs, again
+
+        outs, again = asyncio.run(go())
+        for o, w in zip(outs, want):
+            assert o.token_ids == w.token_ids
+        assert again.token_ids == want[0].token_ids
+        served = {w["url"]: w["served"] for w in json.load(urllib.request.urlopen(f"http://{mgr.get_router_address()}/workers"))["workers"]}
+        assert sum(served.values()) == 9 and min(served.values()) >= 3          # both replicas took a share
+        first = mgr.router.sticky["req-0"]
+        assert mgr.router.sticky["req-0"] == first and len(mgr.router.sticky) == 8
+        # the remote reward-loop manager scores a sample through the router: the judge's text is parsed for a number
+        loop_mgr = RewardLoopManager({"reward": {"reward_manager": "remote", "reward_kwargs": {"judge_max_tokens": 4}}}, tok, None, num_workers=2,
+                                     manager_name="remote", rm_client=mgr.client())
+        s = asyncio.run(loop_mgr.workers[0].compute_score({"prompt_ids": prompts[0], "response_ids": prompts[1][:5]}))
+        assert isinstance(s["reward_score"], float) and "rm_score" in s["reward_extra_info"]
+        loop_mgr.shutdown()
+        mgr.sleep()
+        assert all(e.cache is None for e in engines)
+        mgr.wake_up()
+    finally:
+        mgr.shutdown()
