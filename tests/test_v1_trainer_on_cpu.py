@@ -148,6 +148,50 @@ def test_v1_separate_async_trainer_feeds_a_standalone_replica_and_pushes_weights
     assert replica._proc.poll() is not None                   # the pool was shut down with the trainer
 
 
+def test_v1_separate_async_lends_the_training_engine_while_it_would_wait(tmp_path):
+    """Hybrid lending: after a step the colocated engine joins the balancer and serves requests until the switch threshold of
+    the next batch is sampleable; then it is taken back (its open requests move to the pool) and training proceeds. The
+    threshold adapts and the decision metrics are logged."""
+    import os
+
+    from verl_b200.trainer.ppo.v1.trainer_separate_async import HybridEngineMode
+
+    logf = tmp_path / "lend.jsonl"
+    os.environ["VERL_FILE_LOGGER_PATH"] = str(logf)
+    try:
+        cfg = load_config("ppo_trainer", [o for o in OV if not o.startswith("trainer.logger")] +
+                          ["trainer.logger=[file]", "trainer.total_training_steps=3", f"trainer.default_local_dir={tmp_path}/ckpt_lend",
+                           "actor_rollout_ref.rollout.mode=async", "actor_rollout_ref.rollout.free_cache_engine=false", "trainer.resume_mode=disable",
+                           "+trainer.v1.max_off_policy_threshold=4", "+trainer.v1.async_warmup_batches=0", "+trainer.v1.rollout_num_blocks=64",
+                           "trainer.v1.separate_async.hybrid_rollout.enable_switch=true", "trainer.v1.separate_async.hybrid_rollout.switch_threshold_ratio=0.5"])
+        tr = get_trainer_cls("separate_async")(cfg, reward_fn=load_reward_manager(cfg, None))
+        tr.init()
+        assert tr._switch_enabled and tr.current_mode == HybridEngineMode.TRAINER
+        assert tr._switch_threshold() == max(1, round(0.5 * tr.train_batch_size))
+        served_before = tr._hybrid_replica.server.stats.get("finished", 0)
+        tr.fit()
+    finally:
+        os.environ.pop("VERL_FILE_LOGGER_PATH", None)
+    rows = [json.loads(x)["data"] for x in logf.read_text().splitlines()]
+    assert len(rows) == 3 and all(r["perf/total_num_tokens"] > 0 for r in rows)
+    # with no warm-up batch every step waits for its trajectories: the trainer lent its engine after steps 1 and 2 ...
+    kinds = [k for k, _ in tr.switch_log]
+    assert kinds.count("rollout") >= 1 and kinds.count("trainer") == kinds.count("rollout")
+    assert tr.current_mode == HybridEngineMode.TRAINER
+    assert rows[0]["separate_async/decision/should_switch_to_rollout"] == 1.0 and rows[-1]["separate_async/decision/should_switch_to_rollout"] == 0.0
+    assert "separate_async/switch/threshold_ratio" in rows[0] and rows[0]["separate_async/switch/idle"] == 1.0
+    # ... and the lent engine really served requests
+    assert tr._hybrid_replica.server.stats.get("finished", 0) + tr._hybrid_replica.server.stats.get("aborted", 0) > served_before
+    # adaptive threshold: repeated idle steps push the ratio up, calm ones bring it down to one mini-batch at the lowest
+    tr._switch_threshold_ratio, tr._idle_steps, tr._calm_steps = 0.5, 0, 0
+    for _ in range(2):
+        tr._adapt_switch_threshold(True)
+    assert abs(tr._switch_threshold_ratio - 0.55) < 1e-9
+    for _ in range(40):
+        tr._adapt_switch_threshold(False)
+    assert abs(tr._switch_threshold_ratio - 1.0 / tr.parameter_sync_step) < 1e-9
+
+
 def test_transfer_queue_over_tcp_between_processes(tmp_path):
     """A served TransferQueue: a child process writes trajectories, this process blocks on the server until they are tagged
     finished, reads them back as a batch and sees the child's tags; server-side errors come back as exceptions."""

@@ -89,41 +89,28 @@ __global__ void __launch_bounds__(256) reshard_quant_kernel(const __grid_constan
   const bool vec = (c0 + 8 <= N) && ((ld_src & 7) == 0);
   uint4 regs[8];
   float amax = 0.f;
-  // all eight row loads are issued before anything consumes them: the kernel lives on bytes in flight
-  const int owner0 = (row_begin + r0) / rows_per_rank;
-  const int in0 = (row_begin + r0) - owner0 * rows_per_rank;         // one division per block, rows advance from here
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const int dr = (threadIdx.x >> 4) + 16 * i;
+    const int r = r0 + (threadIdx.x >> 4) + 16 * i;
     regs[i] = make_uint4(0, 0, 0, 0);
-    if (r0 + dr < M_out) {
-      int owner = owner0, in = in0 + dr;
-      while (in >= rows_per_rank) { in -= rows_per_rank; ++owner; }
-      const bf16* base = src.ptr[owner] + (long)in * ld_src;
+    if (r < M_out) {
+      const int g = row_begin + r;                      // row of the full matrix
+      const bf16* base = src.ptr[g / rows_per_rank] + (long)(g % rows_per_rank) * ld_src;
       if (vec) {
         regs[i] = *reinterpret_cast<const uint4*>(base + c0);
       } else {
         bf16* e = reinterpret_cast<bf16*>(&regs[i]);
         for (int j = 0; j < 8; ++j) e[j] = (c0 + j < N) ? base[c0 + j] : __float2bfloat16(0.f);
       }
-    }
-  }
-  if (out_bf16 != nullptr) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = r0 + (threadIdx.x >> 4) + 16 * i;
-      if (r >= M_out) continue;
-      if (vec && (ld_bf16 & 7) == 0) {
-        *reinterpret_cast<uint4*>(out_bf16 + (long)r * ld_bf16 + c0) = regs[i];
-      } else {
-        const bf16* e = reinterpret_cast<const bf16*>(&regs[i]);
-        for (int j = 0; j < 8 && c0 + j < N; ++j) out_bf16[(long)r * ld_bf16 + c0 + j] = e[j];
+      if (out_bf16 != nullptr) {
+        if (vec && (ld_bf16 & 7) == 0) {
+          *reinterpret_cast<uint4*>(out_bf16 + (long)r * ld_bf16 + c0) = regs[i];
+        } else {
+          const bf16* e = reinterpret_cast<const bf16*>(&regs[i]);
+          for (int j = 0; j < 8 && c0 + j < N; ++j) out_bf16[(long)r * ld_bf16 + c0 + j] = e[j];
+        }
       }
     }
-  }
-  if (y == nullptr) return;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
     const bf16* e = reinterpret_cast<const bf16*>(&regs[i]);
 #pragma unroll
     for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(__bfloat162float(e[j])));

@@ -12,14 +12,23 @@ rest; generation never stops for training.
   (a file on CPU). Requests interrupted by the hand-off are resumed by the clients with the tokens they already have
   (partial rollout), so a trajectory may span weight versions.
 
-Reference: ``verl/trainer/ppo/v1/trainer_separate_async.py:46`` (disjoint trainer / rollouter GPU pools, parameter
-synchronisation through the checkpoint engine, staleness control).
+* Lending (``trainer.v1.separate_async.hybrid_rollout.enable_switch``): while the trainer would only wait for trajectories its
+  own GPUs serve generation too. The colocated engine of the training rank joins the balancer after a step ("rollout" mode) and
+  is taken back, with its open requests handed to the pool as partial rollouts, once ``switch_threshold_ratio`` of the next
+  batch is sampleable ("trainer" mode). The threshold adapts: it rises after steps that still idled, falls after calm ones; a
+  switch is only made when the wait it is expected to save exceeds the measured cost of switching there and back.
+
+Reference: ``verl/trainer/ppo/v1/trainer_separate_async.py:40-420`` (disjoint trainer / rollouter GPU pools, parameter
+synchronisation through the checkpoint engine, staleness control, ``HybridEngineMode`` switching).
 """
 
 from __future__ import annotations
 
+import enum
 import os
 import tempfile
+import time
+from collections import deque
 
 from verl_b200.workers.rollout.llm_server import LLMServerManager
 from verl_b200.workers.rollout.replica import RolloutMode, RolloutReplica
@@ -29,7 +38,12 @@ from .checkpoint_callback import CheckpointCallback
 from .replay_buffer import ReplayBufferAsync
 from .trainer_base import PPOTrainer, _g, register_trainer
 
-__all__ = ["PPOTrainerSeparateAsync"]
+__all__ = ["PPOTrainerSeparateAsync", "HybridEngineMode"]
+
+
+class HybridEngineMode(enum.Enum):
+    TRAINER = "trainer"
+    ROLLOUT = "rollout"
 
 
 @register_trainer("separate_async")
@@ -87,6 +101,132 @@ class PPOTrainerSeparateAsync(PPOTrainer):
         self.checkpoint_callback = CheckpointCallback(self.config.trainer)
         self.param_version = 0
         self._export_file = None
+        self._setup_hybrid(local, servers)
+
+    # ------------------------------------------------------------------ lending the training GPUs to generation
+    def _setup_hybrid(self, local, servers: LLMServerManager):
+        from verl_b200.trainer.config import HybridRolloutSwitchConfig
+
+        raw = dict(_g(self.config, "trainer.v1.separate_async.hybrid_rollout", {}) or {})
+        known = {f for f in HybridRolloutSwitchConfig.__dataclass_fields__}
+        self.hybrid_rollout_config = HybridRolloutSwitchConfig(**{k: v for k, v in raw.items() if k in known})
+        self.current_mode = HybridEngineMode.TRAINER
+        self._servers = servers
+        self._hybrid_replica = None
+        self.parameter_sync_step = int(_g(self.config, "trainer.v1.separate_async.parameter_sync_step", 1) or 1)
+        enable = bool(_g(self.config, "actor_rollout_ref.hybrid_engine", True)) and self.hybrid_rollout_config.enable_switch
+        if self.hybrid_rollout_config.enable_switch and not enable:
+            print("[separate_async] hybrid_rollout.enable_switch is ignored because actor_rollout_ref.hybrid_engine=False", flush=True)
+        self._switch_enabled = enable
+        if not enable:
+            return
+        self._hybrid_replica = local.server_manager.replicas[0]            # the colocated engine of this training rank
+        self._hybrid_name = f"hybrid-{self.rank}"
+        c = self.hybrid_rollout_config
+        self._switch_threshold_ratio = float(c.switch_threshold_ratio)
+        self._idle_steps = self._calm_steps = 0
+        self._step_sample_wait_seconds = 0.0
+        self._step_wait_samples = 0
+        self._wait_seconds = 0.0
+        self._wait_samples = 0
+        self._to_rollout_costs: deque = deque(maxlen=int(c.switch_cost_window_size))
+        self._to_trainer_costs: deque = deque(maxlen=int(c.switch_cost_window_size))
+        standalone = max(1, len(self.replicas))
+        self._scaling_factor = (self.world + standalone) / standalone          # generation capacity with / without the lent GPUs
+        self.switch_log: list = []
+
+    def _agree(self, value: float, op: str) -> float:
+        """The controller runs on every rank; decisions that change collective behaviour use the same number everywhere."""
+        if self.world <= 1:
+            return value
+        import torch
+        import torch.distributed as dist
+
+        from verl_b200.single_controller.spmd import init_spmd_process_group
+
+        t = torch.tensor([float(value)], dtype=torch.float64)
+        dist.all_reduce(t, op={"min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX, "sum": dist.ReduceOp.SUM}[op], group=init_spmd_process_group())
+        return float(t.item())
+
+    def _switch_threshold(self) -> int:
+        """Prompt groups that must be sampleable before the training GPUs are taken back (at least one mini-batch)."""
+        mini = max(1, self.train_batch_size // self.parameter_sync_step)
+        return min(max(round(self._switch_threshold_ratio * self.train_batch_size), mini), self.train_batch_size)
+
+    def _sampleable(self, step: int) -> int:
+        return int(self._agree(self.replay_buffer.get_sampleable_count(step, self.partition_id) * self.world, "min"))
+
+    def switch_to_rollout(self):
+        """Wake the colocated engine on the committed weights and let the balancer route requests to it."""
+        t0 = time.perf_counter()
+        self.stages.actor_rollout_wg.update_weights()
+        self._hybrid_replica.wake_up()
+        if getattr(self._hybrid_replica.server, "resume", None) is not None:
+            self._hybrid_replica.server.resume()
+        self._servers.add_server(self._hybrid_name, self._hybrid_replica.server)
+        self.current_mode = HybridEngineMode.ROLLOUT
+        self._to_rollout_costs.append(time.perf_counter() - t0)
+        self.switch_log.append(("rollout", self.global_steps))
+
+    def switch_to_trainer(self):
+        """Stop routing to the colocated engine, hand its open requests to the pool (the clients resume them with the tokens
+        generated so far) and release its KV cache for training."""
+        t0 = time.perf_counter()
+        self._servers.remove_server(self._hybrid_name)
+        self._hybrid_replica.abort_all_requests()
+        self._hybrid_replica.server.wait_idle(timeout=60.0)
+        self._hybrid_replica.sleep()
+        self.current_mode = HybridEngineMode.TRAINER
+        self._to_trainer_costs.append(time.perf_counter() - t0)
+        self.switch_log.append(("trainer", self.global_steps))
+
+    def _adapt_switch_threshold(self, had_idle: bool) -> None:
+        c = self.hybrid_rollout_config
+        if had_idle:
+            self._calm_steps = 0
+            self._idle_steps = min(self._idle_steps + 1, c.switch_threshold_release_steps)
+            if self._idle_steps >= c.switch_threshold_release_steps:
+                self._switch_threshold_ratio = min(1.0, self._switch_threshold_ratio + c.switch_threshold_step_up)
+            return
+        self._idle_steps = 0
+        self._calm_steps = min(self._calm_steps + 1, c.switch_threshold_release_steps)
+        if self._calm_steps >= c.switch_threshold_release_steps:
+            self._switch_threshold_ratio = max(1.0 / self.parameter_sync_step, self._switch_threshold_ratio - c.switch_threshold_step_down)
+
+    def _effective_switch_cost(self):
+        if not self._to_rollout_costs or not self._to_trainer_costs:
+            return None
+        return sum(self._to_rollout_costs) / len(self._to_rollout_costs) + sum(self._to_trainer_costs) / len(self._to_trainer_costs)
+
+    def _lending_decision(self, total_steps: int) -> dict:
+        """After a step: adapt the threshold, then lend the GPUs for the coming wait if that is expected to pay."""
+        c = self.hybrid_rollout_config
+        poll = max(5.0 * float(getattr(self.replay_buffer, "poll_interval_s", 0.01)), 0.05)
+        had_idle = self._agree(self._step_sample_wait_seconds, "max") > poll        # the step really waited for trajectories
+        if self._step_wait_samples > 0 and self._step_sample_wait_seconds > 0:
+            self._wait_seconds += self._step_sample_wait_seconds
+            self._wait_samples += self._step_wait_samples
+        ratio_used = self._switch_threshold_ratio
+        if c.adaptive_switch_threshold:
+            self._adapt_switch_threshold(had_idle)
+        threshold = self._switch_threshold()
+        sampleable = self._sampleable(self.global_steps + 1)
+        remaining = max(0, threshold - sampleable)
+        per_sample = self._agree(self._wait_seconds / self._wait_samples, "max") if self._wait_samples > 0 else None
+        cost = self._effective_switch_cost()
+        cost = self._agree(cost, "max") if cost is not None else None
+        benefit = remaining * per_sample * (1.0 - 1.0 / self._scaling_factor) if per_sample is not None else None
+        should = self.global_steps < total_steps and remaining > 0 and (benefit is None or cost is None or benefit > cost)
+        m = {"separate_async/switch/threshold_ratio": ratio_used, "separate_async/switch/wait_samples": float(self._step_wait_samples),
+             "separate_async/switch/idle": float(had_idle), "separate_async/decision/sampleable_count": float(sampleable),
+             "separate_async/decision/remaining": float(remaining), "separate_async/decision/should_switch_to_rollout": float(should)}
+        if per_sample is not None:
+            m["separate_async/decision/per_sample_time_seconds"] = per_sample
+        if cost is not None:
+            m["separate_async/decision/effective_switch_cost_seconds"] = cost
+        if should and self.current_mode == HybridEngineMode.TRAINER:
+            self.switch_to_rollout()
+        return m
 
     # ------------------------------------------------------------------ weight hand-off
     def sync_weights(self) -> dict:
@@ -118,17 +258,44 @@ class PPOTrainerSeparateAsync(PPOTrainer):
 
     def on_step_begin(self):
         self._submit_prompts(self.train_batch_size)
+        if not self._switch_enabled:
+            return
+        self._step_sample_wait_seconds = 0.0
+        self._step_wait_samples = 0
+        if self.current_mode == HybridEngineMode.ROLLOUT and self._sampleable(self.global_steps) >= self._switch_threshold():
+            self.switch_to_trainer()
 
     def on_sample_begin(self):
         need = max(1, self.train_batch_size // self.world)
+        if self._switch_enabled:
+            have = self.replay_buffer.get_sampleable_count(self.global_steps, self.partition_id)
+            self._step_wait_samples += max(0, need - have)
+            self._sample_start = time.perf_counter()
+            if self.current_mode == HybridEngineMode.ROLLOUT:
+                # the GPUs stay lent until enough of the batch exists; training cannot start before they are back
+                self.replay_buffer.wait_for_sampleable(self.global_steps, self.partition_id, max(1, self._switch_threshold() // self.world))
+                self._agree(0.0, "max")                # every rank has reached its share: switch together
+                self.switch_to_trainer()
         self.replay_buffer.wait_for_sampleable(self.global_steps, self.partition_id, need)
+
+    def on_sample_end(self):
+        if self._switch_enabled:
+            self._step_sample_wait_seconds += time.perf_counter() - self._sample_start
 
     def step(self, metrics: dict, timing_raw: dict):
         out = super().step(metrics, timing_raw)
         metrics.update(self.sync_weights())
+        if self._switch_enabled:
+            metrics.update(self._lending_decision(int(self.stages.total_training_steps)))
         return out
 
+    def on_validate_begin(self):
+        if self._switch_enabled and self.current_mode == HybridEngineMode.ROLLOUT:
+            self.switch_to_trainer()               # validation generates on the colocated engine through the stage trainer
+
     def on_train_end(self):
+        if self._switch_enabled and self.current_mode == HybridEngineMode.ROLLOUT:
+            self.switch_to_trainer()
         self.agent_loop.shutdown()
         for r in getattr(self, "_owned", []):
             r.shutdown()

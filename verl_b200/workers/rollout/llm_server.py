@@ -160,7 +160,18 @@ class LLMServerManager:
 
     def client(self) -> LLMServerClient:
         cls = FullyAsyncLLMServerClient if self.fully_async else LLMServerClient
-        return cls(self.servers, self.balancer)
+        c = cls(self.servers, self.balancer)
+        c.servers = self.servers          # shared, not copied: servers that join or leave later are seen by every client
+        return c
+
+    def add_server(self, name: str, target) -> None:
+        """Let the balancer route to one more server (an in-process ``AsyncRolloutServer`` or a ``host:port`` address)."""
+        self.servers[name] = target
+        self.balancer.add_server(name)
+
+    def remove_server(self, name: str) -> None:
+        """Stop routing to ``name``. Requests it is still running finish (or are aborted by the caller) under its old entry."""
+        self.balancer.remove_server(name)
 
     def prometheus_targets(self) -> list[str]:
         return [r.address for r in self.replicas if r.address]
