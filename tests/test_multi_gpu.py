@@ -231,6 +231,31 @@ for name in ("model.layers.0.self_attn.q_proj.weight", "model.layers.1.mlp.down_
     # (a sign flip of a near-zero gradient costs 2 * lr on single elements, hence the mean as the tight check)
     assert (a - b).abs().max().item() < 2.5e-3 and (a - b).abs().mean().item() < 3e-4, (name, (a - b).abs().max().item(), (a - b).abs().mean().item())
 assert exported["model.layers.0.self_attn.q_proj.weight"].shape == (512, 512)
+# ---- the same engine with context parallelism instead of tensor parallelism (zig-zag placement), and the sharded-DP engine with
+# dynamic context parallelism (every sample on the smallest sub-group that holds it): both must reproduce the single-GPU engine
+cp = MegatronEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "context_parallel_size": world, "context_parallel_zigzag": True}, {"lr": 1e-3}, {})
+cp.initialize()
+lp_cp = cp.infer_batch(data)["model_output"]["log_probs"]
+cp.optimizer_zero_grad()
+cp.forward_backward_batch(data, loss_fn)
+gn_cp = cp.optimizer_step()
+torch.cuda.synchronize()
+_ext.check_status("cp engine")
+d_cp2 = (lp_cp.float() - lp_ref.float()).abs().max().item()
+print("megatron cp", "d_lp", d_cp2, "gn", gn_cp, gn_ref, flush=True)
+assert d_cp2 < 0.06 and abs(gn_cp - gn_ref) < 0.03 * gn_ref, (d_cp2, gn_cp, gn_ref)
+dcp = FSDPEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "use_symmetric_memory": False, "context_parallel_size": world, "dynamic_context_parallel": True,
+                                             "max_seqlen_per_dp_cp_rank": 64}, {"lr": 1e-3}, {})
+dcp.initialize()
+lp_d = dcp.infer_batch(data)["model_output"]["log_probs"]
+dcp.optimizer_zero_grad()
+dcp.forward_backward_batch(data, loss_fn)
+gn_d = dcp.optimizer_step()
+torch.cuda.synchronize()
+_ext.check_status("dynamic cp engine")
+d_d = (lp_d.float() - lp_ref.float()).abs().max().item()
+print("dynamic cp", "d_lp", d_d, "gn", gn_d, gn_ref, "groups", dcp.dcp_stats, flush=True)
+assert d_d < 0.06 and abs(gn_d - gn_ref) < 0.03 * gn_ref, (d_d, gn_d, gn_ref)
 dist.barrier()
 if rank == 0:
     print("SP_TP_OK", d_lp, rel, gn)

@@ -51,7 +51,7 @@ class RolloutReplica:
         addr_file = tempfile.mktemp(prefix="verl_b200_replica_")
         env = dict(os.environ)
         cmd = [sys.executable, "-m", "verl_b200.workers.rollout.replica", "--model", model, "--port", str(port), "--address-file", addr_file,
-               "--name", f"replica-{self.replica_rank}", *extra_args]
+               "--name", f"replica-{self.replica_rank}", "--parent-pid", str(os.getpid()), *extra_args]
         if device is not None:
             # the other GPUs stay visible: weight hand-off maps the trainer's export buffer through CUDA IPC
             cmd += ["--device", str(device)]
@@ -169,6 +169,7 @@ def main(argv=None):
     ap.add_argument("--num-blocks", type=int, default=None)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--device", type=int, default=0, help="CUDA device index of this replica")
+    ap.add_argument("--parent-pid", type=int, default=0, help="exit when this process is gone (a replica must not outlive the job that started it)")
     a = ap.parse_args(argv)
     dev = "cpu"
     if torch.cuda.is_available():
@@ -204,6 +205,8 @@ def main(argv=None):
     try:
         while not done[0]:
             time.sleep(0.2)
+            if a.parent_pid and os.getppid() != a.parent_pid:
+                break
     except KeyboardInterrupt:
         pass
     stop()
