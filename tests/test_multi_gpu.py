@@ -273,6 +273,7 @@ def test_fused_ulysses_and_tp_engine(tmp_path, world):
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
                         "--master-port", "29687", str(script)], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0 and "SP_TP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    print(r.stdout[-1500:])       # the measured differences, visible with -s
 
 
 Z3_WORKER = r"""
