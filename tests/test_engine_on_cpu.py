@@ -189,3 +189,25 @@ def test_two_gloo_ranks_match_single_rank(tmp_path):
     # Adam's first step is sign-like for near-zero gradients, so compare within one learning-rate quantum
     assert (eng.store.flat[:n] - two["flat"][:n]).abs().max() <= 2.1e-3
     assert ((eng.store.flat[:n] - two["flat"][:n]).abs() > 1e-6).float().mean() < 0.02
+
+
+def test_tiled_mlp_matches_the_dense_mlp_and_frees_activations():
+    """`model.tiled_mlp.enabled`: outputs, input gradients and weight gradients (accumulated into main_grad over the tiles) equal
+    the untiled run; only the MLP input is saved for backward."""
+    from verl_b200.models.transformer import _tile_bounds
+
+    assert _tile_bounds(10, 4) == [(0, 3), (3, 6), (6, 9), (9, 10)] and _tile_bounds(1100, 4) == [(0, 384), (384, 768), (768, 1100)]
+    res = {}
+    for tiled in (False, True):
+        mc = {"preset": "tiny-qwen2", "tiled_mlp": {"enabled": tiled, "num_shards": 3}}
+        eng = FSDPEngine(mc, {"seed": 1}, {"lr": 1e-3, "clip_grad": 1.0}, {})
+        eng.initialize()
+        assert eng.model.layers[0].mlp.tiled_shards == (3 if tiled else 0)
+        data = make_batch()
+        lp = eng.infer_batch(data)["model_output"]["log_probs"]
+        eng.optimizer_zero_grad()
+        eng.forward_backward_batch(data, loss_fn)
+        res[tiled] = (lp, eng.store.grad.clone(), eng.optimizer_step())
+    assert torch.allclose(res[True][0], res[False][0], atol=1e-6)
+    assert torch.allclose(res[True][1], res[False][1], atol=1e-6, rtol=1e-4)
+    assert abs(res[True][2] - res[False][2]) < 1e-5

@@ -130,13 +130,62 @@ class MLP(nn.Module):
         self.down_proj = nn.Parameter(torch.empty(cfg.hidden_size, cfg.intermediate_size, **kw))
         self.tp_group = None
 
+        self.tiled_shards = 0          # > 1: token-tiled execution with per-tile recomputation in backward (``_TiledMLP``)
+
     def forward(self, x):
+        if self.tiled_shards > 1 and not getattr(self, "tp_sp", False) and x.shape[0] >= 2 * self.tiled_shards:
+            return _TiledMLP.apply(x, self, self.tiled_shards, *[p for p in self.parameters() if p.requires_grad])
+        return self._dense(x)
+
+    def _dense(self, x):
         if getattr(self, "tp_sp", False):
             tpctx = getattr(self, "tp_ctx", None)
             h = ops.swiglu(allgather_linear(x, self.gate_up_proj, None, self.tp_group, tpctx))
             return linear_reduce_scatter(h, self.down_proj, self.tp_group, tpctx)
         y = _proj(self, "down_proj", ops.swiglu(_proj(self, "gate_up_proj", copy_to_tp(x, self.tp_group))))
         return reduce_from_tp(y, self.tp_group)
+
+
+class _TiledMLP(torch.autograd.Function):
+    """The MLP over ``shards`` slices of the token axis. Forward keeps nothing but the input: the [T, 2I] gate/up activations
+    and the [T, I] product exist for one slice at a time. Backward recomputes each slice and back-propagates through it; the
+    weight gradients of the slices add up in ``main_grad`` (fp32, inside the weight-gradient GEMM) or in ``.grad``.
+    Reference: ``verl/models/transformers/tiled_mlp.py:86-229`` (``TiledMLP`` with a gradient accumulator for FSDP); the
+    parameters are passed as inputs only so that autograd calls this node when they need gradients."""
+
+    @staticmethod
+    def forward(ctx, x, mlp, shards, *params):
+        ctx.mlp, ctx.shards = mlp, shards
+        ctx.save_for_backward(x)
+        bounds = _tile_bounds(x.shape[0], shards)
+        with torch.no_grad():
+            return torch.cat([mlp._dense(x[a:b]) for a, b in bounds], 0)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        mlp = ctx.mlp
+        params = [p for p in mlp.parameters() if p.requires_grad]
+        dx = torch.empty_like(x)
+        acc = [None] * len(params)
+        for a, b in _tile_bounds(x.shape[0], ctx.shards):
+            xs = x[a:b].detach().requires_grad_(True)
+            with torch.enable_grad():
+                ys = mlp._dense(xs)
+            grads = torch.autograd.grad(ys, [xs] + params, dy[a:b], allow_unused=True)
+            dx[a:b] = grads[0]
+            for i, g in enumerate(grads[1:]):       # None when the projection accumulated into main_grad itself
+                if g is not None:
+                    acc[i] = g if acc[i] is None else acc[i] + g
+        return (dx, None, None, *acc)
+
+
+def _tile_bounds(T: int, shards: int):
+    """Token slices of near-equal size, each a multiple of 128 rows where the length allows (full GEMM tiles)."""
+    per = -(-T // shards)
+    if T >= 256 * shards:
+        per = -(-per // 128) * 128
+    return [(a, min(T, a + per)) for a in range(0, T, per)]
 
 
 class MoE(nn.Module):

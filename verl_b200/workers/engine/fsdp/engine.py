@@ -226,6 +226,11 @@ class FSDPEngine(BaseEngine):
 
             load_hf_weights(self.model, os.path.expanduser(path), strict=not cfg.value_head)
         self.model.gradient_checkpointing = bool(cfg_get(self.model_config, "enable_gradient_checkpointing", False))
+        tiled = cfg_get(self.model_config, "tiled_mlp", None) if not isinstance(self.model_config, ModelConfig) else None
+        if tiled is not None and bool(cfg_get(tiled, "enabled", False)):
+            for layer in self.model.layers:
+                if hasattr(layer.mlp, "tiled_shards"):
+                    layer.mlp.tiled_shards = int(cfg_get(tiled, "num_shards", 4))
         lora_rank = int(cfg_get(self.model_config, "lora_rank", 0) or 0) if not isinstance(self.model_config, ModelConfig) else 0
         if lora_rank > 0 and not self.forward_only:
             from verl_b200.models.lora import apply_lora
