@@ -195,12 +195,12 @@ for mode in ("fused", "nccl", "context", "context_zigzag"):
 d_lp = (res["fused"][0] - res["nccl"][0]).abs().max().item()
 g_f, g_n = res["fused"][1], res["nccl"][1]
 rel = ((g_f - g_n).norm() / g_n.norm()).item()
-assert d_lp < 0.06 and rel < 0.05, (d_lp, rel)
+assert d_lp < 0.02 and rel < 0.02, (d_lp, rel)           # measured on 2 B200s: 0.009 / 0.007
 for mode in ("context", "context_zigzag"):
     d_cp = (res[mode][0] - res["nccl"][0]).abs().max().item()
     rel_cp = ((res[mode][1] - g_n).norm() / g_n.norm()).item()
     print(mode, "d_lp", d_cp, "rel grad", rel_cp, flush=True)
-    assert d_cp < 0.06 and rel_cp < 0.05, (mode, d_cp, rel_cp)
+    assert d_cp < 0.02 and rel_cp < 0.02, (mode, d_cp, rel_cp)      # measured: 0.0 / 0.002
 # ---- tensor-parallel engine on NCCL == single-GPU engine
 ref = FSDPEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "use_symmetric_memory": False, "fsdp_size": 1}, {"lr": 1e-3}, {})
 ref.initialize()
@@ -220,7 +220,7 @@ ref.forward_backward_batch(data, loss_fn)
 gn_ref = ref.optimizer_step()
 torch.cuda.synchronize()
 d = (lp_tp.float() - lp_ref.float()).abs().max().item()
-assert torch.isfinite(lp_tp).all() and d < 0.06, d
+assert torch.isfinite(lp_tp).all() and d < 0.02, d
 assert abs(gn - gn_ref) < 0.03 * gn_ref, (gn, gn_ref)
 exported = dict(tp.get_per_tensor_param()[0])
 exported_ref = dict(ref.get_per_tensor_param()[0])
@@ -243,7 +243,7 @@ torch.cuda.synchronize()
 _ext.check_status("cp engine")
 d_cp2 = (lp_cp.float() - lp_ref.float()).abs().max().item()
 print("megatron cp", "d_lp", d_cp2, "gn", gn_cp, gn_ref, flush=True)
-assert d_cp2 < 0.06 and abs(gn_cp - gn_ref) < 0.03 * gn_ref, (d_cp2, gn_cp, gn_ref)
+assert d_cp2 < 0.02 and abs(gn_cp - gn_ref) < 0.01 * gn_ref, (d_cp2, gn_cp, gn_ref)
 dcp = FSDPEngine(PRESETS["tiny-qwen2-gpu"], {"seed": 1, "use_symmetric_memory": False, "context_parallel_size": world, "dynamic_context_parallel": True,
                                              "max_seqlen_per_dp_cp_rank": 64}, {"lr": 1e-3}, {})
 dcp.initialize()
@@ -255,7 +255,7 @@ torch.cuda.synchronize()
 _ext.check_status("dynamic cp engine")
 d_d = (lp_d.float() - lp_ref.float()).abs().max().item()
 print("dynamic cp", "d_lp", d_d, "gn", gn_d, gn_ref, "groups", dcp.dcp_stats, flush=True)
-assert d_d < 0.06 and abs(gn_d - gn_ref) < 0.03 * gn_ref, (d_d, gn_d, gn_ref)
+assert d_d < 0.02 and abs(gn_d - gn_ref) < 0.01 * gn_ref, (d_d, gn_d, gn_ref)
 dist.barrier()
 if rank == 0:
     print("SP_TP_OK", d_lp, rel, gn)
