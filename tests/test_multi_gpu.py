@@ -367,14 +367,16 @@ cfg = ModelConfig(model_type="qwen3_moe", vocab_size=4096, hidden_size=512, inte
                   moe_intermediate_size=256, rope_theta=1e4, max_position_embeddings=4096)
 opt = {"lr": 1e-3, "clip_grad": 1.0, "weight_decay": 0.01}
 res = {}
-for mode in ("ep", "replicated"):
+for mode in ("ep", "ep_nccl", "replicated"):
+    # "ep": dispatch / combine inside the grouped GEMMs over peer memory; "ep_nccl": the all-to-all formulation; both against no EP
     ecfg = {"seed": 1, "use_symmetric_memory": False}
-    if mode == "ep":
-        ecfg.update({"expert_parallel_size": world, "zero3": True, "use_symmetric_memory": True})
+    if mode != "replicated":
+        ecfg.update({"expert_parallel_size": world, "zero3": True, "use_symmetric_memory": True, "fused_moe_dispatch": mode == "ep"})
     eng = EngineRegistry.new("language_model", "fsdp", model_config=cfg, engine_config=ecfg, optimizer_config=opt, checkpoint_config={})
     eng.initialize()
-    if mode == "ep":
+    if mode != "replicated":
         assert type(eng).__name__ == "Zero3Engine" and dict(eng.model.named_parameters())["layers.0.mlp.experts_down"].shape[0] == 4 // world
+        assert (eng._ep_ctx is not None) == (mode == "ep")
     data = make_batch(bs=8, P=70, R=90, vocab=4096).chunk(world)[rank]
     data.meta_info["micro_batch_size_per_gpu"] = 2
     lp = eng.infer_batch(data)["model_output"]["log_probs"]
@@ -384,14 +386,19 @@ for mode in ("ep", "replicated"):
     torch.cuda.synchronize()
     _ext.check_status(mode)
     res[mode] = (lp.clone(), gn, {k: v.detach().float().clone() for k, v in eng.get_per_tensor_param()[0]})
+    if mode == "ep":
+        assert eng._ep_ctx.calls >= 2 * 2 * 3          # two MoE layers, two micro-batches, (infer + train) passes at least
     del eng
-a, b = res["ep"], res["replicated"]
-d_lp = (a[0] - b[0]).abs().max().item()
-print("EP_DIAG", rank, d_lp, a[1], b[1], flush=True)
-assert d_lp < 0.08 and abs(a[1] - b[1]) < 0.05 * max(1.0, b[1]), (d_lp, a[1], b[1])
-assert a[2].keys() == b[2].keys()
-for k in b[2]:
-    assert a[2][k].shape == b[2][k].shape and (a[2][k] - b[2][k]).abs().mean().item() < 2e-3, k
+b = res["replicated"]
+for mode in ("ep", "ep_nccl"):
+    a = res[mode]
+    d_lp = (a[0] - b[0]).abs().max().item()
+    print("EP_DIAG", mode, rank, d_lp, a[1], b[1], flush=True)
+    assert d_lp < 0.08 and abs(a[1] - b[1]) < 0.05 * max(1.0, b[1]), (mode, d_lp, a[1], b[1])
+    assert a[2].keys() == b[2].keys()
+    for k in b[2]:
+        assert a[2][k].shape == b[2][k].shape and (a[2][k] - b[2][k]).abs().mean().item() < 2e-3, (mode, k)
+a = res["ep"]
 dist.barrier()
 if rank == 0:
     print("EP_OK", d_lp, a[1], b[1])

@@ -203,3 +203,74 @@ def test_ulysses_head_scatter_and_k_segmented_gather(o):
             o.gemm_kseg(_table(o_bufs), Kl, Tp, r * Tl, w_o, out, None, r, st, flags if st is not None else None, ep)
             assert _rel(out, ref[r * Tl:(r + 1) * Tl]) < 1e-2, (r, ep)
     _status_clean(o)
+
+
+@pytest.mark.parametrize("T0,T1", [(300, 300), (257, 90)])
+def test_moe_dispatch_and_combine_fused_into_the_grouped_gemms(o, T0, T1):
+    """Expert parallelism over two emulated ranks: the gate/up grouped GEMM fetches its rows from the "ranks" that hold the tokens,
+    the down-projection's epilogue stores weighted rows into the owners' slot buffers; the slot sums must equal a dense fp32
+    evaluation of the same routing. The transposed-weight variants (the two GEMMs of the backward pass) are checked the same way."""
+    from verl_b200.ops.moe import ep_row_tables
+
+    torch.manual_seed(6)
+    H, I, E, k = 512, 256, 8, 2
+    e_local = E // W
+    Ts = [T0, T1]
+    Tc = max(Ts)
+    xs = [torch.randn(Tc, H, device="cuda").bfloat16() for _ in range(W)]            # token buffers (rows >= T are never addressed)
+    gate_up = (0.05 * torch.randn(E, 2 * I, H, device="cuda")).bfloat16()
+    down = (0.05 * torch.randn(E, H, I, device="cuda")).bfloat16()
+    idx_all = torch.full((W, Tc, k), -1, dtype=torch.long, device="cuda")
+    w_all = torch.zeros(W, Tc, k, device="cuda")
+    for r in range(W):
+        idx_all[r, : Ts[r]] = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(Ts[r])])
+        w_all[r, : Ts[r]] = torch.rand(Ts[r], k, device="cuda") + 0.1
+    cbufs = [torch.full((k * Tc * H + 64,), 7.0, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    gbufs = [torch.full((k * Tc * H + 64,), 7.0, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    acts = []
+    for r in range(W):
+        row_src, row_dst, row_w, blk, rng = ep_row_tables(idx_all, w_all, r, e_local)
+        R = row_src.numel()
+        stage = torch.empty(R, H, device="cuda", dtype=torch.bfloat16)
+        flags = torch.empty(R // 128, device="cuda", dtype=torch.int32)
+        gu_l, dn_l = gate_up[r * e_local:(r + 1) * e_local].contiguous(), down[r * e_local:(r + 1) * e_local].contiguous()
+        h = o.gemm_grouped_dispatch(_table(xs), H, row_src, gu_l, blk, stage, flags, False)
+        # the staged operand is the gathered token rows (zeros on padding rows)
+        used = row_src >= 0
+        src_rank, src_tok = (row_src[used] >> 24).long(), (row_src[used] & 0xFFFFFF).long()
+        want_rows = torch.stack(xs)[src_rank, src_tok]
+        blk_used = (blk >= 0).repeat_interleave(128)
+        assert torch.equal(stage[used], want_rows) and torch.all(stage[blk_used & ~used] == 0)
+        e_of_row = blk.long().repeat_interleave(128)[used]
+        want_h = torch.einsum("rh,rnh->rn", want_rows.float(), gu_l.float()[e_of_row])
+        assert _rel(h[used], want_h) < 1e-2
+        a = o.swiglu_fwd(h)
+        o.gemm_grouped_combine(a, dn_l, blk, row_dst, row_w, _table(cbufs), H, False)
+        acts.append((a, row_src, row_dst, row_w, blk, used, e_of_row, dn_l, gu_l, h))
+        # backward-direction variants: input gradients through the transposed weights
+        da = o.gemm_grouped_dispatch(_table(xs), H, row_src, dn_l, blk, stage, flags, True)             # [R, I] = rows @ down[e]
+        want_da = torch.einsum("rh,rhi->ri", want_rows.float(), dn_l.float()[e_of_row])
+        assert _rel(da[used], want_da) < 1e-2
+        ones = (row_dst >= 0).float()
+        o.gemm_grouped_combine(h, gu_l, blk, row_dst, ones, _table(gbufs), H, True)                      # rows of h @ gate_up[e] -> owners
+    torch.cuda.synchronize()
+    for r in range(W):
+        T = Ts[r]
+        y = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+        o.slots_reduce(cbufs[r][: k * Tc * H], k, Tc * H, T, H, None, y)
+        x = xs[r][:T].float()
+        want = torch.zeros(T, H, device="cuda")
+        want_g = torch.zeros(T, H, device="cuda")
+        for j in range(k):
+            e = idx_all[r, :T, j]
+            hh = torch.einsum("th,tnh->tn", x, gate_up.float()[e])
+            hb = hh.bfloat16().float()
+            act = (torch.nn.functional.silu(hb[:, :I]) * hb[:, I:]).bfloat16().float()
+            want += w_all[r, :T, j, None] * torch.einsum("ti,thi->th", act, down.float()[e])
+            want_g += torch.einsum("tn,tnh->th", hb, gate_up.float()[e])
+        assert _rel(y, want) < 2e-2, r
+        g = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+        o.slots_reduce(gbufs[r][: k * Tc * H], k, Tc * H, T, H, None, g)
+        assert _rel(g, want_g) < 2e-2, r
+        assert torch.all(cbufs[r][k * Tc * H:] == 7.0) and torch.all(gbufs[r][k * Tc * H:] == 7.0)
+    _status_clean(o)

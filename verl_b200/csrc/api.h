@@ -100,6 +100,10 @@ int vb_slots_reduce_sig(const long* slot_ptrs, const void* sig, int rank, int wo
                         int cols, const void* residual, void* out, int ld_out, int* err_word, cudaStream_t st);
 int vb_gemm_grouped(const void* A, const void* B, void* C, const int* blk_expert, int R, int N, int K, int E, int lda, int ldc, int b_mn,
                     int* err_word, cudaStream_t stream);
+int vb_gemm_grouped_dispatch(const long* src_ptrs, int world, int ld_src, const int* row_src, const void* B, void* C, const int* blk_expert,
+                             int R, int N, int K, int E, int ldc, int b_mn, void* stage, int* stage_flags, int* err_word, cudaStream_t stream);
+int vb_gemm_grouped_combine(const void* A, const void* B, const int* blk_expert, const int* row_dst, const float* row_w, const long* out_ptrs,
+                            int world, int R, int N, int K, int E, int lda, int ld_out, int b_mn, int* err_word, cudaStream_t stream);
 int vb_gemm_grouped_wgrad(const void* dY, const void* X, void* dW, const void* expert_rng, int R, int M, int N, int E, int ld_dy, int ld_x,
                           int out_f32, int accumulate, int* err_word, cudaStream_t stream);
 int vb_ppo_loss(const float* lp, const float* old_lp, const float* ref_lp, const float* adv, const float* weight, const float* mask,

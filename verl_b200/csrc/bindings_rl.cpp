@@ -92,9 +92,51 @@ void gemm_grouped_wgrad(const Tensor& dy, const Tensor& x, const Tensor& expert_
                                  cur_stream()),
            "gemm_grouped_wgrad");
 }
+// Expert-parallel dispatch fused into the grouped GEMM. src_ptrs: CPU int64 [world] token buffers ([*, K] bf16, row stride ld_src)
+// reachable from this GPU; row_src int32 [R]: (rank << 24) | row, or -1 for padding rows; stage [R, K] bf16 receives the gathered
+// operand (kept for the backward pass), flags int32 [>= R / 128].
+Tensor gemm_grouped_dispatch(const Tensor& src_ptrs, int64_t ld_src, const Tensor& row_src, const Tensor& w, const Tensor& blk_expert, Tensor& stage,
+                             Tensor& flags, bool transposed) {
+  TORCH_CHECK(src_ptrs.scalar_type() == at::kLong && !src_ptrs.is_cuda(), "gemm_grouped_dispatch: pointer table must be a CPU int64 tensor");
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kBFloat16 && w.dim() == 3 && w.is_contiguous(), "gemm_grouped_dispatch: w must be contiguous [E, N, K]");
+  // transposed: w is [E, K, N] (the stored [E, out, in] weight read as the input-gradient operand)
+  const int R = row_src.numel(), E = w.size(0), N = transposed ? w.size(2) : w.size(1), K = transposed ? w.size(1) : w.size(2);
+  TORCH_CHECK(row_src.is_cuda() && row_src.scalar_type() == at::kInt && row_src.is_contiguous(), "gemm_grouped_dispatch: bad row table");
+  TORCH_CHECK(blk_expert.is_cuda() && blk_expert.scalar_type() == at::kInt && blk_expert.numel() * 128 == R, "gemm_grouped_dispatch: bad block table");
+  TORCH_CHECK(stage.is_cuda() && stage.scalar_type() == at::kBFloat16 && stage.is_contiguous() && stage.numel() >= (int64_t)R * K, "gemm_grouped_dispatch: stage too small");
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.numel() * 128 >= R, "gemm_grouped_dispatch: flags too small");
+  c10::cuda::CUDAGuard guard(w.device());
+  Tensor y = at::zeros({R, N}, w.options());
+  check_rc(vb_gemm_grouped_dispatch(src_ptrs.data_ptr<long>(), (int)src_ptrs.numel(), (int)ld_src, row_src.data_ptr<int>(), w.data_ptr(), y.data_ptr(),
+                                    blk_expert.data_ptr<int>(), R, N, K, E, N, transposed, stage.data_ptr(), flags.data_ptr<int>(),
+                                    vb_status_tensor(w.get_device()).data_ptr<int>(), cur_stream()),
+           "gemm_grouped_dispatch");
+  return y;
+}
+
+// Combine fused into the epilogue: row r of (x @ w[e]^T) * row_w[r] is stored as row (row_dst[r] & 0xFFFFFF) of rank (row_dst[r] >> 24)'s
+// [*, N] bf16 buffer out_ptrs[rank] (row stride ld_out).
+void gemm_grouped_combine(const Tensor& x, const Tensor& w, const Tensor& blk_expert, const Tensor& row_dst, const Tensor& row_w, const Tensor& out_ptrs,
+                          int64_t ld_out, bool transposed) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "gemm_grouped_combine: bad x");
+  TORCH_CHECK(w.scalar_type() == at::kBFloat16 && w.dim() == 3 && w.is_contiguous() && (transposed ? w.size(1) : w.size(2)) == x.size(1),
+              "gemm_grouped_combine: w must be contiguous [E, N, K] ([E, K, N] when transposed)");
+  const int R = x.size(0), K = x.size(1), E = w.size(0), N = transposed ? w.size(2) : w.size(1);
+  TORCH_CHECK(blk_expert.is_cuda() && blk_expert.scalar_type() == at::kInt && blk_expert.numel() * 128 == R, "gemm_grouped_combine: bad block table");
+  TORCH_CHECK(row_dst.is_cuda() && row_dst.scalar_type() == at::kInt && row_dst.numel() == R && row_w.is_cuda() && row_w.scalar_type() == at::kFloat &&
+                  row_w.numel() == R, "gemm_grouped_combine: bad row tables");
+  TORCH_CHECK(out_ptrs.scalar_type() == at::kLong && !out_ptrs.is_cuda(), "gemm_grouped_combine: pointer table must be a CPU int64 tensor");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(vb_gemm_grouped_combine(x.data_ptr(), w.data_ptr(), blk_expert.data_ptr<int>(), row_dst.data_ptr<int>(), row_w.data_ptr<float>(),
+                                   out_ptrs.data_ptr<long>(), (int)out_ptrs.numel(), R, N, K, E, (int)x.stride(0), (int)ld_out, transposed,
+                                   vb_status_tensor(x.get_device()).data_ptr<int>(), cur_stream()),
+           "gemm_grouped_combine");
+}
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
+  m.def("gemm_grouped_dispatch(Tensor src_ptrs, int ld_src, Tensor row_src, Tensor w, Tensor blk_expert, Tensor(a!) stage, Tensor(b!) flags, bool transposed=False) -> Tensor", &gemm_grouped_dispatch);
+  m.def("gemm_grouped_combine(Tensor x, Tensor w, Tensor blk_expert, Tensor row_dst, Tensor row_w, Tensor out_ptrs, int ld_out, bool transposed=False) -> ()", &gemm_grouped_combine);
   m.def("gemm_grouped(Tensor x, Tensor w, Tensor blk_expert, bool transposed) -> Tensor", &gemm_grouped);
   m.def("gemm_grouped_wgrad(Tensor dy, Tensor x, Tensor expert_rng, Tensor(a!) dw, bool accumulate) -> ()", &gemm_grouped_wgrad);
 }

@@ -75,6 +75,14 @@ struct DistArgs {
   int num_experts;
   const int* blk_expert;
   const int2* expert_rng;
+  // Expert-parallel dispatch fused into the grouped GEMM's A operand (seg_mode 4, with group_mode 1): row r of the expert-sorted,
+  // block-padded operand is row (row_src[r] & 0xFFFFFF) of rank (row_src[r] >> 24)'s token buffer seg_ptr[rank]; row_src[r] < 0 is
+  // a padding row (zeros). The copy warps gather the rows of a 128-row block into `stage` while earlier blocks are multiplied.
+  const int* row_src;
+  // Combine fused into the epilogue (EPI_PEER with row_dst): output row r, multiplied by row_w[r], becomes row
+  // (row_dst[r] & 0xFFFFFF) of rank (row_dst[r] >> 24)'s buffer peer_out[rank] (row stride ldc); row_dst[r] < 0: not stored.
+  const int* row_dst;
+  const float* row_w;
   void* stage;
   int* stage_flags;
   int stage_epoch;
@@ -256,6 +264,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               } else {
                 tma_load_2d(sa, &dist.seg[owner], k0, m0 % dist.seg_rows, &full_bar[s]);
               }
+            } else if (dist.seg_mode == 4) {
+              if (kb == kb0 && !stage_wait(dist.stage_flags + m0 / 128, dist.stage_epoch, abort_flag, err_word)) { ok = false; break; }
+              tma_load_2d(sa, &dist.stage_map, k0, m0, &full_bar[s]);
             } else if (dist.seg_mode == 3) {
               const int owner = k0 / dist.seg_rows;
               if (dist.stage != nullptr && owner != dist.rank) {
@@ -366,6 +377,50 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int et = threadIdx.x - 192;
       const bf16* const* srcs = reinterpret_cast<const bf16* const*>(dist.seg_ptr);
       bf16* stage = reinterpret_cast<bf16*>(dist.stage);
+      if (dist.seg_mode == 4) {
+        // token dispatch: every row of a used 128-row block is fetched from the rank that holds the token (own rows included:
+        // the operand must be contiguous for the tensor map). 16-row pieces are dealt round-robin over the CTAs, block by
+        // block in the order the tiles are scheduled, so early tiles find their rows first. Unused blocks are skipped by the
+        // producer as well, nothing waits for them.
+        const int vec_per_row = K / 8;
+        const int n_chunks = M / 128;
+        int mine = 0;
+        for (int c = 0; c < n_chunks; ++c) {
+          if (dist.blk_expert[c] < 0) continue;
+          for (int part = 0; part < STAGE_PARTS; ++part) {
+            if ((mine++ % gridDim.x) != blockIdx.x) continue;
+            const int row0 = c * 128 + part * 16;
+            const int total = 16 * vec_per_row;
+            for (int i0 = 0; i0 < total; i0 += CT * 8) {
+              uint4 v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int i = i0 + j * CT + et;
+                v[j] = make_uint4(0, 0, 0, 0);
+                if (i < total) {
+                  const int r = i / vec_per_row, x = i - r * vec_per_row;
+                  const int e = dist.row_src[row0 + r];
+                  if (e >= 0) v[j] = __ldcs(reinterpret_cast<const uint4*>(srcs[e >> 24] + (long)(e & 0xFFFFFF) * dist.ld_seg + x * 8));
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int i = i0 + j * CT + et;
+                if (i < total) {
+                  const int r = i / vec_per_row, x = i - r * vec_per_row;
+                  *reinterpret_cast<uint4*>(stage + (long)(row0 + r) * dist.ld_stage + x * 8) = v[j];
+                }
+              }
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
+            if (et == 0) {
+              asm volatile("fence.proxy.async;" ::: "memory");
+              asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(dist.stage_flags + c) : "memory");
+            }
+          }
+        }
+      } else {
       const bool by_k = dist.seg_mode == 3;
       const int cols = by_k ? dist.seg_rows : K;          // bf16 elements per copied row
       const int vec_per_row = cols / 8;
@@ -419,6 +474,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           asm volatile("fence.proxy.async;" ::: "memory");
           asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(dist.stage_flags + c) : "memory");
         }
+      }
       }
     }
     }
@@ -535,6 +591,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       } else if constexpr (EPI == EPI_PEER) {
+        if (dist.row_dst != nullptr) {
+          // expert outputs go straight to the rank and row of the token they belong to, scaled by the routing weight
+          const int e = row < M ? dist.row_dst[row] : -1;
+          const float w = e >= 0 ? dist.row_w[row] : 0.f;
+          bf16* drow = e >= 0 ? reinterpret_cast<bf16*>(dist.peer_out[e >> 24]) + (long)(e & 0xFFFFFF) * ldc : nullptr;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(taddr + c * 32, v);
+            tmem_ld_wait();
+            const int col0 = n0 + c * 32;
+            if (e >= 0 && col0 + 32 <= N) {
+              uint4 o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                o[j].x = pack_bf16x2(__uint_as_float(v[8 * j]) * w, __uint_as_float(v[8 * j + 1]) * w);
+                o[j].y = pack_bf16x2(__uint_as_float(v[8 * j + 2]) * w, __uint_as_float(v[8 * j + 3]) * w);
+                o[j].z = pack_bf16x2(__uint_as_float(v[8 * j + 4]) * w, __uint_as_float(v[8 * j + 5]) * w);
+                o[j].w = pack_bf16x2(__uint_as_float(v[8 * j + 6]) * w, __uint_as_float(v[8 * j + 7]) * w);
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(drow + col0)[j] = o[j];
+            }
+          }
+          tc_fence_before();
+          mbar_arrive(&tempty_bar[acc]);
+          continue;
+        }
         int r_lo = 0, r_hi = dist.world;
         long row_local = row;
         if (dist.sig_local != nullptr) {          // signalled all-reduce: partials stay local, the peers pull them
@@ -1205,6 +1289,98 @@ extern "C" int vb_gemm_grouped(const void* A, const void* B, void* C, const int*
   if ((R % BM) != 0 || (lda & 7) || (N & 7) || (K & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -4;
   return b_mn ? launch_grouped_fwd<true>(A, B, C, blk_expert, R, N, K, E, lda, ldc, err_word, stream)
               : launch_grouped_fwd<false>(A, B, C, blk_expert, R, N, K, E, lda, ldc, err_word, stream);
+}
+
+// Expert-parallel dispatch fused into the grouped GEMM: Y[R, N] = gather(X)[R, K] * W[e(row block)]^T where row r of the operand
+// is fetched by the kernel's copy warps from src_ptrs[row_src[r] >> 24] (that rank's [*, K] token buffer, row stride ld_src,
+// plain peer loads) into `stage` ([R, K] bf16, local) while the tensor cores work on blocks that have already arrived.
+// stage_flags: R / 128 ints, zeroed here. After the call `stage` holds the gathered operand (the backward pass reuses it).
+namespace vb {
+template <bool B_MN>
+static int launch_grouped_dispatch(const long* src_ptrs, int world, int ld_src, const int* row_src, const void* B, void* C, const int* blk_expert,
+                                   int R, int N, int K, int E, int ldc, void* stage, int* stage_flags, int* err_word, cudaStream_t stream) {
+  constexpr int BN = 256;
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  if (make_tmap_2d(&tmA, stage, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, K, K, BM, BK)) return -1;
+  int rc;
+  if (!B_MN) rc = make_tmap_3d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, E, (uint64_t)K * 2, (uint64_t)N * K * 2, BK, BN, 1);
+  else       rc = make_tmap_3d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, E, (uint64_t)N * 2, (uint64_t)N * K * 2, 64, BK, 1);
+  if (rc) return rc;
+  static bool attr_set = false;
+  auto kern = gemm_bf16_kernel<BN, false, B_MN, EPI_STORE, 8>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  if (cudaMemsetAsync(stage_flags, 0, sizeof(int) * (R / BM), stream) != cudaSuccess) return -13;
+  DistArgs d = {};
+  d.group_mode = 1; d.num_experts = E; d.blk_expert = blk_expert;
+  d.seg_mode = 4; d.row_src = row_src; d.ld_seg = ld_src; d.world = world;
+  for (int r = 0; r < world; ++r) d.seg_ptr[r] = reinterpret_cast<const void*>(src_ptrs[r]);
+  d.stage = stage; d.stage_flags = stage_flags; d.stage_epoch = 1; d.ld_stage = K;
+  d.stage_map = tmA;
+  const int units = (R / BM) * ((N + BN - 1) / BN);
+  const int grid = units < num_sms() ? units : num_sms();
+  const int num_kb = (K + BK - 1) / BK;
+  kern<<<grid, 192 + 32 * 8, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, nullptr, R, N, K, ldc, 0, err_word, LmHeadEpi{}, 1, num_kb, nullptr, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+template <bool B_MN>
+static int launch_grouped_combine(const void* A, const void* B, const int* blk_expert, const int* row_dst, const float* row_w, const long* out_ptrs,
+                                  int world, int R, int N, int K, int E, int lda, int ld_out, int* err_word, cudaStream_t stream) {
+  constexpr int BN = 256;
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, K, lda, BM, BK)) return -1;
+  int rc;
+  if (!B_MN) rc = make_tmap_3d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, E, (uint64_t)K * 2, (uint64_t)N * K * 2, BK, BN, 1);
+  else       rc = make_tmap_3d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, E, (uint64_t)N * 2, (uint64_t)N * K * 2, 64, BK, 1);
+  if (rc) return rc;
+  static bool attr_set = false;
+  auto kern = gemm_bf16_kernel<BN, false, B_MN, EPI_PEER>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  DistArgs d = {};
+  d.group_mode = 1; d.num_experts = E; d.blk_expert = blk_expert;
+  d.world = world; d.row_dst = row_dst; d.row_w = row_w;
+  for (int r = 0; r < world; ++r) d.peer_out[r] = reinterpret_cast<void*>(out_ptrs[r]);
+  const int units = (R / BM) * ((N + BN - 1) / BN);
+  const int grid = units < num_sms() ? units : num_sms();
+  const int num_kb = (K + BK - 1) / BK;
+  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, nullptr, nullptr, R, N, K, ld_out, 0, err_word, LmHeadEpi{}, 1, num_kb, nullptr, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+}  // namespace vb
+
+extern "C" int vb_gemm_grouped_dispatch(const long* src_ptrs, int world, int ld_src, const int* row_src, const void* B, void* C,
+                                        const int* blk_expert, int R, int N, int K, int E, int ldc, int b_mn, void* stage, int* stage_flags,
+                                        int* err_word, cudaStream_t stream) {
+  using namespace vb;
+  if (R <= 0) return 0;
+  if (world < 1 || world > MAX_TP || (R % BM) != 0 || (ld_src & 7) || (N & 7) || (K & 7) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(stage) & 15) || stage == nullptr || stage_flags == nullptr)
+    return -4;
+  return b_mn ? launch_grouped_dispatch<true>(src_ptrs, world, ld_src, row_src, B, C, blk_expert, R, N, K, E, ldc, stage, stage_flags, err_word, stream)
+              : launch_grouped_dispatch<false>(src_ptrs, world, ld_src, row_src, B, C, blk_expert, R, N, K, E, ldc, stage, stage_flags, err_word, stream);
+}
+
+// Combine fused into the grouped GEMM's epilogue: (A[R, K] * W[e(row block)]^T)[r] * row_w[r] is stored as row
+// (row_dst[r] & 0xFFFFFF) of out_ptrs[row_dst[r] >> 24] (row stride ld_out, plain peer stores); rows with row_dst < 0 are dropped.
+// The receivers sum their top-k slots afterwards (a barrier has to separate the two).
+extern "C" int vb_gemm_grouped_combine(const void* A, const void* B, const int* blk_expert, const int* row_dst, const float* row_w,
+                                       const long* out_ptrs, int world, int R, int N, int K, int E, int lda, int ld_out, int b_mn, int* err_word,
+                                       cudaStream_t stream) {
+  using namespace vb;
+  if (R <= 0) return 0;
+  if (world < 1 || world > MAX_TP || (R % BM) != 0 || (lda & 7) || (N % 32) != 0 || (K & 7) || (ld_out & 7) ||
+      (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -4;
+  return b_mn ? launch_grouped_combine<true>(A, B, blk_expert, row_dst, row_w, out_ptrs, world, R, N, K, E, lda, ld_out, err_word, stream)
+              : launch_grouped_combine<false>(A, B, blk_expert, row_dst, row_w, out_ptrs, world, R, N, K, E, lda, ld_out, err_word, stream);
 }
 
 // dW[e][M, N] (+)= dY[rows_e, M]^T * X[rows_e, N] for every expert; expert_rng[e] = (first 128-row block, end block).

@@ -202,6 +202,7 @@ class MoE(nn.Module):
         self.experts_gate_up = nn.Parameter(torch.empty(E, 2 * I, H, **kw))
         self.experts_down = nn.Parameter(torch.empty(E, H, I, **kw))
         self.ep_group = None
+        self.ep_ctx = None      # FusedEPContext: dispatch / combine run inside the grouped GEMMs over peer memory
         self.tp_group = None    # expert tensor parallelism: every expert's intermediate dimension is split
         self.last_topk: Optional[torch.Tensor] = None   # recorded routing (router replay R2)
         self.record_routing = False
@@ -210,7 +211,8 @@ class MoE(nn.Module):
         from verl_b200.ops.moe import moe_forward
 
         out, topk_idx = moe_forward(copy_to_tp(x, self.tp_group), self.router, self.experts_gate_up, self.experts_down,
-                                    self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, forced_topk=forced_topk, ep_group=self.ep_group)
+                                    self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, forced_topk=forced_topk, ep_group=self.ep_group,
+                                    ep_ctx=self.ep_ctx)
         if self.record_routing:
             self.last_topk = topk_idx.detach()
         return reduce_from_tp(out, self.tp_group)

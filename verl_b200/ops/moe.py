@@ -16,7 +16,7 @@ import torch.nn.functional as F
 
 from . import functional as Fn
 
-__all__ = ["route_topk", "moe_forward", "permute_tokens", "unpermute_tokens"]
+__all__ = ["route_topk", "moe_forward", "permute_tokens", "unpermute_tokens", "ep_row_tables", "FusedEPContext"]
 
 
 def route_topk(logits: torch.Tensor, top_k: int, norm_topk_prob: bool, forced_topk: Optional[torch.Tensor] = None):
@@ -149,13 +149,174 @@ class _AllToAllRows(torch.autograd.Function):
         return out, None, None, None
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# Expert parallelism with dispatch and combine fused into the grouped GEMMs (sm_100a, peers reachable over NVLink).
+#   dispatch: the gate/up grouped GEMM fetches every operand row from the rank that holds the token (copy warps gather 128-row
+#             blocks into local staging while the tensor cores multiply blocks that have arrived) — no all-to-all, no permuted copy;
+#   combine:  the down-projection grouped GEMM's epilogue multiplies each output row by its routing weight and stores it into the
+#             token owner's [top_k, T, H] slot buffer; the owner sums its k slots.
+# The backward pass uses the same two kernels in the other direction (gradient rows are gathered from the token owners by the
+# dispatch kernel fused with the down-projection's input-gradient GEMM; input gradients go back through the combine epilogue).
+# Reference: Megatron-Core's alltoall token dispatcher (verl/workers/engine/megatron/transformer_impl.py:266-267,338-339).
+def ep_row_tables(idx_all: torch.Tensor, w_all: torch.Tensor, rank: int, e_local: int):
+    """Routing of ALL ranks' tokens → the row tables of this rank's grouped GEMMs.
+    ``idx_all`` [W, Tc, k] expert ids (−1: no such token), ``w_all`` [W, Tc, k] routing weights. Rows are the (token, slot) pairs
+    routed to experts ``[rank·e_local, (rank+1)·e_local)``, sorted by expert, every expert padded to a multiple of 128 rows.
+    Returns ``row_src`` int32 [R] ((source rank << 24) | token, −1 padding), ``row_dst`` int32 [R] ((source rank << 24) | (slot·Tc +
+    token)), ``row_w`` fp32 [R], ``blk_expert`` int32 [R/128], ``expert_rng`` int32 [e_local, 2]."""
+    W, Tc, k = idx_all.shape
+    lo = rank * e_local
+    flat = idx_all.reshape(-1)
+    sel = ((flat >= lo) & (flat < lo + e_local)).nonzero(as_tuple=True)[0]
+    le = flat.index_select(0, sel) - lo
+    order = torch.argsort(le, stable=True)
+    sel = sel.index_select(0, order)
+    counts = torch.bincount(le, minlength=e_local)
+    n = int(sel.numel())
+    dest, R, blk_expert, rng = padded_layout(counts, n)
+    tok_flat = sel // k
+    src, token, slot = tok_flat // Tc, tok_flat % Tc, sel % k
+    dev = idx_all.device
+    row_src = torch.full((R,), -1, dtype=torch.int32, device=dev)
+    row_dst = torch.full((R,), -1, dtype=torch.int32, device=dev)
+    row_w = torch.zeros(R, dtype=torch.float32, device=dev)
+    row_src[dest] = ((src << 24) | token).to(torch.int32)
+    row_dst[dest] = ((src << 24) | (slot * Tc + token)).to(torch.int32)
+    row_w[dest] = w_all.reshape(-1).index_select(0, sel).float()
+    return row_src, row_dst, row_w, blk_expert, rng
+
+
+class FusedEPContext:
+    """Symmetric buffers of one expert-parallel group: ``xbuf`` [max_tokens, H] holds this rank's tokens (forward) or output
+    gradients (backward) for the peers to fetch, ``cbuf`` [top_k · max_tokens, H] receives the expert outputs (or input gradients)
+    of this rank's tokens, one slot per chosen expert."""
+
+    def __init__(self, group, host_group, max_tokens: int, hidden: int, top_k: int):
+        from verl_b200.parallel.symm_mem import SymmetricBuffer
+
+        from . import _ext
+
+        self.group, self.ops = group, _ext.ops()
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.max_tokens, self.hidden, self.top_k = max_tokens, hidden, top_k
+        self.xbuf = SymmetricBuffer(max_tokens * hidden * 2, group, host_group)
+        self.cbuf = SymmetricBuffer(top_k * max_tokens * hidden * 2, group, host_group)
+        self.calls = 0
+
+    def publish(self, x: torch.Tensor) -> None:
+        """Copy ``x`` [T, H] into the symmetric token buffer and wait until every rank has done so."""
+        self.xbuf.tensor(torch.bfloat16, x.numel()).view_as(x).copy_(x)
+        self.xbuf.barrier()
+
+    def collect(self, T: int, Tc: int) -> torch.Tensor:
+        """After every rank's combine GEMM: sum this rank's top_k slots → [T, H]."""
+        self.cbuf.barrier()
+        out = torch.empty(T, self.hidden, dtype=torch.bfloat16, device=torch.device("cuda", torch.cuda.current_device()))
+        self.ops.slots_reduce(self.cbuf.tensor(torch.bfloat16, self.top_k * Tc * self.hidden), self.top_k, Tc * self.hidden, T, self.hidden, None, out)
+        return out
+
+
+class _FusedEPMoE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, idx, gate_up, down, fctx: FusedEPContext):
+        o = fctx.ops
+        T, H = x.shape
+        k = idx.shape[1]
+        W, rank = fctx.world, fctx.rank
+        e_local = gate_up.shape[0]
+        dev = x.device
+        # routing of all ranks (small): token counts differ between ranks, so pad to the largest
+        tc = torch.tensor([T], dtype=torch.int64, device=dev)
+        dist.all_reduce(tc, op=dist.ReduceOp.MAX, group=fctx.group)
+        Tc = int(tc.item())
+        assert Tc <= fctx.max_tokens, f"{Tc} tokens exceed the expert-parallel buffers ({fctx.max_tokens})"
+        idx_pad = torch.full((Tc, k), -1, dtype=torch.int32, device=dev)
+        idx_pad[:T] = idx.to(torch.int32)
+        w_pad = torch.zeros(Tc, k, dtype=torch.float32, device=dev)
+        w_pad[:T] = w.detach().float()
+        idx_all = torch.empty(W, Tc, k, dtype=torch.int32, device=dev)
+        w_all = torch.empty(W, Tc, k, dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(idx_all, idx_pad, group=fctx.group)
+        dist.all_gather_into_tensor(w_all, w_pad, group=fctx.group)
+        row_src, row_dst, row_w, blk_expert, rng = ep_row_tables(idx_all.long(), w_all, rank, e_local)
+        R = row_src.numel()
+        fctx.publish(x.detach().contiguous())
+        xg = torch.empty(R, H, dtype=torch.bfloat16, device=dev)          # the gathered operand, written by the kernel
+        flags = torch.empty(R // GROUP_BLOCK, dtype=torch.int32, device=dev)
+        h = o.gemm_grouped_dispatch(fctx.xbuf.table(), H, row_src, gate_up, blk_expert, xg, flags, False)
+        a = o.swiglu_fwd(h)
+        o.gemm_grouped_combine(a, down, blk_expert, row_dst, row_w, fctx.cbuf.table(), H, False)
+        y = fctx.collect(T, Tc)
+        fctx.calls += 1
+        ctx.save_for_backward(xg, h, a, gate_up, down, row_src, row_dst, row_w, blk_expert, rng)
+        ctx.fctx, ctx.dims = fctx, (T, Tc, k)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xg, h, a, gate_up, down, row_src, row_dst, row_w, blk_expert, rng = ctx.saved_tensors
+        fctx = ctx.fctx
+        o = fctx.ops
+        T, Tc, k = ctx.dims
+        H = dy.shape[1]
+        R = row_src.numel()
+        dev = dy.device
+        # gradient rows of this rank's experts' outputs live with the token owners: fetch them fused with d(act) = dy_rows @ W_down
+        fctx.publish(dy.contiguous())
+        dyg = torch.empty(R, H, dtype=torch.bfloat16, device=dev)
+        flags = torch.empty(R // GROUP_BLOCK, dtype=torch.int32, device=dev)
+        da = o.gemm_grouped_dispatch(fctx.xbuf.table(), H, row_src, down, blk_expert, dyg, flags, True)      # [R, I], not yet weighted
+        dw_rows = (da.float() * a.float()).sum(-1)                           # d(loss)/d(routing weight) of every row
+        wcol = row_w[:, None]
+        da = (da.float() * wcol).to(torch.bfloat16)
+        dh = o.swiglu_bwd(h, da)
+        dyw = (dyg.float() * wcol).to(torch.bfloat16)
+        d_down = d_gate_up = None
+        for wt, dy_op, x_op, which in ((down, dyw, a, "down"), (gate_up, dh, xg, "gate_up")):
+            mg = getattr(wt, "main_grad", None)
+            if mg is not None:
+                o.gemm_grouped_wgrad(dy_op, x_op, rng, mg, True)
+            else:
+                g = torch.zeros_like(wt)
+                o.gemm_grouped_wgrad(dy_op, x_op, rng, g, False)
+                if which == "down":
+                    d_down = g
+                else:
+                    d_gate_up = g
+        # input gradients travel back to the token owners through the combine epilogue (weight 1), k slots per token
+        ones = (row_dst >= 0).float()
+        o.gemm_grouped_combine(dh, gate_up, blk_expert, row_dst, ones, fctx.cbuf.table(), H, True)
+        dx = fctx.collect(T, Tc)
+        # routing-weight gradients: a few floats per row, gathered by everyone and picked by the owner
+        rc = torch.tensor([R], dtype=torch.int64, device=dev)
+        dist.all_reduce(rc, op=dist.ReduceOp.MAX, group=fctx.group)
+        Rc = int(rc.item())
+        code_l = torch.full((Rc,), -1, dtype=torch.int32, device=dev)
+        code_l[:R] = row_dst
+        val_l = torch.zeros(Rc, dtype=torch.float32, device=dev)
+        val_l[:R] = dw_rows
+        code = torch.empty(fctx.world * Rc, dtype=torch.int32, device=dev)
+        val = torch.empty(fctx.world * Rc, dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(code, code_l, group=fctx.group)
+        dist.all_gather_into_tensor(val, val_l, group=fctx.group)
+        code = code.long()
+        mine = (code >= 0) & ((code >> 24) == fctx.rank)
+        dwk = torch.zeros(k * Tc, dtype=torch.float32, device=dev)
+        dwk[(code[mine] & 0xFFFFFF)] = val[mine]
+        dw = dwk.view(k, Tc).t()[:T].contiguous()
+        return dx, dw, None, d_gate_up, d_down, None
+
+
 def moe_forward(x: torch.Tensor, router_w: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, top_k: int,
-                norm_topk_prob: bool = True, forced_topk: Optional[torch.Tensor] = None, ep_group=None):
-    """x [T, H]; router_w [E, H]; gate_up [E_local, 2I, H]; down [E_local, H, I]. Returns (y [T, H], topk_idx [T, k])."""
+                norm_topk_prob: bool = True, forced_topk: Optional[torch.Tensor] = None, ep_group=None, ep_ctx: Optional[FusedEPContext] = None):
+    """x [T, H]; router_w [E, H]; gate_up [E_local, 2I, H]; down [E_local, H, I]. Returns (y [T, H], topk_idx [T, k]).
+    With ``ep_ctx`` (and bf16 CUDA tensors) the expert-parallel exchange runs inside the grouped GEMMs instead of as all-to-alls."""
     T = x.shape[0]
     E = router_w.shape[0]
     logits = F.linear(x, router_w)
     w, idx, _ = route_topk(logits, top_k, norm_topk_prob, forced_topk)
+    if ep_ctx is not None and Fn.use_native(x) and x.shape[1] % 128 == 0 and gate_up.shape[1] % 256 == 0:
+        return _FusedEPMoE.apply(x, w, idx, gate_up, down, ep_ctx), idx
     xp, order, counts = permute_tokens(x, idx, E)
     if ep_group is None or dist.get_world_size(ep_group) == 1:
         yp = _experts_local(xp, counts, gate_up, down)

@@ -231,9 +231,20 @@ class Zero3Engine(FSDPEngine):
             full = [named[n]._zero3_full_shape for n in sharded]
             gctx = _GatherCtx(max(f[0] * f[1] for f in full), self.device)
         if self._ep:
+            ep_ctx = None
+            if (symm is not None and self.cfg.is_moe and self.world <= 8 and bool(cfg_get(self.engine_config, "fused_moe_dispatch", True))
+                    and self.cfg.hidden_size % 128 == 0 and (2 * self.cfg.moe_intermediate_size) % 256 == 0):
+                # dispatch and combine inside the grouped GEMMs: one token buffer + one slot buffer shared by all layers
+                from verl_b200.ops.moe import FusedEPContext
+                from verl_b200.single_controller.spmd import init_spmd_process_group
+
+                max_tok = int(cfg_get(self.engine_config, "moe_max_tokens", 16384))
+                ep_ctx = FusedEPContext(self.shard_group, init_spmd_process_group(), max_tok, self.cfg.hidden_size, self.cfg.num_experts_per_tok)
+            self._ep_ctx = ep_ctx
             for layer in self.model.layers:
                 if hasattr(layer.mlp, "ep_group"):
                     layer.mlp.ep_group = self.shard_group
+                    layer.mlp.ep_ctx = ep_ctx
         for n, p, off in zip(s.names, s.params, s.offsets):
             if n in self._zero3_rows and p.dim() == 2:
                 p._zero3 = Zero3Shard(self.shard_group, self._zero3_rows[n], p.shape[1], symm, off * 2, gctx)
