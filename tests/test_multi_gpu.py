@@ -387,7 +387,7 @@ for mode in ("ep", "ep_nccl", "replicated"):
     _ext.check_status(mode)
     res[mode] = (lp.clone(), gn, {k: v.detach().float().clone() for k, v in eng.get_per_tensor_param()[0]})
     if mode == "ep":
-        assert eng._ep_ctx.calls >= 2 * 2 * 3          # two MoE layers, two micro-batches, (infer + train) passes at least
+        assert eng._ep_ctx.calls >= 8                  # two MoE layers x two micro-batches x (inference + training forward)
     del eng
 b = res["replicated"]
 for mode in ("ep", "ep_nccl"):
