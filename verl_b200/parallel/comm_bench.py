@@ -66,12 +66,53 @@ def report(rank, name, ms_fused, ms_base, flops, link_bytes):
               f"NCCL+GEMM {ms_base * 1e3:.0f} us ({roof / ms_base:.2f}) | speed-up {ms_base / ms_fused:.2f}x", flush=True)
 
 
+def bench_moe(a, rank, world, host, timer):
+    """One expert-parallel MoE layer forward and forward+backward: dispatch / combine inside the grouped GEMMs against the
+    all-to-all formulation (NCCL all-to-all + the same grouped GEMMs). ``--tokens`` tokens per rank."""
+    from verl_b200.ops.moe import FusedEPContext, moe_forward
+
+    dev = torch.device("cuda")
+    T, H, I, E, k = a.tokens, a.moe_hidden, a.moe_ffn, a.experts, a.top_k
+    el = E // world
+    torch.manual_seed(rank)
+    x = (0.5 * torch.randn(T, H, device=dev)).bfloat16().requires_grad_(True)
+    torch.manual_seed(0)
+    router = (0.02 * torch.randn(E, H, device=dev)).bfloat16().requires_grad_(True)
+    gu = (0.02 * torch.randn(E, 2 * I, H, device=dev)).bfloat16()[rank * el:(rank + 1) * el].contiguous().requires_grad_(True)
+    dn = (0.02 * torch.randn(E, H, I, device=dev)).bfloat16()[rank * el:(rank + 1) * el].contiguous().requires_grad_(True)
+    ctx = FusedEPContext(dist.group.WORLD, host, T, H, k)
+    g = torch.randn(T, H, device=dev).bfloat16()
+
+    def run(ep_ctx, backward):
+        y, _ = moe_forward(x, router, gu, dn, k, True, ep_group=dist.group.WORLD, ep_ctx=ep_ctx)
+        if backward:
+            torch.autograd.grad(y, (x, router, gu, dn), g)
+        return y
+
+    with torch.no_grad():
+        y_f, y_b = run(ctx, False).float(), run(None, False).float()
+    err = ((y_f - y_b).abs().max() / y_b.abs().max()).item()
+    # rows that leave the rank: (W-1)/W of T*k rows of H bf16, once for dispatch and once for combine
+    link = 2.0 * T * k * H * 2 * (world - 1) / world
+    flops = 2.0 * T * k * H * 3 * I
+    with torch.no_grad():
+        ms_f, ms_b = timer(lambda: run(ctx, False)), timer(lambda: run(None, False))
+    report(rank, f"MoE layer forward, EP={world}, {T} tokens/rank, E={E} top-{k}, H={H} I={I} (max rel diff {err:.1e})", ms_f, ms_b, flops, link)
+    ms_f, ms_b = timer(lambda: run(ctx, True)), timer(lambda: run(None, True))
+    report(rank, "MoE layer forward + backward, same shapes", ms_f, ms_b, 3 * flops, 2 * link)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--hidden", type=int, default=3584)
     ap.add_argument("--ffn", type=int, default=18944)
     ap.add_argument("--params-m", type=int, default=512, help="millions of parameters for the optimizer-step paths")
+    ap.add_argument("--only", default="", help="'moe': only the expert-parallel MoE layer (Qwen3-30B-A3B shapes)")
+    ap.add_argument("--experts", type=int, default=128)
+    ap.add_argument("--top-k", dest="top_k", type=int, default=8)
+    ap.add_argument("--moe-hidden", dest="moe_hidden", type=int, default=2048)
+    ap.add_argument("--moe-ffn", dest="moe_ffn", type=int, default=768)
     a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -88,6 +129,11 @@ def main():
     T, H, F = a.tokens, a.hidden, a.ffn
     torch.manual_seed(0)
     W = world
+    if a.only == "moe":
+        bench_moe(a, rank, world, host, timer)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
 
     # ---- 1. sharded optimizer step: reduce-scatter(+scale, +sum g^2) and AdamW(+all-gather)
     n = a.params_m * 1_000_000 // (W * 1024) * (W * 1024)
