@@ -137,6 +137,78 @@ __global__ void grpo_advantage_kernel(const float* __restrict__ scores, const in
   }
 }
 
+
+// ---------------------------------------------------------------- GAE (generalised advantage estimation)
+// One thread per trajectory walks its response window backwards; masked positions carry the running state through
+// (reference semantics: verl/trainer/ppo/core_algos.py compute_gae_advantage_return). Also accumulates the masked sum and sum of
+// squares of the advantages (stats[0..2] = sum, sum of squares, count) for the whitening pass.
+__global__ void gae_kernel(const float* __restrict__ rewards, const float* __restrict__ values, const float* __restrict__ mask, int B, int R,
+                           float gamma, float lam, float* __restrict__ adv, float* __restrict__ ret, float* __restrict__ stats) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  float s = 0.f, s2 = 0.f, n = 0.f;
+  if (b < B) {
+    const long o = (long)b * R;
+    float nextv = 0.f, last = 0.f;
+    for (int t = R - 1; t >= 0; --t) {
+      const float v = values[o + t], m = mask[o + t];
+      const float delta = rewards[o + t] + gamma * nextv - v;
+      const float cand = delta + gamma * lam * last;
+      nextv = v * m + (1.f - m) * nextv;
+      last = cand * m + (1.f - m) * last;
+      adv[o + t] = last;
+      ret[o + t] = last + v;
+      s += last * m;
+      s2 += last * last * m;
+      n += m;
+    }
+  }
+  s = warp_sum(s); s2 = warp_sum(s2); n = warp_sum(n);
+  if ((threadIdx.x & 31) == 0) {
+    atomicAdd(stats, s);
+    atomicAdd(stats + 1, s2);
+    atomicAdd(stats + 2, n);
+  }
+}
+
+// (x - mean) * rsqrt(var_unbiased + 1e-8) with the masked moments of stats (two-pass variance from the raw moments in fp32
+// would cancel badly for large means, so the second moment is recentred here: var = E[x^2] - mean^2 is only used when the
+// caller passes centred data; for GAE advantages the mean is small against the spread).
+__global__ void whiten_kernel(float* __restrict__ x, long n, const float* __restrict__ stats) {
+  const float cnt = stats[2];
+  const float mean = stats[0] / fmaxf(cnt, 1.f);
+  float var = stats[1] / fmaxf(cnt, 1.f) - mean * mean;
+  var = fmaxf(var, 0.f) * (cnt > 1.f ? cnt / (cnt - 1.f) : 1.f);
+  const float r = rsqrtf(var + 1e-8f);
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) x[i] = (x[i] - mean) * r;
+}
+
+// ---------------------------------------------------------------- clipped value loss (forward value, gradient and clip fraction in one pass)
+// per token: l = 0.5 * max((v - R)^2, (clip(v, v_old - c, v_old + c) - R)^2) * weight; grad = dl/dv; stats[0] = weighted sum,
+// stats[1] = number of masked tokens where the clipped branch is the larger one, stats[2] = masked tokens.
+__global__ void __launch_bounds__(256) value_loss_kernel(const float* __restrict__ v, const float* __restrict__ v_old, const float* __restrict__ ret,
+                                                         const float* __restrict__ weight, const float* __restrict__ mask, long n, float clip,
+                                                         float* __restrict__ grad, float* __restrict__ stats) {
+  float loss = 0.f, nclip = 0.f, ntok = 0.f;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const float x = v[i], o = v_old[i], r = ret[i], w = weight[i], m = mask[i];
+    const float c = fminf(fmaxf(x, o - clip), o + clip);
+    const float l1 = (x - r) * (x - r), l2 = (c - r) * (c - r);
+    const bool use2 = l2 > l1;
+    loss += 0.5f * (use2 ? l2 : l1) * w;
+    // the clipped branch has a gradient only where the clip is inactive (c == x)
+    const float g = use2 ? ((c == x) ? (c - r) : 0.f) : (x - r);
+    grad[i] = g * w;
+    nclip += use2 ? m : 0.f;
+    ntok += m;
+  }
+  loss = warp_sum(loss); nclip = warp_sum(nclip); ntok = warp_sum(ntok);
+  if ((threadIdx.x & 31) == 0) {
+    atomicAdd(stats, loss);
+    atomicAdd(stats + 1, nclip);
+    atomicAdd(stats + 2, ntok);
+  }
+}
+
 }  // namespace vb
 
 using namespace vb;
@@ -167,6 +239,30 @@ int vb_grpo_advantage(const float* scores, const int* group, int B, int G, const
   long blocks = (n + 255) / 256;
   if (blocks > 148 * 4) blocks = 148 * 4;
   grpo_advantage_kernel<<<(int)blocks, 256, 0, st>>>(scores, group, mean, stdv, mask, B, R, eps, norm_by_std, adv);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// adv / ret [B, R]; stats[3] zeroed by the caller; whiten != 0 normalises adv in place with its masked moments.
+int vb_gae(const float* rewards, const float* values, const float* mask, int B, int R, float gamma, float lam, int whiten, float* adv, float* ret,
+           float* stats, cudaStream_t st) {
+  if (B <= 0 || R <= 0) return 0;
+  gae_kernel<<<(B + 127) / 128, 128, 0, st>>>(rewards, values, mask, B, R, gamma, lam, adv, ret, stats);
+  if (whiten) {
+    long n = (long)B * R;
+    long blocks = (n + 255) / 256;
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    whiten_kernel<<<(int)blocks, 256, 0, st>>>(adv, n, stats);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// stats[3] zeroed by the caller.
+int vb_value_loss(const float* v, const float* v_old, const float* ret, const float* weight, const float* mask, long n, float clip, float* grad,
+                  float* stats, cudaStream_t st) {
+  if (n <= 0) return 0;
+  long blocks = (n + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  value_loss_kernel<<<(int)blocks, 256, 0, st>>>(v, v_old, ret, weight, mask, n, clip, grad, stats);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
