@@ -109,6 +109,10 @@ int vb_gemm_grouped_wgrad(const void* dY, const void* X, void* dW, const void* e
 int vb_ppo_loss(const float* lp, const float* old_lp, const float* ref_lp, const float* adv, const float* weight, const float* mask,
                 const float* is_w, long n, float clip_lo, float clip_hi, float clip_c, int kl_type, float kl_coef, float* grad,
                 float* loss_out, float* stats, cudaStream_t st);
+int vb_gae(const float* rewards, const float* values, const float* mask, int B, int R, float gamma, float lam, int whiten, float* adv, float* ret,
+           float* stats, cudaStream_t st);
+int vb_value_loss(const float* v, const float* v_old, const float* ret, const float* weight, const float* mask, long n, float clip, float* grad,
+                  float* stats, cudaStream_t st);
 int vb_grpo_advantage(const float* scores, const int* group, int B, int G, const float* mask, int R, float eps, int norm_by_std,
                       float* mean, float* stdv, float* adv, cudaStream_t st);
 int vb_reshard_quant(const long* src_ptrs, int world, int rows_per_rank, long ld_src, int row_begin, void* y, long ldy, float* scale,

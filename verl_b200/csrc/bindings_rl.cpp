@@ -53,9 +53,39 @@ Tensor grpo_advantage(const Tensor& scores, const Tensor& group, int64_t G, cons
            "grpo_advantage");
   return adv;
 }
+
+// rewards / values / mask [B, R] fp32 -> (advantages, returns); whiten: advantages normalised with their masked mean / unbiased variance
+std::tuple<Tensor, Tensor> gae(const Tensor& rewards, const Tensor& values, const Tensor& mask, double gamma, double lam, bool whiten) {
+  TORCH_CHECK(rewards.is_cuda() && rewards.dim() == 2, "gae: rewards must be a CUDA [B, R] tensor");
+  const int64_t n = rewards.numel();
+  check_f32(rewards, n, "rewards"); check_f32(values, n, "values"); check_f32(mask, n, "mask");
+  c10::cuda::CUDAGuard guard(rewards.device());
+  Tensor adv = at::empty_like(rewards), ret = at::empty_like(rewards);
+  Tensor stats = at::zeros({3}, rewards.options());
+  check_rc(vb_gae(rewards.data_ptr<float>(), values.data_ptr<float>(), mask.data_ptr<float>(), (int)rewards.size(0), (int)rewards.size(1), (float)gamma,
+                  (float)lam, whiten, adv.data_ptr<float>(), ret.data_ptr<float>(), stats.data_ptr<float>(), cur_stream()),
+           "gae");
+  return {adv, ret};
+}
+
+// -> (grad wrt vpreds, stats [3] = weighted loss sum, clipped tokens, masked tokens)
+std::tuple<Tensor, Tensor> value_loss(const Tensor& vpreds, const Tensor& values, const Tensor& returns, const Tensor& weight, const Tensor& mask,
+                                      double clip) {
+  const int64_t n = vpreds.numel();
+  check_f32(vpreds, n, "vpreds"); check_f32(values, n, "values"); check_f32(returns, n, "returns"); check_f32(weight, n, "weight"); check_f32(mask, n, "mask");
+  c10::cuda::CUDAGuard guard(vpreds.device());
+  Tensor grad = at::empty_like(vpreds);
+  Tensor stats = at::zeros({3}, vpreds.options());
+  check_rc(vb_value_loss(vpreds.data_ptr<float>(), values.data_ptr<float>(), returns.data_ptr<float>(), weight.data_ptr<float>(), mask.data_ptr<float>(), n,
+                         (float)clip, grad.data_ptr<float>(), stats.data_ptr<float>(), cur_stream()),
+           "value_loss");
+  return {grad, stats};
+}
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
+  m.def("gae(Tensor rewards, Tensor values, Tensor mask, float gamma, float lam, bool whiten) -> (Tensor, Tensor)", &gae);
+  m.def("value_loss(Tensor vpreds, Tensor values, Tensor returns, Tensor weight, Tensor mask, float clip) -> (Tensor, Tensor)", &value_loss);
   m.def("ppo_loss(Tensor lp, Tensor old_lp, Tensor? ref_lp, Tensor adv, Tensor weight, Tensor mask, Tensor? is_w, float clip_lo, float clip_hi, float clip_c, int kl_type, float kl_coef) -> (Tensor, Tensor, Tensor)", &ppo_loss);
   m.def("grpo_advantage(Tensor scores, Tensor group, int G, Tensor mask, float eps, bool norm_by_std) -> Tensor", &grpo_advantage);
 }

@@ -11,7 +11,7 @@ import torch
 
 from . import _ext
 
-__all__ = ["agg_weights", "fused_ppo_loss", "fused_ppo_available", "grpo_advantage", "KL_TYPES"]
+__all__ = ["gae_advantage", "fused_value_loss", "agg_weights", "fused_ppo_loss", "fused_ppo_available", "grpo_advantage", "KL_TYPES"]
 
 KL_TYPES = {None: 0, "kl": 1, "k1": 1, "abs": 2, "mse": 3, "k2": 3, "low_var_kl": 4, "k3": 4}
 
@@ -81,3 +81,33 @@ def grpo_advantage(scores: torch.Tensor, group_index: torch.Tensor, response_mas
     if norm_by_std:
         a = a / (std[group_index.long()] + eps)
     return a[:, None] * response_mask.float()
+
+
+def gae_advantage(token_level_rewards: torch.Tensor, values: torch.Tensor, response_mask: torch.Tensor, gamma: float, lam: float,
+                  whiten: bool = True):
+    """GAE over the response window in one kernel (one thread per trajectory walks backwards; masked positions carry the state
+    through), optionally followed by the masked whitening of the advantages. → (advantages, returns), both fp32 [B, R]."""
+    f = lambda t: t.detach().float().contiguous()          # noqa: E731
+    return _ext.ops().gae(f(token_level_rewards), f(values), f(response_mask), float(gamma), float(lam), bool(whiten))
+
+
+class _FusedValueLoss(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, vpreds, values, returns, weight, mask, clip):
+        f = lambda t: t.detach().float().contiguous()      # noqa: E731
+        grad, stats = _ext.ops().value_loss(f(vpreds), f(values), f(returns), f(weight), f(mask), float(clip))
+        ctx.save_for_backward(grad)
+        ctx.v_dtype = vpreds.dtype
+        ctx.mark_non_differentiable(stats)
+        return stats[0].clone(), stats
+
+    @staticmethod
+    def backward(ctx, g_loss, _g_stats):
+        (grad,) = ctx.saved_tensors
+        return (grad * g_loss).to(ctx.v_dtype), None, None, None, None, None
+
+
+def fused_value_loss(vpreds, values, returns, response_mask, weights, cliprange_value: float):
+    """→ (0.5 · Σ w · max((v − R)², (clip(v, v_old ± ε) − R)²) with gradient to ``vpreds``, clipped fraction)."""
+    loss, stats = _FusedValueLoss.apply(vpreds, values, returns, weights, response_mask, cliprange_value)
+    return loss, stats[1] / stats[2].clamp_min(1.0)

@@ -140,6 +140,15 @@ def _group_stats(scores: torch.Tensor, gid: torch.Tensor, G: int):
 @register_adv_est(AdvantageEstimator.GAE)
 def compute_gae_advantage_return(token_level_rewards, values, response_mask, gamma, lam, **kwargs):
     """GAE with masked positions skipped (state carried through non-response tokens), then whitened."""
+    if token_level_rewards.is_cuda:
+        from verl_b200.ops import _ext
+
+        if _ext.available():       # one scan kernel + one whitening kernel instead of a Python loop over the response length
+            from verl_b200.ops.rl import gae_advantage
+
+            if float(response_mask.sum()) < 2:
+                raise ValueError("masked_var with fewer than two elements and unbiased=True")
+            return gae_advantage(token_level_rewards, values, response_mask, gamma, lam, whiten=True)
     with torch.no_grad():
         nextvalues = torch.zeros_like(values[:, 0])
         lastgaelam = torch.zeros_like(values[:, 0])

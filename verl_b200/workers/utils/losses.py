@@ -140,9 +140,16 @@ def value_loss(config, model_output: dict, data, dp_group=None):
     vpreds = model_output["values"]
     mask = data["response_mask"].to(vpreds.dtype)
     info = {k: data[k] for k in ("dp_size", "batch_num_tokens", "global_batch_size") if k in data and data[k] is not None}
-    loss, clipfrac = core_algos.compute_value_loss(vpreds, data["returns"], data["values"], mask,
-                                                   _get(config, "cliprange_value", 0.5),
-                                                   _get(config, "loss_agg_mode", "token-mean"), **info)
+    from verl_b200.ops import rl as rl_ops
+
+    if rl_ops.fused_ppo_available(vpreds):
+        # one pass: clipped value loss, its gradient and the clip fraction
+        w = rl_ops.agg_weights(mask, _get(config, "loss_agg_mode", "token-mean"), **info)
+        loss, clipfrac = rl_ops.fused_value_loss(vpreds, data["values"], data["returns"], mask, w, _get(config, "cliprange_value", 0.5))
+    else:
+        loss, clipfrac = core_algos.compute_value_loss(vpreds, data["returns"], data["values"], mask,
+                                                       _get(config, "cliprange_value", 0.5),
+                                                       _get(config, "loss_agg_mode", "token-mean"), **info)
     metrics = {
         "critic/vf_loss": Metric(AggregationType.MEAN, loss.detach().item()),
         "critic/vf_clipfrac": Metric(AggregationType.MEAN, clipfrac.detach().item()),
