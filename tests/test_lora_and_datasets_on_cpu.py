@@ -45,6 +45,51 @@ def test_lora_is_identity_at_init_trains_only_adapters_and_merges():
     assert len(dict(merged_hf_named_tensors(eng.model))) == len(exported)
 
 
+def test_merge_lora_script_exports_merged_weights_and_a_peft_adapter(tmp_path):
+    """A LoRA run's checkpoint holds the adapters only; the merge tool folds them into the base weights and also writes them in
+    the PEFT layout (fused projections split per HF module)."""
+    import json
+
+    from safetensors.torch import load_file
+
+    from verl_b200.models.hf_io import save_hf_weights
+    from verl_b200.scripts.merge_lora import merge_lora_checkpoint
+
+    base = DecoderLM(PRESETS["tiny-qwen2"], dtype=torch.float32, seed=1)
+    base_dir = tmp_path / "base"
+    base_dir.mkdir()
+    PRESETS["tiny-qwen2"].save_pretrained(str(base_dir))
+    save_hf_weights(base.hf_named_tensors(), str(base_dir))
+    eng = FSDPEngine(Config({"path": str(base_dir), "lora_rank": 4, "lora_alpha": 8}), {"seed": 1, "model_dtype": "float32"},
+                     {"lr": 1e-2, "weight_decay": 0.0}, {})
+    eng.initialize()
+    for _ in range(2):
+        eng.train_batch(make_batch(), loss_fn)
+    ids = torch.arange(10, 30)
+    want = _logits(eng.model, ids)
+    eng.save_checkpoint(str(tmp_path / "ckpt"), global_step=2)
+    meta = json.load(open(tmp_path / "ckpt" / "fsdp_config.json"))
+    assert meta["lora"]["rank"] == 4 and "qkv_proj" in meta["lora"]["targets"]
+    info = merge_lora_checkpoint(str(base_dir), str(tmp_path / "ckpt"), str(tmp_path / "merged"), dtype=torch.float32)
+    merged = {}
+    for fn in (tmp_path / "merged").iterdir():
+        if fn.suffix == ".safetensors":
+            merged.update(load_file(str(fn)))
+    fresh = DecoderLM(PRESETS["tiny-qwen2"], dtype=torch.float32, seed=9)
+    fresh.load_hf_state_dict(merged)
+    assert torch.allclose(_logits(fresh, ids), want, atol=2e-2)          # merged weights are stored in bf16
+    ad = load_file(str(tmp_path / "merged" / "lora_adapter" / "adapter_model.safetensors"))
+    acfg = json.load(open(tmp_path / "merged" / "lora_adapter" / "adapter_config.json"))
+    assert acfg["r"] == 4 and {"q_proj", "k_proj", "v_proj", "gate_proj", "up_proj", "o_proj", "down_proj"} == set(acfg["target_modules"])
+    cfg = PRESETS["tiny-qwen2"]
+    kq = "base_model.model.model.layers.0.self_attn.q_proj"
+    assert ad[kq + ".lora_A.weight"].shape == (4, cfg.hidden_size) and ad[kq + ".lora_B.weight"].shape == (cfg.num_attention_heads * cfg.head_dim, 4)
+    kv = "base_model.model.model.layers.0.self_attn.v_proj.lora_B.weight"
+    full_b = eng.model.layers[0].self_attn.lora_B_qkv_proj.detach()
+    assert torch.allclose(ad[kv].float(), full_b[-cfg.num_key_value_heads * cfg.head_dim:].float(), atol=1e-2)
+    assert info["num_adapter_tensors"] == len(ad)
+
+
 def test_multiturn_sft_dataset_masks_only_assistant_tokens():
     tok = ByteChatTokenizer()
     rows = [{"messages": [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"},

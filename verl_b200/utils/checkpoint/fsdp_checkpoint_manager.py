@@ -97,7 +97,10 @@ class FSDPCheckpointManager(BaseCheckpointManager):
         zero3 = bool(getattr(e, "_zero3_rows", None))
         if e.rank == 0:
             with open(os.path.join(local_path, "fsdp_config.json"), "w") as f:
-                json.dump({"FSDP_version": 2, "world_size": e.world, "format": "flat_v1"}, f, indent=2)
+                meta = {"FSDP_version": 2, "world_size": e.world, "format": "flat_v1"}
+                if getattr(e.model, "lora_config", None):
+                    meta["lora"] = dict(e.model.lora_config)       # the shards then hold the adapters only (python -m verl_b200.scripts.merge_lora)
+                json.dump(meta, f, indent=2)
             hf_dir = os.path.join(local_path, "huggingface")
             e.cfg.save_pretrained(hf_dir)
             tok_src = getattr(e, "tokenizer_path", None)
