@@ -310,6 +310,36 @@ def bench_lmhead(a):
     with torch.no_grad():
         ms = timeit(lambda: ops.linear_logprob_entropy(h, w, lab, 1.0, True), a.iters)
     report(f"lm_head->logprob+entropy fwd M={M} V={V} K={K}", ms, flops=2.0 * M * V * K)
+    if a.compare:
+        # forward + backward of the whole op against two library formulations of the same thing
+        hg = h.clone().requires_grad_(True)
+
+        def own():
+            lp, ent = ops.linear_logprob_entropy(hg, w, lab, 1.0, False)
+            torch.autograd.grad(lp.sum(), hg)
+
+        ms_o = timeit(own, a.iters)
+        report("  own kernels fwd + bwd (d hidden; the weight gradient is a separate accumulate GEMM)", ms_o, flops=4.0 * M * V * K)
+
+        def torch_ce():
+            logits = torch.nn.functional.linear(hg, w).float()
+            torch.autograd.grad(torch.nn.functional.cross_entropy(logits, lab, reduction="sum"), hg)
+
+        if M * V * 6 < 40e9:
+            report("  cuBLAS logits + torch cross_entropy fwd + bwd", timeit(torch_ce, a.iters), flops=4.0 * M * V * K)
+        try:
+            from liger_kernel.ops.fused_linear_cross_entropy import LigerFusedLinearCrossEntropyFunction as Liger
+        except ImportError as e:
+            print(f"  liger_kernel not importable: {e}")
+            return
+        wg = w.clone().requires_grad_(True)
+
+        def liger():
+            out = Liger.apply(hg, wg, lab, None, None, -100, 0.0, 0.0, "sum")
+            loss = out[0] if isinstance(out, tuple) else out
+            torch.autograd.grad(loss, (hg, wg))
+
+        report("  Liger fused linear + cross-entropy fwd + bwd (Triton; d hidden and d weight)", timeit(liger, a.iters), flops=6.0 * M * V * K)
 
 
 def bench_decode_attn(a):
