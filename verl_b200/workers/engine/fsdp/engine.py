@@ -226,6 +226,13 @@ class FSDPEngine(BaseEngine):
 
             load_hf_weights(self.model, os.path.expanduser(path), strict=not cfg.value_head)
         self.model.gradient_checkpointing = bool(cfg_get(self.model_config, "enable_gradient_checkpointing", False))
+        if not isinstance(self.model_config, ModelConfig) and bool(cfg_get(self.model_config, "enable_activation_offload", False)) \
+                and self.device.type == "cuda" and not self.forward_only:
+            # tensors saved for backward inside the decoder layers wait in pinned host memory (copied on a side stream, prefetched
+            # one layer ahead in backward)
+            from verl_b200.utils.activation_offload import enable_activation_offloading
+
+            enable_activation_offloading(self.model, int(cfg_get(self.model_config, "activation_offload_min_numel", 1 << 20)))
         tiled = cfg_get(self.model_config, "tiled_mlp", None) if not isinstance(self.model_config, ModelConfig) else None
         if tiled is not None and bool(cfg_get(tiled, "enabled", False)):
             for layer in self.model.layers:
@@ -756,6 +763,9 @@ class FSDPEngine(BaseEngine):
                             metrics[k] = v if isinstance(v, Metric) else Metric(AggregationType.MEAN, v)
             for k, v in mo.items():
                 outputs.setdefault(k, []).append(v.detach())
+            off = getattr(self.model, "_activation_offloader", None)
+            if off is not None:
+                off.reset()          # the micro-batch's saved tensors have been consumed (or were never needed: forward only)
         if not forward_only and loss_function is not None:
             self.store.fold_autograd_grads()
         model_output = {k: restore_dynamic_batch(torch.cat(v, 0), mb_indices) for k, v in outputs.items()}
