@@ -100,6 +100,43 @@ def bench_moe(a, rank, world, host, timer):
     report(rank, f"MoE layer forward, EP={world}, {T} tokens/rank, E={E} top-{k}, H={H} I={I} (max rel diff {err:.1e})", ms_f, ms_b, flops, link)
     ms_f, ms_b = timer(lambda: run(ctx, True)), timer(lambda: run(None, True))
     report(rank, "MoE layer forward + backward, same shapes", ms_f, ms_b, 3 * flops, 2 * link)
+    # where the fused forward spends its time: the same steps, timed one by one
+    from verl_b200.ops import _ext
+    from verl_b200.ops.moe import GROUP_BLOCK, ep_row_tables, route_topk
+
+    o = _ext.ops()
+    with torch.no_grad():
+        logits = torch.nn.functional.linear(x, router)
+        w, idx, _ = route_topk(logits, k, True)
+        t_route = timer(lambda: route_topk(torch.nn.functional.linear(x, router), k, True))
+
+        def gather_routing():
+            idx_all = torch.empty(world, T, k, dtype=torch.int32, device=dev)
+            w_all = torch.empty(world, T, k, dtype=torch.float32, device=dev)
+            dist.all_gather_into_tensor(idx_all, idx.to(torch.int32).contiguous())
+            dist.all_gather_into_tensor(w_all, w.float().contiguous())
+            return idx_all, w_all
+
+        idx_all, w_all = gather_routing()
+        t_gather = timer(gather_routing)
+        t_tables = timer(lambda: ep_row_tables(idx_all.long(), w_all, rank, el))
+        row_src, row_dst, row_w, blk, rng = ep_row_tables(idx_all.long(), w_all, rank, el)
+        R = row_src.numel()
+        t_publish = timer(lambda: ctx.publish(x.detach()))
+        xg = torch.empty(R, H, dtype=torch.bfloat16, device=dev)
+        flags = torch.empty(R // GROUP_BLOCK, dtype=torch.int32, device=dev)
+        h = o.gemm_grouped_dispatch(ctx.xbuf.table(), H, row_src, gu.detach(), blk, xg, flags, False)
+        t_dispatch = timer(lambda: o.gemm_grouped_dispatch(ctx.xbuf.table(), H, row_src, gu.detach(), blk, xg, flags, False))
+        t_plain = timer(lambda: o.gemm_grouped(xg, gu.detach(), blk, False))
+        a_ = o.swiglu_fwd(h)
+        t_act = timer(lambda: o.swiglu_fwd(h))
+        t_combine = timer(lambda: o.gemm_grouped_combine(a_, dn.detach(), blk, row_dst, row_w, ctx.cbuf.table(), H, False))
+        t_plain2 = timer(lambda: o.gemm_grouped(a_, dn.detach(), blk, False))
+        t_collect = timer(lambda: ctx.collect(T, T))
+    if rank == 0:
+        print(f"  fused forward by step (us, R = {R} rows): router {t_route * 1e3:.0f} | routing all-gather {t_gather * 1e3:.0f} | row tables {t_tables * 1e3:.0f} | "
+              f"publish + barrier {t_publish * 1e3:.0f} | dispatch GEMM {t_dispatch * 1e3:.0f} (same GEMM on local rows {t_plain * 1e3:.0f}) | swiglu {t_act * 1e3:.0f} | "
+              f"combine GEMM {t_combine * 1e3:.0f} (plain {t_plain2 * 1e3:.0f}) | barrier + slot sum {t_collect * 1e3:.0f}", flush=True)
 
 
 def main():
