@@ -95,6 +95,10 @@ struct DistArgs {
 
 constexpr int STAGE_PARTS = 8;
 constexpr int SIG_FLAGS = 16;
+// shared-memory ring of the fused token dispatch: rows (or 4 KB pieces of longer rows) in flight per SM, one zeroed piece for padding rows
+constexpr int DISPATCH_SLOTS = 7;
+constexpr int DISPATCH_SLOT_BYTES = 4096;
+constexpr int DISPATCH_SMEM_BYTES = (DISPATCH_SLOTS + 1) * DISPATCH_SLOT_BYTES + 64;
 
 __device__ __forceinline__ bool stage_wait(const int* flag, int epoch, volatile int* abort_flag, int* err_word) {
   epoch *= STAGE_PARTS;
@@ -378,47 +382,68 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bf16* const* srcs = reinterpret_cast<const bf16* const*>(dist.seg_ptr);
       bf16* stage = reinterpret_cast<bf16*>(dist.stage);
       if (dist.seg_mode == 4) {
-        // token dispatch: every row of a used 128-row block is fetched from the rank that holds the token (own rows included:
-        // the operand must be contiguous for the tensor map). 16-row pieces are dealt round-robin over the CTAs, block by
-        // block in the order the tiles are scheduled, so early tiles find their rows first. Unused blocks are skipped by the
-        // producer as well, nothing waits for them.
-        const int vec_per_row = K / 8;
-        const int n_chunks = M / 128;
-        int mine = 0;
-        for (int c = 0; c < n_chunks; ++c) {
-          if (dist.blk_expert[c] < 0) continue;
-          for (int part = 0; part < STAGE_PARTS; ++part) {
+        // Token dispatch: every row of a used 128-row block is fetched from the rank that holds the token (own rows included: the
+        // operand must be contiguous for the tensor map). Ordinary loads from a peer are limited by the few requests an SM may
+        // have outstanding (~350 GB/s over the whole GPU, measured), so the rows travel as bulk copies: peer memory -> a ring of
+        // row buffers in shared memory -> the local staging buffer, issued by one thread, DISPATCH_SLOTS rows in flight per SM.
+        // Blocks are dealt to the CTAs round-robin in the order the tiles consume them; a block's flag gets all STAGE_PARTS
+        // at once when its rows have landed. Unused blocks are skipped by the producer as well.
+        uint8_t* bounce = smem + STAGES * Cfg::STAGE_BYTES + 256;
+        uint8_t* zero_row = bounce + DISPATCH_SLOTS * DISPATCH_SLOT_BYTES;
+        uint64_t* bbar = reinterpret_cast<uint64_t*>(zero_row + DISPATCH_SLOT_BYTES);
+        for (int i = et; i < DISPATCH_SLOT_BYTES / 16; i += CT) reinterpret_cast<uint4*>(zero_row)[i] = make_uint4(0, 0, 0, 0);
+        if (et == 0) {
+          for (int j = 0; j < DISPATCH_SLOTS; ++j) mbar_init(&bbar[j], 1);
+          mbar_fence_init();
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");          // the zero row was written by ordinary stores, bulk copies read it
+        asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
+        if (et == 0) {
+          const int row_bytes = K * 2;
+          const int nseg = (row_bytes + DISPATCH_SLOT_BYTES - 1) / DISPATCH_SLOT_BYTES;
+          const int n_chunks = M / 128;
+          uint32_t phase = 0;
+          int mine = 0;
+          bool ok = true;
+          for (int c = 0; c < n_chunks && ok; ++c) {
+            if (dist.blk_expert[c] < 0) continue;
             if ((mine++ % gridDim.x) != blockIdx.x) continue;
-            const int row0 = c * 128 + part * 16;
-            const int total = 16 * vec_per_row;
-            for (int i0 = 0; i0 < total; i0 += CT * 8) {
-              uint4 v[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int i = i0 + j * CT + et;
-                v[j] = make_uint4(0, 0, 0, 0);
-                if (i < total) {
-                  const int r = i / vec_per_row, x = i - r * vec_per_row;
-                  const int e = dist.row_src[row0 + r];
-                  if (e >= 0) v[j] = __ldcs(reinterpret_cast<const uint4*>(srcs[e >> 24] + (long)(e & 0xFFFFFF) * dist.ld_seg + x * 8));
+            const int n_items = 128 * nseg;
+            for (int base = 0; base < n_items && ok; base += DISPATCH_SLOTS) {
+              // the stores of the previous batch must have read their slots before new rows land there
+              asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+              const int nb = min(DISPATCH_SLOTS, n_items - base);
+              for (int j = 0; j < nb; ++j) {
+                const int it = base + j, r = it / nseg, sg = it - r * nseg;
+                const int e = dist.row_src[c * 128 + r];
+                const int off = sg * DISPATCH_SLOT_BYTES;
+                const uint32_t bytes = (uint32_t)min(DISPATCH_SLOT_BYTES, row_bytes - off);
+                if (e >= 0) {
+                  mbar_expect_tx(&bbar[j], bytes);
+                  bulk_load_1d(bounce + j * DISPATCH_SLOT_BYTES,
+                               reinterpret_cast<const uint8_t*>(srcs[e >> 24] + (long)(e & 0xFFFFFF) * dist.ld_seg) + off, bytes, &bbar[j]);
+                } else {
+                  mbar_arrive(&bbar[j]);                          // keeps the slot's phase in step with the others
                 }
               }
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int i = i0 + j * CT + et;
-                if (i < total) {
-                  const int r = i / vec_per_row, x = i - r * vec_per_row;
-                  *reinterpret_cast<uint4*>(stage + (long)(row0 + r) * dist.ld_stage + x * 8) = v[j];
-                }
+              for (int j = 0; j < nb; ++j) {
+                const int it = base + j, r = it / nseg, sg = it - r * nseg;
+                const int e = dist.row_src[c * 128 + r];
+                const int off = sg * DISPATCH_SLOT_BYTES;
+                const uint32_t bytes = (uint32_t)min(DISPATCH_SLOT_BYTES, row_bytes - off);
+                if (!mbar_wait(&bbar[j], phase, abort_flag, err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
+                uint8_t* dst = reinterpret_cast<uint8_t*>(stage + (long)(c * 128 + r) * dist.ld_stage) + off;
+                bulk_store_1d(dst, e >= 0 ? bounce + j * DISPATCH_SLOT_BYTES : zero_row, bytes);
               }
+              for (int j = nb; j < DISPATCH_SLOTS; ++j) mbar_arrive(&bbar[j]);      // unused slots of a short last batch
+              tma_store_commit();
+              phase ^= 1;
             }
-            __threadfence();
-            asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
-            if (et == 0) {
-              asm volatile("fence.proxy.async;" ::: "memory");
-              asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(dist.stage_flags + c) : "memory");
-            }
+            tma_store_wait_all();                                 // the block's rows are in the staging buffer
+            asm volatile("fence.proxy.async;" ::: "memory");
+            asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(dist.stage_flags + c), "n"(STAGE_PARTS) : "memory");
           }
+          tma_store_wait_all();
         }
       } else {
       const bool by_k = dist.seg_mode == 3;
@@ -1307,12 +1332,11 @@ static int launch_grouped_dispatch(const long* src_ptrs, int world, int ld_src, 
   if (!B_MN) rc = make_tmap_3d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, E, (uint64_t)K * 2, (uint64_t)N * K * 2, BK, BN, 1);
   else       rc = make_tmap_3d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, E, (uint64_t)N * 2, (uint64_t)N * K * 2, 64, BK, 1);
   if (rc) return rc;
-  static bool attr_set = false;
+  // the staged all-gather GEMMs share this instantiation and raise the attribute to Cfg::SMEM_BYTES only: set it on every call
+  constexpr int SMEM = Cfg::SMEM_BYTES + DISPATCH_SMEM_BYTES;
+  static_assert(SMEM <= 227 * 1024, "pipeline stages + dispatch ring exceed the shared memory of an SM");
   auto kern = gemm_bf16_kernel<BN, false, B_MN, EPI_STORE, 8>;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -10;
-    attr_set = true;
-  }
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -10;
   if (cudaMemsetAsync(stage_flags, 0, sizeof(int) * (R / BM), stream) != cudaSuccess) return -13;
   DistArgs d = {};
   d.group_mode = 1; d.num_experts = E; d.blk_expert = blk_expert;
@@ -1323,7 +1347,7 @@ static int launch_grouped_dispatch(const long* src_ptrs, int world, int ld_src, 
   const int units = (R / BM) * ((N + BN - 1) / BN);
   const int grid = units < num_sms() ? units : num_sms();
   const int num_kb = (K + BK - 1) / BK;
-  kern<<<grid, 192 + 32 * 8, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, nullptr, R, N, K, ldc, 0, err_word, LmHeadEpi{}, 1, num_kb, nullptr, d);
+  kern<<<grid, 192 + 32 * 8, SMEM, stream>>>(tmA, tmB, C, nullptr, R, N, K, ldc, 0, err_word, LmHeadEpi{}, 1, num_kb, nullptr, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

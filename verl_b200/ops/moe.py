@@ -166,22 +166,30 @@ def ep_row_tables(idx_all: torch.Tensor, w_all: torch.Tensor, rank: int, e_local
     token)), ``row_w`` fp32 [R], ``blk_expert`` int32 [R/128], ``expert_rng`` int32 [e_local, 2]."""
     W, Tc, k = idx_all.shape
     lo = rank * e_local
+    dev = idx_all.device
     flat = idx_all.reshape(-1)
-    sel = ((flat >= lo) & (flat < lo + e_local)).nonzero(as_tuple=True)[0]
-    le = flat.index_select(0, sel) - lo
-    order = torch.argsort(le, stable=True)
-    sel = sel.index_select(0, order)
-    counts = torch.bincount(le, minlength=e_local)
+    sel = ((flat >= lo) & (flat < lo + e_local)).nonzero(as_tuple=True)[0]          # the one host synchronisation: R is needed for allocation
     n = int(sel.numel())
-    dest, R, blk_expert, rng = padded_layout(counts, n)
+    le, order = torch.sort(flat.index_select(0, sel) - lo, stable=True)             # local expert of every row, rows grouped by expert
+    sel = sel.index_select(0, order)
+    counts = torch.zeros(e_local, dtype=torch.long, device=dev).scatter_add_(0, le, torch.ones_like(le))
+    # block-padded layout (same as ``padded_layout``, with the sorted expert ids at hand instead of a repeat_interleave)
+    padded = (counts + GROUP_BLOCK - 1) // GROUP_BLOCK * GROUP_BLOCK
+    pad_end = torch.cumsum(padded, 0)
+    pad_off = pad_end - padded
+    off = torch.cumsum(counts, 0) - counts
+    dest = pad_off[le] + (torch.arange(n, device=dev) - off[le])
+    R = (n + e_local * (GROUP_BLOCK - 1) + GROUP_BLOCK - 1) // GROUP_BLOCK * GROUP_BLOCK
+    starts = torch.arange(R // GROUP_BLOCK, device=dev) * GROUP_BLOCK
+    be = torch.searchsorted(pad_end, starts, right=True)
+    blk_expert = torch.where(starts < pad_end[-1], be, torch.full_like(be, -1)).to(torch.int32)
+    rng = torch.stack([pad_off // GROUP_BLOCK, pad_end // GROUP_BLOCK], 1).to(torch.int32).contiguous()
     tok_flat = sel // k
     src, token, slot = tok_flat // Tc, tok_flat % Tc, sel % k
-    dev = idx_all.device
-    row_src = torch.full((R,), -1, dtype=torch.int32, device=dev)
-    row_dst = torch.full((R,), -1, dtype=torch.int32, device=dev)
+    tables = torch.full((2, R), -1, dtype=torch.int32, device=dev)
+    tables[:, dest] = torch.stack([(src << 24) | token, (src << 24) | (slot * Tc + token)]).to(torch.int32)
+    row_src, row_dst = tables[0], tables[1]
     row_w = torch.zeros(R, dtype=torch.float32, device=dev)
-    row_src[dest] = ((src << 24) | token).to(torch.int32)
-    row_dst[dest] = ((src << 24) | (slot * Tc + token)).to(torch.int32)
     row_w[dest] = w_all.reshape(-1).index_select(0, sel).float()
     return row_src, row_dst, row_w, blk_expert, rng
 
