@@ -373,133 +373,100 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ staging copies (dedicated warps)
     if constexpr (COPY_WARPS > 0) {
     if (dist.stage != nullptr) {
-      // Bring the remote chunks of the gathered operand into local memory, once. A 128-row chunk is copied in
-      // STAGE_PARTS pieces of 16 rows, spread round-robin over the copy warps of all CTAs; each finished piece adds 1 to
-      // the chunk's flag, and a chunk is complete when its flag reaches stage_epoch * STAGE_PARTS. Nothing here waits on
-      // another CTA, so the copies always make progress.
+      // Bring the chunks of the gathered operand that live elsewhere into the local staging buffer, once per call, while the
+      // tensor cores work on chunks that have arrived. Ordinary loads from a peer are limited by the few requests an SM may have
+      // outstanding (~350 GB/s over the whole GPU, measured), so the rows travel as bulk copies: peer memory -> a ring of row
+      // buffers in shared memory -> staging, issued by ONE thread per CTA with DISPATCH_SLOTS pieces of up to 4 KB in flight.
+      // 128-row chunks are dealt to the CTAs round-robin in the order the tiles consume them; a chunk's flag receives all its
+      // STAGE_PARTS at once when its rows have landed. Nothing here waits on another CTA, so the copies always make progress.
+      //   seg_mode 1 / 2: chunk c = rows [128 c, 128 c + 128) of the row-gathered operand (own chunks are read in place);
+      //   seg_mode 3:     chunk (row block, owner) = that owner's K columns of 128 rows;
+      //   seg_mode 4:     token dispatch, row r of a used block comes from (rank, row) = row_src[r] (own rows too: the operand
+      //                   must be contiguous for the tensor map), padding rows are zero-filled.
       constexpr int CT = 32 * COPY_WARPS;                 // copy threads per CTA
       const int et = threadIdx.x - 192;
       const bf16* const* srcs = reinterpret_cast<const bf16* const*>(dist.seg_ptr);
       bf16* stage = reinterpret_cast<bf16*>(dist.stage);
-      if (dist.seg_mode == 4) {
-        // Token dispatch: every row of a used 128-row block is fetched from the rank that holds the token (own rows included: the
-        // operand must be contiguous for the tensor map). Ordinary loads from a peer are limited by the few requests an SM may
-        // have outstanding (~350 GB/s over the whole GPU, measured), so the rows travel as bulk copies: peer memory -> a ring of
-        // row buffers in shared memory -> the local staging buffer, issued by one thread, DISPATCH_SLOTS rows in flight per SM.
-        // Blocks are dealt to the CTAs round-robin in the order the tiles consume them; a block's flag gets all STAGE_PARTS
-        // at once when its rows have landed. Unused blocks are skipped by the producer as well.
-        uint8_t* bounce = smem + STAGES * Cfg::STAGE_BYTES + 256;
-        uint8_t* zero_row = bounce + DISPATCH_SLOTS * DISPATCH_SLOT_BYTES;
-        uint64_t* bbar = reinterpret_cast<uint64_t*>(zero_row + DISPATCH_SLOT_BYTES);
-        for (int i = et; i < DISPATCH_SLOT_BYTES / 16; i += CT) reinterpret_cast<uint4*>(zero_row)[i] = make_uint4(0, 0, 0, 0);
-        if (et == 0) {
-          for (int j = 0; j < DISPATCH_SLOTS; ++j) mbar_init(&bbar[j], 1);
-          mbar_fence_init();
-        }
-        asm volatile("fence.proxy.async;" ::: "memory");          // the zero row was written by ordinary stores, bulk copies read it
-        asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
-        if (et == 0) {
-          const int row_bytes = K * 2;
-          const int nseg = (row_bytes + DISPATCH_SLOT_BYTES - 1) / DISPATCH_SLOT_BYTES;
-          const int n_chunks = M / 128;
-          uint32_t phase = 0;
-          int mine = 0;
-          bool ok = true;
-          for (int c = 0; c < n_chunks && ok; ++c) {
-            if (dist.blk_expert[c] < 0) continue;
-            if ((mine++ % gridDim.x) != blockIdx.x) continue;
-            const int n_items = 128 * nseg;
-            for (int base = 0; base < n_items && ok; base += DISPATCH_SLOTS) {
-              // the stores of the previous batch must have read their slots before new rows land there
-              asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-              const int nb = min(DISPATCH_SLOTS, n_items - base);
-              for (int j = 0; j < nb; ++j) {
-                const int it = base + j, r = it / nseg, sg = it - r * nseg;
-                const int e = dist.row_src[c * 128 + r];
-                const int off = sg * DISPATCH_SLOT_BYTES;
-                const uint32_t bytes = (uint32_t)min(DISPATCH_SLOT_BYTES, row_bytes - off);
-                if (e >= 0) {
-                  mbar_expect_tx(&bbar[j], bytes);
-                  bulk_load_1d(bounce + j * DISPATCH_SLOT_BYTES,
-                               reinterpret_cast<const uint8_t*>(srcs[e >> 24] + (long)(e & 0xFFFFFF) * dist.ld_seg) + off, bytes, &bbar[j]);
-                } else {
-                  mbar_arrive(&bbar[j]);                          // keeps the slot's phase in step with the others
-                }
-              }
-              for (int j = 0; j < nb; ++j) {
-                const int it = base + j, r = it / nseg, sg = it - r * nseg;
-                const int e = dist.row_src[c * 128 + r];
-                const int off = sg * DISPATCH_SLOT_BYTES;
-                const uint32_t bytes = (uint32_t)min(DISPATCH_SLOT_BYTES, row_bytes - off);
-                if (!mbar_wait(&bbar[j], phase, abort_flag, err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
-                uint8_t* dst = reinterpret_cast<uint8_t*>(stage + (long)(c * 128 + r) * dist.ld_stage) + off;
-                bulk_store_1d(dst, e >= 0 ? bounce + j * DISPATCH_SLOT_BYTES : zero_row, bytes);
-              }
-              for (int j = nb; j < DISPATCH_SLOTS; ++j) mbar_arrive(&bbar[j]);      // unused slots of a short last batch
-              tma_store_commit();
-              phase ^= 1;
-            }
-            tma_store_wait_all();                                 // the block's rows are in the staging buffer
-            asm volatile("fence.proxy.async;" ::: "memory");
-            asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(dist.stage_flags + c), "n"(STAGE_PARTS) : "memory");
-          }
-          tma_store_wait_all();
-        }
-      } else {
-      const bool by_k = dist.seg_mode == 3;
-      const int cols = by_k ? dist.seg_rows : K;          // bf16 elements per copied row
-      const int vec_per_row = cols / 8;
-      const int n_chunks = by_k ? ((M + 127) / 128) * dist.n_seg : dist.seg_rows * dist.n_seg / 128;
-      const int n_units = n_chunks * STAGE_PARTS;
-      // skip this rank's own chunks when dealing out the work, so that the remote ones are spread evenly
-      int mine = 0;
-      for (int u = 0; u < n_units; ++u) {
-        const int c = u / STAGE_PARTS, part = u - c * STAGE_PARTS;
-        int owner, row0;
-        const bf16* src;
-        bf16* dst;
-        if (by_k) {
-          const int mc = c / dist.n_seg;
-          owner = c - mc * dist.n_seg;
-          row0 = mc * 128 + part * 16;
-          src = srcs[owner] + (long)(dist.row_off + row0) * dist.ld_seg;
-          dst = stage + (long)row0 * dist.ld_stage + (long)owner * dist.seg_rows;
-        } else {
-          row0 = c * 128 + part * 16;
-          owner = row0 / dist.seg_rows;
-          src = srcs[owner] + (long)(row0 - owner * dist.seg_rows) * dist.ld_seg;
-          dst = stage + (long)row0 * dist.ld_stage;
-        }
-        if (owner == dist.rank) continue;
-        if ((mine++ % gridDim.x) != blockIdx.x) continue;
-        const int rows = by_k ? max(0, min(16, M - row0)) : 16;
-        const int total = rows * vec_per_row;
-        for (int i0 = 0; i0 < total; i0 += CT * 8) {
-          uint4 v[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int i = i0 + j * CT + et;
-            if (i < total) {
-              const int r = i / vec_per_row, x = i - r * vec_per_row;
-              v[j] = __ldcs(reinterpret_cast<const uint4*>(src + (long)r * dist.ld_seg + x * 8));
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int i = i0 + j * CT + et;
-            if (i < total) {
-              const int r = i / vec_per_row, x = i - r * vec_per_row;
-              *reinterpret_cast<uint4*>(dst + (long)r * dist.ld_stage + x * 8) = v[j];
-            }
-          }
-        }
-        __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
-        if (et == 0) {
-          asm volatile("fence.proxy.async;" ::: "memory");
-          asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(dist.stage_flags + c) : "memory");
-        }
+      uint8_t* bounce = smem + STAGES * Cfg::STAGE_BYTES + 256;
+      uint8_t* zero_row = bounce + DISPATCH_SLOTS * DISPATCH_SLOT_BYTES;
+      uint64_t* bbar = reinterpret_cast<uint64_t*>(zero_row + DISPATCH_SLOT_BYTES);
+      for (int i = et; i < DISPATCH_SLOT_BYTES / 16; i += CT) reinterpret_cast<uint4*>(zero_row)[i] = make_uint4(0, 0, 0, 0);
+      if (et == 0) {
+        for (int j = 0; j < DISPATCH_SLOTS; ++j) mbar_init(&bbar[j], 1);
+        mbar_fence_init();
       }
+      asm volatile("fence.proxy.async;" ::: "memory");            // the zero row was written by ordinary stores, bulk copies read it
+      asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
+      if (et == 0) {
+        const int mode = dist.seg_mode;
+        const bool by_k = mode == 3;
+        const int row_bytes = (by_k ? dist.seg_rows : K) * 2;
+        const int nseg = (row_bytes + DISPATCH_SLOT_BYTES - 1) / DISPATCH_SLOT_BYTES;
+        const int n_chunks = mode == 4 ? M / 128 : by_k ? ((M + 127) / 128) * dist.n_seg : dist.seg_rows * dist.n_seg / 128;
+        uint32_t phase = 0;
+        int mine = 0;
+        bool ok = true;
+        for (int c = 0; c < n_chunks && ok; ++c) {
+          int owner = -1, row0, rows = 128;
+          long dst_col = 0;
+          if (mode == 4) {
+            if (dist.blk_expert[c] < 0) continue;                 // unused block: the producer skips it as well
+            row0 = c * 128;
+          } else if (by_k) {
+            const int mc = c / dist.n_seg;
+            owner = c - mc * dist.n_seg;
+            row0 = mc * 128;
+            rows = min(128, M - row0);
+            dst_col = (long)owner * dist.seg_rows;
+          } else {
+            row0 = c * 128;
+            owner = row0 / dist.seg_rows;
+          }
+          if (mode != 4 && owner == dist.rank) continue;           // own chunks are read where they are
+          if ((mine++ % gridDim.x) != blockIdx.x) continue;
+          const int n_items = rows * nseg;
+          for (int base = 0; base < n_items && ok; base += DISPATCH_SLOTS) {
+            // the stores of the previous batch must have read their slots before new rows land there
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            const int nb = min(DISPATCH_SLOTS, n_items - base);
+            for (int j = 0; j < nb; ++j) {
+              const int it = base + j, r = it / nseg, sg = it - r * nseg;
+              const int off = sg * DISPATCH_SLOT_BYTES;
+              const uint32_t bytes = (uint32_t)min(DISPATCH_SLOT_BYTES, row_bytes - off);
+              const bf16* src = nullptr;
+              if (mode == 4) {
+                const int e = dist.row_src[row0 + r];
+                if (e >= 0) src = srcs[e >> 24] + (long)(e & 0xFFFFFF) * dist.ld_seg;
+              } else if (by_k) {
+                src = srcs[owner] + (long)(dist.row_off + row0 + r) * dist.ld_seg;
+              } else {
+                src = srcs[owner] + (long)(row0 + r - owner * dist.seg_rows) * dist.ld_seg;
+              }
+              if (src != nullptr) {
+                mbar_expect_tx(&bbar[j], bytes);
+                bulk_load_1d(bounce + j * DISPATCH_SLOT_BYTES, reinterpret_cast<const uint8_t*>(src) + off, bytes, &bbar[j]);
+              } else {
+                mbar_arrive(&bbar[j]);                            // padding row: keeps the slot's phase in step with the others
+              }
+            }
+            for (int j = 0; j < nb; ++j) {
+              const int it = base + j, r = it / nseg, sg = it - r * nseg;
+              const int off = sg * DISPATCH_SLOT_BYTES;
+              const uint32_t bytes = (uint32_t)min(DISPATCH_SLOT_BYTES, row_bytes - off);
+              const bool pad = mode == 4 && dist.row_src[row0 + r] < 0;
+              if (!mbar_wait(&bbar[j], phase, abort_flag, err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
+              uint8_t* dst = reinterpret_cast<uint8_t*>(stage + (long)(row0 + r) * dist.ld_stage + dst_col) + off;
+              bulk_store_1d(dst, pad ? zero_row : bounce + j * DISPATCH_SLOT_BYTES, bytes);
+            }
+            for (int j = nb; j < DISPATCH_SLOTS; ++j) mbar_arrive(&bbar[j]);        // unused slots of a short last batch
+            tma_store_commit();
+            phase ^= 1;
+          }
+          tma_store_wait_all();                                   // the chunk's rows are in the staging buffer
+          asm volatile("fence.proxy.async;" ::: "memory");
+          asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(dist.stage_flags + c), "n"(STAGE_PARTS) : "memory");
+        }
+        tma_store_wait_all();
       }
     }
     }
@@ -859,10 +826,13 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   if (!B_MN) rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BN, BK);
   else       rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
   if (rc) return rc;
+  // kernels with staging warps carry the bulk-copy ring behind the pipeline stages
+  constexpr int SMEM = Cfg::SMEM_BYTES + (COPY_WARPS > 0 ? DISPATCH_SMEM_BYTES : 0);
+  static_assert(SMEM <= 227 * 1024, "pipeline stages + staging ring exceed the shared memory of an SM");
   static bool attr_set = false;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI, COPY_WARPS, KA>;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return -10;
     attr_set = true;
   }
@@ -873,7 +843,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   if (split_k > 1 && split_ws == nullptr && EPI != EPI_PEER) return -6;
   int units = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * split_k;
   int grid = units < num_sms() ? units : num_sms();
-  kern<<<grid, 192 + 32 * COPY_WARPS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags,
+  kern<<<grid, 192 + 32 * COPY_WARPS, SMEM, stream>>>(tmA, tmB, C, reinterpret_cast<const bf16*>(bias), M, N, K, ldc, flags,
                                                 err_word, epi, split_k, kb_per, split_ws, dist);
   if (cudaGetLastError() != cudaSuccess) return -11;
   if (split_k > 1 && EPI != EPI_PEER) {
