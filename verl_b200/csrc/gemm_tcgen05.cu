@@ -99,6 +99,9 @@ constexpr int SIG_FLAGS = 16;
 constexpr int DISPATCH_SLOTS = 7;
 constexpr int DISPATCH_SLOT_BYTES = 4096;
 constexpr int DISPATCH_SMEM_BYTES = (DISPATCH_SLOTS + 1) * DISPATCH_SLOT_BYTES + 64;
+// combine epilogue: one 128-byte line (+16 bytes so that neighbouring lines start in different banks) per epilogue thread
+constexpr int COMBINE_LINE_PITCH = 144;
+constexpr int COMBINE_SMEM_BYTES = 128 * COMBINE_LINE_PITCH;
 
 __device__ __forceinline__ bool stage_wait(const int* flag, int epoch, volatile int* abort_flag, int* err_word) {
   epoch *= STAGE_PARTS;
@@ -584,27 +587,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       } else if constexpr (EPI == EPI_PEER) {
         if (dist.row_dst != nullptr) {
-          // expert outputs go straight to the rank and row of the token they belong to, scaled by the routing weight
+          // Expert outputs go straight to the rank and row of the token they belong to, scaled by the routing weight. A thread
+          // owns one output row; it packs 64 columns into its own 128-byte line of shared memory (line pitch 144 B: the eight
+          // lanes of a 16-byte store phase hit eight different bank groups) and sends the line as ONE bulk store, so a row
+          // crosses NVLink in 128-byte writes from the copy engine instead of 64-byte stores from the thread.
           const int e = row < M ? dist.row_dst[row] : -1;
           const float w = e >= 0 ? dist.row_w[row] : 0.f;
           bf16* drow = e >= 0 ? reinterpret_cast<bf16*>(dist.peer_out[e >> 24]) + (long)(e & 0xFFFFFF) * ldc : nullptr;
+          uint8_t* line = smem + STAGES * Cfg::STAGE_BYTES + 256 + (q * 32 + lane) * COMBINE_LINE_PITCH;
 #pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(taddr + c * 32, v);
+          for (int c = 0; c < BN / 64; ++c) {
+            uint32_t v[64];
+            tmem_ld_32x32b_x32(taddr + c * 64, v);
+            tmem_ld_32x32b_x32(taddr + c * 64 + 32, v + 32);
             tmem_ld_wait();
-            const int col0 = n0 + c * 32;
-            if (e >= 0 && col0 + 32 <= N) {
-              uint4 o[4];
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the previous store has read this line
+            const int col0 = n0 + c * 64;
+            if (e >= 0 && col0 + 64 <= N) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                o[j].x = pack_bf16x2(__uint_as_float(v[8 * j]) * w, __uint_as_float(v[8 * j + 1]) * w);
-                o[j].y = pack_bf16x2(__uint_as_float(v[8 * j + 2]) * w, __uint_as_float(v[8 * j + 3]) * w);
-                o[j].z = pack_bf16x2(__uint_as_float(v[8 * j + 4]) * w, __uint_as_float(v[8 * j + 5]) * w);
-                o[j].w = pack_bf16x2(__uint_as_float(v[8 * j + 6]) * w, __uint_as_float(v[8 * j + 7]) * w);
+              for (int j = 0; j < 8; ++j) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(v[8 * j]) * w, __uint_as_float(v[8 * j + 1]) * w);
+                o.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]) * w, __uint_as_float(v[8 * j + 3]) * w);
+                o.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]) * w, __uint_as_float(v[8 * j + 5]) * w);
+                o.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]) * w, __uint_as_float(v[8 * j + 7]) * w);
+                reinterpret_cast<uint4*>(line)[j] = o;
               }
-#pragma unroll
-              for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(drow + col0)[j] = o[j];
+              fence_async_smem();                                                 // the line was written by ordinary stores
+              bulk_store_1d(drow + col0, line, 128);
+              tma_store_commit();
             }
           }
           tc_fence_before();
@@ -738,6 +749,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       mbar_arrive(&tempty_bar[acc]);
     }
+    if (EPI == EPI_PEER && dist.row_dst != nullptr) tma_store_wait_all();       // this thread's bulk stores have left shared memory and landed
   }
 
   // ------------------------------------------------------------ teardown
@@ -1332,12 +1344,11 @@ static int launch_grouped_combine(const void* A, const void* B, const int* blk_e
   if (!B_MN) rc = make_tmap_3d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, E, (uint64_t)K * 2, (uint64_t)N * K * 2, BK, BN, 1);
   else       rc = make_tmap_3d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, E, (uint64_t)N * 2, (uint64_t)N * K * 2, 64, BK, 1);
   if (rc) return rc;
-  static bool attr_set = false;
+  // (the plain peer-scatter GEMMs share this instantiation and set the attribute to Cfg::SMEM_BYTES only: set it on every call)
+  constexpr int SMEM = Cfg::SMEM_BYTES + COMBINE_SMEM_BYTES;
+  static_assert(SMEM <= 227 * 1024, "pipeline stages + combine lines exceed the shared memory of an SM");
   auto kern = gemm_bf16_kernel<BN, false, B_MN, EPI_PEER>;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -10;
-    attr_set = true;
-  }
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -10;
   DistArgs d = {};
   d.group_mode = 1; d.num_experts = E; d.blk_expert = blk_expert;
   d.world = world; d.row_dst = row_dst; d.row_w = row_w;
@@ -1345,7 +1356,7 @@ static int launch_grouped_combine(const void* A, const void* B, const int* blk_e
   const int units = (R / BM) * ((N + BN - 1) / BN);
   const int grid = units < num_sms() ? units : num_sms();
   const int num_kb = (K + BK - 1) / BK;
-  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, nullptr, nullptr, R, N, K, ld_out, 0, err_word, LmHeadEpi{}, 1, num_kb, nullptr, d);
+  kern<<<grid, 192, SMEM, stream>>>(tmA, tmB, nullptr, nullptr, R, N, K, ld_out, 0, err_word, LmHeadEpi{}, 1, num_kb, nullptr, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 }  // namespace vb
@@ -1370,7 +1381,7 @@ extern "C" int vb_gemm_grouped_combine(const void* A, const void* B, const int* 
                                        cudaStream_t stream) {
   using namespace vb;
   if (R <= 0) return 0;
-  if (world < 1 || world > MAX_TP || (R % BM) != 0 || (lda & 7) || (N % 32) != 0 || (K & 7) || (ld_out & 7) ||
+  if (world < 1 || world > MAX_TP || (R % BM) != 0 || (lda & 7) || (N % 64) != 0 || (K & 7) || (ld_out & 7) ||
       (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return -4;
   return b_mn ? launch_grouped_combine<true>(A, B, blk_expert, row_dst, row_w, out_ptrs, world, R, N, K, E, lda, ld_out, err_word, stream)
