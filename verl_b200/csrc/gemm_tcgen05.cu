@@ -83,6 +83,7 @@ struct DistArgs {
   // (row_dst[r] & 0xFFFFFF) of rank (row_dst[r] >> 24)'s buffer peer_out[rank] (row stride ldc); row_dst[r] < 0: not stored.
   const int* row_dst;
   const float* row_w;
+  int peer_lines;                    // EPI_PEER: rows leave as 128-byte bulk stores from shared-memory lines (N and head_dim multiples of 64)
   void* stage;
   int* stage_flags;
   int stage_epoch;
@@ -632,6 +633,52 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           r_hi = r_lo + 1;
           row_local = row - (long)r_lo * dist.rows_per_owner;
         }
+        if (dist.peer_lines) {
+          // 64 output columns of this thread's row are packed into its shared-memory line and leave as one 128-byte bulk store
+          // per destination (see the combine epilogue above): the copy engine writes to the peers, not the thread
+          uint8_t* line = smem + STAGES * Cfg::STAGE_BYTES + 256 + (q * 32 + lane) * COMBINE_LINE_PITCH;
+#pragma unroll 1
+          for (int c = 0; c < BN / 64; ++c) {
+            uint32_t v[64];
+            tmem_ld_32x32b_x32(taddr + c * 64, v);
+            tmem_ld_32x32b_x32(taddr + c * 64 + 32, v + 32);
+            tmem_ld_wait();
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the previous store has read this line
+            const int col0 = n0 + c * 64;
+            if (row < M && col0 + 64 <= N) {
+              if (bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __bfloat162float(bias[col0 + j]));
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1]));
+                o.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                o.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                o.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                reinterpret_cast<uint4*>(line)[j] = o;
+              }
+              fence_async_smem();
+              if (dist.head_dim > 0) {
+                const uint16_t e = dist.head_map[col0 / dist.head_dim];
+                bf16* dst = reinterpret_cast<bf16*>(dist.peer_out[e >> 12]) + ((long)dist.row_off + row) * ldc +
+                            (long)(e & 0xFFF) * dist.head_dim + (col0 % dist.head_dim);
+                bulk_store_1d(dst, line, 128);
+              } else {
+                for (int r = r_lo; r < r_hi; ++r) {
+                  const long slot = dist.sig_local != nullptr ? (long)(t % split_k) : (long)dist.rank;
+                  bf16* dst = reinterpret_cast<bf16*>(dist.peer_out[r]) + sig_slot_off + slot * dist.slot_elems + row_local * ldc + col0;
+                  bulk_store_1d(dst, line, 128);
+                }
+              }
+              tma_store_commit();
+            }
+          }
+          tc_fence_before();
+          mbar_arrive(&tempty_bar[acc]);
+          continue;
+        }
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t v[32];
@@ -749,7 +796,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       mbar_arrive(&tempty_bar[acc]);
     }
-    if (EPI == EPI_PEER && dist.row_dst != nullptr) tma_store_wait_all();       // this thread's bulk stores have left shared memory and landed
+    if (EPI == EPI_PEER && (dist.row_dst != nullptr || dist.peer_lines)) tma_store_wait_all();   // this thread's bulk stores have landed
   }
 
   // ------------------------------------------------------------ teardown
@@ -829,7 +876,10 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
                        int split_k = 1, float* split_ws = nullptr, const DistArgs* dist_in = nullptr) {
   using Cfg = GemmCfg<BN, KA>;
   static const DistArgs no_dist = {};
-  const DistArgs& dist = dist_in ? *dist_in : no_dist;
+  DistArgs dist = dist_in ? *dist_in : no_dist;
+  if (EPI == EPI_PEER && dist.row_dst == nullptr)
+    dist.peer_lines = (N % 64 == 0) && (dist.head_dim == 0 || dist.head_dim % 64 == 0) && (ldc % 8 == 0) && (dist.slot_elems % 8 == 0) &&
+                      (dist.sig_half % 8 == 0);
   CUtensorMap tmA, tmB;
   int rc;
   if (!A_MN) rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK);
@@ -839,7 +889,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   else       rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
   if (rc) return rc;
   // kernels with staging warps carry the bulk-copy ring behind the pipeline stages
-  constexpr int SMEM = Cfg::SMEM_BYTES + (COPY_WARPS > 0 ? DISPATCH_SMEM_BYTES : 0);
+  constexpr int SMEM = Cfg::SMEM_BYTES + (COPY_WARPS > 0 ? DISPATCH_SMEM_BYTES : 0) + (EPI == EPI_PEER ? COMBINE_SMEM_BYTES : 0);
   static_assert(SMEM <= 227 * 1024, "pipeline stages + staging ring exceed the shared memory of an SM");
   static bool attr_set = false;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI, COPY_WARPS, KA>;
