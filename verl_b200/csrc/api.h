@@ -109,6 +109,9 @@ int vb_gemm_grouped_wgrad(const void* dY, const void* X, void* dW, const void* e
 int vb_ppo_loss(const float* lp, const float* old_lp, const float* ref_lp, const float* adv, const float* weight, const float* mask,
                 const float* is_w, long n, float clip_lo, float clip_hi, float clip_c, int kl_type, float kl_coef, float* grad,
                 float* loss_out, float* stats, cudaStream_t st);
+int vb_ep_count(const int* idx_all, long n_total, int lo, int e_local, int* counts, cudaStream_t st);
+int vb_ep_fill(const int* idx_all, const float* w_all, long n_total, int Tc, int k, int lo, int e_local, const int* counts, int n_blocks, int* scratch,
+               int* row_src, int* row_dst, float* row_w, int* blk_expert, int* expert_rng, cudaStream_t st);
 int vb_gae(const float* rewards, const float* values, const float* mask, int B, int R, float gamma, float lam, int whiten, float* adv, float* ret,
            float* stats, cudaStream_t st);
 int vb_value_loss(const float* v, const float* v_old, const float* ret, const float* weight, const float* mask, long n, float clip, float* grad,

@@ -162,9 +162,37 @@ void gemm_grouped_combine(const Tensor& x, const Tensor& w, const Tensor& blk_ex
                                    vb_status_tensor(x.get_device()).data_ptr<int>(), cur_stream()),
            "gemm_grouped_combine");
 }
+
+// Row tables of the expert-parallel grouped GEMMs (csrc/moe_tables.cu). idx_all int32 [W, Tc, k], w_all fp32 [W, Tc, k].
+// -> (row_src int32 [R], row_dst int32 [R], row_w fp32 [R], blk_expert int32 [R / 128], expert_rng int32 [e_local, 2])
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> ep_row_tables(const Tensor& idx_all, const Tensor& w_all, int64_t rank, int64_t e_local) {
+  TORCH_CHECK(idx_all.is_cuda() && idx_all.scalar_type() == at::kInt && idx_all.is_contiguous() && idx_all.dim() == 3, "ep_row_tables: idx_all must be int32 [W, Tc, k]");
+  TORCH_CHECK(w_all.is_cuda() && w_all.scalar_type() == at::kFloat && w_all.is_contiguous() && w_all.numel() == idx_all.numel(), "ep_row_tables: bad w_all");
+  TORCH_CHECK(idx_all.size(0) <= 128 && idx_all.size(1) * idx_all.size(2) < (1 << 24), "ep_row_tables: rank / row codes would overflow");
+  c10::cuda::CUDAGuard guard(idx_all.device());
+  const int64_t n_total = idx_all.numel();
+  const int Tc = idx_all.size(1), k = idx_all.size(2), lo = (int)(rank * e_local);
+  auto iopt = idx_all.options();
+  Tensor counts = at::zeros({e_local}, iopt);
+  check_rc(vb_ep_count(idx_all.data_ptr<int>(), n_total, lo, (int)e_local, counts.data_ptr<int>(), cur_stream()), "ep_count");
+  Tensor counts_h = counts.cpu();                                    // the one host synchronisation: the counts size the buffers
+  int64_t n_blocks = 0;
+  for (int64_t e = 0; e < e_local; ++e) n_blocks += (counts_h.data_ptr<int>()[e] + 127) / 128;
+  if (n_blocks == 0) n_blocks = 1;
+  const int64_t R = n_blocks * 128;
+  Tensor row_src = at::empty({R}, iopt), row_dst = at::empty({R}, iopt), blk = at::empty({n_blocks}, iopt), rng = at::empty({e_local, 2}, iopt);
+  Tensor row_w = at::empty({R}, w_all.options());
+  Tensor scratch = at::empty({2 * e_local}, iopt);
+  check_rc(vb_ep_fill(idx_all.data_ptr<int>(), w_all.data_ptr<float>(), n_total, Tc, k, lo, (int)e_local, counts.data_ptr<int>(), (int)n_blocks,
+                      scratch.data_ptr<int>(), row_src.data_ptr<int>(), row_dst.data_ptr<int>(), row_w.data_ptr<float>(), blk.data_ptr<int>(),
+                      rng.data_ptr<int>(), cur_stream()),
+           "ep_fill");
+  return {row_src, row_dst, row_w, blk, rng};
+}
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
+  m.def("ep_row_tables(Tensor idx_all, Tensor w_all, int rank, int e_local) -> (Tensor, Tensor, Tensor, Tensor, Tensor)", &ep_row_tables);
   m.def("gemm_grouped_dispatch(Tensor src_ptrs, int ld_src, Tensor row_src, Tensor w, Tensor blk_expert, Tensor(a!) stage, Tensor(b!) flags, bool transposed=False) -> Tensor", &gemm_grouped_dispatch);
   m.def("gemm_grouped_combine(Tensor x, Tensor w, Tensor blk_expert, Tensor row_dst, Tensor row_w, Tensor out_ptrs, int ld_out, bool transposed=False) -> ()", &gemm_grouped_combine);
   m.def("gemm_grouped(Tensor x, Tensor w, Tensor blk_expert, bool transposed) -> Tensor", &gemm_grouped);

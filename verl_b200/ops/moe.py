@@ -165,6 +165,11 @@ def ep_row_tables(idx_all: torch.Tensor, w_all: torch.Tensor, rank: int, e_local
     Returns ``row_src`` int32 [R] ((source rank << 24) | token, −1 padding), ``row_dst`` int32 [R] ((source rank << 24) | (slot·Tc +
     token)), ``row_w`` fp32 [R], ``blk_expert`` int32 [R/128], ``expert_rng`` int32 [e_local, 2]."""
     W, Tc, k = idx_all.shape
+    if idx_all.is_cuda:
+        from . import _ext
+
+        if _ext.available():      # three launches on the device (csrc/moe_tables.cu) instead of the tensor ops below
+            return _ext.ops().ep_row_tables(idx_all.to(torch.int32).contiguous(), w_all.float().contiguous(), int(rank), int(e_local))
     lo = rank * e_local
     dev = idx_all.device
     flat = idx_all.reshape(-1)
@@ -246,7 +251,7 @@ class _FusedEPMoE(torch.autograd.Function):
         w_all = torch.empty(W, Tc, k, dtype=torch.float32, device=dev)
         dist.all_gather_into_tensor(idx_all, idx_pad, group=fctx.group)
         dist.all_gather_into_tensor(w_all, w_pad, group=fctx.group)
-        row_src, row_dst, row_w, blk_expert, rng = ep_row_tables(idx_all.long(), w_all, rank, e_local)
+        row_src, row_dst, row_w, blk_expert, rng = ep_row_tables(idx_all, w_all, rank, e_local)
         R = row_src.numel()
         fctx.publish(x.detach().contiguous())
         xg = torch.empty(R, H, dtype=torch.bfloat16, device=dev)          # the gathered operand, written by the kernel
