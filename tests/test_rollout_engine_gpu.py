@@ -159,8 +159,8 @@ def test_activation_offload_keeps_gradients_and_moves_the_saved_tensors_to_the_h
     from verl_b200.workers.engine.fsdp.engine import FSDPEngine
 
     res = {}
-    for off in (False, True):
-        eng = FSDPEngine({"preset": "tiny-qwen2-gpu", "enable_activation_offload": off, "activation_offload_min_numel": 4096}, {"seed": 1},
+    for off in (False, "again", True):
+        eng = FSDPEngine({"preset": "tiny-qwen2-gpu", "enable_activation_offload": off is True, "activation_offload_min_numel": 4096}, {"seed": 1},
                          {"lr": 1e-3, "clip_grad": 1.0}, {})
         eng.initialize()
         data = make_batch(bs=8, P=70, R=90, vocab=4096)
@@ -169,7 +169,37 @@ def test_activation_offload_keeps_gradients_and_moves_the_saved_tensors_to_the_h
         eng.forward_backward_batch(data, loss_fn)
         torch.cuda.synchronize()
         res[off] = (eng.store.grad.clone(), eng.optimizer_step())
-        if off:
+        if off is True:
             assert eng.model._activation_offloader.bytes_offloaded > 1 << 20
-    rel = ((res[True][0] - res[False][0]).norm() / res[False][0].norm()).item()          # fp32 atomics in the attention backward reorder sums
-    assert rel < 1e-3 and abs(res[True][1] - res[False][1]) < 1e-3 * res[False][1], (rel, res[True][1], res[False][1])
+    # two plain runs are bit-identical; the offloaded run hands backward fresh, aligned copies of the saved tensors, which may take
+    # another GEMM path than a view of a larger buffer does, so it agrees to bf16 rounding, with the same gradient norm. That the
+    # copies themselves are exact is checked tensor by tensor in the next test.
+    noise = ((res["again"][0] - res[False][0]).norm() / res[False][0].norm()).item()
+    rel = ((res[True][0] - res[False][0]).norm() / res[False][0].norm()).item()
+    assert noise < 1e-6 and rel < 5e-3, (rel, noise)
+    assert abs(res[True][1] - res[False][1]) < 1e-4 * res[False][1], (res[True][1], res[False][1])
+
+
+def test_activation_offload_round_trip_is_bit_exact_and_ordered():
+    """Every tensor saved under the hooks comes back with exactly its bytes, whatever the order backward asks for them in, and
+    small / non-contiguous / parameter tensors are left on the device."""
+    from verl_b200.utils.activation_offload import ActivationOffloader
+
+    off = ActivationOffloader(min_numel=1024, prefetch=True)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    src = [torch.randn(257, 129, device="cuda", generator=g).to(dt) for dt in (torch.bfloat16, torch.float32, torch.bfloat16, torch.float16)]
+    small = torch.randn(8, device="cuda")
+    strided = torch.randn(64, 64, device="cuda").t()
+    par = torch.nn.Parameter(torch.randn(64, 64, device="cuda"))
+    keep = [t.clone() for t in src]
+    packed = [off.pack(t) for t in src]
+    assert all(isinstance(p, tuple) for p in packed)
+    assert off.pack(small) is small and off.pack(strided) is strided and off.pack(par) is par
+    off.stream.synchronize()
+    for t in src:                                     # once the copies have landed the device originals may be overwritten
+        t.zero_()
+    for i in (3, 2, 0, 1):                            # backward order, then out of order
+        back = off.unpack(packed[i])
+        assert back.is_cuda and back.dtype == keep[i].dtype and torch.equal(back, keep[i])
+    assert off.bytes_offloaded == sum(t.numel() * t.element_size() for t in keep)
+    assert off.unpack(small) is small

@@ -192,6 +192,39 @@ def test_v1_separate_async_lends_the_training_engine_while_it_would_wait(tmp_pat
     assert abs(tr._switch_threshold_ratio - 1.0 / tr.parameter_sync_step) < 1e-9
 
 
+def test_v1_separate_async_lending_driven_by_a_registered_policy(tmp_path):
+    """The same lending, decided by a pluggable dynamic-schedule policy (``hybrid_rollout.policy``) through the resource
+    controller: the fixed-ratio policy lends after every step that leaves a gap and takes the engine back at ratio x batch."""
+    import os
+
+    from verl_b200.experimental.fully_async_policy.dynamic_schedule import FixedRatioDynamicSchedulePolicy
+    from verl_b200.trainer.ppo.v1.trainer_separate_async import HybridEngineMode
+
+    logf = tmp_path / "lend_policy.jsonl"
+    os.environ["VERL_FILE_LOGGER_PATH"] = str(logf)
+    try:
+        cfg = load_config("ppo_trainer", [o for o in OV if not o.startswith("trainer.logger")] +
+                          ["trainer.logger=[file]", "trainer.total_training_steps=3", f"trainer.default_local_dir={tmp_path}/ckpt_lend_policy",
+                           "actor_rollout_ref.rollout.mode=async", "actor_rollout_ref.rollout.free_cache_engine=false", "trainer.resume_mode=disable",
+                           "+trainer.v1.max_off_policy_threshold=4", "+trainer.v1.async_warmup_batches=0", "+trainer.v1.rollout_num_blocks=64",
+                           "trainer.v1.separate_async.hybrid_rollout.enable_switch=true", "trainer.v1.separate_async.hybrid_rollout.switch_threshold_ratio=0.5",
+                           "trainer.v1.separate_async.hybrid_rollout.policy=fixed_ratio"])
+        tr = get_trainer_cls("separate_async")(cfg, reward_fn=load_reward_manager(cfg, None))
+        tr.init()
+        ctl = tr._controller
+        assert isinstance(ctl.policy, FixedRatioDynamicSchedulePolicy) and ctl.policy.deactivate_ratio == 0.5 and not ctl.only_hybrid
+        assert tr._switch_threshold() == tr.train_batch_size            # nothing lent yet: the policy asks for no take-back
+        tr.fit()
+    finally:
+        os.environ.pop("VERL_FILE_LOGGER_PATH", None)
+    rows = [json.loads(x)["data"] for x in logf.read_text().splitlines()]
+    assert len(rows) == 3 and all(r["perf/total_num_tokens"] > 0 for r in rows)
+    assert ctl.activate_count >= 1 and ctl.activate_count == ctl.deactivate_count and not ctl.is_hybrid_active
+    assert [k for k, _ in tr.switch_log].count("rollout") == ctl.activate_count and tr.current_mode == HybridEngineMode.TRAINER
+    assert rows[0]["dynamic_schedule/want_activate"] == 1.0 and rows[-1]["dynamic_schedule/want_activate"] == 0.0    # no step left to lend for
+    assert rows[0]["dynamic_schedule/deactivate_ratio"] == 0.5 and ctl.last_activate_duration_s > 0 and ctl.last_deactivate_duration_s > 0
+
+
 def test_transfer_queue_over_tcp_between_processes(tmp_path):
     """A served TransferQueue: a child process writes trajectories, this process blocks on the server until they are tagged
     finished, reads them back as a batch and sees the child's tags; server-side errors come back as exceptions."""

@@ -107,6 +107,10 @@ class HybridRolloutSwitchConfig(BaseConfig):
     switch_threshold_step_down: float = 0.03
     switch_threshold_release_steps: int = 2
     switch_cost_window_size: int = 3
+    # name of a registered dynamic-schedule policy (default / fixed_ratio / static_fully_async / a custom one) that replaces
+    # the built-in threshold logic; null keeps the built-in one
+    policy: Any = None
+    policy_kwargs: dict = field(default_factory=dict)
 
 
 @dataclass

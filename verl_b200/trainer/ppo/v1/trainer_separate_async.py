@@ -46,6 +46,28 @@ class HybridEngineMode(enum.Enum):
     ROLLOUT = "rollout"
 
 
+class _Lender:
+    """What the dynamic-schedule controller drives: the trainer's two mode switches and the balancer's sticky-session table."""
+
+    def __init__(self, trainer: "PPOTrainerSeparateAsync"):
+        self.t = trainer
+
+    def activate(self):
+        self.t.switch_to_rollout()
+
+    def deactivate(self):
+        self.t.switch_to_trainer()
+
+    def rebalance(self):
+        """Forget which server each open conversation was pinned to, so that follow-up turns go to the least-loaded server —
+        the engines that just joined start empty."""
+        bal = getattr(self.t._servers, "balancer", None)
+        n = len(bal.sticky) if bal is not None else 0
+        if bal is not None:
+            bal.sticky.clear()
+        return {"cleared_entries": n}
+
+
 @register_trainer("separate_async")
 class PPOTrainerSeparateAsync(PPOTrainer):
     resumable_generation = True
@@ -134,6 +156,41 @@ class PPOTrainerSeparateAsync(PPOTrainer):
         standalone = max(1, len(self.replicas))
         self._scaling_factor = (self.world + standalone) / standalone          # generation capacity with / without the lent GPUs
         self.switch_log: list = []
+        self._consumed_groups = 0
+        self._controller = None
+        if c.policy:
+            from verl_b200.experimental.fully_async_policy.dynamic_schedule import DynamicResourceController
+
+            kw = dict(c.policy_kwargs or {})
+            kw.setdefault("deactivate_ratio", float(c.switch_threshold_ratio))
+            self._controller = DynamicResourceController(_Lender(self), num_standalone_replicas=len(self.replicas), num_hybrid_replicas=self.world,
+                                                         policy=str(c.policy), policy_kwargs=kw)
+
+    def _schedule_context(self, next_step: int):
+        """What the lending policy sees, with every number agreed across the training ranks. Units are prompt groups: one
+        collection is one mini-batch, one cycle (``parameter_sync_step`` collections) is one training batch."""
+        from verl_b200.experimental.fully_async_policy.dynamic_schedule import DynamicScheduleContext
+
+        mini = max(1, self.train_batch_size // self.parameter_sync_step)
+        ready = self._sampleable(next_step)
+        wait_s = self._agree(self._step_sample_wait_seconds, "max")
+        wait_n = int(self._agree(float(self._step_wait_samples), "max")) * self.world
+        poll = max(5.0 * float(getattr(self.replay_buffer, "poll_interval_s", 0.01)), 0.05)
+        waited = wait_s > poll and wait_n > 0
+        ctl = self._controller
+        ctx = DynamicScheduleContext(required_samples=mini, trigger_parameter_sync_step=self.parameter_sync_step,
+                                     total_generated_samples=self._consumed_groups + ready, expected_samples=self._consumed_groups,
+                                     buffer_samples=int(getattr(self.replay_buffer, "max_off_policy_threshold", 1) or 1) * self.train_batch_size,
+                                     step_wait_times=[wait_s] if waited else [], step_wait_samples=[wait_n] if waited else [])
+        ctx.last_activate_duration_s = self._agree(ctl.last_activate_duration_s, "max")
+        ctx.last_deactivate_duration_s = self._agree(ctl.last_deactivate_duration_s, "max")
+        return ctx
+
+    def _take_back(self):
+        if self._controller is not None:
+            self._controller.deactivate(self.global_steps)
+        else:
+            self.switch_to_trainer()
 
     def _agree(self, value: float, op: str) -> float:
         """The controller runs on every rank; decisions that change collective behaviour use the same number everywhere."""
@@ -151,6 +208,11 @@ class PPOTrainerSeparateAsync(PPOTrainer):
     def _switch_threshold(self) -> int:
         """Prompt groups that must be sampleable before the training GPUs are taken back (at least one mini-batch)."""
         mini = max(1, self.train_batch_size // self.parameter_sync_step)
+        if self._controller is not None:
+            # training cannot start on lent GPUs: a policy that would rather keep them lent still hands them back once the
+            # whole batch is there
+            need = self._controller.wait_threshold(self.global_steps, self._schedule_context(self.global_steps))
+            return self.train_batch_size if need is None else min(need, self.train_batch_size)
         return min(max(round(self._switch_threshold_ratio * self.train_batch_size), mini), self.train_batch_size)
 
     def _sampleable(self, step: int) -> int:
@@ -201,6 +263,12 @@ class PPOTrainerSeparateAsync(PPOTrainer):
     def _lending_decision(self, total_steps: int) -> dict:
         """After a step: adapt the threshold, then lend the GPUs for the coming wait if that is expected to pay."""
         c = self.hybrid_rollout_config
+        self._consumed_groups += self.train_batch_size
+        if self._controller is not None:
+            ctl = self._controller
+            ctl.last_activate_duration_s = self._to_rollout_costs[-1] if self._to_rollout_costs else 0.0
+            ctl.last_deactivate_duration_s = self._to_trainer_costs[-1] if self._to_trainer_costs else 0.0
+            return ctl.after_weight_sync(self.global_steps, self._schedule_context(self.global_steps + 1), more_steps=self.global_steps < total_steps)
         poll = max(5.0 * float(getattr(self.replay_buffer, "poll_interval_s", 0.01)), 0.05)
         had_idle = self._agree(self._step_sample_wait_seconds, "max") > poll        # the step really waited for trajectories
         if self._step_wait_samples > 0 and self._step_sample_wait_seconds > 0:
@@ -263,7 +331,7 @@ class PPOTrainerSeparateAsync(PPOTrainer):
         self._step_sample_wait_seconds = 0.0
         self._step_wait_samples = 0
         if self.current_mode == HybridEngineMode.ROLLOUT and self._sampleable(self.global_steps) >= self._switch_threshold():
-            self.switch_to_trainer()
+            self._take_back()
 
     def on_sample_begin(self):
         need = max(1, self.train_batch_size // self.world)
@@ -275,7 +343,7 @@ class PPOTrainerSeparateAsync(PPOTrainer):
                 # the GPUs stay lent until enough of the batch exists; training cannot start before they are back
                 self.replay_buffer.wait_for_sampleable(self.global_steps, self.partition_id, max(1, self._switch_threshold() // self.world))
                 self._agree(0.0, "max")                # every rank has reached its share: switch together
-                self.switch_to_trainer()
+                self._take_back()
         self.replay_buffer.wait_for_sampleable(self.global_steps, self.partition_id, need)
 
     def on_sample_end(self):
@@ -291,11 +359,11 @@ class PPOTrainerSeparateAsync(PPOTrainer):
 
     def on_validate_begin(self):
         if self._switch_enabled and self.current_mode == HybridEngineMode.ROLLOUT:
-            self.switch_to_trainer()               # validation generates on the colocated engine through the stage trainer
+            self._take_back()               # validation generates on the colocated engine through the stage trainer
 
     def on_train_end(self):
         if self._switch_enabled and self.current_mode == HybridEngineMode.ROLLOUT:
-            self.switch_to_trainer()
+            self._take_back()
         self.agent_loop.shutdown()
         for r in getattr(self, "_owned", []):
             r.shutdown()
