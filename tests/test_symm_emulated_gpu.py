@@ -106,6 +106,14 @@ def test_allgather_a_and_b_fused_into_the_gemm(o, staged):
             out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
             o.gemm_allgather_a(_table(xs), T // W, w, out, bias, r, stage_a, flags_a, ep)
             assert _rel(out, ep * ref + bias.float()) < 1e-2, (r, ep)
+            if staged:      # the same product from the weight stored [K, N] (backward of a row-parallel layer); the peers' rows
+                outt = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)     # of the gathered operand are left in the staging buffer
+                o.gemm_allgather_a(_table(xs), T // W, w.t().contiguous(), outt, None, r, stage_a, flags_a, ep + 10, True)
+                assert _rel(outt, ep * ref) < 1e-2, (r, ep)
+                got = stage_a.view(T, H)
+                for q in range(W):
+                    if q != r:
+                        assert torch.equal(got[q * (T // W):(q + 1) * (T // W)], xs[q])
             out2 = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
             ws = [s * ep for s in w_seg]
             o.gemm_allgather_b(x, _table(ws), N // W, out2, None, r, stage_b, flags_b, ep)
@@ -127,7 +135,10 @@ def test_peer_scatter_epilogue_and_slot_sum(o, scatter_rows):
     slots = [torch.full((W * slot_elems,), 9.0, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
     for r in range(W):                                                # rank r owns K slice r and writes slot r of every receiver
         xk, wk = x[:, r * Kl:(r + 1) * Kl].contiguous(), w[:, r * Kl:(r + 1) * Kl].contiguous()
-        o.gemm_peer_scatter(xk, wk, _table(slots), r, T // W if scatter_rows else 0, slot_elems)
+        if r % 2 == 0:
+            o.gemm_peer_scatter(xk, wk, _table(slots), r, T // W if scatter_rows else 0, slot_elems)
+        else:               # odd ranks pass the weight slice stored [K, N] (the layout an activation-gradient GEMM sees)
+            o.gemm_peer_scatter(xk, wk.t().contiguous(), _table(slots), r, T // W if scatter_rows else 0, slot_elems, True)
     res = torch.randn(rows, N, device="cuda").bfloat16()
     for r in range(W):
         out = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
@@ -202,6 +213,20 @@ def test_ulysses_head_scatter_and_k_segmented_gather(o):
             out = torch.empty(Tl, hidden, device="cuda", dtype=torch.bfloat16)
             o.gemm_kseg(_table(o_bufs), Kl, Tp, r * Tl, w_o, out, None, r, st, flags if st is not None else None, ep)
             assert _rel(out, ref[r * Tl:(r + 1) * Tl]) < 1e-2, (r, ep)
+        out = torch.empty(Tl, hidden, device="cuda", dtype=torch.bfloat16)
+        o.gemm_kseg(_table(o_bufs), Kl, Tp, r * Tl, w_o.t().contiguous(), out, None, r, stage, flags, 3, True)      # weight stored [K, N]
+        assert _rel(out, ref[r * Tl:(r + 1) * Tl]) < 1e-2, r
+    # backward of the output projection: (dY @ W_o) with the sequence -> head routing in the epilogue, W_o as the forward stores it
+    dy = torch.randn(Tp, hidden, device="cuda").bfloat16()
+    dbufs = [torch.full((Tp * Kl + 64,), 5.0, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    q_rank = torch.tensor([h // hq_l for h in range(Hq)], dtype=torch.int32)
+    q_slot = torch.tensor([h % hq_l for h in range(Hq)], dtype=torch.int32)
+    for r in range(W):
+        o.gemm_head_scatter(dy[r * Tl:(r + 1) * Tl].contiguous(), w_o, None, _table(dbufs), Kl, r * Tl, D, q_rank, q_slot, True)
+    want = dy.float() @ w_o.float()
+    for r in range(W):
+        assert _rel(dbufs[r][: Tp * Kl].view(Tp, Kl), want[:, r * Kl:(r + 1) * Kl]) < 1e-2, r
+        assert torch.all(dbufs[r][Tp * Kl:] == 5.0)
     _status_clean(o)
 
 

@@ -55,10 +55,10 @@ int vb_attn_varlen_bwd(const void* q, const void* k, const void* v, long ld, con
                        cudaStream_t st);
 
 int vb_gemm_allgather(int which, const long* seg_ptrs, int world, int seg_rows, int ld_seg, const void* other, int ld_other, void* C,
-                      const void* bias, int M, int N, int K, int ldc, int rank, void* stage, int* stage_flags, int stage_epoch, int* err_word,
-                      cudaStream_t st);
+                      const void* bias, int M, int N, int K, int ldc, int rank, void* stage, int* stage_flags, int stage_epoch, int b_mn,
+                      int* err_word, cudaStream_t st);
 int vb_gemm_peer_scatter(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int ld_slot, const long* out_ptrs,
-                         int rank, int world, int rows_per_owner, long slot_elems, int* err_word, cudaStream_t st);
+                         int rank, int world, int rows_per_owner, long slot_elems, int b_mn, int* err_word, cudaStream_t st);
 int vb_slots_reduce(const void* slots, int world, long slot_elems, long rows, int cols, int ld, const void* residual, void* out,
                     int ld_out, cudaStream_t st);
 long vb_symm_alloc(long nbytes);
@@ -78,10 +78,10 @@ int vb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* bias, i
                       int b_mn, int out_f32, int accumulate, int* err_word, cudaStream_t stream);
 int vb_fp8_block_cast(const void* x, long ldx, void* y, long ldy, float* scale, int M, int N, cudaStream_t st);
 int vb_gemm_head_scatter(const void* A, const void* B, const void* bias, int M, int N, int K, int lda, int ldb, int ld_out, const long* out_ptrs,
-                         int world, int row_off, int head_dim, const int* head_rank, const int* head_slot, int* err_word, cudaStream_t st);
+                         int world, int row_off, int head_dim, const int* head_rank, const int* head_slot, int b_mn, int* err_word, cudaStream_t st);
 int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int ld_seg, int rows_total, int row_off, const void* B, int ldb, void* C,
-                 const void* bias, int M, int N, int ldc, int rank, void* stage, int* stage_flags, int stage_epoch, int* err_word,
-                 cudaStream_t st);
+                 const void* bias, int M, int N, int ldc, int rank, void* stage, int* stage_flags, int stage_epoch, int b_mn,
+                 int* err_word, cudaStream_t st);
 int vb_fp8_row_cast(const void* x, long ldx, void* y, long ldy, float* scale, long M, int K, cudaStream_t st);
 int vb_gemm_fp8_pair(const void* A, const void* B, void* C, const void* bias, const float* a_scale, const float* b_scale, int M, int N, int K,
                      int lda, int ldb, int ldc, int out_f32, int* err_word, cudaStream_t stream);

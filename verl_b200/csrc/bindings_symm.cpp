@@ -123,17 +123,18 @@ static Stage stage_of(const c10::optional<Tensor>& stage, const c10::optional<Te
   return s;
 }
 
+// transposed = true: b is stored [K, N] (the weight of the forward pass used for its activation gradient)
 void gemm_allgather_a(const Tensor& a_ptrs, int64_t seg_rows, const Tensor& b, Tensor& out, const c10::optional<Tensor>& bias, int64_t rank,
-                      const c10::optional<Tensor>& stage, const c10::optional<Tensor>& flags, int64_t epoch) {
+                      const c10::optional<Tensor>& stage, const c10::optional<Tensor>& flags, int64_t epoch, bool transposed) {
   TORCH_CHECK(a_ptrs.scalar_type() == at::kLong && !a_ptrs.is_cuda(), "gemm_allgather_a: pointer table must be a CPU int64 tensor");
   TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.dim() == 2 && b.stride(1) == 1, "gemm_allgather_a: bad b");
-  const int world = a_ptrs.numel(), K = b.size(1), N = b.size(0), M = seg_rows * world;
+  const int world = a_ptrs.numel(), K = transposed ? b.size(0) : b.size(1), N = transposed ? b.size(1) : b.size(0), M = seg_rows * world;
   TORCH_CHECK(out.size(0) == M && out.size(1) == N && out.scalar_type() == at::kBFloat16 && out.stride(1) == 1, "gemm_allgather_a: bad out");
   const void* bias_p = (bias.has_value() && bias->defined()) ? bias->data_ptr() : nullptr;
   c10::cuda::CUDAGuard guard(b.device());
   const Stage st = stage_of(stage, flags, (int64_t)M * K, M / 128);
   check_rc(vb_gemm_allgather(0, a_ptrs.data_ptr<long>(), world, (int)seg_rows, K, b.data_ptr(), (int)b.stride(0), out.data_ptr(), bias_p, M, N, K,
-                             (int)out.stride(0), (int)rank, st.ptr, st.flags, (int)epoch, vb_status_tensor(b.get_device()).data_ptr<int>(), cur_stream()),
+                             (int)out.stride(0), (int)rank, st.ptr, st.flags, (int)epoch, transposed ? 1 : 0, vb_status_tensor(b.get_device()).data_ptr<int>(), cur_stream()),
            "gemm_allgather_a");
 }
 
@@ -148,33 +149,35 @@ void gemm_allgather_b(const Tensor& a, const Tensor& b_ptrs, int64_t seg_rows, T
   c10::cuda::CUDAGuard guard(a.device());
   const Stage st = stage_of(stage, flags, (int64_t)N * K, N / 128);
   check_rc(vb_gemm_allgather(1, b_ptrs.data_ptr<long>(), world, (int)seg_rows, K, a.data_ptr(), (int)a.stride(0), out.data_ptr(), bias_p, M, N, K,
-                             (int)out.stride(0), (int)rank, st.ptr, st.flags, (int)epoch, vb_status_tensor(a.get_device()).data_ptr<int>(), cur_stream()),
+                             (int)out.stride(0), (int)rank, st.ptr, st.flags, (int)epoch, 0, vb_status_tensor(a.get_device()).data_ptr<int>(), cur_stream()),
            "gemm_allgather_b");
 }
 
-void gemm_peer_scatter(const Tensor& a, const Tensor& b, const Tensor& out_ptrs, int64_t rank, int64_t rows_per_owner, int64_t slot_elems) {
+void gemm_peer_scatter(const Tensor& a, const Tensor& b, const Tensor& out_ptrs, int64_t rank, int64_t rows_per_owner, int64_t slot_elems, bool transposed) {
   TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_peer_scatter: bad operands");
   TORCH_CHECK(out_ptrs.scalar_type() == at::kLong && !out_ptrs.is_cuda(), "gemm_peer_scatter: pointer table must be a CPU int64 tensor");
-  const int M = a.size(0), K = a.size(1), N = b.size(0), world = out_ptrs.numel();
+  const int M = a.size(0), K = a.size(1), N = transposed ? b.size(1) : b.size(0), world = out_ptrs.numel();
+  TORCH_CHECK((transposed ? b.size(0) : b.size(1)) == K, "gemm_peer_scatter: inner dimensions differ");
   c10::cuda::CUDAGuard guard(a.device());
   check_rc(vb_gemm_peer_scatter(a.data_ptr(), b.data_ptr(), M, N, K, (int)a.stride(0), (int)b.stride(0), N, out_ptrs.data_ptr<long>(), (int)rank,
-                                world, (int)rows_per_owner, slot_elems, vb_status_tensor(a.get_device()).data_ptr<int>(), cur_stream()),
+                                world, (int)rows_per_owner, slot_elems, transposed ? 1 : 0, vb_status_tensor(a.get_device()).data_ptr<int>(), cur_stream()),
            "gemm_peer_scatter");
 }
 
 // Ulysses, sequence → heads: (a [M, K] token shard) @ (b [N, K])^T (+bias); head h of the result goes to rank head_rank[h],
 // head slot head_slot[h], rows [row_off, row_off + M) of that rank's [*, ld_out] buffer.
 void gemm_head_scatter(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& bias, const Tensor& out_ptrs, int64_t ld_out,
-                       int64_t row_off, int64_t head_dim, const Tensor& head_rank, const Tensor& head_slot) {
+                       int64_t row_off, int64_t head_dim, const Tensor& head_rank, const Tensor& head_slot, bool transposed) {
   TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_head_scatter: bad operands");
   TORCH_CHECK(out_ptrs.scalar_type() == at::kLong && !out_ptrs.is_cuda(), "gemm_head_scatter: pointer table must be a CPU int64 tensor");
   TORCH_CHECK(head_rank.scalar_type() == at::kInt && head_slot.scalar_type() == at::kInt && !head_rank.is_cuda() && !head_slot.is_cuda(), "gemm_head_scatter: head tables must be CPU int32");
-  const int M = a.size(0), K = a.size(1), N = b.size(0), world = out_ptrs.numel();
+  const int M = a.size(0), K = a.size(1), N = transposed ? b.size(1) : b.size(0), world = out_ptrs.numel();
+  TORCH_CHECK((transposed ? b.size(0) : b.size(1)) == K, "gemm_head_scatter: inner dimensions differ");
   TORCH_CHECK(head_rank.numel() * head_dim == N && head_slot.numel() == head_rank.numel(), "gemm_head_scatter: head tables do not cover N");
   const void* bias_p = (bias.has_value() && bias->defined()) ? bias->data_ptr() : nullptr;
   c10::cuda::CUDAGuard guard(a.device());
   check_rc(vb_gemm_head_scatter(a.data_ptr(), b.data_ptr(), bias_p, M, N, K, (int)a.stride(0), (int)b.stride(0), (int)ld_out, out_ptrs.data_ptr<long>(),
-                                world, (int)row_off, (int)head_dim, head_rank.data_ptr<int>(), head_slot.data_ptr<int>(),
+                                world, (int)row_off, (int)head_dim, head_rank.data_ptr<int>(), head_slot.data_ptr<int>(), transposed ? 1 : 0,
                                 vb_status_tensor(a.get_device()).data_ptr<int>(), cur_stream()),
            "gemm_head_scatter");
 }
@@ -182,17 +185,18 @@ void gemm_head_scatter(const Tensor& a, const Tensor& b, const c10::optional<Ten
 // Ulysses, heads → sequence: out [M, N] = A @ b^T where A's K axis is split over ranks: rank r holds columns
 // [r * k_per_rank, ...) as rows [row_off, row_off + M) of its [rows_total, k_per_rank] buffer a_ptrs[r].
 void gemm_kseg(const Tensor& a_ptrs, int64_t k_per_rank, int64_t rows_total, int64_t row_off, const Tensor& b, Tensor& out,
-               const c10::optional<Tensor>& bias, int64_t rank, const c10::optional<Tensor>& stage, const c10::optional<Tensor>& flags, int64_t epoch) {
+               const c10::optional<Tensor>& bias, int64_t rank, const c10::optional<Tensor>& stage, const c10::optional<Tensor>& flags, int64_t epoch,
+               bool transposed) {
   TORCH_CHECK(a_ptrs.scalar_type() == at::kLong && !a_ptrs.is_cuda(), "gemm_kseg: pointer table must be a CPU int64 tensor");
   TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.dim() == 2 && b.stride(1) == 1, "gemm_kseg: bad b");
-  const int world = a_ptrs.numel(), N = b.size(0), M = out.size(0);
-  TORCH_CHECK(b.size(1) == world * k_per_rank && out.size(1) == N && out.scalar_type() == at::kBFloat16 && out.stride(1) == 1, "gemm_kseg: bad shapes");
+  const int world = a_ptrs.numel(), N = transposed ? b.size(1) : b.size(0), M = out.size(0);
+  TORCH_CHECK((transposed ? b.size(0) : b.size(1)) == world * k_per_rank && out.size(1) == N && out.scalar_type() == at::kBFloat16 && out.stride(1) == 1, "gemm_kseg: bad shapes");
   const void* bias_p = (bias.has_value() && bias->defined()) ? bias->data_ptr() : nullptr;
   c10::cuda::CUDAGuard guard(b.device());
   const int64_t Mp = (M + 127) / 128 * 128;
   const Stage st = stage_of(stage, flags, Mp * world * k_per_rank, (Mp / 128) * world);
   check_rc(vb_gemm_kseg(a_ptrs.data_ptr<long>(), world, (int)k_per_rank, (int)k_per_rank, (int)rows_total, (int)row_off, b.data_ptr(), (int)b.stride(0),
-                        out.data_ptr(), bias_p, M, N, (int)out.stride(0), (int)rank, st.ptr, st.flags, (int)epoch,
+                        out.data_ptr(), bias_p, M, N, (int)out.stride(0), (int)rank, st.ptr, st.flags, (int)epoch, transposed ? 1 : 0,
                         vb_status_tensor(b.get_device()).data_ptr<int>(), cur_stream()),
            "gemm_kseg");
 }
@@ -238,11 +242,11 @@ void slots_reduce(const Tensor& slots, int64_t world, int64_t slot_elems, int64_
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(verl_b200, m) {
-  m.def("gemm_allgather_a(Tensor a_ptrs, int seg_rows, Tensor b, Tensor(a!) out, Tensor? bias, int rank=0, Tensor? stage=None, Tensor? flags=None, int epoch=0) -> ()", &gemm_allgather_a);
+  m.def("gemm_allgather_a(Tensor a_ptrs, int seg_rows, Tensor b, Tensor(a!) out, Tensor? bias, int rank=0, Tensor? stage=None, Tensor? flags=None, int epoch=0, bool transposed=False) -> ()", &gemm_allgather_a);
   m.def("gemm_allgather_b(Tensor a, Tensor b_ptrs, int seg_rows, Tensor(a!) out, Tensor? bias, int rank=0, Tensor? stage=None, Tensor? flags=None, int epoch=0) -> ()", &gemm_allgather_b);
-  m.def("gemm_peer_scatter(Tensor a, Tensor b, Tensor out_ptrs, int rank, int rows_per_owner, int slot_elems) -> ()", &gemm_peer_scatter);
-  m.def("gemm_head_scatter(Tensor a, Tensor b, Tensor? bias, Tensor out_ptrs, int ld_out, int row_off, int head_dim, Tensor head_rank, Tensor head_slot) -> ()", &gemm_head_scatter);
-  m.def("gemm_kseg(Tensor a_ptrs, int k_per_rank, int rows_total, int row_off, Tensor b, Tensor(a!) out, Tensor? bias, int rank=0, Tensor? stage=None, Tensor? flags=None, int epoch=0) -> ()", &gemm_kseg);
+  m.def("gemm_peer_scatter(Tensor a, Tensor b, Tensor out_ptrs, int rank, int rows_per_owner, int slot_elems, bool transposed=False) -> ()", &gemm_peer_scatter);
+  m.def("gemm_head_scatter(Tensor a, Tensor b, Tensor? bias, Tensor out_ptrs, int ld_out, int row_off, int head_dim, Tensor head_rank, Tensor head_slot, bool transposed=False) -> ()", &gemm_head_scatter);
+  m.def("gemm_kseg(Tensor a_ptrs, int k_per_rank, int rows_total, int row_off, Tensor b, Tensor(a!) out, Tensor? bias, int rank=0, Tensor? stage=None, Tensor? flags=None, int epoch=0, bool transposed=False) -> ()", &gemm_kseg);
   m.def("gemm_allreduce_sig(Tensor a, Tensor b, Tensor out_ptrs, Tensor sig_ptrs, int rank, int half_elems, Tensor slots_local, Tensor sig_local, Tensor? residual, Tensor(a!) out, int bn=0, int split_k=0, int max_split=8, int phase=0) -> ()", &gemm_allreduce_sig);
   m.def("slots_reduce(Tensor slots, int world, int slot_elems, int rows, int cols, Tensor? residual, Tensor(a!) out) -> ()", &slots_reduce);
 }

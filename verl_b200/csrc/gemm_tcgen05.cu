@@ -1226,24 +1226,24 @@ __global__ void slots_reduce_kernel(const bf16* __restrict__ slots, int world, l
   }
 }
 
-template <int EPI>
+template <int EPI, bool B_MN = false>
 static int launch_dist(int bn, const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb, int ldc,
                        int* err_word, cudaStream_t st, const DistArgs& d, int split_k = 1) {
   if constexpr (EPI == EPI_STORE) {
     if (d.stage != nullptr) {
       switch (bn) {
-        case 256: return launch_gemm<256, false, false, EPI, 8>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
-        case 128: return launch_gemm<128, false, false, EPI, 8>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
-        case 64: return launch_gemm<64, false, false, EPI, 8>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
+        case 256: return launch_gemm<256, false, B_MN, EPI, 8>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
+        case 128: return launch_gemm<128, false, B_MN, EPI, 8>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
+        case 64: return launch_gemm<64, false, B_MN, EPI, 8>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, 1, nullptr, &d);
         default: return -5;
       }
     }
   }
   if (EPI != EPI_PEER) split_k = 1;
   switch (bn) {
-    case 256: return launch_gemm<256, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, split_k, nullptr, &d);
-    case 128: return launch_gemm<128, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, split_k, nullptr, &d);
-    case 64: return launch_gemm<64, false, false, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, split_k, nullptr, &d);
+    case 256: return launch_gemm<256, false, B_MN, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, split_k, nullptr, &d);
+    case 128: return launch_gemm<128, false, B_MN, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, split_k, nullptr, &d);
+    case 64: return launch_gemm<64, false, B_MN, EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, err_word, st, LmHeadEpi{}, split_k, nullptr, &d);
     default: return -5;
   }
 }
@@ -1261,9 +1261,10 @@ static int pick_bn_dist(int M, int N) {
 // `world` equal segments; seg_ptrs[r] is rank r's segment ([seg_rows, K] bf16, row stride ld_seg) reachable from this GPU.
 extern "C" int vb_gemm_allgather(int which, const long* seg_ptrs, int world, int seg_rows, int ld_seg, const void* other, int ld_other,
                                  void* C, const void* bias, int M, int N, int K, int ldc, int rank, void* stage, int* stage_flags,
-                                 int stage_epoch, int* err_word, cudaStream_t st) {
+                                 int stage_epoch, int b_mn, int* err_word, cudaStream_t st) {
   using namespace vb;
   if (world > MAX_TP || world < 1) return -2;
+  if (b_mn && which != 0) return -2;             // the transposed form ([K, N] row-major) exists for the plain operand only
   const int rows_total = which == 0 ? M : N;
   if (seg_rows * world != rows_total || (ld_seg & 7) || (ld_other & 7)) return -4;
   const int bn = pick_bn_dist(M, N);
@@ -1290,20 +1291,22 @@ extern "C" int vb_gemm_allgather(int which, const long* seg_ptrs, int world, int
   // the unsegmented maps built by the launcher for the segmented operand are never used; give them legal extents
   const int Mm = which == 0 ? seg_rows : M, Nn = which == 1 ? seg_rows : N;
   (void)Mm; (void)Nn;
+  if (b_mn) return launch_dist<EPI_STORE, true>(bn, A, B, C, bias, M, N, K, lda, ldb, ldc, err_word, st, d);
   return launch_dist<EPI_STORE>(bn, A, B, C, bias, M, N, K, lda, ldb, ldc, err_word, st, d);
 }
 
 // GEMM whose epilogue scatters the bf16 result into peers' symmetric slot buffers (see DistArgs). rows_per_owner == 0:
 // every rank receives the whole [M,N] partial (all-reduce); > 0: only the owner of each row block (reduce-scatter).
 extern "C" int vb_gemm_peer_scatter(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int ld_slot,
-                                    const long* out_ptrs, int rank, int world, int rows_per_owner, long slot_elems, int* err_word,
-                                    cudaStream_t st) {
+                                    const long* out_ptrs, int rank, int world, int rows_per_owner, long slot_elems, int b_mn,
+                                    int* err_word, cudaStream_t st) {
   using namespace vb;
   if (world > MAX_TP || (N % 32) != 0 || (ld_slot & 7)) return -2;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -4;
   DistArgs d = {};
   d.rank = rank; d.world = world; d.rows_per_owner = rows_per_owner; d.slot_elems = slot_elems;
   for (int r = 0; r < world; ++r) d.peer_out[r] = reinterpret_cast<void*>(out_ptrs[r]);
+  if (b_mn) return launch_dist<EPI_PEER, true>(pick_bn_dist(M, N), A, B, nullptr, nullptr, M, N, K, lda, ldb, ld_slot, err_word, st, d);
   return launch_dist<EPI_PEER>(pick_bn_dist(M, N), A, B, nullptr, nullptr, M, N, K, lda, ldb, ld_slot, err_word, st, d);
 }
 
@@ -1469,7 +1472,7 @@ extern "C" int vb_gemm_grouped_wgrad(const void* dY, const void* X, void* dW, co
 // head_slot[h]. out_ptrs[r] = rank r's [T_total, ld_out] bf16 buffer.
 extern "C" int vb_gemm_head_scatter(const void* A, const void* B, const void* bias, int M, int N, int K, int lda, int ldb, int ld_out,
                                     const long* out_ptrs, int world, int row_off, int head_dim, const int* head_rank, const int* head_slot,
-                                    int* err_word, cudaStream_t st) {
+                                    int b_mn, int* err_word, cudaStream_t st) {
   using namespace vb;
   if (world > MAX_TP || head_dim <= 0 || (head_dim % 32) != 0 || (N % head_dim) != 0 || N / head_dim > 192 || (ld_out & 7)) return -2;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -4;
@@ -1480,6 +1483,7 @@ extern "C" int vb_gemm_head_scatter(const void* A, const void* B, const void* bi
     d.head_map[h] = (uint16_t)((head_rank[h] << 12) | head_slot[h]);
   }
   for (int r = 0; r < world; ++r) d.peer_out[r] = reinterpret_cast<void*>(out_ptrs[r]);
+  if (b_mn) return launch_dist<EPI_PEER, true>(pick_bn_dist(M, N), A, B, nullptr, bias, M, N, K, lda, ldb, ld_out, err_word, st, d);
   return launch_dist<EPI_PEER>(pick_bn_dist(M, N), A, B, nullptr, bias, M, N, K, lda, ldb, ld_out, err_word, st, d);
 }
 
@@ -1488,7 +1492,7 @@ extern "C" int vb_gemm_head_scatter(const void* A, const void* B, const void* bi
 // [T_total, k_per_rank] buffer (seg_ptrs[r], row stride ld_seg), read with TMA straight from that rank's memory.
 extern "C" int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int ld_seg, int rows_total, int row_off, const void* B, int ldb,
                             void* C, const void* bias, int M, int N, int ldc, int rank, void* stage, int* stage_flags, int stage_epoch,
-                            int* err_word, cudaStream_t st) {
+                            int b_mn, int* err_word, cudaStream_t st) {
   using namespace vb;
   if (world > MAX_TP || world < 1 || (k_per_rank % BK) != 0 || (ld_seg & 7) || (ldb & 7)) return -4;
   DistArgs d = {};
@@ -1505,6 +1509,8 @@ extern "C" int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int
     for (int r = 0; r < world; ++r) d.seg_ptr[r] = reinterpret_cast<const void*>(seg_ptrs[r]);
     if (make_tmap_2d(&d.stage_map, stage, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (M + 127) / 128 * 128, K, K, BM, BK)) return -1;
   }
+  if (b_mn)
+    return launch_dist<EPI_STORE, true>(pick_bn_dist(M, N), reinterpret_cast<const void*>(seg_ptrs[0]), B, C, bias, M, N, K, ld_seg, ldb, ldc, err_word, st, d);
   return launch_dist<EPI_STORE>(pick_bn_dist(M, N), reinterpret_cast<const void*>(seg_ptrs[0]), B, C, bias, M, N, K, ld_seg, ldb, ldc, err_word, st, d);
 }
 

@@ -290,8 +290,51 @@ def main():
         ms_f, ms_b = timer(lambda: fu.o_forward(o_loc, w_o, Tl)), timer(o_nccl)
         report(rank, f"head->seq all-to-all + output projection, {Tl} local tokens, SP={W}", ms_f, ms_b, 2.0 * Tl * H * Hq * D,
                (W - 1) * Tl * Hq * D * 2 // W)
+        # forward + backward of both projections: the backward routes d(attention output) through the scatter epilogue and
+        # gathers d(qkv) inside the activation-gradient GEMM; the baseline keeps the fused forward and uses all-to-alls in backward
+        from verl_b200.parallel.ulysses import _FusedOProj, _FusedQKV
+
+        wq_p, wo_p = torch.nn.Parameter(w_qkv.clone()), torch.nn.Parameter(w_o.clone())
+        for p_ in (wq_p, wo_p):
+            p_.main_grad = torch.zeros(p_.shape, device=dev, dtype=torch.float32)
+        g_qkv = torch.randn(T, fu.Cl, device=dev).bfloat16()
+        g_out = torch.randn(Tl, H, device=dev).bfloat16()
+
+        def sp_fb(fused_bwd):
+            fu.fused_backward = fused_bwd
+            xs = x_shard.clone().requires_grad_(True)
+            _FusedQKV.apply(xs, wq_p, None, fu).backward(g_qkv)
+            ol = o_loc.clone().requires_grad_(True)
+            _FusedOProj.apply(ol, wo_p, fu, Tl).backward(g_out)
+
+        ms_f, ms_b = timer(lambda: sp_fb(True)), timer(lambda: sp_fb(False))
+        fu.fused_backward = True
+        report(rank, f"Ulysses QKV + output projection, forward + backward, {Tl} local tokens, SP={W} (baseline: fused forward, all-to-all backward)",
+               ms_f, ms_b, 6.0 * Tl * H * (2 * Hq + 2 * Hkv) * D, 2 * (W - 1) * Tl * (2 * Hq + 2 * Hkv) * D * 2 // W)
     elif rank == 0:
         print(f"Ulysses paths skipped: {cfg.num_key_value_heads} KV heads do not divide by SP={W}")
+
+    # ---- 5. sequence-parallel TP block (column-parallel then row-parallel projection), forward + backward through autograd:
+    # backward = activation-gradient GEMM -> reduce-scatter epilogue (column-parallel) and all-gather -> activation-gradient GEMM
+    # whose staged operand also feeds the weight gradient (row-parallel)
+    from verl_b200.parallel.tp import allgather_linear, linear_reduce_scatter
+
+    w1 = torch.nn.Parameter((0.02 * torch.randn(F // W, H, device=dev)).bfloat16())
+    w2 = torch.nn.Parameter((0.02 * torch.randn(H, F // W, device=dev)).bfloat16())
+    for p_ in (w1, w2):
+        p_.main_grad = torch.zeros(p_.shape, device=dev, dtype=torch.float32)
+    g_sh = torch.randn(Tl, H, device=dev).bfloat16()
+
+    def tp_fb(env):
+        os.environ["VERL_B200_COMM"] = env
+        xs = x_shard.clone().requires_grad_(True)
+        y = allgather_linear(xs, w1, None, dist.group.WORLD, ctx)
+        linear_reduce_scatter(y, w2, dist.group.WORLD, ctx).backward(g_sh)
+
+    ms_f, ms_b = timer(lambda: tp_fb("native")), timer(lambda: tp_fb("nccl"))
+    os.environ["VERL_B200_COMM"] = "native"
+    report(rank, f"sequence-parallel TP block [{T}x{H}] -> {F // W} -> {H}, forward + backward, TP={W}", ms_f, ms_b, 6.0 * T * H * (F // W) * 2,
+           4 * (W - 1) * Tl * H * 2)
     torch.cuda.synchronize()
     _ext.check_status("comm_bench")
     dist.barrier()

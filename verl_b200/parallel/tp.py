@@ -69,18 +69,29 @@ class TPContext:
         self.act.tensor(torch.bfloat16, n).view_as(x_shard).copy_(x_shard)
         self.act.barrier()
 
-    def allgather_linear(self, x_shard: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def allgather_linear(self, x_shard: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                         transposed: bool = False) -> torch.Tensor:
+        """``all_gather(x_shard) @ wᵀ`` (``transposed``: ``@ w``, the weight as the forward pass stores it — the activation
+        gradient of a row-parallel layer). After the fused call the peers' rows of the gathered operand sit in ``self.stage``."""
         rows = x_shard.shape[0]
-        out = torch.empty(rows * self.world, w.shape[0], dtype=torch.bfloat16, device=x_shard.device)
+        out = torch.empty(rows * self.world, w.shape[1] if transposed else w.shape[0], dtype=torch.bfloat16, device=x_shard.device)
         if fused_comm_enabled() and rows % 128 == 0:
             self.stage_activation(x_shard)
             self.stage_epoch += 1
-            self.ops.gemm_allgather_a(self.act.table(), rows, w, out, bias, self.rank, self.stage, self.stage_flags, self.stage_epoch)
+            self.ops.gemm_allgather_a(self.act.table(), rows, w, out, bias, self.rank, self.stage, self.stage_flags, self.stage_epoch, transposed)
             self.act.barrier()      # nobody overwrites its shard while a peer may still be reading it
             return out
         full = torch.empty(rows * self.world, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
         dist.all_gather_into_tensor(full, x_shard.contiguous(), group=self.group)
-        return torch.nn.functional.linear(full, w, bias)
+        return torch.matmul(full, w) if transposed else torch.nn.functional.linear(full, w, bias)
+
+    def gathered_operand(self, x_shard: torch.Tensor) -> torch.Tensor:
+        """The full operand of the last fused ``allgather_linear`` call: the staging buffer holds the peers' rows, this
+        rank's own rows (which the kernel read in place) are copied in. Valid until the next fused call."""
+        rows, k = x_shard.shape
+        full = self.stage[: rows * self.world * k].view(rows * self.world, k)
+        full[self.rank * rows:(self.rank + 1) * rows].copy_(x_shard)
+        return full
 
     # ------------------------------------------------------------------ GEMM → all-reduce / reduce-scatter
     def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -104,18 +115,19 @@ class TPContext:
         dist.all_reduce(y, group=self.group)
         return y + residual if residual is not None else y
 
-    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        T, N = x.shape[0], w.shape[0]
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, transposed: bool = False) -> torch.Tensor:
+        """``reduce_scatter(x @ wᵀ)`` over rows (``transposed``: ``x @ w`` — the activation gradient of a column-parallel layer)."""
+        T, N = x.shape[0], (w.shape[1] if transposed else w.shape[0])
         assert T % self.world == 0
         rows = T // self.world
         if fused_comm_enabled() and N % 32 == 0 and rows * N <= self.slot_elems:
             out = torch.empty(rows, N, dtype=torch.bfloat16, device=x.device)
-            self.ops.gemm_peer_scatter(x, w, self.slots.table(), self.rank, rows, self.slot_elems)
+            self.ops.gemm_peer_scatter(x, w, self.slots.table(), self.rank, rows, self.slot_elems, transposed)
             self.slots.barrier()
             self.ops.slots_reduce(self.slots.tensor(torch.bfloat16), self.world, self.slot_elems, rows, N, None, out)
             self.slots.barrier()
             return out
-        y = torch.nn.functional.linear(x, w)
+        y = torch.matmul(x, w) if transposed else torch.nn.functional.linear(x, w)
         out = torch.empty(rows, N, dtype=y.dtype, device=y.device)
         dist.reduce_scatter_tensor(out, y, group=self.group)
         return out
@@ -286,9 +298,10 @@ class _AllGatherLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_shard, w, bias, group, tpctx):
         ctx.save_for_backward(x_shard, w)
-        ctx.group, ctx.bias_ref = group, bias
+        ctx.group, ctx.bias_ref, ctx.tpctx = group, bias, None
         if tpctx is not None and fused_comm_enabled() and x_shard.is_cuda and x_shard.shape[0] % 128 == 0 and \
                 x_shard.shape[0] * tpctx.world <= tpctx.max_tokens:
+            ctx.tpctx = tpctx
             return tpctx.allgather_linear(x_shard.contiguous(), w, bias)
         return torch.nn.functional.linear(_all_gather_rows(x_shard, group), w, bias)
 
@@ -297,9 +310,22 @@ class _AllGatherLinear(torch.autograd.Function):
         x_shard, w = ctx.saved_tensors
         dy = dy.contiguous()
         dx = None
+        t = ctx.tpctx
+        fused = t is not None and dy.shape[0] % t.world == 0 and w.shape[1] % 32 == 0 and (dy.shape[0] // t.world) * w.shape[1] <= t.slot_elems \
+            and dy.data_ptr() % 16 == 0
+        x_full = work = None
+        if ctx.needs_input_grad[1] and fused:
+            # the gather of the forward input for the weight gradient runs on NCCL's stream underneath the fused dgrad
+            x_full = torch.empty(x_shard.shape[0] * t.world, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
+            work = dist.all_gather_into_tensor(x_full, x_shard.contiguous(), group=ctx.group, async_op=True)
         if ctx.needs_input_grad[0]:
-            dx = _reduce_scatter_rows(_dgrad(dy, w), ctx.group)
-        dw = _wgrad(dy, _all_gather_rows(x_shard, ctx.group), w) if ctx.needs_input_grad[1] else None
+            # activation gradient GEMM with the reduce-scatter in its epilogue (rows go straight to their owners' slots)
+            dx = t.gemm_reduce_scatter(dy, w, transposed=True) if fused else _reduce_scatter_rows(_dgrad(dy, w), ctx.group)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            if work is not None:
+                work.wait()
+            dw = _wgrad(dy, x_full if x_full is not None else _all_gather_rows(x_shard, ctx.group), w)
         db = None
         b = ctx.bias_ref
         if b is not None and ctx.needs_input_grad[2]:
@@ -318,16 +344,26 @@ class _LinearReduceScatter(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, group, tpctx):
         ctx.save_for_backward(x, w)
-        ctx.group = group
+        ctx.group, ctx.tpctx = group, None
         if tpctx is not None and fused_comm_enabled() and x.is_cuda and x.shape[0] % tpctx.world == 0 and w.shape[0] % 32 == 0 and \
                 (x.shape[0] // tpctx.world) * w.shape[0] <= tpctx.slot_elems:
+            ctx.tpctx = tpctx
             return tpctx.gemm_reduce_scatter(x.contiguous(), w)
         return _reduce_scatter_rows(torch.nn.functional.linear(x, w), group)
 
     @staticmethod
     def backward(ctx, dy_shard):
         x, w = ctx.saved_tensors
-        dy = _all_gather_rows(dy_shard.contiguous(), ctx.group)
+        dy_shard = dy_shard.contiguous()
+        t = ctx.tpctx
+        if t is not None and ctx.needs_input_grad[0] and dy_shard.shape[0] % 128 == 0 and dy_shard.shape[1] == t.hidden and \
+                dy_shard.shape[0] * t.world <= t.max_tokens and w.shape[1] % 8 == 0:
+            # all-gather of the output gradient fused into the activation-gradient GEMM; the gathered rows stay in the staging
+            # buffer and feed the weight gradient, so no separate all-gather runs at all
+            dx = t.allgather_linear(dy_shard, w, None, transposed=True)
+            dw = _wgrad(t.gathered_operand(dy_shard), x, w) if ctx.needs_input_grad[1] else None
+            return dx, dw, None, None
+        dy = _all_gather_rows(dy_shard, ctx.group)
         dx = _dgrad(dy, w) if ctx.needs_input_grad[0] else None
         dw = _wgrad(dy, x, w) if ctx.needs_input_grad[1] else None
         return dx, dw, None, None

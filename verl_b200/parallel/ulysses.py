@@ -148,7 +148,10 @@ def ulysses_attention(qkv: torch.Tensor, pb, cfg, group) -> torch.Tensor:
 #     (rows = this rank's token slice) — ``gemm_head_scatter``;
 #   * output projection: the GEMM's A operand is read tile by tile from the ranks that hold the corresponding heads
 #     (K axis split over ranks) — ``gemm_kseg``.
-# Forward only: the backward of both functions uses the all-to-all formulation above with plain GEMMs.
+# Backward mirrors them: d(attention output) = (dY @ W_o) routed to the head owners by the same scatter epilogue, and
+# dX = gather_over_ranks(dQKV) @ W_qkv through the same K-segmented gather (W_qkv's rows permuted into rank-major order); the
+# gathered dQKV left in the staging buffer feeds the weight gradient. Only the re-gather of the attention output for the
+# output projection's weight gradient still uses an NCCL all-to-all.
 def fused_ulysses_available(x: torch.Tensor, cfg, sp: int) -> bool:
     import os
 
@@ -167,6 +170,7 @@ class FusedUlysses:
         from verl_b200.parallel.symm_mem import SymmetricBuffer
 
         self.group, self.cfg, self.ops = group, cfg, _ext.ops()
+        self._host_group = host_group
         self.sp, self.rank = dist.get_world_size(group), dist.get_rank(group)
         D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
         self.hq_l, self.hkv_l = Hq // self.sp, Hkv // self.sp
@@ -189,6 +193,54 @@ class FusedUlysses:
         self.o_stage = torch.empty(tl_max * Hq * D, dtype=torch.bfloat16, device=dev)     # peers' head slices of the local token rows
         self.o_flags = torch.zeros((tl_max // 128) * self.sp + 8, dtype=torch.int32, device=dev)
         self.o_epoch = 0
+        self.fused_backward = True
+        # backward: gradient buffers the peers write (d attention output) or read (d qkv), staging of the gathered d qkv, and the
+        # order in which rank-major columns [rank][q | k | v heads of that rank] appear among the rows of the qkv weight
+        self.do_buf = self.dqkv_buf = None
+        self.tl_max = tl_max
+        self.q_rank = self.head_rank[:Hq].clone()
+        self.q_slot = self.head_slot[:Hq].clone()
+        order = sorted(range(Hq + 2 * Hkv), key=lambda h: (rank_of[h], slot_of[h]))
+        self.row_perm = torch.tensor([h * D + i for h in order for i in range(D)], dtype=torch.long, device=dev)
+        self.col_unperm = torch.argsort(self.row_perm)
+
+    def _backward_buffers(self, host_group=None):
+        if self.do_buf is None:
+            from verl_b200.parallel.symm_mem import SymmetricBuffer
+
+            dev = self.o_stage.device
+            self.do_buf = SymmetricBuffer(self.max_tokens * self.Kl * 2, self.group, self._host_group)
+            self.dqkv_buf = SymmetricBuffer(self.max_tokens * self.Cl * 2, self.group, self._host_group)
+            self.g_stage = torch.empty(self.tl_max * self.sp * self.Cl, dtype=torch.bfloat16, device=dev)
+            self.g_flags = torch.zeros((self.tl_max // 128) * self.sp + 8, dtype=torch.int32, device=dev)
+            self.g_epoch = 0
+
+    def o_backward(self, g, w_o, Tl: int):
+        """d(attention output of the local heads, all tokens) [Tp, Kl] from dY [Tl, hidden]: (dY @ W_o) with head h sent to rank
+        h // hq_l by the GEMM epilogue."""
+        self._backward_buffers()
+        Tp = Tl * self.sp
+        self.do_buf.barrier()             # every rank has copied the previous layer's result out of its buffer
+        self.ops.gemm_head_scatter(g, w_o, None, self.do_buf.table(), self.Kl, self.rank * Tl, self.cfg.head_dim, self.q_rank, self.q_slot, True)
+        self.do_buf.barrier()
+        return self.do_buf.tensor(torch.bfloat16, Tp * self.Kl).view(Tp, self.Kl).clone()
+
+    def qkv_backward(self, g, w, Tl: int):
+        """dX [Tl, hidden] and dQKV in sequence layout [Tl, N] (weight-row order) from g [Tp, Cl] (local heads, all tokens)."""
+        self._backward_buffers()
+        Tp, N = Tl * self.sp, self.sp * self.Cl
+        self.dqkv_buf.tensor(torch.bfloat16, Tp * self.Cl).view(Tp, self.Cl).copy_(g)
+        self.dqkv_buf.barrier()
+        dx = torch.empty(Tl, w.shape[1], dtype=torch.bfloat16, device=g.device)
+        self.g_epoch += 1
+        w_rank_major = w.index_select(0, self.row_perm)          # rows in the order the ranks hold the columns of d qkv
+        self.ops.gemm_kseg(self.dqkv_buf.table(), self.Cl, Tp, self.rank * Tl, w_rank_major, dx, None, self.rank, self.g_stage, self.g_flags,
+                           self.g_epoch, True)
+        Tl_pad = -(-Tl // 128) * 128
+        dy_rm = self.g_stage[: Tl_pad * N].view(Tl_pad, N)[:Tl]
+        dy_rm[:, self.rank * self.Cl:(self.rank + 1) * self.Cl].copy_(g[self.rank * Tl:(self.rank + 1) * Tl])     # own columns were read in place
+        self.dqkv_buf.barrier()           # the peers have finished reading this rank's gradient rows
+        return dx, dy_rm.index_select(1, self.col_unperm)
 
     def qkv_forward(self, x_shard, w, bias):
         Tl = x_shard.shape[0]
@@ -234,10 +286,13 @@ class _FusedQKV(torch.autograd.Function):
 
         x, w = ctx.saved_tensors
         fu = ctx.fu
-        q_w, k_w = fu.hq_l * fu.cfg.head_dim, fu.hkv_l * fu.cfg.head_dim
-        gq, gk, gv = g.split([q_w, k_w, k_w], dim=-1)
-        dy = torch.cat([fu.heads_to_seq(gq.contiguous()), fu.heads_to_seq(gk.contiguous()), fu.heads_to_seq(gv.contiguous())], dim=-1).contiguous()
-        dx = gemm(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
+        if ctx.needs_input_grad[0] and fu.fused_backward and x.shape[0] * fu.sp <= fu.max_tokens:
+            dx, dy = fu.qkv_backward(g.contiguous(), w, x.shape[0])
+        else:
+            q_w, k_w = fu.hq_l * fu.cfg.head_dim, fu.hkv_l * fu.cfg.head_dim
+            gq, gk, gv = g.split([q_w, k_w, k_w], dim=-1)
+            dy = torch.cat([fu.heads_to_seq(gq.contiguous()), fu.heads_to_seq(gk.contiguous()), fu.heads_to_seq(gv.contiguous())], dim=-1).contiguous()
+            dx = gemm(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
         dw = db = None
         if ctx.needs_input_grad[1]:
             mg = getattr(w, "main_grad", None)
@@ -270,7 +325,10 @@ class _FusedOProj(torch.autograd.Function):
         o_local, w_o = ctx.saved_tensors
         fu = ctx.fu
         g = g.contiguous()
-        do_local = fu.seq_to_heads(gemm(g, w_o, b_mn=True)) if ctx.needs_input_grad[0] else None
+        if ctx.needs_input_grad[0] and fu.fused_backward:
+            do_local = fu.o_backward(g, w_o, g.shape[0])
+        else:
+            do_local = fu.seq_to_heads(gemm(g, w_o, b_mn=True)) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.needs_input_grad[1]:
             o_shard = fu.heads_to_seq(o_local).contiguous()

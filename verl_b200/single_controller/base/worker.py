@@ -68,7 +68,11 @@ class Worker(WorkerHelper):
             import torch
 
             if torch.cuda.is_available():
-                torch.cuda.set_device(self._local_rank % torch.cuda.device_count())
+                dev = self._local_rank % torch.cuda.device_count()
+                torch.cuda.set_device(dev)
+                from verl_b200.utils.distributed import set_numa_affinity
+
+                self._cpu_affinity = set_numa_affinity(dev)       # stay on the socket the GPU hangs off (queries NVML only)
         except Exception:
             pass
 
