@@ -101,6 +101,8 @@ def test_allgather_a_and_b_fused_into_the_gemm(o, staged):
         flags_a = torch.zeros(T // 128 + 8, device="cuda", dtype=torch.int32) if staged else None
         stage_b = torch.empty(N * H, device="cuda", dtype=torch.bfloat16) if staged else None
         flags_b = torch.zeros(N // 128 + 8, device="cuda", dtype=torch.int32) if staged else None
+        stage_t = torch.empty(T * H, device="cuda", dtype=torch.bfloat16) if staged else None
+        flags_t = torch.zeros(T // 128 + 8, device="cuda", dtype=torch.int32) if staged else None     # a flag counts the calls on its buffer
         for ep in (1, 2, 3):        # staging flags carry the epoch: later calls must not trust rows staged by earlier ones
             xs = [s * ep for s in x_seg]
             out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
@@ -108,9 +110,9 @@ def test_allgather_a_and_b_fused_into_the_gemm(o, staged):
             assert _rel(out, ep * ref + bias.float()) < 1e-2, (r, ep)
             if staged:      # the same product from the weight stored [K, N] (backward of a row-parallel layer); the peers' rows
                 outt = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)     # of the gathered operand are left in the staging buffer
-                o.gemm_allgather_a(_table(xs), T // W, w.t().contiguous(), outt, None, r, stage_a, flags_a, ep + 10, True)
+                o.gemm_allgather_a(_table(xs), T // W, w.t().contiguous(), outt, None, r, stage_t, flags_t, ep, True)
                 assert _rel(outt, ep * ref) < 1e-2, (r, ep)
-                got = stage_a.view(T, H)
+                got = stage_t.view(T, H)
                 for q in range(W):
                     if q != r:
                         assert torch.equal(got[q * (T // W):(q + 1) * (T // W)], xs[q])

@@ -55,9 +55,9 @@ struct DistArgs {
   uint16_t head_map[192];            // per output head: (destination rank << 12) | destination head slot
   void* peer_out[MAX_TP];
   // Staging of the remote part of a gathered operand: tiles that live on another rank are copied ONCE over NVLink into
-  // `stage` (laid out like the gathered operand) by the epilogue warps at kernel start, 128-row chunk by chunk; a chunk's
-  // flag is set to `stage_epoch` when it has landed and the TMA producer waits for the flags of the tile it is about to
-  // load. Without staging every output tile would fetch its operand tile from the peer again.
+  // `stage` (laid out like the gathered operand) at kernel start, 128-row chunk by chunk; a chunk's flag is set to
+  // `stage_epoch` (times STAGE_PARTS) when it has landed and the TMA producer waits until the flag of the tile it is about to
+  // load has reached that value. Epochs must grow from call to call on one flag buffer. Without staging every output tile would fetch its operand tile from the peer again.
   // Grouped (mixture-of-experts) GEMM. Token rows are sorted by expert and every expert's segment is padded to a multiple
   // of 128 rows, so a 128-row block belongs to exactly one expert.
   //   group_mode 1: C[rows, N] = A[rows, K] * B[e]^T with e = blk_expert[row block] (< 0: block unused, tile skipped);
@@ -468,7 +468,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           tma_store_wait_all();                                   // the chunk's rows are in the staging buffer
           asm volatile("fence.proxy.async;" ::: "memory");
-          asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(dist.stage_flags + c), "n"(STAGE_PARTS) : "memory");
+          // one writer per chunk and call: the flag is SET to the call's epoch (not counted up), so calls whose chunk ranges differ
+          // (another token count, another owner of a row range) cannot leave a flag behind the epoch its next reader expects
+          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(dist.stage_flags + c), "r"(dist.stage_epoch * STAGE_PARTS) : "memory");
         }
         tma_store_wait_all();
       }
