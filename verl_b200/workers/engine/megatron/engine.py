@@ -53,6 +53,33 @@ def _new_groups(rank: int, rank_lists: list[list[int]]):
 
 
 @EngineRegistry.register(model_type="language_model", backend=["megatron"], device=["cuda", "cpu"])
+class _VirtualChunks(torch.nn.Module):
+    """The model chunks one pipeline rank holds under virtual pipeline parallelism (chunk c = virtual stage c * pp + pp_rank)."""
+
+    def __init__(self, chunks):
+        super().__init__()
+        self.chunks = torch.nn.ModuleList(chunks)
+
+    @property
+    def layers(self):
+        return [layer for ch in self.chunks for layer in ch.layers]
+
+    @property
+    def embed_tokens(self):
+        return next(ch.embed_tokens for ch in self.chunks if getattr(ch, "embed_tokens", None) is not None)
+
+    def set_tp_group(self, *args, **kwargs):
+        for ch in self.chunks:
+            ch.set_tp_group(*args, **kwargs)
+
+    def __setattr__(self, name, value):
+        if name in ("gradient_checkpointing", "sp_group"):        # per-chunk switches set on the whole model by the engine
+            for ch in self.chunks:
+                setattr(ch, name, value)
+            return
+        super().__setattr__(name, value)
+
+
 class MegatronEngine(FSDPEngine):
     def __init__(self, model_config, engine_config=None, optimizer_config=None, checkpoint_config=None):
         super().__init__(model_config, engine_config, optimizer_config, checkpoint_config)
@@ -62,10 +89,15 @@ class MegatronEngine(FSDPEngine):
         # into the projections. Off unless asked for (the reference's megatron.yaml turns it on by default).
         self.tp_sp = bool(cfg_get(ec, "sequence_parallel", False)) and self.tp_size > 1
         self.pp_size = int(cfg_get(ec, "pipeline_model_parallel_size", 1) or 1)
-        for key in ("expert_model_parallel_size", "virtual_pipeline_model_parallel_size"):
+        for key in ("expert_model_parallel_size",):
             v = cfg_get(ec, key, None)
             if v not in (None, 1, 0):
                 raise NotImplementedError(f"{key}={v} is not supported by this engine yet")
+        # virtual pipeline stages: every pipeline rank holds `vpp` model chunks (virtual stage s = chunk * pp + pp_rank owns the
+        # s-th of pp * vpp contiguous layer blocks) and runs the interleaved 1F1B schedule, which shrinks the pipeline bubble by vpp
+        self.vpp = int(cfg_get(ec, "virtual_pipeline_model_parallel_size", None) or 1)
+        if self.vpp > 1 and self.pp_size < 2:
+            raise ValueError("virtual_pipeline_model_parallel_size > 1 needs pipeline_model_parallel_size > 1")
         self.cp_size = int(cfg_get(ec, "context_parallel_size", 1) or 1)
         self._cp_zigzag = self.cp_size > 1 and bool(cfg_get(ec, "context_parallel_zigzag", False))
         self._dynamic_cp = False
@@ -105,6 +137,12 @@ class MegatronEngine(FSDPEngine):
             self.pp_group, _ = _new_groups(self.rank, [[rk(p, d, c, t) for p in range(pp)] for d in range(dp) for c in range(cp) for t in range(tp)])
         if tp * pp > 1:
             self.mp_group, _ = _new_groups(self.rank, [[rk(p, d, c, t) for p in range(pp) for t in range(tp)] for d in range(dp) for c in range(cp)])
+        if pp > 1 and self.vpp > 1:
+            # interleaved schedule: four kinds of messages travel between neighbouring ranks (activations to the next rank, activations
+            # wrapping from the last rank to the first, and the two gradient directions). Each kind gets a communicator of its own so
+            # that a send of one kind never queues behind a receive of another on the same stream.
+            lists = [[rk(p, d, c, t) for p in range(pp)] for d in range(dp) for c in range(cp) for t in range(tp)]
+            self._p2p_groups = {kind: _new_groups(self.rank, lists)[0] for kind in ("f", "fw", "b", "bw")}
         if pp > 1:   # first and last stage of each pipeline: gradient sum of tied input/output embeddings
             self.embed_group, _ = _new_groups(self.rank, [[rk(0, d, c, t), rk(pp - 1, d, c, t)] for d in range(dp) for c in range(cp) for t in range(tp)])
         if cp == 1:
@@ -136,12 +174,24 @@ class MegatronEngine(FSDPEngine):
         if tp * pp == 1:
             self.model = full
         else:
-            self.model = DecoderLM(self.local_cfg, dtype=self.dtype, device=self.device, init=False, layer_range=self.layer_range,
-                                   pre_process=self.is_first, post_process=self.is_last)
+            if self.vpp > 1:
+                nv = pp * self.vpp
+                if cfg.num_hidden_layers < nv:
+                    raise ValueError(f"{cfg.num_hidden_layers} layers cannot fill {pp} x {self.vpp} virtual pipeline stages")
+                chunks = []
+                for c in range(self.vpp):
+                    vs = c * pp + self.pp_rank
+                    chunks.append(DecoderLM(self.local_cfg, dtype=self.dtype, device=self.device, init=False,
+                                            layer_range=stage_layer_range(cfg.num_hidden_layers, nv, vs), pre_process=vs == 0, post_process=vs == nv - 1))
+                self.model = _VirtualChunks(chunks)
+                self.layer_range = [ch.layer_offset for ch in chunks]
+            else:
+                self.model = DecoderLM(self.local_cfg, dtype=self.dtype, device=self.device, init=False, layer_range=self.layer_range,
+                                       pre_process=self.is_first, post_process=self.is_last)
             full_params = dict(full.named_parameters())
             with torch.no_grad():
                 for name, p in self.model.named_parameters():
-                    g = local_to_global_name(name, self.model.layer_offset)
+                    g = self._gname(name)
                     p.copy_(shard_param(g, full_params[g], cfg, self.tp_rank, tp))
             del full, full_params
             if tp > 1:
@@ -172,6 +222,19 @@ class MegatronEngine(FSDPEngine):
             self.to("cpu", model=True, optimizer=False, grad=False)
         if self._optimizer_offload and not self.forward_only:
             self.to("cpu", model=False, optimizer=True, grad=True)
+
+    def _gname(self, name: str) -> str:
+        """Parameter name of this rank's model piece → name in the full model."""
+        if self.vpp > 1:
+            _, c, rest = name.split(".", 2)
+            return local_to_global_name(rest, self.model.chunks[int(c)].layer_offset)
+        return local_to_global_name(name, self.model.layer_offset)
+
+    def _chunk(self, chunk: Optional[int]):
+        return self.model if self.vpp == 1 else self.model.chunks[chunk or 0]
+
+    def _virtual_stage(self, chunk: Optional[int]) -> int:
+        return (chunk or 0) * self.pp_size + self.pp_rank
 
     def _tp_host_group(self):
         """gloo twin of this rank's TP group (pointer tables of the symmetric buffers travel through host memory)."""
@@ -208,7 +271,7 @@ class MegatronEngine(FSDPEngine):
         out = []
         tied_copy = self.pp_size > 1 and self.cfg.tie_word_embeddings and not self.cfg.value_head
         for name, p, off in zip(self.store.names, self.store.params, self.store.offsets):
-            g = local_to_global_name(name, self.model.layer_offset)
+            g = self._gname(name)
             copies = 1
             if self.tp_size > 1 and tp_rule(g, self.cfg) is None:
                 copies *= self.tp_size
@@ -256,19 +319,21 @@ class MegatronEngine(FSDPEngine):
         pbl.cp_zigzag = self._cp_zigzag
         return pbl, lab.index_select(0, rows), T + pad
 
-    def _stage_forward(self, mb: dict, meta: dict, h_in: Optional[torch.Tensor]):
-        """Runs this stage on one micro-batch. Returns (stream or None, model_output dict on the last stage)."""
+    def _stage_forward(self, mb: dict, meta: dict, h_in: Optional[torch.Tensor], chunk: Optional[int] = None):
+        """Runs this stage (model chunk ``chunk`` under virtual pipeline parallelism) on one micro-batch. Returns (stream or None,
+        model_output dict on the last stage)."""
         if self.cp_size > 1:
-            return self._stage_forward_cp(mb, meta, h_in)
+            return self._stage_forward_cp(mb, meta, h_in, chunk)
         pb, labels = self._pack(mb)
-        h = self.model.forward_hidden(pb, h_in)
-        if not self.is_last:
+        model = self._chunk(chunk)
+        h = model.forward_hidden(pb, h_in)
+        if not model.post_process:
             return h, None
         R = mb["responses"].shape[1]
         idx, valid = response_gather_index(mb["attention_mask"], R)
         out: dict[str, torch.Tensor] = {}
         if self.cfg.value_head:
-            vals = torch.nn.functional.linear(h, self.model.score).squeeze(-1).float()
+            vals = torch.nn.functional.linear(h, model.score).squeeze(-1).float()
             out["values"] = torch.where(valid, vals[idx.reshape(-1)].reshape(idx.shape), torch.zeros((), device=vals.device))
             return None, out
         temperature = float(meta.get("temperature", 1.0))
@@ -276,10 +341,10 @@ class MegatronEngine(FSDPEngine):
         sel = idx[valid]
         h_sel, lab_sel = h.index_select(0, sel), labels.index_select(0, sel)
         if self.tp_size > 1:
-            lp, ent = vocab_parallel_logprob(copy_to_tp(h_sel, self.tp_group), self.model.output_weight, lab_sel, temperature,
-                                             need_entropy, self.tp_group, self.model.vocab_offset)
+            lp, ent = vocab_parallel_logprob(copy_to_tp(h_sel, self.tp_group), model.output_weight, lab_sel, temperature,
+                                             need_entropy, self.tp_group, model.vocab_offset)
         else:
-            lp, ent = ops.linear_logprob_entropy(h_sel, self.model.output_weight, lab_sel, temperature, need_entropy)
+            lp, ent = ops.linear_logprob_entropy(h_sel, model.output_weight, lab_sel, temperature, need_entropy)
         full = torch.zeros(idx.shape, dtype=torch.float32, device=h.device)
         out["log_probs"] = full.masked_scatter(valid, lp.float())
         if ent is not None:
@@ -292,7 +357,7 @@ class MegatronEngine(FSDPEngine):
             self._score_centering_terms(out, mb, meta, h_sel, valid, temperature)
         return None, out
 
-    def _stage_forward_cp(self, mb: dict, meta: dict, h_in: Optional[torch.Tensor]):
+    def _stage_forward_cp(self, mb: dict, meta: dict, h_in: Optional[torch.Tensor], chunk: Optional[int] = None):
         """The same with context parallelism: the stage works on this rank's token slice; on the last stage the per-token
         outputs of the slices are gathered over the CP group (gradient scaled by cp: the DP×CP average then counts every
         token once) and put back into stream order before the response window is cut out."""
@@ -301,8 +366,9 @@ class MegatronEngine(FSDPEngine):
         pb, labels = FSDPEngine._pack(self, mb)
         T = pb.input_ids.shape[0]
         pbl, lab_l, t_pad = self._cp_slice(pb, labels)
-        h = self.model.forward_hidden(pbl, h_in)
-        if not self.is_last:
+        model = self._chunk(chunk)
+        h = model.forward_hidden(pbl, h_in)
+        if not model.post_process:
             return h, None
         R = mb["responses"].shape[1]
         idx, valid = response_gather_index(mb["attention_mask"], R)
@@ -318,16 +384,16 @@ class MegatronEngine(FSDPEngine):
 
         zero = torch.zeros(idx.shape, dtype=torch.float32, device=h.device)
         if self.cfg.value_head:
-            vals = to_stream(torch.nn.functional.linear(h, self.model.score).squeeze(-1))
+            vals = to_stream(torch.nn.functional.linear(h, model.score).squeeze(-1))
             out["values"] = torch.where(valid, vals[idx.reshape(-1)].reshape(idx.shape), zero)
             return None, out
         temperature = float(meta.get("temperature", 1.0))
         need_entropy = bool(meta.get("calculate_entropy", False))
         if self.tp_size > 1:
-            lp, ent = vocab_parallel_logprob(copy_to_tp(h, self.tp_group), self.model.output_weight, lab_l, temperature, need_entropy,
-                                             self.tp_group, self.model.vocab_offset)
+            lp, ent = vocab_parallel_logprob(copy_to_tp(h, self.tp_group), model.output_weight, lab_l, temperature, need_entropy,
+                                             self.tp_group, model.vocab_offset)
         else:
-            lp, ent = ops.linear_logprob_entropy(h, self.model.output_weight, lab_l, temperature, need_entropy)
+            lp, ent = ops.linear_logprob_entropy(h, model.output_weight, lab_l, temperature, need_entropy)
         out["log_probs"] = torch.where(valid, to_stream(lp)[idx.reshape(-1)].reshape(idx.shape), zero)
         if ent is not None:
             out["entropy"] = torch.where(valid, to_stream(ent)[idx.reshape(-1)].reshape(idx.shape), zero)
@@ -348,6 +414,81 @@ class MegatronEngine(FSDPEngine):
             for r in dist.batch_isend_irecv(reqs):
                 r.wait()
         return recv
+
+    # ------------------------------------------------------------------ interleaved schedule (virtual pipeline stages)
+    def _run_interleaved(self, m: int, train: bool, run_forward, run_backward, shape) -> None:
+        """Interleaved 1F1B over ``pp * vpp`` virtual stages. Micro-batches go through in groups of ``pp``; step k of the forward
+        order is (chunk, micro-batch) = ((k % (pp*vpp)) // pp, (k // (pp*vpp)) * pp + k % pp), the backward order is the same with
+        the chunks reversed. A rank runs ``(pp - rank - 1) * 2 + (vpp - 1) * pp`` forwards ahead, then alternates one forward and one
+        backward, then drains. When the number of micro-batches is not a multiple of ``pp`` the missing ones of the last group are
+        skipped by every rank alike (a valid schedule with steps removed stays valid). Sends are asynchronous and every kind of
+        message has its own communicator, receives are waited for where the data is needed; both ends of a link issue their sends
+        and receives in the same order, so no tags are needed."""
+        pp, v, r = self.pp_size, self.vpp, self.pp_rank
+        nv = pp * v
+        groups = -(-m // pp)
+        total = groups * pp * v
+        nxt, prv = self.pp_ranks[(r + 1) % pp], self.pp_ranks[(r - 1) % pp]
+        g = self._p2p_groups
+        pending: list = []          # (work, tensor) of sends in flight: the tensors must outlive them
+
+        def step_of(k, backward):
+            c = (k % nv) // pp
+            return (v - 1 - c if backward else c), (k // nv) * pp + k % pp
+
+        def send(t, dst, kind):
+            t = t.contiguous()
+            pending.append((dist.isend(t, dst, group=g[kind]), t))
+
+        def recv(shp, src, kind):
+            t = torch.empty(shp, dtype=self.dtype, device=self.device)
+            dist.irecv(t, src, group=g[kind]).wait()
+            return t
+
+        stash: dict = {}
+
+        def forward(k):
+            c, i = step_of(k, False)
+            if i >= m:
+                return
+            vs = c * pp + r
+            h_in = None
+            if vs > 0:
+                h_in = recv(shape(i), prv, "fw" if r == 0 else "f")
+            h_in, stream, loss = run_forward(i, h_in, c)
+            if vs < nv - 1:
+                send(stream.detach(), nxt, "fw" if r == pp - 1 else "f")
+            if train:
+                stash[(c, i)] = (h_in, stream, loss)
+
+        def backward(k):
+            c, i = step_of(k, True)
+            if i >= m:
+                return
+            vs = c * pp + r
+            h_in, stream, loss = stash.pop((c, i))
+            out_grad = None
+            if vs < nv - 1:
+                out_grad = recv(shape(i), nxt, "bw" if r == pp - 1 else "b")
+            in_grad = run_backward(h_in, stream, loss, out_grad)
+            if vs > 0:
+                send(in_grad, prv, "bw" if r == 0 else "b")
+
+        if not train:
+            for k in range(total):
+                forward(k)
+        else:
+            warm = min((pp - r - 1) * 2 + (v - 1) * pp, total)
+            for k in range(warm):
+                forward(k)
+            for j in range(total - warm):
+                forward(warm + j)
+                backward(j)
+            for j in range(total - warm, total):
+                backward(j)
+            assert not stash
+        for w, _ in pending:
+            w.wait()
 
     # ------------------------------------------------------------------ forward / backward over the pipeline
     def forward_backward_batch(self, data, loss_function: Optional[Callable], forward_only: bool = False) -> dict:
@@ -388,12 +529,12 @@ class MegatronEngine(FSDPEngine):
         metrics: dict[str, Metric] = {}
         losses: list[float] = []
 
-        def run_forward(i, h_in):
+        def run_forward(i, h_in, chunk=None):
             mb = micro(i)
             if h_in is not None and train:
                 h_in.requires_grad_(True)
             with (torch.enable_grad() if train else torch.no_grad()):
-                stream, mo = self._stage_forward(mb, meta, h_in)
+                stream, mo = self._stage_forward(mb, meta, h_in, chunk)
                 loss = None
                 if mo is not None:
                     if loss_function is not None:
@@ -419,7 +560,12 @@ class MegatronEngine(FSDPEngine):
 
         first, last = self.is_first, self.is_last
         shape = lambda i: None if i is None or i >= m else (ntoks[i], H)
-        if not train:
+        if self.vpp > 1:
+            self._run_interleaved(m, train, run_forward, run_backward, shape)
+            if train:
+                self.store.fold_autograd_grads()
+                self._sync_replicated_grads()
+        elif not train:
             for i in range(m):
                 h_in = self._exchange(None, None, None if first else shape(i), self.prev_rank)
                 _, stream, _ = run_forward(i, h_in)
@@ -481,7 +627,7 @@ class MegatronEngine(FSDPEngine):
         if self.tp_sp:
             # norms see a different token slice on every TP rank: their gradients are partial sums
             for name, p in self.model.named_parameters():
-                if tp_rule(local_to_global_name(name, self.model.layer_offset), self.cfg) is None and getattr(p, "main_grad", None) is not None \
+                if tp_rule(self._gname(name), self.cfg) is None and getattr(p, "main_grad", None) is not None \
                         and not name.endswith("router"):
                     dist.all_reduce(p.main_grad, group=self.tp_group)
         if self.pp_size > 1 and self.cfg.tie_word_embeddings and not self.cfg.value_head and (self.is_first or self.is_last):
@@ -519,7 +665,7 @@ class MegatronEngine(FSDPEngine):
 
     def _gathered_hf_tensors(self):
         cfg, tp, pp = self.cfg, self.tp_size, self.pp_size
-        local = {local_to_global_name(n, self.model.layer_offset): p for n, p in self.model.named_parameters()}
+        local = {self._gname(n): p for n, p in self.model.named_parameters()}
         # every rank walks the same global list; the tied copy of the embedding on the last stage is skipped
         probe = DecoderLM(cfg, dtype=self.dtype, device="meta", init=False)
         full_shapes = {n: tuple(p.shape) for n, p in probe.named_parameters()}
@@ -527,7 +673,8 @@ class MegatronEngine(FSDPEngine):
         for n in full_shapes:
             if n.startswith("layers."):
                 li = int(n.split(".")[1])
-                owner_stage[n] = next(s for s in range(pp) if li in stage_layer_range(cfg.num_hidden_layers, pp, s))
+                nv = pp * self.vpp          # virtual stage s lives on pipeline rank s % pp
+                owner_stage[n] = next(s for s in range(nv) if li in stage_layer_range(cfg.num_hidden_layers, nv, s)) % pp
             else:
                 owner_stage[n] = 0 if n == "embed_tokens" else pp - 1
 
