@@ -22,22 +22,23 @@ from verl_b200.models.parallel_model import local_to_global_name, tp_rule, unsha
 from verl_b200.workers.engine.megatron.engine import MegatronEngine
 dist.init_process_group("gloo")
 rank, world = dist.get_rank(), dist.get_world_size()
-cfg = PRESETS["tiny-qwen2"].replace(num_hidden_layers=3, tie_word_embeddings=os.environ["TIED"] == "1")
+cfg = PRESETS["tiny-qwen2"].replace(num_hidden_layers=int(os.environ.get("LAYERS", "3")), tie_word_embeddings=os.environ["TIED"] == "1")
 eng = MegatronEngine(cfg, {"seed": 1, "tensor_model_parallel_size": int(os.environ["TP"]), "pipeline_model_parallel_size": int(os.environ["PP"]),
+                           "virtual_pipeline_model_parallel_size": int(os.environ.get("VPP", "1")),
                            "sequence_parallel": os.environ.get("SP", "0") == "1", "context_parallel_size": int(os.environ.get("CP", "1")),
                            "context_parallel_zigzag": os.environ.get("ZIGZAG", "0") == "1"},
                      {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, {})
 eng.initialize()
 exported = {k: v.clone() for k, v in eng.get_per_tensor_param()[0]}
 data = make_batch().chunk(eng.get_data_parallel_size())[eng.get_data_parallel_rank()]
-data.meta_info["micro_batch_size_per_gpu"] = 2
+data.meta_info["micro_batch_size_per_gpu"] = int(os.environ.get("MBS", "2"))
 lp = eng.infer_batch(data)["model_output"]["log_probs"]
 eng.optimizer_zero_grad()
 out = eng.forward_backward_batch(data, loss_fn)
 ent = out["model_output"]["entropy"]
 grads = {}
 for n, p in eng.model.named_parameters():
-    g = local_to_global_name(n, eng.model.layer_offset)
+    g = eng._gname(n)
     mg = p.main_grad.clone()
     if eng.fsdp_size > 1:
         dist.all_reduce(mg, group=eng.fsdp_group); mg /= eng.fsdp_size
@@ -76,29 +77,33 @@ def test_shard_unshard_roundtrip():
     assert [list(stage_layer_range(7, 3, s)) for s in range(3)] == [[0, 1, 2], [3, 4], [5, 6]]
 
 
-@pytest.mark.parametrize("world,tp,pp,tied,sp,cp,zigzag", [
-    (4, 2, 2, False, False, 1, False), (4, 1, 2, True, False, 1, False), (3, 1, 3, True, False, 1, False), (2, 2, 1, True, False, 1, False),
-    (2, 2, 1, False, True, 1, False), (4, 2, 2, True, True, 1, False),
+@pytest.mark.parametrize("world,tp,pp,tied,sp,cp,zigzag,vpp,layers,mbs", [
+    (4, 2, 2, False, False, 1, False, 1, 3, 2), (4, 1, 2, True, False, 1, False, 1, 3, 2), (3, 1, 3, True, False, 1, False, 1, 3, 2),
+    (2, 2, 1, True, False, 1, False, 1, 3, 2), (2, 2, 1, False, True, 1, False, 1, 3, 2), (4, 2, 2, True, True, 1, False, 1, 3, 2),
     # context parallelism: with TP, with PP (zig-zag), with sequence-parallel TP, and with DP on top
-    (4, 2, 1, True, False, 2, False), (4, 1, 2, False, False, 2, True), (4, 2, 1, False, True, 2, False), (4, 1, 1, True, False, 2, True)])
-def test_parallel_ranks_match_single_rank(tmp_path, world, tp, pp, tied, sp, cp, zigzag):
+    (4, 2, 1, True, False, 2, False, 1, 3, 2), (4, 1, 2, False, False, 2, True, 1, 3, 2), (4, 2, 1, False, True, 2, False, 1, 3, 2),
+    (4, 1, 1, True, False, 2, True, 1, 3, 2),
+    # virtual pipeline stages (interleaved 1F1B): 2 ranks x 2 chunks with tied embeddings; with TP and an uneven layer split; three ranks
+    # with a micro-batch count that is not a multiple of the pipeline depth
+    (2, 1, 2, True, False, 1, False, 2, 4, 2), (4, 2, 2, False, False, 1, False, 2, 5, 3), (3, 1, 3, True, False, 1, False, 2, 6, 3)])
+def test_parallel_ranks_match_single_rank(tmp_path, world, tp, pp, tied, sp, cp, zigzag, vpp, layers, mbs):
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     script = tmp_path / "w.py"
     script.write_text(WORKER)
     out = tmp_path / "out.pt"
     env = dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1", TP=str(tp), PP=str(pp), TIED="1" if tied else "0", SP="1" if sp else "0", CP=str(cp),
-               ZIGZAG="1" if zigzag else "0")
+               ZIGZAG="1" if zigzag else "0", VPP=str(vpp), LAYERS=str(layers), MBS=str(mbs))
     ckpt = tmp_path / "ckpt"
     if (world, tp, pp) in ((4, 2, 2), (4, 1, 2)) and not sp:
         env["CKPT"] = str(ckpt)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-                        "--master-port", str(29660 + world + tp + (10 if sp else 0) + 20 * (cp - 1) + (5 if zigzag else 0)), str(script)], env=env, capture_output=True, text=True, timeout=900)
+                        "--master-port", str(29660 + world + tp + (10 if sp else 0) + 20 * (cp - 1) + (5 if zigzag else 0) + 40 * (vpp - 1)), str(script)], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    cfg = PRESETS["tiny-qwen2"].replace(num_hidden_layers=3, tie_word_embeddings=tied)
+    cfg = PRESETS["tiny-qwen2"].replace(num_hidden_layers=layers, tie_word_embeddings=tied)
     eng = FSDPEngine(cfg, {"seed": 1}, {"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, {})
     eng.initialize()
     data = make_batch()
-    data.meta_info["micro_batch_size_per_gpu"] = 2
+    data.meta_info["micro_batch_size_per_gpu"] = mbs
     lp = eng.infer_batch(data)["model_output"]["log_probs"]
     eng.optimizer_zero_grad()
     ent = eng.forward_backward_batch(data, loss_fn)["model_output"]["entropy"]

@@ -34,8 +34,13 @@ class FSDPModelMerger(BaseModelMerger):
     def _merge(self) -> dict[str, torch.Tensor]:
         world = self._get_world_size()
         first = self._load_rank(world, 0)
+        from verl_b200.utils.checkpoint.dtensor_interchange import is_named_tensor_payload, merge_sharded_model_files
+
+        if is_named_tensor_payload(first):
+            # {HF name: DTensor dim-0 shard} files (``checkpoint.model_format: dtensor`` here, or written by the reference's FSDP engine)
+            return {k: v.to(torch.bfloat16) for k, v in merge_sharded_model_files(self.config.local_dir, world).items()}
         if first.get("format") != "flat_v1":
-            raise ValueError("unsupported shard format (expected flat_v1 written by verl_b200's fsdp engine)")
+            raise ValueError("unsupported shard format (expected flat_v1 or named DTensor shards)")
         if first.get("zero3_rows"):
             return self._merge_zero3(world, first)
         fsdp_size = int(first["fsdp_size"])

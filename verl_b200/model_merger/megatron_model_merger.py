@@ -40,11 +40,12 @@ class MegatronModelMerger(BaseModelMerger):
         flat = torch.cat([s["flat_shard"] for s in shards])
         assert flat.numel() >= first["total"], "data-parallel slices do not add up to the recorded buffer length"
         out = {}
-        for name, shape, off in zip(first["names"], first["shapes"], first["offsets"]):
+        gnames = first.get("global_names") or [local_to_global_name(name, int(first["layer_offset"])) for name in first["names"]]
+        for name, shape, off in zip(gnames, first["shapes"], first["offsets"]):
             n = 1
             for d in shape:
                 n *= d
-            out[local_to_global_name(name, int(first["layer_offset"]))] = flat[off: off + n].view(*shape)
+            out[name] = flat[off: off + n].view(*shape)
         return out
 
     def _merge(self) -> dict[str, torch.Tensor]:

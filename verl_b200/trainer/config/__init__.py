@@ -23,6 +23,8 @@ class CheckpointConfig(BaseConfig):
     save_contents: list = field(default_factory=lambda: ["model", "optimizer", "extra"])
     load_contents: list = field(default_factory=lambda: ["model", "optimizer", "extra"])
     async_save: bool = False
+    # flat_v1: this engine's per-rank slice of the flat buffer; dtensor: {HF name: DTensor dim-0 shard}, the reference's payload
+    model_format: str = 'flat_v1'
     strict: bool = True
 
     def __post_init__(self):

@@ -8,8 +8,13 @@ Directory layout (same file names as the reference, ``verl/utils/checkpoint/fsdp
     fsdp_config.json                        {"FSDP_version": 2, "world_size": W, "format": "flat_v1"}
     huggingface/                            config.json (+ safetensors shards when ``hf_model`` is in save_contents)
 
-Only same-world-size reloads are supported for the sharded files (as in the reference); ``huggingface/`` and
+Only same-world-size reloads are supported for the ``flat_v1`` sharded files (as in the reference); ``huggingface/`` and
 ``python -m verl_b200.model_merger`` give the world-size-independent form.
+
+Interchange with the reference's payload (``checkpoint.model_format: dtensor``): the model file then holds ``{HF name:
+DTensor}`` with dim-0 shards exactly as the reference writes it, so its loader and merger read it; on load the format is detected
+from the file, and a checkpoint written by the reference (any world size) is merged and loaded as weights
+(``dtensor_interchange.py``).
 """
 
 from __future__ import annotations
@@ -32,6 +37,11 @@ class FSDPCheckpointManager(BaseCheckpointManager):
         super().__init__(checkpoint_config)
         self.engine = engine
         self._async_thread: Optional[threading.Thread] = None
+        cfg = checkpoint_config or {}
+        fmt = cfg.get("model_format", None) if hasattr(cfg, "get") else getattr(cfg, "model_format", None)
+        self.model_format = str(fmt or "flat_v1")
+        if self.model_format not in ("flat_v1", "dtensor"):
+            raise ValueError(f"checkpoint.model_format must be flat_v1 or dtensor, got {self.model_format!r}")
 
     @property
     def rank(self):
@@ -66,7 +76,14 @@ class FSDPCheckpointManager(BaseCheckpointManager):
         model_f, optim_f, extra_f = self._names(local_path)
         s = e.store
         payload = []
-        if self.should_save_model:
+        zero3_now = bool(getattr(e, "_zero3_rows", None))
+        if self.should_save_model and self.model_format == "dtensor":
+            from .dtensor_interchange import dtensor_model_payload
+
+            if zero3_now or getattr(e.model, "lora_config", None):
+                raise NotImplementedError("checkpoint.model_format=dtensor is available for full resident weights (no ZeRO-3 row sharding, no LoRA adapters)")
+            payload.append((model_f, dtensor_model_payload(e.model.hf_named_tensors(), e.rank, e.world, e.fsdp_size)))
+        elif self.should_save_model:
             shard = s.flat[s.shard_slice].detach().to("cpu", copy=True)
             payload.append((model_f, {"format": "flat_v1", "names": s.names, "shapes": [tuple(p.shape) for p in s.params],
                                       "offsets": s.offsets, "total": s.total, "shard_size": s.shard_size,
@@ -97,7 +114,7 @@ class FSDPCheckpointManager(BaseCheckpointManager):
         zero3 = bool(getattr(e, "_zero3_rows", None))
         if e.rank == 0:
             with open(os.path.join(local_path, "fsdp_config.json"), "w") as f:
-                meta = {"FSDP_version": 2, "world_size": e.world, "format": "flat_v1"}
+                meta = {"FSDP_version": 2, "world_size": e.world, "format": self.model_format}
                 if getattr(e.model, "lora_config", None):
                     meta["lora"] = dict(e.model.lora_config)       # the shards then hold the adapters only (python -m verl_b200.scripts.merge_lora)
                 json.dump(meta, f, indent=2)
@@ -134,10 +151,27 @@ class FSDPCheckpointManager(BaseCheckpointManager):
         e = self.engine
         model_f, optim_f, extra_f = self._names(local_path)
         s = e.store
+        named_format = False
         if self.should_load_model:
-            if not os.path.exists(model_f):
-                raise FileNotFoundError(f"{model_f} not found (sharded checkpoints reload only at the same world size)")
-            st = torch.load(model_f, map_location="cpu", weights_only=False)
+            from .dtensor_interchange import is_named_tensor_payload, merge_sharded_model_files, saved_world_size
+
+            probe = model_f if os.path.exists(model_f) else None
+            if probe is None:       # another world size: only the named-tensor form can be re-cut
+                try:
+                    probe = os.path.join(local_path, f"model_world_size_{saved_world_size(local_path)}_rank_0.pt")
+                except FileNotFoundError:
+                    probe = None
+            if probe is None or not os.path.exists(probe):
+                raise FileNotFoundError(f"{model_f} not found (flat_v1 sharded checkpoints reload only at the same world size)")
+            st = torch.load(probe, map_location="cpu", weights_only=False)
+            named_format = is_named_tensor_payload(st)
+            if not named_format and probe != model_f:
+                raise FileNotFoundError(f"{model_f} not found (flat_v1 sharded checkpoints reload only at the same world size)")
+        if self.should_load_model and named_format:
+            # the reference's payload: every rank merges the dim-0 shards and copies the weights into its resident parameters
+            del st
+            e.model.load_hf_state_dict(merge_sharded_model_files(local_path), strict=True)
+        elif self.should_load_model:
             assert st["total"] == s.total and st["names"] == s.names, "checkpoint layout does not match this model"
             s.flat[s.shard_slice].copy_(st["flat_shard"].to(s.flat.dtype))
             if e.world > 1 and e.fsdp_size > 1:
@@ -148,8 +182,10 @@ class FSDPCheckpointManager(BaseCheckpointManager):
                     dist.all_gather(parts, s.flat[s.shard_slice].clone(), group=e.fsdp_group)
                     s.flat.copy_(torch.cat(parts))
         optimizer_loaded = False
-        if self.should_load_optimizer and not e.forward_only and os.path.exists(optim_f):
+        if self.should_load_optimizer and not e.forward_only and os.path.exists(optim_f) and not named_format:
             st = torch.load(optim_f, map_location="cpu", weights_only=False)
+            if "master" not in st:
+                raise ValueError(f"{optim_f} holds per-parameter optimizer state of another framework; set checkpoint.load_contents=[model] to load the weights only")
             e.master.copy_(st["master"])
             e.exp_avg.copy_(st["exp_avg"])
             e.exp_avg_sq.copy_(st["exp_avg_sq"])

@@ -60,7 +60,9 @@ class MegatronCheckpointManager(BaseCheckpointManager):
             contents.append("model")
             torch.save({"format": "flat_mp_v1", "names": s.names, "shapes": [tuple(p.shape) for p in s.params], "offsets": s.offsets,
                         "total": s.total, "shard_size": s.shard_size, "dtype": str(s.flat.dtype),
-                        "tp_rank": e.tp_rank, "pp_rank": e.pp_rank, "dp_rank": e.fsdp_rank, "layer_offset": e.model.layer_offset,
+                        "tp_rank": e.tp_rank, "pp_rank": e.pp_rank, "dp_rank": e.fsdp_rank, "layer_offset": getattr(e.model, "layer_offset", 0),
+                        # names in the full model (under virtual pipeline stages a rank holds several layer blocks)
+                        "global_names": [e._gname(n) for n in s.names] if hasattr(e, "_gname") else None,
                         "flat_shard": s.flat[s.shard_slice].detach().to("cpu", copy=True)}, model_f)
         if self.should_save_optimizer and not e.forward_only:
             contents.append("optimizer")
@@ -93,6 +95,7 @@ class MegatronCheckpointManager(BaseCheckpointManager):
                 json.dump({"format": "flat_mp_v1", "tensor_model_parallel_size": e.tp_size, "pipeline_model_parallel_size": e.pp_size,
                            # the weights / optimizer state of a (tp, pp) position are cut over the DP x CP ranks: that many shard files
                            "data_parallel_size": e.fsdp_size, "context_parallel_size": int(getattr(e, "cp_size", 1)), "sequence_parallel": bool(getattr(e, "tp_sp", False)),
+                           "virtual_pipeline_model_parallel_size": int(getattr(e, "vpp", 1)),
                            "stage_layers": [[r.start, r.stop] for r in (stage_layer_range(e.cfg.num_hidden_layers, e.pp_size, p) for p in range(e.pp_size))],
                            "model_config": dataclasses.asdict(e.cfg) if dataclasses.is_dataclass(e.cfg) else dict(vars(e.cfg))}, f, indent=2, default=str)
             with open(os.path.join(local_path, "ckpt_contents.json"), "w") as f:

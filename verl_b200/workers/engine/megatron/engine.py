@@ -52,7 +52,6 @@ def _new_groups(rank: int, rank_lists: list[list[int]]):
     return mine, mine_ranks
 
 
-@EngineRegistry.register(model_type="language_model", backend=["megatron"], device=["cuda", "cpu"])
 class _VirtualChunks(torch.nn.Module):
     """The model chunks one pipeline rank holds under virtual pipeline parallelism (chunk c = virtual stage c * pp + pp_rank)."""
 
@@ -80,6 +79,7 @@ class _VirtualChunks(torch.nn.Module):
         super().__setattr__(name, value)
 
 
+@EngineRegistry.register(model_type="language_model", backend=["megatron"], device=["cuda", "cpu"])
 class MegatronEngine(FSDPEngine):
     def __init__(self, model_config, engine_config=None, optimizer_config=None, checkpoint_config=None):
         super().__init__(model_config, engine_config, optimizer_config, checkpoint_config)
