@@ -256,6 +256,28 @@ _ext.check_status("dynamic cp engine")
 d_d = (lp_d.float() - lp_ref.float()).abs().max().item()
 print("dynamic cp", "d_lp", d_d, "gn", gn_d, gn_ref, "groups", dcp.dcp_stats, flush=True)
 assert d_d < 0.02 and abs(gn_d - gn_ref) < 0.01 * gn_ref, (d_d, gn_d, gn_ref)
+# ---- pipeline parallelism with virtual stages on NCCL: 2 ranks x 2 model chunks, interleaved 1F1B, three micro-batches (not a multiple
+# of the pipeline depth), against a single-GPU engine of the same 4-layer model
+cfg4 = PRESETS["tiny-qwen2-gpu"].replace(num_hidden_layers=4)
+ref4 = FSDPEngine(cfg4, {"seed": 1, "use_symmetric_memory": False, "fsdp_size": 1}, {"lr": 1e-3}, {})
+ref4.initialize()
+vp = MegatronEngine(cfg4, {"seed": 1, "pipeline_model_parallel_size": world, "virtual_pipeline_model_parallel_size": 2}, {"lr": 1e-3}, {})
+vp.initialize()
+data6 = make_batch(bs=6, P=40, R=60, vocab=4096)
+data6.meta_info["micro_batch_size_per_gpu"] = 2
+lp_v = vp.infer_batch(data6)["model_output"]["log_probs"]
+vp.optimizer_zero_grad()
+vp.forward_backward_batch(data6, loss_fn)
+gn_v = vp.optimizer_step()
+torch.cuda.synchronize()
+_ext.check_status("vpp engine")
+lp_r4 = ref4.infer_batch(data6)["model_output"]["log_probs"]
+ref4.optimizer_zero_grad()
+ref4.forward_backward_batch(data6, loss_fn)
+gn_r4 = ref4.optimizer_step()
+d_v = (lp_v.float().cpu() - lp_r4.float().cpu()).abs().max().item()
+print("vpp", "d_lp", d_v, "gn", gn_v, gn_r4, flush=True)
+assert d_v < 0.02 and abs(gn_v - gn_r4) < 0.01 * gn_r4, (d_v, gn_v, gn_r4)
 dist.barrier()
 if rank == 0:
     print("SP_TP_OK", d_lp, rel, gn)

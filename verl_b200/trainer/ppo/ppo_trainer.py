@@ -380,6 +380,43 @@ class PPOTrainer:
                 f.write(json.dumps(row, ensure_ascii=False) + "\n")
         return fn
 
+    def _served_teacher_topk(self, batch: DataProto) -> DataProto:
+        """Top-k heads of teachers that run on rollout servers of their own (``distillation.teacher_mode=server``): servers listed in
+        ``distillation.teacher_addresses`` ({routing key: [host:port, ...]}) are used as they are, otherwise one fleet per entry of
+        ``distillation.teacher_models`` is started on ``distillation.teacher_devices``. Samples are routed by
+        ``distillation.teacher_key`` of their non-tensor data when several teachers exist."""
+        from verl_b200.experimental.teacher_loop import AsyncTeacherLLMServerManager, build_teacher_fleet
+        from verl_b200.workers.rollout.llm_server import LLMServerClient
+
+        d = _g(self.config, "actor_rollout_ref.distillation", {})
+        if getattr(self, "_teacher_mgr", None) is None:
+            addrs = dict(_g(d, "teacher_addresses", None) or {})
+            if addrs:
+                clients = {k: LLMServerClient({f"{k}-{i}": a for i, a in enumerate(v if isinstance(v, (list, tuple)) else [v])}) for k, v in addrs.items()}
+                self._teacher_fleet = {}
+            else:
+                models = dict(_g(d, "teacher_models", None) or {})
+                if not models:
+                    tm = _g(d, "teacher_model", {}) or {}
+                    models = {"default": {"model_path": tm.get("path") or tm.get("preset")}}
+                devs = _g(d, "teacher_devices", None)
+                n = sum(int((m.get("num_replicas", 1) if hasattr(m, "get") else 1) or 1) for m in models.values())
+                devs = [None] * n if devs in (None, "", []) else [str(x) for x in (devs if isinstance(devs, (list, tuple)) else str(devs).split(","))]
+                self._teacher_fleet = build_teacher_fleet(models, devs, int(_g(d, "n_gpus_per_node", 8) or 8), _g(self.config, "actor_rollout_ref.rollout", None))
+                clients = {k: m.client() for k, m in self._teacher_fleet.items()}
+            self._teacher_mgr = AsyncTeacherLLMServerManager({"teacher_key": _g(d, "teacher_key", "data_source"), "topk": int(_g(d, "topk", 32)),
+                                                              "teacher_models": {k: {} for k in clients}}, clients)
+        mgr = self._teacher_mgr
+        keys = None
+        if len(mgr.teacher_client) > 1:
+            col = batch.non_tensor_batch.get(mgr.teacher_key)
+            if col is None:
+                raise ValueError(f"multi-teacher distillation routes by {mgr.teacher_key!r}, which the batch does not carry")
+            keys = [str(x) for x in col]
+        ids, lps = mgr.compute_teacher_topk(batch.batch["prompts"], batch.batch["responses"], batch.batch["attention_mask"], keys,
+                                            int(getattr(self.tokenizer, "pad_token_id", 0) or 0))
+        return DataProto.from_dict(tensors={"teacher_topk_ids": ids, "teacher_topk_log_probs": lps})
+
     def _validate(self) -> dict:
         if self.val_dataloader is None or self.val_reward_fn is None:
             return {}
@@ -501,7 +538,10 @@ class PPOTrainer:
                     batch = batch.union(self.ref_policy_wg.compute_ref_log_prob(batch))
             if bool(_g(cfg, "actor_rollout_ref.distillation.enable", False)):
                 with marked_timer("teacher", timing_raw):
-                    batch = batch.union(self.actor_rollout_wg.compute_teacher_topk(batch))
+                    if str(_g(cfg, "actor_rollout_ref.distillation.teacher_mode", "colocated")) == "server":
+                        batch = batch.union(self._served_teacher_topk(batch))
+                    else:
+                        batch = batch.union(self.actor_rollout_wg.compute_teacher_topk(batch))
             if self.use_critic:
                 with marked_timer("values", timing_raw):
                     batch = batch.union(self.critic_wg.compute_values(batch))

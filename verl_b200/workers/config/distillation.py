@@ -41,10 +41,15 @@ class DistillationConfig(BaseConfig):
     nnodes: int = 0
     teacher_key: str = 'data_source'
     teacher_models: dict = field(default_factory=lambda: {})
+    teacher_mode: str = 'colocated'
+    teacher_devices: Any = None
+    teacher_addresses: dict = field(default_factory=lambda: {})
     distillation_loss: DistillationLossConfig = _sub(DistillationLossConfig)
 
     def __post_init__(self):
         if self.loss not in ("forward_kl", "reverse_kl", "jsd"):
             raise ValueError(f"unknown distillation loss {self.loss!r}")
+        if self.teacher_mode not in ("colocated", "server"):
+            raise ValueError(f"distillation.teacher_mode must be colocated or server, got {self.teacher_mode!r}")
         if int(self.topk) < 1:
             raise ValueError("distillation.topk must be >= 1")

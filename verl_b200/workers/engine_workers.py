@@ -263,7 +263,9 @@ class ActorRolloutRefWorker(Worker):
             self.ref.reset()
         dcfg = cfg_get(c, "distillation", None)
         self.teacher = None
-        if dcfg is not None and cfg_get(dcfg, "enable", False) and self._is_actor:
+        # teacher_mode=server: the teachers run on rollout servers of their own and the trainer fetches their top-k heads itself
+        self._distill = bool(dcfg is not None and cfg_get(dcfg, "enable", False) and self._is_actor)
+        if self._distill and str(cfg_get(dcfg, "teacher_mode", "colocated")) == "colocated":
             # frozen teacher colocated with the student (same engine type as the reference policy, its own weights)
             tcfg = _role_cfg(c, "ref" if cfg_get(c, "ref", None) is not None else "actor", "language_model")
             tcfg = dict(tcfg, model=cfg_get(dcfg, "teacher_model"), optim=None)
@@ -506,7 +508,7 @@ class ActorRolloutRefWorker(Worker):
     def update_actor(self, data: DataProto) -> DataProto:
         ac = cfg_get(self.config, "actor")
         meta = dict(data.meta_info)
-        if self.teacher is not None:
+        if self.teacher is not None or getattr(self, "_distill", False):
             meta["distillation"] = True
         meta.setdefault("temperature", float(cfg_get(self.config, "rollout.temperature", 1.0)))
         meta["calculate_entropy"] = bool(cfg_get(ac, "calculate_entropy", False)) or float(cfg_get(ac, "entropy_coeff", 0.0)) != 0.0

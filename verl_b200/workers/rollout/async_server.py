@@ -186,6 +186,9 @@ class AsyncRolloutServer:
             sp = self._held[0][1]
             key = _sp_key(sp)
             futs: list[concurrent.futures.Future] = []
+            if getattr(sp, "prompt_logprobs", -1) >= 0:
+                self._score(self._take(key), int(sp.prompt_logprobs))
+                continue
 
             def admit():
                 if self._paused.is_set():
@@ -214,6 +217,23 @@ class AsyncRolloutServer:
                 self._fail_queued()
             self._idle.set()
 
+    def _score(self, items: list, k: int) -> None:
+        """Teacher-style requests: no generation, the per-position (top-k) log-probs of the sequences themselves."""
+        self._idle.clear()
+        t0 = time.perf_counter()
+        try:
+            res = self.engine.score_prompts([it[0] for it in items], k)
+            for it, (ids, lps) in zip(items, res):
+                self.stats["finished"] += 1
+                it[2].set_result(TokenOutput(token_ids=[], log_probs=[], stop_reason="scored",
+                                             extra_fields={"prompt_ids": ids.tolist(), "prompt_logprobs": lps.tolist()}))
+        except Exception as e:  # noqa: BLE001
+            for it in items:
+                if not it[2].done():
+                    it[2].set_exception(e)
+        self.stats["busy_s"] += time.perf_counter() - t0
+        self._idle.set()
+
     def _fail_queued(self):
         for item in self._take(None) + self._held:
             self.stats["aborted"] += 1
@@ -229,13 +249,14 @@ def build_http_app(server: AsyncRolloutServer):
         p = body.get("sampling_params", body)
         return SamplingParams(temperature=float(p.get("temperature", 1.0)), top_p=float(p.get("top_p", 1.0)), top_k=int(p.get("top_k", -1)),
                               max_tokens=int(p.get("max_tokens", p.get("max_new_tokens", 256))), ignore_eos=bool(p.get("ignore_eos", False)),
-                              seed=int(p.get("seed", 0) or 0), stop_token_ids=tuple(p.get("stop_token_ids", ()) or ()))
+                              seed=int(p.get("seed", 0) or 0), stop_token_ids=tuple(p.get("stop_token_ids", ()) or ()),
+                              prompt_logprobs=int(-1 if p.get("prompt_logprobs") is None else p.get("prompt_logprobs")))
 
     async def generate(req):
         body = await req.json()
         out = await server.generate(body["prompt_ids"], _sp(body), body.get("request_id"))
         return web.json_response({"token_ids": out.token_ids, "log_probs": out.log_probs, "stop_reason": out.stop_reason,
-                                  "num_preempted": out.num_preempted})
+                                  "num_preempted": out.num_preempted, "extra_fields": out.extra_fields or {}})
 
     def _need_tok():
         if server.tokenizer is None:

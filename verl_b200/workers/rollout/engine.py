@@ -43,6 +43,9 @@ class SamplingParams:
     ignore_eos: bool = False
     logprobs: bool = True
     top_logprobs: int = 0      # also return the k most likely tokens (ids + log-probs) at every step (score centering)
+    # >= 0: score the prompt instead of generating — per position the log-prob of the k most likely tokens under the context before it
+    # (0: only the log-prob of the token that is there). What a distillation teacher is asked for.
+    prompt_logprobs: int = -1
     seed: int = 0
     stop_token_ids: Sequence[int] = ()
 
@@ -854,6 +857,56 @@ class InferenceEngine:
                                            top_ids=r["topi"][: r["max_new"]] if "topi" in r else None,
                                            top_log_probs=r["topv"][: r["max_new"]] if "topv" in r else None, routed_experts=self._routed_of(r),
                                            stop_reason=r["stop"] or "length", num_preempted=r["num_preempted"]))
+
+    @torch.no_grad()
+    def score_prompts(self, prompts: Sequence[Sequence[int]], k: int, max_tokens_per_pass: int = 16384, chunk: int = 2048) -> list:
+        """Forward-only scoring of whole sequences (no sampling, no KV cache): for every sequence ``(ids [L, max(k, 1)] int32,
+        log_probs [L, max(k, 1)] float32)``. Row i describes the distribution for token i given tokens < i: with ``k > 0`` its k most
+        likely tokens and their log-probs, with ``k == 0`` the token that is there and its log-prob. Row 0 has no context: it
+        holds the token itself with log-prob 0. Sequences are packed into passes of at most ``max_tokens_per_pass`` tokens and the
+        vocabulary projection runs over ``chunk`` rows at a time, so no [L, V] tensor outlives its chunk."""
+        from verl_b200.models.transformer import PackedBatch
+
+        if getattr(self, "tp_size", 1) > 1:
+            raise NotImplementedError("prompt scoring runs on tensor_model_parallel_size=1 replicas")
+        model, dev = self.model, self.device
+        W = model.output_weight
+        kk = max(int(k), 1)
+        out = [None] * len(prompts)
+        order = sorted(range(len(prompts)), key=lambda i: len(prompts[i]))
+        i = 0
+        while i < len(order):
+            group, tot = [], 0
+            while i < len(order) and (not group or tot + len(prompts[order[i]]) <= max_tokens_per_pass):
+                group.append(order[i])
+                tot += len(prompts[order[i]])
+                i += 1
+            lens = [len(prompts[j]) for j in group]
+            ids = torch.tensor([t for j in group for t in prompts[j]], dtype=torch.long, device=dev)
+            pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).to(dev)
+            cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+            h = model.forward_hidden(PackedBatch(ids, pos, cu.to(dev), cu, max(lens)))
+            top_i = torch.empty(tot, kk, dtype=torch.int32, device=dev)
+            top_l = torch.empty(tot, kk, dtype=torch.float32, device=dev)
+            nxt_all = torch.cat([ids[1:], ids.new_zeros(1)])
+            for a in range(0, tot, chunk):
+                lp = torch.log_softmax(torch.nn.functional.linear(h[a:a + chunk], W).float(), -1)
+                if k > 0:
+                    v, ix = lp.topk(kk, dim=-1)
+                else:      # the log-prob of the NEXT token in the stream (shifted into place below; a sequence's last row is dropped)
+                    nxt = nxt_all[a:a + chunk]
+                    ix, v = nxt[:, None], lp.gather(-1, nxt[:, None])
+                top_i[a:a + lp.shape[0]], top_l[a:a + lp.shape[0]] = ix.to(torch.int32), v
+            top_i, top_l = top_i.cpu(), top_l.cpu()
+            off = 0
+            for j, n in zip(group, lens):
+                oi = torch.empty(n, kk, dtype=torch.int32)
+                ol = torch.zeros(n, kk, dtype=torch.float32)
+                oi[0] = int(prompts[j][0])
+                oi[1:], ol[1:] = top_i[off:off + n - 1], top_l[off:off + n - 1]         # the prediction made at row i-1 describes token i
+                out[j] = (oi, ol)
+                off += n
+        return out
 
     def abort_all(self) -> list[int]:
         """Drop every live request (used when a weight update interrupts generation)."""

@@ -87,12 +87,13 @@ class LLMServerClient:
             sess = await self._http()
             body = {"prompt_ids": list(prompt_ids), "request_id": request_id,
                     "sampling_params": {"temperature": sp.temperature, "top_p": sp.top_p, "top_k": sp.top_k, "max_tokens": sp.max_tokens,
-                                        "ignore_eos": sp.ignore_eos, "seed": sp.seed, "stop_token_ids": list(sp.stop_token_ids)}}
+                                        "ignore_eos": sp.ignore_eos, "seed": sp.seed, "stop_token_ids": list(sp.stop_token_ids),
+                                        "prompt_logprobs": sp.prompt_logprobs if sp.prompt_logprobs >= 0 else None}}
             async with sess.post(f"http://{target}/generate", json=body) as resp:
                 resp.raise_for_status()
                 d = await resp.json()
             return TokenOutput(token_ids=d["token_ids"], log_probs=d.get("log_probs"), stop_reason=d.get("stop_reason"),
-                               num_preempted=d.get("num_preempted", 0))
+                               num_preempted=d.get("num_preempted", 0), extra_fields=d.get("extra_fields") or {})
         return await (target.generate(prompt_ids, sp, request_id, multi_modal) if multi_modal else target.generate(prompt_ids, sp, request_id))
 
     async def generate(self, request_id: Optional[str], prompt_ids, sampling_params: Optional[SamplingParams] = None,
