@@ -96,6 +96,17 @@ def _vl_config():
                                    mrope_section=[2, 3, 3]))
 
 
+def _vl3_config():
+    """The same plumbing size in the Qwen3-VL family: Qwen3 decoder, interleaved rotary streams, deep-stack features after layers 0 and 1."""
+    return ModelConfig(model_type="qwen3", vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=16, rope_theta=10000.0, max_position_embeddings=512, attention_bias=False, qk_norm=True,
+                       torch_dtype="float32",
+                       vision=dict(depth=2, embed_dim=32, num_heads=2, in_channels=3, patch_size=4, temporal_patch_size=2, spatial_merge_size=2,
+                                   hidden_size=64, image_token_id=500, video_token_id=501, vision_start_token_id=502, mrope_section=[4, 2, 2],
+                                   variant="qwen3_vl", intermediate_size=48, num_position_embeddings=36, deepstack_visual_indexes=[0, 1],
+                                   mrope_interleaved=True))
+
+
 def test_config_round_trips_through_the_hf_layout(tmp_path):
     cfg = _vl_config()
     cfg.save_pretrained(str(tmp_path))
@@ -113,7 +124,8 @@ def test_config_round_trips_through_the_hf_layout(tmp_path):
     assert ModelConfig.from_hf_dict(nested).vision == back.vision
 
 
-def test_engine_trains_a_vision_language_model_on_image_prompts(tmp_path):
+@pytest.mark.parametrize("family", ["qwen2_vl", "qwen3_vl"])
+def test_engine_trains_a_vision_language_model_on_image_prompts(tmp_path, family):
     """The sharded-DP engine with a vision-language config: log-probs of a batch whose prompts hold images equal a direct
     forward of the model per sequence, the vision tower receives gradients, and an optimizer step changes it."""
     import numpy as np
@@ -121,7 +133,8 @@ def test_engine_trains_a_vision_language_model_on_image_prompts(tmp_path):
     from verl_b200.protocol import DataProto
     from verl_b200.workers.engine.fsdp.engine import FSDPEngine
 
-    eng = FSDPEngine(_vl_config(), {"seed": 3, "model_dtype": "float32"}, {"lr": 1e-3, "clip_grad": 1.0}, {})
+    v3 = family == "qwen3_vl"
+    eng = FSDPEngine(_vl3_config() if v3 else _vl_config(), {"seed": 3, "model_dtype": "float32"}, {"lr": 1e-3, "clip_grad": 1.0}, {})
     eng.initialize()
     assert type(eng.model).__name__ == "VisionLanguageModel"
     g = torch.Generator().manual_seed(5)
@@ -167,14 +180,20 @@ def test_engine_trains_a_vision_language_model_on_image_prompts(tmp_path):
             assert abs(lp[i, t] - ref[n_prompt - 1 + t, ids[n_prompt + t]]) < 1e-4
     from tests.test_engine_on_cpu import loss_fn
 
-    before = eng.model.visual.merger.mlp[2].weight.detach().clone()
+    last = eng.model.visual.merger.linear_fc2.weight if v3 else eng.model.visual.merger.mlp[2].weight
+    before = last.detach().clone()
     eng.optimizer_zero_grad()
     eng.forward_backward_batch(data, loss_fn)
     assert eng.model.visual.patch_embed.proj.weight.main_grad.abs().sum() > 0
+    if v3:      # the deep-stack merger and the position table are trained through the decoder's stream (the features added after the LAST
+        # decoder layer only change the image rows themselves, which carry no loss: only the first merger of this 2-layer model learns)
+        assert eng.model.visual.deepstack_merger_list[0].linear_fc1.weight.main_grad.abs().sum() > 0
+        assert eng.model.visual.deepstack_merger_list[1].linear_fc1.weight.main_grad.abs().sum() == 0
+        assert eng.model.visual.pos_embed.weight.main_grad.abs().sum() > 0
     gn = eng.optimizer_step()
-    assert gn > 0 and not torch.equal(before, eng.model.visual.merger.mlp[2].weight)
+    assert gn > 0 and not torch.equal(before, last)
     exported = dict(eng.get_per_tensor_param()[0])
-    assert "visual.patch_embed.proj.weight" in exported and "model.layers.0.self_attn.q_proj.weight" in exported
+    assert ("model.visual.patch_embed.proj.weight" if v3 else "visual.patch_embed.proj.weight") in exported and "model.layers.0.self_attn.q_proj.weight" in exported
     # checkpoint → merger → the same tensors under Hugging Face names, and a config that parses back as vision-language
     from verl_b200.model_merger.base_model_merger import ModelMergerConfig
     from verl_b200.model_merger.fsdp_model_merger import FSDPModelMerger
@@ -251,14 +270,19 @@ def test_dataset_builds_multimodal_rows(tmp_path):
     assert batch["position_ids"].shape == (2, 4, 96) and len(batch["multi_modal_inputs"]) == 2
 
 
-def test_rollout_generates_from_image_prompts_like_a_full_forward():
+@pytest.mark.parametrize("family", ["qwen2_vl", "qwen3_vl"])
+def test_rollout_generates_from_image_prompts_like_a_full_forward(family):
     """Greedy decoding with images through the paged rollout engine equals greedy decoding by repeated full forwards of the
-    model (per-token rotary tables at prefill, position offset after the image grid at decode); identical token ids with
-    different images are not shared as one prefix."""
+    model (per-token rotary tables at prefill, position offset after the image grid at decode; for Qwen3-VL also the deep-stack
+    features added after the first layers at prefill); identical token ids with different images are not shared as one prefix."""
     from verl_b200.workers.rollout.engine import InferenceEngine, SamplingParams
 
     torch.manual_seed(0)
-    model = VisionLanguageModel(_vl_config(), dtype=torch.float32, device=torch.device("cpu"), seed=11).eval()
+    model = VisionLanguageModel(_vl_config() if family == "qwen2_vl" else _vl3_config(), dtype=torch.float32, device=torch.device("cpu"), seed=11).eval()
+    if family == "qwen3_vl":
+        with torch.no_grad():      # the seeded init leaves deep-stack outputs tiny: scale them up so that dropping them would change tokens
+            for mod in model.visual.deepstack_merger_list:
+                mod.linear_fc2.weight.mul_(40.0)
     g = torch.Generator().manual_seed(2)
     grid = torch.tensor([[1, 4, 4]])
     prompt = [7, 8, 502] + [500] * 4 + [503, 9, 10, 11]
@@ -411,3 +435,67 @@ def test_sft_dataset_with_images():
     # the text-only dataset is unchanged by the new arguments
     plain = MultiTurnSFTDataset(tokenizer=ByteChatTokenizer(), max_length=96, rows=rows[1:])
     assert torch.equal(plain[0]["input_ids"], b["input_ids"]) and plain[0]["position_ids"].dim() == 1
+
+
+def test_qwen3_vl_tower_deepstack_and_logits_match_hf():
+    """The Qwen3-VL family against Hugging Face: tower (interpolated learned positions, biased patch embedding, tanh-GELU MLP), the
+    deep-stack features added to the decoder's stream after its first layers, the interleaved multimodal rotary embedding and the
+    Qwen3 decoder (per-head q/k norms) — compared on the tower output, the deep-stack features and the logits of a sequence."""
+    try:
+        from transformers import Qwen3VLConfig, Qwen3VLForConditionalGeneration
+    except ImportError:
+        pytest.skip("this transformers build has no Qwen3-VL")
+    torch.manual_seed(0)
+    hf_cfg = Qwen3VLConfig(
+        text_config=dict(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                         head_dim=16, max_position_embeddings=512, rope_parameters={"rope_type": "default", "rope_theta": 10000.0,
+                                                                                     "mrope_section": [4, 2, 2], "mrope_interleaved": True},
+                         tie_word_embeddings=False),
+        vision_config=dict(depth=3, hidden_size=32, intermediate_size=48, num_heads=2, in_channels=3, patch_size=4, temporal_patch_size=2,
+                           spatial_merge_size=2, out_hidden_size=64, num_position_embeddings=36, deepstack_visual_indexes=[0, 2]),
+        image_token_id=500, video_token_id=501, vision_start_token_id=502, vision_end_token_id=503)
+    hf = Qwen3VLForConditionalGeneration(hf_cfg).float().eval()
+    with torch.no_grad():      # biases and norms away from their init values, so that a dropped one shows
+        for n, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+    cfg = ModelConfig.from_hf_dict(hf_cfg.to_dict())
+    v = cfg.vision
+    assert v["variant"] == "qwen3_vl" and v["embed_dim"] == 32 and v["hidden_size"] == 64 and v["deepstack_visual_indexes"] == [0, 2]
+    assert v["mrope_interleaved"] and v["mrope_section"] == [4, 2, 2] and cfg.qk_norm and not cfg.attention_bias and cfg.head_dim == 16
+    cfg = cfg.replace(torch_dtype="float32", rms_norm_eps=hf_cfg.text_config.rms_norm_eps)
+    ours = VisionLanguageModel(cfg, dtype=torch.float32, device=torch.device("cpu"))
+    ours.load_hf_state_dict(hf.state_dict())
+    ours.eval()
+    g = torch.Generator().manual_seed(1)
+    grid = torch.tensor([[1, 6, 10], [1, 4, 4], [1, 2, 6]])
+    pixels = torch.randn(int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum()), 96, generator=g)
+    with torch.no_grad():
+        want = hf.model.visual(pixels, grid_thw=grid)
+        got = ours.visual(pixels, grid)
+    assert got.shape == want.pooler_output.shape == (15 + 4 + 3, 64)
+    assert torch.allclose(got, want.pooler_output, atol=1e-5, rtol=1e-4), (got - want.pooler_output).abs().max()
+    assert len(ours.visual.last_deepstack) == 2
+    for a, b in zip(ours.visual.last_deepstack, want.deepstack_features):
+        assert torch.allclose(a, b, atol=1e-5, rtol=1e-4), (a - b).abs().max()
+    text = lambda n: torch.randint(1, 400, (n,), generator=g).tolist()
+    ids = torch.tensor(text(3) + [502] + [500] * 15 + [503] + text(4) + [502] + [500] * 4 + [503] + [502] + [500] * 3 + [503] + text(5))
+    pos3, _ = get_rope_index(ids, grid, ours.vcfg)
+    with torch.no_grad():
+        want = hf(input_ids=ids[None], pixel_values=pixels, image_grid_thw=grid, attention_mask=torch.ones_like(ids)[None],
+                  position_ids=pos3[:, None].contiguous()).logits[0]
+        pb = PackedBatch(ids, torch.arange(len(ids), dtype=torch.int32), torch.tensor([0, len(ids)], dtype=torch.int32))
+        got = ours(pb, pixel_values=pixels, image_grid_thw=grid, mrope_positions=pos3, return_logits=True)["logits"]
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), (got - want).abs().max()
+    # the deep-stack path matters: without it the logits differ
+    with torch.no_grad():
+        ours.visual.deepstack_merger_list[0].linear_fc2.weight.zero_()
+        ours.visual.deepstack_merger_list[0].linear_fc2.bias.zero_()
+        pb = PackedBatch(ids, torch.arange(len(ids), dtype=torch.int32), torch.tensor([0, len(ids)], dtype=torch.int32))
+        off = ours(pb, pixel_values=pixels, image_grid_thw=grid, mrope_positions=pos3, return_logits=True)["logits"]
+    assert (off - want).abs().max() > 1e-3
+    # names and config round trip in the family's layout
+    names = {n for n, _ in ours.hf_named_tensors()}
+    assert "model.visual.pos_embed.weight" in names and "model.visual.deepstack_merger_list.1.norm.bias" in names
+    back = ModelConfig.from_hf_dict(cfg.to_hf_dict())
+    assert back.vision == cfg.vision and back.qk_norm and back.head_dim == 16

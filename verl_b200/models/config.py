@@ -86,7 +86,7 @@ class ModelConfig:
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
         mt = d.get("model_type", "llama")
         vision = None
-        if mt in ("qwen2_vl", "qwen2_5_vl"):
+        if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl"):
             # vision-language checkpoint: decoder fields sit in text_config (newer layout) or at the top level (older one)
             import dataclasses as _dc
 
@@ -96,8 +96,13 @@ class ModelConfig:
             vision = _dc.asdict(VisionConfig.from_hf_dict(d, text or None))
             vision["mrope_section"] = list(vision["mrope_section"])
             vision["fullatt_block_indexes"] = list(vision["fullatt_block_indexes"])
-            d = {**{k: v for k, v in d.items() if k not in ("text_config", "vision_config")}, **text, "attention_bias": True}
-            mt = "qwen2"
+            vision["deepstack_visual_indexes"] = list(vision["deepstack_visual_indexes"])
+            if mt == "qwen3_vl":      # Qwen3 decoder: per-head q/k norms, no projection biases
+                d = {**{k: v for k, v in d.items() if k not in ("text_config", "vision_config")}, **text, "attention_bias": bool(text.get("attention_bias", False))}
+                mt = "qwen3"
+            else:
+                d = {**{k: v for k, v in d.items() if k not in ("text_config", "vision_config")}, **text, "attention_bias": True}
+                mt = "qwen2"
         known = dict(
             model_type=mt,
             vocab_size=d["vocab_size"],
@@ -157,6 +162,21 @@ class ModelConfig:
             d["num_labels"] = 1
         if self.vision:
             v = dict(self.vision)
+            if v.get("variant") == "qwen3_vl":
+                v.pop("variant")
+                text = {k: d.pop(k) for k in list(d) if k not in ("architectures", "torch_dtype", "tie_word_embeddings")}
+                text.update(model_type="qwen3_vl_text", rope_scaling={"rope_type": "default", "mrope_section": list(v.pop("mrope_section")),
+                                                                      "mrope_interleaved": bool(v.pop("mrope_interleaved", True))})
+                d.update(model_type="qwen3_vl", architectures=["Qwen3VLForConditionalGeneration"], image_token_id=v.pop("image_token_id"),
+                         video_token_id=v.pop("video_token_id"), vision_start_token_id=v.pop("vision_start_token_id"), text_config=text)
+                v["out_hidden_size"], v["hidden_size"] = v.pop("hidden_size"), v.pop("embed_dim")
+                for k in ("mlp_ratio", "window_size", "fullatt_block_indexes"):
+                    v.pop(k, None)
+                v["deepstack_visual_indexes"] = list(v["deepstack_visual_indexes"])
+                d["vision_config"] = v
+                return d
+            for k in ("num_position_embeddings", "deepstack_visual_indexes", "mrope_interleaved"):
+                v.pop(k, None)
             new = v.pop("variant", "qwen2_vl") == "qwen2_5_vl"
             d.update(model_type="qwen2_5_vl" if new else "qwen2_vl",
                      architectures=["Qwen2_5_VLForConditionalGeneration" if new else "Qwen2VLForConditionalGeneration"],

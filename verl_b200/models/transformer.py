@@ -30,7 +30,7 @@ class PackedBatch:
     """Device-side description of a packed micro-batch."""
 
     __slots__ = ("input_ids", "position_ids", "cu_seqlens", "cu_seqlens_cpu", "max_seqlen", "routed_experts", "global_position_ids",
-                 "attn_expand", "visual_embeds", "visual_token_ids", "rope_override", "mm", "cp_zigzag")
+                 "attn_expand", "visual_embeds", "visual_token_ids", "rope_override", "mm", "cp_zigzag", "deepstack_embeds", "visual_rows")
 
     def __init__(self, input_ids, position_ids, cu_seqlens, cu_seqlens_cpu=None, max_seqlen=None, routed_experts=None):
         self.input_ids = input_ids
@@ -50,6 +50,9 @@ class PackedBatch:
         # vision-language models (verl_b200.models.vision): rows that replace the embeddings of the image placeholder tokens,
         # and per-token rotary tables (cos, sin) [T, D/2] of the multimodal rotary embedding
         self.visual_embeds = self.visual_token_ids = self.rope_override = self.mm = None
+        # deep-stack vision features (Qwen3-VL): entry i [n_visual_tokens, H] is added to the stream at the visual rows after decoder
+        # layer i; visual_rows caches the indices of those rows
+        self.deepstack_embeds = self.visual_rows = None
         self.cp_zigzag = False        # context parallelism: the local rows are two chunks of the stream (zig-zag placement)
 
 
@@ -332,15 +335,20 @@ class DecoderLM(nn.Module):
                 h = ops.embedding(pb.input_ids, self.embed_tokens)
             if pb.visual_embeds is not None:
                 is_vis = torch.isin(pb.input_ids, torch.tensor(pb.visual_token_ids, device=pb.input_ids.device))
-                h = h.index_put((is_vis.nonzero(as_tuple=True)[0],), pb.visual_embeds.to(h.dtype))
+                pb.visual_rows = is_vis.nonzero(as_tuple=True)[0]
+                h = h.index_put((pb.visual_rows,), pb.visual_embeds.to(h.dtype))
         else:
             h = h_in
         residual = None
-        for layer in self.layers:
+        deep = pb.deepstack_embeds if self.pre_process else None
+        for li, layer in enumerate(self.layers):
             if self.gradient_checkpointing and torch.is_grad_enabled():
                 h, residual = checkpoint(layer, h, residual, pb, cos, sin, self.sp_group, use_reentrant=False)
             else:
                 h, residual = layer(h, residual, pb, cos, sin, self.sp_group)
+            if deep is not None and li < len(deep) and pb.visual_rows is not None:
+                # the stream after a layer is h + residual: adding to either term adds to the stream
+                h = h.index_add(0, pb.visual_rows, deep[li].to(h.dtype))
         if not self.post_process:
             return h + residual if residual is not None else h
         if residual is None:
@@ -442,7 +450,7 @@ def native_to_hf_tensors(cfg: ModelConfig, params: dict) -> Iterator[tuple[str, 
                 t = params[k]
                 if k == "visual.patch_embed.proj.weight" and v and t.dim() == 2:
                     t = t.view(t.shape[0], v["in_channels"], v["temporal_patch_size"], v["patch_size"], v["patch_size"])
-                yield k, t
+                yield ("model." + k if v.get("variant") == "qwen3_vl" else k), t
         return
     if "embed_tokens" in params:
         yield "model.embed_tokens.weight", params["embed_tokens"]

@@ -45,10 +45,16 @@ class VisionConfig:
     vision_start_token_id: int = 151652
     mrope_section: tuple = (16, 24, 24)
     # Qwen2.5-VL tower: RMSNorm + gated SiLU MLP, attention inside windows of window_size pixels except in the listed blocks
-    variant: str = "qwen2_vl"               # "qwen2_vl" | "qwen2_5_vl"
+    variant: str = "qwen2_vl"               # "qwen2_vl" | "qwen2_5_vl" | "qwen3_vl"
     intermediate_size: int = 0
     window_size: int = 0
     fullatt_block_indexes: tuple = ()
+    # Qwen3-VL tower: learned position table interpolated to the image grid, biased patch embedding, tanh-GELU MLP, and "deep-stack"
+    # mergers after the listed blocks whose outputs are added to the language model's stream after its first layers; the language
+    # model's multimodal rotary embedding interleaves the three position streams over the frequencies instead of chunking them
+    num_position_embeddings: int = 0
+    deepstack_visual_indexes: tuple = ()
+    mrope_interleaved: bool = False
 
     @property
     def patch_dim(self) -> int:
@@ -58,6 +64,14 @@ class VisionConfig:
     def from_hf_dict(cls, d: dict, text: Optional[dict] = None) -> "VisionConfig":
         v = d.get("vision_config", {})
         rope = (text or d).get("rope_scaling") or (text or d).get("rope_parameters") or {}
+        if d.get("model_type") == "qwen3_vl":
+            return cls(depth=v.get("depth", 27), embed_dim=v.get("hidden_size", 1152), num_heads=v.get("num_heads", 16), in_channels=v.get("in_channels", 3),
+                       patch_size=v.get("patch_size", 16), temporal_patch_size=v.get("temporal_patch_size", 2),
+                       spatial_merge_size=v.get("spatial_merge_size", 2), hidden_size=v.get("out_hidden_size", (text or d).get("hidden_size", 4096)),
+                       image_token_id=d.get("image_token_id", 151655), video_token_id=d.get("video_token_id", 151656),
+                       vision_start_token_id=d.get("vision_start_token_id", 151652), mrope_section=tuple(rope.get("mrope_section", (24, 20, 20))),
+                       variant="qwen3_vl", intermediate_size=v.get("intermediate_size", 4304), num_position_embeddings=v.get("num_position_embeddings", 2304),
+                       deepstack_visual_indexes=tuple(v.get("deepstack_visual_indexes", (8, 16, 24))), mrope_interleaved=bool(rope.get("mrope_interleaved", True)))
         if d.get("model_type") == "qwen2_5_vl":
             return cls(depth=v.get("depth", 32), embed_dim=v.get("hidden_size", 1280), num_heads=v.get("num_heads", 16), in_channels=v.get("in_channels", 3),
                        patch_size=v.get("patch_size", 14), temporal_patch_size=v.get("temporal_patch_size", 2),
@@ -85,6 +99,7 @@ class _VisionBlock(nn.Module):
         E, Hm = cfg.embed_dim, int(cfg.embed_dim * cfg.mlp_ratio)
         kw = dict(dtype=dtype, device=device)
         self.gated = cfg.variant == "qwen2_5_vl"
+        self.v3 = cfg.variant == "qwen3_vl"
         self.attn = nn.Module()
         self.attn.qkv, self.attn.proj = nn.Linear(E, 3 * E, **kw), nn.Linear(E, E, **kw)
         self.mlp = nn.Module()
@@ -92,6 +107,9 @@ class _VisionBlock(nn.Module):
             I = cfg.intermediate_size
             self.norm1, self.norm2 = nn.RMSNorm(E, eps=1e-6, **kw), nn.RMSNorm(E, eps=1e-6, **kw)
             self.mlp.gate_proj, self.mlp.up_proj, self.mlp.down_proj = nn.Linear(E, I, **kw), nn.Linear(E, I, **kw), nn.Linear(I, E, **kw)
+        elif self.v3:
+            self.norm1, self.norm2 = nn.LayerNorm(E, eps=1e-6, **kw), nn.LayerNorm(E, eps=1e-6, **kw)
+            self.mlp.linear_fc1, self.mlp.linear_fc2 = nn.Linear(E, cfg.intermediate_size, **kw), nn.Linear(cfg.intermediate_size, E, **kw)
         else:
             self.norm1, self.norm2 = nn.LayerNorm(E, eps=1e-6, **kw), nn.LayerNorm(E, eps=1e-6, **kw)
             self.mlp.fc1, self.mlp.fc2 = nn.Linear(E, Hm, **kw), nn.Linear(Hm, E, **kw)
@@ -112,6 +130,8 @@ class _VisionBlock(nn.Module):
         y = self.norm2(x)
         if self.gated:
             return x + self.mlp.down_proj(F.silu(self.mlp.gate_proj(y)) * self.mlp.up_proj(y))
+        if self.v3:
+            return x + self.mlp.linear_fc2(F.gelu(self.mlp.linear_fc1(y), approximate="tanh"))
         h = self.mlp.fc1(y)
         return x + self.mlp.fc2(h * torch.sigmoid(1.702 * h))       # QuickGELU
 
@@ -123,11 +143,24 @@ class VisionTower(nn.Module):
         kw = dict(dtype=dtype, device=device)
         E, m2 = cfg.embed_dim, cfg.spatial_merge_size ** 2
         self.patch_embed = nn.Module()
-        self.patch_embed.proj = nn.Linear(cfg.patch_dim, E, bias=False, **kw)
+        self.v3 = cfg.variant == "qwen3_vl"
+        self.patch_embed.proj = nn.Linear(cfg.patch_dim, E, bias=self.v3, **kw)
         self.blocks = nn.ModuleList([_VisionBlock(cfg, dtype, device) for _ in range(cfg.depth)])
         self.merger = nn.Module()
-        self.merger.ln_q = nn.RMSNorm(E, eps=1e-6, **kw) if cfg.variant == "qwen2_5_vl" else nn.LayerNorm(E, eps=1e-6, **kw)
-        self.merger.mlp = nn.Sequential(nn.Linear(E * m2, E * m2, **kw), nn.GELU(), nn.Linear(E * m2, cfg.hidden_size, **kw))
+        if self.v3:
+            self.pos_embed = nn.Embedding(cfg.num_position_embeddings, E, **kw)
+
+            def merger(post_shuffle: bool):
+                mod = nn.Module()
+                mod.norm = nn.LayerNorm(E * m2 if post_shuffle else E, eps=1e-6, **kw)
+                mod.linear_fc1, mod.linear_fc2 = nn.Linear(E * m2, E * m2, **kw), nn.Linear(E * m2, cfg.hidden_size, **kw)
+                return mod
+
+            self.merger = merger(False)
+            self.deepstack_merger_list = nn.ModuleList([merger(True) for _ in cfg.deepstack_visual_indexes])
+        else:
+            self.merger.ln_q = nn.RMSNorm(E, eps=1e-6, **kw) if cfg.variant == "qwen2_5_vl" else nn.LayerNorm(E, eps=1e-6, **kw)
+            self.merger.mlp = nn.Sequential(nn.Linear(E * m2, E * m2, **kw), nn.GELU(), nn.Linear(E * m2, cfg.hidden_size, **kw))
         g = torch.Generator(device="cpu").manual_seed(seed + 7919)
         with torch.no_grad():
             for n, p in self.named_parameters():      # seeded, identical in every process: matrices N(0, 0.02²), biases 0, norms 1
@@ -158,6 +191,21 @@ class VisionTower(nn.Module):
         cos, sin = emb.cos()[:, None, :], emb.sin()[:, None, :]
         seg = [int(h * w) for t, h, w in grid_thw.tolist() for _ in range(int(t))]
         m2 = cfg.spatial_merge_size ** 2
+        if self.v3:
+            x = x + self._interpolated_positions(grid_thw.cpu()).to(x.dtype)
+            E = cfg.embed_dim
+
+            def merge(mod, t, post_shuffle):
+                t = mod.norm(t.reshape(-1, E * m2)) if post_shuffle else mod.norm(t).reshape(-1, E * m2)
+                return mod.linear_fc2(F.gelu(mod.linear_fc1(t)))
+
+            deep = []
+            for i, blk in enumerate(self.blocks):
+                x = blk(x, cos, sin, seg)
+                if i in cfg.deepstack_visual_indexes:
+                    deep.append(merge(self.deepstack_merger_list[cfg.deepstack_visual_indexes.index(i)], x, True))
+            self.last_deepstack = deep            # picked up by VisionLanguageModel.embed right after this call
+            return merge(self.merger, x, False)
         if cfg.variant != "qwen2_5_vl":
             for blk in self.blocks:
                 x = blk(x, cos, sin, seg)
@@ -176,6 +224,26 @@ class VisionTower(nn.Module):
             x = blk(x, cos, sin, seg if i in cfg.fullatt_block_indexes else win_seg)
         out = self.merger.mlp(self.merger.ln_q(x).reshape(-1, cfg.embed_dim * m2))
         return out.index_select(0, torch.argsort(win_index))
+
+    def _interpolated_positions(self, grid_thw: torch.Tensor) -> torch.Tensor:
+        """Learned position table (a square grid of ``sqrt(num_position_embeddings)`` points per side) read at the patch centres
+        of each image by bilinear interpolation, in the processor's patch order (patches of one merge window adjacent)."""
+        cfg = self.cfg
+        side, m = int(cfg.num_position_embeddings ** 0.5), cfg.spatial_merge_size
+        table = self.pos_embed.weight
+        out = []
+        for t, h, w in grid_thw.tolist():
+            hs, ws = torch.linspace(0, side - 1, h), torch.linspace(0, side - 1, w)
+            h0, w0 = hs.int(), ws.int()
+            h1, w1 = (h0 + 1).clamp(max=side - 1), (w0 + 1).clamp(max=side - 1)
+            dh, dw = (hs - h0)[:, None], (ws - w0)[None, :]
+            acc = 0
+            for hi, wi, wt in ((h0, w0, (1 - dh) * (1 - dw)), (h0, w1, (1 - dh) * dw), (h1, w0, dh * (1 - dw)), (h1, w1, dh * dw)):
+                idx = (hi[:, None] * side + wi[None, :]).flatten().long().to(table.device)
+                acc = acc + table.index_select(0, idx) * wt.flatten().to(table.device, table.dtype)[:, None]
+            acc = acc.reshape(h // m, m, w // m, m, -1).permute(0, 2, 1, 3, 4).reshape(h * w, -1)
+            out.append(acc.repeat(t, 1))
+        return torch.cat(out, 0)
 
     def _window_index(self, grid_thw: torch.Tensor):
         """Order of the merge groups window by window (windows of ``window_size`` pixels, ragged at the right / bottom edge)
@@ -240,13 +308,19 @@ def get_rope_index(input_ids: torch.Tensor, image_grid_thw: Optional[torch.Tenso
     return full, delta
 
 
-def mrope_tables(pos3: torch.Tensor, head_dim: int, theta: float, mrope_section) -> tuple[torch.Tensor, torch.Tensor]:
+def mrope_tables(pos3: torch.Tensor, head_dim: int, theta: float, mrope_section, interleaved: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """Per-token fp32 cos/sin ``[T, head_dim/2]``: frequency ``i`` reads the temporal, height or width stream according
-    to ``mrope_section`` (their sizes add up to ``head_dim/2``)."""
+    to ``mrope_section`` (their sizes add up to ``head_dim/2``): in three chunks [T.. | H.. | W..], or ``interleaved``
+    (Qwen3-VL): T H W T H W ... for the first ``3 * section`` frequencies of each of H and W, temporal for the rest."""
     half = head_dim // 2
     assert sum(mrope_section) == half, (mrope_section, head_dim)
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=pos3.device) / head_dim))
-    comp = torch.repeat_interleave(torch.arange(3, device=pos3.device), torch.tensor(list(mrope_section), device=pos3.device))
+    if interleaved:
+        comp = torch.zeros(half, dtype=torch.long, device=pos3.device)
+        for stream in (1, 2):
+            comp[stream:mrope_section[stream] * 3:3] = stream
+    else:
+        comp = torch.repeat_interleave(torch.arange(3, device=pos3.device), torch.tensor(list(mrope_section), device=pos3.device))
     p = pos3.float().index_select(0, comp)                    # [half, T]: the stream each frequency follows
     ang = (p * inv[:, None]).t().contiguous()
     return ang.cos().contiguous(), ang.sin().contiguous()
@@ -293,7 +367,9 @@ class VisionLanguageModel(nn.Module):
             pb.visual_token_ids = (self.vcfg.image_token_id, self.vcfg.video_token_id)
             if mm.get("mrope_positions") is not None:
                 pb.rope_override = mrope_tables(mm["mrope_positions"].to(pb.input_ids.device), self.cfg.head_dim, self.cfg.rope_theta,
-                                                self.vcfg.mrope_section)
+                                                self.vcfg.mrope_section, self.vcfg.mrope_interleaved)
+            if self.vcfg.variant == "qwen3_vl" and pb.visual_embeds is not None:
+                pb.deepstack_embeds = self.visual.last_deepstack
         return pb
 
     def forward_hidden(self, pb: PackedBatch, h_in=None):
@@ -320,7 +396,7 @@ class VisionLanguageModel(nn.Module):
         for n, p in self.visual.named_parameters():
             if n == "patch_embed.proj.weight":
                 p = p.view(P.embed_dim, P.in_channels, P.temporal_patch_size, P.patch_size, P.patch_size)
-            yield "visual." + n, p
+            yield ("model.visual." if P.variant == "qwen3_vl" else "visual.") + n, p
 
     @torch.no_grad()
     def load_hf_stream(self, named_tensors) -> int:

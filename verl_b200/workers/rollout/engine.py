@@ -302,6 +302,8 @@ class InferenceEngine:
                 h = layer.mlp(x)
                 if record:
                     routed.append(layer.mlp.last_topk)
+            if visual is not None and len(visual) > 2 and visual[2] is not None and li < len(visual[2]):
+                h = h.index_add(0, visual[0], visual[2][li].to(h.dtype))       # deep-stack vision features join the stream (h + res)
         self._last_routed = torch.stack(routed, 1).to(torch.int16) if record else None      # [T, layers, topk]
         return ops.add_rmsnorm(h, res, m.norm, c.rms_norm_eps)[0]
 
@@ -463,13 +465,15 @@ class InferenceEngine:
             if g is not None and len(g):
                 pix.append(torch.as_tensor(mm["pixel_values"]))
                 grids.append(torch.as_tensor(g).reshape(-1, 3))
-        rope = mrope_tables(torch.cat(pos3, 1).to(self.device), c.head_dim, c.rope_theta, v.mrope_section)
+        rope = mrope_tables(torch.cat(pos3, 1).to(self.device), c.head_dim, c.rope_theta, v.mrope_section, getattr(v, "mrope_interleaved", False))
         visual = None
         if pix:
             rows = self.visual(torch.cat(pix, 0).to(self.device), torch.cat(grids, 0))
             idx = ((tokens == v.image_token_id) | (tokens == v.video_token_id)).nonzero(as_tuple=True)[0]
             assert idx.numel() == rows.shape[0], f"{idx.numel()} image placeholder tokens but {rows.shape[0]} merged patch embeddings"
-            visual = (idx, rows)
+            # Qwen3-VL: the tower also leaves one feature set per deep-stack block, added to the stream after the first decoder layers
+            deep = list(self.visual.last_deepstack) if getattr(v, "variant", "") == "qwen3_vl" else None
+            visual = (idx, rows, deep)
         return rope, visual
 
     def _start_sequences(self, reqs_slots: list, logits: torch.Tensor, sp: SamplingParams):
