@@ -6,8 +6,10 @@
 //   O^T[d, q]  = sum_kv V[kv, d] P[q, kv]   tcgen05.mma M = 128 head dims (V consumed MN-major), N = 16
 // Every thread owns one KV row (softmax numerators) resp. one head-dim row (output) and touches 16 values per tile;
 // row max / sum over the KV axis are warp-shuffle + shared-memory reductions. K/V tiles (128 rows) are fetched by TMA
-// straight from the paged cache via the block table; the kernel is small enough (75 KB shared memory, 32 TMEM columns)
-// for three CTAs per SM, which is what overlaps loads with the serial MMA -> softmax -> MMA chain of each tile. Optional split-KV writes partials merged by
+// straight from the paged cache via the block table; the kernel is small enough (75 KB shared memory, 64 TMEM columns)
+// for three CTAs per SM, which is what overlaps loads with the MMA -> softmax -> MMA chain of each tile. The score
+// accumulator is double-buffered in TMEM: QK^T of tile j+1 is issued right behind the PV product of tile j, so it runs while
+// the threads fold tile j's output and its result is ready when the next iteration asks for it. Optional split-KV writes partials merged by
 // attn_merge_kernel (same layout as the generic paged path).
 #include "common.cuh"
 #include "tma_host.h"
@@ -72,14 +74,14 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_fence_init();
   }
   if (warp == 0) {
-    tmem_alloc<32>(tmem_slot);
+    tmem_alloc<64>(tmem_slot);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tm_S = tmem_base, tm_O = tmem_base + 16;
+  const uint32_t tm_S0 = tmem_base, tm_O = tmem_base + 32;       // scores of even tiles at +0, of odd tiles at +16
   const uint32_t lane_off = uint32_t(warp * 32) << 16;
 
   // which = 0: K rows of tile j into sK, which = 1: V rows into sV (thread 0)
@@ -116,26 +118,32 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   bool ok = true;
   if (n_tiles > 0) ok = mbar_wait(q_bar, 0, abort_flag, p.err_word, VB_ERR_WAIT_MISC);
 
+  // QK^T of tile j into score buffer j & 1 (thread 0; waits for the tile's K rows itself)
+  auto issue_qk = [&](int j) -> bool {
+    if (!mbar_wait(k_bar, j & 1, abort_flag, p.err_word, VB_ERR_WAIT_FULL)) return false;
+    tc_fence_after();
+    const uint32_t ka = smem_u32(sKV), qa = smem_u32(sQ);
+    const uint32_t tm_S = tm_S0 + (j & 1) * 16;
+#pragma unroll
+    for (int k = 0; k < DD / 16; ++k) {
+      umma_f16(tm_S, make_sdesc_sw128(ka + (k >> 2) * D_HALF + (k & 3) * 32, 16, 1024),
+               make_sdesc_sw128(qa + (k >> 2) * (DQ * 128) + (k & 3) * 32, 16, 1024), idesc_s, k != 0);
+    }
+    umma_commit(s_bar);
+    return true;
+  };
+  if (ok && n_tiles > 0 && tid == 0) {
+    if (!issue_qk(0)) *abort_flag = 1;
+  }
+
   for (int j = 0; j < n_tiles && ok; ++j) {
     const uint32_t it_ph = j & 1;
-    if (!mbar_wait(k_bar, it_ph, abort_flag, p.err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
-    uint8_t* sK = sKV;
-    uint8_t* sV = sK + D_TILE;
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t ka = smem_u32(sK), qa = smem_u32(sQ);
-#pragma unroll
-      for (int k = 0; k < DD / 16; ++k) {
-        umma_f16(tm_S, make_sdesc_sw128(ka + (k >> 2) * D_HALF + (k & 3) * 32, 16, 1024),
-                 make_sdesc_sw128(qa + (k >> 2) * (DQ * 128) + (k & 3) * 32, 16, 1024), idesc_s, k != 0);
-      }
-      umma_commit(s_bar);
-    }
+    uint8_t* sV = sKV + D_TILE;
     if (!mbar_wait(s_bar, it_ph, abort_flag, p.err_word, VB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
     tc_fence_after();
     if (tid == 0 && j + 1 < n_tiles) load_half(j + 1, 0);        // the K buffer is free once QK^T has completed
     uint32_t sv[DQ];
-    tmem_ld_32x32b_x16(tm_S + lane_off, sv);
+    tmem_ld_32x32b_x16(tm_S0 + it_ph * 16 + lane_off, sv);
     tmem_ld_wait();
     const bool valid = (tile0 + j) * DT + tid < kv_len;
     float s[DQ];
@@ -188,6 +196,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                  make_sdesc_sw128(pa + (k >> 2) * (DQ * 128) + (k & 3) * 32, 16, 1024), idesc_o, k != 0);
       }
       umma_commit(o_bar);
+      // the next tile's scores: its K rows were requested when this tile's QK^T had completed, and the other score buffer was
+      // last read by the softmax of tile j-1
+      if (j + 1 < n_tiles && !issue_qk(j + 1)) *abort_flag = 1;
     }
 #pragma unroll
     for (int q = 0; q < DQ; ++q) l_run[q] = l_run[q] * alpha[q] + red[q] + red[DQ + q] + red[2 * DQ + q] + red[3 * DQ + q];
@@ -228,7 +239,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       while (globaltimer_ns() - t0 < 2000000ull) { __nanosleep(1000); }
     }
     tc_fence_after();
-    tmem_dealloc<32>(tmem_base);
+    tmem_dealloc<64>(tmem_base);
   }
 }
 
