@@ -31,6 +31,7 @@ class ModelConfig:
     tie_word_embeddings: bool = False
     attention_bias: bool = True          # qwen2: bias on q/k/v projections
     qk_norm: bool = False                # qwen3: RMSNorm on q and k heads
+    mlp_act: str = "swiglu"              # "swiglu": gated SiLU MLP (gate/up fused); "xielu": up -> xIELU (learned per layer) -> down (Apertus)
     initializer_range: float = 0.02
     # mixture of experts (qwen3_moe)
     num_experts: int = 0
@@ -117,7 +118,8 @@ class ModelConfig:
             max_position_embeddings=d.get("max_position_embeddings", 32768),
             tie_word_embeddings=d.get("tie_word_embeddings", False),
             attention_bias=d.get("attention_bias", mt == "qwen2"),
-            qk_norm=mt in ("qwen3", "qwen3_moe"),
+            qk_norm=mt in ("qwen3", "qwen3_moe", "apertus"),
+            mlp_act="xielu" if mt == "apertus" else "swiglu",
             initializer_range=d.get("initializer_range", 0.02),
             num_experts=d.get("num_experts", d.get("num_local_experts", 0)) if "moe" in mt or "mixtral" in mt else 0,
             num_experts_per_tok=d.get("num_experts_per_tok", 0),
@@ -150,7 +152,7 @@ class ModelConfig:
             num_attention_heads=self.num_attention_heads, num_key_value_heads=self.num_key_value_heads,
             head_dim=self.head_dim, rms_norm_eps=self.rms_norm_eps, rope_theta=self.rope_theta,
             max_position_embeddings=self.max_position_embeddings, tie_word_embeddings=self.tie_word_embeddings,
-            attention_bias=self.attention_bias, initializer_range=self.initializer_range, hidden_act="silu",
+            attention_bias=self.attention_bias, initializer_range=self.initializer_range, hidden_act="xielu" if self.mlp_act == "xielu" else "silu",
             pad_token_id=self.pad_token_id, eos_token_id=self.eos_token_id, bos_token_id=self.bos_token_id,
             torch_dtype=self.torch_dtype,
         )

@@ -58,6 +58,8 @@ def tp_rule(name: str, cfg: ModelConfig):
         return 1, [cfg.q_size]
     if leaf == "gate_up_proj":
         return 0, [cfg.intermediate_size, cfg.intermediate_size]
+    if leaf == "up_proj":
+        return 0, [cfg.intermediate_size]
     if leaf == "down_proj":
         return 1, [cfg.intermediate_size]
     if leaf == "experts_gate_up":

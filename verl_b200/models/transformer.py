@@ -129,7 +129,14 @@ class MLP(nn.Module):
     def __init__(self, cfg: ModelConfig, dtype, device):
         super().__init__()
         kw = dict(dtype=dtype, device=device)
-        self.gate_up_proj = nn.Parameter(torch.empty(2 * cfg.intermediate_size, cfg.hidden_size, **kw))
+        self.xielu = getattr(cfg, "mlp_act", "swiglu") == "xielu"
+        if self.xielu:
+            # Apertus: no gate; the activation's two curvature parameters are learned per layer (stored before their softplus)
+            self.up_proj = nn.Parameter(torch.empty(cfg.intermediate_size, cfg.hidden_size, **kw))
+            self.act_alpha_p = nn.Parameter(torch.empty(1, **kw))
+            self.act_alpha_n = nn.Parameter(torch.empty(1, **kw))
+        else:
+            self.gate_up_proj = nn.Parameter(torch.empty(2 * cfg.intermediate_size, cfg.hidden_size, **kw))
         self.down_proj = nn.Parameter(torch.empty(cfg.hidden_size, cfg.intermediate_size, **kw))
         self.tp_group = None
 
@@ -140,7 +147,23 @@ class MLP(nn.Module):
             return _TiledMLP.apply(x, self, self.tiled_shards, *[p for p in self.parameters() if p.requires_grad])
         return self._dense(x)
 
+    XIELU_BETA, XIELU_EPS = 0.5, -1e-6
+
+    def _xielu(self, u):
+        """xIELU (arXiv 2411.13010): alpha_p x^2 + beta x for x > 0, alpha_n (expm1(min(x, eps)) - x) + beta x otherwise."""
+        ap = F.softplus(self.act_alpha_p.float())
+        an = self.XIELU_BETA + F.softplus(self.act_alpha_n.float())
+        x = u.float()
+        y = torch.where(x > 0, ap * x * x + self.XIELU_BETA * x, (torch.expm1(torch.clamp(x, max=self.XIELU_EPS)) - x) * an + self.XIELU_BETA * x)
+        return y.to(u.dtype)
+
     def _dense(self, x):
+        if self.xielu:
+            if getattr(self, "tp_sp", False):
+                tpctx = getattr(self, "tp_ctx", None)
+                return linear_reduce_scatter(self._xielu(allgather_linear(x, self.up_proj, None, self.tp_group, tpctx)), self.down_proj, self.tp_group, tpctx)
+            y = _proj(self, "down_proj", self._xielu(_proj(self, "up_proj", copy_to_tp(x, self.tp_group))))
+            return reduce_from_tp(y, self.tp_group)
         if getattr(self, "tp_sp", False):
             tpctx = getattr(self, "tp_ctx", None)
             h = ops.swiglu(allgather_linear(x, self.gate_up_proj, None, self.tp_group, tpctx))
@@ -297,6 +320,10 @@ class DecoderLM(nn.Module):
                 p.fill_(1.0)
             elif name.endswith("bias"):
                 p.zero_()
+            elif name.endswith("act_alpha_p"):
+                p.fill_(math.log(math.expm1(0.8)))              # softplus^-1 of the published start values (0.8, and 0.8 - beta)
+            elif name.endswith("act_alpha_n"):
+                p.fill_(math.log(math.expm1(0.8 - MLP.XIELU_BETA)))
             else:
                 p.normal_(0.0, std, generator=gen)
 
@@ -459,8 +486,9 @@ def native_to_hf_tensors(cfg: ModelConfig, params: dict) -> Iterator[tuple[str, 
         hp = f"model.layers.{i}."
         if p + "input_layernorm" not in params:
             continue  # pipeline stage that does not own this layer
-        yield hp + "input_layernorm.weight", params[p + "input_layernorm"]
-        yield hp + "post_attention_layernorm.weight", params[p + "post_attention_layernorm"]
+        apertus = getattr(cfg, "mlp_act", "swiglu") == "xielu"
+        yield hp + ("attention_layernorm.weight" if apertus else "input_layernorm.weight"), params[p + "input_layernorm"]
+        yield hp + ("feedforward_layernorm.weight" if apertus else "post_attention_layernorm.weight"), params[p + "post_attention_layernorm"]
         qkv = params[p + "self_attn.qkv_proj"]
         q, k, v = qkv.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=0)
         yield hp + "self_attn.q_proj.weight", q
@@ -483,6 +511,11 @@ def native_to_hf_tensors(cfg: ModelConfig, params: dict) -> Iterator[tuple[str, 
                 yield hp + f"mlp.experts.{e}.gate_proj.weight", gu[e, :I]
                 yield hp + f"mlp.experts.{e}.up_proj.weight", gu[e, I:]
                 yield hp + f"mlp.experts.{e}.down_proj.weight", dn[e]
+        elif apertus:
+            yield hp + "mlp.up_proj.weight", params[p + "mlp.up_proj"]
+            yield hp + "mlp.down_proj.weight", params[p + "mlp.down_proj"]
+            yield hp + "mlp.act_fn.alpha_p", params[p + "mlp.act_alpha_p"]
+            yield hp + "mlp.act_fn.alpha_n", params[p + "mlp.act_alpha_n"]
         else:
             gu = params[p + "mlp.gate_up_proj"]
             I = cfg.intermediate_size
@@ -505,10 +538,12 @@ def hf_to_native_state_dict(cfg: ModelConfig, sd: dict) -> dict:
         out["embed_tokens"] = sd["model.embed_tokens.weight"]
     for i in range(cfg.num_hidden_layers):
         hp, p = f"model.layers.{i}.", f"layers.{i}."
-        if hp + "input_layernorm.weight" not in sd:
+        apertus = getattr(cfg, "mlp_act", "swiglu") == "xielu"
+        n1, n2 = ("attention_layernorm.weight", "feedforward_layernorm.weight") if apertus else ("input_layernorm.weight", "post_attention_layernorm.weight")
+        if hp + n1 not in sd:
             continue
-        out[p + "input_layernorm"] = sd[hp + "input_layernorm.weight"]
-        out[p + "post_attention_layernorm"] = sd[hp + "post_attention_layernorm.weight"]
+        out[p + "input_layernorm"] = sd[hp + n1]
+        out[p + "post_attention_layernorm"] = sd[hp + n2]
         out[p + "self_attn.qkv_proj"] = torch.cat([sd[hp + f"self_attn.{n}_proj.weight"] for n in "qkv"], 0)
         if cfg.attention_bias and hp + "self_attn.q_proj.bias" in sd:
             out[p + "self_attn.qkv_bias"] = torch.cat([sd[hp + f"self_attn.{n}_proj.bias"] for n in "qkv"], 0)
@@ -522,6 +557,11 @@ def hf_to_native_state_dict(cfg: ModelConfig, sd: dict) -> dict:
                 [torch.cat([sd[hp + f"mlp.experts.{e}.gate_proj.weight"], sd[hp + f"mlp.experts.{e}.up_proj.weight"]], 0)
                  for e in range(cfg.num_experts)], 0)
             out[p + "mlp.experts_down"] = torch.stack([sd[hp + f"mlp.experts.{e}.down_proj.weight"] for e in range(cfg.num_experts)], 0)
+        elif apertus:
+            out[p + "mlp.up_proj"] = sd[hp + "mlp.up_proj.weight"]
+            out[p + "mlp.down_proj"] = sd[hp + "mlp.down_proj.weight"]
+            out[p + "mlp.act_alpha_p"] = sd[hp + "mlp.act_fn.alpha_p"].reshape(1)
+            out[p + "mlp.act_alpha_n"] = sd[hp + "mlp.act_fn.alpha_n"].reshape(1)
         else:
             out[p + "mlp.gate_up_proj"] = torch.cat([sd[hp + "mlp.gate_proj.weight"], sd[hp + "mlp.up_proj.weight"]], 0)
             out[p + "mlp.down_proj"] = sd[hp + "mlp.down_proj.weight"]

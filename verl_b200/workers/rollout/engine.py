@@ -107,6 +107,8 @@ class InferenceEngine:
         if hasattr(model, "visual") and hasattr(model, "language_model"):
             self.visual, self.vision_config, model = model.visual, model.vcfg, model.language_model
         self.model = model
+        if getattr(getattr(model, "cfg", None), "mlp_act", "swiglu") != "swiglu" and (quantization or tp_group is not None):
+            raise NotImplementedError("models with an un-gated MLP (Apertus) run in the rollout engine without tensor parallelism or fp8 weights")
         self.tp_group, self.tp = tp_group, tp_ctx
         # "fp8": W8A8 projections (per-output-channel e4m3 weights re-quantised from the live bf16 weights at every wake_up,
         # per-token e4m3 activations, tcgen05 f8f6f4 GEMM); embeddings, norms, lm_head and the KV cache stay bf16.
