@@ -127,8 +127,18 @@ from tests.test_zero3_on_cpu import moe_config
 from verl_b200.workers.engine.base import EngineRegistry
 dist.init_process_group("gloo")
 rank, world = dist.get_rank(), dist.get_world_size()
-eng = EngineRegistry.new("language_model", "fsdp", model_config=moe_config(), engine_config={"seed": 1, "expert_parallel_size": world,
-                         "zero3": os.environ["DENSE"] == "1"}, optimizer_config={"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, checkpoint_config={})
+if os.environ["DENSE"] == "2":      # the Megatron-style names of the same layout: strategy megatron, expert_model_parallel_size = world
+    eng = EngineRegistry.new("language_model", "megatron", model_config=moe_config(), engine_config={"seed": 1, "expert_model_parallel_size": world,
+                             "tensor_model_parallel_size": 1, "pipeline_model_parallel_size": 1}, optimizer_config={"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0},
+                             checkpoint_config={})
+    try:
+        EngineRegistry.new("language_model", "megatron", model_config=moe_config(), engine_config={"expert_model_parallel_size": world, "tensor_model_parallel_size": 2})
+        raise SystemExit("expert parallelism combined with tensor parallelism must be refused")
+    except NotImplementedError:
+        pass
+else:
+    eng = EngineRegistry.new("language_model", "fsdp", model_config=moe_config(), engine_config={"seed": 1, "expert_parallel_size": world,
+                             "zero3": os.environ["DENSE"] == "1"}, optimizer_config={"lr": 1e-3, "weight_decay": 0.01, "clip_grad": 1.0}, checkpoint_config={})
 eng.initialize()
 assert type(eng).__name__ == "Zero3Engine"
 gu = dict(eng.model.named_parameters())["layers.0.mlp.experts_gate_up"]
@@ -155,7 +165,7 @@ def moe_config():
                        moe_intermediate_size=32, rope_theta=1e4, max_position_embeddings=512, torch_dtype="float32")
 
 
-@pytest.mark.parametrize("dense", [0, 1])
+@pytest.mark.parametrize("dense", [0, 1, 2])
 def test_expert_parallel_ranks_match_single_rank(tmp_path, dense):
     """Experts spread over two ranks (tokens reach them by all-to-all), alone and together with row-sharded projections:
     log-probs, gradient norms and exported weights equal a single rank holding every expert."""

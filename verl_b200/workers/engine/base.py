@@ -189,6 +189,33 @@ class EngineRegistry:
             import verl_b200.workers.engine.aliases  # noqa: F401 - third-party backend names of the reference
 
         engine_config = kwargs.get("engine_config", args[1] if len(args) > 1 else None)
+        if backend == "megatron" and model_type == "language_model" and engine_config is not None:
+            def mopt(key, default=1):
+                v = engine_config.get(key, default) if hasattr(engine_config, "get") else getattr(engine_config, key, default)
+                return int(v or default)
+
+            ep = mopt("expert_model_parallel_size")
+            if ep > 1:
+                # expert parallelism over the data-parallel ranks with no tensor / pipeline / context split is exactly the layout of
+                # the expert-parallel sharded engine (experts E/W per rank, dispatch + combine inside the grouped GEMMs): the
+                # Megatron-style strategy names resolve to it. Expert parallelism inside a sub-group of the data-parallel ranks,
+                # or combined with TP / PP / CP, is not built.
+                import torch.distributed as dist
+
+                world = dist.get_world_size() if dist.is_initialized() else int(os.environ.get("WORLD_SIZE", "1"))
+                other = mopt("tensor_model_parallel_size") * mopt("pipeline_model_parallel_size") * mopt("context_parallel_size")
+                if other != 1 or ep != world:
+                    raise NotImplementedError(f"expert_model_parallel_size={ep} needs tensor = pipeline = context parallel size 1 and "
+                                              f"expert_model_parallel_size == world size ({world}) in this build")
+                import verl_b200.workers.engine.fsdp.zero3  # noqa: F401
+
+                ec = dict(engine_config) if hasattr(engine_config, "keys") else {k: getattr(engine_config, k) for k in vars(engine_config)}
+                ec["expert_parallel_size"] = ep
+                if "engine_config" in kwargs:
+                    kwargs["engine_config"] = ec
+                else:
+                    args = (args[0], ec) + tuple(args[2:])
+                return cls.get_engine_cls(model_type, "fsdp_zero3")(*args, **kwargs)
         if backend in ("fsdp", "fsdp2") and model_type == "language_model" and engine_config is not None:
             def opt(key):
                 return engine_config.get(key, False) if hasattr(engine_config, "get") else getattr(engine_config, key, False)
