@@ -133,3 +133,56 @@ def test_union_tensor_dict_mismatch_batch():
 
     with pytest.raises(AssertionError):
         union_tensor_dict(TensorBatch({"a": torch.zeros(2)}), TensorBatch({"b": torch.zeros(3)}))
+
+
+def test_tensordict_helper_surface():
+    """The helper functions the engine path uses on batches: shared vs per-sample non-tensor data, ragged rows, key access across
+    the three places a value can live, concatenation, union, equality and the row-dict constructor."""
+    import numpy as np
+    import pytest
+    import torch
+
+    from verl_b200.protocol import Jagged
+    from verl_b200.utils import tensordict_utils as tu
+
+    rows = [{"ids": torch.arange(3), "score": torch.tensor(0.5), "uid": "a", "tools": [1, 2]},
+            {"ids": torch.arange(5), "score": torch.tensor(1.5), "uid": "b", "tools": []}]
+    d = tu.list_of_dict_to_tensordict(rows)
+    assert isinstance(d.batch["ids"], Jagged) and d.batch["score"].tolist() == [0.5, 1.5] and tu.get(d, "uid") == ["a", "b"]
+    tu.assign_non_tensor_data(d, "temperature", 0.7)
+    tu.assign_non_tensor_stack(d, "extra", [{"k": 1}, {"k": 2}])
+    with pytest.raises(ValueError):
+        tu.assign_non_tensor_stack(d, "bad", [1])
+    assert tu.get(d, "temperature") == 0.7 and tu.get(d, "extra")[1] == {"k": 2} and tu.get(d, "missing", 3) == 3
+    assert tu.unwrap_non_tensor_data(np.array(4)) == 4 and tu.unwrap_non_tensor_data(d.non_tensor_batch["tools"]) == [[1, 2], []]
+    sub = tu.get_keys(d, ["score", "uid", "temperature"])
+    assert set(sub.batch.keys()) == {"score"} and set(sub.non_tensor_batch) == {"uid"} and sub.meta_info == {"temperature": 0.7}
+    with pytest.raises(KeyError):
+        tu.get_keys(d, ["nope"])
+    both = tu.concat_tensordict([d, d])
+    assert len(both) == 4 and [len(r) for r in both.batch["ids"].unbind()] == [3, 5, 3, 5] and tu.get(both, "uid") == ["a", "b", "a", "b"]
+    tu.assert_tensordict_eq(both[:2], d)
+    with pytest.raises(AssertionError, match="differs"):
+        other = tu.list_of_dict_to_tensordict(rows)
+        other.batch["score"] = torch.tensor([0.5, 9.0])
+        tu.assign_non_tensor_data(other, "temperature", 0.7)
+        tu.assign_non_tensor_stack(other, "extra", [{"k": 1}, {"k": 2}])
+        tu.assert_tensordict_eq(other, d)
+    u = tu.union_tensor_dict(tu.get_keys(d, ["score"]), tu.get_tensordict({"adv": torch.ones(2, 4)}))
+    assert set(u.batch.keys()) == {"score", "adv"}
+    popped = tu.pop_keys(d, ["score", "temperature"])
+    assert "score" not in d.batch.keys() and "temperature" not in d.meta_info and popped.batch["score"].shape == (2,)
+    assert tu.pop(d, "uid") == ["a", "b"] and tu.pop(d, "uid", None) is None
+    j = tu.concat_nested_tensors([tu.nested_tensor_from_tensor_list([torch.ones(2), torch.ones(1)]), tu.nested_tensor_from_tensor_list([torch.ones(4)])])
+    assert j.offsets.tolist() == [0, 2, 3, 7]
+    shared = tu.concat_tensordict_with_none_bsz([tu.get_tensordict({}, {"a": 1}), tu.get_tensordict({}, {"a": 1, "b": 2})])
+    assert shared.meta_info == {"a": 1, "b": 2}
+    with pytest.raises(ValueError, match="differs"):
+        tu.concat_tensordict_with_none_bsz([tu.get_tensordict({}, {"a": 1}), tu.get_tensordict({}, {"a": 2})])
+    import pickle
+
+    p = tu.get_tensordict({"position_ids": [torch.zeros(4, 3), torch.zeros(6, 3)]})          # ragged multimodal positions, one [L_i, 3] per sample
+    back = tu.maybe_fix_3d_position_ids(pickle.loads(pickle.dumps(p)))
+    assert [tuple(r.shape) for r in back.batch["position_ids"].unbind()] == [(4, 3), (6, 3)]
+    t = tu.get_tensordict({"x": torch.arange(12).reshape(2, 6).t()[:, :2].t()})
+    assert tu.contiguous(t).batch["x"].is_contiguous()
