@@ -210,3 +210,26 @@ def test_router_replay_end_to_end(tmp_path, mode):
     assert abs(m["actor/ppo_kl"]) < 1e-4
     if mode == "R3":
         assert m["training/rollout_probs_diff_max"] < 1e-4
+
+
+def test_fit_brackets_the_listed_steps_with_the_worker_profilers(tmp_path):
+    """``global_profiler.steps`` + a role's ``profiler.enable``: the trainer starts the workers' profilers before a listed step and
+    stops them after it (one capture for consecutive steps with ``profile_continuous_steps``); the torch tool writes a trace per
+    capture, and the worker entry points run inside named ranges."""
+    prof_dir = tmp_path / "prof"
+    tr = build(tmp_path, ["trainer.total_training_steps=4", "global_profiler.tool=torch", "global_profiler.steps=[2,3]",
+                          "global_profiler.profile_continuous_steps=true", f"global_profiler.save_path={prof_dir}",
+                          "actor_rollout_ref.actor.profiler.enable=true", "actor_rollout_ref.actor.profiler.all_ranks=true"])
+    w = tr.actor_rollout_wg.worker
+    assert w.profiler.enabled and w.profiler.config.tool == "torch" and w.profiler.config.save_path == str(prof_dir)
+    calls = []
+    start, stop = w.profiler.start, w.profiler.stop
+    w.profiler.start = lambda **kw: (calls.append(("start", tr.global_steps, kw.get("profile_step"))), start(**kw))[1]
+    w.profiler.stop = lambda: (calls.append(("stop", tr.global_steps)), stop())[1]
+    tr.fit()
+    assert calls == [("start", 2, 2), ("stop", 3)]                     # steps 2 and 3 share one capture
+    assert any(f.endswith(".json") or f.endswith(".json.gz") for _, _, fs in os.walk(prof_dir) for f in fs), list(os.walk(prof_dir))
+    # a role without profiler.enable stays off, and the facade is a no-op for it
+    tr2 = build(tmp_path, ["trainer.total_training_steps=1", "global_profiler.tool=torch", "global_profiler.steps=[1]"])
+    assert not tr2.actor_rollout_wg.worker.profiler.enabled
+    tr2.fit()

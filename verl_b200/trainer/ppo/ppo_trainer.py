@@ -600,6 +600,22 @@ class PPOTrainer:
         self._last_batch = batch
         return metrics
 
+    def _profiled_groups(self) -> list:
+        groups = [getattr(self, n, None) for n in ("actor_rollout_wg", "ref_policy_wg", "critic_wg", "rm_wg")]
+        out = []
+        for g in groups:
+            if g is not None and hasattr(g, "start_profile") and all(g is not o for o in out):
+                out.append(g)
+        return out
+
+    def _start_profiling(self) -> None:
+        for g in self._profiled_groups():
+            g.start_profile(role="e2e", profile_step=self.global_steps)
+
+    def _stop_profiling(self) -> None:
+        for g in self._profiled_groups():
+            g.stop_profile()
+
     def fit(self):
         cfg = self.config
         is_main = int(os.environ.get("RANK", "0")) == 0 or _g(cfg, "trainer.worker_backend", "spmd") != "spmd"
@@ -620,11 +636,22 @@ class PPOTrainer:
         self.global_steps += 1
         last_val = None
         max_step_time = 0.0
+        prof_steps = {int(x) for x in (_g(cfg, "global_profiler.steps", None) or [])}
+        prof_continuous = bool(_g(cfg, "global_profiler.profile_continuous_steps", False))
+        profiling = False
         for epoch in range(int(cfg.trainer.total_epochs)):
             for batch_dict in self.train_dataloader:
                 t0 = time.perf_counter()
                 is_last = self.global_steps >= self.total_training_steps
+                # the steps listed in global_profiler.steps are bracketed by start/stop on every worker group; consecutive listed
+                # steps share one capture when profile_continuous_steps is set (reference: verl/trainer/ppo/ray_trainer.py:1119-1152)
+                if self.global_steps in prof_steps and not profiling:
+                    self._start_profiling()
+                    profiling = True
                 metrics = self.step(batch_dict)
+                if profiling and (is_last or not (prof_continuous and (self.global_steps + 1) in prof_steps)):
+                    self._stop_profiling()
+                    profiling = False
                 max_step_time = max(max_step_time, time.perf_counter() - t0)
                 test_freq = int(_g(cfg, "trainer.test_freq", -1))
                 if self.val_reward_fn is not None and test_freq > 0 and (is_last or self.global_steps % test_freq == 0):

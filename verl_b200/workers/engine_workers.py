@@ -235,7 +235,51 @@ def _role_cfg(full, role: str, model_type: str):
     return out
 
 
-class ActorRolloutRefWorker(Worker):
+def _annotate(message: str, role: str):
+    from verl_b200.utils.profiler import DistProfiler
+
+    return DistProfiler.annotate(message=message, role=role)
+
+
+def _role_profiler(config, *roles):
+    """``DistProfiler`` of a role worker: the union of the ``profiler`` sections of the roles this process plays (reference:
+    ``verl/workers/engine_workers.py:262-290`` merges actor / rollout / ref profiler configs the same way)."""
+    from verl_b200.utils.profiler import DistProfiler, ProfilerConfig
+
+    known = set(ProfilerConfig.__dataclass_fields__)
+    merged = None
+    for r in roles:
+        sec = cfg_get(config, f"{r}.profiler", None) if r else cfg_get(config, "profiler", None)
+        if sec is None:
+            continue
+        d = {k: (sec.get(k) if hasattr(sec, "get") else getattr(sec, k, None)) for k in known}
+        d = {k: v for k, v in d.items() if v is not None}
+        tool = d.get("tool")
+        tc = d.get("tool_config")
+        if tool and tc is not None and hasattr(tc, "get") and tc.get(tool) is not None:
+            d["tool_config"] = dict(tc.get(tool))         # the per-tool subsection of the role's tool_config
+        elif tc is not None and hasattr(tc, "keys"):
+            d["tool_config"] = dict(tc)
+        d["ranks"] = list(d.get("ranks") or [])
+        pc = ProfilerConfig(**d)
+        merged = pc if merged is None else merged.union(pc)
+    return DistProfiler(int(os.environ.get("RANK", "0")), merged)
+
+
+class _ProfiledWorker:
+    """``start_profile`` / ``stop_profile`` group calls of a role worker (the trainer brackets the steps listed in
+    ``global_profiler.steps`` with them)."""
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def start_profile(self, **kwargs) -> None:
+        self.profiler.start(**kwargs)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def stop_profile(self) -> None:
+        self.profiler.stop()
+
+
+class ActorRolloutRefWorker(Worker, _ProfiledWorker):
     """Colocated actor / reference / rollout roles of one GPU. ``role`` ∈ {actor, ref, rollout, actor_rollout,
     actor_rollout_ref}; ``config`` is the ``actor_rollout_ref`` subtree."""
 
@@ -253,6 +297,7 @@ class ActorRolloutRefWorker(Worker):
         self.ref: Optional[TrainingWorker] = None
         self.rollout = None
         self.device = torch.device(get_device_name())
+        self.profiler = _role_profiler(config, *[r for r, on in (("actor", self._is_actor), ("rollout", self._is_rollout), ("ref", self._is_ref)) if on])
 
     # ------------------------------------------------------------------ build
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
@@ -371,6 +416,7 @@ class ActorRolloutRefWorker(Worker):
         return self._agent_mgr
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("rollout"))
+    @_annotate("generate_sequences", "rollout")
     def generate_sequences(self, prompts: DataProto) -> DataProto:
         """Left-padded prompts in → prompts + right-padded responses out (with rollout log-probs)."""
         from verl_b200.workers.rollout.engine import SamplingParams
@@ -472,6 +518,7 @@ class ActorRolloutRefWorker(Worker):
         return worker.infer_batch(d)["model_output"]
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
+    @_annotate("compute_log_prob", "actor")
     def compute_log_prob(self, data: DataProto) -> DataProto:
         mode = self._router_replay_mode()
         if self.ref is not None and hasattr(self.ref.engine, "prefetch_params") and self.ref.engine.is_param_offload_enabled:
@@ -485,6 +532,7 @@ class ActorRolloutRefWorker(Worker):
         return DataProto.from_dict(tensors=tensors, meta_info={"temperature": data.meta_info.get("temperature", 1.0)})
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
+    @_annotate("compute_ref_log_prob", "ref")
     def compute_ref_log_prob(self, data: DataProto) -> DataProto:
         worker = self.ref if self.ref is not None else self.actor
         mo = self._logprob_pass(worker, data, calculate_entropy=False)      # the frozen policy routes by itself
@@ -505,6 +553,7 @@ class ActorRolloutRefWorker(Worker):
 
     # ------------------------------------------------------------------ update
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
+    @_annotate("update_actor", "actor")
     def update_actor(self, data: DataProto) -> DataProto:
         ac = cfg_get(self.config, "actor")
         meta = dict(data.meta_info)
@@ -540,7 +589,7 @@ class ActorRolloutRefWorker(Worker):
         _wait_checkpoint(self.actor.engine)
 
 
-class CriticWorker(Worker):
+class CriticWorker(Worker, _ProfiledWorker):
     """Value model: ``compute_values`` (forward) and ``update_critic`` (clipped value loss)."""
 
     def __init__(self, config):
@@ -548,6 +597,7 @@ class CriticWorker(Worker):
         ensure_process_group(int(cfg_get(config, "nccl_timeout", 600)))
         self.config = config
         self.critic: Optional[TrainingWorker] = None
+        self.profiler = _role_profiler(config, "")
 
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def init_model(self):
@@ -558,6 +608,7 @@ class CriticWorker(Worker):
         self._register_dispatch_collect_info("critic", dp_rank=eng.get_data_parallel_rank(), is_collect=eng.is_mp_src_rank_with_outputs())
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("critic"))
+    @_annotate("compute_values", "critic")
     def compute_values(self, data: DataProto) -> DataProto:
         d = DataProto(batch=data.batch, non_tensor_batch=_model_inputs(data), meta_info=dict(data.meta_info))
         mo = self.critic.infer_batch(d)["model_output"]
@@ -565,6 +616,7 @@ class CriticWorker(Worker):
         return DataProto.from_dict(tensors={"values": vals})
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("critic"))
+    @_annotate("update_critic", "critic")
     def update_critic(self, data: DataProto) -> DataProto:
         d = DataProto(batch=data.batch, non_tensor_batch=_model_inputs(data), meta_info=dict(data.meta_info))
         metrics = self.critic.train_mini_batch(d)
