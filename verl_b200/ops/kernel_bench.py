@@ -487,9 +487,77 @@ def bench_fused_emulated(a):
     _ext.check_status("fused_emulated")
 
 
+def bench_fused_routed(a):
+    """The routed variants of the fused GEMMs on ONE GPU, every "peer" being a buffer of this GPU: QKV projection with the
+    sequence -> head routing in its epilogue, output projection reading its K-segmented operand from the head owners, and the two
+    grouped GEMMs of an expert-parallel MoE layer (row gather from the token owners into the gate/up GEMM, weighted row scatter
+    from the down projection). Qwen2.5-7B attention shapes / Qwen3-30B-A3B expert shapes; NVLink transport is measured by
+    ``verl_b200.parallel.comm_bench``."""
+    from verl_b200.ops import _ext
+    from verl_b200.ops.moe import ep_row_tables
+
+    o = _ext.ops()
+    W = a.world
+    tab = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64)      # noqa: E731
+    D, Hq, Hkv, H = 128, 28, 4, 3584
+    hq_l, hkv_l = Hq // W, Hkv // W
+    Cl, Kl = (hq_l + 2 * hkv_l) * D, hq_l * D
+    Tl = a.m // W
+    Tp = Tl * W
+    x = torch.randn(Tl, H, device="cuda").bfloat16()
+    w_qkv = (0.02 * torch.randn((Hq + 2 * Hkv) * D, H, device="cuda")).bfloat16()
+    rank_of = [h // hq_l for h in range(Hq)] + [j // hkv_l for _ in range(2) for j in range(Hkv)]
+    slot_of = [h % hq_l for h in range(Hq)] + [base + j % hkv_l for base in (hq_l, hq_l + hkv_l) for j in range(Hkv)]
+    hr, hs = torch.tensor(rank_of, dtype=torch.int32), torch.tensor(slot_of, dtype=torch.int32)
+    bufs = [torch.empty(Tp * Cl, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    ms = timeit(lambda: o.gemm_head_scatter(x, w_qkv, None, tab(bufs), Cl, 0, D, hr, hs), a.iters)
+    report(f"QKV projection with head-scatter epilogue M={Tl} N={(Hq + 2 * Hkv) * D} K={H}", ms, flops=2.0 * Tl * H * (Hq + 2 * Hkv) * D)
+    o_bufs = [torch.randn(Tp, Kl, device="cuda").bfloat16() for _ in range(W)]
+    w_o = (0.02 * torch.randn(H, Hq * D, device="cuda")).bfloat16()
+    Tl_pad = (Tl + 127) // 128 * 128
+    stage = torch.empty(Tl_pad * Hq * D, device="cuda", dtype=torch.bfloat16)
+    flags = torch.zeros((Tl_pad // 128) * W + 8, device="cuda", dtype=torch.int32)
+    out = torch.empty(Tl, H, device="cuda", dtype=torch.bfloat16)
+    ep = [0]
+
+    def kseg():
+        ep[0] += 1
+        o.gemm_kseg(tab(o_bufs), Kl, Tp, 0, w_o, out, None, 0, stage, flags, ep[0])
+
+    ms = timeit(kseg, a.iters)
+    report(f"output projection with K-segmented staged gather M={Tl} N={H} K={Hq * D}", ms, flops=2.0 * Tl * H * Hq * D)
+    del bufs, o_bufs, stage
+    # ---- expert-parallel MoE layer: 128 experts, top-8, hidden 2048, expert FFN 768
+    Hm, I, E, k = 2048, 768, 128, 8
+    e_local = E // W
+    T = a.m
+    xs = [torch.randn(T, Hm, device="cuda").bfloat16() for _ in range(W)]
+    gate_up = (0.02 * torch.randn(e_local, 2 * I, Hm, device="cuda")).bfloat16()
+    down = (0.02 * torch.randn(e_local, Hm, I, device="cuda")).bfloat16()
+    idx_all = torch.stack([torch.rand(T, E, device="cuda").topk(k, -1).indices for _ in range(W)]).to(torch.int32)
+    w_all = torch.rand(W, T, k, device="cuda") + 0.1
+    row_src, row_dst, row_w, blk, _ = ep_row_tables(idx_all, w_all, 0, e_local)
+    R = row_src.numel()
+    stg = torch.empty(R, Hm, device="cuda", dtype=torch.bfloat16)
+    fl = torch.empty(R // 128, device="cuda", dtype=torch.int32)
+    cbufs = [torch.empty(k * T * Hm, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    hbox = [None]
+
+    def dispatch():
+        hbox[0] = o.gemm_grouped_dispatch(tab(xs), Hm, row_src, gate_up, blk, stg, fl, False)
+
+    ms = timeit(dispatch, a.iters)
+    report(f"MoE gate/up grouped GEMM with fused token dispatch R={R} N={2 * I} K={Hm} ({e_local} local experts)", ms, flops=2.0 * R * 2 * I * Hm)
+    act = o.swiglu_fwd(hbox[0])
+    ms = timeit(lambda: o.gemm_grouped_combine(act, down, blk, row_dst, row_w, tab(cbufs), Hm, False), a.iters)
+    report(f"MoE down grouped GEMM with fused weighted combine R={R} N={Hm} K={I}", ms, flops=2.0 * R * Hm * I)
+    torch.cuda.synchronize()
+    _ext.check_status("fused_routed")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_layer", "layer_step", "gemm_fp8", "attn_fwd", "attn_bwd", "lmhead", "decode_attn", "elementwise", "fused_gather", "fused_emulated", "all"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_layer", "layer_step", "gemm_fp8", "attn_fwd", "attn_bwd", "lmhead", "decode_attn", "elementwise", "fused_gather", "fused_emulated", "fused_routed", "all"])
     ap.add_argument("--world", type=int, default=2)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -518,6 +586,9 @@ def main():
         bench_gemm(a)
     if a.kernel == "gemm_layer":
         bench_gemm_layer(a)
+    if a.kernel == "fused_routed":
+        bench_fused_routed(a)
+        return
     if a.kernel == "layer_step":
         bench_layer_step(a)
     if a.kernel in ("gemm_fp8", "all"):
