@@ -26,7 +26,7 @@ import threading
 import time
 
 # The reference publishes no number for this configuration and its package cannot be installed offline (no ray / tensordict /
-# hydra wheels), so the anchor recorded in BASELINE.md is the same GRPO step built from the stock libraries the reference
+# hydra wheels), so the anchor is the same GRPO step built from the stock libraries the reference
 # calls (vLLM 0.22 rollout, transformers + FlashAttention-2 + torch AdamW training; `--impl stocklibs`), measured on one B200:
 # 6528 tokens/s per GPU. vs_baseline = value / (n_gpus x that number), i.e. the baseline is granted perfect weak scaling.
 BASELINE_PUBLISHED = 6528.2
