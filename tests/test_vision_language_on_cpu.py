@@ -248,7 +248,7 @@ def test_dataset_builds_multimodal_rows(tmp_path):
         pad_token_id, chat_template = 0, None
 
         def __call__(self, text, add_special_tokens=False):
-            return {"input_ids": [500 if w == "<image>" else 1 + (hash(w) % 300) for w in text.split()]}
+            return {"input_ids": [500 if w == "<image>" else 501 if w == "<video>" else 1 + (hash(w) % 300) for w in text.split()]}
 
     buf = io.BytesIO()
     Image.fromarray(np.random.default_rng(1).integers(0, 255, (60, 60, 3), dtype=np.uint8)).save(buf, format="PNG")
@@ -268,6 +268,20 @@ def test_dataset_builds_multimodal_rows(tmp_path):
     assert torch.equal(b["position_ids"][0], b["position_ids"][1])                            # text only: all streams equal
     batch = collate_fn([a, b])
     assert batch["position_ids"].shape == (2, 4, 96) and len(batch["multi_modal_inputs"]) == 2
+    # a row with a video (six frames as arrays) before an image: grids and patches follow the order of the marks in the prompt
+    frames = [np.random.default_rng(2).integers(0, 255, (32, 32, 3), dtype=np.uint8) for _ in range(6)]
+    ds.df = pd.DataFrame({"prompt": [[{"role": "user", "content": "watch <video> then look <image> and compare"}]],
+                          "images": [[{"bytes": buf.getvalue()}]], "videos": [[{"frames": frames, "fps": 2.0}]], "data_source": ["v"]})
+    ds.vision = dict(vision, video_token_id=501, tokens_per_second=2)
+    c = ds[0]
+    gv = c["multi_modal_inputs"]["image_grid_thw"]
+    assert gv.shape == (2, 3) and int(gv[0, 0]) == 3 and int(gv[1, 0]) == 1                          # 6 frames = 3 temporal patches, then the image
+    assert int((c["input_ids"] == 501).sum()) == int(gv[0].prod()) // 4 and int((c["input_ids"] == 500).sum()) == int(gv[1].prod()) // 4
+    assert c["multi_modal_inputs"]["pixel_values"].shape[0] == int(gv[0].prod() + gv[1].prod())
+    assert c["multi_modal_inputs"]["grid_t_scale"].tolist() == [2.0, 1.0]                           # 2 frames per patch at 2 fps = 1 s, x 2 tokens per second
+    live = c["attention_mask"].bool()
+    vid = (c["input_ids"] == 501) & live
+    assert sorted(set((c["position_ids"][1][vid] - c["position_ids"][1][vid].min()).tolist())) == [0, 2, 4]   # temporal stream advances by 2 per patch
 
 
 @pytest.mark.parametrize("family", ["qwen2_vl", "qwen3_vl"])
@@ -499,3 +513,59 @@ def test_qwen3_vl_tower_deepstack_and_logits_match_hf():
     assert "model.visual.pos_embed.weight" in names and "model.visual.deepstack_merger_list.1.norm.bias" in names
     back = ModelConfig.from_hf_dict(cfg.to_hf_dict())
     assert back.vision == cfg.vision and back.qk_norm and back.head_dim == 16
+
+
+def test_video_inputs_frames_to_patches_positions_and_tower():
+    """Videos given as frames: patch layout (a video of identical frames repeats the image's patches per temporal patch), frame
+    sampling and padding to the temporal patch size, the 3-stream positions of a prompt that mixes an image and a video against
+    Hugging Face Qwen2.5-VL (temporal stream scaled by seconds-per-patch x tokens-per-second), and the tower on a t > 1 grid."""
+    import numpy as np
+
+    from verl_b200.utils.dataset.vision_utils import expand_visual_tokens, image_to_patches, process_video, video_to_patches
+
+    rng = np.random.default_rng(0)
+    frame = rng.integers(0, 255, (16, 24, 3), dtype=np.uint8)
+    frames, sec = process_video([frame] * 3, factor=8, min_pixels=64, max_pixels=16 * 24)        # 3 frames -> padded to 4
+    assert len(frames) == 4 and frames[0].size == (24, 16) and sec == 1.0
+    pv, gv = video_to_patches(frames, 4, 2, 2)
+    pi, gi = image_to_patches(frames[0], 4, 2, 2)
+    assert gv.tolist() == [[2, 4, 6]] and gi.tolist() == [[1, 4, 6]] and torch.equal(pv[:24], pi) and torch.equal(pv[24:], pi)
+    frames, sec = process_video({"frames": np.stack([frame] * 10), "fps": 5.0}, factor=8, min_pixels=64, max_pixels=16 * 24, fps=2.0)
+    assert len(frames) == 4 and sec == 1.0                                                        # 2 s at 2 fps = 4 frames; 2 frames per patch
+    frames, sec = process_video({"frames": [frame] * 10, "fps": 10.0, "nframes": 4}, factor=8, min_pixels=64, max_pixels=16 * 24)
+    assert len(frames) == 4 and abs(sec - 2 / 4.0) < 1e-9                                         # 4 of 10 frames at 10 fps -> 4 fps
+    assert expand_visual_tokens([1, 500, 2, 501, 3], torch.tensor([[1, 4, 4], [2, 4, 4]]), (500, 501)) == [1] + [500] * 4 + [2] + [501] * 8 + [3]
+    try:
+        from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration
+    except ImportError:
+        pytest.skip("this transformers build has no Qwen2.5-VL")
+    torch.manual_seed(0)
+    hf_cfg = Qwen2_5_VLConfig(
+        text_config=dict(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+                         max_position_embeddings=512, rope_theta=10000.0, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}),
+        vision_config=dict(depth=2, hidden_size=32, intermediate_size=48, num_heads=2, in_channels=3, patch_size=4, temporal_patch_size=2,
+                           spatial_merge_size=2, window_size=16, out_hidden_size=64, fullatt_block_indexes=[1], tokens_per_second=2),
+        image_token_id=500, video_token_id=501, vision_start_token_id=502, vision_end_token_id=503)
+    hf = Qwen2_5_VLForConditionalGeneration(hf_cfg).float().eval()
+    cfg = ModelConfig.from_hf_dict(hf_cfg.to_dict()).replace(torch_dtype="float32")
+    assert cfg.vision["tokens_per_second"] == 2.0
+    ours = VisionLanguageModel(cfg, dtype=torch.float32, device=torch.device("cpu"))
+    ours.load_hf_state_dict(hf.state_dict())
+    img_grid, vid_grid = torch.tensor([[1, 4, 4]]), torch.tensor([[3, 4, 8]])
+    ids = torch.tensor([7, 8, 502] + [500] * 4 + [503, 9, 502] + [501] * 24 + [503, 10, 11])
+    second_per_grid = 1.5                                                                          # e.g. 2 frames per patch sampled at 4/3 fps
+    got, delta = get_rope_index(ids, torch.cat([img_grid, vid_grid]), ours.vcfg,
+                                grid_t_scale=torch.tensor([1.0, second_per_grid * cfg.vision["tokens_per_second"]]))
+    # the published rule (text continues from the largest position + 1; a video's temporal index is
+    # floor(patch index x seconds per patch x tokens per second)), written out by hand for this prompt
+    want = [(0, 0, 0), (1, 1, 1), (2, 2, 2), (3, 3, 3), (3, 3, 4), (3, 4, 3), (3, 4, 4), (5, 5, 5), (6, 6, 6), (7, 7, 7)]
+    want += [(8 + 3 * t, 8 + h, 8 + w) for t in range(3) for h in range(2) for w in range(4)]
+    want += [(15, 15, 15), (16, 16, 16), (17, 17, 17)]
+    assert got.t().tolist() == [list(x) for x in want]
+    assert delta == 18 - len(ids)
+    pix = torch.randn(3 * 4 * 8, 96)
+    with torch.no_grad():
+        w = hf.model.visual(pix, grid_thw=vid_grid)
+        w = w.pooler_output if hasattr(w, "pooler_output") else w
+        g = ours.visual(pix, vid_grid)
+    assert torch.allclose(g, w, atol=1e-5, rtol=1e-4)

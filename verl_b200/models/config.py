@@ -172,13 +172,15 @@ class ModelConfig:
                 d.update(model_type="qwen3_vl", architectures=["Qwen3VLForConditionalGeneration"], image_token_id=v.pop("image_token_id"),
                          video_token_id=v.pop("video_token_id"), vision_start_token_id=v.pop("vision_start_token_id"), text_config=text)
                 v["out_hidden_size"], v["hidden_size"] = v.pop("hidden_size"), v.pop("embed_dim")
-                for k in ("mlp_ratio", "window_size", "fullatt_block_indexes"):
+                for k in ("mlp_ratio", "window_size", "fullatt_block_indexes", "tokens_per_second"):
                     v.pop(k, None)
                 v["deepstack_visual_indexes"] = list(v["deepstack_visual_indexes"])
                 d["vision_config"] = v
                 return d
             for k in ("num_position_embeddings", "deepstack_visual_indexes", "mrope_interleaved"):
                 v.pop(k, None)
+            if v.get("variant", "qwen2_vl") != "qwen2_5_vl":
+                v.pop("tokens_per_second", None)
             new = v.pop("variant", "qwen2_vl") == "qwen2_5_vl"
             d.update(model_type="qwen2_5_vl" if new else "qwen2_vl",
                      architectures=["Qwen2_5_VLForConditionalGeneration" if new else "Qwen2VLForConditionalGeneration"],

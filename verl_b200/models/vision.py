@@ -55,6 +55,7 @@ class VisionConfig:
     num_position_embeddings: int = 0
     deepstack_visual_indexes: tuple = ()
     mrope_interleaved: bool = False
+    tokens_per_second: float = 0.0           # Qwen2.5-VL: temporal positions of a video advance by seconds-per-patch x this (0: by 1 per patch)
 
     @property
     def patch_dim(self) -> int:
@@ -79,7 +80,7 @@ class VisionConfig:
                        image_token_id=d.get("image_token_id", 151655), video_token_id=d.get("video_token_id", 151656),
                        vision_start_token_id=d.get("vision_start_token_id", 151652), mrope_section=tuple(rope.get("mrope_section", (16, 24, 24))),
                        variant="qwen2_5_vl", intermediate_size=v.get("intermediate_size", 3420), window_size=v.get("window_size", 112),
-                       fullatt_block_indexes=tuple(v.get("fullatt_block_indexes", (7, 15, 23, 31))))
+                       fullatt_block_indexes=tuple(v.get("fullatt_block_indexes", (7, 15, 23, 31))), tokens_per_second=float(v.get("tokens_per_second", 2)))
         return cls(depth=v.get("depth", 32), embed_dim=v.get("embed_dim", 1280), num_heads=v.get("num_heads", 16), mlp_ratio=v.get("mlp_ratio", 4.0),
                    in_channels=v.get("in_channels", v.get("in_chans", 3)), patch_size=v.get("patch_size", 14),
                    temporal_patch_size=v.get("temporal_patch_size", 2), spatial_merge_size=v.get("spatial_merge_size", 2),
@@ -269,32 +270,36 @@ class VisionTower(nn.Module):
 
 
 def get_rope_index(input_ids: torch.Tensor, image_grid_thw: Optional[torch.Tensor], cfg: VisionConfig,
-                   attention_mask: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, int]:
+                   attention_mask: Optional[torch.Tensor] = None, grid_t_scale: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, int]:
     """3-stream positions ``[3, L]`` of ONE sequence and the offset ``delta`` such that generated token ``j`` (0-based index
     in the unpadded sequence) sits at position ``j + delta`` in all three streams.
 
     Text tokens advance all streams together. An image block of ``t × h × w`` patches (``h, w`` in merged units) keeps the
     temporal stream at the block start and walks the height / width streams over the grid; the text after it continues
-    from the largest position used so far + 1. Masked (padding) positions get 0."""
+    from the largest position used so far + 1. Masked (padding) positions get 0. ``image_grid_thw`` lists the grids of images AND
+    videos in token order; ``grid_t_scale`` (one factor per grid, default 1) is the number of positions the temporal stream of a
+    video advances per temporal patch (Qwen2.5-VL: seconds per patch x tokens per second; truncated to integers like there)."""
     ids = input_ids if attention_mask is None else input_ids[attention_mask.bool()]
     L = ids.numel()
     m = cfg.spatial_merge_size
     pos = torch.zeros(3, L, dtype=torch.long)
     ids_l = ids.tolist()
     grids = image_grid_thw.tolist() if image_grid_thw is not None else []
+    scales = grid_t_scale.tolist() if grid_t_scale is not None else [1.0] * len(grids)
     i, nxt, g = 0, 0, 0
     while i < L:
         if ids_l[i] in (cfg.image_token_id, cfg.video_token_id) and g < len(grids):
             t, h, w = grids[g]
+            sc = float(scales[g])
             g += 1
             gh, gw = h // m, w // m
             n = t * gh * gw
             assert ids_l[i:i + n] == [ids_l[i]] * n, "image placeholder run does not match image_grid_thw"
-            tt = torch.arange(t).view(t, 1, 1).expand(t, gh, gw).flatten()
+            tt = (torch.arange(t).view(t, 1, 1).expand(t, gh, gw) * sc).long().flatten()
             hh = torch.arange(gh).view(1, gh, 1).expand(t, gh, gw).flatten()
             ww = torch.arange(gw).view(1, 1, gw).expand(t, gh, gw).flatten()
             pos[:, i:i + n] = torch.stack([tt, hh, ww]) + nxt
-            nxt += max(t, gh, gw)
+            nxt += max(int(tt.max()) + 1, gh, gw)
             i += n
         else:
             pos[:, i] = nxt

@@ -540,7 +540,8 @@ class FSDPEngine(BaseEngine):
             for i in range(ids_cpu.shape[0]):
                 r = rows[i] if i < len(rows) and rows[i] else {}
                 g = torch.as_tensor(r["image_grid_thw"]).reshape(-1, 3) if r.get("image_grid_thw") is not None and len(r["image_grid_thw"]) else None
-                p, _ = get_rope_index(ids_cpu[i], g, vcfg, attention_mask=att_cpu[i])
+                sc = torch.as_tensor(r["grid_t_scale"]) if r.get("grid_t_scale") is not None else None
+                p, _ = get_rope_index(ids_cpu[i], g, vcfg, attention_mask=att_cpu[i], grid_t_scale=sc)
                 per_row.append(p[:, att_cpu[i]])
             pos3 = torch.cat(per_row, 1).to(dev)
         return {"pixel_values": torch.cat(pix, 0).to(dev) if pix else None, "image_grid_thw": torch.cat(grids, 0) if grids else None,

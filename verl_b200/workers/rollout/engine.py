@@ -462,7 +462,7 @@ class InferenceEngine:
         for req in reqs:
             mm = req.get("mm") or {}
             g = mm.get("image_grid_thw")
-            p, _ = get_rope_index(torch.as_tensor(req["prompt"] + req["out"]), g, v)
+            p, _ = get_rope_index(torch.as_tensor(req["prompt"] + req["out"]), g, v, grid_t_scale=mm.get("grid_t_scale"))
             pos3.append(p)
             if g is not None and len(g):
                 pix.append(torch.as_tensor(mm["pixel_values"]))
@@ -701,7 +701,7 @@ class InferenceEngine:
                     from verl_b200.models.vision import get_rope_index
 
                     reqs[i]["mm"] = mm
-                    reqs[i]["rope_delta"] = get_rope_index(torch.as_tensor(p), mm.get("image_grid_thw"), self.vision_config)[1]
+                    reqs[i]["rope_delta"] = get_rope_index(torch.as_tensor(p), mm.get("image_grid_thw"), self.vision_config, grid_t_scale=mm.get("grid_t_scale"))[1]
                 self.sched.add(i, len(p), max_new, key, tokens=p, no_chunk=bool(mm), no_cache=bool(mm))
 
         add_requests([(p, None, multi_modal[j] if multi_modal is not None else None) for j, p in enumerate(prompts)])
