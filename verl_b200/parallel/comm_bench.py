@@ -139,13 +139,41 @@ def bench_moe(a, rank, world, host, timer):
               f"combine GEMM {t_combine * 1e3:.0f} (plain {t_plain2 * 1e3:.0f}) | barrier + slot sum {t_collect * 1e3:.0f}", flush=True)
 
 
+def bench_decode(a, rank, world, host, timer):
+    """The two row-parallel projections of a decode step (256 sequences) as GEMM -> all-reduce, every split-K choice next to the
+    plan's own, against cuBLAS + NCCL: attention output projection (K = heads x 128 / W) and MLP down projection (K = ffn / W)."""
+    from verl_b200.ops import _ext
+    from verl_b200.parallel.tp import TPContext
+
+    o = _ext.ops()
+    H, F, W = a.hidden, a.ffn, world
+    dev = torch.device("cuda")
+    ctx = TPContext(dist.group.WORLD, host, max_tokens=512, hidden=H, max_out=H)
+    for name, K in (("down projection", F // W), ("output projection", H // W)):
+        x = torch.randn(256, K, device=dev).bfloat16()
+        w = (0.02 * torch.randn(H, K, device=dev)).bfloat16()
+        os.environ["VERL_B200_COMM"] = "nccl"
+        ms_b = timer(lambda: ctx.gemm_allreduce(x, w))
+        os.environ["VERL_B200_COMM"] = "native"
+        ms_f = timer(lambda: ctx.gemm_allreduce(x, w))
+        report(rank, f"decode GEMM -> all-reduce, {name} [256x{K}] x [{H}x{K}]^T, TP={W}, planned split", ms_f, ms_b, 2.0 * 256 * H * K, (W - 1) * 256 * H * 2)
+        out = torch.empty(256, H, dtype=torch.bfloat16, device=dev)
+        for bn, sk in ((256, 5), (256, 3), (256, 2), (128, 4), (128, 2), (128, 1), (64, 2), (64, 1)):
+            if (K // 64) // sk < 8:
+                continue
+            ms = timer(lambda: o.gemm_allreduce_sig(x, w, ctx.slots2.table(), ctx.sig.table(), ctx.rank, ctx.half_elems, ctx.slots2.tensor(torch.bfloat16),
+                                                    ctx.sig.tensor(torch.int32, 64), None, out, bn, sk))
+            if rank == 0:
+                print(f"    tile N = {bn}, K slices = {sk}: {ms * 1e3:.1f} us", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--hidden", type=int, default=3584)
     ap.add_argument("--ffn", type=int, default=18944)
     ap.add_argument("--params-m", type=int, default=512, help="millions of parameters for the optimizer-step paths")
-    ap.add_argument("--only", default="", help="'moe': only the expert-parallel MoE layer (Qwen3-30B-A3B shapes)")
+    ap.add_argument("--only", default="", help="'moe': only the expert-parallel MoE layer (Qwen3-30B-A3B shapes); 'decode': only the decode-size GEMM -> all-reduce pairs with a split-K sweep")
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--top-k", dest="top_k", type=int, default=8)
     ap.add_argument("--moe-hidden", dest="moe_hidden", type=int, default=2048)
@@ -168,6 +196,11 @@ def main():
     W = world
     if a.only == "moe":
         bench_moe(a, rank, world, host, timer)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
+    if a.only == "decode":
+        bench_decode(a, rank, world, host, timer)
         dist.barrier()
         dist.destroy_process_group()
         return
