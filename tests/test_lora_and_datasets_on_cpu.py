@@ -114,3 +114,32 @@ def test_curriculum_sampler_prefers_medium_difficulty():
     s.update(batch)
     order = list(iter(s))
     assert order[0] == 2 and order[1] == 5 and sorted(order) == list(range(6))
+
+
+def test_rollout_serves_the_trained_adapters(tmp_path):
+    """A LoRA policy is generated from as it is trained: the rollout engine applies the live adapters on top of the shared base
+    weights (no merged copy, no weight hand-off), so after updates the sampler's log-probs still equal the trainer's recomputation;
+    fp8 / tensor-parallel replicas cannot apply adapters unmerged and are refused at the engine (the worker gives them a merged copy)."""
+    import pytest
+
+    from tests.test_trainer_e2e_on_cpu import OV
+    from verl_b200.trainer.ppo.ppo_trainer import PPOTrainer
+    from verl_b200.trainer.ppo.reward import load_reward_manager
+    from verl_b200.utils.config import load_config
+    from verl_b200.workers.rollout.engine import InferenceEngine
+
+    cfg = load_config("ppo_trainer", OV + [f"trainer.default_local_dir={tmp_path}/ckpt", "actor_rollout_ref.model.lora_rank=4", "actor_rollout_ref.model.lora_alpha=8",
+                                           "actor_rollout_ref.actor.optim.lr=5e-2", "trainer.total_training_steps=3"])
+    tr = PPOTrainer(cfg, reward_fn=load_reward_manager(cfg, None), val_reward_fn=None)
+    tr.init_workers()
+    w = tr.actor_rollout_wg.worker
+    assert not w._rollout_owns_model and w.rollout.model is w.actor.engine.model and w.actor.engine.model.lora_config["rank"] == 4
+    it = iter(tr.train_dataloader)
+    for step in (1, 2, 3):
+        tr.global_steps = step
+        m = tr.step(next(it))
+        assert m["training/rollout_probs_diff_max"] < 1e-5, (step, m["training/rollout_probs_diff_max"])
+    assert w.actor.engine.model.layers[0].self_attn.lora_B_qkv_proj.abs().sum() > 0            # the adapters did move
+    assert w.checkpoint_manager.last_stats["path"] == "resident_shared"
+    with pytest.raises(NotImplementedError, match="unmerged"):
+        InferenceEngine(w.actor.engine.model, max_num_seqs=4, max_model_len=64, num_blocks=16, quantization="fp8")

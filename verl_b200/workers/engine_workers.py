@@ -338,9 +338,11 @@ class ActorRolloutRefWorker(Worker, _ProfiledWorker):
         src = self.actor if self.actor is not None else self.ref
         model = src.engine.model
         self._rollout_owns_model = False
-        if getattr(src.engine, "tp_size", 1) * getattr(src.engine, "pp_size", 1) > 1 or getattr(src.engine, "_zero3_rows", None):
-            # the trainer holds only a tensor/pipeline shard (or ZeRO-3 row shards): the rollout replica keeps its own full copy, refreshed by
-            # update_weights() from the engine's per-tensor export
+        lora_needs_merge = bool(getattr(model, "lora_config", None)) and (int(cfg_get(ro, "tensor_model_parallel_size", 1) or 1) > 1 or cfg_get(ro, "quantization", None))
+        if getattr(src.engine, "tp_size", 1) * getattr(src.engine, "pp_size", 1) > 1 or getattr(src.engine, "_zero3_rows", None) or lora_needs_merge:
+            # the trainer holds only a tensor/pipeline shard (or ZeRO-3 row shards), or low-rank adapters that a tensor-parallel / fp8
+            # replica cannot apply unmerged: the rollout replica keeps its own full copy, refreshed by update_weights() from the engine's
+            # per-tensor export (which folds adapters in). A bf16 replica without tensor parallelism serves adapters unmerged instead.
             from verl_b200.models.transformer import DecoderLM
 
             if src.engine.cfg.vision:

@@ -107,6 +107,8 @@ class InferenceEngine:
         if hasattr(model, "visual") and hasattr(model, "language_model"):
             self.visual, self.vision_config, model = model.visual, model.vcfg, model.language_model
         self.model = model
+        if getattr(model, "lora_config", None) and (quantization or tp_group is not None):
+            raise NotImplementedError("adapters are served unmerged only by bf16 replicas without tensor parallelism; give the engine a merged copy instead")
         if getattr(getattr(model, "cfg", None), "mlp_act", "swiglu") != "swiglu" and (quantization or tp_group is not None):
             raise NotImplementedError("models with an un-gated MLP (Apertus) run in the rollout engine without tensor parallelism or fp8 weights")
         self.tp_group, self.tp = tp_group, tp_ctx
@@ -210,6 +212,16 @@ class InferenceEngine:
 
         return (fp8_linear if self.quantization == "fp8" else fp8_block_linear)(x, q[0], q[1], bias)
 
+    def _lora_delta(self, mod, name: str, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        """Low-rank adapters are served as they are trained: ``y + scale * (x A^T) B^T`` from the trainer's live adapter tensors, so
+        a LoRA policy needs no merged copy of the weights and no weight hand-off (reference: LoRA adapters loaded into the serving
+        engine instead of merged weights, verl/workers/rollout/vllm_rollout ``load_format`` / ``lora`` paths)."""
+        ad = getattr(mod, "_lora", None)
+        if not ad or name not in ad:
+            return y
+        a_name, b_name, scale = ad[name]
+        return y + scale * ops.linear(ops.linear(x, getattr(mod, a_name)), getattr(mod, b_name))
+
     def _wake_up_impl(self):
         c = self.cfg
         self._quantise_weights()
@@ -282,7 +294,7 @@ class InferenceEngine:
             else:
                 x, res = ops.add_rmsnorm(h, res, layer.input_layernorm, c.rms_norm_eps)
             at = layer.self_attn
-            qkv = self._linear(x, at.qkv_proj, at.qkv_bias)
+            qkv = self._lora_delta(at, "qkv_proj", x, self._linear(x, at.qkv_proj, at.qkv_bias))
             if c.qk_norm:
                 T = qkv.shape[0]
                 q, k, v = qkv.split([c.q_size, c.kv_size, c.kv_size], dim=-1)
@@ -292,7 +304,7 @@ class InferenceEngine:
             qkv = ops.apply_rope_(qkv, positions, cos, sin, n_rot, c.head_dim)
             self._cache_write(li, qkv, slots)
             o = attn_fn(li, qkv)
-            a = self._row_parallel(o, at.o_proj)
+            a = self._lora_delta(at, "o_proj", o, self._row_parallel(o, at.o_proj))
             x, res = ops.add_rmsnorm(a, res, layer.post_attention_layernorm, c.rms_norm_eps)
             if self.tp_group is not None and not c.is_moe:
                 h = self._row_parallel(ops.swiglu(ops.linear(x, layer.mlp.gate_up_proj)), layer.mlp.down_proj)
