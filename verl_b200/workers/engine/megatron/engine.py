@@ -156,6 +156,9 @@ class MegatronEngine(FSDPEngine):
         self.cfg = cfg
         if cfg.vision:
             raise NotImplementedError("vision-language models run in the sharded data-parallel engine (strategy=fsdp), not under tensor/pipeline parallelism")
+        if not hasattr(self.model_config, "num_hidden_layers") and int(cfg_get(self.model_config, "lora_rank", 0) or 0) > 0:
+            raise NotImplementedError("low-rank adapters are trained by the sharded data-parallel engine (strategy=fsdp); the tensor/pipeline-parallel "
+                                      "engine would silently train every weight, so model.lora_rank > 0 is refused here")
         dt_name = cfg_get(self.engine_config, "model_dtype", None) or (cfg.torch_dtype if self.device.type == "cpu" else "bfloat16")
         self.dtype = _DTYPES.get(str(dt_name), torch.bfloat16)
         seed = int(cfg_get(self.engine_config, "seed", 0))
