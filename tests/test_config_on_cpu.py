@@ -118,3 +118,27 @@ def test_config_tree_composition_and_reference_style_overrides():
     sft = load_config("sft_trainer_engine", ["engine=megatron", "optim=megatron", "engine.tensor_model_parallel_size=2"])
     assert sft.engine.tensor_model_parallel_size == 2 and sft.optim.lr == 1e-5 and sft.model.enable_gradient_checkpointing is True
     assert gen_main(["--check"]) == 0                      # the committed composed files are current
+
+
+def test_every_example_script_parses_against_the_config_tree(monkeypatch):
+    """The override lists of ``examples/*.sh`` (the part after ``main_ppo``) must compose with ``ppo_trainer.yaml`` as they are."""
+    import glob
+    import os
+    import shlex
+
+    from verl_b200.utils.config import load_config
+
+    for k in ("TRAIN", "VAL", "MODEL", "STUDENT", "TEACHER", "MATH_TEACHER", "CODE_TEACHER"):
+        monkeypatch.setenv(k, f"/data/{k.lower()}")
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
+    seen = 0
+    for f in sorted(glob.glob(os.path.join(root, "*.sh"))):
+        body = " ".join(line.rstrip("\\").strip() for line in open(f).read().splitlines() if not line.startswith("#") and not line.startswith("set "))
+        i = body.find("main_ppo")
+        if i < 0:
+            continue
+        args = shlex.split(os.path.expandvars(body[i + len("main_ppo"):].replace('"$@"', "")))
+        cfg = load_config("ppo_trainer", args)
+        assert cfg.data.train_files == "/data/train", f
+        seen += 1
+    assert seen >= 10

@@ -83,6 +83,7 @@ class McoreEngineConfig(BaseConfig):
     pipeline_model_parallel_size: int = 1
     virtual_pipeline_model_parallel_size: Any = None
     context_parallel_size: int = 1
+    context_parallel_zigzag: bool = False
     expert_model_parallel_size: int = 1
     expert_tensor_parallel_size: Any = None
     sequence_parallel: bool = True
