@@ -433,13 +433,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // the stores of the previous batch must have read their slots before new rows land there
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             const int nb = min(DISPATCH_SLOTS, n_items - base);
+            // token dispatch: the batch's row-table entries are fetched together before any copy is issued (each copy's
+            // asm statement orders memory, so entries read one by one inside the loop would cost one global-load latency per row)
+            int ent[DISPATCH_SLOTS];
+            if (mode == 4) {
+#pragma unroll
+              for (int j = 0; j < DISPATCH_SLOTS; ++j) ent[j] = j < nb ? __ldg(dist.row_src + row0 + (base + j) / nseg) : -1;
+            }
             for (int j = 0; j < nb; ++j) {
               const int it = base + j, r = it / nseg, sg = it - r * nseg;
               const int off = sg * DISPATCH_SLOT_BYTES;
               const uint32_t bytes = (uint32_t)min(DISPATCH_SLOT_BYTES, row_bytes - off);
               const bf16* src = nullptr;
               if (mode == 4) {
-                const int e = dist.row_src[row0 + r];
+                const int e = ent[j];
                 if (e >= 0) src = srcs[e >> 24] + (long)(e & 0xFFFFFF) * dist.ld_seg;
               } else if (by_k) {
                 src = srcs[owner] + (long)(dist.row_off + row0 + r) * dist.ld_seg;
@@ -457,7 +464,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               const int it = base + j, r = it / nseg, sg = it - r * nseg;
               const int off = sg * DISPATCH_SLOT_BYTES;
               const uint32_t bytes = (uint32_t)min(DISPATCH_SLOT_BYTES, row_bytes - off);
-              const bool pad = mode == 4 && dist.row_src[row0 + r] < 0;
+              const bool pad = mode == 4 && ent[j] < 0;
               if (!mbar_wait(&bbar[j], phase, abort_flag, err_word, VB_ERR_WAIT_FULL)) { ok = false; break; }
               uint8_t* dst = reinterpret_cast<uint8_t*>(stage + (long)(row0 + r) * dist.ld_stage + dst_col) + off;
               bulk_store_1d(dst, pad ? zero_row : bounce + j * DISPATCH_SLOT_BYTES, bytes);
