@@ -55,9 +55,9 @@ struct DistArgs {
   uint16_t head_map[192];            // per output head: (destination rank << 12) | destination head slot
   void* peer_out[MAX_TP];
   // Staging of the remote part of a gathered operand: tiles that live on another rank are copied ONCE over NVLink into
-  // `stage` (laid out like the gathered operand) at kernel start, 128-row chunk by chunk; a chunk's flag is set to
-  // `stage_epoch` (times STAGE_PARTS) when it has landed and the TMA producer waits until the flag of the tile it is about to
-  // load has reached that value. Epochs must grow from call to call on one flag buffer. Without staging every output tile would fetch its operand tile from the peer again.
+  // `stage` (laid out like the gathered operand) at kernel start, in 16-row pieces dealt out over all CTAs; every piece adds one
+  // to the flag of its 128-row chunk (zeroed by the launcher before the call) and the TMA producer waits until the flag of the
+  // tile it is about to load has counted STAGE_PARTS pieces. Without staging every output tile would fetch its operand tile from the peer again.
   // Grouped (mixture-of-experts) GEMM. Token rows are sorted by expert and every expert's segment is padded to a multiple
   // of 128 rows, so a 128-row block belongs to exactly one expert.
   //   group_mode 1: C[rows, N] = A[rows, K] * B[e]^T with e = blk_expert[row block] (< 0: block unused, tile skipped);
@@ -105,7 +105,7 @@ constexpr int COMBINE_LINE_PITCH = 144;
 constexpr int COMBINE_SMEM_BYTES = 128 * COMBINE_LINE_PITCH;
 
 __device__ __forceinline__ bool stage_wait(const int* flag, int epoch, volatile int* abort_flag, int* err_word) {
-  epoch *= STAGE_PARTS;
+  epoch = STAGE_PARTS;            // the launcher zeroes the flags before every call; every piece of a chunk adds one
   uint64_t t0 = 0;
   uint32_t n = 0;
   while (true) {
@@ -427,8 +427,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             owner = row0 / dist.seg_rows;
           }
           if (mode != 4 && owner == dist.rank) continue;           // own chunks are read where they are
+          // a chunk is dealt out in STAGE_PARTS pieces of 16 rows to consecutive CTAs: with whole chunks per CTA a gather of a few
+          // dozen chunks kept only that many SMs copying (one issuing thread each) while the tiles of all SMs waited for them
+          // (token dispatch keeps whole chunks: it has hundreds of them, and 16-row pieces cost it more in per-piece drains and
+          // lock-step chunk completion than they gain)
+          const int n_parts = mode == 4 ? 1 : STAGE_PARTS;
+          const int PART_ROWS = 128 / n_parts;
+          for (int part = 0; part < n_parts && ok; ++part) {
           if ((mine++ % gridDim.x) != blockIdx.x) continue;
-          const int n_items = rows * nseg;
+          const int r_lo = part * PART_ROWS;
+          const int n_items = max(0, min(PART_ROWS, rows - r_lo)) * nseg;
           for (int base = 0; base < n_items && ok; base += DISPATCH_SLOTS) {
             // the stores of the previous batch must have read their slots before new rows land there
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -438,10 +446,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int ent[DISPATCH_SLOTS];
             if (mode == 4) {
 #pragma unroll
-              for (int j = 0; j < DISPATCH_SLOTS; ++j) ent[j] = j < nb ? __ldg(dist.row_src + row0 + (base + j) / nseg) : -1;
+              for (int j = 0; j < DISPATCH_SLOTS; ++j) ent[j] = j < nb ? __ldg(dist.row_src + row0 + r_lo + (base + j) / nseg) : -1;
             }
             for (int j = 0; j < nb; ++j) {
-              const int it = base + j, r = it / nseg, sg = it - r * nseg;
+              const int it = base + j, r = r_lo + it / nseg, sg = it - (it / nseg) * nseg;
               const int off = sg * DISPATCH_SLOT_BYTES;
               const uint32_t bytes = (uint32_t)min(DISPATCH_SLOT_BYTES, row_bytes - off);
               const bf16* src = nullptr;
@@ -461,7 +469,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
             for (int j = 0; j < nb; ++j) {
-              const int it = base + j, r = it / nseg, sg = it - r * nseg;
+              const int it = base + j, r = r_lo + it / nseg, sg = it - (it / nseg) * nseg;
               const int off = sg * DISPATCH_SLOT_BYTES;
               const uint32_t bytes = (uint32_t)min(DISPATCH_SLOT_BYTES, row_bytes - off);
               const bool pad = mode == 4 && ent[j] < 0;
@@ -473,11 +481,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tma_store_commit();
             phase ^= 1;
           }
-          tma_store_wait_all();                                   // the chunk's rows are in the staging buffer
+          tma_store_wait_all();                                   // this piece's rows are in the staging buffer
           asm volatile("fence.proxy.async;" ::: "memory");
-          // one writer per chunk and call: the flag is SET to the call's epoch (not counted up), so calls whose chunk ranges differ
-          // (another token count, another owner of a row range) cannot leave a flag behind the epoch its next reader expects
-          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(dist.stage_flags + c), "r"(dist.stage_epoch * STAGE_PARTS) : "memory");
+          // the launcher zeroes the flags of the call's chunks; a chunk is complete when all its pieces have reported
+          asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(dist.stage_flags + c), "r"(STAGE_PARTS / n_parts) : "memory");
+          }
         }
         tma_store_wait_all();
       }
@@ -1293,6 +1301,8 @@ extern "C" int vb_gemm_allgather(int which, const long* seg_ptrs, int world, int
     d.stage = stage; d.stage_flags = stage_flags; d.stage_epoch = stage_epoch; d.ld_stage = K; d.ld_seg = ld_seg; d.rank = rank;
     for (int r = 0; r < world; ++r) d.seg_ptr[r] = reinterpret_cast<const void*>(seg_ptrs[r]);
     if (make_tmap_2d(&d.stage_map, stage, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_total, K, K, tile_rows, BK)) return -1;
+    // every 16-row piece of a chunk adds one to the chunk's flag: start the call from zero
+    if (cudaMemsetAsync(stage_flags, 0, sizeof(int) * (rows_total / 128), st) != cudaSuccess) return -13;
   }
   const void* A = which == 0 ? reinterpret_cast<const void*>(seg_ptrs[0]) : other;
   const void* B = which == 0 ? other : reinterpret_cast<const void*>(seg_ptrs[0]);
@@ -1517,6 +1527,7 @@ extern "C" int vb_gemm_kseg(const long* seg_ptrs, int world, int k_per_rank, int
     d.stage = stage; d.stage_flags = stage_flags; d.stage_epoch = stage_epoch; d.ld_stage = K; d.ld_seg = ld_seg; d.rank = rank;
     for (int r = 0; r < world; ++r) d.seg_ptr[r] = reinterpret_cast<const void*>(seg_ptrs[r]);
     if (make_tmap_2d(&d.stage_map, stage, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (M + 127) / 128 * 128, K, K, BM, BK)) return -1;
+    if (cudaMemsetAsync(stage_flags, 0, sizeof(int) * ((M + 127) / 128) * world, st) != cudaSuccess) return -13;
   }
   if (b_mn)
     return launch_dist<EPI_STORE, true>(pick_bn_dist(M, N), reinterpret_cast<const void*>(seg_ptrs[0]), B, C, bias, M, N, K, ld_seg, ldb, ldc, err_word, st, d);

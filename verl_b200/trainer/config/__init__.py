@@ -186,6 +186,10 @@ class DataConfig(BaseConfig):
     vision: Any = None
     image_min_pixels: Any = None
     image_max_pixels: Any = None
+    video_min_pixels: Any = None
+    video_max_pixels: Any = None
+    video_nframes: Any = None
+    video_fps: Any = None
     trust_remote_code: bool = False
     custom_cls: dict = field(default_factory=lambda: {'path': None, 'name': None})
     apply_chat_template_kwargs: dict = field(default_factory=lambda: {})
