@@ -85,7 +85,9 @@ def test_shard_unshard_roundtrip():
     (4, 1, 1, True, False, 2, True, 1, 3, 2),
     # virtual pipeline stages (interleaved 1F1B): 2 ranks x 2 chunks with tied embeddings; with TP and an uneven layer split; three ranks
     # with a micro-batch count that is not a multiple of the pipeline depth
-    (2, 1, 2, True, False, 1, False, 2, 4, 2), (4, 2, 2, False, False, 1, False, 2, 5, 3), (3, 1, 3, True, False, 1, False, 2, 6, 3)])
+    (2, 1, 2, True, False, 1, False, 2, 4, 2), (4, 2, 2, False, False, 1, False, 2, 5, 3), (3, 1, 3, True, False, 1, False, 2, 6, 3),
+    # virtual stages together with zig-zag context parallelism
+    (4, 1, 2, False, False, 2, True, 2, 4, 2)])
 def test_parallel_ranks_match_single_rank(tmp_path, world, tp, pp, tied, sp, cp, zigzag, vpp, layers, mbs):
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     script = tmp_path / "w.py"
