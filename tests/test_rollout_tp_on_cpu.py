@@ -121,3 +121,51 @@ def test_zero3_trainer_feeds_tp2_rollout_slices(tmp_path):
     assert len(rows) == 3
     for row in rows:
         assert abs(row["training/rollout_probs_diff_max"]) < 1e-4
+
+
+VL_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+from verl_b200.models.config import PRESETS
+from verl_b200.models.parallel_model import VisionLanguageRolloutShard
+from verl_b200.models.vision import VisionLanguageModel
+from verl_b200.workers.rollout.engine import InferenceEngine, SamplingParams
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+full = VisionLanguageModel(PRESETS["tiny-qwen2-vl"], dtype=torch.float32, device=torch.device("cpu"), seed=11).eval()
+local = VisionLanguageRolloutShard(full, rank, world)
+assert local.visual is full.visual and local.language_model.layers[0].mlp.down_proj.shape[1] == full.language_model.layers[0].mlp.down_proj.shape[1] // world
+eng = InferenceEngine(local, max_num_seqs=8, max_model_len=64, num_blocks=32, tp_group=dist.group.WORLD, enforce_eager=True)
+g = torch.Generator().manual_seed(2)
+v = full.vcfg
+prompt = [7, 8, v.vision_start_token_id] + [v.image_token_id] * 4 + [9, 10, 11]
+mm = {"pixel_values": torch.randn(16, v.patch_dim, generator=g), "image_grid_thw": torch.tensor([[1, 4, 4]])}
+out = eng.generate([prompt, [5, 6, 7, 8]], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True), multi_modal=[mm, None])
+torch.save([o.token_ids for o in out], os.environ["OUT"] + f".{rank}")
+dist.barrier()
+'''
+
+
+def test_tp2_replica_serves_a_vision_language_model(tmp_path):
+    """The decoder is cut over the replica's ranks, the vision tower runs whole on each of them: image prompts decode to the same
+    tokens as on a single-rank engine."""
+    from verl_b200.models.vision import VisionLanguageModel
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "vl.py"
+    script.write_text(VL_WORKER)
+    out = tmp_path / "vl.pt"
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29775", str(script)], env=dict(os.environ, REPO=repo, OUT=str(out), OMP_NUM_THREADS="1"),
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    a, b = torch.load(str(out) + ".0"), torch.load(str(out) + ".1")
+    assert a == b
+    full = VisionLanguageModel(PRESETS["tiny-qwen2-vl"], dtype=torch.float32, device=torch.device("cpu"), seed=11).eval()
+    g = torch.Generator().manual_seed(2)
+    v = full.vcfg
+    prompt = [7, 8, v.vision_start_token_id] + [v.image_token_id] * 4 + [9, 10, 11]
+    mm = {"pixel_values": torch.randn(16, v.patch_dim, generator=g), "image_grid_thw": torch.tensor([[1, 4, 4]])}
+    want = InferenceEngine(full, max_num_seqs=8, max_model_len=64, num_blocks=32, enforce_eager=True).generate(
+        [prompt, [5, 6, 7, 8]], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True), multi_modal=[mm, None])
+    assert [list(o.token_ids) for o in want] == [list(x) for x in a]

@@ -69,7 +69,7 @@ class CheckpointEngineManager:
                     stats = {"path": "peer_reshard", **self._peer_sync.sync()}
                     tp = 1                                  # the slice is already cut
                 else:
-                    target = getattr(w, "_rollout_full_model", None) or w.rollout.model
+                    target = getattr(w, "_rollout_sync_target", None) or getattr(w, "_rollout_full_model", None) or w.rollout.model
                     n = target.load_hf_stream(eng.get_per_tensor_param()[0])
                     stats = {"path": "per_tensor_gather", "tensors": n}
             elif not eng.store.flat.is_cuda and cuda:

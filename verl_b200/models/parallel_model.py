@@ -22,7 +22,7 @@ import torch
 from verl_b200.models.config import ModelConfig
 
 __all__ = ["local_model_config", "stage_layer_range", "shard_param", "unshard_param", "local_to_global_name", "tp_rule",
-           "build_rollout_shard", "refresh_rollout_shard"]
+           "build_rollout_shard", "refresh_rollout_shard", "VisionLanguageRolloutShard"]
 
 
 def local_model_config(cfg: ModelConfig, tp: int, shard_vocab: bool = True) -> ModelConfig:
@@ -120,6 +120,18 @@ def build_rollout_shard(full, tp_rank: int, tp: int):
         local.lm_head = full.lm_head
     refresh_rollout_shard(local, full, tp_rank, tp)
     return local
+
+
+class VisionLanguageRolloutShard(torch.nn.Module):
+    """What a tensor-parallel rollout replica holds of a vision-language model: its slice of the decoder, and the vision tower
+    whole and shared with the trainer (every rank of the replica embeds the same images and gets the same rows, so nothing has to
+    be exchanged; the tower is a few percent of the model)."""
+
+    def __init__(self, full_vl, tp_rank: int, tp: int):
+        super().__init__()
+        self.visual, self.vcfg = full_vl.visual, full_vl.vcfg
+        self.language_model = build_rollout_shard(full_vl.language_model, tp_rank, tp)
+        self.cfg = self.language_model.cfg
 
 
 def refresh_rollout_shard(local, full, tp_rank: int, tp: int) -> None:

@@ -357,8 +357,6 @@ class ActorRolloutRefWorker(Worker, _ProfiledWorker):
         self._rollout_tp = int(cfg_get(ro, "tensor_model_parallel_size", 1) or 1)
         tp_group = tp_ctx = None
         if self._rollout_tp > 1:
-            if hasattr(model, "visual"):
-                raise NotImplementedError("tensor-parallel rollout replicas do not serve vision-language models yet; use rollout.tensor_model_parallel_size=1")
             model, tp_group, tp_ctx = self._build_rollout_tp(model, ro)
         self.rollout = InferenceEngine(
             model, max_num_seqs=int(cfg_get(ro, "max_num_seqs", 256)), max_model_len=int(max_len),
@@ -386,8 +384,16 @@ class ActorRolloutRefWorker(Worker, _ProfiledWorker):
             hgrp = dist.new_group(ranks, backend="gloo") if cuda else g
             if rank in ranks:
                 mine, host = g, hgrp
+        if hasattr(full_model, "visual") and hasattr(full_model, "language_model"):
+            # vision-language model: the decoder is cut, the tower stays whole on every rank of the replica
+            from verl_b200.models.parallel_model import VisionLanguageRolloutShard
+
+            local = VisionLanguageRolloutShard(full_model, rank % tp, tp)
+            self._rollout_sync_target = full_model          # a replica-owned copy is refreshed as a whole (tower included) ...
+            full_model = full_model.language_model          # ... and update_weights() re-cuts the decoder slice from its decoder
+        else:
+            local = build_rollout_shard(full_model, rank % tp, tp)
         self._rollout_full_model = full_model
-        local = build_rollout_shard(full_model, rank % tp, tp)
         ctx = None
         if cuda and fused_comm_enabled():
             max_tok = int(cfg_get(ro, "max_num_batched_tokens", 8192))
