@@ -75,3 +75,47 @@ def test_apertus_generates_in_the_rollout_engine_and_trains_in_the_engine():
     eng.forward_backward_batch(data, loss_fn)
     assert eng.model.layers[0].mlp.act_alpha_p.main_grad.abs().sum() > 0 and eng.model.layers[1].mlp.up_proj.main_grad.abs().sum() > 0
     assert eng.optimizer_step() > 0
+
+
+@pytest.mark.parametrize("scaling", [
+    {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 64},
+    {"rope_type": "linear", "factor": 4.0},
+    {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64, "beta_fast": 32, "beta_slow": 1},
+])
+def test_rope_scaling_types_match_hf(scaling):
+    """Llama-3.1-style, linear and YaRN rotary scaling: logits of a sequence longer than the original context equal Hugging Face,
+    the rollout engine decodes with the same tables, and the mapping survives the config round trip."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.models.transformer import DecoderLM, PackedBatch
+    from verl_b200.workers.rollout.engine import InferenceEngine, SamplingParams
+
+    torch.manual_seed(0)
+    hf_cfg = LlamaConfig(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         max_position_embeddings=256, rope_parameters={"rope_theta": 10000.0, **scaling}, tie_word_embeddings=False)
+    hf = LlamaForCausalLM(hf_cfg).float().eval()
+    cfg = ModelConfig.from_hf_dict(hf_cfg.to_dict()).replace(torch_dtype="float32", rms_norm_eps=hf_cfg.rms_norm_eps)
+    assert cfg.rope_scaling["rope_type"] == scaling["rope_type"] and "rope_theta" not in cfg.rope_scaling
+    ours = DecoderLM(cfg, dtype=torch.float32)
+    ours.load_hf_state_dict(hf.state_dict())
+    ids = torch.randint(0, 320, (150,))
+    with torch.no_grad():
+        want = hf(input_ids=ids[None]).logits[0]
+        got = ours(PackedBatch(ids, torch.arange(150, dtype=torch.int32), torch.tensor([0, 150], dtype=torch.int32)), return_logits=True)["logits"]
+    assert torch.allclose(got, want, atol=3e-4, rtol=1e-3), (got - want).abs().max()
+    plain = DecoderLM(cfg.replace(rope_scaling=None), dtype=torch.float32)
+    plain.load_hf_state_dict(hf.state_dict())
+    with torch.no_grad():
+        off = plain(PackedBatch(ids, torch.arange(150, dtype=torch.int32), torch.tensor([0, 150], dtype=torch.int32)), return_logits=True)["logits"]
+    assert (off - want).abs().max() > 1e-3                                   # the scaling matters for this input
+    out = InferenceEngine(ours.eval(), max_num_seqs=2, max_model_len=192, num_blocks=8, enforce_eager=True).generate(
+        [ids[:100].tolist()], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))[0]
+    seq = ids[:100].tolist()
+    for _ in range(3):
+        t = torch.tensor(seq)
+        with torch.no_grad():
+            lg = ours(PackedBatch(t, torch.arange(len(seq), dtype=torch.int32), torch.tensor([0, len(seq)], dtype=torch.int32)), return_logits=True)["logits"]
+        seq.append(int(lg[-1].argmax()))
+    assert list(out.token_ids) == seq[-3:]
+    assert ModelConfig.from_hf_dict(cfg.to_hf_dict()).rope_scaling == cfg.rope_scaling

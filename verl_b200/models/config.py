@@ -27,6 +27,7 @@ class ModelConfig:
     head_dim: Optional[int] = None
     rms_norm_eps: float = 1e-6
     rope_theta: float = 1e6
+    rope_scaling: Optional[dict] = None   # HF rope_scaling / rope_parameters mapping (linear, llama3, yarn); None or default: plain RoPE
     max_position_embeddings: int = 32768
     tie_word_embeddings: bool = False
     attention_bias: bool = True          # qwen2: bias on q/k/v projections
@@ -85,6 +86,15 @@ class ModelConfig:
     # ------------------------------------------------------------------ HF interop
     @classmethod
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
+        def _text_rope_scaling(dd):
+            rs = dd.get("rope_scaling") or dd.get("rope_parameters") or None
+            if not rs:
+                return None
+            kind = rs.get("rope_type", rs.get("type", "default"))
+            if kind in (None, "default", "mrope"):
+                return None
+            return {k: v for k, v in rs.items() if k != "rope_theta" and v is not None}
+
         mt = d.get("model_type", "llama")
         vision = None
         if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl"):
@@ -115,6 +125,7 @@ class ModelConfig:
             head_dim=d.get("head_dim"),
             rms_norm_eps=d.get("rms_norm_eps", 1e-6),
             rope_theta=d.get("rope_theta", (d.get("rope_parameters") or {}).get("rope_theta", 10000.0)),
+            rope_scaling=_text_rope_scaling(d),
             max_position_embeddings=d.get("max_position_embeddings", 32768),
             tie_word_embeddings=d.get("tie_word_embeddings", False),
             attention_bias=d.get("attention_bias", mt == "qwen2"),
@@ -156,6 +167,8 @@ class ModelConfig:
             pad_token_id=self.pad_token_id, eos_token_id=self.eos_token_id, bos_token_id=self.bos_token_id,
             torch_dtype=self.torch_dtype,
         )
+        if self.rope_scaling:
+            d["rope_scaling"] = dict(self.rope_scaling)
         if self.is_moe:
             d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                      moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob,

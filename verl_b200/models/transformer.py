@@ -333,7 +333,7 @@ class DecoderLM(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def rope(self, device):
-        return ops.rope_tables(self.cfg.max_position_embeddings, self.cfg.head_dim, self.cfg.rope_theta, device)
+        return ops.rope_tables(self.cfg.max_position_embeddings, self.cfg.head_dim, self.cfg.rope_theta, device, self.cfg.rope_scaling)
 
     def set_tp_group(self, group, vocab_offset: int = 0, sequence_parallel: bool = False, tp_ctx=None):
         """Switch the model to tensor-parallel execution: ``cfg`` must already describe the local shard. With

@@ -178,13 +178,62 @@ def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor, eps: f
 _ROPE_CACHE: dict = {}
 
 
-def rope_tables(max_pos: int, dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
-    """fp32 cos/sin tables [max_pos, dim/2] (HF rotate-half convention: inv_freq = theta^(-2i/dim))."""
-    key = (max_pos, dim, float(theta), str(device))
+def scaled_inv_freq(dim: int, theta: float, scaling: Optional[dict], max_pos: int, device) -> tuple[torch.Tensor, float]:
+    """Rotary frequencies under a Hugging Face ``rope_scaling`` / ``rope_parameters`` mapping, and the factor cos / sin are multiplied
+    by (1 except for YaRN). Types: ``default`` / ``mrope`` (plain), ``linear`` (positions divided by ``factor``), ``llama3`` (long
+    wavelengths divided by ``factor``, a smooth blend between ``low_freq_factor`` and ``high_freq_factor``), ``yarn`` (interpolated
+    and extrapolated frequencies blended by a ramp between the ``beta_fast`` / ``beta_slow`` correction dimensions, attention factor
+    ``0.1 ln(factor) + 1`` unless given). Reference behaviour: ``transformers.modeling_rope_utils`` as used by the reference's models."""
+    inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32, device=device) / dim))
+    kind = str((scaling or {}).get("rope_type", (scaling or {}).get("type", "default")) or "default")
+    if not scaling or kind in ("default", "mrope"):
+        return inv, 1.0
+    factor = float(scaling.get("factor", 1.0))
+    if kind == "linear":
+        return inv / factor, 1.0
+    if kind == "llama3":
+        lo, hi = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+        old = float(scaling.get("original_max_position_embeddings", 8192))
+        wavelen = 2 * math.pi / inv
+        out = torch.where(wavelen > old / lo, inv / factor, inv)
+        smooth = (old / wavelen - lo) / (hi - lo)
+        blended = (1 - smooth) * out / factor + smooth * out
+        medium = ~(wavelen < old / hi) & ~(wavelen > old / lo)
+        return torch.where(medium, blended, out), 1.0
+    if kind == "yarn":
+        orig = float(scaling.get("original_max_position_embeddings") or max_pos)
+        beta_fast, beta_slow = float(scaling.get("beta_fast") or 32), float(scaling.get("beta_slow") or 1)
+        att = scaling.get("attention_factor")
+        ms, ms_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+
+        def get_mscale(scale, m=1.0):
+            return 1.0 if scale <= 1 else 0.1 * float(m) * math.log(scale) + 1.0
+
+        if att is None:
+            att = get_mscale(factor, ms) / get_mscale(factor, ms_all) if ms and ms_all else get_mscale(factor)
+
+        def corr_dim(n_rot):
+            return (dim * math.log(orig / (n_rot * 2 * math.pi))) / (2 * math.log(theta))
+
+        low, high = corr_dim(beta_fast), corr_dim(beta_slow)
+        if scaling.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(dim // 2, dtype=torch.float32, device=device) - low) / (high - low)).clamp(0, 1)
+        extrap = 1 - ramp
+        return (inv / factor) * (1 - extrap) + inv * extrap, float(att)
+    raise NotImplementedError(f"rope scaling type {kind!r} is not supported")
+
+
+def rope_tables(max_pos: int, dim: int, theta: float, device, scaling: Optional[dict] = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 cos/sin tables [max_pos, dim/2] (HF rotate-half convention: inv_freq = theta^(-2i/dim), modified by ``scaling``)."""
+    key = (max_pos, dim, float(theta), str(device), tuple(sorted((k, str(v)) for k, v in (scaling or {}).items())))
     if key not in _ROPE_CACHE:
-        inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32, device=device) / dim))
+        inv, att = scaled_inv_freq(dim, theta, scaling, max_pos, device)
         ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
-        _ROPE_CACHE[key] = (ang.cos().contiguous(), ang.sin().contiguous())
+        _ROPE_CACHE[key] = ((ang.cos() * att).contiguous(), (ang.sin() * att).contiguous())
     return _ROPE_CACHE[key]
 
 
