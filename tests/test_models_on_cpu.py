@@ -119,3 +119,23 @@ def test_rope_scaling_types_match_hf(scaling):
         seq.append(int(lg[-1].argmax()))
     assert list(out.token_ids) == seq[-3:]
     assert ModelConfig.from_hf_dict(cfg.to_hf_dict()).rope_scaling == cfg.rope_scaling
+
+
+def test_sliding_window_checkpoints_are_exact_up_to_the_window_and_refused_beyond():
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.models.transformer import DecoderLM, PackedBatch
+    from verl_b200.workers.rollout.engine import InferenceEngine
+
+    d = dict(model_type="mistral", vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+             max_position_embeddings=256, sliding_window=32, rope_theta=10000.0, torch_dtype="float32")
+    cfg = ModelConfig.from_hf_dict(d)
+    assert cfg.sliding_window == 32 and ModelConfig.from_hf_dict({**d, "model_type": "qwen2", "use_sliding_window": False}).sliding_window == 0
+    m = DecoderLM(cfg, dtype=torch.float32)
+    ok = torch.randint(0, 320, (32,))
+    m(PackedBatch(ok, torch.arange(32, dtype=torch.int32), torch.tensor([0, 32], dtype=torch.int32)), return_logits=True)
+    long = torch.randint(0, 320, (40,))
+    with pytest.raises(NotImplementedError, match="sliding-window"):
+        m(PackedBatch(long, torch.arange(40, dtype=torch.int32), torch.tensor([0, 40], dtype=torch.int32)), return_logits=True)
+    with pytest.raises(NotImplementedError, match="sliding-window"):
+        InferenceEngine(m, max_num_seqs=2, max_model_len=64, num_blocks=8)
+    InferenceEngine(m, max_num_seqs=2, max_model_len=32, num_blocks=8)

@@ -27,6 +27,7 @@ class ModelConfig:
     head_dim: Optional[int] = None
     rms_norm_eps: float = 1e-6
     rope_theta: float = 1e6
+    sliding_window: int = 0              # > 0: the checkpoint expects windowed attention; sequences up to the window are exact, longer ones are refused
     rope_scaling: Optional[dict] = None   # HF rope_scaling / rope_parameters mapping (linear, llama3, yarn); None or default: plain RoPE
     max_position_embeddings: int = 32768
     tie_word_embeddings: bool = False
@@ -126,6 +127,7 @@ class ModelConfig:
             rms_norm_eps=d.get("rms_norm_eps", 1e-6),
             rope_theta=d.get("rope_theta", (d.get("rope_parameters") or {}).get("rope_theta", 10000.0)),
             rope_scaling=_text_rope_scaling(d),
+            sliding_window=int(d.get("sliding_window") or 0) if d.get("use_sliding_window", mt in ("mistral", "mixtral")) else 0,
             max_position_embeddings=d.get("max_position_embeddings", 32768),
             tie_word_embeddings=d.get("tie_word_embeddings", False),
             attention_bias=d.get("attention_bias", mt == "qwen2"),

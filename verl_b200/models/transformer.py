@@ -346,6 +346,10 @@ class DecoderLM(nn.Module):
     def forward_hidden(self, pb: PackedBatch, h_in: Optional[torch.Tensor] = None):
         """Final-normed hidden states [T, H] on the last pipeline stage, the raw residual stream on earlier stages.
         ``h_in`` is the stream received from the previous stage (stages without the embedding)."""
+        if getattr(self.cfg, "sliding_window", 0) and pb.max_seqlen > self.cfg.sliding_window:
+            raise NotImplementedError(f"this checkpoint uses sliding-window attention over {self.cfg.sliding_window} tokens; a sequence of "
+                                      f"{pb.max_seqlen} tokens would need windowed attention kernels, which are not built (full attention is exact "
+                                      "only up to the window)")
         cos, sin = self.rope(pb.input_ids.device)
         if pb.rope_override is not None:
             # multimodal rotary embedding: the tables already hold one row per token, so the rotary kernel indexes them by row

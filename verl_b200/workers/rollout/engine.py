@@ -107,6 +107,10 @@ class InferenceEngine:
         if hasattr(model, "visual") and hasattr(model, "language_model"):
             self.visual, self.vision_config, model = model.visual, model.vcfg, model.language_model
         self.model = model
+        sw = int(getattr(getattr(model, "cfg", None), "sliding_window", 0) or 0)
+        if sw and max_model_len > sw:
+            raise NotImplementedError(f"this checkpoint uses sliding-window attention over {sw} tokens; max_model_len={max_model_len} would need "
+                                      "windowed decode attention, which is not built")
         if getattr(model, "lora_config", None) and (quantization or tp_group is not None):
             raise NotImplementedError("adapters are served unmerged only by bf16 replicas without tensor parallelism; give the engine a merged copy instead")
         if getattr(getattr(model, "cfg", None), "mlp_act", "swiglu") != "swiglu" and (quantization or tp_group is not None):
