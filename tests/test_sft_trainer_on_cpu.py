@@ -41,3 +41,39 @@ def test_sft_on_conversations_with_images(tmp_path, monkeypatch):
               f"trainer.default_local_dir={tmp_path}/ck", "trainer.device=cpu"])
     rows = [json.loads(x)["data"] for x in logf.read_text().splitlines()]
     assert len(rows) == 10 and rows[-1]["train/loss"] < rows[0]["train/loss"] - 0.5
+
+
+def test_sft_resume_continues_with_the_batches_an_uninterrupted_run_sees(tmp_path, monkeypatch):
+    """Stop after step 3 (mid-epoch), restart from the step folder: steps 4-6 see the same batches, so the same losses, as one 6-step run;
+    the tracker names the newest step and retention keeps one folder."""
+    import pytest
+
+    from verl_b200.utils.checkpoint.checkpoint_handler import CheckpointHandler, SkipFirst, extract_step
+
+    def run(tag, ck, steps, extra=()):
+        logf = tmp_path / f"{tag}.jsonl"
+        monkeypatch.setenv("VERL_FILE_LOGGER_PATH", str(logf))
+        sft_main(["data.synthetic.enable=true", "data.synthetic.num_samples=16", "data.train_batch_size=4", "data.micro_batch_size_per_gpu=4",
+                  "data.max_prompt_length=8", "data.max_response_length=8", "model.preset=tiny-qwen2", "optim.lr=1e-3", "optim.lr_warmup_steps_ratio=0.0",
+                  "optim.lr_scheduler_type=constant", "trainer.total_epochs=4", f"trainer.total_training_steps={steps}", "trainer.logger=[file]",
+                  f"trainer.default_local_dir={ck}", "trainer.device=cpu", "trainer.save_freq=3", "trainer.max_ckpt_to_keep=1", *extra])
+        return [json.loads(x) for x in logf.read_text().splitlines()]
+
+    whole = run("whole", tmp_path / "a", 6)
+    first = run("first", tmp_path / "b", 3)
+    assert (tmp_path / "b" / "latest_checkpointed_iteration.txt").read_text() == "3"
+    second = run("second", tmp_path / "b", 6)
+    assert [r["step"] for r in second] == [4, 5, 6]
+    for a, b in zip(whole[3:], second):
+        assert a["data"]["train/loss"] == pytest.approx(b["data"]["train/loss"], rel=1e-5)
+    assert [r["data"]["train/loss"] for r in whole[:3]] == pytest.approx([r["data"]["train/loss"] for r in first], rel=1e-5)
+    assert sorted(p.name for p in (tmp_path / "b").iterdir() if p.is_dir()) == ["global_step_6"]
+    assert (tmp_path / "b" / "latest_checkpointed_iteration.txt").read_text() == "6"
+    # resume_mode=disable starts from scratch in a folder that holds checkpoints; resume_path needs a step folder
+    fresh = run("fresh", tmp_path / "b", 1, ["trainer.resume_mode=disable"])
+    assert [r["step"] for r in fresh] == [1]
+    with pytest.raises(ValueError, match="global_step_N"):
+        CheckpointHandler(None, default_local_dir=str(tmp_path / "b"), resume_mode="resume_path", resume_from_path=str(tmp_path)).resume_path()
+    assert extract_step("/x/global_step_12/actor") == 12 and extract_step("/x/y") is None
+    s = SkipFirst(range(10), 4)
+    assert list(s) == [4, 5, 6, 7, 8, 9] and list(s) == list(range(10))

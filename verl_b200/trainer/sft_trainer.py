@@ -38,7 +38,7 @@ DEFAULT_CONFIG = {
     "engine": {"strategy": "fsdp", "fsdp_size": -1, "model_dtype": None, "ulysses_sequence_parallel_size": 1, "seed": 0},
     "checkpoint": {"save_contents": ["model", "optimizer", "extra"], "load_contents": ["model", "optimizer", "extra"]},
     "trainer": {"total_epochs": 1, "total_training_steps": None, "project_name": "sft", "experiment_name": "run", "logger": ["console"],
-                "default_local_dir": "checkpoints/sft", "save_freq": -1, "test_freq": -1, "resume_mode": "auto", "device": "cuda"},
+                "default_local_dir": "checkpoints/sft", "save_freq": -1, "test_freq": -1, "resume_mode": "auto", "resume_from_path": None, "max_ckpt_to_keep": None, "default_hdfs_dir": None, "device": "cuda"},
 }
 
 
@@ -215,29 +215,31 @@ class SFTTrainer:
     def fit(self):
         cfg = self.config.trainer
         logger = Tracking(cfg.project_name, cfg.experiment_name, cfg.logger) if self.rank == 0 else None
-        from verl_b200.utils.checkpoint.checkpoint_manager import find_latest_ckpt_path
+        from verl_b200.utils.checkpoint.checkpoint_handler import CheckpointHandler, SkipFirst
 
-        root = os.path.expanduser(cfg.default_local_dir)
-        if cfg.get("resume_mode", "auto") != "disable":
-            latest = find_latest_ckpt_path(root)
-            if latest:
-                self.engine.load_checkpoint(latest)
-                self.global_step = int(latest.rstrip("/").split("global_step_")[-1])
-        for epoch in range(int(cfg.total_epochs) + 1):
-            self.sampler.set_epoch(epoch)
-            for batch in self.loader:
+        handler = CheckpointHandler(self.engine, default_local_dir=cfg.default_local_dir, max_ckpt_to_keep=cfg.get("max_ckpt_to_keep"),
+                                    default_hdfs_dir=cfg.get("default_hdfs_dir"), resume_mode=cfg.get("resume_mode", "auto"),
+                                    resume_from_path=cfg.get("resume_from_path"), rank=self.rank)
+        self.global_step, pos = handler.load_checkpoint()
+        steps_per_epoch = max(1, len(self.loader))
+        # a checkpoint without a data position (an older one) continues from where its step count says it was
+        pos = pos or {"epoch": self.global_step // steps_per_epoch, "batches": self.global_step % steps_per_epoch}
+        skipper = SkipFirst(self.sampler)
+        loader = DataLoader(self.train_dataset, batch_size=self.per_rank_bs, sampler=skipper, collate_fn=self.loader.collate_fn, drop_last=True)
+        for epoch in range(int(pos["epoch"]), int(cfg.total_epochs) + 1):
+            skipper.set_epoch(epoch)
+            done = int(pos["batches"]) if epoch == int(pos["epoch"]) else 0
+            skipper.skip_next(done * self.per_rank_bs)
+            for batch in loader:
                 if self.global_step >= self.total_steps:
                     return
                 self.global_step += 1
+                done += 1
                 m = self.train_step(batch)
                 if int(cfg.get("test_freq", -1)) > 0 and self.global_step % int(cfg.test_freq) == 0:
                     m.update(self.validate())
                 if int(cfg.get("save_freq", -1)) > 0 and (self.global_step % int(cfg.save_freq) == 0 or self.global_step == self.total_steps):
-                    path = os.path.join(root, f"global_step_{self.global_step}")
-                    self.engine.save_checkpoint(path, global_step=self.global_step)
-                    if self.rank == 0:
-                        with open(os.path.join(root, "latest_checkpointed_iteration.txt"), "w") as f:
-                            f.write(str(self.global_step))
+                    handler.save_checkpoint(self.global_step, {"epoch": epoch, "batches": done})
                 if logger:
                     logger.log(m, self.global_step)
 
