@@ -77,3 +77,29 @@ def test_sft_resume_continues_with_the_batches_an_uninterrupted_run_sees(tmp_pat
     assert extract_step("/x/global_step_12/actor") == 12 and extract_step("/x/y") is None
     s = SkipFirst(range(10), 4)
     assert list(s) == [4, 5, 6, 7, 8, 9] and list(s) == list(range(10))
+
+
+def test_controller_driven_sft_over_two_workers_trains_saves_and_resumes(tmp_path, monkeypatch):
+    """The driver owns the data; two worker processes (gloo) hold the data-parallel engine. The loss goes down, a checkpoint with the data
+    position lands on disk, and a second driver resumes from it instead of starting over."""
+    from verl_b200.trainer.sft_trainer_controller import main as controller_main
+
+    def run(tag, steps):
+        logf = tmp_path / f"{tag}.jsonl"
+        monkeypatch.setenv("VERL_FILE_LOGGER_PATH", str(logf))
+        controller_main(["data.synthetic.enable=true", "data.synthetic.num_samples=8", "data.train_batch_size=8", "data.micro_batch_size_per_gpu=4",
+                         "data.max_prompt_length=8", "data.max_response_length=8", "model.preset=tiny-qwen2", "optim.lr=3e-3",
+                         "optim.lr_warmup_steps_ratio=0.0", "optim.lr_scheduler_type=constant", "trainer.total_epochs=20",
+                         f"trainer.total_training_steps={steps}", "trainer.logger=[file]", f"trainer.default_local_dir={tmp_path}/ck",
+                         "trainer.device=cpu", "trainer.save_freq=4", "trainer.n_gpus_per_node=2", "trainer.nnodes=1"])
+        return [json.loads(x) for x in logf.read_text().splitlines()]
+
+    rows = run("a", 8)
+    assert [r["step"] for r in rows] == list(range(1, 9))
+    assert rows[-1]["data"]["train/loss"] < rows[0]["data"]["train/loss"] - 0.3
+    ck = tmp_path / "ck"
+    assert (ck / "latest_checkpointed_iteration.txt").read_text() == "8"
+    assert (ck / "global_step_8" / "data.pt").exists() and (ck / "global_step_8" / "model_world_size_2_rank_1.pt").exists()
+    more = run("b", 10)
+    assert [r["step"] for r in more] == [9, 10]
+    assert more[0]["data"]["train/loss"] < rows[0]["data"]["train/loss"] - 0.3   # continued from the trained weights

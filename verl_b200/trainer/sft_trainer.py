@@ -38,7 +38,7 @@ DEFAULT_CONFIG = {
     "engine": {"strategy": "fsdp", "fsdp_size": -1, "model_dtype": None, "ulysses_sequence_parallel_size": 1, "seed": 0},
     "checkpoint": {"save_contents": ["model", "optimizer", "extra"], "load_contents": ["model", "optimizer", "extra"]},
     "trainer": {"total_epochs": 1, "total_training_steps": None, "project_name": "sft", "experiment_name": "run", "logger": ["console"],
-                "default_local_dir": "checkpoints/sft", "save_freq": -1, "test_freq": -1, "resume_mode": "auto", "resume_from_path": None, "max_ckpt_to_keep": None, "default_hdfs_dir": None, "device": "cuda"},
+                "default_local_dir": "checkpoints/sft", "save_freq": -1, "test_freq": -1, "resume_mode": "auto", "resume_from_path": None, "max_ckpt_to_keep": None, "default_hdfs_dir": None, "device": "cuda", "nnodes": 1, "n_gpus_per_node": 1},
 }
 
 
@@ -112,6 +112,39 @@ class SFTDataset(Dataset):
                 "responses": ids[self.P:].clone(), "response_mask": att[self.P:].clone()}
 
 
+def build_sft_datasets(config: Config, tokenizer=None, train_dataset=None, val_dataset=None):
+    """(train, val) datasets of an SFT run: the ones passed in, else conversations (``data.multiturn.enable``), synthetic rows or
+    prompt/response files, as the config says."""
+    mc = dict(config.model)
+    dc = config.data
+    mt = dc.get("multiturn") or {}
+    if mt.get("enable", False):
+        from verl_b200.models.config import PRESETS, ModelConfig
+        from verl_b200.utils.dataset.sft_dataset import MultiTurnSFTDataset
+
+        vis = None
+        if mc.get("preset"):
+            vis = PRESETS[mc["preset"]].vision
+        elif mc.get("path") and os.path.exists(os.path.join(os.path.expanduser(str(mc["path"])), "config.json")):
+            vis = ModelConfig.from_pretrained(os.path.expanduser(str(mc["path"]))).vision
+
+        def conversations(files):
+            return ConversationWindow(MultiTurnSFTDataset(files, tokenizer, max_length=int(mt.get("max_length") or int(dc.max_prompt_length) + int(dc.max_response_length)),
+                                                          messages_key=mt.get("messages_key", "messages"), tools_key=mt.get("tools_key", "tools"),
+                                                          truncation=dc.get("truncation", "right"), vision=vis, images_key=mt.get("images_key", "images"),
+                                                          image_min_pixels=mt.get("image_min_pixels"), image_max_pixels=mt.get("image_max_pixels")))
+
+        if train_dataset is None:
+            train_dataset = conversations(dc.train_files)
+        if val_dataset is None and dc.get("val_files"):
+            val_dataset = conversations(dc.val_files)
+    if train_dataset is None:
+        train_dataset = SFTDataset.synthetic(dc) if dc.synthetic.enable else SFTDataset.from_files(dc.train_files, tokenizer, dc)
+    if val_dataset is None and dc.get("val_files"):
+        val_dataset = SFTDataset.from_files(dc.val_files, tokenizer, dc)
+    return train_dataset, val_dataset
+
+
 class SFTTrainer:
     def __init__(self, config: Config, tokenizer=None, train_dataset=None, val_dataset=None):
         self.config = config
@@ -122,31 +155,7 @@ class SFTTrainer:
         self.engine = EngineRegistry.new("language_model", config.engine.strategy, model_config=Config(mc), engine_config=config.engine,
                                          optimizer_config=config.optim, checkpoint_config=config.checkpoint)
         dc = config.data
-        mt = dc.get("multiturn") or {}
-        if mt.get("enable", False):
-            from verl_b200.models.config import PRESETS, ModelConfig
-            from verl_b200.utils.dataset.sft_dataset import MultiTurnSFTDataset
-
-            vis = None
-            if mc.get("preset"):
-                vis = PRESETS[mc["preset"]].vision
-            elif mc.get("path") and os.path.exists(os.path.join(os.path.expanduser(str(mc["path"])), "config.json")):
-                vis = ModelConfig.from_pretrained(os.path.expanduser(str(mc["path"]))).vision
-
-            def conversations(files):
-                return ConversationWindow(MultiTurnSFTDataset(files, tokenizer, max_length=int(mt.get("max_length") or int(dc.max_prompt_length) + int(dc.max_response_length)),
-                                                              messages_key=mt.get("messages_key", "messages"), tools_key=mt.get("tools_key", "tools"),
-                                                              truncation=dc.get("truncation", "right"), vision=vis, images_key=mt.get("images_key", "images"),
-                                                              image_min_pixels=mt.get("image_min_pixels"), image_max_pixels=mt.get("image_max_pixels")))
-
-            if train_dataset is None:
-                train_dataset = conversations(dc.train_files)
-            if val_dataset is None and dc.get("val_files"):
-                val_dataset = conversations(dc.val_files)
-        if train_dataset is None:
-            train_dataset = SFTDataset.synthetic(dc) if dc.synthetic.enable else SFTDataset.from_files(dc.train_files, tokenizer, dc)
-        if val_dataset is None and dc.get("val_files"):
-            val_dataset = SFTDataset.from_files(dc.val_files, tokenizer, dc)
+        train_dataset, val_dataset = build_sft_datasets(config, tokenizer, train_dataset, val_dataset)
         self.train_dataset, self.val_dataset = train_dataset, val_dataset
         dp, dpr = 1, 0
         per_rank = int(dc.train_batch_size)
