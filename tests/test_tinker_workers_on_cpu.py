@@ -77,3 +77,28 @@ def test_optim_step_params_are_validated():
         _apply_optim_step_params(e, {"lr": "fast"})
     with pytest.raises(TypeError):
         _apply_optim_step_params(e, [1, 2])
+
+
+def test_detach_worker_parks_weights_on_the_host_and_rolls_an_update_back(tmp_path):
+    from verl_b200.experimental.separation import DetachActorWorker
+
+    ref = _trainer(tmp_path)
+    ref.global_steps = 1
+    ref.step(next(iter(ref.train_dataloader)))
+    batch = ref._last_batch
+    tr = _trainer(tmp_path, DetachActorWorker)
+    wg = tr.actor_rollout_wg
+    eng = wg.worker.actor.engine
+    before_flat, before_master = eng.store.flat.clone(), eng.master.clone()
+    assert wg.save_model_to_cpu(0)[0] == before_flat.numel() * before_flat.element_size() + before_master.numel() * 4
+    wg.update_actor(batch)
+    assert not torch.equal(eng.store.flat, before_flat)
+    wg.save_model_to_cpu("after")
+    after_flat = eng.store.flat.clone()
+    assert wg.restore_model_from_cpu(0) == [True]
+    assert torch.equal(eng.store.flat, before_flat) and torch.equal(eng.master, before_master)
+    p = next(iter(eng.model.parameters()))
+    assert p.data_ptr() >= eng.store.flat.data_ptr()            # parameters are still views of the live buffer
+    assert wg.restore_model_from_cpu("after") == [True] and torch.equal(eng.store.flat, after_flat)
+    assert wg.saved_model_keys() == [[0, "after"]] and wg.clear_cpu_model(0) == [True] and wg.clear_cpu_model(0) == [False]
+    assert wg.restore_model_from_cpu(0) == [False]
