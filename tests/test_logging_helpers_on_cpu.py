@@ -49,3 +49,14 @@ def test_trajectory_tracker_dumps_a_snapshot_in_the_background(tmp_path, monkeyp
     files = get_trajectory_tracker().wait()
     assert files == [str(tmp_path / "dumps" / "step1_obs.pt")]
     assert torch.equal(torch.load(files[0])["obs"], torch.arange(4.0))
+
+
+def test_worker_runtime_env_fills_only_what_the_shell_left_open():
+    from verl_b200.trainer.constants_ppo import NVTX_INJECTION_ENV, get_worker_runtime_env
+
+    env = get_worker_runtime_env(None, environ={"NCCL_DEBUG": "INFO"})["env_vars"]
+    assert "NCCL_DEBUG" not in env and env["TOKENIZERS_PARALLELISM"] == "true"
+    cfg = {"global_profiler": {"tool": "torch"}, "trainer": {"disable_nvls": True, "runtime_env": {"env_vars": {"MY_FLAG": 3, "NCCL_DEBUG": "TRACE"}}}}
+    env = get_worker_runtime_env(cfg, environ={})["env_vars"]
+    assert env["NCCL_NVLS_ENABLE"] == "0" and env["MY_FLAG"] == "3" and env["NCCL_DEBUG"] == "TRACE" and NVTX_INJECTION_ENV in env
+    assert "NCCL_NVLS_ENABLE" not in get_worker_runtime_env({"trainer": {}}, environ={})["env_vars"]

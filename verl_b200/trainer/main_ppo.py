@@ -33,6 +33,9 @@ def run_ppo(config):
     from verl_b200.trainer.ppo.ppo_trainer import PPOTrainer
     from verl_b200.trainer.ppo.reward import load_reward_manager
 
+    from verl_b200.trainer.constants_ppo import apply_worker_runtime_env
+
+    apply_worker_runtime_env(config)       # before any worker process or process group exists
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if config.trainer.get("worker_backend", "spmd") == "spmd":
         config.trainer["n_gpus_per_node"] = max(1, world // int(config.trainer.get("nnodes", 1)))
